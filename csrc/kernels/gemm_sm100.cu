@@ -1,0 +1,323 @@
+// Dense bf16 GEMM for sm_100a: D[M,N] = A[M,K] * B[N,K]^T with fp32 accumulation in tensor memory.
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0      TMA producer   : cp.async.bulk.tensor tiles of A and B into a 4-stage shared-memory ring
+//   warp 1      MMA issuer     : one elected lane issues tcgen05.mma (128x256x16) into one of two TMEM accumulators
+//   warps 2..5  epilogue       : tcgen05.ld the finished accumulator, convert, store; overlaps the next tile's MMAs
+//
+// Operand layouts. "K-major" means the reduction index is contiguous in global memory; "MN-major" means the
+// M (for A) or N (for B) index is contiguous. The three combinations cover a linear layer's forward
+// (x[M,K], W[N,K]), its input gradient (dY[M,N'] K-major, W[N',K'] MN-major) and its weight gradient (both
+// MN-major), so no operand is ever transposed in memory.
+//
+// Replaces the reference's GEMM template for tcgen05 (src/dew/nn/kernels/gemm.py:84, templates/gemm/mosaic_gpu.py).
+#include "../common/ptx.cuh"
+#include "../common/tmap.h"
+
+namespace dewb {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;        // 64 bf16 = 128 bytes = one swizzle row
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;   // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int ACC_COLS = BN;           // fp32 columns per accumulator
+constexpr int TMEM_COLS = 2 * ACC_COLS;  // 512: both accumulators
+constexpr int THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+enum Epilogue : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_F32_ACC = 2, EPI_BF16_ACC = 3 };
+
+struct Shared {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& m_blk, int& n_blk) {
+  constexpr int GROUP_M = 8;
+  const int per_group = GROUP_M * tiles_n;
+  const int group = t / per_group;
+  const int first_m = group * GROUP_M;
+  const int gsize = min(tiles_m - first_m, GROUP_M);
+  const int r = t - group * per_group;
+  m_blk = first_m + r % gsize;
+  n_blk = r / gsize;
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 void* __restrict__ Dptr, int M, int N, int K, long long ldd, float alpha, int* __restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: required by the 128-byte swizzle atoms the descriptors assume (base_offset = 0)
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Shared* sh = reinterpret_cast<Shared*>(smem + STAGES * STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_iters = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&sh->tmem_full[a], 1); mbar_init(&sh->tmem_empty[a], 4); }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tma_a); tma_prefetch_desc(&tma_b); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+  volatile int* abort_flag = &sh->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int m_blk, n_blk; tile_coords(t, tiles_m, tiles_n, m_blk, n_blk);
+        const int m0 = m_blk * BM, n0 = n_blk * BN;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); ok = false; break; }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&sh->full[stage], STAGE_BYTES);
+          const int k0 = k * BK;
+          if (!A_MN) {
+            tma_load_2d(sa, &tma_a, &sh->full[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tma_a, &sh->full[stage], m0 + j * 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tma_b, &sh->full[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tma_b, &sh->full[stage], n0 + j * 64, k0);
+          }
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Give the copies already in flight a bounded chance to land before shared memory is released.
+        const long long pending = issued < STAGES ? issued : STAGES;
+        for (long long i = 0; i < pending; ++i) {
+          int s = static_cast<int>((issued - 1 - i) % STAGES);
+          uint32_t ph = static_cast<uint32_t>(((issued - 1 - i) / STAGES) & 1);
+          mbar_wait(&sh->full[s], ph, nullptr, 20000000ull);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0; uint32_t phase = 0;
+      int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&sh->tmem_empty[acc], acc_phase ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&sh->full[stage], phase, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t da = A_MN ? make_sdesc_sw128(sa + kk * 2048, 8192, 1024) : make_sdesc_sw128(sa + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_sdesc_sw128(sb + kk * 2048, 8192, 1024) : make_sdesc_sw128(sb + kk * 32, 16, 1024);
+            umma_bf16_ss(d_tmem, da, db, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&sh->empty[stage]);   // frees the stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&sh->tmem_full[acc]);   // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int m_blk, n_blk; tile_coords(t, tiles_m, tiles_n, m_blk, n_blk);
+      const int row = m_blk * BM + q * 32 + lane;
+      const int n0 = n_blk * BN;
+      if (!mbar_wait(&sh->tmem_full[acc], acc_phase, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * ACC_COLS + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (row < M && col < N) {
+          const bool full = (col + 32 <= N);
+          if (EPI == EPI_BF16 || EPI == EPI_BF16_ACC) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Dptr) + static_cast<long long>(row) * ldd + col;
+            if (full && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+              uint4* o4 = reinterpret_cast<uint4*>(out);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = alpha * __uint_as_float(r[j * 8 + i]);
+                if (EPI == EPI_BF16_ACC) {
+                  const uint4 old = o4[j];
+                  v[0] += bf16_lo(old.x); v[1] += bf16_hi(old.x); v[2] += bf16_lo(old.y); v[3] += bf16_hi(old.y);
+                  v[4] += bf16_lo(old.z); v[5] += bf16_hi(old.z); v[6] += bf16_lo(old.w); v[7] += bf16_hi(old.w);
+                }
+                uint4 pk;
+                pk.x = pack_bf16(v[0], v[1]); pk.y = pack_bf16(v[2], v[3]);
+                pk.z = pack_bf16(v[4], v[5]); pk.w = pack_bf16(v[6], v[7]);
+                o4[j] = pk;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (col + i < N) {
+                  float v = alpha * __uint_as_float(r[i]);
+                  if (EPI == EPI_BF16_ACC) v += __bfloat162float(out[i]);
+                  out[i] = __float2bfloat16(v);
+                }
+              }
+            }
+          } else {
+            float* out = reinterpret_cast<float*>(Dptr) + static_cast<long long>(row) * ldd + col;
+            if (full && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+              float4* o4 = reinterpret_cast<float4*>(out);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(alpha * __uint_as_float(r[j * 4 + 0]), alpha * __uint_as_float(r[j * 4 + 1]),
+                                       alpha * __uint_as_float(r[j * 4 + 2]), alpha * __uint_as_float(r[j * 4 + 3]));
+                if (EPI == EPI_F32_ACC) { const float4 o = o4[j]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+                o4[j] = v;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                if (col + i < N) {
+                  float v = alpha * __uint_as_float(r[i]);
+                  if (EPI == EPI_F32_ACC) v += out[i];
+                  out[i] = v;
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->tmem_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, void* D, int M, int N, int K, long long ldd,
+                      float alpha, int* err, int sms, cudaStream_t stream) {
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, D, M, N, K, ldd, alpha, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, void* D, int M, int N, int K,
+                      long long ldd, float alpha, int* err, int sms, cudaStream_t stream) {
+  switch (epi) {
+    case EPI_BF16: return launch_one<A_MN, B_MN, EPI_BF16>(ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
+    case EPI_F32: return launch_one<A_MN, B_MN, EPI_F32>(ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
+    case EPI_F32_ACC: return launch_one<A_MN, B_MN, EPI_F32_ACC>(ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
+    case EPI_BF16_ACC: return launch_one<A_MN, B_MN, EPI_BF16_ACC>(ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
+  }
+  return -2;
+}
+
+}  // namespace gemm
+}  // namespace dewb
+
+static int g_sm_count[64];
+
+static int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (g_sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_sm_count[dev] = n;
+  }
+  return g_sm_count[dev];
+}
+
+// D[M,N] (ldd) = alpha * op(A) * op(B)^T.
+//   a_mn = 0: A is [M, K] row-major with row stride lda;  a_mn = 1: A is stored as [K, M] row-major (lda = row stride)
+//   b_mn = 0: B is [N, K] row-major with row stride ldb;  b_mn = 1: B is stored as [K, N] row-major
+//   epi: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate (D += ...), 3 bf16 accumulate
+// All row strides must be multiples of 8 elements and base pointers 16-byte aligned (TMA rules).
+// `err` is a device int the kernel sets to a non-zero code if one of its bounded waits gave up.
+// `max_ctas` > 0 caps the persistent grid (used to leave SMs to a concurrent communication kernel).
+extern "C" int dewb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long lda, long long ldb,
+                              long long ldd, int a_mn, int b_mn, int epi, float alpha, int* err, int max_ctas,
+                              void* stream_ptr) {
+  using namespace dewb;
+  using namespace dewb::gemm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  CUtensorMap ta, tb;
+  int r;
+  if (!a_mn) r = make_tmap_2d(&ta, A, M, K, lda, BM, BK, 2, true);
+  else       r = make_tmap_2d(&ta, A, K, M, lda, BK, 64, 2, true);
+  if (r) return 1000 + r;
+  if (!b_mn) r = make_tmap_2d(&tb, B, N, K, ldb, BN, BK, 2, true);
+  else       r = make_tmap_2d(&tb, B, K, N, ldb, BK, 64, 2, true);
+  if (r) return 2000 + r;
+  int sms = sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  if (!a_mn && !b_mn) return launch_epi<false, false>(epi, ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
+  if (!a_mn && b_mn) return launch_epi<false, true>(epi, ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
+  if (a_mn && !b_mn) return launch_epi<true, false>(epi, ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
+  return launch_epi<true, true>(epi, ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
+}

@@ -1,0 +1,10 @@
+from .dit import SimpleDiT
+
+__all__ = ["SimpleDiT", "CausalTransformer", "Mixture"]
+
+
+def __getattr__(name):
+    if name in ("CausalTransformer", "Mixture", "TransformerConfig"):
+        from . import causal_transformer as m
+        return getattr(m, name)
+    raise AttributeError(name)

@@ -1,0 +1,55 @@
+"""Self-attention mixer: fused QKV projection, optional QK-norm, RoPE, GQA, sinks / softcap / window, KV cache.
+
+Capability parity: src/dew/nn/mixers/attention.py:984-1764 (``CausalSelfAttention``), src/dew/nn/rope.py.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from .layers import Linear, RMSNorm, declare
+
+
+class SelfAttention(nn.Module):
+    def __init__(self, features: int, num_heads: int, num_kv_heads: Optional[int] = None, head_dim: Optional[int] = None,
+                 qk_norm: bool = False, bias: bool = False, causal: bool = True, window: Optional[int] = None,
+                 softcap: float = 0.0, sinks: bool = False, norm_eps: float = 1e-6, out_zero_init: bool = False,
+                 init_std: Optional[float] = None, dtype=None, device=None):
+        super().__init__()
+        self.features, self.num_heads = features, num_heads
+        self.num_kv_heads = num_kv_heads or num_heads
+        self.head_dim = head_dim or features // num_heads
+        self.causal, self.window, self.softcap = causal, window, softcap
+        qkv_out = (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
+        self.qkv_proj = Linear(features, qkv_out, bias=bias, axes=("embed", "heads"), init_std=init_std, dtype=dtype, device=device)
+        self.o_proj = Linear(self.num_heads * self.head_dim, features, bias=bias, axes=("heads", "embed"),
+                             init_std=init_std, zero_init=out_zero_init, dtype=dtype, device=device)
+        self.q_norm = RMSNorm(self.head_dim, norm_eps, dtype=dtype, device=device) if qk_norm else None
+        self.k_norm = RMSNorm(self.head_dim, norm_eps, dtype=dtype, device=device) if qk_norm else None
+        self.sinks = declare(nn.Parameter(torch.zeros(num_heads, dtype=dtype, device=device)), ("heads",), "sinks") if sinks else None
+
+    def project(self, x, cos=None, sin=None, positions=None):
+        B, S, _ = x.shape
+        H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+        qkv = self.qkv_proj(x).view(B, S, H + 2 * Hkv, D)
+        if self.q_norm is not None:
+            q = self.q_norm(qkv[:, :, :H])
+            k = self.k_norm(qkv[:, :, H:H + Hkv])
+            qkv = torch.cat([q, k, qkv[:, :, H + Hkv:]], 2)
+        if cos is not None:
+            qkv = ops.rope(qkv, cos, sin, positions, rot_heads=H + Hkv)
+        return qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+
+    def forward(self, x, cos=None, sin=None, positions=None, segment_ids=None, cache=None, layer: int = 0):
+        B, S, _ = x.shape
+        q, k, v = self.project(x, cos, sin, positions)
+        if cache is not None:
+            o = cache.attend(layer, q, k, v, positions, causal=self.causal, window=self.window, softcap=self.softcap,
+                             sinks=self.sinks)
+        else:
+            o = ops.attention(q, k, v, causal=self.causal, window=self.window, softcap=self.softcap, sinks=self.sinks,
+                              segment_ids=segment_ids)
+        return self.o_proj(o.reshape(B, S, self.num_heads * self.head_dim))

@@ -1,0 +1,20 @@
+from .base import (Aux, EMASpec, Exponentiated, Mean, Metric, Moments, Objective, Ratio, Step, Summed, Weighted, pool)
+
+__all__ = ["Aux", "EMASpec", "Exponentiated", "Mean", "Metric", "Moments", "Objective", "Ratio", "Step", "Summed",
+           "Weighted", "pool", "DiffusionObjective", "LMObjective", "JepaObjective", "Supervised"]
+
+
+def __getattr__(name):
+    if name == "DiffusionObjective":
+        from .diffusion import DiffusionObjective
+        return DiffusionObjective
+    if name in ("LMObjective", "Perplexity"):
+        from . import lm
+        return getattr(lm, name)
+    if name == "JepaObjective":
+        from .jepa import JepaObjective
+        return JepaObjective
+    if name == "Supervised":
+        from .supervised import Supervised
+        return Supervised
+    raise AttributeError(name)

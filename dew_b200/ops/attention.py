@@ -1,0 +1,59 @@
+"""Attention dispatch on the GPU: the sm_100a flash kernels or the library arm (cuDNN / flash SDPA via torch).
+
+The selector records, per call, which kernel ran and why the other refused (``explain``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import library as L
+from .selection import Kernel, Requirement, op
+
+_ATTN = op("attention")
+
+
+def _flash_available() -> bool:
+    try:
+        return hasattr(L.load(), "dewb_flash_fwd")
+    except Exception:
+        return False
+
+
+_ATTN.kernels = [
+    Kernel("sm100_flash", [
+        Requirement("built", lambda c: _flash_available(), "flash kernels are not in this build of libdewb.so"),
+        Requirement("dtype", lambda c: c["dtype"] == torch.bfloat16, "bf16 only"),
+        Requirement("head_dim", lambda c: c["D"] in (64, 128), "head_dim must be 64 or 128"),
+        Requirement("features", lambda c: not c["sinks"] and not c["softcap"] and c["window"] is None
+                    and not c["segments"], "sinks / softcap / window / packed segments take the library arm"),
+        Requirement("seq", lambda c: c["S"] == c["T"] and c["S"] % 128 == 0, "needs S == T and S a multiple of 128"),
+        Requirement("gqa", lambda c: c["Hq"] % c["Hkv"] == 0, "query heads must be a multiple of kv heads"),
+    ], receipt="tcgen05 flash forward/backward, csrc/kernels/flash_sm100.cu"),
+    Kernel("sdpa", [], receipt="library arm: torch scaled_dot_product_attention (cuDNN / flash)"),
+]
+
+
+def _sdpa(q, k, v, causal, scale, window, softcap, sinks, segment_ids):
+    if window is not None or softcap or sinks is not None or segment_ids is not None:
+        from .functional import attention_reference
+        return attention_reference(q, k, v, causal, scale, window, softcap, sinks, segment_ids)
+    qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    o = F.scaled_dot_product_attention(qh, kh, vh, is_causal=causal and q.shape[1] > 1, scale=scale,
+                                       enable_gqa=q.shape[2] != k.shape[2])
+    return o.transpose(1, 2)
+
+
+def flash_attention(q, k, v, causal=True, scale=None, window=None, softcap=0.0, sinks=None, segment_ids=None,
+                    kernel: Optional[str] = None):
+    B, S, Hq, D = q.shape
+    case = dict(dtype=q.dtype, D=D, S=S, T=k.shape[1], Hq=Hq, Hkv=k.shape[2], sinks=sinks is not None,
+                softcap=bool(softcap), window=window, segments=segment_ids is not None, causal=causal)
+    which = _ATTN.select(case, forced=kernel)
+    if which == "sm100_flash":
+        from .flash import flash_sm100
+        return flash_sm100(q, k, v, causal, scale if scale is not None else 1.0 / math.sqrt(D))
+    return _sdpa(q, k, v, causal, scale, window, softcap, sinks, segment_ids)

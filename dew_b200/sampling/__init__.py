@@ -1,0 +1,8 @@
+from .guidance import APG, CFG, Autoguidance, CFGPlusPlus, Guidance
+from .solvers import (DDIM, DDPM, DEIS, KDPM2, LMS, PNDM, RK4, TCD, Consistency, DPMSolverMultistep, DPMSolverSDE,
+                      DPMSolverSinglestep, Euler, EulerAncestral, Heun, MultiStepDPM, Solver, UniPC, SOLVERS)
+from .walks import sample, walk_and_decode
+
+__all__ = ["sample", "walk_and_decode", "Solver", "SOLVERS", "Euler", "EulerAncestral", "Heun", "RK4", "KDPM2",
+           "MultiStepDPM", "LMS", "DDPM", "DDIM", "PNDM", "Consistency", "TCD", "DPMSolverMultistep",
+           "DPMSolverSinglestep", "DEIS", "UniPC", "DPMSolverSDE", "CFG", "CFGPlusPlus", "APG", "Autoguidance", "Guidance"]
