@@ -470,6 +470,15 @@ using namespace dewb::ew;
 #define STREAM(p) reinterpret_cast<cudaStream_t>(p)
 #define LAST_ERR() static_cast<int>(cudaGetLastError())
 
+// Select the device for this library's CUDA runtime on the calling thread.
+extern "C" int dewb_set_device(int device) {
+  int cur = -1;
+  if (cudaGetDevice(&cur) == cudaSuccess && cur == device) { cudaFree(0); return 0; }
+  cudaError_t e = cudaSetDevice(device);
+  if (e == cudaSuccess) cudaFree(0);
+  return static_cast<int>(e);
+}
+
 extern "C" int dewb_rmsnorm_fwd(const void* x, const void* other, const void* w, void* y, void* h_out, float* rstd,
                                 long long rows, int d, float eps, int mode, void* stream) {
   if (d % 8 != 0 || rows <= 0) return rows == 0 ? 0 : -3;

@@ -1,0 +1,308 @@
+// Fused gradient reduce-scatter + sharded AdamW + parameter all-gather over NVLink peer memory, in ONE kernel.
+//
+// Every rank holds, per FSDP unit, a full fp32 gradient buffer and a full bf16 parameter buffer in symmetric
+// (peer-mapped) memory, and owns one contiguous shard of the fp32 master weights and Adam moments. After a unit's
+// backward, each rank launches this kernel, which
+//   1. tells its peers "my gradients for this unit are complete" (release store of a sequence number into each
+//      peer's flag array) and waits, with a time limit, for the same word from every peer;
+//   2. for its own shard: pulls the W partial gradients straight from the peers' buffers with plain P2P loads,
+//      sums them in fp32, applies the scale / clip coefficient and the AdamW update to master, m and v;
+//   3. rounds the new weights to bf16 and pushes them into every rank's full parameter buffer (P2P stores), so no
+//      separate all-gather follows;
+//   4. when the last block finishes, tells the peers "my shard is pushed and I no longer read your gradients".
+// Nothing here uses TMA or cluster multicast; peer access is ld/st.global through NVSwitch.
+//
+// Replaces, for the FSDP axis, the collectives XLA inserts around the optimizer in the reference
+// (src/dew/mesh.py:101-146 leading-dim shards; src/dew/training/transaction.py:1292-1392 commit).
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace dewb {
+namespace comm {
+
+constexpr int MAX_RANKS = 8;
+
+struct Peers {
+  void* p[MAX_RANKS];
+};
+
+enum : int { ERR_WAIT_PEER = 5 };
+
+__device__ __forceinline__ uint64_t now_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float4 ld_sys_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_sys_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+
+// Wait until flags[slot * world + r] >= seq for every rank r. Bounded: gives up after `limit_ns` and reports.
+// Called by all threads of a block; returns false (for every thread) on time-out.
+__device__ bool wait_all_peers(const uint32_t* my_flags, int slot, int world, uint32_t seq, unsigned long long limit_ns,
+                               int* err) {
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const uint32_t* f = my_flags + slot * world + threadIdx.x;
+    const uint64_t t0 = now_ns();
+    uint32_t spins = 0;
+    // sequence numbers only grow; signed distance tolerates wrap-around
+    while (static_cast<int32_t>(ld_acquire_sys(f) - seq) < 0) {
+      if ((++spins & 63) == 0) {
+        if (now_ns() - t0 > limit_ns) { ok_flag = 0; atomicCAS(err, 0, ERR_WAIT_PEER); break; }
+        __nanosleep(200);
+      }
+    }
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+struct AdamArgs {
+  float lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, ema_decay;
+};
+
+// mode 0: reduce + AdamW + push (fully fused)
+// mode 1: reduce only -> reduced[shard_len] (fp32) and per-block sum of squares -> sumsq[gridDim.x]
+// mode 2: AdamW from `reduced` (already summed and scaled by grad_scale... no: scaled here) + push; `clip` gives
+//         {sum sq, norm, coefficient} computed between the two phases
+__global__ void __launch_bounds__(512)
+rs_adamw_ag_kernel(Peers grads, Peers params, Peers flags, float* __restrict__ master, float* __restrict__ m,
+                   float* __restrict__ v, float* __restrict__ ema, float* __restrict__ reduced,
+                   float* __restrict__ sumsq, const float* __restrict__ clip, long long shard_begin,
+                   long long shard_len, long long decay_end, int rank, int world, AdamArgs a, uint32_t seq,
+                   int slot_ready, int slot_done, unsigned int* __restrict__ block_counter,
+                   unsigned long long limit_ns, int mode, int skip_nonfinite, int* __restrict__ err) {
+  uint32_t* my_flags = reinterpret_cast<uint32_t*>(flags.p[rank]);
+  if (mode != 2) {
+    // 1. announce + wait: every peer's gradient buffer for this unit is final
+    if (blockIdx.x == 0 && threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(flags.p[threadIdx.x]) + slot_ready * world + rank, seq);
+    }
+    if (!wait_all_peers(my_flags, slot_ready, world, seq, limit_ns, err)) return;
+  }
+  float coef = a.grad_scale;
+  bool skip = false;
+  if (mode == 2 && clip != nullptr) {
+    if (skip_nonfinite && !isfinite(clip[0])) skip = true;
+    coef *= clip[2];
+  }
+  float local_sq = 0.f;
+  const long long nvec = shard_len >> 3;   // 8 elements per thread-iteration; shard_len is a multiple of 8
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long off = i << 3;
+    float g[8];
+    if (mode == 2) {
+      const float4 r0 = *reinterpret_cast<const float4*>(reduced + off);
+      const float4 r1 = *reinterpret_cast<const float4*>(reduced + off + 4);
+      g[0] = r0.x; g[1] = r0.y; g[2] = r0.z; g[3] = r0.w; g[4] = r1.x; g[5] = r1.y; g[6] = r1.z; g[7] = r1.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] = 0.f;
+      for (int r = 0; r < world; ++r) {
+        const float* src = reinterpret_cast<const float*>(grads.p[r]) + shard_begin + off;
+        const float4 x0 = ld_sys_f4(src), x1 = ld_sys_f4(src + 4);
+        g[0] += x0.x; g[1] += x0.y; g[2] += x0.z; g[3] += x0.w; g[4] += x1.x; g[5] += x1.y; g[6] += x1.z; g[7] += x1.w;
+      }
+    }
+    if (mode == 1) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) local_sq += g[j] * g[j];
+      *reinterpret_cast<float4*>(reduced + off) = make_float4(g[0], g[1], g[2], g[3]);
+      *reinterpret_cast<float4*>(reduced + off + 4) = make_float4(g[4], g[5], g[6], g[7]);
+      continue;
+    }
+    float p[8], mm[8], vv[8];
+    {
+      const float4 p0 = *reinterpret_cast<const float4*>(master + off), p1 = *reinterpret_cast<const float4*>(master + off + 4);
+      const float4 m0 = *reinterpret_cast<const float4*>(m + off), m1 = *reinterpret_cast<const float4*>(m + off + 4);
+      const float4 v0 = *reinterpret_cast<const float4*>(v + off), v1 = *reinterpret_cast<const float4*>(v + off + 4);
+      p[0] = p0.x; p[1] = p0.y; p[2] = p0.z; p[3] = p0.w; p[4] = p1.x; p[5] = p1.y; p[6] = p1.z; p[7] = p1.w;
+      mm[0] = m0.x; mm[1] = m0.y; mm[2] = m0.z; mm[3] = m0.w; mm[4] = m1.x; mm[5] = m1.y; mm[6] = m1.z; mm[7] = m1.w;
+      vv[0] = v0.x; vv[1] = v0.y; vv[2] = v0.z; vv[3] = v0.w; vv[4] = v1.x; vv[5] = v1.y; vv[6] = v1.z; vv[7] = v1.w;
+    }
+    if (!skip) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gi = g[j] * coef;
+        mm[j] = a.beta1 * mm[j] + (1.f - a.beta1) * gi;
+        vv[j] = a.beta2 * vv[j] + (1.f - a.beta2) * gi * gi;
+        const float wd = (shard_begin + off + j) < decay_end ? a.wd : 0.f;
+        p[j] = p[j] * (1.f - a.lr * wd) - a.lr * (mm[j] / a.bc1) / (sqrtf(vv[j] / a.bc2) + a.eps);
+      }
+      *reinterpret_cast<float4*>(master + off) = make_float4(p[0], p[1], p[2], p[3]);
+      *reinterpret_cast<float4*>(master + off + 4) = make_float4(p[4], p[5], p[6], p[7]);
+      *reinterpret_cast<float4*>(m + off) = make_float4(mm[0], mm[1], mm[2], mm[3]);
+      *reinterpret_cast<float4*>(m + off + 4) = make_float4(mm[4], mm[5], mm[6], mm[7]);
+      *reinterpret_cast<float4*>(v + off) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      *reinterpret_cast<float4*>(v + off + 4) = make_float4(vv[4], vv[5], vv[6], vv[7]);
+      if (ema != nullptr) {
+        float4 e0 = *reinterpret_cast<const float4*>(ema + off), e1 = *reinterpret_cast<const float4*>(ema + off + 4);
+        const float d = a.ema_decay, c = 1.f - a.ema_decay;
+        e0.x = d * e0.x + c * p[0]; e0.y = d * e0.y + c * p[1]; e0.z = d * e0.z + c * p[2]; e0.w = d * e0.w + c * p[3];
+        e1.x = d * e1.x + c * p[4]; e1.y = d * e1.y + c * p[5]; e1.z = d * e1.z + c * p[6]; e1.w = d * e1.w + c * p[7];
+        *reinterpret_cast<float4*>(ema + off) = e0;
+        *reinterpret_cast<float4*>(ema + off + 4) = e1;
+      }
+    }
+    // 3. push the bf16 weights into every rank's full parameter buffer
+    uint4 pk;
+    pk.x = pack_bf16(p[0], p[1]); pk.y = pack_bf16(p[2], p[3]); pk.z = pack_bf16(p[4], p[5]); pk.w = pack_bf16(p[6], p[7]);
+    for (int r = 0; r < world; ++r) {
+      const int dst = (rank + r) % world;   // stagger destinations so ranks do not all hit the same peer at once
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[dst]) + shard_begin + off) = pk;
+    }
+  }
+  if (mode == 1) {
+    __shared__ float red[32];
+    float s = local_sq;
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      if (threadIdx.x == 0) sumsq[blockIdx.x] = t;
+    }
+  }
+  // 4. last block out tells every peer that this rank is done with the unit
+  __threadfence_system();
+  __syncthreads();
+  __shared__ unsigned int ticket;
+  if (threadIdx.x == 0) ticket = atomicAdd(block_counter, 1u);
+  __syncthreads();
+  if (ticket == gridDim.x - 1) {
+    if (threadIdx.x == 0) *block_counter = 0;
+    if (mode != 1 && threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(flags.p[threadIdx.x]) + slot_done * world + rank, seq);
+    }
+  }
+}
+
+// Stand-alone bounded wait on one flag slot (used before a unit's forward: all peers have pushed its new weights).
+__global__ void wait_flags_kernel(const uint32_t* my_flags, int slot, int world, uint32_t seq,
+                                  unsigned long long limit_ns, int* err) {
+  wait_all_peers(my_flags, slot, world, seq, limit_ns, err);
+}
+
+// Stand-alone signal: write seq into slot[rank] of every peer's flag array.
+__global__ void signal_flags_kernel(Peers flags, int slot, int rank, int world, uint32_t seq) {
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(flags.p[threadIdx.x]) + slot * world + rank, seq);
+  }
+}
+
+// All-gather by pull: dst[r * shard_len + i] = peer r's src[i]  (bf16 or any 16-byte-multiple payload).
+__global__ void allgather_pull_kernel(Peers src, uint4* __restrict__ dst, long long shard_vec, int world) {
+  const long long total = shard_vec * world;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / shard_vec);
+    const long long j = i - r * shard_vec;
+    dst[i] = ld_sys_u4(reinterpret_cast<const uint4*>(src.p[r]) + j);
+  }
+}
+
+// All-reduce (sum) of a small fp32 vector by pull: out[i] = sum_r peer r's src[i]
+__global__ void allreduce_pull_f32_kernel(Peers src, float* __restrict__ out, int n, int world) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = 0.f;
+  for (int r = 0; r < world; ++r) {
+    float x;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(x) : "l"(reinterpret_cast<const float*>(src.p[r]) + i) : "memory");
+    s += x;
+  }
+  out[i] = s;
+}
+
+}  // namespace comm
+}  // namespace dewb
+
+using namespace dewb::comm;
+
+static Peers make_peers(const unsigned long long* ptrs, int world) {
+  Peers p;
+  for (int i = 0; i < MAX_RANKS; ++i) p.p[i] = i < world ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+  return p;
+}
+
+// hyper: {lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, ema_decay}
+extern "C" int dewb_rs_adamw_ag(const unsigned long long* grad_ptrs, const unsigned long long* param_ptrs,
+                                const unsigned long long* flag_ptrs, float* master, float* m, float* v, float* ema,
+                                float* reduced, float* sumsq, const float* clip, long long shard_begin,
+                                long long shard_len, long long decay_end, int rank, int world, const float* hyper,
+                                unsigned int seq, int slot_ready, int slot_done, unsigned int* block_counter,
+                                unsigned long long limit_ns, int mode, int skip_nonfinite, int blocks, int* err,
+                                void* stream) {
+  if (world < 1 || world > MAX_RANKS || (shard_len & 7) || (shard_begin & 7)) return -3;
+  AdamArgs a{hyper[0], hyper[1], hyper[2], hyper[3], hyper[4], hyper[5], hyper[6], hyper[7], hyper[8]};
+  if (blocks <= 0) blocks = 64;
+  rs_adamw_ag_kernel<<<blocks, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_peers(grad_ptrs, world), make_peers(param_ptrs, world), make_peers(flag_ptrs, world), master, m, v, ema,
+      reduced, sumsq, clip, shard_begin, shard_len, decay_end, rank, world, a, seq, slot_ready, slot_done,
+      block_counter, limit_ns, mode, skip_nonfinite, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dewb_wait_flags(const void* my_flags, int slot, int world, unsigned int seq, unsigned long long limit_ns,
+                               int* err, void* stream) {
+  wait_flags_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const uint32_t*>(my_flags),
+                                                                          slot, world, seq, limit_ns, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dewb_signal_flags(const unsigned long long* flag_ptrs, int slot, int rank, int world, unsigned int seq,
+                                 void* stream) {
+  signal_flags_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(make_peers(flag_ptrs, world), slot, rank,
+                                                                            world, seq);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dewb_allgather_pull(const unsigned long long* src_ptrs, void* dst, long long shard_bytes, int world,
+                                   int blocks, void* stream) {
+  if (shard_bytes & 15) return -3;
+  if (blocks <= 0) blocks = 64;
+  allgather_pull_kernel<<<blocks, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_peers(src_ptrs, world), reinterpret_cast<uint4*>(dst), shard_bytes >> 4, world);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int dewb_allreduce_pull_f32(const unsigned long long* src_ptrs, float* out, int n, int world, void* stream) {
+  allreduce_pull_f32_kernel<<<(n + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_peers(src_ptrs, world), out, n, world);
+  return static_cast<int>(cudaGetLastError());
+}

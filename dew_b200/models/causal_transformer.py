@@ -1,0 +1,198 @@
+"""``CausalTransformer``: decoder-only LM backbone - dense (Llama / Qwen / Gemma style), MoE, and hybrid stacks that
+interleave attention with gated-delta-net or Mamba-2 mixers.
+
+Fields follow the reference (src/dew/nn/backbones/causal_transformer.py:165-423): ``emb_features, num_layers,
+num_heads, num_kv_heads, head_dim, mlp_features, max_seq_len, rope_theta / rope_scaling, layer_types, norm_eps,
+qk_norm, tie_embeddings, attention_sinks, softcaps, mixture (MoE), remat``.  Forward structure (reference call
+stack, causal_transformer.py:1044-): embed -> per layer [stream RMSNorm -> mixer -> stream RMSNorm -> MLP | MoE]
+-> final norm -> head.  The residual add is fused into the next norm (one pass emits both the new stream and its
+normalised value).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+import torch.utils.checkpoint as ckpt
+
+from .. import ops
+from ..nn.attention import SelfAttention
+from ..nn.layers import Embedding, Linear, RMSNorm
+from ..nn.mlp import SwiGLU
+from ..utils.registry import register
+
+
+@dataclass
+class Mixture:
+    """MoE description (reference: docs/concepts/moe.md:37-57)."""
+    experts: int = 8
+    top_k: int = 2
+    layers: Optional[Sequence[int]] = None          # which layers are sparse (None = all)
+    score_function: str = "softmax"                  # softmax | sigmoid
+    norm_topk_prob: bool = True
+    scaling: float = 1.0
+    bias: bool = False                               # aux-loss-free balancing bias (selection only)
+    expert_features: Optional[int] = None
+    shared_features: int = 0                         # total hidden width of the shared experts
+    shared_gate: bool = False
+    implementation: str = "auto"
+    dispatch: str = "auto"                           # auto | global | exchange
+    capacity_factor: Optional[float] = None
+    fp8: bool = False                                # block-scaled fp8 expert GEMMs
+    balance_rate: float = 1e-3
+
+
+@dataclass
+class TransformerConfig:
+    vocab_size: int = 32000
+    emb_features: int = 512
+    num_layers: int = 8
+    num_heads: int = 8
+    num_kv_heads: Optional[int] = None
+    head_dim: Optional[int] = None
+    mlp_features: Optional[int] = None
+    max_seq_len: int = 2048
+    rope_theta: float = 10000.0
+    rope_scaling: Optional[dict] = None
+    norm_eps: float = 1e-6
+    qk_norm: bool = True
+    tie_embeddings: bool = True
+    attention_sinks: bool = False
+    attn_softcap: float = 0.0
+    logit_softcap: float = 0.0
+    window: Optional[int] = None
+    layer_types: Optional[Sequence[str]] = None      # per layer: attention | local | gdn | mamba2
+    mixture: Optional[Mixture] = None
+    mixer_options: Dict[str, Any] = field(default_factory=dict)
+    remat: bool = False
+    init_std: float = 0.02
+    embed_scale: bool = False                         # Gemma: multiply embeddings by sqrt(d)
+
+    def kinds(self) -> List[str]:
+        if self.layer_types is None:
+            return ["attention"] * self.num_layers
+        pattern = list(self.layer_types)
+        return [pattern[i % len(pattern)] for i in range(self.num_layers)]
+
+
+def _mixer(cfg: TransformerConfig, kind: str, dtype, device) -> nn.Module:
+    if kind in ("attention", "local"):
+        return SelfAttention(cfg.emb_features, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, qk_norm=cfg.qk_norm,
+                             causal=True, window=cfg.window if kind == "local" or cfg.layer_types is None else None,
+                             softcap=cfg.attn_softcap, sinks=cfg.attention_sinks, norm_eps=cfg.norm_eps,
+                             init_std=cfg.init_std, dtype=dtype, device=device)
+    if kind == "gdn":
+        from ..nn.linear_attention import GatedDeltaNet
+        return GatedDeltaNet(cfg.emb_features, dtype=dtype, device=device, **cfg.mixer_options)
+    if kind == "mamba2":
+        from ..nn.mamba2 import Mamba2
+        return Mamba2(cfg.emb_features, dtype=dtype, device=device, **cfg.mixer_options)
+    raise ValueError(f"unknown layer type {kind!r}; known: attention, local, gdn, mamba2")
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: TransformerConfig, index: int, kind: str, dtype=None, device=None):
+        super().__init__()
+        self.kind, self.index = kind, index
+        self.input_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
+        self.mixer = _mixer(cfg, kind, dtype, device)
+        self.post_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
+        mix = cfg.mixture
+        sparse = mix is not None and (mix.layers is None or index in mix.layers)
+        if sparse:
+            from ..nn.moe import SparseMLP
+            self.mlp = SparseMLP(cfg.emb_features, mix, cfg.mlp_features or 4 * cfg.emb_features, init_std=cfg.init_std,
+                                 dtype=dtype, device=device)
+        else:
+            self.mlp = SwiGLU(cfg.emb_features, cfg.mlp_features or 4 * cfg.emb_features, init_std=cfg.init_std,
+                              dtype=dtype, device=device)
+        self.sparse = sparse
+
+    def forward(self, h, branch, cos, sin, positions, segment_ids, cache):
+        """(stream, pending branch) -> (stream, pending branch); the branch is added by the next norm."""
+        if branch is None:
+            n = self.input_norm(h)
+        else:
+            n, h = self.input_norm(h, branch)
+        if self.kind in ("attention", "local"):
+            a = self.mixer(n, cos, sin, positions, segment_ids, cache, self.index)
+        else:
+            a = self.mixer(n, segment_ids=segment_ids, cache=cache, layer=self.index)
+        n, h = self.post_norm(h, a)
+        return h, self.mlp(n)
+
+
+@register("causal_transformer")
+class CausalTransformer(nn.Module):
+    def __init__(self, config: Optional[TransformerConfig] = None, dtype=None, device=None, **fields):
+        super().__init__()
+        cfg = config or TransformerConfig(**fields)
+        self.config = cfg
+        self.vocab_size = cfg.vocab_size
+        self.embed = Embedding(cfg.vocab_size, cfg.emb_features, cfg.init_std, dtype=dtype, device=device)
+        kinds = cfg.kinds()
+        self.layers = nn.ModuleList([DecoderLayer(cfg, i, k, dtype, device) for i, k in enumerate(kinds)])
+        self.final_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
+        self.head = None if cfg.tie_embeddings else Linear(cfg.emb_features, cfg.vocab_size, axes=("embed", "vocab"),
+                                                           init_std=cfg.init_std, dtype=dtype, device=device)
+        self._rope = None
+
+    # ------------------------------------------------------------------ helpers
+    def head_weight(self) -> torch.Tensor:
+        return self.embed.weight if self.head is None else self.head.weight
+
+    def rope_tables(self, device) -> Tuple[torch.Tensor, torch.Tensor]:
+        cfg = self.config
+        dev = torch.device(device)
+        if self._rope is None or self._rope[0].device != dev:
+            hd = cfg.head_dim or cfg.emb_features // cfg.num_heads
+            self._rope = ops.rope_tables(cfg.max_seq_len, hd, cfg.rope_theta, dev, cfg.rope_scaling)
+        return self._rope
+
+    def hidden(self, tokens, positions=None, segment_ids=None, cache=None, train: bool = False):
+        cfg = self.config
+        h = self.embed(tokens)
+        if cfg.embed_scale:
+            h = h * (cfg.emb_features ** 0.5)
+        cos, sin = self.rope_tables(h.device)
+        branch = None
+        for layer in self.layers:
+            if cfg.remat and train and torch.is_grad_enabled():
+                h, branch = ckpt.checkpoint(layer, h, branch, cos, sin, positions, segment_ids, cache, use_reentrant=False)
+            else:
+                h, branch = layer(h, branch, cos, sin, positions, segment_ids, cache)
+        n, _ = self.final_norm(h, branch)
+        return n
+
+    def logits(self, hidden):
+        out = ops.linear(hidden, self.head_weight())
+        if self.config.logit_softcap > 0:
+            out = self.config.logit_softcap * torch.tanh(out.float() / self.config.logit_softcap)
+        return out
+
+    def forward(self, tokens, train: bool = False, decode: bool = False, positions=None, segment_ids=None, cache=None,
+                return_hidden: bool = False):
+        h = self.hidden(tokens, positions, segment_ids, cache, train)
+        return h if return_hidden else self.logits(h)
+
+    # ------------------------------------------------------------------ accounting
+    def param_count(self, active: bool = False) -> int:
+        total = sum(p.numel() for p in self.parameters())
+        if active and self.config.mixture is not None:
+            mix = self.config.mixture
+            for layer in self.layers:
+                if layer.sparse:
+                    per = layer.mlp.experts.param_count_per_expert()
+                    total -= per * (mix.experts - mix.top_k)
+        return total
+
+    def model_flops(self, tokens: int, seq_len: int) -> float:
+        """Forward FLOPs for ``tokens`` tokens in rows of ``seq_len`` (2 x params-in-matmuls x tokens + attention)."""
+        cfg = self.config
+        hd = cfg.head_dim or cfg.emb_features // cfg.num_heads
+        matmul_params = self.param_count(active=True) - self.embed.weight.numel() * (0 if cfg.tie_embeddings else 1)
+        n_attn = sum(1 for k in cfg.kinds() if k in ("attention", "local"))
+        attn = n_attn * 2 * 2 * cfg.num_heads * hd * seq_len / 2          # causal: half the square
+        return tokens * (2.0 * matmul_params + attn)

@@ -1,0 +1,111 @@
+"""``LMObjective``: next-token cross-entropy with a chunked head that never holds ``[tokens, vocab]`` logits for the
+whole batch, packed-document masking, z-loss, optional multi-token-prediction weight, and ``Perplexity``.
+
+Parity: src/dew/objectives/lm/objective.py:1348-1560 (arguments ``ema_decay, pad_id, head_chunks, head_tile, z_loss,
+token_accuracy, loss_role ...``), src/dew/objectives/lm/chunked.py:774-874 (chunked cross-entropy).
+On a GPU the head is ``ops.linear_cross_entropy``: tcgen05 GEMM tiles + a fused loss/gradient row kernel.
+"""
+from __future__ import annotations
+
+from typing import Any, Mapping, Optional
+
+import torch
+
+from .. import ops
+from .base import Aux, Exponentiated, Objective, Ratio, Step
+
+
+class LMObjective(Objective):
+    def __init__(self, model, seq_len: Optional[int] = None, *, ema_decay: Optional[float] = None,
+                 pad_id: Optional[int] = None, head_chunks: int = 4, head_tile: Optional[int] = None,
+                 z_loss: float = 0.0, token_accuracy: bool = True, variables=None, balance: Optional[float] = None,
+                 mtp_weight: Optional[float] = None, prefix: Optional[int] = None, tokenizer=None):
+        self.model = model
+        self.seq_len = seq_len
+        self.ema_decay = ema_decay
+        self.pad_id = pad_id
+        self.head_chunks, self.head_tile = head_chunks, head_tile
+        self.z_loss = z_loss
+        self.token_accuracy = token_accuracy
+        self.balance = balance
+        self.mtp_weight = mtp_weight
+        self.prefix = prefix
+        self.tokenizer = tokenizer
+        self._given = variables
+
+    def init(self, key=0, variables=None):
+        return super().init(key, variables if variables is not None else self._given)
+
+    def _targets(self, batch):
+        tokens = batch["tokens"]
+        inputs, targets = tokens[:, :-1], tokens[:, 1:].clone()
+        seg = batch.get("segments")
+        seg_in = None
+        if seg is not None:
+            seg_in = seg[:, :-1]
+            targets[(seg[:, 1:] == 0) | (seg[:, 1:] != seg[:, :-1])] = -100     # padding and document boundaries
+        if self.pad_id is not None:
+            targets[targets == self.pad_id] = -100
+        mask = batch.get("loss_mask")
+        if mask is not None:
+            targets[mask[:, 1:] == 0] = -100
+        if self.prefix:
+            targets[:, : self.prefix] = -100
+        return inputs, targets, seg_in
+
+    def loss(self, variables, batch: Mapping[str, torch.Tensor], step: Step):
+        inputs, targets, seg = self._targets(batch)
+        hidden = self.apply(variables, inputs, train=step.train, segment_ids=seg, return_hidden=True)
+        B, S, d = hidden.shape
+        if variables is None:
+            w = self.model.head_weight()
+        else:
+            from ..utils.trees import variables_for_call
+            named = variables_for_call(self.model, variables)
+            w = named["embed.weight"] if self.model.head is None else named["head.weight"]
+        tile = self.head_tile or max(1, (B * S + self.head_chunks - 1) // self.head_chunks)
+        cap = getattr(self.model.config, "logit_softcap", 0.0)
+        total, mass = ops.linear_cross_entropy(hidden.reshape(B * S, d), w, targets.reshape(-1), ignore_index=-100,
+                                               z_loss=self.z_loss, softcap=cap, chunk=tile)
+        massf = mass.to(torch.float32)
+        aux = Aux(metrics={"perplexity": Exponentiated(Ratio(total.detach(), massf)),
+                           "tokens": Ratio(massf, torch.ones((), device=massf.device))})
+        moe_aux = getattr(self.model, "pop_aux", None)
+        if moe_aux is not None:
+            extra = moe_aux()
+            aux.metrics.update(extra.get("metrics", {}))
+            aux.effects.update(extra.get("effects", {}))
+            if self.balance and "balance_loss" in extra:
+                total = total + self.balance * extra["balance_loss"] * massf
+        return Ratio(total, massf), aux
+
+    def scored_tokens(self, batch):
+        t = batch["tokens"]
+        if ("segments" not in batch and "loss_mask" not in batch and self.pad_id is None and not self.prefix):
+            return int(t.shape[0] * (t.shape[1] - 1))        # every target is scored: no device read needed
+        return int((self._targets(batch)[1] != -100).sum())
+
+    def row_tokens(self, batch):
+        t = batch["tokens"]
+        return int(t.shape[0] * (t.shape[1] - 1))
+
+    def model_flops(self, batch):
+        t = batch["tokens"]
+        return self.model.model_flops(t.shape[0] * (t.shape[1] - 1), t.shape[1] - 1)
+
+    def predict(self, variables, batch):
+        return self.apply(variables, batch["tokens"])
+
+    def pipeline(self, state, ema: Optional[bool] = None):
+        from ..inference.tasks import TextGeneration
+        variables = state.averaged if (ema or (ema is None and state.ema is not None)) else state.variables
+        return TextGeneration(self.model, variables, tokenizer=self.tokenizer)
+
+
+class Perplexity:
+    """Metric: ``exp(mean token negative log-likelihood)`` pooled exactly over batches."""
+    name = "perplexity"
+
+    def __call__(self, objective: LMObjective, variables, batch, step: Step):
+        stats, _ = objective.loss(variables, batch, step)
+        return Exponentiated(stats)

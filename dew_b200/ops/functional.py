@@ -408,7 +408,7 @@ def attention(q, k, v, causal: bool = True, scale: Optional[float] = None, windo
               softcap: float = 0.0, sinks=None, segment_ids=None, kernel: Optional[str] = None):
     """Scaled-dot-product attention with GQA; layouts ``[B, S, H, D]``."""
     if L.use_cuda(q):
-        from . import attention as A
+        from . import attn as A
         return A.flash_attention(q, k, v, causal=causal, scale=scale, window=window, softcap=softcap, sinks=sinks,
                                  segment_ids=segment_ids, kernel=kernel)
     return attention_reference(q, k, v, causal, scale, window, softcap, sinks, segment_ids)

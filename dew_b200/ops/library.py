@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import threading
 from pathlib import Path
 from typing import Dict, Optional
 
@@ -61,7 +62,20 @@ def use_cuda(*tensors: torch.Tensor) -> bool:
     if os.environ.get("DEWB_FORCE_REFERENCE") == "1":
         return False
     load()  # raises LibraryMissing on a GPU box without the build
+    ensure_device(t)
     return True
+
+
+_TLS = threading.local()
+
+
+def ensure_device(t: torch.Tensor) -> None:
+    """Make ``t``'s device current for the library's own CUDA runtime on this thread (autograd runs backward on
+    worker threads where nothing has selected a device yet)."""
+    idx = t.device.index if t.device.index is not None else torch.cuda.current_device()
+    if getattr(_TLS, "device", None) != idx:
+        check(load().dewb_set_device(ctypes.c_int(idx)), "set_device")
+        _TLS.device = idx
 
 
 def stream_ptr() -> ctypes.c_void_p:

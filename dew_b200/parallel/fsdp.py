@@ -1,0 +1,494 @@
+"""FSDP engine: parameters, gradients and optimizer state sharded over the ``fsdp`` (and ``data``) axis.
+
+Design for one NVSwitch box with 180 GB per GPU (not a translation of a gather-per-layer ZeRO-3 schedule):
+
+* A **unit** is the embedding, one decoder layer, or the final norm + head.  Each unit's parameters live in one flat
+  bf16 buffer; each rank owns one contiguous *leading* shard of it (the reference's measured choice of leading-dim
+  shards, src/dew/mesh.py:84-93) as fp32 master + Adam moments.
+* Per step, per unit, ONE kernel (``dewb_rs_adamw_ag``) does the gradient reduce-scatter (P2P pulls from the peers'
+  fp32 gradient buffers), the AdamW update of the shard and the parameter all-gather (P2P pushes of the new bf16
+  weights into every rank's full buffer).  It runs on a side stream as soon as the unit's backward has finished,
+  overlapping the backward of earlier layers.  Cross-rank ordering is two sequence-numbered flags per unit in
+  symmetric memory, every wait bounded.
+* The gathered bf16 copy stays resident for the whole step (16 GB for an 8 B model), so microbatches never re-gather;
+  with gradient clipping the kernel runs in two phases around a global-norm reduction.
+* ``world == 1`` is the same code with no peers, so 1-GPU and N-GPU runs share one path.
+
+Reference behaviour covered: FSDP / ZeRO-3 placement of params, grads, optimizer state and EMA
+(src/dew/distributed/placement.py:54-109), microbatch accumulation, skip_nonfinite, clip_grads, EMA
+(src/dew/training/transaction.py:1292-1392).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..objectives.base import Aux, Step, pool
+from ..ops import library as L
+from ..training.state import TrainState
+from ..utils import keys as K
+from ..utils.trees import module_path_to_tree_path, unflatten
+from .symm import SymmetricBuffer
+
+ALIGN = 64          # elements; keeps every parameter 128-byte aligned inside the flat buffer (TMA needs 16 bytes)
+SLOT_READY, SLOT_DONE = 0, 1
+
+
+def default_units(model: nn.Module) -> List[Tuple[str, List[nn.Module]]]:
+    """Embedding | each layer | everything else (final norm, head), in forward order."""
+    layers = getattr(model, "layers", None) or getattr(model, "blocks", None)
+    if layers is None:
+        return [("model", [model])]
+    inside = set()
+    for l in layers:
+        inside.update(id(p) for p in l.parameters())
+    pre, post = [], []
+    seen_layers = False
+    for name, child in model.named_children():
+        if child is layers:
+            seen_layers = True
+            continue
+        (post if seen_layers else pre).append(child)
+    units = []
+    if pre:
+        units.append(("pre", pre))
+    units += [(f"layer{i}", [l]) for i, l in enumerate(layers)]
+    if post:
+        units.append(("post", post))
+    return units
+
+
+@dataclass
+class Unit:
+    name: str
+    params: List[Tuple[str, nn.Parameter]]
+    offset: int = 0            # element offset of the unit inside the arenas
+    size: int = 0              # padded size (multiple of world * ALIGN)
+    decay_end: int = 0         # elements [0, decay_end) take weight decay
+    offsets: Dict[str, int] = field(default_factory=dict)
+
+
+class _Boundary(torch.autograd.Function):
+    """Identity on the unit's input whose backward marks "every gradient of this unit has been produced"."""
+
+    @staticmethod
+    def forward(ctx, x, engine, index):
+        ctx.engine, ctx.index = engine, index
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.engine._unit_backward_done(ctx.index)
+        return g, None, None
+
+
+class FSDPEngine:
+    def __init__(self, trainer, units: Optional[List[Tuple[str, List[nn.Module]]]] = None, group=None,
+                 wait_limit_s: float = 20.0, comm_blocks: int = 48):
+        self.t = trainer
+        self.model: nn.Module = trainer.objective.model
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.wait_limit_ns = int(wait_limit_s * 1e9)
+        self.comm_blocks = comm_blocks
+        self.unit_modules = units or default_units(self.model)
+        self.units: List[Unit] = []
+        self.seq = 0
+        self.built = False
+        self._pending: List[int] = []
+        self._last_micro = False
+        self._hooks: List[Any] = []
+        dev = next(self.model.parameters()).device
+        if dev.type == "meta":
+            dev = torch.device(getattr(trainer, "device", None) or ("cuda" if torch.cuda.is_available() else "cpu"))
+            if dev.type == "cuda" and dev.index is None:
+                dev = torch.device("cuda", torch.cuda.current_device())
+        self.device = dev
+        self.cuda = self.device.type == "cuda"
+
+    # ------------------------------------------------------------------ construction
+    def _is_spared(self, name: str, p: nn.Parameter) -> bool:
+        kind = getattr(p, "dew_kind", "")
+        return kind in ("scale", "bias", "embedding", "sinks") or p.dim() < 2
+
+    def build(self) -> None:
+        if self.built:
+            return
+        cfg = self.t.optimizer.config
+        W = self.world
+        seen = set()
+        total = 0
+        for uname, mods in self.unit_modules:
+            named: List[Tuple[str, nn.Parameter]] = []
+            for m in mods:
+                prefix = next((n for n, mm in self.model.named_modules() if mm is m), "")
+                for n, p in m.named_parameters():
+                    if id(p) in seen:
+                        continue
+                    seen.add(id(p))
+                    named.append(((prefix + "." + n) if prefix else n, p))
+            decay = [(n, p) for n, p in named if not self._is_spared(n, p)]
+            spared = [(n, p) for n, p in named if self._is_spared(n, p)]
+            u = Unit(uname, decay + spared)
+            off = 0
+            for i, (n, p) in enumerate(u.params):
+                if i == len(decay):
+                    u.decay_end = off
+                u.offsets[n] = off
+                off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+            if not spared:
+                u.decay_end = off
+            quantum = W * ALIGN
+            u.size = (off + quantum - 1) // quantum * quantum
+            u.offset = total
+            total += u.size
+            self.units.append(u)
+        self.total = total
+        dev = self.device
+        cdtype = self.t.param_dtype or (torch.bfloat16 if self.cuda else torch.float32)
+        self.compute_dtype = cdtype
+        # arenas: full compute-dtype parameters and full fp32 gradients (peer-visible), flags
+        self.params_arena = SymmetricBuffer(total, cdtype, dev, self.group, zero=True)
+        self.grads_arena = SymmetricBuffer(total, torch.float32, dev, self.group, zero=True)
+        self.flags = SymmetricBuffer(max(64, len(self.units) * 2 * max(W, 1)), torch.int32, dev, self.group, zero=True)
+        shard_total = total // W
+        self.master = torch.empty(shard_total, dtype=torch.float32, device=dev)
+        self.m = torch.zeros(shard_total, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(shard_total, dtype=torch.float32, device=dev)
+        self.ema = None
+        self.block_counter = torch.zeros(len(self.units), dtype=torch.int32, device=dev)
+        self.clip = torch.zeros(4, dtype=torch.float32, device=dev)
+        self.norm_parts = SymmetricBuffer(64, torch.float32, dev, self.group, zero=True) if W > 1 else None
+        # move parameters into the arena (one at a time, releasing the original storage)
+        pa, ga = self.params_arena.tensor, self.grads_arena.tensor
+        self.was_meta = any(p.is_meta for u in self.units for _, p in u.params)
+        owners = {}
+        for mod in self.model.modules():
+            for pname, p in mod._parameters.items():
+                if p is not None:
+                    owners.setdefault(id(p), []).append((mod, pname))
+        with torch.no_grad():
+            for u in self.units:
+                fresh = []
+                for n, p in u.params:
+                    o = u.offset + u.offsets[n]
+                    view = pa[o:o + p.numel()].view(p.shape)
+                    if p.is_meta:
+                        # a model built on the meta device is materialised straight inside the arena
+                        new = nn.Parameter(torch.empty(0, dtype=view.dtype, device=view.device), requires_grad=p.requires_grad)
+                        new.data = view     # .data assignment gives the parameter its own version counter
+                        for attr in ("logical_axes", "dew_kind"):
+                            if hasattr(p, attr):
+                                setattr(new, attr, getattr(p, attr))
+                        for mod, pname in owners[id(p)]:
+                            mod._parameters[pname] = new
+                        p = new
+                    else:
+                        view.copy_(p.data)
+                        p.data = view
+                    p.main_grad = ga[o:o + p.numel()].view(p.shape)
+                    p.grad = None
+                    fresh.append((n, p))
+                u.params = fresh
+        self.device = pa.device
+        self.built = True
+
+    def init_masters(self) -> None:
+        """fp32 masters (and EMA) from the compute-dtype arena: this rank's shard of every unit."""
+        W = self.world
+        pa = self.params_arena.tensor
+        with torch.no_grad():
+            for u in self.units:
+                s = u.size // W
+                src = pa[u.offset + self.rank * s: u.offset + (self.rank + 1) * s]
+                self.master[u.offset // W: u.offset // W + s].copy_(src)
+        if self.t.objective.ema_spec() is not None:
+            self.ema = self.master.clone()
+    def _install_hooks(self) -> None:
+        dev = self.device
+        # unit boundaries: a backward marker at each unit's input
+        for i, (uname, mods) in enumerate(self.unit_modules):
+            first = mods[0]
+            self._hooks.append(first.register_forward_pre_hook(self._make_pre_hook(i), with_kwargs=True))
+        self.comm_stream = torch.cuda.Stream(device=dev) if self.cuda else None
+        self.scratch = torch.empty(2048, dtype=torch.float32, device=dev)
+        self.reduced = None
+
+    def _make_pre_hook(self, index: int):
+        def hook(module, args, kwargs):
+            self._before_unit_forward(index)
+            if not torch.is_grad_enabled():
+                return None
+            new_args = list(args)
+            for j, a in enumerate(new_args):
+                if isinstance(a, torch.Tensor) and a.requires_grad and a.dtype.is_floating_point:
+                    new_args[j] = _Boundary.apply(a, self, index)
+                    return tuple(new_args), kwargs
+            # the first unit's inputs (token ids) carry no gradient: it is finalised after backward returns
+            return None
+        return hook
+
+    # ------------------------------------------------------------------ state
+    def fresh_state(self, key: int) -> TrainState:
+        from ..nn.layers import reset_all
+        if not self.built:
+            seed = int(K.fold_in(key, "init")) & 0x7FFFFFFF                   # same seed on every rank
+            meta = any(p.is_meta for p in self.model.parameters())
+            if not meta:
+                reset_all(self.model, seed)
+            self.build()
+            if meta:
+                reset_all(self.model, seed)
+            self.init_masters()
+            self._install_hooks()
+        state = TrainState(key=key)
+        state.variables = {"params": self._shard_tree(self.master)}
+        state.opt_state = {"count": torch.zeros((), dtype=torch.int64), "mu": self._shard_tree(self.m), "nu": self._shard_tree(self.v)}
+        state.ema = {"params": self._shard_tree(self.ema)} if self.ema is not None else None
+        return state
+
+    def _shard_tree(self, flat: torch.Tensor) -> Dict[str, Any]:
+        """Expose a sharded flat buffer as a tree: one leaf per unit (``<unit>/shard``) holding this rank's shard."""
+        W = self.world
+        return unflatten({f"{u.name}/shard": flat[u.offset // W: (u.offset + u.size) // W] for u in self.units})
+
+    def adopt(self, state: TrainState) -> TrainState:
+        if not self.built:
+            self.build()
+            self.init_masters()
+            self._install_hooks()
+        return state
+
+    def gather_full(self, what: str = "master") -> Dict[str, torch.Tensor]:
+        """Full (unsharded) fp32 tensors by parameter tree path - for checkpoints and evaluation on rank 0."""
+        flat = {"master": self.master, "mu": self.m, "nu": self.v, "ema": self.ema}[what]
+        W = self.world
+        out: Dict[str, torch.Tensor] = {}
+        for u in self.units:
+            s = u.size // W
+            mine = flat[u.offset // W: u.offset // W + s]
+            if W > 1:
+                full = torch.empty(u.size, dtype=flat.dtype, device=flat.device)
+                dist.all_gather_into_tensor(full, mine.contiguous(), group=self.group)
+            else:
+                full = mine
+            for n, p in u.params:
+                o = u.offsets[n]
+                out[module_path_to_tree_path(n)] = full[o:o + p.numel()].view(p.shape).clone()
+        return out
+
+    # ------------------------------------------------------------------ per-unit protocol
+    def _before_unit_forward(self, index: int) -> None:
+        """First forward of a unit in a step: wait until every peer's push of its new weights has landed and the
+        peers have stopped reading its gradient buffer, then clear that buffer."""
+        if not self._first_micro or index in self._cleared:
+            return
+        self._cleared.add(index)
+        u = self.units[index]
+        if self.cuda and self.world > 1 and self.seq > 0:
+            L.check(L.load().dewb_wait_flags(L.ptr(self.flags.tensor), ctypes.c_int(index * 2 + SLOT_DONE),
+                                             ctypes.c_int(self.world), ctypes.c_uint(self.seq),
+                                             ctypes.c_ulonglong(self.wait_limit_ns), L.ptr(L.status(self.device)),
+                                             L.stream_ptr()), "wait_flags")
+            L.count_launches()
+        self.grads_arena.tensor[u.offset:u.offset + u.size].zero_()
+
+    def _unit_backward_done(self, index: int) -> None:
+        if not self._last_micro or index in self._launched:
+            return
+        self._finalize_unit(index)
+
+    def _fold_autograd_grads(self, u: Unit) -> None:
+        """Gradients that arrived through autograd's ``.grad`` (norm scales, embeddings) join the fp32 accumulators."""
+        for n, p in u.params:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(torch.float32))
+                p.grad = None
+
+    def _finalize_unit(self, index: int) -> None:
+        self._launched.add(index)
+        u = self.units[index]
+        self._fold_autograd_grads(u)
+        if self._two_phase:
+            self._launch(index, mode=1)
+        else:
+            self._launch(index, mode=0)
+
+    def _hyper(self, u: Unit):
+        cfg = self.t.optimizer.config
+        o = cfg.optimizer_opts
+        b1, b2 = o.get("b1", 0.9), o.get("b2", 0.999)
+        count = self._count
+        ema_decay = 0.0
+        spec = self.t.objective.ema_spec()
+        if spec is not None:
+            ema_decay = spec.at(self._updates + 1)
+        vals = [self._lr, b1, b2, o.get("eps", 1e-8), cfg.weight_decay, 1 - b1 ** count, 1 - b2 ** count,
+                self._grad_scale, ema_decay]
+        return (ctypes.c_float * 9)(*vals)
+
+    def _launch(self, index: int, mode: int) -> None:
+        u = self.units[index]
+        W, r = self.world, self.rank
+        s = u.size // W
+        lo = u.offset // W
+        if not self.cuda:
+            return self._launch_reference(u, mode)
+        lib = L.load()
+        cur = torch.cuda.current_stream(self.device)
+        self.comm_stream.wait_stream(cur)
+        with torch.cuda.stream(self.comm_stream):
+            esz = self.params_arena.tensor.element_size()
+            rc = lib.dewb_rs_adamw_ag(
+                self.grads_arena.ptr_array(u.offset * 4), self.params_arena.ptr_array(u.offset * esz),
+                self.flags.ptr_array(), L.ptr(self.master[lo:lo + s]), L.ptr(self.m[lo:lo + s]), L.ptr(self.v[lo:lo + s]),
+                L.ptr(self.ema[lo:lo + s] if self.ema is not None else None),
+                L.ptr(self.reduced[lo:lo + s] if self.reduced is not None else None),
+                L.ptr(self.sumsq[index] if self._two_phase else None),
+                L.ptr(self.clip if mode == 2 else None),
+                ctypes.c_longlong(r * s), ctypes.c_longlong(s), ctypes.c_longlong(u.decay_end), ctypes.c_int(r),
+                ctypes.c_int(W), self._hyper(u), ctypes.c_uint(self.seq + 1), ctypes.c_int(index * 2 + SLOT_READY),
+                ctypes.c_int(index * 2 + SLOT_DONE), L.ptr(self.block_counter[index:index + 1]),
+                ctypes.c_ulonglong(self.wait_limit_ns), ctypes.c_int(mode),
+                ctypes.c_int(int(self.t.optimizer.config.skip_nonfinite)), ctypes.c_int(self.comm_blocks),
+                L.ptr(L.status(self.device)), ctypes.c_void_p(self.comm_stream.cuda_stream))
+            L.check(rc, "rs_adamw_ag")
+            L.count_launches()
+
+    def _launch_reference(self, u: Unit, mode: int) -> None:
+        """CPU path (gloo ranks): the same arithmetic with torch collectives - the oracle for the fused kernel."""
+        W, r = self.world, self.rank
+        s = u.size // W
+        lo = u.offset // W
+        g_full = self.grads_arena.tensor[u.offset:u.offset + u.size]
+        if W > 1:
+            g = torch.empty(s, dtype=torch.float32)
+            dist.reduce_scatter_tensor(g, g_full.contiguous(), group=self.group)
+        else:
+            g = g_full.clone()
+        if mode == 1:
+            self.reduced[lo:lo + s].copy_(g)
+            self.sumsq[self.units.index(u)].zero_()
+            self.sumsq[self.units.index(u)][0] = g.pow(2).sum()
+            return
+        if mode == 2:
+            g = self.reduced[lo:lo + s]
+        h = list(self._hyper(u))
+        lr, b1, b2, eps, wd, bc1, bc2, gs, ed = h
+        coef = gs * (float(self.clip[2]) if mode == 2 else 1.0)
+        if mode == 2 and self.t.optimizer.config.skip_nonfinite and not math.isfinite(float(self.clip[0])):
+            return
+        g = g * coef
+        m, v, p = self.m[lo:lo + s], self.v[lo:lo + s], self.master[lo:lo + s]
+        m.mul_(b1).add_(g, alpha=1 - b1)
+        v.mul_(b2).addcmul_(g, g, value=1 - b2)
+        idx = torch.arange(r * s, (r + 1) * s)
+        wdv = torch.where(idx < u.decay_end, torch.tensor(wd), torch.tensor(0.0))
+        p.mul_(1 - lr * wdv).addcdiv_(m / bc1, (v / bc2).sqrt() + eps, value=-lr)
+        if self.ema is not None:
+            self.ema[lo:lo + s].mul_(ed).add_(p, alpha=1 - ed)
+        full = self.params_arena.tensor[u.offset:u.offset + u.size]
+        if W > 1:
+            dist.all_gather_into_tensor(full, p.to(full.dtype).contiguous(), group=self.group)
+        else:
+            full.copy_(p)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, state: TrainState, batch: Mapping[str, torch.Tensor]):
+        from ..training.trainer import _split_rows, tree_detach
+        t = self.t
+        obj = t.objective
+        cfg = t.optimizer.config
+        parts = _split_rows(batch, t.microbatches or 1)
+        step_key = K.fold_in(state.key, state.step)
+        self._lr = float(t.optimizer.schedule(state.step))
+        self._count = int(state.opt_state["count"]) + 1
+        self._updates = state.updates
+        self._two_phase = cfg.clip_grads is not None or cfg.skip_nonfinite
+        if self._two_phase and self.reduced is None:
+            self.reduced = torch.zeros(self.total // self.world, dtype=torch.float32, device=self.device)
+            self.sumsq = torch.zeros(len(self.units), max(self.comm_blocks, 1), dtype=torch.float32, device=self.device)
+        self._cleared, self._launched = set(), set()
+        stats_all, metrics_all, effects = [], {}, {}
+        mass_total = None
+        rows_per = next(iter(parts[0].values())).shape[0]
+        # the pooled mass scales every gradient: it is known before the backward of the last microbatch only if the
+        # objective can count it from the batch (token counts); otherwise fall back to rows
+        mass_known = None
+        if hasattr(obj, "scored_tokens"):
+            try:
+                mass_known = float(sum(obj.scored_tokens(mb) or 0 for mb in parts))
+            except Exception:
+                mass_known = None
+        if mass_known is None or mass_known <= 0:
+            mass_known = float(rows_per * len(parts))
+        if self.world > 1:
+            mk = torch.tensor([mass_known], dtype=torch.float64, device=self.device)
+            dist.all_reduce(mk, group=self.group)
+            mass_known = float(mk.item())
+        self._grad_scale = 1.0 / max(mass_known, 1e-12)
+        first = self.rank * rows_per * len(parts)
+        for i, mb in enumerate(parts):
+            self._first_micro = i == 0
+            self._last_micro = i == len(parts) - 1
+            st = Step(step=state.step, key=step_key, ema=None, train=True, first_index=first, device=self.device)
+            out = obj.loss(None, mb, st)
+            stats, aux = out if isinstance(out, tuple) else (out, Aux())
+            total, mass = obj.reduce_loss(stats)
+            total.backward()
+            stats_all.append(tree_detach(stats))
+            for k, v in aux.metrics.items():
+                metrics_all.setdefault(k, []).append(tree_detach(v))
+            effects.update(aux.effects)
+            first += rows_per
+        # units whose input carries no gradient (the embedding) are finalised here, in reverse order
+        for index in reversed(range(len(self.units))):
+            if index not in self._launched:
+                self._finalize_unit(index)
+        info: Dict[str, Any] = {"learning_rate": self._lr}
+        if self._two_phase:
+            self._second_phase(info)
+        if self.cuda:
+            torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+        self.seq += 1
+        obj.apply_effects(state.variables, effects)
+        new_opt = dict(state.opt_state)
+        new_opt["count"] = torch.tensor(self._count, dtype=torch.int64)
+        rows_total = rows_per * len(parts) * self.world
+        new_state = state.replace(step=state.step + 1, microstep=state.microstep + len(parts), updates=state.updates + 1,
+                                  opt_state=new_opt,
+                                  consumed={"examples": state.consumed.get("examples", 0) + rows_total,
+                                            "tokens": state.consumed.get("tokens", 0) + int(obj.row_tokens(batch) or 0) * self.world})
+        pooled = pool(stats_all)
+        metrics = {"loss": pooled, **{k: pool(v) for k, v in metrics_all.items()}, **info}
+        return new_state, metrics
+
+    def _second_phase(self, info: Dict[str, Any]) -> None:
+        """Global gradient norm from the per-unit partial sums, then the AdamW + push phase for every unit."""
+        cfg = self.t.optimizer.config
+        if self.cuda:
+            torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+        local = self.sumsq.sum().reshape(1) * (self._grad_scale ** 2)
+        if self.world > 1:
+            dist.all_reduce(local, group=self.group)
+        norm = local.sqrt()
+        self.clip[0:1] = local
+        self.clip[1:2] = norm
+        maxn = cfg.clip_grads
+        self.clip[2:3] = torch.where((norm > maxn), maxn / (norm + 1e-6), torch.ones_like(norm)) if maxn else torch.ones_like(norm)
+        info["grad_norm"] = self.clip[1].clone()
+        for index in reversed(range(len(self.units))):
+            self._launch(index, mode=2)
+
+    def close(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []

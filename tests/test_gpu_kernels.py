@@ -1,0 +1,218 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op (GPU only)."""
+import math
+
+import pytest
+import torch
+
+from dew_b200 import ops
+from dew_b200.ops import library as L
+from dew_b200.ops.selection import KernelRefused
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+
+def bf16_floor(ref, other_rounding=None):
+    """RMS error of rounding the fp32 reference to bf16: the error any bf16-output kernel must carry."""
+    return rel_err(ref.to(torch.bfloat16), ref)
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    yield
+    L.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (130, 264, 72), (1000, 520, 392),
+                                   (4096, 4096, 4096), (64, 128, 4096), (8, 256, 128)])
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+def test_gemm_layouts(M, N, K, layout):
+    torch.manual_seed(M * 7 + N * 3 + K)
+    a_mn = layout == "tn"
+    b_mn = layout in ("nn", "tn")
+    A = torch.randn((K, M) if a_mn else (M, K), device=DEV).to(torch.bfloat16)
+    B = torch.randn((K, N) if b_mn else (N, K), device=DEV).to(torch.bfloat16)
+    if (a_mn and M % 8) or (b_mn and N % 8) or K % 8:
+        with pytest.raises(KernelRefused):      # a row stride that breaks the 16-byte TMA rule is refused, not run
+            ops.gemm(A, B, a_mn=a_mn, b_mn=b_mn, kernel="sm100_tcgen05")
+        return
+    out = ops.gemm(A, B, a_mn=a_mn, b_mn=b_mn, kernel="sm100_tcgen05")
+    ref = (A.float().t() if a_mn else A.float()) @ (B.float() if b_mn else B.float().t())
+    assert out.shape == (M, N)
+    err, floor = rel_err(out, ref), bf16_floor(ref)
+    assert err <= 1.5 * floor + 1e-6, (err, floor)
+
+
+@pytest.mark.parametrize("out_dtype,accumulate", [(torch.float32, False), (torch.float32, True), (torch.bfloat16, True)])
+def test_gemm_epilogues(out_dtype, accumulate):
+    torch.manual_seed(3)
+    M, N, K = 300, 520, 200
+    A = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    B = torch.randn(N, K, device=DEV).to(torch.bfloat16)
+    base = torch.randn(M, N, device=DEV).to(out_dtype)
+    out = base.clone()
+    ops.gemm(A, B, out=out, accumulate=accumulate, alpha=0.5, kernel="sm100_tcgen05")
+    ref = 0.5 * (A.float() @ B.float().t()) + (base.float() if accumulate else 0)
+    tol = 1e-5 if out_dtype == torch.float32 else 1.5 * bf16_floor(ref) + 1e-6
+    assert rel_err(out, ref) <= tol
+
+
+def test_gemm_canary_bounds():
+    """Output rows / columns beyond (M, N) must not be touched: the output is a window inside a larger buffer."""
+    torch.manual_seed(5)
+    M, N, K = 200, 264, 136
+    A = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    B = torch.randn(N, K, device=DEV).to(torch.bfloat16)
+    big = torch.full((M + 64, N + 24), 7.0, device=DEV, dtype=torch.bfloat16)
+    window = big[:M, :N]
+    ops.gemm(A, B, out=window, kernel="sm100_tcgen05")
+    assert torch.all(big[M:] == 7.0) and torch.all(big[:, N:] == 7.0)
+    ref = A.float() @ B.float().t()
+    assert rel_err(window, ref) <= 1.5 * bf16_floor(ref) + 1e-6
+
+
+def test_gemm_deterministic():
+    A = torch.randn(512, 1024, device=DEV).to(torch.bfloat16)
+    B = torch.randn(768, 1024, device=DEV).to(torch.bfloat16)
+    a = ops.gemm(A, B, kernel="sm100_tcgen05")
+    b = ops.gemm(A, B, kernel="sm100_tcgen05")
+    assert torch.equal(a, b)
+
+
+def test_linear_autograd_matches_reference():
+    torch.manual_seed(0)
+    x = torch.randn(4, 96, 256, device=DEV).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(384, 256, device=DEV) / 16).to(torch.bfloat16).requires_grad_()
+    y = ops.linear(x, w)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yf = xf @ wf.t()
+    yf.backward(dy.float())
+    assert rel_err(y, yf) <= 1.5 * bf16_floor(yf) + 1e-6
+    assert rel_err(x.grad, xf.grad) <= 1.5 * bf16_floor(xf.grad) + 1e-6
+    assert rel_err(w.grad, wf.grad) <= 1.5 * bf16_floor(wf.grad) + 1e-6
+
+
+@pytest.mark.parametrize("rows,d", [(64, 128), (37, 1000), (512, 4096), (9, 8192)])
+def test_rmsnorm_family(rows, d):
+    torch.manual_seed(rows + d)
+    x = torch.randn(rows, d, device=DEV).to(torch.bfloat16).requires_grad_()
+    b = torch.randn(rows, d, device=DEV).to(torch.bfloat16).requires_grad_()
+    w = (1 + 0.1 * torch.randn(d, device=DEV)).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(rows, d, device=DEV).to(torch.bfloat16)
+    # plain
+    y = ops.rms_norm(x, w, 1e-6)
+    y.backward(dy)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * wf
+    yf.backward(dy.float())
+    assert rel_err(y, yf) <= 2 * bf16_floor(yf)
+    assert rel_err(x.grad, xf.grad) <= 2 * bf16_floor(xf.grad) + 1e-3
+    assert rel_err(w.grad, wf.grad) <= 2e-2
+    # stream: h = x + b, y = norm(h)
+    x.grad = None; w.grad = None
+    y2, h2 = ops.stream_rms_norm(x, b, w, 1e-6)
+    (y2.float() * dy.float()).sum().backward()
+    hf = (x.detach().float() + b.detach().float()).to(torch.bfloat16).float()
+    assert torch.equal(h2.float(), hf)
+    yf2 = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * w.detach().float()
+    assert rel_err(y2, yf2) <= 2 * bf16_floor(yf2)
+    assert torch.equal(x.grad, b.grad)
+    # gated
+    z = torch.randn(rows, d, device=DEV).to(torch.bfloat16).requires_grad_()
+    x.grad = None; w.grad = None
+    y3 = ops.gated_rms_norm(x, z, w, 1e-6)
+    y3.backward(dy)
+    xf, zf, wf = (t.detach().float().requires_grad_() for t in (x, z, w))
+    yf3 = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * wf * torch.nn.functional.silu(zf)
+    yf3.backward(dy.float())
+    assert rel_err(y3, yf3) <= 2 * bf16_floor(yf3)
+    assert rel_err(x.grad, xf.grad) <= 2 * bf16_floor(xf.grad) + 1e-3
+    assert rel_err(z.grad, zf.grad) <= 2 * bf16_floor(zf.grad) + 1e-3
+
+
+@pytest.mark.parametrize("rows,F", [(33, 64), (256, 14336), (1000, 1408)])
+def test_packed_swiglu(rows, F):
+    torch.manual_seed(F)
+    gu = torch.randn(rows, 2 * F, device=DEV).to(torch.bfloat16).requires_grad_()
+    dy = torch.randn(rows, F, device=DEV).to(torch.bfloat16)
+    y = ops.packed_swiglu(gu)
+    y.backward(dy)
+    gf = gu.detach().float().requires_grad_()
+    yf = torch.nn.functional.silu(gf[:, :F]) * gf[:, F:]
+    yf.backward(dy.float())
+    assert rel_err(y, yf) <= 2 * bf16_floor(yf)
+    assert rel_err(gu.grad, gf.grad) <= 2 * bf16_floor(gf.grad) + 1e-3
+
+
+def test_rope_roundtrip_and_reference():
+    torch.manual_seed(1)
+    B, S, H, D = 2, 48, 6, 128
+    x = torch.randn(B, S, H, D, device=DEV).to(torch.bfloat16).requires_grad_()
+    cos, sin = ops.rope_tables(64, D, 10000.0, DEV)
+    y = ops.rope(x, cos, sin, rot_heads=4)
+    ref = ops.rope_reference(x.detach().float(), cos, sin, None, 4)
+    assert rel_err(y, ref) <= 2 * bf16_floor(ref)
+    assert torch.equal(y[:, :, 4:], x.detach()[:, :, 4:])
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf = x.detach().float().requires_grad_()
+    ops.rope_reference(xf, cos, sin, None, 4).backward(dy.float())
+    assert rel_err(x.grad, xf.grad) <= 2 * bf16_floor(xf.grad) + 1e-3
+
+
+@pytest.mark.parametrize("T,d,V,chunk", [(96, 64, 1000, 40), (300, 128, 5008, 128)])
+def test_linear_cross_entropy(T, d, V, chunk):
+    torch.manual_seed(T)
+    h = torch.randn(T, d, device=DEV).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(V, d, device=DEV) / math.sqrt(d)).to(torch.bfloat16).requires_grad_()
+    tg = torch.randint(0, V, (T,), device=DEV)
+    tg[::7] = -100
+    total, mass = ops.linear_cross_entropy(h, w, tg, z_loss=1e-4, chunk=chunk)
+    (total / mass).backward()
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    rt, rm = ops.linear_cross_entropy_reference(hf, wf, tg, z_loss=1e-4)
+    (rt / rm).backward()
+    assert int(mass) == int(rm)
+    assert abs(float(total) - float(rt)) / float(rt) < 5e-3
+    assert rel_err(h.grad, hf.grad) < 3e-2
+    assert rel_err(w.grad, wf.grad) < 3e-2
+
+
+def test_adamw_and_grad_norm_match_torch():
+    torch.manual_seed(2)
+    n = 100_003
+    p = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV).to(torch.bfloat16)
+    ref = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    pb = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    clip = torch.zeros(3, device=DEV)
+    scratch = torch.empty(1024, device=DEV)
+    for step in range(1, 4):
+        ops.grad_norm_(g, clip, scratch, max_norm=1.0)
+        ops.adamw_(p, m, v, g, step=step, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, p_bf16=pb, clip=clip)
+        ref.grad = g.float().clone()
+        torch.nn.utils.clip_grad_norm_([ref], 1.0)
+        opt.step()
+    assert abs(float(clip[1]) - float(g.float().norm())) / float(g.float().norm()) < 1e-4
+    assert rel_err(p, ref.detach()) < 1e-5
+    assert torch.equal(pb, p.to(torch.bfloat16))
+
+
+def test_attention_matches_reference():
+    torch.manual_seed(4)
+    B, S, Hq, Hkv, D = 2, 256, 8, 2, 128
+    q = torch.randn(B, S, Hq, D, device=DEV).to(torch.bfloat16)
+    k = torch.randn(B, S, Hkv, D, device=DEV).to(torch.bfloat16)
+    v = torch.randn(B, S, Hkv, D, device=DEV).to(torch.bfloat16)
+    out = ops.attention(q, k, v, causal=True)
+    ref = ops.attention_reference(q.float(), k.float(), v.float(), causal=True)
+    assert rel_err(out, ref) <= 3 * bf16_floor(ref) + 1e-3
