@@ -228,6 +228,175 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Row-group kernels for d <= 4096: a row is owned by G lanes of one warp (G a power of two <= 32), each lane keeps
+// its VPL 16-byte vectors of the row in registers, reductions are shuffles only (no shared memory, no block barrier),
+// and a block of 8 warps covers 8 * 32 / G rows. These are the fast paths; the block-per-row kernels above remain for
+// wider rows.
+template <int G_>
+__device__ __forceinline__ float group_sum(float v, int G) {
+  for (int o = G >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int MODE, int VPL>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ other, const bf16* __restrict__ w,
+                        bf16* __restrict__ y, bf16* __restrict__ h_out, float* __restrict__ rstd_out, long long rows,
+                        int d, float eps, int G) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gpw = 32 / G;
+  const long long row = (static_cast<long long>(blockIdx.x) * 8 + warp) * gpw + lane / G;
+  const int gl = lane % G;
+  const bool live = row < rows;
+  const int nvec = d >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * d);
+  const uint4* orow = reinterpret_cast<const uint4*>(other + row * d);
+  uint4 cache[VPL];
+  uint4 oth[MODE == 2 ? VPL : 1];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < VPL; ++c) {
+    const int i = gl + c * G;
+    if (live && i < nvec) {
+      cache[c] = xr[i];
+      if (MODE != 0) oth[MODE == 2 ? c : 0] = orow[i];
+      if (MODE == 1) {
+        float f[8], g[8]; unpack8(cache[c], f); unpack8(oth[0], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += g[j];
+        cache[c] = pack8(f);
+        reinterpret_cast<uint4*>(h_out + row * d)[i] = cache[c];
+      }
+      float f[8]; unpack8(cache[c], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
+  }
+  ss = group_sum<0>(ss, G);
+  const float rstd = rsqrtf(ss / d + eps);
+  if (live && gl == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int c = 0; c < VPL; ++c) {
+    const int i = gl + c * G;
+    if (live && i < nvec) {
+      float f[8], g[8]; unpack8(cache[c], f); unpack8(wr[i], g);
+      if (MODE == 2) {
+        float z[8]; unpack8(oth[c], z);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = f[j] * rstd * g[j] * (z[j] / (1.f + __expf(-z[j])));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = f[j] * rstd * g[j];
+      }
+      reinterpret_cast<uint4*>(y + row * d)[i] = pack8(f);
+    }
+  }
+}
+
+// dx (and dz when gated) for one row per lane group; dw is a separate column reduction (rmsnorm_dw_kernel).
+template <bool GATED, int VPL>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_dx_rows_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                           const float* __restrict__ rstd, const bf16* __restrict__ dres, const bf16* __restrict__ z,
+                           bf16* __restrict__ dx, bf16* __restrict__ dz, long long rows, int d, int G) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gpw = 32 / G;
+  const long long row = (static_cast<long long>(blockIdx.x) * 8 + warp) * gpw + lane / G;
+  const int gl = lane % G;
+  const bool live = row < rows;
+  const int nvec = d >> 3;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  const float rs = live ? rstd[row] : 0.f;
+  uint4 gxp[VPL], xhp[VPL];     // g = dy * w (* silu z) and xhat, kept packed in bf16 pairs? no: fp32 needs 2x; keep inputs
+  float dot = 0.f;
+#pragma unroll
+  for (int c = 0; c < VPL; ++c) {
+    const int i = gl + c * G;
+    if (live && i < nvec) {
+      gxp[c] = reinterpret_cast<const uint4*>(dy + row * d)[i];
+      xhp[c] = reinterpret_cast<const uint4*>(x + row * d)[i];
+      float a[8], b[8], ww[8]; unpack8(gxp[c], a); unpack8(xhp[c], b); unpack8(wr[i], ww);
+      if (GATED) {
+        float zz[8], dzv[8]; unpack8(reinterpret_cast<const uint4*>(z + row * d)[i], zz);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float sg = 1.f / (1.f + __expf(-zz[j]));
+          dzv[j] = a[j] * ww[j] * (b[j] * rs) * (sg * (1.f + zz[j] * (1.f - sg)));
+          a[j] *= zz[j] * sg;
+        }
+        reinterpret_cast<uint4*>(dz + row * d)[i] = pack8(dzv);
+        gxp[c] = pack8(a);   // dy * silu(z), rounded to bf16 like every other stored intermediate
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += a[j] * ww[j] * (b[j] * rs);
+    }
+  }
+  dot = group_sum<0>(dot, G) / d;
+#pragma unroll
+  for (int c = 0; c < VPL; ++c) {
+    const int i = gl + c * G;
+    if (live && i < nvec) {
+      float a[8], b[8], ww[8], o[8]; unpack8(gxp[c], a); unpack8(xhp[c], b); unpack8(wr[i], ww);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rs * (a[j] * ww[j] - (b[j] * rs) * dot);
+      if (dres != nullptr) {
+        float r[8]; unpack8(reinterpret_cast<const uint4*>(dres + row * d)[i], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      reinterpret_cast<uint4*>(dx + row * d)[i] = pack8(o);
+    }
+  }
+}
+
+// dw partials: block (32, 8); thread (tx, ty) owns vector column blockIdx.x * 32 + tx and walks rows
+// blockIdx.y * 8 + ty, + gridDim.y * 8, ...; the 8 row-threads fold through shared memory into
+// partial[blockIdx.y, d].
+template <bool GATED>
+__global__ void __launch_bounds__(256)
+rmsnorm_dw_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const float* __restrict__ rstd,
+                  const bf16* __restrict__ z, float* __restrict__ partial, long long rows, int d) {
+  __shared__ float red[8][32][9];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int vec = blockIdx.x * 32 + tx;
+  const int nvec = d >> 3;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (vec < nvec) {
+    for (long long r = static_cast<long long>(blockIdx.y) * 8 + ty; r < rows; r += static_cast<long long>(gridDim.y) * 8) {
+      float a[8], b[8];
+      unpack8(reinterpret_cast<const uint4*>(dy + r * d)[vec], a);
+      unpack8(reinterpret_cast<const uint4*>(x + r * d)[vec], b);
+      const float rs = rstd[r];
+      if (GATED) {
+        float zz[8]; unpack8(reinterpret_cast<const uint4*>(z + r * d)[vec], zz);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] *= zz[j] / (1.f + __expf(-zz[j]));
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += a[j] * b[j] * rs;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[ty][tx][j] = acc[j];
+  __syncthreads();
+  if (ty == 0 && vec < nvec) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) s += red[k][tx][j];
+      acc[j] = s;
+    }
+    float4* out = reinterpret_cast<float4*>(partial + static_cast<long long>(blockIdx.y) * d + vec * 8);
+    out[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+}
+
 // out[col] (+)= sum_r partial[r, col]; one thread per column, coalesced over columns
 __global__ void colsum_kernel(const float* __restrict__ partial, int nrows, int d, float* __restrict__ out_f32,
                               bf16* __restrict__ out_bf16, int accumulate) {
@@ -245,15 +414,28 @@ __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gate, const bf16* __r
                                   long long rows, int F, long long in_stride) {
   const long long nvec = rows * (F >> 3);
   const int fv = F >> 3;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / fv; const int c = static_cast<int>(i - r * fv);
-    float g[8], u[8];
-    unpack8(reinterpret_cast<const uint4*>(gate + r * in_stride)[c], g);
-    unpack8(reinterpret_cast<const uint4*>(up + r * in_stride)[c], u);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nvec; i0 += 4 * stride) {
+    uint4 gv[4], uv[4];
+    long long rr[4]; int cc[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) g[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
-    reinterpret_cast<uint4*>(out + r * F)[c] = pack8(g);
+    for (int k = 0; k < 4; ++k) {           // issue every load of the iteration before any math
+      const long long i = i0 + k * stride;
+      if (i < nvec) {
+        rr[k] = i / fv; cc[k] = static_cast<int>(i - rr[k] * fv);
+        gv[k] = __ldcs(reinterpret_cast<const uint4*>(gate + rr[k] * in_stride) + cc[k]);
+        uv[k] = __ldcs(reinterpret_cast<const uint4*>(up + rr[k] * in_stride) + cc[k]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (i0 + k * stride < nvec) {
+        float g[8], u[8]; unpack8(gv[k], g); unpack8(uv[k], u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+        reinterpret_cast<uint4*>(out + rr[k] * F)[cc[k]] = pack8(g);
+      }
+    }
   }
 }
 __global__ void swiglu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ gate, const bf16* __restrict__ up,
@@ -261,21 +443,35 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __res
                                   long long in_stride) {
   const long long nvec = rows * (F >> 3);
   const int fv = F >> 3;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / fv; const int c = static_cast<int>(i - r * fv);
-    float g[8], u[8], d[8], dg[8], du[8];
-    unpack8(reinterpret_cast<const uint4*>(gate + r * in_stride)[c], g);
-    unpack8(reinterpret_cast<const uint4*>(up + r * in_stride)[c], u);
-    unpack8(reinterpret_cast<const uint4*>(dy + r * F)[c], d);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < nvec; i0 += 2 * stride) {
+    uint4 gv[2], uv[2], dv[2];
+    long long rr[2]; int cc[2];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float sg = 1.f / (1.f + __expf(-g[j]));
-      du[j] = d[j] * g[j] * sg;
-      dg[j] = d[j] * u[j] * sg * (1.f + g[j] * (1.f - sg));
+    for (int k = 0; k < 2; ++k) {
+      const long long i = i0 + k * stride;
+      if (i < nvec) {
+        rr[k] = i / fv; cc[k] = static_cast<int>(i - rr[k] * fv);
+        gv[k] = __ldcs(reinterpret_cast<const uint4*>(gate + rr[k] * in_stride) + cc[k]);
+        uv[k] = __ldcs(reinterpret_cast<const uint4*>(up + rr[k] * in_stride) + cc[k]);
+        dv[k] = __ldcs(reinterpret_cast<const uint4*>(dy + rr[k] * F) + cc[k]);
+      }
     }
-    reinterpret_cast<uint4*>(dgate + r * in_stride)[c] = pack8(dg);
-    reinterpret_cast<uint4*>(dup + r * in_stride)[c] = pack8(du);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (i0 + k * stride < nvec) {
+        float g[8], u[8], d[8], dg[8], du[8];
+        unpack8(gv[k], g); unpack8(uv[k], u); unpack8(dv[k], d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float sg = 1.f / (1.f + __expf(-g[j]));
+          du[j] = d[j] * g[j] * sg;
+          dg[j] = d[j] * u[j] * sg * (1.f + g[j] * (1.f - sg));
+        }
+        reinterpret_cast<uint4*>(dgate + rr[k] * in_stride)[cc[k]] = pack8(dg);
+        reinterpret_cast<uint4*>(dup + rr[k] * in_stride)[cc[k]] = pack8(du);
+      }
+    }
   }
 }
 
@@ -484,6 +680,21 @@ extern "C" int dewb_rmsnorm_fwd(const void* x, const void* other, const void* w,
   if (d % 8 != 0 || rows <= 0) return rows == 0 ? 0 : -3;
   const bf16 *xp = (const bf16*)x, *op = (const bf16*)other, *wp = (const bf16*)w;
   bf16 *yp = (bf16*)y, *hp = (bf16*)h_out;
+  if (d <= 4096) {
+    const int nvec = d >> 3;
+    int G = 32;
+    while (G > 1 && (G >> 1) >= nvec) G >>= 1;
+    const int need = (nvec + G - 1) / G;
+    const long long rows_per_block = 8LL * (32 / G);
+    const unsigned blocks = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
+#define DEWB_FWD_ROWS(MODE, VPL) rmsnorm_fwd_rows_kernel<MODE, VPL><<<blocks, 256, 0, STREAM(stream)>>>(xp, op, wp, yp, hp, rstd, rows, d, eps, G)
+#define DEWB_FWD_MODE(VPL) do { if (mode == 0) DEWB_FWD_ROWS(0, VPL); else if (mode == 1) DEWB_FWD_ROWS(1, VPL); else DEWB_FWD_ROWS(2, VPL); } while (0)
+    if (need <= 1) DEWB_FWD_MODE(1); else if (need <= 2) DEWB_FWD_MODE(2); else if (need <= 4) DEWB_FWD_MODE(4);
+    else if (need <= 8) DEWB_FWD_MODE(8); else DEWB_FWD_MODE(16);
+#undef DEWB_FWD_MODE
+#undef DEWB_FWD_ROWS
+    return LAST_ERR();
+  }
   dim3 grid(static_cast<unsigned>(rows));
   if (mode == 0) rmsnorm_fwd_kernel<0><<<grid, NORM_THREADS, 0, STREAM(stream)>>>(xp, op, wp, yp, hp, rstd, d, eps);
   else if (mode == 1) rmsnorm_fwd_kernel<1><<<grid, NORM_THREADS, 0, STREAM(stream)>>>(xp, op, wp, yp, hp, rstd, d, eps);
@@ -504,6 +715,30 @@ extern "C" int dewb_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
   if (d % 8 != 0 || d > NORM_THREADS * 8 * BWD_COLS) return -3;
   if (rows <= 0) return 0;
   const int blocks = dewb_rmsnorm_bwd_blocks(rows);
+  if (d <= 4096) {
+    const int nvec = d >> 3;
+    int G = 32;
+    while (G > 1 && (G >> 1) >= nvec) G >>= 1;
+    const int need = (nvec + G - 1) / G;
+    const long long rows_per_block = 8LL * (32 / G);
+    const unsigned nb = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
+#define DEWB_BWD_ROWS(GATED, VPL) rmsnorm_bwd_dx_rows_kernel<GATED, VPL><<<nb, 256, 0, STREAM(stream)>>>( \
+      (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, (const bf16*)z, (bf16*)dx, (bf16*)dz, rows, d, G)
+#define DEWB_BWD_G(VPL) do { if (z != nullptr) DEWB_BWD_ROWS(true, VPL); else DEWB_BWD_ROWS(false, VPL); } while (0)
+    if (need <= 1) DEWB_BWD_G(1); else if (need <= 2) DEWB_BWD_G(2); else if (need <= 4) DEWB_BWD_G(4);
+    else if (need <= 8) DEWB_BWD_G(8); else DEWB_BWD_G(16);
+#undef DEWB_BWD_G
+#undef DEWB_BWD_ROWS
+    // dw: column reduction with `blocks` row splits, folded by colsum_kernel
+    int splits = blocks < 1 ? 1 : blocks;
+    const long long max_useful = (rows + 7) / 8;
+    if (splits > max_useful) splits = static_cast<int>(max_useful);
+    dim3 g((nvec + 31) / 32, splits);
+    if (z != nullptr) rmsnorm_dw_kernel<true><<<g, 256, 0, STREAM(stream)>>>((const bf16*)dy, (const bf16*)x, rstd, (const bf16*)z, dw_partial, rows, d);
+    else rmsnorm_dw_kernel<false><<<g, 256, 0, STREAM(stream)>>>((const bf16*)dy, (const bf16*)x, rstd, nullptr, dw_partial, rows, d);
+    colsum_kernel<<<(d + 255) / 256, 256, 0, STREAM(stream)>>>(dw_partial, splits, d, dw_f32, (bf16*)dw_bf16, accumulate);
+    return LAST_ERR();
+  }
   if (z != nullptr)
     rmsnorm_bwd_kernel<true><<<blocks, NORM_THREADS, 0, STREAM(stream)>>>(
         (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, (const bf16*)z, (bf16*)dx, (bf16*)dz,

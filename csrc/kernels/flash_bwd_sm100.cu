@@ -1,0 +1,589 @@
+// Flash attention backward for sm_100a (head_dim 128 or 64, bf16, causal or full, GQA), in three kernels:
+//
+//   delta   : delta[b,h,s] = sum_d dO * O                                   (row kernel)
+//   dQ      : one CTA per 128 query rows; loops over key tiles:
+//                S = Q K^T, dP = dO V^T (tcgen05, TMEM) -> dS = P o (dP - delta) (bf16, shared) -> dQ += dS K
+//   dK / dV : one CTA per 128 keys of one KV head; loops over the query heads of its group and 64-row query blocks:
+//                S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T (bf16, shared) -> dV += P^T dO, dK += dS^T Q
+// Both MMA kernels recompute the probabilities from the saved log-sum-exp, keep their output accumulators in tensor
+// memory for the whole loop and never use atomics, so results are deterministic. A Q / dO / K / V tile sits in shared
+// memory once and serves two products through two descriptors (K-major for the score products, MN-major for the
+// gradient products).
+//
+// Replaces the reference's attention template backward (src/dew/nn/kernels/templates/attention_mosaic_dkv.py,
+// attention_mosaic_dq.py), which it records as 6-9x slower than cuDNN on B200 (src/dew/nn/attention_kernels.py:772-796).
+#include "../common/ptx.cuh"
+#include "../common/tmap.h"
+
+namespace dewb {
+namespace flashbwd {
+
+constexpr int THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                             float* __restrict__ delta, int B, int S, int H, int D, long long do_sb, long long do_ss,
+                             long long do_sh, long long o_sb, long long o_ss, long long o_sh) {
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;   // one warp per (b, s, h)
+  const int lane = threadIdx.x & 31;
+  if (row >= static_cast<long long>(B) * S * H) return;
+  const int h = static_cast<int>(row % H);
+  const long long bs = row / H;
+  const int s = static_cast<int>(bs % S);
+  const int b = static_cast<int>(bs / S);
+  const __nv_bfloat16* a = dO + b * do_sb + s * do_ss + h * do_sh;
+  const __nv_bfloat16* c = O + b * o_sb + s * o_ss + h * o_sh;
+  float acc = 0.f;
+  for (int i = lane * 2; i < D; i += 64) {
+    const uint32_t x = *reinterpret_cast<const uint32_t*>(a + i);
+    const uint32_t y = *reinterpret_cast<const uint32_t*>(c + i);
+    acc += bf16_lo(x) * bf16_lo(y) + bf16_hi(x) * bf16_hi(y);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) delta[(static_cast<long long>(b) * H + h) * S + s] = acc;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// dQ kernel
+template <int D>
+struct DqCfg {
+  static constexpr int BM = 128, BN = 128;
+  static constexpr int SUB = D / 64;
+  static constexpr int TILE = 128 * D * 2;          // a [128 x D] bf16 tile
+  static constexpr int DS_BYTES = BM * BN * 2;
+  static constexpr int SMEM = 2 * TILE + 4 * TILE + DS_BYTES + 1024 + 256;
+  static constexpr int TM_S = 0, TM_DP = 128, TM_DQ = 256, TM_COLS = 512;
+};
+
+struct DqBars {
+  uint64_t q_full;
+  uint64_t k_full[2], v_full[2], kv_empty[2];
+  uint64_t sdp_full, sdp_empty;
+  uint64_t ds_full, dq_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(THREADS, 1)
+flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
+                const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
+                const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dq, int S,
+                int T, int Hq, int Hkv, long long dq_sb, long long dq_ss, long long dq_sh, float scale,
+                int* __restrict__ err) {
+  using C = DqCfg<D>;
+  constexpr int BM = C::BM, BN = C::BN;
+  extern __shared__ uint8_t smem_raw[];
+  {
+    // An earlier launch reported a timed-out wait: leave at once instead of queueing more waits behind it. One
+    // thread reads the status so the whole CTA takes the same branch.
+    __shared__ int poisoned;
+    if (threadIdx.x == 0) poisoned = *reinterpret_cast<volatile int*>(err);
+    __syncthreads();
+    if (poisoned != 0) return;
+  }
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = sQ + C::TILE;
+  uint8_t* sK = sdO + C::TILE;          // 2 stages
+  uint8_t* sV = sK + 2 * C::TILE;       // 2 stages
+  uint8_t* sdS = sV + 2 * C::TILE;
+  DqBars* bars = reinterpret_cast<DqBars*>(sdS + C::DS_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = CAUSAL ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (Hq / Hkv);
+  const int q0 = qt * BM;
+  const int n_tiles = CAUSAL ? min((q0 + BM + (T - S) + BN - 1) / BN, (T + BN - 1) / BN) : (T + BN - 1) / BN;
+  const float scale_log2 = scale * LOG2E;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars->k_full[i], 1); mbar_init(&bars->v_full[i], 1); mbar_init(&bars->kv_empty[i], 1); }
+    mbar_init(&bars->sdp_full, 1); mbar_init(&bars->sdp_empty, 4);
+    mbar_init(&bars->ds_full, 4); mbar_init(&bars->dq_done, 1);
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 5) { tmem_alloc(&bars->tmem_base, C::TM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(&bars->q_full, 2 * C::TILE);
+#pragma unroll
+      for (int t = 0; t < C::SUB; ++t) {
+        tma_load_4d(sQ + t * (BM * 128), &tq, &bars->q_full, t * 64, h, q0, b);
+        tma_load_4d(sdO + t * (BM * 128), &tdo, &bars->q_full, t * 64, h, q0, b);
+      }
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars->kv_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); break; }
+        mbar_expect_tx(&bars->k_full[st], C::TILE);
+#pragma unroll
+        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sK + st * C::TILE + t * (BN * 128), &tk, &bars->k_full[st], t * 64, hk, j * BN, b);
+        mbar_expect_tx(&bars->v_full[st], C::TILE);
+#pragma unroll
+        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sV + st * C::TILE + t * (BN * 128), &tv, &bars->v_full[st], t * 64, hk, j * BN, b);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(BM, BN, 1, 1, 0, 0);
+      constexpr uint32_t idesc_dq = make_idesc(BM, D, 1, 1, 0, 1);
+      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+      if (!ok) atomicCAS(err, 0, ERR_WAIT_FULL);
+      auto issue_scores = [&](int j) -> bool {
+        const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars->k_full[st], ph, abort_flag) || !mbar_wait(&bars->v_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
+        if (!mbar_wait(&bars->sdp_empty, (j & 1) ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), da = smem_u32(sdO), ka = smem_u32(sK + st * C::TILE), va = smem_u32(sV + st * C::TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + C::TM_S, make_sdesc_sw128(qa + off, 16, 1024), make_sdesc_sw128(ka + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + C::TM_DP, make_sdesc_sw128(da + off, 16, 1024), make_sdesc_sw128(va + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->sdp_full);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_scores(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) { ok = issue_scores(j + 1); if (!ok) break; }
+        const int st = j & 1;
+        if (!mbar_wait(&bars->ds_full, j & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(sdS), ka = smem_u32(sK + st * C::TILE);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint32_t aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + C::TM_DQ, make_sdesc_sw128(sa + aoff, 16, 1024),
+                       make_sdesc_sw128(ka + kk * 2048, BN * 128, 1024), idesc_dq, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&bars->kv_empty[st]);
+        umma_commit(&bars->dq_done);
+      }
+    }
+  } else {
+    const int r = warp * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int row = q0 + r;
+    const long long stat = (static_cast<long long>(b) * Hq + h) * S + row;
+    const float lse2 = row < S ? lse[stat] * LOG2E : 0.f;
+    const float dl = row < S ? delta[stat] : 0.f;
+    const int limit = CAUSAL ? (row + (T - S)) : (T - 1);
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (!mbar_wait(&bars->sdp_full, j & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
+      tc_fence_after();
+      const int k0 = j * BN;
+      uint32_t packed[BN / 2];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_S + c * 32, sv);
+        tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DP + c * 32, dv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int key = k0 + c * 32 + i;
+          float p0 = exp2f(__uint_as_float(sv[i]) * scale_log2 - lse2);
+          float p1 = exp2f(__uint_as_float(sv[i + 1]) * scale_log2 - lse2);
+          if (key > limit || key >= T) p0 = 0.f;
+          if (key + 1 > limit || key + 1 >= T) p1 = 0.f;
+          packed[(c * 32 + i) >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->sdp_empty);
+      if (j > 0) {
+        if (!mbar_wait(&bars->dq_done, (j - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+      }
+#pragma unroll
+      for (int c16 = 0; c16 < BN / 8; ++c16) {
+        const uint4 pk = make_uint4(packed[c16 * 4], packed[c16 * 4 + 1], packed[c16 * 4 + 2], packed[c16 * 4 + 3]);
+        const int t = c16 >> 3, c = c16 & 7;
+        *reinterpret_cast<uint4*>(sdS + t * (BM * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = pk;
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->ds_full);
+    }
+    if (ok && n_tiles > 0) {
+      if (!mbar_wait(&bars->dq_done, (n_tiles - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
+    }
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* orow = dq + b * dq_sb + static_cast<long long>(row) * dq_ss + h * dq_sh;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        if (n_tiles > 0) { tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DQ + c * 32, v); tmem_ld_wait(); }
+        else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0;
+        }
+        if (row < S) {
+          uint4* o4 = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 pk;
+            pk.x = pack_bf16(__uint_as_float(v[q * 8 + 0]) * scale, __uint_as_float(v[q * 8 + 1]) * scale);
+            pk.y = pack_bf16(__uint_as_float(v[q * 8 + 2]) * scale, __uint_as_float(v[q * 8 + 3]) * scale);
+            pk.z = pack_bf16(__uint_as_float(v[q * 8 + 4]) * scale, __uint_as_float(v[q * 8 + 5]) * scale);
+            pk.w = pack_bf16(__uint_as_float(v[q * 8 + 6]) * scale, __uint_as_float(v[q * 8 + 7]) * scale);
+            o4[q] = pk;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, C::TM_COLS); }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// dK / dV kernel
+template <int D>
+struct DkvCfg {
+  static constexpr int BKV = 128, BQ = 64;
+  static constexpr int SUB = D / 64;
+  static constexpr int KV_TILE = BKV * D * 2;        // [128 x D]
+  static constexpr int Q_TILE = BQ * D * 2;          // [64 x D]
+  static constexpr int P_BYTES = BKV * BQ * 2;       // [128 x 64]
+  static constexpr int SMEM = 2 * KV_TILE + 4 * Q_TILE + 2 * P_BYTES + 2 * 2 * BQ * 4 + 1024 + 256;
+  static constexpr int TM_ST0 = 0, TM_DPT0 = 64, TM_ST1 = 128, TM_DPT1 = 192, TM_DV = 256, TM_DK = 256 + D, TM_COLS = 512;
+};
+
+struct DkvBars {
+  uint64_t kv_full;
+  uint64_t q_full[2], q_empty[2];
+  uint64_t st_full[2], st_empty[2];
+  uint64_t pds_full, acc_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(THREADS, 1)
+flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
+                 const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
+                 const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dk,
+                 __nv_bfloat16* __restrict__ dv, int S, int T, int Hq, int Hkv, long long dk_sb, long long dk_ss,
+                 long long dk_sh, long long dv_sb, long long dv_ss, long long dv_sh, float scale, int* __restrict__ err) {
+  using C = DkvCfg<D>;
+  constexpr int BKV = C::BKV, BQ = C::BQ;
+  extern __shared__ uint8_t smem_raw[];
+  {
+    // An earlier launch reported a timed-out wait: leave at once instead of queueing more waits behind it. One
+    // thread reads the status so the whole CTA takes the same branch.
+    __shared__ int poisoned;
+    if (threadIdx.x == 0) poisoned = *reinterpret_cast<volatile int*>(err);
+    __syncthreads();
+    if (poisoned != 0) return;
+  }
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + C::KV_TILE;
+  uint8_t* sQ = sV + C::KV_TILE;            // 2 stages
+  uint8_t* sdO = sQ + 2 * C::Q_TILE;        // 2 stages
+  uint8_t* sP = sdO + 2 * C::Q_TILE;
+  uint8_t* sdS = sP + C::P_BYTES;
+  float* sStat = reinterpret_cast<float*>(sdS + C::P_BYTES);   // [2 stages][lse2 64 | delta 64]
+  DkvBars* bars = reinterpret_cast<DkvBars*>(reinterpret_cast<uint8_t*>(sStat) + 2 * 2 * BQ * 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int rep = Hq / Hkv;
+  const int kv0 = kt * BKV;
+  // first query block that can see any key of this tile (causal, bottom-right aligned): q + (T - S) >= kv0
+  const int q_first = CAUSAL ? max(0, kv0 - (T - S)) / BQ : 0;
+  const int nqb = (S + BQ - 1) / BQ - q_first;          // query blocks per head
+  const int iters = nqb > 0 ? nqb * rep : 0;
+  const float scale_log2 = scale * LOG2E;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->q_full[i], 1); mbar_init(&bars->q_empty[i], 1);
+      mbar_init(&bars->st_full[i], 1); mbar_init(&bars->st_empty[i], 4);
+    }
+    mbar_init(&bars->pds_full, 4); mbar_init(&bars->acc_done, 1);
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 5) { tmem_alloc(&bars->tmem_base, C::TM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(&bars->kv_full, 2 * C::KV_TILE);
+#pragma unroll
+      for (int t = 0; t < C::SUB; ++t) {
+        tma_load_4d(sK + t * (BKV * 128), &tk, &bars->kv_full, t * 64, hk, kv0, b);
+        tma_load_4d(sV + t * (BKV * 128), &tv, &bars->kv_full, t * 64, hk, kv0, b);
+      }
+      for (int it = 0; it < iters; ++it) {
+        const int st = it & 1; const uint32_t ph = (it >> 1) & 1;
+        const int h = hk * rep + it / nqb;
+        const int qb = (q_first + it % nqb) * BQ;
+        if (!mbar_wait(&bars->q_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); break; }
+        mbar_expect_tx(&bars->q_full[st], 2 * C::Q_TILE);
+#pragma unroll
+        for (int t = 0; t < C::SUB; ++t) {
+          tma_load_4d(sQ + st * C::Q_TILE + t * (BQ * 128), &tq, &bars->q_full[st], t * 64, h, qb, b);
+          tma_load_4d(sdO + st * C::Q_TILE + t * (BQ * 128), &tdo, &bars->q_full[st], t * 64, h, qb, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_st = make_idesc(BKV, BQ, 1, 1, 0, 0);
+      constexpr uint32_t idesc_acc = make_idesc(BKV, D, 1, 1, 0, 1);
+      bool ok = mbar_wait(&bars->kv_full, 0, abort_flag);
+      if (!ok) atomicCAS(err, 0, ERR_WAIT_FULL);
+      auto issue_scores = [&](int it) -> bool {
+        const int st = it & 1; const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&bars->q_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
+        if (!mbar_wait(&bars->st_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
+        tc_fence_after();
+        const uint32_t ka = smem_u32(sK), va = smem_u32(sV), qa = smem_u32(sQ + st * C::Q_TILE), da = smem_u32(sdO + st * C::Q_TILE);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t aoff = (kk >> 2) * (BKV * 128) + (kk & 3) * 32;
+          const uint32_t boff = (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + (st ? C::TM_ST1 : C::TM_ST0), make_sdesc_sw128(ka + aoff, 16, 1024),
+                       make_sdesc_sw128(qa + boff, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t aoff = (kk >> 2) * (BKV * 128) + (kk & 3) * 32;
+          const uint32_t boff = (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + (st ? C::TM_DPT1 : C::TM_DPT0), make_sdesc_sw128(va + aoff, 16, 1024),
+                       make_sdesc_sw128(da + boff, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->st_full[st]);
+        return true;
+      };
+      if (ok && iters > 0) ok = issue_scores(0);
+      for (int it = 0; it < iters && ok; ++it) {
+        if (it + 1 < iters) { ok = issue_scores(it + 1); if (!ok) break; }
+        const int st = it & 1;
+        if (!mbar_wait(&bars->pds_full, it & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sP), sa = smem_u32(sdS), qa = smem_u32(sQ + st * C::Q_TILE), da = smem_u32(sdO + st * C::Q_TILE);
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk)
+          umma_bf16_ss(tmem + C::TM_DV, make_sdesc_sw128(pa + kk * 32, 16, 1024),
+                       make_sdesc_sw128(da + kk * 2048, BQ * 128, 1024), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk)
+          umma_bf16_ss(tmem + C::TM_DK, make_sdesc_sw128(sa + kk * 32, 16, 1024),
+                       make_sdesc_sw128(qa + kk * 2048, BQ * 128, 1024), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&bars->q_empty[st]);
+        umma_commit(&bars->acc_done);
+      }
+    }
+  } else {
+    const int r = warp * 32 + lane;                 // key row within the tile == TMEM lane
+    const int tid = threadIdx.x;                    // 0..127
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int key = kv0 + r;
+    bool ok = true;
+    for (int it = 0; it < iters && ok; ++it) {
+      const int st = it & 1; const uint32_t ph = (it >> 1) & 1;
+      const int h = hk * rep + it / nqb;
+      const int qb = (q_first + it % nqb) * BQ;
+      // per-query statistics of this block, shared by the 128 threads
+      {
+        float* dst = sStat + st * 2 * BQ;
+        const int qi = qb + (tid & (BQ - 1));
+        const long long idx = (static_cast<long long>(b) * Hq + h) * S + qi;
+        if (tid < BQ) dst[tid] = qi < S ? lse[idx] * LOG2E : INFINITY;     // +inf -> exp2(-inf) = 0 for padded queries
+        else dst[tid] = qi < S ? delta[idx] : 0.f;
+      }
+      named_barrier_sync(1, 128);
+      const float* lse2 = sStat + st * 2 * BQ;
+      const float* dlt = lse2 + BQ;
+      if (!mbar_wait(&bars->st_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
+      tc_fence_after();
+      uint32_t pp[BQ / 2], ds[BQ / 2];
+#pragma unroll
+      for (int c = 0; c < BQ / 32; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TM_ST1 : C::TM_ST0) + c * 32, sv);
+        tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TM_DPT1 : C::TM_DPT0) + c * 32, dv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int qc = c * 32 + i;
+          float p0 = exp2f(__uint_as_float(sv[i]) * scale_log2 - lse2[qc]);
+          float p1 = exp2f(__uint_as_float(sv[i + 1]) * scale_log2 - lse2[qc + 1]);
+          if (CAUSAL) {
+            if (key > qb + qc + (T - S)) p0 = 0.f;
+            if (key > qb + qc + 1 + (T - S)) p1 = 0.f;
+          }
+          if (key >= T) { p0 = 0.f; p1 = 0.f; }
+          pp[qc >> 1] = pack_bf16(p0, p1);
+          ds[qc >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dlt[qc]), p1 * (__uint_as_float(dv[i + 1]) - dlt[qc + 1]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->st_empty[st]);
+      if (it > 0) {
+        if (!mbar_wait(&bars->acc_done, (it - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+      }
+#pragma unroll
+      for (int c = 0; c < BQ / 8; ++c) {
+        const int off = r * 128 + ((c ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[c * 4], pp[c * 4 + 1], pp[c * 4 + 2], pp[c * 4 + 3]);
+        *reinterpret_cast<uint4*>(sdS + off) = make_uint4(ds[c * 4], ds[c * 4 + 1], ds[c * 4 + 2], ds[c * 4 + 3]);
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->pds_full);
+    }
+    if (ok && iters > 0) {
+      if (!mbar_wait(&bars->acc_done, (iters - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
+    }
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* kout = dk + b * dk_sb + static_cast<long long>(key) * dk_ss + hk * dk_sh;
+      __nv_bfloat16* vout = dv + b * dv_sb + static_cast<long long>(key) * dv_ss + hk * dv_sh;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t a[32], g[32];
+        if (iters > 0) {
+          tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DV + c * 32, a);
+          tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DK + c * 32, g);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { a[i] = 0; g[i] = 0; }
+        }
+        if (key < T) {
+          uint4* v4 = reinterpret_cast<uint4*>(vout + c * 32);
+          uint4* k4 = reinterpret_cast<uint4*>(kout + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 pv, pk;
+            pv.x = pack_bf16(__uint_as_float(a[q * 8 + 0]), __uint_as_float(a[q * 8 + 1]));
+            pv.y = pack_bf16(__uint_as_float(a[q * 8 + 2]), __uint_as_float(a[q * 8 + 3]));
+            pv.z = pack_bf16(__uint_as_float(a[q * 8 + 4]), __uint_as_float(a[q * 8 + 5]));
+            pv.w = pack_bf16(__uint_as_float(a[q * 8 + 6]), __uint_as_float(a[q * 8 + 7]));
+            pk.x = pack_bf16(__uint_as_float(g[q * 8 + 0]) * scale, __uint_as_float(g[q * 8 + 1]) * scale);
+            pk.y = pack_bf16(__uint_as_float(g[q * 8 + 2]) * scale, __uint_as_float(g[q * 8 + 3]) * scale);
+            pk.z = pack_bf16(__uint_as_float(g[q * 8 + 4]) * scale, __uint_as_float(g[q * 8 + 5]) * scale);
+            pk.w = pack_bf16(__uint_as_float(g[q * 8 + 6]) * scale, __uint_as_float(g[q * 8 + 7]) * scale);
+            v4[q] = pv; k4[q] = pk;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, C::TM_COLS); }
+}
+
+static int make_map(CUtensorMap* m, const void* base, int B, int L, int H, int D, long long sb, long long sl, long long sh,
+                    int box_rows) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H), static_cast<uint64_t>(L), static_cast<uint64_t>(B)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(sh) * 2, static_cast<uint64_t>(sl) * 2, static_cast<uint64_t>(sb) * 2};
+  const uint32_t box[4] = {64, 1, static_cast<uint32_t>(box_rows), 1};
+  return make_tmap_nd(m, base, 4, dims, strides, box, 2, true);
+}
+
+template <int D, bool CAUSAL>
+static int launch_bwd(const void* dO, const void* q, const void* k, const void* v, const float* lse, const float* delta,
+                      void* dq, void* dk, void* dv, int B, int S, int T, int Hq, int Hkv, const long long* qs,
+                      const long long* ks, const long long* vs, const long long* os, float scale, int* err,
+                      cudaStream_t stream) {
+  // dq shares q's [B,S,Hq,D] contiguous layout, dk / dv are contiguous [B,T,Hkv,D], dO is contiguous [B,S,Hq,D]
+  const long long do_sb = static_cast<long long>(S) * Hq * D, do_ss = static_cast<long long>(Hq) * D, do_sh = D;
+  const long long dkv_sb = static_cast<long long>(T) * Hkv * D, dkv_ss = static_cast<long long>(Hkv) * D, dkv_sh = D;
+  int r;
+  {
+    CUtensorMap tq, tdo, tk, tv;
+    if ((r = make_map(&tq, q, B, S, Hq, D, qs[0], qs[1], qs[2], 128))) return 1000 + r;
+    if ((r = make_map(&tdo, dO, B, S, Hq, D, do_sb, do_ss, do_sh, 128))) return 1100 + r;
+    if ((r = make_map(&tk, k, B, T, Hkv, D, ks[0], ks[1], ks[2], 128))) return 1200 + r;
+    if ((r = make_map(&tv, v, B, T, Hkv, D, vs[0], vs[1], vs[2], 128))) return 1300 + r;
+    auto kern = flash_dq_kernel<D, CAUSAL>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<D>::SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    dim3 grid((S + 127) / 128, Hq, B);
+    kern<<<grid, THREADS, DqCfg<D>::SMEM, stream>>>(tq, tdo, tk, tv, lse, delta, reinterpret_cast<__nv_bfloat16*>(dq), S, T,
+                                                     Hq, Hkv, do_sb, do_ss, do_sh, scale, err);
+    if ((r = static_cast<int>(cudaGetLastError()))) return r;
+  }
+  {
+    CUtensorMap tq, tdo, tk, tv;
+    if ((r = make_map(&tq, q, B, S, Hq, D, qs[0], qs[1], qs[2], 64))) return 2000 + r;
+    if ((r = make_map(&tdo, dO, B, S, Hq, D, do_sb, do_ss, do_sh, 64))) return 2100 + r;
+    if ((r = make_map(&tk, k, B, T, Hkv, D, ks[0], ks[1], ks[2], 128))) return 2200 + r;
+    if ((r = make_map(&tv, v, B, T, Hkv, D, vs[0], vs[1], vs[2], 128))) return 2300 + r;
+    auto kern = flash_dkv_kernel<D, CAUSAL>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<D>::SMEM);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    dim3 grid((T + 127) / 128, Hkv, B);
+    kern<<<grid, THREADS, DkvCfg<D>::SMEM, stream>>>(tq, tdo, tk, tv, lse, delta, reinterpret_cast<__nv_bfloat16*>(dk),
+                                                      reinterpret_cast<__nv_bfloat16*>(dv), S, T, Hq, Hkv, dkv_sb, dkv_ss,
+                                                      dkv_sh, dkv_sb, dkv_ss, dkv_sh, scale, err);
+    if ((r = static_cast<int>(cudaGetLastError()))) return r;
+  }
+  return 0;
+}
+
+}  // namespace flashbwd
+}  // namespace dewb
+
+// dO, dq: contiguous [B,S,Hq,D]; dk, dv: contiguous [B,T,Hkv,D]; q / k / v / out carry their own (batch, sequence,
+// head) element strides; lse [B,Hq,S] from the forward; delta [B,Hq,S] is scratch this call fills.
+extern "C" int dewb_flash_bwd(const void* dO, const void* q, const void* k, const void* v, const void* out,
+                              const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int T, int Hq,
+                              int Hkv, int D, long long q_sb, long long q_ss, long long q_sh, long long k_sb,
+                              long long k_ss, long long k_sh, long long v_sb, long long v_ss, long long v_sh,
+                              long long o_sb, long long o_ss, long long o_sh, float scale, int causal, int* err,
+                              void* stream_ptr) {
+  using namespace dewb::flashbwd;
+  if ((D != 128 && D != 64) || Hq % Hkv != 0) return -3;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  const long long rows = static_cast<long long>(B) * S * Hq;
+  delta_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dO), reinterpret_cast<const __nv_bfloat16*>(out), delta, B, S, Hq, D,
+      static_cast<long long>(S) * Hq * D, static_cast<long long>(Hq) * D, D, o_sb, o_ss, o_sh);
+  const long long qs[3] = {q_sb, q_ss, q_sh}, ks[3] = {k_sb, k_ss, k_sh}, vs[3] = {v_sb, v_ss, v_sh}, os[3] = {o_sb, o_ss, o_sh};
+  if (D == 128)
+    return causal ? launch_bwd<128, true>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, scale, err, stream)
+                  : launch_bwd<128, false>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, scale, err, stream);
+  return causal ? launch_bwd<64, true>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, scale, err, stream)
+                : launch_bwd<64, false>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, scale, err, stream);
+}

@@ -1,0 +1,327 @@
+// Flash attention forward for sm_100a (head_dim 128 or 64, bf16, causal or full, GQA).
+//
+// One CTA per (query tile of 128 rows, query head, batch); 192 threads:
+//   warps 0..3  softmax      : one thread per query row; tcgen05.ld the 128 scores of the row, online softmax in
+//                              the log2 domain, write P (bf16) into shared memory in the 128-byte-swizzled layout
+//   warp 4      TMA producer : Q once, then K and V tiles into 2-stage rings (cp.async.bulk.tensor, no multicast)
+//   warp 5      MMA issuer   : S = Q K^T into one of two TMEM score buffers (so the next tile's scores are computed
+//                              while this tile's softmax runs), then O += P V into the TMEM output accumulator
+// The running maximum is applied lazily: O and l are rescaled only when a row's maximum has grown by more than 2^8
+// since the last rescale, so the TMEM read-modify-write of O is rare.
+//
+// Replaces the reference's attention template forward (src/dew/nn/kernels/templates/attention_mosaic_forward.py) and
+// the vendored FlashAttention wheels, which carry no sm_100 code (kernels/flash_attn/CMakeLists.txt:16,57).
+#include "../common/ptx.cuh"
+#include "../common/tmap.h"
+
+namespace dewb {
+namespace flash {
+
+constexpr int BM = 128;        // query rows per CTA
+constexpr int BN = 128;        // keys per tile
+constexpr int THREADS = 192;
+constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
+
+template <int D>
+struct Cfg {
+  static constexpr int SUB = D / 64;                 // 64-column (128-byte) sub-tiles per row
+  static constexpr int Q_BYTES = BM * D * 2;
+  static constexpr int KV_BYTES = BN * D * 2;
+  static constexpr int P_BYTES = BM * BN * 2;
+  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256;
+  static constexpr int TMEM_S0 = 0, TMEM_S1 = 128, TMEM_O = 256, TMEM_COLS = 512;
+};
+
+struct Bars {
+  uint64_t q_full;
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t s_full[2], s_empty[2];
+  uint64_t p_full, pv_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                 const __grid_constant__ CUtensorMap tv, __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
+                 int S, int T, int Hq, int Hkv, long long o_stride_b, long long o_stride_s, long long o_stride_h,
+                 float scale_log2, int* __restrict__ err) {
+  using C = Cfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  {
+    // An earlier launch reported a timed-out wait: leave at once instead of queueing more waits behind it. One
+    // thread reads the status so the whole CTA takes the same branch.
+    __shared__ int poisoned;
+    if (threadIdx.x == 0) poisoned = *reinterpret_cast<volatile int*>(err);
+    __syncthreads();
+    if (poisoned != 0) return;
+  }
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + C::Q_BYTES;             // 2 stages
+  uint8_t* sV = sK + 2 * C::KV_BYTES;        // 2 stages
+  uint8_t* sP = sV + 2 * C::KV_BYTES;
+  Bars* bars = reinterpret_cast<Bars*>(sP + C::P_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = CAUSAL ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;   // heavy causal tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (Hq / Hkv);
+  const int q0 = qt * BM;
+  // keys visible to this query tile: causal alignment is bottom-right (query i sees keys <= i + T - S)
+  const int n_tiles = CAUSAL ? min((q0 + BM + (T - S) + BN - 1) / BN, (T + BN - 1) / BN) : (T + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1);
+      mbar_init(&bars->v_full[i], 1); mbar_init(&bars->v_empty[i], 1);
+      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_empty[i], 4);
+    }
+    mbar_init(&bars->p_full, 4);
+    mbar_init(&bars->pv_done, 1);
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 5) { tmem_alloc(&bars->tmem_base, C::TMEM_COLS); tmem_relinquish(); }
+  if (warp == 4 && lane == 0) { tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&bars->q_full, C::Q_BYTES);
+#pragma unroll
+      for (int t = 0; t < C::SUB; ++t) tma_load_4d(sQ + t * (BM * 128), &tq, &bars->q_full, t * 64, h, q0, b);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars->k_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); ok = false; break; }
+        mbar_expect_tx(&bars->k_full[st], C::KV_BYTES);
+#pragma unroll
+        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sK + st * C::KV_BYTES + t * (BN * 128), &tk, &bars->k_full[st], t * 64, hk, j * BN, b);
+        if (!mbar_wait(&bars->v_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); ok = false; break; }
+        mbar_expect_tx(&bars->v_full[st], C::KV_BYTES);
+#pragma unroll
+        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sV + st * C::KV_BYTES + t * (BN * 128), &tv, &bars->v_full[st], t * 64, hk, j * BN, b);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc(BM, BN, 1, 1, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc(BM, D, 1, 1, 0, 1);
+      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
+      if (!ok) atomicCAS(err, 0, ERR_WAIT_FULL);
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars->k_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
+        if (!mbar_wait(&bars->s_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * C::KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + (st ? C::TMEM_S1 : C::TMEM_S0), make_sdesc_sw128(qa + off, 16, 1024),
+                       make_sdesc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->k_empty[st]);
+        umma_commit(&bars->s_full[st]);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) { ok = issue_qk(j + 1); if (!ok) break; }
+        const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars->p_full, j & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+        if (!mbar_wait(&bars->v_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); ok = false; break; }
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + st * C::KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint32_t aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + C::TMEM_O, make_sdesc_sw128(pa + aoff, 16, 1024),
+                       make_sdesc_sw128(va + kk * 2048, BN * 128, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&bars->v_empty[st]);
+        umma_commit(&bars->pv_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue (warps 0..3)
+    const int r = warp * 32 + lane;                  // query row within the tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&bars->s_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
+      tc_fence_after();
+      float s[BN];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TMEM_S1 : C::TMEM_S0) + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]) * scale_log2;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_empty[st]);   // the score buffer may be overwritten by tile j + 2
+      const int k0 = j * BN;
+      const int limit = CAUSAL ? (q0 + r + (T - S)) : (T - 1);   // last visible key index for this row
+      if (k0 + BN - 1 > limit || k0 + BN > T) {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) if (k0 + i > limit || k0 + i >= T) s[i] = -INFINITY;
+      }
+      float mt = s[0];
+#pragma unroll
+      for (int i = 1; i < BN; ++i) mt = fmaxf(mt, s[i]);
+      const float m_new = fmaxf(m_used, mt);
+      const bool need = (m_new - m_used > RESCALE_THRESHOLD) || (m_used == -INFINITY && m_new > -INFINITY);
+      const bool any_need = __any_sync(0xffffffffu, need);
+      // PV(j-1) must be complete before P is overwritten or O is rescaled
+      if (j > 0) {
+        if (!mbar_wait(&bars->pv_done, (j - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+        tc_fence_after();
+      }
+      if (any_need) {
+        const float alpha = (need && m_used > -INFINITY) ? exp2f(m_used - m_new) : 1.f;
+        if (need) { m_used = m_new; l *= alpha; }
+        if (j > 0) {
+#pragma unroll
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t v[16];
+            tmem_ld_32x32b_x16(tmem + lane_addr + C::TMEM_O + c * 16, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32b_x16(tmem + lane_addr + C::TMEM_O + c * 16, v);
+          }
+          tmem_st_wait();
+        }
+      }
+      // P = exp2(s - m_used) -> bf16, swizzled into shared memory as the A operand of the PV product
+      const float mu = (m_used == -INFINITY) ? 0.f : m_used;
+      float rowsum = 0.f;
+#pragma unroll
+      for (int c16 = 0; c16 < BN / 8; ++c16) {
+        float p[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { p[i] = exp2f(s[c16 * 8 + i] - mu); }
+        uint4 pk;
+        pk.x = pack_bf16(p[0], p[1]); pk.y = pack_bf16(p[2], p[3]); pk.z = pack_bf16(p[4], p[5]); pk.w = pack_bf16(p[6], p[7]);
+        // sum what the tensor core will see (the bf16-rounded values), so rows of P / l sum to one
+        rowsum += bf16_lo(pk.x) + bf16_hi(pk.x) + bf16_lo(pk.y) + bf16_hi(pk.y) + bf16_lo(pk.z) + bf16_hi(pk.z) +
+                  bf16_lo(pk.w) + bf16_hi(pk.w);
+        const int t = c16 >> 3, c = c16 & 7;
+        *reinterpret_cast<uint4*>(sP + t * (BM * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = pk;
+      }
+      l += rowsum;
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_full);
+    }
+    // epilogue: O / l -> bf16, lse
+    if (ok && n_tiles > 0) {
+      if (!mbar_wait(&bars->pv_done, (n_tiles - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int row = q0 + r;
+      __nv_bfloat16* orow = out + b * o_stride_b + static_cast<long long>(row) * o_stride_s + h * o_stride_h;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        if (n_tiles > 0) { tmem_ld_32x32b_x32(tmem + lane_addr + C::TMEM_O + c * 32, v); tmem_ld_wait(); }
+        else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0;
+        }
+        if (row < S) {
+          uint4* o4 = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 pk;
+            pk.x = pack_bf16(__uint_as_float(v[q * 8 + 0]) * inv, __uint_as_float(v[q * 8 + 1]) * inv);
+            pk.y = pack_bf16(__uint_as_float(v[q * 8 + 2]) * inv, __uint_as_float(v[q * 8 + 3]) * inv);
+            pk.z = pack_bf16(__uint_as_float(v[q * 8 + 4]) * inv, __uint_as_float(v[q * 8 + 5]) * inv);
+            pk.w = pack_bf16(__uint_as_float(v[q * 8 + 6]) * inv, __uint_as_float(v[q * 8 + 7]) * inv);
+            o4[q] = pk;
+          }
+        }
+      }
+      if (row < S && lse != nullptr)
+        lse[(static_cast<long long>(b) * Hq + h) * S + row] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, C::TMEM_COLS);
+  }
+}
+
+template <int D, bool CAUSAL>
+static int launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* out, float* lse, int B,
+                  int S, int T, int Hq, int Hkv, long long osb, long long oss, long long osh, float scale_log2, int* err,
+                  cudaStream_t stream) {
+  auto kern = flash_fwd_kernel<D, CAUSAL>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 grid((S + BM - 1) / BM, Hq, B);
+  kern<<<grid, THREADS, Cfg<D>::SMEM, stream>>>(tq, tk, tv, reinterpret_cast<__nv_bfloat16*>(out), lse, S, T, Hq, Hkv,
+                                                 osb, oss, osh, scale_log2, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// A [B, L, H, D] bf16 tensor with element strides (sb, sl, sh) and unit stride along D, tiled [128 rows x 64 cols].
+static int make_qkv_map(CUtensorMap* m, const void* base, int B, int L, int H, int D, long long sb, long long sl,
+                        long long sh) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(H), static_cast<uint64_t>(L),
+                            static_cast<uint64_t>(B)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(sh) * 2, static_cast<uint64_t>(sl) * 2, static_cast<uint64_t>(sb) * 2};
+  const uint32_t box[4] = {64, 1, 128, 1};
+  return make_tmap_nd(m, base, 4, dims, strides, box, 2, true);
+}
+
+}  // namespace flash
+}  // namespace dewb
+
+// q [B,S,Hq,D], k/v [B,T,Hkv,D] (bf16, unit stride along D, other strides in elements: batch, sequence, head);
+// out [B,S,Hq,D] with its own strides; lse [B,Hq,S] fp32 (natural log), may be null.
+extern "C" int dewb_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int T,
+                              int Hq, int Hkv, int D, long long q_sb, long long q_ss, long long q_sh, long long k_sb,
+                              long long k_ss, long long k_sh, long long v_sb, long long v_ss, long long v_sh,
+                              long long o_sb, long long o_ss, long long o_sh, float scale, int causal, int* err,
+                              void* stream_ptr) {
+  using namespace dewb::flash;
+  if (D != 128 && D != 64) return -3;
+  if (Hq % Hkv != 0) return -3;
+  if ((q_ss % 8) || (q_sh % 8) || (q_sb % 8) || (k_ss % 8) || (k_sh % 8) || (k_sb % 8) || (v_ss % 8) || (v_sh % 8) ||
+      (v_sb % 8) || (o_ss % 8) || (o_sh % 8) || (o_sb % 8))
+    return -3;
+  CUtensorMap tq, tk, tv;
+  int r;
+  if ((r = make_qkv_map(&tq, q, B, S, Hq, D, q_sb, q_ss, q_sh))) return 1000 + r;
+  if ((r = make_qkv_map(&tk, k, B, T, Hkv, D, k_sb, k_ss, k_sh))) return 2000 + r;
+  if ((r = make_qkv_map(&tv, v, B, T, Hkv, D, v_sb, v_ss, v_sh))) return 3000 + r;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  if (D == 128)
+    return causal ? launch<128, true>(tq, tk, tv, out, lse, B, S, T, Hq, Hkv, o_sb, o_ss, o_sh, scale_log2, err, stream)
+                  : launch<128, false>(tq, tk, tv, out, lse, B, S, T, Hq, Hkv, o_sb, o_ss, o_sh, scale_log2, err, stream);
+  return causal ? launch<64, true>(tq, tk, tv, out, lse, B, S, T, Hq, Hkv, o_sb, o_ss, o_sh, scale_log2, err, stream)
+                : launch<64, false>(tq, tk, tv, out, lse, B, S, T, Hq, Hkv, o_sb, o_ss, o_sh, scale_log2, err, stream);
+}

@@ -40,6 +40,33 @@ struct Shared {
   int abort_flag;
 };
 
+// Grouped operation (mixture-of-experts): rows of A are sorted by group and every group's row range starts on a
+// multiple of 128 (padding rows are zero), so an output tile never straddles two groups and a reduction tail never
+// reads another group's rows.
+//   mode 0  dense
+//   mode 1  grouped rows      D[rows of g] = A[rows of g] * B_g^T   (forward and input gradient); B stacks the
+//           groups along its row dimension, `b_rows_per_group` rows each; `tile_group[m_tile]` names the group of
+//           each 128-row tile (< 0: the tile holds no rows)
+//   mode 2  grouped reduction D_g = A[rows of g]^T-style product over the rows of g (weight gradient); the reduction
+//           runs over rows [group_offsets[g], group_offsets[g+1]) and D stacks the groups, `d_group_stride` apart
+struct GroupArgs {
+  const int* tile_group;
+  const int* group_offsets;
+  int mode;
+  int b_rows_per_group;
+  int groups;
+  long long d_group_stride;
+};
+
+struct Tile {
+  int m0, n0;        // output tile origin (within the group for mode 2)
+  int b_row0;        // row offset added to B's stacked-row coordinate (mode 1)
+  int k_begin;       // first reduction index
+  int k_iters;       // reduction steps of BK
+  long long d_off;   // element offset of the group's output (mode 2)
+  bool skip;         // nothing to compute and nothing to store
+};
+
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& m_blk, int& n_blk) {
   constexpr int GROUP_M = 8;
   const int per_group = GROUP_M * tiles_n;
@@ -51,11 +78,45 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   n_blk = r / gsize;
 }
 
+__device__ __forceinline__ Tile decode_tile(int t, int tiles_m, int tiles_n, int K, const GroupArgs& ga) {
+  Tile ti;
+  int m_blk, n_blk;
+  ti.b_row0 = 0; ti.k_begin = 0; ti.k_iters = (K + BK - 1) / BK; ti.d_off = 0; ti.skip = false;
+  if (ga.mode == 2) {
+    const int per = tiles_m * tiles_n;
+    const int g = t / per;
+    tile_coords(t - g * per, tiles_m, tiles_n, m_blk, n_blk);
+    const int r0 = ga.group_offsets[g], r1 = ga.group_offsets[g + 1];
+    ti.k_begin = r0;
+    ti.k_iters = (r1 - r0 + BK - 1) / BK;
+    ti.d_off = static_cast<long long>(g) * ga.d_group_stride;
+  } else {
+    tile_coords(t, tiles_m, tiles_n, m_blk, n_blk);
+    if (ga.mode == 1) {
+      const int g = ga.tile_group[m_blk];
+      ti.skip = g < 0;
+      ti.b_row0 = (g < 0 ? 0 : g) * ga.b_rows_per_group;
+    }
+  }
+  ti.m0 = m_blk * BM;
+  ti.n0 = n_blk * BN;
+  return ti;
+}
+
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 void* __restrict__ Dptr, int M, int N, int K, long long ldd, float alpha, int* __restrict__ err) {
+                 void* __restrict__ Dptr, int M, int N, int K, long long ldd, float alpha, const GroupArgs ga,
+                 int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
+  {
+    // An earlier launch reported a timed-out wait: leave at once instead of queueing more waits behind it. One
+    // thread reads the status so the whole CTA takes the same branch.
+    __shared__ int poisoned;
+    if (threadIdx.x == 0) poisoned = *reinterpret_cast<volatile int*>(err);
+    __syncthreads();
+    if (poisoned != 0) return;
+  }
   // 1024-byte alignment: required by the 128-byte swizzle atoms the descriptors assume (base_offset = 0)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Shared* sh = reinterpret_cast<Shared*>(smem + STAGES * STAGE_BYTES);
@@ -64,8 +125,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM;
   const int tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
-  const int k_iters = (K + BK - 1) / BK;
+  const int num_tiles = tiles_m * tiles_n * (ga.mode == 2 ? ga.groups : 1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&sh->full[s], 1); mbar_init(&sh->empty[s], 1); }
@@ -92,14 +152,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       long long issued = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int m_blk, n_blk; tile_coords(t, tiles_m, tiles_n, m_blk, n_blk);
-        const int m0 = m_blk * BM, n0 = n_blk * BN;
-        for (int k = 0; k < k_iters; ++k) {
+        const Tile ti = decode_tile(t, tiles_m, tiles_n, K, ga);
+        if (ti.skip || ti.k_iters == 0) continue;
+        const int m0 = ti.m0, n0 = ti.n0;
+        for (int k = 0; k < ti.k_iters; ++k) {
           if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); ok = false; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           mbar_expect_tx(&sh->full[stage], STAGE_BYTES);
-          const int k0 = k * BK;
+          const int k0 = ti.k_begin + k * BK;
           if (!A_MN) {
             tma_load_2d(sa, &tma_a, &sh->full[stage], k0, m0);
           } else {
@@ -107,10 +168,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tma_a, &sh->full[stage], m0 + j * 64, k0);
           }
           if (!B_MN) {
-            tma_load_2d(sb, &tma_b, &sh->full[stage], k0, n0);
+            tma_load_2d(sb, &tma_b, &sh->full[stage], k0, ti.b_row0 + n0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tma_b, &sh->full[stage], n0 + j * 64, k0);
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tma_b, &sh->full[stage], n0 + j * 64, ti.b_row0 + k0);
           }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -134,6 +195,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const Tile ti = decode_tile(t, tiles_m, tiles_n, K, ga);
+        if (ti.skip || ti.k_iters == 0) continue;
+        const int k_iters = ti.k_iters;
         if (!mbar_wait(&sh->tmem_empty[acc], acc_phase ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
@@ -162,9 +226,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      int m_blk, n_blk; tile_coords(t, tiles_m, tiles_n, m_blk, n_blk);
-      const int row = m_blk * BM + q * 32 + lane;
-      const int n0 = n_blk * BN;
+      const Tile ti = decode_tile(t, tiles_m, tiles_n, K, ga);
+      if (ti.skip) continue;
+      const int row = ti.m0 + q * 32 + lane;
+      const int n0 = ti.n0;
+      if (ti.k_iters == 0) {
+        // an empty group: its product is zero (nothing to add when accumulating)
+        if ((EPI == EPI_BF16 || EPI == EPI_F32) && row < M) {
+          for (int c = 0; c < BN && n0 + c < N; ++c) {
+            if (EPI == EPI_BF16) reinterpret_cast<__nv_bfloat16*>(Dptr)[ti.d_off + static_cast<long long>(row) * ldd + n0 + c] = __float2bfloat16(0.f);
+            else reinterpret_cast<float*>(Dptr)[ti.d_off + static_cast<long long>(row) * ldd + n0 + c] = 0.f;
+          }
+        }
+        continue;
+      }
       if (!mbar_wait(&sh->tmem_full[acc], acc_phase, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * ACC_COLS + (static_cast<uint32_t>(q * 32) << 16);
@@ -177,7 +252,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (row < M && col < N) {
           const bool full = (col + 32 <= N);
           if (EPI == EPI_BF16 || EPI == EPI_BF16_ACC) {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Dptr) + static_cast<long long>(row) * ldd + col;
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Dptr) + ti.d_off + static_cast<long long>(row) * ldd + col;
             if (full && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
               uint4* o4 = reinterpret_cast<uint4*>(out);
 #pragma unroll
@@ -206,7 +281,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               }
             }
           } else {
-            float* out = reinterpret_cast<float*>(Dptr) + static_cast<long long>(row) * ldd + col;
+            float* out = reinterpret_cast<float*>(Dptr) + ti.d_off + static_cast<long long>(row) * ldd + col;
             if (full && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
               float4* o4 = reinterpret_cast<float4*>(out);
 #pragma unroll
@@ -247,7 +322,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
 template <bool A_MN, bool B_MN, int EPI>
 static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, void* D, int M, int N, int K, long long ldd,
-                      float alpha, int* err, int sms, cudaStream_t stream) {
+                      float alpha, const GroupArgs& ga, int* err, int sms, cudaStream_t stream) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI>;
   static bool configured[64] = {};
   int dev = 0;
@@ -257,22 +332,30 @@ static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, void* D, int
     if (e != cudaSuccess) return static_cast<int>(e);
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * (ga.mode == 2 ? ga.groups : 1);
   const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, D, M, N, K, ldd, alpha, err);
+  kern<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, D, M, N, K, ldd, alpha, ga, err);
   return static_cast<int>(cudaGetLastError());
 }
 
 template <bool A_MN, bool B_MN>
 static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, void* D, int M, int N, int K,
-                      long long ldd, float alpha, int* err, int sms, cudaStream_t stream) {
+                      long long ldd, float alpha, const GroupArgs& ga, int* err, int sms, cudaStream_t stream) {
   switch (epi) {
-    case EPI_BF16: return launch_one<A_MN, B_MN, EPI_BF16>(ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
-    case EPI_F32: return launch_one<A_MN, B_MN, EPI_F32>(ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
-    case EPI_F32_ACC: return launch_one<A_MN, B_MN, EPI_F32_ACC>(ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
-    case EPI_BF16_ACC: return launch_one<A_MN, B_MN, EPI_BF16_ACC>(ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
+    case EPI_BF16: return launch_one<A_MN, B_MN, EPI_BF16>(ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
+    case EPI_F32: return launch_one<A_MN, B_MN, EPI_F32>(ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
+    case EPI_F32_ACC: return launch_one<A_MN, B_MN, EPI_F32_ACC>(ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
+    case EPI_BF16_ACC: return launch_one<A_MN, B_MN, EPI_BF16_ACC>(ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
   }
   return -2;
+}
+
+static int dispatch(int a_mn, int b_mn, int epi, const CUtensorMap& ta, const CUtensorMap& tb, void* D, int M, int N,
+                    int K, long long ldd, float alpha, const GroupArgs& ga, int* err, int sms, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch_epi<false, false>(epi, ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
+  if (!a_mn && b_mn) return launch_epi<false, true>(epi, ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
+  if (a_mn && !b_mn) return launch_epi<true, false>(epi, ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
+  return launch_epi<true, true>(epi, ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
 }
 
 }  // namespace gemm
@@ -316,8 +399,51 @@ extern "C" int dewb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
   if (r) return 2000 + r;
   int sms = sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-  if (!a_mn && !b_mn) return launch_epi<false, false>(epi, ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
-  if (!a_mn && b_mn) return launch_epi<false, true>(epi, ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
-  if (a_mn && !b_mn) return launch_epi<true, false>(epi, ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
-  return launch_epi<true, true>(epi, ta, tb, D, M, N, K, ldd, alpha, err, sms, stream);
+  GroupArgs ga{nullptr, nullptr, 0, 0, 1, 0};
+  return dispatch(a_mn, b_mn, epi, ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
+}
+
+// Grouped rows (mixture-of-experts forward and input gradient):
+//   D[M, N] rows of group g = A[rows of g, K] * B_g^T, with B the groups stacked along rows:
+//     b_mn = 0: B is [G * N, K] (each group [N, K], K contiguous)     - forward with weights [G, N, K]
+//     b_mn = 1: B is [G * K, N] (each group [K, N], N contiguous)     - input gradient with weights [G, K(red), N]
+//   tile_group[ceil(M / 128)]: group id of each 128-row tile of A (group row ranges start on multiples of 128)
+extern "C" int dewb_gmm_bf16(const void* A, const void* B, void* D, const int* tile_group, int M, int N, int K,
+                             int groups, long long lda, long long ldb, long long ldd, int b_mn, int epi, float alpha,
+                             int* err, void* stream_ptr) {
+  using namespace dewb;
+  using namespace dewb::gemm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  if (b_mn && (K % BK)) return -4;      // a reduction tail would read the next group's rows
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  CUtensorMap ta, tb;
+  int r = make_tmap_2d(&ta, A, M, K, lda, BM, BK, 2, true);
+  if (r) return 1000 + r;
+  if (!b_mn) r = make_tmap_2d(&tb, B, static_cast<uint64_t>(groups) * N, K, ldb, BN, BK, 2, true);
+  else       r = make_tmap_2d(&tb, B, static_cast<uint64_t>(groups) * K, N, ldb, BK, 64, 2, true);
+  if (r) return 2000 + r;
+  GroupArgs ga{tile_group, nullptr, 1, b_mn ? K : N, groups, 0};
+  return dispatch(0, b_mn, epi, ta, tb, D, M, N, K, ldd, alpha, ga, err, sm_count(), stream);
+}
+
+// Grouped reduction (mixture-of-experts weight gradient): for every group g,
+//   D_g[M, N] (+)= A[rows of g, M]^T * B[rows of g, N]   with A stored [R, M] and B stored [R, N] (R = all rows),
+//   rows of g = [group_offsets[g], group_offsets[g + 1]) (multiples of 64; padding rows are zero)
+//   D stacks the groups: D_g = D + g * d_group_stride, row stride ldd.
+extern "C" int dewb_tgmm_bf16(const void* A, const void* B, void* D, const int* group_offsets, int R, int M, int N,
+                              int groups, long long lda, long long ldb, long long ldd, long long d_group_stride, int epi,
+                              float alpha, int* err, void* stream_ptr) {
+  using namespace dewb;
+  using namespace dewb::gemm;
+  if (R <= 0 || M <= 0 || N <= 0 || groups <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  CUtensorMap ta, tb;
+  int r = make_tmap_2d(&ta, A, R, M, lda, BK, 64, 2, true);
+  if (r) return 1000 + r;
+  r = make_tmap_2d(&tb, B, R, N, ldb, BK, 64, 2, true);
+  if (r) return 2000 + r;
+  GroupArgs ga{nullptr, group_offsets, 2, 0, groups, d_group_stride};
+  return dispatch(1, 1, epi, ta, tb, D, M, N, R, ldd, alpha, ga, err, sm_count(), stream);
 }

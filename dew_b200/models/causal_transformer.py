@@ -177,6 +177,29 @@ class CausalTransformer(nn.Module):
         h = self.hidden(tokens, positions, segment_ids, cache, train)
         return h if return_hidden else self.logits(h)
 
+    def pop_aux(self) -> Dict[str, Any]:
+        """Collect what the sparse layers recorded in the last forward: the balance loss (a metric and, when the
+        objective weighs it, a loss term) and the aux-loss-free router bias updates (effects written back after the
+        optimizer step; reference: ``load_balance_update`` src/dew/nn/moe.py:271)."""
+        from ..nn.moe import load_balance_update
+        from ..objectives.base import Ratio
+        losses, effects = [], {}
+        for i, layer in enumerate(self.layers):
+            if not layer.sparse or not layer.mlp.last:
+                continue
+            last = layer.mlp.last
+            losses.append(last["balance_loss"])
+            bias = layer.mlp.router.expert_bias
+            if bias is not None:
+                effects[f"layers.{i}.mlp.router.expert_bias"] = load_balance_update(
+                    bias, last["counts"], self.config.mixture.balance_rate).detach()
+            layer.mlp.last = {}
+        if not losses:
+            return {}
+        bl = torch.stack(losses).mean()
+        one = torch.ones((), device=bl.device)
+        return {"balance_loss": bl, "metrics": {"balance_loss": Ratio(bl.detach(), one)}, "effects": effects}
+
     # ------------------------------------------------------------------ accounting
     def param_count(self, active: bool = False) -> int:
         total = sum(p.numel() for p in self.parameters())

@@ -1,0 +1,125 @@
+"""Mixture-of-experts feed-forward: router, expert-sorted grouped GEMMs, shared experts, aux-loss-free balancing,
+capacity, and expert-parallel exchange.
+
+Capability parity: src/dew/nn/moe.py (``Router`` :316-586: softmax / sigmoid scores, top-k, ``norm_topk_prob``, fp32
+logits, selection-only ``expert_bias``; ``load_balance_update`` :271; ``expert_dispatch`` :858-930 with
+``dispatch='global' | 'exchange'`` and ``capacity_factor``; ``SparseMLP`` :1356-1503 with shared experts and
+``shared_gate``), docs/concepts/moe.md:59-106.  Numerics: router logits and every contraction accumulate in fp32.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Dict, Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..ops import grouped as G
+from .layers import Linear, declare
+from .mlp import SwiGLU
+
+
+class Router(nn.Module):
+    def __init__(self, features: int, mix, dtype=None, device=None):
+        super().__init__()
+        self.mix = mix
+        self.weight = declare(nn.Parameter(torch.empty(mix.experts, features, dtype=dtype, device=device)), ("experts", "embed"), "kernel")
+        self.register_buffer("expert_bias", torch.zeros(mix.experts, dtype=torch.float32, device=device) if mix.bias else None, persistent=True)
+        self.reset_parameters()
+
+    def reset_parameters(self, generator=None):
+        with torch.no_grad():
+            self.weight.normal_(0.0, 1.0 / math.sqrt(self.weight.shape[1]), generator=generator)
+
+    def forward(self, x2: torch.Tensor):
+        """``x2 [T, d]`` -> (weights [T, k] fp32, expert ids [T, k], scores [T, E] fp32)."""
+        mix = self.mix
+        logits = F.linear(x2.float(), self.weight.float())
+        scores = torch.softmax(logits, -1) if mix.score_function == "softmax" else torch.sigmoid(logits)
+        select = scores + self.expert_bias if self.expert_bias is not None else scores     # bias steers selection only
+        _, ids = torch.topk(select, mix.top_k, dim=-1)
+        w = scores.gather(-1, ids)
+        if mix.norm_topk_prob:
+            w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
+        return w * mix.scaling, ids, scores
+
+
+def load_balance_update(bias: torch.Tensor, counts: torch.Tensor, rate: float) -> torch.Tensor:
+    """Aux-loss-free balancing: raise the bias of under-loaded experts, lower over-loaded ones by ``rate``."""
+    mean = counts.float().mean()
+    return bias + rate * torch.sign(mean - counts.float())
+
+
+def capacity_positions(ids: torch.Tensor, experts: int, capacity: int) -> torch.Tensor:
+    """Keep-mask over (token, choice) pairs: a pair is kept if fewer than ``capacity`` earlier pairs chose its expert."""
+    flat = ids.reshape(-1)
+    onehot = F.one_hot(flat, experts)
+    rank = (onehot.cumsum(0) - onehot).gather(1, flat[:, None]).squeeze(1)
+    return (rank < capacity).reshape(ids.shape)
+
+
+class ExpertMLP(nn.Module):
+    """E SwiGLU experts with stacked weights: ``gate_up [E, 2F, d]`` and ``down [E, d, F]``."""
+
+    def __init__(self, features: int, hidden: int, experts: int, init_std: Optional[float] = None, dtype=None, device=None):
+        super().__init__()
+        self.features, self.hidden, self.experts_n = features, hidden, experts
+        self.gate_up = declare(nn.Parameter(torch.empty(experts, 2 * hidden, features, dtype=dtype, device=device)), ("experts", "mlp", "embed"), "expert_kernel")
+        self.down = declare(nn.Parameter(torch.empty(experts, features, hidden, dtype=dtype, device=device)), ("experts", "embed", "mlp"), "expert_kernel")
+        self.init_std = init_std
+        self.reset_parameters()
+
+    def reset_parameters(self, generator=None):
+        with torch.no_grad():
+            self.gate_up.normal_(0.0, self.init_std or 1.0 / math.sqrt(self.features), generator=generator)
+            self.down.normal_(0.0, self.init_std or 1.0 / math.sqrt(self.hidden), generator=generator)
+
+    def param_count_per_expert(self) -> int:
+        return 3 * self.features * self.hidden
+
+    def forward(self, xs: torch.Tensor, layout: G.GroupLayout) -> torch.Tensor:
+        h = G.grouped_linear(xs, self.gate_up, layout)
+        return G.grouped_linear(ops.packed_swiglu(h), self.down, layout)
+
+
+class SparseMLP(nn.Module):
+    def __init__(self, features: int, mix, dense_hidden: int, init_std: Optional[float] = None, dtype=None, device=None):
+        super().__init__()
+        self.mix = mix
+        hidden = mix.expert_features or dense_hidden
+        self.router = Router(features, mix, dtype=torch.float32, device=device)
+        self.experts = ExpertMLP(features, hidden, mix.experts, init_std, dtype=dtype, device=device)
+        self.shared = SwiGLU(features, mix.shared_features, init_std, dtype=dtype, device=device) if mix.shared_features else None
+        self.shared_gate = Linear(features, 1, axes=("embed", None), dtype=dtype, device=device) if (mix.shared_gate and mix.shared_features) else None
+        self.last: Dict[str, Any] = {}
+        self.ep = None            # set by dew_b200.parallel.ep.ExpertParallel when the experts are sharded over ranks
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        mix = self.mix
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        T = x2.shape[0]
+        w, ids, scores = self.router(x2)
+        if mix.capacity_factor is not None:
+            cap = max(int(math.ceil(T * mix.top_k / mix.experts * mix.capacity_factor)), int(mix.capacity_factor))
+            keep = capacity_positions(ids, mix.experts, cap)
+            w = w * keep
+        counts = torch.bincount(ids.reshape(-1), minlength=mix.experts)
+        # balance statistics (Switch-style auxiliary loss value, also the signal for the bias update)
+        frac = counts.float() / max(1, T * mix.top_k)
+        self.last = {"counts": counts, "balance_loss": mix.experts * (frac * scores.mean(0)).sum()}
+        if self.ep is not None:
+            y = self.ep.dispatch_compute_combine(self, x2, w, ids)
+        else:
+            layout = G.group_layout(ids, mix.experts)
+            xs = G.permute(x2, layout, mix.top_k)
+            ys = self.experts(xs, layout)
+            y = G.combine(ys, layout, w.to(x2.dtype) if x2.dtype != torch.float32 else w, T)
+        if self.shared is not None:
+            s = self.shared(x2)
+            if self.shared_gate is not None:
+                s = s * torch.sigmoid(self.shared_gate(x2).float()).to(s.dtype)
+            y = y + s
+        return y.reshape(shape)

@@ -23,6 +23,11 @@ def _flash_available() -> bool:
         return False
 
 
+def _bwd_available() -> bool:
+    from .flash import bwd_available
+    return bwd_available()
+
+
 _ATTN.kernels = [
     Kernel("sm100_flash", [
         Requirement("built", lambda c: _flash_available(), "flash kernels are not in this build of libdewb.so"),
@@ -32,6 +37,8 @@ _ATTN.kernels = [
                     and not c["segments"], "sinks / softcap / window / packed segments take the library arm"),
         Requirement("seq", lambda c: c["S"] == c["T"] and c["S"] % 128 == 0, "needs S == T and S a multiple of 128"),
         Requirement("gqa", lambda c: c["Hq"] % c["Hkv"] == 0, "query heads must be a multiple of kv heads"),
+        Requirement("backward", lambda c: not c["grad"] or _bwd_available(), "the backward kernels are not in this build"),
+        Requirement("layout", lambda c: c["unit_d"], "head_dim must have unit stride"),
     ], receipt="tcgen05 flash forward/backward, csrc/kernels/flash_sm100.cu"),
     Kernel("sdpa", [], receipt="library arm: torch scaled_dot_product_attention (cuDNN / flash)"),
 ]
@@ -51,7 +58,9 @@ def flash_attention(q, k, v, causal=True, scale=None, window=None, softcap=0.0, 
                     kernel: Optional[str] = None):
     B, S, Hq, D = q.shape
     case = dict(dtype=q.dtype, D=D, S=S, T=k.shape[1], Hq=Hq, Hkv=k.shape[2], sinks=sinks is not None,
-                softcap=bool(softcap), window=window, segments=segment_ids is not None, causal=causal)
+                softcap=bool(softcap), window=window, segments=segment_ids is not None, causal=causal,
+                grad=torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad),
+                unit_d=q.stride(3) == 1 and k.stride(3) == 1 and v.stride(3) == 1)
     which = _ATTN.select(case, forced=kernel)
     if which == "sm100_flash":
         from .flash import flash_sm100

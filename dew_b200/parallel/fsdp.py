@@ -91,7 +91,7 @@ class _Boundary(torch.autograd.Function):
 
 class FSDPEngine:
     def __init__(self, trainer, units: Optional[List[Tuple[str, List[nn.Module]]]] = None, group=None,
-                 wait_limit_s: float = 20.0, comm_blocks: int = 48):
+                 wait_limit_s: float = 20.0, comm_blocks: int = 148):
         self.t = trainer
         self.model: nn.Module = trainer.objective.model
         self.group = group

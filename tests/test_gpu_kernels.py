@@ -216,3 +216,80 @@ def test_attention_matches_reference():
     out = ops.attention(q, k, v, causal=True)
     ref = ops.attention_reference(q.float(), k.float(), v.float(), causal=True)
     assert rel_err(out, ref) <= 3 * bf16_floor(ref) + 1e-3
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [(1, 128, 1, 1, 128, True), (2, 256, 8, 2, 128, True), (1, 512, 4, 4, 128, False),
+                                                 (2, 384, 4, 2, 64, True), (1, 1024, 2, 1, 128, True)])
+def test_flash_forward_sm100(B, S, Hq, Hkv, D, causal):
+    from dew_b200.ops.flash import flash_fwd
+    torch.manual_seed(S + D)
+    qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV).to(torch.bfloat16)      # packed projection layout
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    out, lse = flash_fwd(q, k, v, causal, 1.0 / math.sqrt(D))
+    ref = ops.attention_reference(q.float(), k.float(), v.float(), causal=causal)
+    assert rel_err(out, ref) <= 3 * bf16_floor(ref) + 2e-3, rel_err(out, ref)
+    rep = Hq // Hkv
+    s = torch.einsum("bshd,bthd->bhst", q.float(), k.float().repeat_interleave(rep, 2)) / math.sqrt(D)
+    if causal:
+        s = s.masked_fill(~torch.tril(torch.ones(S, S, dtype=torch.bool, device=DEV)), float("-inf"))
+    assert torch.allclose(lse, torch.logsumexp(s, -1), atol=2e-2, rtol=1e-3)
+
+
+def test_flash_forward_large_values_rescale():
+    """Rows whose maximum grows tile after tile exercise the lazy rescale of the TMEM accumulator."""
+    from dew_b200.ops.flash import flash_fwd
+    torch.manual_seed(9)
+    B, S, H, D = 1, 512, 2, 128
+    q = torch.randn(B, S, H, D, device=DEV).to(torch.bfloat16)
+    k = (torch.randn(B, S, H, D, device=DEV) * torch.linspace(0.5, 6.0, S, device=DEV)[None, :, None, None]).to(torch.bfloat16)
+    v = torch.randn(B, S, H, D, device=DEV).to(torch.bfloat16)
+    out, _ = flash_fwd(q, k, v, True, 1.0 / math.sqrt(D))
+    ref = ops.attention_reference(q.float(), k.float(), v.float(), causal=True)
+    assert rel_err(out, ref) <= 3 * bf16_floor(ref) + 2e-3, rel_err(out, ref)
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [(1, 128, 1, 1, 128, True), (2, 256, 4, 2, 128, True), (1, 384, 2, 2, 128, False),
+                                                 (1, 256, 4, 1, 64, True), (1, 1024, 4, 2, 128, True)])
+def test_flash_backward_sm100(B, S, Hq, Hkv, D, causal):
+    torch.manual_seed(S * 3 + D)
+    qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV).to(torch.bfloat16).requires_grad_()
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    out = ops.attention(q, k, v, causal=causal, kernel="sm100_flash")
+    do = torch.randn_like(out)
+    out.backward(do)
+    got = qkv.grad.clone()
+    ref_in = qkv.detach().float().requires_grad_()
+    rq, rk, rv = ref_in[:, :, :Hq], ref_in[:, :, Hq:Hq + Hkv], ref_in[:, :, Hq + Hkv:]
+    ref = ops.attention_reference(rq, rk, rv, causal=causal)
+    ref.backward(do.float())
+    for name, sl in (("dq", slice(0, Hq)), ("dk", slice(Hq, Hq + Hkv)), ("dv", slice(Hq + Hkv, None))):
+        g, r = got[:, :, sl], ref_in.grad[:, :, sl]
+        assert rel_err(g, r) <= 3 * bf16_floor(r) + 1.5e-2, (name, rel_err(g, r))
+
+
+@pytest.mark.parametrize("T,k,E,d,F", [(300, 2, 4, 128, 192), (1000, 6, 16, 256, 128), (64, 2, 8, 64, 64)])
+def test_grouped_gemm_forward_backward(T, k, E, d, F):
+    """tcgen05 grouped GEMMs (expert-sorted, 128-aligned groups) against the per-expert fp32 loop."""
+    from dew_b200.ops import grouped as G
+    torch.manual_seed(T + E)
+    ids = torch.randint(0, E, (T, k), device=DEV)
+    if E > 4:
+        ids[ids == 3] = 2                                     # leave one expert empty
+    layout = G.group_layout(ids, E)
+    x = torch.randn(T, d, device=DEV).to(torch.bfloat16)
+    xs = G.permute(x, layout, k).requires_grad_()
+    w = (torch.randn(E, F, d, device=DEV) / math.sqrt(d)).to(torch.bfloat16).requires_grad_()
+    y = G.grouped_linear(xs, w, layout)
+    dy = torch.randn_like(y)
+    # padding rows carry no gradient in a real layer (combine never reads them)
+    used = torch.zeros(layout.rows, dtype=torch.bool, device=DEV)
+    used[layout.positions] = True
+    dy = dy * used[:, None]
+    y.backward(dy)
+    ref_y = G._gmm_reference(xs.detach(), w.detach(), layout, False)
+    assert rel_err(y[used], ref_y[used].float()) <= 1e-2
+    ref_dx = G._gmm_reference(dy, w.detach(), layout, True)
+    assert rel_err(xs.grad[used], ref_dx[used].float()) <= 1e-2
+    ref_dw = G._tgmm_reference(dy, xs.detach(), layout, E)
+    assert rel_err(w.grad, ref_dw) <= 1e-2
+    assert torch.all(y[~used] == 0)                           # zero rows in, zero rows out
