@@ -89,7 +89,7 @@ def gmm_forward(x, w, layout: GroupLayout, transpose_w: bool = False, out=None):
     M, K = x.shape
     N = w.shape[2] if transpose_w else w.shape[1]
     if out is None:
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        out = torch.zeros((M, N), dtype=torch.bfloat16, device=x.device)    # tiles past the rows in use are skipped
     w2 = w.reshape(G * w.shape[1], w.shape[2])
     rc = L.load().dewb_gmm_bf16(L.ptr(x), L.ptr(w2), L.ptr(out), L.ptr(layout.tile_group), c_int(M), c_int(N), c_int(K),
                                 c_int(G), c_ll(x.stride(0)), c_ll(w2.stride(0)), c_ll(out.stride(0)),

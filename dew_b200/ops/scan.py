@@ -1,0 +1,226 @@
+"""Linear-recurrence ops: gated delta rule (GDN), Mamba-2 SSD, short causal depthwise convolution.
+
+Each op has a step-by-step recurrent form (the fp32 / fp64 oracle and the decode step) and a chunked form
+(chunk 64, WY / UT-transform representation for the delta rule) that turns the scan into dense chunk products -
+those products are what runs on the tensor cores on a GPU.
+
+Semantics follow the reference: ``S' = (I - beta k k^T) Gamma S + beta k v^T ; o = S'^T q`` with
+``g = -exp(A_log) softplus(a + dt_bias)``, ``beta = sigmoid(b)``, l2-normalised q, k, fp32 state
+(src/dew/nn/linear.py:1107-1408; src/dew/nn/kernels/recurrence.py:251-329); Mamba-2: decay
+``exp(min(acs_i - acs_j, 0))``, fp32 accumulation (src/dew/nn/kernels/mamba_ssd.py:9-22).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+CHUNK_SIZE = 64
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# gated delta rule
+
+
+def gated_delta_rule_recurrent(q, k, v, g, beta, initial_state=None, scale: Optional[float] = None):
+    """Step-by-step oracle. q,k ``[B,T,H,Dk]``, v ``[B,T,H,Dv]``, g / beta ``[B,T,H]`` -> (o ``[B,T,H,Dv]``, state ``[B,H,Dk,Dv]``)."""
+    B, T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    dt = torch.float64 if q.dtype == torch.float64 else torch.float32
+    scale = scale if scale is not None else Dk ** -0.5
+    S = torch.zeros(B, H, Dk, Dv, dtype=dt, device=q.device) if initial_state is None else initial_state.to(dt).clone()
+    out = torch.empty(B, T, H, Dv, dtype=dt, device=q.device)
+    qf, kf, vf, gf, bf = (x.to(dt) for x in (q, k, v, g, beta))
+    for t in range(T):
+        S = S * torch.exp(gf[:, t])[..., None, None]
+        kt, vt = kf[:, t], vf[:, t]
+        pred = torch.einsum("bhkv,bhk->bhv", S, kt)
+        S = S + torch.einsum("bhk,bhv->bhkv", kt * bf[:, t][..., None], vt - pred)
+        out[:, t] = torch.einsum("bhkv,bhk->bhv", S, qf[:, t] * scale)
+    return out.to(v.dtype), S
+
+
+def gated_delta_rule_step(q, k, v, g, beta, state, scale: Optional[float] = None):
+    """One decode step: q,k ``[B,H,Dk]``, v ``[B,H,Dv]``, g / beta ``[B,H]``, state ``[B,H,Dk,Dv]`` (fp32, updated in place)."""
+    scale = scale if scale is not None else q.shape[-1] ** -0.5
+    state.mul_(torch.exp(g.float())[..., None, None])
+    pred = torch.einsum("bhkv,bhk->bhv", state, k.float())
+    state.add_(torch.einsum("bhk,bhv->bhkv", k.float() * beta.float()[..., None], v.float() - pred))
+    return torch.einsum("bhkv,bhk->bhv", state, q.float() * scale).to(v.dtype)
+
+
+def gated_delta_rule_chunked(q, k, v, g, beta, initial_state=None, scale: Optional[float] = None, chunk: int = CHUNK_SIZE):
+    """Chunked form (WY representation): per chunk, solve ``(I + A) W = beta K`` by forward substitution, then pass the
+    state between chunks.  Differentiable; the dense chunk products dominate the cost."""
+    B, T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    scale = scale if scale is not None else Dk ** -0.5
+    pad = (-T) % chunk
+    f32 = torch.float32 if q.dtype != torch.float64 else torch.float64
+    qf, kf, vf = (x.to(f32).transpose(1, 2) for x in (q, k, v))              # [B,H,T,D]
+    gf, bf = g.to(f32).transpose(1, 2), beta.to(f32).transpose(1, 2)          # [B,H,T]
+    if pad:
+        qf, kf, vf = (F.pad(x, (0, 0, 0, pad)) for x in (qf, kf, vf))
+        gf, bf = F.pad(gf, (0, pad)), F.pad(bf, (0, pad))
+    N = (T + pad) // chunk
+    qf = qf * scale
+    vb = vf * bf[..., None]
+    kb = kf * bf[..., None]
+    rs = lambda x: x.reshape(B, H, N, chunk, *x.shape[3:])
+    qc, kc, vc, kbc, gc = rs(qf), rs(kf), rs(vb), rs(kb), gf.reshape(B, H, N, chunk)
+    gc = gc.cumsum(-1)
+    diff = gc[..., :, None] - gc[..., None, :]
+    tril = torch.tril(torch.ones(chunk, chunk, dtype=torch.bool, device=q.device))
+    L = torch.where(tril, torch.exp(torch.where(tril, diff, torch.zeros_like(diff))), torch.zeros_like(diff))
+    strict = torch.tril(torch.ones(chunk, chunk, dtype=torch.bool, device=q.device), -1)
+    A = -(kbc @ kc.transpose(-1, -2)) * L
+    A = torch.where(strict, A, torch.zeros_like(A))
+    # (I - A)^{-1} by forward substitution, row by row (64 small steps; a 16x16-blocked solve on the GPU kernel)
+    rows = [A[..., 0, :]]
+    for i in range(1, chunk):
+        prev = torch.stack(rows, -2)                                           # [..., i, C]
+        rows.append(A[..., i, :] + (A[..., i, :i, None] * prev[..., :i, :]).sum(-2))
+    Tm = torch.stack(rows, -2) + torch.eye(chunk, dtype=f32, device=q.device)
+    U = Tm @ vc                                                                # [B,H,N,C,Dv]
+    Wm = Tm @ (kbc * torch.exp(gc)[..., None])                                 # [B,H,N,C,Dk]
+    S = torch.zeros(B, H, Dk, Dv, dtype=f32, device=q.device) if initial_state is None else initial_state.to(f32)
+    outs = []
+    for n in range(N):
+        qi, ki, gi = qc[:, :, n], kc[:, :, n], gc[:, :, n]
+        attn = torch.where(tril, (qi @ ki.transpose(-1, -2)) * L[:, :, n], torch.zeros_like(L[:, :, n]))
+        v_new = U[:, :, n] - Wm[:, :, n] @ S
+        o = (qi * torch.exp(gi)[..., None]) @ S + attn @ v_new
+        outs.append(o)
+        glast = gi[..., -1]
+        S = S * torch.exp(glast)[..., None, None] + (ki * torch.exp(glast[..., None] - gi)[..., None]).transpose(-1, -2) @ v_new
+    o = torch.stack(outs, 2).reshape(B, H, N * chunk, Dv)[:, :, :T]
+    return o.transpose(1, 2).to(v.dtype), S
+
+
+def chunk_gated_delta_rule(q, k, v, g, beta, initial_state=None, scale=None, chunk: int = CHUNK_SIZE):
+    """Public entry: chunked on any device (dense chunk products on the GPU run through cuBLAS batched GEMMs until the
+    tcgen05 chunk kernel takes them)."""
+    return gated_delta_rule_chunked(q, k, v, g, beta, initial_state, scale, chunk)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Mamba-2 SSD
+
+
+def ssd_recurrent(x, dt, A, Bm, Cm, D=None, initial_state=None):
+    """Oracle. x ``[B,T,H,P]``, dt ``[B,T,H]`` (after softplus), A ``[H]`` (negative), B / C ``[B,T,G,N]`` (G groups) ->
+    (y ``[B,T,H,P]``, state ``[B,H,P,N]``)."""
+    Bsz, T, H, P = x.shape
+    G, N = Bm.shape[2], Bm.shape[3]
+    rep = H // G
+    f = torch.float64 if x.dtype == torch.float64 else torch.float32
+    S = torch.zeros(Bsz, H, P, N, dtype=f, device=x.device) if initial_state is None else initial_state.to(f).clone()
+    y = torch.empty(Bsz, T, H, P, dtype=f, device=x.device)
+    xf, dtf, Bf, Cf = x.to(f), dt.to(f), Bm.to(f).repeat_interleave(rep, 2), Cm.to(f).repeat_interleave(rep, 2)
+    for t in range(T):
+        dA = torch.exp(dtf[:, t] * A.to(f))                                   # [B,H]
+        S = S * dA[..., None, None] + torch.einsum("bhp,bhn->bhpn", xf[:, t] * dtf[:, t][..., None], Bf[:, t])
+        y[:, t] = torch.einsum("bhpn,bhn->bhp", S, Cf[:, t])
+    if D is not None:
+        y = y + xf * D.to(f)[None, None, :, None]
+    return y.to(x.dtype), S
+
+
+def ssd_chunked(x, dt, A, Bm, Cm, D=None, initial_state=None, chunk: int = CHUNK_SIZE):
+    """Chunked SSD: intra-chunk ``(C B^T o decay) X`` plus a chunk-state pass; fp32 accumulation."""
+    Bsz, T, H, P = x.shape
+    G, N = Bm.shape[2], Bm.shape[3]
+    rep = H // G
+    f = torch.float32 if x.dtype != torch.float64 else torch.float64
+    pad = (-T) % chunk
+    xf, dtf = x.to(f), dt.to(f)
+    Bf, Cf = Bm.to(f).repeat_interleave(rep, 2), Cm.to(f).repeat_interleave(rep, 2)
+    if pad:
+        xf, Bf, Cf = (F.pad(t_, (0, 0, 0, 0, 0, pad)) for t_ in (xf, Bf, Cf))
+        dtf = F.pad(dtf, (0, 0, 0, pad))
+    Nc = (T + pad) // chunk
+    rs = lambda t_: t_.reshape(Bsz, Nc, chunk, *t_.shape[2:])
+    xc, Bc, Cc, dtc = rs(xf), rs(Bf), rs(Cf), rs(dtf)                          # [B,Nc,C,H,...]
+    a = dtc * A.to(f)                                                          # [B,Nc,C,H] log decay per step
+    acs = a.cumsum(2)
+    diff = acs[:, :, :, None, :] - acs[:, :, None, :, :]                       # [B,Nc,C(i),C(j),H]
+    tril = torch.tril(torch.ones(chunk, chunk, dtype=torch.bool, device=x.device))[None, None, :, :, None]
+    Lm = torch.where(tril, torch.exp(torch.clamp(diff, max=0.0)), torch.zeros_like(diff))
+    xdt = xc * dtc[..., None]
+    CB = torch.einsum("bcihn,bcjhn->bcijh", Cc, Bc)
+    y_diag = torch.einsum("bcijh,bcjhp->bcihp", CB * Lm, xdt)
+    decay_to_end = torch.exp(acs[:, :, -1:, :] - acs)                          # [B,Nc,C,H]
+    states = torch.einsum("bcjhn,bcjh,bcjhp->bchpn", Bc, decay_to_end, xdt)    # contribution of each chunk
+    S = torch.zeros(Bsz, H, P, N, dtype=f, device=x.device) if initial_state is None else initial_state.to(f)
+    ys = []
+    for c in range(Nc):
+        y_off = torch.einsum("bihn,bhpn,bih->bihp", Cc[:, c], S, torch.exp(acs[:, c]))
+        ys.append(y_diag[:, c] + y_off)
+        S = S * torch.exp(acs[:, c, -1])[..., None, None] + states[:, c]
+    y = torch.stack(ys, 1).reshape(Bsz, Nc * chunk, H, P)[:, :T]
+    if D is not None:
+        y = y + x.to(f) * D.to(f)[None, None, :, None]
+    return y.to(x.dtype), S
+
+
+def ssd_step(x, dt, A, Bm, Cm, state, D=None):
+    """One decode step: x ``[B,H,P]``, dt ``[B,H]``, B / C ``[B,G,N]``; ``state [B,H,P,N]`` fp32 updated in place."""
+    H, G = x.shape[1], Bm.shape[1]
+    Bf, Cf = Bm.float().repeat_interleave(H // G, 1), Cm.float().repeat_interleave(H // G, 1)
+    state.mul_(torch.exp(dt.float() * A.float())[..., None, None])
+    state.add_(torch.einsum("bhp,bhn->bhpn", x.float() * dt.float()[..., None], Bf))
+    y = torch.einsum("bhpn,bhn->bhp", state, Cf)
+    if D is not None:
+        y = y + x.float() * D.float()[None, :, None]
+    return y.to(x.dtype)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# short causal depthwise convolution
+
+
+def short_conv_reference(x, w, bias=None, activation: bool = True, segment_ids=None, initial=None):
+    """``y[t] = act(sum_j w[c, j] x[t - K + 1 + j] + b)``; x ``[B,T,C]``, w ``[C,K]``.  With ``segment_ids [B,T]`` taps
+    that would cross a document boundary are dropped (packed documents).  ``initial [B,K-1,C]`` prepends history."""
+    B, T, C = x.shape
+    K = w.shape[1]
+    xf = x.float()
+    hist = torch.zeros(B, K - 1, C, dtype=torch.float32, device=x.device) if initial is None else initial.float()
+    xp = torch.cat([hist, xf], 1)
+    y = torch.zeros(B, T, C, dtype=torch.float32, device=x.device)
+    for j in range(K):
+        tap = xp[:, j:j + T]
+        if segment_ids is not None:
+            shift = K - 1 - j
+            if shift > 0:
+                same = torch.ones(B, T, dtype=torch.bool, device=x.device)
+                same[:, shift:] = segment_ids[:, shift:] == segment_ids[:, :-shift]
+                same[:, :shift] = initial is not None
+                tap = tap * same[..., None]
+        y = y + tap * w[:, j].float()
+    if bias is not None:
+        y = y + bias.float()
+    if activation:
+        y = F.silu(y)
+    return y.to(x.dtype)
+
+
+def short_conv(x, w, bias=None, activation: bool = True, segment_ids=None, initial=None):
+    from . import library as L
+    if L.use_cuda(x) and x.dtype == torch.bfloat16 and segment_ids is None and initial is None and hasattr(L.load(), "dewb_short_conv_fwd") \
+            and x.shape[-1] % 8 == 0 and w.shape[1] <= 4:
+        from .conv import short_conv_cuda
+        return short_conv_cuda(x, w, bias, activation)
+    return short_conv_reference(x, w, bias, activation, segment_ids, initial)
+
+
+def short_conv_step(x, w, bias, cache, activation: bool = True):
+    """Decode step: x ``[B,C]``; ``cache [B,K-1,C]`` holds the last K-1 inputs and is rolled in place."""
+    K = w.shape[1]
+    window = torch.cat([cache, x[:, None].to(cache.dtype)], 1)                 # [B,K,C]
+    y = (window.float() * w.float().t()[None]).sum(1)
+    if bias is not None:
+        y = y + bias.float()
+    cache.copy_(window[:, 1:])
+    return (F.silu(y) if activation else y).to(x.dtype)

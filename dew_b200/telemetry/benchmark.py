@@ -52,10 +52,28 @@ class DeviceTime:
         return min(self.samples_ms)
 
 
-def device_time(fn: Callable[[], None], warmup: int = 3, iters: int = 10, flush: Optional[L2Flush] = None) -> DeviceTime:
+def device_time(fn: Callable[[], None], warmup: int = 3, iters: int = 10, flush: Optional[L2Flush] = None,
+                graph: bool = False) -> DeviceTime:
+    """Median-able device time of ``fn``.  ``graph=True`` captures ``fn`` into a CUDA graph first and times replays, so
+    host launch overhead (which dominates kernels of a few tens of microseconds) is excluded."""
     for _ in range(max(3, warmup)):
         fn()
     torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+            with torch.cuda.graph(g, stream=side):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        run = g.replay
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        fn = run
     out = []
     for _ in range(iters):
         if flush is not None:

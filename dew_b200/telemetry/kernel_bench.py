@@ -76,9 +76,14 @@ def bench_rows(out, peaks, flush, iters=10):
             fb, bb = 3 * rows * d * 2, 5 * rows * d * 2
         y = fwd()
         dy = torch.randn_like(y)
-        t_f = device_time(lambda: fwd(), iters=iters, flush=flush)
-        t_fb = device_time(lambda: fwd().backward(dy), iters=iters, flush=flush)
-        t_ref = device_time(lambda: ref(), iters=iters, flush=flush)
+        def fb():
+            for t in (x, w):
+                t.grad = None
+            fwd().backward(dy)
+        # row kernels last tens of microseconds: time CUDA-graph replays so host launch overhead is excluded
+        t_f = device_time(lambda: fwd(), iters=iters, flush=flush, graph=True)
+        t_fb = device_time(fb, iters=iters, flush=flush, graph=True)
+        t_ref = device_time(lambda: ref(), iters=iters, flush=flush, graph=True)
         L.check_status()
         _row(out, kernel=kind, rows=rows, d=d, fwd_us=1000 * t_f.median_ms, fwd_bwd_us=1000 * t_fb.median_ms,
              torch_fwd_us=1000 * t_ref.median_ms, fwd_gbs=fb / t_f.median_ms / 1e6,
@@ -101,6 +106,13 @@ def bench_attention(out, peaks, flush, iters=10):
                 row[f"{name}_error"] = str(e)[:120]
                 continue
             do = torch.randn_like(o)
+            try:
+                L.check_status()
+                ops.attention(q, k, v, causal=True, kernel=name).backward(do)
+                L.check_status()            # never time a kernel that has just reported a timed-out wait
+            except Exception as e:
+                row[f"{name}_error"] = str(e)[:120]
+                continue
             t_f = device_time(lambda: ops.attention(q, k, v, causal=True, kernel=name), iters=iters, flush=flush)
             t_fb = device_time(lambda: ops.attention(q, k, v, causal=True, kernel=name).backward(do), iters=iters, flush=flush)
             row[f"{name}_fwd_ms"], row[f"{name}_fwd_bwd_ms"] = t_f.median_ms, t_fb.median_ms

@@ -1,0 +1,70 @@
+"""Chunked linear recurrences against their step-by-step oracles (float64)."""
+import torch
+
+from dew_b200.ops import scan
+
+
+def test_gated_delta_rule_chunked_matches_recurrent():
+    torch.manual_seed(0)
+    B, T, H, Dk, Dv = 2, 150, 3, 16, 24
+    q = torch.nn.functional.normalize(torch.randn(B, T, H, Dk, dtype=torch.float64), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, Dk, dtype=torch.float64), dim=-1)
+    v = torch.randn(B, T, H, Dv, dtype=torch.float64)
+    g = -torch.rand(B, T, H, dtype=torch.float64) * 0.2
+    beta = torch.rand(B, T, H, dtype=torch.float64)
+    s0 = torch.randn(B, H, Dk, Dv, dtype=torch.float64) * 0.1
+    o1, s1 = scan.gated_delta_rule_recurrent(q, k, v, g, beta, s0)
+    o2, s2 = scan.gated_delta_rule_chunked(q, k, v, g, beta, s0)
+    assert torch.allclose(o1, o2, atol=1e-9) and torch.allclose(s1, s2, atol=1e-9)
+    # decode steps continue the same trajectory
+    st = s0.float().clone()
+    o3 = torch.stack([scan.gated_delta_rule_step(q[:, t].float(), k[:, t].float(), v[:, t].float(), g[:, t].float(),
+                                                 beta[:, t].float(), st) for t in range(8)], 1)
+    assert torch.allclose(o3.double(), o1[:, :8], atol=1e-4)
+
+
+def test_gated_delta_rule_is_differentiable():
+    torch.manual_seed(1)
+    B, T, H, D = 1, 70, 2, 8
+    q0, k0, v = (torch.randn(B, T, H, D, dtype=torch.float64, requires_grad=True) for _ in range(3))
+    q, k = torch.nn.functional.normalize(q0, dim=-1), torch.nn.functional.normalize(k0, dim=-1)   # as the layer does
+    g = (-torch.rand(B, T, H, dtype=torch.float64) * 0.1).requires_grad_()
+    beta = torch.rand(B, T, H, dtype=torch.float64).requires_grad_()
+    f = lambda *a: scan.gated_delta_rule_chunked(*a)[0].pow(2).sum()
+    h = lambda *a: scan.gated_delta_rule_recurrent(*a)[0].pow(2).sum()
+    ga = torch.autograd.grad(f(q, k, v, g, beta), (q0, k0, v, g, beta), retain_graph=True)
+    gb = torch.autograd.grad(h(q, k, v, g, beta), (q0, k0, v, g, beta))
+    for a, b in zip(ga, gb):
+        assert torch.allclose(a, b, atol=1e-8, rtol=1e-8)
+
+
+def test_ssd_chunked_matches_recurrent():
+    torch.manual_seed(2)
+    B, T, H, P, G, N = 2, 130, 4, 8, 2, 16
+    x = torch.randn(B, T, H, P, dtype=torch.float64)
+    dt = torch.nn.functional.softplus(torch.randn(B, T, H, dtype=torch.float64))
+    A = -torch.rand(H, dtype=torch.float64) - 0.1
+    Bm, Cm = torch.randn(B, T, G, N, dtype=torch.float64), torch.randn(B, T, G, N, dtype=torch.float64)
+    D = torch.randn(H, dtype=torch.float64)
+    y1, s1 = scan.ssd_recurrent(x, dt, A, Bm, Cm, D)
+    y2, s2 = scan.ssd_chunked(x, dt, A, Bm, Cm, D)
+    assert torch.allclose(y1, y2, atol=1e-9) and torch.allclose(s1, s2, atol=1e-9)
+    st = torch.zeros(B, H, P, N)
+    y3 = torch.stack([scan.ssd_step(x[:, t].float(), dt[:, t].float(), A.float(), Bm[:, t].float(), Cm[:, t].float(), st, D.float()) for t in range(5)], 1)
+    assert torch.allclose(y3.double(), y1[:, :5], atol=1e-4)
+
+
+def test_short_conv_matches_conv1d_and_respects_documents():
+    torch.manual_seed(3)
+    B, T, C, K = 2, 20, 6, 4
+    x, w, b = torch.randn(B, T, C), torch.randn(C, K), torch.randn(C)
+    y = scan.short_conv_reference(x, w, b, activation=False)
+    ref = torch.nn.functional.conv1d(torch.nn.functional.pad(x.transpose(1, 2), (K - 1, 0)), w[:, None], b, groups=C).transpose(1, 2)
+    assert torch.allclose(y, ref, atol=1e-5)
+    seg = torch.tensor([[1] * 10 + [2] * 10] * B)
+    ys = scan.short_conv_reference(x, w, b, activation=False, segment_ids=seg)
+    y2 = scan.short_conv_reference(x[:, 10:], w, b, activation=False)
+    assert torch.allclose(ys[:, 10:], y2, atol=1e-5)                # the second document starts from zero history
+    cache = torch.zeros(B, K - 1, C)
+    steps = torch.stack([scan.short_conv_step(x[:, t], w, b, cache, activation=False) for t in range(T)], 1)
+    assert torch.allclose(steps, y, atol=1e-5)
