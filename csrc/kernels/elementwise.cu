@@ -825,3 +825,55 @@ extern "C" int dewb_cast_f32_bf16(const float* src, void* dst, long long n, void
   cast_f32_bf16_kernel<<<grid_for(n, 256), 256, 0, STREAM(stream)>>>(src, (bf16*)dst, n);
   return LAST_ERR();
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// RMSNorm backward for callers that cannot allocate (declaration and rules of use: csrc/include/dewb_noalloc.h).
+// The weight-gradient partial sums live in this file-scope device array instead of a caller-provided buffer.
+#include "../include/dewb_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_dw_partial[DEWB_NOALLOC_MAX_SPLITS * DEWB_NOALLOC_MAX_D];
+
+// Device address of the array, per device. In host code the array's name is only a handle for the runtime's symbol
+// table; the address a kernel can use comes from cudaGetSymbolAddress, asked for once with that device current.
+static float* g_noalloc_ptr[64];
+
+extern "C" int dewb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                        const void* dres, void* dx, float* dw_f32, void* dw_bf16, int accumulate,
+                                        long long rows, int d, int device, void* stream) {
+  if (d <= 0 || d % 8 != 0) return -3;
+  if (d > DEWB_NOALLOC_MAX_D) return DEWB_NOALLOC_ERR_TOO_LARGE;
+  if (device < 0 || device >= 64) return -3;
+  if (rows <= 0) return 0;
+  if (g_noalloc_ptr[device] == nullptr) {
+    // one-time set-up for this device (not to be done under stream capture)
+    int cur = -1;
+    cudaError_t e = cudaGetDevice(&cur);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (cur != device && (e = cudaSetDevice(device)) != cudaSuccess) return static_cast<int>(e);
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dw_partial);
+    if (cur != device) cudaSetDevice(cur);
+    if (e != cudaSuccess || p == nullptr) return e != cudaSuccess ? static_cast<int>(e) : DEWB_NOALLOC_ERR_SYMBOL;
+    g_noalloc_ptr[device] = p;
+  }
+  float* partial = g_noalloc_ptr[device];
+  const int nvec = d >> 3;
+  int G = 32;
+  while (G > 1 && (G >> 1) >= nvec) G >>= 1;
+  const int need = (nvec + G - 1) / G;
+  const long long rows_per_block = 8LL * (32 / G);
+  const unsigned nb = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
+#define DEWB_NA_ROWS(VPL) rmsnorm_bwd_dx_rows_kernel<false, VPL><<<nb, 256, 0, STREAM(stream)>>>( \
+    (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, nullptr, (bf16*)dx, nullptr, rows, d, G)
+  if (need <= 1) DEWB_NA_ROWS(1); else if (need <= 2) DEWB_NA_ROWS(2); else if (need <= 4) DEWB_NA_ROWS(4);
+  else if (need <= 8) DEWB_NA_ROWS(8); else DEWB_NA_ROWS(16);
+#undef DEWB_NA_ROWS
+  // every split row of the array that colsum reads below is written here first: stale contents never leak
+  int splits = DEWB_NOALLOC_MAX_SPLITS;
+  const long long max_useful = (rows + 7) / 8;
+  if (splits > max_useful) splits = static_cast<int>(max_useful);
+  dim3 g((nvec + 31) / 32, splits);
+  rmsnorm_dw_kernel<false><<<g, 256, 0, STREAM(stream)>>>((const bf16*)dy, (const bf16*)x, rstd, nullptr, partial, rows, d);
+  colsum_kernel<<<(d + 255) / 256, 256, 0, STREAM(stream)>>>(partial, splits, d, dw_f32, (bf16*)dw_bf16, accumulate);
+  return LAST_ERR();
+}
