@@ -1,0 +1,304 @@
+// Paged decode attention (flash-decoding) for sm_100a: one new query token per row against that row's cached keys.
+//
+// grid = (row, kv head, key split). A CTA handles the G = Hq / Hkv query heads that share its KV head, so every cached
+// key and value is read from HBM exactly once per row. Each of its 4 warps walks 32-key blocks of the split:
+//   scores : lane = key      - each lane reads one key row (16-byte loads) and dots it with the G queries in smem
+//   values : lane = d-slice  - the block's probabilities are broadcast by shuffle; value rows are read coalesced
+// Online softmax per warp in fp32 (log2 domain); warps, then splits, are merged with the usual (max, sum, acc) algebra.
+// The cache is paged: pool [pages, page_size, Hkv, D] for keys and for values, page_table [rows, max_pages] (int32),
+// lengths [rows]. Optional per-token-per-head fp32 scales dequantise int8 / fp8-e4m3 pools.
+// The kernel is bandwidth-bound by design (arithmetic intensity G FLOP/byte); tensor cores would not help at G <= 8.
+//
+// Capability parity: src/dew/nn/kernels/decode_attention.py (attend_paged: BLOCK 32 keys, key splits combined in
+// fp32), src/dew/nn/kv_cache.py:1297-1320 (pool layout), :411-446 (int8 / fp8 KV quantisation).
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+namespace dewb {
+namespace decode {
+
+constexpr int WARPS = 4;
+constexpr int MAX_G = 8;
+
+__device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+// KV element kinds
+enum : int { KV_BF16 = 0, KV_INT8 = 1, KV_FP8 = 2 };
+
+template <int KIND>
+__device__ __forceinline__ void load8(const void* base, long long elem_off, float (&f)[8]) {
+  if (KIND == KV_BF16) {
+    const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + elem_off);
+    f[0] = bf_lo(v.x); f[1] = bf_hi(v.x); f[2] = bf_lo(v.y); f[3] = bf_hi(v.y);
+    f[4] = bf_lo(v.z); f[5] = bf_hi(v.z); f[6] = bf_lo(v.w); f[7] = bf_hi(v.w);
+  } else if (KIND == KV_INT8) {
+    const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const int8_t*>(base) + elem_off);
+    const int8_t* b = reinterpret_cast<const int8_t*>(&v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = static_cast<float>(b[i]);
+  } else {
+    const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(base) + elem_off);
+    const __nv_fp8_e4m3* b = reinterpret_cast<const __nv_fp8_e4m3*>(&v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = static_cast<float>(b[i]);
+  }
+}
+
+// partial results per (row, q head, split): m (log2 domain), l, acc[D]
+template <int D, int KIND>
+__global__ void __launch_bounds__(WARPS * 32)
+paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict__ kpool, const void* __restrict__ vpool,
+                    const float* __restrict__ kscale, const float* __restrict__ vscale,
+                    const int* __restrict__ page_table, const int* __restrict__ lengths, float* __restrict__ part_m,
+                    float* __restrict__ part_l, float* __restrict__ part_acc, int Hq, int Hkv, int page_size,
+                    int max_pages, int splits, float scale_log2, int window) {
+  constexpr int DV = D / 32;                 // value elements per lane
+  const int row = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+  const int G = Hq / Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ float sq[MAX_G][D];
+  __shared__ float sm_m[WARPS][MAX_G], sm_l[WARPS][MAX_G];
+  __shared__ float sm_acc[WARPS][MAX_G][D];
+  const int len = lengths[row];
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int g = i / D, d = i - g * D;
+    sq[g][d] = __bfloat162float(q[(static_cast<long long>(row) * Hq + hk * G + g) * D + d]) * scale_log2;
+  }
+  __syncthreads();
+  // keys of this split: [k_begin, k_end) in 32-key blocks, interleaved across the CTA's warps
+  const int first = (window > 0 && len > window) ? len - window : 0;
+  const int span = len - first;
+  const int per_split = ((span + splits - 1) / splits + 31) / 32 * 32;
+  const int k_begin = first + split * per_split;
+  const int k_end = min(len, k_begin + per_split);
+  float m[MAX_G], l[MAX_G], acc[MAX_G][DV];
+#pragma unroll
+  for (int g = 0; g < MAX_G; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DV; ++i) acc[g][i] = 0.f;
+  }
+  const int* table = page_table + static_cast<long long>(row) * max_pages;
+  for (int kb = k_begin + warp * 32; kb < k_end; kb += WARPS * 32) {
+    const int key = kb + lane;
+    const bool live = key < k_end;
+    float s[MAX_G];
+#pragma unroll
+    for (int g = 0; g < MAX_G; ++g) s[g] = -INFINITY;
+    long long tok = 0;      // (page * page_size + slot) of this lane's key
+    if (live) {
+      const int page = table[key / page_size];
+      tok = static_cast<long long>(page) * page_size + (key % page_size);
+      const long long base = (tok * Hkv + hk) * D;
+      float dot[MAX_G];
+#pragma unroll
+      for (int g = 0; g < MAX_G; ++g) dot[g] = 0.f;
+#pragma unroll 4
+      for (int d0 = 0; d0 < D; d0 += 8) {
+        float kf[8];
+        load8<KIND>(kpool, base + d0, kf);
+#pragma unroll
+        for (int g = 0; g < MAX_G; ++g)
+          if (g < G) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dot[g] += kf[i] * sq[g][d0 + i];
+          }
+      }
+      const float ks = KIND == KV_BF16 ? 1.f : kscale[tok * Hkv + hk];
+#pragma unroll
+      for (int g = 0; g < MAX_G; ++g) if (g < G) s[g] = dot[g] * ks;
+    }
+    // online softmax update (per query head), block maximum by warp reduction
+    float p[MAX_G];
+#pragma unroll
+    for (int g = 0; g < MAX_G; ++g) {
+      if (g < G) {
+        float bm = s[g];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+        const float mn = fmaxf(m[g], bm);
+        const float alpha = m[g] == -INFINITY ? 0.f : exp2f(m[g] - mn);
+        p[g] = live ? exp2f(s[g] - mn) : 0.f;
+        float ps = p[g];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        l[g] = l[g] * alpha + ps;
+        m[g] = mn;
+#pragma unroll
+        for (int i = 0; i < DV; ++i) acc[g][i] *= alpha;
+      }
+    }
+    // values: lane owns columns [lane * DV, lane * DV + DV); walk the block's keys
+    const int nkeys = min(32, k_end - kb);
+    for (int j = 0; j < nkeys; ++j) {
+      const long long tj = __shfl_sync(0xffffffffu, tok, j);
+      const long long vb = (tj * Hkv + hk) * D + lane * DV;
+      float vf[DV];
+      if (KIND == KV_BF16) {
+        const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(vpool) + vb;
+        if (DV == 4) {
+          const uint2 v = *reinterpret_cast<const uint2*>(vp);
+          vf[0] = bf_lo(v.x); vf[1] = bf_hi(v.x); vf[2] = bf_lo(v.y); vf[3] = bf_hi(v.y);
+        } else {
+#pragma unroll
+          for (int i = 0; i < DV; ++i) vf[i] = __bfloat162float(vp[i]);
+        }
+      } else if (KIND == KV_INT8) {
+        const int8_t* vp = reinterpret_cast<const int8_t*>(vpool) + vb;
+#pragma unroll
+        for (int i = 0; i < DV; ++i) vf[i] = static_cast<float>(vp[i]);
+      } else {
+        const __nv_fp8_e4m3* vp = reinterpret_cast<const __nv_fp8_e4m3*>(vpool) + vb;
+#pragma unroll
+        for (int i = 0; i < DV; ++i) vf[i] = static_cast<float>(vp[i]);
+      }
+      const float vs = KIND == KV_BF16 ? 1.f : vscale[tj * Hkv + hk];
+#pragma unroll
+      for (int g = 0; g < MAX_G; ++g) {
+        if (g < G) {
+          const float pj = __shfl_sync(0xffffffffu, p[g], j) * vs;
+#pragma unroll
+          for (int i = 0; i < DV; ++i) acc[g][i] += pj * vf[i];
+        }
+      }
+    }
+  }
+  // merge the CTA's warps
+#pragma unroll
+  for (int g = 0; g < MAX_G; ++g) {
+    if (g < G) {
+      if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
+#pragma unroll
+      for (int i = 0; i < DV; ++i) sm_acc[warp][g][lane * DV + i] = acc[g][i];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int g = i / D, d = i - g * D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, sm_m[w][g]);
+    float ll = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float f = sm_m[w][g] == -INFINITY ? 0.f : exp2f(sm_m[w][g] - mm);
+      ll += sm_l[w][g] * f;
+      a += sm_acc[w][g][d] * f;
+    }
+    const long long o = (static_cast<long long>(row) * Hq + hk * G + g) * splits + split;
+    part_acc[o * D + d] = a;
+    if (d == 0) { part_m[o] = mm; part_l[o] = ll; }
+  }
+}
+
+// out[row, h, :] = sum_s acc_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M); optional attention sink per head
+template <int D>
+__global__ void decode_combine_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l,
+                                      const float* __restrict__ part_acc, const float* __restrict__ sinks,
+                                      __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int Hq, int splits) {
+  const long long rh = blockIdx.x;          // row * Hq + h
+  const int d = threadIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_m[rh * splits + s]);
+  float L = 0.f, a = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_m[rh * splits + s];
+    const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+    L += part_l[rh * splits + s] * f;
+    a += part_acc[(rh * splits + s) * D + d] * f;
+  }
+  if (sinks != nullptr && M > -INFINITY) {
+    const float sk = sinks[rh % Hq] * 1.4426950408889634f;      // the sink is a logit in natural units
+    const float Mn = fmaxf(M, sk);
+    const float f = exp2f(M - Mn);
+    L = L * f + exp2f(sk - Mn);
+    a *= f;
+    M = Mn;
+  }
+  if (d < D) out[rh * D + d] = __float2bfloat16(L > 0.f ? a / L : 0.f);
+  if (d == 0 && lse != nullptr) lse[rh] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+}
+
+// Append one token per row to the paged pools: k_new / v_new [rows, Hkv, D] -> pool slot lengths[row] of the row.
+// KIND 1 / 2 quantise per token per head: scale = absmax / limit (127 for int8, 448 for fp8-e4m3).
+template <int KIND>
+__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
+                                 void* __restrict__ kpool, void* __restrict__ vpool, float* __restrict__ kscale,
+                                 float* __restrict__ vscale, const int* __restrict__ page_table,
+                                 const int* __restrict__ positions, int Hkv, int D, int page_size, int max_pages) {
+  const int row = blockIdx.x, hk = blockIdx.y, which = blockIdx.z;     // which: 0 keys, 1 values
+  const int pos = positions[row];
+  if (pos < 0) return;
+  const int page = page_table[static_cast<long long>(row) * max_pages + pos / page_size];
+  const long long tok = static_cast<long long>(page) * page_size + pos % page_size;
+  const __nv_bfloat16* src = (which ? v_new : k_new) + (static_cast<long long>(row) * Hkv + hk) * D;
+  void* pool = which ? vpool : kpool;
+  const long long dst = (tok * Hkv + hk) * D;
+  if (KIND == KV_BF16) {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) reinterpret_cast<__nv_bfloat16*>(pool)[dst + d] = src[d];
+    return;
+  }
+  __shared__ float red[32];
+  float mx = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) mx = fmaxf(mx, fabsf(__bfloat162float(src[d])));
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = 0.f;
+  for (int w = 0; w < (blockDim.x + 31) / 32; ++w) mx = fmaxf(mx, red[w]);
+  const float limit = KIND == KV_INT8 ? 127.f : 448.f;
+  const float sc = mx > 0.f ? mx / limit : 1.f;
+  if (threadIdx.x == 0) (which ? vscale : kscale)[tok * Hkv + hk] = sc;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float x = __bfloat162float(src[d]) / sc;
+    if (KIND == KV_INT8) reinterpret_cast<int8_t*>(pool)[dst + d] = static_cast<int8_t>(max(-127, min(127, __float2int_rn(x))));
+    else reinterpret_cast<__nv_fp8_e4m3*>(pool)[dst + d] = __nv_fp8_e4m3(x);
+  }
+}
+
+}  // namespace decode
+}  // namespace dewb
+
+using namespace dewb::decode;
+
+// Scratch (caller-provided fp32): part_m, part_l [rows * Hq * splits], part_acc [rows * Hq * splits * D].
+extern "C" int dewb_paged_decode(const void* q, const void* kpool, const void* vpool, const float* kscale,
+                                 const float* vscale, const int* page_table, const int* lengths, const float* sinks,
+                                 void* out, float* lse, float* part_m, float* part_l, float* part_acc, int rows, int Hq,
+                                 int Hkv, int D, int page_size, int max_pages, int splits, float scale, int window,
+                                 int kv_kind, void* stream_ptr) {
+  if (rows <= 0) return 0;
+  if ((D != 64 && D != 128 && D != 256) || Hq % Hkv != 0 || Hq / Hkv > MAX_G || splits < 1) return -3;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(rows, Hkv, splits);
+  const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(q);
+#define DEWB_DECODE(DD, KK) paged_decode_kernel<DD, KK><<<grid, WARPS * 32, 0, stream>>>( \
+    qp, kpool, vpool, kscale, vscale, page_table, lengths, part_m, part_l, part_acc, Hq, Hkv, page_size, max_pages, splits, scale_log2, window)
+#define DEWB_DECODE_D(KK) do { if (D == 64) DEWB_DECODE(64, KK); else if (D == 128) DEWB_DECODE(128, KK); else DEWB_DECODE(256, KK); } while (0)
+  if (kv_kind == KV_BF16) DEWB_DECODE_D(KV_BF16); else if (kv_kind == KV_INT8) DEWB_DECODE_D(KV_INT8); else DEWB_DECODE_D(KV_FP8);
+#undef DEWB_DECODE_D
+#undef DEWB_DECODE
+  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(out);
+  if (D == 64) decode_combine_kernel<64><<<rows * Hq, 64, 0, stream>>>(part_m, part_l, part_acc, sinks, op, lse, Hq, splits);
+  else if (D == 128) decode_combine_kernel<128><<<rows * Hq, 128, 0, stream>>>(part_m, part_l, part_acc, sinks, op, lse, Hq, splits);
+  else decode_combine_kernel<256><<<rows * Hq, 256, 0, stream>>>(part_m, part_l, part_acc, sinks, op, lse, Hq, splits);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// positions[row] = slot to write (the row's current length), or < 0 to skip the row.
+extern "C" int dewb_kv_append(const void* k_new, const void* v_new, void* kpool, void* vpool, float* kscale,
+                              float* vscale, const int* page_table, const int* positions, int rows, int Hkv, int D,
+                              int page_size, int max_pages, int kv_kind, void* stream_ptr) {
+  if (rows <= 0) return 0;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  dim3 grid(rows, Hkv, 2);
+  const __nv_bfloat16 *kp = reinterpret_cast<const __nv_bfloat16*>(k_new), *vp = reinterpret_cast<const __nv_bfloat16*>(v_new);
+  if (kv_kind == KV_BF16) kv_append_kernel<KV_BF16><<<grid, 128, 0, stream>>>(kp, vp, kpool, vpool, kscale, vscale, page_table, positions, Hkv, D, page_size, max_pages);
+  else if (kv_kind == KV_INT8) kv_append_kernel<KV_INT8><<<grid, 128, 0, stream>>>(kp, vp, kpool, vpool, kscale, vscale, page_table, positions, Hkv, D, page_size, max_pages);
+  else kv_append_kernel<KV_FP8><<<grid, 128, 0, stream>>>(kp, vp, kpool, vpool, kscale, vscale, page_table, positions, Hkv, D, page_size, max_pages);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -668,11 +668,9 @@ using namespace dewb::ew;
 
 // Select the device for this library's CUDA runtime on the calling thread.
 extern "C" int dewb_set_device(int device) {
-  int cur = -1;
-  if (cudaGetDevice(&cur) == cudaSuccess && cur == device) { cudaFree(0); return 0; }
-  cudaError_t e = cudaSetDevice(device);
-  if (e == cudaSuccess) cudaFree(0);
-  return static_cast<int>(e);
+  // cudaSetDevice binds (and, the first time, creates) the device's primary context on the calling thread; it is not
+  // a stream operation, so it is legal while another thread's stream is being captured into a graph.
+  return static_cast<int>(cudaSetDevice(device));
 }
 
 extern "C" int dewb_rmsnorm_fwd(const void* x, const void* other, const void* w, void* y, void* h_out, float* rstd,

@@ -48,47 +48,73 @@ def bench_gemm(out, peaks, flush, shapes=None, iters=10):
         del A, B, D
 
 
+def _raw_backward(kind, x, other, w, dy):
+    """The backward launchers called directly (no autograd engine, so the call can be captured into a CUDA graph)."""
+    import ctypes
+    lib = L.load()
+    rows, d = x.shape
+    if kind == "swiglu":
+        F2 = x.shape[1]
+        Fh = F2 // 2
+        dgu = torch.empty_like(x)
+
+        def run():
+            L.check(lib.dewb_swiglu_bwd(L.ptr(dy), L.ptr(x), ctypes.c_void_p(x.data_ptr() + Fh * 2), L.ptr(dgu),
+                                        ctypes.c_void_p(dgu.data_ptr() + Fh * 2), ctypes.c_longlong(rows), ctypes.c_int(Fh),
+                                        ctypes.c_longlong(F2), L.stream_ptr()), "swiglu_bwd")
+        return run
+    rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6).contiguous()
+    blocks = lib.dewb_rmsnorm_bwd_blocks(ctypes.c_longlong(rows))
+    scratch = torch.empty(blocks, d, dtype=torch.float32, device=x.device)
+    dx, dw = torch.empty_like(x), torch.empty(d, dtype=torch.float32, device=x.device)
+    dz = torch.empty_like(x) if kind == "gated_rmsnorm" else None
+    dres = dy if kind == "stream_rmsnorm" else None
+    z = other if kind == "gated_rmsnorm" else None
+
+    def run():
+        L.check(lib.dewb_rmsnorm_bwd(L.ptr(dy), L.ptr(x), L.ptr(w), L.ptr(rstd), L.ptr(dres), L.ptr(z), L.ptr(dx), L.ptr(dz),
+                                     L.ptr(scratch), L.ptr(dw), L.ptr(None), ctypes.c_int(0), ctypes.c_longlong(rows),
+                                     ctypes.c_int(d), L.stream_ptr()), "rmsnorm_bwd")
+    return run
+
+
 def bench_rows(out, peaks, flush, iters=10):
+    """Row kernels last tens of microseconds, so they are timed as CUDA-graph replays (no host launch overhead);
+    bytes are the algorithmic minimum (each operand touched once)."""
     bw = peaks["hbm_gbs"]
     cases = [("rmsnorm", 12288, 2560), ("rmsnorm", 8192, 4096), ("stream_rmsnorm", 12288, 2560), ("stream_rmsnorm", 32768, 4096),
              ("gated_rmsnorm", 12288 * 32, 128), ("swiglu", 12288, 9216), ("swiglu", 8192, 14336)]
     for kind, rows, d in cases:
-        x = torch.randn(rows, d, device="cuda").to(torch.bfloat16).requires_grad_()
-        w = torch.ones(d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-        if kind == "rmsnorm":
-            fwd = lambda: ops.rms_norm(x, w)
-            ref = lambda: ops.rms_norm_reference(x, w)
-            fb, bb = 2 * rows * d * 2, 3 * rows * d * 2
-        elif kind == "stream_rmsnorm":
-            b = torch.randn_like(x)
-            fwd = lambda: ops.stream_rms_norm(x, b, w)[0]
-            ref = lambda: ops.rms_norm_reference(x + b, w)
-            fb, bb = 4 * rows * d * 2, 3 * rows * d * 2
-        elif kind == "gated_rmsnorm":
-            z = torch.randn_like(x).requires_grad_()
-            fwd = lambda: ops.gated_rms_norm(x, z, w)
-            ref = lambda: ops.rms_norm_reference(x, w) * torch.nn.functional.silu(z)
-            fb, bb = 3 * rows * d * 2, 5 * rows * d * 2
-        else:
-            gu = torch.randn(rows, 2 * d, device="cuda").to(torch.bfloat16).requires_grad_()
-            fwd = lambda: ops.packed_swiglu(gu)
-            ref = lambda: torch.nn.functional.silu(gu[:, :d]) * gu[:, d:]
-            fb, bb = 3 * rows * d * 2, 5 * rows * d * 2
-        y = fwd()
-        dy = torch.randn_like(y)
-        def fb():
-            for t in (x, w):
-                t.grad = None
-            fwd().backward(dy)
-        # row kernels last tens of microseconds: time CUDA-graph replays so host launch overhead is excluded
-        t_f = device_time(lambda: fwd(), iters=iters, flush=flush, graph=True)
-        t_fb = device_time(fb, iters=iters, flush=flush, graph=True)
-        t_ref = device_time(lambda: ref(), iters=iters, flush=flush, graph=True)
+        e = rows * d * 2
+        w = torch.ones(d, device="cuda", dtype=torch.bfloat16)
+        x = torch.randn(rows, d, device="cuda").to(torch.bfloat16)
+        other = torch.randn_like(x)
+        with torch.no_grad():
+            if kind == "rmsnorm":
+                fwd, ref = (lambda: ops.rms_norm(x, w)), (lambda: ops.rms_norm_reference(x, w))
+                fb, bb = 2 * e, 3 * e
+            elif kind == "stream_rmsnorm":
+                fwd, ref = (lambda: ops.stream_rms_norm(x, other, w)[0]), (lambda: ops.rms_norm_reference(x + other, w))
+                fb, bb = 4 * e, 4 * e
+            elif kind == "gated_rmsnorm":
+                fwd = lambda: ops.gated_rms_norm(x, other, w)
+                ref = lambda: ops.rms_norm_reference(x, w) * torch.nn.functional.silu(other)
+                fb, bb = 3 * e, 5 * e
+            else:
+                x = torch.randn(rows, 2 * d, device="cuda").to(torch.bfloat16)
+                fwd = lambda: ops.packed_swiglu(x)
+                ref = lambda: torch.nn.functional.silu(x[:, :d]) * x[:, d:]
+                fb, bb = 3 * e, 5 * e
+            dy = torch.randn(rows, d, device="cuda").to(torch.bfloat16)
+            bwd = _raw_backward(kind, x, other, w, dy)
+            t_f = device_time(fwd, iters=iters, flush=flush, graph=True)
+            t_b = device_time(bwd, iters=iters, flush=flush, graph=True)
+            t_ref = device_time(ref, iters=iters, flush=flush, graph=True)
         L.check_status()
-        _row(out, kernel=kind, rows=rows, d=d, fwd_us=1000 * t_f.median_ms, fwd_bwd_us=1000 * t_fb.median_ms,
-             torch_fwd_us=1000 * t_ref.median_ms, fwd_gbs=fb / t_f.median_ms / 1e6,
-             fwd_frac_of_measured=fb / t_f.median_ms / 1e6 / bw,
-             bwd_gbs=bb / max(t_fb.median_ms - t_f.median_ms, 1e-6) / 1e6, peaks=peaks["source"])
+        _row(out, kernel=kind, rows=rows, d=d, fwd_us=1000 * t_f.median_ms, bwd_us=1000 * t_b.median_ms,
+             fwd_bwd_us=1000 * (t_f.median_ms + t_b.median_ms), torch_fwd_us=1000 * t_ref.median_ms,
+             fwd_gbs=fb / t_f.median_ms / 1e6, fwd_frac_of_measured=fb / t_f.median_ms / 1e6 / bw,
+             bwd_gbs=bb / t_b.median_ms / 1e6, bwd_frac_of_measured=bb / t_b.median_ms / 1e6 / bw, peaks=peaks["source"])
 
 
 def bench_attention(out, peaks, flush, iters=10):

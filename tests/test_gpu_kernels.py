@@ -293,3 +293,31 @@ def test_grouped_gemm_forward_backward(T, k, E, d, F):
     ref_dw = G._tgmm_reference(dy, xs.detach(), layout, E)
     assert rel_err(w.grad, ref_dw) <= 1e-2
     assert torch.all(y[~used] == 0)                           # zero rows in, zero rows out
+
+
+@pytest.mark.parametrize("quantized,page_size,D,Hq,Hkv", [(None, 16, 128, 8, 2), (None, 64, 128, 4, 1), ("int8", 16, 128, 8, 2),
+                                                          ("float8_e4m3fn", 32, 64, 4, 4), (None, None, 128, 32, 8)])
+def test_paged_decode_attention(quantized, page_size, D, Hq, Hkv):
+    from dew_b200.nn.kv_cache import KVCache, KVStore, paged_attention_reference
+    torch.manual_seed(11)
+    rows, max_len = 6, 700
+    store = KVStore(KVCache(quantized=quantized, page_size=page_size), 1, rows, max_len, Hkv, D, torch.bfloat16, DEV)
+    if page_size:                                   # scatter the pages so the table matters
+        perm = torch.randperm(store.pages, device=DEV).to(torch.int32)
+        store.page_table.copy_(perm.reshape(rows, store.max_pages))
+    lengths = torch.tensor([1, 17, 256, 511, 640, 699], device=DEV, dtype=torch.int32)
+    S = int(lengths.max())
+    k = torch.randn(rows, S, Hkv, D, device=DEV).to(torch.bfloat16)
+    v = torch.randn(rows, S, Hkv, D, device=DEV).to(torch.bfloat16)
+    pos = torch.arange(S, device=DEV)[None].expand(rows, S).clone()
+    pos[pos >= lengths[:, None]] = -1
+    store.write(0, k, v, pos)
+    # one more token through the append kernel
+    k1 = torch.randn(rows, Hkv, D, device=DEV).to(torch.bfloat16)
+    v1 = torch.randn(rows, Hkv, D, device=DEV).to(torch.bfloat16)
+    store.append(0, k1, v1, lengths)
+    lengths = lengths + 1
+    q = torch.randn(rows, Hq, D, device=DEV).to(torch.bfloat16)
+    out = store.decode_attention(0, q, lengths)
+    ref = paged_attention_reference(store, 0, q.float(), lengths, 1.0 / math.sqrt(D))
+    assert rel_err(out, ref) <= 2e-2, rel_err(out, ref)
