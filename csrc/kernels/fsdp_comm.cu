@@ -306,3 +306,139 @@ extern "C" int dewb_allreduce_pull_f32(const unsigned long long* src_ptrs, float
       make_peers(src_ptrs, world), out, n, world);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// One-shot all-reduce over peer memory with an optional fused "+ residual, RMSNorm" epilogue (tensor-parallel decode):
+// every rank has written its partial [rows, d] (bf16) into its symmetric buffer; the kernel announces that, waits
+// (bounded) for every peer, then each CTA sums one row across the W buffers in fp32, adds the residual stream, writes
+// the new stream, and - in the same pass - normalises it for the next layer.
+// Buffers alternate by sequence parity, so a rank may start writing the next partial as soon as this kernel returns.
+namespace dewb {
+namespace comm {
+
+__global__ void __launch_bounds__(256)
+allreduce_rows_kernel(Peers bufs, Peers flags, const __nv_bfloat16* __restrict__ partial,
+                      const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ norm_w,
+                      __nv_bfloat16* __restrict__ sum_out, __nv_bfloat16* __restrict__ norm_out, int rows, int d,
+                      float eps, int rank, int world, uint32_t* __restrict__ seq_counter,
+                      unsigned int* __restrict__ arrive_counter, long long half_stride, int slot,
+                      unsigned long long limit_ns, int* __restrict__ err) {
+  __shared__ float red[32];
+  __shared__ unsigned int ticket;
+  // The sequence number lives on the device (so a captured CUDA graph can replay this launch): every CTA reads it
+  // before any CTA can have advanced it, because it is advanced by the last CTA to leave.
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(seq_counter) + 1;
+  const long long half = (seq & 1) ? half_stride : 0;
+  uint32_t* my_flags = reinterpret_cast<uint32_t*>(flags.p[rank]);
+  const int nvec0 = d >> 3;
+  // 1. stage this rank's partial rows into its symmetric buffer (the parity half of this sequence number)
+  {
+    uint4* mine = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[rank]) + half);
+    for (int row = blockIdx.x; row < rows; row += gridDim.x)
+      for (int i = threadIdx.x; i < nvec0; i += blockDim.x)
+        mine[static_cast<long long>(row) * nvec0 + i] = reinterpret_cast<const uint4*>(partial + static_cast<long long>(row) * d)[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) ticket = atomicAdd(arrive_counter, 1u);
+  __syncthreads();
+  if (ticket == gridDim.x - 1) {
+    // the last CTA to finish staging announces the whole buffer to every rank (itself included)
+    if (threadIdx.x == 0) *arrive_counter = 0;
+    if (threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(flags.p[threadIdx.x]) + slot * world + rank, seq);
+    }
+  }
+  if (!wait_all_peers(my_flags, slot, world, seq, limit_ns, err)) return;
+  const int nvec = d >> 3;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float ss = 0.f;
+    // d <= 256 * 8 * 4 = 8192: each thread keeps up to 4 vectors of the row
+    float acc[4][8];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int i = threadIdx.x + c * 256;
+      if (i < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[c][j] = 0.f;
+        for (int r = 0; r < world; ++r) {
+          const uint4 v = ld_sys_u4(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(bufs.p[(rank + r) % world]) + half + static_cast<long long>(row) * d) + i);
+          acc[c][0] += __uint_as_float(v.x << 16); acc[c][1] += __uint_as_float(v.x & 0xffff0000u);
+          acc[c][2] += __uint_as_float(v.y << 16); acc[c][3] += __uint_as_float(v.y & 0xffff0000u);
+          acc[c][4] += __uint_as_float(v.z << 16); acc[c][5] += __uint_as_float(v.z & 0xffff0000u);
+          acc[c][6] += __uint_as_float(v.w << 16); acc[c][7] += __uint_as_float(v.w & 0xffff0000u);
+        }
+        if (residual != nullptr) {
+          const uint4 v = reinterpret_cast<const uint4*>(residual + static_cast<long long>(row) * d)[i];
+          acc[c][0] += __uint_as_float(v.x << 16); acc[c][1] += __uint_as_float(v.x & 0xffff0000u);
+          acc[c][2] += __uint_as_float(v.y << 16); acc[c][3] += __uint_as_float(v.y & 0xffff0000u);
+          acc[c][4] += __uint_as_float(v.z << 16); acc[c][5] += __uint_as_float(v.z & 0xffff0000u);
+          acc[c][6] += __uint_as_float(v.w << 16); acc[c][7] += __uint_as_float(v.w & 0xffff0000u);
+        }
+        uint4 pk;
+        pk.x = pack_bf16(acc[c][0], acc[c][1]); pk.y = pack_bf16(acc[c][2], acc[c][3]);
+        pk.z = pack_bf16(acc[c][4], acc[c][5]); pk.w = pack_bf16(acc[c][6], acc[c][7]);
+        if (sum_out != nullptr) reinterpret_cast<uint4*>(sum_out + static_cast<long long>(row) * d)[i] = pk;
+        // normalise what was stored (bf16-rounded), as the stand-alone stream norm does
+        acc[c][0] = __uint_as_float(pk.x << 16); acc[c][1] = __uint_as_float(pk.x & 0xffff0000u);
+        acc[c][2] = __uint_as_float(pk.y << 16); acc[c][3] = __uint_as_float(pk.y & 0xffff0000u);
+        acc[c][4] = __uint_as_float(pk.z << 16); acc[c][5] = __uint_as_float(pk.z & 0xffff0000u);
+        acc[c][6] = __uint_as_float(pk.w << 16); acc[c][7] = __uint_as_float(pk.w & 0xffff0000u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += acc[c][j] * acc[c][j];
+      }
+    }
+    if (norm_out == nullptr) continue;   // (uniform over the block)
+    // block sum
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float t = (threadIdx.x & 31) < 8 ? red[threadIdx.x & 31] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    const float rstd = rsqrtf(t / d + eps);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int i = threadIdx.x + c * 256;
+      if (i < nvec) {
+        const uint4 wv = reinterpret_cast<const uint4*>(norm_w)[i];
+        const float w[8] = {__uint_as_float(wv.x << 16), __uint_as_float(wv.x & 0xffff0000u), __uint_as_float(wv.y << 16),
+                            __uint_as_float(wv.y & 0xffff0000u), __uint_as_float(wv.z << 16), __uint_as_float(wv.z & 0xffff0000u),
+                            __uint_as_float(wv.w << 16), __uint_as_float(wv.w & 0xffff0000u)};
+        uint4 pk;
+        pk.x = pack_bf16(acc[c][0] * rstd * w[0], acc[c][1] * rstd * w[1]); pk.y = pack_bf16(acc[c][2] * rstd * w[2], acc[c][3] * rstd * w[3]);
+        pk.z = pack_bf16(acc[c][4] * rstd * w[4], acc[c][5] * rstd * w[5]); pk.w = pack_bf16(acc[c][6] * rstd * w[6], acc[c][7] * rstd * w[7]);
+        reinterpret_cast<uint4*>(norm_out + static_cast<long long>(row) * d)[i] = pk;
+      }
+    }
+  }
+  // 3. the last CTA to leave advances the sequence number for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(arrive_counter + 1, 1u);
+    if (t == gridDim.x - 1) { arrive_counter[1] = 0; __threadfence(); *seq_counter = seq; }
+  }
+}
+
+}  // namespace comm
+}  // namespace dewb
+
+// buf_ptrs: the W symmetric staging buffers (two halves of `half_stride` elements each, used alternately);
+// `partial` is this rank's local [rows, d] partial sum; `counters`: device uint32[3] = {sequence, arrive, leave},
+// zero-initialised once; out tensors are local.
+extern "C" int dewb_allreduce_rows(const unsigned long long* buf_ptrs, const unsigned long long* flag_ptrs,
+                                   const void* partial, const void* residual, const void* norm_w, void* sum_out,
+                                   void* norm_out, int rows, int d, float eps, int rank, int world,
+                                   unsigned int* counters, long long half_stride, int slot,
+                                   unsigned long long limit_ns, int* err, void* stream) {
+  if (d % 8 != 0 || d > 8192 || world < 1 || world > MAX_RANKS) return -3;
+  if (rows <= 0) return 0;
+  const int blocks = rows < 296 ? rows : 296;      // every CTA must be resident: they wait on one another's staging
+  allreduce_rows_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_peers(buf_ptrs, world), make_peers(flag_ptrs, world), reinterpret_cast<const __nv_bfloat16*>(partial),
+      reinterpret_cast<const __nv_bfloat16*>(residual), reinterpret_cast<const __nv_bfloat16*>(norm_w),
+      reinterpret_cast<__nv_bfloat16*>(sum_out), reinterpret_cast<__nv_bfloat16*>(norm_out), rows, d, eps, rank, world,
+      counters, counters + 1, half_stride, slot, limit_ns, err);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -109,18 +109,26 @@ class DecoderLayer(nn.Module):
             self.mlp = SwiGLU(cfg.emb_features, cfg.mlp_features or 4 * cfg.emb_features, init_std=cfg.init_std,
                               dtype=dtype, device=device)
         self.sparse = sparse
+        self.tp = None          # set by parallel.tp.tensor_parallelize: branches are then partial sums over ranks
+
+    def _norm(self, norm, h, branch):
+        """Add the pending branch into the stream and normalise; under tensor parallelism the branch is a partial sum
+        and the all-reduce is fused with the add and the norm."""
+        if self.tp is not None:
+            return self.tp.reduce_add_norm(branch, h, norm.weight, norm.eps)
+        return norm(h, branch)
 
     def forward(self, h, branch, cos, sin, positions, segment_ids, cache):
         """(stream, pending branch) -> (stream, pending branch); the branch is added by the next norm."""
         if branch is None:
             n = self.input_norm(h)
         else:
-            n, h = self.input_norm(h, branch)
+            n, h = self._norm(self.input_norm, h, branch)
         if self.kind in ("attention", "local"):
             a = self.mixer(n, cos, sin, positions, segment_ids, cache, self.index)
         else:
             a = self.mixer(n, segment_ids=segment_ids, cache=cache, layer=self.index)
-        n, h = self.post_norm(h, a)
+        n, h = self._norm(self.post_norm, h, a)
         return h, self.mlp(n)
 
 
@@ -163,14 +171,34 @@ class CausalTransformer(nn.Module):
                 h, branch = ckpt.checkpoint(layer, h, branch, cos, sin, positions, segment_ids, cache, use_reentrant=False)
             else:
                 h, branch = layer(h, branch, cos, sin, positions, segment_ids, cache)
-        n, _ = self.final_norm(h, branch)
+        tp = getattr(self, "tp", None)
+        if tp is not None:
+            n, _ = tp.reduce_add_norm(branch, h, self.final_norm.weight, self.final_norm.eps)
+        else:
+            n, _ = self.final_norm(h, branch)
         return n
 
     def logits(self, hidden):
+        tp_head = getattr(self, "tp_head", None)
+        if tp_head is not None:
+            # vocabulary-parallel head: this rank's slice of the logits, gathered along the vocabulary
+            local = ops.linear(hidden, tp_head)
+            if self.tp.world == 1:
+                return local
+            parts = [torch.empty_like(local) for _ in range(self.tp.world)]
+            torch.distributed.all_gather(parts, local.contiguous(), group=self.tp.group)
+            return torch.cat(parts, -1)
         out = ops.linear(hidden, self.head_weight())
         if self.config.logit_softcap > 0:
             out = self.config.logit_softcap * torch.tanh(out.float() / self.config.logit_softcap)
         return out
+
+    def next_tokens_greedy(self, hidden: torch.Tensor) -> torch.Tensor:
+        """argmax of the head over ``hidden [R, d]`` - under tensor parallelism without gathering the logits."""
+        tp_head = getattr(self, "tp_head", None)
+        if tp_head is not None and self.config.logit_softcap == 0:
+            return self.tp.argmax_vocab_parallel(ops.linear(hidden, tp_head))
+        return self.logits(hidden).argmax(-1)
 
     def forward(self, tokens, train: bool = False, decode: bool = False, positions=None, segment_ids=None, cache=None,
                 return_hidden: bool = False):

@@ -51,6 +51,11 @@ _GEMM.kernels = [
 ]
 
 
+# Measured cell: with fewer than ~24 output tiles of 128x256 (decode-sized products, e.g. 128 x 768) the persistent
+# kernel leaves most SMs idle; the library's split-K kernels take those calls.
+_GEMM.declared[("skinny",)] = "cublas"
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
          alpha: float = 1.0, max_ctas: int = 0, kernel: Optional[str] = None) -> torch.Tensor:
@@ -72,7 +77,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     case = dict(dtype=a.dtype if a.dtype == b.dtype else None, lda=a.stride(0), ldb=b.stride(0), ldd=out.stride(0),
                 aligned=(a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0),
                 inner_contig=(a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1), M=M, N=N, K=K)
-    which = _GEMM.select(case, forced=kernel)
+    tiles = ((M + 127) // 128) * ((N + 255) // 256)
+    cell = ("skinny",) if tiles < 24 else None
+    which = _GEMM.select(case, forced=kernel, cell=cell)
     if which == "cublas":
         return _gemm_reference_cuda(a, b, a_mn, b_mn, alpha, out, accumulate)
     epi = {(torch.bfloat16, False): 0, (torch.float32, False): 1, (torch.float32, True): 2,

@@ -3,6 +3,13 @@ from .solvers import (DDIM, DDPM, DEIS, KDPM2, LMS, PNDM, RK4, TCD, Consistency,
                       DPMSolverSinglestep, Euler, EulerAncestral, Heun, MultiStepDPM, Solver, UniPC, SOLVERS)
 from .walks import sample, walk_and_decode
 
-__all__ = ["sample", "walk_and_decode", "Solver", "SOLVERS", "Euler", "EulerAncestral", "Heun", "RK4", "KDPM2",
+def __getattr__(name):
+    if name in ("generate", "Sampling", "Generation", "Sample", "Beam", "Speculative", "transform_logits"):
+        from . import text
+        return getattr(text, name)
+    raise AttributeError(name)
+
+
+__all__ = ["generate", "Sampling", "Generation", "Sample", "Beam", "Speculative", "sample", "walk_and_decode", "Solver", "SOLVERS", "Euler", "EulerAncestral", "Heun", "RK4", "KDPM2",
            "MultiStepDPM", "LMS", "DDPM", "DDIM", "PNDM", "Consistency", "TCD", "DPMSolverMultistep",
            "DPMSolverSinglestep", "DEIS", "UniPC", "DPMSolverSDE", "CFG", "CFGPlusPlus", "APG", "Autoguidance", "Guidance"]

@@ -1,0 +1,33 @@
+"""Tensor parallelism: sharded model == full model, on 2 CPU ranks (gloo) and, with GPUs, through the fused peer-memory
+all-reduce + residual + RMSNorm kernel."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+WORKER = os.path.join(os.path.dirname(__file__), "workers", "tp_worker.py")
+
+
+def _run(world, backend, port):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), WORKER, backend]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2"))
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    return json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+
+
+def test_tensor_parallel_two_cpu_ranks():
+    r = _run(2, "gloo", 29631)
+    assert r["err"] < 1e-5 and r["same_tokens"]
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_tensor_parallel_two_gpus_fused_allreduce():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r = _run(2, "nccl", 29632)
+    assert r["err"] < 3e-2, r
