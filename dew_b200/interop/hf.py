@@ -1,0 +1,106 @@
+"""Hugging Face decoder checkpoints <-> ``CausalTransformer``: config translation, weight-name mapping (separate
+q / k / v and gate / up projections are fused here), safetensors load and save.
+
+Parity (capability): src/dew/interop (HF families <-> trees, safetensors), ``Pretrained.load``,
+``PretrainedDecoder.from_model(...).save`` (docs/concepts/inference.md:100-118).  Families covered: Llama, Qwen2 /
+Qwen3 (qk-norm), Mistral (window), Gemma-style (embed scaling) share this mapping.
+"""
+from __future__ import annotations
+
+import json
+import os
+from pathlib import Path
+from typing import Any, Dict, Mapping, Optional
+
+import torch
+
+from ..checkpoints import tensors as TS
+from ..models.causal_transformer import CausalTransformer, TransformerConfig
+
+
+def config_from_hf(cfg: Mapping[str, Any]) -> TransformerConfig:
+    heads = cfg["num_attention_heads"]
+    arch = (cfg.get("architectures") or [""])[0].lower()
+    return TransformerConfig(
+        vocab_size=cfg["vocab_size"], emb_features=cfg["hidden_size"], num_layers=cfg["num_hidden_layers"], num_heads=heads,
+        num_kv_heads=cfg.get("num_key_value_heads", heads), head_dim=cfg.get("head_dim") or cfg["hidden_size"] // heads,
+        mlp_features=cfg["intermediate_size"], max_seq_len=cfg.get("max_position_embeddings", 4096),
+        rope_theta=cfg.get("rope_theta", 10000.0), rope_scaling=cfg.get("rope_scaling"), norm_eps=cfg.get("rms_norm_eps", 1e-6),
+        qk_norm="qwen3" in arch, tie_embeddings=cfg.get("tie_word_embeddings", False), window=cfg.get("sliding_window"),
+        embed_scale="gemma" in arch)
+
+
+def config_to_hf(c: TransformerConfig, architecture: str = "LlamaForCausalLM") -> Dict[str, Any]:
+    return {"architectures": [architecture], "vocab_size": c.vocab_size, "hidden_size": c.emb_features, "num_hidden_layers": c.num_layers,
+            "num_attention_heads": c.num_heads, "num_key_value_heads": c.num_kv_heads or c.num_heads,
+            "head_dim": c.head_dim or c.emb_features // c.num_heads, "intermediate_size": c.mlp_features,
+            "max_position_embeddings": c.max_seq_len, "rope_theta": c.rope_theta, "rope_scaling": c.rope_scaling,
+            "rms_norm_eps": c.norm_eps, "tie_word_embeddings": c.tie_embeddings, "hidden_act": "silu", "torch_dtype": "bfloat16"}
+
+
+def from_hf_state(model: CausalTransformer, hf: Mapping[str, torch.Tensor]) -> None:
+    """Copy HF tensors into ``model`` (fusing q|k|v and gate|up)."""
+    def put(p, t):
+        with torch.no_grad():
+            p.copy_(t.to(p.dtype))
+    put(model.embed.weight, hf["model.embed_tokens.weight"])
+    for i, layer in enumerate(model.layers):
+        pre = f"model.layers.{i}."
+        put(layer.input_norm.weight, hf[pre + "input_layernorm.weight"])
+        put(layer.post_norm.weight, hf[pre + "post_attention_layernorm.weight"])
+        a = layer.mixer
+        put(a.qkv_proj.weight, torch.cat([hf[pre + f"self_attn.{n}_proj.weight"] for n in "qkv"], 0))
+        put(a.o_proj.weight, hf[pre + "self_attn.o_proj.weight"])
+        if a.q_norm is not None and pre + "self_attn.q_norm.weight" in hf:
+            put(a.q_norm.weight, hf[pre + "self_attn.q_norm.weight"])
+            put(a.k_norm.weight, hf[pre + "self_attn.k_norm.weight"])
+        put(layer.mlp.gate_up_proj.weight, torch.cat([hf[pre + "mlp.gate_proj.weight"], hf[pre + "mlp.up_proj.weight"]], 0))
+        put(layer.mlp.down_proj.weight, hf[pre + "mlp.down_proj.weight"])
+    put(model.final_norm.weight, hf["model.norm.weight"])
+    if model.head is not None:
+        put(model.head.weight, hf.get("lm_head.weight", hf["model.embed_tokens.weight"]))
+
+
+def to_hf_state(model: CausalTransformer) -> Dict[str, torch.Tensor]:
+    c = model.config
+    H, Hkv = c.num_heads, c.num_kv_heads or c.num_heads
+    D = c.head_dim or c.emb_features // c.num_heads
+    out = {"model.embed_tokens.weight": model.embed.weight.detach(), "model.norm.weight": model.final_norm.weight.detach()}
+    for i, layer in enumerate(model.layers):
+        pre = f"model.layers.{i}."
+        out[pre + "input_layernorm.weight"] = layer.input_norm.weight.detach()
+        out[pre + "post_attention_layernorm.weight"] = layer.post_norm.weight.detach()
+        w = layer.mixer.qkv_proj.weight.detach()
+        out[pre + "self_attn.q_proj.weight"], out[pre + "self_attn.k_proj.weight"], out[pre + "self_attn.v_proj.weight"] = \
+            w[: H * D], w[H * D:(H + Hkv) * D], w[(H + Hkv) * D:]
+        out[pre + "self_attn.o_proj.weight"] = layer.mixer.o_proj.weight.detach()
+        if layer.mixer.q_norm is not None:
+            out[pre + "self_attn.q_norm.weight"] = layer.mixer.q_norm.weight.detach()
+            out[pre + "self_attn.k_norm.weight"] = layer.mixer.k_norm.weight.detach()
+        gu = layer.mlp.gate_up_proj.weight.detach()
+        F_ = gu.shape[0] // 2
+        out[pre + "mlp.gate_proj.weight"], out[pre + "mlp.up_proj.weight"] = gu[:F_], gu[F_:]
+        out[pre + "mlp.down_proj.weight"] = layer.mlp.down_proj.weight.detach()
+    if model.head is not None:
+        out["lm_head.weight"] = model.head.weight.detach()
+    return {k: v.contiguous() for k, v in out.items()}
+
+
+class Pretrained:
+    @staticmethod
+    def load(directory: os.PathLike, dtype=None, device="cpu") -> CausalTransformer:
+        d = Path(directory)
+        cfg = config_from_hf(json.loads((d / "config.json").read_text()))
+        model = CausalTransformer(cfg, dtype=dtype, device=device)
+        state: Dict[str, torch.Tensor] = {}
+        for f in sorted(d.glob("*.safetensors")):
+            state.update(TS.load_file(f))
+        from_hf_state(model, state)
+        return model
+
+    @staticmethod
+    def save(model: CausalTransformer, directory: os.PathLike, architecture: str = "LlamaForCausalLM") -> None:
+        d = Path(directory)
+        d.mkdir(parents=True, exist_ok=True)
+        (d / "config.json").write_text(json.dumps(config_to_hf(model.config, architecture), indent=1))
+        TS.save_file(to_hf_state(model), d / "model.safetensors", metadata={"format": "pt"})

@@ -209,7 +209,7 @@ def short_conv_reference(x, w, bias=None, activation: bool = True, segment_ids=N
 def short_conv(x, w, bias=None, activation: bool = True, segment_ids=None, initial=None):
     from . import library as L
     if L.use_cuda(x) and x.dtype == torch.bfloat16 and segment_ids is None and initial is None and hasattr(L.load(), "dewb_short_conv_fwd") \
-            and x.shape[-1] % 8 == 0 and w.shape[1] <= 4:
+            and x.shape[-1] % 8 == 0 and 2 <= w.shape[1] <= 4:
         from .conv import short_conv_cuda
         return short_conv_cuda(x, w, bias, activation)
     return short_conv_reference(x, w, bias, activation, segment_ids, initial)

@@ -1,0 +1,69 @@
+"""LoRA, quantisation, HF interop, evaluation metrics."""
+import torch
+
+from dew_b200.eval import metrics as M
+from dew_b200.interop.hf import Pretrained, from_hf_state, to_hf_state
+from dew_b200.models import CausalTransformer
+from dew_b200.nn.lora import LoRALinear, apply_lora, lora_state, merge_all
+from dew_b200.nn.quantization import Quantization, dequantize_weight, fake_quant, quantize_variables, quantize_weight
+from dew_b200.utils.trees import module_variables
+
+
+def _lm(**kw):
+    torch.manual_seed(0)
+    return CausalTransformer(vocab_size=64, emb_features=32, num_layers=2, num_heads=4, num_kv_heads=2, mlp_features=64, max_seq_len=32,
+                             tie_embeddings=False, **kw)
+
+
+def test_lora_trains_only_adapters_and_merges():
+    m = _lm()
+    x = torch.randint(0, 64, (2, 8))
+    before = m(x)
+    wrapped = apply_lora(m, ("qkv_proj", "down_proj"), rank=4)
+    assert len(wrapped) == 4 and all(("lora_" in n) == p.requires_grad for n, p in m.named_parameters())
+    assert torch.allclose(m(x), before, atol=1e-6)                      # B starts at zero
+    for mod in m.modules():
+        if isinstance(mod, LoRALinear):
+            torch.nn.init.normal_(mod.lora_b, std=0.05)
+    y = m(x)
+    merge_all(m)
+    assert torch.allclose(m(x), y, atol=1e-4) and len(lora_state(m)) == 8
+
+
+def test_quantisation_roundtrips():
+    torch.manual_seed(1)
+    w = torch.randn(64, 96)
+    for kind, tol in (("int8", 0.01), ("float8_e4m3fn", 0.04), ("nvfp4", 0.12)):
+        d = dequantize_weight(quantize_weight(w, kind), kind)
+        assert d.shape == w.shape and float((d - w).norm() / w.norm()) < tol, kind
+    g = fake_quant(w.clone().requires_grad_(), "int8")
+    assert g.requires_grad
+    m = _lm()
+    q = quantize_variables(module_variables(m), Quantization("int8", min_size=1024))
+    from dew_b200.utils.trees import flatten
+    changed = [k for k, v in flatten(q).items() if not torch.equal(v, flatten(module_variables(m))[k])]
+    assert changed and not any("embed" in k or "norm" in k for k in changed)
+
+
+def test_hf_roundtrip(tmp_path):
+    m = _lm(qk_norm=False)
+    Pretrained.save(m, tmp_path / "hf")
+    m2 = Pretrained.load(tmp_path / "hf")
+    x = torch.randint(0, 64, (2, 8))
+    assert torch.allclose(m(x), m2(x), atol=1e-6)
+    hf = to_hf_state(m)
+    assert hf["model.layers.0.self_attn.k_proj.weight"].shape == (2 * 8, 32)
+    m3 = _lm(qk_norm=False)
+    from_hf_state(m3, hf)
+    assert torch.allclose(m(x), m3(x), atol=1e-6)
+
+
+def test_metrics():
+    torch.manual_seed(2)
+    a = torch.rand(4, 16, 16, 3) * 2 - 1
+    assert float(M.psnr(a, a + 0.01).min()) > 40 and float(M.ssim(a, a).min()) > 0.999
+    assert float(M.ssim(a, torch.rand_like(a) * 2 - 1).max()) < 0.5
+    f = torch.randn(500, 8)
+    assert M.frechet_distance(f, f) < 1e-6 and M.frechet_distance(f, f + 3) > 50
+    p = torch.softmax(torch.randn(100, 5) * 3, -1)
+    assert 0 <= M.expected_calibration_error(p, p.argmax(-1)) <= 1

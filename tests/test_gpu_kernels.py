@@ -321,3 +321,24 @@ def test_paged_decode_attention(quantized, page_size, D, Hq, Hkv):
     out = store.decode_attention(0, q, lengths)
     ref = paged_attention_reference(store, 0, q.float(), lengths, 1.0 / math.sqrt(D))
     assert rel_err(out, ref) <= 2e-2, rel_err(out, ref)
+
+
+@pytest.mark.parametrize("B,T,C,K,act,bias", [(2, 200, 64, 4, True, False), (1, 1000, 4096 + 8, 4, True, True), (3, 65, 128, 3, False, True)])
+def test_short_conv_forward_backward(B, T, C, K, act, bias):
+    from dew_b200.ops import scan
+    torch.manual_seed(T)
+    x = torch.randn(B, T, C, device=DEV).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(C, K, device=DEV) * 0.5).requires_grad_()
+    b = torch.randn(C, device=DEV).requires_grad_() if bias else None
+    y = scan.short_conv(x, w, b, act)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    bf = b.detach().clone().requires_grad_() if bias else None
+    ref = scan.short_conv_reference(xf, wf, bf, act)
+    ref.backward(dy.float())
+    assert rel_err(y, ref) <= 2 * bf16_floor(ref) + 1e-3
+    assert rel_err(x.grad, xf.grad) <= 2 * bf16_floor(xf.grad) + 2e-3
+    assert rel_err(w.grad, wf.grad) <= 1e-2
+    if bias:
+        assert rel_err(b.grad, bf.grad) <= 1e-2
