@@ -1,0 +1,54 @@
+"""Configuration overrides, sweeps, the CLI's train / inspect commands, and pipeline(dir) from a run record."""
+import json
+
+import pytest
+import torch
+
+from dew_b200.cli import main as cli
+from dew_b200.config import RunConfig, apply_overrides, set_path, sweep
+
+
+def _recipe(tmp_path, **trainer):
+    cfg = RunConfig()
+    cfg.model.fields = dict(vocab_size=259, emb_features=32, num_layers=1, num_heads=4, mlp_features=64, max_seq_len=64)
+    cfg.data.seq_len, cfg.data.batch = 16, 4
+    cfg.tokenizer = "byte"
+    for k, v in trainer.items():
+        setattr(cfg.trainer, k, v)
+    p = tmp_path / "recipe.json"
+    cfg.save(p)
+    return p
+
+
+def test_overrides_and_unknown_paths():
+    cfg = apply_overrides(RunConfig(), ["trainer.mesh.fsdp=8", "optimizer.learning_rate=1e-3", "model.fields.num_layers=3", "trainer.resume=never"])
+    assert cfg.trainer.mesh.fsdp == 8 and cfg.optimizer.learning_rate == 1e-3 and cfg.model.fields["num_layers"] == 3
+    with pytest.raises(KeyError):
+        set_path(cfg, "trainer.no_such_field", 1)
+    again = RunConfig.from_record(cfg.to_record())
+    assert again.trainer.mesh.fsdp == 8 and not cfg.changes(again)
+    again.model.fields["num_layers"] = 5
+    assert cfg.changes(again) == {"fields.num_layers": (3, 5)}
+    points = list(sweep(RunConfig(), {"optimizer.learning_rate": [1e-3, 3e-4], "trainer.key": [0, 1]}))
+    assert len(points) == 4 and len({p.trainer.name for p in points}) == 4
+
+
+def test_cli_train_writes_checkpoint_and_pipeline_reads_it(tmp_path, capsys):
+    recipe = _recipe(tmp_path, steps=4, log_every=2, checkpoint_dir=str(tmp_path / "run"))
+    assert cli.main(["train", str(recipe), "--cpu", "--set", "optimizer.learning_rate=1e-3"]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["step"] == 4
+    from dew_b200.inference import pipeline
+    task = pipeline(tmp_path / "run")
+    gen = task(["hello"], max_new_tokens=3)
+    assert int(gen.lengths[0]) == 8 and isinstance(gen.text[0], str)
+    assert cli.main(["export", str(tmp_path / "run"), str(tmp_path / "hf")]) == 0
+    assert (tmp_path / "hf" / "model.safetensors").exists()
+
+
+def test_cli_inspect_reports_placement(tmp_path, capsys):
+    recipe = _recipe(tmp_path)
+    assert cli.main(["inspect", str(recipe), "--devices", "8", "--set", "trainer.mesh.fsdp=8"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["mesh"]["fsdp"] == 8 and rep["fits"]
+    assert cli.main(["launch", "--dry-run", "--processes-per-host", "2", "--", "python", "x.py"]) == 0
