@@ -87,6 +87,15 @@ __device__ bool wait_all_peers(const uint32_t* my_flags, int slot, int world, ui
   return ok_flag != 0;
 }
 
+// True (for the whole CTA) when an earlier launch has already reported a timed-out wait: later launches leave at once
+// instead of each waiting out its own limit.
+__device__ bool status_poisoned(const int* err) {
+  __shared__ int poisoned;
+  if (threadIdx.x == 0) poisoned = *reinterpret_cast<const volatile int*>(err);
+  __syncthreads();
+  return poisoned != 0;
+}
+
 struct AdamArgs {
   float lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, ema_decay;
 };
@@ -102,6 +111,7 @@ rs_adamw_ag_kernel(Peers grads, Peers params, Peers flags, float* __restrict__ m
                    long long shard_len, long long decay_end, int rank, int world, AdamArgs a, uint32_t seq,
                    int slot_ready, int slot_done, unsigned int* __restrict__ block_counter,
                    unsigned long long limit_ns, int mode, int skip_nonfinite, int* __restrict__ err) {
+  if (status_poisoned(err)) return;
   uint32_t* my_flags = reinterpret_cast<uint32_t*>(flags.p[rank]);
   if (mode != 2) {
     // 1. announce + wait: every peer's gradient buffer for this unit is final
@@ -214,6 +224,7 @@ rs_adamw_ag_kernel(Peers grads, Peers params, Peers flags, float* __restrict__ m
 // Stand-alone bounded wait on one flag slot (used before a unit's forward: all peers have pushed its new weights).
 __global__ void wait_flags_kernel(const uint32_t* my_flags, int slot, int world, uint32_t seq,
                                   unsigned long long limit_ns, int* err) {
+  if (status_poisoned(err)) return;
   wait_all_peers(my_flags, slot, world, seq, limit_ns, err);
 }
 
@@ -325,6 +336,7 @@ allreduce_rows_kernel(Peers bufs, Peers flags, const __nv_bfloat16* __restrict__
                       unsigned long long limit_ns, int* __restrict__ err) {
   __shared__ float red[32];
   __shared__ unsigned int ticket;
+  if (status_poisoned(err)) return;
   // The sequence number lives on the device (so a captured CUDA graph can replay this launch): every CTA reads it
   // before any CTA can have advanced it, because it is advanced by the last CTA to leave.
   const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(seq_counter) + 1;

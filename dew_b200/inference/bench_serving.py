@@ -101,8 +101,14 @@ def main(argv=None):
             with open(args.out, "a") as f:
                 f.write(json.dumps(out) + "\n")
     if world > 1:
+        # Leave through a barrier and a hard exit: tearing the NCCL communicator down after its collectives were
+        # captured into a CUDA graph can block, and nothing remains to be flushed but stdout.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+    import sys
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":

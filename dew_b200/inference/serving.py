@@ -242,12 +242,24 @@ class Server:
         if not hasattr(self, "_in_pos"):
             self._in_pos = torch.full((self.slots,), -1, dtype=torch.long, device=self.device)
             self._prev = torch.zeros(self.slots, dtype=torch.long, device=self.device)
-            self._host_pos = torch.full((self.slots,), -1, dtype=torch.long, pin_memory=self.device.type == "cuda")
+            # The device runs behind the host, so a pinned staging buffer may still be waiting to be copied when the
+            # next step is prepared: rotate over more buffers than steps can be in flight.
+            self._host_ring = [torch.full((self.slots,), -1, dtype=torch.long, pin_memory=self.device.type == "cuda") for _ in range(8)]
+            self._ring_events = [None] * 8
+            self._ring_at = 0
+        self._ring_at = (self._ring_at + 1) % len(self._host_ring)
+        if self._ring_events[self._ring_at] is not None:
+            self._ring_events[self._ring_at].synchronize()
+        self._host_pos = self._host_ring[self._ring_at]
         self._host_pos.fill_(-1)
         for s, r in active:
             if r.generated + 1 < r.ticket.max_new_tokens:
                 self._host_pos[s] = len(r.ticket.prompt) + r.generated
         self._in_pos.copy_(self._host_pos, non_blocking=True)
+        if self.device.type == "cuda":
+            e = torch.cuda.Event()
+            e.record()
+            self._ring_events[self._ring_at] = e
         greedy = all((r.ticket.sampling or self.sampling).greedy for _, r in active)
         if bool((self._host_pos >= 0).any()):
             if self.cuda_graph and greedy:

@@ -1,0 +1,19 @@
+"""Expert parallelism over 2 and 4 CPU ranks equals the unsharded mixture-of-experts layer."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+WORKER = os.path.join(os.path.dirname(__file__), "workers", "ep_worker.py")
+
+
+@pytest.mark.parametrize("world,port", [(2, 29641), (4, 29642)])
+def test_expert_parallel_matches_single_process(world, port):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), WORKER]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-3000:]
+    r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    assert r["out_err"] < 1e-5 and r["dx_err"] < 1e-4 and r["dw_err"] < 1e-4, r

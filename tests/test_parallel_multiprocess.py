@@ -1,0 +1,31 @@
+"""Sequence-parallel attention (Ulysses and gathered keys), GPipe and DiLoCo on 2 CPU ranks."""
+import json
+import os
+import subprocess
+import sys
+
+from dew_b200.parallel.pp import stage_slices
+from dew_b200.parallel.sp import all_to_all_moves_less, stripe, unstripe
+
+import torch
+
+WORKER = os.path.join(os.path.dirname(__file__), "workers", "par_worker.py")
+
+
+def test_two_rank_strategies():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29651", WORKER]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-3000:]
+    r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    for key in ("ulysses_out", "ulysses_dq", "ulysses_dk", "gathered_out", "pp_grad", "pp_loss", "diloco_spread"):
+        assert r[key] < 1e-4, (key, r)
+    assert r["diloco_took"] == 1.0
+
+
+def test_helpers():
+    assert [list(s) for s in stage_slices(7, 3)] == [[0, 1, 2], [3, 4], [5, 6]]
+    x = torch.arange(16.0)[None, :, None]
+    assert torch.equal(unstripe(stripe(x, 2), 2), x)
+    assert stripe(x, 2)[0, :, 0].tolist()[:8] == [0, 1, 2, 3, 12, 13, 14, 15]
+    assert all_to_all_moves_less(8192, 32, 8, 128, 8) and not all_to_all_moves_less(8192, 64, 1, 128, 2)
