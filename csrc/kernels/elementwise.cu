@@ -7,6 +7,7 @@
 // src/dew/averaging.py:116-139 (ema_update).
 #include <cstdint>
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 namespace dewb {
@@ -652,6 +653,36 @@ __global__ void cast_f32_bf16_kernel(const float* __restrict__ src, bf16* __rest
     dst[i] = __float2bfloat16(src[i]);
 }
 
+// Row-wise fp8 quantisation: scale[row] = absmax(row) / 448; q = e4m3(x / scale). One warp per row.
+__global__ void quantize_rows_fp8_kernel(const bf16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale,
+                                         long long rows, int d) {
+  const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * d);
+  const int nvec = d >> 3;
+  float mx = 0.f;
+  for (int i = lane; i < nvec; i += 32) {
+    float f[8]; unpack8(xr[i], f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(f[j]));
+  }
+  mx = warp_max(mx);
+  const float sc = mx > 0.f ? mx / 448.f : 1.f;
+  if (lane == 0) scale[row] = sc;
+  const float inv = 1.f / sc;
+  for (int i = lane; i < nvec; i += 32) {
+    float f[8]; unpack8(xr[i], f);
+    uint32_t lo4 = 0, hi4 = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      lo4 |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(f[j] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+      hi4 |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(f[4 + j] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+    }
+    reinterpret_cast<uint2*>(q + row * d)[i] = make_uint2(lo4, hi4);
+  }
+}
+
 static inline int grid_for(long long work, int threads, int cap = 148 * 16) {
   long long b = (work + threads - 1) / threads;
   if (b < 1) b = 1;
@@ -809,6 +840,15 @@ extern "C" int dewb_adamw(float* p, float* m, float* v, const void* g, int g_is_
     adamw_kernel<float><<<blocks, 256, 0, STREAM(stream)>>>(p, m, v, (const float*)g, (bf16*)p_bf16, ema, n, lr, beta1,
                                                             beta2, eps, wd, bc1, bc2, grad_scale, clip, ema_decay,
                                                             skip_nonfinite);
+  return LAST_ERR();
+}
+
+// x [rows, d] bf16 (d % 8 == 0) -> q [rows, d] e4m3 bytes and scale [rows] fp32.
+extern "C" int dewb_quantize_rows_fp8(const void* x, void* q, float* scale, long long rows, int d, void* stream) {
+  if (d % 8 != 0) return -3;
+  if (rows <= 0) return 0;
+  quantize_rows_fp8_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, STREAM(stream)>>>(
+      (const bf16*)x, (uint8_t*)q, scale, rows, d);
   return LAST_ERR();
 }
 

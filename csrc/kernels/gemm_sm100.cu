@@ -56,6 +56,8 @@ struct GroupArgs {
   int b_rows_per_group;
   int groups;
   long long d_group_stride;
+  const float* row_scale;   // fp8: per-row scale of A (length M), or null
+  const float* col_scale;   // fp8: per-row scale of the stacked B operand (indexed by B's row), or null
 };
 
 struct Tile {
@@ -78,10 +80,10 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   n_blk = r / gsize;
 }
 
-__device__ __forceinline__ Tile decode_tile(int t, int tiles_m, int tiles_n, int K, const GroupArgs& ga) {
+__device__ __forceinline__ Tile decode_tile(int t, int tiles_m, int tiles_n, int K, const GroupArgs& ga, int bk = BK) {
   Tile ti;
   int m_blk, n_blk;
-  ti.b_row0 = 0; ti.k_begin = 0; ti.k_iters = (K + BK - 1) / BK; ti.d_off = 0; ti.skip = false;
+  ti.b_row0 = 0; ti.k_begin = 0; ti.k_iters = (K + bk - 1) / bk; ti.d_off = 0; ti.skip = false;
   if (ga.mode == 2) {
     const int per = tiles_m * tiles_n;
     const int g = t / per;
@@ -103,7 +105,9 @@ __device__ __forceinline__ Tile decode_tile(int t, int tiles_m, int tiles_n, int
   return ti;
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+// FP8 = true: operands are e4m3 bytes (K-major only), 128 elements per 128-byte swizzle row, tcgen05 kind::f8f6f4
+// with K = 32 per instruction; the epilogue applies the row-wise scales of both operands.
+template <bool A_MN, bool B_MN, int EPI, bool FP8 = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  void* __restrict__ Dptr, int M, int N, int K, long long ldd, float alpha, const GroupArgs ga,
@@ -152,7 +156,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       long long issued = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const Tile ti = decode_tile(t, tiles_m, tiles_n, K, ga);
+        const Tile ti = decode_tile(t, tiles_m, tiles_n, K, ga, FP8 ? 2 * BK : BK);
         if (ti.skip || ti.k_iters == 0) continue;
         const int m0 = ti.m0, n0 = ti.n0;
         for (int k = 0; k < ti.k_iters; ++k) {
@@ -160,7 +164,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           mbar_expect_tx(&sh->full[stage], STAGE_BYTES);
-          const int k0 = ti.k_begin + k * BK;
+          const int k0 = ti.k_begin + k * (FP8 ? 2 * BK : BK);
           if (!A_MN) {
             tma_load_2d(sa, &tma_a, &sh->full[stage], k0, m0);
           } else {
@@ -190,12 +194,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc = FP8 ? make_idesc(BM, BN, 0, 0, 0, 0) : make_idesc(BM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0; uint32_t phase = 0;
       int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const Tile ti = decode_tile(t, tiles_m, tiles_n, K, ga);
+        const Tile ti = decode_tile(t, tiles_m, tiles_n, K, ga, FP8 ? 2 * BK : BK);
         if (ti.skip || ti.k_iters == 0) continue;
         const int k_iters = ti.k_iters;
         if (!mbar_wait(&sh->tmem_empty[acc], acc_phase ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); ok = false; break; }
@@ -210,7 +214,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           for (int kk = 0; kk < BK / 16; ++kk) {
             const uint64_t da = A_MN ? make_sdesc_sw128(sa + kk * 2048, 8192, 1024) : make_sdesc_sw128(sa + kk * 32, 16, 1024);
             const uint64_t db = B_MN ? make_sdesc_sw128(sb + kk * 2048, 8192, 1024) : make_sdesc_sw128(sb + kk * 32, 16, 1024);
-            umma_bf16_ss(d_tmem, da, db, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+            if (FP8) umma_f8_ss(d_tmem, da, db, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+            else umma_bf16_ss(d_tmem, da, db, idesc, (k > 0 || kk > 0) ? 1u : 0u);
           }
           umma_commit(&sh->empty[stage]);   // frees the stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -226,7 +231,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      const Tile ti = decode_tile(t, tiles_m, tiles_n, K, ga);
+      const Tile ti = decode_tile(t, tiles_m, tiles_n, K, ga, FP8 ? 2 * BK : BK);
       if (ti.skip) continue;
       const int row = ti.m0 + q * 32 + lane;
       const int n0 = ti.n0;
@@ -249,6 +254,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
         const int col = n0 + c * 32;
+        if (FP8 && row < M && col < N) {
+          const float rs = ga.row_scale != nullptr ? ga.row_scale[row] : 1.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float cs = (ga.col_scale != nullptr && col + i < N) ? ga.col_scale[ti.b_row0 + col + i] : 1.f;
+            r[i] = __float_as_uint(__uint_as_float(r[i]) * rs * cs);
+          }
+        }
         if (row < M && col < N) {
           const bool full = (col + 32 <= N);
           if (EPI == EPI_BF16 || EPI == EPI_BF16_ACC) {
@@ -350,6 +363,17 @@ static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, voi
   return -2;
 }
 
+static int launch_fp8(const CUtensorMap& ta, const CUtensorMap& tb, void* D, int M, int N, int K, long long ldd, float alpha,
+                      const GroupArgs& ga, int* err, int sms, cudaStream_t stream) {
+  auto kern = gemm_bf16_kernel<false, false, EPI_BF16, true>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, THREADS, SMEM_BYTES, stream>>>(ta, tb, D, M, N, K, ldd, alpha, ga, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
 static int dispatch(int a_mn, int b_mn, int epi, const CUtensorMap& ta, const CUtensorMap& tb, void* D, int M, int N,
                     int K, long long ldd, float alpha, const GroupArgs& ga, int* err, int sms, cudaStream_t stream) {
   if (!a_mn && !b_mn) return launch_epi<false, false>(epi, ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
@@ -399,7 +423,7 @@ extern "C" int dewb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
   if (r) return 2000 + r;
   int sms = sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-  GroupArgs ga{nullptr, nullptr, 0, 0, 1, 0};
+  GroupArgs ga{nullptr, nullptr, 0, 0, 1, 0, nullptr, nullptr};
   return dispatch(a_mn, b_mn, epi, ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
 }
 
@@ -423,7 +447,7 @@ extern "C" int dewb_gmm_bf16(const void* A, const void* B, void* D, const int* t
   if (!b_mn) r = make_tmap_2d(&tb, B, static_cast<uint64_t>(groups) * N, K, ldb, BN, BK, 2, true);
   else       r = make_tmap_2d(&tb, B, static_cast<uint64_t>(groups) * K, N, ldb, BK, 64, 2, true);
   if (r) return 2000 + r;
-  GroupArgs ga{tile_group, nullptr, 1, b_mn ? K : N, groups, 0};
+  GroupArgs ga{tile_group, nullptr, 1, b_mn ? K : N, groups, 0, nullptr, nullptr};
   return dispatch(0, b_mn, epi, ta, tb, D, M, N, K, ldd, alpha, ga, err, sm_count(), stream);
 }
 
@@ -444,6 +468,26 @@ extern "C" int dewb_tgmm_bf16(const void* A, const void* B, void* D, const int* 
   if (r) return 1000 + r;
   r = make_tmap_2d(&tb, B, R, N, ldb, BK, 64, 2, true);
   if (r) return 2000 + r;
-  GroupArgs ga{nullptr, group_offsets, 2, 0, groups, d_group_stride};
+  GroupArgs ga{nullptr, group_offsets, 2, 0, groups, d_group_stride, nullptr, nullptr};
   return dispatch(1, 1, epi, ta, tb, D, M, N, R, ldd, alpha, ga, err, sm_count(), stream);
+}
+
+// Row-wise scaled fp8 (e4m3) GEMM, dense or grouped rows: D[M,N] (bf16) = (A_q * a_scale[row]) * (B_q * b_scale[row of B])^T.
+//   A_q [M, K] and B_q [groups * N, K] are e4m3 bytes, K contiguous, K a multiple of 16; scales are fp32.
+//   tile_group: null for a dense product (groups = 1), else the group of each 128-row tile of A as in dewb_gmm_bf16.
+extern "C" int dewb_gemm_fp8(const void* A, const void* B, void* D, const float* a_scale, const float* b_scale,
+                             const int* tile_group, int M, int N, int K, int groups, long long lda, long long ldb,
+                             long long ldd, int* err, void* stream_ptr) {
+  using namespace dewb;
+  using namespace dewb::gemm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 16) || (ldb % 16) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  CUtensorMap ta, tb;
+  int r = make_tmap_2d(&ta, A, M, K, lda, BM, 2 * BK, 1, true);
+  if (r) return 1000 + r;
+  r = make_tmap_2d(&tb, B, static_cast<uint64_t>(groups) * N, K, ldb, BN, 2 * BK, 1, true);
+  if (r) return 2000 + r;
+  GroupArgs ga{tile_group, nullptr, tile_group != nullptr ? 1 : 0, N, groups, 0, a_scale, b_scale};
+  return launch_fp8(ta, tb, D, M, N, K, ldd, 1.f, ga, err, sm_count(), stream);
 }

@@ -80,6 +80,10 @@ class ExpertMLP(nn.Module):
         return 3 * self.features * self.hidden
 
     def forward(self, xs: torch.Tensor, layout: G.GroupLayout) -> torch.Tensor:
+        if getattr(self, "fp8", False) and xs.dtype == torch.bfloat16:
+            from ..ops.fp8 import fp8_grouped_linear
+            h = fp8_grouped_linear(xs, self.gate_up, layout)
+            return fp8_grouped_linear(ops.packed_swiglu(h), self.down, layout)
         h = G.grouped_linear(xs, self.gate_up, layout)
         return G.grouped_linear(ops.packed_swiglu(h), self.down, layout)
 
@@ -91,6 +95,7 @@ class SparseMLP(nn.Module):
         hidden = mix.expert_features or dense_hidden
         self.router = Router(features, mix, dtype=torch.float32, device=device)
         self.experts = ExpertMLP(features, hidden, mix.experts, init_std, dtype=dtype, device=device)
+        self.experts.fp8 = bool(mix.fp8)
         self.shared = SwiGLU(features, mix.shared_features, init_std, dtype=dtype, device=device) if mix.shared_features else None
         self.shared_gate = Linear(features, 1, axes=("embed", None), dtype=dtype, device=device) if (mix.shared_gate and mix.shared_features) else None
         self.last: Dict[str, Any] = {}

@@ -342,3 +342,38 @@ def test_short_conv_forward_backward(B, T, C, K, act, bias):
     assert rel_err(w.grad, wf.grad) <= 1e-2
     if bias:
         assert rel_err(b.grad, bf.grad) <= 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (1000, 264, 1024), (4096, 4096, 4096)])
+def test_fp8_rowwise_gemm(M, N, K):
+    from dew_b200.ops import fp8
+    torch.manual_seed(M)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    b = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    aq, asc = fp8.quantize_rows(a)
+    bq, bsc = fp8.quantize_rows(b)
+    # the quantiser itself: values round-trip within e4m3 precision, scales are absmax / 448
+    assert torch.allclose(asc, a.float().abs().amax(-1) / 448.0, rtol=1e-3)
+    out = fp8.gemm_fp8(aq, asc, bq, bsc)
+    exact_q = (aq.float() * asc[:, None]) @ (bq.float() * bsc[:, None]).t()           # what the kernel must compute
+    assert rel_err(out, exact_q) <= 1.5 * bf16_floor(exact_q) + 1e-4
+    ref = a.float() @ b.float().t()
+    assert rel_err(out, ref) < 0.06                                                   # fp8 quantisation error itself
+
+
+def test_fp8_grouped_linear_matches_bf16_path():
+    from dew_b200.ops import grouped as G
+    from dew_b200.ops.fp8 import fp8_grouped_linear
+    torch.manual_seed(5)
+    T, k, E, d, F = 500, 2, 8, 256, 384
+    ids = torch.randint(0, E, (T, k), device=DEV)
+    layout = G.group_layout(ids, E)
+    xs = G.permute(torch.randn(T, d, device=DEV).to(torch.bfloat16), layout, k).requires_grad_()
+    w = (torch.randn(E, F, d, device=DEV) / math.sqrt(d)).to(torch.bfloat16).requires_grad_()
+    y8 = fp8_grouped_linear(xs, w, layout)
+    y16 = G.grouped_linear(xs.detach(), w.detach(), layout)
+    used = torch.zeros(layout.rows, dtype=torch.bool, device=DEV)
+    used[layout.positions] = True
+    assert rel_err(y8[used], y16[used].float()) < 0.06
+    (y8 * used[:, None]).sum().backward()
+    assert xs.grad is not None and w.grad is not None and torch.isfinite(w.grad.float()).all()
