@@ -7,4 +7,10 @@ def __getattr__(name):
     if name in ("CausalTransformer", "Mixture", "TransformerConfig"):
         from . import causal_transformer as m
         return getattr(m, name)
+    if name in ("UNet", "UViT", "SimpleUDiT", "SimpleMMDiT", "VideoDiT", "HybridDiT"):
+        from . import diffusion_backbones as m
+        return getattr(m, name)
+    if name in ("KLAutoEncoder", "ViT"):
+        from . import autoencoders as m
+        return getattr(m, name)
     raise AttributeError(name)
