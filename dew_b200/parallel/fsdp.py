@@ -34,7 +34,7 @@ from ..objectives.base import Aux, Step, pool
 from ..ops import library as L
 from ..training.state import TrainState
 from ..utils import keys as K
-from ..utils.trees import module_path_to_tree_path, unflatten
+from ..utils.trees import flatten, module_path_to_tree_path, unflatten
 from .symm import SymmetricBuffer
 
 ALIGN = 64          # elements; keeps every parameter 128-byte aligned inside the flat buffer (TMA needs 16 bytes)
@@ -284,6 +284,97 @@ class FSDPEngine:
                 o = u.offsets[n]
                 out[module_path_to_tree_path(n)] = full[o:o + p.numel()].view(p.shape).clone()
         return out
+
+    # ------------------------------------------------------------------ checkpoints (layout-free full trees)
+    def export_state(self, state: TrainState, to: str = "cpu") -> Optional[TrainState]:
+        """Collective.  The state with whole (unsharded) fp32 trees keyed by parameter path, as a checkpoint stores it,
+        so a checkpoint written at one world size restores at another.  Units are gathered one at a time and moved to
+        ``to`` on rank 0 only; other ranks return None."""
+        keep = self.rank == 0
+
+        def whole(flat):
+            if flat is None:
+                return None
+            W = self.world
+            out: Dict[str, torch.Tensor] = {}
+            for u in self.units:
+                s = u.size // W
+                mine = flat[u.offset // W: u.offset // W + s]
+                if W > 1:
+                    full = torch.empty(u.size, dtype=flat.dtype, device=flat.device)
+                    dist.all_gather_into_tensor(full, mine.contiguous(), group=self.group)
+                else:
+                    full = mine
+                if keep:
+                    for n, p in u.params:
+                        o = u.offsets[n]
+                        out[module_path_to_tree_path(n)] = full[o:o + p.numel()].view(p.shape).to(to, copy=True)
+            return unflatten(out)
+
+        trees = {k: whole(v) for k, v in (("params", self.master), ("mu", self.m), ("nu", self.v), ("ema", self.ema))}
+        if not keep:
+            return None
+        import dataclasses as _dc
+        full = _dc.replace(state)
+        full.variables = {"params": trees["params"]}
+        full.opt_state = {"count": state.opt_state["count"].to(to) if isinstance(state.opt_state.get("count"), torch.Tensor) else state.opt_state.get("count"),
+                          "mu": trees["mu"], "nu": trees["nu"]}
+        full.ema = {"params": trees["ema"]} if trees["ema"] is not None else None
+        return full
+
+    def import_state(self, full: TrainState, state: TrainState) -> TrainState:
+        """Every rank reads a whole-tree state (e.g. a restored checkpoint) and copies the slices that fall into its own
+        shards; the compute-dtype arena is then rebuilt from the new masters.  Returns ``state`` with counters adopted."""
+        W, r = self.world, self.rank
+
+        def scatter(tree, flat):
+            if tree is None or flat is None:
+                return
+            leaves = flatten(tree)
+            with torch.no_grad():
+                for u in self.units:
+                    s = u.size // W
+                    lo, hi = r * s, (r + 1) * s                                  # this rank's range inside the unit
+                    base = u.offset // W
+                    for n, p in u.params:
+                        src = leaves.get(module_path_to_tree_path(n))
+                        if src is None:
+                            raise KeyError(f"checkpoint lacks {module_path_to_tree_path(n)}")
+                        o = u.offsets[n]
+                        a, b = max(o, lo), min(o + p.numel(), hi)
+                        if a < b:
+                            flat[base + a - lo: base + b - lo].copy_(src.reshape(-1)[a - o: b - o])
+
+        scatter(full.variables["params"], self.master)
+        scatter(full.opt_state.get("mu"), self.m)
+        scatter(full.opt_state.get("nu"), self.v)
+        if self.ema is not None:
+            scatter((full.ema or full.variables)["params"], self.ema)
+        self.refresh_compute_copy()
+        for f in ("step", "microstep", "updates", "consumed", "key", "deferred"):
+            if hasattr(full, f):
+                setattr(state, f, getattr(full, f))
+        c = full.opt_state.get("count")
+        if c is not None:
+            state.opt_state["count"] = torch.as_tensor(c).to(torch.int64)
+        return state
+
+    def refresh_compute_copy(self) -> None:
+        """Rebuild every rank's full compute-dtype parameters from the fp32 master shards (an all-gather)."""
+        W = self.world
+        pa = self.params_arena.tensor
+        with torch.no_grad():
+            for u in self.units:
+                s = u.size // W
+                mine = self.master[u.offset // W: u.offset // W + s].to(pa.dtype)
+                if W > 1:
+                    dist.all_gather_into_tensor(pa[u.offset: u.offset + u.size], mine, group=self.group)
+                else:
+                    pa[u.offset: u.offset + u.size].copy_(mine)
+        if self.cuda:
+            torch.cuda.synchronize(self.device)
+        if W > 1:
+            dist.barrier(group=self.group)
 
     # ------------------------------------------------------------------ per-unit protocol
     def _before_unit_forward(self, index: int) -> None:

@@ -277,7 +277,11 @@ class Trainer:
                 start_step = self.checkpoints.resumed(resume)
             state = eng.fresh_state(self.key)
             if start_step is not None:
-                state = eng.adopt(self.checkpoints.restore(state, start_step))
+                if hasattr(eng, "import_state"):
+                    # sharded engines read the layout-free checkpoint and keep the slices of their own shards
+                    state = eng.import_state(self.checkpoints.restore(None, start_step), state)
+                else:
+                    state = eng.adopt(self.checkpoints.restore(state, start_step))
                 pos = state.deferred
                 if pos is not None and hasattr(loader, "restore"):
                     loader.restore(pos)
@@ -364,6 +368,11 @@ class Trainer:
         pos = loader.position() if hasattr(loader, "position") else None
         last = next((h for h in reversed(self.history) if "loss" in h), {})
         m = {k: v for k, v in last.items() if isinstance(v, (int, float)) and k != "step"}
+        eng = self.engine()
+        if hasattr(eng, "export_state"):
+            state = eng.export_state(state)            # collective; whole trees on rank 0, None elsewhere
+            if state is None:
+                return
         self.checkpoints.save(state.step, state, saved=pos, metrics=m)
 
     def evaluate(self, state: TrainState, data, steps: Optional[int] = None) -> Dict[str, float]:

@@ -48,3 +48,27 @@ def test_fsdp_two_gpus_fused_kernel():
         assert abs(a - b) < 3e-2 * max(1.0, abs(a)), (one, two)
     clipped = _run(2, "nccl", clip="0.5", port=29623)
     assert clipped["losses"][-1] < clipped["losses"][0]
+
+
+def _run_ckpt(world, directory, steps, port):
+    worker = os.path.join(os.path.dirname(__file__), "workers", "ckpt_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), worker, str(directory), str(steps)]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2"))
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    line = next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))
+    return json.loads(line[len("RESULT "):])
+
+
+def test_fsdp_checkpoint_resumes_at_another_world_size(tmp_path):
+    """5 uninterrupted steps on 2 ranks == 3 steps on 2 ranks, checkpoint, then 2 more steps on ONE rank: the checkpoint
+    holds whole trees, so it restores into any sharding (weights, Adam moments, EMA, data position)."""
+    straight = _run_ckpt(2, tmp_path / "a", 5, 29631)
+    first = _run_ckpt(2, tmp_path / "b", 3, 29632)
+    assert first["step"] == 3
+    resumed = _run_ckpt(1, tmp_path / "b", 5, 29633)
+    assert resumed["step"] == 5 and len(resumed["losses"]) == 2
+    assert abs(resumed["digest"] - straight["digest"]) < 2e-4 * straight["digest"], (resumed, straight)
+    assert abs(resumed["ema"] - straight["ema"]) < 2e-4 * straight["ema"]
+    for a, b in zip(straight["losses"][3:], resumed["losses"]):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(a))
