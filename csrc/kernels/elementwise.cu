@@ -478,10 +478,10 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __res
 
 // ---------------------------------------------------------------------------------------------------------
 // RoPE (rotate-half convention) applied in place to the first `rot_heads` heads of a packed
-// [tokens, heads, D] tensor; positions[t] indexes cos/sin [max_pos, D/2] (fp32). sign = -1 gives the backward.
+// [tokens, heads, D] tensor; positions[t] indexes cos/sin [table_rows, D/2] (fp32). sign = -1 gives the backward.
 __global__ void rope_kernel(bf16* __restrict__ x, const float* __restrict__ cosb, const float* __restrict__ sinb,
                             const int* __restrict__ positions, long long tokens, int heads, int rot_heads, int D,
-                            float sign) {
+                            int table_rows, float sign) {
   const int half = D >> 1;
   const int hv = half >> 3;  // uint4 vectors per half
   const long long total = tokens * rot_heads * hv;
@@ -491,7 +491,8 @@ __global__ void rope_kernel(bf16* __restrict__ x, const float* __restrict__ cosb
     const long long th = i / hv;
     const int h = static_cast<int>(th % rot_heads);
     const long long t = th / rot_heads;
-    const int pos = positions != nullptr ? positions[t] : static_cast<int>(t);
+    int pos = positions != nullptr ? positions[t] : static_cast<int>(t);
+    pos = min(max(pos, 0), table_rows - 1);     // a position past the tables reads their last row, never outside them
     bf16* base = x + (t * heads + h) * D;
     uint4* p1 = reinterpret_cast<uint4*>(base) + c;
     uint4* p2 = reinterpret_cast<uint4*>(base + half) + c;
@@ -798,11 +799,11 @@ extern "C" int dewb_swiglu_bwd(const void* dy, const void* gate, const void* up,
 }
 
 extern "C" int dewb_rope(void* x, const float* cosb, const float* sinb, const int* positions, long long tokens,
-                         int heads, int rot_heads, int D, float sign, void* stream) {
-  if (D % 16 != 0) return -3;
+                         int heads, int rot_heads, int D, int table_rows, float sign, void* stream) {
+  if (D % 16 != 0 || table_rows <= 0) return -3;
   if (tokens <= 0 || rot_heads <= 0) return 0;
   rope_kernel<<<grid_for(tokens * rot_heads * (D >> 4), 256), 256, 0, STREAM(stream)>>>(
-      (bf16*)x, cosb, sinb, positions, tokens, heads, rot_heads, D, sign);
+      (bf16*)x, cosb, sinb, positions, tokens, heads, rot_heads, D, table_rows, sign);
   return LAST_ERR();
 }
 

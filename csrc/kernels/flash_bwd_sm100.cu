@@ -8,7 +8,9 @@
 // Both MMA kernels recompute the probabilities from the saved log-sum-exp, keep their output accumulators in tensor
 // memory for the whole loop and never use atomics, so results are deterministic. A Q / dO / K / V tile sits in shared
 // memory once and serves two products through two descriptors (K-major for the score products, MN-major for the
-// gradient products).
+// gradient products). The exponentials, not the tensor core, bound both MMA kernels, so each runs eight softmax warps:
+// two threads per TMEM lane, each taking half of the tile's columns (no reduction crosses the two: the row statistics
+// come from the forward pass and the delta kernel).
 //
 // Replaces the reference's attention template backward (src/dew/nn/kernels/templates/attention_mosaic_dkv.py,
 // attention_mosaic_dq.py), which it records as 6-9x slower than cuDNN on B200 (src/dew/nn/attention_kernels.py:772-796).
@@ -18,7 +20,8 @@
 namespace dewb {
 namespace flashbwd {
 
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;            // 8 softmax warps (two threads per TMEM lane), a TMA warp, an MMA warp
+constexpr int TMA_WARP = 8, MMA_WARP = 9;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
@@ -107,20 +110,20 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&bars->k_full[i], 1); mbar_init(&bars->v_full[i], 1); mbar_init(&bars->kv_empty[i], 1); }
-    mbar_init(&bars->sdp_full, 1); mbar_init(&bars->sdp_empty, 4);
-    mbar_init(&bars->ds_full, 4); mbar_init(&bars->dq_done, 1);
+    mbar_init(&bars->sdp_full, 1); mbar_init(&bars->sdp_empty, 8);
+    mbar_init(&bars->ds_full, 8); mbar_init(&bars->dq_done, 1);
     bars->abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 5) { tmem_alloc(&bars->tmem_base, C::TM_COLS); tmem_relinquish(); }
+  if (warp == MMA_WARP) { tmem_alloc(&bars->tmem_base, C::TM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
   volatile int* abort_flag = &bars->abort_flag;
 
-  if (warp == 4) {
+  if (warp == TMA_WARP) {
     if (lane == 0) {
       mbar_expect_tx(&bars->q_full, 2 * C::TILE);
 #pragma unroll
@@ -139,7 +142,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         for (int t = 0; t < C::SUB; ++t) tma_load_4d(sV + st * C::TILE + t * (BN * 128), &tv, &bars->v_full[st], t * 64, hk, j * BN, b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(BM, BN, 1, 1, 0, 0);
       constexpr uint32_t idesc_dq = make_idesc(BM, D, 1, 1, 0, 1);
@@ -182,8 +185,11 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
     }
   } else {
-    const int r = warp * 32 + lane;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    // two threads per query row: warps w and w + 4 read TMEM lane quarter w & 3 and take 64 of the 128 key columns each
+    constexpr int HC = BN / 2;
+    const int q4 = warp & 3, half = warp >> 2;
+    const int r = q4 * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
     const int row = q0 + r;
     const long long stat = (static_cast<long long>(b) * Hq + h) * S + row;
     const float lse2 = row < S ? lse[stat] * LOG2E : 0.f;
@@ -191,15 +197,15 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const int limit = CAUSAL ? (row + (T - S)) : (T - 1);
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!mbar_wait(&bars->sdp_full, j & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->sdp_full, j & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
       tc_fence_after();
-      const int k0 = j * BN;
-      uint32_t packed[BN / 2];
+      const int k0 = j * BN + half * HC;
+      uint32_t packed[HC / 2];
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < HC / 32; ++c) {
         uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_S + c * 32, sv);
-        tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DP + c * 32, dv);
+        tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_S + half * HC + c * 32, sv);
+        tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DP + half * HC + c * 32, dv);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -215,13 +221,13 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->sdp_empty);
       if (j > 0) {
-        if (!mbar_wait(&bars->dq_done, (j - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->dq_done, (j - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
       }
+      // column half `half` is the 64-column (128-byte) sub-tile `half` of dS; c is the 16-byte chunk within the row
 #pragma unroll
-      for (int c16 = 0; c16 < BN / 8; ++c16) {
-        const uint4 pk = make_uint4(packed[c16 * 4], packed[c16 * 4 + 1], packed[c16 * 4 + 2], packed[c16 * 4 + 3]);
-        const int t = c16 >> 3, c = c16 & 7;
-        *reinterpret_cast<uint4*>(sdS + t * (BM * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = pk;
+      for (int c = 0; c < HC / 8; ++c) {
+        const uint4 pk = make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
+        *reinterpret_cast<uint4*>(sdS + half * (BM * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = pk;
       }
       fence_proxy_async();
       tc_fence_before();
@@ -229,15 +235,15 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       if (lane == 0) mbar_arrive(&bars->ds_full);
     }
     if (ok && n_tiles > 0) {
-      if (!mbar_wait(&bars->dq_done, (n_tiles - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->dq_done, (n_tiles - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
     }
     if (ok) {
       tc_fence_after();
-      __nv_bfloat16* orow = dq + b * dq_sb + static_cast<long long>(row) * dq_ss + h * dq_sh;
+      __nv_bfloat16* orow = dq + b * dq_sb + static_cast<long long>(row) * dq_ss + h * dq_sh + half * (D / 2);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t v[32];
-        if (n_tiles > 0) { tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DQ + c * 32, v); tmem_ld_wait(); }
+        if (n_tiles > 0) { tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DQ + half * (D / 2) + c * 32, v); tmem_ld_wait(); }
         else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0;
@@ -259,7 +265,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, C::TM_COLS); }
+  if (warp == MMA_WARP) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, C::TM_COLS); }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -326,21 +332,21 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     mbar_init(&bars->kv_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->q_full[i], 1); mbar_init(&bars->q_empty[i], 1);
-      mbar_init(&bars->st_full[i], 1); mbar_init(&bars->st_empty[i], 4);
+      mbar_init(&bars->st_full[i], 1); mbar_init(&bars->st_empty[i], 8);
     }
-    mbar_init(&bars->pds_full, 4); mbar_init(&bars->acc_done, 1);
+    mbar_init(&bars->pds_full, 8); mbar_init(&bars->acc_done, 1);
     bars->abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 5) { tmem_alloc(&bars->tmem_base, C::TM_COLS); tmem_relinquish(); }
+  if (warp == MMA_WARP) { tmem_alloc(&bars->tmem_base, C::TM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
   volatile int* abort_flag = &bars->abort_flag;
 
-  if (warp == 4) {
+  if (warp == TMA_WARP) {
     if (lane == 0) {
       mbar_expect_tx(&bars->kv_full, 2 * C::KV_TILE);
 #pragma unroll
@@ -361,7 +367,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP) {
     if (lane == 0) {
       constexpr uint32_t idesc_st = make_idesc(BKV, BQ, 1, 1, 0, 0);
       constexpr uint32_t idesc_acc = make_idesc(BKV, D, 1, 1, 0, 1);
@@ -410,58 +416,72 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       }
     }
   } else {
-    const int r = warp * 32 + lane;                 // key row within the tile == TMEM lane
-    const int tid = threadIdx.x;                    // 0..127
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    // two threads per key row: warps w and w + 4 read TMEM lane quarter w & 3 and take 32 of the 64 query columns each
+    constexpr int HC = BQ / 2;
+    const int q4 = warp & 3, half = warp >> 2;
+    const int r = q4 * 32 + lane;                   // key row within the tile == TMEM lane
+    const int tid = threadIdx.x;                    // 0..255
+    const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
     const int key = kv0 + r;
     bool ok = true;
-    for (int it = 0; it < iters && ok; ++it) {
+    // All 256 threads meet at a named barrier once per iteration, so no thread leaves the loop early: after a wait
+    // gives up, `ok` turns false for the whole warp and the remaining iterations only keep the barrier count.
+    for (int it = 0; it < iters; ++it) {
       const int st = it & 1; const uint32_t ph = (it >> 1) & 1;
       const int h = hk * rep + it / nqb;
       const int qb = (q_first + it % nqb) * BQ;
-      // per-query statistics of this block, shared by the 128 threads
-      {
+      // per-query statistics of this block, shared by all softmax threads
+      if (tid < 2 * BQ) {
         float* dst = sStat + st * 2 * BQ;
         const int qi = qb + (tid & (BQ - 1));
         const long long idx = (static_cast<long long>(b) * Hq + h) * S + qi;
         if (tid < BQ) dst[tid] = qi < S ? lse[idx] * LOG2E : INFINITY;     // +inf -> exp2(-inf) = 0 for padded queries
         else dst[tid] = qi < S ? delta[idx] : 0.f;
       }
-      named_barrier_sync(1, 128);
-      const float* lse2 = sStat + st * 2 * BQ;
-      const float* dlt = lse2 + BQ;
-      if (!mbar_wait(&bars->st_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
+      named_barrier_sync(1, 256);
+      if (!ok) continue;
+      const float4* lse4 = reinterpret_cast<const float4*>(sStat + st * 2 * BQ + half * HC);
+      const float4* dlt4 = reinterpret_cast<const float4*>(sStat + st * 2 * BQ + BQ + half * HC);
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->st_full[st], ph, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; continue; }
       tc_fence_after();
-      uint32_t pp[BQ / 2], ds[BQ / 2];
-#pragma unroll
-      for (int c = 0; c < BQ / 32; ++c) {
+      uint32_t pp[HC / 2], ds[HC / 2];
+      {
         uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TM_ST1 : C::TM_ST0) + c * 32, sv);
-        tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TM_DPT1 : C::TM_DPT0) + c * 32, dv);
+        tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TM_ST1 : C::TM_ST0) + half * HC, sv);
+        tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TM_DPT1 : C::TM_DPT0) + half * HC, dv);
         tmem_ld_wait();
+        const int qbase = qb + half * HC + (T - S);
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int qc = c * 32 + i;
-          float p0 = exp2f(__uint_as_float(sv[i]) * scale_log2 - lse2[qc]);
-          float p1 = exp2f(__uint_as_float(sv[i + 1]) * scale_log2 - lse2[qc + 1]);
+        for (int i = 0; i < 32; i += 4) {
+          const float4 l4 = lse4[i >> 2], d4 = dlt4[i >> 2];
+          float p0 = exp2f(__uint_as_float(sv[i]) * scale_log2 - l4.x);
+          float p1 = exp2f(__uint_as_float(sv[i + 1]) * scale_log2 - l4.y);
+          float p2 = exp2f(__uint_as_float(sv[i + 2]) * scale_log2 - l4.z);
+          float p3 = exp2f(__uint_as_float(sv[i + 3]) * scale_log2 - l4.w);
           if (CAUSAL) {
-            if (key > qb + qc + (T - S)) p0 = 0.f;
-            if (key > qb + qc + 1 + (T - S)) p1 = 0.f;
+            if (key > qbase + i) p0 = 0.f;
+            if (key > qbase + i + 1) p1 = 0.f;
+            if (key > qbase + i + 2) p2 = 0.f;
+            if (key > qbase + i + 3) p3 = 0.f;
           }
-          if (key >= T) { p0 = 0.f; p1 = 0.f; }
-          pp[qc >> 1] = pack_bf16(p0, p1);
-          ds[qc >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dlt[qc]), p1 * (__uint_as_float(dv[i + 1]) - dlt[qc + 1]));
+          if (key >= T) { p0 = 0.f; p1 = 0.f; p2 = 0.f; p3 = 0.f; }
+          pp[i >> 1] = pack_bf16(p0, p1);
+          pp[(i >> 1) + 1] = pack_bf16(p2, p3);
+          ds[i >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - d4.x), p1 * (__uint_as_float(dv[i + 1]) - d4.y));
+          ds[(i >> 1) + 1] = pack_bf16(p2 * (__uint_as_float(dv[i + 2]) - d4.z), p3 * (__uint_as_float(dv[i + 3]) - d4.w));
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->st_empty[st]);
       if (it > 0) {
-        if (!mbar_wait(&bars->acc_done, (it - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->acc_done, (it - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; continue; }
       }
+      // each key row of P^T / dS^T is one 128-byte swizzled row; this thread writes 16-byte chunks half*4 .. half*4+3
 #pragma unroll
-      for (int c = 0; c < BQ / 8; ++c) {
-        const int off = r * 128 + ((c ^ (r & 7)) << 4);
+      for (int c = 0; c < HC / 8; ++c) {
+        const int chunk = half * (HC / 8) + c;
+        const int off = r * 128 + ((chunk ^ (r & 7)) << 4);
         *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[c * 4], pp[c * 4 + 1], pp[c * 4 + 2], pp[c * 4 + 3]);
         *reinterpret_cast<uint4*>(sdS + off) = make_uint4(ds[c * 4], ds[c * 4 + 1], ds[c * 4 + 2], ds[c * 4 + 3]);
       }
@@ -471,18 +491,18 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       if (lane == 0) mbar_arrive(&bars->pds_full);
     }
     if (ok && iters > 0) {
-      if (!mbar_wait(&bars->acc_done, (iters - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->acc_done, (iters - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
     }
     if (ok) {
       tc_fence_after();
-      __nv_bfloat16* kout = dk + b * dk_sb + static_cast<long long>(key) * dk_ss + hk * dk_sh;
-      __nv_bfloat16* vout = dv + b * dv_sb + static_cast<long long>(key) * dv_ss + hk * dv_sh;
+      __nv_bfloat16* kout = dk + b * dk_sb + static_cast<long long>(key) * dk_ss + hk * dk_sh + half * (D / 2);
+      __nv_bfloat16* vout = dv + b * dv_sb + static_cast<long long>(key) * dv_ss + hk * dv_sh + half * (D / 2);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t a[32], g[32];
         if (iters > 0) {
-          tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DV + c * 32, a);
-          tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DK + c * 32, g);
+          tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DV + half * (D / 2) + c * 32, a);
+          tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DK + half * (D / 2) + c * 32, g);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -510,7 +530,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, C::TM_COLS); }
+  if (warp == MMA_WARP) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem, C::TM_COLS); }
 }
 
 static int make_map(CUtensorMap* m, const void* base, int B, int L, int H, int D, long long sb, long long sl, long long sh,
@@ -524,11 +544,10 @@ static int make_map(CUtensorMap* m, const void* base, int B, int L, int H, int D
 template <int D, bool CAUSAL>
 static int launch_bwd(const void* dO, const void* q, const void* k, const void* v, const float* lse, const float* delta,
                       void* dq, void* dk, void* dv, int B, int S, int T, int Hq, int Hkv, const long long* qs,
-                      const long long* ks, const long long* vs, const long long* os, float scale, int* err,
+                      const long long* ks, const long long* vs, const long long* os, const long long* dos,
+                      const long long* dqs, const long long* dks, const long long* dvs, float scale, int* err,
                       cudaStream_t stream) {
-  // dq shares q's [B,S,Hq,D] contiguous layout, dk / dv are contiguous [B,T,Hkv,D], dO is contiguous [B,S,Hq,D]
-  const long long do_sb = static_cast<long long>(S) * Hq * D, do_ss = static_cast<long long>(Hq) * D, do_sh = D;
-  const long long dkv_sb = static_cast<long long>(T) * Hkv * D, dkv_ss = static_cast<long long>(Hkv) * D, dkv_sh = D;
+  const long long do_sb = dos[0], do_ss = dos[1], do_sh = dos[2];
   int r;
   {
     CUtensorMap tq, tdo, tk, tv;
@@ -541,7 +560,7 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
     if (e != cudaSuccess) return static_cast<int>(e);
     dim3 grid((S + 127) / 128, Hq, B);
     kern<<<grid, THREADS, DqCfg<D>::SMEM, stream>>>(tq, tdo, tk, tv, lse, delta, reinterpret_cast<__nv_bfloat16*>(dq), S, T,
-                                                     Hq, Hkv, do_sb, do_ss, do_sh, scale, err);
+                                                     Hq, Hkv, dqs[0], dqs[1], dqs[2], scale, err);
     if ((r = static_cast<int>(cudaGetLastError()))) return r;
   }
   {
@@ -555,8 +574,8 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
     if (e != cudaSuccess) return static_cast<int>(e);
     dim3 grid((T + 127) / 128, Hkv, B);
     kern<<<grid, THREADS, DkvCfg<D>::SMEM, stream>>>(tq, tdo, tk, tv, lse, delta, reinterpret_cast<__nv_bfloat16*>(dk),
-                                                      reinterpret_cast<__nv_bfloat16*>(dv), S, T, Hq, Hkv, dkv_sb, dkv_ss,
-                                                      dkv_sh, dkv_sb, dkv_ss, dkv_sh, scale, err);
+                                                      reinterpret_cast<__nv_bfloat16*>(dv), S, T, Hq, Hkv, dks[0], dks[1],
+                                                      dks[2], dvs[0], dvs[1], dvs[2], scale, err);
     if ((r = static_cast<int>(cudaGetLastError()))) return r;
   }
   return 0;
@@ -565,25 +584,27 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
 }  // namespace flashbwd
 }  // namespace dewb
 
-// dO, dq: contiguous [B,S,Hq,D]; dk, dv: contiguous [B,T,Hkv,D]; q / k / v / out carry their own (batch, sequence,
-// head) element strides; lse [B,Hq,S] from the forward; delta [B,Hq,S] is scratch this call fills.
+// Every tensor is [B, length, heads, D] bf16 with unit stride along D and its own (batch, sequence, head) element
+// strides, so q / k / v may be views of one fused projection output and dq / dk / dv views of one fused gradient
+// buffer. lse [B,Hq,S] comes from the forward; delta [B,Hq,S] is scratch this call fills.
+// `strides` holds 8 triples in the order q, k, v, out, dO, dq, dk, dv.
 extern "C" int dewb_flash_bwd(const void* dO, const void* q, const void* k, const void* v, const void* out,
                               const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int T, int Hq,
-                              int Hkv, int D, long long q_sb, long long q_ss, long long q_sh, long long k_sb,
-                              long long k_ss, long long k_sh, long long v_sb, long long v_ss, long long v_sh,
-                              long long o_sb, long long o_ss, long long o_sh, float scale, int causal, int* err,
+                              int Hkv, int D, const long long* strides, float scale, int causal, int* err,
                               void* stream_ptr) {
   using namespace dewb::flashbwd;
   if ((D != 128 && D != 64) || Hq % Hkv != 0) return -3;
+  const long long *qs = strides, *ks = strides + 3, *vs = strides + 6, *os = strides + 9, *dos = strides + 12,
+                  *dqs = strides + 15, *dks = strides + 18, *dvs = strides + 21;
+  for (int i = 0; i < 24; ++i) if (strides[i] % 8) return -3;       // 16-byte rows for TMA and the uint4 stores
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
   const long long rows = static_cast<long long>(B) * S * Hq;
   delta_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(dO), reinterpret_cast<const __nv_bfloat16*>(out), delta, B, S, Hq, D,
-      static_cast<long long>(S) * Hq * D, static_cast<long long>(Hq) * D, D, o_sb, o_ss, o_sh);
-  const long long qs[3] = {q_sb, q_ss, q_sh}, ks[3] = {k_sb, k_ss, k_sh}, vs[3] = {v_sb, v_ss, v_sh}, os[3] = {o_sb, o_ss, o_sh};
+      dos[0], dos[1], dos[2], os[0], os[1], os[2]);
   if (D == 128)
-    return causal ? launch_bwd<128, true>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, scale, err, stream)
-                  : launch_bwd<128, false>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, scale, err, stream);
-  return causal ? launch_bwd<64, true>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, scale, err, stream)
-                : launch_bwd<64, false>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, scale, err, stream);
+    return causal ? launch_bwd<128, true>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream)
+                  : launch_bwd<128, false>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream);
+  return causal ? launch_bwd<64, true>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream)
+                : launch_bwd<64, false>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream);
 }

@@ -1,10 +1,13 @@
 // Flash attention forward for sm_100a (head_dim 128 or 64, bf16, causal or full, GQA).
 //
-// One CTA per (query tile of 128 rows, query head, batch); 192 threads:
-//   warps 0..3  softmax      : one thread per query row; tcgen05.ld the 128 scores of the row, online softmax in
-//                              the log2 domain, write P (bf16) into shared memory in the 128-byte-swizzled layout
-//   warp 4      TMA producer : Q once, then K and V tiles into 2-stage rings (cp.async.bulk.tensor, no multicast)
-//   warp 5      MMA issuer   : S = Q K^T into one of two TMEM score buffers (so the next tile's scores are computed
+// One CTA per (query tile of 128 rows, query head, batch); 320 threads:
+//   warps 0..7  softmax      : two threads per query row (warps w and w + 4 share TMEM lane quarter w & 3 and take 64
+//                              of the 128 key columns each; the row maximum is exchanged through shared memory);
+//                              tcgen05.ld the scores, online softmax in the log2 domain, write P (bf16) into shared
+//                              memory in the 128-byte-swizzled layout.  The exponentials, not the tensor core, bound
+//                              this kernel, so the softmax gets eight warps.
+//   warp 8      TMA producer : Q once, then K and V tiles into 2-stage rings (cp.async.bulk.tensor, no multicast)
+//   warp 9      MMA issuer   : S = Q K^T into one of two TMEM score buffers (so the next tile's scores are computed
 //                              while this tile's softmax runs), then O += P V into the TMEM output accumulator
 // The running maximum is applied lazily: O and l are rescaled only when a row's maximum has grown by more than 2^8
 // since the last rescale, so the TMEM read-modify-write of O is rare.
@@ -19,8 +22,13 @@ namespace flash {
 
 constexpr int BM = 128;        // query rows per CTA
 constexpr int BN = 128;        // keys per tile
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;
+constexpr int TMA_WARP = 8, MMA_WARP = 9;
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 template <int D>
 struct Cfg {
@@ -28,7 +36,7 @@ struct Cfg {
   static constexpr int Q_BYTES = BM * D * 2;
   static constexpr int KV_BYTES = BN * D * 2;
   static constexpr int P_BYTES = BM * BN * 2;
-  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256;
+  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256 + 6 * BM * 4;
   static constexpr int TMEM_S0 = 0, TMEM_S1 = 128, TMEM_O = 256, TMEM_COLS = 512;
 };
 
@@ -39,6 +47,8 @@ struct Bars {
   uint64_t p_full, pv_done;
   uint32_t tmem_base;
   int abort_flag;
+  float xmax[2][2][BM];   // [tile parity][column half][row]: partial row maxima exchanged between the two halves
+  float xsum[2][BM];      // [column half][row]: partial row sums, combined once at the end
 };
 
 template <int D, bool CAUSAL>
@@ -77,23 +87,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1);
       mbar_init(&bars->v_full[i], 1); mbar_init(&bars->v_empty[i], 1);
-      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_empty[i], 4);
+      mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_empty[i], 8);
     }
-    mbar_init(&bars->p_full, 4);
+    mbar_init(&bars->p_full, 8);
     mbar_init(&bars->pv_done, 1);
     bars->abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 5) { tmem_alloc(&bars->tmem_base, C::TMEM_COLS); tmem_relinquish(); }
-  if (warp == 4 && lane == 0) { tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv); }
+  if (warp == MMA_WARP) { tmem_alloc(&bars->tmem_base, C::TMEM_COLS); tmem_relinquish(); }
+  if (warp == TMA_WARP && lane == 0) { tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
   volatile int* abort_flag = &bars->abort_flag;
 
-  if (warp == 4) {
+  if (warp == TMA_WARP) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(&bars->q_full, C::Q_BYTES);
@@ -112,7 +122,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         for (int t = 0; t < C::SUB; ++t) tma_load_4d(sV + st * C::KV_BYTES + t * (BN * 128), &tv, &bars->v_full[st], t * 64, hk, j * BN, b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(BM, BN, 1, 1, 0, 0);
@@ -154,42 +164,58 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax + epilogue (warps 0..3)
-    const int r = warp * 32 + lane;                  // query row within the tile == TMEM lane
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    // ------------------------------------------------------------------ softmax + epilogue (warps 0..7)
+    constexpr int HC = BN / 2;                       // key columns per thread
+    const int q4 = warp & 3, half = warp >> 2;
+    const int r = q4 * 32 + lane;                    // query row within the tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    // Both threads of a row meet at a named barrier once per tile, so no thread may leave the loop early: after a
+    // wait gives up, `ok` turns false for the whole warp and the remaining iterations only keep the barrier count.
+    for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(&bars->s_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
-      tc_fence_after();
-      float s[BN];
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TMEM_S1 : C::TMEM_S0) + c * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]) * scale_log2;
+      float s[HC];
+      float mt = -INFINITY;
+      if (ok) {
+        const bool got = mbar_wait(&bars->s_full[st], ph, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_empty[st]);   // the score buffer may be overwritten by tile j + 2
-      const int k0 = j * BN;
-      const int limit = CAUSAL ? (q0 + r + (T - S)) : (T - 1);   // last visible key index for this row
-      if (k0 + BN - 1 > limit || k0 + BN > T) {
+      if (ok) {
+        tc_fence_after();
 #pragma unroll
-        for (int i = 0; i < BN; ++i) if (k0 + i > limit || k0 + i >= T) s[i] = -INFINITY;
+        for (int c = 0; c < HC / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TMEM_S1 : C::TMEM_S0) + half * HC + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]) * scale_log2;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->s_empty[st]);   // the score buffer may be overwritten by tile j + 2
+        const int k0 = j * BN + half * HC;
+        const int limit = CAUSAL ? (q0 + r + (T - S)) : (T - 1);   // last visible key index for this row
+        if (k0 + HC - 1 > limit || k0 + HC > T) {
+#pragma unroll
+          for (int i = 0; i < HC; ++i) if (k0 + i > limit || k0 + i >= T) s[i] = -INFINITY;
+        }
+        mt = s[0];
+#pragma unroll
+        for (int i = 1; i < HC; ++i) mt = fmaxf(mt, s[i]);
       }
-      float mt = s[0];
-#pragma unroll
-      for (int i = 1; i < BN; ++i) mt = fmaxf(mt, s[i]);
+      // the row's maximum over all 128 columns: exchange with the thread that holds the other half of the row
+      bars->xmax[j & 1][half][r] = mt;
+      named_barrier_sync(1 + q4, 64);
+      if (!ok) continue;
+      mt = fmaxf(mt, bars->xmax[j & 1][half ^ 1][r]);
       const float m_new = fmaxf(m_used, mt);
       const bool need = (m_new - m_used > RESCALE_THRESHOLD) || (m_used == -INFINITY && m_new > -INFINITY);
       const bool any_need = __any_sync(0xffffffffu, need);
       // PV(j-1) must be complete before P is overwritten or O is rescaled
       if (j > 0) {
-        if (!mbar_wait(&bars->pv_done, (j - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+        const bool got = mbar_wait(&bars->pv_done, (j - 1) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; continue; }
         tc_fence_after();
       }
       if (any_need) {
@@ -197,13 +223,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         if (need) { m_used = m_new; l *= alpha; }
         if (j > 0) {
 #pragma unroll
-          for (int c = 0; c < D / 16; ++c) {
+          for (int c = 0; c < D / 32; ++c) {           // this thread's half of the output columns
             uint32_t v[16];
-            tmem_ld_32x32b_x16(tmem + lane_addr + C::TMEM_O + c * 16, v);
+            const uint32_t col = C::TMEM_O + half * (D / 2) + c * 16;
+            tmem_ld_32x32b_x16(tmem + lane_addr + col, v);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32b_x16(tmem + lane_addr + C::TMEM_O + c * 16, v);
+            tmem_st_32x32b_x16(tmem + lane_addr + col, v);
           }
           tmem_st_wait();
         }
@@ -212,17 +239,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       const float mu = (m_used == -INFINITY) ? 0.f : m_used;
       float rowsum = 0.f;
 #pragma unroll
-      for (int c16 = 0; c16 < BN / 8; ++c16) {
+      for (int i8 = 0; i8 < HC / 8; ++i8) {
         float p[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { p[i] = exp2f(s[c16 * 8 + i] - mu); }
+        for (int i = 0; i < 8; ++i) { p[i] = exp2f(s[i8 * 8 + i] - mu); }
         uint4 pk;
         pk.x = pack_bf16(p[0], p[1]); pk.y = pack_bf16(p[2], p[3]); pk.z = pack_bf16(p[4], p[5]); pk.w = pack_bf16(p[6], p[7]);
         // sum what the tensor core will see (the bf16-rounded values), so rows of P / l sum to one
         rowsum += bf16_lo(pk.x) + bf16_hi(pk.x) + bf16_lo(pk.y) + bf16_hi(pk.y) + bf16_lo(pk.z) + bf16_hi(pk.z) +
                   bf16_lo(pk.w) + bf16_hi(pk.w);
-        const int t = c16 >> 3, c = c16 & 7;
-        *reinterpret_cast<uint4*>(sP + t * (BM * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = pk;
+        // column half `half` is the 64-column (128-byte) sub-tile `half` of P; i8 is the 16-byte chunk within the row
+        *reinterpret_cast<uint4*>(sP + half * (BM * 128) + r * 128 + ((i8 ^ (r & 7)) << 4)) = pk;
       }
       l += rowsum;
       fence_proxy_async();
@@ -232,17 +259,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     }
     // epilogue: O / l -> bf16, lse
     if (ok && n_tiles > 0) {
-      if (!mbar_wait(&bars->pv_done, (n_tiles - 1) & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
+      const bool got = mbar_wait(&bars->pv_done, (n_tiles - 1) & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
     }
+    // the row sum over all columns (both threads of a row reach this barrier: neither branch above skips it)
+    bars->xsum[half][r] = l;
+    named_barrier_sync(1 + q4, 64);
+    l += bars->xsum[half ^ 1][r];
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int row = q0 + r;
-      __nv_bfloat16* orow = out + b * o_stride_b + static_cast<long long>(row) * o_stride_s + h * o_stride_h;
+      __nv_bfloat16* orow = out + b * o_stride_b + static_cast<long long>(row) * o_stride_s + h * o_stride_h + half * (D / 2);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t v[32];
-        if (n_tiles > 0) { tmem_ld_32x32b_x32(tmem + lane_addr + C::TMEM_O + c * 32, v); tmem_ld_wait(); }
+        if (n_tiles > 0) { tmem_ld_32x32b_x32(tmem + lane_addr + C::TMEM_O + half * (D / 2) + c * 32, v); tmem_ld_wait(); }
         else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0;
@@ -260,13 +292,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
           }
         }
       }
-      if (row < S && lse != nullptr)
+      if (half == 0 && row < S && lse != nullptr)
         lse[(static_cast<long long>(b) * Hq + h) * S + row] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem, C::TMEM_COLS);

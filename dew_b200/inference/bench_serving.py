@@ -47,7 +47,7 @@ def main(argv=None):
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     cfg = dict(vocab_size=128256, emb_features=4096, num_layers=args.layers, num_heads=32, num_kv_heads=8, head_dim=128,
-               mlp_features=14336, max_seq_len=4096, rope_theta=500000.0, qk_norm=False, tie_embeddings=False, norm_eps=1e-5)
+               mlp_features=14336, max_seq_len=max(4096, args.max_prompt + args.new_tokens), rope_theta=500000.0, qk_norm=False, tie_embeddings=False, norm_eps=1e-5)
     torch.manual_seed(0)
     # build and shard layer by layer on the device in bf16 (same seed on every rank -> identical full weights)
     model = CausalTransformer(dtype=torch.bfloat16, device=dev, **cfg).eval()

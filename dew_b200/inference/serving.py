@@ -58,6 +58,9 @@ class Server:
                  tokenizer=None, prefill_budget: Optional[int] = None, cuda_graph: bool = False, clock: Callable[[], float] = time.perf_counter):
         self.model, self.variables, self.tokenizer = model, variables, tokenizer
         self.slots, self.capacity = slots, capacity
+        limit = getattr(getattr(model, "config", None), "max_seq_len", None)
+        if limit is not None and capacity > limit:
+            raise ValueError(f"row capacity {capacity} exceeds the model's max_seq_len {limit} (its rotary tables end there)")
         spec = kv_cache if isinstance(kv_cache, KVCache) else KVCache(page_size=kv_cache if isinstance(kv_cache, int) else 16)
         if spec.page_size is None:
             spec = KVCache(spec.quantized, capacity, spec.pages, spec.groups, spec.offloaded)

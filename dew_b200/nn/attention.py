@@ -45,6 +45,13 @@ class SelfAttention(nn.Module):
 
     def forward(self, x, cos=None, sin=None, positions=None, segment_ids=None, cache=None, layer: int = 0):
         B, S, _ = x.shape
+        if (cache is None and x.is_cuda and self.q_norm is None and self.window is None and not self.softcap
+                and self.sinks is None and segment_ids is None):
+            from ..ops.attn import packed_attention
+            H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+            o = packed_attention(self.qkv_proj(x).view(B, S, H + 2 * Hkv, D), cos, sin, positions, H, Hkv, self.causal)
+            if o is not None:
+                return self.o_proj(o.reshape(B, S, H * D))
         q, k, v = self.project(x, cos, sin, positions)
         if cache is not None:
             o = cache.attend(layer, q, k, v, positions, causal=self.causal, window=self.window, softcap=self.softcap,

@@ -66,3 +66,17 @@ def flash_attention(q, k, v, causal=True, scale=None, window=None, softcap=0.0, 
         from .flash import flash_sm100
         return flash_sm100(q, k, v, causal, scale if scale is not None else 1.0 / math.sqrt(D))
     return _sdpa(q, k, v, causal, scale, window, softcap, sinks, segment_ids)
+
+
+def packed_attention(qkv, cos, sin, positions, Hq: int, Hkv: int, causal: bool = True, scale: Optional[float] = None):
+    """RoPE + attention over a packed projection ``[B, S, Hq + 2 Hkv, D]`` when the sm_100a flash kernels take the case
+    (one fused autograd node, no slice copies); returns None when they do not, and the caller takes the general path."""
+    B, S, H, D = qkv.shape
+    if not (L.use_cuda(qkv) and qkv.is_contiguous()):
+        return None
+    case = dict(dtype=qkv.dtype, D=D, S=S, T=S, Hq=Hq, Hkv=Hkv, sinks=False, softcap=False, window=None, segments=False,
+                causal=causal, grad=torch.is_grad_enabled() and qkv.requires_grad, unit_d=True)
+    if _ATTN.select(case) != "sm100_flash":
+        return None
+    from .flash import packed_rope_flash
+    return packed_rope_flash(qkv, cos, sin, positions, Hq, Hkv, causal, scale if scale is not None else 1.0 / math.sqrt(D))

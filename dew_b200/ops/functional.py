@@ -47,8 +47,27 @@ _GEMM.kernels = [
         Requirement("align", lambda c: c["aligned"], "base pointers must be 16-byte aligned"),
         Requirement("inner", lambda c: c["inner_contig"], "the contiguous dimension must have stride 1"),
     ], receipt="tcgen05 128x256x64 persistent kernel, csrc/kernels/gemm_sm100.cu"),
+    Kernel("sm100_pair", [
+        Requirement("built", lambda c: _pair_built(), "the CTA-pair kernel is not in this build of libdewb.so"),
+        Requirement("dtype", lambda c: c["dtype"] == torch.bfloat16, "operands must be bf16"),
+        Requirement("ld", lambda c: c["lda"] % 8 == 0 and c["ldb"] % 8 == 0 and c["ldd"] % 8 == 0,
+                    "row strides must be multiples of 8 elements (16-byte TMA rule)"),
+        Requirement("align", lambda c: c["aligned"], "base pointers must be 16-byte aligned"),
+        Requirement("inner", lambda c: c["inner_contig"], "the contiguous dimension must have stride 1"),
+    ], receipt="tcgen05 cta_group::2 256x256x64 persistent kernel on CTA pairs, csrc/kernels/gemm_pair_sm100.cu"),
     Kernel("cublas", [], receipt="library arm (torch.matmul)"),
 ]
+
+
+def _pair_built() -> bool:
+    try:
+        return hasattr(L.load(), "dewb_gemm_pair_bf16")
+    except Exception:
+        return False
+
+
+# Which of this library's two dense kernels large products take ("sm100_tcgen05" or "sm100_pair").
+LARGE_GEMM = os.environ.get("DEWB_LARGE_GEMM", "sm100_tcgen05")
 
 
 # Measured cell: with fewer than ~24 output tiles of 128x256 (decode-sized products, e.g. 128 x 768) the persistent
@@ -79,16 +98,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                 inner_contig=(a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1), M=M, N=N, K=K)
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
     cell = ("skinny",) if tiles < 24 else None
+    if kernel is None and cell is None and LARGE_GEMM == "sm100_pair" and tiles >= 148:
+        kernel = "sm100_pair"
     which = _GEMM.select(case, forced=kernel, cell=cell)
     if which == "cublas":
         return _gemm_reference_cuda(a, b, a_mn, b_mn, alpha, out, accumulate)
     epi = {(torch.bfloat16, False): 0, (torch.float32, False): 1, (torch.float32, True): 2,
            (torch.bfloat16, True): 3}[(out.dtype, bool(accumulate))]
     lib = L.load()
-    rc = lib.dewb_gemm_bf16(L.ptr(a), L.ptr(b), L.ptr(out), c_int(M), c_int(N), c_int(K), c_ll(a.stride(0)),
-                            c_ll(b.stride(0)), c_ll(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)), c_int(epi),
-                            c_float(alpha), L.ptr(L.status(a.device)), c_int(max_ctas), L.stream_ptr())
-    L.check(rc, "gemm_bf16")
+    fn = lib.dewb_gemm_pair_bf16 if which == "sm100_pair" else lib.dewb_gemm_bf16
+    rc = fn(L.ptr(a), L.ptr(b), L.ptr(out), c_int(M), c_int(N), c_int(K), c_ll(a.stride(0)),
+            c_ll(b.stride(0)), c_ll(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)), c_int(epi),
+            c_float(alpha), L.ptr(L.status(a.device)), c_int(max_ctas), L.stream_ptr())
+    L.check(rc, which)
     L.count_launches()
     return out
 
@@ -344,7 +366,7 @@ class _Rope(torch.autograd.Function):
         elif out.dim() == 4 and out.shape[0] > 1:
             pos = torch.arange(out.shape[1], device=x.device, dtype=torch.int32).repeat(out.shape[0])
         L.check(lib.dewb_rope(L.ptr(out), L.ptr(cos), L.ptr(sin), L.ptr(pos), c_ll(tokens), c_int(H), c_int(rot_heads),
-                              c_int(D), c_float(1.0), L.stream_ptr()), "rope")
+                              c_int(D), c_int(cos.shape[0]), c_float(1.0), L.stream_ptr()), "rope")
         L.count_launches()
         ctx.save_for_backward(cos, sin, pos)
         ctx.rot_heads = rot_heads
@@ -359,7 +381,7 @@ class _Rope(torch.autograd.Function):
         dx = dx.contiguous()
         tokens = dx.numel() // (H * D)
         L.check(lib.dewb_rope(L.ptr(dx), L.ptr(cos), L.ptr(sin), L.ptr(pos), c_ll(tokens), c_int(H),
-                              c_int(ctx.rot_heads), c_int(D), c_float(-1.0), L.stream_ptr()), "rope_bwd")
+                              c_int(ctx.rot_heads), c_int(D), c_int(cos.shape[0]), c_float(-1.0), L.stream_ptr()), "rope_bwd")
         L.count_launches()
         return dx, None, None, None, None
 

@@ -42,9 +42,19 @@ def bench_gemm(out, peaks, flush, shapes=None, iters=10):
         c = device_time(lambda: ops.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=D, kernel="cublas"), iters=iters, flush=flush)
         L.check_status()
         tf, ctf = flops / t.median_ms / 1e9, flops / c.median_ms / 1e9
+        pair = {}
+        if hasattr(L.load(), "dewb_gemm_pair_bf16") and N >= 256:
+            ref = D.clone()
+            ops.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=ref, kernel="sm100_tcgen05")
+            p = device_time(lambda: ops.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=D, kernel="sm100_pair"), iters=iters, flush=flush)
+            L.check_status()
+            ptf = flops / p.median_ms / 1e9
+            pair = dict(pair_ms=p.median_ms, pair_tflops=ptf, pair_frac_of_measured=ptf / peaks["bf16_tflops"],
+                        pair_time_over_cublas=p.median_ms / c.median_ms, pair_equals_single=bool(torch.equal(D, ref)))
+            del ref
         _row(out, kernel="gemm_sm100", name=name, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, ms=t.median_ms, tflops=tf,
              frac_of_measured=tf / peaks["bf16_tflops"], cublas_ms=c.median_ms, cublas_tflops=ctf,
-             time_over_cublas=t.median_ms / c.median_ms, peaks=peaks["source"])
+             time_over_cublas=t.median_ms / c.median_ms, peaks=peaks["source"], **pair)
         del A, B, D
 
 

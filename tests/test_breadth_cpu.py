@@ -1,4 +1,5 @@
 """LoRA, quantisation, HF interop, evaluation metrics."""
+import pytest
 import torch
 
 from dew_b200.eval import metrics as M
@@ -67,3 +68,27 @@ def test_metrics():
     assert M.frechet_distance(f, f) < 1e-6 and M.frechet_distance(f, f + 3) > 50
     p = torch.softmax(torch.randn(100, 5) * 3, -1)
     assert 0 <= M.expected_calibration_error(p, p.argmax(-1)) <= 1
+
+
+def test_nccl_weight_push_orders_chunks_and_aborts_on_failure():
+    from dew_b200.inference.nccl import FakeCollectives, NCCLPush, PushFailed, UniqueId
+    tensors = {"b.weight": torch.arange(10, dtype=torch.float32), "a.weight": torch.ones(3, 5, dtype=torch.bfloat16)}
+    announced = []
+    fake = FakeCollectives()
+    push = NCCLPush(receivers=2, collectives=fake, announce=lambda *a: announced.append(a), chunk_bytes=16)
+    push.push(tensors, version=7)
+    assert fake.calls[0] == ("open", 0, 3) and fake.calls[1] == ("all_reduce", 1)
+    uid_b64, names, shapes, dtypes, version = announced[0]
+    assert names == ["a.weight", "b.weight"] and shapes == [(3, 5), (10,)] and dtypes == ["bfloat16", "float32"] and version == 7
+    assert bytes(UniqueId.from_b64(uid_b64).internal) == bytes(fake.unique_id().internal)
+    # a.weight: 15 bf16 in 8-element pieces; b.weight: 10 fp32 in 4-element pieces - in name order
+    sizes = [c[1] for c in fake.calls if c[0] == "broadcast"]
+    assert sizes == [8, 7, 4, 4, 2]
+    assert torch.equal(torch.cat(fake.received[2:]), tensors["b.weight"]) and push.pushed == [7]
+    push.push(tensors, version=8)                       # the open group is reused: no second rendezvous
+    assert sum(c[0] == "open" for c in fake.calls) == 1 and announced[1][0] is None
+    bad = FakeCollectives(fail_at=1)
+    p2 = NCCLPush(receivers=1, collectives=bad, announce=lambda *a: None, chunk_bytes=16)
+    with pytest.raises(PushFailed):
+        p2.push(tensors, version=1)
+    assert bad.aborted and p2.comm is None and p2.pushed == []

@@ -267,6 +267,52 @@ def test_flash_backward_sm100(B, S, Hq, Hkv, D, causal):
         assert rel_err(g, r) <= 3 * bf16_floor(r) + 1.5e-2, (name, rel_err(g, r))
 
 
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn,dtype,acc", [
+    (512, 512, 256, False, False, torch.bfloat16, False), (384, 768, 192, False, True, torch.bfloat16, False),
+    (300, 520, 136, True, True, torch.float32, True), (1024, 256, 64, True, False, torch.float32, False),
+    (2048, 4096, 1024, False, False, torch.bfloat16, True)])
+def test_gemm_pair_kernel_matches_reference(M, N, K, a_mn, b_mn, dtype, acc):
+    """The CTA-pair (cta_group::2) kernel: every operand layout, epilogue, odd sizes with row / column / reduction tails."""
+    torch.manual_seed(M + N + K)
+    A = torch.randn((K, M) if a_mn else (M, K), device=DEV).to(torch.bfloat16)
+    B = torch.randn((K, N) if b_mn else (N, K), device=DEV).to(torch.bfloat16)
+    pad = torch.full((M + 2, N), 7.0, device=DEV, dtype=dtype)          # canary rows after the output
+    out = pad[:M]
+    if acc:
+        out.normal_()
+    before = out.float().clone()
+    ops.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=out, accumulate=acc, kernel="sm100_pair")
+    L.check_status()
+    ref = (A.float().t() if a_mn else A.float()) @ (B.float() if b_mn else B.float().t())
+    if acc:
+        ref = ref + before
+    assert rel_err(out, ref) <= 2 * bf16_floor(ref) + 1e-5, rel_err(out, ref)
+    assert bool((pad[M:] == 7.0).all())
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv,D", [(2, 256, 4, 2, 128), (1, 512, 8, 2, 64)])
+def test_packed_rope_flash_matches_unfused_reference(B, S, Hq, Hkv, D):
+    """One autograd node for RoPE + attention over the packed projection (in-place rotation, packed gradient buffer)
+    against fp32 rope + attention through plain autograd."""
+    from dew_b200.ops.attn import packed_attention
+    torch.manual_seed(B * S + D)
+    cos, sin = ops.rope_tables(S, D, 10000.0, device=DEV)
+    base = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV).to(torch.bfloat16)
+    x = base.clone().requires_grad_()
+    out = packed_attention(x * 1.0, cos, sin, None, Hq, Hkv, True)          # `* 1.0`: a fresh tensor the op may rotate in place
+    assert out is not None
+    do = torch.randn_like(out)
+    out.backward(do)
+    ref_in = base.float().requires_grad_()
+    r = ops.rope_reference(ref_in, cos, sin, None, Hq + Hkv)
+    ref = ops.attention_reference(r[:, :, :Hq], r[:, :, Hq:Hq + Hkv], r[:, :, Hq + Hkv:], causal=True)
+    ref.backward(do.float())
+    assert rel_err(out, ref) <= 3 * bf16_floor(ref) + 3e-3, rel_err(out, ref)
+    for name, sl in (("dq", slice(0, Hq)), ("dk", slice(Hq, Hq + Hkv)), ("dv", slice(Hq + Hkv, None))):
+        g, rr = x.grad[:, :, sl], ref_in.grad[:, :, sl]
+        assert rel_err(g, rr) <= 3 * bf16_floor(rr) + 1.5e-2, (name, rel_err(g, rr))
+
+
 @pytest.mark.parametrize("T,k,E,d,F", [(300, 2, 4, 128, 192), (1000, 6, 16, 256, 128), (64, 2, 8, 64, 64)])
 def test_grouped_gemm_forward_backward(T, k, E, d, F):
     """tcgen05 grouped GEMMs (expert-sorted, 128-aligned groups) against the per-expert fp32 loop."""

@@ -69,7 +69,7 @@ def test_server_with_cuda_graph_matches_offline_generation():
     from dew_b200.sampling.text import Sampling, generate
     torch.manual_seed(0)
     m = CausalTransformer(vocab_size=512, emb_features=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64,
-                          mlp_features=512, max_seq_len=256, qk_norm=False, tie_embeddings=False).to("cuda", torch.bfloat16).eval()
+                          mlp_features=512, max_seq_len=512, qk_norm=False, tie_embeddings=False).to("cuda", torch.bfloat16).eval()
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(1, 500, (int(n),), generator=g).tolist() for n in (128, 256, 128, 384, 128, 256)]
     offline = generate(m, None, prompts, 8, sampling=Sampling(temperature=0.0))
