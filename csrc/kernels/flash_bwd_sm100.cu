@@ -30,7 +30,8 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
 
 // ---------------------------------------------------------------------------------------------------------------
 __global__ void delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
-                             float* __restrict__ delta, int B, int S, int H, int D, long long do_sb, long long do_ss,
+                             const float* __restrict__ lse, float* __restrict__ delta, float* __restrict__ lse2, int B,
+                             int S, int H, int D, long long do_sb, long long do_ss,
                              long long do_sh, long long o_sb, long long o_ss, long long o_sh) {
   const long long row = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;   // one warp per (b, s, h)
   const int lane = threadIdx.x & 31;
@@ -49,7 +50,11 @@ __global__ void delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bf
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) delta[(static_cast<long long>(b) * H + h) * S + s] = acc;
+  if (lane == 0) {
+    const long long o = (static_cast<long long>(b) * H + h) * S + s;
+    delta[o] = acc;
+    lse2[o] = lse[o] * LOG2E;          // the log-sum-exp in log2 units, as both MMA kernels use it
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -210,8 +215,8 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const int key = k0 + c * 32 + i;
-          float p0 = exp2f(__uint_as_float(sv[i]) * scale_log2 - lse2);
-          float p1 = exp2f(__uint_as_float(sv[i + 1]) * scale_log2 - lse2);
+          float p0 = fast_exp2(__uint_as_float(sv[i]) * scale_log2 - lse2);
+          float p1 = fast_exp2(__uint_as_float(sv[i + 1]) * scale_log2 - lse2);
           if (key > limit || key >= T) p0 = 0.f;
           if (key + 1 > limit || key + 1 >= T) p1 = 0.f;
           packed[(c * 32 + i) >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));
@@ -294,7 +299,7 @@ template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
                  const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
-                 const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dk,
+                 const float* __restrict__ lse2, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dk,
                  __nv_bfloat16* __restrict__ dv, int S, int T, int Hq, int Hkv, long long dk_sb, long long dk_ss,
                  long long dk_sh, long long dv_sb, long long dv_ss, long long dv_sh, float scale, int* __restrict__ err) {
   using C = DkvCfg<D>;
@@ -359,12 +364,16 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         const int h = hk * rep + it / nqb;
         const int qb = (q_first + it % nqb) * BQ;
         if (!mbar_wait(&bars->q_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); break; }
-        mbar_expect_tx(&bars->q_full[st], 2 * C::Q_TILE);
+        mbar_expect_tx(&bars->q_full[st], 2 * C::Q_TILE + 2 * BQ * 4);
 #pragma unroll
         for (int t = 0; t < C::SUB; ++t) {
           tma_load_4d(sQ + st * C::Q_TILE + t * (BQ * 128), &tq, &bars->q_full[st], t * 64, h, qb, b);
           tma_load_4d(sdO + st * C::Q_TILE + t * (BQ * 128), &tdo, &bars->q_full[st], t * 64, h, qb, b);
         }
+        // the block's per-query statistics ride the same barrier: 64 log-sum-exps (log2 units) and 64 deltas
+        const long long stat = (static_cast<long long>(b) * Hq + h) * S + qb;
+        bulk_load_1d(sStat + st * 2 * BQ, lse2 + stat, BQ * 4, &bars->q_full[st]);
+        bulk_load_1d(sStat + st * 2 * BQ + BQ, delta + stat, BQ * 4, &bars->q_full[st]);
       }
     }
   } else if (warp == MMA_WARP) {
@@ -420,26 +429,15 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     constexpr int HC = BQ / 2;
     const int q4 = warp & 3, half = warp >> 2;
     const int r = q4 * 32 + lane;                   // key row within the tile == TMEM lane
-    const int tid = threadIdx.x;                    // 0..255
     const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
     const int key = kv0 + r;
     bool ok = true;
-    // All 256 threads meet at a named barrier once per iteration, so no thread leaves the loop early: after a wait
-    // gives up, `ok` turns false for the whole warp and the remaining iterations only keep the barrier count.
     for (int it = 0; it < iters; ++it) {
       const int st = it & 1; const uint32_t ph = (it >> 1) & 1;
-      const int h = hk * rep + it / nqb;
       const int qb = (q_first + it % nqb) * BQ;
-      // per-query statistics of this block, shared by all softmax threads
-      if (tid < 2 * BQ) {
-        float* dst = sStat + st * 2 * BQ;
-        const int qi = qb + (tid & (BQ - 1));
-        const long long idx = (static_cast<long long>(b) * Hq + h) * S + qi;
-        if (tid < BQ) dst[tid] = qi < S ? lse[idx] * LOG2E : INFINITY;     // +inf -> exp2(-inf) = 0 for padded queries
-        else dst[tid] = qi < S ? delta[idx] : 0.f;
-      }
-      named_barrier_sync(1, 256);
-      if (!ok) continue;
+      if (!ok) break;
+      // the block's statistics arrived with its Q / dO tiles
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_full[st], ph, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_FULL); ok = false; continue; }
       const float4* lse4 = reinterpret_cast<const float4*>(sStat + st * 2 * BQ + half * HC);
       const float4* dlt4 = reinterpret_cast<const float4*>(sStat + st * 2 * BQ + BQ + half * HC);
       if (!__all_sync(0xffffffffu, mbar_wait(&bars->st_full[st], ph, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; continue; }
@@ -454,10 +452,10 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 l4 = lse4[i >> 2], d4 = dlt4[i >> 2];
-          float p0 = exp2f(__uint_as_float(sv[i]) * scale_log2 - l4.x);
-          float p1 = exp2f(__uint_as_float(sv[i + 1]) * scale_log2 - l4.y);
-          float p2 = exp2f(__uint_as_float(sv[i + 2]) * scale_log2 - l4.z);
-          float p3 = exp2f(__uint_as_float(sv[i + 3]) * scale_log2 - l4.w);
+          float p0 = fast_exp2(__uint_as_float(sv[i]) * scale_log2 - l4.x);
+          float p1 = fast_exp2(__uint_as_float(sv[i + 1]) * scale_log2 - l4.y);
+          float p2 = fast_exp2(__uint_as_float(sv[i + 2]) * scale_log2 - l4.z);
+          float p3 = fast_exp2(__uint_as_float(sv[i + 3]) * scale_log2 - l4.w);
           if (CAUSAL) {
             if (key > qbase + i) p0 = 0.f;
             if (key > qbase + i + 1) p1 = 0.f;
@@ -542,7 +540,7 @@ static int make_map(CUtensorMap* m, const void* base, int B, int L, int H, int D
 }
 
 template <int D, bool CAUSAL>
-static int launch_bwd(const void* dO, const void* q, const void* k, const void* v, const float* lse, const float* delta,
+static int launch_bwd(const void* dO, const void* q, const void* k, const void* v, const float* lse, const float* lse2, const float* delta,
                       void* dq, void* dk, void* dv, int B, int S, int T, int Hq, int Hkv, const long long* qs,
                       const long long* ks, const long long* vs, const long long* os, const long long* dos,
                       const long long* dqs, const long long* dks, const long long* dvs, float scale, int* err,
@@ -573,7 +571,7 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<D>::SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
     dim3 grid((T + 127) / 128, Hkv, B);
-    kern<<<grid, THREADS, DkvCfg<D>::SMEM, stream>>>(tq, tdo, tk, tv, lse, delta, reinterpret_cast<__nv_bfloat16*>(dk),
+    kern<<<grid, THREADS, DkvCfg<D>::SMEM, stream>>>(tq, tdo, tk, tv, lse2, delta, reinterpret_cast<__nv_bfloat16*>(dk),
                                                       reinterpret_cast<__nv_bfloat16*>(dv), S, T, Hq, Hkv, dks[0], dks[1],
                                                       dks[2], dvs[0], dvs[1], dvs[2], scale, err);
     if ((r = static_cast<int>(cudaGetLastError()))) return r;
@@ -586,25 +584,27 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
 
 // Every tensor is [B, length, heads, D] bf16 with unit stride along D and its own (batch, sequence, head) element
 // strides, so q / k / v may be views of one fused projection output and dq / dk / dv views of one fused gradient
-// buffer. lse [B,Hq,S] comes from the forward; delta [B,Hq,S] is scratch this call fills.
+// buffer. lse [B,Hq,S] comes from the forward; delta is scratch of 2 * B * Hq * S floats this call fills (delta, then
+// the log-sum-exp in log2 units). S must be a multiple of 64 (the statistics travel by 256-byte bulk copies).
 // `strides` holds 8 triples in the order q, k, v, out, dO, dq, dk, dv.
 extern "C" int dewb_flash_bwd(const void* dO, const void* q, const void* k, const void* v, const void* out,
                               const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int T, int Hq,
                               int Hkv, int D, const long long* strides, float scale, int causal, int* err,
                               void* stream_ptr) {
   using namespace dewb::flashbwd;
-  if ((D != 128 && D != 64) || Hq % Hkv != 0) return -3;
+  if ((D != 128 && D != 64) || Hq % Hkv != 0 || S % 64 != 0) return -3;
   const long long *qs = strides, *ks = strides + 3, *vs = strides + 6, *os = strides + 9, *dos = strides + 12,
                   *dqs = strides + 15, *dks = strides + 18, *dvs = strides + 21;
   for (int i = 0; i < 24; ++i) if (strides[i] % 8) return -3;       // 16-byte rows for TMA and the uint4 stores
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
   const long long rows = static_cast<long long>(B) * S * Hq;
   delta_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(dO), reinterpret_cast<const __nv_bfloat16*>(out), delta, B, S, Hq, D,
-      dos[0], dos[1], dos[2], os[0], os[1], os[2]);
+      reinterpret_cast<const __nv_bfloat16*>(dO), reinterpret_cast<const __nv_bfloat16*>(out), lse, delta,
+      delta + static_cast<long long>(B) * Hq * S, B, S, Hq, D, dos[0], dos[1], dos[2], os[0], os[1], os[2]);
+  const float* lse2 = delta + static_cast<long long>(B) * Hq * S;
   if (D == 128)
-    return causal ? launch_bwd<128, true>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream)
-                  : launch_bwd<128, false>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream);
-  return causal ? launch_bwd<64, true>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream)
-                : launch_bwd<64, false>(dO, q, k, v, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream);
+    return causal ? launch_bwd<128, true>(dO, q, k, v, lse, lse2, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream)
+                  : launch_bwd<128, false>(dO, q, k, v, lse, lse2, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream);
+  return causal ? launch_bwd<64, true>(dO, q, k, v, lse, lse2, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream)
+                : launch_bwd<64, false>(dO, q, k, v, lse, lse2, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream);
 }

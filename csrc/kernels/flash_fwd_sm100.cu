@@ -183,13 +183,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       }
       if (ok) {
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < HC / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TMEM_S1 : C::TMEM_S0) + half * HC + c * 32, v);
+        {
+          // both 32-column loads are in flight before the single wait
+          uint32_t v0[32], v1[32];
+          const uint32_t sbase = tmem + lane_addr + (st ? C::TMEM_S1 : C::TMEM_S0) + half * HC;
+          tmem_ld_32x32b_x32(sbase, v0);
+          tmem_ld_32x32b_x32(sbase + 32, v1);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]) * scale_log2;
+          for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(v0[i]) * scale_log2; s[32 + i] = __uint_as_float(v1[i]) * scale_log2; }
         }
         tc_fence_before();
         __syncwarp();
@@ -200,9 +202,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < HC; ++i) if (k0 + i > limit || k0 + i >= T) s[i] = -INFINITY;
         }
-        mt = s[0];
+        {
+          // four independent chains, not one of 64 dependent maxima
+          float m0 = s[0], m1 = s[1], m2 = s[2], m3 = s[3];
 #pragma unroll
-        for (int i = 1; i < HC; ++i) mt = fmaxf(mt, s[i]);
+          for (int i = 4; i < HC; i += 4) { m0 = fmaxf(m0, s[i]); m1 = fmaxf(m1, s[i + 1]); m2 = fmaxf(m2, s[i + 2]); m3 = fmaxf(m3, s[i + 3]); }
+          mt = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        }
       }
       // the row's maximum over all 128 columns: exchange with the thread that holds the other half of the row
       bars->xmax[j & 1][half][r] = mt;
@@ -219,7 +225,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         tc_fence_after();
       }
       if (any_need) {
-        const float alpha = (need && m_used > -INFINITY) ? exp2f(m_used - m_new) : 1.f;
+        const float alpha = (need && m_used > -INFINITY) ? fast_exp2(m_used - m_new) : 1.f;
         if (need) { m_used = m_new; l *= alpha; }
         if (j > 0) {
 #pragma unroll
@@ -237,21 +243,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       }
       // P = exp2(s - m_used) -> bf16, swizzled into shared memory as the A operand of the PV product
       const float mu = (m_used == -INFINITY) ? 0.f : m_used;
-      float rowsum = 0.f;
+      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;      // independent partial sums (fp32, before the bf16 rounding)
 #pragma unroll
       for (int i8 = 0; i8 < HC / 8; ++i8) {
         float p[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { p[i] = exp2f(s[i8 * 8 + i] - mu); }
+        for (int i = 0; i < 8; ++i) { p[i] = fast_exp2(s[i8 * 8 + i] - mu); }
         uint4 pk;
         pk.x = pack_bf16(p[0], p[1]); pk.y = pack_bf16(p[2], p[3]); pk.z = pack_bf16(p[4], p[5]); pk.w = pack_bf16(p[6], p[7]);
-        // sum what the tensor core will see (the bf16-rounded values), so rows of P / l sum to one
-        rowsum += bf16_lo(pk.x) + bf16_hi(pk.x) + bf16_lo(pk.y) + bf16_hi(pk.y) + bf16_lo(pk.z) + bf16_hi(pk.z) +
-                  bf16_lo(pk.w) + bf16_hi(pk.w);
+        rs0 += p[0] + p[4]; rs1 += p[1] + p[5]; rs2 += p[2] + p[6]; rs3 += p[3] + p[7];
         // column half `half` is the 64-column (128-byte) sub-tile `half` of P; i8 is the 16-byte chunk within the row
         *reinterpret_cast<uint4*>(sP + half * (BM * 128) + r * 128 + ((i8 ^ (r & 7)) << 4)) = pk;
       }
-      l += rowsum;
+      l += (rs0 + rs1) + (rs2 + rs3);
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();

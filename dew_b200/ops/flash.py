@@ -48,7 +48,7 @@ def flash_bwd(do, q, k, v, out, lse, causal: bool, scale: float, grads=None):
         dv = torch.empty((B, T, Hkv, D), dtype=q.dtype, device=q.device)
     else:
         dq, dk, dv = grads
-    delta = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    delta = torch.empty((2, B, Hq, S), dtype=torch.float32, device=q.device)     # delta, then lse in log2 units
     if do.stride(3) != 1 or any(st % 8 for st in do.stride()[:3]):
         do = do.contiguous()
     st = []

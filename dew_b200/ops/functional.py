@@ -67,7 +67,7 @@ def _pair_built() -> bool:
 
 
 # Which of this library's two dense kernels large products take ("sm100_tcgen05" or "sm100_pair").
-LARGE_GEMM = os.environ.get("DEWB_LARGE_GEMM", "sm100_tcgen05")
+LARGE_GEMM = os.environ.get("DEWB_LARGE_GEMM", "sm100_pair")
 
 
 # Measured cell: with fewer than ~24 output tiles of 128x256 (decode-sized products, e.g. 128 x 768) the persistent
@@ -98,7 +98,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                 inner_contig=(a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1), M=M, N=N, K=K)
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
     cell = ("skinny",) if tiles < 24 else None
-    if kernel is None and cell is None and LARGE_GEMM == "sm100_pair" and tiles >= 148:
+    if kernel is None and cell is None and LARGE_GEMM == "sm100_pair" and tiles >= 148 and N <= 32768 and _pair_built():
+        # measured: the pair kernel is 5-15 % faster on the layer shapes; the single-CTA kernel keeps the very wide head
         kernel = "sm100_pair"
     which = _GEMM.select(case, forced=kernel, cell=cell)
     if which == "cublas":

@@ -127,15 +127,15 @@ def bench_rows(out, peaks, flush, iters=10):
              bwd_gbs=bb / t_b.median_ms / 1e6, bwd_frac_of_measured=bb / t_b.median_ms / 1e6 / bw, peaks=peaks["source"])
 
 
-def bench_attention(out, peaks, flush, iters=10):
+def bench_attention(out, peaks, flush, iters=10, shapes=None, kernels=("sm100_flash", "sdpa")):
     import torch.nn.functional as F
-    for B, S, Hq, Hkv, D in [(2, 4096, 32, 8, 128), (1, 16384, 32, 8, 128), (8, 4096, 32, 8, 128)]:
+    for B, S, Hq, Hkv, D in shapes or [(2, 4096, 32, 8, 128), (1, 16384, 32, 8, 128), (8, 4096, 32, 8, 128)]:
         q = torch.randn(B, S, Hq, D, device="cuda").to(torch.bfloat16).requires_grad_()
         k = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_()
         v = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_()
         flops = 4.0 * B * Hq * S * S * D / 2
         row = dict(kernel="attention", B=B, S=S, Hq=Hq, Hkv=Hkv, D=D)
-        for name in ("sm100_flash", "sdpa"):
+        for name in kernels:
             try:
                 o = ops.attention(q, k, v, causal=True, kernel=name)
             except Exception as e:
@@ -164,6 +164,7 @@ def main(argv=None):
     ap.add_argument("--only", default="gemm,rows,attention")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--gemm-shape", default=None, help="M,N,K[,a_mn,b_mn]: time one GEMM shape only (small profiling case)")
+    ap.add_argument("--attn-shape", default=None, help="B,S,Hq,Hkv,D: time this library's attention kernels on one shape only")
     args = ap.parse_args(argv)
     peaks = measured_peaks()
     flush = L2Flush()
@@ -173,6 +174,10 @@ def main(argv=None):
         f = [int(x) for x in args.gemm_shape.split(",")]
         f += [0] * (5 - len(f))
         bench_gemm(out, peaks, flush, shapes=[("custom", f[0], f[1], f[2], bool(f[3]), bool(f[4]))], iters=args.iters)
+        return
+    if args.attn_shape:
+        bench_attention(out, peaks, flush, iters=args.iters, shapes=[tuple(int(x) for x in args.attn_shape.split(","))],
+                        kernels=("sm100_flash",))
         return
     if "gemm" in only:
         bench_gemm(out, peaks, flush, iters=args.iters)

@@ -269,7 +269,7 @@ def test_flash_backward_sm100(B, S, Hq, Hkv, D, causal):
 
 @pytest.mark.parametrize("M,N,K,a_mn,b_mn,dtype,acc", [
     (512, 512, 256, False, False, torch.bfloat16, False), (384, 768, 192, False, True, torch.bfloat16, False),
-    (300, 520, 136, True, True, torch.float32, True), (1024, 256, 64, True, False, torch.float32, False),
+    (304, 520, 136, True, True, torch.float32, True), (1024, 256, 64, True, False, torch.float32, False),
     (2048, 4096, 1024, False, False, torch.bfloat16, True)])
 def test_gemm_pair_kernel_matches_reference(M, N, K, a_mn, b_mn, dtype, acc):
     """The CTA-pair (cta_group::2) kernel: every operand layout, epilogue, odd sizes with row / column / reduction tails."""
