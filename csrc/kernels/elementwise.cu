@@ -296,6 +296,137 @@ rmsnorm_fwd_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ oth
   }
 }
 
+// Wide rows (1024 <= d <= 8192): one 128-thread block per row, VPT 16-byte vectors per thread, every load of the row
+// issued before the first use. Low register count keeps 12+ blocks resident per SM, which is what hides DRAM latency.
+__device__ __forceinline__ float block128_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) red[warp] = v;
+  __syncthreads();
+  return red[0] + red[1] + red[2] + red[3];
+}
+
+template <int MODE, int VPT>
+__global__ void __launch_bounds__(128)
+rmsnorm_fwd_block_kernel(const bf16* __restrict__ x, const bf16* __restrict__ other, const bf16* __restrict__ w,
+                         bf16* __restrict__ y, bf16* __restrict__ h_out, float* __restrict__ rstd_out, int d, float eps) {
+  __shared__ float red[4];
+  const long long row = blockIdx.x;
+  const int nvec = d >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * d);
+  const uint4* orow = reinterpret_cast<const uint4*>(other + row * d);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4 cache[VPT], oth[MODE != 0 ? VPT : 1], wv[VPT];
+#pragma unroll
+  for (int c = 0; c < VPT; ++c) {
+    const int i = threadIdx.x + c * 128;
+    if (i < nvec) {
+      cache[c] = xr[i];
+      if (MODE != 0) oth[c] = orow[i];
+      wv[c] = wr[i];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < VPT; ++c) {
+    const int i = threadIdx.x + c * 128;
+    if (i < nvec) {
+      float f[8]; unpack8(cache[c], f);
+      if (MODE == 1) {
+        float g[8]; unpack8(oth[c], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += g[j];
+        cache[c] = pack8(f);
+        reinterpret_cast<uint4*>(h_out + row * d)[i] = cache[c];
+        unpack8(cache[c], f);            // the statistics see the rounded sum, as every later reader does
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
+  }
+  ss = block128_sum(ss, red);
+  const float rstd = rsqrtf(ss / d + eps);
+  if (threadIdx.x == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+#pragma unroll
+  for (int c = 0; c < VPT; ++c) {
+    const int i = threadIdx.x + c * 128;
+    if (i < nvec) {
+      float f[8], g[8]; unpack8(cache[c], f); unpack8(wv[c], g);
+      if (MODE == 2) {
+        float z[8]; unpack8(oth[c], z);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = f[j] * rstd * g[j] * (z[j] / (1.f + __expf(-z[j])));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = f[j] * rstd * g[j];
+      }
+      reinterpret_cast<uint4*>(y + row * d)[i] = pack8(f);
+    }
+  }
+}
+
+template <bool GATED, int VPT>
+__global__ void __launch_bounds__(128)
+rmsnorm_bwd_dx_block_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                            const float* __restrict__ rstd, const bf16* __restrict__ dres, const bf16* __restrict__ z,
+                            bf16* __restrict__ dx, bf16* __restrict__ dz, int d) {
+  __shared__ float red[4];
+  const long long row = blockIdx.x;
+  const int nvec = d >> 3;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  const float rs = rstd[row];
+  uint4 gv[VPT], xv[VPT], wv[VPT], rv[VPT], zv[GATED ? VPT : 1];
+#pragma unroll
+  for (int c = 0; c < VPT; ++c) {
+    const int i = threadIdx.x + c * 128;
+    if (i < nvec) {
+      gv[c] = reinterpret_cast<const uint4*>(dy + row * d)[i];
+      xv[c] = reinterpret_cast<const uint4*>(x + row * d)[i];
+      wv[c] = wr[i];
+      if (dres != nullptr) rv[c] = reinterpret_cast<const uint4*>(dres + row * d)[i];
+      if (GATED) zv[c] = reinterpret_cast<const uint4*>(z + row * d)[i];
+    }
+  }
+  float dot = 0.f;
+#pragma unroll
+  for (int c = 0; c < VPT; ++c) {
+    const int i = threadIdx.x + c * 128;
+    if (i < nvec) {
+      float a[8], b[8], ww[8]; unpack8(gv[c], a); unpack8(xv[c], b); unpack8(wv[c], ww);
+      if (GATED) {
+        float zz[8], dzv[8]; unpack8(zv[c], zz);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float sg = 1.f / (1.f + __expf(-zz[j]));
+          dzv[j] = a[j] * ww[j] * (b[j] * rs) * (sg * (1.f + zz[j] * (1.f - sg)));
+          a[j] *= zz[j] * sg;
+        }
+        reinterpret_cast<uint4*>(dz + row * d)[i] = pack8(dzv);
+        gv[c] = pack8(a);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += a[j] * ww[j] * (b[j] * rs);
+    }
+  }
+  dot = block128_sum(dot, red) / d;
+#pragma unroll
+  for (int c = 0; c < VPT; ++c) {
+    const int i = threadIdx.x + c * 128;
+    if (i < nvec) {
+      float a[8], b[8], ww[8], o[8]; unpack8(gv[c], a); unpack8(xv[c], b); unpack8(wv[c], ww);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = rs * (a[j] * ww[j] - (b[j] * rs) * dot);
+      if (dres != nullptr) {
+        float r[8]; unpack8(rv[c], r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
+      }
+      reinterpret_cast<uint4*>(dx + row * d)[i] = pack8(o);
+    }
+  }
+}
+
 // dx (and dz when gated) for one row per lane group; dw is a separate column reduction (rmsnorm_dw_kernel).
 template <bool GATED, int VPL>
 __global__ void __launch_bounds__(256)
@@ -717,6 +848,16 @@ extern "C" int dewb_rmsnorm_fwd(const void* x, const void* other, const void* w,
     const int need = (nvec + G - 1) / G;
     const long long rows_per_block = 8LL * (32 / G);
     const unsigned blocks = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
+    if (nvec >= 128) {
+      const int vpt = (nvec + 127) / 128;
+      const unsigned nb = static_cast<unsigned>(rows);
+#define DEWB_FWD_BLOCK(MODE, VPT) rmsnorm_fwd_block_kernel<MODE, VPT><<<nb, 128, 0, STREAM(stream)>>>(xp, op, wp, yp, hp, rstd, d, eps)
+#define DEWB_FWD_BMODE(VPT) do { if (mode == 0) DEWB_FWD_BLOCK(0, VPT); else if (mode == 1) DEWB_FWD_BLOCK(1, VPT); else DEWB_FWD_BLOCK(2, VPT); } while (0)
+      if (vpt <= 1) DEWB_FWD_BMODE(1); else if (vpt <= 2) DEWB_FWD_BMODE(2); else DEWB_FWD_BMODE(4);
+#undef DEWB_FWD_BMODE
+#undef DEWB_FWD_BLOCK
+      return LAST_ERR();
+    }
 #define DEWB_FWD_ROWS(MODE, VPL) rmsnorm_fwd_rows_kernel<MODE, VPL><<<blocks, 256, 0, STREAM(stream)>>>(xp, op, wp, yp, hp, rstd, rows, d, eps, G)
 #define DEWB_FWD_MODE(VPL) do { if (mode == 0) DEWB_FWD_ROWS(0, VPL); else if (mode == 1) DEWB_FWD_ROWS(1, VPL); else DEWB_FWD_ROWS(2, VPL); } while (0)
     if (need <= 1) DEWB_FWD_MODE(1); else if (need <= 2) DEWB_FWD_MODE(2); else if (need <= 4) DEWB_FWD_MODE(4);
@@ -755,8 +896,17 @@ extern "C" int dewb_rmsnorm_bwd(const void* dy, const void* x, const void* w, co
 #define DEWB_BWD_ROWS(GATED, VPL) rmsnorm_bwd_dx_rows_kernel<GATED, VPL><<<nb, 256, 0, STREAM(stream)>>>( \
       (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, (const bf16*)z, (bf16*)dx, (bf16*)dz, rows, d, G)
 #define DEWB_BWD_G(VPL) do { if (z != nullptr) DEWB_BWD_ROWS(true, VPL); else DEWB_BWD_ROWS(false, VPL); } while (0)
-    if (need <= 1) DEWB_BWD_G(1); else if (need <= 2) DEWB_BWD_G(2); else if (need <= 4) DEWB_BWD_G(4);
+#define DEWB_BWD_BLOCK(GATED, VPT) rmsnorm_bwd_dx_block_kernel<GATED, VPT><<<static_cast<unsigned>(rows), 128, 0, STREAM(stream)>>>( \
+      (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, (const bf16*)z, (bf16*)dx, (bf16*)dz, d)
+#define DEWB_BWD_B(VPT) do { if (z != nullptr) DEWB_BWD_BLOCK(true, VPT); else DEWB_BWD_BLOCK(false, VPT); } while (0)
+    if (nvec >= 128) {
+      const int vpt = (nvec + 127) / 128;
+      if (vpt <= 1) DEWB_BWD_B(1); else if (vpt <= 2) DEWB_BWD_B(2); else DEWB_BWD_B(4);
+    }
+    else if (need <= 1) DEWB_BWD_G(1); else if (need <= 2) DEWB_BWD_G(2); else if (need <= 4) DEWB_BWD_G(4);
     else if (need <= 8) DEWB_BWD_G(8); else DEWB_BWD_G(16);
+#undef DEWB_BWD_B
+#undef DEWB_BWD_BLOCK
 #undef DEWB_BWD_G
 #undef DEWB_BWD_ROWS
     // dw: column reduction with `blocks` row splits, folded by colsum_kernel

@@ -275,22 +275,32 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
 // ---------------------------------------------------------------------------------------------------------------
 // dK / dV kernel
+//   warps 0..3  softmax group 0 : iterations 0, 2, 4, ...   one thread per key row, all 64 query columns
+//   warps 4..7  softmax group 1 : iterations 1, 3, 5, ...
+//               Each group owns a pair of TMEM score buffers (S^T, dP^T) and a pair of shared-memory operand buffers
+//               (P^T, dS^T); the gradient accumulators dV and dK are shared (the MMA thread issues every product,
+//               and accumulation commutes). While one group computes its exponentials the other loads scores or
+//               stores operands. No reduction crosses threads: the row statistics come with the Q / dO tiles.
+//   warp 8      TMA producer : K, V once; then Q, dO tiles and the block's 64 + 64 statistics into a 3-stage ring
+//   warp 9      MMA issuer   : scores two iterations ahead, gradient products as each group delivers its operands
 template <int D>
 struct DkvCfg {
-  static constexpr int BKV = 128, BQ = 64;
+  static constexpr int BKV = 128, BQ = 64, QSTAGES = 3;
   static constexpr int SUB = D / 64;
   static constexpr int KV_TILE = BKV * D * 2;        // [128 x D]
   static constexpr int Q_TILE = BQ * D * 2;          // [64 x D]
   static constexpr int P_BYTES = BKV * BQ * 2;       // [128 x 64]
-  static constexpr int SMEM = 2 * KV_TILE + 4 * Q_TILE + 2 * P_BYTES + 2 * 2 * BQ * 4 + 1024 + 256;
+  static constexpr int STAT_BYTES = 2 * BQ * 4;      // per stage: 64 log-sum-exps, 64 deltas
+  static constexpr int SMEM = 2 * KV_TILE + QSTAGES * 2 * Q_TILE + 4 * P_BYTES + QSTAGES * STAT_BYTES + 1024 + 256;
   static constexpr int TM_ST0 = 0, TM_DPT0 = 64, TM_ST1 = 128, TM_DPT1 = 192, TM_DV = 256, TM_DK = 256 + D, TM_COLS = 512;
 };
 
 struct DkvBars {
   uint64_t kv_full;
-  uint64_t q_full[2], q_empty[2];
-  uint64_t st_full[2], st_empty[2];
-  uint64_t pds_full, acc_done;
+  uint64_t q_full[3], q_empty[3];
+  uint64_t st_full[2], st_empty[2];     // per softmax group
+  uint64_t pds_full[2], acc_done[2];    // per softmax group
+  uint64_t all_done;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -303,7 +313,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
                  __nv_bfloat16* __restrict__ dv, int S, int T, int Hq, int Hkv, long long dk_sb, long long dk_ss,
                  long long dk_sh, long long dv_sb, long long dv_ss, long long dv_sh, float scale, int* __restrict__ err) {
   using C = DkvCfg<D>;
-  constexpr int BKV = C::BKV, BQ = C::BQ;
+  constexpr int BKV = C::BKV, BQ = C::BQ, QS = C::QSTAGES;
   extern __shared__ uint8_t smem_raw[];
   {
     // An earlier launch reported a timed-out wait: leave at once instead of queueing more waits behind it. One
@@ -316,12 +326,12 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + C::KV_TILE;
-  uint8_t* sQ = sV + C::KV_TILE;            // 2 stages
-  uint8_t* sdO = sQ + 2 * C::Q_TILE;        // 2 stages
-  uint8_t* sP = sdO + 2 * C::Q_TILE;
-  uint8_t* sdS = sP + C::P_BYTES;
-  float* sStat = reinterpret_cast<float*>(sdS + C::P_BYTES);   // [2 stages][lse2 64 | delta 64]
-  DkvBars* bars = reinterpret_cast<DkvBars*>(reinterpret_cast<uint8_t*>(sStat) + 2 * 2 * BQ * 4);
+  uint8_t* sQ = sV + C::KV_TILE;             // QS stages
+  uint8_t* sdO = sQ + QS * C::Q_TILE;        // QS stages
+  uint8_t* sP = sdO + QS * C::Q_TILE;        // one per group
+  uint8_t* sdS = sP + 2 * C::P_BYTES;        // one per group
+  float* sStat = reinterpret_cast<float*>(sdS + 2 * C::P_BYTES);   // [QS stages][lse2 64 | delta 64]
+  DkvBars* bars = reinterpret_cast<DkvBars*>(reinterpret_cast<uint8_t*>(sStat) + QS * C::STAT_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -335,11 +345,12 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->kv_full, 1);
+    for (int i = 0; i < QS; ++i) { mbar_init(&bars->q_full[i], 1); mbar_init(&bars->q_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->q_full[i], 1); mbar_init(&bars->q_empty[i], 1);
-      mbar_init(&bars->st_full[i], 1); mbar_init(&bars->st_empty[i], 8);
+      mbar_init(&bars->st_full[i], 1); mbar_init(&bars->st_empty[i], 4);
+      mbar_init(&bars->pds_full[i], 4); mbar_init(&bars->acc_done[i], 1);
     }
-    mbar_init(&bars->pds_full, 8); mbar_init(&bars->acc_done, 1);
+    mbar_init(&bars->all_done, 1);
     bars->abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -360,58 +371,62 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         tma_load_4d(sV + t * (BKV * 128), &tv, &bars->kv_full, t * 64, hk, kv0, b);
       }
       for (int it = 0; it < iters; ++it) {
-        const int st = it & 1; const uint32_t ph = (it >> 1) & 1;
+        const int qs = it % QS; const uint32_t ph = (it / QS) & 1;
         const int h = hk * rep + it / nqb;
         const int qb = (q_first + it % nqb) * BQ;
-        if (!mbar_wait(&bars->q_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); break; }
-        mbar_expect_tx(&bars->q_full[st], 2 * C::Q_TILE + 2 * BQ * 4);
+        if (!mbar_wait(&bars->q_empty[qs], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); break; }
+        mbar_expect_tx(&bars->q_full[qs], 2 * C::Q_TILE + C::STAT_BYTES);
 #pragma unroll
         for (int t = 0; t < C::SUB; ++t) {
-          tma_load_4d(sQ + st * C::Q_TILE + t * (BQ * 128), &tq, &bars->q_full[st], t * 64, h, qb, b);
-          tma_load_4d(sdO + st * C::Q_TILE + t * (BQ * 128), &tdo, &bars->q_full[st], t * 64, h, qb, b);
+          tma_load_4d(sQ + qs * C::Q_TILE + t * (BQ * 128), &tq, &bars->q_full[qs], t * 64, h, qb, b);
+          tma_load_4d(sdO + qs * C::Q_TILE + t * (BQ * 128), &tdo, &bars->q_full[qs], t * 64, h, qb, b);
         }
         // the block's per-query statistics ride the same barrier: 64 log-sum-exps (log2 units) and 64 deltas
         const long long stat = (static_cast<long long>(b) * Hq + h) * S + qb;
-        bulk_load_1d(sStat + st * 2 * BQ, lse2 + stat, BQ * 4, &bars->q_full[st]);
-        bulk_load_1d(sStat + st * 2 * BQ + BQ, delta + stat, BQ * 4, &bars->q_full[st]);
+        bulk_load_1d(sStat + qs * 2 * BQ, lse2 + stat, BQ * 4, &bars->q_full[qs]);
+        bulk_load_1d(sStat + qs * 2 * BQ + BQ, delta + stat, BQ * 4, &bars->q_full[qs]);
       }
     }
   } else if (warp == MMA_WARP) {
+    // Iteration `it` belongs to group g = it & 1 (its number within the group is it >> 1) and to Q stage it % QS.
     if (lane == 0) {
       constexpr uint32_t idesc_st = make_idesc(BKV, BQ, 1, 1, 0, 0);
       constexpr uint32_t idesc_acc = make_idesc(BKV, D, 1, 1, 0, 1);
       bool ok = mbar_wait(&bars->kv_full, 0, abort_flag);
       if (!ok) atomicCAS(err, 0, ERR_WAIT_FULL);
       auto issue_scores = [&](int it) -> bool {
-        const int st = it & 1; const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&bars->q_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
-        if (!mbar_wait(&bars->st_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
+        const int g = it & 1; const uint32_t phg = (it >> 1) & 1;
+        const int qs = it % QS; const uint32_t phq = (it / QS) & 1;
+        if (!mbar_wait(&bars->q_full[qs], phq, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
+        if (!mbar_wait(&bars->st_empty[g], phg ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
         tc_fence_after();
-        const uint32_t ka = smem_u32(sK), va = smem_u32(sV), qa = smem_u32(sQ + st * C::Q_TILE), da = smem_u32(sdO + st * C::Q_TILE);
+        const uint32_t ka = smem_u32(sK), va = smem_u32(sV), qa = smem_u32(sQ + qs * C::Q_TILE), da = smem_u32(sdO + qs * C::Q_TILE);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t aoff = (kk >> 2) * (BKV * 128) + (kk & 3) * 32;
           const uint32_t boff = (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tmem + (st ? C::TM_ST1 : C::TM_ST0), make_sdesc_sw128(ka + aoff, 16, 1024),
+          umma_bf16_ss(tmem + (g ? C::TM_ST1 : C::TM_ST0), make_sdesc_sw128(ka + aoff, 16, 1024),
                        make_sdesc_sw128(qa + boff, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t aoff = (kk >> 2) * (BKV * 128) + (kk & 3) * 32;
           const uint32_t boff = (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tmem + (st ? C::TM_DPT1 : C::TM_DPT0), make_sdesc_sw128(va + aoff, 16, 1024),
+          umma_bf16_ss(tmem + (g ? C::TM_DPT1 : C::TM_DPT0), make_sdesc_sw128(va + aoff, 16, 1024),
                        make_sdesc_sw128(da + boff, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&bars->st_full[st]);
+        umma_commit(&bars->st_full[g]);
         return true;
       };
       if (ok && iters > 0) ok = issue_scores(0);
+      if (ok && iters > 1) ok = issue_scores(1);
       for (int it = 0; it < iters && ok; ++it) {
-        if (it + 1 < iters) { ok = issue_scores(it + 1); if (!ok) break; }
-        const int st = it & 1;
-        if (!mbar_wait(&bars->pds_full, it & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+        const int g = it & 1; const uint32_t phg = (it >> 1) & 1;
+        const int qs = it % QS;
+        if (!mbar_wait(&bars->pds_full[g], phg, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
         tc_fence_after();
-        const uint32_t pa = smem_u32(sP), sa = smem_u32(sdS), qa = smem_u32(sQ + st * C::Q_TILE), da = smem_u32(sdO + st * C::Q_TILE);
+        const uint32_t pa = smem_u32(sP + g * C::P_BYTES), sa = smem_u32(sdS + g * C::P_BYTES);
+        const uint32_t qa = smem_u32(sQ + qs * C::Q_TILE), da = smem_u32(sdO + qs * C::Q_TILE);
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk)
           umma_bf16_ss(tmem + C::TM_DV, make_sdesc_sw128(pa + kk * 32, 16, 1024),
@@ -420,38 +435,43 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         for (int kk = 0; kk < BQ / 16; ++kk)
           umma_bf16_ss(tmem + C::TM_DK, make_sdesc_sw128(sa + kk * 32, 16, 1024),
                        make_sdesc_sw128(qa + kk * 2048, BQ * 128, 1024), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&bars->q_empty[st]);
-        umma_commit(&bars->acc_done);
+        umma_commit(&bars->q_empty[qs]);
+        umma_commit(&bars->acc_done[g]);
+        if (it + 2 < iters) ok = issue_scores(it + 2);
       }
+      if (ok) umma_commit(&bars->all_done);        // every product issued above has completed when this fires
     }
   } else {
-    // two threads per key row: warps w and w + 4 read TMEM lane quarter w & 3 and take 32 of the 64 query columns each
-    constexpr int HC = BQ / 2;
-    const int q4 = warp & 3, half = warp >> 2;
+    const int q4 = warp & 3, g = warp >> 2;
     const int r = q4 * 32 + lane;                   // key row within the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
     const int key = kv0 + r;
+    uint8_t* myP = sP + g * C::P_BYTES;
+    uint8_t* mydS = sdS + g * C::P_BYTES;
+    const uint32_t st_col = g ? C::TM_ST1 : C::TM_ST0, dp_col = g ? C::TM_DPT1 : C::TM_DPT0;
     bool ok = true;
-    for (int it = 0; it < iters; ++it) {
-      const int st = it & 1; const uint32_t ph = (it >> 1) & 1;
+    int mine = 0;
+    for (int it = g; it < iters && ok; it += 2, ++mine) {
+      const uint32_t phg = mine & 1;
+      const int qs = it % QS; const uint32_t phq = (it / QS) & 1;
       const int qb = (q_first + it % nqb) * BQ;
-      if (!ok) break;
       // the block's statistics arrived with its Q / dO tiles
-      if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_full[st], ph, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_FULL); ok = false; continue; }
-      const float4* lse4 = reinterpret_cast<const float4*>(sStat + st * 2 * BQ + half * HC);
-      const float4* dlt4 = reinterpret_cast<const float4*>(sStat + st * 2 * BQ + BQ + half * HC);
-      if (!__all_sync(0xffffffffu, mbar_wait(&bars->st_full[st], ph, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; continue; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_full[qs], phq, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_FULL); ok = false; break; }
+      const float4* lse4 = reinterpret_cast<const float4*>(sStat + qs * 2 * BQ);
+      const float4* dlt4 = reinterpret_cast<const float4*>(sStat + qs * 2 * BQ + BQ);
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->st_full[g], phg, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
       tc_fence_after();
-      uint32_t pp[HC / 2], ds[HC / 2];
-      {
+      uint32_t pp[BQ / 2], ds[BQ / 2];
+#pragma unroll
+      for (int c = 0; c < BQ / 32; ++c) {
         uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TM_ST1 : C::TM_ST0) + half * HC, sv);
-        tmem_ld_32x32b_x32(tmem + lane_addr + (st ? C::TM_DPT1 : C::TM_DPT0) + half * HC, dv);
+        tmem_ld_32x32b_x32(tmem + lane_addr + st_col + c * 32, sv);
+        tmem_ld_32x32b_x32(tmem + lane_addr + dp_col + c * 32, dv);
         tmem_ld_wait();
-        const int qbase = qb + half * HC + (T - S);
+        const int qbase = qb + c * 32 + (T - S);
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          const float4 l4 = lse4[i >> 2], d4 = dlt4[i >> 2];
+          const float4 l4 = lse4[(c * 32 + i) >> 2], d4 = dlt4[(c * 32 + i) >> 2];
           float p0 = fast_exp2(__uint_as_float(sv[i]) * scale_log2 - l4.x);
           float p1 = fast_exp2(__uint_as_float(sv[i + 1]) * scale_log2 - l4.y);
           float p2 = fast_exp2(__uint_as_float(sv[i + 2]) * scale_log2 - l4.z);
@@ -463,48 +483,50 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
             if (key > qbase + i + 3) p3 = 0.f;
           }
           if (key >= T) { p0 = 0.f; p1 = 0.f; p2 = 0.f; p3 = 0.f; }
-          pp[i >> 1] = pack_bf16(p0, p1);
-          pp[(i >> 1) + 1] = pack_bf16(p2, p3);
-          ds[i >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - d4.x), p1 * (__uint_as_float(dv[i + 1]) - d4.y));
-          ds[(i >> 1) + 1] = pack_bf16(p2 * (__uint_as_float(dv[i + 2]) - d4.z), p3 * (__uint_as_float(dv[i + 3]) - d4.w));
+          const int o = (c * 32 + i) >> 1;
+          pp[o] = pack_bf16(p0, p1);
+          pp[o + 1] = pack_bf16(p2, p3);
+          ds[o] = pack_bf16(p0 * (__uint_as_float(dv[i]) - d4.x), p1 * (__uint_as_float(dv[i + 1]) - d4.y));
+          ds[o + 1] = pack_bf16(p2 * (__uint_as_float(dv[i + 2]) - d4.z), p3 * (__uint_as_float(dv[i + 3]) - d4.w));
         }
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->st_empty[st]);
-      if (it > 0) {
-        if (!__all_sync(0xffffffffu, mbar_wait(&bars->acc_done, (it - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; continue; }
+      if (lane == 0) mbar_arrive(&bars->st_empty[g]);
+      // this group's previous gradient products must have read its operand buffers
+      if (mine > 0) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->acc_done[g], (mine - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
       }
-      // each key row of P^T / dS^T is one 128-byte swizzled row; this thread writes 16-byte chunks half*4 .. half*4+3
+      // each key row of P^T / dS^T is one 128-byte swizzled row of eight 16-byte chunks
 #pragma unroll
-      for (int c = 0; c < HC / 8; ++c) {
-        const int chunk = half * (HC / 8) + c;
-        const int off = r * 128 + ((chunk ^ (r & 7)) << 4);
-        *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[c * 4], pp[c * 4 + 1], pp[c * 4 + 2], pp[c * 4 + 3]);
-        *reinterpret_cast<uint4*>(sdS + off) = make_uint4(ds[c * 4], ds[c * 4 + 1], ds[c * 4 + 2], ds[c * 4 + 3]);
+      for (int c = 0; c < BQ / 8; ++c) {
+        const int off = r * 128 + ((c ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(myP + off) = make_uint4(pp[c * 4], pp[c * 4 + 1], pp[c * 4 + 2], pp[c * 4 + 3]);
+        *reinterpret_cast<uint4*>(mydS + off) = make_uint4(ds[c * 4], ds[c * 4 + 1], ds[c * 4 + 2], ds[c * 4 + 3]);
       }
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->pds_full);
+      if (lane == 0) mbar_arrive(&bars->pds_full[g]);
     }
     if (ok && iters > 0) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&bars->acc_done, (iters - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->all_done, 0, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
     }
     if (ok) {
       tc_fence_after();
-      __nv_bfloat16* kout = dk + b * dk_sb + static_cast<long long>(key) * dk_ss + hk * dk_sh + half * (D / 2);
-      __nv_bfloat16* vout = dv + b * dv_sb + static_cast<long long>(key) * dv_ss + hk * dv_sh + half * (D / 2);
+      // group g writes gradient columns [g * D/2, (g + 1) * D/2)
+      __nv_bfloat16* kout = dk + b * dk_sb + static_cast<long long>(key) * dk_ss + hk * dk_sh + g * (D / 2);
+      __nv_bfloat16* vout = dv + b * dv_sb + static_cast<long long>(key) * dv_ss + hk * dv_sh + g * (D / 2);
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
-        uint32_t a[32], g[32];
+        uint32_t a[32], gr[32];
         if (iters > 0) {
-          tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DV + half * (D / 2) + c * 32, a);
-          tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DK + half * (D / 2) + c * 32, g);
+          tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DV + g * (D / 2) + c * 32, a);
+          tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DK + g * (D / 2) + c * 32, gr);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) { a[i] = 0; g[i] = 0; }
+          for (int i = 0; i < 32; ++i) { a[i] = 0; gr[i] = 0; }
         }
         if (key < T) {
           uint4* v4 = reinterpret_cast<uint4*>(vout + c * 32);
@@ -516,10 +538,10 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
             pv.y = pack_bf16(__uint_as_float(a[q * 8 + 2]), __uint_as_float(a[q * 8 + 3]));
             pv.z = pack_bf16(__uint_as_float(a[q * 8 + 4]), __uint_as_float(a[q * 8 + 5]));
             pv.w = pack_bf16(__uint_as_float(a[q * 8 + 6]), __uint_as_float(a[q * 8 + 7]));
-            pk.x = pack_bf16(__uint_as_float(g[q * 8 + 0]) * scale, __uint_as_float(g[q * 8 + 1]) * scale);
-            pk.y = pack_bf16(__uint_as_float(g[q * 8 + 2]) * scale, __uint_as_float(g[q * 8 + 3]) * scale);
-            pk.z = pack_bf16(__uint_as_float(g[q * 8 + 4]) * scale, __uint_as_float(g[q * 8 + 5]) * scale);
-            pk.w = pack_bf16(__uint_as_float(g[q * 8 + 6]) * scale, __uint_as_float(g[q * 8 + 7]) * scale);
+            pk.x = pack_bf16(__uint_as_float(gr[q * 8 + 0]) * scale, __uint_as_float(gr[q * 8 + 1]) * scale);
+            pk.y = pack_bf16(__uint_as_float(gr[q * 8 + 2]) * scale, __uint_as_float(gr[q * 8 + 3]) * scale);
+            pk.z = pack_bf16(__uint_as_float(gr[q * 8 + 4]) * scale, __uint_as_float(gr[q * 8 + 5]) * scale);
+            pk.w = pack_bf16(__uint_as_float(gr[q * 8 + 6]) * scale, __uint_as_float(gr[q * 8 + 7]) * scale);
             v4[q] = pv; k4[q] = pk;
           }
         }

@@ -78,10 +78,13 @@ def test_server_with_cuda_graph_matches_offline_generation():
         tickets = [server.submit(p, 8) for p in prompts]
         server.run(max_steps=400)
         L.check_status()
-        agree = 0
+        agree, whole = 0, 0
         for r, t in enumerate(tickets):
             assert t.done
             want = offline.tokens[r, len(prompts[r]): int(offline.lengths[r])].tolist()
             agree += sum(a == b for a, b in zip(t.tokens, want))
-        # bf16 ties can flip an argmax between the batched and per-request paths; demand near-total agreement
-        assert agree >= 0.9 * 8 * len(prompts), (graph, agree)
+            whole += int(list(t.tokens) == want)
+        # A random-init model has near-tied logits, and the batched decode products round differently from the
+        # per-request ones: a flipped argmax changes the rest of that request.  Corrupted KV pages or positions would
+        # break most requests, so demand that most agree in full and that the total stays high.
+        assert whole >= len(prompts) - 2 and agree >= 0.7 * 8 * len(prompts), (graph, agree, whole)
