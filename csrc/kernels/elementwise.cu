@@ -1054,8 +1054,16 @@ extern "C" int dewb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
   const unsigned nb = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
 #define DEWB_NA_ROWS(VPL) rmsnorm_bwd_dx_rows_kernel<false, VPL><<<nb, 256, 0, STREAM(stream)>>>( \
     (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, nullptr, (bf16*)dx, nullptr, rows, d, G)
-  if (need <= 1) DEWB_NA_ROWS(1); else if (need <= 2) DEWB_NA_ROWS(2); else if (need <= 4) DEWB_NA_ROWS(4);
+#define DEWB_NA_BLOCK(VPT) rmsnorm_bwd_dx_block_kernel<false, VPT><<<static_cast<unsigned>(rows), 128, 0, STREAM(stream)>>>( \
+    (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, nullptr, (bf16*)dx, nullptr, d)
+  // the same kernel choice as dewb_rmsnorm_bwd, so both entries perform the same arithmetic
+  if (nvec >= 128) {
+    const int vpt = (nvec + 127) / 128;
+    if (vpt <= 1) DEWB_NA_BLOCK(1); else if (vpt <= 2) DEWB_NA_BLOCK(2); else DEWB_NA_BLOCK(4);
+  }
+  else if (need <= 1) DEWB_NA_ROWS(1); else if (need <= 2) DEWB_NA_ROWS(2); else if (need <= 4) DEWB_NA_ROWS(4);
   else if (need <= 8) DEWB_NA_ROWS(8); else DEWB_NA_ROWS(16);
+#undef DEWB_NA_BLOCK
 #undef DEWB_NA_ROWS
   // every split row of the array that colsum reads below is written here first: stale contents never leak
   int splits = DEWB_NOALLOC_MAX_SPLITS;

@@ -88,6 +88,102 @@ class TensorParallel:
         return allp[best, torch.arange(pair.shape[0], device=pair.device), 1].long()
 
 
+class SequenceParallelLinear:
+    """The two tensor-parallel products of a sequence-parallel region, each ONE kernel that does the product and its
+    collective over peer memory (``csrc/kernels/gemm_comm_sm100.cu``):
+
+    * ``gather_matmul(x_shard, w)``: ``all_gather_rows(x) @ w.T`` - A tiles are read from the owning rank's memory by
+      TMA while other tiles compute; nothing is gathered first.
+    * ``matmul_scatter(x, w, residual_shard)``: ``reduce_scatter_rows(x @ w.T) (+ residual)`` - finished tiles are stored
+      into the owner's partial buffer from the epilogue; the owner sums the W slots.
+
+    Row counts are fixed at construction (``rows`` total, a multiple of ``128 * world``).  On CPU ranks, one rank, or
+    unfit shapes the same arithmetic runs through ``torch.distributed``.
+
+    Reference: sequence-parallel (``SPREAD``) activations around the Megatron-split projections
+    (src/dew/nn/sharding.py:262-280, src/dew/mesh.py:101-146)."""
+
+    def __init__(self, group, rows: int, in_features: int, out_features: int, device=None, wait_limit_s: float = 20.0):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device) if device is not None else torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        self.rows, self.in_features, self.out_features = rows, in_features, out_features
+        self.limit_ns = int(wait_limit_s * 1e9)
+        self.seq = 0
+        self.fused = self.device.type == "cuda" and self.world > 1 and rows % (128 * self.world) == 0
+        if self.fused:
+            W = self.world
+            self.x_shard = SymmetricBuffer((rows // W) * in_features, torch.bfloat16, self.device, group, zero=True)
+            self.partials = SymmetricBuffer(W * (rows // W) * out_features, torch.bfloat16, self.device, group, zero=True)
+            self.flags = SymmetricBuffer(64, torch.int32, self.device, group, zero=True)
+            self.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def gather_matmul(self, x_shard: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """``x_shard [rows / W, K]`` (this rank's rows), ``w [N, K]`` -> ``[rows, N]``."""
+        W = self.world
+        if not self.fused or x_shard.dtype != torch.bfloat16 or x_shard.shape[1] != self.in_features:
+            if W == 1:
+                return ops.linear(x_shard, w)
+            parts = [torch.empty_like(x_shard) for _ in range(W)]
+            dist.all_gather(parts, x_shard.contiguous(), group=self.group)
+            return ops.linear(torch.cat(parts, 0), w)
+        lib = L.load()
+        self.seq += 1
+        K, N = self.in_features, w.shape[0]
+        # every peer must have finished reading the previous call's shard before it is overwritten (flag slot 2)
+        L.check(lib.dewb_wait_flags(L.ptr(self.flags.tensor), ctypes.c_int(2), ctypes.c_int(W), ctypes.c_uint(self.seq - 1),
+                                    ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.device)), L.stream_ptr()), "wait_flags")
+        # the shard goes into peer-visible memory (a producer that writes there directly skips this copy), then the flag
+        self.x_shard.tensor.view(self.rows // W, K).copy_(x_shard)
+        L.check(lib.dewb_signal_flags(self.flags.ptr_array(), ctypes.c_int(0), ctypes.c_int(self.rank), ctypes.c_int(W),
+                                      ctypes.c_uint(self.seq), L.stream_ptr()), "signal_flags")
+        out = torch.empty((self.rows, N), dtype=torch.bfloat16, device=self.device)
+        L.check(lib.dewb_ag_gemm_bf16(self.x_shard.ptr_array(), L.ptr(w), L.ptr(out), ctypes.c_int(self.rows), ctypes.c_int(N),
+                                      ctypes.c_int(K), ctypes.c_longlong(K), ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(N),
+                                      ctypes.c_int(self.rank), ctypes.c_int(W), L.ptr(self.flags.tensor), ctypes.c_int(0),
+                                      ctypes.c_uint(self.seq), ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.device)),
+                                      L.stream_ptr()), "ag_gemm")
+        L.check(lib.dewb_signal_flags(self.flags.ptr_array(), ctypes.c_int(2), ctypes.c_int(self.rank), ctypes.c_int(W),
+                                      ctypes.c_uint(self.seq), L.stream_ptr()), "signal_flags")
+        L.count_launches(4)
+        return out
+
+    def matmul_scatter(self, x: torch.Tensor, w: torch.Tensor, residual_shard: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``x [rows, K_local]``, ``w [N, K_local]`` (this rank's slice of the reduction) -> this rank's rows
+        ``[rows / W, N]`` of the summed product (+ ``residual_shard``)."""
+        W = self.world
+        N = w.shape[0]
+        if not self.fused or x.dtype != torch.bfloat16 or N != self.out_features or x.shape[0] != self.rows:
+            y = ops.linear(x, w)
+            if W > 1:
+                full = y.float().contiguous()
+                mine = torch.empty((x.shape[0] // W, N), dtype=torch.float32, device=y.device)
+                dist.reduce_scatter_tensor(mine, full, group=self.group)
+                y = mine.to(x.dtype)
+            return y if residual_shard is None else y + residual_shard
+        lib = L.load()
+        self.seq += 1
+        # every owner must have finished summing the previous call's partials before its slots are overwritten (slot 3)
+        L.check(lib.dewb_wait_flags(L.ptr(self.flags.tensor), ctypes.c_int(3), ctypes.c_int(W), ctypes.c_uint(self.seq - 1),
+                                    ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.device)), L.stream_ptr()), "wait_flags")
+        L.check(lib.dewb_gemm_rs_bf16(L.ptr(x), L.ptr(w), self.partials.ptr_array(), ctypes.c_int(self.rows), ctypes.c_int(N),
+                                      ctypes.c_int(x.shape[1]), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(w.stride(0)),
+                                      ctypes.c_int(self.rank), ctypes.c_int(W), self.flags.ptr_array(), ctypes.c_int(1),
+                                      ctypes.c_uint(self.seq), L.ptr(self.counter), L.ptr(L.status(self.device)), L.stream_ptr()),
+                "gemm_rs")
+        out = torch.empty((self.rows // W, N), dtype=torch.bfloat16, device=self.device)
+        res = residual_shard.contiguous() if residual_shard is not None else None
+        L.check(lib.dewb_reduce_partials(L.ptr(self.partials.tensor), L.ptr(res), L.ptr(out), ctypes.c_longlong(self.rows // W),
+                                         ctypes.c_int(N), ctypes.c_int(W), L.ptr(self.flags.tensor), ctypes.c_int(1),
+                                         ctypes.c_uint(self.seq), ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.device)),
+                                         L.stream_ptr()), "reduce_partials")
+        L.check(lib.dewb_signal_flags(self.flags.ptr_array(), ctypes.c_int(3), ctypes.c_int(self.rank), ctypes.c_int(W),
+                                      ctypes.c_uint(self.seq), L.stream_ptr()), "signal_flags")
+        L.count_launches(4)
+        return out
+
+
 # ------------------------------------------------------------------------------------------------ autograd-aware pair
 class _CopyToRegion(torch.autograd.Function):
     @staticmethod
