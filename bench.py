@@ -101,7 +101,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="dew_b200")
-    ap.add_argument("--micro", type=int, default=None, help="sequences per microbatch (default 1 at N=1, 2 otherwise)")
+    ap.add_argument("--micro", type=int, default=None, help="sequences per microbatch (default 2 at N=1, where memory allows no more, 4 otherwise)")
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="sequences per GPU per step")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the result is then not a valid headline)")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -133,7 +133,7 @@ def main() -> None:
     cfg = dict(MODEL)
     if args.layers:
         cfg["num_layers"] = args.layers
-    micro = args.micro or (1 if world == 1 else 2)
+    micro = args.micro or (2 if world == 1 else 4)
     rows = args.rows
     assert rows % micro == 0
     model = CausalTransformer(device="meta", dtype=torch.bfloat16, **cfg)
@@ -160,7 +160,19 @@ def main() -> None:
 
     # ---- device-timed region (inputs resident)
     for i in range(args.warmup):
-        state, metrics = engine.step(state, device_batches[i])
+        try:
+            state, metrics = engine.step(state, device_batches[i])
+        except torch.cuda.OutOfMemoryError:
+            # one GPU holds all 144 GB of parameter / optimizer state; if the allocator cannot fit two sequences of
+            # activations beside it, fall back to one sequence per microbatch (decided in the untimed warm-up only)
+            if world > 1 or micro == 1:
+                raise
+            micro = 1
+            trainer.microbatches = rows
+            for p in model.parameters():
+                p.grad = None
+            torch.cuda.empty_cache()
+            state, metrics = engine.step(state, device_batches[i])
     sync()
     L.check_status()
     if args.profile:

@@ -58,22 +58,29 @@ __global__ void delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bf
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// dQ kernel
+// dQ kernel: one CTA per 128 query rows of one head; Q and dO stay in shared memory, key blocks of 64 stream through a
+// 4-stage K / V ring.
+//   warps 0..3  softmax group 0 : key blocks 0, 2, 4, ...   one thread per query row (its lse and delta in registers)
+//   warps 4..7  softmax group 1 : key blocks 1, 3, 5, ...
+//               each group owns a pair of TMEM score buffers (S, dP) and a shared-memory dS buffer; dQ is one accumulator
+//   warp 8      TMA producer;  warp 9  MMA issuer (scores two blocks ahead, dQ += dS K as each group delivers dS)
 template <int D>
 struct DqCfg {
-  static constexpr int BM = 128, BN = 128;
+  static constexpr int BM = 128, BN = 64, KSTAGES = 4;
   static constexpr int SUB = D / 64;
-  static constexpr int TILE = 128 * D * 2;          // a [128 x D] bf16 tile
-  static constexpr int DS_BYTES = BM * BN * 2;
-  static constexpr int SMEM = 2 * TILE + 4 * TILE + DS_BYTES + 1024 + 256;
-  static constexpr int TM_S = 0, TM_DP = 128, TM_DQ = 256, TM_COLS = 512;
+  static constexpr int Q_TILE = BM * D * 2;          // [128 x D]
+  static constexpr int KV_TILE = BN * D * 2;         // [64 x D]
+  static constexpr int DS_BYTES = BM * BN * 2;       // [128 x 64]
+  static constexpr int SMEM = 2 * Q_TILE + KSTAGES * 2 * KV_TILE + 2 * DS_BYTES + 1024 + 256;
+  static constexpr int TM_S0 = 0, TM_DP0 = 64, TM_S1 = 128, TM_DP1 = 192, TM_DQ = 256, TM_COLS = 512;
 };
 
 struct DqBars {
   uint64_t q_full;
-  uint64_t k_full[2], v_full[2], kv_empty[2];
-  uint64_t sdp_full, sdp_empty;
-  uint64_t ds_full, dq_done;
+  uint64_t kv_full[4], kv_empty[4];
+  uint64_t sdp_full[2], sdp_empty[2];   // per softmax group
+  uint64_t ds_full[2], dq_done[2];      // per softmax group
+  uint64_t all_done;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -86,7 +93,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
                 int T, int Hq, int Hkv, long long dq_sb, long long dq_ss, long long dq_sh, float scale,
                 int* __restrict__ err) {
   using C = DqCfg<D>;
-  constexpr int BM = C::BM, BN = C::BN;
+  constexpr int BM = C::BM, BN = C::BN, KS = C::KSTAGES;
   extern __shared__ uint8_t smem_raw[];
   {
     // An earlier launch reported a timed-out wait: leave at once instead of queueing more waits behind it. One
@@ -98,25 +105,28 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   }
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sdO = sQ + C::TILE;
-  uint8_t* sK = sdO + C::TILE;          // 2 stages
-  uint8_t* sV = sK + 2 * C::TILE;       // 2 stages
-  uint8_t* sdS = sV + 2 * C::TILE;
-  DqBars* bars = reinterpret_cast<DqBars*>(sdS + C::DS_BYTES);
+  uint8_t* sdO = sQ + C::Q_TILE;
+  uint8_t* sK = sdO + C::Q_TILE;             // KS stages
+  uint8_t* sV = sK + KS * C::KV_TILE;        // KS stages
+  uint8_t* sdS = sV + KS * C::KV_TILE;       // one per group
+  DqBars* bars = reinterpret_cast<DqBars*>(sdS + 2 * C::DS_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = CAUSAL ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (Hq / Hkv);
   const int q0 = qt * BM;
-  const int n_tiles = CAUSAL ? min((q0 + BM + (T - S) + BN - 1) / BN, (T + BN - 1) / BN) : (T + BN - 1) / BN;
+  const int iters = CAUSAL ? min((q0 + BM + (T - S) + BN - 1) / BN, (T + BN - 1) / BN) : (T + BN - 1) / BN;
   const float scale_log2 = scale * LOG2E;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&bars->k_full[i], 1); mbar_init(&bars->v_full[i], 1); mbar_init(&bars->kv_empty[i], 1); }
-    mbar_init(&bars->sdp_full, 1); mbar_init(&bars->sdp_empty, 8);
-    mbar_init(&bars->ds_full, 8); mbar_init(&bars->dq_done, 1);
+    for (int i = 0; i < KS; ++i) { mbar_init(&bars->kv_full[i], 1); mbar_init(&bars->kv_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->sdp_full[i], 1); mbar_init(&bars->sdp_empty[i], 4);
+      mbar_init(&bars->ds_full[i], 4); mbar_init(&bars->dq_done[i], 1);
+    }
+    mbar_init(&bars->all_done, 1);
     bars->abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -130,87 +140,96 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   if (warp == TMA_WARP) {
     if (lane == 0) {
-      mbar_expect_tx(&bars->q_full, 2 * C::TILE);
+      mbar_expect_tx(&bars->q_full, 2 * C::Q_TILE);
 #pragma unroll
       for (int t = 0; t < C::SUB; ++t) {
         tma_load_4d(sQ + t * (BM * 128), &tq, &bars->q_full, t * 64, h, q0, b);
         tma_load_4d(sdO + t * (BM * 128), &tdo, &bars->q_full, t * 64, h, q0, b);
       }
-      for (int j = 0; j < n_tiles; ++j) {
-        const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&bars->kv_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); break; }
-        mbar_expect_tx(&bars->k_full[st], C::TILE);
+      for (int it = 0; it < iters; ++it) {
+        const int ks = it % KS; const uint32_t ph = (it / KS) & 1;
+        if (!mbar_wait(&bars->kv_empty[ks], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); break; }
+        mbar_expect_tx(&bars->kv_full[ks], 2 * C::KV_TILE);
 #pragma unroll
-        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sK + st * C::TILE + t * (BN * 128), &tk, &bars->k_full[st], t * 64, hk, j * BN, b);
-        mbar_expect_tx(&bars->v_full[st], C::TILE);
-#pragma unroll
-        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sV + st * C::TILE + t * (BN * 128), &tv, &bars->v_full[st], t * 64, hk, j * BN, b);
+        for (int t = 0; t < C::SUB; ++t) {
+          tma_load_4d(sK + ks * C::KV_TILE + t * (BN * 128), &tk, &bars->kv_full[ks], t * 64, hk, it * BN, b);
+          tma_load_4d(sV + ks * C::KV_TILE + t * (BN * 128), &tv, &bars->kv_full[ks], t * 64, hk, it * BN, b);
+        }
       }
     }
   } else if (warp == MMA_WARP) {
+    // Key block `it` belongs to group g = it & 1 (its number within the group is it >> 1) and to ring stage it % KS.
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(BM, BN, 1, 1, 0, 0);
       constexpr uint32_t idesc_dq = make_idesc(BM, D, 1, 1, 0, 1);
       bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
       if (!ok) atomicCAS(err, 0, ERR_WAIT_FULL);
-      auto issue_scores = [&](int j) -> bool {
-        const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&bars->k_full[st], ph, abort_flag) || !mbar_wait(&bars->v_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
-        if (!mbar_wait(&bars->sdp_empty, (j & 1) ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
+      auto issue_scores = [&](int it) -> bool {
+        const int g = it & 1; const uint32_t phg = (it >> 1) & 1;
+        const int ks = it % KS; const uint32_t phk = (it / KS) & 1;
+        if (!mbar_wait(&bars->kv_full[ks], phk, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
+        if (!mbar_wait(&bars->sdp_empty[g], phg ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), da = smem_u32(sdO), ka = smem_u32(sK + st * C::TILE), va = smem_u32(sV + st * C::TILE);
+        const uint32_t qa = smem_u32(sQ), da = smem_u32(sdO), ka = smem_u32(sK + ks * C::KV_TILE), va = smem_u32(sV + ks * C::KV_TILE);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tmem + C::TM_S, make_sdesc_sw128(qa + off, 16, 1024), make_sdesc_sw128(ka + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          const uint32_t aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+          const uint32_t boff = (kk >> 2) * (BN * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + (g ? C::TM_S1 : C::TM_S0), make_sdesc_sw128(qa + aoff, 16, 1024),
+                       make_sdesc_sw128(ka + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * (128 * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tmem + C::TM_DP, make_sdesc_sw128(da + off, 16, 1024), make_sdesc_sw128(va + off, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          const uint32_t aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+          const uint32_t boff = (kk >> 2) * (BN * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + (g ? C::TM_DP1 : C::TM_DP0), make_sdesc_sw128(da + aoff, 16, 1024),
+                       make_sdesc_sw128(va + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&bars->sdp_full);
+        umma_commit(&bars->sdp_full[g]);
         return true;
       };
-      if (ok && n_tiles > 0) ok = issue_scores(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) { ok = issue_scores(j + 1); if (!ok) break; }
-        const int st = j & 1;
-        if (!mbar_wait(&bars->ds_full, j & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+      if (ok && iters > 0) ok = issue_scores(0);
+      if (ok && iters > 1) ok = issue_scores(1);
+      for (int it = 0; it < iters && ok; ++it) {
+        const int g = it & 1; const uint32_t phg = (it >> 1) & 1;
+        const int ks = it % KS;
+        if (!mbar_wait(&bars->ds_full[g], phg, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
         tc_fence_after();
-        const uint32_t sa = smem_u32(sdS), ka = smem_u32(sK + st * C::TILE);
+        const uint32_t sa = smem_u32(sdS + g * C::DS_BYTES), ka = smem_u32(sK + ks * C::KV_TILE);
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint32_t aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tmem + C::TM_DQ, make_sdesc_sw128(sa + aoff, 16, 1024),
-                       make_sdesc_sw128(ka + kk * 2048, BN * 128, 1024), idesc_dq, (j > 0 || kk > 0) ? 1u : 0u);
-        }
-        umma_commit(&bars->kv_empty[st]);
-        umma_commit(&bars->dq_done);
+        for (int kk = 0; kk < BN / 16; ++kk)
+          umma_bf16_ss(tmem + C::TM_DQ, make_sdesc_sw128(sa + kk * 32, 16, 1024),
+                       make_sdesc_sw128(ka + kk * 2048, BN * 128, 1024), idesc_dq, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&bars->kv_empty[ks]);
+        umma_commit(&bars->dq_done[g]);
+        if (it + 2 < iters) ok = issue_scores(it + 2);
       }
+      if (ok) umma_commit(&bars->all_done);
     }
   } else {
-    // two threads per query row: warps w and w + 4 read TMEM lane quarter w & 3 and take 64 of the 128 key columns each
-    constexpr int HC = BN / 2;
-    const int q4 = warp & 3, half = warp >> 2;
-    const int r = q4 * 32 + lane;
+    const int q4 = warp & 3, g = warp >> 2;
+    const int r = q4 * 32 + lane;                   // query row within the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
     const int row = q0 + r;
     const long long stat = (static_cast<long long>(b) * Hq + h) * S + row;
     const float lse2 = row < S ? lse[stat] * LOG2E : 0.f;
     const float dl = row < S ? delta[stat] : 0.f;
     const int limit = CAUSAL ? (row + (T - S)) : (T - 1);
+    uint8_t* mydS = sdS + g * C::DS_BYTES;
+    const uint32_t s_col = g ? C::TM_S1 : C::TM_S0, dp_col = g ? C::TM_DP1 : C::TM_DP0;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&bars->sdp_full, j & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
+    int mine = 0;
+    for (int it = g; it < iters && ok; it += 2, ++mine) {
+      const uint32_t phg = mine & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->sdp_full[g], phg, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
       tc_fence_after();
-      const int k0 = j * BN + half * HC;
-      uint32_t packed[HC / 2];
+      const int k0 = it * BN;
+      uint32_t packed[BN / 2];
 #pragma unroll
-      for (int c = 0; c < HC / 32; ++c) {
+      for (int c = 0; c < BN / 32; ++c) {
         uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_S + half * HC + c * 32, sv);
-        tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DP + half * HC + c * 32, dv);
+        tmem_ld_32x32b_x32(tmem + lane_addr + s_col + c * 32, sv);
+        tmem_ld_32x32b_x32(tmem + lane_addr + dp_col + c * 32, dv);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -224,31 +243,32 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->sdp_empty);
-      if (j > 0) {
-        if (!__all_sync(0xffffffffu, mbar_wait(&bars->dq_done, (j - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+      if (lane == 0) mbar_arrive(&bars->sdp_empty[g]);
+      // this group's previous dQ product must have read its dS buffer
+      if (mine > 0) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&bars->dq_done[g], (mine - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
       }
-      // column half `half` is the 64-column (128-byte) sub-tile `half` of dS; c is the 16-byte chunk within the row
+      // each query row of dS is one 128-byte swizzled row of eight 16-byte chunks
 #pragma unroll
-      for (int c = 0; c < HC / 8; ++c) {
-        const uint4 pk = make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
-        *reinterpret_cast<uint4*>(sdS + half * (BM * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = pk;
-      }
+      for (int c = 0; c < BN / 8; ++c)
+        *reinterpret_cast<uint4*>(mydS + r * 128 + ((c ^ (r & 7)) << 4)) =
+            make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->ds_full);
+      if (lane == 0) mbar_arrive(&bars->ds_full[g]);
     }
-    if (ok && n_tiles > 0) {
-      if (!__all_sync(0xffffffffu, mbar_wait(&bars->dq_done, (n_tiles - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
+    if (ok && iters > 0) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->all_done, 0, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
     }
     if (ok) {
       tc_fence_after();
-      __nv_bfloat16* orow = dq + b * dq_sb + static_cast<long long>(row) * dq_ss + h * dq_sh + half * (D / 2);
+      // group g writes gradient columns [g * D/2, (g + 1) * D/2)
+      __nv_bfloat16* orow = dq + b * dq_sb + static_cast<long long>(row) * dq_ss + h * dq_sh + g * (D / 2);
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
         uint32_t v[32];
-        if (n_tiles > 0) { tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DQ + half * (D / 2) + c * 32, v); tmem_ld_wait(); }
+        if (iters > 0) { tmem_ld_32x32b_x32(tmem + lane_addr + C::TM_DQ + g * (D / 2) + c * 32, v); tmem_ld_wait(); }
         else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0;
@@ -334,7 +354,11 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   DkvBars* bars = reinterpret_cast<DkvBars*>(reinterpret_cast<uint8_t*>(sStat) + QS * C::STAT_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  // 1-D grid ordered by key tile first, so that with causal masking the long CTAs (early key tiles see every later
+  // query block) of ALL heads start first and the short ones fill the tail: blocks are issued in index order.
+  const int per_tile = static_cast<int>(gridDim.x) / ((T + BKV - 1) / BKV);      // = Hkv * batch
+  const int kt = blockIdx.x / per_tile;
+  const int hk = (blockIdx.x % per_tile) % Hkv, b = (blockIdx.x % per_tile) / Hkv;
   const int rep = Hq / Hkv;
   const int kv0 = kt * BKV;
   // first query block that can see any key of this tile (causal, bottom-right aligned): q + (T - S) >= kv0
@@ -573,8 +597,8 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
     CUtensorMap tq, tdo, tk, tv;
     if ((r = make_map(&tq, q, B, S, Hq, D, qs[0], qs[1], qs[2], 128))) return 1000 + r;
     if ((r = make_map(&tdo, dO, B, S, Hq, D, do_sb, do_ss, do_sh, 128))) return 1100 + r;
-    if ((r = make_map(&tk, k, B, T, Hkv, D, ks[0], ks[1], ks[2], 128))) return 1200 + r;
-    if ((r = make_map(&tv, v, B, T, Hkv, D, vs[0], vs[1], vs[2], 128))) return 1300 + r;
+    if ((r = make_map(&tk, k, B, T, Hkv, D, ks[0], ks[1], ks[2], 64))) return 1200 + r;
+    if ((r = make_map(&tv, v, B, T, Hkv, D, vs[0], vs[1], vs[2], 64))) return 1300 + r;
     auto kern = flash_dq_kernel<D, CAUSAL>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<D>::SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -592,7 +616,7 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
     auto kern = flash_dkv_kernel<D, CAUSAL>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<D>::SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
-    dim3 grid((T + 127) / 128, Hkv, B);
+    dim3 grid(((T + 127) / 128) * Hkv * B, 1, 1);
     kern<<<grid, THREADS, DkvCfg<D>::SMEM, stream>>>(tq, tdo, tk, tv, lse2, delta, reinterpret_cast<__nv_bfloat16*>(dk),
                                                       reinterpret_cast<__nv_bfloat16*>(dv), S, T, Hq, Hkv, dks[0], dks[1],
                                                       dks[2], dvs[0], dvs[1], dvs[2], scale, err);

@@ -36,20 +36,25 @@ struct Cfg {
   static constexpr int Q_BYTES = BM * D * 2;
   static constexpr int KV_BYTES = BN * D * 2;
   static constexpr int P_BYTES = BM * BN * 2;
-  static constexpr int SMEM = Q_BYTES + 4 * KV_BYTES + P_BYTES + 1024 + 256 + 6 * BM * 4;
+  static constexpr int KSTAGES = 3;                  // K is consumed one tile ahead of V: it needs the deeper ring
+  static constexpr int TILE_BYTES = Q_BYTES + (KSTAGES + 2) * KV_BYTES + P_BYTES;
+  static constexpr int SMEM = TILE_BYTES + 2560;      // + barriers and the row-maximum exchange (see Bars); no slack to spare
   static constexpr int TMEM_S0 = 0, TMEM_S1 = 128, TMEM_O = 256, TMEM_COLS = 512;
 };
 
 struct Bars {
   uint64_t q_full;
-  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t k_full[3], k_empty[3], v_full[2], v_empty[2];
   uint64_t s_full[2], s_empty[2];
   uint64_t p_full, pv_done;
   uint32_t tmem_base;
   int abort_flag;
-  float xmax[2][2][BM];   // [tile parity][column half][row]: partial row maxima exchanged between the two halves
-  float xsum[2][BM];      // [column half][row]: partial row sums, combined once at the end
+  int poisoned;
+  float xmax[2][2][BM];   // [tile parity][column half][row]: partial row maxima exchanged between the two halves; the
+                          // parity the last tile did not use carries the partial row sums at the end
 };
+
+static_assert(sizeof(Bars) <= 2560, "Bars must fit the space Cfg::SMEM leaves after the tiles");
 
 template <int D, bool CAUSAL>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -58,21 +63,26 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
                  int S, int T, int Hq, int Hkv, long long o_stride_b, long long o_stride_s, long long o_stride_h,
                  float scale_log2, int* __restrict__ err) {
   using C = Cfg<D>;
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // The tiles fill 224 KiB, so this kernel has no static shared memory and no alignment slack: the dynamic window must
+  // start on a 1024-byte boundary (the 128-byte swizzle atoms need it). If it ever did not, refuse instead of overrunning.
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(err, 0, ERR_BAD_ARG);
+    return;
+  }
+  uint8_t* smem = smem_raw;
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + C::Q_BYTES;             // KSTAGES stages
+  uint8_t* sV = sK + C::KSTAGES * C::KV_BYTES;   // 2 stages
+  uint8_t* sP = sV + 2 * C::KV_BYTES;
+  Bars* bars = reinterpret_cast<Bars*>(sP + C::P_BYTES);
   {
     // An earlier launch reported a timed-out wait: leave at once instead of queueing more waits behind it. One
     // thread reads the status so the whole CTA takes the same branch.
-    __shared__ int poisoned;
-    if (threadIdx.x == 0) poisoned = *reinterpret_cast<volatile int*>(err);
+    if (threadIdx.x == 0) bars->poisoned = *reinterpret_cast<volatile int*>(err);
     __syncthreads();
-    if (poisoned != 0) return;
+    if (bars->poisoned != 0) return;
   }
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + C::Q_BYTES;             // 2 stages
-  uint8_t* sV = sK + 2 * C::KV_BYTES;        // 2 stages
-  uint8_t* sP = sV + 2 * C::KV_BYTES;
-  Bars* bars = reinterpret_cast<Bars*>(sP + C::P_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = CAUSAL ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;   // heavy causal tiles first
@@ -84,8 +94,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
+    for (int i = 0; i < C::KSTAGES; ++i) { mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1);
       mbar_init(&bars->v_full[i], 1); mbar_init(&bars->v_empty[i], 1);
       mbar_init(&bars->s_full[i], 1); mbar_init(&bars->s_empty[i], 8);
     }
@@ -112,10 +122,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&bars->k_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); ok = false; break; }
-        mbar_expect_tx(&bars->k_full[st], C::KV_BYTES);
+        const int ks = j % C::KSTAGES; const uint32_t kph = (j / C::KSTAGES) & 1;
+        if (!mbar_wait(&bars->k_empty[ks], kph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); ok = false; break; }
+        mbar_expect_tx(&bars->k_full[ks], C::KV_BYTES);
 #pragma unroll
-        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sK + st * C::KV_BYTES + t * (BN * 128), &tk, &bars->k_full[st], t * 64, hk, j * BN, b);
+        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sK + ks * C::KV_BYTES + t * (BN * 128), &tk, &bars->k_full[ks], t * 64, hk, j * BN, b);
         if (!mbar_wait(&bars->v_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); ok = false; break; }
         mbar_expect_tx(&bars->v_full[st], C::KV_BYTES);
 #pragma unroll
@@ -131,17 +142,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       if (!ok) atomicCAS(err, 0, ERR_WAIT_FULL);
       auto issue_qk = [&](int j) -> bool {
         const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&bars->k_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
+        const int ks = j % C::KSTAGES; const uint32_t kph = (j / C::KSTAGES) & 1;
+        if (!mbar_wait(&bars->k_full[ks], kph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
         if (!mbar_wait(&bars->s_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * C::KV_BYTES);
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + ks * C::KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
           umma_bf16_ss(tmem + (st ? C::TMEM_S1 : C::TMEM_S0), make_sdesc_sw128(qa + off, 16, 1024),
                        make_sdesc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&bars->k_empty[st]);
+        umma_commit(&bars->k_empty[ks]);
         umma_commit(&bars->s_full[st]);
         return true;
       };
@@ -267,9 +279,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       if (!__all_sync(0xffffffffu, got)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; }
     }
     // the row sum over all columns (both threads of a row reach this barrier: neither branch above skips it)
-    bars->xsum[half][r] = l;
+    bars->xmax[n_tiles & 1][half][r] = l;      // the parity buffer the last tile left alone
     named_barrier_sync(1 + q4, 64);
-    l += bars->xsum[half ^ 1][r];
+    l += bars->xmax[n_tiles & 1][half ^ 1][r];
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;

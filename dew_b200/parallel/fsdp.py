@@ -73,6 +73,18 @@ class Unit:
     size: int = 0              # padded size (multiple of world * ALIGN)
     decay_end: int = 0         # elements [0, decay_end) take weight decay
     offsets: Dict[str, int] = field(default_factory=dict)
+    world: int = 1             # ranks the unit is sharded over: the engine's group, or 1 for rank-local (expert-parallel) units
+    rank: int = 0
+    shard_offset: int = 0      # element offset of this rank's shard inside master / moments / EMA
+    group: int = 0             # index of the module group (one backward boundary) the unit belongs to
+
+    @property
+    def shard_size(self) -> int:
+        return self.size // self.world
+
+    @property
+    def local(self) -> bool:
+        return self.world == 1
 
 
 class _Boundary(torch.autograd.Function):
@@ -126,7 +138,9 @@ class FSDPEngine:
         W = self.world
         seen = set()
         total = 0
-        for uname, mods in self.unit_modules:
+        shard_total = 0
+        self.groups: List[List[int]] = []
+        for gi, (uname, mods) in enumerate(self.unit_modules):
             named: List[Tuple[str, nn.Parameter]] = []
             for m in mods:
                 prefix = next((n for n, mm in self.model.named_modules() if mm is m), "")
@@ -135,22 +149,34 @@ class FSDPEngine:
                         continue
                     seen.add(id(p))
                     named.append(((prefix + "." + n) if prefix else n, p))
-            decay = [(n, p) for n, p in named if not self._is_spared(n, p)]
-            spared = [(n, p) for n, p in named if self._is_spared(n, p)]
-            u = Unit(uname, decay + spared)
-            off = 0
-            for i, (n, p) in enumerate(u.params):
-                if i == len(decay):
+            # parameters that are already one rank's slice of an expert-parallel layer form a rank-local unit: their
+            # gradients are complete on this rank (every token routed here contributed), so nothing is reduced or gathered
+            shared = [(n, p) for n, p in named if not getattr(p, "expert_parallel", False)]
+            local = [(n, p) for n, p in named if getattr(p, "expert_parallel", False)]
+            members = []
+            for suffix, plist, uw, ur in (("", shared, W, self.rank), (".local", local, 1, 0)):
+                if not plist:
+                    continue
+                decay = [(n, p) for n, p in plist if not self._is_spared(n, p)]
+                spared = [(n, p) for n, p in plist if self._is_spared(n, p)]
+                u = Unit(uname + suffix, decay + spared, world=uw, rank=ur, group=gi)
+                off = 0
+                for i, (n, p) in enumerate(u.params):
+                    if i == len(decay):
+                        u.decay_end = off
+                    u.offsets[n] = off
+                    off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+                if not spared:
                     u.decay_end = off
-                u.offsets[n] = off
-                off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
-            if not spared:
-                u.decay_end = off
-            quantum = W * ALIGN
-            u.size = (off + quantum - 1) // quantum * quantum
-            u.offset = total
-            total += u.size
-            self.units.append(u)
+                quantum = uw * ALIGN
+                u.size = (off + quantum - 1) // quantum * quantum
+                u.offset = total
+                u.shard_offset = shard_total
+                total += u.size
+                shard_total += u.shard_size
+                members.append(len(self.units))
+                self.units.append(u)
+            self.groups.append(members)
         self.total = total
         dev = self.device
         cdtype = self.t.param_dtype or (torch.bfloat16 if self.cuda else torch.float32)
@@ -159,7 +185,7 @@ class FSDPEngine:
         self.params_arena = SymmetricBuffer(total, cdtype, dev, self.group, zero=True)
         self.grads_arena = SymmetricBuffer(total, torch.float32, dev, self.group, zero=True)
         self.flags = SymmetricBuffer(max(64, len(self.units) * 2 * max(W, 1)), torch.int32, dev, self.group, zero=True)
-        shard_total = total // W
+        self.shard_total = shard_total
         self.master = torch.empty(shard_total, dtype=torch.float32, device=dev)
         self.m = torch.zeros(shard_total, dtype=torch.float32, device=dev)
         self.v = torch.zeros(shard_total, dtype=torch.float32, device=dev)
@@ -207,9 +233,9 @@ class FSDPEngine:
         pa = self.params_arena.tensor
         with torch.no_grad():
             for u in self.units:
-                s = u.size // W
-                src = pa[u.offset + self.rank * s: u.offset + (self.rank + 1) * s]
-                self.master[u.offset // W: u.offset // W + s].copy_(src)
+                s = u.shard_size
+                src = pa[u.offset + u.rank * s: u.offset + (u.rank + 1) * s]
+                self.master[u.shard_offset: u.shard_offset + s].copy_(src)
         if self.t.objective.ema_spec() is not None:
             self.ema = self.master.clone()
     def _install_hooks(self) -> None:
@@ -242,7 +268,9 @@ class FSDPEngine:
         if not self.built:
             seed = int(K.fold_in(key, "init")) & 0x7FFFFFFF                   # same seed on every rank
             meta = any(p.is_meta for p in self.model.parameters())
-            if not meta:
+            # a model whose experts were already split over the ranks was initialised (same seed) before the split
+            presharded = any(getattr(p, "expert_parallel", False) for p in self.model.parameters())
+            if not meta and not presharded:
                 reset_all(self.model, seed)
             self.build()
             if meta:
@@ -257,8 +285,7 @@ class FSDPEngine:
 
     def _shard_tree(self, flat: torch.Tensor) -> Dict[str, Any]:
         """Expose a sharded flat buffer as a tree: one leaf per unit (``<unit>/shard``) holding this rank's shard."""
-        W = self.world
-        return unflatten({f"{u.name}/shard": flat[u.offset // W: (u.offset + u.size) // W] for u in self.units})
+        return unflatten({f"{u.name}/shard": flat[u.shard_offset: u.shard_offset + u.shard_size] for u in self.units})
 
     def adopt(self, state: TrainState) -> TrainState:
         if not self.built:
@@ -267,22 +294,40 @@ class FSDPEngine:
             self._install_hooks()
         return state
 
+    def _whole_unit(self, u: Unit, flat: torch.Tensor) -> Dict[str, torch.Tensor]:
+        """The unit's tensors in full, by parameter tree path (collective over the engine's group).  A sharded unit is
+        all-gathered; a rank-local (expert-parallel) unit holds a different slice of the experts on every rank, so the
+        ranks' copies are concatenated along the expert dimension."""
+        W = self.world
+        mine = flat[u.shard_offset: u.shard_offset + u.shard_size]
+        out: Dict[str, torch.Tensor] = {}
+        if W == 1:
+            for n, p in u.params:
+                o = u.offsets[n]
+                out[module_path_to_tree_path(n)] = mine[o:o + p.numel()].view(p.shape)
+            return out
+        if u.local:
+            every = torch.empty(W * u.size, dtype=flat.dtype, device=flat.device)
+            dist.all_gather_into_tensor(every, mine.contiguous(), group=self.group)
+            every = every.view(W, u.size)
+            for n, p in u.params:
+                o = u.offsets[n]
+                out[module_path_to_tree_path(n)] = every[:, o:o + p.numel()].reshape((W * p.shape[0],) + tuple(p.shape[1:]))
+            return out
+        full = torch.empty(u.size, dtype=flat.dtype, device=flat.device)
+        dist.all_gather_into_tensor(full, mine.contiguous(), group=self.group)
+        for n, p in u.params:
+            o = u.offsets[n]
+            out[module_path_to_tree_path(n)] = full[o:o + p.numel()].view(p.shape)
+        return out
+
     def gather_full(self, what: str = "master") -> Dict[str, torch.Tensor]:
         """Full (unsharded) fp32 tensors by parameter tree path - for checkpoints and evaluation on rank 0."""
         flat = {"master": self.master, "mu": self.m, "nu": self.v, "ema": self.ema}[what]
-        W = self.world
         out: Dict[str, torch.Tensor] = {}
         for u in self.units:
-            s = u.size // W
-            mine = flat[u.offset // W: u.offset // W + s]
-            if W > 1:
-                full = torch.empty(u.size, dtype=flat.dtype, device=flat.device)
-                dist.all_gather_into_tensor(full, mine.contiguous(), group=self.group)
-            else:
-                full = mine
-            for n, p in u.params:
-                o = u.offsets[n]
-                out[module_path_to_tree_path(n)] = full[o:o + p.numel()].view(p.shape).clone()
+            for k, v in self._whole_unit(u, flat).items():
+                out[k] = v.clone()
         return out
 
     # ------------------------------------------------------------------ checkpoints (layout-free full trees)
@@ -295,20 +340,11 @@ class FSDPEngine:
         def whole(flat):
             if flat is None:
                 return None
-            W = self.world
             out: Dict[str, torch.Tensor] = {}
             for u in self.units:
-                s = u.size // W
-                mine = flat[u.offset // W: u.offset // W + s]
-                if W > 1:
-                    full = torch.empty(u.size, dtype=flat.dtype, device=flat.device)
-                    dist.all_gather_into_tensor(full, mine.contiguous(), group=self.group)
-                else:
-                    full = mine
-                if keep:
-                    for n, p in u.params:
-                        o = u.offsets[n]
-                        out[module_path_to_tree_path(n)] = full[o:o + p.numel()].view(p.shape).to(to, copy=True)
+                for k, v in self._whole_unit(u, flat).items():
+                    if keep:
+                        out[k] = v.to(to, copy=True)
             return unflatten(out)
 
         trees = {k: whole(v) for k, v in (("params", self.master), ("mu", self.m), ("nu", self.v), ("ema", self.ema))}
@@ -333,13 +369,16 @@ class FSDPEngine:
             leaves = flatten(tree)
             with torch.no_grad():
                 for u in self.units:
-                    s = u.size // W
-                    lo, hi = r * s, (r + 1) * s                                  # this rank's range inside the unit
-                    base = u.offset // W
+                    s = u.shard_size
+                    lo, hi = u.rank * s, (u.rank + 1) * s                         # this rank's range inside the unit
+                    base = u.shard_offset
                     for n, p in u.params:
                         src = leaves.get(module_path_to_tree_path(n))
                         if src is None:
                             raise KeyError(f"checkpoint lacks {module_path_to_tree_path(n)}")
+                        if u.local and W > 1:
+                            # the checkpoint holds every rank's experts along the leading dimension: keep this rank's
+                            src = src[r * p.shape[0]:(r + 1) * p.shape[0]]
                         o = u.offsets[n]
                         a, b = max(o, lo), min(o + p.numel(), hi)
                         if a < b:
@@ -365,9 +404,8 @@ class FSDPEngine:
         pa = self.params_arena.tensor
         with torch.no_grad():
             for u in self.units:
-                s = u.size // W
-                mine = self.master[u.offset // W: u.offset // W + s].to(pa.dtype)
-                if W > 1:
+                mine = self.master[u.shard_offset: u.shard_offset + u.shard_size].to(pa.dtype)
+                if W > 1 and not u.local:
                     dist.all_gather_into_tensor(pa[u.offset: u.offset + u.size], mine, group=self.group)
                 else:
                     pa[u.offset: u.offset + u.size].copy_(mine)
@@ -377,25 +415,26 @@ class FSDPEngine:
             dist.barrier(group=self.group)
 
     # ------------------------------------------------------------------ per-unit protocol
-    def _before_unit_forward(self, index: int) -> None:
-        """First forward of a unit in a step: wait until every peer's push of its new weights has landed and the
-        peers have stopped reading its gradient buffer, then clear that buffer."""
-        if not self._first_micro or index in self._cleared:
+    def _before_unit_forward(self, group: int) -> None:
+        """First forward of a module group in a step: wait until every peer's push of its new weights has landed and
+        the peers have stopped reading its gradient buffer, then clear that buffer."""
+        if not self._first_micro or group in self._cleared:
             return
-        self._cleared.add(index)
-        u = self.units[index]
-        if self.cuda and self.world > 1 and self.seq > 0:
-            L.check(L.load().dewb_wait_flags(L.ptr(self.flags.tensor), ctypes.c_int(index * 2 + SLOT_DONE),
-                                             ctypes.c_int(self.world), ctypes.c_uint(self.seq),
-                                             ctypes.c_ulonglong(self.wait_limit_ns), L.ptr(L.status(self.device)),
-                                             L.stream_ptr()), "wait_flags")
-            L.count_launches()
-        self.grads_arena.tensor[u.offset:u.offset + u.size].zero_()
+        self._cleared.add(group)
+        for index in self.groups[group]:
+            u = self.units[index]
+            if self.cuda and self.world > 1 and self.seq > 0 and not u.local:
+                L.check(L.load().dewb_wait_flags(L.ptr(self.flags.tensor), ctypes.c_int(index * 2 + SLOT_DONE),
+                                                 ctypes.c_int(self.world), ctypes.c_uint(self.seq),
+                                                 ctypes.c_ulonglong(self.wait_limit_ns), L.ptr(L.status(self.device)),
+                                                 L.stream_ptr()), "wait_flags")
+                L.count_launches()
+            self.grads_arena.tensor[u.offset:u.offset + u.size].zero_()
 
-    def _unit_backward_done(self, index: int) -> None:
-        if not self._last_micro or index in self._launched:
+    def _unit_backward_done(self, group: int) -> None:
+        if not self._last_micro or group in self._launched:
             return
-        self._finalize_unit(index)
+        self._finalize_unit(group)
 
     def _fold_autograd_grads(self, u: Unit) -> None:
         """Gradients that arrived through autograd's ``.grad`` (norm scales, embeddings) join the fp32 accumulators."""
@@ -404,14 +443,11 @@ class FSDPEngine:
                 p.main_grad.add_(p.grad.to(torch.float32))
                 p.grad = None
 
-    def _finalize_unit(self, index: int) -> None:
-        self._launched.add(index)
-        u = self.units[index]
-        self._fold_autograd_grads(u)
-        if self._two_phase:
-            self._launch(index, mode=1)
-        else:
-            self._launch(index, mode=0)
+    def _finalize_unit(self, group: int) -> None:
+        self._launched.add(group)
+        for index in self.groups[group]:
+            self._fold_autograd_grads(self.units[index])
+            self._launch(index, mode=1 if self._two_phase else 0)
 
     def _hyper(self, u: Unit):
         cfg = self.t.optimizer.config
@@ -428,9 +464,9 @@ class FSDPEngine:
 
     def _launch(self, index: int, mode: int) -> None:
         u = self.units[index]
-        W, r = self.world, self.rank
-        s = u.size // W
-        lo = u.offset // W
+        W, r = u.world, u.rank
+        s = u.shard_size
+        lo = u.shard_offset
         if not self.cuda:
             return self._launch_reference(u, mode)
         lib = L.load()
@@ -438,9 +474,11 @@ class FSDPEngine:
         self.comm_stream.wait_stream(cur)
         with torch.cuda.stream(self.comm_stream):
             esz = self.params_arena.tensor.element_size()
+            own = u.local and self.world > 1          # a rank-local unit sees only this rank's buffers
             rc = lib.dewb_rs_adamw_ag(
-                self.grads_arena.ptr_array(u.offset * 4), self.params_arena.ptr_array(u.offset * esz),
-                self.flags.ptr_array(), L.ptr(self.master[lo:lo + s]), L.ptr(self.m[lo:lo + s]), L.ptr(self.v[lo:lo + s]),
+                self.grads_arena.own_ptr_array(u.offset * 4) if own else self.grads_arena.ptr_array(u.offset * 4),
+                self.params_arena.own_ptr_array(u.offset * esz) if own else self.params_arena.ptr_array(u.offset * esz),
+                self.flags.own_ptr_array() if own else self.flags.ptr_array(), L.ptr(self.master[lo:lo + s]), L.ptr(self.m[lo:lo + s]), L.ptr(self.v[lo:lo + s]),
                 L.ptr(self.ema[lo:lo + s] if self.ema is not None else None),
                 L.ptr(self.reduced[lo:lo + s] if self.reduced is not None else None),
                 L.ptr(self.sumsq[index] if self._two_phase else None),
@@ -456,9 +494,9 @@ class FSDPEngine:
 
     def _launch_reference(self, u: Unit, mode: int) -> None:
         """CPU path (gloo ranks): the same arithmetic with torch collectives - the oracle for the fused kernel."""
-        W, r = self.world, self.rank
-        s = u.size // W
-        lo = u.offset // W
+        W, r = u.world, u.rank
+        s = u.shard_size
+        lo = u.shard_offset
         g_full = self.grads_arena.tensor[u.offset:u.offset + u.size]
         if W > 1:
             g = torch.empty(s, dtype=torch.float32)
@@ -505,7 +543,7 @@ class FSDPEngine:
         self._updates = state.updates
         self._two_phase = cfg.clip_grads is not None or cfg.skip_nonfinite
         if self._two_phase and self.reduced is None:
-            self.reduced = torch.zeros(self.total // self.world, dtype=torch.float32, device=self.device)
+            self.reduced = torch.zeros(self.shard_total, dtype=torch.float32, device=self.device)
             self.sumsq = torch.zeros(len(self.units), max(self.comm_blocks, 1), dtype=torch.float32, device=self.device)
         self._cleared, self._launched = set(), set()
         stats_all, metrics_all, effects = [], {}, {}
@@ -541,9 +579,9 @@ class FSDPEngine:
             effects.update(aux.effects)
             first += rows_per
         # units whose input carries no gradient (the embedding) are finalised here, in reverse order
-        for index in reversed(range(len(self.units))):
-            if index not in self._launched:
-                self._finalize_unit(index)
+        for group in reversed(range(len(self.groups))):
+            if group not in self._launched:
+                self._finalize_unit(group)
         info: Dict[str, Any] = {"learning_rate": self._lr}
         if self._two_phase:
             self._second_phase(info)

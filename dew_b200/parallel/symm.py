@@ -49,6 +49,11 @@ class SymmetricBuffer:
         import ctypes
         return (ctypes.c_ulonglong * 8)(*([p + offset_bytes for p in self.ptrs] + [0] * (8 - len(self.ptrs))))
 
+    def own_ptr_array(self, offset_bytes: int = 0):
+        """ctypes array holding only this rank's base address (for kernels run with a world of one)."""
+        import ctypes
+        return (ctypes.c_ulonglong * 8)(*([self.tensor.data_ptr() + offset_bytes] + [0] * 7))
+
     def peer(self, rank: int, numel: Optional[int] = None, offset: int = 0) -> torch.Tensor:
         """A tensor view of ``rank``'s buffer (for host-side checks; kernels take ``ptr_array``)."""
         if self.handle is None:

@@ -114,10 +114,23 @@ class SequenceParallelLinear:
         self.fused = self.device.type == "cuda" and self.world > 1 and rows % (128 * self.world) == 0
         if self.fused:
             W = self.world
-            self.x_shard = SymmetricBuffer((rows // W) * in_features, torch.bfloat16, self.device, group, zero=True)
-            self.partials = SymmetricBuffer(W * (rows // W) * out_features, torch.bfloat16, self.device, group, zero=True)
+            Ms = rows // W
+            # peers read the shard and write the partial slots: both are double-buffered by call parity
+            self.x_shard = SymmetricBuffer(2 * Ms * in_features, torch.bfloat16, self.device, group, zero=True)
+            self.partials = SymmetricBuffer(2 * W * Ms * out_features, torch.bfloat16, self.device, group, zero=True)
             self.flags = SymmetricBuffer(64, torch.int32, self.device, group, zero=True)
+            self.staging = torch.empty((rows, in_features), dtype=torch.bfloat16, device=self.device)
+            self.block_ready = torch.zeros(rows // 128, dtype=torch.int32, device=self.device)
             self.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.ag_calls = 0
+            self.rs_calls = 0
+
+    def shard_buffer(self) -> torch.Tensor:
+        """The peer-visible buffer the NEXT ``gather_matmul`` reads this rank's rows from: a producer that writes its
+        output here (and passes this very tensor) saves the copy."""
+        Ms = self.rows // self.world
+        n = Ms * self.in_features
+        return self.x_shard.tensor[(self.ag_calls & 1) * n:((self.ag_calls & 1) + 1) * n].view(Ms, self.in_features)
 
     def gather_matmul(self, x_shard: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
         """``x_shard [rows / W, K]`` (this rank's rows), ``w [N, K]`` -> ``[rows, N]``."""
@@ -129,24 +142,20 @@ class SequenceParallelLinear:
             dist.all_gather(parts, x_shard.contiguous(), group=self.group)
             return ops.linear(torch.cat(parts, 0), w)
         lib = L.load()
-        self.seq += 1
         K, N = self.in_features, w.shape[0]
-        # every peer must have finished reading the previous call's shard before it is overwritten (flag slot 2)
-        L.check(lib.dewb_wait_flags(L.ptr(self.flags.tensor), ctypes.c_int(2), ctypes.c_int(W), ctypes.c_uint(self.seq - 1),
-                                    ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.device)), L.stream_ptr()), "wait_flags")
-        # the shard goes into peer-visible memory (a producer that writes there directly skips this copy), then the flag
-        self.x_shard.tensor.view(self.rows // W, K).copy_(x_shard)
-        L.check(lib.dewb_signal_flags(self.flags.ptr_array(), ctypes.c_int(0), ctypes.c_int(self.rank), ctypes.c_int(W),
-                                      ctypes.c_uint(self.seq), L.stream_ptr()), "signal_flags")
+        buf = self.shard_buffer()
+        if x_shard.data_ptr() != buf.data_ptr():
+            buf.copy_(x_shard)
+        parity = self.ag_calls & 1
+        self.ag_calls += 1
         out = torch.empty((self.rows, N), dtype=torch.bfloat16, device=self.device)
-        L.check(lib.dewb_ag_gemm_bf16(self.x_shard.ptr_array(), L.ptr(w), L.ptr(out), ctypes.c_int(self.rows), ctypes.c_int(N),
+        L.check(lib.dewb_ag_gemm_bf16(self.x_shard.ptr_array(parity * (self.rows // W) * K * 2), L.ptr(w), L.ptr(out), L.ptr(self.staging),
+                                      L.ptr(self.block_ready), ctypes.c_uint(self.ag_calls), ctypes.c_int(self.rows), ctypes.c_int(N),
                                       ctypes.c_int(K), ctypes.c_longlong(K), ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(N),
-                                      ctypes.c_int(self.rank), ctypes.c_int(W), L.ptr(self.flags.tensor), ctypes.c_int(0),
-                                      ctypes.c_uint(self.seq), ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.device)),
-                                      L.stream_ptr()), "ag_gemm")
-        L.check(lib.dewb_signal_flags(self.flags.ptr_array(), ctypes.c_int(2), ctypes.c_int(self.rank), ctypes.c_int(W),
-                                      ctypes.c_uint(self.seq), L.stream_ptr()), "signal_flags")
-        L.count_launches(4)
+                                      ctypes.c_int(self.rank), ctypes.c_int(W), self.flags.ptr_array(), L.ptr(self.flags.tensor),
+                                      ctypes.c_int(0), ctypes.c_uint(self.ag_calls), ctypes.c_ulonglong(self.limit_ns),
+                                      L.ptr(L.status(self.device)), L.stream_ptr()), "ag_gemm")
+        L.count_launches()
         return out
 
     def matmul_scatter(self, x: torch.Tensor, w: torch.Tensor, residual_shard: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -163,24 +172,23 @@ class SequenceParallelLinear:
                 y = mine.to(x.dtype)
             return y if residual_shard is None else y + residual_shard
         lib = L.load()
-        self.seq += 1
-        # every owner must have finished summing the previous call's partials before its slots are overwritten (slot 3)
-        L.check(lib.dewb_wait_flags(L.ptr(self.flags.tensor), ctypes.c_int(3), ctypes.c_int(W), ctypes.c_uint(self.seq - 1),
-                                    ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.device)), L.stream_ptr()), "wait_flags")
-        L.check(lib.dewb_gemm_rs_bf16(L.ptr(x), L.ptr(w), self.partials.ptr_array(), ctypes.c_int(self.rows), ctypes.c_int(N),
+        parity = self.rs_calls & 1
+        self.rs_calls += 1
+        Ms = self.rows // W
+        off = parity * W * Ms * N * 2
+        L.check(lib.dewb_gemm_rs_bf16(L.ptr(x), L.ptr(w), self.partials.ptr_array(off), ctypes.c_int(self.rows), ctypes.c_int(N),
                                       ctypes.c_int(x.shape[1]), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(w.stride(0)),
                                       ctypes.c_int(self.rank), ctypes.c_int(W), self.flags.ptr_array(), ctypes.c_int(1),
-                                      ctypes.c_uint(self.seq), L.ptr(self.counter), L.ptr(L.status(self.device)), L.stream_ptr()),
+                                      ctypes.c_uint(self.rs_calls), L.ptr(self.counter), L.ptr(L.status(self.device)), L.stream_ptr()),
                 "gemm_rs")
-        out = torch.empty((self.rows // W, N), dtype=torch.bfloat16, device=self.device)
+        out = torch.empty((Ms, N), dtype=torch.bfloat16, device=self.device)
         res = residual_shard.contiguous() if residual_shard is not None else None
-        L.check(lib.dewb_reduce_partials(L.ptr(self.partials.tensor), L.ptr(res), L.ptr(out), ctypes.c_longlong(self.rows // W),
+        mine = self.partials.tensor[parity * W * Ms * N:(parity + 1) * W * Ms * N]
+        L.check(lib.dewb_reduce_partials(L.ptr(mine), L.ptr(res), L.ptr(out), ctypes.c_longlong(Ms),
                                          ctypes.c_int(N), ctypes.c_int(W), L.ptr(self.flags.tensor), ctypes.c_int(1),
-                                         ctypes.c_uint(self.seq), ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.device)),
+                                         ctypes.c_uint(self.rs_calls), ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.device)),
                                          L.stream_ptr()), "reduce_partials")
-        L.check(lib.dewb_signal_flags(self.flags.ptr_array(), ctypes.c_int(3), ctypes.c_int(self.rank), ctypes.c_int(W),
-                                      ctypes.c_uint(self.seq), L.stream_ptr()), "signal_flags")
-        L.count_launches(4)
+        L.count_launches(2)
         return out
 
 
