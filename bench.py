@@ -32,6 +32,28 @@ MODEL = dict(vocab_size=128256, emb_features=4096, num_layers=32, num_heads=32, 
 SEQ_LEN = 4096
 ROWS_PER_GPU = 32
 
+# The other training configurations (selected with --config; the headline above is the default and the only one the
+# one-line contract of this script describes):
+#   moe     d_model 2048, 24 layers, 16 heads, 64 routed experts (FFN 1408, SwiGLU) top-6 softmax + 2 shared experts,
+#           row-scaled fp8 expert GEMMs, expert parallelism over all N ranks, sequence 4096, 16 sequences per GPU
+#   hybrid  d_model 2048, 24 layers in a 3 x gated-delta-net (16 heads x 128, short conv 4) + 1 x attention pattern,
+#           sequence 8192, 8 sequences per GPU, FSDP
+CONFIGS = {
+    "dense": dict(model=MODEL, seq=4096, rows=32, metric="train tokens/sec (dense 8B LM, FSDP)",
+                  name="llama-style 8B: d4096 L32 H32/8kv ffn14336 vocab128256"),
+    "moe": dict(model=dict(vocab_size=32768, emb_features=2048, num_layers=24, num_heads=16, num_kv_heads=16, head_dim=128,
+                           mlp_features=1408, max_seq_len=4096, qk_norm=False, tie_embeddings=False, norm_eps=1e-5),
+                mixture=dict(experts=64, top_k=6, expert_features=1408, shared_features=2 * 1408, fp8=True),
+                seq=4096, rows=16, metric="train tokens/sec (MoE LM, expert parallel)",
+                name="MoE: d2048 L24 H16 64 experts x 1408 top-6 + 2 shared, fp8 expert GEMMs, vocab 32768"),
+    "hybrid": dict(model=dict(vocab_size=32768, emb_features=2048, num_layers=24, num_heads=16, num_kv_heads=16, head_dim=128,
+                              mlp_features=5632, max_seq_len=8192, qk_norm=False, tie_embeddings=False, norm_eps=1e-5,
+                              layer_types=("gdn", "gdn", "gdn", "attention"),
+                              mixer_options=dict(num_k_heads=16, num_v_heads=16, head_k_dim=128, head_v_dim=128, conv_size=4)),
+                   seq=8192, rows=8, metric="train tokens/sec (hybrid GDN LM, FSDP)",
+                   name="hybrid: d2048 L24 (3 gated-delta-net 16x128 conv4 : 1 attention), vocab 32768"),
+}
+
 
 def reference_arm(args) -> None:
     """The reference needs its pinned JAX fork (jax 0.12.0.1.post118 + jaxlib / PJRT plugin) and flax / optax /
@@ -102,7 +124,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="dew_b200")
     ap.add_argument("--micro", type=int, default=None, help="sequences per microbatch (default 2 at N=1, where memory allows no more, 4 otherwise)")
-    ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="sequences per GPU per step")
+    ap.add_argument("--rows", type=int, default=None, help="sequences per GPU per step (default: the configuration's)")
+    ap.add_argument("--config", default="dense", choices=sorted(CONFIGS), help="training configuration (default: the headline)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the result is then not a valid headline)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--profile", default=None, help="write a torch.profiler kernel table for one step to this file")
@@ -130,13 +153,28 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=dev)
     L.load()
 
-    cfg = dict(MODEL)
+    conf = CONFIGS[args.config]
+    SEQ_LEN = conf["seq"]
+    cfg = dict(conf["model"])
     if args.layers:
         cfg["num_layers"] = args.layers
-    micro = args.micro or (2 if world == 1 else 4)
-    rows = args.rows
+    micro = args.micro or ((2 if world == 1 else 4) if args.config == "dense" else 2)
+    rows = args.rows or conf["rows"]
     assert rows % micro == 0
-    model = CausalTransformer(device="meta", dtype=torch.bfloat16, **cfg)
+    if args.config == "moe":
+        # experts are split over the ranks before the engine takes the parameters: build on the device, same seed everywhere
+        from dew_b200.models.causal_transformer import Mixture
+        from dew_b200.nn.layers import reset_all
+        from dew_b200.parallel.ep import ExpertParallel
+        model = CausalTransformer(device=dev, dtype=torch.bfloat16, mixture=Mixture(**conf["mixture"]), **cfg)
+        reset_all(model, 1234)
+        if world > 1:
+            ExpertParallel().shard(model)
+        else:
+            next(p for n, p in model.named_parameters() if "experts.gate_up" in n).expert_parallel = True   # initialised above
+        torch.cuda.empty_cache()
+    else:
+        model = CausalTransformer(device="meta", dtype=torch.bfloat16, **cfg)
     objective = LMObjective(model, SEQ_LEN, ema_decay=None)
     tracker = dew.MemoryTracker()
     trainer = dew.Trainer(objective, dew.OptimConfig(learning_rate=3e-4, weight_decay=0.1, optimizer_opts={"b2": 0.95}),
@@ -241,13 +279,15 @@ def main() -> None:
         flops = model.model_flops(tokens_per_step // world, SEQ_LEN) * 3
         mfu = flops * args.steps / (ms / 1e3) / 2.25e15
         out = {
-            "metric": "train tokens/sec (dense 8B LM, FSDP)", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "metric": conf["metric"], "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": value / (BASELINE_TOK_S_PER_GPU * world), "dtype": "bf16",
+            "scaling": "weak", "vs_baseline": value / (BASELINE_TOK_S_PER_GPU * world) if args.config == "dense" else None,
+            "dtype": "bf16" if args.config != "moe" else "bf16 (fp8 e4m3 expert GEMMs)",
             "data": "synthetic (uniform random token ids from a seed; random-init weights)",
-            "config": {"model": "llama-style 8B: d4096 L32 H32/8kv ffn14336 vocab128256", "params": n_params,
+            "config": {"model": conf["name"], "params": n_params,
                        "global_batch": rows * world, "seq_len": SEQ_LEN, "micro_batch": micro,
-                       "parallelism": f"fsdp{world}", "optimizer": "AdamW fp32 masters+moments",
+                       "parallelism": f"fsdp{world}" + (f"+ep{world}" if args.config == "moe" else ""),
+                       "optimizer": "AdamW fp32 masters+moments",
                        "l2": "inputs larger than L2 (16 GB of weights stream every microbatch)",
                        "baseline": "BASELINE.md reference-equivalent mark 190K tok/s at 8xB200, scaled per GPU"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "loss": loss, "mfu_datasheet": mfu,
