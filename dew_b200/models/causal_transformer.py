@@ -89,7 +89,16 @@ def _mixer(cfg: TransformerConfig, kind: str, dtype, device) -> nn.Module:
     if kind == "mamba2":
         from ..nn.mamba2 import Mamba2
         return Mamba2(cfg.emb_features, dtype=dtype, device=device, **cfg.mixer_options)
-    raise ValueError(f"unknown layer type {kind!r}; known: attention, local, gdn, mamba2")
+    if kind == "mamba":
+        from ..nn.mamba import Mamba
+        return Mamba(cfg.emb_features, dtype=dtype, device=device, **cfg.mixer_options)
+    if kind == "kda":
+        from ..nn.kda import KimiDeltaAttention
+        return KimiDeltaAttention(cfg.emb_features, dtype=dtype, device=device, **cfg.mixer_options)
+    if kind == "mla":
+        from ..nn.mla import MultiHeadLatentAttention
+        return MultiHeadLatentAttention(cfg.emb_features, cfg.num_heads, norm_eps=cfg.norm_eps, dtype=dtype, device=device, **cfg.mixer_options)
+    raise ValueError(f"unknown layer type {kind!r}; known: attention, local, gdn, mamba2, mamba, kda, mla")
 
 
 class DecoderLayer(nn.Module):
@@ -124,7 +133,7 @@ class DecoderLayer(nn.Module):
             n = self.input_norm(h)
         else:
             n, h = self._norm(self.input_norm, h, branch)
-        if self.kind in ("attention", "local"):
+        if self.kind in ("attention", "local", "mla"):
             a = self.mixer(n, cos, sin, positions, segment_ids, cache, self.index)
         else:
             a = self.mixer(n, segment_ids=segment_ids, cache=cache, layer=self.index)

@@ -66,6 +66,10 @@ def _pair_built() -> bool:
         return False
 
 
+_TUNE = bool(int(os.environ.get("DEWB_TUNE", "0")))
+from .tuning import KernelOp as _KernelOp  # noqa: E402
+_GEMM_TUNER = _KernelOp("gemm_bf16")
+
 # Which of this library's two dense kernels large products take ("sm100_tcgen05" or "sm100_pair").
 LARGE_GEMM = os.environ.get("DEWB_LARGE_GEMM", "sm100_pair")
 
@@ -98,9 +102,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                 inner_contig=(a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1), M=M, N=N, K=K)
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
     cell = ("skinny",) if tiles < 24 else None
-    if kernel is None and cell is None and LARGE_GEMM == "sm100_pair" and tiles >= 148 and N <= 32768 and _pair_built():
-        # measured: the pair kernel is 5-15 % faster on the layer shapes; the single-CTA kernel keeps the very wide head
-        kernel = "sm100_pair"
+    if kernel is None and cell is None and tiles >= 148 and _pair_built():
+        # measured: the pair kernel is 5-15 % faster on the layer shapes; the single-CTA kernel keeps the very wide head.
+        # With DEWB_TUNE=1 the two are timed once per shape and the pick is cached on disk (ops/tuning.py).
+        first = "sm100_pair" if (LARGE_GEMM == "sm100_pair" and N <= 32768) else "sm100_tcgen05"
+        other = "sm100_tcgen05" if first == "sm100_pair" else "sm100_pair"
+        if _TUNE and not torch.cuda.is_current_stream_capturing():
+            scratch = torch.empty_like(out)
+            kernel = _GEMM_TUNER.pick((M, N, K, a_mn, b_mn, str(out.dtype), bool(accumulate)), [first, other],
+                                      lambda name: gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=scratch, alpha=alpha, kernel=name), tune=True)
+        else:
+            kernel = first
     which = _GEMM.select(case, forced=kernel, cell=cell)
     if which == "cublas":
         return _gemm_reference_cuda(a, b, a_mn, b_mn, alpha, out, accumulate)

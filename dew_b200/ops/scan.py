@@ -224,3 +224,138 @@ def short_conv_step(x, w, bias, cache, activation: bool = True):
         y = y + bias.float()
     cache.copy_(window[:, 1:])
     return (F.silu(y) if activation else y).to(x.dtype)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Kimi delta attention (KDA): the gated delta rule with a per-channel (not per-head) decay.
+# Reference: src/dew/nn/kernels/fla_kda.py (chunked kernels), src/dew/nn/kda.py.
+def kda_recurrent(q, k, v, g, beta, initial_state=None, scale: Optional[float] = None):
+    """``q, k [B,T,H,Dk]``, ``v [B,T,H,Dv]``, ``g [B,T,H,Dk]`` (log decay per key channel, <= 0), ``beta [B,T,H]``.
+    ``S_t = (I - beta k k^T) diag(exp(g_t)) S_{t-1} + beta k v^T``;  ``o_t = S_t^T q_t * scale``.  fp32 state."""
+    B, T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    scale = Dk ** -0.5 if scale is None else scale
+    S = torch.zeros(B, H, Dk, Dv, dtype=torch.float32, device=q.device) if initial_state is None else initial_state.float().clone()
+    out = []
+    qf, kf, vf, gf, bf = q.float(), k.float(), v.float(), g.float(), beta.float()
+    for t in range(T):
+        S = S * gf[:, t].exp().unsqueeze(-1)
+        kv = torch.einsum("bhk,bhkv->bhv", kf[:, t], S)
+        S = S + torch.einsum("bhk,bhv->bhkv", kf[:, t], (vf[:, t] - kv) * bf[:, t].unsqueeze(-1))
+        out.append(torch.einsum("bhk,bhkv->bhv", qf[:, t] * scale, S))
+    return torch.stack(out, 1).to(v.dtype), S
+
+
+def kda_chunked(q, k, v, g, beta, initial_state=None, scale: Optional[float] = None, chunk: int = CHUNK_SIZE):
+    """Chunk-parallel form: inside a chunk the decay is folded into q and k (``q~ = q exp(G)``, ``k~ = k exp(-G)`` with
+    ``G`` the running sum of ``g``), which reduces the recurrence to the ungated delta rule's WY representation; the state
+    crosses chunks in fp32.  Equals ``kda_recurrent`` up to rounding."""
+    B, T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    scale = Dk ** -0.5 if scale is None else scale
+    pad = (-T) % chunk
+    if pad:
+        z = lambda x: torch.nn.functional.pad(x, (0, 0) * (x.dim() - 2) + (0, pad))
+        q, k, v, g = z(q), z(k), z(v), z(g)
+        beta = torch.nn.functional.pad(beta, (0, 0, 0, pad))
+    N = q.shape[1] // chunk
+    f = lambda x: x.float().reshape(B, N, chunk, H, -1).permute(0, 1, 3, 2, 4)          # [B,N,H,C,D]
+    qf, kf, vf, gf = f(q) * scale, f(k), f(v), f(g)
+    bf = beta.float().reshape(B, N, chunk, H).permute(0, 1, 3, 2)                       # [B,N,H,C]
+    G = gf.cumsum(-2)                                                                   # [B,N,H,C,Dk]
+    qd, kd = qf * G.exp(), kf * (-G).exp()                                              # decay folded in
+    kb = kf * G.exp()                                                                   # key as the state of chunk start sees it
+    S = torch.zeros(B, H, Dk, Dv, dtype=torch.float32, device=q.device) if initial_state is None else initial_state.float().clone()
+    eye = torch.eye(chunk, device=q.device)
+    lower = torch.tril(torch.ones(chunk, chunk, device=q.device), -1)
+    outs = []
+    for n in range(N):
+        A = torch.einsum("bhik,bhjk->bhij", kb[:, n], kd[:, n]) * lower * bf[:, n].unsqueeze(-1)      # strictly lower
+        Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A).contiguous(), upper=False)        # (I + A)^-1
+        rhs = (vf[:, n] - torch.einsum("bhik,bhkv->bhiv", kb[:, n], S)) * bf[:, n].unsqueeze(-1)
+        U = torch.einsum("bhij,bhjv->bhiv", Tm, rhs)                                    # corrected values
+        attn = torch.einsum("bhik,bhjk->bhij", qd[:, n], kd[:, n]) * (lower + eye)
+        outs.append(torch.einsum("bhik,bhkv->bhiv", qd[:, n], S) + torch.einsum("bhij,bhjv->bhiv", attn, U))
+        last = G[:, n, :, -1]                                                           # [B,H,Dk]
+        S = S * last.exp().unsqueeze(-1) + torch.einsum("bhik,bhiv->bhkv", kd[:, n] * last.exp().unsqueeze(-2), U)
+    o = torch.stack(outs, 1).permute(0, 1, 3, 2, 4).reshape(B, N * chunk, H, Dv)[:, :T]
+    return o.to(v.dtype), S
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Mamba-1 selective scan.  Reference: src/dew/nn/kernels/templates/recurrence/selective.py, src/dew/nn/mixers/mamba.py.
+def selective_scan_reference(x, dt, A, Bm, Cm, D=None, z=None, initial_state=None):
+    """``x, dt [B,T,C]``, ``A [C,N]`` (negative), ``Bm, Cm [B,T,N]``: ``h_t = exp(dt A) h_{t-1} + dt B x``; ``y = C h + D x``,
+    optionally gated by ``silu(z)``.  Sequential over T, fp32 state ``[B,C,N]``."""
+    Bsz, T, C = x.shape
+    h = torch.zeros(Bsz, C, A.shape[1], dtype=torch.float32, device=x.device) if initial_state is None else initial_state.float().clone()
+    xf, dtf, Af, Bf, Cf = x.float(), dt.float(), A.float(), Bm.float(), Cm.float()
+    ys = []
+    for t in range(T):
+        dA = torch.exp(dtf[:, t].unsqueeze(-1) * Af)
+        h = dA * h + (dtf[:, t] * xf[:, t]).unsqueeze(-1) * Bf[:, t].unsqueeze(1)
+        ys.append(torch.einsum("bcn,bn->bc", h, Cf[:, t]))
+    y = torch.stack(ys, 1)
+    if D is not None:
+        y = y + xf * D.float()
+    if z is not None:
+        y = y * torch.nn.functional.silu(z.float())
+    return y.to(x.dtype), h
+
+
+def selective_scan(x, dt, A, Bm, Cm, D=None, z=None, initial_state=None, chunk: int = 64):
+    """Chunked selective scan: a log-depth (Hillis-Steele) prefix combine of ``(decay, increment)`` pairs inside each chunk,
+    state carried across chunks - O(T log chunk) parallel work instead of T sequential steps."""
+    Bsz, T, C = x.shape
+    N = A.shape[1]
+    pad = (-T) % chunk
+    xf, dtf = x.float(), dt.float()
+    Bf, Cf = Bm.float(), Cm.float()
+    if pad:
+        p3 = lambda t: torch.nn.functional.pad(t, (0, 0, 0, pad))
+        xf, dtf, Bf, Cf = p3(xf), p3(dtf), p3(Bf), p3(Cf)
+    n = xf.shape[1] // chunk
+    a = torch.exp(dtf.unsqueeze(-1) * A.float()).reshape(Bsz, n, chunk, C, N)                      # decay per step
+    b = ((dtf * xf).unsqueeze(-1) * Bf.unsqueeze(2)).reshape(Bsz, n, chunk, C, N)                  # increment per step
+    # inclusive scan of the affine maps h -> a h + b along the chunk axis
+    step = 1
+    while step < chunk:
+        a_prev = torch.cat([torch.ones_like(a[:, :, :step]), a[:, :, :-step]], 2)
+        b_prev = torch.cat([torch.zeros_like(b[:, :, :step]), b[:, :, :-step]], 2)
+        b = a * b_prev + b
+        a = a * a_prev
+        step *= 2
+    h = torch.zeros(Bsz, C, N, dtype=torch.float32, device=x.device) if initial_state is None else initial_state.float().clone()
+    ys = []
+    Cc = Cf.reshape(Bsz, n, chunk, N)
+    for i in range(n):
+        hs = a[:, i] * h.unsqueeze(1) + b[:, i]                                                   # [B, chunk, C, N]
+        ys.append(torch.einsum("btcn,btn->btc", hs, Cc[:, i]))
+        h = hs[:, -1]
+    y = torch.cat(ys, 1)[:, :T]
+    if D is not None:
+        y = y + x.float() * D.float()
+    if z is not None:
+        y = y * torch.nn.functional.silu(z.float())
+    return y.to(x.dtype), h
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# RWKV-4 time mixing (wkv).  Reference: src/dew/nn/kernels/wkv4.py.
+def wkv4(w, u, k, v):
+    """``w, u [C]`` (decay ``exp(-exp(w))`` per channel, bonus ``u``), ``k, v [B,T,C]``: the numerically stable running
+    ratio ``(sum_j<t e^{-(t-1-j) e^w + k_j} v_j + e^{u + k_t} v_t) / (same with v = 1)``."""
+    B, T, C = k.shape
+    wf, uf, kf, vf = -torch.exp(w.float()), u.float(), k.float(), v.float()
+    num = torch.zeros(B, C, device=k.device); den = torch.zeros(B, C, device=k.device)
+    mx = torch.full((B, C), -1e38, device=k.device)
+    out = []
+    for t in range(T):
+        kt, vt = kf[:, t], vf[:, t]
+        m1 = torch.maximum(mx, uf + kt)
+        e1, e2 = torch.exp(mx - m1), torch.exp(uf + kt - m1)
+        out.append((e1 * num + e2 * vt) / (e1 * den + e2))
+        m2 = torch.maximum(mx + wf, kt)
+        e1, e2 = torch.exp(mx + wf - m2), torch.exp(kt - m2)
+        num, den, mx = e1 * num + e2 * vt, e1 * den + e2, m2
+    return torch.stack(out, 1).to(v.dtype)

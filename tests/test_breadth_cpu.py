@@ -92,3 +92,24 @@ def test_nccl_weight_push_orders_chunks_and_aborts_on_failure():
     with pytest.raises(PushFailed):
         p2.push(tensors, version=1)
     assert bad.aborted and p2.comm is None and p2.pushed == []
+
+
+def test_tuning_cache_measures_once_and_persists(tmp_path):
+    import time
+    from dew_b200.ops.tuning import KernelOp, TuningCache
+    calls = []
+    def run(name):
+        calls.append(name)
+        time.sleep(0.002 if name == "slow" else 0.0)
+        if name == "refuses":
+            raise RuntimeError("no")
+    cache = TuningCache(str(tmp_path / "t.json"))
+    op = KernelOp("demo", cache)
+    assert op.pick((128, 256), ["slow", "fast", "refuses"], run, tune=False) == "slow"          # untuned: first candidate, no timing
+    assert calls == []
+    assert op.pick((128, 256), ["slow", "fast", "refuses"], run, tune=True) == "fast"
+    n = len(calls)
+    assert op.pick((128, 256), ["slow", "fast"], run, tune=True) == "fast" and len(calls) == n  # memoised
+    again = KernelOp("demo", TuningCache(str(tmp_path / "t.json")))                             # a later process reads the file
+    assert again.pick((128, 256), ["slow", "fast"], run, tune=False) == "fast" and len(calls) == n
+    assert again.pick((1, 1), ["slow", "fast"], run, tune=False) == "slow"
