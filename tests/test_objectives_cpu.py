@@ -99,3 +99,59 @@ def test_placement_report_for_a_target_machine():
     assert bad["refusals"]
     tiny = placement_report(model, MeshSpec(), Layout(), devices=1, memory_bytes=1e6)
     assert not tiny["fits"]
+
+
+def test_masked_and_block_diffusion_lm_train_and_sample():
+    from dew_b200.objectives.discrete import BlockDiffusionLM, MaskedDiffusionLM
+    torch.manual_seed(0)
+    V = 20
+    class Bidirectional(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = torch.nn.Embedding(V + 1, 32)
+            self.mix = torch.nn.GRU(32, 32, batch_first=True, bidirectional=True)
+            self.out = torch.nn.Linear(64, V + 1)
+        def forward(self, tokens):
+            return self.out(self.mix(self.emb(tokens))[0])
+    data = (torch.arange(12)[None] + torch.arange(16)[:, None]) % V            # rows are arithmetic progressions
+    for cls, kw in ((MaskedDiffusionLM, {}), (BlockDiffusionLM, {"block": 4})):
+        obj = cls(Bidirectional(), mask_id=V, **kw)
+        tr = dew.Trainer(obj, dew.OptimConfig(learning_rate=1e-2, weight_decay=0.0), tracker=(t := dew.MemoryTracker()))
+        st = tr.fit(dew.Memory({"tokens": data}).repeat().batched(16), steps=60, log_every=20)
+        assert t.rows[-1]["masked_ce"] < t.rows[0]["masked_ce"]
+        x = obj.sample(st.variables, 3, 12, steps=6, generator=torch.Generator().manual_seed(0))
+        assert x.shape == (3, 12) and int((x == V).sum()) == 0
+    assert BlockDiffusionLM.block_causal_mask(6, 2).tolist()[2] == [True, True, True, True, False, False]
+
+
+def test_consistency_and_world_model_objectives():
+    from dew_b200.objectives.consistency import ConsistencyObjective, WorldModelObjective
+    torch.manual_seed(0)
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.f = torch.nn.Sequential(torch.nn.Linear(5, 32), torch.nn.SiLU(), torch.nn.Linear(32, 4))
+        def forward(self, x, t):
+            return self.f(torch.cat([x, t[:, None]], -1))
+    obj = ConsistencyObjective(Net(), levels=8, ema_decay=0.9)
+    # boundary condition: at sigma_min the denoiser is the identity
+    x = torch.randn(3, 4)
+    assert torch.allclose(obj.denoise(None, x, torch.full((3,), obj.smin)), x, atol=1e-5)
+    tr = dew.Trainer(obj, dew.OptimConfig(learning_rate=2e-3, weight_decay=0.0), tracker=(t := dew.MemoryTracker()))
+    st = tr.fit(dew.Memory({"sample": torch.randn(64, 4) * 0.5}).repeat().batched(16), steps=30, log_every=10)
+    assert obj.generate(st.averaged, (5, 4), steps=2).shape == (5, 4) and all(r["loss"] == r["loss"] for r in t.rows)
+
+    class World(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.enc, self.dyn = torch.nn.Linear(6, 8), torch.nn.Linear(8 + 2, 8)
+            self.rew, self.don = torch.nn.Linear(8 + 2, 1), torch.nn.Linear(8, 1)
+        def encode(self, o): return self.enc(o)
+        def dynamics(self, z, a): return self.dyn(torch.cat([z, a], -1))
+        def reward(self, z, a): return self.rew(torch.cat([z, a], -1))
+        def done(self, z): return self.don(z)
+    batch = {"observation": torch.randn(8, 5, 6), "action": torch.randn(8, 4, 2), "reward": torch.randn(8, 4), "done": torch.zeros(8, 4)}
+    wobj = WorldModelObjective(World(), horizon=3)
+    tr = dew.Trainer(wobj, dew.OptimConfig(learning_rate=1e-2, weight_decay=0.0), tracker=(t := dew.MemoryTracker()))
+    tr.fit(dew.Loader(lambda part: iter([batch] * 30), batch=8), steps=20, log_every=5)
+    assert t.rows[-1]["loss"] < t.rows[0]["loss"]
