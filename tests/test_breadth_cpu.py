@@ -113,3 +113,30 @@ def test_tuning_cache_measures_once_and_persists(tmp_path):
     again = KernelOp("demo", TuningCache(str(tmp_path / "t.json")))                             # a later process reads the file
     assert again.pick((128, 256), ["slow", "fast"], run, tune=False) == "fast" and len(calls) == n
     assert again.pick((1, 1), ["slow", "fast"], run, tune=False) == "slow"
+
+
+def test_mixture_is_reproducible_and_restorable_and_scoring_and_clients():
+    from dew_b200.data.mixing import Mixture, PhasedStream
+    from dew_b200.inference.clients import OpenAIClient
+    from dew_b200.inference.scoring import multiple_choice_accuracy, score
+    a, b = [("a", i) for i in range(100)], [("b", i) for i in range(100)]
+    m1 = iter(Mixture([(a, 3.0), (b, 1.0)], seed=5))
+    first = [next(m1) for _ in range(40)]
+    assert 20 < sum(r[0] == "a" for r in first) < 38
+    m2 = Mixture([(a, 3.0), (b, 1.0)], seed=5)
+    it = iter(m2)
+    [next(it) for _ in range(25)]
+    pos = m2.position()
+    m3 = Mixture([(a, 3.0), (b, 1.0)], seed=5); m3.restore(pos)
+    assert [next(iter(m3)) for _ in range(1)] + [next(m3) for _ in range(14)] == first[25:40]
+    ph = PhasedStream([(2, ["x"] * 10), (4, ["y"] * 10)])
+    assert [next(ph) for _ in range(4)] == ["x", "x", "y", "y"]
+    torch.manual_seed(0)
+    m = CausalTransformer(vocab_size=32, emb_features=32, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=16, mlp_features=64, max_seq_len=32)
+    s = score(m, [[1, 2, 3], [4, 5]], [[6, 7], [8, 9, 10]])
+    full = torch.log_softmax(m(torch.tensor([[1, 2, 3, 6, 7]])).float(), -1)[0]
+    assert abs(s[0][0] - float(full[2, 6] + full[3, 7])) < 1e-4 and s[0][1] == 2 and s[1][1] == 3
+    assert 0.0 <= multiple_choice_accuracy(m, [([1, 2], [[3], [4, 5]], 0)]) <= 1.0
+    sent = {}
+    client = OpenAIClient(model="m", transport=lambda url, body, headers, timeout: sent.update(url=url, body=body) or {"choices": [{"message": {"content": "hi"}}]})
+    assert client.chat([{"role": "user", "content": "x"}]) == "hi" and sent["url"].endswith("/chat/completions") and sent["body"]["model"] == "m"
