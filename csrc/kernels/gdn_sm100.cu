@@ -1,0 +1,794 @@
+// Gated delta rule (chunk 64, 128-wide keys and values) for sm_100a: three kernels.
+//
+//   gdn_prepare_kernel   one CTA per 128 tokens (two chunks) of one (batch, head).  TMA brings the K, Q and V rows;
+//                        K K^T and Q K^T are two 128x128x128 tcgen05 products (only the two 64x64 diagonal blocks are
+//                        used); the strictly lower system (I + A) [W | U] = [beta e^g K | beta V] is solved by forward
+//                        substitution in fp32, one right-hand-side column per thread, the A row broadcast from shared
+//                        memory.  Writes gc (cumulative log decay inside the chunk), W, U, P = scale * (Q K^T) e^{g_i-g_j}
+//                        (lower triangle) and, for the backward, Qg = scale * e^g Q.
+//   gdn_scan_fwd_kernel  one CTA per (batch, head), chunks in order.  The state is kept transposed (rows = value index):
+//                        fp32 in the registers of 128 threads (one value row each) and bf16 as a K-major operand tile in
+//                        shared memory, so every product has M = 128:
+//                          acc1 = S^T W^T, o1 = S^T Q^T            (after the state tile is written)
+//                          Vn^T = U^T - acc1 ;  o2 = Vn^T P^T ;  dS = (Vn e^{g_L - g})^T K
+//                          O^T = scale e^{g} o1 + o2 ;  S^T <- e^{g_L} S^T + dS
+//   gdn_scan_bwd_kernel  the same walk from the last chunk to the first for the state gradient G (also transposed):
+//                          a = dO^T P, b = G^T K^T ;  dVn^T = a + e^{g_L - g} b
+//                          G^T <- e^{g_L} G^T + dO^T Qg - dVn^T W
+//                        and stores G as it stands on entry to each chunk (the gradient of that chunk's exit state).
+//
+// Warp roles in the scans: warps 0..3 math (thread = TMEM lane = value index), warp 4 TMA producer (2-stage ring of
+// per-chunk operand tiles), warp 5 MMA issuer.  Every wait is bounded; a timed-out wait records a status code, raises
+// the CTA's abort flag, and all roles leave through the common exit that frees the tensor memory.
+//
+// Replaces the reference's fla-style kernels KktSolve / RecomputeWU / ChunkFwdH / ChunkFwdO / ChunkBwdDhu
+// (src/dew/nn/kernels/fla_gdn.py:199-795) and the recurrence template's chunk_forward / mainloop
+// (src/dew/nn/kernels/templates/recurrence/).
+#include "../common/ptx.cuh"
+#include "../common/tmap.h"
+
+namespace dewb {
+namespace gdn {
+
+constexpr int HD = 128;           // key and value head dimension
+constexpr int CH = 64;            // chunk length
+constexpr int PT = 128;           // tokens per prepare CTA
+constexpr uint32_t FULL = 0xffffffffu;
+
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Byte offset of the 16-byte piece `c16` (8 bf16) of row `r` inside a 128-byte-swizzled tile whose rows are 128 bytes.
+__device__ __forceinline__ uint32_t swz(int r, int c16) { return static_cast<uint32_t>(r * 128 + ((c16 ^ (r & 7)) << 4)); }
+
+// ------------------------------------------------------------------------------------------------------------------
+// prepare
+
+constexpr int PREP_THREADS = 256;
+constexpr int PREP_TILE = PT * HD * 2;                 // 32 KiB: a [128 x 128] bf16 tile as two 64-column sub-tiles
+constexpr int PREP_SMEM = 3 * PREP_TILE + 2048;
+
+struct PrepTail {
+  float g[PT];          // cumulative log decay inside the chunk
+  float beta[PT];
+  float eg[PT];         // e^{g}
+  float warp_sum[4];
+  uint64_t bar_load, bar_mma;
+  uint32_t tmem_base;
+  int poisoned, abort_flag;
+};
+static_assert(sizeof(PrepTail) <= 2048, "PrepTail must fit its slot");
+
+__global__ void __launch_bounds__(PREP_THREADS, 2)
+gdn_prepare_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                   const __grid_constant__ CUtensorMap tv, const float* __restrict__ g, const float* __restrict__ beta,
+                   float* __restrict__ gc_out, __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ U,
+                   __nv_bfloat16* __restrict__ P, __nv_bfloat16* __restrict__ Qg, int T, int H, int Tp, float scale,
+                   int* __restrict__ err) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(err, 0, ERR_BAD_ARG);
+    return;
+  }
+  uint8_t* sK = smem;
+  uint8_t* sQ = smem + PREP_TILE;
+  uint8_t* sV = smem + 2 * PREP_TILE;
+  float* sA = reinterpret_cast<float*>(sQ);              // the Q tile's space is reused for A once Q has been consumed
+  PrepTail* tail = reinterpret_cast<PrepTail*>(smem + 3 * PREP_TILE);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) tail->poisoned = *reinterpret_cast<volatile int*>(err);
+  __syncthreads();
+  if (tail->poisoned != 0) return;
+
+  const int x = blockIdx.y, b = x / H, h = x % H;
+  const int t0 = blockIdx.x * PT;
+  if (tid == 0) {
+    mbar_init(&tail->bar_load, 1);
+    mbar_init(&tail->bar_mma, 1);
+    tail->abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 0) { tmem_alloc(&tail->tmem_base, 256); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tail->tmem_base;
+  volatile int* abort_flag = &tail->abort_flag;
+
+  if (tid == 0) {
+    mbar_expect_tx(&tail->bar_load, 3 * PREP_TILE);
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      tma_load_4d(sK + s * (PT * 128), &tk, &tail->bar_load, s * 64, h, t0, b);
+      tma_load_4d(sQ + s * (PT * 128), &tq, &tail->bar_load, s * 64, h, t0, b);
+      tma_load_4d(sV + s * (PT * 128), &tv, &tail->bar_load, s * 64, h, t0, b);
+    }
+  }
+  // cumulative log decay inside each chunk (tokens past the end: no decay, no write strength)
+  if (tid < PT) {
+    const int t = t0 + tid;
+    const bool valid = t < T;
+    float gi = valid ? g[(static_cast<long long>(b) * T + t) * H + h] : 0.f;
+    const float bi = valid ? beta[(static_cast<long long>(b) * T + t) * H + h] : 0.f;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float up = __shfl_up_sync(FULL, gi, d);
+      if (lane >= d) gi += up;
+    }
+    if (lane == 31) tail->warp_sum[warp] = gi;
+    tail->beta[tid] = bi;
+    tail->g[tid] = gi;     // finished below for the second warp of each chunk
+  }
+  __syncthreads();
+  if (tid < PT) {
+    float gi = tail->g[tid];
+    if (warp & 1) gi += tail->warp_sum[warp - 1];
+    tail->g[tid] = gi;
+    tail->eg[tid] = __expf(gi);
+    gc_out[static_cast<long long>(x) * Tp + t0 + tid] = gi;
+  }
+  __syncthreads();
+
+  bool ok = true;
+  if (tid == 0) {
+    if (!mbar_wait(&tail->bar_load, 0, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); }
+    else {
+      tc_fence_after();
+      constexpr uint32_t idesc = make_idesc(128, 128, 1, 1, 0, 0);
+      const uint32_t ka = smem_u32(sK), qa = smem_u32(sQ);
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) {
+        const uint32_t off = (kk >> 2) * (PT * 128) + (kk & 3) * 32;
+        umma_bf16_ss(tmem, make_sdesc_sw128(ka + off, 16, 1024), make_sdesc_sw128(ka + off, 16, 1024), idesc, kk > 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) {
+        const uint32_t off = (kk >> 2) * (PT * 128) + (kk & 3) * 32;
+        umma_bf16_ss(tmem + 128, make_sdesc_sw128(qa + off, 16, 1024), make_sdesc_sw128(ka + off, 16, 1024), idesc, kk > 0 ? 1u : 0u);
+      }
+      umma_commit(&tail->bar_mma);
+    }
+  }
+  if (warp < 4) {
+    // thread = token row i of the 128; its chunk's 64 columns of both score matrices
+    const int i = tid, c = i >> 6, il = i & 63;
+    const bool got = mbar_wait(&tail->bar_mma, 0, abort_flag);
+    if (!__all_sync(FULL, got)) { if (lane == 0) atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; }
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const float gi = tail->g[i], bi = tail->beta[i];
+    const long long row = static_cast<long long>(x) * Tp + t0 + i;
+    float a[CH];
+    if (ok) {
+      tc_fence_after();
+      uint32_t v0[32], v1[32];
+      // P row: scale * (q_i . k_j) * e^{g_i - g_j} for j <= i
+      tmem_ld_32x32b_x32(tmem + lane_addr + 128 + c * 64, v0);
+      tmem_ld_32x32b_x32(tmem + lane_addr + 128 + c * 64 + 32, v1);
+      tmem_ld_wait();
+      uint4* prow = reinterpret_cast<uint4*>(P + row * CH);
+#pragma unroll
+      for (int j8 = 0; j8 < 8; ++j8) {
+        float p[8];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          const int j = j8 * 8 + jj;
+          const float s = __uint_as_float(j < 32 ? v0[j & 31] : v1[j & 31]);
+          p[jj] = (j <= il) ? scale * s * __expf(gi - tail->g[c * 64 + j]) : 0.f;
+        }
+        uint4 pk;
+        pk.x = pack_bf16(p[0], p[1]); pk.y = pack_bf16(p[2], p[3]); pk.z = pack_bf16(p[4], p[5]); pk.w = pack_bf16(p[6], p[7]);
+        prow[j8] = pk;
+      }
+      // A row: beta_i * (k_i . k_j) * e^{g_i - g_j} for j < i
+      tmem_ld_32x32b_x32(tmem + lane_addr + c * 64, v0);
+      tmem_ld_32x32b_x32(tmem + lane_addr + c * 64 + 32, v1);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const float s = __uint_as_float(j < 32 ? v0[j & 31] : v1[j & 31]);
+        a[j] = (j < il) ? bi * s * __expf(gi - tail->g[c * 64 + j]) : 0.f;
+      }
+      if (Qg != nullptr) {
+        const float m = scale * tail->eg[i];
+        uint4* qrow = reinterpret_cast<uint4*>(Qg + row * HD);
+#pragma unroll
+        for (int c16 = 0; c16 < 16; ++c16) {
+          const uint4 in = *reinterpret_cast<const uint4*>(sQ + (c16 >> 3) * (PT * 128) + swz(i, c16 & 7));
+          uint4 o;
+          o.x = pack_bf16(bf16_lo(in.x) * m, bf16_hi(in.x) * m); o.y = pack_bf16(bf16_lo(in.y) * m, bf16_hi(in.y) * m);
+          o.z = pack_bf16(bf16_lo(in.z) * m, bf16_hi(in.z) * m); o.w = pack_bf16(bf16_lo(in.w) * m, bf16_hi(in.w) * m);
+          qrow[c16] = o;
+        }
+      }
+    }
+    // every row of Q has been read (by the tensor core and by its thread) before A overwrites the tile
+    named_barrier_sync(1, 128);
+    if (ok) {
+      // row i of chunk c at sA[c][il][.], its columns rotated by 4 * il so that neither these stores nor the broadcast
+      // reads of the solve meet a bank conflict
+      float4* arow = reinterpret_cast<float4*>(sA + c * (CH * CH) + il * CH);
+#pragma unroll
+      for (int j4 = 0; j4 < 16; ++j4)
+        arow[(j4 + il) & 15] = make_float4(a[j4 * 4], a[j4 * 4 + 1], a[j4 * 4 + 2], a[j4 * 4 + 3]);
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (tail->abort_flag == 0) {
+    // forward substitution: thread = one column of [W | U]; x_i = r_i - sum_{j < i} A_ij x_j
+    const int col = tid & 127;
+    const bool is_w = tid < 128;
+    const uint8_t* src = (is_w ? sK : sV) + (col >> 6) * (PT * 128) + (col & 7) * 2;
+    const int c16 = (col & 63) >> 3;
+    __nv_bfloat16* dst = (is_w ? W : U) + (static_cast<long long>(x) * Tp + t0) * HD + col;
+#pragma unroll 1
+    for (int c = 0; c < 2; ++c) {
+      float xv[CH];
+#pragma unroll
+      for (int i = 0; i < CH; ++i) xv[i] = 0.f;
+      const float* Ac = sA + c * (CH * CH);
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int r = c * 64 + i;
+        const float raw = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(src + swz(r, c16)));
+        float acc = raw * tail->beta[r] * (is_w ? tail->eg[r] : 1.f);
+        const float4* arow = reinterpret_cast<const float4*>(Ac + i * CH);
+#pragma unroll
+        for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
+          const float4 av = arow[(j4 + i) & 15];
+          acc = fmaf(-av.x, xv[j4 * 4], acc);
+          acc = fmaf(-av.y, xv[j4 * 4 + 1], acc);
+          acc = fmaf(-av.z, xv[j4 * 4 + 2], acc);
+          acc = fmaf(-av.w, xv[j4 * 4 + 3], acc);
+        }
+        xv[i] = acc;
+        dst[static_cast<long long>(r) * HD] = __float2bfloat16(acc);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// scans
+
+constexpr int SCAN_THREADS = 192;
+constexpr int TMA_WARP = 4, MMA_WARP = 5;
+constexpr int T16 = CH * HD * 2;                       // 16 KiB: a [64 x 128] bf16 tile (two 64-column sub-tiles)
+constexpr int T8 = CH * CH * 2;                        // 8 KiB: P
+constexpr int STAGE = 4 * T16 + T8;                    // 72 KiB of tiles per chunk
+constexpr int OFF_STATE = 2 * STAGE;                   // [128 x 128] bf16 state tile (32 KiB)
+constexpr int OFF_VN = OFF_STATE + 2 * T16;            // two [128 x 64] bf16 tiles (16 KiB each)
+constexpr int OFF_G = OFF_VN + 2 * T16;                // g of the two stages
+constexpr int OFF_BARS = OFF_G + 2 * CH * 4;
+constexpr int SCAN_SMEM = OFF_BARS + 256;
+
+struct ScanBars {
+  uint64_t in_full[2], in_empty[2], s_ready, acc_full, vn_ready, out_full;
+  uint32_t tmem_base;
+  int abort_flag, poisoned;
+};
+static_assert(sizeof(ScanBars) <= 256, "ScanBars must fit its slot");
+static_assert(SCAN_SMEM <= 232448, "scan kernels exceed the shared memory of an SM");
+
+// Writes this thread's row (128 values) of the transposed state as bf16 into the K-major operand tile.
+__device__ __forceinline__ void write_state_row(uint8_t* tile, int v, const float (&S)[HD]) {
+#pragma unroll
+  for (int c16 = 0; c16 < 16; ++c16) {
+    uint4 pk;
+    pk.x = pack_bf16(S[c16 * 8 + 0], S[c16 * 8 + 1]); pk.y = pack_bf16(S[c16 * 8 + 2], S[c16 * 8 + 3]);
+    pk.z = pack_bf16(S[c16 * 8 + 4], S[c16 * 8 + 5]); pk.w = pack_bf16(S[c16 * 8 + 6], S[c16 * 8 + 7]);
+    *reinterpret_cast<uint4*>(tile + (c16 >> 3) * (HD * 128) + swz(v, c16 & 7)) = pk;
+  }
+}
+
+struct ScanCommon {
+  uint8_t* smem;
+  ScanBars* bars;
+  uint32_t tmem;
+  volatile int* abort_flag;
+};
+
+// Common prologue: status check, barriers, tensor memory.  Returns false if the CTA must leave at once.
+__device__ __forceinline__ bool scan_prologue(uint8_t* smem, int* err, ScanCommon& sc) {
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(err, 0, ERR_BAD_ARG);
+    return false;
+  }
+  ScanBars* bars = reinterpret_cast<ScanBars*>(smem + OFF_BARS);
+  if (threadIdx.x == 0) bars->poisoned = *reinterpret_cast<volatile int*>(err);
+  __syncthreads();
+  if (bars->poisoned != 0) return false;
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars->in_full[i], 1); mbar_init(&bars->in_empty[i], 4); }
+    mbar_init(&bars->s_ready, 4);
+    mbar_init(&bars->acc_full, 1);
+    mbar_init(&bars->vn_ready, 4);
+    mbar_init(&bars->out_full, 1);
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == MMA_WARP) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  sc.smem = smem;
+  sc.bars = bars;
+  sc.tmem = bars->tmem_base;
+  sc.abort_flag = &bars->abort_flag;
+  return true;
+}
+
+__device__ __forceinline__ void scan_epilogue(const ScanCommon& sc) {
+  tc_fence_before();
+  __syncthreads();
+  if ((threadIdx.x >> 5) == MMA_WARP) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(sc.tmem, 512);
+  }
+}
+
+// Warp-uniform bounded wait for the math warps.
+__device__ __forceinline__ bool math_wait(uint64_t* bar, uint32_t parity, const ScanCommon& sc, int* err, int code) {
+  const bool got = mbar_wait(bar, parity, sc.abort_flag);
+  if (!__all_sync(FULL, got)) {
+    if ((threadIdx.x & 31) == 0) atomicCAS(err, 0, code);
+    return false;
+  }
+  return true;
+}
+
+// Stage tile offsets of the forward scan: W, U, Q, K, P.  Of the backward scan: dO, Qg, K, W, P.
+constexpr int F_W = 0, F_U = T16, F_Q = 2 * T16, F_K = 3 * T16, F_P = 4 * T16;
+constexpr int B_DO = 0, B_QG = T16, B_K = 2 * T16, B_W = 3 * T16, B_P = 4 * T16;
+
+__global__ void __launch_bounds__(SCAN_THREADS, 1)
+gdn_scan_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                    const __grid_constant__ CUtensorMap tw, const __grid_constant__ CUtensorMap tu,
+                    const __grid_constant__ CUtensorMap tp, const float* __restrict__ gc,
+                    const float* __restrict__ initial, __nv_bfloat16* __restrict__ out, float* __restrict__ final_state,
+                    __nv_bfloat16* __restrict__ states, int T, int H, int Tp, int N, float scale, int* __restrict__ err) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  ScanCommon sc;
+  if (!scan_prologue(smem, err, sc)) return;
+  ScanBars* bars = sc.bars;
+  const uint32_t tmem = sc.tmem;
+  volatile int* abort_flag = sc.abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int x = blockIdx.x, b = x / H, h = x % H;
+  uint8_t* sState = smem + OFF_STATE;
+  uint8_t* sVn = smem + OFF_VN;
+  uint8_t* sVd = smem + OFF_VN + T16;
+  float* sG = reinterpret_cast<float*>(smem + OFF_G);
+  constexpr int TM_ACC1 = 0, TM_O1 = 64, TM_O2 = 128, TM_DS = 256;
+
+  if (warp == TMA_WARP) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tw); tma_prefetch_desc(&tu); tma_prefetch_desc(&tp);
+      for (int n = 0; n < N; ++n) {
+        const int s = n & 1; const uint32_t ph = (n >> 1) & 1;
+        if (!mbar_wait(&bars->in_empty[s], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); break; }
+        uint8_t* st = smem + s * STAGE;
+        uint64_t* bar = &bars->in_full[s];
+        mbar_expect_tx(bar, STAGE + CH * 4);
+        const int row = x * Tp + n * CH;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          tma_load_2d(st + F_W + t * (CH * 128), &tw, bar, t * 64, row);
+          tma_load_2d(st + F_U + t * (CH * 128), &tu, bar, t * 64, row);
+          tma_load_4d(st + F_Q + t * (CH * 128), &tq, bar, t * 64, h, n * CH, b);
+          tma_load_4d(st + F_K + t * (CH * 128), &tk, bar, t * 64, h, n * CH, b);
+        }
+        tma_load_2d(st + F_P, &tp, bar, 0, row);
+        bulk_load_1d(sG + s * CH, gc + static_cast<long long>(x) * Tp + n * CH, CH * 4, bar);
+      }
+    }
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_n64 = make_idesc(128, 64, 1, 1, 0, 0);
+      constexpr uint32_t idesc_ds = make_idesc(128, 128, 1, 1, 0, 1);
+      const uint32_t sa = smem_u32(sState), vna = smem_u32(sVn), vda = smem_u32(sVd);
+      for (int n = 0; n < N; ++n) {
+        const int s = n & 1; const uint32_t ph = (n >> 1) & 1;
+        const uint32_t st = smem_u32(smem + s * STAGE);
+        if (!mbar_wait(&bars->in_full[s], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); break; }
+        if (!mbar_wait(&bars->s_ready, n & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t aoff = (kk >> 2) * (HD * 128) + (kk & 3) * 32, boff = (kk >> 2) * (CH * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + TM_ACC1, make_sdesc_sw128(sa + aoff, 16, 1024), make_sdesc_sw128(st + F_W + boff, 16, 1024),
+                       idesc_n64, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->acc_full);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t aoff = (kk >> 2) * (HD * 128) + (kk & 3) * 32, boff = (kk >> 2) * (CH * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + TM_O1, make_sdesc_sw128(sa + aoff, 16, 1024), make_sdesc_sw128(st + F_Q + boff, 16, 1024),
+                       idesc_n64, kk > 0 ? 1u : 0u);
+        }
+        if (!mbar_wait(&bars->vn_ready, n & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < CH / 16; ++kk) {
+          umma_bf16_ss(tmem + TM_O2, make_sdesc_sw128(vna + kk * 32, 16, 1024), make_sdesc_sw128(st + F_P + kk * 32, 16, 1024),
+                       idesc_n64, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < CH / 16; ++kk) {
+          umma_bf16_ss(tmem + TM_DS, make_sdesc_sw128(vda + kk * 32, 16, 1024),
+                       make_sdesc_sw128(st + F_K + kk * 2048, CH * 128, 1024), idesc_ds, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->out_full);
+      }
+    }
+  } else {
+    const int v = tid;                                   // value index == TMEM lane == row of the transposed state
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    float S[HD];
+    if (initial != nullptr) {
+      const float* src = initial + static_cast<long long>(x) * HD * HD + v;
+#pragma unroll
+      for (int d = 0; d < HD; ++d) S[d] = src[d * HD];
+    } else {
+#pragma unroll
+      for (int d = 0; d < HD; ++d) S[d] = 0.f;
+    }
+    write_state_row(sState, v, S);
+    fence_proxy_async();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bars->s_ready);
+    bool ok = true;
+    for (int n = 0; n < N && ok; ++n) {
+      const int s = n & 1; const uint32_t ph = (n >> 1) & 1;
+      const uint8_t* st = smem + s * STAGE;
+      const float* gs = sG + s * CH;
+      if (!math_wait(&bars->in_full[s], ph, sc, err, ERR_WAIT_FULL)) { ok = false; break; }
+      if (!math_wait(&bars->acc_full, n & 1, sc, err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const float gl = gs[CH - 1];
+      // Vn^T row: U[j][v] - acc1[j]; the copy for the state update carries e^{g_L - g_j}
+      const uint8_t* ucol = st + F_U + (v >> 6) * (CH * 128) + (v & 7) * 2;
+      const int uc16 = (v & 63) >> 3;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t a[32];
+        tmem_ld_32x32b_x32(tmem + lane_addr + TM_ACC1 + half * 32, a);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j8 = 0; j8 < 4; ++j8) {
+          float vn[8], vd[8];
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) {
+            const int j = half * 32 + j8 * 8 + jj;
+            const float u = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(ucol + swz(j, uc16)));
+            vn[jj] = u - __uint_as_float(a[j8 * 8 + jj]);
+            vd[jj] = vn[jj] * __expf(gl - gs[j]);
+          }
+          uint4 p0, p1;
+          p0.x = pack_bf16(vn[0], vn[1]); p0.y = pack_bf16(vn[2], vn[3]); p0.z = pack_bf16(vn[4], vn[5]); p0.w = pack_bf16(vn[6], vn[7]);
+          p1.x = pack_bf16(vd[0], vd[1]); p1.y = pack_bf16(vd[2], vd[3]); p1.z = pack_bf16(vd[4], vd[5]); p1.w = pack_bf16(vd[6], vd[7]);
+          *reinterpret_cast<uint4*>(sVn + swz(v, half * 4 + j8)) = p0;
+          *reinterpret_cast<uint4*>(sVd + swz(v, half * 4 + j8)) = p1;
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->vn_ready);
+      if (states != nullptr) {
+        // the state on entry to this chunk, as the operand tile holds it (row v = 128 bf16)
+        uint4* dst = reinterpret_cast<uint4*>(states + ((static_cast<long long>(x) * N + n) * HD + v) * HD);
+#pragma unroll
+        for (int c16 = 0; c16 < 16; ++c16) {
+          uint4 pk;
+          pk.x = pack_bf16(S[c16 * 8 + 0], S[c16 * 8 + 1]); pk.y = pack_bf16(S[c16 * 8 + 2], S[c16 * 8 + 3]);
+          pk.z = pack_bf16(S[c16 * 8 + 4], S[c16 * 8 + 5]); pk.w = pack_bf16(S[c16 * 8 + 6], S[c16 * 8 + 7]);
+          dst[c16] = pk;
+        }
+      }
+      if (!math_wait(&bars->out_full, n & 1, sc, err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      // O^T row
+      __nv_bfloat16* orow = out + ((static_cast<long long>(b) * T + n * CH) * H + h) * HD + v;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t o1[32], o2[32];
+        tmem_ld_32x32b_x32(tmem + lane_addr + TM_O1 + half * 32, o1);
+        tmem_ld_32x32b_x32(tmem + lane_addr + TM_O2 + half * 32, o2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ii = 0; ii < 32; ++ii) {
+          const int i = half * 32 + ii;
+          const float o = scale * __expf(gs[i]) * __uint_as_float(o1[ii]) + __uint_as_float(o2[ii]);
+          if (n * CH + i < T) orow[static_cast<long long>(i) * H * HD] = __float2bfloat16(o);
+        }
+      }
+      // S^T <- e^{g_L} S^T + dS
+      const float dl = __expf(gl);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t d[32];
+        tmem_ld_32x32b_x32(tmem + lane_addr + TM_DS + q * 32, d);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) S[q * 32 + i] = fmaf(S[q * 32 + i], dl, __uint_as_float(d[i]));
+      }
+      write_state_row(sState, v, S);
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(&bars->s_ready); mbar_arrive(&bars->in_empty[s]); }
+    }
+    if (ok && final_state != nullptr) {
+      float* dst = final_state + static_cast<long long>(x) * HD * HD + v;
+#pragma unroll
+      for (int d = 0; d < HD; ++d) dst[d * HD] = S[d];
+    }
+  }
+  scan_epilogue(sc);
+}
+
+__global__ void __launch_bounds__(SCAN_THREADS, 1)
+gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tdo, const __grid_constant__ CUtensorMap tk,
+                    const __grid_constant__ CUtensorMap tw, const __grid_constant__ CUtensorMap tqg,
+                    const __grid_constant__ CUtensorMap tp, const float* __restrict__ gc,
+                    const float* __restrict__ d_final, float* __restrict__ dstates, float* __restrict__ d_initial, int T,
+                    int H, int Tp, int N, int* __restrict__ err) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  ScanCommon sc;
+  if (!scan_prologue(smem, err, sc)) return;
+  ScanBars* bars = sc.bars;
+  const uint32_t tmem = sc.tmem;
+  volatile int* abort_flag = sc.abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int x = blockIdx.x, b = x / H, h = x % H;
+  uint8_t* sState = smem + OFF_STATE;                    // G^T as bf16
+  uint8_t* sDvn = smem + OFF_VN;                         // -dVn^T as bf16
+  float* sG = reinterpret_cast<float*>(smem + OFF_G);
+  constexpr int TM_A = 0, TM_B = 64, TM_DD = 128;
+
+  if (warp == TMA_WARP) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tdo); tma_prefetch_desc(&tk); tma_prefetch_desc(&tw); tma_prefetch_desc(&tqg); tma_prefetch_desc(&tp);
+      for (int it = 0; it < N; ++it) {
+        const int n = N - 1 - it;
+        const int s = it & 1; const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&bars->in_empty[s], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); break; }
+        uint8_t* st = smem + s * STAGE;
+        uint64_t* bar = &bars->in_full[s];
+        mbar_expect_tx(bar, STAGE + CH * 4);
+        const int row = x * Tp + n * CH;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          tma_load_4d(st + B_DO + t * (CH * 128), &tdo, bar, t * 64, h, n * CH, b);
+          tma_load_2d(st + B_QG + t * (CH * 128), &tqg, bar, t * 64, row);
+          tma_load_4d(st + B_K + t * (CH * 128), &tk, bar, t * 64, h, n * CH, b);
+          tma_load_2d(st + B_W + t * (CH * 128), &tw, bar, t * 64, row);
+        }
+        tma_load_2d(st + B_P, &tp, bar, 0, row);
+        bulk_load_1d(sG + s * CH, gc + static_cast<long long>(x) * Tp + n * CH, CH * 4, bar);
+      }
+    }
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_a = make_idesc(128, 64, 1, 1, 1, 1);      // dO^T P: both operands MN-major
+      constexpr uint32_t idesc_b = make_idesc(128, 64, 1, 1, 0, 0);      // G^T K^T: both K-major
+      constexpr uint32_t idesc_dq = make_idesc(128, 128, 1, 1, 1, 1);    // dO^T Qg
+      constexpr uint32_t idesc_dw = make_idesc(128, 128, 1, 1, 0, 1);    // (-dVn^T) W
+      const uint32_t sa = smem_u32(sState), dva = smem_u32(sDvn);
+      for (int it = 0; it < N; ++it) {
+        const int s = it & 1; const uint32_t ph = (it >> 1) & 1;
+        const uint32_t st = smem_u32(smem + s * STAGE);
+        if (!mbar_wait(&bars->in_full[s], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); break; }
+        if (!mbar_wait(&bars->s_ready, it & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < CH / 16; ++kk) {
+          umma_bf16_ss(tmem + TM_A, make_sdesc_sw128(st + B_DO + kk * 2048, CH * 128, 1024),
+                       make_sdesc_sw128(st + B_P + kk * 2048, CH * 128, 1024), idesc_a, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t aoff = (kk >> 2) * (HD * 128) + (kk & 3) * 32, boff = (kk >> 2) * (CH * 128) + (kk & 3) * 32;
+          umma_bf16_ss(tmem + TM_B, make_sdesc_sw128(sa + aoff, 16, 1024), make_sdesc_sw128(st + B_K + boff, 16, 1024),
+                       idesc_b, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->acc_full);
+#pragma unroll
+        for (int kk = 0; kk < CH / 16; ++kk) {
+          umma_bf16_ss(tmem + TM_DD, make_sdesc_sw128(st + B_DO + kk * 2048, CH * 128, 1024),
+                       make_sdesc_sw128(st + B_QG + kk * 2048, CH * 128, 1024), idesc_dq, kk > 0 ? 1u : 0u);
+        }
+        if (!mbar_wait(&bars->vn_ready, it & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < CH / 16; ++kk) {
+          umma_bf16_ss(tmem + TM_DD, make_sdesc_sw128(dva + kk * 32, 16, 1024),
+                       make_sdesc_sw128(st + B_W + kk * 2048, CH * 128, 1024), idesc_dw, 1u);
+        }
+        umma_commit(&bars->out_full);
+      }
+    }
+  } else {
+    const int v = tid;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    float G[HD];
+    if (d_final != nullptr) {
+      const float* src = d_final + static_cast<long long>(x) * HD * HD + v;
+#pragma unroll
+      for (int d = 0; d < HD; ++d) G[d] = src[d * HD];
+    } else {
+#pragma unroll
+      for (int d = 0; d < HD; ++d) G[d] = 0.f;
+    }
+    write_state_row(sState, v, G);
+    fence_proxy_async();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bars->s_ready);
+    bool ok = true;
+    for (int it = 0; it < N && ok; ++it) {
+      const int n = N - 1 - it;
+      const int s = it & 1; const uint32_t ph = (it >> 1) & 1;
+      const float* gs = sG + s * CH;
+      {
+        // the gradient of this chunk's exit state, [Dk, Dv] with the value index contiguous
+        float* dst = dstates + (static_cast<long long>(x) * N + n) * HD * HD + v;
+#pragma unroll
+        for (int d = 0; d < HD; ++d) dst[d * HD] = G[d];
+      }
+      if (!math_wait(&bars->in_full[s], ph, sc, err, ERR_WAIT_FULL)) { ok = false; break; }
+      if (!math_wait(&bars->acc_full, it & 1, sc, err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const float gl = gs[CH - 1];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t a[32], bb[32];
+        tmem_ld_32x32b_x32(tmem + lane_addr + TM_A + half * 32, a);
+        tmem_ld_32x32b_x32(tmem + lane_addr + TM_B + half * 32, bb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j8 = 0; j8 < 4; ++j8) {
+          float nv[8];
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) {
+            const int j = half * 32 + j8 * 8 + jj;
+            nv[jj] = -(__uint_as_float(a[j8 * 8 + jj]) + __expf(gl - gs[j]) * __uint_as_float(bb[j8 * 8 + jj]));
+          }
+          uint4 p0;
+          p0.x = pack_bf16(nv[0], nv[1]); p0.y = pack_bf16(nv[2], nv[3]); p0.z = pack_bf16(nv[4], nv[5]); p0.w = pack_bf16(nv[6], nv[7]);
+          *reinterpret_cast<uint4*>(sDvn + swz(v, half * 4 + j8)) = p0;
+        }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->vn_ready);
+      if (!math_wait(&bars->out_full, it & 1, sc, err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const float dl = __expf(gl);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t d[32];
+        tmem_ld_32x32b_x32(tmem + lane_addr + TM_DD + q * 32, d);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) G[q * 32 + i] = fmaf(G[q * 32 + i], dl, __uint_as_float(d[i]));
+      }
+      write_state_row(sState, v, G);
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(&bars->s_ready); mbar_arrive(&bars->in_empty[s]); }
+    }
+    if (ok && d_initial != nullptr) {
+      float* dst = d_initial + static_cast<long long>(x) * HD * HD + v;
+#pragma unroll
+      for (int d = 0; d < HD; ++d) dst[d * HD] = G[d];
+    }
+  }
+  scan_epilogue(sc);
+}
+
+// A [B, T, H, 128] bf16 tensor with element strides (sb, st, sh), tiled [rows x 64 columns].
+static int make_bthd_map(CUtensorMap* m, const void* base, int B, int T, int H, long long sb, long long st, long long sh,
+                         int box_rows) {
+  const uint64_t dims[4] = {static_cast<uint64_t>(HD), static_cast<uint64_t>(H), static_cast<uint64_t>(T), static_cast<uint64_t>(B)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(sh) * 2, static_cast<uint64_t>(st) * 2, static_cast<uint64_t>(sb) * 2};
+  const uint32_t box[4] = {64, 1, static_cast<uint32_t>(box_rows), 1};
+  return make_tmap_nd(m, base, 4, dims, strides, box, 2, true);
+}
+
+static bool strides_ok(long long sb, long long st, long long sh) { return (sb % 8) == 0 && (st % 8) == 0 && (sh % 8) == 0; }
+
+}  // namespace gdn
+}  // namespace dewb
+
+// q, k, v: bf16 [B, T, H, 128] (unit stride along the head dimension; the other strides in elements: batch, token, head);
+// g, beta: fp32 [B, T, H] contiguous.  With X = B * H and Tp = T rounded up to 128:
+// gc fp32 [X, Tp]; W, U bf16 [X, Tp, 128]; P bf16 [X, Tp, 64]; Qg bf16 [X, Tp, 128] or null.
+extern "C" int dewb_gdn_prepare(const void* q, const void* k, const void* v, const float* g, const float* beta, float* gc,
+                                void* W, void* U, void* P, void* Qg, int B, int T, int H, long long q_sb, long long q_st,
+                                long long q_sh, long long k_sb, long long k_st, long long k_sh, long long v_sb,
+                                long long v_st, long long v_sh, float scale, int* err, void* stream_ptr) {
+  using namespace dewb::gdn;
+  if (B <= 0 || T <= 0 || H <= 0) return -3;
+  if (!strides_ok(q_sb, q_st, q_sh) || !strides_ok(k_sb, k_st, k_sh) || !strides_ok(v_sb, v_st, v_sh)) return -3;
+  const int Tp = (T + PT - 1) / PT * PT;
+  CUtensorMap tq, tk, tv;
+  int r;
+  if ((r = make_bthd_map(&tq, q, B, T, H, q_sb, q_st, q_sh, PT))) return 1000 + r;
+  if ((r = make_bthd_map(&tk, k, B, T, H, k_sb, k_st, k_sh, PT))) return 2000 + r;
+  if ((r = make_bthd_map(&tv, v, B, T, H, v_sb, v_st, v_sh, PT))) return 3000 + r;
+  cudaError_t e = cudaFuncSetAttribute(gdn_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREP_SMEM);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 grid(Tp / PT, B * H);
+  gdn_prepare_kernel<<<grid, PREP_THREADS, PREP_SMEM, reinterpret_cast<cudaStream_t>(stream_ptr)>>>(
+      tq, tk, tv, g, beta, gc, reinterpret_cast<__nv_bfloat16*>(W), reinterpret_cast<__nv_bfloat16*>(U),
+      reinterpret_cast<__nv_bfloat16*>(P), reinterpret_cast<__nv_bfloat16*>(Qg), T, H, Tp, scale, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out bf16 [B, T, H, 128] contiguous; initial / final_state fp32 [X, 128 (key), 128 (value)] (initial may be null);
+// states bf16 [X, N, 128 (value), 128 (key)] or null: the state on entry to each chunk, transposed.
+extern "C" int dewb_gdn_scan_fwd(const void* q, const void* k, const float* gc, const void* W, const void* U, const void* P,
+                                 const float* initial, void* out, float* final_state, void* states, int B, int T, int H,
+                                 int Tp, long long q_sb, long long q_st, long long q_sh, long long k_sb, long long k_st,
+                                 long long k_sh, float scale, int* err, void* stream_ptr) {
+  using namespace dewb::gdn;
+  if (B <= 0 || T <= 0 || H <= 0 || Tp % PT != 0 || Tp < T) return -3;
+  if (!strides_ok(q_sb, q_st, q_sh) || !strides_ok(k_sb, k_st, k_sh)) return -3;
+  const int N = (T + CH - 1) / CH;
+  const uint64_t rows = static_cast<uint64_t>(B) * H * Tp;
+  CUtensorMap tq, tk, tw, tu, tp;
+  int r;
+  if ((r = make_bthd_map(&tq, q, B, T, H, q_sb, q_st, q_sh, CH))) return 1000 + r;
+  if ((r = make_bthd_map(&tk, k, B, T, H, k_sb, k_st, k_sh, CH))) return 2000 + r;
+  if ((r = dewb::make_tmap_2d(&tw, W, rows, HD, HD, CH, 64, 2, true))) return 3000 + r;
+  if ((r = dewb::make_tmap_2d(&tu, U, rows, HD, HD, CH, 64, 2, true))) return 4000 + r;
+  if ((r = dewb::make_tmap_2d(&tp, P, rows, CH, CH, CH, 64, 2, true))) return 5000 + r;
+  cudaError_t e = cudaFuncSetAttribute(gdn_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  gdn_scan_fwd_kernel<<<B * H, SCAN_THREADS, SCAN_SMEM, reinterpret_cast<cudaStream_t>(stream_ptr)>>>(
+      tq, tk, tw, tu, tp, gc, initial, reinterpret_cast<__nv_bfloat16*>(out), final_state,
+      reinterpret_cast<__nv_bfloat16*>(states), T, H, Tp, N, scale, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// d_out bf16 [B, T, H, 128] (strides in elements); d_final fp32 [X, 128, 128] or null; dstates fp32 [X, N, 128 (key),
+// 128 (value)]: the gradient of each chunk's exit state; d_initial fp32 [X, 128, 128].
+extern "C" int dewb_gdn_scan_bwd(const void* d_out, const void* k, const float* gc, const void* W, const void* P,
+                                 const void* Qg, const float* d_final, float* dstates, float* d_initial, int B, int T,
+                                 int H, int Tp, long long do_sb, long long do_st, long long do_sh, long long k_sb,
+                                 long long k_st, long long k_sh, int* err, void* stream_ptr) {
+  using namespace dewb::gdn;
+  if (B <= 0 || T <= 0 || H <= 0 || Tp % PT != 0 || Tp < T) return -3;
+  if (!strides_ok(do_sb, do_st, do_sh) || !strides_ok(k_sb, k_st, k_sh)) return -3;
+  const int N = (T + CH - 1) / CH;
+  const uint64_t rows = static_cast<uint64_t>(B) * H * Tp;
+  CUtensorMap tdo, tk, tw, tqg, tp;
+  int r;
+  if ((r = make_bthd_map(&tdo, d_out, B, T, H, do_sb, do_st, do_sh, CH))) return 1000 + r;
+  if ((r = make_bthd_map(&tk, k, B, T, H, k_sb, k_st, k_sh, CH))) return 2000 + r;
+  if ((r = dewb::make_tmap_2d(&tw, W, rows, HD, HD, CH, 64, 2, true))) return 3000 + r;
+  if ((r = dewb::make_tmap_2d(&tqg, Qg, rows, HD, HD, CH, 64, 2, true))) return 4000 + r;
+  if ((r = dewb::make_tmap_2d(&tp, P, rows, CH, CH, CH, 64, 2, true))) return 5000 + r;
+  cudaError_t e = cudaFuncSetAttribute(gdn_scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  gdn_scan_bwd_kernel<<<B * H, SCAN_THREADS, SCAN_SMEM, reinterpret_cast<cudaStream_t>(stream_ptr)>>>(
+      tdo, tk, tw, tqg, tp, gc, d_final, dstates, d_initial, T, H, Tp, N, err);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -99,8 +99,13 @@ def gated_delta_rule_chunked(q, k, v, g, beta, initial_state=None, scale: Option
 
 
 def chunk_gated_delta_rule(q, k, v, g, beta, initial_state=None, scale=None, chunk: int = CHUNK_SIZE):
-    """Public entry: chunked on any device (dense chunk products on the GPU run through cuBLAS batched GEMMs until the
-    tcgen05 chunk kernel takes them)."""
+    """Public entry.  CUDA tensors with 128-wide keys and values run the sm_100a kernels (``ops/gdn.py``: prepare, forward
+    scan, reverse scan on tcgen05); other head sizes on a GPU and every CPU call use the differentiable chunked form."""
+    if q.is_cuda and chunk == CHUNK_SIZE:
+        from . import gdn
+        if gdn.kernel_available(q, v):
+            o, S = gdn.gated_delta_rule(q, k, v, g, beta, initial_state, scale)
+            return o.to(v.dtype), S
     return gated_delta_rule_chunked(q, k, v, g, beta, initial_state, scale, chunk)
 
 

@@ -158,6 +158,33 @@ def bench_attention(out, peaks, flush, iters=10, shapes=None, kernels=("sm100_fl
         _row(out, **row)
 
 
+def bench_gdn(out, peaks, flush, iters=10, shapes=None):
+    """Gated delta rule, forward and forward + backward, on the reference's receipt shapes
+    (src/dew/nn/kernels/fla_gdn.py:624-626: 1 x 4096, 32 and 48 value heads of 128) and the hybrid configuration's layer."""
+    from ..ops import scan
+    for B, T, H in shapes or [(1, 4096, 32), (1, 4096, 48), (2, 8192, 16)]:
+        q = torch.nn.functional.normalize(torch.randn(B, T, H, 128, device="cuda"), dim=-1).to(torch.bfloat16).requires_grad_()
+        k = torch.nn.functional.normalize(torch.randn(B, T, H, 128, device="cuda"), dim=-1).to(torch.bfloat16).requires_grad_()
+        v = torch.randn(B, T, H, 128, device="cuda").to(torch.bfloat16).requires_grad_()
+        g = (-torch.rand(B, T, H, device="cuda") * 0.3).requires_grad_()
+        beta = torch.rand(B, T, H, device="cuda").requires_grad_()
+        o, _ = scan.chunk_gated_delta_rule(q, k, v, g, beta)
+        do = torch.randn_like(o)
+        o.backward(do)
+        L.check_status()
+        t_f = device_time(lambda: scan.chunk_gated_delta_rule(q, k, v, g, beta), iters=iters, flush=flush)
+        t_fb = device_time(lambda: scan.chunk_gated_delta_rule(q, k, v, g, beta)[0].backward(do), iters=iters, flush=flush)
+        with torch.no_grad():
+            from ..ops import gdn
+            scale = 128 ** -0.5
+            t_p = device_time(lambda: gdn.prepare_cuda(q, k, v, g, beta, scale, False), iters=iters, flush=flush)
+            gc, W, U, P, _ = gdn.prepare_cuda(q, k, v, g, beta, scale, False)
+            t_s = device_time(lambda: gdn.scan_fwd_cuda(q, k, gc, W, U, P, scale, None, False), iters=iters, flush=flush)
+        L.check_status()
+        _row(out, kernel="gdn", B=B, T=T, H=H, fwd_ms=t_f.median_ms, fwd_bwd_ms=t_fb.median_ms, prepare_ms=t_p.median_ms,
+             scan_fwd_ms=t_s.median_ms)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=None)
@@ -185,6 +212,8 @@ def main(argv=None):
         bench_rows(out, peaks, flush, iters=args.iters)
     if "attention" in only:
         bench_attention(out, peaks, flush, iters=args.iters)
+    if "gdn" in only:
+        bench_gdn(out, peaks, flush, iters=args.iters)
 
 
 if __name__ == "__main__":

@@ -390,6 +390,59 @@ def test_short_conv_forward_backward(B, T, C, K, act, bias):
         assert rel_err(b.grad, bf.grad) <= 1e-2
 
 
+def _gdn_inputs(B, T, H, seed, with_state):
+    torch.manual_seed(seed)
+    q = torch.nn.functional.normalize(torch.randn(B, T, H, 128, device=DEV), dim=-1).to(torch.bfloat16)
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, 128, device=DEV), dim=-1).to(torch.bfloat16)
+    v = torch.randn(B, T, H, 128, device=DEV).to(torch.bfloat16)
+    g = -torch.rand(B, T, H, device=DEV) * 0.3
+    beta = torch.rand(B, T, H, device=DEV)
+    s0 = torch.randn(B, H, 128, 128, device=DEV) * 0.1 if with_state else None
+    return q, k, v, g, beta, s0
+
+
+@pytest.mark.parametrize("B,T,H,with_state", [(1, 64, 1, False), (2, 300, 3, True), (1, 1024, 2, False)])
+def test_gdn_kernel_stages_match_their_restatements(B, T, H, with_state):
+    """Each of the three gated-delta-rule kernels against the PyTorch restatement of the same stage (fp32)."""
+    from dew_b200.ops import gdn
+    q, k, v, g, beta, s0 = _gdn_inputs(B, T, H, T, with_state)
+    scale = 128 ** -0.5
+    gc, W, U, P, Qg = gdn.prepare_cuda(q, k, v, g, beta, scale, True)
+    rgc, rW, rU, rP, rQg = gdn.prepare_reference(q.float(), k.float(), v.float(), g, beta, scale)
+    assert torch.allclose(gc, rgc, atol=1e-4)
+    for got, ref in ((W, rW), (U, rU), (P, rP), (Qg, rQg)):
+        assert rel_err(got, ref) <= 2 * bf16_floor(ref) + 1e-3
+    # the scans, fed the kernel's own (bf16) intermediates so that only the scan is under test
+    o, final, states = gdn.scan_fwd_cuda(q, k, gc, W, U, P, scale, s0, True)
+    ro, rfinal, rstates = gdn.scan_fwd_reference(q.float(), k.float(), gc, W.float(), U.float(), P.float(), scale, s0, True)
+    assert rel_err(o, ro) <= 2e-2
+    assert rel_err(final, rfinal) <= 2e-2
+    assert rel_err(states, rstates) <= 2e-2
+    do = torch.randn(B, T, H, 128, device=DEV).to(torch.bfloat16)
+    dfin = torch.randn(B * H, 128, 128, device=DEV) * 0.1 if with_state else None
+    ds, dinit = gdn.scan_bwd_cuda(do, k, gc, W, P, Qg, dfin)
+    rds, rdinit = gdn.scan_bwd_reference(do.float(), k.float(), gc, W.float(), P.float(), Qg.float(), dfin)
+    assert rel_err(ds, rds) <= 2e-2
+    assert rel_err(dinit, rdinit) <= 2e-2
+
+
+@pytest.mark.parametrize("B,T,H,with_state", [(2, 200, 2, True), (1, 512, 4, False)])
+def test_gdn_forward_backward_against_recurrent_oracle(B, T, H, with_state):
+    from dew_b200.ops import scan
+    q, k, v, g, beta, s0 = _gdn_inputs(B, T, H, 100 + T, with_state)
+    leaves = [t.clone().requires_grad_() for t in (q, k, v, g, beta)] + ([s0.clone().requires_grad_()] if with_state else [])
+    o, S = scan.chunk_gated_delta_rule(*leaves[:5], initial_state=leaves[5] if with_state else None)
+    do = torch.randn_like(o)
+    dS = torch.randn_like(S) * 0.1
+    torch.autograd.backward((o, S), (do, dS))
+    ref_leaves = [t.detach().float().requires_grad_() for t in leaves]
+    ro, rS = scan.gated_delta_rule_chunked(*ref_leaves[:5], initial_state=ref_leaves[5] if with_state else None)
+    torch.autograd.backward((ro, rS), (do.float(), dS))
+    assert rel_err(o, ro) <= 2e-2 and rel_err(S, rS) <= 2e-2
+    for name, a, b in zip(("dq", "dk", "dv", "dg", "dbeta", "ds0"), leaves, ref_leaves):
+        assert rel_err(a.grad, b.grad) <= 4e-2, (name, rel_err(a.grad, b.grad))
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 512, 256), (1000, 264, 1024), (4096, 4096, 4096)])
 def test_fp8_rowwise_gemm(M, N, K):
     from dew_b200.ops import fp8
