@@ -144,7 +144,7 @@ def _chunk_local(qc, kc, vc, gr, bc, S0, scale: float):
     return O, S1
 
 
-def chunk_local_grads(q, k, v, g, beta, states, dstates, do, scale: float, slab_chunks: int = 4096):
+def chunk_local_grads(q, k, v, g, beta, states, dstates, do, scale: float, slab_chunks: int = 4096, analytic: bool = True):
     """Gradients of q, k, v, g, beta given every chunk's entry state and exit-state gradient; fp32, batched in slabs of
     chunks so the temporaries stay bounded."""
     B, T, H, Dk = q.shape
@@ -164,15 +164,72 @@ def chunk_local_grads(q, k, v, g, beta, states, dstates, do, scale: float, slab_
     Y = X * N
     for a in range(0, Y, slab_chunks):
         sl = slice(a, min(Y, a + slab_chunks))
-        ins = [t[sl].detach().requires_grad_(True) for t in (qc, kc, vc, gr, bc)]
-        with torch.enable_grad():
-            O, S1 = _chunk_local(*ins, S0[sl].to(f), scale)
-            res = torch.autograd.grad((O, S1), ins, (doc[sl], dS1[sl].to(f)))
+        if analytic:
+            res = _chunk_local_analytic(qc[sl], kc[sl], vc[sl], gr[sl], bc[sl], S0[sl].to(f), doc[sl], dS1[sl].to(f), scale)
+        else:
+            ins = [t[sl].detach().requires_grad_(True) for t in (qc, kc, vc, gr, bc)]
+            with torch.enable_grad():
+                O, S1 = _chunk_local(*ins, S0[sl].to(f), scale)
+                res = torch.autograd.grad((O, S1), ins, (doc[sl], dS1[sl].to(f)))
         for dst, r in zip(grads, res):
             dst[sl] = r
     back = lambda x, D: x.reshape(X, Tc, D)[:, :T].reshape(B, H, T, D).permute(0, 2, 1, 3)
     back1 = lambda x: x.reshape(X, Tc)[:, :T].reshape(B, H, T).permute(0, 2, 1)
     return back(grads[0], Dk), back(grads[1], Dk), back(grads[2], Dv), back1(grads[3]), back1(grads[4])
+
+
+def _chunk_local_analytic(qc, kc, vc, gr, bc, S0, dO, dS1, scale: float):
+    """Closed-form gradients of one chunk (batched over chunks), the same quantities ``torch.autograd`` gives for
+    ``_chunk_local``.  With ``M = I + A``, ``T = M^-1``, ``W = T (beta e^g K)``, ``U = T (beta V)``:
+
+        dVn = P^T dO + Kd dS1                      dW = -dVn S0^T,  dU = dVn
+        dQ  = scale e^g (dO S0^T) + (dP o D) K     dP = tril(dO Vn^T) (scale folded into ``Gt = scale dP o D``)
+        dKt = T^T dW, dVt = T^T dU                 dA = -strict(dKt W^T + dVt U^T)
+        dK  = Gt^T Q + e^{g_L - g} (Vn dS1^T) + beta e^g dKt + Bt K + Bt^T K      with Bt = dA o (beta_i D_ij)
+        dV  = beta dVt
+    and the decay / write-strength gradients collect the row sums of the same products."""
+    gc = gr.cumsum(-1)
+    eg = gc.exp()
+    gl = gc[..., -1:]
+    diff = gc[..., :, None] - gc[..., None, :]
+    incl = torch.tril(torch.ones(CHUNK, CHUNK, dtype=torch.bool, device=qc.device))
+    strict = torch.tril(torch.ones(CHUNK, CHUNK, dtype=torch.bool, device=qc.device), -1)
+    zero = torch.zeros_like(diff)
+    D = torch.where(incl, torch.exp(torch.where(incl, diff, zero)), zero)
+    kk = kc @ kc.transpose(-1, -2)
+    kkD = torch.where(strict, kk * D, zero)
+    A = bc[..., None] * kkD
+    eye = torch.eye(CHUNK, dtype=qc.dtype, device=qc.device)
+    Tm = torch.linalg.solve_triangular(eye + A, eye.expand_as(A).contiguous(), upper=False)
+    Kt = kc * (bc * eg)[..., None]
+    W, U = Tm @ Kt, Tm @ (vc * bc[..., None])
+    Vn = U - W @ S0
+    qk = qc @ kc.transpose(-1, -2)
+    P = scale * qk * D
+    tail = (gl - gc).exp()                                    # e^{g_L - g}
+    Kd = kc * tail[..., None]
+    dVn = P.transpose(-1, -2) @ dO + Kd @ dS1
+    S0t = S0.transpose(-1, -2)
+    dQ1 = (scale * eg)[..., None] * (dO @ S0t)
+    Gt = scale * torch.where(incl, dO @ Vn.transpose(-1, -2), zero) * D
+    dQ = dQ1 + Gt @ kc
+    dKd = Vn @ dS1.transpose(-1, -2)
+    dW = -(dVn @ S0t)
+    Tt = Tm.transpose(-1, -2)
+    dKt, dVt = Tt @ dW, Tt @ dVn
+    dA = -torch.where(strict, dKt @ W.transpose(-1, -2) + dVt @ U.transpose(-1, -2), zero)
+    Bt = dA * bc[..., None] * D
+    dK = Gt.transpose(-1, -2) @ qc + tail[..., None] * dKd + (bc * eg)[..., None] * dKt + Bt @ kc + Bt.transpose(-1, -2) @ kc
+    dV = bc[..., None] * dVt
+    dbeta = (dVt * vc).sum(-1) + eg * (dKt * kc).sum(-1) + (dA * kkD).sum(-1)
+    E = dA * A
+    GP = Gt * qk                                              # dP o P
+    kdk = (dKd * Kd).sum(-1)
+    dgc = (dQ1 * qc).sum(-1) + GP.sum(-1) - GP.sum(-2) - kdk + (dKt * Kt).sum(-1) + E.sum(-1) - E.sum(-2)
+    dgl = kdk.sum(-1) + gl[..., 0].exp() * (dS1 * S0).sum((-1, -2))
+    dgc = torch.cat([dgc[..., :-1], (dgc[..., -1] + dgl)[..., None]], -1)
+    dg = dgc.flip(-1).cumsum(-1).flip(-1)
+    return dQ, dK, dV, dg, dbeta
 
 
 # ---------------------------------------------------------------------------------------------------------------
