@@ -21,7 +21,12 @@ from .layers import Linear, declare
 from .mlp import SwiGLU
 
 
+_SELF_GROUP = "self"        # marks a token exchange that spans this rank only, whatever process group exists
+
+
 class Router(nn.Module):
+    use_kernels = True        # False: PyTorch top-k (the comparison arm of the tests)
+
     def __init__(self, features: int, mix, dtype=None, device=None):
         super().__init__()
         self.mix = mix
@@ -37,6 +42,9 @@ class Router(nn.Module):
         """``x2 [T, d]`` -> (weights [T, k] fp32, expert ids [T, k], scores [T, E] fp32)."""
         mix = self.mix
         logits = F.linear(x2.float(), self.weight.float())
+        if logits.is_cuda and mix.experts <= 256 and mix.top_k <= 16 and self.use_kernels:
+            from ..ops.routing import route
+            return route(logits, self.expert_bias, mix.top_k, mix.score_function, mix.norm_topk_prob, mix.scaling)
         scores = torch.softmax(logits, -1) if mix.score_function == "softmax" else torch.sigmoid(logits)
         select = scores + self.expert_bias if self.expert_bias is not None else scores     # bias steers selection only
         _, ids = torch.topk(select, mix.top_k, dim=-1)
@@ -89,6 +97,8 @@ class ExpertMLP(nn.Module):
 
 
 class SparseMLP(nn.Module):
+    use_kernels = True        # False: routing and dispatch / combine by PyTorch index ops (the comparison arm of the tests)
+
     def __init__(self, features: int, mix, dense_hidden: int, init_std: Optional[float] = None, dtype=None, device=None):
         super().__init__()
         self.mix = mix
@@ -100,12 +110,14 @@ class SparseMLP(nn.Module):
         self.shared_gate = Linear(features, 1, axes=("embed", None), dtype=dtype, device=device) if (mix.shared_gate and mix.shared_features) else None
         self.last: Dict[str, Any] = {}
         self.ep = None            # set by dew_b200.parallel.ep.ExpertParallel when the experts are sharded over ranks
+        self._exchange = None     # this layer's single-rank token exchange (created on first use on a GPU)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         mix = self.mix
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         T = x2.shape[0]
+        self.router.use_kernels = self.use_kernels
         w, ids, scores = self.router(x2)
         if mix.capacity_factor is not None:
             cap = max(int(math.ceil(T * mix.top_k / mix.experts * mix.capacity_factor)), int(mix.capacity_factor))
@@ -117,6 +129,12 @@ class SparseMLP(nn.Module):
         self.last = {"counts": counts, "balance_loss": mix.experts * (frac * scores.mean(0)).sum()}
         if self.ep is not None:
             y = self.ep.dispatch_compute_combine(self, x2, w, ids)
+        elif x2.is_cuda and x2.dtype == torch.bfloat16 and mix.experts <= 256 and mix.top_k <= 16 and self.use_kernels:
+            # one rank: the same device-planned dispatch / combine kernels, with this rank as its own only peer
+            from ..parallel.ep import TokenExchange, exchange_experts
+            if self._exchange is None:
+                self._exchange = TokenExchange(mix.experts, _SELF_GROUP)
+            y = exchange_experts(self._exchange, self.experts, x2, w, ids)
         else:
             layout = G.group_layout(ids, mix.experts)
             xs = G.permute(x2, layout, mix.top_k)

@@ -17,12 +17,15 @@ count all-gather (:1168), capacity factor (docs/concepts/moe.md:95).
 """
 from __future__ import annotations
 
+import ctypes
 from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
 
 from ..ops import grouped as G
+from ..ops import library as L
+from .symm import SymmetricBuffer
 
 
 class _AllToAll(torch.autograd.Function):
@@ -46,11 +49,201 @@ def all_to_all_rows(x, send_splits, recv_splits, group=None):
     return _AllToAll.apply(x, list(send_splits), list(recv_splits), group)
 
 
+class _LocalBuffer:
+    """Plain device memory with the interface of ``SymmetricBuffer``, for an exchange that spans one rank."""
+
+    def __init__(self, numel: int, dtype, device):
+        self.tensor = torch.zeros(numel, dtype=dtype, device=device)
+
+    def ptr_array(self, offset_bytes: int = 0):
+        return (ctypes.c_ulonglong * 8)(*([self.tensor.data_ptr() + offset_bytes] + [0] * 7))
+
+
+class ExchangePlan:
+    """Where every (token, choice) pair goes: destination rank and row, plus this rank's layout as an owner."""
+
+    def __init__(self, dest_rank, dest_pos, layout, info, tokens: int, top_k: int):
+        self.dest_rank, self.dest_pos, self.layout, self.info = dest_rank, dest_pos, layout, info
+        self.tokens, self.top_k = tokens, top_k
+
+
+class TokenExchange:
+    """Dispatch and combine of expert rows through peer memory, planned on the device (no host synchronisation).
+
+    ``plan``  ranks every pair inside its expert, exchanges the per-expert counts through symmetric memory and derives
+              the placement every rank agrees on;
+    ``push``  stores token rows straight into the owners' expert-sorted receive buffers (peer stores) and returns this
+              rank's received rows;
+    ``pull``  loads each token's result rows from the owners' output buffers (peer loads) and sums them with the
+              routing weights.
+    One rank runs the same kernels with itself as the only peer.  Shapes must be the same on every rank of the group.
+    The receive buffer holds ``capacity_factor`` times a rank's fair share of rows (all of them with one rank); pairs
+    past its end are dropped and the device status word reports it.
+    Kernels: ``csrc/kernels/moe_sm100.cu``."""
+
+    SLOT_COUNTS, SLOT_READY, SLOT_PUSHED, SLOT_OUT, SLOT_PULLED = 0, 1, 2, 3, 4
+
+    def __init__(self, experts: int, group: Optional[dist.ProcessGroup] = None, capacity_factor: float = 2.0, wait_limit_s: float = 20.0):
+        local = isinstance(group, str) and group == "self"           # a one-rank exchange inside a larger job
+        self.group = None if local else group
+        self.world = dist.get_world_size(group) if (dist.is_initialized() and not local) else 1
+        self.rank = dist.get_rank(group) if (dist.is_initialized() and not local) else 0
+        self.local = local
+        if experts % self.world:
+            raise ValueError(f"{experts} experts do not divide over {self.world} ranks")
+        self.experts, self.per = experts, experts // self.world
+        self.capacity_factor = capacity_factor
+        self.limit_ns = int(wait_limit_s * 1e9)
+        self.seq = 0
+        self.last_pull = 0
+        self.rows_cap = 0
+        self.features = 0
+        self.recv = self.out = self.counts = self.flags = None
+
+    def _ensure(self, pairs: int, features: int, device) -> None:
+        share = pairs if self.world == 1 else int(pairs * self.capacity_factor)
+        need = G.padded_rows(share, self.per)
+        if self.recv is not None and need <= self.rows_cap and features == self.features:
+            return
+        self.rows_cap, self.features = need, features
+        make = (lambda n, dt: _LocalBuffer(n, dt, device)) if self.world == 1 else \
+            (lambda n, dt: SymmetricBuffer(n, dt, device, self.group, zero=True))
+        self.recv, self.out = make(need * features, torch.bfloat16), make(need * features, torch.bfloat16)
+        if self.counts is None:
+            self.counts, self.flags = make(max(64, self.experts), torch.int32), make(64, torch.int32)
+            self.counter = torch.zeros(4, dtype=torch.int32, device=device)
+
+    def _signal(self, slot: int) -> None:
+        if self.world > 1:
+            L.check(L.load().dewb_signal_flags(self.flags.ptr_array(), ctypes.c_int(slot), ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                               ctypes.c_uint(self.seq), L.stream_ptr()), "signal_flags")
+
+    def _wait(self, slot: int, seq: int) -> None:
+        if self.world > 1:
+            L.check(L.load().dewb_wait_flags(L.ptr(self.flags.tensor), ctypes.c_int(slot), ctypes.c_int(self.world), ctypes.c_uint(seq),
+                                             ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.flags.tensor.device)), L.stream_ptr()),
+                    "wait_flags")
+
+    def plan(self, ids: torch.Tensor, features: int) -> ExchangePlan:
+        T, k = ids.shape
+        pairs = T * k
+        dev = ids.device
+        L.ensure_device(ids)
+        self._ensure(pairs, features, dev)
+        lib = L.load()
+        ids32 = ids.to(torch.int32).contiguous().reshape(-1)
+        rank_in_group = torch.empty(pairs, dtype=torch.int32, device=dev)
+        self.seq += 1
+        L.check(lib.dewb_moe_rank(L.ptr(ids32), ctypes.c_int(pairs), ctypes.c_int(self.experts), L.ptr(rank_in_group),
+                                  L.ptr(self.counts.tensor), L.stream_ptr()), "moe_rank")
+        self._signal(self.SLOT_COUNTS)
+        dest_rank = torch.empty(pairs, dtype=torch.int32, device=dev)
+        dest_pos = torch.empty(pairs, dtype=torch.int32, device=dev)
+        offsets = torch.empty(self.per + 1, dtype=torch.int32, device=dev)
+        local_counts = torch.empty(self.per, dtype=torch.int32, device=dev)
+        tile_group = torch.empty(self.rows_cap // 128, dtype=torch.int32, device=dev)
+        info = torch.empty(2, dtype=torch.int32, device=dev)
+        L.check(lib.dewb_moe_plan(self.counts.ptr_array(), L.ptr(self.flags.tensor), ctypes.c_int(self.SLOT_COUNTS), ctypes.c_uint(self.seq),
+                                  ctypes.c_ulonglong(self.limit_ns), L.ptr(ids32), L.ptr(rank_in_group), ctypes.c_int(pairs),
+                                  ctypes.c_int(self.experts), ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(self.rows_cap),
+                                  L.ptr(dest_rank), L.ptr(dest_pos), L.ptr(offsets), L.ptr(local_counts), L.ptr(tile_group), L.ptr(info),
+                                  L.ptr(L.status(dev)), L.stream_ptr()), "moe_plan")
+        L.count_launches(2)
+        layout = G.GroupLayout(None, local_counts, offsets, tile_group, self.rows_cap)
+        return ExchangePlan(dest_rank, dest_pos, layout, info, T, k)
+
+    def push(self, x: torch.Tensor, plan: ExchangePlan, pair_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``x [T, d]`` bf16 -> this rank's received rows ``[rows_cap, d]`` (expert-sorted, padding rows zero)."""
+        T, d = x.shape
+        assert d == self.features and x.dtype == torch.bfloat16
+        L.ensure_device(x)
+        self.seq += 1
+        self.recv.tensor.zero_()
+        self._signal(self.SLOT_READY)
+        ps = None if pair_scale is None else pair_scale.float().contiguous()
+        L.check(L.load().dewb_moe_push(L.ptr(x.contiguous()), L.ptr(ps), L.ptr(plan.dest_rank), L.ptr(plan.dest_pos), self.recv.ptr_array(),
+                                       None, self.flags.ptr_array(), L.ptr(self.flags.tensor), ctypes.c_int(self.SLOT_READY),
+                                       ctypes.c_int(self.SLOT_PUSHED), ctypes.c_uint(self.seq), ctypes.c_ulonglong(self.limit_ns),
+                                       L.ptr(self.counter), ctypes.c_int(T), ctypes.c_int(d), ctypes.c_int(plan.top_k), ctypes.c_int(self.rank),
+                                       ctypes.c_int(self.world), ctypes.c_int(0), L.ptr(L.status(x.device)), L.stream_ptr()), "moe_push")
+        L.count_launches()
+        self._wait(self.SLOT_PUSHED, self.seq)
+        return self.recv.tensor.view(self.rows_cap, d).clone()
+
+    def pull(self, rows: torch.Tensor, plan: ExchangePlan, weights: Optional[torch.Tensor] = None, keep_rows: bool = False):
+        """``rows [rows_cap, d]`` on every owner -> ``out [T, d]``: each token's k rows, weighted and summed (fp32 accumulate)."""
+        d = rows.shape[1]
+        T, k = plan.tokens, plan.top_k
+        L.ensure_device(rows)
+        self.seq += 1
+        if self.last_pull:
+            self._wait(self.SLOT_PULLED, self.last_pull)          # nobody still reads the previous contents of `out`
+        self.out.tensor.view(self.rows_cap, d).copy_(rows)
+        self._signal(self.SLOT_OUT)
+        out = torch.empty(T, d, dtype=torch.bfloat16, device=rows.device)
+        gathered = torch.empty(T * k, d, dtype=torch.bfloat16, device=rows.device) if keep_rows else None
+        w = None if weights is None else weights.float().contiguous()
+        L.check(L.load().dewb_moe_pull(self.out.ptr_array(), L.ptr(w), L.ptr(plan.dest_rank), L.ptr(plan.dest_pos), L.ptr(out), L.ptr(gathered),
+                                       self.flags.ptr_array(), L.ptr(self.flags.tensor), ctypes.c_int(self.SLOT_OUT), ctypes.c_int(self.SLOT_PULLED),
+                                       ctypes.c_uint(self.seq), ctypes.c_ulonglong(self.limit_ns), L.ptr(self.counter[1:]), ctypes.c_int(T),
+                                       ctypes.c_int(d), ctypes.c_int(k), ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                       L.ptr(L.status(rows.device)), L.stream_ptr()), "moe_pull")
+        L.count_launches()
+        self.last_pull = self.seq
+        return out, gathered
+
+
+class _PushRows(torch.autograd.Function):
+    """Dispatch; its backward is a combine with unit weights (the sum of a token's k row gradients)."""
+
+    @staticmethod
+    def forward(ctx, x, exchange, plan):
+        ctx.exchange, ctx.plan = exchange, plan
+        return exchange.push(x, plan)
+
+    @staticmethod
+    def backward(ctx, d_rows):
+        dx, _ = ctx.exchange.pull(d_rows.contiguous(), ctx.plan, None)
+        return dx, None, None
+
+
+class _PullRows(torch.autograd.Function):
+    """Combine; its backward dispatches ``w[t, j] * dy[t]`` to the owners and takes ``dw[t, j] = <dy[t], row(t, j)>``."""
+
+    @staticmethod
+    def forward(ctx, rows, weights, exchange, plan):
+        ctx.exchange, ctx.plan = exchange, plan
+        out, gathered = exchange.pull(rows, plan, weights, keep_rows=weights.requires_grad)
+        ctx.save_for_backward(weights, gathered)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        weights, gathered = ctx.saved_tensors
+        plan = ctx.plan
+        dy = dy.contiguous()
+        d_rows = ctx.exchange.push(dy, plan, pair_scale=weights.reshape(-1))
+        dw = None
+        if gathered is not None:
+            dw = (gathered.view(plan.tokens, plan.top_k, -1).float() * dy.float().unsqueeze(1)).sum(-1).to(weights.dtype)
+        return d_rows, dw, None, None
+
+
+def exchange_experts(exchange: TokenExchange, experts, x2: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """plan -> dispatch -> grouped expert MLP on the received rows -> combine, all on this library's kernels."""
+    plan = exchange.plan(ids, x2.shape[1])
+    rows = _PushRows.apply(x2, exchange, plan)
+    out_rows = experts(rows, plan.layout)
+    return _PullRows.apply(out_rows, weights.float(), exchange, plan)
+
+
 class ExpertParallel:
-    def __init__(self, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, fused: bool = True, capacity_factor: float = 2.0):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.fused, self.capacity_factor = fused, capacity_factor
+        self.exchange: Optional[TokenExchange] = None        # one set of symmetric buffers shared by every sparse layer
 
     # ------------------------------------------------------------------ sharding the experts of a model
     def shard(self, model) -> None:
@@ -72,6 +265,11 @@ class ExpertParallel:
 
     # ------------------------------------------------------------------ the exchange
     def dispatch_compute_combine(self, mlp, x2: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        if x2.is_cuda and x2.dtype == torch.bfloat16 and L.use_cuda(x2) and self.fused:
+            # device-planned exchange over peer memory (TokenExchange); the path below is the NCCL / gloo form of the same protocol
+            if self.exchange is None:
+                self.exchange = TokenExchange(mlp.mix.experts, self.group, self.capacity_factor)
+            return exchange_experts(self.exchange, mlp.experts, x2, weights, ids)
         W, E = self.world, mlp.mix.experts
         per = E // W
         T, k = ids.shape

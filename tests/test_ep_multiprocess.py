@@ -37,3 +37,20 @@ def test_moe_lm_trains_under_fsdp_with_expert_parallel_units():
         assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (one, two)
     assert abs(one["digest"] - two["digest"]) < 1e-3 * one["digest"], (one["digest"], two["digest"])
     assert two["experts"] == one["experts"]              # the export concatenates every rank's experts
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_expert_parallel_two_gpus_peer_memory_exchange():
+    """Dispatch by peer stores into the owners' expert-sorted buffers and combine by peer loads (one kernel each), against
+    the NCCL all-to-all form of the same layer; three calls in a row so that buffers and flags are reused."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    worker = os.path.join(os.path.dirname(__file__), "workers", "ep_gpu_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29661", worker]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2"))
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    assert max(r["errs"]) < 5e-2, r

@@ -390,6 +390,78 @@ def test_short_conv_forward_backward(B, T, C, K, act, bias):
         assert rel_err(b.grad, bf.grad) <= 1e-2
 
 
+@pytest.mark.parametrize("T,E,k,fn,norm,with_bias", [(1000, 64, 6, "softmax", True, False), (333, 8, 2, "softmax", False, True),
+                                                      (512, 160, 8, "sigmoid", True, True), (64, 256, 1, "softmax", False, False)])
+def test_moe_route_kernel(T, E, k, fn, norm, with_bias):
+    from dew_b200.ops.routing import route, _formula
+    torch.manual_seed(T + E)
+    logits = (torch.randn(T, E, device=DEV) * 2).requires_grad_()
+    bias = torch.randn(E, device=DEV) * 0.01 if with_bias else None
+    w, ids, scores = route(logits, bias, k, fn, norm, 1.5)
+    ref_scores = torch.softmax(logits, -1) if fn == "softmax" else torch.sigmoid(logits)
+    sel = ref_scores + bias if with_bias else ref_scores
+    ref_ids = torch.topk(sel, k, dim=-1).indices
+    assert torch.equal(ids.sort(-1).values, ref_ids.sort(-1).values)
+    assert torch.allclose(scores, ref_scores, atol=1e-6, rtol=1e-4)
+    ref_w, _ = _formula(logits, ids, fn, norm, 1.5)
+    assert torch.allclose(w, ref_w, atol=1e-6, rtol=1e-4)
+    dw, dsc = torch.randn_like(w), torch.randn_like(scores)
+    (g,) = torch.autograd.grad((w, scores), logits, (dw, dsc))
+    lg = logits.detach().clone().requires_grad_()
+    rw, rs = _formula(lg, ids, fn, norm, 1.5)
+    (rg,) = torch.autograd.grad((rw, rs), lg, (dw, dsc))
+    assert torch.allclose(g, rg, atol=1e-6, rtol=1e-4)
+
+
+@pytest.mark.parametrize("T,d,E,k", [(300, 256, 8, 2), (1024, 512, 64, 6), (77, 128, 16, 4)])
+def test_moe_token_exchange_single_rank(T, d, E, k):
+    """plan / push / pull kernels with this rank as its own peer against the index arithmetic in PyTorch."""
+    from dew_b200.ops import grouped as G
+    from dew_b200.parallel.ep import TokenExchange
+    torch.manual_seed(T)
+    x = torch.randn(T, d, device=DEV).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(T)])
+    w = torch.rand(T, k, device=DEV)
+    ex = TokenExchange(E, "self")
+    plan = ex.plan(ids, d)
+    ref = G.group_layout(ids.reshape(-1), E)
+    assert int(plan.info[1]) == 0 and int(plan.info[0]) == int(ref.offsets[-1])
+    assert torch.equal(plan.layout.offsets, ref.offsets) and torch.equal(plan.layout.counts, ref.counts)
+    assert torch.equal(plan.layout.tile_group, ref.tile_group)
+    assert torch.equal(plan.dest_pos.long(), ref.positions) and int(plan.dest_rank.abs().max()) == 0
+    rows = ex.push(x, plan)
+    assert torch.equal(rows, G.permute(x, ref, k))
+    y = torch.randn_like(rows)
+    out, kept = ex.pull(y, plan, w, keep_rows=True)
+    assert rel_err(out, G.combine(y, ref, w, T)) <= 1e-2
+    assert torch.equal(kept, y.index_select(0, ref.positions))
+    scaled = ex.push(x, plan, pair_scale=w.reshape(-1))
+    want = torch.zeros_like(rows).index_copy(0, ref.positions, (x.float().repeat_interleave(k, 0) * w.reshape(-1, 1)).to(torch.bfloat16))
+    assert rel_err(scaled, want) <= 1e-2
+
+
+def test_sparse_mlp_exchange_path_matches_index_path():
+    """The mixture layer on the routing / exchange kernels against the same layer on PyTorch index ops (outputs, gradients)."""
+    from dew_b200.models.causal_transformer import Mixture
+    from dew_b200.nn import moe as M
+    mix = Mixture(experts=16, top_k=4, expert_features=128, shared_features=128)
+    torch.manual_seed(0)
+    a = M.SparseMLP(256, mix, 512).to(DEV, torch.bfloat16)
+    torch.manual_seed(0)
+    b = M.SparseMLP(256, mix, 512).to(DEV, torch.bfloat16)
+    b.use_kernels = False
+    x = torch.randn(2, 300, 256, device=DEV).to(torch.bfloat16)
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ya, yb = a(xa), b(xb)
+    assert rel_err(ya, yb) <= 2e-2
+    dy = torch.randn_like(ya)
+    ya.backward(dy)
+    yb.backward(dy)
+    assert rel_err(xa.grad, xb.grad) <= 3e-2
+    for (n, pa), (_, pb) in zip(a.named_parameters(), b.named_parameters()):
+        assert rel_err(pa.grad, pb.grad) <= 5e-2, n
+
+
 def _gdn_inputs(B, T, H, seed, with_state):
     torch.manual_seed(seed)
     q = torch.nn.functional.normalize(torch.randn(B, T, H, 128, device=DEV), dim=-1).to(torch.bfloat16)
