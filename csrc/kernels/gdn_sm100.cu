@@ -358,7 +358,8 @@ gdn_scan_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     const __grid_constant__ CUtensorMap tw, const __grid_constant__ CUtensorMap tu,
                     const __grid_constant__ CUtensorMap tp, const float* __restrict__ gc,
                     const float* __restrict__ initial, __nv_bfloat16* __restrict__ out, float* __restrict__ final_state,
-                    __nv_bfloat16* __restrict__ states, int T, int H, int Tp, int N, float scale, int* __restrict__ err) {
+                    __nv_bfloat16* __restrict__ states, __nv_bfloat16* __restrict__ vn_out, int T, int H, int Tp, int N,
+                    float scale, int* __restrict__ err) {
   extern __shared__ __align__(1024) uint8_t smem[];
   ScanCommon sc;
   if (!scan_prologue(smem, err, sc)) return;
@@ -476,6 +477,7 @@ gdn_scan_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
             const float u = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(ucol + swz(j, uc16)));
             vn[jj] = u - __uint_as_float(a[j8 * 8 + jj]);
             vd[jj] = vn[jj] * __expf(gl - gs[j]);
+            if (vn_out != nullptr) vn_out[(static_cast<long long>(x) * Tp + n * CH + j) * HD + v] = __float2bfloat16(vn[jj]);
           }
           uint4 p0, p1;
           p0.x = pack_bf16(vn[0], vn[1]); p0.y = pack_bf16(vn[2], vn[3]); p0.z = pack_bf16(vn[4], vn[5]); p0.w = pack_bf16(vn[6], vn[7]);
@@ -545,8 +547,9 @@ __global__ void __launch_bounds__(SCAN_THREADS, 1)
 gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tdo, const __grid_constant__ CUtensorMap tk,
                     const __grid_constant__ CUtensorMap tw, const __grid_constant__ CUtensorMap tqg,
                     const __grid_constant__ CUtensorMap tp, const float* __restrict__ gc,
-                    const float* __restrict__ d_final, float* __restrict__ dstates, float* __restrict__ d_initial, int T,
-                    int H, int Tp, int N, int* __restrict__ err) {
+                    const float* __restrict__ d_final, float* __restrict__ dstates, __nv_bfloat16* __restrict__ dstates_bf16,
+                    __nv_bfloat16* __restrict__ dvn_out, float* __restrict__ d_initial, int T, int H, int Tp, int N,
+                    int* __restrict__ err) {
   extern __shared__ __align__(1024) uint8_t smem[];
   ScanCommon sc;
   if (!scan_prologue(smem, err, sc)) return;
@@ -644,11 +647,16 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tdo, const __grid_consta
       const int n = N - 1 - it;
       const int s = it & 1; const uint32_t ph = (it >> 1) & 1;
       const float* gs = sG + s * CH;
-      {
+      if (dstates != nullptr) {
         // the gradient of this chunk's exit state, [Dk, Dv] with the value index contiguous
         float* dst = dstates + (static_cast<long long>(x) * N + n) * HD * HD + v;
 #pragma unroll
         for (int d = 0; d < HD; ++d) dst[d * HD] = G[d];
+      }
+      if (dstates_bf16 != nullptr) {
+        __nv_bfloat16* dst = dstates_bf16 + (static_cast<long long>(x) * N + n) * HD * HD + v;
+#pragma unroll
+        for (int d = 0; d < HD; ++d) dst[d * HD] = __float2bfloat16(G[d]);
       }
       if (!math_wait(&bars->in_full[s], ph, sc, err, ERR_WAIT_FULL)) { ok = false; break; }
       if (!math_wait(&bars->acc_full, it & 1, sc, err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
@@ -667,6 +675,7 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tdo, const __grid_consta
           for (int jj = 0; jj < 8; ++jj) {
             const int j = half * 32 + j8 * 8 + jj;
             nv[jj] = -(__uint_as_float(a[j8 * 8 + jj]) + __expf(gl - gs[j]) * __uint_as_float(bb[j8 * 8 + jj]));
+            if (dvn_out != nullptr) dvn_out[(static_cast<long long>(x) * Tp + n * CH + j) * HD + v] = __float2bfloat16(-nv[jj]);
           }
           uint4 p0;
           p0.x = pack_bf16(nv[0], nv[1]); p0.y = pack_bf16(nv[2], nv[3]); p0.z = pack_bf16(nv[4], nv[5]); p0.w = pack_bf16(nv[6], nv[7]);
@@ -743,10 +752,11 @@ extern "C" int dewb_gdn_prepare(const void* q, const void* k, const void* v, con
 }
 
 // out bf16 [B, T, H, 128] contiguous; initial / final_state fp32 [X, 128 (key), 128 (value)] (initial may be null);
-// states bf16 [X, N, 128 (value), 128 (key)] or null: the state on entry to each chunk, transposed.
+// states bf16 [X, N, 128 (value), 128 (key)] or null: the state on entry to each chunk, transposed;
+// vn_out bf16 [X, Tp, 128] or null: the corrected values Vn = U - W S of every chunk (the backward reads them).
 extern "C" int dewb_gdn_scan_fwd(const void* q, const void* k, const float* gc, const void* W, const void* U, const void* P,
-                                 const float* initial, void* out, float* final_state, void* states, int B, int T, int H,
-                                 int Tp, long long q_sb, long long q_st, long long q_sh, long long k_sb, long long k_st,
+                                 const float* initial, void* out, float* final_state, void* states, void* vn_out, int B,
+                                 int T, int H, int Tp, long long q_sb, long long q_st, long long q_sh, long long k_sb, long long k_st,
                                  long long k_sh, float scale, int* err, void* stream_ptr) {
   using namespace dewb::gdn;
   if (B <= 0 || T <= 0 || H <= 0 || Tp % PT != 0 || Tp < T) return -3;
@@ -764,15 +774,16 @@ extern "C" int dewb_gdn_scan_fwd(const void* q, const void* k, const float* gc, 
   if (e != cudaSuccess) return static_cast<int>(e);
   gdn_scan_fwd_kernel<<<B * H, SCAN_THREADS, SCAN_SMEM, reinterpret_cast<cudaStream_t>(stream_ptr)>>>(
       tq, tk, tw, tu, tp, gc, initial, reinterpret_cast<__nv_bfloat16*>(out), final_state,
-      reinterpret_cast<__nv_bfloat16*>(states), T, H, Tp, N, scale, err);
+      reinterpret_cast<__nv_bfloat16*>(states), reinterpret_cast<__nv_bfloat16*>(vn_out), T, H, Tp, N, scale, err);
   return static_cast<int>(cudaGetLastError());
 }
 
 // d_out bf16 [B, T, H, 128] (strides in elements); d_final fp32 [X, 128, 128] or null; dstates fp32 [X, N, 128 (key),
-// 128 (value)]: the gradient of each chunk's exit state; d_initial fp32 [X, 128, 128].
+// 128 (value)] (or null) and dstates_bf16 (same shape, bf16, or null): the gradient of each chunk's exit state;
+// dvn_out bf16 [X, Tp, 128] or null: dVn of every chunk; d_initial fp32 [X, 128, 128].
 extern "C" int dewb_gdn_scan_bwd(const void* d_out, const void* k, const float* gc, const void* W, const void* P,
-                                 const void* Qg, const float* d_final, float* dstates, float* d_initial, int B, int T,
-                                 int H, int Tp, long long do_sb, long long do_st, long long do_sh, long long k_sb,
+                                 const void* Qg, const float* d_final, float* dstates, void* dstates_bf16, void* dvn_out,
+                                 float* d_initial, int B, int T, int H, int Tp, long long do_sb, long long do_st, long long do_sh, long long k_sb,
                                  long long k_st, long long k_sh, int* err, void* stream_ptr) {
   using namespace dewb::gdn;
   if (B <= 0 || T <= 0 || H <= 0 || Tp % PT != 0 || Tp < T) return -3;
@@ -789,6 +800,7 @@ extern "C" int dewb_gdn_scan_bwd(const void* d_out, const void* k, const float* 
   cudaError_t e = cudaFuncSetAttribute(gdn_scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SCAN_SMEM);
   if (e != cudaSuccess) return static_cast<int>(e);
   gdn_scan_bwd_kernel<<<B * H, SCAN_THREADS, SCAN_SMEM, reinterpret_cast<cudaStream_t>(stream_ptr)>>>(
-      tdo, tk, tw, tqg, tp, gc, d_final, dstates, d_initial, T, H, Tp, N, err);
+      tdo, tk, tw, tqg, tp, gc, d_final, dstates, reinterpret_cast<__nv_bfloat16*>(dstates_bf16),
+      reinterpret_cast<__nv_bfloat16*>(dvn_out), d_initial, T, H, Tp, N, err);
   return static_cast<int>(cudaGetLastError());
 }

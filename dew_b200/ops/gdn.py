@@ -260,7 +260,7 @@ def prepare_cuda(q, k, v, g, beta, scale: float, want_qg: bool):
     return gc, W, U, P, Qg
 
 
-def scan_fwd_cuda(q, k, gc, W, U, P, scale: float, initial_state, save_states: bool):
+def scan_fwd_cuda(q, k, gc, W, U, P, scale: float, initial_state, save_states: bool, save_vn: bool = False):
     B, T, H, _ = q.shape
     X, Tp = B * H, gc.shape[1]
     N = (T + CHUNK - 1) // CHUNK
@@ -268,34 +268,82 @@ def scan_fwd_cuda(q, k, gc, W, U, P, scale: float, initial_state, save_states: b
     o = torch.empty(B, T, H, HEAD_DIM, dtype=torch.bfloat16, device=dev)
     final = torch.empty(X, HEAD_DIM, HEAD_DIM, dtype=torch.float32, device=dev)
     states = torch.empty(X, N, HEAD_DIM, HEAD_DIM, dtype=torch.bfloat16, device=dev) if save_states else None
+    vn = None
+    if save_vn:
+        vn = torch.empty(X, Tp, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        vn[:, N * CHUNK:].zero_()                      # the chunk the padding to 128 adds is never visited
     init = None if initial_state is None else initial_state.reshape(X, HEAD_DIM, HEAD_DIM).float().contiguous()
     lib = L.load()
     L.ensure_device(q)
     rc = lib.dewb_gdn_scan_fwd(L.ptr(q), L.ptr(k), L.ptr(gc), L.ptr(W), L.ptr(U), L.ptr(P), L.ptr(init), L.ptr(o), L.ptr(final),
-                               L.ptr(states), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(Tp),
+                               L.ptr(states), L.ptr(vn), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(Tp),
                                *_strides3(q), *_strides3(k), ctypes.c_float(scale), L.ptr(L.status(dev)), L.stream_ptr())
     L.check(rc, "gdn_scan_fwd")
     L.count_launches()
     # the kernel stores each chunk-entry state transposed ([Dv, Dk], the operand tile it keeps in shared memory)
+    if save_vn:
+        return o, final, states, vn                     # raw layouts, as the backward kernels read them
     return o, final, (states.transpose(-1, -2) if save_states else None)
 
 
-def scan_bwd_cuda(do, k, gc, W, P, Qg, d_final):
+def scan_bwd_cuda(do, k, gc, W, P, Qg, d_final, for_kernels: bool = False):
     B, T, H, _ = do.shape
     X, Tp = B * H, gc.shape[1]
     N = (T + CHUNK - 1) // CHUNK
     dev = do.device
-    dstates = torch.empty(X, N, HEAD_DIM, HEAD_DIM, dtype=torch.float32, device=dev)
+    dstates = None if for_kernels else torch.empty(X, N, HEAD_DIM, HEAD_DIM, dtype=torch.float32, device=dev)
+    dstates16 = dvn = None
+    if for_kernels:
+        dstates16 = torch.empty(X, N, HEAD_DIM, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        dvn = torch.empty(X, Tp, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        dvn[:, N * CHUNK:].zero_()
     d_init = torch.empty(X, HEAD_DIM, HEAD_DIM, dtype=torch.float32, device=dev)
     dfin = None if d_final is None else d_final.reshape(X, HEAD_DIM, HEAD_DIM).float().contiguous()
     lib = L.load()
     L.ensure_device(do)
     rc = lib.dewb_gdn_scan_bwd(L.ptr(do), L.ptr(k), L.ptr(gc), L.ptr(W), L.ptr(P), L.ptr(Qg), L.ptr(dfin), L.ptr(dstates),
-                               L.ptr(d_init), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(Tp),
+                               L.ptr(dstates16), L.ptr(dvn), L.ptr(d_init), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(Tp),
                                *_strides3(do), *_strides3(k), L.ptr(L.status(dev)), L.stream_ptr())
     L.check(rc, "gdn_scan_bwd")
     L.count_launches()
+    if for_kernels:
+        return dstates16, dvn, d_init
     return dstates, d_init
+
+
+def local_bwd_cuda(q, k, v, do, gc, beta, W, U, P, vn, dvn, states_raw, dstates16, scale: float):
+    """The chunk-local gradients on the two backward kernels (``csrc/kernels/gdn_bwd_sm100.cu``): dq, dk, dv (bf16) and
+    dg, dbeta (fp32), from the intermediates the prepare kernel and the two scans leave in memory."""
+    B, T, H, _ = q.shape
+    X, Tp = B * H, gc.shape[1]
+    N = (T + CHUNK - 1) // CHUNK
+    dev = q.device
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    dKt, dVt = torch.empty(X, Tp, HEAD_DIM, **bf), torch.empty(X, Tp, HEAD_DIM, **bf)
+    if N * CHUNK < Tp:
+        dKt[:, N * CHUNK:].zero_()
+        dVt[:, N * CHUNK:].zero_()
+    dq_part = torch.empty(B, T, H, HEAD_DIM, dtype=torch.float32, device=dev)
+    dk_part = torch.empty_like(dq_part)
+    gpart = torch.empty(X, Tp, dtype=torch.float32, device=dev)
+    bpart = torch.empty_like(gpart)
+    dq, dk, dv = (torch.empty(B, T, H, HEAD_DIM, **bf) for _ in range(3))
+    dg = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    dbeta = torch.empty_like(dg)
+    L.ensure_device(q)
+    rc = L.load().dewb_gdn_bwd_local(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(do), L.ptr(vn), L.ptr(dvn), L.ptr(W), L.ptr(U), L.ptr(P),
+                                     L.ptr(gc), L.ptr(beta), L.ptr(states_raw), L.ptr(dstates16), L.ptr(dKt), L.ptr(dVt),
+                                     L.ptr(dq_part), L.ptr(dk_part), L.ptr(gpart), L.ptr(bpart), L.ptr(dq), L.ptr(dk), L.ptr(dv),
+                                     L.ptr(dg), L.ptr(dbeta), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(Tp),
+                                     ctypes.c_float(scale), L.ptr(L.status(dev)), L.stream_ptr())
+    L.check(rc, "gdn_bwd_local")
+    L.count_launches(2)
+    return dq, dk, dv, dg, dbeta
+
+
+def local_kernels_available() -> bool:
+    import os
+    return hasattr(L.load(), "dewb_gdn_bwd_local") and os.environ.get("DEWB_GDN_LOCAL", "kernel") != "torch"
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -333,6 +381,14 @@ class _GatedDeltaRule(torch.autograd.Function):
         scale = ctx.scale
         B, T, H, Dk = q.shape
         Dv = v.shape[-1]
+        if _stages(q) and local_kernels_available():
+            do = do.contiguous().to(torch.bfloat16)
+            gc, W, U, P, Qg = prepare_cuda(q, k, v, g, beta, scale, True)
+            _, _, states_raw, vn = scan_fwd_cuda(q, k, gc, W, U, P, scale, initial_state, True, save_vn=True)
+            dstates16, dvn, d_init = scan_bwd_cuda(do, k, gc, W, P, Qg, dfinal, for_kernels=True)
+            dq, dk, dv, dg, dbeta = local_bwd_cuda(q, k, v, do, gc, beta, W, U, P, vn, dvn, states_raw, dstates16, scale)
+            d_init = d_init.reshape(B, H, Dk, Dv).to(initial_state.dtype) if ctx.has_initial else None
+            return dq, dk, dv, dg.to(g.dtype), dbeta.to(beta.dtype), d_init, None
         if _stages(q):
             do = do.contiguous().to(torch.bfloat16)
             gc, W, U, P, Qg = prepare_cuda(q, k, v, g, beta, scale, True)

@@ -498,6 +498,25 @@ def test_gdn_kernel_stages_match_their_restatements(B, T, H, with_state):
     assert rel_err(dinit, rdinit) <= 2e-2
 
 
+@pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 300, 2), (1, 1024, 3)])
+def test_gdn_local_backward_kernels_match_closed_form(B, T, H):
+    """The two chunk-local backward kernels against the closed-form gradients in PyTorch, both fed the same
+    intermediates (entry states, exit-state gradients, Vn, dVn) from the scan kernels."""
+    from dew_b200.ops import gdn
+    q, k, v, g, beta, s0 = _gdn_inputs(B, T, H, 7 * T, True)
+    scale = 128 ** -0.5
+    do = torch.randn(B, T, H, 128, device=DEV).to(torch.bfloat16)
+    gc, W, U, P, Qg = gdn.prepare_cuda(q, k, v, g, beta, scale, True)
+    _, _, states_raw, vn = gdn.scan_fwd_cuda(q, k, gc, W, U, P, scale, s0, True, save_vn=True)
+    dstates16, dvn, _ = gdn.scan_bwd_cuda(do, k, gc, W, P, Qg, None, for_kernels=True)
+    got = gdn.local_bwd_cuda(q, k, v, do, gc, beta, W, U, P, vn, dvn, states_raw, dstates16, scale)
+    L.check_status()
+    ref = gdn.chunk_local_grads(q, k, v, g, beta, states_raw.transpose(-1, -2).float(), dstates16.float(), do, scale)
+    for name, a, b in zip(("dq", "dk", "dv", "dg", "dbeta"), got, ref):
+        assert torch.isfinite(a.float()).all(), name
+        assert rel_err(a, b) <= 3e-2, (name, rel_err(a, b))
+
+
 @pytest.mark.parametrize("B,T,H,with_state", [(2, 200, 2, True), (1, 512, 4, False)])
 def test_gdn_forward_backward_against_recurrent_oracle(B, T, H, with_state):
     from dew_b200.ops import scan
