@@ -51,10 +51,25 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// v[k] holds this lane's term for token k (32 tokens); on return lane l holds the sum over the warp of token l's terms.
+// 31 shuffles for 32 sums (a butterfly that halves the token set at every step) instead of 5 per sum.
+__device__ __forceinline__ float reduce_scatter32(float (&v)[32], int lane) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const bool upper = (lane & o) != 0;
+#pragma unroll
+    for (int k = 0; k < o; ++k) {
+      const float send = upper ? v[k] : v[k + o];
+      const float keep = upper ? v[k + o] : v[k];
+      v[k] = keep + __shfl_xor_sync(FULL, send, o);
+    }
+  }
+  return v[0];
+}
+
 struct Tail {
   float g[PT], beta[PT], eg[PT];
   float sum_q[PT], sum_k[PT], sum_kd[PT], sum_v[PT];       // state kernel: per-token sums over the feature index
-  float col_gp[PT], col_e[PT];                               // pair kernel: column sums of dP o P and dA o A
   float dss[2];                                              // <dS1, S0> per chunk
   float red[8];
   uint64_t bar[6];
@@ -146,6 +161,7 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
       umma_commit(bar_kk);
     }
   }
+  if (warp == 0) __syncwarp();      // the issuing thread's warp-mates park here instead of spinning beside it
   if (warp < 4) {
     // token row i: A[i][j] = beta_i (k_i . k_j) e^{g_i - g_j} (j < i), stored transposed: sAT[c][j][i], each row of the
     // transpose rotated by four floats per row so that the solve's broadcast float4 reads stay aligned and these
@@ -219,6 +235,7 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
         umma_commit(bar_mma);
       }
     }
+    if (warp == 0) __syncwarp();
     // everybody: the tiles have landed (the per-thread wait gives the acquire) and the products are complete
     bool ok = mbar_wait(bar_in, c & 1, abort_flag);
     ok = mbar_wait(bar_mma, c & 1, abort_flag) && ok;
@@ -245,17 +262,17 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
       // back substitution: x_i = r_i - sum_{j > i} A[j][i] x_j  (xs holds r, then x)
 #pragma unroll
       for (int i = CH - 2; i >= 0; --i) {
-        float acc = xs[i];
+        float acc = xs[i], acc1 = 0.f;                     // two chains: half the dependent latency per row
         const float4* arow = reinterpret_cast<const float4*>(at + i * CH);
 #pragma unroll
         for (int j4 = (i + 1) >> 2; j4 < 16; ++j4) {
           const float4 av = arow[(j4 + i) & 15];
           if (j4 * 4 + 0 > i) acc = fmaf(-av.x, xs[j4 * 4 + 0], acc);
-          if (j4 * 4 + 1 > i) acc = fmaf(-av.y, xs[j4 * 4 + 1], acc);
+          if (j4 * 4 + 1 > i) acc1 = fmaf(-av.y, xs[j4 * 4 + 1], acc1);
           if (j4 * 4 + 2 > i) acc = fmaf(-av.z, xs[j4 * 4 + 2], acc);
-          if (j4 * 4 + 3 > i) acc = fmaf(-av.w, xs[j4 * 4 + 3], acc);
+          if (j4 * 4 + 3 > i) acc1 = fmaf(-av.w, xs[j4 * 4 + 3], acc1);
         }
-        xs[i] = acc;
+        xs[i] = acc + acc1;
       }
       if (tid < 128) {
         // dKt column; dk_part = e^{g_L - g} dKd + beta e^g dKt; sums over the key index
@@ -265,27 +282,39 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
         tmem_ld_wait();
         const float gl = tail->g[c * 64 + 63];
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          const int r = c * 64 + j;
-          const float kv = tile_get(sK, PT, r, f);
-          const float dkd = __expf(gl - tail->g[r]) * __uint_as_float(j < 32 ? v0[j & 31] : v1[j & 31]);
-          dKt[(trow + j) * HD + f] = __float2bfloat16(xs[j]);
-          const int t = n * CH + j;
-          if (t < T) dk_part[((static_cast<long long>(b) * T + t) * H + h) * HD + f] = dkd + tail->beta[r] * tail->eg[r] * xs[j];
-          const float s1 = warp_sum(xs[j] * kv), s2 = warp_sum(dkd * kv);
-          if (lane == 0) { atomicAdd(&tail->sum_k[r], s1); atomicAdd(&tail->sum_kd[r], s2); }
+        for (int half = 0; half < 2; ++half) {
+          float p1[32], p2[32];
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            const int j = half * 32 + jj, r = c * 64 + j;
+            const float kv = tile_get(sK, PT, r, f);
+            const float dkd = __expf(gl - tail->g[r]) * __uint_as_float(half == 0 ? v0[jj] : v1[jj]);
+            dKt[(trow + j) * HD + f] = __float2bfloat16(xs[j]);
+            const int t = n * CH + j;
+            if (t < T) dk_part[((static_cast<long long>(b) * T + t) * H + h) * HD + f] = dkd + tail->beta[r] * tail->eg[r] * xs[j];
+            p1[jj] = xs[j] * kv;
+            p2[jj] = dkd * kv;
+          }
+          const float s1 = reduce_scatter32(p1, lane), s2 = reduce_scatter32(p2, lane);
+          atomicAdd(&tail->sum_k[c * 64 + half * 32 + lane], s1);
+          atomicAdd(&tail->sum_kd[c * 64 + half * 32 + lane], s2);
         }
         tmem_ld_32x32b_x32(tmem + lane_addr + TM_X1, v0);
         tmem_ld_32x32b_x32(tmem + lane_addr + TM_X1 + 32, v1);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          const int r = c * 64 + j;
-          const float dq1 = scale * tail->eg[r] * __uint_as_float(j < 32 ? v0[j & 31] : v1[j & 31]);
-          const int t = n * CH + j;
-          if (t < T) dq_part[((static_cast<long long>(b) * T + t) * H + h) * HD + f] = dq1;
-          const float s = warp_sum(dq1 * tile_get(sQ, CH, j, f));
-          if (lane == 0) atomicAdd(&tail->sum_q[r], s);
+        for (int half = 0; half < 2; ++half) {
+          float p1[32];
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            const int j = half * 32 + jj, r = c * 64 + j;
+            const float dq1 = scale * tail->eg[r] * __uint_as_float(half == 0 ? v0[jj] : v1[jj]);
+            const int t = n * CH + j;
+            if (t < T) dq_part[((static_cast<long long>(b) * T + t) * H + h) * HD + f] = dq1;
+            p1[jj] = dq1 * tile_get(sQ, CH, j, f);
+          }
+          const float s = reduce_scatter32(p1, lane);
+          atomicAdd(&tail->sum_q[c * 64 + half * 32 + lane], s);
         }
         // <dS1, S0>: row f of dS1 against column f of the transposed state tile
         float acc = 0.f;
@@ -295,13 +324,18 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
         if (lane == 0) atomicAdd(&tail->dss[c], acc);
       } else {
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          const int r = c * 64 + j;
-          dVt[(trow + j) * HD + f] = __float2bfloat16(xs[j]);
-          const int t = n * CH + j;
-          if (t < T) dv[((static_cast<long long>(b) * T + t) * H + h) * HD + f] = __float2bfloat16(tail->beta[r] * xs[j]);
-          const float s = warp_sum(xs[j] * tile_get(sV, CH, j, f));
-          if (lane == 0) atomicAdd(&tail->sum_v[r], s);
+        for (int half = 0; half < 2; ++half) {
+          float p1[32];
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            const int j = half * 32 + jj, r = c * 64 + j;
+            dVt[(trow + j) * HD + f] = __float2bfloat16(xs[j]);
+            const int t = n * CH + j;
+            if (t < T) dv[((static_cast<long long>(b) * T + t) * H + h) * HD + f] = __float2bfloat16(tail->beta[r] * xs[j]);
+            p1[jj] = xs[j] * tile_get(sV, CH, j, f);
+          }
+          const float s = reduce_scatter32(p1, lane);
+          atomicAdd(&tail->sum_v[c * 64 + half * 32 + lane], s);
         }
       }
       tc_fence_before();
@@ -360,7 +394,7 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
   const int t0 = blockIdx.x * PT;
   uint8_t* b0 = smem;              // K
   uint8_t* b1 = smem + T32;        // dO, then dVt, then Bt
-  uint8_t* b2 = smem + 2 * T32;    // Vn, then U
+  uint8_t* b2 = smem + 2 * T32;    // Vn, then U, then the fp32 matrix dP o P + dA o A
   uint8_t* b3 = smem + 3 * T32;    // dKt, then Q
   uint8_t* b4 = smem + 4 * T32;    // W, then Gt
   uint64_t* bar_a = &tail->bar[0];   // K, dO, Vn, dKt, W landed
@@ -381,8 +415,6 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
     tail->g[tid] = gi;
     tail->eg[tid] = __expf(gi);
     tail->beta[tid] = t < T ? beta[(static_cast<long long>(b) * T + t) * H + h] : 0.f;
-    tail->col_gp[tid] = 0.f;
-    tail->col_e[tid] = 0.f;
   }
   tc_fence_before();
   __syncthreads();
@@ -450,10 +482,18 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
       umma_commit(bar_y);
     }
   }
+  if (warp == 0) __syncwarp();
   float row_gp = 0.f, row_e = 0.f, row_b = 0.f;
   if (warp < 4) {
     // token row i: its chunk's 64 columns of K K^T, dP and dA -> the Gt and Bt operand tiles and the decay / strength sums
     const int i = tid, c = i >> 6, il = i & 63;
+    // this row of P (64 bf16) is fetched before the waits so that its latency hides behind the products
+    uint4 pv8[8];
+    {
+      const uint4* pr = reinterpret_cast<const uint4*>(P + (static_cast<long long>(prow) + i) * CH);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) pv8[u] = __ldg(pr + u);
+    }
     bool ok = mbar_wait(bar_y, 0, abort_flag);
     ok = mbar_wait(bar_b, 0, abort_flag) && ok;
     ok = __all_sync(FULL, ok);
@@ -462,7 +502,6 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
       tc_fence_after();
       const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
       const float gi = tail->g[i], bi = tail->beta[i];
-      const uint4* prow_p = reinterpret_cast<const uint4*>(P + (static_cast<long long>(prow) + i) * CH);
       uint8_t* gt_row = b4 + c * (PT * 128);        // Gt[i][j]: column block c (64 columns) is sub-tile c
       uint8_t* bt_row = b1 + c * (PT * 128);
       const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
@@ -481,9 +520,9 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
         tmem_ld_wait();
 #pragma unroll
         for (int j8 = 0; j8 < 4; ++j8) {
-          const uint4 pv = prow_p[half * 4 + j8];
+          const uint4 pv = pv8[half * 4 + j8];
           const uint32_t pw[4] = {pv.x, pv.y, pv.z, pv.w};
-          float gt[8], bt[8];
+          float gt[8], bt[8], mrow[8];
 #pragma unroll
           for (int jj = 0; jj < 8; ++jj) {
             const int j = half * 32 + j8 * 8 + jj;
@@ -497,11 +536,13 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
             bt[jj] = dav * bi * dcy;
             const float e = dav * bi * kkd;
             row_gp += gp; row_e += e; row_b += dav * kkd;
-            // column sums: every thread of a warp adds to a different column at any one time only if the columns are
-            // visited in a rotated order; here the order is the same for all rows, so the adds are atomic
-            if (j <= il) atomicAdd(&tail->col_gp[c * 64 + j], gp);
-            if (j < il) atomicAdd(&tail->col_e[c * 64 + j], e);
+            mrow[jj] = gp + e;
           }
+          // dP o P + dA o A of this row, kept for the column sums (rows rotated by one float4 per row: no bank conflicts
+          // for these stores nor for the column reads below)
+          float4* mr = reinterpret_cast<float4*>(b2) + (c * CH + il) * 16;
+          mr[(half * 8 + j8 * 2 + il) & 15] = make_float4(mrow[0], mrow[1], mrow[2], mrow[3]);
+          mr[(half * 8 + j8 * 2 + 1 + il) & 15] = make_float4(mrow[4], mrow[5], mrow[6], mrow[7]);
           uint4 g4, b4v;
           g4.x = pack_bf16(gt[0], gt[1]); g4.y = pack_bf16(gt[2], gt[3]); g4.z = pack_bf16(gt[4], gt[5]); g4.w = pack_bf16(gt[6], gt[7]);
           b4v.x = pack_bf16(bt[0], bt[1]); b4v.y = pack_bf16(bt[2], bt[3]); b4v.z = pack_bf16(bt[4], bt[5]); b4v.w = pack_bf16(bt[6], bt[7]);
@@ -547,7 +588,15 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
   if (warp < 4 && tail->abort_flag == 0) {
     // d gc of token i, then d g by the reverse running sum inside the chunk; d beta
     const int i = tid;
-    float dgc = gpart[static_cast<long long>(prow) + i] + row_gp - tail->col_gp[i] + row_e - tail->col_e[i];
+    float col = 0.f;
+    {
+      // column (i & 63) of this chunk's 64 x 64 block of dP o P + dA o A
+      const float* m = reinterpret_cast<const float*>(b2) + (i >> 6) * (CH * CH);
+      const int j = i & 63;
+#pragma unroll 8
+      for (int r = 0; r < CH; ++r) col += m[r * CH + ((j + 4 * r) & 63)];
+    }
+    float dgc = gpart[static_cast<long long>(prow) + i] + row_gp + row_e - col;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       const float dn = __shfl_down_sync(FULL, dgc, d);
@@ -572,6 +621,15 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) {
       uint32_t a[32], c2[32];
+      // all 64 loads of the partial sums are in flight before the first of them is used
+      float pq[32], pk[32];
+#pragma unroll
+      for (int ii = 0; ii < 32; ++ii) {
+        const int t = min(t0 + q4 * 32 + ii, T - 1);
+        const long long o = ((static_cast<long long>(b) * T + t) * H + h) * HD + f;
+        pq[ii] = __ldg(dq_part + o);
+        pk[ii] = __ldg(dk_part + o);
+      }
       tmem_ld_32x32b_x32(tmem + lane_addr + TM_KK + q4 * 32, a);
       tmem_ld_32x32b_x32(tmem + lane_addr + TM_DP + q4 * 32, c2);
       tmem_ld_wait();
@@ -580,8 +638,8 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
         const int t = t0 + q4 * 32 + ii;
         if (t < T) {
           const long long o = ((static_cast<long long>(b) * T + t) * H + h) * HD + f;
-          dq[o] = __float2bfloat16(dq_part[o] + __uint_as_float(a[ii]));
-          dk[o] = __float2bfloat16(dk_part[o] + __uint_as_float(c2[ii]));
+          dq[o] = __float2bfloat16(pq[ii] + __uint_as_float(a[ii]));
+          dk[o] = __float2bfloat16(pk[ii] + __uint_as_float(c2[ii]));
         }
       }
     }

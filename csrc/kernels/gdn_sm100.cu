@@ -151,6 +151,8 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       umma_commit(&tail->bar_mma);
     }
   }
+  // the other lanes of the issuing thread's warp park here instead of spinning on the barrier beside it
+  if (warp == 0) __syncwarp();
   if (warp < 4) {
     // thread = token row i of the 128; its chunk's 64 columns of both score matrices
     const int i = tid, c = i >> 6, il = i & 63;
@@ -233,16 +235,17 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
       for (int i = 0; i < CH; ++i) {
         const int r = c * 64 + i;
         const float raw = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(src + swz(r, c16)));
-        float acc = raw * tail->beta[r] * (is_w ? tail->eg[r] : 1.f);
+        float acc = raw * tail->beta[r] * (is_w ? tail->eg[r] : 1.f), acc1 = 0.f;      // two chains per row
         const float4* arow = reinterpret_cast<const float4*>(Ac + i * CH);
 #pragma unroll
         for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
           const float4 av = arow[(j4 + i) & 15];
           acc = fmaf(-av.x, xv[j4 * 4], acc);
-          acc = fmaf(-av.y, xv[j4 * 4 + 1], acc);
+          acc1 = fmaf(-av.y, xv[j4 * 4 + 1], acc1);
           acc = fmaf(-av.z, xv[j4 * 4 + 2], acc);
-          acc = fmaf(-av.w, xv[j4 * 4 + 3], acc);
+          acc1 = fmaf(-av.w, xv[j4 * 4 + 3], acc1);
         }
+        acc += acc1;
         xv[i] = acc;
         dst[static_cast<long long>(r) * HD] = __float2bfloat16(acc);
       }

@@ -191,6 +191,7 @@ def main(argv=None):
     ap.add_argument("--only", default="gemm,rows,attention")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--gemm-shape", default=None, help="M,N,K[,a_mn,b_mn]: time one GEMM shape only (small profiling case)")
+    ap.add_argument("--gdn-shape", default=None, help="B,T,H: time the gated-delta-rule kernels on one shape only (small profiling case)")
     ap.add_argument("--attn-shape", default=None, help="B,S,Hq,Hkv,D: time this library's attention kernels on one shape only")
     args = ap.parse_args(argv)
     peaks = measured_peaks()
@@ -201,6 +202,9 @@ def main(argv=None):
         f = [int(x) for x in args.gemm_shape.split(",")]
         f += [0] * (5 - len(f))
         bench_gemm(out, peaks, flush, shapes=[("custom", f[0], f[1], f[2], bool(f[3]), bool(f[4]))], iters=args.iters)
+        return
+    if args.gdn_shape:
+        bench_gdn(out, peaks, flush, iters=args.iters, shapes=[tuple(int(x) for x in args.gdn_shape.split(","))])
         return
     if args.attn_shape:
         bench_attention(out, peaks, flush, iters=args.iters, shapes=[tuple(int(x) for x in args.attn_shape.split(","))],
