@@ -83,8 +83,8 @@ class GatedDeltaNet(nn.Module):
         state = cache.recurrent(layer, B, self) if cache is not None and hasattr(cache, "recurrent") else None
         qkv = self.conv1d(qkv, segment_ids, state["conv"] if state is not None else None)
         q, k, v = qkv.split([self.key_dim, self.key_dim, self.value_dim], -1)
-        q = F.normalize(q.float().reshape(B, T, self.hk, self.dk), dim=-1)
-        k = F.normalize(k.float().reshape(B, T, self.hk, self.dk), dim=-1)
+        q = ops.l2_normalize(q.reshape(B, T, self.hk, self.dk))        # bf16 row kernel on a GPU, fp32 F.normalize elsewhere
+        k = ops.l2_normalize(k.reshape(B, T, self.hk, self.dk))
         v = v.reshape(B, T, self.hv, self.dv)
         rep = self.hv // self.hk
         if rep > 1:
@@ -95,7 +95,8 @@ class GatedDeltaNet(nn.Module):
         if state is not None and T == 1:
             o = scan.gated_delta_rule_step(q[:, 0], k[:, 0], v[:, 0].float(), g[:, 0], beta[:, 0], state["S"])[:, None]
         else:
-            o, S = scan.chunk_gated_delta_rule(q, k, v.float(), g, beta, initial_state=state["S"] if state is not None else None)
+            o, S = scan.chunk_gated_delta_rule(q, k, v if v.is_cuda else v.float(), g, beta,
+                                               initial_state=state["S"] if state is not None else None)
             if state is not None:
                 state["S"].copy_(S)
         o = ops.gated_rms_norm(o.to(x.dtype).reshape(B, T, self.hv, self.dv), z.reshape(B, T, self.hv, self.dv), self.norm_weight, self.norm_eps)

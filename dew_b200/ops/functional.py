@@ -194,6 +194,48 @@ def rms_norm_reference(x, w, eps=1e-6):
     return y.to(x.dtype)
 
 
+class _L2Norm(torch.autograd.Function):
+    """``y = x / max(||x||, eps)`` over the last axis on the row kernel (``csrc/kernels/l2norm.cu``); x may be a strided
+    ``[B, T, H, D]`` view of a wider projection, y and dx are contiguous."""
+
+    @staticmethod
+    def forward(ctx, x, eps):
+        B, T, H, D = x.shape
+        rows = B * T * H
+        y = torch.empty(B, T, H, D, dtype=torch.bfloat16, device=x.device)
+        rnorm = torch.empty(rows, dtype=torch.float32, device=x.device)
+        L.ensure_device(x)
+        L.check(L.load().dewb_l2norm_fwd(L.ptr(x), L.ptr(y), L.ptr(rnorm), ctypes.c_longlong(rows), ctypes.c_int(H),
+                                         ctypes.c_longlong(x.stride(1)), ctypes.c_longlong(x.stride(2)), ctypes.c_int(D),
+                                         ctypes.c_float(eps), L.stream_ptr()), "l2norm_fwd")
+        L.count_launches()
+        ctx.save_for_backward(y, rnorm)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        y, rnorm = ctx.saved_tensors
+        dy = dy.contiguous().to(torch.bfloat16)
+        dx = torch.empty_like(y)
+        L.ensure_device(y)
+        L.check(L.load().dewb_l2norm_bwd(L.ptr(y), L.ptr(dy), L.ptr(rnorm), L.ptr(dx), ctypes.c_longlong(rnorm.numel()),
+                                         ctypes.c_int(y.shape[-1]), L.stream_ptr()), "l2norm_bwd")
+        L.count_launches()
+        return dx, None
+
+
+def l2_normalize(x: torch.Tensor, eps: float = 1e-12) -> torch.Tensor:
+    """``x [B, T, H, D] -> x / max(||x||_2, eps)`` over D.  bf16 CUDA tensors (D <= 1024, D % 8 == 0) run the row kernel and
+    return bf16; anything else is ``F.normalize`` in fp32."""
+    if (x.dim() == 4 and x.dtype == torch.bfloat16 and L.use_cuda(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 1024
+            and hasattr(L.load(), "dewb_l2norm_fwd")):
+        if not (x.stride(3) == 1 and x.stride(0) == x.shape[1] * x.stride(1) and x.stride(1) % 8 == 0 and x.stride(2) % 8 == 0
+                and x.data_ptr() % 16 == 0):
+            x = x.contiguous()
+        return _L2Norm.apply(x, float(eps))
+    return torch.nn.functional.normalize(x.float(), dim=-1, eps=eps)
+
+
 def _bwd_scratch(rows: int, d: int, device) -> torch.Tensor:
     blocks = L.load().dewb_rmsnorm_bwd_blocks(c_ll(rows))
     return torch.empty((blocks, d), dtype=torch.float32, device=device)

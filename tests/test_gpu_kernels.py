@@ -462,6 +462,48 @@ def test_sparse_mlp_exchange_path_matches_index_path():
         assert rel_err(pa.grad, pb.grad) <= 5e-2, n
 
 
+@pytest.mark.parametrize("B,T,H,D,strided", [(2, 100, 4, 128, True), (1, 333, 3, 64, False), (2, 50, 2, 256, True)])
+def test_l2_normalize_kernel(B, T, H, D, strided):
+    torch.manual_seed(T)
+    wide = torch.randn(B, T, 3 * H * D + 8, device=DEV).to(torch.bfloat16)
+    src = wide[..., 8:8 + H * D] if strided else wide[..., :H * D].contiguous()
+    x = src.reshape(B, T, H, D).detach().requires_grad_()
+    y = ops.l2_normalize(x)
+    assert y.dtype == torch.bfloat16 and y.is_contiguous()
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf = x.detach().float().requires_grad_()
+    ref = torch.nn.functional.normalize(xf, dim=-1)
+    ref.backward(dy.float())
+    assert rel_err(y, ref) <= 2 * bf16_floor(ref)
+    assert rel_err(x.grad, xf.grad) <= 2e-2
+
+
+def test_gated_delta_net_layer_gpu_matches_cpu_reference():
+    """The whole mixer (projections, short conv, l2-norm, gated delta rule kernels, gated norm) on the GPU in bf16 against the
+    same module in fp32 on the CPU."""
+    from dew_b200.nn.linear_attention import GatedDeltaNet
+    torch.manual_seed(0)
+    ref = GatedDeltaNet(256, num_k_heads=2, num_v_heads=2, head_k_dim=128, head_v_dim=128)
+    gpu = GatedDeltaNet(256, num_k_heads=2, num_v_heads=2, head_k_dim=128, head_v_dim=128)
+    gpu.load_state_dict(ref.state_dict())
+    gpu = gpu.to(DEV)
+    for n, p in gpu.named_parameters():
+        if n not in ("A_log", "dt_bias"):
+            p.data = p.data.to(torch.bfloat16)
+    x = torch.randn(2, 200, 256) * 0.5
+    xr = x.clone().requires_grad_()
+    xg = x.to(DEV, torch.bfloat16).requires_grad_()
+    yr, yg = ref(xr), gpu(xg)
+    assert rel_err(yg.cpu(), yr) <= 5e-2
+    dy = torch.randn_like(yr)
+    yr.backward(dy)
+    yg.backward(dy.to(DEV, torch.bfloat16))
+    assert rel_err(xg.grad.cpu(), xr.grad) <= 8e-2
+    assert rel_err(gpu.A_log.grad.cpu(), ref.A_log.grad) <= 8e-2
+    assert rel_err(gpu.in_proj_qkvz.weight.grad.cpu(), ref.in_proj_qkvz.weight.grad) <= 8e-2
+
+
 def _gdn_inputs(B, T, H, seed, with_state):
     torch.manual_seed(seed)
     q = torch.nn.functional.normalize(torch.randn(B, T, H, 128, device=DEV), dim=-1).to(torch.bfloat16)
