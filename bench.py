@@ -128,6 +128,8 @@ def main() -> None:
     ap.add_argument("--config", default="dense", choices=sorted(CONFIGS), help="training configuration (default: the headline)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the result is then not a valid headline)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
+                    help="moe: token exchange by this library's peer-memory kernels (default) or by NCCL all-to-all (comparison arm)")
     ap.add_argument("--profile", default=None, help="write a torch.profiler kernel table for one step to this file")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -169,7 +171,7 @@ def main() -> None:
         model = CausalTransformer(device=dev, dtype=torch.bfloat16, mixture=Mixture(**conf["mixture"]), **cfg)
         reset_all(model, 1234)
         if world > 1:
-            ExpertParallel().shard(model)
+            ExpertParallel(fused=args.ep == "peer").shard(model)
         else:
             next(p for n, p in model.named_parameters() if "experts.gate_up" in n).expert_parallel = True   # initialised above
         torch.cuda.empty_cache()
@@ -286,7 +288,7 @@ def main() -> None:
             "data": "synthetic (uniform random token ids from a seed; random-init weights)",
             "config": {"model": conf["name"], "params": n_params,
                        "global_batch": rows * world, "seq_len": SEQ_LEN, "micro_batch": micro,
-                       "parallelism": f"fsdp{world}" + (f"+ep{world}" if args.config == "moe" else ""),
+                       "parallelism": f"fsdp{world}" + (f"+ep{world} ({args.ep} exchange)" if args.config == "moe" else ""),
                        "optimizer": "AdamW fp32 masters+moments",
                        "l2": "inputs larger than L2 (16 GB of weights stream every microbatch)",
                        "baseline": "BASELINE.md reference-equivalent mark 190K tok/s at 8xB200, scaled per GPU"},

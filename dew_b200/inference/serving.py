@@ -216,6 +216,13 @@ class Server:
         s = row.ticket.sampling or self.sampling
         if s.greedy:
             return logits[0].argmax(-1)
+        if logits.is_cuda:
+            from ..ops import sample as S
+            from ..sampling.text import plain_filters
+            if plain_filters(s) and S.kernel_ok(logits):
+                # temperature and the top-k / min-p / top-p thresholds inside the sampling kernel; the uniform comes from the row's key
+                g = K.generator(K.fold_in(K.fold_in(K.key(row.ticket.key), "draw"), step), "cpu")
+                return S.sample_rows(logits, torch.rand(1, generator=g), max(s.temperature, 1e-6), s.top_k, s.top_p, s.min_p)[0]
         hist = torch.tensor([row.ticket.prompt + row.ticket.tokens], device=logits.device)
         x = transform_logits(logits, hist, torch.tensor([hist.shape[1]], device=logits.device), s, step)
         p = torch.softmax(x, -1)[0]

@@ -103,7 +103,25 @@ def transform_logits(logits: torch.Tensor, history: torch.Tensor, history_len: t
     return x
 
 
+def plain_filters(s: Sampling) -> bool:
+    """True when only temperature / top-k / min-p / top-p shape the distribution (what the sampling kernel does itself)."""
+    return (s.repetition_penalty == 1.0 and not s.presence_penalty and not s.frequency_penalty and s.no_repeat_ngram_size == 0
+            and s.typical_p >= 1.0 and not (s.eos_token_ids and s.min_new_tokens > 0))
+
+
+def row_uniforms(row_keys: Sequence[int], step: int) -> torch.Tensor:
+    """One uniform number per row from the row's keyed generator (the same keys the multinomial draws use)."""
+    return torch.stack([torch.rand(1, generator=K.generator(K.fold_in(k, step), "cpu"))[0] for k in row_keys])
+
+
 def draw(logits: torch.Tensor, s: Sampling, row_keys: Sequence[int], step: int) -> torch.Tensor:
+    """Draw from already transformed logits.  On a GPU: the argmax / inverse-CDF kernels (no per-row host round trip)."""
+    if logits.is_cuda:
+        from ..ops import sample as S
+        if S.kernel_ok(logits):
+            if s.greedy:
+                return S.argmax_rows(logits)
+            return S.sample_rows(logits, row_uniforms(row_keys, step))
     if s.greedy:
         return logits.argmax(-1)
     p = torch.softmax(logits, -1)

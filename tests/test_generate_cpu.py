@@ -59,3 +59,18 @@ def test_beam_and_speculative():
     assert int(g.lengths[0]) == 8
     sp = Speculative(draft=d, lookahead=3).run(m, None, [[2, 3, 4]], 6)
     assert sp.tokens[0, :9].tolist() == _greedy_no_cache(m, [2, 3, 4], 6)    # exact for greedy decoding
+
+
+def test_sample_rows_reference_path_matches_transform_logits():
+    """The sampling op's CPU path keeps the same tokens as the Sampling transforms (no ties in random logits)."""
+    import torch
+    from dew_b200.ops import sample as S
+    from dew_b200.sampling.text import Sampling, transform_logits
+    torch.manual_seed(0)
+    logits = torch.randn(5, 300) * 2
+    s = Sampling(temperature=0.8, top_k=40, top_p=0.9, min_p=0.01)
+    a = S.filtered_reference(logits, s.temperature, s.top_k, s.top_p, s.min_p)
+    b = transform_logits(logits, torch.zeros(5, 1, dtype=torch.long), torch.zeros(5, dtype=torch.long), s, 0)
+    assert torch.equal(torch.isfinite(a), torch.isfinite(b))
+    tok = S.sample_rows(logits, torch.rand(5), s.temperature, s.top_k, s.top_p, s.min_p)
+    assert torch.isfinite(a.gather(-1, tok[:, None])).all()

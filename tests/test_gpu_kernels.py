@@ -504,6 +504,50 @@ def test_gated_delta_net_layer_gpu_matches_cpu_reference():
     assert rel_err(gpu.in_proj_qkvz.weight.grad.cpu(), ref.in_proj_qkvz.weight.grad) <= 8e-2
 
 
+@pytest.mark.parametrize("V,dtype", [(1000, torch.float32), (128256, torch.bfloat16), (32768, torch.float32)])
+def test_argmax_rows_kernel(V, dtype):
+    from dew_b200.ops import sample as S
+    torch.manual_seed(V)
+    x = torch.randn(7, V, device=DEV).to(dtype)
+    x[3, 5] = x[3, 900] = 50.0                                   # a tie: the lower index wins
+    got = S.argmax_rows(x)
+    want = torch.stack([torch.nonzero(r == r.max())[0, 0] for r in x.float()])
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("V,temperature,top_k,top_p,min_p", [(1000, 1.0, None, 1.0, 0.0), (5000, 0.7, 50, 1.0, 0.0),
+                                                            (128256, 1.3, None, 0.9, 0.0), (32768, 0.8, 200, 0.95, 0.02),
+                                                            (777, 1.0, 5, 0.5, 0.0)])
+def test_sample_rows_kernel_filters_and_inverse_cdf(V, temperature, top_k, top_p, min_p):
+    """The kept set equals the thresholds' set, and the drawn token is the inverse CDF of the filtered distribution at u."""
+    from dew_b200.ops import sample as S
+    torch.manual_seed(V)
+    R = 16
+    logits = torch.randn(R, V, device=DEV) * 3
+    u = torch.rand(R, device=DEV)
+    tok, kept = S.sample_rows(logits, u, temperature, top_k, top_p, min_p, return_kept=True)
+    ref = S.filtered_reference(logits, temperature, top_k, top_p, min_p)
+    ref_kept = torch.isfinite(ref).sum(-1)
+    assert (kept.long() - ref_kept).abs().max() <= 1             # a threshold may fall between two nearly equal masses
+    assert torch.isfinite(ref.gather(-1, tok[:, None])).all()    # every draw is a kept token
+    e = torch.exp(ref.double() - ref.double().max(-1, keepdim=True).values)
+    cdf = e.cumsum(-1) / e.sum(-1, keepdim=True)
+    hi = cdf.gather(-1, tok[:, None])[:, 0]
+    lo = hi - (e / e.sum(-1, keepdim=True)).gather(-1, tok[:, None])[:, 0]
+    same_set = kept.long() == ref_kept
+    assert ((u.double() >= lo - 1e-4) & (u.double() <= hi + 1e-4))[same_set].all()
+
+
+def test_sample_rows_kernel_distribution():
+    from dew_b200.ops import sample as S
+    torch.manual_seed(0)
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 3.0, -30.0]], device=DEV).repeat(20000, 1)
+    tok = S.sample_rows(logits, torch.rand(20000, device=DEV), 1.0, 4, 1.0, 0.0)
+    freq = torch.bincount(tok, minlength=6).float() / 20000
+    want = torch.softmax(torch.tensor([2.0, 1.0, 0.0, float("-inf"), 3.0, float("-inf")]), -1).to(DEV)
+    assert (freq - want).abs().max() < 0.015
+
+
 def _gdn_inputs(B, T, H, seed, with_state):
     torch.manual_seed(seed)
     q = torch.nn.functional.normalize(torch.randn(B, T, H, 128, device=DEV), dim=-1).to(torch.bfloat16)
