@@ -65,7 +65,7 @@ class Mamba2(nn.Module):
         if state is not None and T == 1:
             y = scan.ssd_step(xs[:, 0], dt[:, 0], A, Bm[:, 0], Cm[:, 0], state["S"], self.D)[:, None]
         else:
-            y, S = scan.ssd_chunked(xs, dt, A, Bm, Cm, self.D, initial_state=state["S"] if state is not None else None)
+            y, S = scan.ssd(xs, dt, A, Bm, Cm, self.D, initial_state=state["S"] if state is not None else None)
             if state is not None:
                 state["S"].copy_(S)
         y = ops.gated_rms_norm(y.to(x.dtype).reshape(B, T, self.inner), z, self.norm_weight, self.norm_eps)

@@ -132,6 +132,16 @@ def ssd_recurrent(x, dt, A, Bm, Cm, D=None, initial_state=None):
     return y.to(x.dtype), S
 
 
+def ssd(x, dt, A, Bm, Cm, D=None, initial_state=None):
+    """Public entry: CUDA tensors with head dimension 64 and state dimension 128 run the sm_100a scan kernel
+    (``ops/ssd.py``); everything else the loop-free chunked form below."""
+    if x.is_cuda:
+        from . import ssd as K
+        if K.kernel_available(x, Bm):
+            return K.ssd(x, dt, A, Bm, Cm, D, initial_state)
+    return ssd_chunked(x, dt, A, Bm, Cm, D, initial_state)
+
+
 def ssd_chunked(x, dt, A, Bm, Cm, D=None, initial_state=None, chunk: int = CHUNK_SIZE):
     """Chunked SSD: intra-chunk ``(C B^T o decay) X`` plus a chunk-state pass; fp32 accumulation."""
     Bsz, T, H, P = x.shape
@@ -157,13 +167,22 @@ def ssd_chunked(x, dt, A, Bm, Cm, D=None, initial_state=None, chunk: int = CHUNK
     y_diag = torch.einsum("bcijh,bcjhp->bcihp", CB * Lm, xdt)
     decay_to_end = torch.exp(acs[:, :, -1:, :] - acs)                          # [B,Nc,C,H]
     states = torch.einsum("bcjhn,bcjh,bcjhp->bchpn", Bc, decay_to_end, xdt)    # contribution of each chunk
-    S = torch.zeros(Bsz, H, P, N, dtype=f, device=x.device) if initial_state is None else initial_state.to(f)
-    ys = []
-    for c in range(Nc):
-        y_off = torch.einsum("bihn,bhpn,bih->bihp", Cc[:, c], S, torch.exp(acs[:, c]))
-        ys.append(y_diag[:, c] + y_off)
-        S = S * torch.exp(acs[:, c, -1])[..., None, None] + states[:, c]
-    y = torch.stack(ys, 1).reshape(Bsz, Nc * chunk, H, P)[:, :T]
+    S0 = torch.zeros(Bsz, H, P, N, dtype=f, device=x.device) if initial_state is None else initial_state.to(f)
+    # state passing without a loop over chunks: the state on entry to chunk c is sum_{c' < c} exp(sum of the chunk decays
+    # between them) * (chunk c' contribution), one [Nc + 1, Nc + 1] lower-triangular product per (batch, head)
+    tot = acs[:, :, -1, :]                                                      # [B,Nc,H] log decay of each whole chunk
+    csum = torch.cat([torch.zeros_like(tot[:, :1]), tot.cumsum(1)], 1)         # [B,Nc+1,H]
+    seg = csum[:, :, None, :] - csum[:, None, :, :]                            # [B, c, c', H]: decay from the end of chunk c'-1 ... to the start of chunk c
+    lower = torch.tril(torch.ones(Nc + 1, Nc + 1, dtype=torch.bool, device=x.device), -1)[None, :, :, None]
+    contrib = torch.cat([S0[:, None], states], 1)                              # entry 0: the initial state, entry c'+1: chunk c'
+    # state before chunk c = sum_{e <= c} exp(csum[c] - csum[e]) * contrib[e]
+    le = torch.tril(torch.ones(Nc + 1, Nc + 1, dtype=torch.bool, device=x.device))[None, :, :, None]
+    wts = torch.where(le, torch.exp(torch.where(le, seg, torch.zeros_like(seg))), torch.zeros_like(seg))
+    entry = torch.einsum("bceh,behpn->bchpn", wts, contrib)                     # [B,Nc+1,H,P,N]; entry[c] = state before chunk c
+    del lower
+    y_off = torch.einsum("bcihn,bchpn,bcih->bcihp", Cc, entry[:, :Nc], torch.exp(acs))
+    y = (y_diag + y_off).reshape(Bsz, Nc * chunk, H, P)[:, :T]
+    S = entry[:, Nc]
     if D is not None:
         y = y + x.to(f) * D.to(f)[None, None, :, None]
     return y.to(x.dtype), S

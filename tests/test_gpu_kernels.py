@@ -548,6 +548,29 @@ def test_sample_rows_kernel_distribution():
     assert (freq - want).abs().max() < 0.015
 
 
+@pytest.mark.parametrize("B,T,H,G,with_state", [(1, 64, 2, 1, False), (2, 300, 4, 2, True), (1, 1024, 8, 1, False)])
+def test_ssd_scan_kernel_against_recurrent_oracle(B, T, H, G, with_state):
+    from dew_b200.ops import scan
+    torch.manual_seed(T + H)
+    x = torch.randn(B, T, H, 64, device=DEV).to(torch.bfloat16)
+    dt = torch.nn.functional.softplus(torch.randn(B, T, H, device=DEV) - 2)
+    A = -torch.rand(H, device=DEV) * 4 - 0.5
+    Bm = (torch.randn(B, T, G, 128, device=DEV) / 8).to(torch.bfloat16)
+    Cm = (torch.randn(B, T, G, 128, device=DEV) / 8).to(torch.bfloat16)
+    D = torch.randn(H, device=DEV)
+    s0 = torch.randn(B, H, 64, 128, device=DEV) * 0.2 if with_state else None
+    leaves = [t.clone().requires_grad_() for t in (x, dt, Bm, Cm)]
+    y, S = scan.ssd(leaves[0], leaves[1], A, leaves[2], leaves[3], D, s0)
+    ref_leaves = [t.detach().float().requires_grad_() for t in leaves]
+    ry, rS = scan.ssd_recurrent(ref_leaves[0], ref_leaves[1], A, ref_leaves[2], ref_leaves[3], D, s0)
+    assert rel_err(y, ry) <= 2e-2 and rel_err(S, rS) <= 2e-2
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ry.backward(dy.float())
+    for name, a, b in zip(("dx", "ddt", "dB", "dC"), leaves, ref_leaves):
+        assert rel_err(a.grad, b.grad) <= 4e-2, (name, rel_err(a.grad, b.grad))
+
+
 def _gdn_inputs(B, T, H, seed, with_state):
     torch.manual_seed(seed)
     q = torch.nn.functional.normalize(torch.randn(B, T, H, 128, device=DEV), dim=-1).to(torch.bfloat16)
