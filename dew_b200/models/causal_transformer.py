@@ -98,7 +98,13 @@ def _mixer(cfg: TransformerConfig, kind: str, dtype, device) -> nn.Module:
     if kind == "mla":
         from ..nn.mla import MultiHeadLatentAttention
         return MultiHeadLatentAttention(cfg.emb_features, cfg.num_heads, norm_eps=cfg.norm_eps, dtype=dtype, device=device, **cfg.mixer_options)
-    raise ValueError(f"unknown layer type {kind!r}; known: attention, local, gdn, mamba2, mamba, kda, mla")
+    if kind == "lightning":
+        from ..nn.recurrent_mixers import LightningAttention
+        return LightningAttention(cfg.emb_features, layers=cfg.num_layers, norm_eps=cfg.norm_eps, dtype=dtype, device=device, **cfg.mixer_options)
+    if kind == "mamba3":
+        from ..nn.recurrent_mixers import Mamba3
+        return Mamba3(cfg.emb_features, dtype=dtype, device=device, **cfg.mixer_options)
+    raise ValueError(f"unknown layer type {kind!r}; known: attention, local, gdn, mamba2, mamba, mamba3, kda, mla, lightning")
 
 
 class DecoderLayer(nn.Module):
