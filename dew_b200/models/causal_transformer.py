@@ -69,6 +69,7 @@ class TransformerConfig:
     remat: bool = False
     init_std: float = 0.02
     embed_scale: bool = False                         # Gemma: multiply embeddings by sqrt(d)
+    mtp_depth: int = 0                                # multi-token prediction: extra sequential heads for tokens t+2, t+3, ...
 
     def kinds(self) -> List[str]:
         if self.layer_types is None:
@@ -147,6 +148,27 @@ class DecoderLayer(nn.Module):
         return h, self.mlp(n)
 
 
+class MTPBlock(nn.Module):
+    """One multi-token-prediction depth (DeepSeek-V3 style): the previous depth's hidden state and the embedding of the
+    next known token are normalised, concatenated, projected back to the model width and passed through one decoder
+    layer; the shared head then predicts one token further ahead.  Reference: ``mtp_weight`` of
+    src/dew/objectives/lm/objective.py:1348-1560 and the MTP fields of src/dew/nn/backbones/causal_transformer.py:165-423."""
+
+    def __init__(self, cfg: TransformerConfig, index: int, dtype=None, device=None):
+        super().__init__()
+        self.hidden_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
+        self.token_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
+        self.proj = Linear(2 * cfg.emb_features, cfg.emb_features, axes=("embed", "embed"), init_std=cfg.init_std, dtype=dtype, device=device)
+        self.layer = DecoderLayer(cfg, cfg.num_layers + index, "attention", dtype, device)
+        self.out_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
+
+    def forward(self, h_prev, token_emb, cos, sin, segment_ids):
+        x = self.proj(torch.cat([self.hidden_norm(h_prev), self.token_norm(token_emb)], -1))
+        h, branch = self.layer(x, None, cos, sin, None, segment_ids, None)
+        n, _ = self.out_norm(h, branch)
+        return n
+
+
 @register("causal_transformer")
 class CausalTransformer(nn.Module):
     def __init__(self, config: Optional[TransformerConfig] = None, dtype=None, device=None, **fields):
@@ -160,7 +182,28 @@ class CausalTransformer(nn.Module):
         self.final_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
         self.head = None if cfg.tie_embeddings else Linear(cfg.emb_features, cfg.vocab_size, axes=("embed", "vocab"),
                                                            init_std=cfg.init_std, dtype=dtype, device=device)
+        self.mtp = nn.ModuleList([MTPBlock(cfg, i, dtype, device) for i in range(cfg.mtp_depth)]) if cfg.mtp_depth > 0 else None
         self._rope = None
+
+    def mtp_hiddens(self, hidden: torch.Tensor, tokens: torch.Tensor, segment_ids=None) -> List[torch.Tensor]:
+        """Hidden states of the multi-token-prediction depths.  ``hidden [B,S,d]`` is the trunk's final hidden state for the
+        inputs ``tokens[:, :S]``; ``tokens [B,S+1]`` carries one more token.  Depth k (1-based) returns ``[B, S-k, d]``: position
+        t combines depth k-1's state at t with the embedding of token t+k and predicts token t+k+1."""
+        outs = []
+        cos, sin = self.rope_tables(hidden.device)
+        S = hidden.shape[1]
+        h = hidden
+        for k, block in enumerate(self.mtp or (), start=1):
+            n = S - k
+            if n <= 0:
+                break
+            emb = self.embed(tokens[:, k:k + n])
+            if self.config.embed_scale:
+                emb = emb * (self.config.emb_features ** 0.5)
+            seg = None if segment_ids is None else segment_ids[:, :n]
+            h = block(h[:, :n], emb, cos, sin, seg)
+            outs.append(h)
+        return outs
 
     # ------------------------------------------------------------------ helpers
     def head_weight(self) -> torch.Tensor:

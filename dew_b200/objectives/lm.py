@@ -68,8 +68,22 @@ class LMObjective(Objective):
         total, mass = ops.linear_cross_entropy(hidden.reshape(B * S, d), w, targets.reshape(-1), ignore_index=-100,
                                                z_loss=self.z_loss, softcap=cap, chunk=tile)
         massf = mass.to(torch.float32)
+        mtp_metrics = {}
+        if self.mtp_weight and getattr(self.model, "mtp", None) is not None and variables is None:
+            # depth k scores token t+k+1 from position t: the main targets shifted by k, averaged over the depths
+            tokens = batch["tokens"]
+            depths = self.model.mtp_hiddens(hidden, tokens[:, : S + 1], seg)
+            extra = hidden.new_zeros((), dtype=torch.float32)
+            for k, hk in enumerate(depths, start=1):
+                tk = targets[:, k:]
+                lk, mk = ops.linear_cross_entropy(hk.reshape(-1, d), w, tk.reshape(-1), ignore_index=-100, softcap=cap, chunk=tile)
+                mkf = mk.to(torch.float32).clamp_min(1.0)
+                extra = extra + lk / mkf
+                mtp_metrics[f"mtp_loss_{k}"] = Ratio(lk.detach(), mkf)
+            if depths:
+                total = total + self.mtp_weight * (extra / len(depths)) * massf
         aux = Aux(metrics={"perplexity": Exponentiated(Ratio(total.detach(), massf)),
-                           "tokens": Ratio(massf, torch.ones((), device=massf.device))})
+                           "tokens": Ratio(massf, torch.ones((), device=massf.device)), **mtp_metrics})
         moe_aux = getattr(self.model, "pop_aux", None)
         if moe_aux is not None:
             extra = moe_aux()

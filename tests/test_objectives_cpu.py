@@ -155,3 +155,27 @@ def test_consistency_and_world_model_objectives():
     tr = dew.Trainer(wobj, dew.OptimConfig(learning_rate=1e-2, weight_decay=0.0), tracker=(t := dew.MemoryTracker()))
     tr.fit(dew.Loader(lambda part: iter([batch] * 30), batch=8), steps=20, log_every=5)
     assert t.rows[-1]["loss"] < t.rows[0]["loss"]
+
+
+def test_multi_token_prediction_heads_train():
+    """MTP depths add their cross-entropy (weighted) to the loss, report their own metrics and receive gradients."""
+    import torch
+    from dew_b200.models import CausalTransformer
+    from dew_b200.objectives.base import Step
+    from dew_b200.objectives.lm import LMObjective
+    torch.manual_seed(0)
+    model = CausalTransformer(vocab_size=50, emb_features=32, num_layers=2, num_heads=4, head_dim=8, mlp_features=64, max_seq_len=32,
+                              mtp_depth=2)
+    plain = LMObjective(model, 16)
+    mtp = LMObjective(model, 16, mtp_weight=0.3)
+    batch = {"tokens": torch.randint(0, 50, (3, 17))}
+    s0, _ = plain.loss(None, batch, Step(train=True))
+    s1, aux = mtp.loss(None, batch, Step(train=True))
+    l0, l1 = float(s0.value()), float(s1.value())
+    assert l1 > l0 and "mtp_loss_1" in aux.metrics and "mtp_loss_2" in aux.metrics
+    want = l0 + 0.3 * 0.5 * (float(aux.metrics["mtp_loss_1"].value()) + float(aux.metrics["mtp_loss_2"].value()))
+    assert abs(l1 - want) < 1e-4
+    s1.value().backward()
+    assert model.mtp[1].proj.weight.grad.abs().sum() > 0
+    hs = model.mtp_hiddens(model(batch["tokens"][:, :-1], return_hidden=True), batch["tokens"])
+    assert [h.shape[1] for h in hs] == [15, 14]
