@@ -1,0 +1,51 @@
+"""Interval books, token clock and the fit search."""
+import math
+
+import pytest
+import torch
+
+from dew_b200.training import interval as I
+from dew_b200.training.planning import FitSearch, NoPlanFits, Plan, ladder
+
+
+def test_book_sums_and_nonfinite_streak():
+    it = I.Interval({"log": 2, "checkpoint": 4})
+    it.add(torch.tensor(6.0), torch.tensor(3.0), examples=2, tokens=10, flops=100.0)
+    it.add(torch.tensor(float("nan")), torch.tensor(3.0), examples=2, tokens=10, committed=False)
+    assert it.due(2) == ["log"] and it.due(4) == ["log", "checkpoint"] and it.due(3) == []
+    row = it.take("log")
+    assert row["loss"] == pytest.approx(2.0) and row["steps"] == 2 and row["nonfinite_steps"] == 1
+    assert it.clock.consumed_tokens == 20 and it.clock.committed_tokens == 10
+    assert I.streak_of(it.books["log"]).current == 1            # the streak survives the restart of the sums
+    for _ in range(4):
+        it.add(torch.tensor(float("inf")), torch.tensor(1.0))
+    with pytest.raises(I.NonFiniteLoss):
+        I.checked_finite(I.streak_of(it.books["log"]), 6, skips=True)
+    it.add(torch.tensor(1.0), torch.tensor(1.0))
+    assert I.streak_of(it.books["log"]).current == 0
+    both = it.take("checkpoint")
+    assert both["steps"] == 7 and math.isfinite(both["loss"])
+
+
+def test_token_clock_control_round_trip_and_crossing():
+    c = I.TokenClock()
+    c.dispatched(4, 100)
+    c.update_boundary()
+    before = c.committed_tokens
+    c.dispatched(4, 100)
+    c.update_boundary()
+    assert c.crossed(before, 150) and not c.crossed(before, 250)
+    again = I.TokenClock.from_control(c.control())
+    assert again.committed_tokens == 200 and again.consumed_examples == 8
+
+
+def test_fit_search_walks_the_ladder():
+    assert ladder(8)[:4] == [Plan(8, False), Plan(8, True), Plan(4, False), Plan(4, True)]
+    # memory model: 10 GiB of state + 3 GiB per row, a third of the activations with rematerialisation
+    gib = 1 << 30
+    cost = lambda p: 10 * gib + p.microbatch * 3 * gib // (3 if p.remat else 1)
+    s = FitSearch(8, capacity_bytes=24 * gib, limit_fraction=0.9, measure=cost)
+    assert s.run() == Plan(8, True)                      # 18 GiB fits 21.6; 34 GiB without remat does not
+    assert [t.fits for t in s.trials] == [False, True] and "remat" in s.report()
+    with pytest.raises(NoPlanFits):
+        FitSearch(2, capacity_bytes=8 * gib, measure=cost).run()
