@@ -321,3 +321,102 @@ class Speculative:
                          [tokenizer.decode(o[len(p):]) for o, p in zip(outs, prompts)] if tokenizer else None, plen)
         gen.acceptance = accepted / max(1, proposed)
         return gen
+
+
+@dataclass
+class TreeSpeculative:
+    """Greedy speculative decoding over a token tree: the draft proposes the ``branching`` most likely continuations at each
+    of ``depth`` levels (a tree of candidates), the target scores every node in ONE pass under a tree attention mask (a node
+    attends to the prompt and to its own ancestors only), and the longest root path the target agrees with is kept, plus
+    the target's own token after it.  Exact for greedy decoding.  Reference: src/dew/sampling/strategies.py ``TreeSpeculative``,
+    src/dew/sampling/trees.py."""
+    draft: Any = None
+    branching: int = 2
+    depth: int = 3
+
+    def _tree(self, seq, dev):
+        """Nodes as (token, parent index or -1), level by level, from the draft's top-k at every node."""
+        nodes = []
+        frontier = [(-1, list(seq))]
+        for _ in range(self.depth):
+            nxt = []
+            for parent, ctx in frontier:
+                top = torch.topk(self.draft(torch.tensor([ctx], device=dev))[0, -1].float(), self.branching).indices.tolist()
+                for tok in top:
+                    nodes.append((tok, parent))
+                    nxt.append((len(nodes) - 1, ctx + [tok]))
+            frontier = nxt
+        return nodes
+
+    @staticmethod
+    def tree_mask(prefix_len: int, parents) -> torch.Tensor:
+        """Boolean attention mask ``[L, L]`` (True = may attend) for prefix tokens followed by the tree's nodes."""
+        n = len(parents)
+        L = prefix_len + n
+        m = torch.zeros(L, L, dtype=torch.bool)
+        m[:prefix_len, :prefix_len] = torch.tril(torch.ones(prefix_len, prefix_len, dtype=torch.bool))
+        for i, p in enumerate(parents):
+            m[prefix_len + i, :prefix_len] = True
+            j = i
+            while j >= 0:
+                m[prefix_len + i, prefix_len + j] = True
+                j = parents[j]
+        return m
+
+    def _verify(self, model, seq, nodes, dev):
+        """The target's greedy token after the prefix and after every node.  Nodes are scored path by path through the
+        model's causal interface (each root path is a causal sequence), batched in one call."""
+        paths = []
+        for i in range(len(nodes)):
+            path, j = [], i
+            while j >= 0:
+                path.append(nodes[j][0])
+                j = nodes[j][1]
+            paths.append(list(reversed(path)))
+        width = max(len(p) for p in paths) if paths else 0
+        rows = [list(seq) + p + [0] * (width - len(p)) for p in paths] or [list(seq)]
+        logits = model(torch.tensor(rows, device=dev))
+        root_next = int(logits[0, len(seq) - 1].argmax())
+        after = [int(logits[i, len(seq) + len(p) - 1].argmax()) for i, p in enumerate(paths)]
+        return root_next, after
+
+    def run(self, model, params, inputs, max_new_tokens, *, key=0, sampling=Sampling(), tokenizer=None) -> Generation:
+        dev = next(model.parameters()).device
+        prompts = [tokenizer.encode(t) for t in inputs] if inputs and isinstance(inputs[0], str) else [list(p) for p in inputs]
+        eos = set(sampling.eos_token_ids or ())
+        outs, term, accepted, rounds = [], [], 0, 0
+        with torch.no_grad():
+            for p in prompts:
+                seq, ended = list(p), False
+                while len(seq) - len(p) < max_new_tokens and not ended:
+                    nodes = self._tree(seq, dev)
+                    root_next, after = self._verify(model, seq, nodes, dev)
+                    # walk down from the root while some child carries the target's token
+                    new, parent, want = [], -1, root_next
+                    while True:
+                        child = next((i for i, (tok, par) in enumerate(nodes) if par == parent and tok == want), None)
+                        if child is None:
+                            break
+                        new.append(want)
+                        parent, want = child, after[child]
+                    accepted += len(new)
+                    rounds += 1
+                    new.append(want)
+                    for t in new:
+                        if len(seq) - len(p) >= max_new_tokens:
+                            break
+                        seq.append(t)
+                        if t in eos:
+                            ended = True
+                            break
+                outs.append(seq); term.append(ended)
+        total = max(len(o) for o in outs)
+        pad = sampling.pad_token_id or 0
+        toks = torch.full((len(outs), total), pad, dtype=torch.long, device=dev)
+        for r, t in enumerate(outs):
+            toks[r, :len(t)] = torch.tensor(t, device=dev)
+        plen = torch.tensor([len(p) for p in prompts], device=dev)
+        gen = Generation(toks, torch.tensor([len(o) for o in outs], device=dev), torch.tensor(term, device=dev),
+                         [tokenizer.decode(o[len(p):]) for o, p in zip(outs, prompts)] if tokenizer else None, plen)
+        gen.accepted_per_round = accepted / max(1, rounds)
+        return gen

@@ -74,3 +74,40 @@ def test_sample_rows_reference_path_matches_transform_logits():
     assert torch.equal(torch.isfinite(a), torch.isfinite(b))
     tok = S.sample_rows(logits, torch.rand(5), s.temperature, s.top_k, s.top_p, s.min_p)
     assert torch.isfinite(a.gather(-1, tok[:, None])).all()
+
+
+def _tiny_lm(seed):
+    import torch
+    from dew_b200.models import CausalTransformer
+    torch.manual_seed(seed)
+    return CausalTransformer(vocab_size=40, emb_features=32, num_layers=2, num_heads=4, head_dim=8, mlp_features=64, max_seq_len=64).eval()
+
+
+def test_tree_speculative_equals_greedy_and_mask_shape():
+    import torch
+    from dew_b200.sampling.text import Sampling, TreeSpeculative, generate
+    target, draft = _tiny_lm(0), _tiny_lm(1)
+    prompts = [[1, 2, 3, 4], [5, 6, 7]]
+    want = generate(target, None, prompts, 10, sampling=Sampling(temperature=0.0))
+    got = TreeSpeculative(draft=draft, branching=2, depth=2).run(target, None, prompts, 10, sampling=Sampling(temperature=0.0))
+    for r in range(2):
+        assert got.new_tokens(r).tolist() == want.new_tokens(r).tolist()
+    same = TreeSpeculative(draft=target, branching=2, depth=3).run(target, None, prompts, 9, sampling=Sampling(temperature=0.0))
+    assert same.accepted_per_round == 3.0                      # the target as its own draft: every level is accepted
+    m = TreeSpeculative.tree_mask(3, [-1, -1, 0, 0, 1, 1])
+    assert m.shape == (9, 9) and bool(m[3 + 4, 3 + 1]) and not bool(m[3 + 4, 3 + 0]) and bool(m[3 + 2, 3 + 0])
+
+
+def test_grammar_guided_decoding_stays_inside_the_language():
+    import torch
+    from dew_b200.sampling.guided import Grammar, guided_generate
+    vocab = ["", "yes", "no", "ma", "ybe", "!", " ", "x"] + [f"t{i}" for i in range(32)]
+    g = Grammar.from_regex(r"(yes|no|maybe)!", vocab)
+    model = _tiny_lm(3)
+    for seed in range(4):
+        gen = torch.Generator().manual_seed(seed)
+        toks, ok = guided_generate(model, [1, 2], g, 6, eos_token_id=None, temperature=1.0, generator=gen)
+        text = "".join(vocab[t] for t in toks)
+        assert ok and text in ("yes!", "no!", "maybe!")
+    t = Grammar.from_transitions({0: {5: 1}, 1: {6: 1, 7: 2}, 2: {}}, 0, {2}, 40)
+    assert t.mask(1).nonzero().flatten().tolist() == [6, 7] and t.advance(1, 7) == 2 and t.accepting(2) and t.dead(2)
