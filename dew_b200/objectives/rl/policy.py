@@ -77,3 +77,67 @@ class PPO(Objective):
         m = mask.sum()
         return Ratio((per * mask).sum(), m), Aux(metrics={"entropy": Ratio((ent.detach() * mask).sum(), m),
                                                            "value_loss": Ratio((value.detach() * mask).sum(), m)})
+
+
+class FlowGRPO(Objective):
+    """GRPO for flow-matching samplers (Flow-GRPO): the ODE sampler is turned into an SDE with the same marginals so that
+    every denoising step is a Gaussian policy, ``x_{t-dt} ~ N(mean_theta(x_t, t), sigma_t^2 dt)``; images sampled in groups from
+    one prompt are rewarded, rewards are whitened inside the group, and the clipped policy-gradient ratio is taken per
+    step from the Gaussian log-densities (old policy = the sampler that produced the trajectory), with an optional KL
+    pull towards a frozen reference velocity.  ``batch``: ``x [rows, steps + 1, ...]`` the stored trajectory, ``t [steps + 1]`` its
+    time grid (1 -> 0), ``old_logp [rows, steps]``, ``rewards [rows]``.  The model is called as ``model(x, t)`` -> velocity.
+    Reference: src/dew/objectives/rl/ (FlowGRPO)."""
+
+    def __init__(self, model, group: int = 4, clip: float = 0.2, noise_level: float = 0.7, kl_weight: float = 0.0, reference=None):
+        self.model, self.group, self.clip, self.a, self.kl_weight, self.reference = model, group, clip, noise_level, kl_weight, reference
+        self.ema_decay = None
+
+    def step_distribution(self, variables, x, t, dt):
+        """Mean and standard deviation of the SDE step from ``t`` to ``t - dt`` on the path ``x_t = (1 - t) x_0 + t eps``."""
+        tt = t.clamp(1e-3, 1 - 1e-3)
+        v = self.apply(variables, x, t.expand(x.shape[0])).float()
+        sigma = self.a * torch.sqrt(tt / (1 - tt))
+        # score of the marginal expressed through the velocity: x_0 = x - t v, eps = x + (1 - t) v
+        drift = v + (sigma ** 2 / (2 * tt)) * (x + (1 - tt) * v)
+        mean = x - drift * dt
+        return mean, sigma * torch.sqrt(dt), v
+
+    def logp(self, variables, x_t, x_next, t, dt):
+        mean, std, v = self.step_distribution(variables, x_t, t, dt)
+        lp = -0.5 * (((x_next - mean) / std) ** 2).reshape(x_t.shape[0], -1).sum(1) - x_t[0].numel() * torch.log(std)
+        return lp, v
+
+    @torch.no_grad()
+    def rollout(self, variables, shape, steps: int, generator=None, device="cpu"):
+        """Sample trajectories with the SDE sampler: returns ``x [rows, steps + 1, ...]``, the time grid and ``old_logp``."""
+        x = torch.randn(shape, generator=generator).to(device)
+        grid = torch.linspace(1.0, 0.0, steps + 1, device=device)
+        xs, lps = [x], []
+        for i in range(steps):
+            t, dt = grid[i], grid[i] - grid[i + 1]
+            mean, std, _ = self.step_distribution(variables, x, t, dt)
+            x = mean + std * torch.randn(shape, generator=generator).to(device)
+            lp, _ = self.logp(variables, xs[-1], x, t, dt)
+            xs.append(x)
+            lps.append(lp)
+        return torch.stack(xs, 1), grid, torch.stack(lps, 1)
+
+    def loss(self, variables, batch, step: Step):
+        x, grid, old, rewards = batch["x"].float(), batch["t"].float(), batch["old_logp"].float(), batch["rewards"].float()
+        rows, steps = old.shape
+        adv = group_advantages(rewards, self.group)
+        total = x.new_zeros(())
+        kl = x.new_zeros(())
+        for i in range(steps):
+            t, dt = grid[i], grid[i] - grid[i + 1]
+            lp, v = self.logp(variables, x[:, i], x[:, i + 1], t, dt)
+            ratio = torch.exp(lp - old[:, i])
+            surr = torch.minimum(ratio * adv, ratio.clamp(1 - self.clip, 1 + self.clip) * adv)
+            total = total - surr.sum()
+            if self.kl_weight and self.reference is not None:
+                with torch.no_grad():
+                    v_ref = self.reference(x[:, i], t.expand(rows)).float()
+                kl = kl + ((v - v_ref) ** 2).reshape(rows, -1).mean(1).sum()
+        total = total + self.kl_weight * kl
+        mass = torch.tensor(float(rows * steps), device=x.device)
+        return Ratio(total, mass), Aux(metrics={"reward": Ratio(rewards.sum(), torch.tensor(float(rows), device=x.device))})
