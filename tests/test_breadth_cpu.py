@@ -140,3 +140,28 @@ def test_mixture_is_reproducible_and_restorable_and_scoring_and_clients():
     sent = {}
     client = OpenAIClient(model="m", transport=lambda url, body, headers, timeout: sent.update(url=url, body=body) or {"choices": [{"message": {"content": "hi"}}]})
     assert client.chat([{"role": "user", "content": "x"}]) == "hi" and sent["url"].endswith("/chat/completions") and sent["body"]["model"] == "m"
+
+
+def test_gguf_round_trip_and_block_formats(tmp_path):
+    import numpy as np
+    import torch
+    from dew_b200.interop import gguf
+    torch.manual_seed(0)
+    tensors = {"tok.weight": torch.randn(8, 64), "blk.0.w": torch.randn(4, 32).half(), "blk.0.b": torch.randn(64).to(torch.bfloat16),
+               "blk.0.q": torch.randn(2, 64)}
+    path = str(tmp_path / "m.gguf")
+    gguf.write(path, {"general.architecture": "llama", "llama.block_count": 1, "tokenizer.ggml.tokens": ["a", "b"], "rope": 10000.0},
+               tensors, quantize={"blk.0.q": gguf.Q8_0})
+    meta, got = gguf.read(path)
+    assert meta["general.architecture"] == "llama" and meta["llama.block_count"] == 1 and meta["tokenizer.ggml.tokens"] == ["a", "b"]
+    assert torch.equal(got["tok.weight"], tensors["tok.weight"]) and torch.equal(got["blk.0.w"], tensors["blk.0.w"])
+    assert torch.equal(got["blk.0.b"], tensors["blk.0.b"])
+    assert (got["blk.0.q"] - tensors["blk.0.q"]).abs().max() < 0.03           # 8-bit blocks
+    infos = gguf.read(path, load_tensors=False)[1]
+    assert [i.name for i in infos] == list(tensors) and infos[0].shape == (8, 64)
+    # Q4_0: value = (nibble - 8) * d, low nibbles first
+    d = np.float16(0.5)
+    raw = np.zeros(1, dtype=np.dtype([("d", "<f2"), ("q", "u1", (16,))]))
+    raw["d"], raw["q"] = d, np.arange(16, dtype=np.uint8) | (np.arange(15, -1, -1, dtype=np.uint8) << 4)
+    vals = gguf.dequantize(raw.tobytes(), gguf.Q4_0, (32,))
+    assert vals[:16].tolist() == [(i - 8) * 0.5 for i in range(16)] and vals[16:].tolist() == [(15 - i - 8) * 0.5 for i in range(16)]
