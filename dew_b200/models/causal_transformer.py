@@ -70,6 +70,8 @@ class TransformerConfig:
     init_std: float = 0.02
     embed_scale: bool = False                         # Gemma: multiply embeddings by sqrt(d)
     mtp_depth: int = 0                                # multi-token prediction: extra sequential heads for tokens t+2, t+3, ...
+    hyper_connections: int = 0                        # n > 1: n residual streams with learned read / write weights per sub-layer
+    altup: int = 0                                    # K > 1: AltUp - K blocks, one of which every sub-layer computes on
 
     def kinds(self) -> List[str]:
         if self.layer_types is None:
@@ -126,6 +128,27 @@ class DecoderLayer(nn.Module):
                               dtype=dtype, device=device)
         self.sparse = sparse
         self.tp = None          # set by parallel.tp.tensor_parallelize: branches are then partial sums over ranks
+        self.streams = None
+        if cfg.hyper_connections > 1 or cfg.altup > 1:
+            from ..nn.streams import AltUp, HyperConnections
+            if cfg.hyper_connections > 1:
+                self.streams = nn.ModuleList([HyperConnections(cfg.emb_features, cfg.hyper_connections, 2 * index + j, dtype=dtype, device=device)
+                                              for j in range(2)])
+            else:
+                self.streams = nn.ModuleList([AltUp(cfg.altup, 2 * index + j, device=device) for j in range(2)])
+
+    def forward_streams(self, H, cos, sin, positions, segment_ids, cache):
+        """The layer over several residual streams ``H [B,S,n,d]``: each sub-layer reads its input from the streams, and its
+        output is written back by the learned connection (no fused add + norm on this path)."""
+        x, ctx = self.streams[0].read(H)
+        n = self.input_norm(x)
+        if self.kind in ("attention", "local", "mla"):
+            a = self.mixer(n, cos, sin, positions, segment_ids, cache, self.index)
+        else:
+            a = self.mixer(n, segment_ids=segment_ids, cache=cache, layer=self.index)
+        H = self.streams[0].write(H, a, ctx)
+        x, ctx = self.streams[1].read(H)
+        return self.streams[1].write(H, self.mlp(self.post_norm(x)), ctx)
 
     def _norm(self, norm, h, branch):
         """Add the pending branch into the stream and normalise; under tensor parallelism the branch is a partial sum
@@ -223,6 +246,18 @@ class CausalTransformer(nn.Module):
         if cfg.embed_scale:
             h = h * (cfg.emb_features ** 0.5)
         cos, sin = self.rope_tables(h.device)
+        n_streams = max(cfg.hyper_connections, cfg.altup)
+        if n_streams > 1:
+            from ..nn.streams import expand_streams
+            H = expand_streams(h, n_streams)
+            for layer in self.layers:
+                if cfg.remat and train and torch.is_grad_enabled():
+                    H = ckpt.checkpoint(layer.forward_streams, H, cos, sin, positions, segment_ids, cache, use_reentrant=False)
+                else:
+                    H = layer.forward_streams(H, cos, sin, positions, segment_ids, cache)
+            # hyper-connections sum the streams; AltUp averages its blocks
+            h = H.sum(2) if cfg.hyper_connections > 1 else H.mean(2)
+            return self.final_norm(h)
         branch = None
         for layer in self.layers:
             if cfg.remat and train and torch.is_grad_enabled():

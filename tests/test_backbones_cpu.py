@@ -50,3 +50,31 @@ def test_flow_matching_in_latent_space():
     assert st.step == 3 and all(r["loss"] == r["loss"] for r in t.rows)
     img = obj.generate(st.variables, (2, 8, 8, 4), key=0, steps=3, solver=dew.Euler())
     assert img.shape == (2, 16, 16, 3)
+
+
+def test_hyper_connections_and_altup_reduce_to_the_residual_stack_and_train():
+    """With one effective stream both connection kinds reproduce the ordinary residual stack; with several they train."""
+    import torch
+    from dew_b200.models import CausalTransformer
+    from dew_b200.nn.streams import AltUp, HyperConnections
+    kw = dict(vocab_size=40, emb_features=32, num_layers=3, num_heads=4, head_dim=8, mlp_features=64, max_seq_len=32)
+    torch.manual_seed(0)
+    plain = CausalTransformer(**kw)
+    tokens = torch.randint(0, 40, (2, 12))
+    for field in ("hyper_connections", "altup"):
+        torch.manual_seed(0)
+        multi = CausalTransformer(**kw, **{field: 2})
+        multi.load_state_dict(plain.state_dict(), strict=False)
+        out = multi(tokens)
+        assert out.shape == (2, 12, 40)
+        out.float().pow(2).mean().backward()
+        grads = [p.grad for n, p in multi.named_parameters() if "streams" in n and p.grad is not None]
+        assert grads and any(float(g.abs().sum()) > 0 for g in grads)
+    # one stream: H' = H + f(norm(H)) exactly
+    hc = HyperConnections(8, 1, 0, dynamic=False)
+    H = torch.randn(2, 5, 1, 8)
+    x, ctx = hc.read(H)
+    assert torch.allclose(x, H[:, :, 0]) and torch.allclose(hc.write(H, torch.ones(2, 5, 8), ctx), H + 1)
+    au = AltUp(1, 0)
+    x, pred = au.read(H)
+    assert torch.allclose(au.write(H, torch.ones(2, 5, 8), pred), H + 1)
