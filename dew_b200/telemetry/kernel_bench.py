@@ -185,6 +185,81 @@ def bench_gdn(out, peaks, flush, iters=10, shapes=None):
              scan_fwd_ms=t_s.median_ms)
 
 
+def bench_ssd(out, peaks, flush, iters=10, shapes=None):
+    """Mamba-2 SSD forward: the scan kernel against the loop-free chunked form in PyTorch."""
+    from ..ops import scan
+    for B, T, H, G in shapes or [(1, 4096, 64, 1), (2, 8192, 32, 1)]:
+        x = torch.randn(B, T, H, 64, device="cuda").to(torch.bfloat16)
+        dt = torch.nn.functional.softplus(torch.randn(B, T, H, device="cuda") - 2)
+        A = -torch.rand(H, device="cuda") * 4 - 0.5
+        Bm = (torch.randn(B, T, G, 128, device="cuda") / 8).to(torch.bfloat16)
+        Cm = (torch.randn(B, T, G, 128, device="cuda") / 8).to(torch.bfloat16)
+        with torch.no_grad():
+            from ..ops import ssd as K
+            t_k = device_time(lambda: scan.ssd(x, dt, A, Bm, Cm), iters=iters, flush=flush)
+            prep = K.prepare(x, dt, A, Bm, Cm)
+            t_s = device_time(lambda: K.scan_cuda(*prep, None), iters=iters, flush=flush)
+            t_t = device_time(lambda: scan.ssd_chunked(x, dt, A, Bm, Cm), iters=max(2, iters // 3), flush=flush)
+        L.check_status()
+        _row(out, kernel="ssd", B=B, T=T, H=H, G=G, fwd_ms=t_k.median_ms, scan_kernel_ms=t_s.median_ms, torch_chunked_ms=t_t.median_ms)
+
+
+def bench_sampling(out, peaks, flush, iters=10):
+    """Token draws over a 128256-entry vocabulary, 128 rows: the kernels against the PyTorch transforms + multinomial."""
+    from ..ops import sample as S
+    from ..sampling.text import Sampling, transform_logits
+    R, V = 128, 128256
+    logits = torch.randn(R, V, device="cuda") * 3
+    u = torch.rand(R, device="cuda")
+    s = Sampling(temperature=0.8, top_k=50, top_p=0.95, min_p=0.02)
+    hist, hl = torch.zeros(R, 1, dtype=torch.long, device="cuda"), torch.zeros(R, dtype=torch.long, device="cuda")
+
+    def torch_path():
+        x = transform_logits(logits, hist, hl, s, 0)
+        return torch.multinomial(torch.softmax(x, -1), 1)
+
+    t_a = device_time(lambda: S.argmax_rows(logits), iters=iters, flush=flush)
+    t_ta = device_time(lambda: logits.argmax(-1), iters=iters, flush=flush)
+    t_s = device_time(lambda: S.sample_rows(logits, u, s.temperature, s.top_k, s.top_p, s.min_p), iters=iters, flush=flush)
+    t_ts = device_time(torch_path, iters=iters, flush=flush)
+    bytes_ = R * V * 4
+    _row(out, kernel="sampling", rows=R, vocab=V, argmax_ms=t_a.median_ms, argmax_gbs=bytes_ / t_a.median_ms / 1e6,
+         argmax_frac_of_measured=bytes_ / t_a.median_ms / 1e6 / peaks["hbm_gbs"], torch_argmax_ms=t_ta.median_ms,
+         sample_ms=t_s.median_ms, torch_filters_multinomial_ms=t_ts.median_ms)
+
+
+def bench_moe(out, peaks, flush, iters=10):
+    """Single-rank token exchange (config-3 layer shape: 16384 tokens x 2048, 64 experts, top 6): plan + dispatch + combine on
+    the kernels against the PyTorch index-op chain."""
+    from ..ops import grouped as G
+    from ..ops.routing import route
+    from ..parallel.ep import TokenExchange
+    T, d, E, k = 16384, 2048, 64, 6
+    x = torch.randn(T, d, device="cuda").to(torch.bfloat16)
+    logits = torch.randn(T, E, device="cuda")
+    w, ids, _ = route(logits, None, k, "softmax", True, 1.0)
+    ex = TokenExchange(E, "self")
+    plan = ex.plan(ids, d)
+    rows = ex.push(x, plan)
+
+    def torch_chain():
+        layout = G.group_layout(ids.reshape(-1), E)
+        xs = G.permute(x, layout, k)
+        return G.combine(xs, layout, w, T)
+
+    t_r = device_time(lambda: route(logits, None, k, "softmax", True, 1.0), iters=iters, flush=flush)
+    t_tr = device_time(lambda: torch.topk(torch.softmax(logits, -1), k), iters=iters, flush=flush)
+    t_p = device_time(lambda: ex.plan(ids, d), iters=iters, flush=flush)
+    t_d = device_time(lambda: ex.push(x, plan), iters=iters, flush=flush)
+    t_c = device_time(lambda: ex.pull(rows, plan, w), iters=iters, flush=flush)
+    t_t = device_time(torch_chain, iters=iters, flush=flush)
+    L.check_status()
+    moved = T * k * d * 2
+    _row(out, kernel="moe_exchange", tokens=T, d=d, experts=E, top_k=k, route_ms=t_r.median_ms, torch_softmax_topk_ms=t_tr.median_ms,
+         plan_ms=t_p.median_ms, dispatch_ms=t_d.median_ms, combine_ms=t_c.median_ms, torch_layout_permute_combine_ms=t_t.median_ms,
+         combine_gbs=(moved + T * d * 2) / t_c.median_ms / 1e6)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=None)
@@ -218,6 +293,12 @@ def main(argv=None):
         bench_attention(out, peaks, flush, iters=args.iters)
     if "gdn" in only:
         bench_gdn(out, peaks, flush, iters=args.iters)
+    if "ssd" in only:
+        bench_ssd(out, peaks, flush, iters=args.iters)
+    if "sampling" in only:
+        bench_sampling(out, peaks, flush, iters=args.iters)
+    if "moe" in only:
+        bench_moe(out, peaks, flush, iters=args.iters)
 
 
 if __name__ == "__main__":
