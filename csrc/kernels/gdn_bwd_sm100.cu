@@ -94,8 +94,8 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
                      const __grid_constant__ CUtensorMap tst, const __grid_constant__ CUtensorMap tds,
                      const float* __restrict__ gc, const float* __restrict__ beta, __nv_bfloat16* __restrict__ dKt,
                      __nv_bfloat16* __restrict__ dVt, __nv_bfloat16* __restrict__ dv, float* __restrict__ dq_part,
-                     float* __restrict__ dk_part, float* __restrict__ gpart, float* __restrict__ bpart, int T, int H, int Tp,
-                     int N, float scale, int* __restrict__ err) {
+                     float* __restrict__ dk_part, float* __restrict__ gpart, float* __restrict__ bpart, int T, int H, int rep,
+                     int Tp, int N, float scale, int* __restrict__ err) {
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) atomicCAS(err, 0, ERR_BAD_ARG);
@@ -146,8 +146,8 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
 
   if (tid == 0) {
     mbar_expect_tx(bar_k, T32);
-    tma_load_4d(sK, &tk, bar_k, 0, h, t0, b);
-    tma_load_4d(sK + PT * 128, &tk, bar_k, 64, h, t0, b);
+    tma_load_4d(sK, &tk, bar_k, 0, h / rep, t0, b);                       // `rep` value heads share a key head
+    tma_load_4d(sK + PT * 128, &tk, bar_k, 64, h / rep, t0, b);
     if (!mbar_wait(bar_k, 0, abort_flag)) atomicCAS(err, 0, ERR_WAIT_FULL);
     else {
       tc_fence_after();
@@ -205,7 +205,7 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
         tma_load_2d(sdVn + s * (CH * 128), &tdvn, bar_in, s * 64, trow);
         tma_load_2d(sVn + s * (CH * 128), &tvn, bar_in, s * 64, trow);
         tma_load_4d(sV + s * (CH * 128), &tv, bar_in, s * 64, h, n * CH, b);
-        tma_load_4d(sQ + s * (CH * 128), &tq, bar_in, s * 64, h, n * CH, b);
+        tma_load_4d(sQ + s * (CH * 128), &tq, bar_in, s * 64, h / rep, n * CH, b);
       }
       if (!mbar_wait(bar_in, c & 1, abort_flag)) atomicCAS(err, 0, ERR_WAIT_FULL);
       else {
@@ -378,7 +378,7 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
                     const float* __restrict__ gc, const float* __restrict__ beta, const __nv_bfloat16* __restrict__ P,
                     const float* __restrict__ dq_part, const float* __restrict__ dk_part, const float* __restrict__ gpart,
                     const float* __restrict__ bpart, __nv_bfloat16* __restrict__ dq, __nv_bfloat16* __restrict__ dk,
-                    float* __restrict__ dg, float* __restrict__ dbeta, int T, int H, int Tp, float scale,
+                    float* __restrict__ dg, float* __restrict__ dbeta, int T, int H, int rep, int Tp, float scale,
                     int* __restrict__ err) {
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {
@@ -429,7 +429,7 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
     mbar_expect_tx(bar_a, 5 * T32);
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
-      tma_load_4d(b0 + s * (PT * 128), &tk, bar_a, s * 64, h, t0, b);
+      tma_load_4d(b0 + s * (PT * 128), &tk, bar_a, s * 64, h / rep, t0, b);
       tma_load_4d(b1 + s * (PT * 128), &tdo, bar_a, s * 64, h, t0, b);
       tma_load_2d(b2 + s * (PT * 128), &tvn, bar_a, s * 64, prow);
       tma_load_2d(b3 + s * (PT * 128), &tdkt, bar_a, s * 64, prow);
@@ -466,7 +466,7 @@ gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constan
       for (int s = 0; s < 2; ++s) {
         tma_load_2d(b1 + s * (PT * 128), &tdvt, bar_b, s * 64, prow);
         tma_load_2d(b2 + s * (PT * 128), &tu, bar_b, s * 64, prow);
-        tma_load_4d(b3 + s * (PT * 128), &tq, bar_b, s * 64, h, t0, b);
+        tma_load_4d(b3 + s * (PT * 128), &tq, bar_b, s * 64, h / rep, t0, b);
       }
       ok = mbar_wait(bar_b, 0, abort_flag);
       if (!ok) atomicCAS(err, 0, ERR_WAIT_FULL);
@@ -666,7 +666,8 @@ static int make_bthd_map(CUtensorMap* m, const void* base, int B, int T, int H, 
 }  // namespace gdnb
 }  // namespace dewb
 
-// q, k, v, d_out: bf16 [B, T, H, 128] contiguous.  With X = B * H, N = ceil(T / 64), Tp = T rounded up to 128:
+// q, k: bf16 [B, T, H / rep, 128], v, d_out: bf16 [B, T, H, 128], contiguous (`rep` value heads share one key head; dq and dk come
+// back per value head and the caller sums each group of `rep`).  With X = B * H, N = ceil(T / 64), Tp = T rounded up to 128:
 // vn, dvn, W, U bf16 [X, Tp, 128]; P bf16 [X, Tp, 64]; gc fp32 [X, Tp]; beta fp32 [B, T, H];
 // states bf16 [X, N, 128 (value), 128 (key)]; dstates bf16 [X, N, 128 (key), 128 (value)].
 // Scratch (caller-allocated): dKt, dVt bf16 [X, Tp, 128]; dq_part, dk_part fp32 [B, T, H, 128]; gpart, bpart fp32 [X, Tp].
@@ -675,21 +676,23 @@ extern "C" int dewb_gdn_bwd_local(const void* q, const void* k, const void* v, c
                                   const void* dvn, const void* W, const void* U, const void* P, const float* gc,
                                   const float* beta, const void* states, const void* dstates, void* dKt, void* dVt,
                                   float* dq_part, float* dk_part, float* gpart, float* bpart, void* dq, void* dk, void* dv,
-                                  float* dg, float* dbeta, int B, int T, int H, int Tp, float scale, int* err,
+                                  float* dg, float* dbeta, int B, int T, int H, int rep, int Tp, float scale, int* err,
                                   void* stream_ptr) {
   using namespace dewb::gdnb;
   using bf = __nv_bfloat16;
-  if (B <= 0 || T <= 0 || H <= 0 || Tp % PT != 0 || Tp < T) return -3;
+  if (B <= 0 || T <= 0 || H <= 0 || Tp % PT != 0 || Tp < T || rep <= 0 || H % rep != 0) return -3;
   const int N = (T + CH - 1) / CH;
   const int X = B * H;
+  const int Hk = H / rep;
   const long long sb = static_cast<long long>(T) * H * HD, st = static_cast<long long>(H) * HD, sh = HD;
+  const long long sbk = static_cast<long long>(T) * Hk * HD, stk = static_cast<long long>(Hk) * HD;
   const uint64_t rows = static_cast<uint64_t>(X) * Tp, srows = static_cast<uint64_t>(X) * N * HD;
   CUtensorMap tq64, tv64, tdo64, tk128, tq128, tdo128, tvn64, tdvn64, tvn128, tst, tds, tdkt, tdvt, tw, tu;
   int r;
-  if ((r = make_bthd_map(&tk128, k, B, T, H, sb, st, sh, PT))) return 1000 + r;
-  if ((r = make_bthd_map(&tq128, q, B, T, H, sb, st, sh, PT))) return 1100 + r;
+  if ((r = make_bthd_map(&tk128, k, B, T, Hk, sbk, stk, sh, PT))) return 1000 + r;
+  if ((r = make_bthd_map(&tq128, q, B, T, Hk, sbk, stk, sh, PT))) return 1100 + r;
   if ((r = make_bthd_map(&tdo128, d_out, B, T, H, sb, st, sh, PT))) return 1200 + r;
-  if ((r = make_bthd_map(&tq64, q, B, T, H, sb, st, sh, CH))) return 1300 + r;
+  if ((r = make_bthd_map(&tq64, q, B, T, Hk, sbk, stk, sh, CH))) return 1300 + r;
   if ((r = make_bthd_map(&tv64, v, B, T, H, sb, st, sh, CH))) return 1400 + r;
   if ((r = make_bthd_map(&tdo64, d_out, B, T, H, sb, st, sh, CH))) return 1500 + r;
   if ((r = dewb::make_tmap_2d(&tvn64, vn, rows, HD, HD, CH, 64, 2, true))) return 2000 + r;
@@ -709,11 +712,11 @@ extern "C" int dewb_gdn_bwd_local(const void* q, const void* k, const void* v, c
   dim3 grid(Tp / PT, X);
   gdn_bwd_state_kernel<<<grid, THREADS, STATE_SMEM, stream>>>(
       tk128, tq64, tv64, tdo64, tvn64, tdvn64, tst, tds, gc, beta, reinterpret_cast<bf*>(dKt), reinterpret_cast<bf*>(dVt),
-      reinterpret_cast<bf*>(dv), dq_part, dk_part, gpart, bpart, T, H, Tp, N, scale, err);
+      reinterpret_cast<bf*>(dv), dq_part, dk_part, gpart, bpart, T, H, rep, Tp, N, scale, err);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   gdn_bwd_pair_kernel<<<grid, THREADS, PAIR_SMEM, stream>>>(
       tk128, tq128, tdo128, tvn128, tdkt, tdvt, tw, tu, gc, beta, reinterpret_cast<const bf*>(P), dq_part, dk_part, gpart,
-      bpart, reinterpret_cast<bf*>(dq), reinterpret_cast<bf*>(dk), dg, dbeta, T, H, Tp, scale, err);
+      bpart, reinterpret_cast<bf*>(dq), reinterpret_cast<bf*>(dk), dg, dbeta, T, H, rep, Tp, scale, err);
   return static_cast<int>(cudaGetLastError());
 }

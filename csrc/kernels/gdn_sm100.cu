@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(PREP_THREADS, 2)
 gdn_prepare_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                    const __grid_constant__ CUtensorMap tv, const float* __restrict__ g, const float* __restrict__ beta,
                    float* __restrict__ gc_out, __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ U,
-                   __nv_bfloat16* __restrict__ P, __nv_bfloat16* __restrict__ Qg, int T, int H, int Tp, float scale,
+                   __nv_bfloat16* __restrict__ P, __nv_bfloat16* __restrict__ Qg, int T, int H, int rep, int Tp, float scale,
                    int* __restrict__ err) {
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {
@@ -101,8 +101,8 @@ gdn_prepare_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
     mbar_expect_tx(&tail->bar_load, 3 * PREP_TILE);
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
-      tma_load_4d(sK + s * (PT * 128), &tk, &tail->bar_load, s * 64, h, t0, b);
-      tma_load_4d(sQ + s * (PT * 128), &tq, &tail->bar_load, s * 64, h, t0, b);
+      tma_load_4d(sK + s * (PT * 128), &tk, &tail->bar_load, s * 64, h / rep, t0, b);      // `rep` value heads share a key head
+      tma_load_4d(sQ + s * (PT * 128), &tq, &tail->bar_load, s * 64, h / rep, t0, b);
       tma_load_4d(sV + s * (PT * 128), &tv, &tail->bar_load, s * 64, h, t0, b);
     }
   }
@@ -361,8 +361,8 @@ gdn_scan_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
                     const __grid_constant__ CUtensorMap tw, const __grid_constant__ CUtensorMap tu,
                     const __grid_constant__ CUtensorMap tp, const float* __restrict__ gc,
                     const float* __restrict__ initial, __nv_bfloat16* __restrict__ out, float* __restrict__ final_state,
-                    __nv_bfloat16* __restrict__ states, __nv_bfloat16* __restrict__ vn_out, int T, int H, int Tp, int N,
-                    float scale, int* __restrict__ err) {
+                    __nv_bfloat16* __restrict__ states, __nv_bfloat16* __restrict__ vn_out, int T, int H, int rep, int Tp,
+                    int N, float scale, int* __restrict__ err) {
   extern __shared__ __align__(1024) uint8_t smem[];
   ScanCommon sc;
   if (!scan_prologue(smem, err, sc)) return;
@@ -391,8 +391,8 @@ gdn_scan_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         for (int t = 0; t < 2; ++t) {
           tma_load_2d(st + F_W + t * (CH * 128), &tw, bar, t * 64, row);
           tma_load_2d(st + F_U + t * (CH * 128), &tu, bar, t * 64, row);
-          tma_load_4d(st + F_Q + t * (CH * 128), &tq, bar, t * 64, h, n * CH, b);
-          tma_load_4d(st + F_K + t * (CH * 128), &tk, bar, t * 64, h, n * CH, b);
+          tma_load_4d(st + F_Q + t * (CH * 128), &tq, bar, t * 64, h / rep, n * CH, b);
+          tma_load_4d(st + F_K + t * (CH * 128), &tk, bar, t * 64, h / rep, n * CH, b);
         }
         tma_load_2d(st + F_P, &tp, bar, 0, row);
         bulk_load_1d(sG + s * CH, gc + static_cast<long long>(x) * Tp + n * CH, CH * 4, bar);
@@ -551,7 +551,7 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tdo, const __grid_consta
                     const __grid_constant__ CUtensorMap tw, const __grid_constant__ CUtensorMap tqg,
                     const __grid_constant__ CUtensorMap tp, const float* __restrict__ gc,
                     const float* __restrict__ d_final, float* __restrict__ dstates, __nv_bfloat16* __restrict__ dstates_bf16,
-                    __nv_bfloat16* __restrict__ dvn_out, float* __restrict__ d_initial, int T, int H, int Tp, int N,
+                    __nv_bfloat16* __restrict__ dvn_out, float* __restrict__ d_initial, int T, int H, int rep, int Tp, int N,
                     int* __restrict__ err) {
   extern __shared__ __align__(1024) uint8_t smem[];
   ScanCommon sc;
@@ -581,7 +581,7 @@ gdn_scan_bwd_kernel(const __grid_constant__ CUtensorMap tdo, const __grid_consta
         for (int t = 0; t < 2; ++t) {
           tma_load_4d(st + B_DO + t * (CH * 128), &tdo, bar, t * 64, h, n * CH, b);
           tma_load_2d(st + B_QG + t * (CH * 128), &tqg, bar, t * 64, row);
-          tma_load_4d(st + B_K + t * (CH * 128), &tk, bar, t * 64, h, n * CH, b);
+          tma_load_4d(st + B_K + t * (CH * 128), &tk, bar, t * 64, h / rep, n * CH, b);
           tma_load_2d(st + B_W + t * (CH * 128), &tw, bar, t * 64, row);
         }
         tma_load_2d(st + B_P, &tp, bar, 0, row);
@@ -729,28 +729,29 @@ static bool strides_ok(long long sb, long long st, long long sh) { return (sb % 
 }  // namespace gdn
 }  // namespace dewb
 
-// q, k, v: bf16 [B, T, H, 128] (unit stride along the head dimension; the other strides in elements: batch, token, head);
+// q, k: bf16 [B, T, H / rep, 128], v: bf16 [B, T, H, 128] (`rep` consecutive value heads share one key head; unit stride along
+// the head dimension; the other strides in elements: batch, token, head);
 // g, beta: fp32 [B, T, H] contiguous.  With X = B * H and Tp = T rounded up to 128:
 // gc fp32 [X, Tp]; W, U bf16 [X, Tp, 128]; P bf16 [X, Tp, 64]; Qg bf16 [X, Tp, 128] or null.
 extern "C" int dewb_gdn_prepare(const void* q, const void* k, const void* v, const float* g, const float* beta, float* gc,
-                                void* W, void* U, void* P, void* Qg, int B, int T, int H, long long q_sb, long long q_st,
+                                void* W, void* U, void* P, void* Qg, int B, int T, int H, int rep, long long q_sb, long long q_st,
                                 long long q_sh, long long k_sb, long long k_st, long long k_sh, long long v_sb,
                                 long long v_st, long long v_sh, float scale, int* err, void* stream_ptr) {
   using namespace dewb::gdn;
-  if (B <= 0 || T <= 0 || H <= 0) return -3;
+  if (B <= 0 || T <= 0 || H <= 0 || rep <= 0 || H % rep != 0) return -3;
   if (!strides_ok(q_sb, q_st, q_sh) || !strides_ok(k_sb, k_st, k_sh) || !strides_ok(v_sb, v_st, v_sh)) return -3;
   const int Tp = (T + PT - 1) / PT * PT;
   CUtensorMap tq, tk, tv;
   int r;
-  if ((r = make_bthd_map(&tq, q, B, T, H, q_sb, q_st, q_sh, PT))) return 1000 + r;
-  if ((r = make_bthd_map(&tk, k, B, T, H, k_sb, k_st, k_sh, PT))) return 2000 + r;
+  if ((r = make_bthd_map(&tq, q, B, T, H / rep, q_sb, q_st, q_sh, PT))) return 1000 + r;
+  if ((r = make_bthd_map(&tk, k, B, T, H / rep, k_sb, k_st, k_sh, PT))) return 2000 + r;
   if ((r = make_bthd_map(&tv, v, B, T, H, v_sb, v_st, v_sh, PT))) return 3000 + r;
   cudaError_t e = cudaFuncSetAttribute(gdn_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREP_SMEM);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(Tp / PT, B * H);
   gdn_prepare_kernel<<<grid, PREP_THREADS, PREP_SMEM, reinterpret_cast<cudaStream_t>(stream_ptr)>>>(
       tq, tk, tv, g, beta, gc, reinterpret_cast<__nv_bfloat16*>(W), reinterpret_cast<__nv_bfloat16*>(U),
-      reinterpret_cast<__nv_bfloat16*>(P), reinterpret_cast<__nv_bfloat16*>(Qg), T, H, Tp, scale, err);
+      reinterpret_cast<__nv_bfloat16*>(P), reinterpret_cast<__nv_bfloat16*>(Qg), T, H, rep, Tp, scale, err);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -759,7 +760,7 @@ extern "C" int dewb_gdn_prepare(const void* q, const void* k, const void* v, con
 // vn_out bf16 [X, Tp, 128] or null: the corrected values Vn = U - W S of every chunk (the backward reads them).
 extern "C" int dewb_gdn_scan_fwd(const void* q, const void* k, const float* gc, const void* W, const void* U, const void* P,
                                  const float* initial, void* out, float* final_state, void* states, void* vn_out, int B,
-                                 int T, int H, int Tp, long long q_sb, long long q_st, long long q_sh, long long k_sb, long long k_st,
+                                 int T, int H, int rep, int Tp, long long q_sb, long long q_st, long long q_sh, long long k_sb, long long k_st,
                                  long long k_sh, float scale, int* err, void* stream_ptr) {
   using namespace dewb::gdn;
   if (B <= 0 || T <= 0 || H <= 0 || Tp % PT != 0 || Tp < T) return -3;
@@ -768,8 +769,9 @@ extern "C" int dewb_gdn_scan_fwd(const void* q, const void* k, const float* gc, 
   const uint64_t rows = static_cast<uint64_t>(B) * H * Tp;
   CUtensorMap tq, tk, tw, tu, tp;
   int r;
-  if ((r = make_bthd_map(&tq, q, B, T, H, q_sb, q_st, q_sh, CH))) return 1000 + r;
-  if ((r = make_bthd_map(&tk, k, B, T, H, k_sb, k_st, k_sh, CH))) return 2000 + r;
+  if (rep <= 0 || H % rep != 0) return -3;
+  if ((r = make_bthd_map(&tq, q, B, T, H / rep, q_sb, q_st, q_sh, CH))) return 1000 + r;
+  if ((r = make_bthd_map(&tk, k, B, T, H / rep, k_sb, k_st, k_sh, CH))) return 2000 + r;
   if ((r = dewb::make_tmap_2d(&tw, W, rows, HD, HD, CH, 64, 2, true))) return 3000 + r;
   if ((r = dewb::make_tmap_2d(&tu, U, rows, HD, HD, CH, 64, 2, true))) return 4000 + r;
   if ((r = dewb::make_tmap_2d(&tp, P, rows, CH, CH, CH, 64, 2, true))) return 5000 + r;
@@ -777,7 +779,7 @@ extern "C" int dewb_gdn_scan_fwd(const void* q, const void* k, const float* gc, 
   if (e != cudaSuccess) return static_cast<int>(e);
   gdn_scan_fwd_kernel<<<B * H, SCAN_THREADS, SCAN_SMEM, reinterpret_cast<cudaStream_t>(stream_ptr)>>>(
       tq, tk, tw, tu, tp, gc, initial, reinterpret_cast<__nv_bfloat16*>(out), final_state,
-      reinterpret_cast<__nv_bfloat16*>(states), reinterpret_cast<__nv_bfloat16*>(vn_out), T, H, Tp, N, scale, err);
+      reinterpret_cast<__nv_bfloat16*>(states), reinterpret_cast<__nv_bfloat16*>(vn_out), T, H, rep, Tp, N, scale, err);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -786,7 +788,7 @@ extern "C" int dewb_gdn_scan_fwd(const void* q, const void* k, const float* gc, 
 // dvn_out bf16 [X, Tp, 128] or null: dVn of every chunk; d_initial fp32 [X, 128, 128].
 extern "C" int dewb_gdn_scan_bwd(const void* d_out, const void* k, const float* gc, const void* W, const void* P,
                                  const void* Qg, const float* d_final, float* dstates, void* dstates_bf16, void* dvn_out,
-                                 float* d_initial, int B, int T, int H, int Tp, long long do_sb, long long do_st, long long do_sh, long long k_sb,
+                                 float* d_initial, int B, int T, int H, int rep, int Tp, long long do_sb, long long do_st, long long do_sh, long long k_sb,
                                  long long k_st, long long k_sh, int* err, void* stream_ptr) {
   using namespace dewb::gdn;
   if (B <= 0 || T <= 0 || H <= 0 || Tp % PT != 0 || Tp < T) return -3;
@@ -796,7 +798,8 @@ extern "C" int dewb_gdn_scan_bwd(const void* d_out, const void* k, const float* 
   CUtensorMap tdo, tk, tw, tqg, tp;
   int r;
   if ((r = make_bthd_map(&tdo, d_out, B, T, H, do_sb, do_st, do_sh, CH))) return 1000 + r;
-  if ((r = make_bthd_map(&tk, k, B, T, H, k_sb, k_st, k_sh, CH))) return 2000 + r;
+  if (rep <= 0 || H % rep != 0) return -3;
+  if ((r = make_bthd_map(&tk, k, B, T, H / rep, k_sb, k_st, k_sh, CH))) return 2000 + r;
   if ((r = dewb::make_tmap_2d(&tw, W, rows, HD, HD, CH, 64, 2, true))) return 3000 + r;
   if ((r = dewb::make_tmap_2d(&tqg, Qg, rows, HD, HD, CH, 64, 2, true))) return 4000 + r;
   if ((r = dewb::make_tmap_2d(&tp, P, rows, CH, CH, CH, 64, 2, true))) return 5000 + r;
@@ -804,6 +807,6 @@ extern "C" int dewb_gdn_scan_bwd(const void* d_out, const void* k, const float* 
   if (e != cudaSuccess) return static_cast<int>(e);
   gdn_scan_bwd_kernel<<<B * H, SCAN_THREADS, SCAN_SMEM, reinterpret_cast<cudaStream_t>(stream_ptr)>>>(
       tdo, tk, tw, tqg, tp, gc, d_final, dstates, reinterpret_cast<__nv_bfloat16*>(dstates_bf16),
-      reinterpret_cast<__nv_bfloat16*>(dvn_out), d_initial, T, H, Tp, N, err);
+      reinterpret_cast<__nv_bfloat16*>(dvn_out), d_initial, T, H, rep, Tp, N, err);
   return static_cast<int>(cudaGetLastError());
 }

@@ -87,8 +87,9 @@ class GatedDeltaNet(nn.Module):
         k = ops.l2_normalize(k.reshape(B, T, self.hk, self.dk))
         v = v.reshape(B, T, self.hv, self.dv)
         rep = self.hv // self.hk
-        if rep > 1:
-            q, k = q.repeat_interleave(rep, 2), k.repeat_interleave(rep, 2)
+        decode = state is not None and T == 1
+        if rep > 1 and decode:
+            q, k = q.repeat_interleave(rep, 2), k.repeat_interleave(rep, 2)      # the chunked op shares key heads itself
         b, a = ba[..., : self.hv], ba[..., self.hv:]
         beta = torch.sigmoid(b)
         g = -torch.exp(self.A_log.float()) * F.softplus(a + self.dt_bias.float())

@@ -242,7 +242,9 @@ def _strides3(t):
 
 
 def prepare_cuda(q, k, v, g, beta, scale: float, want_qg: bool):
-    B, T, H, _ = q.shape
+    """q, k may carry fewer heads than v (``rep = Hv / Hk`` consecutive value heads share a key head)."""
+    B, T, H, _ = v.shape
+    rep = H // q.shape[2]
     X, Tp = B * H, padded_len(T)
     dev = q.device
     gc = torch.empty(X, Tp, dtype=torch.float32, device=dev)
@@ -253,7 +255,7 @@ def prepare_cuda(q, k, v, g, beta, scale: float, want_qg: bool):
     lib = L.load()
     L.ensure_device(q)
     rc = lib.dewb_gdn_prepare(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta), L.ptr(gc), L.ptr(W), L.ptr(U), L.ptr(P),
-                              L.ptr(Qg), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), *_strides3(q), *_strides3(k),
+                              L.ptr(Qg), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(rep), *_strides3(q), *_strides3(k),
                               *_strides3(v), ctypes.c_float(scale), L.ptr(L.status(dev)), L.stream_ptr())
     L.check(rc, "gdn_prepare")
     L.count_launches()
@@ -261,8 +263,10 @@ def prepare_cuda(q, k, v, g, beta, scale: float, want_qg: bool):
 
 
 def scan_fwd_cuda(q, k, gc, W, U, P, scale: float, initial_state, save_states: bool, save_vn: bool = False):
-    B, T, H, _ = q.shape
-    X, Tp = B * H, gc.shape[1]
+    B, T = q.shape[:2]
+    X, Tp = W.shape[0], gc.shape[1]
+    H = X // B
+    rep = H // q.shape[2]
     N = (T + CHUNK - 1) // CHUNK
     dev = q.device
     o = torch.empty(B, T, H, HEAD_DIM, dtype=torch.bfloat16, device=dev)
@@ -276,7 +280,7 @@ def scan_fwd_cuda(q, k, gc, W, U, P, scale: float, initial_state, save_states: b
     lib = L.load()
     L.ensure_device(q)
     rc = lib.dewb_gdn_scan_fwd(L.ptr(q), L.ptr(k), L.ptr(gc), L.ptr(W), L.ptr(U), L.ptr(P), L.ptr(init), L.ptr(o), L.ptr(final),
-                               L.ptr(states), L.ptr(vn), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(Tp),
+                               L.ptr(states), L.ptr(vn), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(rep), ctypes.c_int(Tp),
                                *_strides3(q), *_strides3(k), ctypes.c_float(scale), L.ptr(L.status(dev)), L.stream_ptr())
     L.check(rc, "gdn_scan_fwd")
     L.count_launches()
@@ -289,6 +293,7 @@ def scan_fwd_cuda(q, k, gc, W, U, P, scale: float, initial_state, save_states: b
 def scan_bwd_cuda(do, k, gc, W, P, Qg, d_final, for_kernels: bool = False):
     B, T, H, _ = do.shape
     X, Tp = B * H, gc.shape[1]
+    rep = H // k.shape[2]
     N = (T + CHUNK - 1) // CHUNK
     dev = do.device
     dstates = None if for_kernels else torch.empty(X, N, HEAD_DIM, HEAD_DIM, dtype=torch.float32, device=dev)
@@ -302,7 +307,8 @@ def scan_bwd_cuda(do, k, gc, W, P, Qg, d_final, for_kernels: bool = False):
     lib = L.load()
     L.ensure_device(do)
     rc = lib.dewb_gdn_scan_bwd(L.ptr(do), L.ptr(k), L.ptr(gc), L.ptr(W), L.ptr(P), L.ptr(Qg), L.ptr(dfin), L.ptr(dstates),
-                               L.ptr(dstates16), L.ptr(dvn), L.ptr(d_init), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(Tp),
+                               L.ptr(dstates16), L.ptr(dvn), L.ptr(d_init), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(rep),
+                               ctypes.c_int(Tp),
                                *_strides3(do), *_strides3(k), L.ptr(L.status(dev)), L.stream_ptr())
     L.check(rc, "gdn_scan_bwd")
     L.count_launches()
@@ -314,7 +320,8 @@ def scan_bwd_cuda(do, k, gc, W, P, Qg, d_final, for_kernels: bool = False):
 def local_bwd_cuda(q, k, v, do, gc, beta, W, U, P, vn, dvn, states_raw, dstates16, scale: float):
     """The chunk-local gradients on the two backward kernels (``csrc/kernels/gdn_bwd_sm100.cu``): dq, dk, dv (bf16) and
     dg, dbeta (fp32), from the intermediates the prepare kernel and the two scans leave in memory."""
-    B, T, H, _ = q.shape
+    B, T, H, _ = v.shape
+    rep = H // q.shape[2]
     X, Tp = B * H, gc.shape[1]
     N = (T + CHUNK - 1) // CHUNK
     dev = q.device
@@ -334,10 +341,14 @@ def local_bwd_cuda(q, k, v, do, gc, beta, W, U, P, vn, dvn, states_raw, dstates1
     rc = L.load().dewb_gdn_bwd_local(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(do), L.ptr(vn), L.ptr(dvn), L.ptr(W), L.ptr(U), L.ptr(P),
                                      L.ptr(gc), L.ptr(beta), L.ptr(states_raw), L.ptr(dstates16), L.ptr(dKt), L.ptr(dVt),
                                      L.ptr(dq_part), L.ptr(dk_part), L.ptr(gpart), L.ptr(bpart), L.ptr(dq), L.ptr(dk), L.ptr(dv),
-                                     L.ptr(dg), L.ptr(dbeta), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(Tp),
+                                     L.ptr(dg), L.ptr(dbeta), ctypes.c_int(B), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_int(rep), ctypes.c_int(Tp),
                                      ctypes.c_float(scale), L.ptr(L.status(dev)), L.stream_ptr())
     L.check(rc, "gdn_bwd_local")
     L.count_launches(2)
+    if rep > 1:                      # the kernels return dq, dk per value head: sum each group of `rep`
+        Hk = H // rep
+        dq = dq.view(B, T, Hk, rep, HEAD_DIM).float().sum(3).to(torch.bfloat16)
+        dk = dk.view(B, T, Hk, rep, HEAD_DIM).float().sum(3).to(torch.bfloat16)
     return dq, dk, dv, dg, dbeta
 
 
@@ -365,7 +376,9 @@ class _GatedDeltaRule(torch.autograd.Function):
         ctx.scale = scale
         ctx.has_initial = initial_state is not None
         ctx.save_for_backward(q, k, v, g, beta, initial_state)
-        B, T, H, Dk = q.shape
+        B, T, H, Dk = v.shape[0], v.shape[1], v.shape[2], q.shape[3]
+        if not q.is_cuda and q.shape[2] != H:
+            raise ValueError("shared key heads are a kernel-path feature: repeat q and k over the value heads on the CPU path")
         if _stages(q):
             gc, W, U, P, _ = prepare_cuda(q, k, v, g, beta, scale, False)
             o, final, _ = scan_fwd_cuda(q, k, gc, W, U, P, scale, initial_state, False)
@@ -379,7 +392,7 @@ class _GatedDeltaRule(torch.autograd.Function):
     def backward(ctx, do, dfinal):
         q, k, v, g, beta, initial_state = ctx.saved_tensors
         scale = ctx.scale
-        B, T, H, Dk = q.shape
+        B, T, H, Dk = v.shape[0], v.shape[1], v.shape[2], q.shape[3]
         Dv = v.shape[-1]
         if _stages(q) and local_kernels_available():
             do = do.contiguous().to(torch.bfloat16)
@@ -389,6 +402,10 @@ class _GatedDeltaRule(torch.autograd.Function):
             dq, dk, dv, dg, dbeta = local_bwd_cuda(q, k, v, do, gc, beta, W, U, P, vn, dvn, states_raw, dstates16, scale)
             d_init = d_init.reshape(B, H, Dk, Dv).to(initial_state.dtype) if ctx.has_initial else None
             return dq, dk, dv, dg.to(g.dtype), dbeta.to(beta.dtype), d_init, None
+        rep = H // q.shape[2]
+        q_in, k_in = q, k
+        if rep > 1:                  # the PyTorch chunk-local path works per value head
+            q, k = q.repeat_interleave(rep, 2), k.repeat_interleave(rep, 2)
         if _stages(q):
             do = do.contiguous().to(torch.bfloat16)
             gc, W, U, P, Qg = prepare_cuda(q, k, v, g, beta, scale, True)
@@ -399,13 +416,18 @@ class _GatedDeltaRule(torch.autograd.Function):
             _, _, states = scan_fwd_reference(q, k, gc, W, U, P, scale, initial_state, True)
             dstates, d_init = scan_bwd_reference(do, k, gc, W, P, Qg, dfinal)
         dq, dk, dv, dg, dbeta = chunk_local_grads(q, k, v, g, beta, states, dstates, do, scale)
+        if rep > 1:
+            dq = dq.reshape(B, T, H // rep, rep, Dk).sum(3)
+            dk = dk.reshape(B, T, H // rep, rep, Dk).sum(3)
+            q, k = q_in, k_in
         d_init = d_init.reshape(B, H, Dk, Dv).to(initial_state.dtype) if ctx.has_initial else None
         return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dg.to(g.dtype), dbeta.to(beta.dtype), d_init, None
 
 
 def gated_delta_rule(q, k, v, g, beta, initial_state=None, scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """q, k ``[B,T,H,Dk]``, v ``[B,T,H,Dv]``, g (log decay, <= 0) and beta ``[B,T,H]`` -> (o ``[B,T,H,Dv]``, state ``[B,H,Dk,Dv]``
-    fp32).  On a GPU (128-wide heads) q, k, v are taken in bf16 and g, beta in fp32."""
+    """q, k ``[B,T,Hk,Dk]``, v ``[B,T,H,Dv]``, g (log decay, <= 0) and beta ``[B,T,H]`` -> (o ``[B,T,H,Dv]``, state ``[B,H,Dk,Dv]``
+    fp32).  On a GPU (128-wide heads) q, k, v are taken in bf16 and g, beta in fp32, and ``Hk`` may divide ``H`` (each key head
+    serves ``H / Hk`` consecutive value heads without being copied)."""
     scale = float(q.shape[-1] ** -0.5 if scale is None else scale)
     if q.is_cuda:
         q, k, v = (x.to(torch.bfloat16).contiguous() for x in (q, k, v))

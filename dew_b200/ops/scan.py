@@ -106,6 +106,9 @@ def chunk_gated_delta_rule(q, k, v, g, beta, initial_state=None, scale=None, chu
         if gdn.kernel_available(q, v):
             o, S = gdn.gated_delta_rule(q, k, v, g, beta, initial_state, scale)
             return o.to(v.dtype), S
+    if q.shape[2] != v.shape[2]:                 # shared key heads: the chunked form works per value head
+        rep = v.shape[2] // q.shape[2]
+        q, k = q.repeat_interleave(rep, 2), k.repeat_interleave(rep, 2)
     return gated_delta_rule_chunked(q, k, v, g, beta, initial_state, scale, chunk)
 
 

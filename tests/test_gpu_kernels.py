@@ -607,6 +607,24 @@ def test_gdn_kernel_stages_match_their_restatements(B, T, H, with_state):
     assert rel_err(dinit, rdinit) <= 2e-2
 
 
+def test_gdn_shared_key_heads_match_repeated_heads():
+    """Two value heads per key head read the key head in place: same outputs and gradients as with q, k repeated."""
+    from dew_b200.ops import scan
+    B, T, Hk, rep = 2, 200, 2, 2
+    q, k, v, g, beta, _ = _gdn_inputs(B, T, Hk * rep, 11, False)
+    q, k = q[:, :, :Hk].contiguous(), k[:, :, :Hk].contiguous()
+    a = [t.clone().requires_grad_() for t in (q, k, v, g, beta)]
+    b = [t.clone().requires_grad_() for t in (q, k, v, g, beta)]
+    oa, Sa = scan.chunk_gated_delta_rule(*a)
+    ob, Sb = scan.chunk_gated_delta_rule(b[0].repeat_interleave(rep, 2), b[1].repeat_interleave(rep, 2), *b[2:])
+    assert torch.equal(oa, ob) and torch.equal(Sa, Sb)
+    do = torch.randn_like(oa)
+    oa.backward(do)
+    ob.backward(do)
+    for name, x, y in zip(("dq", "dk", "dv", "dg", "dbeta"), a, b):
+        assert rel_err(x.grad, y.grad) <= 1e-2, (name, rel_err(x.grad, y.grad))
+
+
 @pytest.mark.parametrize("B,T,H", [(1, 128, 1), (2, 300, 2), (1, 1024, 3)])
 def test_gdn_local_backward_kernels_match_closed_form(B, T, H):
     """The two chunk-local backward kernels against the closed-form gradients in PyTorch, both fed the same

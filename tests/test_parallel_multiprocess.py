@@ -29,3 +29,18 @@ def test_helpers():
     assert torch.equal(unstripe(stripe(x, 2), 2), x)
     assert stripe(x, 2)[0, :, 0].tolist()[:8] == [0, 1, 2, 3, 12, 13, 14, 15]
     assert all_to_all_moves_less(8192, 32, 8, 128, 8) and not all_to_all_moves_less(8192, 64, 1, 128, 2)
+
+
+def test_link_probe_two_cpu_ranks():
+    import json
+    import os
+    import subprocess
+    import sys
+    worker = os.path.join(os.path.dirname(__file__), "workers", "probe_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29671", worker]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-3000:]
+    r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    assert r["rows"] == 10 and r["positive"] and r["mem"] == 0 and r["table_lines"] == 11 and r["spread"] is False
+    assert r["names"] == ["all_gather", "all_reduce", "all_to_all", "exchange", "reduce_scatter"]
