@@ -92,3 +92,62 @@ class WorldModelObjective(Objective):
         per = (lat + self.rw * rew + self.dw * don) / H
         mass = torch.tensor(float(B), device=per.device)
         return Ratio(per.sum(), mass), Aux(metrics={"latent_mse": Ratio((lat / H).sum(), mass), "reward_mse": Ratio((rew / H).sum(), mass)})
+
+
+def lambda_returns(rewards: torch.Tensor, values: torch.Tensor, continues: torch.Tensor, lam: float = 0.95) -> torch.Tensor:
+    """TD(lambda) targets along an imagined trajectory.  rewards, continues ``[H, B]`` (continues = gamma * (1 - done)),
+    values ``[H + 1, B]`` (the last row bootstraps): ``G_t = r_t + c_t ((1 - lam) V_{t+1} + lam G_{t+1})``."""
+    H = rewards.shape[0]
+    out = [None] * H
+    nxt = values[-1]
+    for t in range(H - 1, -1, -1):
+        nxt = rewards[t] + continues[t] * ((1 - lam) * values[t + 1] + lam * nxt)
+        out[t] = nxt
+    return torch.stack(out, 0)
+
+
+class DreamerObjective(Objective):
+    """Actor-critic learning in imagination (Dreamer): from encoded start states the actor's actions are rolled through the
+    learned dynamics for ``horizon`` steps; the critic regresses the lambda-returns of predicted rewards (targets without
+    gradient), and the actor ascends the same returns by backpropagating through the dynamics and reward models, with an
+    entropy bonus.  ``model`` is a world model as in ``WorldModelObjective`` plus ``actor(z) -> (mean, log_std)`` and
+    ``critic(z) -> value``; only actor and critic receive gradients here (the world model's outputs are used as fixed
+    functions: its parameters are excluded by the caller's parameter groups or frozen).
+    Reference: src/dew/objectives/rl/ (dreamer), src/dew/rl/skydreamer.py."""
+
+    def __init__(self, model, horizon: int = 15, gamma: float = 0.99, lam: float = 0.95, entropy: float = 1e-3,
+                 ema_decay: Optional[float] = None):
+        self.model, self.horizon, self.gamma, self.lam, self.entropy, self.ema_decay = model, horizon, gamma, lam, entropy, ema_decay
+
+    def imagine(self, z0: torch.Tensor, step: Step):
+        m = self.model
+        zs, rewards, conts, ents = [z0], [], [], []
+        z = z0
+        for t in range(self.horizon):
+            mean, log_std = m.actor(z.detach() if t == 0 else z)
+            std = log_std.clamp(-5, 2).exp()
+            eps = step.sample(f"action_{t}", tuple(mean.shape[1:]), mean.shape[0]).to(mean.device)
+            action = torch.tanh(mean + std * eps)                          # reparameterised draw
+            rewards.append(m.reward(z, action).reshape(-1))
+            z = m.dynamics(z, action)
+            conts.append(self.gamma * (1 - torch.sigmoid(m.done(z).reshape(-1))))
+            ents.append((log_std + 0.5 * math.log(2 * math.pi * math.e)).sum(-1))
+            zs.append(z)
+        return torch.stack(zs, 0), torch.stack(rewards, 0), torch.stack(conts, 0), torch.stack(ents, 0)
+
+    def loss(self, variables, batch, step: Step):
+        m = self.model
+        obs = batch["observation"]
+        with torch.no_grad():
+            z0 = m.encode(obs.reshape(-1, *obs.shape[2:]) if obs.dim() > 2 and "action" in batch else obs)
+        zs, rewards, conts, ents = self.imagine(z0, step)
+        values = m.critic(zs.reshape(-1, zs.shape[-1])).reshape(zs.shape[0], -1)
+        targets = lambda_returns(rewards, values.detach(), conts.detach(), self.lam)
+        # discount weights: later imagined steps count less once an episode is likely over
+        weights = torch.cumprod(torch.cat([torch.ones_like(conts[:1]), conts[:-1]], 0), 0).detach()
+        actor_loss = -(weights * (lambda_returns(rewards, values.detach(), conts, self.lam) + self.entropy * ents)).mean(0)
+        critic_loss = (weights * (values[:-1] - targets.detach()) ** 2).mean(0)
+        per = actor_loss + critic_loss
+        mass = torch.tensor(float(per.shape[0]), device=per.device)
+        return Ratio(per.sum(), mass), Aux(metrics={"imagined_return": Ratio(targets[0].detach().sum(), mass),
+                                                    "critic_loss": Ratio(critic_loss.detach().sum(), mass)})
