@@ -1,5 +1,5 @@
 """Process presets: ``EDM``, ``Karras``, ``Cosine``, ``CosineContinuous``, ``Linear``, ``Exp``, ``Sqrt``,
-``Flow``, ``ResolutionShift``.  Calling a preset builds its ``Process``.
+``Flow``, ``ResolutionShift``, ``JiT``, ``MeanFlow``, ``Shortcut``.  Calling a preset builds its ``Process``.
 
 Parity: src/dew/diffusion/presets.py:94-396 (EDM regimes pixel -1.2/1.2 and latent -0.4/1.0; Karras rho grid).
 """
@@ -143,3 +143,38 @@ class ResolutionShift:
 
     def __call__(self) -> Process:
         return Flow(shift=(self.pixels / self.base_pixels) ** 0.5, logit_normal=self.logit_normal)()
+
+
+@dataclass(frozen=True)
+class JiT:
+    """"Just image Transformers": the rectified-flow path with the network predicting the clean image (x-prediction) and the
+    loss taken on the implied velocity, which keeps a plain ViT on raw pixels well-conditioned at every noise level."""
+    shift: float = 1.0
+    logit_normal: bool = True
+
+    def __call__(self) -> Process:
+        sched = FlowNoiseScheduler(self.shift, self.logit_normal)
+        return Process(sched, DirectPredictionTransform(), ScheduleWeighting(), FlowNoiseScheduler(self.shift))
+
+
+@dataclass(frozen=True)
+class MeanFlow:
+    """The flow path for average-velocity training: the process is ``Flow``'s; the objective to pair it with is
+    ``dew_b200.objectives.few_step.MeanFlowObjective`` (the network takes the interval's start ``r`` beside ``t``)."""
+    flow_ratio: float = 0.5
+    shift: float = 1.0
+    objective: str = "MeanFlowObjective"
+
+    def __call__(self) -> Process:
+        return Flow(shift=self.shift)()
+
+
+@dataclass(frozen=True)
+class Shortcut:
+    """The flow path for shortcut models (step size as an input): pair with ``few_step.ShortcutObjective``."""
+    max_log2_steps: int = 7
+    shift: float = 1.0
+    objective: str = "ShortcutObjective"
+
+    def __call__(self) -> Process:
+        return Flow(shift=self.shift)()

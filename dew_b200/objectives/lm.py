@@ -19,7 +19,19 @@ class LMObjective(Objective):
     def __init__(self, model, seq_len: Optional[int] = None, *, ema_decay: Optional[float] = None,
                  pad_id: Optional[int] = None, head_chunks: int = 4, head_tile: Optional[int] = None,
                  z_loss: float = 0.0, token_accuracy: bool = True, variables=None, balance: Optional[float] = None,
-                 mtp_weight: Optional[float] = None, prefix: Optional[int] = None, tokenizer=None):
+                 mtp_weight: Optional[float] = None, prefix: Optional[int] = None, tokenizer=None, samples: Optional[dict] = None,
+                 loss_role: Optional[int] = None, exit_entropy: Optional[float] = None, pass_weights=None, indexer=None, adaptation=None):
+        """``samples``: preview settings ``{"prompt": [...token ids or text], "max_new_tokens": n, "sampling": Sampling}``;
+        ``loss_role``: score only the targets whose ``batch["roles"]`` entry equals this role id (chat fine-tuning on the
+        assistant's tokens).  ``exit_entropy`` / ``pass_weights`` (per-pass exits of a looped decoder), ``indexer`` (training a
+        sparse-attention indexer beside dense attention) and ``adaptation`` (in-context level stepping) name reference
+        features whose model-side parts are not in this library: asking for them raises."""
+        unsupported = {"exit_entropy": exit_entropy, "pass_weights": pass_weights, "indexer": indexer, "adaptation": adaptation}
+        asked = [k for k, v in unsupported.items() if v is not None]
+        if asked:
+            raise NotImplementedError(f"LMObjective({', '.join(asked)}=...) needs a looped decoder / attention indexer / in-context "
+                                      "decoder, which this library does not provide")
+        self.samples, self.loss_role = samples, loss_role
         self.model = model
         self.seq_len = seq_len
         self.ema_decay = ema_decay
@@ -51,6 +63,8 @@ class LMObjective(Objective):
             targets[mask[:, 1:] == 0] = -100
         if self.prefix:
             targets[:, : self.prefix] = -100
+        if self.loss_role is not None and "roles" in batch:
+            targets[batch["roles"][:, 1:] != self.loss_role] = -100
         return inputs, targets, seg_in
 
     def loss(self, variables, batch: Mapping[str, torch.Tensor], step: Step):
@@ -95,7 +109,8 @@ class LMObjective(Objective):
 
     def scored_tokens(self, batch):
         t = batch["tokens"]
-        if ("segments" not in batch and "loss_mask" not in batch and self.pad_id is None and not self.prefix):
+        if ("segments" not in batch and "loss_mask" not in batch and self.pad_id is None and not self.prefix
+                and not (self.loss_role is not None and "roles" in batch)):
             return int(t.shape[0] * (t.shape[1] - 1))        # every target is scored: no device read needed
         return int((self._targets(batch)[1] != -100).sum())
 
@@ -109,6 +124,20 @@ class LMObjective(Objective):
 
     def predict(self, variables, batch):
         return self.apply(variables, batch["tokens"])
+
+    def preview(self, variables, batch=None, key=0, **kw):
+        """Text samples from the current weights (``samples`` settings): a ``TextSamples`` artifact, or None."""
+        if not self.samples or not self.samples.get("max_new_tokens"):
+            return None
+        from ..sampling.text import Sampling, generate
+        from ..utils.artifacts import TextSamples
+        prompt = self.samples.get("prompt", [[0]])
+        prompts = prompt if (prompt and isinstance(prompt[0], (list, tuple, str))) else [prompt]
+        gen = generate(self.model, variables, prompts, int(self.samples["max_new_tokens"]), key=key,
+                       sampling=self.samples.get("sampling", Sampling(temperature=0.0)), tokenizer=self.tokenizer)
+        texts = gen.text if gen.text is not None else [" ".join(map(str, gen.new_tokens(r).tolist())) for r in range(len(prompts))]
+        shown = [p if isinstance(p, str) else " ".join(map(str, p)) for p in prompts]
+        return TextSamples(shown, texts)
 
     def pipeline(self, state, ema: Optional[bool] = None):
         from ..inference.tasks import TextGeneration

@@ -26,6 +26,23 @@ from .state import TrainState
 from .tracker import MemoryTracker
 
 
+@dataclass(frozen=True)
+class Cooldown:
+    """A learning-rate cooldown window: from step ``at`` the rate falls from 1x to ``floor``x over ``steps`` steps ("linear",
+    "cosine" or "sqrt" - one minus the square root of the progress, the WSD recipe) and stays there."""
+    at: int
+    steps: int
+    floor: float = 0.0
+    shape: str = "linear"
+
+    def factor(self, step: int) -> float:
+        if step < self.at:
+            return 1.0
+        x = min(1.0, (step - self.at) / max(1, self.steps))
+        fall = {"linear": x, "cosine": 0.5 * (1 - math.cos(math.pi * x)), "sqrt": math.sqrt(x)}[self.shape]
+        return 1.0 - (1.0 - self.floor) * fall
+
+
 class Preempted(SystemExit):
     """Raised after a preemption checkpoint; exit status 143 like a SIGTERM'd process."""
 
@@ -268,8 +285,15 @@ class Trainer:
             log_every: int = 100, eval_every: Optional[int] = None, checkpoint_every: Optional[Union[int, str]] = None,
             checkpoint_final: bool = True, metrics: Sequence[Any] = (), preview: Optional[int] = None,
             best: Optional[Best] = None, stop: Optional[Plateau] = None, validation=None, restore_best: bool = False,
-            observe: Optional[Callable] = None, device_prefetch: int = 0) -> TrainState:
+            observe: Optional[Callable] = None, device_prefetch: int = 0, cooldowns: Sequence["Cooldown"] = (),
+            summaries: Optional[Callable[[TrainState], Dict[str, float]]] = None) -> TrainState:
+        """``cooldowns``: learning-rate cooldown windows applied on top of the optimizer's schedule for this fit (branching a
+        decayed run off a constant-rate trunk); ``summaries``: a callable whose scalars are logged beside the loss at the
+        logging cadence (weight norms, router statistics, ...)."""
         eng = self.engine()
+        base_schedule = self.optimizer.schedule
+        if cooldowns:
+            self.optimizer.schedule = lambda step: base_schedule(step) * math.prod(c.factor(step) for c in cooldowns)
         it, loader = _iterate(dataset)
         start_step = None
         if state is None:
@@ -336,6 +360,8 @@ class Trainer:
                 rows = next(iter(batch.values())).shape[0]
                 row["samples_per_sec"] = rows * len(window) / max(now - t_last, 1e-9)
                 t_last, window = now, []
+                if summaries is not None:
+                    row.update({k: float(v) for k, v in summaries(state).items()})
                 self.history.append({"step": state.step, **row})
                 if tracker is not None:
                     tracker.log(state.step, row)
@@ -362,6 +388,7 @@ class Trainer:
             self.checkpoints.wait()
         if restore_best and self.checkpoints is not None and self.checkpoints.best() is not None:
             state = eng.adopt(self.checkpoints.restore(state, self.checkpoints.best()))
+        self.optimizer.schedule = base_schedule
         return state
 
     def _save(self, state: TrainState, loader) -> None:

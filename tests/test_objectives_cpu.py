@@ -1,4 +1,5 @@
 """Objectives beyond diffusion / LM: supervised, JEPA, DPO, GRPO, PPO, distillation; placement report."""
+import pytest
 import torch
 import torch.nn as nn
 
@@ -235,3 +236,27 @@ def test_flow_grpo_raises_the_reward():
         stats, aux = obj.loss(None, {"x": xs, "t": grid, "old_logp": old, "rewards": r}, Step(train=True, key=it))
         opt.zero_grad(); stats.value().backward(); opt.step()
     assert sum(means[-5:]) / 5 > sum(means[:5]) / 5
+
+
+def test_fit_cooldown_summaries_loss_role_and_preview():
+    import dew_b200 as dew
+    from dew_b200.models import CausalTransformer
+    from dew_b200.objectives.lm import LMObjective
+    torch.manual_seed(0)
+    model = CausalTransformer(vocab_size=32, emb_features=32, num_layers=1, num_heads=4, head_dim=8, mlp_features=64, max_seq_len=16)
+    obj = LMObjective(model, 8, loss_role=2, samples={"prompt": [1, 2, 3], "max_new_tokens": 4})
+    tokens = torch.randint(0, 32, (16, 9))
+    roles = torch.ones(16, 9, dtype=torch.long)
+    roles[:, 5:] = 2
+    assert obj.scored_tokens({"tokens": tokens, "roles": roles}) == 16 * 4        # only the role's targets are scored
+    trainer = dew.Trainer(obj, dew.OptimConfig(learning_rate=1e-2), tracker=dew.MemoryTracker())
+    state = trainer.fit(dew.Memory({"tokens": tokens, "roles": roles}).repeat().batched(8), steps=10, log_every=2,
+                        cooldowns=[dew.Cooldown(at=4, steps=4, floor=0.1)], summaries=lambda st: {"updates": st.step})
+    rates = [r["learning_rate"] for r in trainer.tracker.rows if "learning_rate" in r]
+    assert rates[0] == pytest.approx(1e-2) and rates[-1] == pytest.approx(1e-3, rel=1e-3) and all("updates" in r for r in trainer.tracker.rows if "loss" in r)
+    assert trainer.optimizer.schedule(9) == pytest.approx(1e-2)                    # the trunk schedule is back after the fit
+    art = obj.preview(state.variables, key=0)
+    assert len(art.completions) == 1 and len(art.completions[0].split()) == 4
+    with pytest.raises(NotImplementedError):
+        LMObjective(model, 8, exit_entropy=0.1)
+    assert dew.Cooldown(0, 10, 0.0, "sqrt").factor(10) == 0.0 and dew.Cooldown(5, 10).factor(3) == 1.0
