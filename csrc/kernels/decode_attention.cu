@@ -48,7 +48,9 @@ __device__ __forceinline__ void load8(const void* base, long long elem_off, floa
 }
 
 // partial results per (row, q head, split): m (log2 domain), l, acc[D]
-template <int D, int KIND>
+// GT: the number of query heads per KV head when it is 1, 2, 4 or 8 (arrays and loops sized for it, no predicates);
+// 0 = any count up to MAX_G, checked at run time.
+template <int D, int KIND, int GT>
 __global__ void __launch_bounds__(WARPS * 32)
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict__ kpool, const void* __restrict__ vpool,
                     const float* __restrict__ kscale, const float* __restrict__ vscale,
@@ -57,11 +59,14 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
                     int max_pages, int splits, float scale_log2, int window) {
   constexpr int DV = D / 32;                 // value elements per lane
   const int row = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
-  const int G = Hq / Hkv;
+  constexpr int GM = GT ? GT : MAX_G;          // compile-time bound of every per-head array and loop
+  const int G = GT ? GT : Hq / Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __shared__ float sq[MAX_G][D];
-  __shared__ float sm_m[WARPS][MAX_G], sm_l[WARPS][MAX_G];
-  __shared__ float sm_acc[WARPS][MAX_G][D];
+  __shared__ __align__(16) float sq[GM][D];
+  __shared__ float sm_m[WARPS][GM], sm_l[WARPS][GM];
+  __shared__ float sm_acc[WARPS][GM][D];
+  __shared__ __align__(16) float sp[WARPS][32][GM];      // the current block's probabilities, [key][head]: one broadcast read per key
+  __shared__ int stok[WARPS][32];                         // and the pool token index of each of its keys
   const int len = lengths[row];
   for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
     const int g = i / D, d = i - g * D;
@@ -74,9 +79,9 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
   const int per_split = ((span + splits - 1) / splits + 31) / 32 * 32;
   const int k_begin = first + split * per_split;
   const int k_end = min(len, k_begin + per_split);
-  float m[MAX_G], l[MAX_G], acc[MAX_G][DV];
+  float m[GM], l[GM], acc[GM][DV];
 #pragma unroll
-  for (int g = 0; g < MAX_G; ++g) {
+  for (int g = 0; g < GM; ++g) {
     m[g] = -INFINITY; l[g] = 0.f;
 #pragma unroll
     for (int i = 0; i < DV; ++i) acc[g][i] = 0.f;
@@ -85,37 +90,45 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
   for (int kb = k_begin + warp * 32; kb < k_end; kb += WARPS * 32) {
     const int key = kb + lane;
     const bool live = key < k_end;
-    float s[MAX_G];
+    float s[GM];
 #pragma unroll
-    for (int g = 0; g < MAX_G; ++g) s[g] = -INFINITY;
+    for (int g = 0; g < GM; ++g) s[g] = -INFINITY;
     long long tok = 0;      // (page * page_size + slot) of this lane's key
     if (live) {
       const int page = table[key / page_size];
       tok = static_cast<long long>(page) * page_size + (key % page_size);
       const long long base = (tok * Hkv + hk) * D;
-      float dot[MAX_G];
+      float dot[GM];
 #pragma unroll
-      for (int g = 0; g < MAX_G; ++g) dot[g] = 0.f;
-#pragma unroll 4
-      for (int d0 = 0; d0 < D; d0 += 8) {
-        float kf[8];
-        load8<KIND>(kpool, base + d0, kf);
+      for (int g = 0; g < GM; ++g) dot[g] = 0.f;
+      // the key row in halves of 64 values: all eight loads of a half are in flight before the first is used, and the
+      // queries come from shared memory as float4 broadcasts
 #pragma unroll
-        for (int g = 0; g < MAX_G; ++g)
-          if (g < G) {
+      for (int h0 = 0; h0 < D; h0 += 64) {
+        float kf[8][8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) dot[g] += kf[i] * sq[g][d0 + i];
-          }
+        for (int c = 0; c < 8; ++c) load8<KIND>(kpool, base + h0 + c * 8, kf[c]);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+#pragma unroll
+          for (int g = 0; g < GM; ++g)
+            if (GT != 0 || g < G) {
+              const float4 qa = *reinterpret_cast<const float4*>(&sq[g][h0 + c * 8]);
+              const float4 qb = *reinterpret_cast<const float4*>(&sq[g][h0 + c * 8 + 4]);
+              dot[g] += kf[c][0] * qa.x + kf[c][1] * qa.y + kf[c][2] * qa.z + kf[c][3] * qa.w + kf[c][4] * qb.x + kf[c][5] * qb.y +
+                        kf[c][6] * qb.z + kf[c][7] * qb.w;
+            }
+        }
       }
       const float ks = KIND == KV_BF16 ? 1.f : kscale[tok * Hkv + hk];
 #pragma unroll
-      for (int g = 0; g < MAX_G; ++g) if (g < G) s[g] = dot[g] * ks;
+      for (int g = 0; g < GM; ++g) if (GT != 0 || g < G) s[g] = dot[g] * ks;
     }
     // online softmax update (per query head), block maximum by warp reduction
-    float p[MAX_G];
+    float p[GM];
 #pragma unroll
-    for (int g = 0; g < MAX_G; ++g) {
-      if (g < G) {
+    for (int g = 0; g < GM; ++g) {
+      if (GT != 0 || g < G) {
         float bm = s[g];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
@@ -132,44 +145,72 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const void* __restrict_
       }
     }
     // values: lane owns columns [lane * DV, lane * DV + DV); walk the block's keys
+    // eight keys at a time: their addresses, then their eight loads (all in flight together), then the products; keys
+    // past the end of the block carry zero probability and re-read a valid row
     const int nkeys = min(32, k_end - kb);
-    for (int j = 0; j < nkeys; ++j) {
-      const long long tj = __shfl_sync(0xffffffffu, tok, j);
-      const long long vb = (tj * Hkv + hk) * D + lane * DV;
-      float vf[DV];
-      if (KIND == KV_BF16) {
-        const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(vpool) + vb;
-        if (DV == 4) {
-          const uint2 v = *reinterpret_cast<const uint2*>(vp);
-          vf[0] = bf_lo(v.x); vf[1] = bf_hi(v.x); vf[2] = bf_lo(v.y); vf[3] = bf_hi(v.y);
+    __syncwarp();
+#pragma unroll
+    for (int g = 0; g < GM; ++g) sp[warp][lane][g] = (GT != 0 || g < G) ? p[g] : 0.f;
+    stok[warp][lane] = static_cast<int>(tok);
+    __syncwarp();
+    for (int j0 = 0; j0 < nkeys; j0 += 8) {
+      long long tj[8];
+      float vf[8][DV];
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) tj[jj] = stok[warp][min(j0 + jj, nkeys - 1)];
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        const long long vb = (tj[jj] * Hkv + hk) * D + lane * DV;
+        if (KIND == KV_BF16) {
+          const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(vpool) + vb;
+          if (DV == 4) {
+            const uint2 v = *reinterpret_cast<const uint2*>(vp);
+            vf[jj][0] = bf_lo(v.x); vf[jj][1] = bf_hi(v.x); vf[jj][2] = bf_lo(v.y); vf[jj][3] = bf_hi(v.y);
+          } else {
+#pragma unroll
+            for (int i = 0; i < DV; ++i) vf[jj][i] = __bfloat162float(vp[i]);
+          }
+        } else if (KIND == KV_INT8) {
+          const int8_t* vp = reinterpret_cast<const int8_t*>(vpool) + vb;
+#pragma unroll
+          for (int i = 0; i < DV; ++i) vf[jj][i] = static_cast<float>(vp[i]);
+        } else {
+          const __nv_fp8_e4m3* vp = reinterpret_cast<const __nv_fp8_e4m3*>(vpool) + vb;
+#pragma unroll
+          for (int i = 0; i < DV; ++i) vf[jj][i] = static_cast<float>(vp[i]);
+        }
+      }
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        const int j = min(j0 + jj, 31);
+        const bool on = j0 + jj < nkeys;
+        const float vs = KIND == KV_BF16 ? 1.f : vscale[tj[jj] * Hkv + hk];
+        float pk[GM];
+        if (GM % 4 == 0) {
+#pragma unroll
+          for (int g4 = 0; g4 < GM / 4; ++g4) {
+            const float4 t4 = *reinterpret_cast<const float4*>(&sp[warp][j][g4 * 4]);
+            pk[g4 * 4] = t4.x; pk[g4 * 4 + 1] = t4.y; pk[g4 * 4 + 2] = t4.z; pk[g4 * 4 + 3] = t4.w;
+          }
         } else {
 #pragma unroll
-          for (int i = 0; i < DV; ++i) vf[i] = __bfloat162float(vp[i]);
+          for (int g = 0; g < GM; ++g) pk[g] = sp[warp][j][g];
         }
-      } else if (KIND == KV_INT8) {
-        const int8_t* vp = reinterpret_cast<const int8_t*>(vpool) + vb;
 #pragma unroll
-        for (int i = 0; i < DV; ++i) vf[i] = static_cast<float>(vp[i]);
-      } else {
-        const __nv_fp8_e4m3* vp = reinterpret_cast<const __nv_fp8_e4m3*>(vpool) + vb;
+        for (int g = 0; g < GM; ++g) {
+          if (GT != 0 || g < G) {
+            const float pj = on ? pk[g] * vs : 0.f;
 #pragma unroll
-        for (int i = 0; i < DV; ++i) vf[i] = static_cast<float>(vp[i]);
-      }
-      const float vs = KIND == KV_BF16 ? 1.f : vscale[tj * Hkv + hk];
-#pragma unroll
-      for (int g = 0; g < MAX_G; ++g) {
-        if (g < G) {
-          const float pj = __shfl_sync(0xffffffffu, p[g], j) * vs;
-#pragma unroll
-          for (int i = 0; i < DV; ++i) acc[g][i] += pj * vf[i];
+            for (int i = 0; i < DV; ++i) acc[g][i] += pj * vf[jj][i];
+          }
         }
       }
     }
   }
   // merge the CTA's warps
 #pragma unroll
-  for (int g = 0; g < MAX_G; ++g) {
-    if (g < G) {
+  for (int g = 0; g < GM; ++g) {
+    if (GT != 0 || g < G) {
       if (lane == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
 #pragma unroll
       for (int i = 0; i < DV; ++i) sm_acc[warp][g][lane * DV + i] = acc[g][i];
@@ -276,12 +317,16 @@ extern "C" int dewb_paged_decode(const void* q, const void* kpool, const void* v
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(rows, Hkv, splits);
   const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(q);
-#define DEWB_DECODE(DD, KK) paged_decode_kernel<DD, KK><<<grid, WARPS * 32, 0, stream>>>( \
+  const int Gq = Hq / Hkv;
+#define DEWB_DECODE_G(DD, KK, GG) paged_decode_kernel<DD, KK, GG><<<grid, WARPS * 32, 0, stream>>>( \
     qp, kpool, vpool, kscale, vscale, page_table, lengths, part_m, part_l, part_acc, Hq, Hkv, page_size, max_pages, splits, scale_log2, window)
+#define DEWB_DECODE(DD, KK) do { if (Gq == 4) DEWB_DECODE_G(DD, KK, 4); else if (Gq == 8) DEWB_DECODE_G(DD, KK, 8); \
+    else if (Gq == 1) DEWB_DECODE_G(DD, KK, 1); else if (Gq == 2) DEWB_DECODE_G(DD, KK, 2); else DEWB_DECODE_G(DD, KK, 0); } while (0)
 #define DEWB_DECODE_D(KK) do { if (D == 64) DEWB_DECODE(64, KK); else if (D == 128) DEWB_DECODE(128, KK); else DEWB_DECODE(256, KK); } while (0)
   if (kv_kind == KV_BF16) DEWB_DECODE_D(KV_BF16); else if (kv_kind == KV_INT8) DEWB_DECODE_D(KV_INT8); else DEWB_DECODE_D(KV_FP8);
 #undef DEWB_DECODE_D
 #undef DEWB_DECODE
+#undef DEWB_DECODE_G
   __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(out);
   if (D == 64) decode_combine_kernel<64><<<rows * Hq, 64, 0, stream>>>(part_m, part_l, part_acc, sinks, op, lse, Hq, splits);
   else if (D == 128) decode_combine_kernel<128><<<rows * Hq, 128, 0, stream>>>(part_m, part_l, part_acc, sinks, op, lse, Hq, splits);
@@ -300,5 +345,18 @@ extern "C" int dewb_kv_append(const void* k_new, const void* v_new, void* kpool,
   if (kv_kind == KV_BF16) kv_append_kernel<KV_BF16><<<grid, 128, 0, stream>>>(kp, vp, kpool, vpool, kscale, vscale, page_table, positions, Hkv, D, page_size, max_pages);
   else if (kv_kind == KV_INT8) kv_append_kernel<KV_INT8><<<grid, 128, 0, stream>>>(kp, vp, kpool, vpool, kscale, vscale, page_table, positions, Hkv, D, page_size, max_pages);
   else kv_append_kernel<KV_FP8><<<grid, 128, 0, stream>>>(kp, vp, kpool, vpool, kscale, vscale, page_table, positions, Hkv, D, page_size, max_pages);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// The second stage alone: out [rows, Hq, D] bf16 from the per-split partials (used after dewb_paged_decode_stream).
+extern "C" int dewb_decode_combine(const float* part_m, const float* part_l, const float* part_acc, const float* sinks,
+                                   void* out, float* lse, int rows, int Hq, int D, int splits, void* stream_ptr) {
+  if (rows <= 0) return 0;
+  if (D != 64 && D != 128 && D != 256) return -3;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(out);
+  if (D == 64) decode_combine_kernel<64><<<rows * Hq, 64, 0, stream>>>(part_m, part_l, part_acc, sinks, op, lse, Hq, splits);
+  else if (D == 128) decode_combine_kernel<128><<<rows * Hq, 128, 0, stream>>>(part_m, part_l, part_acc, sinks, op, lse, Hq, splits);
+  else decode_combine_kernel<256><<<rows * Hq, 256, 0, stream>>>(part_m, part_l, part_acc, sinks, op, lse, Hq, splits);
   return static_cast<int>(cudaGetLastError());
 }

@@ -1,0 +1,257 @@
+// Paged decode attention, streamed: a producer warp brings whole 64-key pages of K and V into a shared-memory ring with
+// TMA (one [64 x 128] tile each, 128-byte swizzle, no multicast) while four consumer warps compute from shared memory
+// on the tensor cores.  bf16 pools, head dimension 128, up to 8 query heads per KV head, page size a multiple of 64.
+//
+// grid = (row, kv head, key split), 160 threads.  Per 64-key tile each consumer warp owns 16 keys:
+//   S   = Q K^T   mma.sync m16n8k16 (rows = the query heads of the group, padded to 16; K fragments by ldmatrix)
+//   online softmax in the log2 domain, per head row, inside the warp (quad reductions)
+//   O  += P V     the score accumulators re-packed as the A operand, V fragments by ldmatrix.trans
+// The per-warp (max, sum, O) are merged in shared memory and written as one partial per (row, head, split); the
+// combine kernel of decode_attention.cu finishes (splits, sinks, normalisation).  The producer runs up to three tiles
+// ahead, so the memory latency is hidden by the ring rather than by occupancy.
+// The query count per KV head is far below the 64 rows tcgen05 needs, which is why this kernel uses the warp-level MMA.
+//
+// Capability parity: src/dew/nn/kernels/decode_attention.py (attend_paged), src/dew/nn/kernels/templates/attention_decode.py.
+#include "../common/ptx.cuh"
+#include "../common/tmap.h"
+
+namespace dewb {
+namespace decode2 {
+
+constexpr int D = 128;
+constexpr int TK = 64;                       // keys per tile (one page or a page-aligned part of one)
+constexpr int STAGES = 3;
+constexpr int CONSUMERS = 4;
+constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr int TILE_BYTES = TK * D * 2;       // 16 KiB: two 64-column halves of [64 rows x 128 B]
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;  // K and V
+constexpr int OFF_Q = STAGES * STAGE_BYTES;  // [8 heads][128] bf16
+constexpr int OFF_BARS = OFF_Q + 8 * D * 2;
+constexpr int SMEM = OFF_BARS + 128;
+constexpr uint32_t FULL = 0xffffffffu;
+
+struct Bars {
+  uint64_t full[STAGES], empty[STAGES];
+  int abort_flag, poisoned;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D (+)= A B, A [16 x 16] row-major bf16 (a1, a3: rows 8..15), B [16 x 8] as two k-halves, fp32 accumulate
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 16-byte piece `chunk` (8 values, 0..15) of row `r` of a [64 x 128] bf16 tile stored as two swizzled 64-column halves
+__device__ __forceinline__ uint32_t tile_addr(uint32_t tile, int r, int chunk) {
+  return tile + (chunk >> 3) * (TK * 128) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(THREADS, 2)
+paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
+                        const __nv_bfloat16* __restrict__ q, const int* __restrict__ page_table,
+                        const int* __restrict__ lengths, float* __restrict__ part_m, float* __restrict__ part_l,
+                        float* __restrict__ part_acc, int Hq, int Hkv, int page_size, int max_pages, int splits,
+                        float scale_log2, int window, int* __restrict__ err) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(err, 0, ERR_BAD_ARG);
+    return;
+  }
+  Bars* bars = reinterpret_cast<Bars*>(smem + OFF_BARS);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) bars->poisoned = *reinterpret_cast<volatile int*>(err);
+  __syncthreads();
+  if (bars->poisoned != 0) return;
+  const int row = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+  const int G = Hq / Hkv;
+  const int len = lengths[row];
+  // this split's keys, in whole 64-key tiles: [t_begin, t_end) tile indices of the row; keys outside [first, len) are masked
+  const int first = (window > 0 && len > window) ? len - window : 0;
+  const int tile_lo = first / TK, tile_hi = (len + TK - 1) / TK;
+  const int per_split = (tile_hi - tile_lo + splits - 1) / splits;
+  const int t_begin = tile_lo + split * per_split;
+  const int t_end = min(tile_hi, t_begin + per_split);
+  const int ntiles = max(0, t_end - t_begin);
+
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem + OFF_Q);
+  if (tid == 0) {
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&bars->full[i], 1); mbar_init(&bars->empty[i], CONSUMERS); }
+    bars->abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  for (int i = tid; i < 8 * D; i += THREADS) {
+    const int g = i / D, d = i - g * D;
+    sQ[i] = g < G ? q[(static_cast<long long>(row) * Hq + hk * G + g) * D + d] : __float2bfloat16(0.f);
+  }
+  __syncthreads();
+  volatile int* abort_flag = &bars->abort_flag;
+  const uint32_t ring = smem_u32(smem);
+
+  // per-warp running state of the group's heads: this lane's head row is lane / 4
+  float m_run = -INFINITY, l_run = 0.f;
+  float o[16][4];
+#pragma unroll
+  for (int n = 0; n < 16; ++n) { o[n][0] = 0.f; o[n][1] = 0.f; o[n][2] = 0.f; o[n][3] = 0.f; }
+
+  if (warp == CONSUMERS) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tk);
+      tma_prefetch_desc(&tv);
+      const int* table = page_table + static_cast<long long>(row) * max_pages;
+      for (int t = 0; t < ntiles; ++t) {
+        const int s = t % STAGES;
+        const uint32_t ph = (t / STAGES) & 1;
+        if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); break; }
+        const int key0 = (t_begin + t) * TK;
+        const int page = table[key0 / page_size];
+        const int row0 = page * page_size + key0 % page_size;
+        uint8_t* st = smem + s * STAGE_BYTES;
+        mbar_expect_tx(&bars->full[s], STAGE_BYTES);
+        tma_load_2d(st, &tk, &bars->full[s], hk * D, row0);
+        tma_load_2d(st + TK * 128, &tk, &bars->full[s], hk * D + 64, row0);
+        tma_load_2d(st + TILE_BYTES, &tv, &bars->full[s], hk * D, row0);
+        tma_load_2d(st + TILE_BYTES + TK * 128, &tv, &bars->full[s], hk * D + 64, row0);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ consumers
+    // Q fragments: A operand rows = heads; rows 8..15 do not exist (a1 = a3 = 0)
+    uint32_t qa0[8], qa2[8];
+    {
+      const int g = lane >> 2, c = (lane & 3) * 2;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        qa0[ks] = *reinterpret_cast<const uint32_t*>(sQ + g * D + ks * 16 + c);
+        qa2[ks] = *reinterpret_cast<const uint32_t*>(sQ + g * D + ks * 16 + 8 + c);
+      }
+    }
+    bool ok = true;
+    for (int t = 0; t < ntiles && ok; ++t) {
+      const int s = t % STAGES;
+      const uint32_t ph = (t / STAGES) & 1;
+      {
+        const bool got = mbar_wait(&bars->full[s], ph, abort_flag);
+        if (!__all_sync(FULL, got)) { if (lane == 0) atomicCAS(err, 0, ERR_WAIT_FULL); ok = false; break; }
+      }
+      const uint32_t kt = ring + s * STAGE_BYTES, vt = kt + TILE_BYTES;
+      const int kw = warp * 16;                           // this warp's 16 keys of the tile
+      // scores: two blocks of 8 keys
+      float sc[2][4];
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) { sc[nb][0] = 0.f; sc[nb][1] = 0.f; sc[nb][2] = 0.f; sc[nb][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        // four 8x8 matrices: (keys 0..7, dims lo), (keys 0..7, dims hi), (keys 8..15, dims lo), (keys 8..15, dims hi)
+        const int mat = lane >> 3, r8 = lane & 7;
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(tile_addr(kt, kw + (mat >> 1) * 8 + r8, ks * 2 + (mat & 1)), b0, b1, b2, b3);
+        mma_16816(sc[0], qa0[ks], 0u, qa2[ks], 0u, b0, b1);
+        mma_16816(sc[1], qa0[ks], 0u, qa2[ks], 0u, b2, b3);
+      }
+      // mask and online softmax for head row lane / 4 (values of rows 8..15, sc[.][2..3], are ignored)
+      const int key_base = (t_begin + t) * TK + kw + (lane & 3) * 2;
+      float pv[4];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int key = key_base + (i >> 1) * 8 + (i & 1);
+        const float v = (key >= first && key < len) ? sc[i >> 1][i & 1] * scale_log2 : -INFINITY;
+        pv[i] = v;
+        mx = fmaxf(mx, v);
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+      float ps = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { pv[i] = (m_new == -INFINITY) ? 0.f : exp2f(pv[i] - m_new); ps += pv[i]; }
+      ps += __shfl_xor_sync(FULL, ps, 1);
+      ps += __shfl_xor_sync(FULL, ps, 2);
+      l_run = l_run * alpha + ps;
+      m_run = m_new;
+#pragma unroll
+      for (int n = 0; n < 16; ++n) { o[n][0] *= alpha; o[n][1] *= alpha; }
+      // P as the A operand of the second product: keys 0..7 -> a0, keys 8..15 -> a2
+      const uint32_t pa0 = pack_bf16(pv[0], pv[1]), pa2 = pack_bf16(pv[2], pv[3]);
+#pragma unroll
+      for (int nb2 = 0; nb2 < 8; ++nb2) {
+        // four transposed 8x8 matrices: (keys lo, dims chunk 2 nb2), (keys hi, same chunk), (keys lo, chunk + 1), (keys hi, chunk + 1)
+        const int mat = lane >> 3, r8 = lane & 7;
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(tile_addr(vt, kw + (mat & 1) * 8 + r8, nb2 * 2 + (mat >> 1)), b0, b1, b2, b3);
+        mma_16816(o[nb2 * 2], pa0, 0u, pa2, 0u, b0, b1);
+        mma_16816(o[nb2 * 2 + 1], pa0, 0u, pa2, 0u, b2, b3);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->empty[s]);
+    }
+  }
+  // merge the four consumer warps (the ring is free: every tile has been consumed or the CTA is leaving)
+  __syncthreads();
+  float* sm_m = reinterpret_cast<float*>(smem);                      // [4][8]
+  float* sm_l = sm_m + CONSUMERS * 8;                                // [4][8]
+  float* sm_acc = sm_l + CONSUMERS * 8;                              // [4][8][128]
+  if (warp < CONSUMERS) {
+    const int g = lane >> 2, c = (lane & 3) * 2;
+    if ((lane & 3) == 0) { sm_m[warp * 8 + g] = m_run; sm_l[warp * 8 + g] = l_run; }
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      sm_acc[(warp * 8 + g) * D + n * 8 + c] = o[n][0];
+      sm_acc[(warp * 8 + g) * D + n * 8 + c + 1] = o[n][1];
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < G * D; i += THREADS) {
+    const int g = i / D, d = i - g * D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < CONSUMERS; ++w) mm = fmaxf(mm, sm_m[w * 8 + g]);
+    float ll = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < CONSUMERS; ++w) {
+      const float f = sm_m[w * 8 + g] == -INFINITY ? 0.f : exp2f(sm_m[w * 8 + g] - mm);
+      ll += sm_l[w * 8 + g] * f;
+      a += sm_acc[(w * 8 + g) * D + d] * f;
+    }
+    const long long oidx = (static_cast<long long>(row) * Hq + hk * G + g) * splits + split;
+    part_acc[oidx * D + d] = a;
+    if (d == 0) { part_m[oidx] = mm; part_l[oidx] = ll; }
+  }
+}
+
+}  // namespace decode2
+}  // namespace dewb
+
+// The streamed form of the paged decode attention's first stage: writes the per-split partials (part_m, part_l in the log2
+// domain, part_acc) exactly as the first-stage kernel of dewb_paged_decode does; the caller runs the same combine.
+// kpool / vpool: bf16 [pool_tokens, Hkv, 128] (pool_tokens = pages * page_size), page_size a multiple of 64, Hq / Hkv <= 8.
+extern "C" int dewb_paged_decode_stream(const void* q, const void* kpool, const void* vpool, long long pool_tokens,
+                                        const int* page_table, const int* lengths, float* part_m, float* part_l,
+                                        float* part_acc, int rows, int Hq, int Hkv, int page_size, int max_pages, int splits,
+                                        float scale, int window, int* err, void* stream_ptr) {
+  using namespace dewb::decode2;
+  if (rows <= 0) return 0;
+  if (Hq % Hkv != 0 || Hq / Hkv > 8 || page_size % TK != 0 || splits < 1 || pool_tokens <= 0) return -3;
+  CUtensorMap tk, tv;
+  int r;
+  const uint64_t cols = static_cast<uint64_t>(Hkv) * D;
+  if ((r = dewb::make_tmap_2d(&tk, kpool, static_cast<uint64_t>(pool_tokens), cols, cols, TK, 64, 2, true))) return 1000 + r;
+  if ((r = dewb::make_tmap_2d(&tv, vpool, static_cast<uint64_t>(pool_tokens), cols, cols, TK, 64, 2, true))) return 2000 + r;
+  cudaError_t e = cudaFuncSetAttribute(paged_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 grid(rows, Hkv, splits);
+  paged_decode_tma_kernel<<<grid, THREADS, SMEM, reinterpret_cast<cudaStream_t>(stream_ptr)>>>(
+      tk, tv, reinterpret_cast<const __nv_bfloat16*>(q), page_table, lengths, part_m, part_l, part_acc, Hq, Hkv, page_size,
+      max_pages, splits, scale * 1.4426950408889634f, window, err);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -31,6 +31,7 @@ def main(argv=None):
     ap.add_argument("--chunk", type=int, default=2048)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--profile", default=None, help="write a torch.profiler kernel table of eight decode steps to this file")
     args = ap.parse_args(argv)
 
     from ..models import CausalTransformer
@@ -73,6 +74,16 @@ def main(argv=None):
         server.step()
     torch.cuda.synchronize()
     t_prefill = time.perf_counter() - t0
+    if args.profile:
+        for _ in range(3):
+            server.step()
+        with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA]) as prof:
+            for _ in range(8):
+                server.step()
+            torch.cuda.synchronize()
+        if rank == 0:
+            with open(args.profile, "w") as f:
+                f.write(prof.key_averages().table(sort_by="self_cuda_time_total", row_limit=40, max_name_column_width=90))
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     decoded0 = server.decoded_tokens
     steps0 = server.steps

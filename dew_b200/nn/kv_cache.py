@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -163,12 +164,30 @@ class KVStore:
             longest = self.max_len
             while splits < 16 and R * self.kv_heads * splits < 592 and longest // (splits * 2) >= 256:
                 splits *= 2
+            # a warp walks its keys 32 at a time with a few dependent memory round trips per step: keep a CTA's share of
+            # the longest possible row near 512 keys so that the walk is short and there are CTAs to overlap
+            splits = max(splits, min(16, (longest + 511) // 512))
             n = R * Hq * splits
             if self._scratch is None or self._scratch[0].numel() < n:
                 self._scratch = (torch.empty(n, dtype=torch.float32, device=q.device), torch.empty(n, dtype=torch.float32, device=q.device),
                                  torch.empty(n * D, dtype=torch.float32, device=q.device))
             pm, pl, pa = self._scratch
             out = torch.empty_like(q)
+            if (self.kind == 0 and D == 128 and self.page_size % 64 == 0 and hasattr(lib, "dewb_paged_decode_stream")
+                    and os.environ.get("DEWB_DECODE", "stream") == "stream"):
+                # streamed form: TMA page tiles into a shared-memory ring, scores and values on the warp-level tensor cores
+                lens = lengths.to(torch.int32).contiguous()
+                L.check(lib.dewb_paged_decode_stream(L.ptr(q.contiguous()), L.ptr(self.k[layer]), L.ptr(self.v[layer]),
+                                                     ctypes.c_longlong(self.pages * self.page_size), L.ptr(self.page_table), L.ptr(lens),
+                                                     L.ptr(pm), L.ptr(pl), L.ptr(pa), ctypes.c_int(R), ctypes.c_int(Hq),
+                                                     ctypes.c_int(self.kv_heads), ctypes.c_int(self.page_size), ctypes.c_int(self.max_pages),
+                                                     ctypes.c_int(splits), ctypes.c_float(scale), ctypes.c_int(window or 0),
+                                                     L.ptr(L.status(q.device)), L.stream_ptr()), "paged_decode_stream")
+                L.check(lib.dewb_decode_combine(L.ptr(pm), L.ptr(pl), L.ptr(pa), L.ptr(sinks.float().contiguous() if sinks is not None else None),
+                                                L.ptr(out), L.ptr(None), ctypes.c_int(R), ctypes.c_int(Hq), ctypes.c_int(D), ctypes.c_int(splits),
+                                                L.stream_ptr()), "decode_combine")
+                L.count_launches(2)
+                return out
             L.check(lib.dewb_paged_decode(L.ptr(q.contiguous()), L.ptr(self.k[layer]), L.ptr(self.v[layer]),
                                           L.ptr(self.k_scale[layer] if self.kind else None),
                                           L.ptr(self.v_scale[layer] if self.kind else None), L.ptr(self.page_table),

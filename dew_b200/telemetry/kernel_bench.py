@@ -260,6 +260,24 @@ def bench_moe(out, peaks, flush, iters=10):
          combine_gbs=(moved + T * d * 2) / t_c.median_ms / 1e6)
 
 
+def bench_decode(out, peaks, flush, iters=10, rows=128, max_len=2304):
+    """Paged decode attention at the serving configuration: 128 rows, 32 query / 8 KV heads of 128, page 64, context lengths
+    uniform in [128, max_len]; the bytes are the keys and values each row reads once."""
+    from ..nn.kv_cache import KVCache, KVStore
+    store = KVStore(KVCache(page_size=64), 1, rows, max_len, 8, 128, torch.bfloat16, "cuda")
+    store.k.normal_()
+    store.v.normal_()
+    g = torch.Generator().manual_seed(0)
+    lengths = torch.randint(128, max_len + 1, (rows,), generator=g).to("cuda", torch.int32)
+    q = torch.randn(rows, 32, 128, device="cuda").to(torch.bfloat16)
+    ref = store.decode_attention(0, q, lengths)
+    t = device_time(lambda: store.decode_attention(0, q, lengths), iters=iters, flush=flush)
+    L.check_status()
+    nbytes = int(lengths.sum()) * 8 * 128 * 2 * 2
+    _row(out, kernel="paged_decode", rows=rows, max_len=max_len, mean_len=float(lengths.float().mean()), ms=t.median_ms,
+         gbs=nbytes / t.median_ms / 1e6, frac_of_measured=nbytes / t.median_ms / 1e6 / peaks["hbm_gbs"], finite=bool(torch.isfinite(ref.float()).all()))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=None)
@@ -299,6 +317,8 @@ def main(argv=None):
         bench_sampling(out, peaks, flush, iters=args.iters)
     if "moe" in only:
         bench_moe(out, peaks, flush, iters=args.iters)
+    if "decode" in only:
+        bench_decode(out, peaks, flush, iters=args.iters)
 
 
 if __name__ == "__main__":

@@ -342,7 +342,8 @@ def test_grouped_gemm_forward_backward(T, k, E, d, F):
 
 
 @pytest.mark.parametrize("quantized,page_size,D,Hq,Hkv", [(None, 16, 128, 8, 2), (None, 64, 128, 4, 1), ("int8", 16, 128, 8, 2),
-                                                          ("float8_e4m3fn", 32, 64, 4, 4), (None, None, 128, 32, 8)])
+                                                          ("float8_e4m3fn", 32, 64, 4, 4), (None, None, 128, 32, 8),
+                                                          (None, 64, 128, 32, 8), (None, 128, 128, 8, 1), (None, 64, 128, 6, 2)])
 def test_paged_decode_attention(quantized, page_size, D, Hq, Hkv):
     from dew_b200.nn.kv_cache import KVCache, KVStore, paged_attention_reference
     torch.manual_seed(11)
@@ -367,6 +368,37 @@ def test_paged_decode_attention(quantized, page_size, D, Hq, Hkv):
     out = store.decode_attention(0, q, lengths)
     ref = paged_attention_reference(store, 0, q.float(), lengths, 1.0 / math.sqrt(D))
     assert rel_err(out, ref) <= 2e-2, rel_err(out, ref)
+
+
+def test_paged_decode_streamed_kernel_window_sinks_and_long_rows():
+    """The TMA-streamed decode kernel (64-key pages, bf16) with a sliding window, attention sinks and rows long enough for
+    several key splits, against the reference; and against the first-generation kernel on the same store."""
+    import os
+    from dew_b200.nn.kv_cache import KVCache, KVStore, paged_attention_reference
+    torch.manual_seed(5)
+    rows, max_len, Hq, Hkv, D = 9, 2304, 32, 8, 128
+    store = KVStore(KVCache(page_size=64), 1, rows, max_len, Hkv, D, torch.bfloat16, DEV)
+    perm = torch.randperm(store.pages, device=DEV).to(torch.int32)
+    store.page_table.copy_(perm.reshape(rows, store.max_pages))
+    lengths = torch.tensor([1, 63, 64, 65, 500, 1024, 1500, 2303, 2304], device=DEV, dtype=torch.int32)
+    S = int(lengths.max())
+    k = torch.randn(rows, S, Hkv, D, device=DEV).to(torch.bfloat16)
+    v = torch.randn(rows, S, Hkv, D, device=DEV).to(torch.bfloat16)
+    pos = torch.arange(S, device=DEV)[None].expand(rows, S).clone()
+    pos[pos >= lengths[:, None]] = -1
+    store.write(0, k, v, pos)
+    q = torch.randn(rows, Hq, D, device=DEV).to(torch.bfloat16)
+    sinks = torch.randn(Hq, device=DEV)
+    for window, sk in ((None, None), (300, None), (None, sinks), (1000, sinks)):
+        out = store.decode_attention(0, q, lengths, window=window, sinks=sk)
+        ref = paged_attention_reference(store, 0, q.float(), lengths, 1.0 / math.sqrt(D), window, sk, 0.0)
+        assert rel_err(out, ref) <= 2e-2, (window, sk is not None, rel_err(out, ref))
+        os.environ["DEWB_DECODE"] = "lanes"
+        try:
+            old = store.decode_attention(0, q, lengths, window=window, sinks=sk)
+        finally:
+            os.environ.pop("DEWB_DECODE")
+        assert rel_err(out, old) <= 2e-2
 
 
 @pytest.mark.parametrize("B,T,C,K,act,bias", [(2, 200, 64, 4, True, False), (1, 1000, 4096 + 8, 4, True, True), (3, 65, 128, 3, False, True)])
