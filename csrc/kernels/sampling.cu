@@ -72,7 +72,35 @@ argmax_rows_kernel(const T* __restrict__ logits, long long row_stride, int V, lo
   const T* row = logits + blockIdx.x * row_stride;
   float best = -INFINITY;
   int idx = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  // 16-byte loads over the aligned body of the row, four in flight per thread; scalar loads for the rest
+  constexpr int PER = 16 / static_cast<int>(sizeof(T));
+  int body = 0;
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    body = V / PER * PER;
+    const uint4* rv = reinterpret_cast<const uint4*>(row);
+    const int nvec = body / PER;
+    for (int v0 = threadIdx.x; v0 < nvec; v0 += 4 * blockDim.x) {
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int vi = v0 + u * blockDim.x;
+        raw[u] = vi < nvec ? rv[vi] : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int vi = v0 + u * blockDim.x;
+        if (vi >= nvec) continue;
+        const T* e = reinterpret_cast<const T*>(&raw[u]);
+#pragma unroll
+        for (int c = 0; c < PER; ++c) {
+          const float x = load_logit(e, c);
+          const int i = vi * PER + c;
+          if (x > best || (x == best && i < idx)) { best = x; idx = i; }
+        }
+      }
+    }
+  }
+  for (int i = body + threadIdx.x; i < V; i += blockDim.x) {
     const float x = load_logit(row, i);
     if (x > best || (x == best && i < idx)) { best = x; idx = i; }
   }

@@ -69,6 +69,14 @@ def main(argv=None):
         dist.barrier()
     t0 = time.perf_counter()
     tickets = [server.submit(p, args.new_tokens) for p in prompts]
+    if args.profile:
+        with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA]) as pprof:
+            for _ in range(2):
+                server.step()
+            torch.cuda.synchronize()
+        if rank == 0:
+            with open(args.profile + ".prefill", "w") as f:
+                f.write(pprof.key_averages().table(sort_by="self_cuda_time_total", row_limit=40, max_name_column_width=90))
     # prefill phase: step until every row has its prompt in the cache
     while any(r is None or r.prefilled < len(r.ticket.prompt) for r in server.rows) and server.busy:
         server.step()

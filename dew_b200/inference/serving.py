@@ -202,13 +202,20 @@ class Server:
                 last.append(len(piece) - 1)
             slots = torch.tensor([s for s, _ in members], device=self.device)
             with torch.no_grad():
-                logits = self._call(ids, positions=pos, cache=self.store.select(slots))
+                # the head runs only on each row's last position (the only logits a prefill chunk can need)
+                if hasattr(self.model, "logits"):
+                    hidden = self._call(ids, positions=pos, cache=self.store.select(slots), return_hidden=True)
+                    picked = hidden[torch.arange(len(members), device=self.device), torch.tensor(last, device=self.device)]
+                    last_logits = self.model.logits(picked)
+                else:
+                    full = self._call(ids, positions=pos, cache=self.store.select(slots))
+                    last_logits = full[torch.arange(len(members), device=self.device), torch.tensor(last, device=self.device)]
             self.store.select(None)
             for i, (s, r) in enumerate(members):
                 r.prefilled += last[i] + 1
                 if r.prefilled >= len(r.ticket.prompt):
                     self.ledger.publish(r.ticket.prompt, r.pages)
-                    tok = self._draw(logits[i, last[i]][None], r, 0)
+                    tok = self._draw(last_logits[i][None], r, 0)
                     self.last_tokens[s] = tok
                     r.pending_first = True
 
