@@ -192,6 +192,10 @@ class Server:
             groups.setdefault(r.prefilled, []).append((s, r))
         for start, members in groups.items():
             width = min(self.chunk, max(len(r.ticket.prompt) - start for _, r in members))
+            if self.device.type == "cuda" and width > 1:
+                # a multiple of 128 keeps the chunk on the flash kernels and the set of shapes small; the pad positions are -1
+                # (not written to the cache, never attended to by the real positions before them)
+                width = (width + 127) // 128 * 128
             ids = torch.zeros(len(members), width, dtype=torch.long, device=self.device)
             pos = torch.full((len(members), width), -1, dtype=torch.long, device=self.device)
             last = []
