@@ -196,15 +196,20 @@ class Server:
                 # a multiple of 128 keeps the chunk on the flash kernels and the set of shapes small; the pad positions are -1
                 # (not written to the cache, never attended to by the real positions before them)
                 width = (width + 127) // 128 * 128
-            ids = torch.zeros(len(members), width, dtype=torch.long, device=self.device)
-            pos = torch.full((len(members), width), -1, dtype=torch.long, device=self.device)
+            # the batch is assembled on the host and crosses to the device once
+            ids_h = torch.zeros(len(members), width, dtype=torch.long)
+            pos_h = torch.full((len(members), width), -1, dtype=torch.long)
             last = []
+            longest = 0
             for i, (s, r) in enumerate(members):
                 piece = r.ticket.prompt[start:start + width]
-                ids[i, :len(piece)] = torch.tensor(piece, device=self.device)
-                pos[i, :len(piece)] = torch.arange(start, start + len(piece), device=self.device)
+                ids_h[i, :len(piece)] = torch.tensor(piece, dtype=torch.long)
+                pos_h[i, :len(piece)] = torch.arange(start, start + len(piece))
                 last.append(len(piece) - 1)
+                longest = max(longest, len(piece))
+            ids, pos = ids_h.to(self.device, non_blocking=True), pos_h.to(self.device, non_blocking=True)
             slots = torch.tensor([s for s, _ in members], device=self.device)
+            self.store.chunk_span = (start, start + longest)
             with torch.no_grad():
                 # the head runs only on each row's last position (the only logits a prefill chunk can need)
                 if hasattr(self.model, "logits"):
@@ -215,6 +220,7 @@ class Server:
                     full = self._call(ids, positions=pos, cache=self.store.select(slots))
                     last_logits = full[torch.arange(len(members), device=self.device), torch.tensor(last, device=self.device)]
             self.store.select(None)
+            self.store.chunk_span = None
             for i, (s, r) in enumerate(members):
                 r.prefilled += last[i] + 1
                 if r.prefilled >= len(r.ticket.prompt):

@@ -89,6 +89,7 @@ class KVStore:
         self.dtype, self.device = dtype, torch.device(device)
         self.row_ids: Optional[torch.Tensor] = None      # rows of the store addressed by the batch rows of a call
         self._scratch = None
+        self.chunk_span: Optional[Tuple[int, int]] = None      # (first position, one past the last) of the prefill chunk in flight, when the caller knows
 
     # ------------------------------------------------------------------ addressing
     def select(self, row_ids: Optional[torch.Tensor]) -> "KVStore":
@@ -214,10 +215,17 @@ class KVStore:
             lengths = torch.where(pos >= 0, pos + 1, torch.zeros_like(pos))
             return self.decode_attention(layer, q[:, 0], lengths, window=window, sinks=sinks, softcap=softcap)[:, None]
         self.write(layer, k, v, positions)
-        start = int(positions[:, 0].clamp_min(0).min())
-        if start == 0 and bool((positions[:, 0] <= 0).all()):
+        if self.chunk_span is not None:
+            # the caller knows where this chunk starts and ends (a server batching rows by start offset): no device read
+            start, total, fresh = self.chunk_span[0], self.chunk_span[1], self.chunk_span[0] == 0
+        else:
+            start = int(positions[:, 0].clamp_min(0).min())
+            fresh = start == 0 and bool((positions[:, 0] <= 0).all())
+            total = None
+        if fresh:
             return ops.attention(q, k, v, causal=causal, window=window, softcap=softcap, sinks=sinks)
-        total = int(positions.max()) + 1
+        if total is None:
+            total = int(positions.max()) + 1
         kc, vc = self.gather(layer, total, dtype=q.dtype)
         # bottom-right aligned causal attention of the chunk against everything cached so far (rows share `start`)
         return ops.attention_reference(q, kc, vc, causal=causal, window=window, softcap=softcap, sinks=sinks)
