@@ -44,3 +44,19 @@ def test_link_probe_two_cpu_ranks():
     r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
     assert r["rows"] == 10 and r["positive"] and r["mem"] == 0 and r["table_lines"] == 11 and r["spread"] is False
     assert r["names"] == ["all_gather", "all_reduce", "all_to_all", "exchange", "reduce_scatter"]
+
+
+def test_sequence_parallel_conv_band_scan_and_parallel_reductions():
+    import json
+    import os
+    import subprocess
+    import sys
+    worker = os.path.join(os.path.dirname(__file__), "workers", "sp_ops_worker.py")
+    for world, port in ((2, 29681), (3, 29682)):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+               "--master-port", str(port), worker]
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="1"))
+        assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-3000:]
+        r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+        assert all(v < 1e-4 for v in r.values()), r
+        assert {"conv_out", "band_out", "scan_out", "scan_state", "vce_loss", "norm"} <= set(r)
