@@ -102,6 +102,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// The same wait taken by every lane of a converged warp; true only if it succeeded for all of them.  A warp that issues
+// tensor-core products waits like this and issues under `elect_one()`, so that its control flow and the operand
+// descriptors stay warp-uniform: computed by a single lane inside a divergent branch, every product paid for moving
+// its descriptors to the uniform registers and the issuing thread, not the tensor pipe, set the kernel's pace.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag = nullptr) {
+  const bool got = mbar_wait(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, got);
+}
+
 // ----------------------------------------------------------------------------------------------------------
 // TMA: tiled loads into this CTA's shared memory (no multicast), completion on an mbarrier
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* desc) {

@@ -2,13 +2,15 @@
 //
 //   delta   : delta[b,h,s] = sum_d dO * O                                   (row kernel)
 //   dQ      : one CTA per 128 query rows; loops over key tiles:
-//                S = Q K^T, dP = dO V^T (tcgen05, TMEM) -> dS = P o (dP - delta) (bf16, shared) -> dQ += dS K
+//                S = Q K^T, dP = dO V^T (tcgen05, TMEM) -> dS = P o (dP - delta) (bf16, written over S in TMEM) -> dQ += dS K
 //   dK / dV : one CTA per 128 keys of one KV head; loops over the query heads of its group and 64-row query blocks:
-//                S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T (bf16, shared) -> dV += P^T dO, dK += dS^T Q
+//                S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T (bf16, written over S^T / dP^T in TMEM) -> dV += P^T dO, dK += dS^T Q
 // Both MMA kernels recompute the probabilities from the saved log-sum-exp, keep their output accumulators in tensor
 // memory for the whole loop and never use atomics, so results are deterministic. A Q / dO / K / V tile sits in shared
 // memory once and serves two products through two descriptors (K-major for the score products, MN-major for the
-// gradient products). The exponentials, not the tensor core, bound both MMA kernels, so each runs eight softmax warps:
+// gradient products). The gradient products read their A operand (P^T, dS^T, dS) from tensor memory, where the softmax
+// threads leave it with tcgen05.st: with both operands in shared memory the operand fetch (about 95 bytes per cycle
+// measured against 128 needed), not the tensor pipe, set the pace. The exponentials, not the tensor core, bound both MMA kernels, so each runs eight softmax warps:
 // two threads per TMEM lane, each taking half of the tile's columns (no reduction crosses the two: the row statistics
 // come from the forward pass and the delta kernel).
 //
@@ -16,6 +18,7 @@
 // attention_mosaic_dq.py), which it records as 6-9x slower than cuDNN on B200 (src/dew/nn/attention_kernels.py:772-796).
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
+#include <type_traits>
 
 namespace dewb {
 namespace flashbwd {
@@ -58,28 +61,32 @@ __global__ void delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bf
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// dQ kernel: one CTA per 128 query rows of one head; Q and dO stay in shared memory, key blocks of 64 stream through a
-// 4-stage K / V ring.
+// dQ kernel: one CTA per 128 query rows of one head; key blocks of 64 stream through a 5-stage K / V ring. Q and dO are
+// the A operands of every score product of the CTA: the softmax threads copy them once from shared to tensor memory, so
+// the score products fetch only the 64-key K / V block from shared memory (with Q / dO read from shared memory for every
+// block, the operand fetch and not the tensor pipe set the pace).
 //   warps 0..3  softmax group 0 : key blocks 0, 2, 4, ...   one thread per query row (its lse and delta in registers)
 //   warps 4..7  softmax group 1 : key blocks 1, 3, 5, ...
-//               each group owns a pair of TMEM score buffers (S, dP) and a shared-memory dS buffer; dQ is one accumulator
+//               each group owns a pair of TMEM score buffers (S, dP) and writes dS (bf16) over the first 32 columns of
+//               its S buffer; dQ is one accumulator
 //   warp 8      TMA producer;  warp 9  MMA issuer (scores two blocks ahead, dQ += dS K as each group delivers dS)
 template <int D>
 struct DqCfg {
-  static constexpr int BM = 128, BN = 64, KSTAGES = 4;
+  static constexpr int BM = 128, BN = 64, KSTAGES = 5;
   static constexpr int SUB = D / 64;
   static constexpr int Q_TILE = BM * D * 2;          // [128 x D]
   static constexpr int KV_TILE = BN * D * 2;         // [64 x D]
-  static constexpr int DS_BYTES = BM * BN * 2;       // [128 x 64]
-  static constexpr int SMEM = 2 * Q_TILE + KSTAGES * 2 * KV_TILE + 2 * DS_BYTES + 1024 + 256;
+  static constexpr int SMEM = 2 * Q_TILE + KSTAGES * 2 * KV_TILE + 1024 + 256;
   static constexpr int TM_S0 = 0, TM_DP0 = 64, TM_S1 = 128, TM_DP1 = 192, TM_DQ = 256, TM_COLS = 512;
+  static constexpr int TM_QA = 384, TM_DOA = 448;    // Q and dO as tensor-memory A operands (D / 2 packed columns each)
 };
 
 struct DqBars {
   uint64_t q_full;
-  uint64_t kv_full[4], kv_empty[4];
-  uint64_t sdp_full[2], sdp_empty[2];   // per softmax group
-  uint64_t ds_full[2], dq_done[2];      // per softmax group
+  uint64_t kv_full[5], kv_empty[5];
+  uint64_t sdp_full[2];                 // per softmax group
+  uint64_t ds_full[2];                  // per softmax group
+  uint64_t a_ready;                     // Q and dO copied to tensor memory (one arrival per softmax warp)
   uint64_t all_done;
   uint32_t tmem_base;
   int abort_flag;
@@ -108,8 +115,7 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   uint8_t* sdO = sQ + C::Q_TILE;
   uint8_t* sK = sdO + C::Q_TILE;             // KS stages
   uint8_t* sV = sK + KS * C::KV_TILE;        // KS stages
-  uint8_t* sdS = sV + KS * C::KV_TILE;       // one per group
-  DqBars* bars = reinterpret_cast<DqBars*>(sdS + 2 * C::DS_BYTES);
+  DqBars* bars = reinterpret_cast<DqBars*>(sV + KS * C::KV_TILE);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = CAUSAL ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
@@ -123,10 +129,11 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     mbar_init(&bars->q_full, 1);
     for (int i = 0; i < KS; ++i) { mbar_init(&bars->kv_full[i], 1); mbar_init(&bars->kv_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->sdp_full[i], 1); mbar_init(&bars->sdp_empty[i], 4);
-      mbar_init(&bars->ds_full[i], 4); mbar_init(&bars->dq_done[i], 1);
+      mbar_init(&bars->sdp_full[i], 1);
+      mbar_init(&bars->ds_full[i], 4);
     }
     mbar_init(&bars->all_done, 1);
+    mbar_init(&bars->a_ready, 8);
     bars->abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -159,53 +166,66 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     }
   } else if (warp == MMA_WARP) {
     // Key block `it` belongs to group g = it & 1 (its number within the group is it >> 1) and to ring stage it % KS.
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc(BM, BN, 1, 1, 0, 0);
-      constexpr uint32_t idesc_dq = make_idesc(BM, D, 1, 1, 0, 1);
-      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
-      if (!ok) atomicCAS(err, 0, ERR_WAIT_FULL);
-      auto issue_scores = [&](int it) -> bool {
-        const int g = it & 1; const uint32_t phg = (it >> 1) & 1;
-        const int ks = it % KS; const uint32_t phk = (it / KS) & 1;
-        if (!mbar_wait(&bars->kv_full[ks], phk, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
-        if (!mbar_wait(&bars->sdp_empty[g], phg ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
-        tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), da = smem_u32(sdO), ka = smem_u32(sK + ks * C::KV_TILE), va = smem_u32(sV + ks * C::KV_TILE);
+    // The whole warp runs this loop and waits together; one elected lane issues (see mbar_wait_warp).
+    constexpr uint32_t idesc_s = make_idesc(BM, BN, 1, 1, 0, 0);
+    constexpr uint32_t idesc_dq = make_idesc(BM, D, 1, 1, 0, 1);
+    bool ok = mbar_wait_warp(&bars->a_ready, 0, abort_flag);
+    if (!ok && lane == 0) atomicCAS(err, 0, ERR_WAIT_FULL);
+    tc_fence_after();
+    // The score products of block `it` (one lane, inside an elected region).  The group's score buffers hold dS of its
+    // previous block until that block's dQ product has read it; that product was issued by the same lane before these
+    // and the tensor pipe runs one thread's products in order.
+    auto score_products = [&](int it) {
+      const int g = it & 1;
+      const int ks = it % KS;
+      const uint32_t ka = smem_u32(sK + ks * C::KV_TILE), va = smem_u32(sV + ks * C::KV_TILE);
+      const uint32_t ts = tmem + (g ? C::TM_S1 : C::TM_S0), tdp = tmem + (g ? C::TM_DP1 : C::TM_DP0);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-          const uint32_t boff = (kk >> 2) * (BN * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tmem + (g ? C::TM_S1 : C::TM_S0), make_sdesc_sw128(qa + aoff, 16, 1024),
-                       make_sdesc_sw128(ka + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
+      for (int kk = 0; kk < D / 16; ++kk) {           // 16 features of Q / dO = 8 packed 32-bit columns
+        const uint32_t boff = (kk >> 2) * (BN * 128) + (kk & 3) * 32;
+        umma_bf16_ts(ts, tmem + C::TM_QA + kk * 8, make_sdesc_sw128(ka + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+      }
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-          const uint32_t boff = (kk >> 2) * (BN * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tmem + (g ? C::TM_DP1 : C::TM_DP0), make_sdesc_sw128(da + aoff, 16, 1024),
-                       make_sdesc_sw128(va + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&bars->sdp_full[g]);
-        return true;
-      };
-      if (ok && iters > 0) ok = issue_scores(0);
-      if (ok && iters > 1) ok = issue_scores(1);
-      for (int it = 0; it < iters && ok; ++it) {
-        const int g = it & 1; const uint32_t phg = (it >> 1) & 1;
-        const int ks = it % KS;
-        if (!mbar_wait(&bars->ds_full[g], phg, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
-        tc_fence_after();
-        const uint32_t sa = smem_u32(sdS + g * C::DS_BYTES), ka = smem_u32(sK + ks * C::KV_TILE);
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t boff = (kk >> 2) * (BN * 128) + (kk & 3) * 32;
+        umma_bf16_ts(tdp, tmem + C::TM_DOA + kk * 8, make_sdesc_sw128(va + boff, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+      }
+      umma_commit(&bars->sdp_full[g]);
+    };
+    auto issue_scores = [&](int it) -> bool {
+      if (!mbar_wait_warp(&bars->kv_full[it % KS], (it / KS) & 1, abort_flag)) { if (lane == 0) atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
+      tc_fence_after();
+      if (elect_one()) score_products(it);
+      __syncwarp();
+      return true;
+    };
+    if (ok && iters > 0) ok = issue_scores(0);
+    if (ok && iters > 1) ok = issue_scores(1);
+    for (int it = 0; it < iters && ok; ++it) {
+      const int g = it & 1; const uint32_t phg = (it >> 1) & 1;
+      const int ks = it % KS;
+      {
+        // two lanes wait at the same time: for this block's dS and for the K / V block the next score products read
+        bool got = true;
+        if (lane == 0) got = mbar_wait(&bars->ds_full[g], phg, abort_flag);
+        else if (lane == 1 && it + 2 < iters) got = mbar_wait(&bars->kv_full[(it + 2) % KS], ((it + 2) / KS) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) { if (lane == 0) atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+      }
+      tc_fence_after();
+      const uint32_t ka = smem_u32(sK + ks * C::KV_TILE);
+      const uint32_t tds = tmem + (g ? C::TM_S1 : C::TM_S0);      // 16 keys of dS = 8 packed 32-bit columns
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          umma_bf16_ss(tmem + C::TM_DQ, make_sdesc_sw128(sa + kk * 32, 16, 1024),
-                       make_sdesc_sw128(ka + kk * 2048, BN * 128, 1024), idesc_dq, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_bf16_ts(tmem + C::TM_DQ, tds + kk * 8, make_sdesc_sw128(ka + kk * 2048, BN * 128, 1024), idesc_dq,
+                       (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&bars->kv_empty[ks]);
-        umma_commit(&bars->dq_done[g]);
-        if (it + 2 < iters) ok = issue_scores(it + 2);
+        if (it + 2 < iters) score_products(it + 2);
       }
-      if (ok) umma_commit(&bars->all_done);
+      __syncwarp();
     }
+    if (ok && elect_one()) umma_commit(&bars->all_done);
+    __syncwarp();
   } else {
     const int q4 = warp & 3, g = warp >> 2;
     const int r = q4 * 32 + lane;                   // query row within the tile == TMEM lane
@@ -215,9 +235,34 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const float lse2 = row < S ? lse[stat] * LOG2E : 0.f;
     const float dl = row < S ? delta[stat] : 0.f;
     const int limit = CAUSAL ? (row + (T - S)) : (T - 1);
-    uint8_t* mydS = sdS + g * C::DS_BYTES;
     const uint32_t s_col = g ? C::TM_S1 : C::TM_S0, dp_col = g ? C::TM_DP1 : C::TM_DP0;
     bool ok = true;
+    {
+      // Group 0 copies its row of Q, group 1 its row of dO, from the swizzled shared tile to tensor memory: lane = row,
+      // 32-bit column w = features 2w, 2w + 1 (the layout of a tensor-memory A operand).
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->q_full, 0, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_FULL); ok = false; }
+      if (ok) {
+        const uint8_t* src = (g ? sdO : sQ) + r * 128;
+        const uint32_t dst = tmem + lane_addr + (g ? C::TM_DOA : C::TM_QA);
+#pragma unroll
+        for (int t = 0; t < C::SUB; ++t) {
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t w[16];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const uint4 x = *reinterpret_cast<const uint4*>(src + t * (BM * 128) + (((hf * 4 + c) ^ (r & 7)) << 4));
+              w[c * 4] = x.x; w[c * 4 + 1] = x.y; w[c * 4 + 2] = x.z; w[c * 4 + 3] = x.w;
+            }
+            tmem_st_32x32b_x16(dst + t * 32 + hf * 16, w);
+          }
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (ok && lane == 0) mbar_arrive(&bars->a_ready);
+    }
     int mine = 0;
     for (int it = g; it < iters && ok; it += 2, ++mine) {
       const uint32_t phg = mine & 1;
@@ -225,35 +270,40 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tc_fence_after();
       const int k0 = it * BN;
       uint32_t packed[BN / 2];
+      auto block = [&](auto masked_tag) {
+        constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem + lane_addr + s_col + c * 32, sv);
-        tmem_ld_32x32b_x32(tmem + lane_addr + dp_col + c * 32, dv);
-        tmem_ld_wait();
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t sv[32], dv[32];
+          tmem_ld_32x32b_x32(tmem + lane_addr + s_col + c * 32, sv);
+          tmem_ld_32x32b_x32(tmem + lane_addr + dp_col + c * 32, dv);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int key = k0 + c * 32 + i;
-          float p0 = fast_exp2(__uint_as_float(sv[i]) * scale_log2 - lse2);
-          float p1 = fast_exp2(__uint_as_float(sv[i + 1]) * scale_log2 - lse2);
-          if (key > limit || key >= T) p0 = 0.f;
-          if (key + 1 > limit || key + 1 >= T) p1 = 0.f;
-          packed[(c * 32 + i) >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));
+          for (int i = 0; i < 32; i += 2) {
+            const int key = k0 + c * 32 + i;
+            float p0 = fast_exp2(__uint_as_float(sv[i]) * scale_log2 - lse2);
+            float p1 = fast_exp2(__uint_as_float(sv[i + 1]) * scale_log2 - lse2);
+            if (MASKED) {
+              if (key > limit || key >= T) p0 = 0.f;
+              if (key + 1 > limit || key + 1 >= T) p1 = 0.f;
+            }
+            packed[(c * 32 + i) >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));
+          }
         }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->sdp_empty[g]);
-      // this group's previous dQ product must have read its dS buffer
-      if (mine > 0) {
-        if (!__all_sync(0xffffffffu, mbar_wait(&bars->dq_done[g], (mine - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
-      }
-      // each query row of dS is one 128-byte swizzled row of eight 16-byte chunks
+      };
+      // only blocks that reach past the first row's last visible key (or past T) need the comparisons: one branch per warp
+      const int warp_limit = CAUSAL ? (q0 + q4 * 32 + (T - S)) : (T - 1);
+      if (k0 + BN - 1 > warp_limit || k0 + BN > T) block(std::true_type{}); else block(std::false_type{});
+      // dS (bf16 pairs) over the first 32 columns of this group's S buffer: each thread overwrites only its own row,
+      // whose scores it holds in registers
+      {
+        uint32_t lo[16], hi[16];
 #pragma unroll
-      for (int c = 0; c < BN / 8; ++c)
-        *reinterpret_cast<uint4*>(mydS + r * 128 + ((c ^ (r & 7)) << 4)) =
-            make_uint4(packed[c * 4], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
-      fence_proxy_async();
+        for (int i = 0; i < 16; ++i) { lo[i] = packed[i]; hi[i] = packed[16 + i]; }
+        tmem_st_32x32b_x16(tmem + lane_addr + s_col, lo);
+        tmem_st_32x32b_x16(tmem + lane_addr + s_col + 16, hi);
+        tmem_st_wait();
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->ds_full[g]);
@@ -297,29 +347,28 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 // dK / dV kernel
 //   warps 0..3  softmax group 0 : iterations 0, 2, 4, ...   one thread per key row, all 64 query columns
 //   warps 4..7  softmax group 1 : iterations 1, 3, 5, ...
-//               Each group owns a pair of TMEM score buffers (S^T, dP^T) and a pair of shared-memory operand buffers
-//               (P^T, dS^T); the gradient accumulators dV and dK are shared (the MMA thread issues every product,
+//               Each group owns a pair of TMEM score buffers (S^T, dP^T) and writes P^T and dS^T (bf16) over their first
+//               32 columns; the gradient accumulators dV and dK are shared (the MMA thread issues every product,
 //               and accumulation commutes). While one group computes its exponentials the other loads scores or
 //               stores operands. No reduction crosses threads: the row statistics come with the Q / dO tiles.
-//   warp 8      TMA producer : K, V once; then Q, dO tiles and the block's 64 + 64 statistics into a 3-stage ring
+//   warp 8      TMA producer : K, V once; then Q, dO tiles and the block's 64 + 64 statistics into a 4-stage ring
 //   warp 9      MMA issuer   : scores two iterations ahead, gradient products as each group delivers its operands
 template <int D>
 struct DkvCfg {
-  static constexpr int BKV = 128, BQ = 64, QSTAGES = 3;
+  static constexpr int BKV = 128, BQ = 64, QSTAGES = 4;
   static constexpr int SUB = D / 64;
   static constexpr int KV_TILE = BKV * D * 2;        // [128 x D]
   static constexpr int Q_TILE = BQ * D * 2;          // [64 x D]
-  static constexpr int P_BYTES = BKV * BQ * 2;       // [128 x 64]
   static constexpr int STAT_BYTES = 2 * BQ * 4;      // per stage: 64 log-sum-exps, 64 deltas
-  static constexpr int SMEM = 2 * KV_TILE + QSTAGES * 2 * Q_TILE + 4 * P_BYTES + QSTAGES * STAT_BYTES + 1024 + 256;
+  static constexpr int SMEM = 2 * KV_TILE + QSTAGES * 2 * Q_TILE + QSTAGES * STAT_BYTES + 1024 + 256;
   static constexpr int TM_ST0 = 0, TM_DPT0 = 64, TM_ST1 = 128, TM_DPT1 = 192, TM_DV = 256, TM_DK = 256 + D, TM_COLS = 512;
 };
 
 struct DkvBars {
   uint64_t kv_full;
-  uint64_t q_full[3], q_empty[3];
-  uint64_t st_full[2], st_empty[2];     // per softmax group
-  uint64_t pds_full[2], acc_done[2];    // per softmax group
+  uint64_t q_full[5], q_empty[5];
+  uint64_t st_full[2];                  // per softmax group
+  uint64_t pds_full[2];                 // per softmax group
   uint64_t all_done;
   uint32_t tmem_base;
   int abort_flag;
@@ -348,9 +397,7 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   uint8_t* sV = sK + C::KV_TILE;
   uint8_t* sQ = sV + C::KV_TILE;             // QS stages
   uint8_t* sdO = sQ + QS * C::Q_TILE;        // QS stages
-  uint8_t* sP = sdO + QS * C::Q_TILE;        // one per group
-  uint8_t* sdS = sP + 2 * C::P_BYTES;        // one per group
-  float* sStat = reinterpret_cast<float*>(sdS + 2 * C::P_BYTES);   // [QS stages][lse2 64 | delta 64]
+  float* sStat = reinterpret_cast<float*>(sdO + QS * C::Q_TILE);   // [QS stages][lse2 64 | delta 64]
   DkvBars* bars = reinterpret_cast<DkvBars*>(reinterpret_cast<uint8_t*>(sStat) + QS * C::STAT_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -371,8 +418,8 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     mbar_init(&bars->kv_full, 1);
     for (int i = 0; i < QS; ++i) { mbar_init(&bars->q_full[i], 1); mbar_init(&bars->q_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->st_full[i], 1); mbar_init(&bars->st_empty[i], 4);
-      mbar_init(&bars->pds_full[i], 4); mbar_init(&bars->acc_done[i], 1);
+      mbar_init(&bars->st_full[i], 1);
+      mbar_init(&bars->pds_full[i], 4);
     }
     mbar_init(&bars->all_done, 1);
     bars->abort_flag = 0;
@@ -413,65 +460,79 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     }
   } else if (warp == MMA_WARP) {
     // Iteration `it` belongs to group g = it & 1 (its number within the group is it >> 1) and to Q stage it % QS.
-    if (lane == 0) {
-      constexpr uint32_t idesc_st = make_idesc(BKV, BQ, 1, 1, 0, 0);
-      constexpr uint32_t idesc_acc = make_idesc(BKV, D, 1, 1, 0, 1);
-      bool ok = mbar_wait(&bars->kv_full, 0, abort_flag);
-      if (!ok) atomicCAS(err, 0, ERR_WAIT_FULL);
-      auto issue_scores = [&](int it) -> bool {
-        const int g = it & 1; const uint32_t phg = (it >> 1) & 1;
-        const int qs = it % QS; const uint32_t phq = (it / QS) & 1;
-        if (!mbar_wait(&bars->q_full[qs], phq, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
-        if (!mbar_wait(&bars->st_empty[g], phg ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
-        tc_fence_after();
-        const uint32_t ka = smem_u32(sK), va = smem_u32(sV), qa = smem_u32(sQ + qs * C::Q_TILE), da = smem_u32(sdO + qs * C::Q_TILE);
+    // The whole warp runs this loop and waits together; one elected lane issues (see mbar_wait_warp).
+    constexpr uint32_t idesc_st = make_idesc(BKV, BQ, 1, 1, 0, 0);
+    constexpr uint32_t idesc_acc = make_idesc(BKV, D, 1, 1, 0, 1);
+    bool ok = mbar_wait_warp(&bars->kv_full, 0, abort_flag);
+    if (!ok && lane == 0) atomicCAS(err, 0, ERR_WAIT_FULL);
+    const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
+    // The score products of iteration `it` (one lane, inside an elected region).  The group's score buffers hold P^T /
+    // dS^T of its previous iteration until that iteration's gradient products have read them; those were issued by the
+    // same lane before these and the tensor pipe runs one thread's products in order.
+    auto score_products = [&](int it) {
+      const int g = it & 1;
+      const int qs = it % QS;
+      const uint32_t qa = smem_u32(sQ + qs * C::Q_TILE), da = smem_u32(sdO + qs * C::Q_TILE);
+      const uint32_t tst = tmem + (g ? C::TM_ST1 : C::TM_ST0), tdp = tmem + (g ? C::TM_DPT1 : C::TM_DPT0);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t aoff = (kk >> 2) * (BKV * 128) + (kk & 3) * 32;
-          const uint32_t boff = (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tmem + (g ? C::TM_ST1 : C::TM_ST0), make_sdesc_sw128(ka + aoff, 16, 1024),
-                       make_sdesc_sw128(qa + boff, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t aoff = (kk >> 2) * (BKV * 128) + (kk & 3) * 32;
-          const uint32_t boff = (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tmem + (g ? C::TM_DPT1 : C::TM_DPT0), make_sdesc_sw128(va + aoff, 16, 1024),
-                       make_sdesc_sw128(da + boff, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&bars->st_full[g]);
-        return true;
-      };
-      if (ok && iters > 0) ok = issue_scores(0);
-      if (ok && iters > 1) ok = issue_scores(1);
-      for (int it = 0; it < iters && ok; ++it) {
-        const int g = it & 1; const uint32_t phg = (it >> 1) & 1;
-        const int qs = it % QS;
-        if (!mbar_wait(&bars->pds_full[g], phg, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
-        tc_fence_after();
-        const uint32_t pa = smem_u32(sP + g * C::P_BYTES), sa = smem_u32(sdS + g * C::P_BYTES);
-        const uint32_t qa = smem_u32(sQ + qs * C::Q_TILE), da = smem_u32(sdO + qs * C::Q_TILE);
-#pragma unroll
-        for (int kk = 0; kk < BQ / 16; ++kk)
-          umma_bf16_ss(tmem + C::TM_DV, make_sdesc_sw128(pa + kk * 32, 16, 1024),
-                       make_sdesc_sw128(da + kk * 2048, BQ * 128, 1024), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < BQ / 16; ++kk)
-          umma_bf16_ss(tmem + C::TM_DK, make_sdesc_sw128(sa + kk * 32, 16, 1024),
-                       make_sdesc_sw128(qa + kk * 2048, BQ * 128, 1024), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&bars->q_empty[qs]);
-        umma_commit(&bars->acc_done[g]);
-        if (it + 2 < iters) ok = issue_scores(it + 2);
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t aoff = (kk >> 2) * (BKV * 128) + (kk & 3) * 32;
+        const uint32_t boff = (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
+        umma_bf16_ss(tst, make_sdesc_sw128(ka + aoff, 16, 1024), make_sdesc_sw128(qa + boff, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
       }
-      if (ok) umma_commit(&bars->all_done);        // every product issued above has completed when this fires
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t aoff = (kk >> 2) * (BKV * 128) + (kk & 3) * 32;
+        const uint32_t boff = (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
+        umma_bf16_ss(tdp, make_sdesc_sw128(va + aoff, 16, 1024), make_sdesc_sw128(da + boff, 16, 1024), idesc_st, kk > 0 ? 1u : 0u);
+      }
+      umma_commit(&bars->st_full[g]);
+    };
+    auto issue_scores = [&](int it) -> bool {
+      if (!mbar_wait_warp(&bars->q_full[it % QS], (it / QS) & 1, abort_flag)) { if (lane == 0) atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
+      tc_fence_after();
+      if (elect_one()) score_products(it);
+      __syncwarp();
+      return true;
+    };
+    if (ok && iters > 0) ok = issue_scores(0);
+    if (ok && iters > 1) ok = issue_scores(1);
+    for (int it = 0; it < iters && ok; ++it) {
+      const int g = it & 1; const uint32_t phg = (it >> 1) & 1;
+      const int qs = it % QS;
+      {
+        // two lanes wait at the same time: for this iteration's P^T / dS^T and for the Q / dO block the next score
+        // products read
+        bool got = true;
+        if (lane == 0) got = mbar_wait(&bars->pds_full[g], phg, abort_flag);
+        else if (lane == 1 && it + 2 < iters) got = mbar_wait(&bars->q_full[(it + 2) % QS], ((it + 2) / QS) & 1, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) { if (lane == 0) atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+      }
+      tc_fence_after();
+      const uint32_t qa = smem_u32(sQ + qs * C::Q_TILE), da = smem_u32(sdO + qs * C::Q_TILE);
+      const uint32_t tp = tmem + (g ? C::TM_ST1 : C::TM_ST0), tds = tmem + (g ? C::TM_DPT1 : C::TM_DPT0);
+      if (elect_one()) {
+        // 16 queries of P^T / dS^T = 8 packed 32-bit columns
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk)
+          umma_bf16_ts(tmem + C::TM_DV, tp + kk * 8, make_sdesc_sw128(da + kk * 2048, BQ * 128, 1024), idesc_acc,
+                       (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < BQ / 16; ++kk)
+          umma_bf16_ts(tmem + C::TM_DK, tds + kk * 8, make_sdesc_sw128(qa + kk * 2048, BQ * 128, 1024), idesc_acc,
+                       (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&bars->q_empty[qs]);
+        if (it + 2 < iters) score_products(it + 2);
+      }
+      __syncwarp();
     }
+    if (ok && elect_one()) umma_commit(&bars->all_done);        // every product issued above has completed when this fires
+    __syncwarp();
   } else {
     const int q4 = warp & 3, g = warp >> 2;
     const int r = q4 * 32 + lane;                   // key row within the tile == TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
     const int key = kv0 + r;
-    uint8_t* myP = sP + g * C::P_BYTES;
-    uint8_t* mydS = sdS + g * C::P_BYTES;
     const uint32_t st_col = g ? C::TM_ST1 : C::TM_ST0, dp_col = g ? C::TM_DPT1 : C::TM_DPT0;
     bool ok = true;
     int mine = 0;
@@ -486,49 +547,57 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       if (!__all_sync(0xffffffffu, mbar_wait(&bars->st_full[g], phg, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
       tc_fence_after();
       uint32_t pp[BQ / 2], ds[BQ / 2];
+      auto block = [&](auto masked_tag) {
+        constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
-      for (int c = 0; c < BQ / 32; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem + lane_addr + st_col + c * 32, sv);
-        tmem_ld_32x32b_x32(tmem + lane_addr + dp_col + c * 32, dv);
-        tmem_ld_wait();
-        const int qbase = qb + c * 32 + (T - S);
+        for (int c = 0; c < BQ / 32; ++c) {
+          uint32_t sv[32], dv[32];
+          tmem_ld_32x32b_x32(tmem + lane_addr + st_col + c * 32, sv);
+          tmem_ld_32x32b_x32(tmem + lane_addr + dp_col + c * 32, dv);
+          tmem_ld_wait();
+          const int qbase = qb + c * 32 + (T - S);
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float4 l4 = lse4[(c * 32 + i) >> 2], d4 = dlt4[(c * 32 + i) >> 2];
-          float p0 = fast_exp2(__uint_as_float(sv[i]) * scale_log2 - l4.x);
-          float p1 = fast_exp2(__uint_as_float(sv[i + 1]) * scale_log2 - l4.y);
-          float p2 = fast_exp2(__uint_as_float(sv[i + 2]) * scale_log2 - l4.z);
-          float p3 = fast_exp2(__uint_as_float(sv[i + 3]) * scale_log2 - l4.w);
-          if (CAUSAL) {
-            if (key > qbase + i) p0 = 0.f;
-            if (key > qbase + i + 1) p1 = 0.f;
-            if (key > qbase + i + 2) p2 = 0.f;
-            if (key > qbase + i + 3) p3 = 0.f;
+          for (int i = 0; i < 32; i += 4) {
+            const float4 l4 = lse4[(c * 32 + i) >> 2], d4 = dlt4[(c * 32 + i) >> 2];
+            float p0 = fast_exp2(__uint_as_float(sv[i]) * scale_log2 - l4.x);
+            float p1 = fast_exp2(__uint_as_float(sv[i + 1]) * scale_log2 - l4.y);
+            float p2 = fast_exp2(__uint_as_float(sv[i + 2]) * scale_log2 - l4.z);
+            float p3 = fast_exp2(__uint_as_float(sv[i + 3]) * scale_log2 - l4.w);
+            if (MASKED) {
+              if (CAUSAL) {
+                if (key > qbase + i) p0 = 0.f;
+                if (key > qbase + i + 1) p1 = 0.f;
+                if (key > qbase + i + 2) p2 = 0.f;
+                if (key > qbase + i + 3) p3 = 0.f;
+              }
+              if (key >= T) { p0 = 0.f; p1 = 0.f; p2 = 0.f; p3 = 0.f; }
+            }
+            const int o = (c * 32 + i) >> 1;
+            pp[o] = pack_bf16(p0, p1);
+            pp[o + 1] = pack_bf16(p2, p3);
+            ds[o] = pack_bf16(p0 * (__uint_as_float(dv[i]) - d4.x), p1 * (__uint_as_float(dv[i + 1]) - d4.y));
+            ds[o + 1] = pack_bf16(p2 * (__uint_as_float(dv[i + 2]) - d4.z), p3 * (__uint_as_float(dv[i + 3]) - d4.w));
           }
-          if (key >= T) { p0 = 0.f; p1 = 0.f; p2 = 0.f; p3 = 0.f; }
-          const int o = (c * 32 + i) >> 1;
-          pp[o] = pack_bf16(p0, p1);
-          pp[o + 1] = pack_bf16(p2, p3);
-          ds[o] = pack_bf16(p0 * (__uint_as_float(dv[i]) - d4.x), p1 * (__uint_as_float(dv[i + 1]) - d4.y));
-          ds[o + 1] = pack_bf16(p2 * (__uint_as_float(dv[i + 2]) - d4.z), p3 * (__uint_as_float(dv[i + 3]) - d4.w));
         }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->st_empty[g]);
-      // this group's previous gradient products must have read its operand buffers
-      if (mine > 0) {
-        if (!__all_sync(0xffffffffu, mbar_wait(&bars->acc_done[g], (mine - 1) & 1, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
-      }
-      // each key row of P^T / dS^T is one 128-byte swizzled row of eight 16-byte chunks
+      };
+      // only query blocks that start before this warp's last key (or key rows past T) need the comparisons: one branch
+      // per warp
+      const int warp_last_key = kv0 + q4 * 32 + 31;
+      if ((CAUSAL && warp_last_key > qb + (T - S)) || warp_last_key >= T) block(std::true_type{}); else block(std::false_type{});
+      // P^T and dS^T (bf16 pairs) over the first 32 columns of this group's S^T and dP^T buffers: each thread overwrites
+      // only its own row, whose scores it holds in registers
+      {
+        uint32_t t0[16], t1[16];
 #pragma unroll
-      for (int c = 0; c < BQ / 8; ++c) {
-        const int off = r * 128 + ((c ^ (r & 7)) << 4);
-        *reinterpret_cast<uint4*>(myP + off) = make_uint4(pp[c * 4], pp[c * 4 + 1], pp[c * 4 + 2], pp[c * 4 + 3]);
-        *reinterpret_cast<uint4*>(mydS + off) = make_uint4(ds[c * 4], ds[c * 4 + 1], ds[c * 4 + 2], ds[c * 4 + 3]);
+        for (int i = 0; i < 16; ++i) { t0[i] = pp[i]; t1[i] = pp[16 + i]; }
+        tmem_st_32x32b_x16(tmem + lane_addr + st_col, t0);
+        tmem_st_32x32b_x16(tmem + lane_addr + st_col + 16, t1);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { t0[i] = ds[i]; t1[i] = ds[16 + i]; }
+        tmem_st_32x32b_x16(tmem + lane_addr + dp_col, t0);
+        tmem_st_32x32b_x16(tmem + lane_addr + dp_col + 16, t1);
+        tmem_st_wait();
       }
-      fence_proxy_async();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->pds_full[g]);
@@ -584,6 +653,8 @@ static int make_map(CUtensorMap* m, const void* base, int B, int L, int H, int D
   const uint32_t box[4] = {64, 1, static_cast<uint32_t>(box_rows), 1};
   return make_tmap_nd(m, base, 4, dims, strides, box, 2, true);
 }
+
+static_assert(DqCfg<128>::SMEM + 64 <= 232448 && DkvCfg<128>::SMEM + 64 <= 232448, "over the 227 KB a CTA may use");
 
 template <int D, bool CAUSAL>
 static int launch_bwd(const void* dO, const void* q, const void* k, const void* v, const float* lse, const float* lse2, const float* delta,

@@ -56,7 +56,11 @@ struct Bars {
 
 static_assert(sizeof(Bars) <= 2560, "Bars must fit the space Cfg::SMEM leaves after the tiles");
 
-template <int D, bool CAUSAL>
+// PT = true keeps P in tensor memory: each softmax thread overwrites its part of the score buffer with the packed bf16
+// probabilities (tcgen05.st) and the P V product reads its A operand from there, so P never crosses shared memory (no
+// 32 KB store + 32 KB operand fetch per tile) and the softmax of the next tile need not wait for the product to drain
+// a shared buffer.  PT = false is the shared-memory form (P in the 128-byte-swizzled K-major layout).
+template <int D, bool CAUSAL, bool PT>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                  const __grid_constant__ CUtensorMap tv, __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
@@ -135,45 +139,60 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     }
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = make_idesc(BM, BN, 1, 1, 0, 0);
-      constexpr uint32_t idesc_pv = make_idesc(BM, D, 1, 1, 0, 1);
-      bool ok = mbar_wait(&bars->q_full, 0, abort_flag);
-      if (!ok) atomicCAS(err, 0, ERR_WAIT_FULL);
-      auto issue_qk = [&](int j) -> bool {
-        const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
-        const int ks = j % C::KSTAGES; const uint32_t kph = (j / C::KSTAGES) & 1;
-        if (!mbar_wait(&bars->k_full[ks], kph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
-        if (!mbar_wait(&bars->s_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
-        tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + ks * C::KV_BYTES);
+    // The whole warp runs this loop and waits together; one elected lane issues (see mbar_wait_warp).
+    constexpr uint32_t idesc_qk = make_idesc(BM, BN, 1, 1, 0, 0);
+    constexpr uint32_t idesc_pv = make_idesc(BM, D, 1, 1, 0, 1);
+    bool ok = mbar_wait_warp(&bars->q_full, 0, abort_flag);
+    if (!ok && lane == 0) atomicCAS(err, 0, ERR_WAIT_FULL);
+    const uint32_t qa = smem_u32(sQ), pa = smem_u32(sP);
+    auto issue_qk = [&](int j) -> bool {
+      const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
+      const int ks = j % C::KSTAGES; const uint32_t kph = (j / C::KSTAGES) & 1;
+      if (!mbar_wait_warp(&bars->k_full[ks], kph, abort_flag)) { if (lane == 0) atomicCAS(err, 0, ERR_WAIT_FULL); return false; }
+      // PT: the score buffer holds P(j - 2) until P V(j - 2) has read it; that product was issued by the same lane before
+      // this one and the tensor pipe runs one thread's products in order, so no barrier is needed.
+      if (!PT && !mbar_wait_warp(&bars->s_empty[st], ph ^ 1, abort_flag)) { if (lane == 0) atomicCAS(err, 0, ERR_WAIT_TMEM_EMPTY); return false; }
+      tc_fence_after();
+      const uint32_t ka = smem_u32(sK + ks * C::KV_BYTES);
+      const uint32_t ts = tmem + (st ? C::TMEM_S1 : C::TMEM_S0);
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tmem + (st ? C::TMEM_S1 : C::TMEM_S0), make_sdesc_sw128(qa + off, 16, 1024),
-                       make_sdesc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+          umma_bf16_ss(ts, make_sdesc_sw128(qa + off, 16, 1024), make_sdesc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
         }
         umma_commit(&bars->k_empty[ks]);
         umma_commit(&bars->s_full[st]);
-        return true;
-      };
-      if (ok && n_tiles > 0) ok = issue_qk(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) { ok = issue_qk(j + 1); if (!ok) break; }
-        const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&bars->p_full, j & 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
-        if (!mbar_wait(&bars->v_full[st], ph, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_FULL); ok = false; break; }
-        tc_fence_after();
-        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + st * C::KV_BYTES);
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok && n_tiles > 0) ok = issue_qk(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (j + 1 < n_tiles) { ok = issue_qk(j + 1); if (!ok) break; }
+      const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait_warp(&bars->p_full, j & 1, abort_flag)) { if (lane == 0) atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; break; }
+      if (!mbar_wait_warp(&bars->v_full[st], ph, abort_flag)) { if (lane == 0) atomicCAS(err, 0, ERR_WAIT_FULL); ok = false; break; }
+      tc_fence_after();
+      const uint32_t va = smem_u32(sV + st * C::KV_BYTES);
+      const uint32_t tp = tmem + (st ? C::TMEM_S1 : C::TMEM_S0);
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint32_t aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-          umma_bf16_ss(tmem + C::TMEM_O, make_sdesc_sw128(pa + aoff, 16, 1024),
-                       make_sdesc_sw128(va + kk * 2048, BN * 128, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          if (PT) {
+            // 16 keys of P = 8 packed 32-bit columns of the score buffer this tile used
+            umma_bf16_ts(tmem + C::TMEM_O, tp + kk * 8, make_sdesc_sw128(va + kk * 2048, BN * 128, 1024), idesc_pv,
+                         (j > 0 || kk > 0) ? 1u : 0u);
+          } else {
+            const uint32_t aoff = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
+            umma_bf16_ss(tmem + C::TMEM_O, make_sdesc_sw128(pa + aoff, 16, 1024),
+                         make_sdesc_sw128(va + kk * 2048, BN * 128, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          }
         }
         umma_commit(&bars->v_empty[st]);
         umma_commit(&bars->pv_done);
       }
+      __syncwarp();
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue (warps 0..7)
@@ -207,7 +226,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->s_empty[st]);   // the score buffer may be overwritten by tile j + 2
+        if (!PT && lane == 0) mbar_arrive(&bars->s_empty[st]);   // the score buffer may be overwritten by tile j + 2
         const int k0 = j * BN + half * HC;
         const int limit = CAUSAL ? (q0 + r + (T - S)) : (T - 1);   // last visible key index for this row
         if (k0 + HC - 1 > limit || k0 + HC > T) {
@@ -230,8 +249,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       const float m_new = fmaxf(m_used, mt);
       const bool need = (m_new - m_used > RESCALE_THRESHOLD) || (m_used == -INFINITY && m_new > -INFINITY);
       const bool any_need = __any_sync(0xffffffffu, need);
-      // PV(j-1) must be complete before P is overwritten or O is rescaled
-      if (j > 0) {
+      // PV(j-1) must be complete before the shared P buffer is overwritten or O is rescaled (PT: only the latter)
+      if (j > 0 && (!PT || any_need)) {
         const bool got = mbar_wait(&bars->pv_done, (j - 1) & 1, abort_flag);
         if (!__all_sync(0xffffffffu, got)) { atomicCAS(err, 0, ERR_WAIT_OTHER); ok = false; continue; }
         tc_fence_after();
@@ -256,6 +275,23 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       // P = exp2(s - m_used) -> bf16, swizzled into shared memory as the A operand of the PV product
       const float mu = (m_used == -INFINITY) ? 0.f : m_used;
       float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;      // independent partial sums (fp32, before the bf16 rounding)
+      if (PT) {
+        // keys [half * 64, half * 64 + 64) of this row -> packed columns [half * 32, half * 32 + 32) of the score buffer.
+        // Both threads of the row hold their scores in registers since the barrier above, so the columns may be reused.
+        const uint32_t pbase = tmem + lane_addr + (st ? C::TMEM_S1 : C::TMEM_S0) + half * (HC / 2);
+#pragma unroll
+        for (int c = 0; c < HC / 32; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float a = fast_exp2(s[c * 32 + 2 * i] - mu), b2 = fast_exp2(s[c * 32 + 2 * i + 1] - mu);
+            pk[i] = pack_bf16(a, b2);
+            if (i & 1) { rs2 += a; rs3 += b2; } else { rs0 += a; rs1 += b2; }
+          }
+          tmem_st_32x32b_x16(pbase + c * 16, pk);
+        }
+        tmem_st_wait();
+      } else
 #pragma unroll
       for (int i8 = 0; i8 < HC / 8; ++i8) {
         float p[8];
@@ -268,7 +304,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         *reinterpret_cast<uint4*>(sP + half * (BM * 128) + r * 128 + ((i8 ^ (r & 7)) << 4)) = pk;
       }
       l += (rs0 + rs1) + (rs2 + rs3);
-      fence_proxy_async();
+      if (!PT) fence_proxy_async();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full);
@@ -321,11 +357,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   }
 }
 
-template <int D, bool CAUSAL>
+template <int D, bool CAUSAL, bool PT>
 static int launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* out, float* lse, int B,
                   int S, int T, int Hq, int Hkv, long long osb, long long oss, long long osh, float scale_log2, int* err,
                   cudaStream_t stream) {
-  auto kern = flash_fwd_kernel<D, CAUSAL>;
+  auto kern = flash_fwd_kernel<D, CAUSAL, PT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid((S + BM - 1) / BM, Hq, B);
@@ -344,8 +380,18 @@ static int make_qkv_map(CUtensorMap* m, const void* base, int B, int L, int H, i
   return make_tmap_nd(m, base, 4, dims, strides, box, 2, true);
 }
 
+static int g_variant = 1;     // 0: P through shared memory, 1: P in tensor memory (default)
+
 }  // namespace flash
 }  // namespace dewb
+
+// Selects the forward variant for later launches of this process (0: P through shared memory, 1: P in tensor memory);
+// returns the previous value.
+extern "C" int dewb_flash_set_variant(int variant) {
+  const int old = dewb::flash::g_variant;
+  dewb::flash::g_variant = variant;
+  return old;
+}
 
 // q [B,S,Hq,D], k/v [B,T,Hkv,D] (bf16, unit stride along D, other strides in elements: batch, sequence, head);
 // out [B,S,Hq,D] with its own strides; lse [B,Hq,S] fp32 (natural log), may be null.
@@ -367,9 +413,13 @@ extern "C" int dewb_flash_fwd(const void* q, const void* k, const void* v, void*
   if ((r = make_qkv_map(&tv, v, B, T, Hkv, D, v_sb, v_ss, v_sh))) return 3000 + r;
   const float scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
-  if (D == 128)
-    return causal ? launch<128, true>(tq, tk, tv, out, lse, B, S, T, Hq, Hkv, o_sb, o_ss, o_sh, scale_log2, err, stream)
-                  : launch<128, false>(tq, tk, tv, out, lse, B, S, T, Hq, Hkv, o_sb, o_ss, o_sh, scale_log2, err, stream);
-  return causal ? launch<64, true>(tq, tk, tv, out, lse, B, S, T, Hq, Hkv, o_sb, o_ss, o_sh, scale_log2, err, stream)
-                : launch<64, false>(tq, tk, tv, out, lse, B, S, T, Hq, Hkv, o_sb, o_ss, o_sh, scale_log2, err, stream);
+#define DEWB_FLASH_GO(DD, CC, PP) launch<DD, CC, PP>(tq, tk, tv, out, lse, B, S, T, Hq, Hkv, o_sb, o_ss, o_sh, scale_log2, err, stream)
+  const bool pt = g_variant != 0;
+  if (D == 128) {
+    if (causal) return pt ? DEWB_FLASH_GO(128, true, true) : DEWB_FLASH_GO(128, true, false);
+    return pt ? DEWB_FLASH_GO(128, false, true) : DEWB_FLASH_GO(128, false, false);
+  }
+  if (causal) return pt ? DEWB_FLASH_GO(64, true, true) : DEWB_FLASH_GO(64, true, false);
+  return pt ? DEWB_FLASH_GO(64, false, true) : DEWB_FLASH_GO(64, false, false);
+#undef DEWB_FLASH_GO
 }

@@ -135,6 +135,11 @@ def bench_attention(out, peaks, flush, iters=10, shapes=None, kernels=("sm100_fl
         v = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_()
         flops = 4.0 * B * Hq * S * S * D / 2
         row = dict(kernel="attention", B=B, S=S, Hq=Hq, Hkv=Hkv, D=D)
+        with torch.no_grad():       # numerics of this library's forward against the library arm, on every run
+            a = ops.attention(q, k, v, causal=True, kernel="sm100_flash").float()
+            b = ops.attention(q, k, v, causal=True, kernel="sdpa").float()
+            row["fwd_max_abs_diff_vs_sdpa"] = float((a - b).abs().max())
+            del a, b
         for name in kernels:
             try:
                 o = ops.attention(q, k, v, causal=True, kernel=name)
@@ -286,7 +291,10 @@ def main(argv=None):
     ap.add_argument("--gemm-shape", default=None, help="M,N,K[,a_mn,b_mn]: time one GEMM shape only (small profiling case)")
     ap.add_argument("--gdn-shape", default=None, help="B,T,H: time the gated-delta-rule kernels on one shape only (small profiling case)")
     ap.add_argument("--attn-shape", default=None, help="B,S,Hq,Hkv,D: time this library's attention kernels on one shape only")
+    ap.add_argument("--flash-variant", type=int, default=None, help="forward variant: 0 = P through shared memory, 1 = P in tensor memory")
     args = ap.parse_args(argv)
+    if args.flash_variant is not None:
+        L.load().dewb_flash_set_variant(int(args.flash_variant))
     peaks = measured_peaks()
     flush = L2Flush()
     out = open(args.out, "a") if args.out else None

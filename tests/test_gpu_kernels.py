@@ -220,8 +220,11 @@ def test_attention_matches_reference():
 
 @pytest.mark.parametrize("B,S,Hq,Hkv,D,causal", [(1, 128, 1, 1, 128, True), (2, 256, 8, 2, 128, True), (1, 512, 4, 4, 128, False),
                                                  (2, 384, 4, 2, 64, True), (1, 1024, 2, 1, 128, True)])
-def test_flash_forward_sm100(B, S, Hq, Hkv, D, causal):
+@pytest.mark.parametrize("variant", [1, 0])
+def test_flash_forward_sm100(B, S, Hq, Hkv, D, causal, variant, flash_variant):
+    """variant 1 keeps P in tensor memory (the default), 0 passes it through shared memory."""
     from dew_b200.ops.flash import flash_fwd
+    flash_variant(variant)
     torch.manual_seed(S + D)
     qkv = torch.randn(B, S, Hq + 2 * Hkv, D, device=DEV).to(torch.bfloat16)      # packed projection layout
     q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
@@ -235,9 +238,24 @@ def test_flash_forward_sm100(B, S, Hq, Hkv, D, causal):
     assert torch.allclose(lse, torch.logsumexp(s, -1), atol=2e-2, rtol=1e-3)
 
 
-def test_flash_forward_large_values_rescale():
+@pytest.fixture
+def flash_variant():
+    """Selects the forward variant for one test and restores the previous one afterwards."""
+    lib = L.load()
+    previous = []
+
+    def select(v):
+        previous.append(lib.dewb_flash_set_variant(int(v)))
+    yield select
+    if previous:
+        lib.dewb_flash_set_variant(previous[0])
+
+
+@pytest.mark.parametrize("variant", [1, 0])
+def test_flash_forward_large_values_rescale(variant, flash_variant):
     """Rows whose maximum grows tile after tile exercise the lazy rescale of the TMEM accumulator."""
     from dew_b200.ops.flash import flash_fwd
+    flash_variant(variant)
     torch.manual_seed(9)
     B, S, H, D = 1, 512, 2, 128
     q = torch.randn(B, S, H, D, device=DEV).to(torch.bfloat16)
