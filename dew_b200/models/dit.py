@@ -22,13 +22,13 @@ class SimpleDiT(nn.Module):
                  mlp_ratio: float = 4.0, input_channels: int = 3, output_channels: int = 3, adaln_silu: bool = True,
                  text_features: Optional[int] = None, num_classes: Optional[int] = None,
                  routes: Sequence[Sequence[float]] = (), patch_bottleneck: Optional[int] = None,
-                 interval: bool = False, time_scale: float = 16.0, dtype=None, device=None):
+                 interval: bool = False, time_scale: float = 16.0, guidance_embed: bool = False, dtype=None, device=None):
         super().__init__()
         self.patch_size, self.emb_features, self.num_layers, self.num_heads = patch_size, emb_features, num_layers, num_heads
         self.mlp_ratio, self.input_channels, self.output_channels = mlp_ratio, input_channels, output_channels
         self.routes = tuple(tuple(r) for r in routes)
         self.embed = PatchEmbedding(patch_size, input_channels, emb_features, patch_bottleneck, dtype=dtype, device=device)
-        self.conditioning = ConditioningEmbed(emb_features, text_features, num_classes, time_scale, interval, dtype=dtype, device=device)
+        self.conditioning = ConditioningEmbed(emb_features, text_features, num_classes, time_scale, interval, guidance_embed, dtype=dtype, device=device)
         self.blocks = nn.ModuleList([ModulatedBlock(emb_features, num_heads, mlp_ratio, adaln_silu, dtype=dtype, device=device)
                                      for _ in range(num_layers)])
         self.output = PatchSequenceOutput(emb_features, patch_size, output_channels, dtype=dtype, device=device)
@@ -40,7 +40,7 @@ class SimpleDiT(nn.Module):
         dt = self.embed.proj.weight.dtype
         tokens = self.embed(x.to(dt))
         tokens = tokens + sincos_2d(gh, gw, self.emb_features, tokens.device).to(dt)[None]
-        c = self.conditioning(temb, conditions.get("text"), conditions.get("label"), duration)
+        c = self.conditioning(temb, conditions.get("text"), conditions.get("label"), duration, conditions.get("guidance"))
         routed = None
         for i, block in enumerate(self.blocks):
             if train and self.routes:

@@ -54,9 +54,12 @@ class ConditioningEmbed(nn.Module):
     """Time (Fourier -> MLP) plus optional pooled text / class conditioning -> one vector per example."""
 
     def __init__(self, features: int, text_features: Optional[int] = None, num_classes: Optional[int] = None,
-                 time_scale: float = 16.0, interval: bool = False, dtype=None, device=None):
+                 time_scale: float = 16.0, interval: bool = False, guidance_embed: bool = False, dtype=None, device=None):
         super().__init__()
         self.features, self.time_scale, self.interval = features, time_scale, interval
+        # a guidance-distilled student reads its guidance scale beside the time (as FLUX.1 [dev] does)
+        self.g1 = Linear(features, features, bias=True, dtype=dtype, device=device) if guidance_embed else None
+        self.g2 = Linear(features, features, bias=True, zero_init=True, dtype=dtype, device=device) if guidance_embed else None
         self.t1 = Linear(features, features, bias=True, dtype=dtype, device=device)
         self.t2 = Linear(features, features, bias=True, dtype=dtype, device=device)
         self.d1 = Linear(features, features, bias=True, dtype=dtype, device=device) if interval else None
@@ -64,9 +67,11 @@ class ConditioningEmbed(nn.Module):
         self.classes = nn.Embedding(num_classes + 1, features, dtype=dtype, device=device) if num_classes else None
         self.num_classes = num_classes
 
-    def forward(self, t, context=None, labels=None, duration=None):
+    def forward(self, t, context=None, labels=None, duration=None, guidance=None):
         dt = self.t1.weight.dtype
         c = self.t2(F.silu(self.t1(sinusoidal(t, self.features, scale=self.time_scale).to(dt))))
+        if self.g1 is not None and guidance is not None:
+            c = c + self.g2(F.silu(self.g1(sinusoidal(guidance, self.features, scale=self.time_scale).to(dt))))
         if self.d1 is not None and duration is not None:
             c = c + self.d1(sinusoidal(duration, self.features, scale=self.time_scale).to(dt))
         if self.text is not None and context is not None:

@@ -14,6 +14,12 @@ def __getattr__(name):
     if name == "JepaObjective":
         from .jepa import JepaObjective
         return JepaObjective
+    if name in ("Alignment", "AlignedDiffusionObjective", "GuidanceDistillationObjective", "Projector", "spatial_zscore"):
+        from . import diffusion_extras
+        return getattr(diffusion_extras, name)
+    if name in ("ExpertBalance", "refuse_fixed_routers", "UntrainedRouter"):
+        from . import routing
+        return getattr(routing, name)
     if name == "Supervised":
         from .supervised import Supervised
         return Supervised
