@@ -109,6 +109,7 @@ class SparseMLP(nn.Module):
         self.shared = SwiGLU(features, mix.shared_features, init_std, dtype=dtype, device=device) if mix.shared_features else None
         self.shared_gate = Linear(features, 1, axes=("embed", None), dtype=dtype, device=device) if (mix.shared_gate and mix.shared_features) else None
         self.last: Dict[str, Any] = {}
+        self.keep_router_outputs = False   # set by objectives.routing.ExpertBalance: keep per-token scores / choices / log partitions
         self.ep = None            # set by dew_b200.parallel.ep.ExpertParallel when the experts are sharded over ranks
         self._exchange = None     # this layer's single-rank token exchange (created on first use on a GPU)
 
@@ -127,6 +128,9 @@ class SparseMLP(nn.Module):
         # balance statistics (Switch-style auxiliary loss value, also the signal for the bias update)
         frac = counts.float() / max(1, T * mix.top_k)
         self.last = {"counts": counts, "balance_loss": mix.experts * (frac * scores.mean(0)).sum()}
+        if self.keep_router_outputs:
+            self.last.update(scores=scores, ids=ids, shape=(int(math.prod(shape[:-2])) if len(shape) > 2 else 1, int(shape[-2])),
+                             log_z=torch.logsumexp(F.linear(x2.float(), self.router.weight.float()), -1))
         if self.ep is not None:
             y = self.ep.dispatch_compute_combine(self, x2, w, ids)
         elif x2.is_cuda and x2.dtype == torch.bfloat16 and mix.experts <= 256 and mix.top_k <= 16 and self.use_kernels:

@@ -40,6 +40,8 @@ class LMObjective(Objective):
         self.z_loss = z_loss
         self.token_accuracy = token_accuracy
         self.balance = balance
+        if balance is not None and not isinstance(balance, (int, float)):
+            balance.prepare(model)          # an ExpertBalance: the sparse layers keep what its terms read
         self.mtp_weight = mtp_weight
         self.prefix = prefix
         self.tokenizer = tokenizer
@@ -98,8 +100,15 @@ class LMObjective(Objective):
                 total = total + self.mtp_weight * (extra / len(depths)) * massf
         aux = Aux(metrics={"perplexity": Exponentiated(Ratio(total.detach(), massf)),
                            "tokens": Ratio(massf, torch.ones((), device=massf.device)), **mtp_metrics})
+        from .routing import ExpertBalance
+        if isinstance(self.balance, ExpertBalance):
+            # the run's router policy reads the sparse layers' records (and clears them, so pop_aux below adds nothing twice)
+            routed, raux = self.balance.compose(self.model, Ratio(total, massf), batch.get("segments"))
+            total = routed.total
+            aux.metrics.update(raux.metrics)
+            aux.effects.update(raux.effects)
         moe_aux = getattr(self.model, "pop_aux", None)
-        if moe_aux is not None:
+        if moe_aux is not None and not isinstance(self.balance, ExpertBalance):
             extra = moe_aux()
             aux.metrics.update(extra.get("metrics", {}))
             aux.effects.update(extra.get("effects", {}))
