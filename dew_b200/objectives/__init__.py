@@ -17,6 +17,9 @@ def __getattr__(name):
     if name in ("Alignment", "AlignedDiffusionObjective", "GuidanceDistillationObjective", "Projector", "spatial_zscore"):
         from . import diffusion_extras
         return getattr(diffusion_extras, name)
+    if name in ("AdversarialDistillationObjective",):
+        from . import adversarial
+        return getattr(adversarial, name)
     if name in ("ExpertBalance", "refuse_fixed_routers", "UntrainedRouter"):
         from . import routing
         return getattr(routing, name)
