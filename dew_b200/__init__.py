@@ -14,7 +14,7 @@ from typing import Any
 __version__ = "0.1.0"
 
 _EXPORTS = {
-    "Trainer": "training", "TrainState": "training", "Cooldown": "training", "Best": "training", "Plateau": "training",
+    "Trainer": "training", "TrainState": "training", "Cooldown": "training", "Best": "training", "Plateau": "training", "Pause": "training",
     "Evaluation": "training", "ProfileWindow": "training", "Tracker": "training", "LocalTracker": "training",
     "WandbTracker": "training", "Wandb": "training", "MLflowTracker": "training", "TensorBoardTracker": "training",
     "Trackers": "training", "MemoryTracker": "training",

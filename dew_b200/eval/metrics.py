@@ -4,7 +4,7 @@ lm-eval harness, calibration)."""
 from __future__ import annotations
 
 import math
-from typing import Callable, Optional
+from typing import Callable, Optional, Sequence
 
 import torch
 import torch.nn.functional as F
@@ -47,6 +47,23 @@ def frechet_distance(feat_a: torch.Tensor, feat_b: torch.Tensor) -> float:
 def fid(images_a: torch.Tensor, images_b: torch.Tensor, encoder: Callable[[torch.Tensor], torch.Tensor]) -> float:
     with torch.no_grad():
         return frechet_distance(encoder(images_a), encoder(images_b))
+
+
+def lpips(a: torch.Tensor, b: torch.Tensor, features: Callable[[torch.Tensor], Sequence[torch.Tensor]],
+          weights: Optional[Sequence[torch.Tensor]] = None) -> torch.Tensor:
+    """Learned perceptual image patch similarity (Zhang et al. 2018) per pair: ``features(images NHWC in [-1, 1])`` returns the
+    chosen layers' activations ``[B, C_l, H_l, W_l]`` (a frozen AlexNet / VGG loaded by the caller: no weights ship here);
+    each is unit-normalised over channels, the squared difference weighted per channel (``weights[l] [C_l]``, uniform when
+    None), averaged over space and summed over layers."""
+    fa, fb = features(a), features(b)
+    total = torch.zeros(a.shape[0], device=a.device)
+    for i, (x, y) in enumerate(zip(fa, fb)):
+        x = x.float() / x.float().pow(2).sum(1, keepdim=True).add(1e-10).sqrt()
+        y = y.float() / y.float().pow(2).sum(1, keepdim=True).add(1e-10).sqrt()
+        d = (x - y) ** 2
+        w = torch.full((x.shape[1],), 1.0 / x.shape[1], device=x.device) if weights is None else weights[i].to(x.device).float()
+        total = total + (d * w[None, :, None, None]).sum(1).mean((1, 2))
+    return total
 
 
 def clip_score(image_features: torch.Tensor, text_features: torch.Tensor) -> torch.Tensor:

@@ -72,6 +72,26 @@ class Plateau:
         return self._bad >= self.patience
 
 
+@dataclass(frozen=True)
+class Pause:
+    """End the run once it has trained ``fraction`` of its budget, its state and data position written in full, so a run
+    resumed from that checkpoint trains on as one that never paused (the budget still sizes the schedule).  Resume without it,
+    or with a later fraction, to go on.  Reference: src/dew/training/budget.py:123-160."""
+    fraction: float
+
+    def __post_init__(self):
+        if not 0 < self.fraction < 1:
+            raise ValueError(f"Pause needs a fraction of the budget in (0, 1), got {self.fraction}")
+
+    def at(self, steps: int) -> int:
+        """The step a run of ``steps`` pauses at: the whole update nearest the fraction; a pause before the first update or
+        at the budget's end is refused (the run would not start, or ends there anyway)."""
+        step = round(self.fraction * steps)
+        if step <= 0 or step >= steps:
+            raise ValueError(f"a pause at {self.fraction} of {steps} steps falls on step {step}: before the first update or at the end")
+        return step
+
+
 @dataclass
 class Best:
     """Track the best value of a metric (used with ``Checkpoints(ranking=...)`` and ``restore_best``)."""
@@ -286,7 +306,7 @@ class Trainer:
             checkpoint_final: bool = True, metrics: Sequence[Any] = (), preview: Optional[int] = None,
             best: Optional[Best] = None, stop: Optional[Plateau] = None, validation=None, restore_best: bool = False,
             observe: Optional[Callable] = None, device_prefetch: int = 0, cooldowns: Sequence["Cooldown"] = (),
-            summaries: Optional[Callable[[TrainState], Dict[str, float]]] = None) -> TrainState:
+            summaries: Optional[Callable[[TrainState], Dict[str, float]]] = None, pause: Optional[Pause] = None) -> TrainState:
         """``cooldowns``: learning-rate cooldown windows applied on top of the optimizer's schedule for this fit (branching a
         decayed run off a constant-rate trunk); ``summaries``: a callable whose scalars are logged beside the loss at the
         logging cadence (weight norms, router statistics, ...)."""
@@ -316,6 +336,8 @@ class Trainer:
             state = eng.adopt(state)
         target = _target_steps(steps, epochs, tokens, examples, loader, self.objective)
         every = _every(checkpoint_every, target)
+        if pause is not None:
+            target = pause.at(target)           # cadences above stay those of the whole budget; the final checkpoint is the pause's
         self._install_preemption()
         tracker = self.tracker
         window: List[Dict[str, Any]] = []

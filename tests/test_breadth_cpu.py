@@ -165,3 +165,21 @@ def test_gguf_round_trip_and_block_formats(tmp_path):
     raw["d"], raw["q"] = d, np.arange(16, dtype=np.uint8) | (np.arange(15, -1, -1, dtype=np.uint8) << 4)
     vals = gguf.dequantize(raw.tobytes(), gguf.Q4_0, (32,))
     assert vals[:16].tolist() == [(i - 8) * 0.5 for i in range(16)] and vals[16:].tolist() == [(15 - i - 8) * 0.5 for i in range(16)]
+
+
+def test_lpips_is_zero_for_equal_images_and_grows_with_distortion():
+    import torch
+    from dew_b200.eval.metrics import lpips
+    torch.manual_seed(0)
+    conv1, conv2 = torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.Conv2d(8, 12, 3, stride=2, padding=1)
+
+    def feats(x):
+        h1 = torch.relu(conv1(x.permute(0, 3, 1, 2)))
+        return [h1, torch.relu(conv2(h1))]
+    a = torch.rand(3, 16, 16, 3) * 2 - 1
+    with torch.no_grad():
+        assert float(lpips(a, a, feats).abs().max()) < 1e-8
+        small, large = lpips(a, a + 0.05 * torch.randn_like(a), feats), lpips(a, a + 0.5 * torch.randn_like(a), feats)
+        assert small.shape == (3,) and bool((large > small).all())
+        w = [torch.zeros(8), torch.zeros(12)]
+        assert float(lpips(a, -a, feats, w).abs().max()) == 0.0

@@ -49,3 +49,25 @@ def test_fit_search_walks_the_ladder():
     assert [t.fits for t in s.trials] == [False, True] and "remat" in s.report()
     with pytest.raises(NoPlanFits):
         FitSearch(2, capacity_bytes=8 * gib, measure=cost).run()
+
+
+def test_pause_ends_the_run_at_a_fraction_and_a_resume_goes_on(tmp_path):
+    import dew_b200 as dew
+    from dew_b200.models import CausalTransformer
+    from dew_b200.objectives.lm import LMObjective
+    with pytest.raises(ValueError):
+        dew.Pause(1.0)
+    assert dew.Pause(0.5).at(10) == 5
+    with pytest.raises(ValueError):
+        dew.Pause(0.01).at(10)
+
+    def trainer():
+        torch.manual_seed(0)
+        m = CausalTransformer(vocab_size=32, emb_features=16, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=8, mlp_features=24, max_seq_len=8)
+        return dew.Trainer(LMObjective(m, 8, ema_decay=None), dew.OptimConfig(learning_rate=1e-2), key=0, checkpoints=dew.Checkpoints(str(tmp_path / "run")))
+    g = torch.Generator().manual_seed(0)
+    data = [{"tokens": torch.randint(0, 32, (2, 9), generator=g)} for _ in range(8)]
+    state = trainer().fit(list(data), steps=8, pause=dew.Pause(0.5), log_every=1000)
+    assert state.step == 4
+    state = trainer().fit(list(data), steps=8, log_every=1000)               # resumes from the pause's checkpoint
+    assert state.step == 8
