@@ -51,3 +51,53 @@ def test_ledger_accounting():
     led.release(s1.pages)
     led.release(s2.pages)
     assert led.available() == 6
+
+
+def test_rollout_server_draws_versions_and_rescoring():
+    import torch
+    from dew_b200.inference.rollouts import NativeRolloutServer, rescore
+    from dew_b200.inference.serving import Server
+    from dew_b200.models import CausalTransformer
+    from dew_b200.utils.trees import module_variables
+    torch.manual_seed(0)
+    model = CausalTransformer(vocab_size=48, emb_features=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16, mlp_features=48, max_seq_len=64)
+    direct = Server(model, slots=4, capacity=32)
+    expect = direct([[1, 2, 3], [4, 5, 6, 7]], 6)
+    with NativeRolloutServer(Server(model, slots=4, capacity=32), version=3) as rs:
+        futs = [rs.submit([1, 2, 3], 6), rs.submit([4, 5, 6, 7], 6)]
+        draws = [f.result(timeout=120) for f in futs]
+        assert [d.tokens for d in draws] == expect and all(d.version == 3 and not d.stale for d in draws)
+        # new weights under a later version: later draws carry it, and differ from the old policy's
+        other = {"params": {k: (v + 0.3 * torch.randn_like(v) if v.dtype.is_floating_point else v) for k, v in _flat(module_variables(model)["params"])}}
+        rs.load(_unflat(other["params"]), 4)
+        later = rs.submit([1, 2, 3], 6).result(timeout=120)
+        assert later.version == 4 and later.tokens != draws[0].tokens
+        import pytest
+        with pytest.raises(ValueError):
+            rs.load(None, 2)
+        with pytest.raises(ValueError):
+            rs.submit(list(range(30)), 10)
+    lp = rescore(model, None, draws)
+    assert [len(x) for x in lp] == [6, 6] and all(bool((x <= 0).all()) for x in lp)
+    # greedy draws are each step's argmax, so every rescored token is its row's most likely one
+    tok = torch.tensor([draws[0].prompt + draws[0].tokens])
+    with torch.no_grad():
+        best = torch.log_softmax(model(tok[:, :-1]).float(), -1).max(-1).values[0, 2:]
+    assert torch.allclose(lp[0], best, atol=1e-5)
+
+
+def _flat(tree, prefix=()):
+    out = []
+    for k, v in tree.items():
+        out += _flat(v, prefix + (k,)) if isinstance(v, dict) else [(prefix + (k,), v)]
+    return out
+
+
+def _unflat(flat):
+    root = {}
+    for path, v in flat.items():
+        node = root
+        for k in path[:-1]:
+            node = node.setdefault(k, {})
+        node[path[-1]] = v
+    return {"params": root}
