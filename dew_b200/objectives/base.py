@@ -220,13 +220,16 @@ class Objective:
     """Base class.  Subclasses set ``self.model`` (an ``nn.Module``) and implement ``loss``."""
     model: torch.nn.Module
     ema_decay: Optional[float] = None
+    starts_from_model: bool = False     # fine-tuning objectives (preference / policy optimisation): ``init`` keeps the module's
+                                        # current weights instead of drawing new ones when no starting tree is given
 
     # -- construction of state
     def init(self, key: K.Key = 0, variables: Optional[Mapping[str, Any]] = None) -> Dict[str, Any]:
         """Initialise (or adopt) the variables: a ``{'params': tree}`` whose leaves alias the model's parameters."""
         from ..nn.layers import reset_all
         if variables is None:
-            reset_all(self.model, int(key) & 0x7FFFFFFF)
+            if not self.starts_from_model:
+                reset_all(self.model, int(key) & 0x7FFFFFFF)
             return module_variables(self.model)
         flat = variables_for_call(self.model, variables)
         with torch.no_grad():

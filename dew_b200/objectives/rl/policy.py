@@ -32,6 +32,7 @@ def _token_logprobs(logits, tokens):
 
 
 class GRPO(Objective):
+    starts_from_model = True
     """batch: ``tokens [B,S]``, ``mask [B,S]`` (1 on completion tokens), ``rewards [B]``, ``old_logprobs [B,S-1]``."""
 
     def __init__(self, model, group: int = 4, clip: float = 0.2, kl: float = 0.04):
@@ -58,6 +59,7 @@ class GRPO(Objective):
 
 
 class PPO(Objective):
+    starts_from_model = True
     """The model returns ``(logits, values)``; batch: ``tokens, mask, advantages [B,S-1], returns [B,S-1], old_logprobs``."""
 
     def __init__(self, model, clip: float = 0.2, value_coef: float = 0.5, entropy_coef: float = 0.0):
@@ -80,6 +82,7 @@ class PPO(Objective):
 
 
 class FlowGRPO(Objective):
+    starts_from_model = True
     """GRPO for flow-matching samplers (Flow-GRPO): the ODE sampler is turned into an SDE with the same marginals so that
     every denoising step is a Gaussian policy, ``x_{t-dt} ~ N(mean_theta(x_t, t), sigma_t^2 dt)``; images sampled in groups from
     one prompt are rewarded, rewards are whitened inside the group, and the clipped policy-gradient ratio is taken per

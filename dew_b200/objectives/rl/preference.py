@@ -17,6 +17,7 @@ def sequence_logprob(logits: torch.Tensor, tokens: torch.Tensor, mask: torch.Ten
 
 
 class DPO(Objective):
+    starts_from_model = True
     def __init__(self, model, beta: float = 0.1, label_smoothing: float = 0.0):
         self.model, self.beta, self.label_smoothing = model, beta, label_smoothing
         self.ema_decay = EMASpec.constant(1.0)          # the EMA slot never moves: it is the reference policy

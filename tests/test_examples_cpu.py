@@ -33,3 +33,13 @@ def test_train_masked_lm_example():
 
 def test_evaluate_and_serve_example():
     assert _load("evaluate_and_serve").main(["--device", "cpu"])
+
+
+def test_train_jepa_example():
+    losses, acc = _load("train_jepa").main(["--steps", "40", "--device", "cpu"])
+    assert losses[-1] < losses[0] and acc >= 0.5
+
+
+def test_train_rlvr_example():
+    history = _load("train_rlvr").main(["--rounds", "6", "--pretrain", "60", "--device", "cpu"])
+    assert len(history) == 6 and all(0.0 <= h <= 1.0 for h in history)
