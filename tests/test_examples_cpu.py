@@ -43,3 +43,24 @@ def test_train_jepa_example():
 def test_train_rlvr_example():
     history = _load("train_rlvr").main(["--rounds", "6", "--pretrain", "60", "--device", "cpu"])
     assert len(history) == 6 and all(0.0 <= h <= 1.0 for h in history)
+
+
+def test_moe_mesh_example_on_two_cpu_ranks():
+    import json
+    import subprocess
+    import sys
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29571", os.path.join(ROOT, "examples", "moe_mesh.py"), "--steps", "12", "--backend", "gloo"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert out.returncode == 0, out.stdout[-1500:] + out.stderr[-3000:]
+    r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    assert r["world"] == 2 and r["last"] < r["first"]
+
+
+def test_sample_text_to_image_example():
+    hits, total = _load("sample_text_to_image").main(["--steps", "150", "--device", "cpu"])
+    assert total == 6 and hits >= 3
+
+
+def test_train_supervised_example():
+    assert _load("train_supervised").main(["--steps", "300", "--device", "cpu"]) > 0.7
