@@ -183,3 +183,42 @@ def test_lpips_is_zero_for_equal_images_and_grows_with_distortion():
         assert small.shape == (3,) and bool((large > small).all())
         w = [torch.zeros(8), torch.zeros(12)]
         assert float(lpips(a, -a, feats, w).abs().max()) == 0.0
+
+
+def test_parity_gate_passes_equal_arms_and_fails_a_wrong_row():
+    import pytest
+    import torch
+    from dew_b200.utils.parity import assert_on_par, assess
+
+    def inputs(seed):
+        g = torch.Generator().manual_seed(seed)
+        return torch.randn(32, 64, generator=g, dtype=torch.float64), torch.randn(64, 48, generator=g, dtype=torch.float64)
+
+    def truth(seed):
+        a, b = inputs(seed)
+        return {"y": a @ b, "n": (a @ b).norm(dim=-1)}
+
+    def bf16(seed):
+        a, b = inputs(seed)
+        y = (a.bfloat16() @ b.bfloat16()).float()
+        return {"y": y, "n": y.norm(dim=-1)}
+
+    def fp32(seed):
+        a, b = inputs(seed)
+        y = a.float() @ b.float()
+        return {"y": y, "n": y.norm(dim=-1)}
+
+    found = assert_on_par(fp32, bf16, truth)                  # fp32 is far more exact than the bf16 reference
+    assert {f.leaf for f in found} == {"y", "n"} and all(f.ratio < 0.1 for f in found)
+    assert all(f.ok for f in assess(bf16, bf16, truth, range(8)))
+    over = {f.leaf: f for f in assess(bf16, fp32, truth, range(8))}           # the other way round is over
+    assert over["y"].status in ("over", "rows_over")
+    assert assess(fp32, bf16, truth, range(3))[0].status == "inconclusive"     # too few seeds decide nothing
+
+    def one_bad_row(seed):
+        out = bf16(seed)
+        y = out["y"].clone()
+        y[5] += 3.0
+        return {"y": y, "n": out["n"]}
+    with pytest.raises(AssertionError):
+        assert_on_par(one_bad_row, bf16, truth)

@@ -765,3 +765,50 @@ def test_raycast_kernel_matches_cpu_restatement(fisheye):
     close = (got - ref).abs().max(-1).values < 2e-3
     assert close.float().mean() > 0.995, float(close.float().mean())
     assert float((got - ref).abs().mean()) < 2e-3
+
+
+def test_kernels_are_on_par_with_pytorch_bf16_against_float64():
+    """The accuracy contract (``dew_b200.utils.parity``): over 8 seeds, each kernel's error from the float64 truth is within
+    1.5x that of the same op computed by PyTorch in bf16, and its worst row within 4x, forward and backward."""
+    import torch.nn.functional as F
+    from dew_b200.utils.parity import assert_on_par
+
+    def norm_inputs(seed):
+        g = torch.Generator(device=DEV).manual_seed(seed)
+        return (torch.randn(512, 1024, device=DEV, generator=g).to(torch.bfloat16), (1 + 0.1 * torch.randn(1024, device=DEV, generator=g)).to(torch.bfloat16),
+                torch.randn(512, 1024, device=DEV, generator=g).to(torch.bfloat16))
+
+    def norm_arm(fn, dtype):
+        def run(seed):
+            x, w, dy = norm_inputs(seed)
+            x, w = x.to(dtype).requires_grad_(), w.to(dtype).requires_grad_()
+            y = fn(x, w)
+            y.backward(dy.to(y.dtype))
+            return {"y": y, "dx": x.grad, "dw": w.grad}
+        return run
+    plain = lambda x, w: (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()).to(x.dtype)
+    exact = lambda x, w: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+    assert_on_par(norm_arm(lambda x, w: ops.rms_norm(x, w, 1e-6), torch.bfloat16), norm_arm(plain, torch.bfloat16), norm_arm(exact, torch.float64))
+
+    def attn_inputs(seed):
+        g = torch.Generator(device=DEV).manual_seed(100 + seed)
+        mk = lambda h: torch.randn(1, 512, h, 128, device=DEV, generator=g).to(torch.bfloat16)
+        return mk(4), mk(2), mk(2), mk(4)
+
+    def attn_arm(kind):
+        def run(seed):
+            q, k, v, do = attn_inputs(seed)
+            if kind == "truth":
+                q, k, v = (t.double().requires_grad_() for t in (q, k, v))
+                kk, vv = (t.repeat_interleave(2, 2) for t in (k, v))
+                sc = torch.einsum("bshd,bthd->bhst", q, kk) / math.sqrt(128)
+                sc = sc.masked_fill(~torch.tril(torch.ones(512, 512, dtype=torch.bool, device=DEV)), float("-inf"))
+                o = torch.einsum("bhst,bthd->bshd", torch.softmax(sc, -1), vv)
+            else:
+                q, k, v = (t.requires_grad_() for t in (q, k, v))
+                o = ops.attention(q, k, v, causal=True, kernel="sm100_flash" if kind == "kernel" else "sdpa")
+            o.backward(do.to(o.dtype))
+            return {"o": o, "dq": q.grad, "dk": k.grad, "dv": v.grad}
+        return run
+    assert_on_par(attn_arm("kernel"), attn_arm("sdpa"), attn_arm("truth"))
+    L.check_status()
