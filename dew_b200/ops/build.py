@@ -93,6 +93,30 @@ def ptxas_report() -> str:
     return "\n".join(out)
 
 
+def kernel_resources() -> dict:
+    """``{(file, kernel symbol): {"registers", "spill_stores", "spill_loads", "stack"}}`` parsed from the ptxas logs of the
+    last compile (the resource gate of the tests reads this: a kernel that starts to spill shows up here, before any GPU run)."""
+    import re
+    found = {}
+    for log in sorted(OBJ_DIR.glob("*.ptxas.log")):
+        entry = None
+        for line in log.read_text().splitlines():
+            m = re.search(r"Compiling entry function '([^']+)' for 'sm_100a'", line)
+            if m:
+                entry = (log.name.split(".")[0], m.group(1))
+                found[entry] = {"registers": 0, "spill_stores": 0, "spill_loads": 0, "stack": 0}
+                continue
+            if entry is None:
+                continue
+            m = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", line)
+            if m:
+                found[entry].update(stack=int(m.group(1)), spill_stores=int(m.group(2)), spill_loads=int(m.group(3)))
+            m = re.search(r"Used (\d+) registers", line)
+            if m:
+                found[entry]["registers"] = int(m.group(1))
+    return found
+
+
 if __name__ == "__main__":
     build(verbose=True, force="--force" in sys.argv)
     if "--report" in sys.argv:

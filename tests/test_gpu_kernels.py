@@ -812,3 +812,61 @@ def test_kernels_are_on_par_with_pytorch_bf16_against_float64():
         return run
     assert_on_par(attn_arm("kernel"), attn_arm("sdpa"), attn_arm("truth"))
     L.check_status()
+
+
+def test_atomics_free_kernels_are_bitwise_repeatable():
+    """Run-twice determinism (the stand-in for a race detector here): kernels that promise no atomics must return the same
+    bits on the same inputs - a missing barrier or a buffer reused too early shows up as a difference."""
+    from dew_b200.ops import scan
+    from dew_b200.parallel.ep import TokenExchange
+    torch.manual_seed(5)
+
+    def twice(fn):
+        a = fn()
+        torch.cuda.synchronize()
+        b = fn()
+        torch.cuda.synchronize()
+        for x, y in zip(a, b):
+            assert torch.equal(x, y)
+
+    # flash attention forward and backward (dQ, dK, dV without atomics)
+    qkv = torch.randn(2, 1024, 4 + 2 * 2, 128, device=DEV).to(torch.bfloat16)
+    do = torch.randn(2, 1024, 4, 128, device=DEV).to(torch.bfloat16)
+
+    def attn():
+        x = qkv.clone().requires_grad_()
+        o = ops.attention(x[:, :, :4], x[:, :, 4:6], x[:, :, 6:], causal=True, kernel="sm100_flash")
+        o.backward(do)
+        return o.detach(), x.grad
+    twice(attn)
+    # gated delta rule forward + backward
+    q, k, v, g, beta, _ = _gdn_inputs(1, 512, 2, 77, False)
+
+    def gdn():
+        leaves = [t.clone().requires_grad_() for t in (q, k, v, g, beta)]
+        o, S = scan.chunk_gated_delta_rule(*leaves)
+        torch.autograd.backward((o, S), (torch.ones_like(o), torch.ones_like(S) * 0.1))
+        return (o.detach(), S.detach(), *[t.grad for t in leaves])
+    twice(gdn)
+    # MoE exchange: plan, dispatch, combine
+    x = torch.randn(512, 256, device=DEV).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(16, device=DEV)[:4] for _ in range(512)])
+    w = torch.rand(512, 4, device=DEV)
+    ex = TokenExchange(16, "self")
+
+    def moe():
+        plan = ex.plan(ids, 256)
+        rows = ex.push(x, plan)
+        out = ex.pull(rows, plan, w)
+        return rows, out
+    twice(moe)
+    # CTA-pair GEMM with fp32 accumulation into an existing buffer
+    A, Bm = torch.randn(1024, 512, device=DEV).to(torch.bfloat16), torch.randn(1024, 768, device=DEV).to(torch.bfloat16)
+    base = torch.randn(512, 768, device=DEV)
+
+    def wgrad():
+        out = base.clone()
+        ops.gemm(A, Bm, a_mn=True, b_mn=True, out=out, accumulate=True, kernel="sm100_pair")
+        return (out,)
+    twice(wgrad)
+    L.check_status()
