@@ -69,8 +69,10 @@ __device__ __forceinline__ float reduce_scatter32(float (&v)[32], int lane) {
 
 struct Tail {
   float g[PT], beta[PT], eg[PT];
-  float sum_q[PT], sum_k[PT], sum_kd[PT], sum_v[PT];       // state kernel: per-token sums over the feature index
-  float dss[2];                                              // <dS1, S0> per chunk
+  // state kernel: per-token sums over the feature index.  Each of the four warps that share a token keeps its own slot and
+  // the reader adds the slots in a fixed order, so the gradients of g and beta are bitwise repeatable (no shared atomics).
+  float sum_q[4][PT], sum_k[4][PT], sum_kd[4][PT], sum_v[4][PT];
+  float dss[2][4];                                           // <dS1, S0> per chunk, one slot per warp
   float red[8];
   uint64_t bar[6];
   uint32_t tmem_base;
@@ -83,8 +85,9 @@ struct Tail {
 constexpr int S_OFF_K = 0, S_OFF_S = T32, S_OFF_G = 2 * T32, S_OFF_DO = 3 * T32, S_OFF_DVN = 3 * T32 + T16,
               S_OFF_VN = 3 * T32 + 2 * T16, S_OFF_V = 3 * T32 + 3 * T16, S_OFF_Q = 3 * T32 + 4 * T16,
               S_OFF_AT = 3 * T32 + 5 * T16, S_OFF_TAIL = S_OFF_AT + 2 * CH * CH * 4;
-constexpr int STATE_SMEM = S_OFF_TAIL + 5120;
-static_assert(sizeof(Tail) <= 5120, "Tail must fit its slot");
+constexpr int TAIL_BYTES = 10240;
+constexpr int STATE_SMEM = S_OFF_TAIL + TAIL_BYTES;
+static_assert(sizeof(Tail) <= TAIL_BYTES, "Tail must fit its slot");
 static_assert(STATE_SMEM <= 232448, "state kernel exceeds the shared memory of an SM");
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -134,9 +137,10 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
     tail->g[tid] = gi;
     tail->eg[tid] = __expf(gi);
     tail->beta[tid] = t < T ? beta[(static_cast<long long>(b) * T + t) * H + h] : 0.f;
-    tail->sum_q[tid] = 0.f; tail->sum_k[tid] = 0.f; tail->sum_kd[tid] = 0.f; tail->sum_v[tid] = 0.f;
+#pragma unroll
+    for (int w4 = 0; w4 < 4; ++w4) { tail->sum_q[w4][tid] = 0.f; tail->sum_k[w4][tid] = 0.f; tail->sum_kd[w4][tid] = 0.f; tail->sum_v[w4][tid] = 0.f; }
   }
-  if (tid < 2) tail->dss[tid] = 0.f;
+  if (tid < 8) tail->dss[tid >> 2][tid & 3] = 0.f;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -296,8 +300,8 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
             p2[jj] = dkd * kv;
           }
           const float s1 = reduce_scatter32(p1, lane), s2 = reduce_scatter32(p2, lane);
-          atomicAdd(&tail->sum_k[c * 64 + half * 32 + lane], s1);
-          atomicAdd(&tail->sum_kd[c * 64 + half * 32 + lane], s2);
+          tail->sum_k[warp & 3][c * 64 + half * 32 + lane] = s1;
+          tail->sum_kd[warp & 3][c * 64 + half * 32 + lane] = s2;
         }
         tmem_ld_32x32b_x32(tmem + lane_addr + TM_X1, v0);
         tmem_ld_32x32b_x32(tmem + lane_addr + TM_X1 + 32, v1);
@@ -314,14 +318,14 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
             p1[jj] = dq1 * tile_get(sQ, CH, j, f);
           }
           const float s = reduce_scatter32(p1, lane);
-          atomicAdd(&tail->sum_q[c * 64 + half * 32 + lane], s);
+          tail->sum_q[warp & 3][c * 64 + half * 32 + lane] = s;
         }
         // <dS1, S0>: row f of dS1 against column f of the transposed state tile
         float acc = 0.f;
 #pragma unroll 8
         for (int v = 0; v < HD; ++v) acc = fmaf(tile_get(sG, PT, f, v), tile_get(sS, PT, v, f), acc);
         acc = warp_sum(acc);
-        if (lane == 0) atomicAdd(&tail->dss[c], acc);
+        if (lane == 0) tail->dss[c][warp & 3] = acc;
       } else {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
@@ -335,7 +339,7 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
             p1[jj] = xs[j] * tile_get(sV, CH, j, f);
           }
           const float s = reduce_scatter32(p1, lane);
-          atomicAdd(&tail->sum_v[c * 64 + half * 32 + lane], s);
+          tail->sum_v[warp & 3][c * 64 + half * 32 + lane] = s;
         }
       }
       tc_fence_before();
@@ -346,14 +350,16 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
   // per-token partial gradients of gc and beta
   if (tid < PT && tail->abort_flag == 0) {
     const int i = tid, c = i >> 6;
-    float dg = tail->sum_q[i] - tail->sum_kd[i] + tail->beta[i] * tail->eg[i] * tail->sum_k[i];
+    auto four = [](const float (*a)[PT], int j) { return (a[0][j] + a[1][j]) + (a[2][j] + a[3][j]); };
+    const float sq = four(tail->sum_q, i), sk = four(tail->sum_k, i), skd = four(tail->sum_kd, i), sv = four(tail->sum_v, i);
+    float dg = sq - skd + tail->beta[i] * tail->eg[i] * sk;
     if ((i & 63) == 63) {
       float tot = 0.f;
-      for (int j = 0; j < CH; ++j) tot += tail->sum_kd[c * 64 + j];
-      dg += tot + tail->eg[i] * tail->dss[c];
+      for (int j = 0; j < CH; ++j) tot += four(tail->sum_kd, c * 64 + j);
+      dg += tot + tail->eg[i] * ((tail->dss[c][0] + tail->dss[c][1]) + (tail->dss[c][2] + tail->dss[c][3]));
     }
     gpart[static_cast<long long>(x) * Tp + t0 + i] = dg;
-    bpart[static_cast<long long>(x) * Tp + t0 + i] = tail->sum_v[i] + tail->eg[i] * tail->sum_k[i];
+    bpart[static_cast<long long>(x) * Tp + t0 + i] = sv + tail->eg[i] * sk;
   }
   tc_fence_before();
   __syncthreads();
@@ -368,7 +374,7 @@ gdn_bwd_state_kernel(const __grid_constant__ CUtensorMap tk, const __grid_consta
 // pair kernel
 
 constexpr int P_OFF_TAIL = 5 * T32;
-constexpr int PAIR_SMEM = P_OFF_TAIL + 5120;
+constexpr int PAIR_SMEM = P_OFF_TAIL + TAIL_BYTES;
 
 __global__ void __launch_bounds__(THREADS, 1)
 gdn_bwd_pair_kernel(const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tq,
