@@ -275,3 +275,168 @@ class HybridDiT(_TokenBackbone):
                 h = modulate(b["norm"](t), sh, sc)
                 t = t + g.unsqueeze(1) * (b["fwd"](h) + b["bwd"](h.flip(1)).flip(1))
         return self.output(t, c, grid)
+
+
+# ------------------------------------------------------------------------------------------------ more families
+@register("unet_3d")
+class UNet3D(nn.Module):
+    """Video UNet ``[B, T, H, W, C]``: the 2-D UNet's residual blocks run per frame, and after every level a temporal
+    attention mixes each location over the frames (factorised space / time, as video diffusion UNets do)."""
+
+    def __init__(self, input_channels=3, output_channels=3, features: Sequence[int] = (32, 64), blocks_per_level: int = 1,
+                 text_features: Optional[int] = None, num_classes: Optional[int] = None, heads: int = 4):
+        super().__init__()
+        temb = features[0] * 4
+        self.cond = ConditioningEmbed(temb, text_features, num_classes)
+        self.inp = nn.Conv2d(input_channels, features[0], 3, padding=1)
+        self.down, self.down_t, self.up, self.up_t = nn.ModuleList(), nn.ModuleList(), nn.ModuleList(), nn.ModuleList()
+        self.pool, self.unpool = nn.ModuleList(), nn.ModuleList()
+        c = features[0]
+        for lvl, f in enumerate(features):
+            self.down.append(nn.ModuleList([_ResBlock(c if i == 0 else f, f, temb) for i in range(blocks_per_level)]))
+            self.down_t.append(_TemporalAttention(f, heads))
+            self.pool.append(nn.Conv2d(f, f, 3, stride=2, padding=1) if lvl < len(features) - 1 else nn.Identity())
+            c = f
+        self.mid = _ResBlock(c, c, temb)
+        for lvl, f in reversed(list(enumerate(features))):
+            self.up.append(nn.ModuleList([_ResBlock((c + f) if i == 0 else f, f, temb) for i in range(blocks_per_level)]))
+            self.up_t.append(_TemporalAttention(f, heads))
+            self.unpool.append(nn.Upsample(scale_factor=2, mode="nearest") if lvl > 0 else nn.Identity())
+            c = f
+        self.out = nn.Sequential(nn.GroupNorm(min(8, c), c), nn.SiLU(), nn.Conv2d(c, output_channels, 3, padding=1))
+        nn.init.zeros_(self.out[-1].weight); nn.init.zeros_(self.out[-1].bias)
+
+    def forward(self, x, temb, textcontext=None, train=False, duration=None):
+        ctx = _ctx(textcontext)
+        B, T, H, W, C = x.shape
+        t = self.cond(temb, ctx.get("text"), ctx.get("label")).repeat_interleave(T, 0)
+        h = self.inp(x.reshape(B * T, H, W, C).permute(0, 3, 1, 2))
+        skips = []
+        for blocks, mix, pool in zip(self.down, self.down_t, self.pool):
+            for b in blocks:
+                h = b(h, t)
+            h = mix(h, T)
+            skips.append(h)
+            h = pool(h)
+        h = self.mid(h, t)
+        for blocks, mix, unpool in zip(self.up, self.up_t, self.unpool):
+            s = skips.pop()
+            if h.shape[-2:] != s.shape[-2:]:
+                h = F.interpolate(h, size=s.shape[-2:], mode="nearest")
+            h = torch.cat([h, s], 1)
+            for b in blocks:
+                h = b(h, t)
+            h = unpool(mix(h, T))
+        if h.shape[-2:] != (H, W):
+            h = F.interpolate(h, size=(H, W), mode="nearest")
+        return self.out(h).permute(0, 2, 3, 1).reshape(B, T, H, W, -1).float()
+
+
+class _TemporalAttention(nn.Module):
+    """Self-attention over the frame axis at every pixel of ``[B*T, C, h, w]`` feature maps (residual, zero-initialised out)."""
+
+    def __init__(self, channels: int, heads: int):
+        super().__init__()
+        self.norm = nn.GroupNorm(min(8, channels), channels)
+        self.attn = SelfAttention(channels, heads, bias=True, causal=False)
+        self.gate = nn.Parameter(torch.zeros(()))
+
+    def forward(self, x, frames: int):
+        BT, C, h, w = x.shape
+        B = BT // frames
+        seq = self.norm(x).reshape(B, frames, C, h * w).permute(0, 3, 1, 2).reshape(B * h * w, frames, C)
+        y = self.attn(seq).reshape(B, h * w, frames, C).permute(0, 2, 3, 1).reshape(BT, C, h, w)
+        return x + self.gate * y
+
+
+@register("hierarchical_mmdit")
+class HierarchicalMMDiT(_TokenBackbone):
+    """Joint text-image blocks at two resolutions: fine tokens, then 2 x 2 merged coarse tokens (4x fewer, the bulk of the
+    depth), then fine again with a skip from the first stage."""
+
+    def __init__(self, patch_size=2, emb_features=128, num_layers=(1, 2, 1), num_heads=4, mlp_ratio=4.0, input_channels=3, output_channels=3,
+                 text_features=64, num_classes=None):
+        super().__init__(patch_size, emb_features, input_channels, output_channels, text_features, num_classes)
+        d = emb_features
+        self.text_in = Linear(text_features, d, bias=True)
+        mk = lambda n: nn.ModuleList([_JointBlock(d, num_heads, mlp_ratio) for _ in range(n)])
+        self.fine_in, self.coarse, self.fine_out = mk(num_layers[0]), mk(num_layers[1]), mk(num_layers[2])
+        self.merge = Linear(4 * d, d, bias=True)
+        self.split = Linear(d, 4 * d, bias=True)
+        self.skip = Linear(2 * d, d, bias=True)
+
+    def forward(self, x, temb, textcontext=None, train=False, duration=None):
+        ctx = _ctx(textcontext)
+        img, (gh, gw) = self.tokens(x)
+        if gh % 2 or gw % 2:
+            raise ValueError("the token grid must be even in both directions to merge 2 x 2 tokens")
+        text = ctx.get("text")
+        if text is None:
+            text = torch.zeros(x.shape[0], 1, self.text_in.in_features, device=x.device)
+        c = self.conditioning(temb, text, ctx.get("label"))
+        txt = self.text_in(text.to(img.dtype))
+        for b in self.fine_in:
+            img, txt = b(img, txt, c)
+        B, N, d = img.shape
+        first = img
+        coarse = self.merge(img.reshape(B, gh // 2, 2, gw // 2, 2, d).permute(0, 1, 3, 2, 4, 5).reshape(B, N // 4, 4 * d))
+        for b in self.coarse:
+            coarse, txt = b(coarse, txt, c)
+        fine = self.split(coarse).reshape(B, gh // 2, gw // 2, 2, 2, d).permute(0, 1, 3, 2, 4, 5).reshape(B, N, d)
+        img = self.skip(torch.cat([fine, first], -1))
+        for b in self.fine_out:
+            img, txt = b(img, txt, c)
+        return self.output(img, c, (gh, gw))
+
+
+@register("ssm_dit")
+class SSMDiT(HybridDiT):
+    """A DiT whose every block is a bidirectional Mamba-2 mixer under adaLN modulation (no attention)."""
+
+    def __init__(self, **kw):
+        kw.setdefault("pattern", "mamba2")
+        super().__init__(**kw)
+
+
+@register("jepa_encoder")
+class JepaEncoder(nn.Module):
+    """ViT encoder over image patches for JEPA: ``images [B, H, W, C]`` or patch tokens -> ``[B, tokens, features]``; ``keep``
+    (a bool mask over tokens) runs the blocks on the kept tokens only, the way a context encoder sees a masked image."""
+
+    def __init__(self, patch_size=4, emb_features=128, num_layers=4, num_heads=4, mlp_ratio=4.0, input_channels=3, frames: int = 1):
+        super().__init__()
+        self.patch_size, self.emb_features, self.frames = patch_size, emb_features, frames
+        self.embed = PatchEmbedding(patch_size, input_channels, emb_features)
+        self.blocks = nn.ModuleList([nn.ModuleDict({"n1": LayerNorm(emb_features), "attn": SelfAttention(emb_features, num_heads, bias=True, causal=False),
+                                                    "n2": LayerNorm(emb_features), "mlp": GeluMLP(emb_features, int(emb_features * mlp_ratio))})
+                                     for _ in range(num_layers)])
+        self.norm = LayerNorm(emb_features)
+
+    def tokens(self, x):
+        if x.dim() == 5:                                   # video: frames are embedded one by one, time added as a second signal
+            B, T, H, W, C = x.shape
+            tok = self.embed(x.reshape(B * T, H, W, C))
+            gh, gw = H // self.patch_size, W // self.patch_size
+            tok = tok + sincos_2d(gh, gw, self.emb_features, tok.device).to(tok.dtype)[None]
+            tok = tok.reshape(B, T, gh * gw, -1) + sinusoidal(torch.arange(T, device=x.device).float(), self.emb_features).to(tok.dtype)[None, :, None]
+            return tok.reshape(B, T * gh * gw, -1)
+        B, H, W, C = x.shape
+        tok = self.embed(x)
+        return tok + sincos_2d(H // self.patch_size, W // self.patch_size, self.emb_features, tok.device).to(tok.dtype)[None]
+
+    def forward(self, x, keep: Optional[torch.Tensor] = None):
+        tok = self.tokens(x) if x.dim() >= 4 else x
+        if keep is not None:
+            tok = tok[:, keep]
+        for b in self.blocks:
+            tok = tok + b["attn"](b["n1"](tok))
+            tok = tok + b["mlp"](b["n2"](tok))
+        return self.norm(tok)
+
+
+@register("jepa_video_encoder")
+class JepaVideoEncoder(JepaEncoder):
+    """The same encoder over ``[B, T, H, W, C]`` clips (space-time tokens, joint attention)."""
+
+    def __init__(self, frames: int = 8, **kw):
+        super().__init__(frames=frames, **kw)

@@ -78,3 +78,44 @@ def test_hyper_connections_and_altup_reduce_to_the_residual_stack_and_train():
     au = AltUp(1, 0)
     x, pred = au.read(H)
     assert torch.allclose(au.write(H, torch.ones(2, 5, 8), pred), H + 1)
+
+
+def test_more_backbone_families_forward_and_backward():
+    import torch
+    from dew_b200.models.diffusion_backbones import HierarchicalMMDiT, JepaEncoder, JepaVideoEncoder, SSMDiT, UNet3D
+    from dew_b200.utils.registry import lookup
+    torch.manual_seed(0)
+    t = torch.rand(2)
+    vid = torch.randn(2, 3, 16, 16, 3)
+    net = UNet3D(features=(16, 32), heads=2)
+    for p in net.out[-1].parameters():
+        torch.nn.init.normal_(p, std=0.02)
+    y = net(vid, t)
+    assert y.shape == vid.shape
+    y.pow(2).mean().backward()
+    assert all(p.grad is not None for n, p in net.named_parameters() if "gate" not in n or True)
+    # temporal mixing: with open gates a change in one frame reaches the others
+    with torch.no_grad():
+        for m in net.modules():
+            if hasattr(m, "gate"):
+                m.gate.fill_(1.0)
+        other = vid.clone(); other[:, 0] += 1.0
+        assert float((net(other, t)[:, 2] - net(vid, t)[:, 2]).abs().max()) > 0
+    img = torch.randn(2, 16, 16, 3)
+    h = HierarchicalMMDiT(emb_features=32, num_heads=2, text_features=8)
+    for p in h.output.out.parameters():
+        torch.nn.init.normal_(p, std=0.02)
+    out = h(img, t, {"text": torch.randn(2, 5, 8)})
+    assert out.shape == img.shape
+    out.pow(2).mean().backward()
+    assert h.merge.weight.grad is not None and float(h.merge.weight.grad.abs().sum()) > 0
+    s = SSMDiT(emb_features=64, num_layers=2, num_heads=2, state_dim=16)
+    assert s.kinds == ["mamba2", "mamba2"] and s(img, t).shape == img.shape
+    enc = JepaEncoder(emb_features=32, num_layers=2, num_heads=2)
+    full = enc(img)
+    keep = torch.zeros(16, dtype=torch.bool); keep[:6] = True
+    assert full.shape == (2, 16, 32) and enc(img, keep).shape == (2, 6, 32)
+    venc = JepaVideoEncoder(frames=3, emb_features=32, num_layers=1, num_heads=2)
+    assert venc(vid).shape == (2, 3 * 16, 32)
+    for name in ("unet_3d", "hierarchical_mmdit", "ssm_dit", "jepa_encoder", "jepa_video_encoder"):
+        assert lookup(name) is not None
