@@ -222,3 +222,46 @@ def test_parity_gate_passes_equal_arms_and_fails_a_wrong_row():
         return {"y": y, "n": out["n"]}
     with pytest.raises(AssertionError):
         assert_on_par(one_bad_row, bf16, truth)
+
+
+def test_chat_rendering_roles_and_token_shards(tmp_path):
+    import numpy as np
+    import pytest
+    import torch
+    from dew_b200.data import ByteTokenizer
+    from dew_b200.data.chat import ChatTemplate, Conversation, Role, chat_batch, render_conversation, render_prompt
+    from dew_b200.data.sinks import read_token_shards, write_jsonl, write_token_shards
+    tok = ByteTokenizer()
+    conv = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "2+2?"}, {"role": "assistant", "content": "4"}]
+    r = render_conversation(tok, conv)
+    text = bytes(r["tokens"].tolist()).decode()
+    assert text == "<|im_start|>system\nbe brief<|im_end|>\n<|im_start|>user\n2+2?<|im_end|>\n<|im_start|>assistant\n4<|im_end|>\n"
+    scored = bytes(r["tokens"][r["roles"] == Role.ASSISTANT].tolist()).decode()
+    assert scored == "4<|im_end|>\n"                                        # the answer and its closing frame
+    assert bytes(r["tokens"][r["roles"] == Role.USER].tolist()).decode() == "2+2?"
+    unscored = render_conversation(tok, conv, ChatTemplate(score_close=False))
+    assert bytes(unscored["tokens"][unscored["roles"] == Role.ASSISTANT].tolist()).decode() == "4"
+    prompt = bytes(render_prompt(tok, conv).tolist()).decode()
+    assert prompt.endswith("<|im_start|>assistant\n") and "4<|im_end|>" not in prompt
+    batch = chat_batch(tok, [conv, conv[1:]], seq_len=48)
+    assert batch["tokens"].shape == (2, 49) and batch["roles"].shape == (2, 49)
+    with pytest.raises(ValueError):
+        Conversation.of([{"role": "user", "content": "x"}, {"role": "system", "content": "late"}])
+    with pytest.raises(ValueError):
+        Conversation.of([{"role": "narrator", "content": "x"}])
+    # the objective scores the assistant's tokens only
+    from dew_b200.models import CausalTransformer
+    from dew_b200.objectives import Step
+    from dew_b200.objectives.lm import LMObjective
+    torch.manual_seed(0)
+    m = CausalTransformer(vocab_size=256, emb_features=16, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=8, mlp_features=24, max_seq_len=48)
+    obj = LMObjective(m, 48, ema_decay=None, loss_role=int(Role.ASSISTANT))
+    stat, _ = obj.loss(None, batch, Step(key=0, train=False))
+    assert int(stat.mass) == int((batch["roles"][:, 1:] == Role.ASSISTANT).sum())
+    # shards
+    docs = [list(range(i, i + 5 + i)) for i in range(7)]
+    index = write_token_shards(docs, tmp_path / "shards", shard_tokens=20, vocab_size=256, eos_id=255)
+    assert len(index["shards"]) > 1 and index["tokens"] == sum(len(d) + 1 for d in docs)
+    back = list(read_token_shards(tmp_path / "shards"))
+    assert len(back) == 7 and all(np.array_equal(b, np.array(d + [255])) for b, d in zip(back, docs))
+    assert write_jsonl([{"a": 1}, {"a": 2}], tmp_path / "r.jsonl") == 2 and (tmp_path / "r.jsonl").read_text().count("\n") == 2
