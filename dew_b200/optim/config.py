@@ -82,13 +82,19 @@ class Optimizer:
         zeros = lambda p: torch.zeros_like(p, dtype=sd if p.dtype.is_floating_point else p.dtype)
         state: Dict[str, Any] = {"count": torch.zeros((), dtype=torch.int64)}
         kind = self.config.optimizer
-        if kind in ("adamw", "adam", "lamb", "laprop", "muon"):
+        if kind in ("adamw", "adam", "lamb", "laprop", "muon", "normuon"):
             state["mu"] = unflatten({k: zeros(v) for k, v in flat.items()})
             state["nu"] = unflatten({k: zeros(v) for k, v in flat.items()})
+        elif kind == "m3":
+            # fast momentum, second moment, slow momentum, the open chunk's gradient sum and the slow direction read by the
+            # next chunk (fp32 at least: the sums do not decay)
+            f32 = lambda p: torch.zeros_like(p, dtype=torch.float32 if p.dtype.is_floating_point else p.dtype)
+            for name in ("mu", "nu", "slow", "chunk", "slow_direction"):
+                state[name] = unflatten({k: f32(v) for k, v in flat.items()})
         elif kind in ("sgd", "lion"):
             state["mu"] = unflatten({k: zeros(v) for k, v in flat.items()})
         else:
-            raise ValueError(f"unknown optimizer {kind!r}; known: adamw, adam, sgd, lamb, laprop, lion, muon")
+            raise ValueError(f"unknown optimizer {kind!r}; known: adamw, adam, sgd, lamb, laprop, lion, muon, normuon, m3")
         return state
 
     # ------------------------------------------------------------------ gradient norm / clipping
@@ -155,6 +161,41 @@ class Optimizer:
                 wn, un = p.float().norm(), upd.norm()
                 trust = float(wn / un) if float(wn) > 0 and float(un) > 0 else 1.0
                 p.add_(upd.to(p.dtype), alpha=-plr * trust)
+            elif kind == "m3":
+                # Multi-scale Momentum Muon (Nested Learning, arXiv 2512.24695, Algorithm 1): direction
+                # (O1 + alpha O2) / sqrt(V + eps); M1 += beta1 g, V += beta2 g^2 (sums, no decay); every `frequency` updates
+                # the slow momentum M2 += beta3 * (the chunk's gradient sum) and O2 = orthogonalised M2 for the next chunk.
+                slow, chunk, sdir = (flatten(state[n]) for n in ("slow", "chunk", "slow_direction"))
+                gf = g.float() * coef
+                beta3, alpha, freq = opts.get("b3", 0.9), opts.get("alpha", 0.5), int(opts.get("frequency", 4))
+                mu[path].add_(gf, alpha=opts.get("b1", 0.9))
+                nu[path].add_(gf * gf, alpha=opts.get("b2", 0.999))
+                matrix = p.dim() == 2
+                o1 = newton_schulz(mu[path], opts.get("ns_steps", 5)) if matrix else mu[path] / (mu[path].norm() + 1e-7)
+                direction = (o1 + alpha * sdir[path]) / torch.sqrt(nu[path] + opts.get("eps", 1e-8))
+                p.mul_(1 - plr * wd).add_(direction.to(p.dtype), alpha=-plr)
+                chunk[path].add_(gf)
+                if count % freq == 0:
+                    slow[path].add_(chunk[path], alpha=beta3)
+                    chunk[path].zero_()
+                    sdir[path].copy_(newton_schulz(slow[path], opts.get("ns_steps", 5)) if matrix else slow[path] / (slow[path].norm() + 1e-7))
+            elif kind == "normuon":
+                # NorMuon (arXiv 2510.05491): Muon's orthogonal update, each output neuron (row) divided by the root of its
+                # decayed mean square, the matrix scaled back to the orthogonal update's Frobenius norm
+                if p.dim() == 2 and "embed" not in path and "head" not in path:
+                    m = mu[path]
+                    mom = opts.get("momentum", 0.95)
+                    m.mul_(mom).add_(g.to(m.dtype), alpha=coef)
+                    u = newton_schulz(g.float() * coef + mom * m.float(), opts.get("ns_steps", 5))
+                    row = nu[path][:, :1]
+                    b2n = opts.get("neuron_b2", 0.95)
+                    row.copy_((row.float() * b2n + (1 - b2n) * u.pow(2).mean(1, keepdim=True)).to(row.dtype))
+                    normed = u / (row.float().sqrt() + opts.get("neuron_eps", 1e-10))
+                    normed = normed * (u.norm() / (normed.norm() + 1e-20))
+                    normed = normed * max(1.0, p.shape[0] / p.shape[1]) ** 0.5
+                    p.mul_(1 - plr * wd).add_(normed.to(p.dtype), alpha=-plr)
+                else:
+                    _adamw_generic(p, mu[path], nu[path], g, count, plr * opts.get("adam_lr_scale", 1.0), b1, b2, eps, wd, coef)
             elif kind == "muon":
                 if p.dim() == 2 and "embed" not in path and "head" not in path:
                     m = mu[path]

@@ -265,3 +265,34 @@ def test_chat_rendering_roles_and_token_shards(tmp_path):
     back = list(read_token_shards(tmp_path / "shards"))
     assert len(back) == 7 and all(np.array_equal(b, np.array(d + [255])) for b, d in zip(back, docs))
     assert write_jsonl([{"a": 1}, {"a": 2}], tmp_path / "r.jsonl") == 2 and (tmp_path / "r.jsonl").read_text().count("\n") == 2
+
+
+def test_normuon_and_m3_optimizers_reduce_a_quadratic_and_keep_their_rules():
+    import torch
+    from dew_b200.optim.config import OptimConfig, newton_schulz
+    torch.manual_seed(0)
+    target = torch.randn(12, 8)
+    for kind, opts, lr in (("normuon", {}, 0.05), ("m3", {"frequency": 3, "alpha": 0.5, "b1": 0.9, "b2": 1.0, "b3": 0.9, "eps": 1e-2}, 1.0)):
+        opt = OptimConfig(optimizer=kind, optimizer_opts=opts, learning_rate=lr, weight_decay=0.0).build()
+        params = {"layer": {"kernel": torch.zeros(12, 8), "bias": torch.zeros(8)}}
+        state = opt.init(params)
+        first = None
+        for step in range(60):
+            w, b = params["layer"]["kernel"], params["layer"]["bias"]
+            grads = {"layer": {"kernel": 2 * (w - target), "bias": 2 * (b - 1.0)}}
+            loss = float(((w - target) ** 2).sum() + ((b - 1.0) ** 2).sum())
+            first = loss if first is None else first
+            state, info = opt.update(params, grads, state, step)
+        assert loss < (0.5 if kind == "normuon" else 0.8) * first, (kind, first, loss)
+        assert int(state["count"]) == 60
+    # M3's first step: O2 is zero, so the direction is NS(beta1 g) / sqrt(beta2 g^2 + eps)
+    opt = OptimConfig(optimizer="m3", optimizer_opts={"frequency": 2, "b1": 1.0, "b2": 1.0, "eps": 1e-8}, learning_rate=1.0, weight_decay=0.0).build()
+    params = {"w": torch.zeros(6, 4)}
+    g = torch.randn(6, 4)
+    state = opt.init(params)
+    state, _ = opt.update(params, {"w": g}, state, 0)
+    assert torch.allclose(params["w"], -newton_schulz(g) / torch.sqrt(g * g + 1e-8), atol=1e-5)
+    assert float(state["slow"]["w"].abs().sum()) == 0.0 and torch.allclose(state["chunk"]["w"], g)
+    state, _ = opt.update(params, {"w": g}, state, 1)            # the chunk closes: slow momentum and its direction appear
+    assert torch.allclose(state["slow"]["w"], 0.9 * 2 * g, atol=1e-6) and float(state["chunk"]["w"].abs().sum()) == 0.0
+    assert float(state["slow_direction"]["w"].abs().sum()) > 0
