@@ -30,6 +30,24 @@ class SelfAttention(nn.Module):
         self.q_norm = RMSNorm(self.head_dim, norm_eps, dtype=dtype, device=device) if qk_norm else None
         self.k_norm = RMSNorm(self.head_dim, norm_eps, dtype=dtype, device=device) if qk_norm else None
         self.sinks = declare(nn.Parameter(torch.zeros(num_heads, dtype=dtype, device=device)), ("heads",), "sinks") if sinks else None
+        self.track_qk_max = False      # set by dew_b200.optim.qk_clip.watch: record each head's largest attention logit
+        self.qk_max: Optional[torch.Tensor] = None
+
+    @torch.no_grad()
+    def _record_qk_max(self, q, k):
+        """Per query head, the largest visible logit ``scale * q . k`` of this call (exact, computed in key blocks)."""
+        B, S, H, D = q.shape
+        T, Hkv = k.shape[1], k.shape[2]
+        qf = q.float().reshape(B, S, Hkv, H // Hkv, D)
+        best = torch.full((H,), float("-inf"), device=q.device)
+        qi = torch.arange(S, device=q.device)[:, None] + (T - S)
+        for t0 in range(0, T, 1024):
+            kb = k[:, t0:t0 + 1024].float()
+            s = torch.einsum("bsgrd,btgd->bgrst", qf, kb) * (D ** -0.5)
+            if self.causal:
+                s = s.masked_fill(~(torch.arange(t0, t0 + kb.shape[1], device=q.device)[None, :] <= qi), float("-inf"))
+            best = torch.maximum(best, s.amax((0, 3, 4)).reshape(H))
+        self.qk_max = best if self.qk_max is None else torch.maximum(self.qk_max, best)
 
     def project(self, x, cos=None, sin=None, positions=None):
         B, S, _ = x.shape
@@ -46,13 +64,15 @@ class SelfAttention(nn.Module):
     def forward(self, x, cos=None, sin=None, positions=None, segment_ids=None, cache=None, layer: int = 0):
         B, S, _ = x.shape
         if (cache is None and x.is_cuda and self.q_norm is None and self.window is None and not self.softcap
-                and self.sinks is None and segment_ids is None):
+                and self.sinks is None and segment_ids is None and not self.track_qk_max):
             from ..ops.attn import packed_attention
             H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
             o = packed_attention(self.qkv_proj(x).view(B, S, H + 2 * Hkv, D), cos, sin, positions, H, Hkv, self.causal)
             if o is not None:
                 return self.o_proj(o.reshape(B, S, H * D))
         q, k, v = self.project(x, cos, sin, positions)
+        if self.track_qk_max and cache is None and self.training:
+            self._record_qk_max(q, k)
         if cache is not None:
             o = cache.attend(layer, q, k, v, positions, causal=self.causal, window=self.window, softcap=self.softcap,
                              sinks=self.sinks)

@@ -296,3 +296,37 @@ def test_normuon_and_m3_optimizers_reduce_a_quadratic_and_keep_their_rules():
     state, _ = opt.update(params, {"w": g}, state, 1)            # the chunk closes: slow momentum and its direction appear
     assert torch.allclose(state["slow"]["w"], 0.9 * 2 * g, atol=1e-6) and float(state["chunk"]["w"].abs().sum()) == 0.0
     assert float(state["slow_direction"]["w"].abs().sum()) > 0
+
+
+def test_qk_clip_bounds_the_logits_of_exceeding_groups_only():
+    import torch
+    from dew_b200.nn.attention import SelfAttention
+    from dew_b200.optim.qk_clip import qk_clip, watch
+    torch.manual_seed(0)
+    layer = SelfAttention(32, num_heads=4, num_kv_heads=2, head_dim=8, causal=True).train()
+    with torch.no_grad():
+        w = layer.qkv_proj.weight.view(8, 8, 32)
+        w[0:2] *= 12.0                      # the query heads of group 0 run hot
+        w[4] *= 12.0                        # and so does their key head
+    assert watch(layer) == 1
+    x = torch.randn(2, 24, 32)
+    layer(x)
+    before = layer.qk_max.clone()
+    assert before.shape == (4,) and float(before[:2].max()) > 10 > float(before[2:].max())
+    # exact: against the dense logits
+    q, k, _ = layer.project(x)
+    s = torch.einsum("bshd,bthd->bhst", q.float(), k.float().repeat_interleave(2, 2)) / 8 ** 0.5
+    s = s.masked_fill(~torch.tril(torch.ones(24, 24, dtype=torch.bool)), float("-inf"))
+    assert torch.allclose(before, s.amax((0, 2, 3)), atol=1e-4)
+    kept = layer.qkv_proj.weight.detach().clone()
+    seen = qk_clip(layer, tau=10.0)
+    assert torch.equal(next(iter(seen.values())), before) and layer.qk_max is None
+    w2 = layer.qkv_proj.weight.view(8, 8, 32)
+    assert torch.equal(w2[2:4], kept.view(8, 8, 32)[2:4]) and torch.equal(w2[5:], kept.view(8, 8, 32)[5:])     # group 1 and V untouched
+    layer(x)
+    after = layer.qk_max
+    assert float(after[:2].max()) <= 10.0 + 1e-3 and torch.allclose(after[2:], before[2:], atol=1e-5)
+    qk_clip(layer, tau=10.0)
+    watch(layer, False)
+    layer(x)
+    assert layer.qk_max is None
