@@ -291,7 +291,7 @@ def main() -> None:
                        "parallelism": f"fsdp{world}" + (f"+ep{world} ({args.ep} exchange)" if args.config == "moe" else ""),
                        "optimizer": "AdamW fp32 masters+moments",
                        "l2": "inputs larger than L2 (16 GB of weights stream every microbatch)",
-                       "baseline": "BASELINE.md reference-equivalent mark 190K tok/s at 8xB200, scaled per GPU"},
+                       "baseline": "reference-equivalent mark 190K tok/s at 8xB200, scaled per GPU"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "loss": loss, "mfu_datasheet": mfu,
             "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9, "impl": "dew_b200",
         }
