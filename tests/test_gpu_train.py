@@ -88,3 +88,27 @@ def test_server_with_cuda_graph_matches_offline_generation():
         # per-request ones: a flipped argmax changes the rest of that request.  Corrupted KV pages or positions would
         # break most requests, so demand that most agree in full and that the total stays high.
         assert whole >= len(prompts) - 2 and agree >= 0.7 * 8 * len(prompts), (graph, agree, whole)
+
+
+def test_host_banks_stream_layers_on_a_side_stream():
+    """Layer weights in pinned host memory, two device slots, copies on a side stream: same logits as the resident model,
+    over several calls in a row (the wrap-around prefetch), and only two layers' worth of weights on the device."""
+    from dew_b200.inference.banks import HostBanks
+    from dew_b200.models import CausalTransformer
+    torch.manual_seed(0)
+    model = CausalTransformer(vocab_size=512, emb_features=256, num_layers=6, num_heads=4, num_kv_heads=2, head_dim=64, mlp_features=512,
+                              max_seq_len=256, qk_norm=False).to("cuda", torch.bfloat16).eval()
+    tokens = torch.randint(0, 512, (2, 128), device="cuda")
+    with torch.no_grad():
+        want = model(tokens).float()
+    banks = HostBanks(model.layers, "cuda", slots=2)
+    assert banks.slots == 2 and all(t.is_pinned() for t in banks.host[0].values())
+    with torch.no_grad():
+        outs = [model(tokens).float() for _ in range(3)]
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o, want)
+    assert banks.copies == 2 + 3 * 6
+    banks.release()
+    with torch.no_grad():
+        assert torch.equal(model(tokens).float(), want)

@@ -101,3 +101,36 @@ def _unflat(flat):
             node = node.setdefault(k, {})
         node[path[-1]] = v
     return {"params": root}
+
+
+def test_host_banks_stream_layers_and_reproduce_the_resident_model():
+    import torch
+    from dew_b200.inference.banks import HostBanks
+    from dew_b200.models import CausalTransformer
+    from dew_b200.sampling.text import Sampling, generate
+    torch.manual_seed(0)
+    model = CausalTransformer(vocab_size=64, emb_features=32, num_layers=6, num_heads=2, num_kv_heads=2, head_dim=16, mlp_features=48, max_seq_len=32).eval()
+    tokens = torch.randint(0, 64, (2, 12))
+    with torch.no_grad():
+        want = model(tokens)
+        text = generate(model, None, [[1, 2, 3]], 6, sampling=Sampling(temperature=0.0)).tokens
+    banks = HostBanks(model.layers, "cpu", slots=4)           # 4 does not divide 6 layers: falls back to 3 slots
+    assert banks.slots == 3 and banks.host_bytes() == 2 * banks.device_bytes()
+    assert all(p.numel() == 0 for p in model.layers[0].parameters())           # nothing of a layer stays on the device between uses
+    with torch.no_grad():
+        got = model(tokens)
+        again = model(tokens)
+        text2 = generate(model, None, [[1, 2, 3]], 6, sampling=Sampling(temperature=0.0)).tokens
+    assert torch.equal(got, want) and torch.equal(again, want) and torch.equal(text2, text)
+    assert banks.copies >= 12                                  # every call streams every layer
+    # a reload of one layer's host weights changes the output; releasing restores ordinary parameters
+    banks.load(2, {n: torch.zeros_like(t) for n, t in banks.host[2].items()})
+    with torch.no_grad():
+        assert not torch.equal(model(tokens), want)
+    banks.release()
+    assert all(p.numel() > 0 for p in model.layers[5].parameters())
+    import pytest
+    mixed = CausalTransformer(vocab_size=64, emb_features=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16, mlp_features=48, max_seq_len=32,
+                              layer_types=("mamba2", "attention"), mixer_options=dict(state_dim=16, head_dim=16))
+    with pytest.raises(ValueError):
+        HostBanks(mixed.layers, "cpu")
