@@ -330,3 +330,34 @@ def test_qk_clip_bounds_the_logits_of_exceeding_groups_only():
     watch(layer, False)
     layer(x)
     assert layer.qk_max is None
+
+
+def test_harness_adapter_scores_and_generates():
+    import torch
+    from types import SimpleNamespace
+    from dew_b200.data import ByteTokenizer
+    from dew_b200.eval.harness import HarnessModel
+    from dew_b200.inference.scoring import score
+    from dew_b200.models import CausalTransformer
+    torch.manual_seed(0)
+    model = CausalTransformer(vocab_size=259, emb_features=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16, mlp_features=48, max_seq_len=64).eval()
+    lm = HarnessModel(model, ByteTokenizer(), max_length=48, batch_size=4, max_gen_tokens=8)
+    reqs = [SimpleNamespace(args=("The sky is ", "blue")), SimpleNamespace(args=("The sky is ", "green")), ("", "x")]
+    res = lm.loglikelihood(reqs)
+    assert len(res) == 3 and all(lp < 0 and isinstance(g, bool) for lp, g in res)
+    # the context's trailing space travels with the continuation; the numbers equal a direct scoring call
+    direct = score(model, [list(b"The sky is")], [list(b" blue")])[0]
+    assert abs(res[0][0] - direct[0]) < 1e-4
+    # rolling: a document longer than the window equals the sum of its windows
+    doc = "abcdefghij" * 12
+    rolled = lm.loglikelihood_rolling([SimpleNamespace(args=(doc,))])[0]
+    ids = list(doc.encode())
+    want, prev = 0.0, 257
+    rest = ids
+    for lo in range(0, len(rest), 47):
+        win = rest[lo:lo + 47]
+        want += score(model, [[prev]], [win], batch=1)[0][0]
+        prev = win[-1]
+    assert abs(rolled - want) < 1e-3 and rolled < 0
+    outs = lm.generate_until([SimpleNamespace(args=("hello", {"until": ["\n"], "max_gen_toks": 6}))])
+    assert len(outs) == 1 and isinstance(outs[0], str) and "\n" not in outs[0]
