@@ -82,7 +82,8 @@ class ObjectiveConfig:
 
 @dataclass
 class DataConfig:
-    source: str = "synthetic"          # synthetic | token_files | memory
+    source: str = "synthetic"          # synthetic (token ids) | synthetic_images | token_files
+    image_shape: Tuple[int, int, int] = (32, 32, 3)
     path: Optional[str] = None
     batch: int = 8
     seq_len: int = 128
@@ -228,7 +229,12 @@ def build(config: RunConfig, device=None):
         objective = LMObjective(model, dc.seq_len, tokenizer=tokenizer, **config.objective.options)
     elif config.objective.name == "diffusion":
         from ..objectives.diffusion import DiffusionObjective
-        objective = DiffusionObjective(model, **config.objective.options)
+        from .. import Field, InputSpec
+        from ..diffusion import presets
+        opts = dict(config.objective.options)
+        process = opts.pop("process", "edm")
+        process = {"edm": presets.EDM(regime="pixel"), "flow": presets.Flow()}[process] if isinstance(process, str) else process
+        objective = DiffusionObjective(model, process, InputSpec(Field("sample", tuple(dc.image_shape))), **opts)
     else:
         objective = lookup(config.objective.name, "objective")(model, **config.objective.options)
     ckpt = None
@@ -247,8 +253,12 @@ def build(config: RunConfig, device=None):
         rows = torch.randint(0, vocab, (max(64, dc.batch * 8), dc.seq_len + 1), generator=g)
         dataset = D.Memory({"tokens": rows}).shuffle(dc.seed).repeat().batched(dc.batch)
         dataset.seq_len = dc.seq_len
+    elif dc.source == "synthetic_images":
+        g = torch.Generator().manual_seed(dc.seed)
+        images = torch.rand(max(64, dc.batch * 8), *dc.image_shape, generator=g) * 2 - 1
+        dataset = D.Memory({"sample": images}).shuffle(dc.seed).repeat().batched(dc.batch)
     elif dc.source == "token_files":
         dataset = D.TokenFiles(dc.path).shuffle(dc.seed).repeat().pipe(D.presets.token_windows, seq_len=dc.seq_len, batch=dc.batch).workers(dc.workers)
     else:
-        raise ValueError(f"unknown data source {dc.source!r}; known: synthetic, token_files")
+        raise ValueError(f"unknown data source {dc.source!r}; known: synthetic, synthetic_images, token_files")
     return trainer, dataset

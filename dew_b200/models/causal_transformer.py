@@ -11,7 +11,7 @@ normalised value).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from typing import Mapping, Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.nn as nn
@@ -72,6 +72,10 @@ class TransformerConfig:
     mtp_depth: int = 0                                # multi-token prediction: extra sequential heads for tokens t+2, t+3, ...
     hyper_connections: int = 0                        # n > 1: n residual streams with learned read / write weights per sub-layer
     altup: int = 0                                    # K > 1: AltUp - K blocks, one of which every sub-layer computes on
+
+    def __post_init__(self):
+        if isinstance(self.mixture, Mapping):             # a run record (JSON) carries the mixture as a plain mapping
+            self.mixture = Mixture(**self.mixture)
 
     def kinds(self) -> List[str]:
         if self.layer_types is None:

@@ -52,3 +52,23 @@ def test_cli_inspect_reports_placement(tmp_path, capsys):
     rep = json.loads(capsys.readouterr().out)
     assert rep["mesh"]["fsdp"] == 8 and rep["fits"]
     assert cli.main(["launch", "--dry-run", "--processes-per-host", "2", "--", "python", "x.py"]) == 0
+
+
+@pytest.mark.parametrize("recipe,shrink", [
+    ("lm/train.py", ["model.fields.emb_features=32", "model.fields.num_layers=1", "model.fields.num_heads=2", "model.fields.num_kv_heads=2",
+                     "model.fields.mlp_features=48", "model.fields.vocab_size=64", "model.fields.max_seq_len=16", "data.seq_len=16", "data.batch=2"]),
+    ("lm/moe.py", ["model.fields.emb_features=32", "model.fields.num_layers=1", "model.fields.num_heads=2", "model.fields.num_kv_heads=2",
+                   "model.fields.mlp_features=48", "model.fields.vocab_size=64", "model.fields.max_seq_len=16", "data.seq_len=16", "data.batch=2",
+                   "model.fields.mixture.experts=4", "model.fields.mixture.top_k=2", "model.fields.mixture.expert_features=16",
+                   "model.fields.mixture.shared_features=16"]),
+    ("diffusion/train.py", ["model.fields.emb_features=32", "model.fields.num_layers=1", "model.fields.num_heads=2", "data.image_shape=[16,16,3]", "data.batch=2"]),
+])
+def test_shipped_recipes_train_through_the_cli(recipe, shrink, tmp_path, capsys):
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "recipes", recipe)
+    args = ["train", path, "--cpu", "--set", "trainer.steps=3", "--set", f"trainer.checkpoint_dir={tmp_path / 'run'}", "--set", "trainer.log_every=1"]
+    for s in shrink:
+        args += ["--set", s]
+    assert cli.main(args) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["step"] == 3
