@@ -40,6 +40,7 @@ struct Cfg {
   static constexpr int TILE_BYTES = Q_BYTES + (KSTAGES + 2) * KV_BYTES + P_BYTES;
   static constexpr int SMEM = TILE_BYTES + 2560;      // + barriers and the row-maximum exchange (see Bars); no slack to spare
   static constexpr int TMEM_S0 = 0, TMEM_S1 = 128, TMEM_O = 256, TMEM_COLS = 512;
+  static constexpr int TMEM_QA = 384;                // PT: Q as a tensor-memory A operand (D / 2 packed columns)
 };
 
 struct Bars {
@@ -47,6 +48,7 @@ struct Bars {
   uint64_t k_full[3], k_empty[3], v_full[2], v_empty[2];
   uint64_t s_full[2], s_empty[2];
   uint64_t p_full, pv_done;
+  uint64_t qa_ready;                   // PT: Q copied to tensor memory (one arrival per softmax warp)
   uint32_t tmem_base;
   int abort_flag;
   int poisoned;
@@ -105,6 +107,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     }
     mbar_init(&bars->p_full, 8);
     mbar_init(&bars->pv_done, 1);
+    mbar_init(&bars->qa_ready, 8);
     bars->abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -142,8 +145,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     // The whole warp runs this loop and waits together; one elected lane issues (see mbar_wait_warp).
     constexpr uint32_t idesc_qk = make_idesc(BM, BN, 1, 1, 0, 0);
     constexpr uint32_t idesc_pv = make_idesc(BM, D, 1, 1, 0, 1);
-    bool ok = mbar_wait_warp(&bars->q_full, 0, abort_flag);
+    // PT: Q is the A operand of every score product of the CTA, so the softmax warps copy it once to tensor memory and
+    // the score products fetch only K from shared memory
+    bool ok = mbar_wait_warp(PT ? &bars->qa_ready : &bars->q_full, 0, abort_flag);
     if (!ok && lane == 0) atomicCAS(err, 0, ERR_WAIT_FULL);
+    tc_fence_after();
     const uint32_t qa = smem_u32(sQ), pa = smem_u32(sP);
     auto issue_qk = [&](int j) -> bool {
       const int st = j & 1; const uint32_t ph = (j >> 1) & 1;
@@ -159,7 +165,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * (BM * 128) + (kk & 3) * 32;
-          umma_bf16_ss(ts, make_sdesc_sw128(qa + off, 16, 1024), make_sdesc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+          if (PT) umma_bf16_ts(ts, tmem + C::TMEM_QA + kk * 8, make_sdesc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+          else umma_bf16_ss(ts, make_sdesc_sw128(qa + off, 16, 1024), make_sdesc_sw128(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
         }
         umma_commit(&bars->k_empty[ks]);
         umma_commit(&bars->s_full[st]);
@@ -202,6 +209,30 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
+    if (PT) {
+      // this thread's half of its query row, from the swizzled shared tile to tensor memory: lane = row, 32-bit column w
+      // = features 2w, 2w + 1 (the layout of a tensor-memory A operand)
+      const bool got = mbar_wait(&bars->q_full, 0, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) { atomicCAS(err, 0, ERR_WAIT_FULL); ok = false; }
+      if (ok) {
+        constexpr int CH16 = D / 16;                  // 16-byte chunks (8 features, 4 columns) per thread
+#pragma unroll
+        for (int g4 = 0; g4 < CH16 / 4; ++g4) {
+          uint32_t w[16];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int chunk = half * CH16 + g4 * 4 + c;         // within the row of D features
+            const uint4 x = *reinterpret_cast<const uint4*>(sQ + (chunk >> 3) * (BM * 128) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4));
+            w[c * 4] = x.x; w[c * 4 + 1] = x.y; w[c * 4 + 2] = x.z; w[c * 4 + 3] = x.w;
+          }
+          tmem_st_32x32b_x16(tmem + lane_addr + C::TMEM_QA + (half * CH16 + g4 * 4) * 4, w);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      __syncwarp();
+      if (ok && lane == 0) mbar_arrive(&bars->qa_ready);
+    }
     // Both threads of a row meet at a named barrier once per tile, so no thread may leave the loop early: after a
     // wait gives up, `ok` turns false for the whole warp and the remaining iterations only keep the barrier count.
     for (int j = 0; j < n_tiles; ++j) {
