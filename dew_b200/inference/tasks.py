@@ -37,6 +37,22 @@ class TextGeneration:
         src = self.variables if self.variables is not None else module_variables(self.model)
         return replace(self, variables=quantize_variables(src, quantization))
 
+    def offloaded(self, slots: int = 2) -> "TextGeneration":
+        """Keep the decoder layers' weights in pinned host memory and stream them through ``slots`` device-resident copies
+        while generating (``dew_b200.inference.banks.HostBanks``): for models larger than the GPU.  Bound variables are
+        written into the module first, since the banks read the module's own parameters."""
+        from .banks import HostBanks
+        if self.variables is not None:
+            from ..utils.trees import variables_for_call
+            with torch.no_grad():
+                for n, v in variables_for_call(self.model, self.variables).items():
+                    if n in dict(self.model.named_parameters()):
+                        self.model.get_parameter(n).copy_(v)
+        dev = next(self.model.parameters()).device
+        new = replace(self, variables=None)
+        new.banks = self.banks = HostBanks(self.model.layers, dev, slots)      # both tasks share the one module, so both name its banks
+        return new
+
     def score(self, tokens: torch.Tensor) -> torch.Tensor:
         """Per-token log-probabilities ``[B, S-1]`` of ``tokens`` under the model."""
         with torch.no_grad():

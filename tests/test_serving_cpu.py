@@ -134,3 +134,17 @@ def test_host_banks_stream_layers_and_reproduce_the_resident_model():
                               layer_types=("mamba2", "attention"), mixer_options=dict(state_dim=16, head_dim=16))
     with pytest.raises(ValueError):
         HostBanks(mixed.layers, "cpu")
+
+
+def test_text_generation_task_with_offloaded_layers():
+    import torch
+    from dew_b200.inference.tasks import TextGeneration
+    from dew_b200.models import CausalTransformer
+    torch.manual_seed(0)
+    model = CausalTransformer(vocab_size=64, emb_features=32, num_layers=4, num_heads=2, num_kv_heads=2, head_dim=16, mlp_features=48, max_seq_len=32).eval()
+    task = TextGeneration(model)
+    want = task([[1, 2, 3], [4, 5]], max_new_tokens=5).tokens
+    off = task.offloaded(slots=2)
+    assert torch.equal(off([[1, 2, 3], [4, 5]], max_new_tokens=5).tokens, want)
+    assert all(p.numel() == 0 for p in model.layers[1].parameters())
+    task.banks.release()
