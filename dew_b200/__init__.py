@@ -22,7 +22,7 @@ _EXPORTS = {
     "Ratio": "objectives", "Moments": "objectives", "Supervised": "objectives", "DiffusionObjective": "objectives",
     "LMObjective": "objectives", "JepaObjective": "objectives",
     "MeshSpec": "parallel.mesh", "Layout": "parallel.layout",
-    "Checkpoints": "checkpoints", "Keep": "checkpoints", "Ranking": "checkpoints",
+    "Checkpoints": "checkpoints", "CorruptCheckpoint": "checkpoints", "Keep": "checkpoints", "Ranking": "checkpoints",
     "Dataset": "data", "Memory": "data", "Loader": "data", "TokenFiles": "data", "ByteTokenizer": "data",
     "Process": "diffusion", "EDM": "diffusion", "Flow": "diffusion", "Karras": "diffusion",
     "InputSpec": "inputs", "Field": "inputs", "Condition": "inputs", "unit_range": "inputs",

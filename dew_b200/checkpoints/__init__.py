@@ -105,12 +105,25 @@ def _split_scalars(flat: Mapping[str, Any]):
     return tensors, scalars
 
 
+class CorruptCheckpoint(RuntimeError):
+    """A step whose files do not match the digests written with them."""
+
+
+def _file_sha256(path) -> str:
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        for block in iter(lambda: f.read(1 << 22), b""):
+            h.update(block)
+    return h.hexdigest()
+
+
 class Checkpoints:
     def __init__(self, directory: os.PathLike, *, keep: Union[Keep, int] = Keep.latest,
                  local_directory: Optional[os.PathLike] = None, local_every: Optional[int] = None,
                  ranking: Optional[Ranking] = None, kinds: Optional[Mapping[str, str]] = None,
-                 process_index: int = 0, process_count: int = 1):
+                 process_index: int = 0, process_count: int = 1, verify_on_read: bool = True):
         self.directory = Path(directory)
+        self.verify_on_read = verify_on_read        # check every item's file digest when it is read
         self.keep = Keep(keep) if isinstance(keep, int) else keep
         self.local_directory = Path(local_directory) if local_directory else None
         self.local_every = local_every
@@ -150,14 +163,37 @@ class Checkpoints:
         step = self.latest() if step is None else step
         return read_json(self.directory / str(step) / METADATA)
 
+    def verify(self, step: Optional[int] = None) -> Dict[str, bool]:
+        """Per item of ``step``: whether its tensor file still has the digest recorded when it was written (items written
+        before digests were recorded count as intact)."""
+        step = self.latest() if step is None else step
+        out = {}
+        root = self.directory / str(step)
+        for d in sorted(p for p in root.iterdir() if p.is_dir()):
+            meta, data = d / "_METADATA.json", d / "tree.safetensors"
+            if not meta.exists():
+                continue
+            want = read_json(meta).get("sha256")
+            out[d.name] = data.exists() and (want is None or _file_sha256(data) == want)
+        return out
+
     def resumed(self, resume: str = "auto") -> Optional[int]:
-        """The step a run resumes from under ``resume`` = 'auto' | 'require' | 'never'."""
+        """The step a run resumes from under ``resume`` = 'auto' | 'require' | 'never': the newest step whose files are
+        intact (a step cut short or damaged on disk is passed over for the one before it, with a warning)."""
         if resume == "never":
             return None
-        latest = self.latest()
-        if latest is None and resume == "require":
-            raise FileNotFoundError(f"resume='require' but {self.directory} holds no checkpoint")
-        return latest
+        for step in reversed(self.steps()):
+            try:
+                intact = all(self.verify(step).values())
+            except OSError:
+                intact = False
+            if intact:
+                return step
+            import warnings
+            warnings.warn(f"checkpoint step {step} in {self.directory} failed its integrity check; trying the step before it")
+        if resume == "require":
+            raise FileNotFoundError(f"resume='require' but {self.directory} holds no intact checkpoint")
+        return None
 
     # ------------------------------------------------------------------ run record
     def write_run(self, record: Mapping[str, Any]) -> None:
@@ -176,7 +212,7 @@ class Checkpoints:
         TS.save_file(tensors, d / "tree.safetensors")
         atomic_write_json(d / "_METADATA.json", {
             "tree": {k: {"shape": list(v.shape), "dtype": str(v.dtype)} for k, v in tensors.items()},
-            "scalars": scalars})
+            "scalars": scalars, "sha256": _file_sha256(d / "tree.safetensors")})
 
     def save(self, step: int, state: Union[TrainState, Mapping[str, Any]], saved: Optional[Mapping[str, Any]] = None,
              metrics: Optional[Mapping[str, float]] = None, *, weights_only: bool = False, rung: Any = None,
@@ -312,6 +348,10 @@ class Checkpoints:
         d = self.directory / str(step) / item
         if not d.exists():
             raise FileNotFoundError(f"step {step} holds no {item!r} item (it may have been cut to its model item)")
+        if self.verify_on_read:
+            want = read_json(d / "_METADATA.json").get("sha256")
+            if want is not None and _file_sha256(d / "tree.safetensors") != want:
+                raise CorruptCheckpoint(f"{d / 'tree.safetensors'} does not match the digest written with it")
         out: Dict[str, Any] = dict(TS.load_file(d / "tree.safetensors"))
         out.update(read_json(d / "_METADATA.json").get("scalars", {}))
         return out

@@ -71,3 +71,38 @@ def test_pause_ends_the_run_at_a_fraction_and_a_resume_goes_on(tmp_path):
     assert state.step == 4
     state = trainer().fit(list(data), steps=8, log_every=1000)               # resumes from the pause's checkpoint
     assert state.step == 8
+
+
+def test_checkpoint_integrity_passes_over_a_damaged_step(tmp_path):
+    import warnings
+    import dew_b200 as dew
+    from dew_b200.checkpoints import CorruptCheckpoint
+    from dew_b200.models import CausalTransformer
+    from dew_b200.objectives.lm import LMObjective
+
+    def trainer():
+        torch.manual_seed(0)
+        m = CausalTransformer(vocab_size=32, emb_features=16, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=8, mlp_features=24, max_seq_len=8)
+        return dew.Trainer(LMObjective(m, 8, ema_decay=None), dew.OptimConfig(learning_rate=1e-2), key=0,
+                           checkpoints=dew.Checkpoints(str(tmp_path / "run"), keep=3))
+    g = torch.Generator().manual_seed(0)
+    data = [{"tokens": torch.randint(0, 32, (2, 9), generator=g)} for _ in range(6)]
+    t = trainer()
+    t.fit(list(data), steps=6, checkpoint_every=2, log_every=1000)
+    ck = t.checkpoints
+    ck.wait()
+    assert ck.steps() == [2, 4, 6] and all(ck.verify(6).values()) and ck.resumed() == 6
+    # damage the newest step's model file: flip a byte in the middle
+    victim = next((tmp_path / "run" / "6").glob("*/tree.safetensors"))
+    raw = bytearray(victim.read_bytes())
+    raw[len(raw) // 2] ^= 0xFF
+    victim.write_bytes(bytes(raw))
+    assert not all(ck.verify(6).values())
+    with pytest.raises(CorruptCheckpoint):
+        ck.restore(None, 6)
+    with warnings.catch_warnings(record=True) as caught:
+        warnings.simplefilter("always")
+        assert ck.resumed() == 4
+    assert any("integrity" in str(w.message) for w in caught)
+    state = trainer().fit(list(data), steps=6, log_every=1000)        # resumes from step 4, not the damaged 6
+    assert state.step == 6
