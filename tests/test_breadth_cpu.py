@@ -361,3 +361,44 @@ def test_harness_adapter_scores_and_generates():
     assert abs(rolled - want) < 1e-3 and rolled < 0
     outs = lm.generate_until([SimpleNamespace(args=("hello", {"until": ["\n"], "max_gen_toks": 6}))])
     assert len(outs) == 1 and isinstance(outs[0], str) and "\n" not in outs[0]
+
+
+def test_categorical_functions_against_direct_forms():
+    import torch
+    import torch.nn.functional as F
+    from dew_b200.nn import categorical as C
+    torch.manual_seed(0)
+    logits, ref = torch.randn(5, 7), torch.randn(5, 7)
+    labels = torch.randint(0, 7, (5,))
+    assert torch.allclose(C.cross_entropy(logits, labels), F.cross_entropy(logits, labels, reduction="none"), atol=1e-6)
+    t = torch.softmax(torch.randn(5, 7), -1)
+    assert torch.allclose(C.soft_cross_entropy(logits, t), -(t * torch.log_softmax(logits, -1)).sum(-1), atol=1e-6)
+    p = torch.softmax(logits, -1)
+    assert torch.allclose(C.entropy(logits), -(p * p.log()).sum(-1), atol=1e-6)
+    assert torch.allclose(C.kl_divergence(logits, ref), F.kl_div(torch.log_softmax(ref, -1), p, reduction="none").sum(-1), atol=1e-6)
+    assert float(C.kl_divergence(logits, logits).abs().max()) < 1e-7
+    # masked classes take no probability and add no term; bf16 inputs are widened
+    where = torch.tensor([True, True, False, True, True, True, False])
+    lp = C.log_probs(logits.bfloat16(), where)
+    assert lp.dtype == torch.float32 and torch.isinf(lp[:, 2]).all() and torch.allclose(lp.exp().sum(-1), torch.ones(5), atol=1e-5)
+    assert torch.isfinite(C.entropy(logits, where)).all() and torch.isfinite(C.kl_divergence(logits, ref, where)).all()
+    sm = C.smoothed(F.one_hot(labels, 7).float(), 0.1, where)
+    assert torch.allclose(sm.sum(-1), torch.ones(5)) and float(sm[:, 2].abs().max()) <= 0.9 * 1.0 and torch.all(sm[labels != 2][:, 2] == 0)
+    onehot = F.one_hot(labels, 7).float()
+    assert torch.allclose(C.brier(logits, onehot), ((p - onehot) ** 2).sum(-1), atol=1e-6)
+    assert torch.all(C.spherical(logits, onehot) >= 0) and torch.all(C.ranked_probability(logits, onehot) >= 0)
+    assert float(C.ranked_probability(torch.log(onehot + 1e-9) * 50, onehot).max()) < 1e-6
+    same = logits[:, None].expand(5, 3, 7)
+    assert float(C.group_divergence(same).abs().max()) < 1e-6 and float(C.group_divergence(torch.randn(5, 3, 7)).min()) > 0
+    # the block-wise partition equals the whole one
+    big = torch.randn(4, 50) * 5
+    run = None
+    for lo in range(0, 50, 16):
+        run = C.rescaled(run, big[:, lo:lo + 16])
+    assert torch.allclose(C.log_partition(run), torch.logsumexp(big, -1), atol=1e-5)
+    lab = torch.randint(0, 50, (4,))
+    assert torch.allclose(C.target_loss(run, big.gather(-1, lab[:, None])[:, 0]), F.cross_entropy(big, lab, reduction="none"), atol=1e-5)
+    seg = torch.tensor([0, 0, 2, 2, 2, 3])
+    x = torch.randn(6)
+    out = C.segment_log_partition(x, seg, 4)
+    assert torch.allclose(out[0], torch.logsumexp(x[:2], 0)) and torch.allclose(out[2], torch.logsumexp(x[2:5], 0)) and out[1] == float("-inf")
