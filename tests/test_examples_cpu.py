@@ -64,3 +64,19 @@ def test_sample_text_to_image_example():
 
 def test_train_supervised_example():
     assert _load("train_supervised").main(["--steps", "300", "--device", "cpu"]) > 0.7
+
+
+def test_pinn_burgers_example_and_gauss_newton_on_a_linear_system():
+    import torch
+    from dew_b200.optim.gauss_newton import LevenbergMarquardt, gauss_newton_direction
+    # on a linear least-squares problem one undamped step lands on the solution, primal and dual alike
+    torch.manual_seed(0)
+    A, b = torch.randn(12, 4, dtype=torch.float64), torch.randn(12, dtype=torch.float64)
+    x = torch.zeros(4, dtype=torch.float64)
+    step = gauss_newton_direction(A @ x - b, A, 1e-12)
+    assert torch.allclose(x - step, torch.linalg.lstsq(A, b[:, None]).solution[:, 0], atol=1e-8)
+    wide = torch.randn(3, 7, dtype=torch.float64)
+    d = gauss_newton_direction(wide @ torch.zeros(7, dtype=torch.float64) - b[:3], wide, 1e-12)
+    assert torch.allclose(wide @ (-d), b[:3], atol=1e-8)                     # the dual solve satisfies every residual
+    history = _load("pinn_burgers").main(["--steps", "12"])
+    assert history[-1] < 0.05 * history[0]
