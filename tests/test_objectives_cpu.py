@@ -260,3 +260,37 @@ def test_fit_cooldown_summaries_loss_role_and_preview():
     with pytest.raises(NotImplementedError):
         LMObjective(model, 8, exit_entropy=0.1)
     assert dew.Cooldown(0, 10, 0.0, "sqrt").factor(10) == 0.0 and dew.Cooldown(5, 10).factor(3) == 1.0
+
+
+def test_node_perturbation_estimates_the_gradient_and_trains_without_backprop():
+    import torch
+    import dew_b200 as dew
+    from dew_b200.models import CausalTransformer
+    from dew_b200.objectives import Step
+    from dew_b200.objectives.lm import LMObjective
+    from dew_b200.objectives.perturbation import NodePerturbation
+    torch.manual_seed(0)
+    model = CausalTransformer(vocab_size=32, emb_features=32, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=16, mlp_features=48, max_seq_len=16,
+                              tie_embeddings=False)
+    tokens = torch.randint(0, 32, (8, 17))
+    # the true gradient of the head
+    model.zero_grad()
+    stat, _ = LMObjective(model, 16, ema_decay=None).loss(None, {"tokens": tokens}, Step(key=0, train=True))
+    (stat.total / stat.mass).backward()
+    true = model.head.weight.grad.clone()
+    est = torch.zeros_like(true)
+    obj = NodePerturbation(model, 16, sigma=1e-2, draws=16)
+    for k in range(8):
+        model.zero_grad()
+        s, aux = obj.loss(None, {"tokens": tokens}, Step(key=k, train=True))
+        assert abs(float(s.total / s.mass) - float(stat.total / stat.mass)) < 1e-4          # the value is the clean loss
+        (s.total / s.mass).backward()
+        est += model.head.weight.grad
+    cos = float((est * true).sum() / (est.norm() * true.norm()))
+    assert cos > 0.15, cos                     # a noisy but aligned estimate (every node is jittered at once)
+    # a few hundred forward-only steps lower the loss on a fixed batch
+    trainer = dew.Trainer(NodePerturbation(model, 16, sigma=1e-2, draws=4), dew.OptimConfig(learning_rate=3e-3, weight_decay=0.0), key=0,
+                          tracker=dew.MemoryTracker())
+    trainer.fit([{"tokens": tokens}] * 120, steps=120, log_every=20)
+    losses = [r["loss"] for r in trainer.tracker.rows if "loss" in r]
+    assert losses[-1] < losses[0] - 0.1, losses
