@@ -80,3 +80,10 @@ def test_pinn_burgers_example_and_gauss_newton_on_a_linear_system():
     assert torch.allclose(wide @ (-d), b[:3], atol=1e-8)                     # the dual solve satisfies every residual
     history = _load("pinn_burgers").main(["--steps", "12"])
     assert history[-1] < 0.05 * history[0]
+
+
+def test_route_decisions_example():
+    report = _load("route_decisions").main(["--steps", "200"])
+    assert set(report) == {"parity", "half", "multiple_of_five"}
+    assert report["half"]["accuracy"] > 0.85 and report["parity"]["accuracy"] > 0.85
+    assert all(0.0 <= r["answered"] <= 1.0 for r in report.values())
