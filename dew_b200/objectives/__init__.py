@@ -17,6 +17,9 @@ def __getattr__(name):
     if name in ("Alignment", "AlignedDiffusionObjective", "GuidanceDistillationObjective", "Projector", "spatial_zscore"):
         from . import diffusion_extras
         return getattr(diffusion_extras, name)
+    if name == "EndToEndObjective":
+        from .end_to_end import EndToEndObjective
+        return EndToEndObjective
     if name == "NodePerturbation":
         from .perturbation import NodePerturbation
         return NodePerturbation

@@ -108,3 +108,42 @@ def test_guidance_distillation_matches_the_guided_teacher():
     assert torch.allclose(guide(c, u, torch.tensor([1.0, 0.0, 2.0])), torch.stack([c[0], u[1], u[2] + 2 * (c[2] - u[2])]))
     with pytest.raises(ValueError):
         GuidanceDistillationObjective(_dit(), presets.Flow(), InputSpec(Field("sample", (16, 16, 3))))
+
+
+def test_end_to_end_objective_routes_each_gradient_to_its_part():
+    from dew_b200.models.autoencoders import KLAutoEncoder
+    from dew_b200.objectives.end_to_end import EndToEndObjective
+    torch.manual_seed(0)
+    vae = KLAutoEncoder(channels=3, latent_channels=4, features=8, downsample=1, scale=1.0)
+    dit = SimpleDiT(patch_size=2, emb_features=32, num_layers=2, num_heads=2, input_channels=4, output_channels=4)
+    al = Alignment(layer="blocks.0", encoder=lambda px: _patch_means(px), projector="mlp", width=16, resolution=None)
+    obj = EndToEndObjective(dit, vae, presets.Flow(), InputSpec(Field("sample", (8, 8, 4))), alignment=al, hidden_features=32, encoder_features=6,
+                            vae_align=1.5, kl_weight=1e-4, ema_decay=None)
+    batch = {"sample": torch.rand(4, 16, 16, 3) * 2 - 1}
+    v = obj.init(0)
+    stat, aux = obj.loss(v, batch, Step(key=2, train=True))
+    assert {"denoising", "reconstruction", "alignment", "latent_alignment", "latent_std"} <= set(aux.metrics)
+    (stat.total / stat.mass).backward()
+    named = dict(obj.model.named_parameters())
+    g = lambda prefix: sum(float(p.grad.abs().sum()) for n, p in named.items() if n.startswith(prefix) and p.grad is not None)
+    assert g("autoencoder.encoder") > 0 and g("autoencoder.decoder") > 0 and g("denoiser.backbone") > 0 and g("denoiser.alignment_projector") > 0
+    # the denoising loss does not reach the encoder: with the latent's alignment term off and the reconstruction term
+    # cancelled, the encoder's gradient is exactly zero although the diffusion model still trains
+    obj.model.zero_grad()
+    cancel = lambda recon, images: -(recon - images).abs().reshape(images.shape[0], -1).mean(1)
+    obj2 = EndToEndObjective(dit, vae, presets.Flow(), InputSpec(Field("sample", (8, 8, 4))), alignment=al, hidden_features=32, encoder_features=6,
+                             vae_align=0.0, kl_weight=0.0, extra_vae_loss=cancel, ema_decay=None)
+    s2, _ = obj2.loss(None, batch, Step(key=2, train=True))
+    (s2.total / s2.mass).backward()
+    named2 = dict(obj2.model.named_parameters())
+    assert all(p.grad is None or float(p.grad.abs().sum()) < 1e-10 for n, p in named2.items() if n.startswith("autoencoder.encoder"))
+    assert any(p.grad is not None and float(p.grad.abs().sum()) > 0 for n, p in named2.items() if n.startswith("denoiser.backbone"))
+    obj2.model.zero_grad()
+    # a few steps train all parts
+    trainer = dew.Trainer(obj, dew.OptimConfig(learning_rate=1e-3), key=0)
+    before = {n: p.detach().clone() for n, p in obj.model.named_parameters()}
+    trainer.fit([batch] * 4, steps=4)
+    moved = {n.split(".")[0] + "." + n.split(".")[1] for n, p in obj.model.named_parameters() if not torch.equal(p, before[n])}
+    assert {"autoencoder.encoder", "autoencoder.decoder", "denoiser.backbone", "denoiser.alignment_projector"} <= moved
+    x = obj.generate(None, (2, 8, 8, 4), key=1, steps=3)
+    assert x.shape == (2, 16, 16, 3)
