@@ -294,3 +294,46 @@ def test_node_perturbation_estimates_the_gradient_and_trains_without_backprop():
     trainer.fit([{"tokens": tokens}] * 120, steps=120, log_every=20)
     losses = [r["loss"] for r in trainer.tracker.rows if "loss" in r]
     assert losses[-1] < losses[0] - 0.1, losses
+
+
+def test_adaptive_lm_objective_steps_a_level_in_context():
+    import torch
+    import dew_b200 as dew
+    from dew_b200.models import CausalTransformer
+    from dew_b200.objectives import Step
+    from dew_b200.objectives.adaptation import AdaptiveLMObjective, ChunkAdaptation, Continuum
+    from dew_b200.objectives.lm import LMObjective
+    torch.manual_seed(0)
+    model = CausalTransformer(vocab_size=32, emb_features=32, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=16, mlp_features=48, max_seq_len=32,
+                              tie_embeddings=False)
+    tokens = torch.randint(0, 32, (3, 33))
+    plain, _ = LMObjective(model, 32, ema_decay=None).loss(None, {"tokens": tokens}, Step(key=0, train=True))
+    # the level starts as the identity, and a single window takes no step: the loss is the model's own
+    obj = AdaptiveLMObjective(model, 32, ChunkAdaptation(window=32, rate=0.1))
+    one, aux = obj.loss(None, {"tokens": tokens}, Step(key=0, train=True))
+    assert torch.allclose(one.total / one.mass, plain.total / plain.mass, atol=1e-5) and float(aux.metrics["level_step"].value()) == 0.0
+    # windows of 8: later windows read a stepped level, so the loss differs, and the start gets a (meta-)gradient
+    obj8 = AdaptiveLMObjective(model, 32, ChunkAdaptation(window=8, rate=0.5))
+    with torch.no_grad():
+        obj8.model.continuum.up.normal_(0, 0.05)
+    s8, a8 = obj8.loss(None, {"tokens": tokens}, Step(key=0, train=True))
+    assert float(a8.metrics["level_step"].value()) > 0
+    (s8.total / s8.mass).backward()
+    assert obj8.model.continuum.down.grad is not None and float(obj8.model.continuum.down.grad.abs().sum()) > 0
+    full = obj8.model.continuum.down.grad.clone()
+    obj8.model.zero_grad()
+    first = AdaptiveLMObjective(model, 32, ChunkAdaptation(window=8, rate=0.5, first_order=True))
+    first.model.continuum.load_state_dict(obj8.model.continuum.state_dict())
+    sf, _ = first.loss(None, {"tokens": tokens}, Step(key=0, train=True))
+    assert torch.allclose(sf.total, s8.total, atol=1e-5)                       # same forward ...
+    (sf.total / sf.mass).backward()
+    assert not torch.allclose(first.model.continuum.down.grad, full, atol=1e-7)   # ... different gradient without the meta term
+    # adapting in context helps on rows that repeat themselves: after training, the stepped level beats the frozen one
+    rep = torch.randint(0, 32, (16, 8)).repeat(1, 5)[:, :33]
+    trainer = dew.Trainer(obj8, dew.OptimConfig(learning_rate=3e-3, weight_decay=0.0), key=0, tracker=dew.MemoryTracker())
+    trainer.fit([{"tokens": rep}] * 40, steps=40, log_every=10)
+    losses = [r["loss"] for r in trainer.tracker.rows if "loss" in r]
+    assert losses[-1] < losses[0]
+    lvl = Continuum(4, 6)
+    x = torch.randn(2, 3, 4)
+    assert torch.equal(lvl(x), x)
