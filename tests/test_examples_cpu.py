@@ -87,3 +87,8 @@ def test_route_decisions_example():
     assert set(report) == {"parity", "half", "multiple_of_five"}
     assert report["half"]["accuracy"] > 0.85 and report["parity"]["accuracy"] > 0.85
     assert all(0.0 <= r["answered"] <= 1.0 for r in report.values())
+
+
+def test_sft_chat_example():
+    losses, right, answers = _load("sft_chat").main(["--steps", "150", "--device", "cpu"])
+    assert losses[-1] < 0.5 * losses[0] and right >= 3 and set(answers) == {"red", "green", "blue", "pink", "grey", "gold"}
