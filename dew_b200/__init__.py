@@ -17,7 +17,7 @@ _EXPORTS = {
     "Trainer": "training", "TrainState": "training", "Cooldown": "training", "Best": "training", "Plateau": "training", "Pause": "training",
     "Evaluation": "training", "ProfileWindow": "training", "Tracker": "training", "LocalTracker": "training",
     "WandbTracker": "training", "Wandb": "training", "MLflowTracker": "training", "TensorBoardTracker": "training",
-    "Trackers": "training", "MemoryTracker": "training",
+    "Trackers": "training", "MemoryTracker": "training", "ConsoleTracker": "training",
     "Step": "objectives", "Aux": "objectives", "EMASpec": "objectives", "Objective": "objectives", "Mean": "objectives",
     "Ratio": "objectives", "Moments": "objectives", "Supervised": "objectives", "DiffusionObjective": "objectives",
     "LMObjective": "objectives", "JepaObjective": "objectives",

@@ -1,7 +1,7 @@
 from .state import CHECKPOINTED, MODEL_STATE, TrainState
-from .tracker import LocalTracker, MemoryTracker, MLflowTracker, TensorBoardTracker, Tracker, Trackers, Wandb, WandbTracker
+from .tracker import ConsoleTracker, LocalTracker, MemoryTracker, MLflowTracker, TensorBoardTracker, Tracker, Trackers, Wandb, WandbTracker
 from .trainer import Best, Cooldown, Evaluation, Pause, Plateau, Preempted, ProfileWindow, Trainer
 
 __all__ = ["Cooldown", "Trainer", "TrainState", "Best", "Plateau", "Pause", "Evaluation", "ProfileWindow", "Preempted", "Tracker",
-           "LocalTracker", "MemoryTracker", "WandbTracker", "Wandb", "MLflowTracker", "TensorBoardTracker", "Trackers",
+           "LocalTracker", "ConsoleTracker", "MemoryTracker", "WandbTracker", "Wandb", "MLflowTracker", "TensorBoardTracker", "Trackers",
            "CHECKPOINTED", "MODEL_STATE"]

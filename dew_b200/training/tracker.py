@@ -167,6 +167,56 @@ class TensorBoardTracker:
             self._writer.close()
 
 
+class ConsoleTracker:
+    """One compact line per logged step on a stream: the step (of ``steps`` when known), the chosen scalars, the rate of the
+    ``rate_key`` metric per second since the previous line, and an estimate of the time left.
+    Reference: src/dew/training/display.py (the run's console display)."""
+
+    def __init__(self, steps: Optional[int] = None, keys: Sequence[str] = ("loss", "learning_rate", "grad_norm"), rate_key: str = "tokens",
+                 stream=None, clock=time.monotonic):
+        import sys
+        self.steps, self.keys, self.rate_key = steps, tuple(keys), rate_key
+        self.stream = stream if stream is not None else sys.stderr
+        self.clock = clock
+        self._last = None               # (time, step)
+        self._first = None
+
+    @staticmethod
+    def _fmt(v) -> str:
+        if isinstance(v, float):
+            return f"{v:.3e}" if (abs(v) < 1e-3 or abs(v) >= 1e4) and v != 0 else f"{v:.4f}"
+        return str(v)
+
+    @staticmethod
+    def _span(seconds: float) -> str:
+        s = int(max(seconds, 0))
+        return f"{s // 3600}:{s % 3600 // 60:02d}:{s % 60:02d}"
+
+    def log(self, step: int, metrics: Mapping[str, Any]) -> None:
+        now = self.clock()
+        row = {k: _scalar(v) for k, v in metrics.items()}
+        parts = [f"step {int(step)}" + (f"/{self.steps}" if self.steps else "")]
+        parts += [f"{k} {self._fmt(row[k])}" for k in self.keys if k in row and row[k] is not None]
+        if self._last is not None and now > self._last[0]:
+            dt, dsteps = now - self._last[0], int(step) - self._last[1]
+            if self.rate_key in row and isinstance(row[self.rate_key], (int, float)) and dsteps > 0:
+                parts.append(f"{row[self.rate_key] * dsteps / dt:,.0f} {self.rate_key}/s")
+            parts.append(f"{dt / max(dsteps, 1):.3f} s/step")
+        if self._first is None:
+            self._first = (now, int(step))
+        elif self.steps and int(step) > self._first[1]:
+            per = (now - self._first[0]) / (int(step) - self._first[1])
+            parts.append(f"eta {self._span(per * (self.steps - int(step)))}")
+        self._last = (now, int(step))
+        print(" | ".join(parts), file=self.stream, flush=True)
+
+    def artifact(self, step: int, name: str, value: Any) -> None:
+        print(f"step {int(step)} | artifact {name}: {type(value).__name__}", file=self.stream, flush=True)
+
+    def close(self) -> None:
+        pass
+
+
 class Trackers:
     def __init__(self, *trackers):
         self.trackers = list(trackers)

@@ -106,3 +106,20 @@ def test_checkpoint_integrity_passes_over_a_damaged_step(tmp_path):
     assert any("integrity" in str(w.message) for w in caught)
     state = trainer().fit(list(data), steps=6, log_every=1000)        # resumes from step 4, not the damaged 6
     assert state.step == 6
+
+
+def test_console_tracker_lines():
+    import io
+    import dew_b200 as dew
+    ticks = iter([0.0, 2.0, 4.0])
+    out = io.StringIO()
+    t = dew.ConsoleTracker(steps=30, stream=out, clock=lambda: next(ticks))
+    t.log(10, {"loss": torch.tensor(2.5), "tokens": 1000, "learning_rate": 3e-4})
+    t.log(20, {"loss": 2.25, "tokens": 1000, "learning_rate": 3e-4})
+    t.log(30, {"loss": 2.0, "tokens": 1000})
+    lines = out.getvalue().splitlines()
+    assert lines[0].startswith("step 10/30 | loss 2.5000 | learning_rate 3.000e-04")
+    assert "5,000 tokens/s" in lines[1] and "0.200 s/step" in lines[1] and "eta 0:00:02" in lines[1]
+    assert lines[2].startswith("step 30/30") and "eta 0:00:00" in lines[2]
+    dew.Trackers(t, dew.MemoryTracker()).artifact(30, "grid", object())
+    assert "artifact grid" in out.getvalue()
