@@ -207,7 +207,7 @@ def build(config: RunConfig, device=None):
     from ..checkpoints.state_trees import leaf_kinds
     from ..optim import OptimConfig, schedules
     from ..parallel.mesh import MeshSpec
-    from ..training import LocalTracker, Trainer
+    from ..training import ConsoleTracker, LocalTracker, Trackers, Trainer
     from ..models import causal_transformer, dit  # noqa: F401  (registers the built-in models)
     model_cls = lookup(config.model.name, "model")
     model = model_cls(**config.model.fields)
@@ -244,7 +244,8 @@ def build(config: RunConfig, device=None):
     m = tc.mesh
     mesh = MeshSpec(fsdp=m.fsdp, expert=m.expert, tensor=m.tensor, sequence=m.sequence, stage=m.stage, replicas=m.replicas, diloco=m.diloco)
     trainer = Trainer(objective, optim, key=tc.key, mesh=mesh, microbatches=tc.microbatches, accumulation=tc.accumulation,
-                      checkpoints=ckpt, tracker=LocalTracker(tc.checkpoint_dir + "/logs", tc.name) if tc.checkpoint_dir else None,
+                      checkpoints=ckpt, tracker=(Trackers(LocalTracker(tc.checkpoint_dir + "/logs", tc.name), ConsoleTracker(tc.steps)) if tc.checkpoint_dir
+                               else ConsoleTracker(tc.steps)),
                       skip_nonfinite=tc.skip_nonfinite, data_resume=tc.data_resume,
                       param_dtype=None if (device is None or str(device) == "cpu") else getattr(torch, tc.precision))
     if dc.source == "synthetic":
