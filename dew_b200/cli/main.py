@@ -1,4 +1,4 @@
-"""``dewb`` command line: ``train``, ``profile``, ``inspect``, ``export``, ``data export``, ``launch``.
+"""``dewb`` command line: ``train``, ``sweep``, ``profile``, ``inspect``, ``export``, ``data export``, ``launch``.
 
 Parity: src/dew/_cli/main.py (subcommands Train with ``--set path=value``, Profile, Inspect, Export, DataExport),
 src/dew/_cli/launch.py.  Importing this module imports no CUDA library.
@@ -72,6 +72,38 @@ def cmd_export(args) -> int:
     return 0
 
 
+def cmd_sweep(args) -> int:
+    """Train every point of a grid (``--grid path=v1,v2``, repeated; the Cartesian product) one after another, each in its
+    own directory under the recipe's checkpoint directory, and print one JSON line per point plus the best one."""
+    import torch
+
+    from ..config import _parse, apply_overrides, build, sweep
+    base = apply_overrides(_load_recipe(args.recipe), args.set or [])
+    grid = {}
+    for item in args.grid or []:
+        path, _, values = item.partition("=")
+        if not values:
+            raise SystemExit(f"--grid takes path=v1,v2,..., got {item!r}")
+        grid[path] = [_parse(v) for v in values.split(",")]
+    device = "cuda" if torch.cuda.is_available() and not args.cpu else "cpu"
+    results = []
+    for cfg in sweep(base, grid):
+        if cfg.trainer.checkpoint_dir:
+            cfg.trainer.checkpoint_dir = str(Path(cfg.trainer.checkpoint_dir) / cfg.trainer.name)
+        trainer, dataset = build(cfg, device=device)
+        tc = cfg.trainer
+        state = trainer.fit(dataset, steps=tc.steps, epochs=tc.epochs, tokens=tc.tokens, examples=tc.examples, log_every=tc.log_every,
+                            checkpoint_every=tc.checkpoint_every, checkpoint_final=tc.checkpoint_final, resume=tc.resume)
+        last = next((h for h in reversed(trainer.history) if "loss" in h), {})
+        row = {"name": tc.name, "step": state.step, "loss": last.get("loss")}
+        results.append(row)
+        print(json.dumps(row))
+    scored = [r for r in results if isinstance(r["loss"], (int, float))]
+    if scored:
+        print(json.dumps({"best": min(scored, key=lambda r: r["loss"])["name"], "points": len(results)}))
+    return 0
+
+
 def cmd_profile(args) -> int:
     from ..telemetry import kernel_bench
     kernel_bench.main(["--only", args.only] + (["--out", args.out] if args.out else []))
@@ -101,6 +133,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     sub = ap.add_subparsers(dest="command", required=True)
     t = sub.add_parser("train"); t.add_argument("recipe"); t.add_argument("--set", action="append"); t.add_argument("--cpu", action="store_true")
     t.set_defaults(fn=cmd_train)
+    w = sub.add_parser("sweep"); w.add_argument("recipe"); w.add_argument("--set", action="append"); w.add_argument("--grid", action="append")
+    w.add_argument("--cpu", action="store_true"); w.set_defaults(fn=cmd_sweep)
     i = sub.add_parser("inspect"); i.add_argument("recipe"); i.add_argument("--set", action="append")
     i.add_argument("--devices", type=int, default=8); i.add_argument("--memory-gb", type=float, default=180.0); i.set_defaults(fn=cmd_inspect)
     e = sub.add_parser("export"); e.add_argument("checkpoint"); e.add_argument("out"); e.set_defaults(fn=cmd_export)

@@ -72,3 +72,12 @@ def test_shipped_recipes_train_through_the_cli(recipe, shrink, tmp_path, capsys)
     assert cli.main(args) == 0
     out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert out["step"] == 3
+
+
+def test_cli_sweep_trains_every_point(tmp_path, capsys):
+    recipe = _recipe(tmp_path, steps=3, log_every=1, checkpoint_dir=str(tmp_path / "sweep"))
+    assert cli.main(["sweep", str(recipe), "--cpu", "--grid", "optimizer.learning_rate=1e-3,3e-3", "--grid", "trainer.key=0,1"]) == 0
+    lines = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert len(lines) == 5 and lines[-1]["points"] == 4 and lines[-1]["best"] in {l["name"] for l in lines[:4]}
+    assert all(l["step"] == 3 for l in lines[:4]) and len({l["name"] for l in lines[:4]}) == 4
+    assert len(list((tmp_path / "sweep").iterdir())) == 4
