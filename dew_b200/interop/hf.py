@@ -21,21 +21,36 @@ from ..models.causal_transformer import CausalTransformer, TransformerConfig
 def config_from_hf(cfg: Mapping[str, Any]) -> TransformerConfig:
     heads = cfg["num_attention_heads"]
     arch = (cfg.get("architectures") or [""])[0].lower()
-    return TransformerConfig(
+    # newer configs nest the rotary settings: {"rope_parameters": {"rope_theta": ..., "rope_type": "default" | "llama3" | ...}}
+    rope = cfg.get("rope_parameters") or {}
+    theta = rope.get("rope_theta", cfg.get("rope_theta", 10000.0))
+    scaling = cfg.get("rope_scaling")
+    if scaling is None and rope.get("rope_type", "default") != "default":
+        scaling = {k: v for k, v in rope.items() if k != "rope_theta"}
+    experts = cfg.get("num_local_experts") or cfg.get("num_experts")
+    mixture = None
+    if experts:
+        from ..models.causal_transformer import Mixture
+        # Mixtral renormalises the chosen weights always; Qwen-MoE says so in ``norm_topk_prob``
+        mixture = Mixture(experts=int(experts), top_k=int(cfg.get("num_experts_per_tok", 2)),
+                          expert_features=int(cfg.get("moe_intermediate_size") or cfg["intermediate_size"]),
+                          norm_topk_prob=bool(cfg.get("norm_topk_prob", True)) if "mixtral" not in arch else True)
+    return TransformerConfig(mixture=mixture, 
         vocab_size=cfg["vocab_size"], emb_features=cfg["hidden_size"], num_layers=cfg["num_hidden_layers"], num_heads=heads,
         num_kv_heads=cfg.get("num_key_value_heads", heads), head_dim=cfg.get("head_dim") or cfg["hidden_size"] // heads,
         mlp_features=cfg["intermediate_size"], max_seq_len=cfg.get("max_position_embeddings", 4096),
-        rope_theta=cfg.get("rope_theta", 10000.0), rope_scaling=cfg.get("rope_scaling"), norm_eps=cfg.get("rms_norm_eps", 1e-6),
+        rope_theta=theta, rope_scaling=scaling, norm_eps=cfg.get("rms_norm_eps", 1e-6),
         qk_norm="qwen3" in arch, tie_embeddings=cfg.get("tie_word_embeddings", False), window=cfg.get("sliding_window"),
         embed_scale="gemma" in arch)
 
 
-def config_to_hf(c: TransformerConfig, architecture: str = "LlamaForCausalLM") -> Dict[str, Any]:
-    return {"architectures": [architecture], "vocab_size": c.vocab_size, "hidden_size": c.emb_features, "num_hidden_layers": c.num_layers,
+def config_to_hf(c: TransformerConfig, architecture: str = "LlamaForCausalLM", dtype: str = "bfloat16") -> Dict[str, Any]:
+    rope = {"rope_theta": c.rope_theta, "rope_type": "default"} if not c.rope_scaling else {"rope_theta": c.rope_theta, **c.rope_scaling}
+    return {"rope_parameters": rope, "dtype": dtype, "architectures": [architecture], "vocab_size": c.vocab_size, "hidden_size": c.emb_features, "num_hidden_layers": c.num_layers,
             "num_attention_heads": c.num_heads, "num_key_value_heads": c.num_kv_heads or c.num_heads,
             "head_dim": c.head_dim or c.emb_features // c.num_heads, "intermediate_size": c.mlp_features,
             "max_position_embeddings": c.max_seq_len, "rope_theta": c.rope_theta, "rope_scaling": c.rope_scaling,
-            "rms_norm_eps": c.norm_eps, "tie_word_embeddings": c.tie_embeddings, "hidden_act": "silu", "torch_dtype": "bfloat16"}
+            "rms_norm_eps": c.norm_eps, "tie_word_embeddings": c.tie_embeddings, "hidden_act": "silu", "torch_dtype": dtype}
 
 
 def from_hf_state(model: CausalTransformer, hf: Mapping[str, torch.Tensor]) -> None:
@@ -54,11 +69,37 @@ def from_hf_state(model: CausalTransformer, hf: Mapping[str, torch.Tensor]) -> N
         if a.q_norm is not None and pre + "self_attn.q_norm.weight" in hf:
             put(a.q_norm.weight, hf[pre + "self_attn.q_norm.weight"])
             put(a.k_norm.weight, hf[pre + "self_attn.k_norm.weight"])
+        if getattr(layer, "sparse", False):
+            _put_experts(put, layer.mlp, hf, pre)
+            continue
         put(layer.mlp.gate_up_proj.weight, torch.cat([hf[pre + "mlp.gate_proj.weight"], hf[pre + "mlp.up_proj.weight"]], 0))
         put(layer.mlp.down_proj.weight, hf[pre + "mlp.down_proj.weight"])
     put(model.final_norm.weight, hf["model.norm.weight"])
     if model.head is not None:
         put(model.head.weight, hf.get("lm_head.weight", hf["model.embed_tokens.weight"]))
+
+
+def _put_experts(put, mlp, hf: Mapping[str, torch.Tensor], pre: str) -> None:
+    """A sparse layer's router and experts from either naming: stacked tensors (``mlp.gate.weight``, ``mlp.experts.gate_up_proj``
+    ``[E, 2F, d]``, ``mlp.experts.down_proj`` ``[E, d, F]``) or one tensor per expert (Mixtral's ``block_sparse_moe.experts.j.w1 /
+    w3 / w2``, Qwen-MoE's ``mlp.experts.j.gate_proj / up_proj / down_proj``)."""
+    E = mlp.mix.experts
+    for gate in ("mlp.gate.weight", "block_sparse_moe.gate.weight"):
+        if pre + gate in hf:
+            put(mlp.router.weight, hf[pre + gate])
+            break
+    else:
+        raise KeyError(f"no router weight under {pre}")
+    if pre + "mlp.experts.gate_up_proj" in hf:
+        put(mlp.experts.gate_up, hf[pre + "mlp.experts.gate_up_proj"])
+        put(mlp.experts.down, hf[pre + "mlp.experts.down_proj"])
+        return
+    if pre + "block_sparse_moe.experts.0.w1.weight" in hf:
+        names = ("block_sparse_moe.experts.{}.w1.weight", "block_sparse_moe.experts.{}.w3.weight", "block_sparse_moe.experts.{}.w2.weight")
+    else:
+        names = ("mlp.experts.{}.gate_proj.weight", "mlp.experts.{}.up_proj.weight", "mlp.experts.{}.down_proj.weight")
+    put(mlp.experts.gate_up, torch.stack([torch.cat([hf[pre + names[0].format(j)], hf[pre + names[1].format(j)]], 0) for j in range(E)]))
+    put(mlp.experts.down, torch.stack([hf[pre + names[2].format(j)] for j in range(E)]))
 
 
 def to_hf_state(model: CausalTransformer) -> Dict[str, torch.Tensor]:
@@ -77,6 +118,11 @@ def to_hf_state(model: CausalTransformer) -> Dict[str, torch.Tensor]:
         if layer.mixer.q_norm is not None:
             out[pre + "self_attn.q_norm.weight"] = layer.mixer.q_norm.weight.detach()
             out[pre + "self_attn.k_norm.weight"] = layer.mixer.k_norm.weight.detach()
+        if getattr(layer, "sparse", False):
+            out[pre + "mlp.gate.weight"] = layer.mlp.router.weight.detach()
+            out[pre + "mlp.experts.gate_up_proj"] = layer.mlp.experts.gate_up.detach()
+            out[pre + "mlp.experts.down_proj"] = layer.mlp.experts.down.detach()
+            continue
         gu = layer.mlp.gate_up_proj.weight.detach()
         F_ = gu.shape[0] // 2
         out[pre + "mlp.gate_proj.weight"], out[pre + "mlp.up_proj.weight"] = gu[:F_], gu[F_:]
@@ -102,5 +148,6 @@ class Pretrained:
     def save(model: CausalTransformer, directory: os.PathLike, architecture: str = "LlamaForCausalLM") -> None:
         d = Path(directory)
         d.mkdir(parents=True, exist_ok=True)
-        (d / "config.json").write_text(json.dumps(config_to_hf(model.config, architecture), indent=1))
+        dtype = str(next(model.parameters()).dtype).replace("torch.", "")
+        (d / "config.json").write_text(json.dumps(config_to_hf(model.config, architecture, dtype), indent=1))
         TS.save_file(to_hf_state(model), d / "model.safetensors", metadata={"format": "pt"})
