@@ -46,7 +46,12 @@ def config_from_hf(cfg: Mapping[str, Any]) -> TransformerConfig:
 
 def config_to_hf(c: TransformerConfig, architecture: str = "LlamaForCausalLM", dtype: str = "bfloat16") -> Dict[str, Any]:
     rope = {"rope_theta": c.rope_theta, "rope_type": "default"} if not c.rope_scaling else {"rope_theta": c.rope_theta, **c.rope_scaling}
-    return {"rope_parameters": rope, "dtype": dtype, "architectures": [architecture], "vocab_size": c.vocab_size, "hidden_size": c.emb_features, "num_hidden_layers": c.num_layers,
+    moe = {}
+    if c.mixture is not None:
+        m = c.mixture
+        moe = {"num_experts": m.experts, "num_local_experts": m.experts, "num_experts_per_tok": m.top_k, "norm_topk_prob": m.norm_topk_prob,
+               "moe_intermediate_size": m.expert_features or c.mlp_features, "decoder_sparse_step": 1, "mlp_only_layers": []}
+    return {**moe, "rope_parameters": rope, "dtype": dtype, "architectures": [architecture], "vocab_size": c.vocab_size, "hidden_size": c.emb_features, "num_hidden_layers": c.num_layers,
             "num_attention_heads": c.num_heads, "num_key_value_heads": c.num_kv_heads or c.num_heads,
             "head_dim": c.head_dim or c.emb_features // c.num_heads, "intermediate_size": c.mlp_features,
             "max_position_embeddings": c.max_seq_len, "rope_theta": c.rope_theta, "rope_scaling": c.rope_scaling,
@@ -102,7 +107,7 @@ def _put_experts(put, mlp, hf: Mapping[str, torch.Tensor], pre: str) -> None:
     put(mlp.experts.down, torch.stack([hf[pre + names[2].format(j)] for j in range(E)]))
 
 
-def to_hf_state(model: CausalTransformer) -> Dict[str, torch.Tensor]:
+def to_hf_state(model: CausalTransformer, architecture: str = "LlamaForCausalLM") -> Dict[str, torch.Tensor]:
     c = model.config
     H, Hkv = c.num_heads, c.num_kv_heads or c.num_heads
     D = c.head_dim or c.emb_features // c.num_heads
@@ -119,9 +124,15 @@ def to_hf_state(model: CausalTransformer) -> Dict[str, torch.Tensor]:
             out[pre + "self_attn.q_norm.weight"] = layer.mixer.q_norm.weight.detach()
             out[pre + "self_attn.k_norm.weight"] = layer.mixer.k_norm.weight.detach()
         if getattr(layer, "sparse", False):
-            out[pre + "mlp.gate.weight"] = layer.mlp.router.weight.detach()
-            out[pre + "mlp.experts.gate_up_proj"] = layer.mlp.experts.gate_up.detach()
-            out[pre + "mlp.experts.down_proj"] = layer.mlp.experts.down.detach()
+            # one tensor per expert, under the names the target family stores on disk
+            gu_all, dn_all = layer.mlp.experts.gate_up.detach(), layer.mlp.experts.down.detach()
+            Fe = gu_all.shape[1] // 2
+            mixtral = "mixtral" in architecture.lower()
+            out[pre + ("block_sparse_moe.gate.weight" if mixtral else "mlp.gate.weight")] = layer.mlp.router.weight.detach()
+            for j in range(gu_all.shape[0]):
+                base = pre + (f"block_sparse_moe.experts.{j}." if mixtral else f"mlp.experts.{j}.")
+                g_n, u_n, d_n = ("w1", "w3", "w2") if mixtral else ("gate_proj", "up_proj", "down_proj")
+                out[base + g_n + ".weight"], out[base + u_n + ".weight"], out[base + d_n + ".weight"] = gu_all[j, :Fe], gu_all[j, Fe:], dn_all[j]
             continue
         gu = layer.mlp.gate_up_proj.weight.detach()
         F_ = gu.shape[0] // 2
@@ -150,4 +161,4 @@ class Pretrained:
         d.mkdir(parents=True, exist_ok=True)
         dtype = str(next(model.parameters()).dtype).replace("torch.", "")
         (d / "config.json").write_text(json.dumps(config_to_hf(model.config, architecture, dtype), indent=1))
-        TS.save_file(to_hf_state(model), d / "model.safetensors", metadata={"format": "pt"})
+        TS.save_file(to_hf_state(model, architecture), d / "model.safetensors", metadata={"format": "pt"})

@@ -52,3 +52,17 @@ def test_mixtral_parity(tmp_path):
                                      sliding_window=None, tie_word_embeddings=False)
     mine = _compare(transformers.MixtralForCausalLM(cfg), tmp_path / "mixtral", 128, atol=5e-5)
     assert mine.config.mixture.experts == 4 and mine.config.mixture.top_k == 2
+
+
+def test_qwen3_moe_parity_and_export(tmp_path):
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3MoeConfig(vocab_size=128, hidden_size=64, intermediate_size=112, moe_intermediate_size=32, num_hidden_layers=2,
+                                      num_attention_heads=4, num_key_value_heads=2, head_dim=16, num_experts=4, num_experts_per_tok=2,
+                                      norm_topk_prob=True, max_position_embeddings=64, tie_word_embeddings=False, decoder_sparse_step=1,
+                                      mlp_only_layers=[])
+    mine = _compare(transformers.Qwen3MoeForCausalLM(cfg), tmp_path / "q3moe", 128, atol=5e-5)
+    Pretrained.save(mine, tmp_path / "back", architecture="Qwen3MoeForCausalLM")
+    again = transformers.Qwen3MoeForCausalLM.from_pretrained(tmp_path / "back").eval()
+    tok = torch.randint(0, 128, (1, 13))
+    with torch.no_grad():
+        assert torch.allclose(again(tok).logits.float(), mine(tok).float(), atol=5e-5)
