@@ -66,3 +66,18 @@ def test_qwen3_moe_parity_and_export(tmp_path):
     tok = torch.randint(0, 128, (1, 13))
     with torch.no_grad():
         assert torch.allclose(again(tok).logits.float(), mine(tok).float(), atol=5e-5)
+
+
+def test_greedy_generation_matches_transformers(tmp_path):
+    from dew_b200.sampling.text import Sampling, generate
+    torch.manual_seed(0)
+    cfg = transformers.LlamaConfig(vocab_size=128, hidden_size=64, intermediate_size=112, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, max_position_embeddings=64, tie_word_embeddings=False, eos_token_id=None, bos_token_id=None)
+    hf = transformers.LlamaForCausalLM(cfg).eval()
+    hf.save_pretrained(tmp_path / "m", safe_serialization=True)
+    mine = Pretrained.load(tmp_path / "m").eval()
+    prompt = [5, 17, 99, 3, 42]
+    with torch.no_grad():
+        want = hf.generate(torch.tensor([prompt]), max_new_tokens=10, do_sample=False, pad_token_id=0)[0, len(prompt):].tolist()
+    got = generate(mine, None, [prompt], 10, sampling=Sampling(temperature=0.0))
+    assert [int(t) for t in got.new_tokens(0)] == want
