@@ -162,3 +162,33 @@ class Pretrained:
         dtype = str(next(model.parameters()).dtype).replace("torch.", "")
         (d / "config.json").write_text(json.dumps(config_to_hf(model.config, architecture, dtype), indent=1))
         TS.save_file(to_hf_state(model, architecture), d / "model.safetensors", metadata={"format": "pt"})
+
+
+# ------------------------------------------------------------------------------------------------ gated delta net layers
+def _qkvz_from_grouped(w: torch.Tensor, hk: int, hv: int, dk: int, dv: int) -> torch.Tensor:
+    """Qwen3-Next stores the fused projection grouped by key head (``[q | k | v of the group | z of the group]`` per key
+    head); this library keeps ``[q of all heads | k | v | z]``."""
+    rep = hv // hk
+    blk = w.reshape(hk, 2 * dk + 2 * rep * dv, -1)
+    q, k = blk[:, :dk], blk[:, dk:2 * dk]
+    v, z = blk[:, 2 * dk:2 * dk + rep * dv], blk[:, 2 * dk + rep * dv:]
+    return torch.cat([q.reshape(hk * dk, -1), k.reshape(hk * dk, -1), v.reshape(hv * dv, -1), z.reshape(hv * dv, -1)], 0)
+
+
+def _ba_from_grouped(w: torch.Tensor, hk: int, hv: int) -> torch.Tensor:
+    rep = hv // hk
+    blk = w.reshape(hk, 2 * rep, -1)
+    return torch.cat([blk[:, :rep].reshape(hv, -1), blk[:, rep:].reshape(hv, -1)], 0)
+
+
+def load_gated_delta_net(mixer, hf: Mapping[str, torch.Tensor], prefix: str = "") -> None:
+    """Copy a Qwen3-Next ``linear_attn`` layer (``in_proj_qkvz``, ``in_proj_ba``, ``conv1d``, ``A_log``, ``dt_bias``, ``norm``,
+    ``out_proj``) into a ``GatedDeltaNet`` mixer, reordering the fused projections."""
+    with torch.no_grad():
+        mixer.in_proj_qkvz.weight.copy_(_qkvz_from_grouped(hf[prefix + "in_proj_qkvz.weight"], mixer.hk, mixer.hv, mixer.dk, mixer.dv))
+        mixer.in_proj_ba.weight.copy_(_ba_from_grouped(hf[prefix + "in_proj_ba.weight"], mixer.hk, mixer.hv))
+        mixer.conv1d.weight.copy_(hf[prefix + "conv1d.weight"].reshape(mixer.conv1d.weight.shape))
+        mixer.A_log.copy_(hf[prefix + "A_log"])
+        mixer.dt_bias.copy_(hf[prefix + "dt_bias"])
+        mixer.norm_weight.copy_(hf[prefix + "norm.weight"])
+        mixer.out_proj.weight.copy_(hf[prefix + "out_proj.weight"])

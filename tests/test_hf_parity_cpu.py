@@ -81,3 +81,34 @@ def test_greedy_generation_matches_transformers(tmp_path):
         want = hf.generate(torch.tensor([prompt]), max_new_tokens=10, do_sample=False, pad_token_id=0)[0, len(prompt):].tolist()
     got = generate(mine, None, [prompt], 10, sampling=Sampling(temperature=0.0))
     assert [int(t) for t in got.new_tokens(0)] == want
+
+
+def test_gated_delta_net_layer_matches_qwen3_next():
+    """The gated-delta-rule mixer (short conv, l2-normalised q / k, decay and write gates, chunked delta rule, gated RMSNorm)
+    against the Qwen3-Next layer of transformers, weights copied through the interop."""
+    import warnings
+    from dew_b200.interop.hf import load_gated_delta_net
+    from dew_b200.nn.linear_attention import GatedDeltaNet
+    try:
+        from transformers.models.qwen3_next import modeling_qwen3_next as Q
+    except Exception:
+        pytest.skip("this transformers has no Qwen3-Next")
+    torch.manual_seed(0)
+    cfg = transformers.Qwen3NextConfig(vocab_size=64, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                       num_key_value_heads=2, head_dim=16, linear_num_key_heads=2, linear_num_value_heads=4,
+                                       linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4, num_experts=0,
+                                       max_position_embeddings=128, layer_types=["linear_attention", "full_attention"])
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        hf = Q.Qwen3NextGatedDeltaNet(cfg, 0).eval()
+    with torch.no_grad():
+        hf.A_log.copy_(torch.randn(4) * 0.5)
+        hf.dt_bias.copy_(torch.randn(4) * 0.5)
+        hf.norm.weight.copy_(1 + 0.1 * torch.randn(16))
+    mine = GatedDeltaNet(64, num_k_heads=2, num_v_heads=4, head_k_dim=16, head_v_dim=16, conv_size=4, norm_eps=cfg.rms_norm_eps).eval()
+    load_gated_delta_net(mine, hf.state_dict())
+    for T in (24, 100):                                       # one chunk and several
+        x = torch.randn(2, T, 64)
+        with torch.no_grad():
+            a, b = hf(x), mine(x)
+        assert float((a - b).abs().max()) < 2e-5 * max(1.0, float(a.abs().max())), (T, float((a - b).abs().max()))
