@@ -192,3 +192,18 @@ def load_gated_delta_net(mixer, hf: Mapping[str, torch.Tensor], prefix: str = ""
         mixer.dt_bias.copy_(hf[prefix + "dt_bias"])
         mixer.norm_weight.copy_(hf[prefix + "norm.weight"])
         mixer.out_proj.weight.copy_(hf[prefix + "out_proj.weight"])
+
+
+def load_mamba2(mixer, hf: Mapping[str, torch.Tensor], prefix: str = "") -> None:
+    """Copy a transformers ``Mamba2Mixer`` (``in_proj`` as ``[z | x B C | dt]``, depthwise ``conv1d``, ``A_log``, ``D``, ``dt_bias``,
+    gated ``norm``, ``out_proj``) into a ``Mamba2`` mixer: the layouts agree, only the conv weight drops its singleton axis."""
+    with torch.no_grad():
+        mixer.in_proj.weight.copy_(hf[prefix + "in_proj.weight"])
+        mixer.out_proj.weight.copy_(hf[prefix + "out_proj.weight"])
+        mixer.conv1d.weight.copy_(hf[prefix + "conv1d.weight"].reshape(mixer.conv1d.weight.shape))
+        if prefix + "conv1d.bias" in hf and getattr(mixer.conv1d, "bias", None) is not None:
+            mixer.conv1d.bias.copy_(hf[prefix + "conv1d.bias"])
+        mixer.A_log.copy_(hf[prefix + "A_log"])
+        mixer.dt_bias.copy_(hf[prefix + "dt_bias"])
+        mixer.D.copy_(hf[prefix + "D"])
+        mixer.norm_weight.copy_(hf[prefix + "norm.weight"])

@@ -20,8 +20,9 @@ from .linear_attention import ShortConv
 
 class Mamba2(nn.Module):
     def __init__(self, features: int, state_dim: int = 128, head_dim: int = 64, expand: int = 2, groups: int = 1, conv_size: int = 4,
-                 norm_eps: float = 1e-6, dtype=None, device=None):
+                 norm_eps: float = 1e-6, gate_after: bool = False, dtype=None, device=None):
         super().__init__()
+        self.gate_after = gate_after
         self.features, self.N, self.P, self.G = features, state_dim, head_dim, groups
         self.inner = expand * features
         self.H = self.inner // head_dim
@@ -68,5 +69,10 @@ class Mamba2(nn.Module):
             y, S = scan.ssd(xs, dt, A, Bm, Cm, self.D, initial_state=state["S"] if state is not None else None)
             if state is not None:
                 state["S"].copy_(S)
-        y = ops.gated_rms_norm(y.to(x.dtype).reshape(B, T, self.inner), z, self.norm_weight, self.norm_eps)
+        y = y.to(x.dtype).reshape(B, T, self.inner)
+        if self.gate_after:
+            y = ops.gated_rms_norm(y, z, self.norm_weight, self.norm_eps)              # norm, then gate (Falcon-H1's order)
+        else:
+            # Mamba-2's own order: the gate first, the norm over the whole width after (modeling_mamba2.py MambaRMSNormGated)
+            y = ops.rms_norm((y.float() * F.silu(z.float())).to(x.dtype), self.norm_weight, self.norm_eps)
         return self.out_proj(y)

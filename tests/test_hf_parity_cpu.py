@@ -112,3 +112,29 @@ def test_gated_delta_net_layer_matches_qwen3_next():
         with torch.no_grad():
             a, b = hf(x), mine(x)
         assert float((a - b).abs().max()) < 2e-5 * max(1.0, float(a.abs().max())), (T, float((a - b).abs().max()))
+
+
+def test_mamba2_layer_matches_transformers():
+    import warnings
+    from dew_b200.interop.hf import load_mamba2
+    from dew_b200.nn.mamba2 import Mamba2
+    from transformers.models.mamba2 import modeling_mamba2 as M
+    torch.manual_seed(0)
+    cfg = transformers.Mamba2Config(vocab_size=64, hidden_size=64, state_size=16, num_hidden_layers=1, expand=2, head_dim=16, num_heads=8, n_groups=1,
+                                    conv_kernel=4, chunk_size=32, use_bias=False, use_conv_bias=True, rms_norm=True)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        hf = M.Mamba2Mixer(cfg, 0).eval()
+    with torch.no_grad():
+        hf.A_log.copy_(torch.log(torch.rand(8) * 4 + 1))
+        hf.dt_bias.copy_(torch.randn(8) * 0.5)
+        hf.D.copy_(torch.randn(8))
+        hf.norm.weight.copy_(1 + 0.1 * torch.randn(128))
+        hf.conv1d.bias.copy_(torch.randn(160) * 0.1)
+    mine = Mamba2(64, state_dim=16, head_dim=16, norm_eps=cfg.layer_norm_epsilon).eval()
+    load_mamba2(mine, hf.state_dict())
+    for T in (24, 80):
+        x = torch.randn(2, T, 64)
+        with torch.no_grad():
+            a, b = hf(x), mine(x)
+        assert float((a - b).abs().max()) < 2e-5 * max(1.0, float(a.abs().max())), (T, float((a - b).abs().max()))
