@@ -138,3 +138,31 @@ def test_mamba2_layer_matches_transformers():
         with torch.no_grad():
             a, b = hf(x), mine(x)
         assert float((a - b).abs().max()) < 2e-5 * max(1.0, float(a.abs().max())), (T, float((a - b).abs().max()))
+
+
+def test_mamba1_layer_matches_transformers():
+    import warnings
+    from dew_b200.nn.mamba import Mamba
+    from transformers.models.mamba import modeling_mamba as M
+    torch.manual_seed(0)
+    cfg = transformers.MambaConfig(vocab_size=64, hidden_size=64, state_size=8, num_hidden_layers=1, expand=2, conv_kernel=4, time_step_rank=4,
+                                   use_bias=False, use_conv_bias=True)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        hf = M.MambaMixer(cfg, 0).eval()
+    mine = Mamba(64, state_dim=8, expand=2, conv_size=4, dt_rank=4).eval()
+    with torch.no_grad():
+        hf.A_log.copy_(torch.log(torch.rand(128, 8) * 4 + 0.5))
+        hf.D.copy_(torch.randn(128))
+        hf.conv1d.bias.copy_(torch.randn(128) * 0.1)
+        hf.dt_proj.bias.copy_(torch.randn(128) * 0.3)
+        sd, named = hf.state_dict(), dict(mine.named_parameters())
+        for k in ("A_log", "D", "in_proj.weight", "x_proj.weight", "dt_proj.weight", "dt_proj.bias", "out_proj.weight"):
+            named[k].copy_(sd[k])
+        mine.conv.weight.copy_(sd["conv1d.weight"].reshape(128, 4))
+        mine.conv.bias.copy_(sd["conv1d.bias"])
+    for T in (20, 70):
+        x = torch.randn(2, T, 64)
+        with torch.no_grad():
+            a, b = hf(x), mine(x)
+        assert float((a - b).abs().max()) < 1e-5, (T, float((a - b).abs().max()))
