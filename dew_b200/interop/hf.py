@@ -207,3 +207,24 @@ def load_mamba2(mixer, hf: Mapping[str, torch.Tensor], prefix: str = "") -> None
         mixer.dt_bias.copy_(hf[prefix + "dt_bias"])
         mixer.D.copy_(hf[prefix + "D"])
         mixer.norm_weight.copy_(hf[prefix + "norm.weight"])
+
+
+def load_mla(mixer, hf: Mapping[str, torch.Tensor], prefix: str = "") -> None:
+    """Copy a DeepSeek-V3 attention layer (``q_a_proj``, ``q_a_layernorm``, ``q_b_proj``, ``kv_a_proj_with_mqa``, ``kv_a_layernorm``,
+    ``kv_b_proj``, ``o_proj``) into a ``MultiHeadLatentAttention``.  DeepSeek stores the rotary dimensions interleaved
+    (pairs ``(2i, 2i + 1)``); this library rotates halves, so the rotary rows of the query up-projection (per head) and of
+    the latent down-projection are reordered to ``[even | odd]``."""
+    H, nope, rope = mixer.h, mixer.nope, mixer.rope
+    perm = torch.cat([torch.arange(0, rope, 2), torch.arange(1, rope, 2)])
+    with torch.no_grad():
+        mixer.q_down.weight.copy_(hf[prefix + "q_a_proj.weight"])
+        mixer.q_norm.weight.copy_(hf[prefix + "q_a_layernorm.weight"])
+        qb = hf[prefix + "q_b_proj.weight"].reshape(H, nope + rope, -1).clone()
+        qb[:, nope:] = qb[:, nope:][:, perm]
+        mixer.q_up.weight.copy_(qb.reshape(H * (nope + rope), -1))
+        kv = hf[prefix + "kv_a_proj_with_mqa.weight"].clone()
+        kv[-rope:] = kv[-rope:][perm]
+        mixer.kv_down.weight.copy_(kv)
+        mixer.kv_norm.weight.copy_(hf[prefix + "kv_a_layernorm.weight"])
+        mixer.kv_up.weight.copy_(hf[prefix + "kv_b_proj.weight"])
+        mixer.o_proj.weight.copy_(hf[prefix + "o_proj.weight"])

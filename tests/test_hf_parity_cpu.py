@@ -166,3 +166,35 @@ def test_mamba1_layer_matches_transformers():
         with torch.no_grad():
             a, b = hf(x), mine(x)
         assert float((a - b).abs().max()) < 1e-5, (T, float((a - b).abs().max()))
+
+
+def test_multi_head_latent_attention_matches_deepseek_v3():
+    import warnings
+    from dew_b200 import ops
+    from dew_b200.interop.hf import load_mla
+    from dew_b200.nn.mla import MultiHeadLatentAttention
+    from transformers.models.deepseek_v3 import modeling_deepseek_v3 as D
+    torch.manual_seed(0)
+    cfg = transformers.DeepseekV3Config(vocab_size=64, hidden_size=64, intermediate_size=96, num_hidden_layers=1, num_attention_heads=4,
+                                        num_key_value_heads=4, q_lora_rank=24, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8,
+                                        v_head_dim=16, max_position_embeddings=64, rope_scaling=None, n_routed_experts=4, first_k_dense_replace=1)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        hf = D.DeepseekV3Attention(cfg, 0).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.copy_(1 + 0.1 * torch.randn_like(p))
+    mine = MultiHeadLatentAttention(64, 4, kv_latent=16, q_latent=24, nope_dim=16, rope_dim=8, v_dim=16, norm_eps=cfg.rms_norm_eps).eval()
+    load_mla(mine, hf.state_dict())
+    B, T = 2, 12
+    x = torch.randn(B, T, 64)
+    mask = torch.full((T, T), float("-inf")).triu(1)[None, None]
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 8, 2).float() / 8))
+    ang = torch.arange(T).float()[:, None] * inv[None]
+    emb = torch.cat([ang, ang], -1)
+    cos, sin = ops.rope_tables(64, 8, 10000.0, "cpu", None)
+    with torch.no_grad():
+        a = hf(x, position_embeddings=(emb.cos()[None].expand(B, T, 8), emb.sin()[None].expand(B, T, 8)), attention_mask=mask)[0]
+        b = mine(x, cos, sin)
+    assert float((a - b).abs().max()) < 1e-5, float((a - b).abs().max())
