@@ -42,6 +42,8 @@ class Mixture:
     capacity_factor: Optional[float] = None
     fp8: bool = False                                # block-scaled fp8 expert GEMMs
     balance_rate: float = 1e-3
+    groups: int = 1                                  # DeepSeek-V3's group-limited routing: experts in ``groups`` groups ...
+    topk_groups: int = 1                             # ... of which each token may use the ``topk_groups`` best (by their top-2 sum)
 
 
 @dataclass

@@ -42,11 +42,20 @@ class Router(nn.Module):
         """``x2 [T, d]`` -> (weights [T, k] fp32, expert ids [T, k], scores [T, E] fp32)."""
         mix = self.mix
         logits = F.linear(x2.float(), self.weight.float())
-        if logits.is_cuda and mix.experts <= 256 and mix.top_k <= 16 and self.use_kernels:
+        grouped = getattr(mix, "groups", 1) > 1
+        if logits.is_cuda and mix.experts <= 256 and mix.top_k <= 16 and self.use_kernels and not grouped:
             from ..ops.routing import route
             return route(logits, self.expert_bias, mix.top_k, mix.score_function, mix.norm_topk_prob, mix.scaling)
         scores = torch.softmax(logits, -1) if mix.score_function == "softmax" else torch.sigmoid(logits)
         select = scores + self.expert_bias if self.expert_bias is not None else scores     # bias steers selection only
+        if grouped:
+            # group-limited routing (DeepSeek-V3): a group's score is the sum of its two best experts; experts outside the
+            # token's best ``topk_groups`` groups cannot be chosen
+            T, E = select.shape
+            per = E // mix.groups
+            gscore = select.view(T, mix.groups, per).topk(min(2, per), -1).values.sum(-1)
+            keep = torch.zeros_like(gscore).scatter_(1, gscore.topk(mix.topk_groups, -1).indices, 1.0).bool()
+            select = select.masked_fill(~keep[:, :, None].expand(T, mix.groups, per).reshape(T, E), 0.0)
         _, ids = torch.topk(select, mix.top_k, dim=-1)
         w = scores.gather(-1, ids)
         if mix.norm_topk_prob:

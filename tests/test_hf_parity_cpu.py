@@ -198,3 +198,35 @@ def test_multi_head_latent_attention_matches_deepseek_v3():
         a = hf(x, position_embeddings=(emb.cos()[None].expand(B, T, 8), emb.sin()[None].expand(B, T, 8)), attention_mask=mask)[0]
         b = mine(x, cos, sin)
     assert float((a - b).abs().max()) < 1e-5, float((a - b).abs().max())
+
+
+def test_group_limited_router_matches_deepseek_v3():
+    import warnings
+    from dew_b200.models.causal_transformer import Mixture
+    from dew_b200.nn.moe import Router
+    from transformers.models.deepseek_v3 import modeling_deepseek_v3 as D
+    torch.manual_seed(0)
+    cfg = transformers.DeepseekV3Config(vocab_size=64, hidden_size=32, intermediate_size=48, moe_intermediate_size=16, num_hidden_layers=1,
+                                        num_attention_heads=2, num_key_value_heads=2, n_routed_experts=16, num_experts_per_tok=4, n_group=4,
+                                        topk_group=2, norm_topk_prob=True, routed_scaling_factor=2.5, q_lora_rank=8, kv_lora_rank=8,
+                                        qk_nope_head_dim=8, qk_rope_head_dim=8, v_head_dim=8, first_k_dense_replace=0)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        hf = D.DeepseekV3MoE(cfg).eval()
+    with torch.no_grad():
+        hf.gate.weight.normal_(0, 0.5)
+        hf.gate.e_score_correction_bias.normal_(0, 0.1)
+    mix = Mixture(experts=16, top_k=4, score_function="sigmoid", norm_topk_prob=True, scaling=2.5, bias=True, groups=4, topk_groups=2)
+    mine = Router(32, mix)
+    with torch.no_grad():
+        mine.weight.copy_(hf.gate.weight)
+        mine.expert_bias.copy_(hf.gate.e_score_correction_bias)
+    x = torch.randn(40, 32)
+    with torch.no_grad():
+        logits = hf.gate(x)
+        out = hf.route_tokens_to_experts(logits) if hasattr(hf, "route_tokens_to_experts") else logits
+        ids_hf, w_hf = out
+        w, ids, _ = mine(x)
+    order_a, order_b = ids_hf.sort(-1), ids.sort(-1)
+    assert torch.equal(order_a.values, order_b.values)
+    assert torch.allclose(w_hf.gather(-1, order_a.indices).float(), w.gather(-1, order_b.indices), atol=1e-5)
