@@ -230,3 +230,39 @@ def test_group_limited_router_matches_deepseek_v3():
     order_a, order_b = ids_hf.sort(-1), ids.sort(-1)
     assert torch.equal(order_a.values, order_b.values)
     assert torch.allclose(w_hf.gather(-1, order_a.indices).float(), w.gather(-1, order_b.indices), atol=1e-5)
+
+
+def test_sparse_mlp_matches_deepseek_v3_moe_block():
+    """Routed experts under group-limited sigmoid routing plus the shared experts, against transformers' block."""
+    import warnings
+    from dew_b200.models.causal_transformer import Mixture
+    from dew_b200.nn.moe import SparseMLP
+    from transformers.models.deepseek_v3 import modeling_deepseek_v3 as D
+    torch.manual_seed(0)
+    cfg = transformers.DeepseekV3Config(vocab_size=64, hidden_size=32, intermediate_size=48, moe_intermediate_size=16, num_hidden_layers=1,
+                                        num_attention_heads=2, num_key_value_heads=2, n_routed_experts=8, num_experts_per_tok=3, n_group=4,
+                                        topk_group=2, norm_topk_prob=True, routed_scaling_factor=2.5, n_shared_experts=2, q_lora_rank=8,
+                                        kv_lora_rank=8, qk_nope_head_dim=8, qk_rope_head_dim=8, v_head_dim=8, first_k_dense_replace=0)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        hf = D.DeepseekV3MoE(cfg).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.normal_(0, 0.2)
+    sd = hf.state_dict()
+    if "experts.gate_up_proj" not in sd:
+        pytest.skip("this transformers stores the experts one module each")
+    mix = Mixture(experts=8, top_k=3, score_function="sigmoid", norm_topk_prob=True, scaling=2.5, bias=True, groups=4, topk_groups=2,
+                  expert_features=16, shared_features=32)
+    mine = SparseMLP(32, mix, 48).eval()
+    with torch.no_grad():
+        mine.router.weight.copy_(sd["gate.weight"])
+        mine.router.expert_bias.copy_(sd["gate.e_score_correction_bias"])
+        mine.experts.gate_up.copy_(sd["experts.gate_up_proj"])
+        mine.experts.down.copy_(sd["experts.down_proj"])
+        mine.shared.gate_up_proj.weight.copy_(torch.cat([sd["shared_experts.gate_proj.weight"], sd["shared_experts.up_proj.weight"]], 0))
+        mine.shared.down_proj.weight.copy_(sd["shared_experts.down_proj.weight"])
+    x = torch.randn(2, 9, 32)
+    with torch.no_grad():
+        a, b = hf(x), mine(x)
+    assert float((a - b).abs().max()) < 2e-5 * max(1.0, float(a.abs().max()))
