@@ -24,6 +24,11 @@
  *     overwrites the part it reads before reading it, so calls that run one after another are independent; two calls
  *     that overlap on the GPU (different streams without an ordering between them) race on the array and must be
  *     ordered by the caller.
+ *   - `device` is made the current CUDA device for the whole call (the address look-up and every launch) and the
+ *     caller's current device is put back before the call returns, so the caller need not have `device` current;
+ *     `stream` must belong to `device` (null selects its default stream).
+ *   - Host threads: the first calls on a device may come from several threads at once (they all store the same
+ *     address); after that the entry point keeps no host-side state.  The rule on overlapping GPU work above still holds.
  *   - No cudaMalloc, cudaFree or allocating library routine is called, on the first call or any later one.
  */
 #ifndef DEWB_NOALLOC_H_

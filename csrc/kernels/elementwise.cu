@@ -1026,23 +1026,31 @@ static __device__ __align__(256) float g_noalloc_dw_partial[DEWB_NOALLOC_MAX_SPL
 // table; the address a kernel can use comes from cudaGetSymbolAddress, asked for once with that device current.
 static float* g_noalloc_ptr[64];
 
-extern "C" int dewb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
-                                        const void* dres, void* dx, float* dw_f32, void* dw_bf16, int accumulate,
-                                        long long rows, int d, int device, void* stream) {
-  if (d <= 0 || d % 8 != 0) return -3;
-  if (d > DEWB_NOALLOC_MAX_D) return DEWB_NOALLOC_ERR_TOO_LARGE;
-  if (device < 0 || device >= 64) return -3;
-  if (rows <= 0) return 0;
+namespace {
+// Makes `device` the current device for the lifetime of the object and puts the caller's device back afterwards, on
+// every return path: the address looked up below and the kernels launched with it must belong to the same device.
+struct NoallocDeviceScope {
+  int prev = -1;
+  int target;
+  cudaError_t err = cudaSuccess;
+  explicit NoallocDeviceScope(int device) : target(device) {
+    err = cudaGetDevice(&prev);
+    if (err == cudaSuccess && prev != target) err = cudaSetDevice(target);
+  }
+  ~NoallocDeviceScope() {
+    if (prev >= 0 && prev != target) cudaSetDevice(prev);
+  }
+};
+}  // namespace
+
+static int noalloc_body(const void* dy, const void* x, const void* w, const float* rstd, const void* dres, void* dx,
+                        float* dw_f32, void* dw_bf16, int accumulate, long long rows, int d, int device, void* stream) {
   if (g_noalloc_ptr[device] == nullptr) {
-    // one-time set-up for this device (not to be done under stream capture)
-    int cur = -1;
-    cudaError_t e = cudaGetDevice(&cur);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    if (cur != device && (e = cudaSetDevice(device)) != cudaSuccess) return static_cast<int>(e);
+    // one-time set-up for this device (not to be done under stream capture); `device` is current here
     float* p = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dw_partial);
-    if (cur != device) cudaSetDevice(cur);
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dw_partial);
     if (e != cudaSuccess || p == nullptr) return e != cudaSuccess ? static_cast<int>(e) : DEWB_NOALLOC_ERR_SYMBOL;
+    // concurrent first calls from several host threads all store the same value: the race is harmless
     g_noalloc_ptr[device] = p;
   }
   float* partial = g_noalloc_ptr[device];
@@ -1073,4 +1081,18 @@ extern "C" int dewb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const voi
   rmsnorm_dw_kernel<false><<<g, 256, 0, STREAM(stream)>>>((const bf16*)dy, (const bf16*)x, rstd, nullptr, partial, rows, d);
   colsum_kernel<<<(d + 255) / 256, 256, 0, STREAM(stream)>>>(partial, splits, d, dw_f32, (bf16*)dw_bf16, accumulate);
   return LAST_ERR();
+}
+
+extern "C" int dewb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                        const void* dres, void* dx, float* dw_f32, void* dw_bf16, int accumulate,
+                                        long long rows, int d, int device, void* stream) {
+  if (d <= 0 || d % 8 != 0) return -3;
+  if (d > DEWB_NOALLOC_MAX_D) return DEWB_NOALLOC_ERR_TOO_LARGE;
+  if (device < 0 || device >= 64) return -3;
+  if (rows <= 0) return 0;
+  // `device` stays current from the address look-up to the last launch, whatever device the caller had current;
+  // `stream` must be a stream of `device` (or null for its default stream)
+  NoallocDeviceScope scope(device);
+  if (scope.err != cudaSuccess) return static_cast<int>(scope.err);
+  return noalloc_body(dy, x, w, rstd, dres, dx, dw_f32, dw_bf16, accumulate, rows, d, device, stream);
 }

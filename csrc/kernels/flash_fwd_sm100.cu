@@ -18,7 +18,7 @@
 #include "../common/tmap.h"
 
 namespace dewb {
-namespace flash {
+namespace attnfwd {
 
 constexpr int BM = 128;        // query rows per CTA
 constexpr int BN = 128;        // keys per tile
@@ -413,14 +413,14 @@ static int make_qkv_map(CUtensorMap* m, const void* base, int B, int L, int H, i
 
 static int g_variant = 1;     // 0: P through shared memory, 1: P in tensor memory (default)
 
-}  // namespace flash
+}  // namespace attnfwd
 }  // namespace dewb
 
 // Selects the forward variant for later launches of this process (0: P through shared memory, 1: P in tensor memory);
 // returns the previous value.
 extern "C" int dewb_flash_set_variant(int variant) {
-  const int old = dewb::flash::g_variant;
-  dewb::flash::g_variant = variant;
+  const int old = dewb::attnfwd::g_variant;
+  dewb::attnfwd::g_variant = variant;
   return old;
 }
 
@@ -431,7 +431,7 @@ extern "C" int dewb_flash_fwd(const void* q, const void* k, const void* v, void*
                               long long k_ss, long long k_sh, long long v_sb, long long v_ss, long long v_sh,
                               long long o_sb, long long o_ss, long long o_sh, float scale, int causal, int* err,
                               void* stream_ptr) {
-  using namespace dewb::flash;
+  using namespace dewb::attnfwd;
   if (D != 128 && D != 64) return -3;
   if (Hq % Hkv != 0) return -3;
   if ((q_ss % 8) || (q_sh % 8) || (q_sb % 8) || (k_ss % 8) || (k_sh % 8) || (k_sb % 8) || (v_ss % 8) || (v_sh % 8) ||

@@ -249,12 +249,16 @@ class Checkpoints:
             payload = {"model": _to_cpu(model)}
             if not weights_only:
                 resume: Dict[str, Any] = {"key": int(state.key)}
-                for name in ("mu", "nu"):
-                    if name in state.opt_state:
-                        st = ST.to_stored(state.opt_state[name], self.kinds)
-                        resume.update({f"opt_state/{name}/params/{k}": v for k, v in st.items()})
+                # every tree of the optimizer state that mirrors the parameters (mu / nu, M3's slow / chunk / slow_direction,
+                # any later optimizer's) is stored leaf by leaf under the parameters' stored names; the rest (count, ...)
+                # as tensors or plain scalars
                 for k, v in state.opt_state.items():
-                    if k not in ("mu", "nu"):
+                    if k == "profiles":
+                        continue
+                    if isinstance(v, Mapping):
+                        st = ST.to_stored(v, self.kinds)
+                        resume.update({f"opt_state/{k}/params/{kk}": vv for kk, vv in st.items()})
+                    else:
                         resume[f"opt_state/{k}"] = v
                 if state.scale is not None:
                     resume.update({f"scale/{k}": v for k, v in flatten(state.scale).items()})
@@ -414,14 +418,23 @@ class Checkpoints:
             res = self._read_item(step, "resume")
             state.key = int(res.get("key", 0))
             opt: Dict[str, Any] = {}
-            for name in ("mu", "nu"):
-                pre = f"opt_state/{name}/params/"
-                st = {k[len(pre):]: v for k, v in res.items() if k.startswith(pre)}
-                if st:
-                    opt[name] = unflatten(conv(st))
+            trees: Dict[str, Dict[str, Any]] = {}
             for k, v in res.items():
-                if k.startswith("opt_state/") and not k.startswith(("opt_state/mu/", "opt_state/nu/")):
-                    opt[k[len("opt_state/"):]] = v
+                if not k.startswith("opt_state/"):
+                    continue
+                name, _, rest = k[len("opt_state/"):].partition("/")
+                if rest.startswith("params/"):
+                    trees.setdefault(name, {})[rest[len("params/"):]] = v
+                elif not rest:
+                    opt[name] = v
+            for name, st in trees.items():
+                # a tree that mirrors the parameters converts back through their stored names; a narrower one (a state
+                # kept for some leaves only) keeps the leaves it has
+                try:
+                    got = conv(st)
+                except KeyError:
+                    got = dict(st)
+                opt[name] = unflatten(got)
             state.opt_state = opt
             state.consumed = {k[len("consumed/"):]: int(v) for k, v in res.items() if k.startswith("consumed/")}
             sc = {k[len("scale/"):]: v for k, v in res.items() if k.startswith("scale/")}
@@ -435,10 +448,10 @@ class Checkpoints:
                 _copy_into(template.ema, state.ema)
                 state.ema = template.ema
             if template.opt_state and state.opt_state:
-                for name in ("mu", "nu"):
-                    if name in template.opt_state and name in state.opt_state:
-                        _copy_into(template.opt_state[name], state.opt_state[name])
-                        state.opt_state[name] = template.opt_state[name]
+                for name, tree in template.opt_state.items():
+                    if isinstance(tree, Mapping) and isinstance(state.opt_state.get(name), Mapping):
+                        _copy_into(tree, state.opt_state[name])
+                        state.opt_state[name] = tree
         return state
 
     def posthoc_ema(self, std: float, step: Optional[int] = None) -> Dict[str, Any]:

@@ -342,7 +342,20 @@ class CausalTransformer(nn.Module):
         """Forward FLOPs for ``tokens`` tokens in rows of ``seq_len`` (2 x params-in-matmuls x tokens + attention)."""
         cfg = self.config
         hd = cfg.head_dim or cfg.emb_features // cfg.num_heads
-        matmul_params = self.param_count(active=True) - self.embed.weight.numel() * (0 if cfg.tie_embeddings else 1)
+        # parameters that take part in a product per token: everything but the routed experts (of which a token visits
+        # top_k, whatever slice of them this rank holds under expert parallelism) and the embedding table (a lookup,
+        # unless it doubles as the head)
+        matmul_params = 0
+        for name, p in self.named_parameters():
+            if ".mlp.experts." in name or name == "tp_head":
+                continue
+            matmul_params += p.numel()
+        mix = cfg.mixture
+        if mix is not None:
+            sparse_layers = sum(1 for layer in self.layers if layer.sparse)
+            matmul_params += sparse_layers * mix.top_k * 3 * cfg.emb_features * (mix.expert_features or cfg.mlp_features or 4 * cfg.emb_features)
+        if not cfg.tie_embeddings:
+            matmul_params -= self.embed.weight.numel()
         n_attn = sum(1 for k in cfg.kinds() if k in ("attention", "local"))
         attn = n_attn * 2 * 2 * cfg.num_heads * hd * seq_len / 2          # causal: half the square
         return tokens * (2.0 * matmul_params + attn)

@@ -116,10 +116,15 @@ class LMObjective(Objective):
                 total = total + self.balance * extra["balance_loss"] * massf
         return Ratio(total, massf), aux
 
+    def uniform_mass(self, batch) -> bool:
+        """Whether every target of ``batch`` is scored, so that its mass follows from its shape alone (the same on every
+        rank that holds a batch of this shape)."""
+        return ("segments" not in batch and "loss_mask" not in batch and self.pad_id is None and not self.prefix
+                and not (self.loss_role is not None and "roles" in batch))
+
     def scored_tokens(self, batch):
         t = batch["tokens"]
-        if ("segments" not in batch and "loss_mask" not in batch and self.pad_id is None and not self.prefix
-                and not (self.loss_role is not None and "roles" in batch)):
+        if self.uniform_mass(batch):
             return int(t.shape[0] * (t.shape[1] - 1))        # every target is scored: no device read needed
         return int((self._targets(batch)[1] != -100).sum())
 

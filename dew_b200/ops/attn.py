@@ -47,6 +47,10 @@ _ATTN.kernels = [
 def _sdpa(q, k, v, causal, scale, window, softcap, sinks, segment_ids):
     if window is not None or softcap or sinks is not None or segment_ids is not None:
         from .functional import attention_reference
+        if q.is_cuda and q.shape[1] >= 2048:
+            import warnings
+            warnings.warn("attention with a window / soft-cap / sinks / packed segments that the sm_100a kernel refused runs "
+                          f"the O(S^2)-memory PyTorch path on the GPU (S = {q.shape[1]})", stacklevel=3)
         return attention_reference(q, k, v, causal, scale, window, softcap, sinks, segment_ids)
     qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
     o = F.scaled_dot_product_attention(qh, kh, vh, is_causal=causal and q.shape[1] > 1, scale=scale,

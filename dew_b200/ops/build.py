@@ -40,8 +40,9 @@ def sources() -> List[Path]:
 def _digest(path: Path) -> str:
     h = hashlib.sha256()
     h.update(path.read_bytes())
-    for hdr in sorted((CSRC / "common").glob("*")):
-        h.update(hdr.read_bytes())
+    for folder in ("common", "include"):                       # every header a kernel file may include
+        for hdr in sorted((CSRC / folder).glob("*")):
+            h.update(hdr.read_bytes())
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
     return h.hexdigest()[:16]
 

@@ -19,6 +19,13 @@ from typing import Any, Callable, Dict, Hashable, Optional, Sequence
 import torch
 
 _LOCK = threading.Lock()
+ENABLED: Optional[bool] = None          # set by ``enable``; None defers to the DEWB_TUNE environment variable
+
+
+def enable(on: bool = True) -> None:
+    """Let ``KernelOp.pick`` measure candidates it has no cached pick for (``Trainer(tune_kernels=True)`` calls this)."""
+    global ENABLED
+    ENABLED = bool(on)
 
 
 def default_path() -> str:
@@ -111,7 +118,8 @@ class KernelOp:
         if hit is not None and hit.get("choice") in candidates:
             self.picks[k] = hit["choice"]
             return hit["choice"]
-        tune = bool(int(os.environ.get("DEWB_TUNE", "0"))) if tune is None else tune
+        if tune is None:
+            tune = ENABLED if ENABLED is not None else bool(int(os.environ.get("DEWB_TUNE", "0")))
         if not tune or run is None:
             return candidates[0]
         timings: Dict[str, float] = {}

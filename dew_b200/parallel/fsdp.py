@@ -1,6 +1,8 @@
-"""FSDP engine: parameters, gradients and optimizer state sharded over the ``fsdp`` (and ``data``) axis.
+"""FSDP engine: optimizer state (fp32 masters, Adam moments, EMA) sharded over the ``fsdp`` (and ``data``) axis, with a
+resident gathered compute copy of the parameters and a full fp32 gradient accumulator on every rank.
 
-Design for one NVSwitch box with 180 GB per GPU (not a translation of a gather-per-layer ZeRO-3 schedule):
+In ZeRO terms this is stage 1-2 for memory (masters / moments / EMA are sharded, the bf16 parameters and the fp32
+gradient accumulators are not) with stage-3 placement of the update.  Design for one NVSwitch box with 180 GB per GPU:
 
 * A **unit** is the embedding, one decoder layer, or the final norm + head.  Each unit's parameters live in one flat
   bf16 buffer; each rank owns one contiguous *leading* shard of it (the reference's measured choice of leading-dim
@@ -14,7 +16,7 @@ Design for one NVSwitch box with 180 GB per GPU (not a translation of a gather-p
   with gradient clipping the kernel runs in two phases around a global-norm reduction.
 * ``world == 1`` is the same code with no peers, so 1-GPU and N-GPU runs share one path.
 
-Reference behaviour covered: FSDP / ZeRO-3 placement of params, grads, optimizer state and EMA
+Reference behaviour covered: sharded placement of masters, optimizer state and EMA
 (src/dew/distributed/placement.py:54-109), microbatch accumulation, skip_nonfinite, clip_grads, EMA
 (src/dew/training/transaction.py:1292-1392).
 """
@@ -135,6 +137,21 @@ class FSDPEngine:
         if self.built:
             return
         cfg = self.t.optimizer.config
+        # the fused kernel implements AdamW (decay on matrices, none on scales / biases / embeddings) with fp32 state; a run
+        # configured otherwise would silently train with a different rule, so it is refused here
+        refused = []
+        if cfg.optimizer not in ("adamw", "adam"):
+            refused.append(f"optimizer={cfg.optimizer!r} (the sharded update kernel implements adam / adamw)")
+        if cfg.param_groups:
+            refused.append("param_groups (per-group learning-rate scales / weight decay)")
+        if cfg.state_dtype != "float32":
+            refused.append(f"state_dtype={cfg.state_dtype!r} (moments are fp32)")
+        if tuple(cfg.spared) != tuple(type(cfg)().spared):
+            refused.append("a custom `spared` list (the kernel spares scales, biases, embeddings and sinks)")
+        if refused:
+            raise NotImplementedError("FSDPEngine does not support: " + "; ".join(refused) +
+                                      ". Use adamw with the default groups, or a mesh without fsdp / data sharding.")
+        self._adam_decay = cfg.weight_decay if cfg.optimizer == "adamw" else 0.0
         W = self.world
         seen = set()
         total = 0
@@ -423,13 +440,29 @@ class FSDPEngine:
         self._cleared.add(group)
         for index in self.groups[group]:
             u = self.units[index]
-            if self.cuda and self.world > 1 and self.seq > 0 and not u.local:
+            if self.cuda and self.world > 1 and self.seq > 0 and not u.local and getattr(self, "_synced_seq", -1) != self.seq:
                 L.check(L.load().dewb_wait_flags(L.ptr(self.flags.tensor), ctypes.c_int(index * 2 + SLOT_DONE),
                                                  ctypes.c_int(self.world), ctypes.c_uint(self.seq),
                                                  ctypes.c_ulonglong(self.wait_limit_ns), L.ptr(L.status(self.device)),
                                                  L.stream_ptr()), "wait_flags")
                 L.count_launches()
             self.grads_arena.tensor[u.offset:u.offset + u.size].zero_()
+
+    def _await_pushes(self) -> None:
+        """After a step: this rank's stream waits (bounded) until every peer's push of every unit's new weights has landed
+        in this rank's parameter arena, so whatever runs next on it - an evaluation, a preview, a checkpoint export, the
+        next step's first forward - reads whole weights of the new step.  One tiny kernel per sharded unit."""
+        if not (self.cuda and self.world > 1 and self.seq > 0):
+            return
+        lib = L.load()
+        for index, u in enumerate(self.units):
+            if u.local:
+                continue
+            L.check(lib.dewb_wait_flags(L.ptr(self.flags.tensor), ctypes.c_int(index * 2 + SLOT_DONE), ctypes.c_int(self.world),
+                                        ctypes.c_uint(self.seq), ctypes.c_ulonglong(self.wait_limit_ns),
+                                        L.ptr(L.status(self.device)), L.stream_ptr()), "wait_flags")
+            L.count_launches()
+        self._synced_seq = self.seq
 
     def _unit_backward_done(self, group: int) -> None:
         if not self._last_micro or group in self._launched:
@@ -458,7 +491,7 @@ class FSDPEngine:
         spec = self.t.objective.ema_spec()
         if spec is not None:
             ema_decay = spec.at(self._updates + 1)
-        vals = [self._lr, b1, b2, o.get("eps", 1e-8), cfg.weight_decay, 1 - b1 ** count, 1 - b2 ** count,
+        vals = [self._lr, b1, b2, o.get("eps", 1e-8), self._adam_decay, 1 - b1 ** count, 1 - b2 ** count,
                 self._grad_scale, ema_decay]
         return (ctypes.c_float * 9)(*vals)
 
@@ -560,9 +593,14 @@ class FSDPEngine:
         if mass_known is None or mass_known <= 0:
             mass_known = float(rows_per * len(parts))
         if self.world > 1:
-            mk = torch.tensor([mass_known], dtype=torch.float64, device=self.device)
-            dist.all_reduce(mk, group=self.group)
-            mass_known = float(mk.item())
+            uniform = getattr(obj, "uniform_mass", None)
+            if not hasattr(obj, "scored_tokens") or (callable(uniform) and all(uniform(mb) for mb in parts)):
+                # every rank scores the same number of targets (no padding, equal rows): no exchange, no host sync
+                mass_known = mass_known * self.world
+            else:
+                mk = torch.tensor([mass_known], dtype=torch.float64, device=self.device)
+                dist.all_reduce(mk, group=self.group)
+                mass_known = float(mk.item())
         self._grad_scale = 1.0 / max(mass_known, 1e-12)
         first = self.rank * rows_per * len(parts)
         for i, mb in enumerate(parts):
@@ -588,12 +626,19 @@ class FSDPEngine:
         if self.cuda:
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
         self.seq += 1
-        obj.apply_effects(state.variables, effects)
+        self._await_pushes()
+        # a step whose gradient norm was not finite changed nothing (the kernel left masters, moments and EMA alone): the
+        # update count and the EMA schedule do not advance either
+        skipped = bool(self._two_phase and cfg.skip_nonfinite and not math.isfinite(float(self.clip[0])))
+        if skipped:
+            info["skipped"] = True
+        else:
+            obj.apply_effects(state.variables, effects)
         new_opt = dict(state.opt_state)
-        new_opt["count"] = torch.tensor(self._count, dtype=torch.int64)
+        new_opt["count"] = torch.tensor(self._count - (1 if skipped else 0), dtype=torch.int64)
         rows_total = rows_per * len(parts) * self.world
-        new_state = state.replace(step=state.step + 1, microstep=state.microstep + len(parts), updates=state.updates + 1,
-                                  opt_state=new_opt,
+        new_state = state.replace(step=state.step + 1, microstep=state.microstep + len(parts),
+                                  updates=state.updates + (0 if skipped else 1), opt_state=new_opt,
                                   consumed={"examples": state.consumed.get("examples", 0) + rows_total,
                                             "tokens": state.consumed.get("tokens", 0) + int(obj.row_tokens(batch) or 0) * self.world})
         pooled = pool(stats_all)

@@ -1,6 +1,6 @@
 """Pipeline parallelism (GPipe): the layer stack is cut into ``stage`` consecutive groups, microbatches flow forward
 through the stages and gradients flow back, activations moving between neighbouring ranks with point-to-point sends and
-receives (NCCL p2p on GPUs, issued on a side stream so they overlap compute).
+receives (NCCL p2p on GPUs).
 
 Parity: src/dew/nn/backbones/decoder_stack.py:1468-1593 (``run_pipeline``: GPipe only - "Dew does not implement a 1F1B
 schedule", docs/concepts/distributed.md:256 - microbatch_count, stage-local optimizer state), src/dew/training/stages.py.

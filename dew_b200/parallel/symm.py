@@ -7,7 +7,13 @@ On one process, or on CPU ranks, a plain tensor stands in (world 1 has no peers)
 """
 from __future__ import annotations
 
+import os
 from typing import List, Optional
+
+# No rank of this library is ever bound to an NVLink multicast (NVLS) object: the kernels here use plain peer loads and
+# stores, and a rank that exits while its memory is bound to a multicast object can raise NVLink faults on its peers'
+# GPUs.  PyTorch reads this switch when it creates its first symmetric-memory block, i.e. after this import.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 import torch
 import torch.distributed as dist
@@ -35,10 +41,7 @@ class SymmetricBuffer:
             self.tensor = sm.empty(numel, dtype=dtype, device=dev)
             self.handle = sm.rendezvous(self.tensor, g)
             self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
-            try:
-                self.multicast_ptr = int(self.handle.multicast_ptr) if self.handle.has_multicast_support(dev.type, dev.index or 0) else 0
-            except Exception:
-                self.multicast_ptr = 0
+            self.multicast_ptr = 0          # multicast mappings are switched off (see the top of this file)
             if zero:
                 self.tensor.zero_()
             torch.cuda.synchronize(dev)

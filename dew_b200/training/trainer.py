@@ -155,7 +155,12 @@ class LocalEngine:
         ema = None
         if spec is not None:
             ema = {"params": tree_map(lambda x: x.detach().clone(), variables["params"])}
-        return TrainState(variables=variables, opt_state=opt_state, ema=ema, key=key)
+        scale = None
+        if t.dynamic_scale:
+            # loss scaling for narrow gradients: the loss is multiplied by `scale` before backward and the gradients divided by
+            # it; a step with a non-finite gradient is dropped and halves the scale, `growth_interval` good steps double it
+            scale = {"scale": torch.tensor(float(2 ** 15)), "good_steps": torch.tensor(0, dtype=torch.int64)}
+        return TrainState(variables=variables, opt_state=opt_state, ema=ema, key=key, scale=scale)
 
     def adopt(self, state: TrainState) -> TrainState:
         """Bind a restored state: the module's parameters take the state's values."""
@@ -210,6 +215,17 @@ class LocalEngine:
         new_opt, info = t.optimizer.update(state.variables["params"], unflatten(grads), state.opt_state,
                                            state.step, grad_scale=inv)
         skipped = bool(info.get("skipped", False))
+        new_scale = state.scale
+        if state.scale:
+            cur, good = float(state.scale["scale"]), int(state.scale["good_steps"])
+            if skipped:
+                cur, good = max(cur * 0.5, 1.0), 0
+            else:
+                good += 1
+                if good >= t.scale_growth_interval:
+                    cur, good = min(cur * 2.0, float(2 ** 24)), 0
+            new_scale = {"scale": torch.tensor(cur), "good_steps": torch.tensor(good, dtype=torch.int64)}
+            info["loss_scale"] = cur
         if not skipped and self.compute is not None:
             masters = flatten(state.variables["params"])
             with torch.no_grad():
@@ -224,7 +240,7 @@ class LocalEngine:
             ema_update(ema["params"], state.variables["params"], decay)
         rows_total = first
         new_state = state.replace(step=state.step + 1, microstep=state.microstep + len(parts),
-                                  updates=state.updates + (0 if skipped else 1), opt_state=new_opt, ema=ema,
+                                  updates=state.updates + (0 if skipped else 1), opt_state=new_opt, ema=ema, scale=new_scale,
                                   consumed={"examples": state.consumed.get("examples", 0) + rows_total,
                                             "tokens": state.consumed.get("tokens", 0) + int(obj.row_tokens(batch) or 0)})
         metrics = {"loss": pooled, **{k: pool(v) for k, v in metrics_all.items()}, **info}
@@ -257,6 +273,14 @@ class Trainer:
         self.mesh, self.layout = mesh, layout
         self.microbatches = microbatches if microbatches is not None else (accumulation if accumulation > 1 else None)
         self.dynamic_scale = dynamic_scale
+        self.scale_growth_interval = 2000
+        if dynamic_scale:
+            self.optimizer.config.skip_nonfinite = True      # an overflowed step must be dropped, not applied
+        if tune_kernels:
+            from ..ops import tuning
+            tuning.enable(True)
+        self.tune_kernels = tune_kernels
+        self._diloco_runner = None
         self.checkpoints, self.tracker = checkpoints, tracker
         self.custom_step = step
         self.profile = profile
@@ -372,6 +396,8 @@ class Trainer:
                     os.makedirs(self.profile.directory, exist_ok=True)
                     prof.export_chrome_trace(os.path.join(self.profile.directory, f"trace_{state.step}.json"))
                 prof = None
+            if self.diloco is not None:
+                self._diloco_step(state)
             window.append(m)
             if observe is not None:
                 observe(state, m)
@@ -413,6 +439,32 @@ class Trainer:
         self.optimizer.schedule = base_schedule
         return state
 
+    def _diloco_step(self, state: TrainState) -> None:
+        """DiLoCo: after every `every` inner steps the replicas along the mesh's ``diloco`` axis average how far they moved
+        and apply it with the outer optimizer; the compute copies are refreshed from the new masters."""
+        from ..parallel.diloco import DiLoCo, DiLoCoConfig
+        if self._diloco_runner is None:
+            cfg = self.diloco if isinstance(self.diloco, DiLoCoConfig) else DiLoCoConfig(**dict(self.diloco)) if isinstance(self.diloco, Mapping) else DiLoCoConfig()
+            eng = self.engine()
+            if hasattr(eng, "master"):
+                masters = [eng.master]                                   # the sharded engine's flat fp32 shard
+            else:
+                masters = [v for v in flatten(state.variables["params"]).values() if v.dtype.is_floating_point]
+            group = None
+            mesh = getattr(eng, "mesh", None)
+            if mesh is not None:
+                group = mesh.group("diloco")
+            self._diloco_runner = DiLoCo(masters, cfg, group=group)
+        if self._diloco_runner.after_inner_step():
+            eng = self.engine()
+            if hasattr(eng, "refresh_compute_copy"):
+                eng.refresh_compute_copy()
+            elif getattr(eng, "compute", None) is not None:
+                masters = flatten(state.variables["params"])
+                with torch.no_grad():
+                    for k, c in eng.compute.items():
+                        c.copy_(masters[k])
+
     def _save(self, state: TrainState, loader) -> None:
         pos = loader.position() if hasattr(loader, "position") else None
         last = next((h for h in reversed(self.history) if "loss" in h), {})
@@ -433,7 +485,7 @@ class Trainer:
                 break
             batch = _to_device(batch, self.objective.model)
             out = self.objective.evaluate(state.averaged if state.ema is not None else None, batch,
-                                          Step(step=state.step, key=K.fold_in(self.key, ("eval", i).__hash__() & 0xFFFF), train=False, device=dev))
+                                          Step(step=state.step, key=K.fold_in(K.fold_in(self.key, "eval"), i), train=False, device=dev))
             for k, v in out.items():
                 acc.setdefault(k, []).append(v)
         return {k: float(pool(v).value()) for k, v in acc.items() if v and hasattr(v[0], "value")}

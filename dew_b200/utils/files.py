@@ -25,7 +25,20 @@ def atomic_write_bytes(path: os.PathLike, data: bytes) -> None:
 
 
 def atomic_write_json(path: os.PathLike, value: Any) -> None:
-    atomic_write_bytes(path, json.dumps(value, indent=1, sort_keys=True, default=str).encode())
+    """Values JSON cannot express raise ``TypeError``: a tensor or an object written as its ``repr`` would read back as
+    a string and lose the state it stood for."""
+    atomic_write_bytes(path, json.dumps(value, indent=1, sort_keys=True, default=_plain).encode())
+
+
+def _plain(v: Any) -> Any:
+    # paths, sets / tuples and zero-dimensional numpy / torch numbers have one obvious JSON form; anything else is refused
+    if isinstance(v, Path):
+        return str(v)
+    if isinstance(v, (set, frozenset, tuple)):
+        return list(v)
+    if hasattr(v, "item") and getattr(v, "ndim", None) == 0:
+        return v.item()
+    raise TypeError(f"{type(v).__name__} is not JSON serialisable: store tensors in the item's tensor file")
 
 
 def read_json(path: os.PathLike) -> Any:

@@ -29,6 +29,7 @@ def test_fsdp_two_cpu_ranks_match_one_rank():
     for a, b in zip(one["losses"], two["losses"]):
         assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (one, two)
     assert abs(one["digest"] - two["digest"]) < 1e-3 * one["digest"]
+    assert one["arena_ok"] and two["arena_ok"]
 
 
 def test_fsdp_two_cpu_ranks_with_clipping():
@@ -38,15 +39,19 @@ def test_fsdp_two_cpu_ranks_with_clipping():
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-def test_fsdp_two_gpus_fused_kernel():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fsdp_gpus_fused_kernel(world):
+    """The fused reduce-scatter + AdamW + all-gather kernel on `world` GPUs against one GPU on the same global batch, and
+    the compute copy read straight after a step against the gathered masters."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     one = _run(1, "nccl", port=29621)
-    two = _run(2, "nccl", port=29622)
-    assert two["losses"][-1] < two["losses"][0]
-    for a, b in zip(one["losses"], two["losses"]):
-        assert abs(a - b) < 3e-2 * max(1.0, abs(a)), (one, two)
-    clipped = _run(2, "nccl", clip="0.5", port=29623)
+    many = _run(world, "nccl", port=29622 + world)
+    assert many["losses"][-1] < many["losses"][0] and many["arena_ok"]
+    for a, b in zip(one["losses"], many["losses"]):
+        assert abs(a - b) < 3e-2 * max(1.0, abs(a)), (one, many)
+    assert abs(one["digest"] - many["digest"]) < 5e-3 * one["digest"]
+    clipped = _run(world, "nccl", clip="0.5", port=29640 + world)
     assert clipped["losses"][-1] < clipped["losses"][0]
 
 

@@ -123,3 +123,43 @@ def test_console_tracker_lines():
     assert lines[2].startswith("step 30/30") and "eta 0:00:00" in lines[2]
     dew.Trackers(t, dew.MemoryTracker()).artifact(30, "grid", object())
     assert "artifact grid" in out.getvalue()
+
+
+@pytest.mark.parametrize("kind", ["m3", "muon", "normuon", "lion", "adamw"])
+def test_optimizer_state_of_every_kind_round_trips_through_a_checkpoint(tmp_path, kind):
+    """Every tensor tree of the optimizer state (M3's slow / chunk / slow_direction beside mu / nu) is stored as tensors
+    and comes back as tensors, so that the step after a resume equals the step of the run that was never stopped."""
+    import dew_b200 as dew
+    from dew_b200.models import CausalTransformer
+    from dew_b200.objectives.lm import LMObjective
+
+    def trainer(directory):
+        torch.manual_seed(0)
+        m = CausalTransformer(vocab_size=32, emb_features=16, num_layers=1, num_heads=2, num_kv_heads=2, head_dim=8, mlp_features=24, max_seq_len=8)
+        opts = {"frequency": 2} if kind == "m3" else {}
+        return dew.Trainer(LMObjective(m, 8, ema_decay=None), dew.OptimConfig(optimizer=kind, learning_rate=1e-3, optimizer_opts=opts), key=0,
+                           checkpoints=dew.Checkpoints(str(directory), keep=4))
+    g = torch.Generator().manual_seed(0)
+    data = [{"tokens": torch.randint(0, 32, (2, 9), generator=g)} for _ in range(5)]
+    whole = trainer(tmp_path / "whole").fit(list(data), steps=5, log_every=1000)
+    first = trainer(tmp_path / "cut")
+    first.fit(list(data), steps=3, log_every=1000)
+    first.checkpoints.wait()
+    restored = first.checkpoints.restore(None)
+    from dew_b200.utils.trees import flatten
+    for name, tree in restored.opt_state.items():
+        if isinstance(tree, dict):
+            assert all(isinstance(v, torch.Tensor) for v in flatten(tree).values()), name
+    resumed = trainer(tmp_path / "cut").fit(list(data[3:]), steps=5, log_every=1000)      # a list has no position: hand it the rest
+    a, b = flatten(whole.variables["params"]), flatten(resumed.variables["params"])
+    assert a.keys() == b.keys()
+    for k in a:
+        assert torch.equal(a[k], b[k]), (kind, k)
+
+
+def test_json_records_refuse_values_they_cannot_express(tmp_path):
+    from dew_b200.utils.files import atomic_write_json, read_json
+    atomic_write_json(tmp_path / "ok.json", {"a": torch.tensor(3), "b": (1, 2), "c": tmp_path})
+    assert read_json(tmp_path / "ok.json")["a"] == 3
+    with pytest.raises(TypeError):
+        atomic_write_json(tmp_path / "bad.json", {"a": torch.zeros(3)})

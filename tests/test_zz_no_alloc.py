@@ -71,7 +71,8 @@ def test_noalloc_entry_matches_ordinary_entry_twice_in_a_row():
     for (x, dy, dres, w, rstd), (dx, dw) in zip(cases, outs):          # two calls in a row, sharing the array
         assert _noalloc(lib, x, dy, dres, w, rstd, dx, dw) == 0
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before
+    assert torch.cuda.memory_allocated() == before     # sees torch's allocator only; that the library allocates nothing rests on its source
+    assert torch.cuda.current_device() == 0            # the call leaves the caller's current device as it found it
     for (x, dy, dres, w, rstd), (dx, dw) in zip(cases, outs):
         ref_dx, ref_dw = _ordinary(lib, x, dy, dres, w, rstd)
         torch.cuda.synchronize()

@@ -32,9 +32,9 @@ def main():
                               mlp_features=256, max_seq_len=128, qk_norm=False, tie_embeddings=False).to(dev)
     # every rank draws the same global batches and takes its own rows
     gen = torch.Generator().manual_seed(7)
-    fixed = torch.randint(0, 264, (8, 129), generator=gen)     # one global batch, repeated: the model memorises it
+    fixed = torch.randint(0, 264, (16, 129), generator=gen)     # one global batch, repeated: the model memorises it
     batches = [fixed for _ in range(6)]
-    per = 8 // world
+    per = 16 // world
     trainer = dew.Trainer(LMObjective(model, 128), dew.OptimConfig(learning_rate=2e-3, weight_decay=0.01, clip_grads=clip),
                           key=3, param_dtype=torch.bfloat16 if dev.type == "cuda" else None, microbatches=2)
     trainer.device = dev
@@ -49,14 +49,27 @@ def main():
         parts = torch.stack([stat.total.float(), stat.mass.float()]).to(dev)
         dist.all_reduce(parts)
         losses.append(float(parts[0] / parts[1]))
+    # straight after the step, with no synchronisation of its own: the compute copy this rank would evaluate with already
+    # holds every peer's new weights (compared below with the gathered masters)
+    arena_now = engine.params_arena.tensor.clone()
     if dev.type == "cuda":
         from dew_b200.ops import library as L
         torch.cuda.synchronize()
         L.check_status()
     full = engine.gather_full("master")
+    arena_ok = True
+    for u in engine.units:
+        for n, p in u.params:
+            o = u.offset + u.offsets[n]
+            from dew_b200.utils.trees import module_path_to_tree_path
+            want = full[module_path_to_tree_path(n)].to(arena_now.dtype).reshape(-1)
+            arena_ok = arena_ok and bool(torch.equal(arena_now[o:o + p.numel()], want.to(arena_now.device)))
+    ok = torch.tensor([1.0 if arena_ok else 0.0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    arena_ok = bool(ok.item() > 0)
     digest = float(sum(v.double().abs().sum() for v in full.values()))
     if rank == 0:
-        print("RESULT " + json.dumps({"losses": losses, "digest": digest, "world": world}))
+        print("RESULT " + json.dumps({"losses": losses, "digest": digest, "world": world, "arena_ok": arena_ok}))
     dist.barrier()
     dist.destroy_process_group()
 
