@@ -24,7 +24,10 @@ import time
 os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "1")
 
-BASELINE_TOK_S_PER_GPU = 190_000 / 8      # reference-equivalent mark for this config (8 x B200), per GPU
+# No like-for-like number is published for this configuration on B200s.  The mark below is derived (the reference's best
+# per-GPU rate for the same model class, 4 x H100 at 10.5 K tokens/s/GPU, scaled by the dense bf16 peak ratio 2250 / 989); it is
+# reported as `vs_derived_mark`, never as `vs_baseline`.
+DERIVED_MARK_TOK_S_PER_GPU = 190_000 / 8
 
 MODEL = dict(vocab_size=128256, emb_features=4096, num_layers=32, num_heads=32, num_kv_heads=8, head_dim=128,
              mlp_features=14336, max_seq_len=4096, rope_theta=500000.0, qk_norm=False, tie_embeddings=False,
@@ -117,6 +120,30 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def run_others(args, rank: int, local: int, world: int):
+    """Times 3 steps (after 3 warm-up steps, device-timed, no end-to-end pass) of the MoE and hybrid configurations at the same
+    number of GPUs, each in a fresh child process per rank, and returns ``{name: that run's JSON}``.  The MoE model (14 B
+    parameters with fp32 masters and moments) does not fit one GPU, so at one GPU it is reported as such."""
+    out = {}
+    base_port = int(os.environ.get("MASTER_PORT", "29500"))
+    for idx, name in enumerate(("moe", "hybrid")):
+        if name == "moe" and world == 1:
+            out[name] = {"unavailable": "14 B parameters x 18 bytes of training state do not fit one 180 GB GPU; measured from 2 GPUs up"}
+            continue
+        env = dict(os.environ, MASTER_PORT=str(base_port + 17 + idx), MASTER_ADDR=os.environ.get("MASTER_ADDR", "127.0.0.1"))
+        cmd = [sys.executable, os.path.abspath(__file__), "--config", name, "--gpus", str(world), "--steps", "3", "--warmup", "3",
+               "--skip-e2e", "--others", "none"]
+        try:
+            res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=420)
+            line = next((l for l in res.stdout.splitlines() if l.startswith("{")), None)
+            if rank == 0:
+                out[name] = json.loads(line) if line else {"failed": (res.stderr or res.stdout)[-400:]}
+        except Exception as e:  # a child that fails costs this key only, never the headline
+            if rank == 0:
+                out[name] = {"failed": f"{type(e).__name__}: {str(e)[:200]}"}
+    return out if rank == 0 else None
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -131,9 +158,26 @@ def main() -> None:
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="moe: token exchange by this library's peer-memory kernels (default) or by NCCL all-to-all (comparison arm)")
     ap.add_argument("--profile", default=None, help="write a torch.profiler kernel table for one step to this file")
+    ap.add_argument("--others", default="auto", choices=["auto", "none"],
+                    help="auto: the default (dense) run also times 3 steps of the moe and hybrid configurations in child processes "
+                         "and reports them under `others`")
+    ap.add_argument("--compile", action="store_true", help="torch_nccl arm only: torch.compile each decoder layer")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.impl == "torch_nccl":
+        # the library arm: stock PyTorch modules / cuBLAS / cuDNN SDPA / FSDP2 over NCCL, none of this framework's code
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+        import torch_arm
+        return torch_arm.main([a for a in sys.argv[1:] if a not in ("--impl", "torch_nccl")])
+    # no rank of this job binds its symmetric memory to an NVLink multicast object (set before the first rendezvous)
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+    # the other two training configurations run first, in child processes, while this process holds no device memory
+    others = None
+    if args.config == "dense" and args.others == "auto" and not args.layers:
+        others = run_others(args, int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")),
+                            int(os.environ.get("WORLD_SIZE", "1")))
 
     import torch
     import torch.distributed as dist
@@ -191,6 +235,11 @@ def main() -> None:
     n_batches = args.warmup + 2 * args.steps + 2
     host = [torch.randint(0, cfg["vocab_size"], (rows, SEQ_LEN + 1), generator=gen).pin_memory() for _ in range(n_batches)]
     device_batches = [{"tokens": h.to(dev)} for h in host[: args.warmup + args.steps]]
+    # the first warm-up step runs the SAME rows on every rank (rank 0's seed): each rank's own loss must then equal every
+    # other rank's, and equals what a one-GPU run of this script reports as `loss_first_step` (same seed, same weights)
+    first_rows = torch.randint(0, cfg["vocab_size"], (rows, SEQ_LEN + 1), generator=torch.Generator().manual_seed(1234))
+    device_batches[0] = {"tokens": first_rows.to(dev)}
+    loss_first = None
 
     def sync():
         torch.cuda.synchronize(dev)
@@ -213,6 +262,16 @@ def main() -> None:
                 p.grad = None
             torch.cuda.empty_cache()
             state, metrics = engine.step(state, device_batches[i])
+        if i == 0:
+            stat = metrics["loss"]
+            mine = (stat.total.float() / stat.mass.float()).reshape(1).to(dev)
+            loss_first = float(mine)
+            if world > 1:
+                every = [torch.empty_like(mine) for _ in range(world)]
+                dist.all_gather(every, mine)
+                spread = float(torch.stack(every).max() - torch.stack(every).min())
+                # identical rows and identical (gathered) weights: the ranks may differ by the rounding of their own kernels only
+                assert spread <= 2e-2 * max(1.0, abs(loss_first)), f"ranks disagree on the loss of identical rows: {[float(x) for x in every]}"
     sync()
     L.check_status()
     if args.profile:
@@ -277,23 +336,29 @@ def main() -> None:
                "ms_per_step": ms2 / args.steps}
         L.check_status()
 
+    peak_mem = torch.cuda.max_memory_allocated(dev) / 1e9
+    flops = model.model_flops(tokens_per_step // world, SEQ_LEN) * 3
     if rank == 0:
-        flops = model.model_flops(tokens_per_step // world, SEQ_LEN) * 3
         mfu = flops * args.steps / (ms / 1e3) / 2.25e15
+        l2_note = {"dense": "inputs larger than L2 (16 GB of weights stream every microbatch)",
+                   "moe": "inputs larger than L2 (expert and attention weights of 24 layers stream every microbatch)",
+                   "hybrid": "inputs larger than L2 (2.9 GB of weights and 8192-token activations stream every microbatch)"}[args.config]
         out = {
             "metric": conf["metric"], "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": value / (BASELINE_TOK_S_PER_GPU * world) if args.config == "dense" else None,
+            "scaling": "weak", "vs_baseline": None,
+            "vs_derived_mark": value / (DERIVED_MARK_TOK_S_PER_GPU * world) if args.config == "dense" else None,
             "dtype": "bf16" if args.config != "moe" else "bf16 (fp8 e4m3 expert GEMMs)",
             "data": "synthetic (uniform random token ids from a seed; random-init weights)",
             "config": {"model": conf["name"], "params": n_params,
                        "global_batch": rows * world, "seq_len": SEQ_LEN, "micro_batch": micro,
                        "parallelism": f"fsdp{world}" + (f"+ep{world} ({args.ep} exchange)" if args.config == "moe" else ""),
                        "optimizer": "AdamW fp32 masters+moments",
-                       "l2": "inputs larger than L2 (16 GB of weights stream every microbatch)",
-                       "baseline": "reference-equivalent mark 190K tok/s at 8xB200, scaled per GPU"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "loss": loss, "mfu_datasheet": mfu,
-            "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9, "impl": "dew_b200",
+                       "l2": l2_note,
+                       "baseline": "no published number for this configuration on B200 (vs_baseline null)" + (
+                           "; vs_derived_mark = value / (190K tok/s at 8 GPUs, scaled per GPU), a mark derived from the reference's 4xH100 rate" if args.config == "dense" else "")},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "loss": loss, "loss_first_step": loss_first,
+            "mfu_datasheet": mfu, "peak_mem_gb": peak_mem, "impl": "dew_b200", "others": others,
         }
         if args.layers:
             out["invalid"] = "debug run with fewer layers"

@@ -160,6 +160,12 @@ class DecoderLayer(nn.Module):
         """Add the pending branch into the stream and normalise; under tensor parallelism the branch is a partial sum
         and the all-reduce is fused with the add and the norm."""
         if self.tp is not None:
+            if getattr(self, "tp_training", False):
+                # training: the partial sums meet in an all-reduce autograd can differentiate; the normalised activations enter
+                # the next sharded product through the conjugate operator (its backward sums the partial input gradients)
+                from ..parallel.tp import copy_to_region, reduce_from_region
+                n, h = norm(h, reduce_from_region(branch, self.tp.group))
+                return copy_to_region(n, self.tp.group), h
             return self.tp.reduce_add_norm(branch, h, norm.weight, norm.eps)
         return norm(h, branch)
 
@@ -167,6 +173,9 @@ class DecoderLayer(nn.Module):
         """(stream, pending branch) -> (stream, pending branch); the branch is added by the next norm."""
         if branch is None:
             n = self.input_norm(h)
+            if self.tp is not None and getattr(self, "tp_training", False):
+                from ..parallel.tp import copy_to_region
+                n = copy_to_region(n, self.tp.group)
         else:
             n, h = self._norm(self.input_norm, h, branch)
         if self.kind in ("attention", "local", "mla"):
@@ -271,7 +280,10 @@ class CausalTransformer(nn.Module):
             else:
                 h, branch = layer(h, branch, cos, sin, positions, segment_ids, cache)
         tp = getattr(self, "tp", None)
-        if tp is not None:
+        if tp is not None and getattr(self, "tp_training", False):
+            from ..parallel.tp import reduce_from_region
+            n, _ = self.final_norm(h, reduce_from_region(branch, tp.group))
+        elif tp is not None:
             n, _ = tp.reduce_add_norm(branch, h, self.final_norm.weight, self.final_norm.eps)
         else:
             n, _ = self.final_norm(h, branch)

@@ -81,8 +81,18 @@ class LMObjective(Objective):
             w = named["embed.weight"] if self.model.head is None else named["head.weight"]
         tile = self.head_tile or max(1, (B * S + self.head_chunks - 1) // self.head_chunks)
         cap = getattr(self.model.config, "logit_softcap", 0.0)
-        total, mass = ops.linear_cross_entropy(hidden.reshape(B * S, d), w, targets.reshape(-1), ignore_index=-100,
-                                               z_loss=self.z_loss, softcap=cap, chunk=tile)
+        tp_head = getattr(self.model, "tp_head", None)
+        if tp_head is not None and getattr(self.model, "tp_training", False):
+            # vocabulary-parallel head: every tensor rank scores its slice of the vocabulary; maxima, sums and the target
+            # logit meet in all-reduces, and the hidden state's gradient is summed over the ranks in the backward
+            from ..parallel.sp_ops import vocab_parallel_cross_entropy
+            from ..parallel.tp import copy_to_region
+            group = self.model.tp.group
+            total, mass = vocab_parallel_cross_entropy(copy_to_region(hidden.reshape(B * S, d), group), tp_head,
+                                                       targets.reshape(-1), group=group, ignore_index=-100)
+        else:
+            total, mass = ops.linear_cross_entropy(hidden.reshape(B * S, d), w, targets.reshape(-1), ignore_index=-100,
+                                                   z_loss=self.z_loss, softcap=cap, chunk=tile)
         massf = mass.to(torch.float32)
         mtp_metrics = {}
         if self.mtp_weight and getattr(self.model, "mtp", None) is not None and variables is None:

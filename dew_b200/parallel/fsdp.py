@@ -105,12 +105,23 @@ class _Boundary(torch.autograd.Function):
 
 class FSDPEngine:
     def __init__(self, trainer, units: Optional[List[Tuple[str, List[nn.Module]]]] = None, group=None,
-                 wait_limit_s: float = 20.0, comm_blocks: int = 148):
+                 wait_limit_s: float = 20.0, comm_blocks: int = 148, replica_group=None, local_group=None,
+                 batch_ranks: Optional[int] = None, batch_index: Optional[int] = None, mesh=None):
+        """``group``: the ranks the state is sharded over.  ``replica_group`` (hybrid sharding): ranks that hold the same
+        shard on another replica of the sharded group; each unit's gradients are summed over it before the sharded update.
+        ``local_group``: the ranks over which rank-local (expert-parallel) units' gradients are summed - those that hold the
+        same experts and saw other rows.  ``batch_ranks`` / ``batch_index``: how many ranks see different rows of the global
+        batch, and this rank's index among them (defaults: the sharded group times the replicas)."""
         self.t = trainer
         self.model: nn.Module = trainer.objective.model
         self.group = group
+        self.mesh = mesh
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.replica_group, self.local_group = replica_group, local_group
+        self.replicas = dist.get_world_size(replica_group) if (replica_group is not None and dist.is_initialized()) else 1
+        self.batch_ranks = batch_ranks if batch_ranks is not None else self.world * self.replicas
+        self.batch_index = batch_index if batch_index is not None else self.rank
         self.wait_limit_ns = int(wait_limit_s * 1e9)
         self.comm_blocks = comm_blocks
         self.unit_modules = units or default_units(self.model)
@@ -157,6 +168,9 @@ class FSDPEngine:
         total = 0
         shard_total = 0
         self.groups: List[List[int]] = []
+        covered = {id(p) for _, mods in self.unit_modules for m in mods for p in m.parameters()}
+        # parameters held by the model itself rather than by one of the unit modules (a vocabulary-parallel head) join the last unit
+        leftovers = [(n, p) for n, p in self.model.named_parameters() if id(p) not in covered]
         for gi, (uname, mods) in enumerate(self.unit_modules):
             named: List[Tuple[str, nn.Parameter]] = []
             for m in mods:
@@ -166,6 +180,8 @@ class FSDPEngine:
                         continue
                     seen.add(id(p))
                     named.append(((prefix + "." + n) if prefix else n, p))
+            if gi == len(self.unit_modules) - 1:
+                named += leftovers
             # parameters that are already one rank's slice of an expert-parallel layer form a rank-local unit: their
             # gradients are complete on this rank (every token routed here contributed), so nothing is reduced or gathered
             shared = [(n, p) for n, p in named if not getattr(p, "expert_parallel", False)]
@@ -286,7 +302,7 @@ class FSDPEngine:
             seed = int(K.fold_in(key, "init")) & 0x7FFFFFFF                   # same seed on every rank
             meta = any(p.is_meta for p in self.model.parameters())
             # a model whose experts were already split over the ranks was initialised (same seed) before the split
-            presharded = any(getattr(p, "expert_parallel", False) for p in self.model.parameters())
+            presharded = any(getattr(p, "expert_parallel", False) or getattr(p, "tensor_parallel", False) for p in self.model.parameters())
             if not meta and not presharded:
                 reset_all(self.model, seed)
             self.build()
@@ -476,10 +492,26 @@ class FSDPEngine:
                 p.main_grad.add_(p.grad.to(torch.float32))
                 p.grad = None
 
+    def _sum_over(self, u: Unit, group) -> None:
+        """Sum the unit's fp32 gradient accumulator over ``group`` (NCCL / gloo all-reduce, on the communication stream on a
+        GPU so it overlaps the backward of earlier layers)."""
+        g = self.grads_arena.tensor[u.offset:u.offset + u.size]
+        if self.cuda:
+            self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self.comm_stream):
+                dist.all_reduce(g, group=group)
+        else:
+            dist.all_reduce(g, group=group)
+
     def _finalize_unit(self, group: int) -> None:
         self._launched.add(group)
         for index in self.groups[group]:
-            self._fold_autograd_grads(self.units[index])
+            u = self.units[index]
+            self._fold_autograd_grads(u)
+            if u.local and self.local_group is not None:
+                self._sum_over(u, self.local_group)
+            elif not u.local and self.replica_group is not None:
+                self._sum_over(u, self.replica_group)
             self._launch(index, mode=1 if self._two_phase else 0)
 
     def _hyper(self, u: Unit):
@@ -592,17 +624,19 @@ class FSDPEngine:
                 mass_known = None
         if mass_known is None or mass_known <= 0:
             mass_known = float(rows_per * len(parts))
-        if self.world > 1:
+        if self.batch_ranks > 1:
             uniform = getattr(obj, "uniform_mass", None)
             if not hasattr(obj, "scored_tokens") or (callable(uniform) and all(uniform(mb) for mb in parts)):
                 # every rank scores the same number of targets (no padding, equal rows): no exchange, no host sync
-                mass_known = mass_known * self.world
+                mass_known = mass_known * self.batch_ranks
             else:
                 mk = torch.tensor([mass_known], dtype=torch.float64, device=self.device)
                 dist.all_reduce(mk, group=self.group)
-                mass_known = float(mk.item())
+                if self.replica_group is not None:
+                    dist.all_reduce(mk, group=self.replica_group)
+                mass_known = float(mk.item()) * self.batch_ranks / (self.world * self.replicas)
         self._grad_scale = 1.0 / max(mass_known, 1e-12)
-        first = self.rank * rows_per * len(parts)
+        first = self.batch_index * rows_per * len(parts)
         for i, mb in enumerate(parts):
             self._first_micro = i == 0
             self._last_micro = i == len(parts) - 1
@@ -636,11 +670,11 @@ class FSDPEngine:
             obj.apply_effects(state.variables, effects)
         new_opt = dict(state.opt_state)
         new_opt["count"] = torch.tensor(self._count - (1 if skipped else 0), dtype=torch.int64)
-        rows_total = rows_per * len(parts) * self.world
+        rows_total = rows_per * len(parts) * self.batch_ranks
         new_state = state.replace(step=state.step + 1, microstep=state.microstep + len(parts),
                                   updates=state.updates + (0 if skipped else 1), opt_state=new_opt,
                                   consumed={"examples": state.consumed.get("examples", 0) + rows_total,
-                                            "tokens": state.consumed.get("tokens", 0) + int(obj.row_tokens(batch) or 0) * self.world})
+                                            "tokens": state.consumed.get("tokens", 0) + int(obj.row_tokens(batch) or 0) * self.batch_ranks})
         pooled = pool(stats_all)
         metrics = {"loss": pooled, **{k: pool(v) for k, v in metrics_all.items()}, **info}
         return new_state, metrics
@@ -651,6 +685,24 @@ class FSDPEngine:
         if self.cuda:
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
         local = self.sumsq.sum().reshape(1) * (self._grad_scale ** 2)
+        tensor_group = getattr(self, "tensor_group", None)
+        if tensor_group is not None:
+            # under tensor parallelism every tensor rank holds other slices of the sharded matrices but the SAME norm scales
+            # and embeddings: those are counted once, the sharded ones summed over the tensor ranks
+            rep = torch.zeros(1, dtype=torch.float32, device=self.device)
+            for u in self.units:
+                s_, lo_ = u.shard_size, u.rank * u.shard_size
+                for n, p in u.params:
+                    if getattr(p, "tensor_parallel", False):
+                        continue
+                    o = u.offsets[n]
+                    a, b = max(o, lo_), min(o + p.numel(), lo_ + s_)
+                    if a < b:
+                        rep += self.reduced[u.shard_offset + a - lo_: u.shard_offset + b - lo_].pow(2).sum()
+            rep = rep * (self._grad_scale ** 2)
+            sharded = local - rep
+            dist.all_reduce(sharded, group=tensor_group)
+            local = sharded + rep
         if self.world > 1:
             dist.all_reduce(local, group=self.group)
         norm = local.sqrt()

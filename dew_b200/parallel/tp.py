@@ -239,9 +239,11 @@ def _shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
     return w[:, rank * n:(rank + 1) * n].clone()
 
 
-def tensor_parallelize(model, tp: TensorParallel):
+def tensor_parallelize(model, tp: TensorParallel, training: bool = False):
     """Shard a ``CausalTransformer`` in place over ``tp``'s group. Heads, KV heads, MLP width and vocabulary must
-    divide by the group size."""
+    divide by the group size.  With ``training`` the vocabulary-parallel head is a trainable parameter and the layers run
+    the autograd-aware conjugate pair around their sharded products (identity forward / all-reduce backward in front of the
+    column-parallel projections, all-reduce forward / identity backward behind the row-parallel ones)."""
     W, r = tp.world, tp.rank
     cfg = model.config
     Hq, Hkv = cfg.num_heads, cfg.num_kv_heads or cfg.num_heads
@@ -270,10 +272,26 @@ def tensor_parallelize(model, tp: TensorParallel):
                 mlp.hidden = F_ // W
             layer.tp = tp
         head_w = model.head_weight().data
-        model.tp_head = nn.Parameter(_shard_rows(head_w, r, W), requires_grad=False)
+        model.tp_head = nn.Parameter(_shard_rows(head_w, r, W), requires_grad=training)
+        if training:
+            for attr in ("logical_axes", "dew_kind"):
+                src = model.head.weight if model.head is not None else model.embed.weight
+                if hasattr(src, attr):
+                    setattr(model.tp_head, attr, getattr(src, attr))
+            model.tp_head.dew_kind = "kernel"
         if model.head is not None:
             model.head = None
             model.config.tie_embeddings = True      # the full head is gone; logits come from `tp_head`
+    for layer in model.layers:
+        for mod, names in ((layer.mixer, ("qkv_proj", "o_proj")), (layer.mlp, ("gate_up_proj", "down_proj"))):
+            for nm in names:
+                lin = getattr(mod, nm, None)
+                if lin is not None:
+                    lin.weight.tensor_parallel = True          # this rank's slice: other tensor ranks hold the other slices
+    model.tp_head.tensor_parallel = True
     model.tp = tp
+    model.tp_training = training
+    for layer in model.layers:
+        layer.tp_training = training
     model.local_kv_heads = Hkv // W
     return model

@@ -5,7 +5,10 @@ src/dew/training/transaction.py (``Transaction.step`` :1766-1884: microbatch loo
 optimizer -> effects -> EMA -> skip_nonfinite).  The step itself is delegated to an *engine*:
 
 * ``LocalEngine``   one device; fp32 masters and a bf16 compute copy on a GPU, AdamW through the fused flat kernel
-* ``FSDPEngine``    (``dew_b200.parallel.fsdp``) ZeRO-3 shards with the fused reduce-scatter + AdamW kernel
+* ``FSDPEngine``    (``dew_b200.parallel.fsdp``) sharded masters / moments / EMA with the fused reduce-scatter + AdamW +
+                    all-gather kernel, a resident gathered compute copy and full fp32 gradient accumulators
+* ``PipelineEngine`` / ``DataParallelEngine`` and the compositions with tensor / expert parallelism:
+                    ``dew_b200.parallel.compose.build_engine`` turns ``Trainer(mesh=MeshSpec(...))`` into the engine
 """
 from __future__ import annotations
 
@@ -204,6 +207,9 @@ class LocalEngine:
             first += rows
         pooled = pool(stats_all)
         mass_f = float(mass_total)
+        sync = getattr(self, "grad_sync", None)
+        if sync is not None:
+            mass_f = sync(list(self.model.parameters()), mass_f)        # data parallelism: gradients and mass summed over the ranks
         inv = 1.0 / max(mass_f, 1e-12)
         if state.scale:
             inv /= float(state.scale["scale"])
@@ -295,15 +301,11 @@ class Trainer:
 
     # ------------------------------------------------------------------ engine / state
     def engine(self):
+        """The engine the mesh asks for, built once: every axis of ``MeshSpec`` (fsdp, data / replicas, tensor, expert, stage)
+        is composed by ``dew_b200.parallel.compose.build_engine``; without a mesh, or on one process, the local engine."""
         if self._engine is None:
-            world = 1
-            if self.mesh is not None:
-                world = getattr(self.mesh, "world", lambda: 1)()
-            if self.mesh is not None and world > 1 and (getattr(self.mesh, "fsdp", 1) > 1 or getattr(self.mesh, "data_size", lambda: 1)() > 1):
-                from ..parallel.fsdp import FSDPEngine
-                self._engine = FSDPEngine(self)
-            else:
-                self._engine = LocalEngine(self)
+            from ..parallel.compose import build_engine
+            self._engine = build_engine(self)
         return self._engine
 
     def _fresh_state(self) -> TrainState:
