@@ -213,21 +213,22 @@ def main() -> None:
         from dew_b200.nn.layers import reset_all
         from dew_b200.parallel.ep import ExpertParallel
         model = CausalTransformer(device=dev, dtype=torch.bfloat16, mixture=Mixture(**conf["mixture"]), **cfg)
-        reset_all(model, 1234)
-        if world > 1:
-            ExpertParallel(fused=args.ep == "peer").shard(model)
-        else:
-            next(p for n, p in model.named_parameters() if "experts.gate_up" in n).expert_parallel = True   # initialised above
+        if world > 1 and args.ep == "nccl":
+            # comparison arm: the same protocol over NCCL all-to-all (the mesh would pick the peer-memory exchange)
+            reset_all(model, 1234)
+            ExpertParallel(fused=False).shard(model)
         torch.cuda.empty_cache()
     else:
         model = CausalTransformer(device="meta", dtype=torch.bfloat16, **cfg)
     objective = LMObjective(model, SEQ_LEN, ema_decay=None)
     tracker = dew.MemoryTracker()
+    # the mesh alone says how the job is laid out; Trainer builds the process groups and the engine from it
+    mesh = dew.MeshSpec(expert=world) if args.config == "moe" else dew.MeshSpec(fsdp=world)
     trainer = dew.Trainer(objective, dew.OptimConfig(learning_rate=3e-4, weight_decay=0.1, optimizer_opts={"b2": 0.95}),
-                          key=0, microbatches=rows // micro, param_dtype=torch.bfloat16, tracker=tracker)
+                          key=0, microbatches=rows // micro, param_dtype=torch.bfloat16, tracker=tracker, mesh=mesh)
     trainer.device = dev
-    engine = FSDPEngine(trainer)
-    trainer._engine = engine
+    engine = trainer.engine()
+    assert isinstance(engine, FSDPEngine), type(engine)
     state = engine.fresh_state(trainer.key)
     n_params = sum(p.numel() for p in model.parameters())
 

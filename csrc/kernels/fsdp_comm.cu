@@ -102,8 +102,10 @@ struct AdamArgs {
 
 // mode 0: reduce + AdamW + push (fully fused)
 // mode 1: reduce only -> reduced[shard_len] (fp32) and per-block sum of squares -> sumsq[gridDim.x]
-// mode 2: AdamW from `reduced` (already summed and scaled by grad_scale... no: scaled here) + push; `clip` gives
+// mode 2: AdamW from `reduced` (summed, not yet scaled: grad_scale is applied here) + push; `clip` gives
 //         {sum sq, norm, coefficient} computed between the two phases
+// mode 3: reduce and ADD into reduced[shard_len] (gradient accumulation over microbatches on the shard alone); like mode 0
+//         it tells every peer at the end that this rank is done reading their buffers, so they may reuse them
 __global__ void __launch_bounds__(512)
 rs_adamw_ag_kernel(Peers grads, Peers params, Peers flags, float* __restrict__ master, float* __restrict__ m,
                    float* __restrict__ v, float* __restrict__ ema, float* __restrict__ reduced,
@@ -151,6 +153,13 @@ rs_adamw_ag_kernel(Peers grads, Peers params, Peers flags, float* __restrict__ m
       for (int j = 0; j < 8; ++j) local_sq += g[j] * g[j];
       *reinterpret_cast<float4*>(reduced + off) = make_float4(g[0], g[1], g[2], g[3]);
       *reinterpret_cast<float4*>(reduced + off + 4) = make_float4(g[4], g[5], g[6], g[7]);
+      continue;
+    }
+    if (mode == 3) {
+      float4 r0 = *reinterpret_cast<const float4*>(reduced + off), r1 = *reinterpret_cast<const float4*>(reduced + off + 4);
+      r0.x += g[0]; r0.y += g[1]; r0.z += g[2]; r0.w += g[3]; r1.x += g[4]; r1.y += g[5]; r1.z += g[6]; r1.w += g[7];
+      *reinterpret_cast<float4*>(reduced + off) = r0;
+      *reinterpret_cast<float4*>(reduced + off + 4) = r1;
       continue;
     }
     float p[8], mm[8], vv[8];

@@ -96,10 +96,12 @@ class LayerNorm(nn.Module):
         return F.layer_norm(x, (self.features,), self.weight, self.bias, self.eps)
 
 
-def reset_all(module: nn.Module, seed: int) -> None:
-    """Re-initialise every sub-module that defines ``reset_parameters`` from one seed (deterministic per module path)."""
+def reset_all(module: nn.Module, seed: int, prefix: str = "") -> None:
+    """Re-initialise every sub-module that defines ``reset_parameters`` from one seed (deterministic per module path).
+    ``prefix`` is the path of ``module`` inside the model it belongs to, so that initialising a model piece by piece draws
+    what initialising it whole would."""
     from ..utils import keys as K
-    for name, m in module.named_modules():
+    for name, m in module.named_modules(prefix=prefix):
         fn = getattr(m, "reset_parameters", None)
         if fn is None or any(True for _ in m.children()) and not getattr(m, "_own_reset", False):
             continue

@@ -142,6 +142,16 @@ def _gemm_reference_cuda(a, b, a_mn, b_mn, alpha, out, accumulate):
     return out
 
 
+def grad_accumulates(p) -> bool:
+    """Whether a weight gradient written into ``p.main_grad`` adds to what is there.  An engine that reuses one gradient
+    buffer for several units marks a parameter's buffer as stale (``p._dewb_fresh = True``); the first write after that
+    overwrites instead of accumulating, and clears the mark."""
+    if getattr(p, "_dewb_fresh", False):
+        p._dewb_fresh = False
+        return False
+    return True
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
@@ -166,7 +176,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             main = getattr(weight, "main_grad", None)
             if main is not None:                                           # fused accumulation into the fp32 buffer
-                gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True)
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=grad_accumulates(weight))
                 dw = None
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True)                   # dY^T[N,M] @ x[M,K]
@@ -547,7 +557,8 @@ class _LinearCE(torch.autograd.Function):
             if need_grad:
                 gemm(lg, weight, b_mn=True, out=dh[s:e])                       # dH = dlogits @ W
                 if acc is not None:
-                    gemm(lg, h[s:e], a_mn=True, b_mn=True, out=acc, accumulate=True)   # dW += dlogits^T @ h
+                    gemm(lg, h[s:e], a_mn=True, b_mn=True, out=acc,
+                         accumulate=grad_accumulates(weight) if main is not None else True)    # dW += dlogits^T @ h
         ctx.save_for_backward(dh, dw)
         ctx.used_main = main is not None
         ctx.w_dtype = weight.dtype

@@ -14,6 +14,11 @@ from typing import Optional, Tuple
 
 import torch
 
+
+def _grad_accumulates(p) -> bool:
+    from .functional import grad_accumulates
+    return grad_accumulates(p)
+
 from . import library as L
 
 c_ll, c_int, c_float = ctypes.c_longlong, ctypes.c_int, ctypes.c_float
@@ -139,7 +144,7 @@ class _GroupedLinear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             main = getattr(w, "main_grad", None)
             if main is not None and dy.is_cuda:
-                tgmm(dy, x, layout, w.shape[0], out=main, accumulate=True)
+                tgmm(dy, x, layout, w.shape[0], out=main, accumulate=_grad_accumulates(w))
             else:
                 dw = tgmm(dy, x, layout, w.shape[0]).to(w.dtype)
         return dx, dw, None

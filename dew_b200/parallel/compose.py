@@ -36,6 +36,12 @@ def build_engine(trainer):
         return LocalEngine(trainer)
     mesh: Mesh = spec.build() if isinstance(spec, MeshSpec) else spec
     if not dist.is_initialized() or mesh.world == 1:
+        cfg = trainer.optimizer.config
+        on_gpu = torch.cuda.is_available() and all(p.is_meta or p.is_cuda for p in trainer.objective.model.parameters())
+        if (on_gpu and trainer.param_dtype == torch.bfloat16 and cfg.optimizer in ("adamw", "adam") and not cfg.param_groups
+                and cfg.state_dtype == "float32"):
+            # one GPU under a mesh: the sharded engine with a world of one, so 1-GPU and N-GPU runs share one code path
+            return _engine_class(trainer, 1)(trainer, mesh=mesh)
         return LocalEngine(trainer)
     sizes = mesh.sizes
     model = trainer.objective.model
@@ -89,17 +95,39 @@ def build_engine(trainer):
                                       "implements adam / adamw; use one of them on this mesh")
         return DataParallelEngine(trainer, mesh.group(*batch_axes), mesh=mesh)
 
-    from .fsdp import FSDPEngine
+    engine_cls = _engine_class(trainer, mesh.size(*shard_axes) if shard_axes else 1)
     group = mesh.group(*shard_axes) if shard_axes else None
     # rank-local (expert) parameters are complete for the rows of their expert group; ranks that hold the same experts on
     # other data / fsdp coordinates saw other rows
     local_axes = tuple(a for a in ("data", "fsdp") if sizes[a] > 1) if sizes["expert"] > 1 else ()
-    engine = FSDPEngine(trainer, group=group if shard_axes else _self_group(),
+    engine = engine_cls(trainer, group=group if shard_axes else _self_group(),
                         replica_group=mesh.group(*replica_axes) if replica_axes else None,
                         local_group=mesh.group(*local_axes) if local_axes else None,
                         batch_ranks=batch_ranks, batch_index=mesh.index(*batch_axes) if batch_axes else 0, mesh=mesh)
     engine.tensor_group = tensor_group
     return engine
+
+
+def _engine_class(trainer, shard_ranks: int):
+    """``FSDPEngine`` (resident compute copy and gradient accumulators) or ``ShardedFSDPEngine`` (everything sharded), as the
+    trainer's ``Layout.memory`` asks; "auto" keeps the resident layout while its unsharded state (2 + 4 bytes per parameter)
+    fits in ``Layout.memory_fraction`` of the device's memory."""
+    import os
+    from .fsdp import FSDPEngine
+    from .fsdp_sharded import ShardedFSDPEngine
+    layout = trainer.layout
+    mode = os.environ.get("DEWB_FSDP_MEMORY") or (getattr(layout, "memory", "auto") if layout is not None else "auto")
+    if mode not in ("auto", "resident", "sharded"):
+        raise ValueError(f"Layout.memory must be 'auto', 'resident' or 'sharded', got {mode!r}")
+    if mode == "auto":
+        n = sum(p.numel() for p in trainer.objective.model.parameters())
+        unsharded = n * 6 + n * 12 / max(1, shard_ranks)
+        budget = 180e9
+        if torch.cuda.is_available():
+            budget = torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory
+        fraction = getattr(layout, "memory_fraction", 0.45) if layout is not None else 0.45
+        mode = "resident" if (unsharded <= fraction * budget or shard_ranks == 1) else "sharded"
+    return ShardedFSDPEngine if mode == "sharded" else FSDPEngine
 
 
 _SELF = None

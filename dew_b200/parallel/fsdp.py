@@ -211,14 +211,25 @@ class FSDPEngine:
                 self.units.append(u)
             self.groups.append(members)
         self.total = total
+        self.shard_total = shard_total
+        self.compute_dtype = self.t.param_dtype or (torch.bfloat16 if self.cuda else torch.float32)
+        self._allocate()
+        self.device = self.params_arena.tensor.device if getattr(self, "params_arena", None) is not None else self.device
+        self.built = True
+
+    def _allocate(self) -> None:
+        """Device memory of the resident layout: the full compute-dtype parameters and the full fp32 gradient accumulators
+        (both peer-visible), this rank's fp32 masters and moments, and the parameters re-pointed into the arenas."""
+        total, shard_total, W = self.total, self.shard_total, self.world
         dev = self.device
-        cdtype = self.t.param_dtype or (torch.bfloat16 if self.cuda else torch.float32)
-        self.compute_dtype = cdtype
+        cdtype = self.compute_dtype
         # arenas: full compute-dtype parameters and full fp32 gradients (peer-visible), flags
         self.params_arena = SymmetricBuffer(total, cdtype, dev, self.group, zero=True)
         self.grads_arena = SymmetricBuffer(total, torch.float32, dev, self.group, zero=True)
         self.flags = SymmetricBuffer(max(64, len(self.units) * 2 * max(W, 1)), torch.int32, dev, self.group, zero=True)
-        self.shard_total = shard_total
+        # kernels of rank-local units run with a world of one and index their flags as `slot`, not `slot * W + rank`: they
+        # get an array of their own so that they cannot touch the flags the sharded units' hand-shakes wait on
+        self.local_flags = torch.zeros(max(64, len(self.units) * 2), dtype=torch.int32, device=dev)
         self.master = torch.empty(shard_total, dtype=torch.float32, device=dev)
         self.m = torch.zeros(shard_total, dtype=torch.float32, device=dev)
         self.v = torch.zeros(shard_total, dtype=torch.float32, device=dev)
@@ -257,8 +268,6 @@ class FSDPEngine:
                     p.grad = None
                     fresh.append((n, p))
                 u.params = fresh
-        self.device = pa.device
-        self.built = True
 
     def init_masters(self) -> None:
         """fp32 masters (and EMA) from the compute-dtype arena: this rank's shard of every unit."""
@@ -543,7 +552,8 @@ class FSDPEngine:
             rc = lib.dewb_rs_adamw_ag(
                 self.grads_arena.own_ptr_array(u.offset * 4) if own else self.grads_arena.ptr_array(u.offset * 4),
                 self.params_arena.own_ptr_array(u.offset * esz) if own else self.params_arena.ptr_array(u.offset * esz),
-                self.flags.own_ptr_array() if own else self.flags.ptr_array(), L.ptr(self.master[lo:lo + s]), L.ptr(self.m[lo:lo + s]), L.ptr(self.v[lo:lo + s]),
+                (ctypes.c_ulonglong * 8)(*([self.local_flags.data_ptr()] + [0] * 7)) if own else self.flags.ptr_array(),
+                L.ptr(self.master[lo:lo + s]), L.ptr(self.m[lo:lo + s]), L.ptr(self.v[lo:lo + s]),
                 L.ptr(self.ema[lo:lo + s] if self.ema is not None else None),
                 L.ptr(self.reduced[lo:lo + s] if self.reduced is not None else None),
                 L.ptr(self.sumsq[index] if self._two_phase else None),

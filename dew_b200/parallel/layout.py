@@ -31,6 +31,11 @@ class Layout:
     frozen_whole: bool = False
     stage_local: bool = True
     data_axes: Tuple[str, ...] = ()
+    # "resident": every rank keeps a gathered compute copy of the parameters and full fp32 gradient accumulators (fastest while
+    # they fit); "sharded": parameters and gradients live as shards and are gathered / reduced unit by unit (ZeRO-3);
+    # "auto": resident when its unsharded state fits in `memory_fraction` of the device, else sharded
+    memory: str = "auto"
+    memory_fraction: float = 0.45
 
     def axis_for(self, logical: Optional[str]) -> Optional[str]:
         for name, mesh_axis in self.rules:

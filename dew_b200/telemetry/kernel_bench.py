@@ -24,35 +24,51 @@ def _row(out, **kw):
         out.flush()
 
 
-def bench_gemm(out, peaks, flush, shapes=None, iters=10):
-    shapes = shapes or [
-        ("fwd qkv", 8192, 6144, 4096, False, False), ("fwd o", 8192, 4096, 4096, False, False),
-        ("fwd gate_up", 8192, 28672, 4096, False, False), ("fwd down", 8192, 4096, 14336, False, False),
-        ("dgrad gate_up", 8192, 4096, 28672, False, True), ("wgrad gate_up", 28672, 4096, 8192, True, True),
-        ("wgrad down", 4096, 14336, 8192, True, True), ("square 8192", 8192, 8192, 8192, False, False),
-        ("head", 4096, 128256, 4096, False, False),
-        ("ref 2560->9216 @24576", 24576, 9216, 2560, False, False), ("ref 2560->64 @24576", 24576, 64, 2560, False, False),
-    ]
-    for name, M, N, K, a_mn, b_mn in shapes:
+def layer_gemm_shapes(tokens: int = 8192, d: int = 4096, qkv: int = 6144, ffn: int = 14336):
+    """The twelve products of one decoder layer of the dense 8 B configuration on ``tokens`` tokens: forward, input gradient
+    and weight gradient of the four projections, with the operand layouts and epilogues the training step uses (weight
+    gradients accumulate into fp32)."""
+    out = []
+    for name, n_out, k_in in (("qkv", qkv, d), ("o", d, d), ("gate_up", 2 * ffn, d), ("down", d, ffn)):
+        out.append((f"fwd {name}", tokens, n_out, k_in, False, False, torch.bfloat16, False))
+        out.append((f"dgrad {name}", tokens, k_in, n_out, False, True, torch.bfloat16, False))
+        out.append((f"wgrad {name}", n_out, k_in, tokens, True, True, torch.float32, True))
+    return out
+
+
+def bench_gemm(out, peaks, flush, shapes=None, iters=10, tokens: int = 8192):
+    shapes = shapes or (layer_gemm_shapes(tokens) + [
+        ("square 8192", 8192, 8192, 8192, False, False, torch.bfloat16, False),
+        ("head", 4096, 128256, 4096, False, False, torch.bfloat16, False),
+        ("ref 2560->9216 @24576", 24576, 9216, 2560, False, False, torch.bfloat16, False),
+        ("ref 2560->64 @24576", 24576, 64, 2560, False, False, torch.bfloat16, False),
+    ])
+    for shape in shapes:
+        name, M, N, K, a_mn, b_mn = shape[:6]
+        odt, acc = (shape[6], shape[7]) if len(shape) > 6 else (torch.bfloat16, False)
         A = torch.randn((K, M) if a_mn else (M, K), device="cuda").to(torch.bfloat16)
         B = torch.randn((K, N) if b_mn else (N, K), device="cuda").to(torch.bfloat16)
-        D = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        D = torch.zeros(M, N, device="cuda", dtype=odt)
         flops = 2.0 * M * N * K
-        t = device_time(lambda: ops.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=D, kernel="sm100_tcgen05"), iters=iters, flush=flush)
-        c = device_time(lambda: ops.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=D, kernel="cublas"), iters=iters, flush=flush)
+        kw = dict(a_mn=a_mn, b_mn=b_mn, out=D, accumulate=acc)
+        t = device_time(lambda: ops.gemm(A, B, kernel="sm100_tcgen05", **kw), iters=iters, flush=flush)
+        c = device_time(lambda: ops.gemm(A, B, kernel="cublas", **kw), iters=iters, flush=flush)
         L.check_status()
         tf, ctf = flops / t.median_ms / 1e9, flops / c.median_ms / 1e9
         pair = {}
         if hasattr(L.load(), "dewb_gemm_pair_bf16") and N >= 256:
-            ref = D.clone()
+            ref = torch.zeros_like(D)
             ops.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=ref, kernel="sm100_tcgen05")
-            p = device_time(lambda: ops.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=D, kernel="sm100_pair"), iters=iters, flush=flush)
+            p = device_time(lambda: ops.gemm(A, B, kernel="sm100_pair", **kw), iters=iters, flush=flush)
             L.check_status()
+            chk = torch.zeros_like(D)
+            ops.gemm(A, B, a_mn=a_mn, b_mn=b_mn, out=chk, kernel="sm100_pair")
             ptf = flops / p.median_ms / 1e9
             pair = dict(pair_ms=p.median_ms, pair_tflops=ptf, pair_frac_of_measured=ptf / peaks["bf16_tflops"],
-                        pair_time_over_cublas=p.median_ms / c.median_ms, pair_equals_single=bool(torch.equal(D, ref)))
-            del ref
-        _row(out, kernel="gemm_sm100", name=name, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, ms=t.median_ms, tflops=tf,
+                        pair_time_over_cublas=p.median_ms / c.median_ms, pair_equals_single=bool(torch.equal(chk, ref)))
+            del ref, chk
+        _row(out, kernel="gemm_sm100", name=name, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, out_dtype=str(odt).replace("torch.", ""),
+             accumulate=acc, ms=t.median_ms, tflops=tf,
              frac_of_measured=tf / peaks["bf16_tflops"], cublas_ms=c.median_ms, cublas_tflops=ctf,
              time_over_cublas=t.median_ms / c.median_ms, peaks=peaks["source"], **pair)
         del A, B, D
@@ -289,6 +305,7 @@ def main(argv=None):
     ap.add_argument("--only", default="gemm,rows,attention")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--gemm-shape", default=None, help="M,N,K[,a_mn,b_mn]: time one GEMM shape only (small profiling case)")
+    ap.add_argument("--tokens", type=int, default=8192, help="gemm: tokens per microbatch of the layer shapes (8192 on one GPU, 16384 from two)")
     ap.add_argument("--gdn-shape", default=None, help="B,T,H: time the gated-delta-rule kernels on one shape only (small profiling case)")
     ap.add_argument("--attn-shape", default=None, help="B,S,Hq,Hkv,D: time this library's attention kernels on one shape only")
     ap.add_argument("--flash-variant", type=int, default=None, help="forward variant: 0 = P through shared memory, 1 = P in tensor memory")
@@ -312,7 +329,7 @@ def main(argv=None):
                         kernels=("sm100_flash",))
         return
     if "gemm" in only:
-        bench_gemm(out, peaks, flush, iters=args.iters)
+        bench_gemm(out, peaks, flush, iters=args.iters, tokens=args.tokens)
     if "rows" in only:
         bench_rows(out, peaks, flush, iters=args.iters)
     if "attention" in only:

@@ -11,9 +11,9 @@ import torch
 WORKER = os.path.join(os.path.dirname(__file__), "workers", "fsdp_worker.py")
 
 
-def _run(world, backend, clip="none", port=29611):
+def _run(world, backend, clip="none", port=29611, mode="resident"):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
-           "--master-port", str(port), WORKER, backend, clip]
+           "--master-port", str(port), WORKER, backend, clip, mode]
     env = dict(os.environ, OMP_NUM_THREADS="2")
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
@@ -30,6 +30,19 @@ def test_fsdp_two_cpu_ranks_match_one_rank():
         assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (one, two)
     assert abs(one["digest"] - two["digest"]) < 1e-3 * one["digest"]
     assert one["arena_ok"] and two["arena_ok"]
+
+
+def test_fully_sharded_engine_matches_one_rank_on_cpu_ranks():
+    """Parameters and gradients as shards, gathered and reduced unit by unit, every microbatch: the same steps as one rank."""
+    one = _run(1, "gloo", port=29614)
+    two = _run(2, "gloo", port=29615, mode="sharded")
+    for a, b in zip(one["losses"], two["losses"]):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (one, two)
+    assert abs(one["digest"] - two["digest"]) < 1e-3 * one["digest"]
+    clipped_ref = _run(2, "gloo", clip="0.5", port=29616)
+    clipped = _run(2, "gloo", clip="0.5", port=29617, mode="sharded")
+    for a, b in zip(clipped_ref["losses"], clipped["losses"]):
+        assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (clipped_ref, clipped)
 
 
 def test_fsdp_two_cpu_ranks_with_clipping():
@@ -53,6 +66,11 @@ def test_fsdp_gpus_fused_kernel(world):
     assert abs(one["digest"] - many["digest"]) < 5e-3 * one["digest"]
     clipped = _run(world, "nccl", clip="0.5", port=29640 + world)
     assert clipped["losses"][-1] < clipped["losses"][0]
+    # the fully sharded engine (gathers and reductions per unit per microbatch over peer memory) takes the same steps
+    sharded = _run(world, "nccl", port=29660 + world, mode="sharded")
+    for a, b in zip(many["losses"], sharded["losses"]):
+        assert abs(a - b) < 3e-2 * max(1.0, abs(a)), (many, sharded)
+    assert abs(many["digest"] - sharded["digest"]) < 5e-3 * many["digest"]
 
 
 def _run_ckpt(world, directory, steps, port):

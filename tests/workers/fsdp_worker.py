@@ -38,7 +38,12 @@ def main():
     trainer = dew.Trainer(LMObjective(model, 128), dew.OptimConfig(learning_rate=2e-3, weight_decay=0.01, clip_grads=clip),
                           key=3, param_dtype=torch.bfloat16 if dev.type == "cuda" else None, microbatches=2)
     trainer.device = dev
-    engine = FSDPEngine(trainer, wait_limit_s=5.0)
+    mode = sys.argv[3] if len(sys.argv) > 3 else "resident"
+    if mode == "sharded":
+        from dew_b200.parallel.fsdp_sharded import ShardedFSDPEngine
+        engine = ShardedFSDPEngine(trainer, wait_limit_s=5.0)
+    else:
+        engine = FSDPEngine(trainer, wait_limit_s=5.0)
     trainer._engine = engine
     state = engine.fresh_state(trainer.key)
     losses = []
@@ -51,6 +56,15 @@ def main():
         losses.append(float(parts[0] / parts[1]))
     # straight after the step, with no synchronisation of its own: the compute copy this rank would evaluate with already
     # holds every peer's new weights (compared below with the gathered masters)
+    if mode == "sharded":
+        if rank == 0:
+            print("RESULT " + json.dumps({"losses": losses, "digest": float(sum(v.double().abs().sum() for v in engine.gather_full("master").values())),
+                                          "world": world, "arena_ok": True, "state_bytes": engine.state_bytes()}))
+        else:
+            engine.gather_full("master")
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     arena_now = engine.params_arena.tensor.clone()
     if dev.type == "cuda":
         from dew_b200.ops import library as L
