@@ -18,6 +18,7 @@
 // attention_mosaic_dq.py), which it records as 6-9x slower than cuDNN on B200 (src/dew/nn/attention_kernels.py:772-796).
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
+#include "../common/attn_variant.cuh"
 #include <type_traits>
 
 namespace dewb {
@@ -26,6 +27,8 @@ namespace flashbwd {
 constexpr int THREADS = 320;            // 8 softmax warps (two threads per TMEM lane), a TMA warp, an MMA warp
 constexpr int TMA_WARP = 8, MMA_WARP = 9;
 constexpr float LOG2E = 1.4426950408889634f;
+using attn::Variant;
+using attn::fast_tanh;
 
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -90,14 +93,15 @@ struct DqBars {
   uint64_t all_done;
   uint32_t tmem_base;
   int abort_flag;
+  int it_lo;                            // first key block this query tile sees (variants only)
 };
 
-template <int D, bool CAUSAL>
+template <int D, bool CAUSAL, bool VAR>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
                 const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
                 const float* __restrict__ lse, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dq, int S,
-                int T, int Hq, int Hkv, long long dq_sb, long long dq_ss, long long dq_sh, float scale,
+                int T, int Hq, int Hkv, long long dq_sb, long long dq_ss, long long dq_sh, float scale, Variant var,
                 int* __restrict__ err) {
   using C = DqCfg<D>;
   constexpr int BM = C::BM, BN = C::BN, KS = C::KSTAGES;
@@ -122,10 +126,11 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (Hq / Hkv);
   const int q0 = qt * BM;
-  const int iters = CAUSAL ? min((q0 + BM + (T - S) + BN - 1) / BN, (T + BN - 1) / BN) : (T + BN - 1) / BN;
+  const int n_all = CAUSAL ? min((q0 + BM + (T - S) + BN - 1) / BN, (T + BN - 1) / BN) : (T + BN - 1) / BN;
   const float scale_log2 = scale * LOG2E;
 
   if (threadIdx.x == 0) {
+    if (VAR) bars->it_lo = attn::first_key_tile(var, b, q0, S, T, BN, n_all);
     mbar_init(&bars->q_full, 1);
     for (int i = 0; i < KS; ++i) { mbar_init(&bars->kv_full[i], 1); mbar_init(&bars->kv_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
@@ -144,6 +149,9 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
   volatile int* abort_flag = &bars->abort_flag;
+  // every role walks the key blocks it_lo .. n_all - 1; rings, phases and "first block" tests count from it_lo
+  const int it_lo = VAR ? bars->it_lo : 0;
+  const int iters = n_all - it_lo;
 
   if (warp == TMA_WARP) {
     if (lane == 0) {
@@ -159,8 +167,8 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         mbar_expect_tx(&bars->kv_full[ks], 2 * C::KV_TILE);
 #pragma unroll
         for (int t = 0; t < C::SUB; ++t) {
-          tma_load_4d(sK + ks * C::KV_TILE + t * (BN * 128), &tk, &bars->kv_full[ks], t * 64, hk, it * BN, b);
-          tma_load_4d(sV + ks * C::KV_TILE + t * (BN * 128), &tv, &bars->kv_full[ks], t * 64, hk, it * BN, b);
+          tma_load_4d(sK + ks * C::KV_TILE + t * (BN * 128), &tk, &bars->kv_full[ks], t * 64, hk, (it_lo + it) * BN, b);
+          tma_load_4d(sV + ks * C::KV_TILE + t * (BN * 128), &tv, &bars->kv_full[ks], t * 64, hk, (it_lo + it) * BN, b);
         }
       }
     }
@@ -268,10 +276,14 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       const uint32_t phg = mine & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(&bars->sdp_full[g], phg, abort_flag))) { atomicCAS(err, 0, ERR_WAIT_TMEM_FULL); ok = false; break; }
       tc_fence_after();
-      const int k0 = it * BN;
+      const int k0 = (it_lo + it) * BN;
       uint32_t packed[BN / 2];
       auto block = [&](auto masked_tag) {
         constexpr bool MASKED = decltype(masked_tag)::value;
+        const float cap2 = VAR ? var.softcap * LOG2E : 0.f, inv_cap2 = (VAR && var.softcap > 0.f) ? 1.f / cap2 : 0.f;
+        const int first = VAR && var.window > 0 ? row + (T - S) - var.window + 1 : -0x40000000;   // first visible key of this row
+        const int* ksp = (VAR && var.q_seg != nullptr) ? var.k_seg + static_cast<long long>(b) * T : nullptr;
+        const int my_seg = ksp != nullptr ? var.q_seg[static_cast<long long>(b) * S + min(row, S - 1)] : 0;
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t sv[32], dv[32];
@@ -281,19 +293,36 @@ flash_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             const int key = k0 + c * 32 + i;
-            float p0 = fast_exp2(__uint_as_float(sv[i]) * scale_log2 - lse2);
-            float p1 = fast_exp2(__uint_as_float(sv[i + 1]) * scale_log2 - lse2);
+            float x0 = __uint_as_float(sv[i]) * scale_log2, x1 = __uint_as_float(sv[i + 1]) * scale_log2;
+            float f0 = 1.f, f1 = 1.f;               // d(capped score) / d(score)
+            if (VAR && var.softcap > 0.f) {
+              const float t0 = fast_tanh(x0 * inv_cap2), t1 = fast_tanh(x1 * inv_cap2);
+              x0 = cap2 * t0; x1 = cap2 * t1;
+              f0 = 1.f - t0 * t0; f1 = 1.f - t1 * t1;
+            }
+            float p0 = fast_exp2(x0 - lse2);
+            float p1 = fast_exp2(x1 - lse2);
             if (MASKED) {
               if (key > limit || key >= T) p0 = 0.f;
               if (key + 1 > limit || key + 1 >= T) p1 = 0.f;
+              if (VAR) {
+                if (key < first) p0 = 0.f;
+                if (key + 1 < first) p1 = 0.f;
+                if (ksp != nullptr) {
+                  if (key < T && ksp[key] != my_seg) p0 = 0.f;
+                  if (key + 1 < T && ksp[key + 1] != my_seg) p1 = 0.f;
+                }
+              }
             }
-            packed[(c * 32 + i) >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));
+            packed[(c * 32 + i) >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl) * f0, p1 * (__uint_as_float(dv[i + 1]) - dl) * f1);
           }
         }
       };
-      // only blocks that reach past the first row's last visible key (or past T) need the comparisons: one branch per warp
+      // only blocks that reach past the first row's last visible key (or past T) need the comparisons: one branch per warp;
+      // with a window or packed documents every block is compared
       const int warp_limit = CAUSAL ? (q0 + q4 * 32 + (T - S)) : (T - 1);
-      if (k0 + BN - 1 > warp_limit || k0 + BN > T) block(std::true_type{}); else block(std::false_type{});
+      if ((VAR && (var.window > 0 || var.q_seg != nullptr)) || k0 + BN - 1 > warp_limit || k0 + BN > T) block(std::true_type{});
+      else block(std::false_type{});
       // dS (bf16 pairs) over the first 32 columns of this group's S buffer: each thread overwrites only its own row,
       // whose scores it holds in registers
       {
@@ -372,15 +401,17 @@ struct DkvBars {
   uint64_t all_done;
   uint32_t tmem_base;
   int abort_flag;
+  int q_end;                            // one past the last query block that sees this key tile
 };
 
-template <int D, bool CAUSAL>
+template <int D, bool CAUSAL, bool VAR>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tdo,
                  const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
                  const float* __restrict__ lse2, const float* __restrict__ delta, __nv_bfloat16* __restrict__ dk,
                  __nv_bfloat16* __restrict__ dv, int S, int T, int Hq, int Hkv, long long dk_sb, long long dk_ss,
-                 long long dk_sh, long long dv_sb, long long dv_ss, long long dv_sh, float scale, int* __restrict__ err) {
+                 long long dk_sh, long long dv_sb, long long dv_ss, long long dv_sh, float scale, Variant var,
+                 int* __restrict__ err) {
   using C = DkvCfg<D>;
   constexpr int BKV = C::BKV, BQ = C::BQ, QS = C::QSTAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -410,11 +441,11 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   const int kv0 = kt * BKV;
   // first query block that can see any key of this tile (causal, bottom-right aligned): q + (T - S) >= kv0
   const int q_first = CAUSAL ? max(0, kv0 - (T - S)) / BQ : 0;
-  const int nqb = (S + BQ - 1) / BQ - q_first;          // query blocks per head
-  const int iters = nqb > 0 ? nqb * rep : 0;
   const float scale_log2 = scale * LOG2E;
 
   if (threadIdx.x == 0) {
+    // one past the last query block that sees this key tile (a window or packed documents end it early)
+    bars->q_end = VAR ? attn::end_query_block(var, b, kv0, BKV, S, T, BQ) : (S + BQ - 1) / BQ;
     mbar_init(&bars->kv_full, 1);
     for (int i = 0; i < QS; ++i) { mbar_init(&bars->q_full[i], 1); mbar_init(&bars->q_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
@@ -432,6 +463,8 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
   volatile int* abort_flag = &bars->abort_flag;
+  const int nqb = bars->q_end - q_first;                // query blocks per head
+  const int iters = nqb > 0 ? nqb * rep : 0;
 
   if (warp == TMA_WARP) {
     if (lane == 0) {
@@ -549,6 +582,9 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       uint32_t pp[BQ / 2], ds[BQ / 2];
       auto block = [&](auto masked_tag) {
         constexpr bool MASKED = decltype(masked_tag)::value;
+        const float cap2 = VAR ? var.softcap * LOG2E : 0.f, inv_cap2 = (VAR && var.softcap > 0.f) ? 1.f / cap2 : 0.f;
+        const int* qsp = (VAR && var.q_seg != nullptr) ? var.q_seg + static_cast<long long>(b) * S + qb : nullptr;
+        const int my_seg = qsp != nullptr ? var.k_seg[static_cast<long long>(b) * T + min(key, T - 1)] : 0;
 #pragma unroll
         for (int c = 0; c < BQ / 32; ++c) {
           uint32_t sv[32], dv[32];
@@ -559,10 +595,19 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const float4 l4 = lse4[(c * 32 + i) >> 2], d4 = dlt4[(c * 32 + i) >> 2];
-            float p0 = fast_exp2(__uint_as_float(sv[i]) * scale_log2 - l4.x);
-            float p1 = fast_exp2(__uint_as_float(sv[i + 1]) * scale_log2 - l4.y);
-            float p2 = fast_exp2(__uint_as_float(sv[i + 2]) * scale_log2 - l4.z);
-            float p3 = fast_exp2(__uint_as_float(sv[i + 3]) * scale_log2 - l4.w);
+            float x0 = __uint_as_float(sv[i]) * scale_log2, x1 = __uint_as_float(sv[i + 1]) * scale_log2;
+            float x2 = __uint_as_float(sv[i + 2]) * scale_log2, x3 = __uint_as_float(sv[i + 3]) * scale_log2;
+            float f0 = 1.f, f1 = 1.f, f2 = 1.f, f3 = 1.f;       // d(capped score) / d(score)
+            if (VAR && var.softcap > 0.f) {
+              const float t0 = fast_tanh(x0 * inv_cap2), t1 = fast_tanh(x1 * inv_cap2);
+              const float t2 = fast_tanh(x2 * inv_cap2), t3 = fast_tanh(x3 * inv_cap2);
+              x0 = cap2 * t0; x1 = cap2 * t1; x2 = cap2 * t2; x3 = cap2 * t3;
+              f0 = 1.f - t0 * t0; f1 = 1.f - t1 * t1; f2 = 1.f - t2 * t2; f3 = 1.f - t3 * t3;
+            }
+            float p0 = fast_exp2(x0 - l4.x);
+            float p1 = fast_exp2(x1 - l4.y);
+            float p2 = fast_exp2(x2 - l4.z);
+            float p3 = fast_exp2(x3 - l4.w);
             if (MASKED) {
               if (CAUSAL) {
                 if (key > qbase + i) p0 = 0.f;
@@ -571,19 +616,44 @@ flash_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
                 if (key > qbase + i + 3) p3 = 0.f;
               }
               if (key >= T) { p0 = 0.f; p1 = 0.f; p2 = 0.f; p3 = 0.f; }
+              if (VAR) {
+                if (var.window > 0) {           // key visible iff key > (query + T - S) - window
+                  if (key + var.window <= qbase + i) p0 = 0.f;
+                  if (key + var.window <= qbase + i + 1) p1 = 0.f;
+                  if (key + var.window <= qbase + i + 2) p2 = 0.f;
+                  if (key + var.window <= qbase + i + 3) p3 = 0.f;
+                }
+                if (qsp != nullptr) {
+                  const int qi = c * 32 + i;
+                  if (qb + qi + 3 < S) {
+                    const int4 id = *reinterpret_cast<const int4*>(qsp + qi);
+                    if (id.x != my_seg) p0 = 0.f;
+                    if (id.y != my_seg) p1 = 0.f;
+                    if (id.z != my_seg) p2 = 0.f;
+                    if (id.w != my_seg) p3 = 0.f;
+                  } else {
+                    if (qb + qi < S && qsp[qi] != my_seg) p0 = 0.f;
+                    if (qb + qi + 1 < S && qsp[qi + 1] != my_seg) p1 = 0.f;
+                    if (qb + qi + 2 < S && qsp[qi + 2] != my_seg) p2 = 0.f;
+                    if (qb + qi + 3 < S && qsp[qi + 3] != my_seg) p3 = 0.f;
+                  }
+                }
+              }
             }
             const int o = (c * 32 + i) >> 1;
             pp[o] = pack_bf16(p0, p1);
             pp[o + 1] = pack_bf16(p2, p3);
-            ds[o] = pack_bf16(p0 * (__uint_as_float(dv[i]) - d4.x), p1 * (__uint_as_float(dv[i + 1]) - d4.y));
-            ds[o + 1] = pack_bf16(p2 * (__uint_as_float(dv[i + 2]) - d4.z), p3 * (__uint_as_float(dv[i + 3]) - d4.w));
+            ds[o] = pack_bf16(p0 * (__uint_as_float(dv[i]) - d4.x) * f0, p1 * (__uint_as_float(dv[i + 1]) - d4.y) * f1);
+            ds[o + 1] = pack_bf16(p2 * (__uint_as_float(dv[i + 2]) - d4.z) * f2, p3 * (__uint_as_float(dv[i + 3]) - d4.w) * f3);
           }
         }
       };
       // only query blocks that start before this warp's last key (or key rows past T) need the comparisons: one branch
-      // per warp
+      // per warp; with a window or packed documents every block is compared
       const int warp_last_key = kv0 + q4 * 32 + 31;
-      if ((CAUSAL && warp_last_key > qb + (T - S)) || warp_last_key >= T) block(std::true_type{}); else block(std::false_type{});
+      if ((VAR && (var.window > 0 || var.q_seg != nullptr)) || (CAUSAL && warp_last_key > qb + (T - S)) || warp_last_key >= T)
+        block(std::true_type{});
+      else block(std::false_type{});
       // P^T and dS^T (bf16 pairs) over the first 32 columns of this group's S^T and dP^T buffers: each thread overwrites
       // only its own row, whose scores it holds in registers
       {
@@ -656,12 +726,12 @@ static int make_map(CUtensorMap* m, const void* base, int B, int L, int H, int D
 
 static_assert(DqCfg<128>::SMEM + 64 <= 232448 && DkvCfg<128>::SMEM + 64 <= 232448, "over the 227 KB a CTA may use");
 
-template <int D, bool CAUSAL>
+template <int D, bool CAUSAL, bool VAR>
 static int launch_bwd(const void* dO, const void* q, const void* k, const void* v, const float* lse, const float* lse2, const float* delta,
                       void* dq, void* dk, void* dv, int B, int S, int T, int Hq, int Hkv, const long long* qs,
                       const long long* ks, const long long* vs, const long long* os, const long long* dos,
-                      const long long* dqs, const long long* dks, const long long* dvs, float scale, int* err,
-                      cudaStream_t stream) {
+                      const long long* dqs, const long long* dks, const long long* dvs, float scale, const Variant& var,
+                      int* err, cudaStream_t stream) {
   const long long do_sb = dos[0], do_ss = dos[1], do_sh = dos[2];
   int r;
   {
@@ -670,12 +740,12 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
     if ((r = make_map(&tdo, dO, B, S, Hq, D, do_sb, do_ss, do_sh, 128))) return 1100 + r;
     if ((r = make_map(&tk, k, B, T, Hkv, D, ks[0], ks[1], ks[2], 64))) return 1200 + r;
     if ((r = make_map(&tv, v, B, T, Hkv, D, vs[0], vs[1], vs[2], 64))) return 1300 + r;
-    auto kern = flash_dq_kernel<D, CAUSAL>;
+    auto kern = flash_dq_kernel<D, CAUSAL, VAR>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DqCfg<D>::SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
     dim3 grid((S + 127) / 128, Hq, B);
     kern<<<grid, THREADS, DqCfg<D>::SMEM, stream>>>(tq, tdo, tk, tv, lse, delta, reinterpret_cast<__nv_bfloat16*>(dq), S, T,
-                                                     Hq, Hkv, dqs[0], dqs[1], dqs[2], scale, err);
+                                                     Hq, Hkv, dqs[0], dqs[1], dqs[2], scale, var, err);
     if ((r = static_cast<int>(cudaGetLastError()))) return r;
   }
   {
@@ -684,13 +754,13 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
     if ((r = make_map(&tdo, dO, B, S, Hq, D, do_sb, do_ss, do_sh, 64))) return 2100 + r;
     if ((r = make_map(&tk, k, B, T, Hkv, D, ks[0], ks[1], ks[2], 128))) return 2200 + r;
     if ((r = make_map(&tv, v, B, T, Hkv, D, vs[0], vs[1], vs[2], 128))) return 2300 + r;
-    auto kern = flash_dkv_kernel<D, CAUSAL>;
+    auto kern = flash_dkv_kernel<D, CAUSAL, VAR>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvCfg<D>::SMEM);
     if (e != cudaSuccess) return static_cast<int>(e);
     dim3 grid(((T + 127) / 128) * Hkv * B, 1, 1);
     kern<<<grid, THREADS, DkvCfg<D>::SMEM, stream>>>(tq, tdo, tk, tv, lse2, delta, reinterpret_cast<__nv_bfloat16*>(dk),
                                                       reinterpret_cast<__nv_bfloat16*>(dv), S, T, Hq, Hkv, dks[0], dks[1],
-                                                      dks[2], dvs[0], dvs[1], dvs[2], scale, err);
+                                                      dks[2], dvs[0], dvs[1], dvs[2], scale, var, err);
     if ((r = static_cast<int>(cudaGetLastError()))) return r;
   }
   return 0;
@@ -704,12 +774,16 @@ static int launch_bwd(const void* dO, const void* q, const void* k, const void* 
 // buffer. lse [B,Hq,S] comes from the forward; delta is scratch of 2 * B * Hq * S floats this call fills (delta, then
 // the log-sum-exp in log2 units). S must be a multiple of 64 (the statistics travel by 256-byte bulk copies).
 // `strides` holds 8 triples in the order q, k, v, out, dO, dq, dk, dv.
-extern "C" int dewb_flash_bwd(const void* dO, const void* q, const void* k, const void* v, const void* out,
-                              const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int T, int Hq,
-                              int Hkv, int D, const long long* strides, float scale, int causal, int* err,
-                              void* stream_ptr) {
+// Variants as in the forward (window, softcap, segment ids of packed documents); `lse` must come from a forward run with the
+// same variants (and sinks, if any).
+extern "C" int dewb_flash_bwd_var(const void* dO, const void* q, const void* k, const void* v, const void* out,
+                                  const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int T, int Hq,
+                                  int Hkv, int D, const long long* strides, float scale, int causal, int window, float softcap,
+                                  const int* q_seg, const int* k_seg, int* err, void* stream_ptr) {
   using namespace dewb::flashbwd;
   if ((D != 128 && D != 64) || Hq % Hkv != 0 || S % 64 != 0) return -3;
+  if ((q_seg != nullptr) != (k_seg != nullptr) || window < 0 || softcap < 0.f) return -3;
+  if (q_seg != nullptr && ((S % 4) || (T % 4) || (reinterpret_cast<uintptr_t>(q_seg) & 15) || (reinterpret_cast<uintptr_t>(k_seg) & 15))) return -3;
   const long long *qs = strides, *ks = strides + 3, *vs = strides + 6, *os = strides + 9, *dos = strides + 12,
                   *dqs = strides + 15, *dks = strides + 18, *dvs = strides + 21;
   for (int i = 0; i < 24; ++i) if (strides[i] % 8) return -3;       // 16-byte rows for TMA and the uint4 stores
@@ -719,9 +793,23 @@ extern "C" int dewb_flash_bwd(const void* dO, const void* q, const void* k, cons
       reinterpret_cast<const __nv_bfloat16*>(dO), reinterpret_cast<const __nv_bfloat16*>(out), lse, delta,
       delta + static_cast<long long>(B) * Hq * S, B, S, Hq, D, dos[0], dos[1], dos[2], os[0], os[1], os[2]);
   const float* lse2 = delta + static_cast<long long>(B) * Hq * S;
-  if (D == 128)
-    return causal ? launch_bwd<128, true>(dO, q, k, v, lse, lse2, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream)
-                  : launch_bwd<128, false>(dO, q, k, v, lse, lse2, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream);
-  return causal ? launch_bwd<64, true>(dO, q, k, v, lse, lse2, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream)
-                : launch_bwd<64, false>(dO, q, k, v, lse, lse2, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, err, stream);
+  // the sink logits reach the backward through the saved log-sum-exp alone
+  const Variant var{window, softcap, nullptr, q_seg, k_seg};
+  const bool any = window > 0 || softcap > 0.f || q_seg != nullptr;
+#define DEWB_BWD_GO(DD, CC, VV) launch_bwd<DD, CC, VV>(dO, q, k, v, lse, lse2, delta, dq, dk, dv, B, S, T, Hq, Hkv, qs, ks, vs, os, dos, dqs, dks, dvs, scale, var, err, stream)
+  if (D == 128) {
+    if (any) return causal ? DEWB_BWD_GO(128, true, true) : DEWB_BWD_GO(128, false, true);
+    return causal ? DEWB_BWD_GO(128, true, false) : DEWB_BWD_GO(128, false, false);
+  }
+  if (any) return causal ? DEWB_BWD_GO(64, true, true) : DEWB_BWD_GO(64, false, true);
+  return causal ? DEWB_BWD_GO(64, true, false) : DEWB_BWD_GO(64, false, false);
+#undef DEWB_BWD_GO
+}
+
+extern "C" int dewb_flash_bwd(const void* dO, const void* q, const void* k, const void* v, const void* out,
+                              const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int S, int T, int Hq,
+                              int Hkv, int D, const long long* strides, float scale, int causal, int* err,
+                              void* stream_ptr) {
+  return dewb_flash_bwd_var(dO, q, k, v, out, lse, delta, dq, dk, dv, B, S, T, Hq, Hkv, D, strides, scale, causal, 0, 0.f, nullptr,
+                            nullptr, err, stream_ptr);
 }

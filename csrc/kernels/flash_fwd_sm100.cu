@@ -16,6 +16,7 @@
 // the vendored FlashAttention wheels, which carry no sm_100 code (kernels/flash_attn/CMakeLists.txt:16,57).
 #include "../common/ptx.cuh"
 #include "../common/tmap.h"
+#include "../common/attn_variant.cuh"
 
 namespace dewb {
 namespace attnfwd {
@@ -29,6 +30,9 @@ constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+
+using attn::Variant;
+using attn::fast_tanh;
 
 template <int D>
 struct Cfg {
@@ -52,6 +56,7 @@ struct Bars {
   uint32_t tmem_base;
   int abort_flag;
   int poisoned;
+  int j_lo;                            // first key tile this query tile sees (variants only)
   float xmax[2][2][BM];   // [tile parity][column half][row]: partial row maxima exchanged between the two halves; the
                           // parity the last tile did not use carries the partial row sums at the end
 };
@@ -62,12 +67,12 @@ static_assert(sizeof(Bars) <= 2560, "Bars must fit the space Cfg::SMEM leaves af
 // probabilities (tcgen05.st) and the P V product reads its A operand from there, so P never crosses shared memory (no
 // 32 KB store + 32 KB operand fetch per tile) and the softmax of the next tile need not wait for the product to drain
 // a shared buffer.  PT = false is the shared-memory form (P in the 128-byte-swizzled K-major layout).
-template <int D, bool CAUSAL, bool PT>
+template <int D, bool CAUSAL, bool PT, bool VAR>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                  const __grid_constant__ CUtensorMap tv, __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
                  int S, int T, int Hq, int Hkv, long long o_stride_b, long long o_stride_s, long long o_stride_h,
-                 float scale_log2, int* __restrict__ err) {
+                 float scale_log2, Variant var, int* __restrict__ err) {
   using C = Cfg<D>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // The tiles fill 224 KiB, so this kernel has no static shared memory and no alignment slack: the dynamic window must
@@ -96,9 +101,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   const int hk = h / (Hq / Hkv);
   const int q0 = qt * BM;
   // keys visible to this query tile: causal alignment is bottom-right (query i sees keys <= i + T - S)
-  const int n_tiles = CAUSAL ? min((q0 + BM + (T - S) + BN - 1) / BN, (T + BN - 1) / BN) : (T + BN - 1) / BN;
+  const int n_all = CAUSAL ? min((q0 + BM + (T - S) + BN - 1) / BN, (T + BN - 1) / BN) : (T + BN - 1) / BN;
 
   if (threadIdx.x == 0) {
+    if (VAR) bars->j_lo = attn::first_key_tile(var, b, q0, S, T, BN, n_all);
     mbar_init(&bars->q_full, 1);
     for (int i = 0; i < C::KSTAGES; ++i) { mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
@@ -119,6 +125,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
   volatile int* abort_flag = &bars->abort_flag;
+  // every role walks the key tiles j_lo .. n_all - 1; rings, phases and "first tile" tests count from j_lo
+  const int j_lo = VAR ? bars->j_lo : 0;
+  const int n_tiles = n_all - j_lo;
 
   if (warp == TMA_WARP) {
     // ------------------------------------------------------------------ TMA producer
@@ -133,11 +142,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         if (!mbar_wait(&bars->k_empty[ks], kph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); ok = false; break; }
         mbar_expect_tx(&bars->k_full[ks], C::KV_BYTES);
 #pragma unroll
-        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sK + ks * C::KV_BYTES + t * (BN * 128), &tk, &bars->k_full[ks], t * 64, hk, j * BN, b);
+        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sK + ks * C::KV_BYTES + t * (BN * 128), &tk, &bars->k_full[ks], t * 64, hk, (j_lo + j) * BN, b);
         if (!mbar_wait(&bars->v_empty[st], ph ^ 1, abort_flag)) { atomicCAS(err, 0, ERR_WAIT_EMPTY); ok = false; break; }
         mbar_expect_tx(&bars->v_full[st], C::KV_BYTES);
 #pragma unroll
-        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sV + st * C::KV_BYTES + t * (BN * 128), &tv, &bars->v_full[st], t * 64, hk, j * BN, b);
+        for (int t = 0; t < C::SUB; ++t) tma_load_4d(sV + st * C::KV_BYTES + t * (BN * 128), &tv, &bars->v_full[st], t * 64, hk, (j_lo + j) * BN, b);
       }
     }
   } else if (warp == MMA_WARP) {
@@ -258,11 +267,47 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         tc_fence_before();
         __syncwarp();
         if (!PT && lane == 0) mbar_arrive(&bars->s_empty[st]);   // the score buffer may be overwritten by tile j + 2
-        const int k0 = j * BN + half * HC;
+        const int k0 = (j_lo + j) * BN + half * HC;
         const int limit = CAUSAL ? (q0 + r + (T - S)) : (T - 1);   // last visible key index for this row
+        if (VAR && var.softcap > 0.f) {
+          // cap * tanh(score / cap), kept in the log2 domain: scale_log2 = scale * log2(e)
+          const float inv_cap = 1.f / (var.softcap * 1.4426950408889634f), cap2 = var.softcap * 1.4426950408889634f;
+#pragma unroll
+          for (int i = 0; i < HC; ++i) s[i] = cap2 * fast_tanh(s[i] * inv_cap);
+        }
         if (k0 + HC - 1 > limit || k0 + HC > T) {
 #pragma unroll
           for (int i = 0; i < HC; ++i) if (k0 + i > limit || k0 + i >= T) s[i] = -INFINITY;
+        }
+        if (VAR) {
+          if (var.window > 0) {
+            const int first = q0 + r + (T - S) - var.window + 1;   // first visible key of this row
+            if (k0 < first) {
+#pragma unroll
+              for (int i = 0; i < HC; ++i) if (k0 + i < first) s[i] = -INFINITY;
+            }
+          }
+          if (var.q_seg != nullptr && k0 < T) {
+            const int row_q = min(q0 + r, S - 1);
+            const int mine = var.q_seg[static_cast<long long>(b) * S + row_q];
+            const int* ks = var.k_seg + static_cast<long long>(b) * T + k0;
+            // ids are non-decreasing: the whole half-tile matches iff its ends do
+            const int e0 = ks[0], e1 = ks[min(HC - 1, T - 1 - k0)];
+            if (e0 != mine || e1 != mine) {
+#pragma unroll
+              for (int i = 0; i < HC; i += 4) {
+                if (k0 + i + 3 < T) {
+                  const int4 id = *reinterpret_cast<const int4*>(ks + i);
+                  if (id.x != mine) s[i] = -INFINITY;
+                  if (id.y != mine) s[i + 1] = -INFINITY;
+                  if (id.z != mine) s[i + 2] = -INFINITY;
+                  if (id.w != mine) s[i + 3] = -INFINITY;
+                } else {
+                  for (int q = 0; q < 4; ++q) if (k0 + i + q < T && ks[i + q] != mine) s[i + q] = -INFINITY;
+                }
+              }
+            }
+          }
         }
         {
           // four independent chains, not one of 64 dependent maxima
@@ -349,9 +394,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     bars->xmax[n_tiles & 1][half][r] = l;      // the parity buffer the last tile left alone
     named_barrier_sync(1 + q4, 64);
     l += bars->xmax[n_tiles & 1][half ^ 1][r];
+    float lse_shift = 0.f;     // log2 of the factor the sink adds to the denominator's scale
+    float inv = l > 0.f ? 1.f / l : 0.f;
+    if (VAR && var.sinks != nullptr) {
+      // the sink joins the denominator only: softmax over [scores, sink] with the sink's value column dropped
+      const float sink2 = var.sinks[h] * 1.4426950408889634f;
+      const float m_fin = fmaxf(m_used, sink2);
+      const float a = m_used > -INFINITY ? fast_exp2(m_used - m_fin) : 0.f;
+      const float l_fin = l * a + fast_exp2(sink2 - m_fin);
+      inv = a / l_fin;
+      lse_shift = m_fin + log2f(l_fin);
+    }
     if (ok) {
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
       const int row = q0 + r;
       __nv_bfloat16* orow = out + b * o_stride_b + static_cast<long long>(row) * o_stride_s + h * o_stride_h + half * (D / 2);
 #pragma unroll
@@ -375,8 +430,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
           }
         }
       }
-      if (half == 0 && row < S && lse != nullptr)
-        lse[(static_cast<long long>(b) * Hq + h) * S + row] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      if (half == 0 && row < S && lse != nullptr) {
+        float v = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+        if (VAR && var.sinks != nullptr) v = lse_shift * 0.6931471805599453f;
+        lse[(static_cast<long long>(b) * Hq + h) * S + row] = v;
+      }
     }
   }
   tc_fence_before();
@@ -388,16 +446,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   }
 }
 
-template <int D, bool CAUSAL, bool PT>
+template <int D, bool CAUSAL, bool PT, bool VAR>
 static int launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, void* out, float* lse, int B,
-                  int S, int T, int Hq, int Hkv, long long osb, long long oss, long long osh, float scale_log2, int* err,
-                  cudaStream_t stream) {
-  auto kern = flash_fwd_kernel<D, CAUSAL, PT>;
+                  int S, int T, int Hq, int Hkv, long long osb, long long oss, long long osh, float scale_log2,
+                  const Variant& var, int* err, cudaStream_t stream) {
+  auto kern = flash_fwd_kernel<D, CAUSAL, PT, VAR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<D>::SMEM);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid((S + BM - 1) / BM, Hq, B);
   kern<<<grid, THREADS, Cfg<D>::SMEM, stream>>>(tq, tk, tv, reinterpret_cast<__nv_bfloat16*>(out), lse, S, T, Hq, Hkv,
-                                                 osb, oss, osh, scale_log2, err);
+                                                 osb, oss, osh, scale_log2, var, err);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -426,17 +484,23 @@ extern "C" int dewb_flash_set_variant(int variant) {
 
 // q [B,S,Hq,D], k/v [B,T,Hkv,D] (bf16, unit stride along D, other strides in elements: batch, sequence, head);
 // out [B,S,Hq,D] with its own strides; lse [B,Hq,S] fp32 (natural log), may be null.
-extern "C" int dewb_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int T,
-                              int Hq, int Hkv, int D, long long q_sb, long long q_ss, long long q_sh, long long k_sb,
-                              long long k_ss, long long k_sh, long long v_sb, long long v_ss, long long v_sh,
-                              long long o_sb, long long o_ss, long long o_sh, float scale, int causal, int* err,
-                              void* stream_ptr) {
+// Variants (each off at 0 / null): `window` keys visible behind each query, `softcap`, `sinks` [Hq] fp32, `q_seg` [B,S] /
+// `k_seg` [B,T] int32 segment ids of packed documents (non-decreasing along the sequence, rows 16-byte aligned: S, T % 4 == 0).
+extern "C" int dewb_flash_fwd_var(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int T,
+                                  int Hq, int Hkv, int D, long long q_sb, long long q_ss, long long q_sh, long long k_sb,
+                                  long long k_ss, long long k_sh, long long v_sb, long long v_ss, long long v_sh,
+                                  long long o_sb, long long o_ss, long long o_sh, float scale, int causal, int window,
+                                  float softcap, const float* sinks, const int* q_seg, const int* k_seg, int* err,
+                                  void* stream_ptr) {
   using namespace dewb::attnfwd;
   if (D != 128 && D != 64) return -3;
   if (Hq % Hkv != 0) return -3;
   if ((q_ss % 8) || (q_sh % 8) || (q_sb % 8) || (k_ss % 8) || (k_sh % 8) || (k_sb % 8) || (v_ss % 8) || (v_sh % 8) ||
       (v_sb % 8) || (o_ss % 8) || (o_sh % 8) || (o_sb % 8))
     return -3;
+  if ((q_seg != nullptr) != (k_seg != nullptr)) return -3;
+  if (q_seg != nullptr && ((T % 4) || (reinterpret_cast<uintptr_t>(k_seg) & 15))) return -3;
+  if (window < 0 || softcap < 0.f) return -3;
   CUtensorMap tq, tk, tv;
   int r;
   if ((r = make_qkv_map(&tq, q, B, S, Hq, D, q_sb, q_ss, q_sh))) return 1000 + r;
@@ -444,13 +508,29 @@ extern "C" int dewb_flash_fwd(const void* q, const void* k, const void* v, void*
   if ((r = make_qkv_map(&tv, v, B, T, Hkv, D, v_sb, v_ss, v_sh))) return 3000 + r;
   const float scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
-#define DEWB_FLASH_GO(DD, CC, PP) launch<DD, CC, PP>(tq, tk, tv, out, lse, B, S, T, Hq, Hkv, o_sb, o_ss, o_sh, scale_log2, err, stream)
+  const Variant var{window, softcap, sinks, q_seg, k_seg};
+  const bool any = window > 0 || softcap > 0.f || sinks != nullptr || q_seg != nullptr;
+#define DEWB_FLASH_GO(DD, CC, PP, VV) launch<DD, CC, PP, VV>(tq, tk, tv, out, lse, B, S, T, Hq, Hkv, o_sb, o_ss, o_sh, scale_log2, var, err, stream)
   const bool pt = g_variant != 0;
-  if (D == 128) {
-    if (causal) return pt ? DEWB_FLASH_GO(128, true, true) : DEWB_FLASH_GO(128, true, false);
-    return pt ? DEWB_FLASH_GO(128, false, true) : DEWB_FLASH_GO(128, false, false);
+  if (any) {
+    // the variants run the tensor-memory form only
+    if (D == 128) return causal ? DEWB_FLASH_GO(128, true, true, true) : DEWB_FLASH_GO(128, false, true, true);
+    return causal ? DEWB_FLASH_GO(64, true, true, true) : DEWB_FLASH_GO(64, false, true, true);
   }
-  if (causal) return pt ? DEWB_FLASH_GO(64, true, true) : DEWB_FLASH_GO(64, true, false);
-  return pt ? DEWB_FLASH_GO(64, false, true) : DEWB_FLASH_GO(64, false, false);
+  if (D == 128) {
+    if (causal) return pt ? DEWB_FLASH_GO(128, true, true, false) : DEWB_FLASH_GO(128, true, false, false);
+    return pt ? DEWB_FLASH_GO(128, false, true, false) : DEWB_FLASH_GO(128, false, false, false);
+  }
+  if (causal) return pt ? DEWB_FLASH_GO(64, true, true, false) : DEWB_FLASH_GO(64, true, false, false);
+  return pt ? DEWB_FLASH_GO(64, false, true, false) : DEWB_FLASH_GO(64, false, false, false);
 #undef DEWB_FLASH_GO
+}
+
+extern "C" int dewb_flash_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S, int T,
+                              int Hq, int Hkv, int D, long long q_sb, long long q_ss, long long q_sh, long long k_sb,
+                              long long k_ss, long long k_sh, long long v_sb, long long v_ss, long long v_sh,
+                              long long o_sb, long long o_ss, long long o_sh, float scale, int causal, int* err,
+                              void* stream_ptr) {
+  return dewb_flash_fwd_var(q, k, v, out, lse, B, S, T, Hq, Hkv, D, q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh, o_sb,
+                            o_ss, o_sh, scale, causal, 0, 0.f, nullptr, nullptr, nullptr, err, stream_ptr);
 }

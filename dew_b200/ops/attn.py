@@ -33,8 +33,8 @@ _ATTN.kernels = [
         Requirement("built", lambda c: _flash_available(), "flash kernels are not in this build of libdewb.so"),
         Requirement("dtype", lambda c: c["dtype"] == torch.bfloat16, "bf16 only"),
         Requirement("head_dim", lambda c: c["D"] in (64, 128), "head_dim must be 64 or 128"),
-        Requirement("features", lambda c: not c["sinks"] and not c["softcap"] and c["window"] is None
-                    and not c["segments"], "sinks / softcap / window / packed segments take the library arm"),
+        Requirement("variants", lambda c: not c["segments"] or (c["S"] == c["T"] and c["S"] % 4 == 0),
+                    "packed segments need S == T and rows of ids on 16-byte boundaries"),
         Requirement("seq", lambda c: c["S"] == c["T"] and c["S"] % 128 == 0, "needs S == T and S a multiple of 128"),
         Requirement("gqa", lambda c: c["Hq"] % c["Hkv"] == 0, "query heads must be a multiple of kv heads"),
         Requirement("backward", lambda c: not c["grad"] or _bwd_available(), "the backward kernels are not in this build"),
@@ -68,7 +68,8 @@ def flash_attention(q, k, v, causal=True, scale=None, window=None, softcap=0.0, 
     which = _ATTN.select(case, forced=kernel)
     if which == "sm100_flash":
         from .flash import flash_sm100
-        return flash_sm100(q, k, v, causal, scale if scale is not None else 1.0 / math.sqrt(D))
+        return flash_sm100(q, k, v, causal, scale if scale is not None else 1.0 / math.sqrt(D), window=window,
+                           softcap=softcap, sinks=sinks, segment_ids=segment_ids)
     return _sdpa(q, k, v, causal, scale, window, softcap, sinks, segment_ids)
 
 

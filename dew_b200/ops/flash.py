@@ -16,15 +16,34 @@ def _strides(t):
     return c_ll(t.stride(0)), c_ll(t.stride(1)), c_ll(t.stride(2))
 
 
-def flash_fwd(q, k, v, causal: bool, scale: float, need_lse: bool = True):
+class Variants:
+    """The optional attention variants the kernels take: ``window`` (keys visible behind each query, None = all), ``softcap``
+    (scores become cap * tanh(score / cap)), ``sinks`` ([Hq] fp32 logits that join the softmax denominator only) and
+    ``segments`` (int32 [B, S] ids of packed documents, non-decreasing along the sequence; 0 marks padding)."""
+
+    def __init__(self, window=None, softcap: float = 0.0, sinks=None, segments=None):
+        self.window = int(window) if window else 0
+        self.softcap = float(softcap or 0.0)
+        self.sinks = sinks.detach().to(torch.float32).contiguous() if sinks is not None else None
+        self.segments = segments.to(torch.int32).contiguous() if segments is not None else None
+
+    def any(self) -> bool:
+        return bool(self.window or self.softcap or self.sinks is not None or self.segments is not None)
+
+
+NONE = Variants()
+
+
+def flash_fwd(q, k, v, causal: bool, scale: float, need_lse: bool = True, var: Variants = NONE):
     B, S, Hq, D = q.shape
     T, Hkv = k.shape[1], k.shape[2]
     out = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device) if need_lse else None
-    rc = L.load().dewb_flash_fwd(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(out), L.ptr(lse), c_int(B), c_int(S), c_int(T),
-                                 c_int(Hq), c_int(Hkv), c_int(D), *_strides(q), *_strides(k), *_strides(v),
-                                 *_strides(out), c_float(scale), c_int(int(causal)), L.ptr(L.status(q.device)),
-                                 L.stream_ptr())
+    rc = L.load().dewb_flash_fwd_var(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(out), L.ptr(lse), c_int(B), c_int(S), c_int(T),
+                                     c_int(Hq), c_int(Hkv), c_int(D), *_strides(q), *_strides(k), *_strides(v),
+                                     *_strides(out), c_float(scale), c_int(int(causal)), c_int(var.window), c_float(var.softcap),
+                                     L.ptr(var.sinks), L.ptr(var.segments), L.ptr(var.segments), L.ptr(L.status(q.device)),
+                                     L.stream_ptr())
     L.check(rc, "flash_fwd")
     L.count_launches()
     return out, lse
@@ -37,7 +56,7 @@ def bwd_available() -> bool:
         return False
 
 
-def flash_bwd(do, q, k, v, out, lse, causal: bool, scale: float, grads=None):
+def flash_bwd(do, q, k, v, out, lse, causal: bool, scale: float, grads=None, var: Variants = NONE, want_delta: bool = False):
     """dq, dk, dv.  ``grads`` may supply the three output tensors (e.g. views of one fused ``[B, S, H + 2 Hkv, D]``
     gradient buffer); any strides with a unit stride along D and 16-byte aligned rows are taken as they are."""
     B, S, Hq, D = q.shape
@@ -56,33 +75,46 @@ def flash_bwd(do, q, k, v, out, lse, causal: bool, scale: float, grads=None):
         assert t.stride(3) == 1
         st += [t.stride(0), t.stride(1), t.stride(2)]
     strides = (c_ll * 24)(*st)
-    rc = L.load().dewb_flash_bwd(L.ptr(do), L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(out), L.ptr(lse), L.ptr(delta), L.ptr(dq),
-                                 L.ptr(dk), L.ptr(dv), c_int(B), c_int(S), c_int(T), c_int(Hq), c_int(Hkv), c_int(D),
-                                 strides, c_float(scale), c_int(int(causal)), L.ptr(L.status(q.device)), L.stream_ptr())
+    rc = L.load().dewb_flash_bwd_var(L.ptr(do), L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(out), L.ptr(lse), L.ptr(delta), L.ptr(dq),
+                                     L.ptr(dk), L.ptr(dv), c_int(B), c_int(S), c_int(T), c_int(Hq), c_int(Hkv), c_int(D),
+                                     strides, c_float(scale), c_int(int(causal)), c_int(var.window), c_float(var.softcap),
+                                     L.ptr(var.segments), L.ptr(var.segments), L.ptr(L.status(q.device)), L.stream_ptr())
     L.check(rc, "flash_bwd")
     L.count_launches(3)
+    if want_delta:
+        return dq, dk, dv, delta[0]
     return dq, dk, dv
 
 
 class _Flash(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale):
-        out, lse = flash_fwd(q, k, v, causal, scale)
+    def forward(ctx, q, k, v, causal, scale, var, sinks):
+        out, lse = flash_fwd(q, k, v, causal, scale, var=var)
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.causal, ctx.scale = causal, scale
+        ctx.causal, ctx.scale, ctx.var = causal, scale, var
+        ctx.sinks_grad = sinks is not None and sinks.requires_grad
         return out
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, out, lse = ctx.saved_tensors
-        dq, dk, dv = flash_bwd(do, q, k, v, out, lse, ctx.causal, ctx.scale)
-        return dq, dk, dv, None, None
+        var = ctx.var
+        if ctx.sinks_grad:
+            dq, dk, dv, delta = flash_bwd(do, q, k, v, out, lse, ctx.causal, ctx.scale, var=var, want_delta=True)
+            # the sink's probability in every row is exp(sink - lse); its value column is zero, so its logit gradient is
+            # -p_sink * delta, summed over batch and rows
+            p_sink = torch.exp(var.sinks.to(lse.dtype)[None, :, None] - lse)
+            dsinks = -(p_sink * delta).sum((0, 2))
+            return dq, dk, dv, None, None, None, dsinks
+        dq, dk, dv = flash_bwd(do, q, k, v, out, lse, ctx.causal, ctx.scale, var=var)
+        return dq, dk, dv, None, None, None, None
 
 
-def flash_sm100(q, k, v, causal: bool, scale: float):
-    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
-        return _Flash.apply(q, k, v, causal, scale)
-    return flash_fwd(q, k, v, causal, scale, need_lse=False)[0]
+def flash_sm100(q, k, v, causal: bool, scale: float, window=None, softcap: float = 0.0, sinks=None, segment_ids=None):
+    var = Variants(window, softcap, sinks, segment_ids)
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad or (sinks is not None and sinks.requires_grad)):
+        return _Flash.apply(q, k, v, causal, scale, var, sinks)
+    return flash_fwd(q, k, v, causal, scale, need_lse=False, var=var)[0]
 
 
 class _PackedRopeFlash(torch.autograd.Function):

@@ -237,6 +237,32 @@ def exchange_experts(exchange: TokenExchange, experts, x2: torch.Tensor, weights
     return _PullRows.apply(out_rows, weights.float(), exchange, plan)
 
 
+class _GatherExperts(torch.autograd.Function):
+    """All-gather of a rank's expert slice ``[E / W, ...]`` along the expert axis -> ``[E, ...]``; the backward is a
+    reduce-scatter (sum) of the full gradient, so every owner receives its experts' gradient from all ranks' tokens."""
+
+    @staticmethod
+    def forward(ctx, w, group):
+        ctx.group = group
+        W = dist.get_world_size(group)
+        out = w.new_empty((W * w.shape[0],) + tuple(w.shape[1:]))
+        dist.all_gather_into_tensor(out, w.contiguous(), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        W = dist.get_world_size(ctx.group)
+        mine = g.new_empty((g.shape[0] // W,) + tuple(g.shape[1:]))
+        if g.dtype == torch.bfloat16 and not g.is_cuda:
+            gf = g.float().contiguous()
+            mf = gf.new_empty(mine.shape)
+            dist.reduce_scatter_tensor(mf, gf, group=ctx.group)
+            mine = mf.to(g.dtype)
+        else:
+            dist.reduce_scatter_tensor(mine, g.contiguous(), group=ctx.group)
+        return mine, None
+
+
 class ExpertParallel:
     def __init__(self, group: Optional[dist.ProcessGroup] = None, fused: bool = True, capacity_factor: float = 2.0):
         self.group = group
@@ -263,8 +289,26 @@ class ExpertParallel:
                 ex.experts_n = per
                 m.ep = self
 
+    # ------------------------------------------------------------------ dispatch='global': weights travel, tokens stay
+    def gathered_experts(self, mlp, x2: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """``dispatch='global'``: every rank all-gathers the experts' weights along the expert axis and runs all experts on
+        its own tokens; the backward reduce-scatters the weight gradients back to their owners.  It moves
+        ``3 d F E (W - 1) / W`` weight elements per layer instead of ``2 k d`` per token, so it wins when a rank's tokens
+        outnumber ``1.5 F E / k`` (reference: ``Gathered`` / ``dispatch='global'``, src/dew/nn/moe.py:648,858-930)."""
+        T, k = ids.shape
+        gate_up = _GatherExperts.apply(mlp.experts.gate_up, self.group)
+        down = _GatherExperts.apply(mlp.experts.down, self.group)
+        layout = G.group_layout(ids, mlp.mix.experts)
+        xs = G.permute(x2, layout, k)
+        h = G.grouped_linear(xs, gate_up, layout)
+        from .. import ops
+        ys = G.grouped_linear(ops.packed_swiglu(h), down, layout)
+        return G.combine(ys, layout, weights.to(x2.dtype) if x2.dtype != torch.float32 else weights, T)
+
     # ------------------------------------------------------------------ the exchange
     def dispatch_compute_combine(self, mlp, x2: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        if getattr(mlp.mix, "dispatch", "auto") == "global" and self.world > 1:
+            return self.gathered_experts(mlp, x2, weights, ids)
         if x2.is_cuda and x2.dtype == torch.bfloat16 and L.use_cuda(x2) and self.fused:
             # device-planned exchange over peer memory (TokenExchange); the path below is the NCCL / gloo form of the same protocol
             if self.exchange is None:

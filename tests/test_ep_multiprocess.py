@@ -19,6 +19,17 @@ def test_expert_parallel_matches_single_process(world, port):
     assert r["out_err"] < 1e-5 and r["dx_err"] < 1e-4 and r["dw_err"] < 1e-4, r
 
 
+def test_expert_parallel_with_gathered_weights_matches_single_process():
+    """``dispatch='global'``: the experts' weights are all-gathered and every rank runs its own tokens; the weight gradients
+    return to their owners by a reduce-scatter."""
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29655", WORKER, "global"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-3000:]
+    r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    assert r["out_err"] < 1e-5 and r["dx_err"] < 1e-4 and r["dw_err"] < 1e-4, r
+
+
 def _run_moe(world, port):
     worker = os.path.join(os.path.dirname(__file__), "workers", "moe_fsdp_worker.py")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",

@@ -1016,3 +1016,54 @@ def test_gemm_ce_gdn_and_grouped_gemm_are_on_par_with_pytorch_bf16_against_float
             return {"o": o, "S": S.float() if kind != "truth" else S}
         return run
     assert_on_par(gdn_arm("kernel"), gdn_arm("torch"), gdn_arm("truth"))
+
+
+@pytest.mark.parametrize("variant", ["window", "softcap", "sinks", "segments", "window+softcap+sinks", "segments+padding", "full_window"])
+def test_flash_variants_forward_backward_on_the_sm100_kernels(variant):
+    """Sliding window, soft-capping, attention sinks and packed documents run on the tcgen05 flash kernels (no eager path):
+    outputs and every gradient against the fp32 reference of the same variant."""
+    torch.manual_seed(hash(variant) % 1000)
+    B, S, Hq, Hkv, D = 2, 512, 4, 2, 128
+    causal = variant != "full_window"
+    q, k, v = (torch.randn(B, S, h, D, device=DEV).to(torch.bfloat16).requires_grad_() for h in (Hq, Hkv, Hkv))
+    kw = {}
+    sinks = None
+    if "window" in variant:
+        kw["window"] = 200
+    if "softcap" in variant:
+        kw["softcap"] = 20.0
+    if "sinks" in variant:
+        sinks = torch.randn(Hq, device=DEV).requires_grad_()
+        kw["sinks"] = sinks
+    if "segments" in variant:
+        seg = torch.ones(B, S, dtype=torch.int32, device=DEV)
+        seg[0, 100:333] = 2
+        seg[0, 333:] = 3
+        seg[1, 256:] = 2
+        if "padding" in variant:
+            seg[0, 470:] = 0                                  # padding after the last document
+            seg[1, 300:] = 0
+        kw["segment_ids"] = seg
+    out = ops.attention(q, k, v, causal=causal, kernel="sm100_flash", **kw)
+    do = torch.randn_like(out)
+    out.backward(do)
+    got = [q.grad.clone(), k.grad.clone(), v.grad.clone()] + ([sinks.grad.clone()] if sinks is not None else [])
+    rq, rk, rv = (t.detach().float().requires_grad_() for t in (q, k, v))
+    rkw = dict(kw)
+    if sinks is not None:
+        rs = sinks.detach().clone().requires_grad_()
+        rkw["sinks"] = rs
+    ref = ops.attention_reference(rq, rk, rv, causal=causal, **rkw)
+    ref.backward(do.float())
+    want = [rq.grad, rk.grad, rv.grad] + ([rs.grad] if sinks is not None else [])
+    live = torch.ones(B, S, dtype=torch.bool, device=DEV)
+    if "padding" in variant:
+        live = kw["segment_ids"] != 0                      # padded rows attend to padding only; nothing reads them
+    assert rel_err(out[live], ref[live]) <= 3 * bf16_floor(ref[live]) + 2e-3, rel_err(out[live], ref[live])
+    for name, g, r in zip(("dq", "dk", "dv", "dsinks"), got, want):
+        assert rel_err(g, r) <= 3 * bf16_floor(r) + 1.5e-2, (name, rel_err(g, r))
+    # the selector no longer sends any variant to the eager path on a GPU
+    from dew_b200.ops import attn as A
+    case = dict(dtype=torch.bfloat16, D=D, S=S, T=S, Hq=Hq, Hkv=Hkv, sinks=sinks is not None, softcap=bool(kw.get("softcap")),
+                window=kw.get("window"), segments="segment_ids" in kw, causal=causal, grad=True, unit_d=True)
+    assert A._ATTN.select(case) == "sm100_flash"

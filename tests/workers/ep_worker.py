@@ -16,7 +16,8 @@ from dew_b200.parallel.ep import ExpertParallel  # noqa: E402
 def main():
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
-    mix = Mixture(experts=8, top_k=2, expert_features=16, shared_features=16)
+    dispatch = sys.argv[1] if len(sys.argv) > 1 else "auto"
+    mix = Mixture(experts=8, top_k=2, expert_features=16, shared_features=16, dispatch=dispatch)
     torch.manual_seed(0)
     full = SparseMLP(32, mix, 64)
     torch.manual_seed(0)
