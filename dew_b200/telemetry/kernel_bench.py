@@ -143,6 +143,31 @@ def bench_rows(out, peaks, flush, iters=10):
              bwd_gbs=bb / t_b.median_ms / 1e6, bwd_frac_of_measured=bb / t_b.median_ms / 1e6 / bw, peaks=peaks["source"])
 
 
+def bench_attention_variants(out, peaks, flush, iters=10):
+    """The attention variants on the sm_100a kernels at one long row (1 x 12288 tokens, 32 / 8 heads of 128): plain causal,
+    a 2048-key window, soft-capping, sinks, and the row packed as 6 documents of 2048 tokens (segment ids), forward and
+    forward + backward; FLOPs count the visible (query, key) pairs only."""
+    B, S, Hq, Hkv, D = 1, 12288, 32, 8, 128
+    q = torch.randn(B, S, Hq, D, device="cuda").to(torch.bfloat16).requires_grad_()
+    k = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_()
+    v = torch.randn(B, S, Hkv, D, device="cuda").to(torch.bfloat16).requires_grad_()
+    seg = (torch.arange(S, device="cuda") // 2048 + 1).to(torch.int32)[None].expand(B, S).contiguous()
+    sinks = torch.zeros(Hq, device="cuda")
+    pairs_causal = S * (S + 1) / 2
+    cases = [("causal", {}, pairs_causal), ("window 2048", dict(window=2048), 2048 * S - 2048 * 2047 / 2),
+             ("softcap 30", dict(softcap=30.0), pairs_causal), ("sinks", dict(sinks=sinks), pairs_causal),
+             ("6 packed documents", dict(segment_ids=seg), 6 * 2048 * 2049 / 2)]
+    for name, kw, pairs in cases:
+        o = ops.attention(q, k, v, causal=True, kernel="sm100_flash", **kw)
+        do = torch.randn_like(o)
+        t_f = device_time(lambda: ops.attention(q, k, v, causal=True, kernel="sm100_flash", **kw), iters=iters, flush=flush)
+        t_fb = device_time(lambda: ops.attention(q, k, v, causal=True, kernel="sm100_flash", **kw).backward(do), iters=iters, flush=flush)
+        L.check_status()
+        flops = 4.0 * B * Hq * pairs * D
+        _row(out, kernel="attention_variant", variant=name, B=B, S=S, Hq=Hq, Hkv=Hkv, D=D, fwd_ms=t_f.median_ms,
+             fwd_bwd_ms=t_fb.median_ms, fwd_tflops=flops / t_f.median_ms / 1e9, fwd_bwd_tflops=3.5 * flops / t_fb.median_ms / 1e9)
+
+
 def bench_attention(out, peaks, flush, iters=10, shapes=None, kernels=("sm100_flash", "sdpa")):
     import torch.nn.functional as F
     for B, S, Hq, Hkv, D in shapes or [(2, 4096, 32, 8, 128), (1, 16384, 32, 8, 128), (8, 4096, 32, 8, 128)]:
@@ -334,6 +359,8 @@ def main(argv=None):
         bench_rows(out, peaks, flush, iters=args.iters)
     if "attention" in only:
         bench_attention(out, peaks, flush, iters=args.iters)
+    if "attention_variants" in only:
+        bench_attention_variants(out, peaks, flush, iters=args.iters)
     if "gdn" in only:
         bench_gdn(out, peaks, flush, iters=args.iters)
     if "ssd" in only:
