@@ -334,6 +334,70 @@ extern "C" int dewb_paged_decode(const void* q, const void* kpool, const void* v
   return static_cast<int>(cudaGetLastError());
 }
 
+// One decode step's packed projection output qkv [rows, Hq + 2 Hkv, D] (bf16): rotate the query and key heads in place
+// (rotate-half RoPE at positions[row]; cos / sin [table_rows, D / 2] fp32, null = no rotation) and write the row's rotated key
+// heads and its value heads into the paged bf16 cache at slot positions[row].  One launch where a rotation kernel, an append
+// kernel and four copies of strided slices ran.  Rows with positions[row] < 0 are left alone.
+__global__ void rope_append_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosb, const float* __restrict__ sinb,
+                                   const int* __restrict__ positions, int Hq, int Hkv, int D, int table_rows,
+                                   __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool,
+                                   const int* __restrict__ page_table, int page_size, int max_pages) {
+  const int row = blockIdx.x, head = blockIdx.y;
+  const int pos = positions[row];
+  if (pos < 0) return;
+  const int half = D >> 1;
+  const int c = threadIdx.x;                                   // uint4 chunk within a half
+  if (c >= (half >> 3)) return;
+  __nv_bfloat16* base = qkv + (static_cast<long long>(row) * (Hq + 2 * Hkv) + head) * D;
+  uint4 lo = *(reinterpret_cast<const uint4*>(base) + c);
+  uint4 hi = *(reinterpret_cast<const uint4*>(base + half) + c);
+  const bool is_v = head >= Hq + Hkv;
+  if (!is_v && cosb != nullptr) {
+    const int tp = min(pos, table_rows - 1);
+    const float4* cp = reinterpret_cast<const float4*>(cosb + static_cast<long long>(tp) * half + c * 8);
+    const float4* sp = reinterpret_cast<const float4*>(sinb + static_cast<long long>(tp) * half + c * 8);
+    const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const uint32_t a[4] = {lo.x, lo.y, lo.z, lo.w}, b[4] = {hi.x, hi.y, hi.z, hi.w};
+    uint32_t o1[4], o2[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a0 = __uint_as_float(a[j] << 16), a1 = __uint_as_float(a[j] & 0xffff0000u);
+      const float b0 = __uint_as_float(b[j] << 16), b1 = __uint_as_float(b[j] & 0xffff0000u);
+      const float x0 = a0 * cs[2 * j] - b0 * sn[2 * j], x1 = a1 * cs[2 * j + 1] - b1 * sn[2 * j + 1];
+      const float y0 = b0 * cs[2 * j] + a0 * sn[2 * j], y1 = b1 * cs[2 * j + 1] + a1 * sn[2 * j + 1];
+      __nv_bfloat162 p = __floats2bfloat162_rn(x0, x1), q2 = __floats2bfloat162_rn(y0, y1);
+      o1[j] = *reinterpret_cast<uint32_t*>(&p);
+      o2[j] = *reinterpret_cast<uint32_t*>(&q2);
+    }
+    lo = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+    hi = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+    *(reinterpret_cast<uint4*>(base) + c) = lo;
+    *(reinterpret_cast<uint4*>(base + half) + c) = hi;
+  }
+  if (head >= Hq) {
+    const int hk = is_v ? head - Hq - Hkv : head - Hq;
+    const int page = page_table[static_cast<long long>(row) * max_pages + pos / page_size];
+    const long long tok = static_cast<long long>(page) * page_size + pos % page_size;
+    __nv_bfloat16* dst = (is_v ? vpool : kpool) + (tok * Hkv + hk) * D;
+    *(reinterpret_cast<uint4*>(dst) + c) = lo;
+    *(reinterpret_cast<uint4*>(dst + half) + c) = hi;
+  }
+}
+
+extern "C" int dewb_rope_append(void* qkv, const float* cosb, const float* sinb, const int* positions, int rows, int Hq, int Hkv,
+                                int D, int table_rows, void* kpool, void* vpool, const int* page_table, int page_size,
+                                int max_pages, void* stream_ptr) {
+  if (rows <= 0) return 0;
+  if (D % 16 != 0 || D > 512 || (cosb != nullptr && table_rows <= 0)) return -3;
+  dim3 grid(rows, Hq + 2 * Hkv);
+  rope_append_kernel<<<grid, 32, 0, reinterpret_cast<cudaStream_t>(stream_ptr)>>>(
+      reinterpret_cast<__nv_bfloat16*>(qkv), cosb, sinb, positions, Hq, Hkv, D, table_rows, reinterpret_cast<__nv_bfloat16*>(kpool),
+      reinterpret_cast<__nv_bfloat16*>(vpool), page_table, page_size, max_pages);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // positions[row] = slot to write (the row's current length), or < 0 to skip the row.
 extern "C" int dewb_kv_append(const void* k_new, const void* v_new, void* kpool, void* vpool, float* kscale,
                               float* vscale, const int* page_table, const int* positions, int rows, int Hkv, int D,

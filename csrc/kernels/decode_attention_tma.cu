@@ -58,7 +58,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tk, const __grid_con
                         const __nv_bfloat16* __restrict__ q, const int* __restrict__ page_table,
                         const int* __restrict__ lengths, float* __restrict__ part_m, float* __restrict__ part_l,
                         float* __restrict__ part_acc, int Hq, int Hkv, int page_size, int max_pages, int splits,
-                        float scale_log2, int window, int* __restrict__ err) {
+                        float scale_log2, int window, long long q_row_stride, int* __restrict__ err) {
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) atomicCAS(err, 0, ERR_BAD_ARG);
@@ -89,7 +89,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tk, const __grid_con
   }
   for (int i = tid; i < 8 * D; i += THREADS) {
     const int g = i / D, d = i - g * D;
-    sQ[i] = g < G ? q[(static_cast<long long>(row) * Hq + hk * G + g) * D + d] : __float2bfloat16(0.f);
+    sQ[i] = g < G ? q[static_cast<long long>(row) * q_row_stride + (hk * G + g) * D + d] : __float2bfloat16(0.f);
   }
   __syncthreads();
   volatile int* abort_flag = &bars->abort_flag;
@@ -235,10 +235,11 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tk, const __grid_con
 // The streamed form of the paged decode attention's first stage: writes the per-split partials (part_m, part_l in the log2
 // domain, part_acc) exactly as the first-stage kernel of dewb_paged_decode does; the caller runs the same combine.
 // kpool / vpool: bf16 [pool_tokens, Hkv, 128] (pool_tokens = pages * page_size), page_size a multiple of 64, Hq / Hkv <= 8.
+// q_row_stride: elements between the query rows (0 = packed [rows, Hq, 128]); a packed projection output can be read in place.
 extern "C" int dewb_paged_decode_stream(const void* q, const void* kpool, const void* vpool, long long pool_tokens,
                                         const int* page_table, const int* lengths, float* part_m, float* part_l,
                                         float* part_acc, int rows, int Hq, int Hkv, int page_size, int max_pages, int splits,
-                                        float scale, int window, int* err, void* stream_ptr) {
+                                        float scale, int window, long long q_row_stride, int* err, void* stream_ptr) {
   using namespace dewb::decode2;
   if (rows <= 0) return 0;
   if (Hq % Hkv != 0 || Hq / Hkv > 8 || page_size % TK != 0 || splits < 1 || pool_tokens <= 0) return -3;
@@ -252,6 +253,6 @@ extern "C" int dewb_paged_decode_stream(const void* q, const void* kpool, const 
   dim3 grid(rows, Hkv, splits);
   paged_decode_tma_kernel<<<grid, THREADS, SMEM, reinterpret_cast<cudaStream_t>(stream_ptr)>>>(
       tk, tv, reinterpret_cast<const __nv_bfloat16*>(q), page_table, lengths, part_m, part_l, part_acc, Hq, Hkv, page_size,
-      max_pages, splits, scale * 1.4426950408889634f, window, err);
+      max_pages, splits, scale * 1.4426950408889634f, window, q_row_stride > 0 ? q_row_stride : static_cast<long long>(Hq) * D, err);
   return static_cast<int>(cudaGetLastError());
 }

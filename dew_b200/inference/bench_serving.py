@@ -32,6 +32,9 @@ def main(argv=None):
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--out", default=None)
     ap.add_argument("--profile", default=None, help="write a torch.profiler kernel table of eight decode steps to this file")
+    ap.add_argument("--arrival-rate", type=float, default=0.0,
+                    help="open loop: requests arrive as a Poisson process of this many per second (seeded) while the server runs; "
+                         "time to first token and inter-token latency are measured from each request's own arrival")
     args = ap.parse_args(argv)
 
     from ..models import CausalTransformer
@@ -67,6 +70,8 @@ def main(argv=None):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    if args.arrival_rate > 0:
+        return open_loop(args, server, prompts, lens, rank, world, dev, L)
     t0 = time.perf_counter()
     tickets = [server.submit(p, args.new_tokens) for p in prompts]
     if args.profile:
@@ -127,6 +132,69 @@ def main(argv=None):
     import sys
     sys.stdout.flush()
     sys.stderr.flush()
+    os._exit(0)
+
+
+def open_loop(args, server, prompts, lens, rank, world, dev, L):
+    """Open-loop workload (the reference's arrival harness, tools/benchmark_lm_serving.py:60-80): request i arrives at a seeded
+    Poisson time whether or not the server is busy; rank 0's clock decides how many have arrived before each step and tells
+    the other ranks, so that every tensor-parallel rank admits the same requests at the same step."""
+    import random
+    rng = random.Random(4321)
+    at, arrivals = 0.0, []
+    for _ in prompts:
+        at += rng.expovariate(args.arrival_rate)
+        arrivals.append(at)
+    # warm the kernels / graphs outside the measurement
+    warm = server.submit(prompts[0][:128], 4)
+    server.run()
+    torch.cuda.synchronize()
+    tickets, token_times = [], {}
+    nxt = 0
+    count = torch.zeros(1, dtype=torch.int64, device=dev)
+    t0 = time.perf_counter()
+    while nxt < len(prompts) or server.busy:
+        now = time.perf_counter() - t0
+        due = nxt
+        while due < len(prompts) and arrivals[due] <= now:
+            due += 1
+        if world > 1:
+            count[0] = due
+            dist.broadcast(count, src=0)
+            due = int(count.item())
+        for i in range(nxt, due):
+            times = []
+            t = server.submit(prompts[i], args.new_tokens, on_token=lambda tok, times=times: times.append(time.perf_counter()))
+            t.submitted = t0 + arrivals[i]                          # measured from the arrival, not from the admission
+            tickets.append(t)
+            token_times[id(t)] = times
+        nxt = due
+        if server.busy:
+            server.step()
+        else:
+            time.sleep(min(0.001, max(0.0, arrivals[nxt] - now))) if nxt < len(prompts) else None
+    torch.cuda.synchronize()
+    total_s = time.perf_counter() - t0
+    L.check_status()
+    ttft = sorted(t.first_token_time for t in tickets if t.first_token_time is not None)
+    itl = sorted(b - a for t in tickets for a, b in zip(token_times[id(t)], token_times[id(t)][1:]))
+    pct = lambda xs, p: xs[min(len(xs) - 1, int(len(xs) * p))] if xs else None
+    out = {"metric": "open-loop serving", "arrival_rate_per_s": args.arrival_rate, "requests": len(tickets), "n_gpus": world,
+           "new_tokens_each": args.new_tokens, "output_tokens_per_s": sum(len(t.tokens) for t in tickets) / total_s,
+           "ttft_p50_s": pct(ttft, 0.5), "ttft_p90_s": pct(ttft, 0.9), "ttft_p99_s": pct(ttft, 0.99),
+           "itl_p50_ms": 1e3 * pct(itl, 0.5) if itl else None, "itl_p90_ms": 1e3 * pct(itl, 0.9) if itl else None,
+           "wall_s": total_s, "prompt_tokens": sum(lens), "layers": args.layers, "dtype": "bf16",
+           "data": "synthetic prompts, random-init weights", "gpu_launches": L.LAUNCHES}
+    if rank == 0:
+        print(json.dumps(out))
+        if args.out:
+            with open(args.out, "a") as f:
+                f.write(json.dumps(out) + "\n")
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    import sys
+    sys.stdout.flush()
     os._exit(0)
 
 

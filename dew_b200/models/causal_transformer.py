@@ -40,7 +40,7 @@ class Mixture:
     implementation: str = "auto"
     dispatch: str = "auto"                           # auto | global | exchange
     capacity_factor: Optional[float] = None
-    fp8: bool = False                                # block-scaled fp8 expert GEMMs
+    fp8: Any = False                                 # True: block-scaled MXFP8 expert GEMMs (1 x 32 blocks); 'row': row / channel scaled e4m3
     balance_rate: float = 1e-3
     groups: int = 1                                  # DeepSeek-V3's group-limited routing: experts in ``groups`` groups ...
     topk_groups: int = 1                             # ... of which each token may use the ``topk_groups`` best (by their top-2 sum)

@@ -70,6 +70,13 @@ class SelfAttention(nn.Module):
             o = packed_attention(self.qkv_proj(x).view(B, S, H + 2 * Hkv, D), cos, sin, positions, H, Hkv, self.causal)
             if o is not None:
                 return self.o_proj(o.reshape(B, S, H * D))
+        if cache is not None and S == 1 and self.q_norm is None and positions is not None and hasattr(cache, "decode_packed"):
+            # decode step: rotation, cache append and attention straight from the packed projection (no slices, no copies)
+            H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
+            qkv = self.qkv_proj(x).view(B, H + 2 * Hkv, D)
+            if cache.can_decode_packed(qkv, H, self.softcap):
+                o = cache.decode_packed(layer, qkv, cos, sin, positions.reshape(-1), H, window=self.window, sinks=self.sinks)
+                return self.o_proj(o.reshape(B, 1, H * D))
         q, k, v = self.project(x, cos, sin, positions)
         if self.track_qk_max and cache is None and self.training:
             self._record_qk_max(q, k)

@@ -137,6 +137,62 @@ class KVStore:
             return
         self.write(layer, k[:, None], v[:, None], positions[:, None])
 
+    # ------------------------------------------------------------------ the fused decode step
+    def _step_ints(self, positions: torch.Tensor):
+        """(positions, lengths) of a decode step as int32, computed once per step: every layer of a forward passes the same
+        positions tensor, so the conversions and the ``where`` run for the first layer only."""
+        key = (positions.data_ptr(), positions._version, tuple(positions.shape), torch.cuda.is_current_stream_capturing() if positions.is_cuda else False)
+        cached = getattr(self, "_ints", None)
+        if cached is not None and cached[0] == key:
+            return cached[1], cached[2]
+        pos32 = positions.to(torch.int32).contiguous()
+        lens32 = torch.where(pos32 >= 0, pos32 + 1, torch.zeros_like(pos32))
+        self._ints = (key, pos32, lens32)
+        return pos32, lens32
+
+    def can_decode_packed(self, qkv: torch.Tensor, Hq: int, softcap: float = 0.0) -> bool:
+        return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and self.kind == 0 and self.row_ids is None
+                and qkv.shape[0] == self.rows and self.head_dim == 128 and self.page_size % 64 == 0 and not softcap
+                and Hq // self.kv_heads <= 8 and os.environ.get("DEWB_DECODE", "stream") == "stream"
+                and hasattr(L.load(), "dewb_rope_append"))
+
+    def decode_packed(self, layer: int, qkv: torch.Tensor, cos, sin, positions: torch.Tensor, Hq: int, window=None, sinks=None):
+        """One decode step of a layer straight from the packed projection output ``qkv [R, Hq + 2 Hkv, D]``: one kernel rotates
+        the query / key heads in place and appends the keys and values to the paged cache, then the streamed paged-attention
+        kernel reads the queries where they are (row stride of the packed tensor).  Returns ``[R, Hq, D]``."""
+        lib = L.load()
+        R, H, D = qkv.shape
+        pos32, lens32 = self._step_ints(positions)
+        L.check(lib.dewb_rope_append(L.ptr(qkv), L.ptr(cos), L.ptr(sin), L.ptr(pos32), ctypes.c_int(R), ctypes.c_int(Hq),
+                                     ctypes.c_int(self.kv_heads), ctypes.c_int(D), ctypes.c_int(cos.shape[0] if cos is not None else 0),
+                                     L.ptr(self.k[layer]), L.ptr(self.v[layer]), L.ptr(self.page_table), ctypes.c_int(self.page_size),
+                                     ctypes.c_int(self.max_pages), L.stream_ptr()), "rope_append")
+        splits = 1
+        longest = self.max_len
+        while splits < 16 and R * self.kv_heads * splits < 592 and longest // (splits * 2) >= 256:
+            splits *= 2
+        splits = max(splits, min(16, (longest + 511) // 512))
+        n = R * Hq * splits
+        if self._scratch is None or self._scratch[0].numel() < n:
+            self._scratch = (torch.empty(n, dtype=torch.float32, device=qkv.device), torch.empty(n, dtype=torch.float32, device=qkv.device),
+                             torch.empty(n * D, dtype=torch.float32, device=qkv.device))
+        pm, pl, pa = self._scratch
+        out = torch.empty((R, Hq, D), dtype=qkv.dtype, device=qkv.device)
+        L.check(lib.dewb_paged_decode_stream(L.ptr(qkv), L.ptr(self.k[layer]), L.ptr(self.v[layer]),
+                                             ctypes.c_longlong(self.pages * self.page_size), L.ptr(self.page_table), L.ptr(lens32),
+                                             L.ptr(pm), L.ptr(pl), L.ptr(pa), ctypes.c_int(R), ctypes.c_int(Hq),
+                                             ctypes.c_int(self.kv_heads), ctypes.c_int(self.page_size), ctypes.c_int(self.max_pages),
+                                             ctypes.c_int(splits), ctypes.c_float(1.0 / math.sqrt(D)), ctypes.c_int(window or 0),
+                                             ctypes.c_longlong(H * D), L.ptr(L.status(qkv.device)), L.stream_ptr()), "paged_decode_stream")
+        sk = getattr(self, "_sinks32", None)
+        if sinks is not None and (sk is None or sk[0] is not sinks):
+            self._sinks32 = sk = (sinks, sinks.detach().float().contiguous())
+        L.check(lib.dewb_decode_combine(L.ptr(pm), L.ptr(pl), L.ptr(pa), L.ptr(sk[1] if sinks is not None else None),
+                                        L.ptr(out), L.ptr(None), ctypes.c_int(R), ctypes.c_int(Hq), ctypes.c_int(D), ctypes.c_int(splits),
+                                        L.stream_ptr()), "decode_combine")
+        L.count_launches(3)
+        return out
+
     # ------------------------------------------------------------------ reads
     def gather(self, layer: int, length: int, dtype=None) -> Tuple[torch.Tensor, torch.Tensor]:
         """Dense ``[R, length, Hkv, D]`` views of the selected rows' first ``length`` cached tokens."""
@@ -183,7 +239,7 @@ class KVStore:
                                                      L.ptr(pm), L.ptr(pl), L.ptr(pa), ctypes.c_int(R), ctypes.c_int(Hq),
                                                      ctypes.c_int(self.kv_heads), ctypes.c_int(self.page_size), ctypes.c_int(self.max_pages),
                                                      ctypes.c_int(splits), ctypes.c_float(scale), ctypes.c_int(window or 0),
-                                                     L.ptr(L.status(q.device)), L.stream_ptr()), "paged_decode_stream")
+                                                     ctypes.c_longlong(0), L.ptr(L.status(q.device)), L.stream_ptr()), "paged_decode_stream")
                 L.check(lib.dewb_decode_combine(L.ptr(pm), L.ptr(pl), L.ptr(pa), L.ptr(sinks.float().contiguous() if sinks is not None else None),
                                                 L.ptr(out), L.ptr(None), ctypes.c_int(R), ctypes.c_int(Hq), ctypes.c_int(D), ctypes.c_int(splits),
                                                 L.stream_ptr()), "decode_combine")
@@ -214,6 +270,7 @@ class KVStore:
             self.append(layer, k[:, 0], v[:, 0], pos)
             lengths = torch.where(pos >= 0, pos + 1, torch.zeros_like(pos))
             return self.decode_attention(layer, q[:, 0], lengths, window=window, sinks=sinks, softcap=softcap)[:, None]
+
         self.write(layer, k, v, positions)
         if self.chunk_span is not None:
             # the caller knows where this chunk starts and ends (a server batching rows by start offset): no device read

@@ -97,8 +97,14 @@ class ExpertMLP(nn.Module):
         return 3 * self.features * self.hidden
 
     def forward(self, xs: torch.Tensor, layout: G.GroupLayout) -> torch.Tensor:
-        if getattr(self, "fp8", False) and xs.dtype == torch.bfloat16:
-            from ..ops.fp8 import fp8_grouped_linear
+        mode = getattr(self, "fp8", False)
+        if mode and xs.dtype == torch.bfloat16:
+            from ..ops import mx
+            if mode != "row" and mx.usable(self.features, 2 * self.hidden) and mx.usable(self.hidden, self.features):
+                # block-scaled MXFP8 (1 x 32 blocks, ue8m0 scales applied by the tensor core)
+                h = mx.mx_grouped_linear(xs, self.gate_up, layout)
+                return mx.mx_grouped_linear(ops.packed_swiglu(h), self.down, layout)
+            from ..ops.fp8 import fp8_grouped_linear            # row / channel scaled e4m3
             h = fp8_grouped_linear(xs, self.gate_up, layout)
             return fp8_grouped_linear(ops.packed_swiglu(h), self.down, layout)
         h = G.grouped_linear(xs, self.gate_up, layout)
@@ -114,7 +120,7 @@ class SparseMLP(nn.Module):
         hidden = mix.expert_features or dense_hidden
         self.router = Router(features, mix, dtype=torch.float32, device=device)
         self.experts = ExpertMLP(features, hidden, mix.experts, init_std, dtype=dtype, device=device)
-        self.experts.fp8 = bool(mix.fp8)
+        self.experts.fp8 = mix.fp8            # False | True (block-scaled MXFP8 where the sizes allow) | 'row' (row / channel scaled)
         self.shared = SwiGLU(features, mix.shared_features, init_std, dtype=dtype, device=device) if mix.shared_features else None
         self.shared_gate = Linear(features, 1, axes=("embed", None), dtype=dtype, device=device) if (mix.shared_gate and mix.shared_features) else None
         self.last: Dict[str, Any] = {}

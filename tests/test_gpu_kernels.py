@@ -1067,3 +1067,94 @@ def test_flash_variants_forward_backward_on_the_sm100_kernels(variant):
     case = dict(dtype=torch.bfloat16, D=D, S=S, T=S, Hq=Hq, Hkv=Hkv, sinks=sinks is not None, softcap=bool(kw.get("softcap")),
                 window=kw.get("window"), segments="segment_ids" in kw, causal=causal, grad=True, unit_d=True)
     assert A._ATTN.select(case) == "sm100_flash"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 192, 128), (256, 384, 256), (1000, 2816, 2048), (4096, 2048, 1408 - 1408 % 128)])
+def test_mxfp8_block_scaled_gemm(M, N, K):
+    """tcgen05 kind::mxf8f6f4.block_scale: the quantiser equals the PyTorch restatement bit for bit, and the product equals the
+    fp32 product of the de-quantised operands (the tensor core applies the 1 x 32 block scales itself)."""
+    from dew_b200.ops import mx
+    torch.manual_seed(M + N)
+    # blocks of very different magnitude within a row, so that a wrong scale factor cannot hide
+    mag = torch.exp2(torch.randint(-6, 7, (M, K // 32), device=DEV).float()).repeat_interleave(32, 1)
+    a = (torch.randn(M, K, device=DEV) * mag).to(torch.bfloat16)
+    magb = torch.exp2(torch.randint(-5, 6, (N, K // 32), device=DEV).float()).repeat_interleave(32, 1)
+    b = (torch.randn(N, K, device=DEV) * magb / math.sqrt(K)).to(torch.bfloat16)
+    aq, sa = mx.quantize_mx(a)
+    bq, sb = mx.quantize_mx(b, sf_rows=(N + 192 + 127) // 128 * 128)
+    rq, re = mx.quantize_mx_reference(a)
+    assert torch.equal(aq.view(torch.uint8), rq.view(torch.uint8))
+    assert torch.equal(mx.unpack_scales(sa, M, K), re)
+    out = mx.gemm_mx(aq, sa, bq, sb)
+    ref = mx.dequantize_mx(aq, mx.unpack_scales(sa, M, K)) @ mx.dequantize_mx(bq, mx.unpack_scales(sb, N, K)).t()
+    assert rel_err(out, ref) <= 2 * bf16_floor(ref) + 1e-3, rel_err(out, ref)
+    # and the quantisation itself costs what 1 x 32 e4m3 blocks cost against the bf16 product
+    exact = a.float() @ b.float().t()
+    assert rel_err(out, exact) < 6e-2
+
+
+def test_mxfp8_grouped_linear_forward_backward():
+    """Expert projection in MXFP8 (forward and input gradient on the block-scaled kernel, weight gradient in bf16) against the
+    bf16 grouped GEMM."""
+    from dew_b200.ops import grouped as G
+    from dew_b200.ops import mx
+    torch.manual_seed(3)
+    T, k, E, d, F_ = 1000, 2, 8, 256, 384
+    ids = torch.randint(0, E, (T, k), device=DEV)
+    ids[ids == 5] = 4                                       # one empty expert
+    layout = G.group_layout(ids, E)
+    xs = G.permute(torch.randn(T, d, device=DEV).to(torch.bfloat16), layout, k)
+    used = torch.zeros(layout.rows, dtype=torch.bool, device=DEV)
+    used[layout.positions] = True
+    w = (torch.randn(E, F_, d, device=DEV) / math.sqrt(d)).to(torch.bfloat16)
+    a, b = xs.clone().requires_grad_(), w.clone().requires_grad_()
+    y = mx.mx_grouped_linear(a, b, layout)
+    dy = torch.randn_like(y) * used[:, None]
+    y.backward(dy)
+    ra, rb = xs.clone().requires_grad_(), w.clone().requires_grad_()
+    ry = G.grouped_linear(ra, rb, layout)
+    ry.backward(dy)
+    assert rel_err(y[used], ry[used]) < 6e-2
+    assert rel_err(a.grad[used], ra.grad[used]) < 6e-2
+    assert rel_err(b.grad, rb.grad) < 1e-2                  # the weight gradient runs the bf16 kernel in both
+    assert torch.all(y[~used] == 0)
+
+
+def test_fused_decode_step_from_the_packed_projection():
+    """Rotation + cache append in one kernel and paged attention reading the queries in place equal the unfused path
+    (rope kernel, append kernel, contiguous slices, attention) bit for bit, and a -1 position leaves its row alone."""
+    from dew_b200.nn.kv_cache import KVCache, KVStore
+    torch.manual_seed(21)
+    rows, max_len, Hq, Hkv, D = 6, 700, 8, 2, 128
+
+    def filled():
+        torch.manual_seed(22)
+        store = KVStore(KVCache(page_size=64), 1, rows, max_len, Hkv, D, torch.bfloat16, DEV)
+        perm = torch.randperm(store.pages, device=DEV, generator=torch.Generator(device=DEV).manual_seed(1)).to(torch.int32)
+        store.page_table.copy_(perm.reshape(rows, store.max_pages))
+        lengths = torch.tensor([1, 17, 256, 511, 640, 300], device=DEV)
+        S = int(lengths.max())
+        k = torch.randn(rows, S, Hkv, D, device=DEV).to(torch.bfloat16)
+        v = torch.randn(rows, S, Hkv, D, device=DEV).to(torch.bfloat16)
+        pos = torch.arange(S, device=DEV)[None].expand(rows, S).clone()
+        pos[pos >= lengths[:, None]] = -1
+        store.write(0, k, v, pos)
+        return store, lengths
+    cos, sin = ops.rope_tables(1024, D, 10000.0, torch.device(DEV))
+    qkv = torch.randn(rows, Hq + 2 * Hkv, D, device=DEV).to(torch.bfloat16)
+    a, lengths = filled()
+    positions = lengths.clone()
+    positions[5] = -1                                              # an idle row
+    fused_in = qkv.clone()
+    assert a.can_decode_packed(fused_in, Hq)
+    fused = a.decode_packed(0, fused_in, cos, sin, positions, Hq)
+    b, _ = filled()
+    rot = ops.rope(qkv.clone()[:, None], cos, sin, positions.clamp_min(0)[:, None], rot_heads=Hq + Hkv)[:, 0]
+    q, k, v = rot[:, :Hq], rot[:, Hq:Hq + Hkv], rot[:, Hq + Hkv:]
+    plain = b.attend(0, q[:, None], k[:, None], v[:, None], positions[:, None])[:, 0]
+    live = positions >= 0
+    assert torch.equal(fused_in[5], qkv[5])                        # the idle row's projection was not rotated
+    assert torch.equal(fused_in[live][:, :Hq + Hkv], rot[live][:, :Hq + Hkv]), "rotation differs"
+    assert torch.equal(a.v[0], b.v[0]), "value cache differs"
+    assert torch.equal(a.k[0], b.k[0]), "key cache differs"
+    assert torch.equal(fused[live], plain[live]), float((fused[live].float() - plain[live].float()).abs().max())
