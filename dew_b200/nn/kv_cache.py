@@ -127,10 +127,13 @@ class KVStore:
         """One token per row: ``k, v [R, Hkv, D]`` written at ``positions [R]``."""
         if L.use_cuda(k) and k.dtype == torch.bfloat16 and self.row_ids is None and k.shape[0] == self.rows:
             lib = L.load()
-            L.check(lib.dewb_kv_append(L.ptr(k.contiguous()), L.ptr(v.contiguous()), L.ptr(self.k[layer]), L.ptr(self.v[layer]),
+            # every temporary stays referenced until the launch is enqueued: a temporary released between two `L.ptr` calls hands
+            # its block back to the allocator, and the next temporary of the same size would take (and overwrite) it
+            kc, vc, pos32 = k.contiguous(), v.contiguous(), positions.to(torch.int32).contiguous()
+            L.check(lib.dewb_kv_append(L.ptr(kc), L.ptr(vc), L.ptr(self.k[layer]), L.ptr(self.v[layer]),
                                        L.ptr(self.k_scale[layer] if self.kind else None),
                                        L.ptr(self.v_scale[layer] if self.kind else None), L.ptr(self.page_table),
-                                       L.ptr(positions.to(torch.int32).contiguous()), ctypes.c_int(k.shape[0]),
+                                       L.ptr(pos32), ctypes.c_int(k.shape[0]),
                                        ctypes.c_int(self.kv_heads), ctypes.c_int(self.head_dim), ctypes.c_int(self.page_size),
                                        ctypes.c_int(self.max_pages), ctypes.c_int(self.kind), L.stream_ptr()), "kv_append")
             L.count_launches()
@@ -230,26 +233,26 @@ class KVStore:
                                  torch.empty(n * D, dtype=torch.float32, device=q.device))
             pm, pl, pa = self._scratch
             out = torch.empty_like(q)
+            qc, lens32 = q.contiguous(), lengths.to(torch.int32).contiguous()      # kept referenced across the launches below
+            sinks32 = sinks.float().contiguous() if sinks is not None else None
             if (self.kind == 0 and D == 128 and self.page_size % 64 == 0 and hasattr(lib, "dewb_paged_decode_stream")
                     and os.environ.get("DEWB_DECODE", "stream") == "stream"):
                 # streamed form: TMA page tiles into a shared-memory ring, scores and values on the warp-level tensor cores
-                lens = lengths.to(torch.int32).contiguous()
-                L.check(lib.dewb_paged_decode_stream(L.ptr(q.contiguous()), L.ptr(self.k[layer]), L.ptr(self.v[layer]),
-                                                     ctypes.c_longlong(self.pages * self.page_size), L.ptr(self.page_table), L.ptr(lens),
+                L.check(lib.dewb_paged_decode_stream(L.ptr(qc), L.ptr(self.k[layer]), L.ptr(self.v[layer]),
+                                                     ctypes.c_longlong(self.pages * self.page_size), L.ptr(self.page_table), L.ptr(lens32),
                                                      L.ptr(pm), L.ptr(pl), L.ptr(pa), ctypes.c_int(R), ctypes.c_int(Hq),
                                                      ctypes.c_int(self.kv_heads), ctypes.c_int(self.page_size), ctypes.c_int(self.max_pages),
                                                      ctypes.c_int(splits), ctypes.c_float(scale), ctypes.c_int(window or 0),
                                                      ctypes.c_longlong(0), L.ptr(L.status(q.device)), L.stream_ptr()), "paged_decode_stream")
-                L.check(lib.dewb_decode_combine(L.ptr(pm), L.ptr(pl), L.ptr(pa), L.ptr(sinks.float().contiguous() if sinks is not None else None),
+                L.check(lib.dewb_decode_combine(L.ptr(pm), L.ptr(pl), L.ptr(pa), L.ptr(sinks32),
                                                 L.ptr(out), L.ptr(None), ctypes.c_int(R), ctypes.c_int(Hq), ctypes.c_int(D), ctypes.c_int(splits),
                                                 L.stream_ptr()), "decode_combine")
                 L.count_launches(2)
                 return out
-            L.check(lib.dewb_paged_decode(L.ptr(q.contiguous()), L.ptr(self.k[layer]), L.ptr(self.v[layer]),
+            L.check(lib.dewb_paged_decode(L.ptr(qc), L.ptr(self.k[layer]), L.ptr(self.v[layer]),
                                           L.ptr(self.k_scale[layer] if self.kind else None),
                                           L.ptr(self.v_scale[layer] if self.kind else None), L.ptr(self.page_table),
-                                          L.ptr(lengths.to(torch.int32).contiguous()),
-                                          L.ptr(sinks.float().contiguous() if sinks is not None else None), L.ptr(out), L.ptr(None),
+                                          L.ptr(lens32), L.ptr(sinks32), L.ptr(out), L.ptr(None),
                                           L.ptr(pm), L.ptr(pl), L.ptr(pa), ctypes.c_int(R), ctypes.c_int(Hq),
                                           ctypes.c_int(self.kv_heads), ctypes.c_int(D), ctypes.c_int(self.page_size),
                                           ctypes.c_int(self.max_pages), ctypes.c_int(splits), ctypes.c_float(scale),

@@ -161,7 +161,8 @@ class TokenExchange:
         self.recv.tensor.zero_()
         self._signal(self.SLOT_READY)
         ps = None if pair_scale is None else pair_scale.float().contiguous()
-        L.check(L.load().dewb_moe_push(L.ptr(x.contiguous()), L.ptr(ps), L.ptr(plan.dest_rank), L.ptr(plan.dest_pos), self.recv.ptr_array(),
+        xc = x.contiguous()                    # referenced until the launch is enqueued
+        L.check(L.load().dewb_moe_push(L.ptr(xc), L.ptr(ps), L.ptr(plan.dest_rank), L.ptr(plan.dest_pos), self.recv.ptr_array(),
                                        None, self.flags.ptr_array(), L.ptr(self.flags.tensor), ctypes.c_int(self.SLOT_READY),
                                        ctypes.c_int(self.SLOT_PUSHED), ctypes.c_uint(self.seq), ctypes.c_ulonglong(self.limit_ns),
                                        L.ptr(self.counter), ctypes.c_int(T), ctypes.c_int(d), ctypes.c_int(plan.top_k), ctypes.c_int(self.rank),

@@ -62,8 +62,10 @@ class TensorParallel:
         h = torch.empty((rows, d), dtype=torch.bfloat16, device=self.device)
         n = torch.empty_like(h) if norm_w is not None else None
         res = residual.reshape(-1, d).contiguous() if residual is not None else None
-        L.check(L.load().dewb_allreduce_rows(self.buf.ptr_array(), self.flags.ptr_array(), L.ptr(p2.contiguous()), L.ptr(res),
-                                             L.ptr(norm_w.to(torch.bfloat16) if norm_w is not None else None), L.ptr(h), L.ptr(n),
+        pc = p2.contiguous()                                         # both referenced until the launch is enqueued
+        wc = norm_w.to(torch.bfloat16) if norm_w is not None else None
+        L.check(L.load().dewb_allreduce_rows(self.buf.ptr_array(), self.flags.ptr_array(), L.ptr(pc), L.ptr(res),
+                                             L.ptr(wc), L.ptr(h), L.ptr(n),
                                              ctypes.c_int(rows), ctypes.c_int(d), ctypes.c_float(eps), ctypes.c_int(self.rank),
                                              ctypes.c_int(self.world), L.ptr(self.counters),
                                              ctypes.c_longlong(self.max_rows * self.features), ctypes.c_int(0),
