@@ -1,5 +1,10 @@
 from . import presets
+from .cache import Cached
 from .dataset import DataPartition, Dataset, Files, Loader, Memory, TokenFiles, collate
+from .mixing import Mixture, PhasedStream, RampedStream
+from .packing import Packer, pack_whole
+from .sources import Hub, JsonLines, Parquet
 from .tokenizer import ByteTokenizer
 
-__all__ = ["Dataset", "Memory", "Files", "TokenFiles", "Loader", "DataPartition", "ByteTokenizer", "presets", "collate"]
+__all__ = ["Dataset", "Memory", "Files", "TokenFiles", "Loader", "DataPartition", "ByteTokenizer", "presets", "collate", "Cached",
+           "Packer", "pack_whole", "Hub", "JsonLines", "Parquet", "Mixture", "PhasedStream", "RampedStream"]
