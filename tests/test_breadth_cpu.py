@@ -402,3 +402,32 @@ def test_categorical_functions_against_direct_forms():
     x = torch.randn(6)
     out = C.segment_log_partition(x, seg, 4)
     assert torch.allclose(out[0], torch.logsumexp(x[:2], 0)) and torch.allclose(out[2], torch.logsumexp(x[2:5], 0)) and out[1] == float("-inf")
+
+
+def test_route_report_cost_model_and_resource_model():
+    """The run-time view of the selector, the roofline cost model and the occupancy model (reference: kernel_routes,
+    generation.py device facts, launches.py)."""
+    from dew_b200.ops import cost, resources
+    from dew_b200.ops.selection import Kernel, Op, Requirement, format_route_report, route_report, OPS
+    op = Op("toy")
+    OPS["toy"] = op
+    op.kernels = [Kernel("fast", [Requirement("even", lambda c: c["n"] % 2 == 0, "n must be even")]), Kernel("any", [])]
+    assert [op.select({"n": n}) for n in (2, 3, 5)] == ["fast", "any", "any"]
+    rep = route_report()["toy"]
+    assert rep["fast"]["calls"] == 1 and rep["any"]["calls"] == 2 and rep["any"]["after_refusals"] == {"fast: even": 2}
+    assert "after fast: even" in format_route_report({"toy": rep})
+    del OPS["toy"]
+    dev = cost.Device()
+    big = cost.gemm(8192, 4096, 4096, dev=dev)
+    assert big.bound == "compute" and 0.15 < big.ms < 0.30
+    skinny = cost.gemm(128, 768, 4096, dev=dev)
+    assert skinny.bound in ("memory", "launch") and skinny.ms < 0.01
+    rows = cost.estimate(0.0, 12288 * 2560 * 2 * 2, "rows", dev=dev)
+    assert rows.bound == "memory" and 0.015 < rows.ms < 0.03
+    step = cost.decoder_step(8192, 4096, 32, 14336, 32, 8, 128, 128256, 4096, dev=dev)
+    assert 250 < step["total_ms"] < 500 and step["gemm_ms"] > 0.6 * step["total_ms"]      # one 8192-token microbatch of the 8 B model
+    occ = resources.occupancy(168, resources.LAUNCHES["flash_fwd_kernel"])
+    assert occ.ctas_per_sm == 1 and occ.by_shared == 1 and occ.by_tmem == 1 and occ.by_registers == 1
+    two = resources.occupancy(96, resources.Launch(128, 100 * 1024, 0))
+    assert two.ctas_per_sm == 2 and two.limiter == "shared memory"
+    assert resources.occupancy(255, resources.Launch(1024, 0, 0)).limiter == "registers"

@@ -72,3 +72,15 @@ def test_expert_parallel_inside_fsdp():
     got = _run(4, {"expert": 2, "fsdp": 2}, moe=True, port=29710)
     assert got["engine"] == "FSDPEngine"
     _close(ref, got, tol=5e-3)
+
+
+def test_local_checkpoint_lost_by_one_rank_is_recovered_from_its_replica(tmp_path):
+    """Hybrid sharding keeps every shard on two ranks: a rank that lost its local (emergency) checkpoint gets its shards from
+    the other holder; when both holders lost theirs the step is refused (src/dew/checkpoints/_replicas.py)."""
+    worker = os.path.join(os.path.dirname(__file__), "workers", "replica_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+           "--master-port", "29720", worker, str(tmp_path)]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    assert r["recovered"] and r["refused"] and len(r["holders_of_1"]) == 2 and r["steps_rank0"] == [2], r
