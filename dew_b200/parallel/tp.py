@@ -50,6 +50,9 @@ class TensorParallel:
         p2 = partial.reshape(-1, d)
         rows = p2.shape[0]
         if self.world == 1:
+            if residual is not None and norm_w is not None:
+                n, h = ops.stream_rms_norm(residual.reshape(-1, d), p2, norm_w, eps)      # add + norm in one kernel
+                return n.reshape(shape), h.reshape(shape)
             h = p2 if residual is None else (p2.float() + residual.reshape(-1, d).float()).to(p2.dtype)
             n = ops.rms_norm(h, norm_w, eps) if norm_w is not None else None
             return (None if n is None else n.reshape(shape)), h.reshape(shape)

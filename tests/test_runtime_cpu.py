@@ -163,3 +163,36 @@ def test_json_records_refuse_values_they_cannot_express(tmp_path):
     assert read_json(tmp_path / "ok.json")["a"] == 3
     with pytest.raises(TypeError):
         atomic_write_json(tmp_path / "bad.json", {"a": torch.zeros(3)})
+
+
+def test_step_flops_are_counted_and_scale_with_the_batch():
+    from dew_b200.models import CausalTransformer
+    from dew_b200.objectives.lm import LMObjective
+    from dew_b200.telemetry.instrumentation import model_flops_utilization, step_flops
+    torch.manual_seed(0)
+    m = CausalTransformer(vocab_size=64, emb_features=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16, mlp_features=64, max_seq_len=16, tie_embeddings=False)
+    obj = LMObjective(m, 16, ema_decay=None)
+    batch = {"tokens": torch.randint(0, 64, (4, 17))}
+    f = step_flops(obj, batch)
+    analytic = m.model_flops(4 * 16, 16) * 3
+    assert 0.7 < f.total / analytic < 1.4, (f.total, analytic)            # counted FLOPs agree with 6 N D + attention
+    assert 1.7 < f.backward / f.forward < 2.3
+    half = step_flops(obj, batch, rows=2)
+    assert abs(half.total - f.total) / f.total < 0.05                     # counted on two rows and scaled
+    assert abs(model_flops_utilization(2.25e15, 1000.0) - 1.0) < 1e-9
+
+
+def test_benchmark_step_smoke_and_perf_gate(tmp_path):
+    import json
+    from dew_b200.telemetry import benchmark_step, perf_gate
+    rows = benchmark_step.run("cpu-smoke", ["causal_transformer"])
+    assert rows and rows[0]["ms_p50"] > 0 and rows[0]["gflop_per_step"] > 0
+    rec = tmp_path / "records.jsonl"
+    rec.write_text("\n".join(json.dumps(r) for r in rows) + "\n" + json.dumps({"metric": "tok/s", "n_gpus": 1, "value": 100.0, "e2e": {"value": 98.0}}))
+    gate = tmp_path / "gate.json"
+    gate.write_text(json.dumps({"gates": [{"match": {"metric": "tok/s", "n_gpus": 1}, "field": "value", "min": 102, "tolerance": 0.03},
+                                          {"match": {"metric": "tok/s"}, "field": "e2e.value", "min": 90},
+                                          {"match": {"model": "causal_transformer"}, "field": "ms_p50", "max": 1e6}]}))
+    assert perf_gate.main(["--records", str(rec), "--gate", str(gate)]) == 0       # 100 >= 102 * 0.97
+    gate.write_text(json.dumps({"gates": [{"match": {"metric": "tok/s"}, "field": "value", "min": 120}, {"match": {"metric": "absent"}, "field": "value", "min": 1}]}))
+    assert perf_gate.main(["--records", str(rec), "--gate", str(gate)]) == 1
