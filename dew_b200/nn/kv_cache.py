@@ -91,6 +91,29 @@ class KVStore:
         self._scratch = None
         self.chunk_span: Optional[Tuple[int, int]] = None      # (first position, one past the last) of the prefill chunk in flight, when the caller knows
 
+    # ------------------------------------------------------------------ latent rows (multi-head latent attention)
+    def latent(self, layer: int, width: int) -> torch.Tensor:
+        """``[rows, max_len, width]`` per layer: what multi-head latent attention caches per token (its normalised KV latent
+        and the shared rotary key) instead of per-head keys and values.  Allocated on first use."""
+        bank = self.__dict__.setdefault("_latent", {})
+        if layer not in bank:
+            bank[layer] = torch.zeros(self.rows, self.max_len, width, dtype=self.dtype, device=self.device)
+        return bank[layer]
+
+    def write_latent(self, layer: int, values: torch.Tensor, positions: torch.Tensor) -> None:
+        """``values [R, S, width]`` at ``positions [R, S]`` of the selected rows (negative positions are skipped)."""
+        R, S = positions.shape
+        buf = self.latent(layer, values.shape[-1])
+        rows = self._rows(R)[:, None].expand(R, S)
+        live = positions >= 0
+        buf[rows[live], positions[live].long()] = values[live].to(buf.dtype)
+
+    def read_latent(self, layer: int, width: int, length: int) -> torch.Tensor:
+        """The selected rows' first ``length`` cached latents ``[R, length, width]``."""
+        buf = self.latent(layer, width)
+        rows = self._rows(self.rows if self.row_ids is None else self.row_ids.numel())
+        return buf[rows, :length]
+
     # ------------------------------------------------------------------ addressing
     def select(self, row_ids: Optional[torch.Tensor]) -> "KVStore":
         """Batch row ``i`` of the next calls addresses store row ``row_ids[i]`` (None: identity)."""

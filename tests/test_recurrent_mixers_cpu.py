@@ -52,3 +52,26 @@ def test_mamba3_parallel_matches_complex_recurrence():
     layer = R.Mamba3(16, state_dim=8, head_dim=8)
     xx = torch.randn(2, 12, 16)
     assert torch.allclose(layer(xx), layer(xx, recurrent=True), atol=1e-4)
+
+
+def test_mla_latent_cache_decodes_like_the_full_forward():
+    """Multi-head latent attention with a latent KV cache: prefill a prompt, then decode token by token through the absorbed
+    form (queries folded through the key up-projection, values rebuilt after the sum); every step equals the row of the full
+    causal forward, and the cache holds kv_latent + rope_dim numbers per token (src/dew/nn/mla.py)."""
+    import torch
+    from dew_b200 import ops
+    from dew_b200.nn.kv_cache import KVCache, KVStore
+    from dew_b200.nn.mla import MultiHeadLatentAttention
+    torch.manual_seed(0)
+    m = MultiHeadLatentAttention(32, 4, kv_latent=16, q_latent=24, nope_dim=8, rope_dim=4, v_dim=8)
+    cos, sin = ops.rope_tables(32, 4, 10000.0, torch.device("cpu"))
+    x = torch.randn(2, 12, 32)
+    pos = torch.arange(12)[None].expand(2, 12)
+    full = m(x, cos, sin, pos)
+    store = KVStore(KVCache(), 1, 2, 32, 1, 4, torch.float32, "cpu")
+    first = m(x[:, :7], cos, sin, pos[:, :7], cache=store, layer=0)
+    assert torch.allclose(first, full[:, :7], atol=1e-5)
+    for t in range(7, 12):
+        step = m(x[:, t:t + 1], cos, sin, pos[:, t:t + 1], cache=store, layer=0)
+        assert torch.allclose(step[:, 0], full[:, t], atol=1e-5), t
+    assert store.latent(0, 20).shape == (2, 32, 20)            # 16 latent + 4 rotary numbers per token, no per-head keys / values
