@@ -81,3 +81,43 @@ def test_cli_sweep_trains_every_point(tmp_path, capsys):
     assert len(lines) == 5 and lines[-1]["points"] == 4 and lines[-1]["best"] in {l["name"] for l in lines[:4]}
     assert all(l["step"] == 3 for l in lines[:4]) and len({l["name"] for l in lines[:4]}) == 4
     assert len(list((tmp_path / "sweep").iterdir())) == 4
+
+
+def test_records_rebuild_objects_and_refuse_unknown_names_and_fields():
+    """A record names a class by import path (or alias) and its fields; rebuilding converts fields by annotation, and unknown
+    aliases, unknown fields and untrusted packages raise (src/dew/registry.py)."""
+    import pytest
+    import torch
+    from dew_b200.models.causal_transformer import Mixture, TransformerConfig
+    from dew_b200.optim import OptimConfig
+    from dew_b200.utils import registry as R
+    cfg = TransformerConfig(vocab_size=64, emb_features=32, num_layers=2, num_heads=2, layer_types=("gdn", "attention"),
+                            mixture=Mixture(experts=4, top_k=2))
+    rec = R.to_record(cfg)
+    assert rec["class"] == "dew_b200.models.causal_transformer:TransformerConfig" and rec["fields"]["mixture"]["fields"]["experts"] == 4
+    import json
+    back = R.from_record(json.loads(json.dumps(rec)))
+    assert back == cfg and isinstance(back.layer_types, tuple) and isinstance(back.mixture, Mixture)
+    opt = R.from_record({"class": "optim", "fields": {"learning_rate": 1, "optimizer": "lion"}}, kind="optimizer")
+    assert isinstance(opt, OptimConfig) and isinstance(opt.learning_rate, (int, float)) and opt.optimizer == "lion"
+    model = R.from_record({"class": "causal_transformer", "fields": {"vocab_size": 32, "emb_features": 16, "num_layers": 1, "num_heads": 2}}, kind="model")
+    assert sum(p.numel() for p in model.parameters()) > 0
+    assert R.from_record(R.to_record(torch.bfloat16)) is torch.bfloat16
+    assert R.from_record({"function": "dew_b200.utils.registry:lookup"}) is R.lookup
+    with pytest.raises(KeyError, match="known"):
+        R.from_record({"class": "no_such_model"}, kind="model")
+    with pytest.raises(TypeError, match="has no field"):
+        R.from_record({"class": "optim", "fields": {"learning_rat": 1}}, kind="optimizer")
+    with pytest.raises(PermissionError, match="trusted"):
+        R.from_record({"class": "subprocess:Popen", "fields": {"args": ["true"]}})
+    with pytest.raises(R.Unrecordable):
+        R.to_record(torch.zeros(2))
+
+    @R.register("toy_model", "model")
+    class Toy(torch.nn.Module):
+        def __init__(self, width: int = 4):
+            super().__init__()
+            self.width = width
+    assert "toy_model" in R.registry("model") and R.lookup("toy_model") is Toy
+    with pytest.raises(ValueError, match="already"):
+        R.register("toy_model", "model")(object)
