@@ -89,3 +89,127 @@ class _FakeQuant(torch.autograd.Function):
 
 def fake_quant(w: torch.Tensor, kind: str = "int8") -> torch.Tensor:
     return _FakeQuant.apply(w, kind)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Quantised modules (weights stay quantised in memory), QAT wrappers and activation calibration
+import torch.nn as nn  # noqa: E402
+
+
+class QuantizedLinear(nn.Module):
+    """A ``Linear`` whose weight lives in memory in its quantised form.  fp8 weights on a GPU multiply through the
+    row-scaled e4m3 tensor-core GEMM (activations quantised per row on the way in); every other case de-quantises the
+    weight for the call.  ``from_linear`` quantises an existing layer."""
+
+    def __init__(self, in_features: int, out_features: int, kind: str, stored: Mapping[str, torch.Tensor], bias=None, dtype=torch.bfloat16):
+        super().__init__()
+        self.in_features, self.out_features, self.kind, self.dtype = in_features, out_features, kind, dtype
+        for k, v in stored.items():
+            self.register_buffer(f"q_{k}", v)
+        self.bias = bias
+
+    @classmethod
+    def from_linear(cls, lin, kind: str) -> "QuantizedLinear":
+        return cls(lin.in_features, lin.out_features, kind, quantize_weight(lin.weight.detach(), kind), lin.bias, lin.weight.dtype)
+
+    def stored(self) -> Dict[str, torch.Tensor]:
+        return {k[2:]: v for k, v in self._buffers.items() if k.startswith("q_")}
+
+    @property
+    def weight(self) -> torch.Tensor:
+        return dequantize_weight(self.stored(), self.kind, self.dtype)
+
+    def bytes(self) -> int:
+        return sum(v.numel() * v.element_size() for v in self.stored().values())
+
+    def forward(self, x):
+        from .. import ops
+        if self.kind == "float8_e4m3fn" and x.is_cuda and x.dtype == torch.bfloat16 and self.in_features % 16 == 0:
+            from ..ops.fp8 import gemm_fp8, quantize_rows
+            x2 = x.reshape(-1, self.in_features)
+            xq, xs = quantize_rows(x2)
+            y = gemm_fp8(xq, xs, self.q_q, self.q_scale).reshape(*x.shape[:-1], self.out_features)
+            return y if self.bias is None else y + self.bias
+        return ops.linear(x, self.weight.to(x.dtype), self.bias)
+
+
+def quantize_model(model: nn.Module, q: Quantization) -> Dict[str, int]:
+    """Replace every eligible ``Linear`` of ``model`` in place by a ``QuantizedLinear``; returns bytes before / after."""
+    from .layers import Linear
+    before = after = 0
+    for path, module in list(model.named_modules()):
+        for name, child in list(module.named_children()):
+            full = f"{path}.{name}" if path else name
+            if isinstance(child, Linear) and child.weight.numel() >= q.min_size and not any(s in full for s in q.skip):
+                ql = QuantizedLinear.from_linear(child, q.kind)
+                before += child.weight.numel() * child.weight.element_size()
+                after += ql.bytes()
+                setattr(module, name, ql)
+    return {"bytes_before": before, "bytes_after": after}
+
+
+class QATLinear(nn.Module):
+    """Quantisation-aware training: the forward sees the weight after a quantise / de-quantise round trip, the backward passes
+    straight through to the full-precision weight, which keeps training."""
+
+    def __init__(self, base, kind: str = "int8"):
+        super().__init__()
+        self.base, self.kind = base, kind
+
+    @property
+    def weight(self):
+        return self.base.weight
+
+    def forward(self, x):
+        from .. import ops
+        return ops.linear(x, fake_quant(self.base.weight, self.kind), self.base.bias)
+
+
+def prepare_qat(model: nn.Module, q: Quantization) -> int:
+    from .layers import Linear
+    n = 0
+    for path, module in list(model.named_modules()):
+        for name, child in list(module.named_children()):
+            full = f"{path}.{name}" if path else name
+            if isinstance(child, Linear) and child.weight.numel() >= q.min_size and not any(s in full for s in q.skip):
+                setattr(module, name, QATLinear(child, q.kind))
+                n += 1
+    return n
+
+
+def convert_qat(model: nn.Module) -> int:
+    """After QAT: every ``QATLinear`` becomes a ``QuantizedLinear`` of the weights it trained."""
+    n = 0
+    for module in list(model.modules()):
+        for name, child in list(module.named_children()):
+            if isinstance(child, QATLinear):
+                setattr(module, name, QuantizedLinear.from_linear(child.base, child.kind))
+                n += 1
+    return n
+
+
+class Calibrator:
+    """Static activation ranges: run representative batches with ``observe(model)`` active and read ``scales()`` - the absolute
+    maximum each ``Linear`` saw at its input over the calibration set, divided by the format's largest value."""
+
+    def __init__(self, kind: str = "float8_e4m3fn"):
+        self.limit = {"int8": 127.0, "float8_e4m3fn": 448.0, "nvfp4": 6.0}[kind]
+        self.amax: Dict[str, float] = {}
+        self._hooks = []
+
+    def observe(self, model: nn.Module):
+        from .layers import Linear
+        for name, m in model.named_modules():
+            if isinstance(m, (Linear, QuantizedLinear)):
+                def hook(mod, args, name=name):
+                    self.amax[name] = max(self.amax.get(name, 0.0), float(args[0].detach().abs().amax()))
+                self._hooks.append(m.register_forward_pre_hook(hook))
+        return self
+
+    def close(self):
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+
+    def scales(self) -> Dict[str, float]:
+        return {k: (v / self.limit if v > 0 else 1.0) for k, v in self.amax.items()}

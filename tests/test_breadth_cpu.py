@@ -431,3 +431,77 @@ def test_route_report_cost_model_and_resource_model():
     two = resources.occupancy(96, resources.Launch(128, 100 * 1024, 0))
     assert two.ctas_per_sm == 2 and two.limiter == "shared memory"
     assert resources.occupancy(255, resources.Launch(1024, 0, 0)).limiter == "registers"
+
+
+def test_lora_variants_quantised_base_and_peft_names():
+    from dew_b200.nn.lora import (DoRALinear, LoRAConfig, adapters_disabled, apply_lora_config, from_peft_state, load_lora_state,
+                                  lora_state, merge_all, to_peft_state)
+    torch.manual_seed(0)
+    m = _lm(qk_norm=False)
+    x = torch.randint(0, 64, (2, 8))
+    base_out = m(x)
+    paths = apply_lora_config(m, LoRAConfig(targets=("qkv_proj", "down_proj"), rank=4, rank_pattern={r"layers\.0\.": 2}, rs=True))
+    assert any("layers.0" in p for p in paths)
+    assert m.layers[0].mixer.qkv_proj.rank == 2 and m.layers[1].mixer.qkv_proj.rank == 4
+    assert torch.allclose(m(x), base_out, atol=1e-6)                      # B starts at zero
+    for n, p in m.named_parameters():
+        if "lora_b" in n:
+            torch.nn.init.normal_(p, std=0.05)
+    tuned = m(x)
+    assert not torch.allclose(tuned, base_out, atol=1e-4)
+    with adapters_disabled(m):
+        assert torch.allclose(m(x), base_out, atol=1e-6)                   # the base model, no second copy of the weights
+    peft = to_peft_state(m)
+    assert all(k.startswith("base_model.model.") for k in peft)
+    m2 = _lm(qk_norm=False)
+    m2.load_state_dict({k: v for k, v in _strip_lora(m.state_dict()).items()}, strict=False)
+    apply_lora_config(m2, LoRAConfig(targets=("qkv_proj", "down_proj"), rank=4, rank_pattern={r"layers\.0\.": 2}, rs=True))
+    load_lora_state(m2, from_peft_state(peft))
+    assert torch.allclose(m2(x), tuned, atol=1e-5)
+    merge_all(m)
+    assert torch.allclose(m(x), tuned, atol=1e-4)
+    # DoRA starts as the base, and merging keeps its output
+    d = _lm(qk_norm=False)
+    ref = d(x)
+    apply_lora_config(d, LoRAConfig(targets=("o_proj",), rank=4, dora=True))
+    assert isinstance(d.layers[0].mixer.o_proj, DoRALinear) and torch.allclose(d(x), ref, atol=1e-5)
+    for n, p in d.named_parameters():
+        if "lora_b" in n:
+            torch.nn.init.normal_(p, std=0.05)
+    out = d(x)
+    merge_all(d)
+    assert torch.allclose(d(x), out, atol=1e-4)
+    # a quantised frozen base under the adapters
+    qm = _lm(qk_norm=False)
+    ref = qm(x)
+    apply_lora_config(qm, LoRAConfig(targets=("gate_up_proj",), rank=4, quantize_base="int8"))
+    assert (qm(x) - ref).abs().max() < 0.05 and not any(n.endswith("gate_up_proj.base.weight") for n, _ in qm.named_parameters())
+    with pytest.raises(ValueError, match="no Linear matches"):
+        apply_lora_config(_lm(), LoRAConfig(targets=("nothing_like_this",)))
+
+
+def _strip_lora(sd):
+    return {k.replace(".base.", "."): v for k, v in sd.items() if "lora_" not in k and "magnitude" not in k}
+
+
+def test_quantised_modules_qat_and_calibration():
+    from dew_b200.nn.quantization import Calibrator, Quantization, QuantizedLinear, convert_qat, prepare_qat, quantize_model
+    torch.manual_seed(1)
+    m = _lm(qk_norm=False)
+    x = torch.randint(0, 64, (2, 8))
+    ref = m(x)
+    cal = Calibrator("int8").observe(m)
+    m(x)
+    cal.close()
+    assert cal.scales() and all(v > 0 for v in cal.scales().values())
+    report = quantize_model(m, Quantization(kind="int8", min_size=64))
+    assert report["bytes_after"] < 0.4 * report["bytes_before"]            # int8 + one fp32 scale per row vs fp32 weights
+    assert any(isinstance(mod, QuantizedLinear) for mod in m.modules())
+    assert (m(x) - ref).abs().max() < 0.1
+    q = _lm(qk_norm=False)
+    n = prepare_qat(q, Quantization(kind="int8", min_size=64))
+    assert n > 0
+    loss = q(x).float().pow(2).mean()
+    loss.backward()
+    assert all(p.grad is not None for nme, p in q.named_parameters() if nme.endswith("qkv_proj.base.weight"))   # straight-through
+    assert convert_qat(q) == n and any(isinstance(mod, QuantizedLinear) for mod in q.modules())
