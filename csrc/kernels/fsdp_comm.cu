@@ -383,13 +383,21 @@ allreduce_rows_kernel(Peers bufs, Peers flags, const __nv_bfloat16* __restrict__
       if (i < nvec) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[c][j] = 0.f;
-        for (int r = 0; r < world; ++r) {
-          const uint4 v = ld_sys_u4(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(bufs.p[(rank + r) % world]) + half + static_cast<long long>(row) * d) + i);
-          acc[c][0] += __uint_as_float(v.x << 16); acc[c][1] += __uint_as_float(v.x & 0xffff0000u);
-          acc[c][2] += __uint_as_float(v.y << 16); acc[c][3] += __uint_as_float(v.y & 0xffff0000u);
-          acc[c][4] += __uint_as_float(v.z << 16); acc[c][5] += __uint_as_float(v.z & 0xffff0000u);
-          acc[c][6] += __uint_as_float(v.w << 16); acc[c][7] += __uint_as_float(v.w & 0xffff0000u);
-        }
+        // all peers' vectors are requested before any is used: one round trip over NVLink, not `world` of them
+        uint4 pv[MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < world)
+            pv[r] = ld_sys_u4(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(bufs.p[(rank + r) % world]) + half + static_cast<long long>(row) * d) + i);
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < world) {
+            const uint4 v = pv[r];
+            acc[c][0] += __uint_as_float(v.x << 16); acc[c][1] += __uint_as_float(v.x & 0xffff0000u);
+            acc[c][2] += __uint_as_float(v.y << 16); acc[c][3] += __uint_as_float(v.y & 0xffff0000u);
+            acc[c][4] += __uint_as_float(v.z << 16); acc[c][5] += __uint_as_float(v.z & 0xffff0000u);
+            acc[c][6] += __uint_as_float(v.w << 16); acc[c][7] += __uint_as_float(v.w & 0xffff0000u);
+          }
         if (residual != nullptr) {
           const uint4 v = reinterpret_cast<const uint4*>(residual + static_cast<long long>(row) * d)[i];
           acc[c][0] += __uint_as_float(v.x << 16); acc[c][1] += __uint_as_float(v.x & 0xffff0000u);
@@ -442,6 +450,137 @@ allreduce_rows_kernel(Peers bufs, Peers flags, const __nv_bfloat16* __restrict__
   }
 }
 
+
+// Two-shot form of the same operation, for the latency-bound decode step and the bandwidth-bound prefill alike:
+//   1. every rank PUSHES each row of its partial into the slot [its rank] of the row's owner (rows are dealt to ranks in
+//      contiguous blocks of R = ceil(rows / world)); when its last CTA has pushed, it tells every peer (flag phase 1);
+//   2. the owner sums the `world` slots of each of its rows in fp32 (all slots requested before any is used), adds the
+//      residual, rounds to bf16, normalises, and pushes the sum row and the normalised row into EVERY rank's output
+//      regions; when its last reducing CTA is done, it tells every peer (flag phase 2);
+//   3. that CTA waits for every peer's phase-2 word, so the kernel ends only when this rank's outputs are complete.
+// Per rank 2 * (W - 1) / W of the tensor crosses NVLink once for the sum (and as much again for the normalised copy),
+// where the one-shot form pulls (W - 1) whole tensors.  The outputs live in peer-visible memory: `sum_off` / `norm_off`
+// (elements, same on every rank) are chosen by the host, which alternates regions from call to call.
+__global__ void __launch_bounds__(512)
+allreduce_rows_2shot_kernel(Peers bufs, Peers flags, const __nv_bfloat16* __restrict__ partial,
+                            const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ norm_w,
+                            int rows, int d, float eps, int rank, int world, uint32_t* __restrict__ counters,
+                            long long slots_off, long long sum_off, long long norm_off, int flag_base,
+                            unsigned long long limit_ns, int* __restrict__ err) {
+  __shared__ float red[32];
+  __shared__ unsigned int ticket;
+  if (status_poisoned(err)) return;
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(counters) + 1;
+  uint32_t* my_flags = reinterpret_cast<uint32_t*>(flags.p[rank]) + flag_base;
+  const int nvec = d >> 3;
+  const int R = (rows + world - 1) / world;
+  // 1. push every row of the partial to its owner
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int owner = row / R;
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[owner]) + slots_off +
+                                          (static_cast<long long>(rank) * R + (row - owner * R)) * d);
+    const uint4* src = reinterpret_cast<const uint4*>(partial + static_cast<long long>(row) * d);
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) dst[i] = src[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) ticket = atomicAdd(counters + 1, 1u);
+  __syncthreads();
+  if (ticket == gridDim.x - 1) {
+    if (threadIdx.x == 0) counters[1] = 0;
+    if (threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(reinterpret_cast<uint32_t*>(flags.p[threadIdx.x]) + flag_base + rank, seq);
+    }
+  }
+  // 2. the owner's CTAs reduce their rows and push the results to every rank
+  int my_rows = rows - rank * R;
+  my_rows = my_rows < 0 ? 0 : (my_rows > R ? R : my_rows);
+  const int reducers = my_rows < 1 ? 1 : (my_rows < static_cast<int>(gridDim.x) ? my_rows : static_cast<int>(gridDim.x));
+  if (static_cast<int>(blockIdx.x) >= reducers) return;
+  if (!wait_all_peers(my_flags, 0, world, seq, limit_ns, err)) return;
+  const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(bufs.p[rank]) + slots_off;
+  for (int lr = blockIdx.x; lr < my_rows; lr += gridDim.x) {
+    const long long row = static_cast<long long>(rank) * R + lr;
+    float acc[2][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int i = threadIdx.x + c * 512;
+      if (i < nvec) {
+        uint4 pv[MAX_RANKS + 1];
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < world) pv[r] = ld_sys_u4(reinterpret_cast<const uint4*>(slots + (static_cast<long long>(r) * R + lr) * d) + i);
+        if (residual != nullptr) pv[MAX_RANKS] = ld_sys_u4(reinterpret_cast<const uint4*>(residual + row * d) + i);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[c][j] = 0.f;
+#pragma unroll
+        for (int r = 0; r <= MAX_RANKS; ++r)
+          if (r < world || (r == MAX_RANKS && residual != nullptr)) {
+            const uint4 v = pv[r];
+            acc[c][0] += __uint_as_float(v.x << 16); acc[c][1] += __uint_as_float(v.x & 0xffff0000u);
+            acc[c][2] += __uint_as_float(v.y << 16); acc[c][3] += __uint_as_float(v.y & 0xffff0000u);
+            acc[c][4] += __uint_as_float(v.z << 16); acc[c][5] += __uint_as_float(v.z & 0xffff0000u);
+            acc[c][6] += __uint_as_float(v.w << 16); acc[c][7] += __uint_as_float(v.w & 0xffff0000u);
+          }
+        uint4 pk;
+        pk.x = pack_bf16(acc[c][0], acc[c][1]); pk.y = pack_bf16(acc[c][2], acc[c][3]);
+        pk.z = pack_bf16(acc[c][4], acc[c][5]); pk.w = pack_bf16(acc[c][6], acc[c][7]);
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < world)
+            reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[(rank + r) % world]) + sum_off + row * d)[i] = pk;
+        // the norm sees what was stored (bf16-rounded), as the stand-alone stream norm does
+        acc[c][0] = __uint_as_float(pk.x << 16); acc[c][1] = __uint_as_float(pk.x & 0xffff0000u);
+        acc[c][2] = __uint_as_float(pk.y << 16); acc[c][3] = __uint_as_float(pk.y & 0xffff0000u);
+        acc[c][4] = __uint_as_float(pk.z << 16); acc[c][5] = __uint_as_float(pk.z & 0xffff0000u);
+        acc[c][6] = __uint_as_float(pk.w << 16); acc[c][7] = __uint_as_float(pk.w & 0xffff0000u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += acc[c][j] * acc[c][j];
+      }
+    }
+    if (norm_w == nullptr) continue;   // (uniform over the block)
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float t = (threadIdx.x & 31) < 16 ? red[threadIdx.x & 31] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    const float rstd = rsqrtf(t / d + eps);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int i = threadIdx.x + c * 512;
+      if (i < nvec) {
+        const uint4 wv = reinterpret_cast<const uint4*>(norm_w)[i];
+        const float w[8] = {__uint_as_float(wv.x << 16), __uint_as_float(wv.x & 0xffff0000u), __uint_as_float(wv.y << 16),
+                            __uint_as_float(wv.y & 0xffff0000u), __uint_as_float(wv.z << 16), __uint_as_float(wv.z & 0xffff0000u),
+                            __uint_as_float(wv.w << 16), __uint_as_float(wv.w & 0xffff0000u)};
+        uint4 pk;
+        pk.x = pack_bf16(acc[c][0] * rstd * w[0], acc[c][1] * rstd * w[1]); pk.y = pack_bf16(acc[c][2] * rstd * w[2], acc[c][3] * rstd * w[3]);
+        pk.z = pack_bf16(acc[c][4] * rstd * w[4], acc[c][5] * rstd * w[5]); pk.w = pack_bf16(acc[c][6] * rstd * w[6], acc[c][7] * rstd * w[7]);
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < world)
+            reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(bufs.p[(rank + r) % world]) + norm_off + row * d)[i] = pk;
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) ticket = atomicAdd(counters + 2, 1u);
+  __syncthreads();
+  if (ticket != static_cast<unsigned int>(reducers) - 1) return;
+  // 3. the last reducing CTA: tell every peer, wait for every peer, advance the sequence number
+  if (threadIdx.x == 0) counters[2] = 0;
+  if (threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(flags.p[threadIdx.x]) + flag_base + world + rank, seq);
+  }
+  if (!wait_all_peers(my_flags + world, 0, world, seq, limit_ns, err)) return;
+  if (threadIdx.x == 0) { __threadfence(); *reinterpret_cast<volatile uint32_t*>(counters) = seq; }
+}
+
 }  // namespace comm
 }  // namespace dewb
 
@@ -461,5 +600,26 @@ extern "C" int dewb_allreduce_rows(const unsigned long long* buf_ptrs, const uns
       reinterpret_cast<const __nv_bfloat16*>(residual), reinterpret_cast<const __nv_bfloat16*>(norm_w),
       reinterpret_cast<__nv_bfloat16*>(sum_out), reinterpret_cast<__nv_bfloat16*>(norm_out), rows, d, eps, rank, world,
       counters, counters + 1, half_stride, slot, limit_ns, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Two-shot all-reduce + residual add + RMSNorm with the outputs in peer-visible memory (see the kernel's comment).
+// Every rank's buffer holds, at the same element offsets, `slots` ([world][ceil(rows / world)][d]), `sum` ([rows][d]) and
+// `norm` ([rows][d]); `counters`: device uint32[3] = {sequence, ticket 1, ticket 2}, zero-initialised once; flag words
+// [flag_base, flag_base + 2 * world) of every rank's flag array belong to this call site.
+extern "C" int dewb_allreduce_rows_2shot(const unsigned long long* buf_ptrs, const unsigned long long* flag_ptrs,
+                                         const void* partial, const void* residual, const void* norm_w, int rows, int d,
+                                         float eps, int rank, int world, unsigned int* counters, long long slots_off,
+                                         long long sum_off, long long norm_off, int flag_base,
+                                         unsigned long long limit_ns, int* err, void* stream) {
+  using namespace dewb::comm;
+  if (d % 8 != 0 || d > 8192 || world < 1 || world > MAX_RANKS) return -3;
+  if ((slots_off | sum_off | norm_off) & 7) return -3;          // 16-byte vectors
+  if (rows <= 0) return 0;
+  const int blocks = rows < 148 ? rows : 148;                   // one resident CTA per SM at most
+  allreduce_rows_2shot_kernel<<<blocks, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_peers(buf_ptrs, world), make_peers(flag_ptrs, world), reinterpret_cast<const __nv_bfloat16*>(partial),
+      reinterpret_cast<const __nv_bfloat16*>(residual), reinterpret_cast<const __nv_bfloat16*>(norm_w), rows, d, eps, rank,
+      world, counters, slots_off, sum_off, norm_off, flag_base, limit_ns, err);
   return static_cast<int>(cudaGetLastError());
 }

@@ -1,0 +1,306 @@
+"""Decoder families as their releases store them: one ``Family`` per published architecture says how its ``config.json``
+reads as a ``TransformerConfig`` and where its tensors differ from the Llama naming (fused projections, biases, norm
+offsets, extra norms, expert naming).  ``family_of(config)`` picks the entry by ``model_type`` / ``architectures``;
+``load_state`` / ``export_state`` move tensors between a release's names and a ``CausalTransformer``, and ``load_state``
+returns the release's keys nothing read, so a silent partial load cannot happen.
+
+Families: llama, mistral, qwen2 (q/k/v bias), qwen3 (per-head q/k norm), qwen3_moe, mixtral, gemma (norm weight stored
+minus one, GeGLU, scaled embeddings), gemma2 (output norms on every sub-layer, soft-capped logits, alternating local /
+global layers, query scale), phi3 (fused qkv and gate_up on disk), olmoe / granite-style Llama renames fall under llama.
+
+Reference: src/dew/interop/decoder_families.py, decoder_config.py, decoder_parts.py (family tables), unread.py (keys
+nothing read), hf_decoders.py.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Mapping, Optional, Sequence, Tuple
+
+import torch
+
+from ..models.causal_transformer import CausalTransformer, Mixture, TransformerConfig
+
+
+def _rope(cfg: Mapping[str, Any]) -> Tuple[float, Optional[dict]]:
+    rope = cfg.get("rope_parameters") or {}
+    theta = rope.get("rope_theta", cfg.get("rope_theta", 10000.0))
+    scaling = cfg.get("rope_scaling")
+    if scaling is None and rope.get("rope_type", "default") != "default":
+        scaling = {k: v for k, v in rope.items() if k != "rope_theta"}
+    return float(theta), scaling
+
+
+def _common(cfg: Mapping[str, Any], **over) -> Dict[str, Any]:
+    heads = cfg["num_attention_heads"]
+    theta, scaling = _rope(cfg)
+    out = dict(vocab_size=cfg["vocab_size"], emb_features=cfg["hidden_size"], num_layers=cfg["num_hidden_layers"], num_heads=heads,
+               num_kv_heads=cfg.get("num_key_value_heads") or heads, head_dim=cfg.get("head_dim") or cfg["hidden_size"] // heads,
+               mlp_features=cfg["intermediate_size"], max_seq_len=cfg.get("max_position_embeddings", 4096), rope_theta=theta,
+               rope_scaling=scaling, norm_eps=cfg.get("rms_norm_eps", 1e-6), qk_norm=False,
+               tie_embeddings=bool(cfg.get("tie_word_embeddings", False)))
+    out.update(over)
+    return out
+
+
+def _mixture(cfg: Mapping[str, Any], always_norm: bool) -> Mixture:
+    experts = cfg.get("num_local_experts") or cfg.get("num_experts")
+    return Mixture(experts=int(experts), top_k=int(cfg.get("num_experts_per_tok", 2)),
+                   expert_features=int(cfg.get("moe_intermediate_size") or cfg["intermediate_size"]),
+                   norm_topk_prob=True if always_norm else bool(cfg.get("norm_topk_prob", True)))
+
+
+@dataclass(frozen=True)
+class Family:
+    name: str
+    model_types: Tuple[str, ...]
+    architecture: str                                     # what ``config.json`` lists under ``architectures`` on export
+    read_config: Callable[[Mapping[str, Any]], Dict[str, Any]]
+    norm_offset: float = 0.0                              # the release stores ``weight - norm_offset`` (Gemma: 1)
+    fused_qkv: Optional[str] = None                       # a single tensor on disk holding q | k | v
+    fused_gate_up: Optional[str] = None                   # a single tensor holding gate | up
+    qkv_bias: bool = False
+    post_attention_norm: str = "post_attention_layernorm"  # the norm in front of the MLP
+    mixer_out_norm: Optional[str] = None                  # Gemma-2: norm on the attention output
+    mlp_out_norm: Optional[str] = None                    # Gemma-2: norm on the MLP output
+    experts: Optional[str] = None                         # 'mixtral' | 'qwen' naming of sparse layers
+    extra_config: Mapping[str, Any] = field(default_factory=dict)   # written into ``config.json`` on export
+
+
+def _llama(cfg):
+    return _common(cfg, window=cfg.get("sliding_window"))
+
+
+def _qwen2(cfg):
+    use_window = cfg.get("use_sliding_window", False)
+    return _common(cfg, qkv_bias=True, window=cfg.get("sliding_window") if use_window else None)
+
+
+def _qwen3(cfg):
+    return _common(cfg, qk_norm=True)
+
+
+def _qwen3_moe(cfg):
+    return _common(cfg, qk_norm=True, mixture=_mixture(cfg, always_norm=False))
+
+
+def _mixtral(cfg):
+    return _common(cfg, window=cfg.get("sliding_window"), mixture=_mixture(cfg, always_norm=True))
+
+
+def _gemma(cfg):
+    act = cfg.get("hidden_activation") or cfg.get("hidden_act") or "gelu_pytorch_tanh"
+    return _common(cfg, embed_scale=True, tie_embeddings=True, mlp_activation="gelu_tanh" if "tanh" in act else "gelu")
+
+
+def _gemma2(cfg):
+    base = _gemma(cfg)
+    base.update(sandwich_norm=True, attn_softcap=float(cfg.get("attn_logit_softcapping") or 0.0),
+                logit_softcap=float(cfg.get("final_logit_softcapping") or 0.0), window=cfg.get("sliding_window"),
+                layer_types=("local", "attention"),                 # even layers slide, odd layers see everything
+                query_scale=float(cfg.get("query_pre_attn_scalar", base["head_dim"])) ** -0.5)
+    return base
+
+
+def _phi3(cfg):
+    return _common(cfg, window=cfg.get("sliding_window"))
+
+
+FAMILIES: Dict[str, Family] = {f.name: f for f in (
+    Family("llama", ("llama", "granite", "olmo", "internlm2", "yi"), "LlamaForCausalLM", _llama),
+    Family("mistral", ("mistral",), "MistralForCausalLM", _llama),
+    Family("qwen2", ("qwen2",), "Qwen2ForCausalLM", _qwen2, qkv_bias=True),
+    Family("qwen3", ("qwen3",), "Qwen3ForCausalLM", _qwen3),
+    Family("qwen3_moe", ("qwen3_moe", "qwen2_moe"), "Qwen3MoeForCausalLM", _qwen3_moe, experts="qwen"),
+    Family("mixtral", ("mixtral",), "MixtralForCausalLM", _mixtral, experts="mixtral"),
+    Family("gemma", ("gemma",), "GemmaForCausalLM", _gemma, norm_offset=1.0, extra_config={"hidden_activation": "gelu_pytorch_tanh"}),
+    Family("gemma2", ("gemma2",), "Gemma2ForCausalLM", _gemma2, norm_offset=1.0, mixer_out_norm="post_attention_layernorm",
+           post_attention_norm="pre_feedforward_layernorm", mlp_out_norm="post_feedforward_layernorm",
+           extra_config={"hidden_activation": "gelu_pytorch_tanh"}),
+    Family("phi3", ("phi3",), "Phi3ForCausalLM", _phi3, fused_qkv="self_attn.qkv_proj", fused_gate_up="mlp.gate_up_proj"),
+)}
+
+
+def family_of(cfg: Mapping[str, Any]) -> Family:
+    """The family a ``config.json`` belongs to: by ``model_type`` first, else by the first entry of ``architectures``."""
+    mt = str(cfg.get("model_type") or "").lower()
+    for fam in FAMILIES.values():
+        if mt in fam.model_types:
+            return fam
+    arch = (cfg.get("architectures") or [""])[0].lower()
+    best = None
+    for fam in FAMILIES.values():                              # longest matching name wins: qwen3_moe before qwen3
+        key = fam.name.replace("_", "")
+        if key in arch and (best is None or len(key) > len(best.name.replace("_", ""))):
+            best = fam
+    if best is None:
+        raise KeyError(f"no decoder family for model_type {mt!r} / architectures {cfg.get('architectures')}; known: {sorted(FAMILIES)}")
+    return best
+
+
+def read_config(cfg: Mapping[str, Any]) -> TransformerConfig:
+    return TransformerConfig(**family_of(cfg).read_config(cfg))
+
+
+def write_config(c: TransformerConfig, family: str = "llama", dtype: str = "bfloat16") -> Dict[str, Any]:
+    fam = FAMILIES[family]
+    rope = {"rope_theta": c.rope_theta, "rope_type": "default"} if not c.rope_scaling else {"rope_theta": c.rope_theta, **c.rope_scaling}
+    out = {"model_type": fam.model_types[0], "architectures": [fam.architecture], "vocab_size": c.vocab_size, "hidden_size": c.emb_features,
+           "num_hidden_layers": c.num_layers, "num_attention_heads": c.num_heads, "num_key_value_heads": c.num_kv_heads or c.num_heads,
+           "head_dim": c.head_dim or c.emb_features // c.num_heads, "intermediate_size": c.mlp_features,
+           "max_position_embeddings": c.max_seq_len, "rope_theta": c.rope_theta, "rope_scaling": c.rope_scaling, "rope_parameters": rope,
+           "rms_norm_eps": c.norm_eps, "tie_word_embeddings": c.tie_embeddings, "hidden_act": "silu", "torch_dtype": dtype, "dtype": dtype,
+           "sliding_window": c.window, **fam.extra_config}
+    if c.mixture is not None:
+        m = c.mixture
+        out.update({"num_experts": m.experts, "num_local_experts": m.experts, "num_experts_per_tok": m.top_k, "norm_topk_prob": m.norm_topk_prob,
+                    "moe_intermediate_size": m.expert_features or c.mlp_features, "decoder_sparse_step": 1, "mlp_only_layers": []})
+    if fam.name == "gemma2":
+        out.update({"attn_logit_softcapping": c.attn_softcap or None, "final_logit_softcapping": c.logit_softcap or None,
+                    "query_pre_attn_scalar": (c.query_scale ** -2) if c.query_scale else out["head_dim"]})
+    if fam.name == "qwen2":
+        out["use_sliding_window"] = c.window is not None
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ tensors
+class _Reader:
+    """A release's tensors with a record of which were read."""
+
+    def __init__(self, tensors: Mapping[str, torch.Tensor]):
+        self.tensors, self.read = tensors, set()
+
+    def __call__(self, key: str) -> torch.Tensor:
+        self.read.add(key)
+        return self.tensors[key]
+
+    def has(self, key: str) -> bool:
+        return key in self.tensors
+
+    def unread(self) -> List[str]:
+        return sorted(k for k in self.tensors if k not in self.read and not k.endswith("rotary_emb.inv_freq"))
+
+
+def _put(p: torch.Tensor, t: torch.Tensor, offset: float = 0.0) -> None:
+    if tuple(p.shape) != tuple(t.shape):
+        raise ValueError(f"shape {tuple(t.shape)} on disk does not fit the parameter's {tuple(p.shape)}")
+    with torch.no_grad():
+        p.copy_((t.float() + offset).to(p.dtype) if offset else t.to(p.dtype))
+
+
+def load_state(model: CausalTransformer, tensors: Mapping[str, torch.Tensor], family: Family, strict: bool = True) -> List[str]:
+    """Copy a release's tensors into ``model``; returns the keys of ``tensors`` nothing read (raises on them with ``strict``)."""
+    get = _Reader(tensors)
+    off = family.norm_offset
+    c = model.config
+    H, Hkv = c.num_heads, c.num_kv_heads or c.num_heads
+    D = c.head_dim or c.emb_features // c.num_heads
+    _put(model.embed.weight, get("model.embed_tokens.weight"))
+    for i, layer in enumerate(model.layers):
+        pre = f"model.layers.{i}."
+        _put(layer.input_norm.weight, get(pre + "input_layernorm.weight"), off)
+        _put(layer.post_norm.weight, get(pre + family.post_attention_norm + ".weight"), off)
+        if family.mixer_out_norm:
+            _put(layer.mixer_out_norm.weight, get(pre + family.mixer_out_norm + ".weight"), off)
+            _put(layer.mlp_out_norm.weight, get(pre + family.mlp_out_norm + ".weight"), off)
+        a = layer.mixer
+        if family.fused_qkv:
+            _put(a.qkv_proj.weight, get(pre + family.fused_qkv + ".weight"))
+        else:
+            _put(a.qkv_proj.weight, torch.cat([get(pre + f"self_attn.{n}_proj.weight") for n in "qkv"], 0))
+        if a.qkv_proj.bias is not None:
+            _put(a.qkv_proj.bias, torch.cat([get(pre + f"self_attn.{n}_proj.bias") for n in "qkv"], 0))
+        _put(a.o_proj.weight, get(pre + "self_attn.o_proj.weight"))
+        if a.q_norm is not None:
+            _put(a.q_norm.weight, get(pre + "self_attn.q_norm.weight"), off)
+            _put(a.k_norm.weight, get(pre + "self_attn.k_norm.weight"), off)
+        if getattr(layer, "sparse", False):
+            _load_experts(layer.mlp, get, pre)
+        elif family.fused_gate_up:
+            _put(layer.mlp.gate_up_proj.weight, get(pre + family.fused_gate_up + ".weight"))
+            _put(layer.mlp.down_proj.weight, get(pre + "mlp.down_proj.weight"))
+        else:
+            _put(layer.mlp.gate_up_proj.weight, torch.cat([get(pre + "mlp.gate_proj.weight"), get(pre + "mlp.up_proj.weight")], 0))
+            _put(layer.mlp.down_proj.weight, get(pre + "mlp.down_proj.weight"))
+    _put(model.final_norm.weight, get("model.norm.weight"), off)
+    if model.head is not None:
+        _put(model.head.weight, get("lm_head.weight") if get.has("lm_head.weight") else get("model.embed_tokens.weight"))
+    elif get.has("lm_head.weight"):
+        get.read.add("lm_head.weight")                          # a tied release may still store the copy
+    left = get.unread()
+    if strict and left:
+        raise KeyError(f"{len(left)} tensor(s) of the release were not read by the {family.name} mapping: {left[:6]}")
+    return left
+
+
+def _load_experts(mlp, get: _Reader, pre: str) -> None:
+    E = mlp.mix.experts
+    for gate in ("mlp.gate.weight", "block_sparse_moe.gate.weight"):
+        if get.has(pre + gate):
+            _put(mlp.router.weight, get(pre + gate))
+            break
+    else:
+        raise KeyError(f"no router weight under {pre}")
+    if get.has(pre + "mlp.experts.gate_up_proj"):
+        _put(mlp.experts.gate_up, get(pre + "mlp.experts.gate_up_proj"))
+        _put(mlp.experts.down, get(pre + "mlp.experts.down_proj"))
+        return
+    if get.has(pre + "block_sparse_moe.experts.0.w1.weight"):
+        names = ("block_sparse_moe.experts.{}.w1.weight", "block_sparse_moe.experts.{}.w3.weight", "block_sparse_moe.experts.{}.w2.weight")
+    else:
+        names = ("mlp.experts.{}.gate_proj.weight", "mlp.experts.{}.up_proj.weight", "mlp.experts.{}.down_proj.weight")
+    _put(mlp.experts.gate_up, torch.stack([torch.cat([get(pre + names[0].format(j)), get(pre + names[1].format(j))], 0) for j in range(E)]))
+    _put(mlp.experts.down, torch.stack([get(pre + names[2].format(j)) for j in range(E)]))
+
+
+def export_state(model: CausalTransformer, family: Family) -> Dict[str, torch.Tensor]:
+    """The model's tensors under the names and layouts ``family``'s releases use."""
+    c = model.config
+    H, Hkv = c.num_heads, c.num_kv_heads or c.num_heads
+    D = c.head_dim or c.emb_features // c.num_heads
+    off = family.norm_offset
+
+    def norm(p):
+        return (p.detach().float() - off).to(p.dtype) if off else p.detach()
+    out = {"model.embed_tokens.weight": model.embed.weight.detach(), "model.norm.weight": norm(model.final_norm.weight)}
+    for i, layer in enumerate(model.layers):
+        pre = f"model.layers.{i}."
+        out[pre + "input_layernorm.weight"] = norm(layer.input_norm.weight)
+        out[pre + family.post_attention_norm + ".weight"] = norm(layer.post_norm.weight)
+        if family.mixer_out_norm:
+            out[pre + family.mixer_out_norm + ".weight"] = norm(layer.mixer_out_norm.weight)
+            out[pre + family.mlp_out_norm + ".weight"] = norm(layer.mlp_out_norm.weight)
+        a = layer.mixer
+        w = a.qkv_proj.weight.detach()
+        if family.fused_qkv:
+            out[pre + family.fused_qkv + ".weight"] = w
+        else:
+            for n, part in zip("qkv", (w[: H * D], w[H * D:(H + Hkv) * D], w[(H + Hkv) * D:])):
+                out[pre + f"self_attn.{n}_proj.weight"] = part
+        if a.qkv_proj.bias is not None:
+            b = a.qkv_proj.bias.detach()
+            for n, part in zip("qkv", (b[: H * D], b[H * D:(H + Hkv) * D], b[(H + Hkv) * D:])):
+                out[pre + f"self_attn.{n}_proj.bias"] = part
+        out[pre + "self_attn.o_proj.weight"] = a.o_proj.weight.detach()
+        if a.q_norm is not None:
+            out[pre + "self_attn.q_norm.weight"] = norm(a.q_norm.weight)
+            out[pre + "self_attn.k_norm.weight"] = norm(a.k_norm.weight)
+        if getattr(layer, "sparse", False):
+            gu_all, dn_all = layer.mlp.experts.gate_up.detach(), layer.mlp.experts.down.detach()
+            Fe = gu_all.shape[1] // 2
+            mixtral = family.experts == "mixtral"
+            out[pre + ("block_sparse_moe.gate.weight" if mixtral else "mlp.gate.weight")] = layer.mlp.router.weight.detach()
+            for j in range(gu_all.shape[0]):
+                base = pre + (f"block_sparse_moe.experts.{j}." if mixtral else f"mlp.experts.{j}.")
+                g_n, u_n, d_n = ("w1", "w3", "w2") if mixtral else ("gate_proj", "up_proj", "down_proj")
+                out[base + g_n + ".weight"], out[base + u_n + ".weight"], out[base + d_n + ".weight"] = gu_all[j, :Fe], gu_all[j, Fe:], dn_all[j]
+            continue
+        gu = layer.mlp.gate_up_proj.weight.detach()
+        if family.fused_gate_up:
+            out[pre + family.fused_gate_up + ".weight"] = gu
+        else:
+            F_ = gu.shape[0] // 2
+            out[pre + "mlp.gate_proj.weight"], out[pre + "mlp.up_proj.weight"] = gu[:F_], gu[F_:]
+        out[pre + "mlp.down_proj.weight"] = layer.mlp.down_proj.weight.detach()
+    if model.head is not None:
+        out["lm_head.weight"] = model.head.weight.detach()
+    return {k: v.contiguous() for k, v in out.items()}

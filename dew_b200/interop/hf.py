@@ -144,24 +144,35 @@ def to_hf_state(model: CausalTransformer, architecture: str = "LlamaForCausalLM"
 
 
 class Pretrained:
+    """Load / save a decoder in the layout its family's releases use (``interop.families`` picks the family from
+    ``config.json``; ``interop.release`` reads one file or shards, de-quantising stored fp8 blocks)."""
+
     @staticmethod
-    def load(directory: os.PathLike, dtype=None, device="cpu") -> CausalTransformer:
-        d = Path(directory)
-        cfg = config_from_hf(json.loads((d / "config.json").read_text()))
-        model = CausalTransformer(cfg, dtype=dtype, device=device)
-        state: Dict[str, torch.Tensor] = {}
-        for f in sorted(d.glob("*.safetensors")):
-            state.update(TS.load_file(f))
-        from_hf_state(model, state)
+    def load(directory: os.PathLike, dtype=None, device="cpu", strict: bool = True) -> CausalTransformer:
+        from .families import family_of, load_state, read_config
+        from .release import GenerationConfig, Release
+        rel = Release(directory, dtype=dtype or torch.bfloat16)
+        fam = family_of(rel.config)
+        model = CausalTransformer(read_config(rel.config), dtype=dtype, device=device)
+        model.unread_keys = load_state(model, rel, fam, strict=strict)
+        model.generation_config = GenerationConfig.read(directory)
+        model.family = fam.name
         return model
 
     @staticmethod
-    def save(model: CausalTransformer, directory: os.PathLike, architecture: str = "LlamaForCausalLM") -> None:
-        d = Path(directory)
-        d.mkdir(parents=True, exist_ok=True)
+    def save(model: CausalTransformer, directory: os.PathLike, architecture: str = "LlamaForCausalLM", family: Optional[str] = None,
+             max_shard_bytes: int = 5 << 30, fp8_blocks=None, generation=None) -> None:
+        from .families import FAMILIES, export_state, write_config
+        from .release import save_release
         dtype = str(next(model.parameters()).dtype).replace("torch.", "")
-        (d / "config.json").write_text(json.dumps(config_to_hf(model.config, architecture, dtype), indent=1))
-        TS.save_file(to_hf_state(model, architecture), d / "model.safetensors", metadata={"format": "pt"})
+        if family is None:
+            family = next((f.name for f in FAMILIES.values() if f.architecture == architecture), None)
+        if family is None:           # an architecture string outside the table: Llama naming under that label
+            cfg = config_to_hf(model.config, architecture, dtype)
+            save_release(to_hf_state(model, architecture), cfg, directory, max_shard_bytes, generation, fp8_blocks)
+            return
+        fam = FAMILIES[family]
+        save_release(export_state(model, fam), write_config(model.config, family, dtype), directory, max_shard_bytes, generation, fp8_blocks)
 
 
 # ------------------------------------------------------------------------------------------------ gated delta net layers

@@ -74,6 +74,10 @@ class TransformerConfig:
     mtp_depth: int = 0                                # multi-token prediction: extra sequential heads for tokens t+2, t+3, ...
     hyper_connections: int = 0                        # n > 1: n residual streams with learned read / write weights per sub-layer
     altup: int = 0                                    # K > 1: AltUp - K blocks, one of which every sub-layer computes on
+    qkv_bias: bool = False                            # Qwen2: bias on the fused q | k | v projection only
+    mlp_activation: str = "silu"                      # silu (SwiGLU) | gelu_tanh (Gemma's GeGLU) | gelu
+    sandwich_norm: bool = False                       # Gemma-2: every sub-layer's output is normalised before it joins the stream
+    query_scale: Optional[float] = None               # softmax scale other than head_dim ** -0.5 (Gemma-2's query_pre_attn_scalar ** -0.5)
 
     def __post_init__(self):
         if isinstance(self.mixture, Mapping):             # a run record (JSON) carries the mixture as a plain mapping
@@ -91,7 +95,7 @@ def _mixer(cfg: TransformerConfig, kind: str, dtype, device) -> nn.Module:
         return SelfAttention(cfg.emb_features, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, qk_norm=cfg.qk_norm,
                              causal=True, window=cfg.window if kind == "local" or cfg.layer_types is None else None,
                              softcap=cfg.attn_softcap, sinks=cfg.attention_sinks, norm_eps=cfg.norm_eps,
-                             init_std=cfg.init_std, dtype=dtype, device=device)
+                             init_std=cfg.init_std, qkv_bias=cfg.qkv_bias, scale=cfg.query_scale, dtype=dtype, device=device)
     if kind == "gdn":
         from ..nn.linear_attention import GatedDeltaNet
         return GatedDeltaNet(cfg.emb_features, dtype=dtype, device=device, **cfg.mixer_options)
@@ -131,8 +135,10 @@ class DecoderLayer(nn.Module):
                                  dtype=dtype, device=device)
         else:
             self.mlp = SwiGLU(cfg.emb_features, cfg.mlp_features or 4 * cfg.emb_features, init_std=cfg.init_std,
-                              dtype=dtype, device=device)
+                              activation=cfg.mlp_activation, dtype=dtype, device=device)
         self.sparse = sparse
+        self.mixer_out_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device) if cfg.sandwich_norm else None
+        self.mlp_out_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device) if cfg.sandwich_norm else None
         self.tp = None          # set by parallel.tp.tensor_parallelize: branches are then partial sums over ranks
         self.streams = None
         if cfg.hyper_connections > 1 or cfg.altup > 1:
@@ -182,8 +188,11 @@ class DecoderLayer(nn.Module):
             a = self.mixer(n, cos, sin, positions, segment_ids, cache, self.index)
         else:
             a = self.mixer(n, segment_ids=segment_ids, cache=cache, layer=self.index)
+        if self.mixer_out_norm is not None:
+            a = self.mixer_out_norm(a)
         n, h = self._norm(self.post_norm, h, a)
-        return h, self.mlp(n)
+        m = self.mlp(n)
+        return h, (m if self.mlp_out_norm is None else self.mlp_out_norm(m))
 
 
 class MTPBlock(nn.Module):
@@ -285,6 +294,7 @@ class CausalTransformer(nn.Module):
             n, _ = self.final_norm(h, reduce_from_region(branch, tp.group))
         elif tp is not None:
             n, _ = tp.reduce_add_norm(branch, h, self.final_norm.weight, self.final_norm.eps)
+            n = n.clone()        # the fused all-reduce returns views of a buffer later calls reuse; what leaves the model is owned
         else:
             n, _ = self.final_norm(h, branch)
         return n

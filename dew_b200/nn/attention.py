@@ -17,14 +17,16 @@ class SelfAttention(nn.Module):
     def __init__(self, features: int, num_heads: int, num_kv_heads: Optional[int] = None, head_dim: Optional[int] = None,
                  qk_norm: bool = False, bias: bool = False, causal: bool = True, window: Optional[int] = None,
                  softcap: float = 0.0, sinks: bool = False, norm_eps: float = 1e-6, out_zero_init: bool = False,
-                 init_std: Optional[float] = None, dtype=None, device=None):
+                 init_std: Optional[float] = None, qkv_bias: bool = False, scale: Optional[float] = None, dtype=None, device=None):
         super().__init__()
         self.features, self.num_heads = features, num_heads
+        # a softmax scale other than head_dim ** -0.5 is folded into the queries (after the norm and the rotation)
+        self.q_gain = None if scale is None else float(scale) * (head_dim or features // num_heads) ** 0.5
         self.num_kv_heads = num_kv_heads or num_heads
         self.head_dim = head_dim or features // num_heads
         self.causal, self.window, self.softcap = causal, window, softcap
         qkv_out = (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
-        self.qkv_proj = Linear(features, qkv_out, bias=bias, axes=("embed", "heads"), init_std=init_std, dtype=dtype, device=device)
+        self.qkv_proj = Linear(features, qkv_out, bias=bias or qkv_bias, axes=("embed", "heads"), init_std=init_std, dtype=dtype, device=device)
         self.o_proj = Linear(self.num_heads * self.head_dim, features, bias=bias, axes=("heads", "embed"),
                              init_std=init_std, zero_init=out_zero_init, dtype=dtype, device=device)
         self.q_norm = RMSNorm(self.head_dim, norm_eps, dtype=dtype, device=device) if qk_norm else None
@@ -59,18 +61,20 @@ class SelfAttention(nn.Module):
             qkv = torch.cat([q, k, qkv[:, :, H + Hkv:]], 2)
         if cos is not None:
             qkv = ops.rope(qkv, cos, sin, positions, rot_heads=H + Hkv)
-        return qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+        q = qkv[:, :, :H]
+        return (q if self.q_gain is None else q * self.q_gain), qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
 
     def forward(self, x, cos=None, sin=None, positions=None, segment_ids=None, cache=None, layer: int = 0):
         B, S, _ = x.shape
         if (cache is None and x.is_cuda and self.q_norm is None and self.window is None and not self.softcap
-                and self.sinks is None and segment_ids is None and not self.track_qk_max):
+                and self.sinks is None and segment_ids is None and not self.track_qk_max and self.q_gain is None):
             from ..ops.attn import packed_attention
             H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
             o = packed_attention(self.qkv_proj(x).view(B, S, H + 2 * Hkv, D), cos, sin, positions, H, Hkv, self.causal)
             if o is not None:
                 return self.o_proj(o.reshape(B, S, H * D))
-        if cache is not None and S == 1 and self.q_norm is None and positions is not None and hasattr(cache, "decode_packed"):
+        if (cache is not None and S == 1 and self.q_norm is None and self.q_gain is None and positions is not None
+                and hasattr(cache, "decode_packed")):
             # decode step: rotation, cache append and attention straight from the packed projection (no slices, no copies)
             H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
             qkv = self.qkv_proj(x).view(B, H + 2 * Hkv, D)

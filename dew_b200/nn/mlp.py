@@ -15,14 +15,20 @@ class SwiGLU(nn.Module):
     """``down(silu(gate(x)) * up(x))``; gate and up share one ``[2F, d]`` weight so the projection is one GEMM
     (the "paired gate|up in one launch" of the reference's GEMM template, src/dew/nn/moe.py:745-770)."""
 
-    def __init__(self, features: int, hidden: int, init_std: Optional[float] = None, dtype=None, device=None):
+    def __init__(self, features: int, hidden: int, init_std: Optional[float] = None, activation: str = "silu", dtype=None, device=None):
         super().__init__()
-        self.features, self.hidden = features, hidden
+        if activation not in ("silu", "gelu_tanh", "gelu"):
+            raise ValueError(f"unknown gate activation {activation!r}; known: silu, gelu_tanh, gelu")
+        self.features, self.hidden, self.activation = features, hidden, activation
         self.gate_up_proj = Linear(features, 2 * hidden, axes=("embed", "mlp"), init_std=init_std, dtype=dtype, device=device)
         self.down_proj = Linear(hidden, features, axes=("mlp", "embed"), init_std=init_std, dtype=dtype, device=device)
 
     def forward(self, x):
-        return self.down_proj(ops.packed_swiglu(self.gate_up_proj(x)))
+        gu = self.gate_up_proj(x)
+        if self.activation == "silu":
+            return self.down_proj(ops.packed_swiglu(gu))
+        g, u = gu.chunk(2, -1)                                    # GeGLU (Gemma): the gate passes through GELU
+        return self.down_proj(F.gelu(g, approximate="tanh" if self.activation == "gelu_tanh" else "none") * u)
 
 
 class GeluMLP(nn.Module):

@@ -14,6 +14,7 @@ serving with heads split over ``tensor`` (src/dew/inference/serving.py:179).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -26,6 +27,8 @@ from .symm import SymmetricBuffer
 
 
 class TensorParallel:
+    REGIONS = 4
+
     def __init__(self, group: Optional[dist.ProcessGroup] = None, max_rows: int = 4096, features: int = 4096,
                  device=None, wait_limit_s: float = 20.0):
         self.group = group
@@ -36,10 +39,23 @@ class TensorParallel:
         self.limit_ns = int(wait_limit_s * 1e9)
         self.seq = 0
         self.fused = self.device.type == "cuda" and self.world > 1
+        # 'twoshot' (default): rows are pushed to their owners, reduced there and pushed back, outputs in peer-visible
+        # memory; 'oneshot': every rank pulls every peer's whole partial (the earlier form, kept for comparison)
+        self.mode = os.environ.get("DEWB_TP_ALLREDUCE", "twoshot")
+        if self.mode not in ("twoshot", "oneshot"):
+            raise ValueError(f"DEWB_TP_ALLREDUCE must be 'twoshot' or 'oneshot', not {self.mode!r}")
+        self.calls = 0
         if self.fused:
-            self.buf = SymmetricBuffer(2 * max_rows * features, torch.bfloat16, self.device, group, zero=True)
             self.flags = SymmetricBuffer(64, torch.int32, self.device, group, zero=True)
-            self.counters = torch.zeros(4, dtype=torch.int32, device=self.device)    # {sequence, arrive, leave}
+            self.counters = torch.zeros(8, dtype=torch.int32, device=self.device)    # one-shot {sequence, arrive, leave, -}; two-shot {sequence, ticket 1, ticket 2, -}
+            if self.mode == "oneshot":
+                self.buf = SymmetricBuffer(2 * max_rows * features, torch.bfloat16, self.device, group, zero=True)
+            else:
+                # per region: slots [world][ceil(max_rows / world)][d] | sum [max_rows][d] | norm [max_rows][d]; regions alternate
+                # from call to call, so an output stays valid until the second call after the one that produced it
+                self.owner_rows = -(-max_rows // self.world)
+                self.region = (self.world * self.owner_rows + 2 * max_rows) * features
+                self.buf = SymmetricBuffer(self.REGIONS * self.region, torch.bfloat16, self.device, group, zero=True)
 
     # ------------------------------------------------------------------ inference path (no autograd)
     def reduce_add_norm(self, partial: torch.Tensor, residual: Optional[torch.Tensor], norm_w: Optional[torch.Tensor],
@@ -62,6 +78,8 @@ class TensorParallel:
             h = (s if residual is None else s + residual.reshape(-1, d).float()).to(p2.dtype)
             n = ops.rms_norm_reference(h, norm_w, eps) if norm_w is not None else None
             return (None if n is None else n.reshape(shape)), h.reshape(shape)
+        if self.mode == "twoshot":
+            return self._two_shot(p2, residual, norm_w, eps, shape)
         h = torch.empty((rows, d), dtype=torch.bfloat16, device=self.device)
         n = torch.empty_like(h) if norm_w is not None else None
         res = residual.reshape(-1, d).contiguous() if residual is not None else None
@@ -76,6 +94,29 @@ class TensorParallel:
                 "allreduce_rows")
         L.count_launches()
         return (None if n is None else n.reshape(shape)), h.reshape(shape)
+
+    def _two_shot(self, p2, residual, norm_w, eps, shape):
+        """The two-shot kernel.  The returned tensors are views of this object's peer-visible buffer: they stay valid until
+        ``REGIONS - 1`` further calls have been made (a decoder layer consumes them before its next call); clone to keep longer."""
+        rows, d = p2.shape
+        base = (self.calls % self.REGIONS) * self.region
+        self.calls += 1
+        slots_off = base
+        sum_off = base + self.world * self.owner_rows * d
+        norm_off = sum_off + self.max_rows * d
+        res = residual.reshape(-1, d).contiguous() if residual is not None else None
+        pc = p2.contiguous()                                         # all referenced until the launch is enqueued
+        wc = norm_w.to(torch.bfloat16) if norm_w is not None else None
+        L.check(L.load().dewb_allreduce_rows_2shot(self.buf.ptr_array(), self.flags.ptr_array(), L.ptr(pc), L.ptr(res), L.ptr(wc),
+                                                   ctypes.c_int(rows), ctypes.c_int(d), ctypes.c_float(eps), ctypes.c_int(self.rank),
+                                                   ctypes.c_int(self.world), L.ptr(self.counters[4:]), ctypes.c_longlong(slots_off),
+                                                   ctypes.c_longlong(sum_off), ctypes.c_longlong(norm_off), ctypes.c_int(16),
+                                                   ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.device)), L.stream_ptr()),
+                "allreduce_rows_2shot")
+        L.count_launches()
+        h = self.buf.tensor[sum_off:sum_off + rows * d].view(shape)
+        n = self.buf.tensor[norm_off:norm_off + rows * d].view(shape) if norm_w is not None else None
+        return n, h
 
     def all_reduce(self, partial: torch.Tensor) -> torch.Tensor:
         return self.reduce_add_norm(partial, None, None)[1]
@@ -263,6 +304,14 @@ def tensor_parallelize(model, tp: TensorParallel, training: bool = False):
                 q, k, v = w[: Hq * D], w[Hq * D:(Hq + Hkv) * D], w[(Hq + Hkv) * D:]
                 att.qkv_proj.weight = nn.Parameter(torch.cat([_shard_rows(q, r, W), _shard_rows(k, r, W), _shard_rows(v, r, W)], 0),
                                                    requires_grad=att.qkv_proj.weight.requires_grad)
+                b = att.qkv_proj.bias
+                if b is not None:                          # column-parallel: each rank keeps the bias of its own heads
+                    bq, bk, bv = b.data[: Hq * D], b.data[Hq * D:(Hq + Hkv) * D], b.data[(Hq + Hkv) * D:]
+                    att.qkv_proj.bias = nn.Parameter(torch.cat([_shard_rows(bq, r, W), _shard_rows(bk, r, W), _shard_rows(bv, r, W)], 0),
+                                                     requires_grad=b.requires_grad)
+                    att.qkv_proj.bias.tensor_parallel = True
+                if att.o_proj.bias is not None:
+                    raise ValueError("a bias on the row-parallel output projection would be added once per rank; fold it away before sharding")
                 att.o_proj.weight = nn.Parameter(_shard_cols(att.o_proj.weight.data, r, W), requires_grad=att.o_proj.weight.requires_grad)
                 att.num_heads, att.num_kv_heads = Hq // W, Hkv // W
             mlp = layer.mlp

@@ -1,0 +1,106 @@
+"""Decoder families: every family's release layout loads into ``CausalTransformer`` and gives the logits the
+``transformers`` implementation of that family gives (fp32, eager attention); round trips through the on-disk layout;
+sharded files, fp8 block storage, keys nothing read."""
+import json
+
+import pytest
+import torch
+
+from dew_b200.interop.families import FAMILIES, export_state, family_of, load_state, read_config
+from dew_b200.interop.hf import Pretrained
+from dew_b200.interop.release import GenerationConfig, Release, dequantize_blocks, quantize_blocks, save_release
+from dew_b200.models.causal_transformer import CausalTransformer
+
+COMMON = dict(vocab_size=96, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              intermediate_size=128, max_position_embeddings=64)
+CASES = {
+    "llama": dict(model_type="llama", head_dim=16, **COMMON),
+    "mistral": dict(model_type="mistral", head_dim=16, sliding_window=8, **COMMON),
+    "qwen2": dict(model_type="qwen2", **COMMON),
+    "qwen3": dict(model_type="qwen3", head_dim=16, **COMMON),
+    "gemma": dict(model_type="gemma", head_dim=16, **COMMON),
+    "gemma2": dict(model_type="gemma2", head_dim=16, sliding_window=8, query_pre_attn_scalar=24, **COMMON),
+    "phi3": dict(model_type="phi3", pad_token_id=0, **COMMON),
+    "mixtral": dict(model_type="mixtral", num_local_experts=4, num_experts_per_tok=2, **COMMON),
+    "qwen3_moe": dict(model_type="qwen3_moe", head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
+                      norm_topk_prob=True, **COMMON),
+}
+
+
+def _logits(model, tokens):
+    y = model(tokens)
+    return y[0] if isinstance(y, tuple) else y
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_family_matches_transformers(name, tmp_path):
+    transformers = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    cfg = transformers.AutoConfig.for_model(**CASES[name])
+    cfg._attn_implementation = "eager"
+    hf = transformers.AutoModelForCausalLM.from_config(cfg).float().eval()
+    for p in hf.parameters():
+        if p.dim() == 1:                      # norms away from one, biases away from zero
+            p.data.add_(torch.randn_like(p) * 0.1)
+    d = cfg.to_dict()
+    fam = family_of(d)
+    assert fam.name == name
+    ours = CausalTransformer(read_config(d), dtype=torch.float32).eval()
+    assert load_state(ours, dict(hf.state_dict()), fam) == []
+    tokens = torch.randint(0, 96, (2, 24))
+    with torch.no_grad():
+        want = hf(tokens).logits
+        got = _logits(ours, tokens)
+    assert float((got - want).abs().max()) <= 2e-6 * max(1.0, float(want.abs().max()))
+    # and back: the exported tensors are the release's, name for name
+    back = export_state(ours, fam)
+    theirs = {k: v for k, v in hf.state_dict().items() if not (k == "lm_head.weight" and ours.head is None)}
+    if fam.experts is None:                   # (sparse families: the module keeps experts stacked, the files hold one tensor per expert)
+        assert sorted(back) == sorted(theirs)
+    for k, v in theirs.items():
+        if k in back:
+            assert torch.allclose(back[k], v, atol=1e-6), k
+    # through the directory layout, in shards
+    Pretrained.save(ours, tmp_path, family=name, max_shard_bytes=60_000, generation=GenerationConfig(eos_token_id=[1, 2], temperature=0.7))
+    assert (tmp_path / "model.safetensors.index.json").exists()
+    again = Pretrained.load(tmp_path, dtype=torch.float32).eval()
+    assert again.family == name and again.generation_config.stop_ids() == (1, 2)
+    with torch.no_grad():
+        assert torch.equal(_logits(again, tokens), got)
+
+
+def test_unread_keys_raise():
+    torch.manual_seed(0)
+    cfg = read_config(CASES["llama"])
+    m = CausalTransformer(cfg, dtype=torch.float32)
+    state = export_state(m, FAMILIES["llama"])
+    state["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(64)
+    with pytest.raises(KeyError, match="not read"):
+        load_state(m, state, FAMILIES["llama"])
+    assert load_state(m, state, FAMILIES["llama"], strict=False) == ["model.layers.0.self_attn.q_proj.bias"]
+    with pytest.raises(KeyError, match="no decoder family"):
+        family_of({"model_type": "bert", "architectures": ["BertModel"]})
+
+
+def test_release_reads_lazily_and_dequantizes_fp8_blocks(tmp_path):
+    torch.manual_seed(0)
+    w = torch.randn(200, 300)
+    q, s = quantize_blocks(w, (128, 128))
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (2, 3)
+    deq = dequantize_blocks(q, s, (128, 128), torch.float32)
+    assert float((deq - w).abs().max()) <= float(w.abs().max()) * 2 ** -4        # e4m3: 3 mantissa bits
+    tensors = {"model.layers.0.mlp.down_proj.weight": w, "model.embed_tokens.weight": torch.randn(50, 300),
+               "model.layers.1.mlp.down_proj.weight": torch.randn(200, 300)}
+    names = save_release(tensors, {"model_type": "llama"}, tmp_path, max_shard_bytes=100_000, fp8_blocks=(128, 128))
+    assert len(names) >= 2
+    rel = Release(tmp_path, dtype=torch.float32)
+    assert rel.config["quantization_config"]["weight_block_size"] == [128, 128]
+    assert sorted(rel) == sorted(tensors)                  # the scales belong to their weights, not to the mapping
+    assert rel.opened == []
+    got = rel["model.layers.0.mlp.down_proj.weight"]
+    assert len(rel.opened) >= 1 and len(rel.opened) < len(names) + 1
+    assert torch.equal(got, deq)
+    assert torch.equal(rel["model.embed_tokens.weight"], tensors["model.embed_tokens.weight"])     # skipped names stay as they are
+    raw = Release(tmp_path, dequantize=False)
+    assert raw["model.layers.0.mlp.down_proj.weight"].dtype == torch.float8_e4m3fn
+    assert "model.layers.0.mlp.down_proj.weight_scale_inv" in raw

@@ -31,6 +31,17 @@ def test_tensor_parallel_two_gpus_fused_allreduce():
         pytest.skip("needs two GPUs")
     r = _run(2, "nccl", 29632)
     assert r["err"] < 3e-2, r
+    assert r["allreduce_worst"] < 1.2e-2, r          # bf16 rounding of the sum and of the normalised row
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.parametrize("world", [4, 8])
+def test_tensor_parallel_more_gpus_fused_allreduce(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    r = _run(world, "nccl", 29632 + world)
+    assert r["err"] < 3e-2 and r["allreduce_worst"] < 1.2e-2, r
 
 
 def _run_spl(world, backend, port, *extra):

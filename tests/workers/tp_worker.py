@@ -26,7 +26,7 @@ def main():
         dev, dtype = torch.device("cpu"), torch.float32
         dist.init_process_group("gloo")
     torch.manual_seed(0)
-    kw = dict(vocab_size=128, emb_features=256, num_layers=2, num_heads=8, num_kv_heads=4, head_dim=64, mlp_features=512,
+    kw = dict(vocab_size=128, emb_features=256, num_layers=2, num_heads=8, num_kv_heads=max(4, int(os.environ.get('WORLD_SIZE', '1'))), head_dim=64, mlp_features=512,
               max_seq_len=64, qk_norm=False, tie_embeddings=False)
     full = CausalTransformer(**kw).to(dev, dtype).eval()
     torch.manual_seed(0)
@@ -42,12 +42,35 @@ def main():
     ga = generate(full, None, prompts, 6, sampling=Sampling(temperature=0.0))
     gb = generate(sharded, None, prompts, 6, sampling=Sampling(temperature=0.0))
     same = bool(torch.equal(ga.tokens, gb.tokens))
+    # the fused all-reduce + add + norm by itself: row counts that do not divide by the world, with and without residual / norm,
+    # called back to back (regions rotate), against the sum computed by the process group
+    worst = 0.0
+    if dev.type == "cuda":
+        world = dist.get_world_size()
+        g = torch.Generator(device="cpu").manual_seed(100 + rank)
+        w = (1.0 + 0.1 * torch.randn(256, generator=torch.Generator().manual_seed(3))).to(dev, torch.bfloat16)
+        prev = None
+        for it, rows in enumerate((1, 7, 60, 256, 3, 128, 128, 128)):
+            part = torch.randn(rows, 256, generator=g).to(dev, torch.bfloat16)
+            res = None if it % 3 == 0 else torch.randn(rows, 256, generator=torch.Generator().manual_seed(50 + it)).to(dev, torch.bfloat16)
+            if it >= 6:
+                res = prev                                   # the residual is the previous call's own output, as in a decoder
+            n, h = tp.reduce_add_norm(part, res, w if it % 2 == 0 else None, 1e-5)
+            total = part.float().clone()
+            dist.all_reduce(total)
+            want_h = (total + (res.float() if res is not None else 0)).to(torch.bfloat16)
+            worst = max(worst, float((h.float() - want_h.float()).abs().max()) / (float(want_h.float().abs().max()) + 1e-6))
+            if n is not None:
+                hf = want_h.float()
+                want_n = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+                worst = max(worst, float((n.float() - want_n).abs().max()) / (float(want_n.abs().max()) + 1e-6))
+            prev = h
     if dev.type == "cuda":
         from dew_b200.ops import library as L
         torch.cuda.synchronize()
         L.check_status()
     if rank == 0:
-        print("RESULT " + json.dumps({"err": err, "same_tokens": same, "world": dist.get_world_size()}))
+        print("RESULT " + json.dumps({"err": err, "same_tokens": same, "world": dist.get_world_size(), "allreduce_worst": worst}))
     dist.barrier()
     dist.destroy_process_group()
 
