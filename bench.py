@@ -38,7 +38,7 @@ ROWS_PER_GPU = 32
 # The other training configurations (selected with --config; the headline above is the default and the only one the
 # one-line contract of this script describes):
 #   moe     d_model 2048, 24 layers, 16 heads, 64 routed experts (FFN 1408, SwiGLU) top-6 softmax + 2 shared experts,
-#           row-scaled fp8 expert GEMMs, expert parallelism over all N ranks, sequence 4096, 16 sequences per GPU
+#           block-scaled MXFP8 expert GEMMs (1 x 32 ue8m0 blocks; forward and input gradient, bf16 weight gradient), expert parallelism over all N ranks, sequence 4096, 16 sequences per GPU
 #   hybrid  d_model 2048, 24 layers in a 3 x gated-delta-net (16 heads x 128, short conv 4) + 1 x attention pattern,
 #           sequence 8192, 8 sequences per GPU, FSDP
 CONFIGS = {
@@ -48,7 +48,7 @@ CONFIGS = {
                            mlp_features=1408, max_seq_len=4096, qk_norm=False, tie_embeddings=False, norm_eps=1e-5),
                 mixture=dict(experts=64, top_k=6, expert_features=1408, shared_features=2 * 1408, fp8=True),
                 seq=4096, rows=16, metric="train tokens/sec (MoE LM, expert parallel)",
-                name="MoE: d2048 L24 H16 64 experts x 1408 top-6 + 2 shared, fp8 expert GEMMs, vocab 32768"),
+                name="MoE: d2048 L24 H16 64 experts x 1408 top-6 + 2 shared, MXFP8 expert GEMMs, vocab 32768"),
     "hybrid": dict(model=dict(vocab_size=32768, emb_features=2048, num_layers=24, num_heads=16, num_kv_heads=16, head_dim=128,
                               mlp_features=5632, max_seq_len=8192, qk_norm=False, tie_embeddings=False, norm_eps=1e-5,
                               layer_types=("gdn", "gdn", "gdn", "attention"),
@@ -349,7 +349,7 @@ def main() -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None,
             "vs_derived_mark": value / (DERIVED_MARK_TOK_S_PER_GPU * world) if args.config == "dense" else None,
-            "dtype": "bf16" if args.config != "moe" else "bf16 (fp8 e4m3 expert GEMMs)",
+            "dtype": "bf16" if args.config != "moe" else "bf16 (block-scaled MXFP8 e4m3 expert GEMMs: forward and input gradient)",
             "data": "synthetic (uniform random token ids from a seed; random-init weights)",
             "config": {"model": conf["name"], "params": n_params,
                        "global_batch": rows * world, "seq_len": SEQ_LEN, "micro_batch": micro,

@@ -359,9 +359,8 @@ allreduce_rows_kernel(Peers bufs, Peers flags, const __nv_bfloat16* __restrict__
       for (int i = threadIdx.x; i < nvec0; i += blockDim.x)
         mine[static_cast<long long>(row) * nvec0 + i] = reinterpret_cast<const uint4*>(partial + static_cast<long long>(row) * d)[i];
   }
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) ticket = atomicAdd(arrive_counter, 1u);
+  if (threadIdx.x == 0) { __threadfence_system(); ticket = atomicAdd(arrive_counter, 1u); }
   __syncthreads();
   if (ticket == gridDim.x - 1) {
     // the last CTA to finish staging announces the whole buffer to every rank (itself included)
@@ -482,9 +481,9 @@ allreduce_rows_2shot_kernel(Peers bufs, Peers flags, const __nv_bfloat16* __rest
     const uint4* src = reinterpret_cast<const uint4*>(partial + static_cast<long long>(row) * d);
     for (int i = threadIdx.x; i < nvec; i += blockDim.x) dst[i] = src[i];
   }
-  __threadfence_system();
+  // the block's stores are ordered before the barrier, and thread 0's system-scope fence after it is cumulative over them
   __syncthreads();
-  if (threadIdx.x == 0) ticket = atomicAdd(counters + 1, 1u);
+  if (threadIdx.x == 0) { __threadfence_system(); ticket = atomicAdd(counters + 1, 1u); }
   __syncthreads();
   if (ticket == gridDim.x - 1) {
     if (threadIdx.x == 0) counters[1] = 0;
@@ -566,9 +565,8 @@ allreduce_rows_2shot_kernel(Peers bufs, Peers flags, const __nv_bfloat16* __rest
       }
     }
   }
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) ticket = atomicAdd(counters + 2, 1u);
+  if (threadIdx.x == 0) { __threadfence_system(); ticket = atomicAdd(counters + 2, 1u); }
   __syncthreads();
   if (ticket != static_cast<unsigned int>(reducers) - 1) return;
   // 3. the last reducing CTA: tell every peer, wait for every peer, advance the sequence number
@@ -579,6 +577,172 @@ allreduce_rows_2shot_kernel(Peers bufs, Peers flags, const __nv_bfloat16* __rest
   }
   if (!wait_all_peers(my_flags + world, 0, world, seq, limit_ns, err)) return;
   if (threadIdx.x == 0) { __threadfence(); *reinterpret_cast<volatile uint32_t*>(counters) = seq; }
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Low-latency form for the decode step (a few hundred rows): the same two shots, but every 16-byte store carries its own
+// arrival flag - {2 bf16, seq, 2 bf16, seq} - so a receiver polls the data it needs and no fence, flag store or ticket sits
+// between the phases (each 8-byte half of an aligned 16-byte store arrives whole).  Twice the bytes, a third of the latency.
+//   1. every rank pushes each row of its partial, in that format, into slot [its rank] of the row's owner;
+//   2. the owner polls the `world` slots of each of its rows, sums in fp32, adds the residual, rounds to bf16 and pushes the
+//      sum row, in that format, to every rank (itself included);
+//   3. every rank polls the sum rows, writes them to its own (ordinary) output and normalises them there.
+// `seq` (device counter + 1, the same on every rank) is the flag value: whatever an earlier call left in a region carries
+// another number.  The host alternates regions from call to call; a rank can run at most one call ahead of a peer (it needs
+// that peer's next push to go further), so two regions suffice.  Polls are bounded: on time-out the error word is set and the
+// kernel runs to its end on whatever it read.
+struct LLine { uint32_t d0, f0, d1, f1; };
+
+__device__ __forceinline__ void st_ll(void* p, uint32_t d0, uint32_t d1, uint32_t seq) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(seq), "r"(d1), "r"(seq) : "memory");
+}
+__device__ __forceinline__ LLine ld_ll(const void* p) {
+  LLine v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.d0), "=r"(v.f0), "=r"(v.d1), "=r"(v.f1) : "l"(p) : "memory");
+  return v;
+}
+
+template <int N>
+__device__ __forceinline__ bool poll_lines(const uint8_t* const (&addr)[N], LLine (&out)[N], int n, uint32_t seq,
+                                           unsigned long long limit_ns, int* err) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    bool all = true;
+#pragma unroll
+    for (int k = 0; k < N; ++k)
+      if (k < n) {
+        out[k] = ld_ll(addr[k]);
+        all = all && out[k].f0 == seq && out[k].f1 == seq;
+      }
+    if (all) return true;
+    if ((++spins & 31) == 0) {
+      if (t0 == 0) t0 = now_ns();
+      else if (now_ns() - t0 > limit_ns) { atomicCAS(err, 0, ERR_WAIT_PEER); return false; }
+    }
+  }
+}
+
+__device__ __forceinline__ void add_bf16x2(float& a, float& b, uint32_t v) {
+  a += __uint_as_float(v << 16);
+  b += __uint_as_float(v & 0xffff0000u);
+}
+
+__global__ void __launch_bounds__(512)
+allreduce_rows_ll_kernel(Peers bufs, const __nv_bfloat16* __restrict__ partial, const __nv_bfloat16* __restrict__ residual,
+                         const __nv_bfloat16* __restrict__ norm_w, __nv_bfloat16* __restrict__ sum_out,
+                         __nv_bfloat16* __restrict__ norm_out, int rows, int d, float eps, int rank, int world,
+                         uint32_t* __restrict__ counters, long long slots_off, long long sums_off,
+                         unsigned long long limit_ns, int* __restrict__ err) {
+  __shared__ float red[32];
+  if (status_poisoned(err)) return;
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(counters) + 1;
+  const int nvec = d >> 3;                       // 8 bf16 = two lines per vector
+  const long long row_bytes = static_cast<long long>(d) * 4;     // a row in line format
+  const int R = (rows + world - 1) / world;
+  // 1. push the partial's rows to their owners
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int owner = row / R;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(bufs.p[owner]) + slots_off + (static_cast<long long>(rank) * R + (row - owner * R)) * row_bytes;
+    const uint4* src = reinterpret_cast<const uint4*>(partial + static_cast<long long>(row) * d);
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const uint4 v = src[i];
+      st_ll(dst + i * 32, v.x, v.y, seq);
+      st_ll(dst + i * 32 + 16, v.z, v.w, seq);
+    }
+  }
+  // 2. the owner's rows: poll the slots, reduce, push the sums to every rank
+  int my_rows = rows - rank * R;
+  my_rows = my_rows < 0 ? 0 : (my_rows > R ? R : my_rows);
+  const uint8_t* slots = reinterpret_cast<const uint8_t*>(bufs.p[rank]) + slots_off;
+  for (int lr = blockIdx.x; lr < my_rows; lr += gridDim.x) {
+    const long long row = static_cast<long long>(rank) * R + lr;
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const uint8_t* addr[2 * MAX_RANKS];
+      LLine ln[2 * MAX_RANKS];
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r) {
+        const uint8_t* base = slots + (static_cast<long long>(r < world ? r : 0) * R + lr) * row_bytes + i * 32;
+        addr[2 * r] = base;
+        addr[2 * r + 1] = base + 16;
+      }
+      poll_lines<2 * MAX_RANKS>(addr, ln, 2 * world, seq, limit_ns, err);
+      float a[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = 0.f;
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r)
+        if (r < world) {
+          add_bf16x2(a[0], a[1], ln[2 * r].d0); add_bf16x2(a[2], a[3], ln[2 * r].d1);
+          add_bf16x2(a[4], a[5], ln[2 * r + 1].d0); add_bf16x2(a[6], a[7], ln[2 * r + 1].d1);
+        }
+      if (residual != nullptr) {
+        const uint4 v = reinterpret_cast<const uint4*>(residual + row * d)[i];
+        add_bf16x2(a[0], a[1], v.x); add_bf16x2(a[2], a[3], v.y); add_bf16x2(a[4], a[5], v.z); add_bf16x2(a[6], a[7], v.w);
+      }
+      const uint32_t p0 = pack_bf16(a[0], a[1]), p1 = pack_bf16(a[2], a[3]), p2 = pack_bf16(a[4], a[5]), p3 = pack_bf16(a[6], a[7]);
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r)
+        if (r < world) {
+          uint8_t* dst = reinterpret_cast<uint8_t*>(bufs.p[(rank + r) % world]) + sums_off + row * row_bytes + i * 32;
+          st_ll(dst, p0, p1, seq);
+          st_ll(dst + 16, p2, p3, seq);
+        }
+    }
+  }
+  // 3. every rank: poll the sum rows, write them out, normalise
+  const uint8_t* sums = reinterpret_cast<const uint8_t*>(bufs.p[rank]) + sums_off;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float acc[2][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int i = threadIdx.x + c * 512;
+      if (i < nvec) {
+        const uint8_t* addr[2] = {sums + row * row_bytes + i * 32, sums + row * row_bytes + i * 32 + 16};
+        LLine ln[2];
+        poll_lines<2>(addr, ln, 2, seq, limit_ns, err);
+        uint4 pk;
+        pk.x = ln[0].d0; pk.y = ln[0].d1; pk.z = ln[1].d0; pk.w = ln[1].d1;
+        if (sum_out != nullptr) reinterpret_cast<uint4*>(sum_out + static_cast<long long>(row) * d)[i] = pk;
+        acc[c][0] = __uint_as_float(pk.x << 16); acc[c][1] = __uint_as_float(pk.x & 0xffff0000u);
+        acc[c][2] = __uint_as_float(pk.y << 16); acc[c][3] = __uint_as_float(pk.y & 0xffff0000u);
+        acc[c][4] = __uint_as_float(pk.z << 16); acc[c][5] = __uint_as_float(pk.z & 0xffff0000u);
+        acc[c][6] = __uint_as_float(pk.w << 16); acc[c][7] = __uint_as_float(pk.w & 0xffff0000u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += acc[c][j] * acc[c][j];
+      }
+    }
+    if (norm_out == nullptr) continue;   // (uniform over the block)
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float t = (threadIdx.x & 31) < 16 ? red[threadIdx.x & 31] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    const float rstd = rsqrtf(t / d + eps);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const int i = threadIdx.x + c * 512;
+      if (i < nvec) {
+        const uint4 wv = reinterpret_cast<const uint4*>(norm_w)[i];
+        const float w[8] = {__uint_as_float(wv.x << 16), __uint_as_float(wv.x & 0xffff0000u), __uint_as_float(wv.y << 16),
+                            __uint_as_float(wv.y & 0xffff0000u), __uint_as_float(wv.z << 16), __uint_as_float(wv.z & 0xffff0000u),
+                            __uint_as_float(wv.w << 16), __uint_as_float(wv.w & 0xffff0000u)};
+        uint4 pk;
+        pk.x = pack_bf16(acc[c][0] * rstd * w[0], acc[c][1] * rstd * w[1]); pk.y = pack_bf16(acc[c][2] * rstd * w[2], acc[c][3] * rstd * w[3]);
+        pk.z = pack_bf16(acc[c][4] * rstd * w[4], acc[c][5] * rstd * w[5]); pk.w = pack_bf16(acc[c][6] * rstd * w[6], acc[c][7] * rstd * w[7]);
+        reinterpret_cast<uint4*>(norm_out + static_cast<long long>(row) * d)[i] = pk;
+      }
+    }
+  }
+  // the last CTA to leave advances the sequence number for the next launch (every CTA read it before it could leave)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(counters + 1, 1u);
+    if (t == gridDim.x - 1) { counters[1] = 0; __threadfence(); *reinterpret_cast<volatile uint32_t*>(counters) = seq; }
+  }
 }
 
 }  // namespace comm
@@ -621,5 +785,25 @@ extern "C" int dewb_allreduce_rows_2shot(const unsigned long long* buf_ptrs, con
       make_peers(buf_ptrs, world), make_peers(flag_ptrs, world), reinterpret_cast<const __nv_bfloat16*>(partial),
       reinterpret_cast<const __nv_bfloat16*>(residual), reinterpret_cast<const __nv_bfloat16*>(norm_w), rows, d, eps, rank,
       world, counters, slots_off, sum_off, norm_off, flag_base, limit_ns, err);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Low-latency all-reduce + residual add + RMSNorm (see the kernel's comment).  Every rank's byte buffer holds, at the same
+// byte offsets, `slots` ([world][ceil(rows / world)][d] in line format, 4 bytes per element) and `sums` ([rows][d], same
+// format); `counters`: device uint32[2] = {sequence, leave ticket}, zero-initialised once; the outputs are ordinary local tensors.
+extern "C" int dewb_allreduce_rows_ll(const unsigned long long* buf_ptrs, const void* partial, const void* residual,
+                                      const void* norm_w, void* sum_out, void* norm_out, int rows, int d, float eps, int rank,
+                                      int world, unsigned int* counters, long long slots_off, long long sums_off,
+                                      unsigned long long limit_ns, int* err, void* stream) {
+  using namespace dewb::comm;
+  if (d % 8 != 0 || d > 8192 || world < 1 || world > MAX_RANKS) return -3;
+  if ((slots_off | sums_off) & 15) return -3;
+  if (rows <= 0) return 0;
+  const int blocks = rows < 148 ? rows : 148;                   // every CTA must be resident: they poll what others push
+  allreduce_rows_ll_kernel<<<blocks, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      make_peers(buf_ptrs, world), reinterpret_cast<const __nv_bfloat16*>(partial),
+      reinterpret_cast<const __nv_bfloat16*>(residual), reinterpret_cast<const __nv_bfloat16*>(norm_w),
+      reinterpret_cast<__nv_bfloat16*>(sum_out), reinterpret_cast<__nv_bfloat16*>(norm_out), rows, d, eps, rank, world, counters,
+      slots_off, sums_off, limit_ns, err);
   return static_cast<int>(cudaGetLastError());
 }

@@ -30,6 +30,7 @@ def main(argv=None):
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--chunk", type=int, default=2048)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--prefill-rows", type=int, default=16384, help="rows the fused all-reduce buffers hold (a prefill step's token budget)")
     ap.add_argument("--out", default=None)
     ap.add_argument("--profile", default=None, help="write a torch.profiler kernel table of eight decode steps to this file")
     ap.add_argument("--arrival-rate", type=float, default=0.0,
@@ -58,7 +59,7 @@ def main(argv=None):
     for p in model.parameters():
         p.requires_grad_(False)
     capacity = args.max_prompt + args.new_tokens
-    tp = TensorParallel(None, max_rows=max(args.requests, args.chunk), features=cfg["emb_features"], device=dev)
+    tp = TensorParallel(None, max_rows=max(args.requests, args.chunk, args.prefill_rows), features=cfg["emb_features"], device=dev)
     tensor_parallelize(model, tp)
     torch.cuda.empty_cache()
     server = Server(model, slots=args.requests, capacity=capacity, kv_cache=KVCache(page_size=args.page_size),
@@ -100,22 +101,39 @@ def main(argv=None):
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     decoded0 = server.decoded_tokens
     steps0 = server.steps
+    wait0, wall0 = server.wait_s, time.perf_counter()
     start.record()
     server.run()
     end.record()
     torch.cuda.synchronize()
+    host_busy_ms = 1e3 * ((time.perf_counter() - wall0) - (server.wait_s - wait0)) / max(1, server.steps - steps0)
     L.check_status()
     ms = start.elapsed_time(end)
     if world > 1:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    # the decode step by itself: the captured graph replayed back to back at the final sequence lengths (no host work between
+    # replays), so that a step bound by the host shows as a gap between this number and ms_per_decode_step
+    graph_ms = None
+    if getattr(server, "_graph", None) is not None:
+        server._in_pos.copy_(torch.tensor([n + args.new_tokens - 2 for n in lens], device=dev))
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        start.record()
+        for _ in range(20):
+            server._graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        L.check_status()
+        graph_ms = start.elapsed_time(end) / 20
     new_tokens = sum(len(t.tokens) for t in tickets)
     decode_tokens = server.decoded_tokens - decoded0
     ttft = sorted(t.first_token_time for t in tickets)
     out = {"metric": "TP decode tokens/sec", "value": decode_tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
            "requests": args.requests, "new_tokens_each": args.new_tokens, "decode_steps": server.steps - steps0,
-           "ms_per_decode_step": ms / max(1, server.steps - steps0), "prefill_s": t_prefill,
+           "ms_per_decode_step": ms / max(1, server.steps - steps0), "graph_replay_ms": graph_ms, "host_busy_ms_per_step": host_busy_ms, "prefill_s": t_prefill,
            "ttft_p50_s": ttft[len(ttft) // 2], "ttft_p90_s": ttft[int(len(ttft) * 0.9)], "total_new_tokens": new_tokens,
            "prompt_tokens": sum(lens), "layers": args.layers, "cuda_graph": not args.no_graph, "page_size": args.page_size,
            "dtype": "bf16", "data": "synthetic prompts, random-init weights", "gpu_launches": L.LAUNCHES}

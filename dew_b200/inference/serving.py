@@ -86,6 +86,7 @@ class Server:
         self.cuda_graph = cuda_graph and self.device.type == "cuda"
         self._graph = None
         self.steps = 0
+        self.wait_s = 0.0
         self.decoded_tokens = 0
         if variables is None:
             self._call = lambda t, **kw: model(t, **kw)
@@ -160,6 +161,8 @@ class Server:
         self.steps += 1
 
     def _seat(self) -> None:
+        if not self.queue:
+            return
         for slot in range(self.slots):
             if self.rows[slot] is not None or not self.queue:
                 continue
@@ -278,17 +281,23 @@ class Server:
         if self._ring_events[self._ring_at] is not None:
             self._ring_events[self._ring_at].synchronize()
         self._host_pos = self._host_ring[self._ring_at]
-        self._host_pos.fill_(-1)
+        # one list, written into the pinned buffer in one assignment (per-element tensor writes cost microseconds each)
+        vals = [-1] * self.slots
+        greedy = True
+        default_greedy = self.sampling.greedy
         for s, r in active:
-            if r.generated + 1 < r.ticket.max_new_tokens:
-                self._host_pos[s] = len(r.ticket.prompt) + r.generated
+            t = r.ticket
+            if r.generated + 1 < t.max_new_tokens:
+                vals[s] = len(t.prompt) + r.generated
+            greedy = greedy and (default_greedy if t.sampling is None else t.sampling.greedy)
+        self._host_pos.numpy()[:] = vals
+        any_live = max(vals) >= 0
         self._in_pos.copy_(self._host_pos, non_blocking=True)
         if self.device.type == "cuda":
             e = torch.cuda.Event()
             e.record()
             self._ring_events[self._ring_at] = e
-        greedy = all((r.ticket.sampling or self.sampling).greedy for _, r in active)
-        if bool((self._host_pos >= 0).any()):
+        if any_live:
             if self.cuda_graph and greedy:
                 if self._graph is None:
                     self._decode_program(True)                      # warm-up (allocations, lazy initialisation)
@@ -309,7 +318,7 @@ class Server:
                             self.last_tokens[s] = self._draw(self._logits[s][None], r, r.generated + 1)
         else:
             self._prev.copy_(self.last_tokens)
-        snapshot = [(s, r) for s, r in active]
+        snapshot = active
         # hand the tokens that were the *input* of this step to the host, asynchronously
         host = torch.empty(self.slots, dtype=torch.long, pin_memory=self.device.type == "cuda")
         host.copy_(self._prev, non_blocking=True)
@@ -332,13 +341,16 @@ class Server:
         while len(later) > keep:
             host, snapshot, ev = later.popleft()
             if ev is not None:
+                t_wait = time.perf_counter()
                 ev.synchronize()
+                self.wait_s += time.perf_counter() - t_wait       # time the host stood waiting for the device
             now = self.clock()
+            toks = host.tolist()
             for s, r in snapshot:
                 t = r.ticket
                 if t.done:
                     continue
-                tok = int(host[s])
+                tok = toks[s]
                 t.tokens.append(tok)
                 self.decoded_tokens += 1
                 if t.first_token_time is None:

@@ -182,6 +182,43 @@ class KVStore:
                 and Hq // self.kv_heads <= 8 and os.environ.get("DEWB_DECODE", "stream") == "stream"
                 and hasattr(L.load(), "dewb_rope_append"))
 
+    MIN_TILES = 4            # fewest 64-key tiles one CTA of the balanced decode kernel takes (bounds the parts a row is cut into)
+
+    def _fused_decode(self, lib, layer: int, q, q_row_stride: int, lens32, R: int, Hq: int, D: int, window, sinks32, out) -> None:
+        """The streamed paged-attention kernel finishing its rows itself.  Up to 1024 rows take the balanced persistent form
+        (every CTA moves the same number of tiles, whatever the rows' lengths); more rows take one CTA per (row, head, chunk)."""
+        longest = min(self.max_len, window) if window else self.max_len
+        max_tiles = -(-longest // 64) + 1                                 # (+ 1: a window that straddles a tile boundary)
+        persist = R <= 1024 and os.environ.get("DEWB_DECODE_PERSIST", "1") == "1"
+        if persist:
+            min_tiles = int(os.environ.get("DEWB_DECODE_MIN_TILES", self.MIN_TILES))
+            splits = (max_tiles - 1) // min_tiles + 2
+        else:
+            chunk = 8
+            splits = max(1, -(-max_tiles // chunk))
+        n = R * Hq * splits
+        if self._scratch is None or self._scratch[0].numel() < n:
+            self._scratch = (torch.empty(n, dtype=torch.float32, device=q.device), torch.empty(n, dtype=torch.float32, device=q.device),
+                             torch.empty(n * D, dtype=torch.float32, device=q.device))
+        if getattr(self, "_arrivals", None) is None or self._arrivals.numel() < R * self.kv_heads:
+            self._arrivals = torch.zeros(R * self.kv_heads, dtype=torch.int32, device=q.device)
+        pm, pl, pa = self._scratch
+        common = (L.ptr(q), L.ptr(self.k[layer]), L.ptr(self.v[layer]), ctypes.c_longlong(self.pages * self.page_size),
+                  L.ptr(self.page_table), L.ptr(lens32), L.ptr(pm), L.ptr(pl), L.ptr(pa), L.ptr(self._arrivals), L.ptr(sinks32),
+                  L.ptr(out), ctypes.c_int(R), ctypes.c_int(Hq), ctypes.c_int(self.kv_heads), ctypes.c_int(self.page_size),
+                  ctypes.c_int(self.max_pages), ctypes.c_int(splits))
+        if persist:
+            if getattr(self, "_ctas", None) is None:
+                self._ctas = 2 * torch.cuda.get_device_properties(q.device).multi_processor_count
+            L.check(lib.dewb_paged_decode_persist(*common, ctypes.c_int(min_tiles), ctypes.c_float(1.0 / math.sqrt(D)),
+                                                  ctypes.c_int(window or 0), ctypes.c_longlong(q_row_stride), ctypes.c_int(self._ctas),
+                                                  L.ptr(L.status(q.device)), L.stream_ptr()), "paged_decode_persist")
+        else:
+            L.check(lib.dewb_paged_decode_fused(*common, ctypes.c_int(chunk), ctypes.c_float(1.0 / math.sqrt(D)),
+                                                ctypes.c_int(window or 0), ctypes.c_longlong(q_row_stride),
+                                                L.ptr(L.status(q.device)), L.stream_ptr()), "paged_decode_fused")
+        L.count_launches()
+
     def decode_packed(self, layer: int, qkv: torch.Tensor, cos, sin, positions: torch.Tensor, Hq: int, window=None, sinks=None):
         """One decode step of a layer straight from the packed projection output ``qkv [R, Hq + 2 Hkv, D]``: one kernel rotates
         the query / key heads in place and appends the keys and values to the paged cache, then the streamed paged-attention
@@ -193,30 +230,12 @@ class KVStore:
                                      ctypes.c_int(self.kv_heads), ctypes.c_int(D), ctypes.c_int(cos.shape[0] if cos is not None else 0),
                                      L.ptr(self.k[layer]), L.ptr(self.v[layer]), L.ptr(self.page_table), ctypes.c_int(self.page_size),
                                      ctypes.c_int(self.max_pages), L.stream_ptr()), "rope_append")
-        splits = 1
-        longest = self.max_len
-        while splits < 16 and R * self.kv_heads * splits < 592 and longest // (splits * 2) >= 256:
-            splits *= 2
-        splits = max(splits, min(16, (longest + 511) // 512))
-        n = R * Hq * splits
-        if self._scratch is None or self._scratch[0].numel() < n:
-            self._scratch = (torch.empty(n, dtype=torch.float32, device=qkv.device), torch.empty(n, dtype=torch.float32, device=qkv.device),
-                             torch.empty(n * D, dtype=torch.float32, device=qkv.device))
-        pm, pl, pa = self._scratch
         out = torch.empty((R, Hq, D), dtype=qkv.dtype, device=qkv.device)
-        L.check(lib.dewb_paged_decode_stream(L.ptr(qkv), L.ptr(self.k[layer]), L.ptr(self.v[layer]),
-                                             ctypes.c_longlong(self.pages * self.page_size), L.ptr(self.page_table), L.ptr(lens32),
-                                             L.ptr(pm), L.ptr(pl), L.ptr(pa), ctypes.c_int(R), ctypes.c_int(Hq),
-                                             ctypes.c_int(self.kv_heads), ctypes.c_int(self.page_size), ctypes.c_int(self.max_pages),
-                                             ctypes.c_int(splits), ctypes.c_float(1.0 / math.sqrt(D)), ctypes.c_int(window or 0),
-                                             ctypes.c_longlong(H * D), L.ptr(L.status(qkv.device)), L.stream_ptr()), "paged_decode_stream")
         sk = getattr(self, "_sinks32", None)
         if sinks is not None and (sk is None or sk[0] is not sinks):
             self._sinks32 = sk = (sinks, sinks.detach().float().contiguous())
-        L.check(lib.dewb_decode_combine(L.ptr(pm), L.ptr(pl), L.ptr(pa), L.ptr(sk[1] if sinks is not None else None),
-                                        L.ptr(out), L.ptr(None), ctypes.c_int(R), ctypes.c_int(Hq), ctypes.c_int(D), ctypes.c_int(splits),
-                                        L.stream_ptr()), "decode_combine")
-        L.count_launches(3)
+        self._fused_decode(lib, layer, qkv, H * D, lens32, R, Hq, D, window, sk[1] if sinks is not None else None, out)
+        L.count_launches(1)
         return out
 
     # ------------------------------------------------------------------ reads
@@ -260,6 +279,9 @@ class KVStore:
             sinks32 = sinks.float().contiguous() if sinks is not None else None
             if (self.kind == 0 and D == 128 and self.page_size % 64 == 0 and hasattr(lib, "dewb_paged_decode_stream")
                     and os.environ.get("DEWB_DECODE", "stream") == "stream"):
+                if scale == 1.0 / math.sqrt(D) and os.environ.get("DEWB_DECODE_FUSED", "1") == "1":
+                    self._fused_decode(lib, layer, qc, 0, lens32, R, Hq, D, window, sinks32, out)
+                    return out
                 # streamed form: TMA page tiles into a shared-memory ring, scores and values on the warp-level tensor cores
                 L.check(lib.dewb_paged_decode_stream(L.ptr(qc), L.ptr(self.k[layer]), L.ptr(self.v[layer]),
                                                      ctypes.c_longlong(self.pages * self.page_size), L.ptr(self.page_table), L.ptr(lens32),

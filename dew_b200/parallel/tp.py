@@ -28,6 +28,7 @@ from .symm import SymmetricBuffer
 
 class TensorParallel:
     REGIONS = 4
+    LL_ROWS = 512
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None, max_rows: int = 4096, features: int = 4096,
                  device=None, wait_limit_s: float = 20.0):
@@ -39,23 +40,34 @@ class TensorParallel:
         self.limit_ns = int(wait_limit_s * 1e9)
         self.seq = 0
         self.fused = self.device.type == "cuda" and self.world > 1
-        # 'twoshot' (default): rows are pushed to their owners, reduced there and pushed back, outputs in peer-visible
-        # memory; 'oneshot': every rank pulls every peer's whole partial (the earlier form, kept for comparison)
-        self.mode = os.environ.get("DEWB_TP_ALLREDUCE", "twoshot")
-        if self.mode not in ("twoshot", "oneshot"):
-            raise ValueError(f"DEWB_TP_ALLREDUCE must be 'twoshot' or 'oneshot', not {self.mode!r}")
+        # How the fused all-reduce + add + norm moves its rows (DEWB_TP_ALLREDUCE):
+        #   'auto' (default)  up to LL_ROWS rows take the low-latency kernel (every 16-byte store carries its own arrival flag,
+        #                     ordinary local outputs); more rows take the two-shot kernel below
+        #   'twoshot'         rows are pushed to their owners, reduced there and pushed back; a flag per phase; outputs in
+        #                     peer-visible memory
+        #   'oneshot'         every rank pulls every peer's whole partial (the earlier form, kept for comparison)
+        self.mode = os.environ.get("DEWB_TP_ALLREDUCE", "auto")
+        if self.mode not in ("auto", "ll", "twoshot", "oneshot"):
+            raise ValueError(f"DEWB_TP_ALLREDUCE must be auto, ll, twoshot or oneshot, not {self.mode!r}")
         self.calls = 0
         if self.fused:
             self.flags = SymmetricBuffer(64, torch.int32, self.device, group, zero=True)
-            self.counters = torch.zeros(8, dtype=torch.int32, device=self.device)    # one-shot {sequence, arrive, leave, -}; two-shot {sequence, ticket 1, ticket 2, -}
+            # one-shot {sequence, arrive, leave, -}; two-shot {sequence, ticket 1, ticket 2, -}; low-latency {sequence, leave}
+            self.counters = torch.zeros(12, dtype=torch.int32, device=self.device)
             if self.mode == "oneshot":
                 self.buf = SymmetricBuffer(2 * max_rows * features, torch.bfloat16, self.device, group, zero=True)
             else:
                 # per region: slots [world][ceil(max_rows / world)][d] | sum [max_rows][d] | norm [max_rows][d]; regions alternate
-                # from call to call, so an output stays valid until the second call after the one that produced it
+                # from call to call, so an output stays valid until REGIONS - 1 further calls have been made
                 self.owner_rows = -(-max_rows // self.world)
                 self.region = (self.world * self.owner_rows + 2 * max_rows) * features
                 self.buf = SymmetricBuffer(self.REGIONS * self.region, torch.bfloat16, self.device, group, zero=True)
+            if self.mode in ("auto", "ll"):
+                # line format: 4 bytes per element; per region: slots [world][ceil(ll_rows / world)][d] | sums [ll_rows][d]
+                self.ll_rows = min(max_rows, self.LL_ROWS) if self.mode == "auto" else max_rows
+                self.ll_owner_rows = -(-self.ll_rows // self.world)
+                self.ll_region = (self.world * self.ll_owner_rows + self.ll_rows) * features * 4
+                self.ll_buf = SymmetricBuffer(2 * self.ll_region // 4, torch.int32, self.device, group, zero=True)
 
     # ------------------------------------------------------------------ inference path (no autograd)
     def reduce_add_norm(self, partial: torch.Tensor, residual: Optional[torch.Tensor], norm_w: Optional[torch.Tensor],
@@ -72,13 +84,27 @@ class TensorParallel:
             h = p2 if residual is None else (p2.float() + residual.reshape(-1, d).float()).to(p2.dtype)
             n = ops.rms_norm(h, norm_w, eps) if norm_w is not None else None
             return (None if n is None else n.reshape(shape)), h.reshape(shape)
+        if self.fused and rows > self.max_rows and d == self.features and p2.dtype == torch.bfloat16:
+            # more rows than the peer-visible buffers hold: the fused kernel block by block, results gathered into one tensor
+            h = torch.empty((rows, d), dtype=torch.bfloat16, device=self.device)
+            n = torch.empty_like(h) if norm_w is not None else None
+            res2 = residual.reshape(-1, d) if residual is not None else None
+            for r0 in range(0, rows, self.max_rows):
+                r1 = min(rows, r0 + self.max_rows)
+                nb, hb = self.reduce_add_norm(p2[r0:r1], None if res2 is None else res2[r0:r1], norm_w, eps)
+                h[r0:r1].copy_(hb)
+                if n is not None:
+                    n[r0:r1].copy_(nb)
+            return (None if n is None else n.reshape(shape)), h.reshape(shape)
         if not self.fused or rows > self.max_rows or d != self.features or p2.dtype != torch.bfloat16:
             s = p2.float().contiguous()
             dist.all_reduce(s, group=self.group)
             h = (s if residual is None else s + residual.reshape(-1, d).float()).to(p2.dtype)
             n = ops.rms_norm_reference(h, norm_w, eps) if norm_w is not None else None
             return (None if n is None else n.reshape(shape)), h.reshape(shape)
-        if self.mode == "twoshot":
+        if self.mode in ("auto", "ll") and rows <= self.ll_rows:
+            return self._low_latency(p2, residual, norm_w, eps, shape)
+        if self.mode != "oneshot":
             return self._two_shot(p2, residual, norm_w, eps, shape)
         h = torch.empty((rows, d), dtype=torch.bfloat16, device=self.device)
         n = torch.empty_like(h) if norm_w is not None else None
@@ -92,6 +118,26 @@ class TensorParallel:
                                              ctypes.c_longlong(self.max_rows * self.features), ctypes.c_int(0),
                                              ctypes.c_ulonglong(self.limit_ns), L.ptr(L.status(self.device)), L.stream_ptr()),
                 "allreduce_rows")
+        L.count_launches()
+        return (None if n is None else n.reshape(shape)), h.reshape(shape)
+
+    def _low_latency(self, p2, residual, norm_w, eps, shape):
+        rows, d = p2.shape
+        base = (self.calls & 1) * self.ll_region
+        self.calls += 1
+        # the row geometry of the call (not of the buffer) places the slots, so both offsets depend on this call's rows only
+        owner_rows = -(-rows // self.world)
+        sums_off = base + self.world * owner_rows * d * 4
+        h = torch.empty((rows, d), dtype=torch.bfloat16, device=self.device)
+        n = torch.empty_like(h) if norm_w is not None else None
+        res = residual.reshape(-1, d).contiguous() if residual is not None else None
+        pc = p2.contiguous()                                         # all referenced until the launch is enqueued
+        wc = norm_w.to(torch.bfloat16) if norm_w is not None else None
+        L.check(L.load().dewb_allreduce_rows_ll(self.ll_buf.ptr_array(), L.ptr(pc), L.ptr(res), L.ptr(wc), L.ptr(h), L.ptr(n),
+                                                ctypes.c_int(rows), ctypes.c_int(d), ctypes.c_float(eps), ctypes.c_int(self.rank),
+                                                ctypes.c_int(self.world), L.ptr(self.counters[8:]), ctypes.c_longlong(base),
+                                                ctypes.c_longlong(sums_off), ctypes.c_ulonglong(self.limit_ns),
+                                                L.ptr(L.status(self.device)), L.stream_ptr()), "allreduce_rows_ll")
         L.count_launches()
         return (None if n is None else n.reshape(shape)), h.reshape(shape)
 

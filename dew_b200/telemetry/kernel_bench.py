@@ -307,21 +307,23 @@ def bench_moe(out, peaks, flush, iters=10):
 
 
 def bench_decode(out, peaks, flush, iters=10, rows=128, max_len=2304):
-    """Paged decode attention at the serving configuration: 128 rows, 32 query / 8 KV heads of 128, page 64, context lengths
-    uniform in [128, max_len]; the bytes are the keys and values each row reads once."""
+    """Paged decode attention at the serving configuration: 128 rows, page 64, context lengths uniform in [128, max_len], with
+    the heads of one GPU (32 query / 8 KV) and of one of eight tensor-parallel ranks (4 / 1); the bytes are the keys and values
+    each row reads once.  ``DEWB_DECODE_PERSIST=0`` times the one-CTA-per-chunk form instead of the balanced one."""
     from ..nn.kv_cache import KVCache, KVStore
-    store = KVStore(KVCache(page_size=64), 1, rows, max_len, 8, 128, torch.bfloat16, "cuda")
-    store.k.normal_()
-    store.v.normal_()
-    g = torch.Generator().manual_seed(0)
-    lengths = torch.randint(128, max_len + 1, (rows,), generator=g).to("cuda", torch.int32)
-    q = torch.randn(rows, 32, 128, device="cuda").to(torch.bfloat16)
-    ref = store.decode_attention(0, q, lengths)
-    t = device_time(lambda: store.decode_attention(0, q, lengths), iters=iters, flush=flush)
-    L.check_status()
-    nbytes = int(lengths.sum()) * 8 * 128 * 2 * 2
-    _row(out, kernel="paged_decode", rows=rows, max_len=max_len, mean_len=float(lengths.float().mean()), ms=t.median_ms,
-         gbs=nbytes / t.median_ms / 1e6, frac_of_measured=nbytes / t.median_ms / 1e6 / peaks["hbm_gbs"], finite=bool(torch.isfinite(ref.float()).all()))
+    for Hq, Hkv in ((32, 8), (4, 1)):
+        store = KVStore(KVCache(page_size=64), 1, rows, max_len, Hkv, 128, torch.bfloat16, "cuda")
+        store.k.normal_()
+        store.v.normal_()
+        g = torch.Generator().manual_seed(0)
+        lengths = torch.randint(128, max_len + 1, (rows,), generator=g).to("cuda", torch.int32)
+        q = torch.randn(rows, Hq, 128, device="cuda").to(torch.bfloat16)
+        ref = store.decode_attention(0, q, lengths)
+        t = device_time(lambda: store.decode_attention(0, q, lengths), iters=iters, flush=flush)
+        L.check_status()
+        nbytes = int(lengths.sum()) * Hkv * 128 * 2 * 2
+        _row(out, kernel="paged_decode", rows=rows, heads=f"{Hq}/{Hkv}", max_len=max_len, mean_len=float(lengths.float().mean()), ms=t.median_ms,
+             gbs=nbytes / t.median_ms / 1e6, frac_of_measured=nbytes / t.median_ms / 1e6 / peaks["hbm_gbs"], finite=bool(torch.isfinite(ref.float()).all()))
 
 
 def main(argv=None):

@@ -419,6 +419,42 @@ def test_paged_decode_streamed_kernel_window_sinks_and_long_rows():
         assert rel_err(out, old) <= 2e-2
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(4, 1), (32, 8)])
+def test_paged_decode_balanced_persistent_kernel(Hq, Hkv):
+    """The balanced persistent form of the streamed decode kernel (every CTA takes the same number of tiles; rows cut across
+    CTAs are merged by the last one to arrive) on a serving-sized batch: 128 rows of very different lengths, some empty, against
+    the reference and against the one-CTA-per-chunk form; twice, so that the self-resetting tickets are seen to reset."""
+    import os
+    from dew_b200.nn.kv_cache import KVCache, KVStore, paged_attention_reference
+    torch.manual_seed(17)
+    rows, max_len, D = 128, 2304, 128
+    store = KVStore(KVCache(page_size=64), 1, rows, max_len, Hkv, D, torch.bfloat16, DEV)
+    perm = torch.randperm(store.pages, device=DEV).to(torch.int32)
+    store.page_table.copy_(perm.reshape(rows, store.max_pages))
+    store.k.normal_()
+    store.v.normal_()
+    lengths = torch.randint(1, max_len + 1, (rows,), device=DEV, dtype=torch.int32)
+    lengths[::17] = 0                                    # rows that hold nothing yet
+    lengths[5], lengths[6] = 1, 2304
+    q = torch.randn(rows, Hq, D, device=DEV).to(torch.bfloat16)
+    sinks = torch.randn(Hq, device=DEV)
+    for window, sk in ((None, None), (700, sinks)):
+        ref = paged_attention_reference(store, 0, q.float(), lengths, 1.0 / math.sqrt(D), window, sk, 0.0)
+        live = lengths > 0
+        for _ in range(2):
+            out = store.decode_attention(0, q, lengths, window=window, sinks=sk)
+            assert rel_err(out[live], ref[live]) <= 2e-2, (window, rel_err(out[live], ref[live]))
+            assert torch.all(out[~live] == 0)
+        os.environ["DEWB_DECODE_PERSIST"] = "0"
+        try:
+            chunked = store.decode_attention(0, q, lengths, window=window, sinks=sk)
+        finally:
+            os.environ.pop("DEWB_DECODE_PERSIST")
+        assert rel_err(chunked[live], ref[live]) <= 2e-2
+    assert int(store._arrivals.abs().sum()) == 0
+    L.check_status()
+
+
 @pytest.mark.parametrize("B,T,C,K,act,bias", [(2, 200, 64, 4, True, False), (1, 1000, 4096 + 8, 4, True, True), (3, 65, 128, 3, False, True)])
 def test_short_conv_forward_backward(B, T, C, K, act, bias):
     from dew_b200.ops import scan

@@ -11,10 +11,10 @@ import torch
 WORKER = os.path.join(os.path.dirname(__file__), "workers", "tp_worker.py")
 
 
-def _run(world, backend, port):
+def _run(world, backend, port, mode="auto"):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), WORKER, backend]
-    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2"))
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2", DEWB_TP_ALLREDUCE=mode))
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     return json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
 
@@ -29,9 +29,10 @@ def test_tensor_parallel_two_cpu_ranks():
 def test_tensor_parallel_two_gpus_fused_allreduce():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    r = _run(2, "nccl", 29632)
-    assert r["err"] < 3e-2, r
-    assert r["allreduce_worst"] < 1.2e-2, r          # bf16 rounding of the sum and of the normalised row
+    for i, mode in enumerate(("auto", "twoshot", "oneshot")):        # low-latency lines, two flagged shots, one-shot pull
+        r = _run(2, "nccl", 29632 + 20 * i, mode)
+        assert r["err"] < 3e-2, (mode, r)
+        assert r["allreduce_worst"] < 1.2e-2, (mode, r)          # bf16 rounding of the sum and of the normalised row
 
 
 @pytest.mark.gpu
@@ -40,8 +41,9 @@ def test_tensor_parallel_two_gpus_fused_allreduce():
 def test_tensor_parallel_more_gpus_fused_allreduce(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    r = _run(world, "nccl", 29632 + world)
-    assert r["err"] < 3e-2 and r["allreduce_worst"] < 1.2e-2, r
+    for i, mode in enumerate(("auto", "twoshot")):
+        r = _run(world, "nccl", 29632 + world + 20 * i, mode)
+        assert r["err"] < 3e-2 and r["allreduce_worst"] < 1.2e-2, (mode, r)
 
 
 def _run_spl(world, backend, port, *extra):

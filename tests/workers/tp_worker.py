@@ -50,10 +50,10 @@ def main():
         g = torch.Generator(device="cpu").manual_seed(100 + rank)
         w = (1.0 + 0.1 * torch.randn(256, generator=torch.Generator().manual_seed(3))).to(dev, torch.bfloat16)
         prev = None
-        for it, rows in enumerate((1, 7, 60, 256, 3, 128, 128, 128)):
+        for it, rows in enumerate((1, 7, 60, 256, 3, 600, 128, 128, 128)):
             part = torch.randn(rows, 256, generator=g).to(dev, torch.bfloat16)
             res = None if it % 3 == 0 else torch.randn(rows, 256, generator=torch.Generator().manual_seed(50 + it)).to(dev, torch.bfloat16)
-            if it >= 6:
+            if it >= 7:
                 res = prev                                   # the residual is the previous call's own output, as in a decoder
             n, h = tp.reduce_add_norm(part, res, w if it % 2 == 0 else None, 1e-5)
             total = part.float().clone()
