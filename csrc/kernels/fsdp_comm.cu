@@ -656,9 +656,15 @@ allreduce_rows_ll_kernel(Peers bufs, const __nv_bfloat16* __restrict__ partial, 
   int my_rows = rows - rank * R;
   my_rows = my_rows < 0 ? 0 : (my_rows > R ? R : my_rows);
   const uint8_t* slots = reinterpret_cast<const uint8_t*>(bufs.p[rank]) + slots_off;
-  for (int lr = blockIdx.x; lr < my_rows; lr += gridDim.x) {
-    const long long row = static_cast<long long>(rank) * R + lr;
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+  // The owned rows are few (rows / world): their vectors are dealt to ALL CTAs in warp-sized runs, so that the pushes to the
+  // peers leave from every SM instead of from `my_rows` of them.
+  const int total_vec = my_rows * nvec;
+  const int lane = threadIdx.x & 31;
+  for (int run = (threadIdx.x >> 5) * gridDim.x + blockIdx.x; run * 32 < total_vec; run += gridDim.x * (blockDim.x >> 5)) {
+    const int v = run * 32 + lane;
+    if (v < total_vec) {
+      const int lr = v / nvec, i = v - lr * nvec;
+      const long long row = static_cast<long long>(rank) * R + lr;
       const uint8_t* addr[2 * MAX_RANKS];
       LLine ln[2 * MAX_RANKS];
 #pragma unroll
@@ -678,8 +684,8 @@ allreduce_rows_ll_kernel(Peers bufs, const __nv_bfloat16* __restrict__ partial, 
           add_bf16x2(a[4], a[5], ln[2 * r + 1].d0); add_bf16x2(a[6], a[7], ln[2 * r + 1].d1);
         }
       if (residual != nullptr) {
-        const uint4 v = reinterpret_cast<const uint4*>(residual + row * d)[i];
-        add_bf16x2(a[0], a[1], v.x); add_bf16x2(a[2], a[3], v.y); add_bf16x2(a[4], a[5], v.z); add_bf16x2(a[6], a[7], v.w);
+        const uint4 rv = reinterpret_cast<const uint4*>(residual + row * d)[i];
+        add_bf16x2(a[0], a[1], rv.x); add_bf16x2(a[2], a[3], rv.y); add_bf16x2(a[4], a[5], rv.z); add_bf16x2(a[6], a[7], rv.w);
       }
       const uint32_t p0 = pack_bf16(a[0], a[1]), p1 = pack_bf16(a[2], a[3]), p2 = pack_bf16(a[4], a[5]), p3 = pack_bf16(a[6], a[7]);
 #pragma unroll

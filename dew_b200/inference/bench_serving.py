@@ -73,6 +73,12 @@ def main(argv=None):
         dist.barrier()
     if args.arrival_rate > 0:
         return open_loop(args, server, prompts, lens, rank, world, dev, L)
+    # a warm server: one short request first (library handles, lazily loaded kernels, the decode graph), outside the measurement
+    server.submit(prompts[0][:args.min_prompt], 4)
+    server.run()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     t0 = time.perf_counter()
     tickets = [server.submit(p, args.new_tokens) for p in prompts]
     if args.profile:

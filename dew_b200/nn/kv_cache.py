@@ -78,7 +78,9 @@ class KVStore:
         self.pages = spec.pages or rows * self.max_pages
         self.kind = KINDS[spec.quantized]
         store = {0: dtype, 1: torch.int8, 2: torch.float8_e4m3fn}[self.kind]
-        shape = (layers, self.pages, self.page_size, kv_heads, head_dim)
+        # one page beyond the addressable pool: writes of padding positions land there, so that a write needs no data-dependent
+        # shapes (and therefore no host synchronisation); no page table entry ever names it
+        shape = (layers, self.pages + 1, self.page_size, kv_heads, head_dim)
         self.k = torch.zeros(shape, dtype=store, device=device)
         self.v = torch.zeros(shape, dtype=store, device=device)
         self.k_scale = torch.ones(shape[:-1], dtype=torch.float32, device=device) if self.kind else None
@@ -132,10 +134,11 @@ class KVStore:
     def write(self, layer: int, k: torch.Tensor, v: torch.Tensor, positions: torch.Tensor) -> None:
         """Store ``k, v [R, S, Hkv, D]`` at ``positions [R, S]`` (negative positions are skipped)."""
         R, S = positions.shape
-        rows = self._rows(R)[:, None].expand(R, S)
-        live = positions >= 0
-        slots = self._slots(rows[live], positions[live])
-        kk, vv = k[live], v[live]
+        rows = self._rows(R)[:, None].expand(R, S).reshape(-1)
+        flat = positions.reshape(-1)
+        live = flat >= 0
+        slots = torch.where(live, self._slots(rows, flat.clamp_min(0)), self.pages * self.page_size)      # padding -> the spare page
+        kk, vv = k.reshape(R * S, self.kv_heads, self.head_dim), v.reshape(R * S, self.kv_heads, self.head_dim)
         kp, vp = self.k[layer].reshape(-1, self.kv_heads, self.head_dim), self.v[layer].reshape(-1, self.kv_heads, self.head_dim)
         if self.kind:
             kq, ks = quantize(kk, self.spec.quantized)

@@ -319,11 +319,51 @@ def bench_decode(out, peaks, flush, iters=10, rows=128, max_len=2304):
         lengths = torch.randint(128, max_len + 1, (rows,), generator=g).to("cuda", torch.int32)
         q = torch.randn(rows, Hq, 128, device="cuda").to(torch.bfloat16)
         ref = store.decode_attention(0, q, lengths)
-        t = device_time(lambda: store.decode_attention(0, q, lengths), iters=iters, flush=flush)
+        t = device_time(lambda: store.decode_attention(0, q, lengths), iters=iters, flush=flush, graph=True)     # a launch of tens of microseconds: replayed from a graph
         L.check_status()
         nbytes = int(lengths.sum()) * Hkv * 128 * 2 * 2
         _row(out, kernel="paged_decode", rows=rows, heads=f"{Hq}/{Hkv}", max_len=max_len, mean_len=float(lengths.float().mean()), ms=t.median_ms,
              gbs=nbytes / t.median_ms / 1e6, frac_of_measured=nbytes / t.median_ms / 1e6 / peaks["hbm_gbs"], finite=bool(torch.isfinite(ref.float()).all()))
+
+
+def bench_mx(out, peaks, flush, iters=10):
+    """Block-scaled MXFP8 products at the expert shapes of the MoE configuration (tokens x 2816 x 2048 and tokens x 2048 x 1408),
+    dense: quantiser time, product time, against this library's bf16 product of the same shape."""
+    from .. import ops
+    from ..ops import mx
+    for M, N, K in ((16384, 2816, 2048), (16384, 2048, 1408), (98304, 2816, 2048)):
+        x = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        w = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+        xq, xs = mx.quantize_mx(x)
+        wq, ws = mx.quantize_mx(w, sf_rows=mx._pad128(N + mx.TILE_N))
+        t_q = device_time(lambda: mx.quantize_mx(x), iters=iters, flush=flush)
+        t_g = device_time(lambda: mx.gemm_mx(xq, xs, wq, ws), iters=iters, flush=flush)
+        t_b = device_time(lambda: ops.linear(x, w), iters=iters, flush=flush)
+        L.check_status()
+        fl = 2.0 * M * N * K
+        _row(out, kernel="gemm_mxfp8", M=M, N=N, K=K, quantize_ms=t_q.median_ms, quantize_gbs=(M * K * 3 + M * K / 32) / t_q.median_ms / 1e6,
+             ms=t_g.median_ms, tflops=fl / t_g.median_ms / 1e9, bf16_ms=t_b.median_ms, bf16_tflops=fl / t_b.median_ms / 1e9,
+             frac_of_measured_bf16_peak=fl / t_g.median_ms / 1e9 / peaks["bf16_tflops"])
+
+
+def bench_conv(out, peaks, flush, iters=10):
+    """Depthwise causal short convolution (kernel 4, SiLU) at the hybrid configuration's layer: 8 x 8192 tokens x 6144 channels."""
+    from ..ops.conv import short_conv_cuda
+    B, T, C, K = 8, 8192, 6144, 4
+    x = torch.randn(B, T, C, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    w = torch.randn(C, K, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    t_f = device_time(lambda: short_conv_cuda(x.detach(), w.detach()), iters=iters, flush=flush)
+    dy = torch.randn(B, T, C, device="cuda").to(torch.bfloat16)
+
+    def both():
+        x.grad = None
+        w.grad = None
+        short_conv_cuda(x, w).backward(dy)
+    t_b = device_time(both, iters=iters, flush=flush)
+    L.check_status()
+    nbytes = B * T * C * 2
+    _row(out, kernel="short_conv", B=B, T=T, C=C, K=K, fwd_ms=t_f.median_ms, fwd_gbs=2 * nbytes / t_f.median_ms / 1e6,
+         fwd_frac_of_measured=2 * nbytes / t_f.median_ms / 1e6 / peaks["hbm_gbs"], fwd_bwd_ms=t_b.median_ms)
 
 
 def main(argv=None):
@@ -371,6 +411,10 @@ def main(argv=None):
         bench_sampling(out, peaks, flush, iters=args.iters)
     if "moe" in only:
         bench_moe(out, peaks, flush, iters=args.iters)
+    if "mx" in only:
+        bench_mx(out, peaks, flush, iters=args.iters)
+    if "conv" in only:
+        bench_conv(out, peaks, flush, iters=args.iters)
     if "decode" in only:
         bench_decode(out, peaks, flush, iters=args.iters)
 
