@@ -24,9 +24,11 @@ class SwiGLU(nn.Module):
         self.down_proj = Linear(hidden, features, axes=("mlp", "embed"), init_std=init_std, dtype=dtype, device=device)
 
     def forward(self, x):
-        gu = self.gate_up_proj(x)
         if self.activation == "silu":
-            return self.down_proj(ops.packed_swiglu(gu))
+            if self.gate_up_proj.bias is None and type(self.gate_up_proj).__name__ == "Linear":
+                return self.down_proj(ops.linear_swiglu(x, self.gate_up_proj.weight))
+            return self.down_proj(ops.packed_swiglu(self.gate_up_proj(x)))
+        gu = self.gate_up_proj(x)
         g, u = gu.chunk(2, -1)                                    # GeGLU (Gemma): the gate passes through GELU
         return self.down_proj(F.gelu(g, approximate="tanh" if self.activation == "gelu_tanh" else "none") * u)
 

@@ -55,8 +55,38 @@ _GEMM.kernels = [
         Requirement("align", lambda c: c["aligned"], "base pointers must be 16-byte aligned"),
         Requirement("inner", lambda c: c["inner_contig"], "the contiguous dimension must have stride 1"),
     ], receipt="tcgen05 cta_group::2 256x256x64 persistent kernel on CTA pairs, csrc/kernels/gemm_pair_sm100.cu"),
+    Kernel("sm100_skinny", [
+        Requirement("built", lambda c: _skinny_built(), "the weight-streaming kernel is not in this build of libdewb.so"),
+        Requirement("rows", lambda c: c["M"] <= 128, "at most 128 rows (one tile of batch rows)"),
+        Requirement("plain", lambda c: c.get("plain", False), "K-major operands, bf16 output, no accumulation, alpha = 1"),
+        Requirement("dtype", lambda c: c["dtype"] == torch.bfloat16, "operands must be bf16"),
+        Requirement("ld", lambda c: c["lda"] % 8 == 0 and c["ldb"] % 8 == 0 and c["K"] % 8 == 0,
+                    "row strides and K must be multiples of 8 elements (16-byte TMA rule)"),
+        Requirement("align", lambda c: c["aligned"], "base pointers must be 16-byte aligned"),
+        Requirement("inner", lambda c: c["inner_contig"], "the contiguous dimension must have stride 1"),
+    ], receipt="tcgen05 weight-streaming kernel, K split over a thread-block cluster and summed through distributed shared "
+               "memory, csrc/kernels/gemm_skinny_sm100.cu"),
     Kernel("cublas", [], receipt="library arm (torch.matmul)"),
 ]
+
+
+def _skinny_built() -> bool:
+    try:
+        return hasattr(L.load(), "dewb_gemm_skinny_bf16")
+    except Exception:
+        return False
+
+
+def skinny_split(N: int, K: int, tile_cols: int = 128) -> int:
+    """CTAs per output tile of the weight-streaming kernel: enough to cover the SMs, a power of two up to 8, and at least two
+    reduction steps of 64 for every CTA."""
+    tiles = -(-N // tile_cols)
+    want = max(1, 148 // max(1, tiles))
+    steps = -(-K // 64)
+    split = 1
+    while split * 2 <= min(8, want) and steps // (split * 2) >= 2:
+        split *= 2
+    return split
 
 
 def _pair_built() -> bool:
@@ -77,6 +107,9 @@ LARGE_GEMM = os.environ.get("DEWB_LARGE_GEMM", "sm100_pair")
 # Measured cell: with fewer than ~24 output tiles of 128x256 (decode-sized products, e.g. 128 x 768) the persistent
 # kernel leaves most SMs idle; the library's split-K kernels take those calls.
 _GEMM.declared[("skinny",)] = "cublas"
+# Decode-sized products (at most 128 rows) stream the weight once: the cluster split-K kernel (DEWB_DECODE_GEMM=cublas: library arm).
+_GEMM.declared[("decode",)] = os.environ.get("DEWB_DECODE_GEMM", "sm100_skinny")
+_SKINNY_PDL = int(os.environ.get("DEWB_SKINNY_PDL", "1"))
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
@@ -99,9 +132,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         accumulate = False
     case = dict(dtype=a.dtype if a.dtype == b.dtype else None, lda=a.stride(0), ldb=b.stride(0), ldd=out.stride(0),
                 aligned=(a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0),
-                inner_contig=(a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1), M=M, N=N, K=K)
+                inner_contig=(a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1), M=M, N=N, K=K,
+                plain=(not a_mn and not b_mn and out.dtype == torch.bfloat16 and not accumulate and alpha == 1.0))
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
-    cell = ("skinny",) if tiles < 24 else None
+    cell = ("decode",) if (M <= 128 and case["plain"]) else (("skinny",) if tiles < 24 else None)
     if kernel is None and cell is None and tiles >= 148 and _pair_built():
         # measured: the pair kernel is 5-15 % faster on the layer shapes; the single-CTA kernel keeps the very wide head.
         # With DEWB_TUNE=1 the two are timed once per shape and the pick is cached on disk (ops/tuning.py).
@@ -116,6 +150,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     which = _GEMM.select(case, forced=kernel, cell=cell)
     if which == "cublas":
         return _gemm_reference_cuda(a, b, a_mn, b_mn, alpha, out, accumulate)
+    if which == "sm100_skinny":
+        rc = L.load().dewb_gemm_skinny_bf16(L.ptr(a), L.ptr(b), L.ptr(out), c_int(M), c_int(N), c_int(K), c_ll(a.stride(0)), c_ll(b.stride(0)),
+                                            c_ll(out.stride(0)), c_int(skinny_split(N, K)), c_int(0), c_int(_SKINNY_PDL),
+                                            L.ptr(L.status(a.device)), L.stream_ptr())
+        L.check(rc, which)
+        L.count_launches()
+        return out
     epi = {(torch.bfloat16, False): 0, (torch.float32, False): 1, (torch.float32, True): 2,
            (torch.bfloat16, True): 3}[(out.dtype, bool(accumulate))]
     lib = L.load()
@@ -369,6 +410,26 @@ def packed_swiglu(gu: torch.Tensor) -> torch.Tensor:
         return _PackedSwiGLU.apply(gu.contiguous())
     g, u = gu[..., :Fh], gu[..., Fh:]
     return (F.silu(g.float()) * u.float()).to(gu.dtype)
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(x Wg^T) * (x Wu^T)`` for the packed ``[2 F, d]`` weight.  Decode-sized inputs (at most 128 rows, no autograd) run as ONE
+    kernel: the weight-streaming GEMM applies the activation in its epilogue, so the ``[rows, 2 F]`` intermediate never exists."""
+    Fh = w_gate_up.shape[0] // 2
+    x2 = x.reshape(-1, x.shape[-1])
+    M, K = x2.shape
+    if (L.use_cuda(x2, w_gate_up) and M <= 128 and x2.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and Fh % 64 == 0
+            and K % 8 == 0 and x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and w_gate_up.is_contiguous() and x2.data_ptr() % 16 == 0
+            and not (torch.is_grad_enabled() and (x.requires_grad or w_gate_up.requires_grad)) and _skinny_built()
+            and _GEMM.declared.get(("decode",)) == "sm100_skinny"):
+        out = torch.empty((M, Fh), dtype=torch.bfloat16, device=x.device)
+        rc = L.load().dewb_gemm_skinny_bf16(L.ptr(x2), L.ptr(w_gate_up), L.ptr(out), c_int(M), c_int(Fh), c_int(K), c_ll(x2.stride(0)),
+                                            c_ll(w_gate_up.stride(0)), c_ll(Fh), c_int(skinny_split(Fh, K, 64)), c_int(1), c_int(_SKINNY_PDL),
+                                            L.ptr(L.status(x.device)), L.stream_ptr())
+        L.check(rc, "sm100_skinny")
+        L.count_launches()
+        return out.reshape(*x.shape[:-1], Fh)
+    return packed_swiglu(linear(x, w_gate_up))
 
 
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:

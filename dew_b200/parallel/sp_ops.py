@@ -26,6 +26,20 @@ import torch.nn.functional as F
 from .. import ops
 from ..ops import scan
 
+_LINK = None
+
+
+def use_peer_link(link) -> None:
+    """Route this module's exchanges through a ``parallel.peer_link.PeerLink`` (one kernel per exchange over NVLink peer memory,
+    arrival tags inside the data) instead of ``torch.distributed`` point-to-point calls; ``None`` switches back.  The link's group
+    must be the group the functions are called with."""
+    global _LINK
+    _LINK = link
+
+
+def _linked(x: torch.Tensor, group) -> bool:
+    return _LINK is not None and _LINK.group is group and x.is_cuda
+
 
 class _ShiftFromPrevious(torch.autograd.Function):
     """out on rank r = x of rank r - 1 (zeros on rank 0); backward shifts the gradient the other way."""
@@ -43,8 +57,11 @@ class _ShiftFromPrevious(torch.autograd.Function):
 def _shift(x: torch.Tensor, group, direction: int) -> torch.Tensor:
     """direction +1: receive from rank - 1, send to rank + 1; -1: the reverse.  Edge ranks receive zeros."""
     rank, N = dist.get_rank(group), dist.get_world_size(group)
-    out = torch.zeros_like(x)
     src, dst = rank - direction, rank + direction
+    if _linked(x, group):
+        got = _LINK.exchange(x, dst if 0 <= dst < N else None, src if 0 <= src < N else None)
+        return got if got is not None else torch.zeros_like(x)
+    out = torch.zeros_like(x)
     ops_ = []
     if 0 <= dst < N:
         ops_.append(dist.P2POp(dist.isend, x, dist.get_global_rank(group, dst) if group is not None else dst, group))
@@ -103,6 +120,8 @@ class _HandOver(torch.autograd.Function):
         ctx.group = group
         rank = dist.get_rank(group)
         src = rank - 1
+        if _linked(like, group):
+            return _LINK.exchange(None, None, src, like=like.detach())
         buf = torch.zeros_like(like)
         dist.recv(buf, dist.get_global_rank(group, src) if group is not None else src, group=group)
         return buf
@@ -111,6 +130,9 @@ class _HandOver(torch.autograd.Function):
     def backward(ctx, g):
         rank = dist.get_rank(ctx.group)
         dst = rank - 1
+        if _linked(g, ctx.group):
+            _LINK.exchange(g.contiguous(), dst, None)
+            return torch.zeros_like(g), None
         dist.send(g.contiguous(), dist.get_global_rank(ctx.group, dst) if ctx.group is not None else dst, group=ctx.group)
         return torch.zeros_like(g), None
 
@@ -138,9 +160,12 @@ class _HandOverSend(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, group):
-        ctx.group, ctx.shape = group, x.shape
+        ctx.group, ctx.shape, ctx.dtype = group, x.shape, x.dtype
         rank = dist.get_rank(group)
         dst = rank + 1
+        if _linked(x, group):
+            _LINK.exchange(x.contiguous(), dst, None)
+            return x.new_zeros(())
         dist.send(x.contiguous(), dist.get_global_rank(group, dst) if group is not None else dst, group=group)
         return x.new_zeros(())
 
@@ -148,6 +173,8 @@ class _HandOverSend(torch.autograd.Function):
     def backward(ctx, g):
         rank = dist.get_rank(ctx.group)
         src = rank + 1
+        if _linked(g, ctx.group):
+            return _LINK.exchange(None, None, src, like=torch.empty(ctx.shape, dtype=ctx.dtype, device=g.device)), None
         buf = torch.zeros(ctx.shape, dtype=g.dtype, device=g.device)
         dist.recv(buf, dist.get_global_rank(ctx.group, src) if ctx.group is not None else src, group=ctx.group)
         return buf, None
@@ -161,8 +188,11 @@ def vocab_parallel_cross_entropy(hidden: torch.Tensor, weight_shard: torch.Tenso
     Vs = weight_shard.shape[0]
     logits = hidden.float() @ weight_shard.float().t()                          # [T, V / N]
     local_max = logits.max(-1).values.detach()
-    gmax = local_max.clone()
-    dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
+    if _linked(local_max, group):
+        gmax = _LINK.all_reduce(local_max, "max")
+    else:
+        gmax = local_max.clone()
+        dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
     sumexp = _AllReduceSum.apply(torch.exp(logits - gmax[:, None]).sum(-1), group)
     lo = rank * Vs
     mine = (targets >= lo) & (targets < lo + Vs)
@@ -178,6 +208,8 @@ class _AllReduceSum(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, group):
+        if _linked(x, group) and x.dtype == torch.float32:
+            return _LINK.all_reduce(x, "sum")
         y = x.clone()
         dist.all_reduce(y, group=group)
         return y

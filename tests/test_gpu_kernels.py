@@ -1194,3 +1194,48 @@ def test_fused_decode_step_from_the_packed_projection():
     assert torch.equal(a.v[0], b.v[0]), "value cache differs"
     assert torch.equal(a.k[0], b.k[0]), "key cache differs"
     assert torch.equal(fused[live], plain[live]), float((fused[live].float() - plain[live].float()).abs().max())
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 768, 4096), (128, 4096, 512), (128, 4096, 1792), (1, 768, 4096), (7, 200, 520), (100, 16032, 4096),
+                                   (128, 128, 64), (33, 3584, 4096)])
+@pytest.mark.parametrize("pdl", [1, 0])
+def test_weight_streaming_gemm_for_decode(M, N, K, pdl, monkeypatch):
+    """The decode-sized product (at most 128 rows): tcgen05 tiles with K split over a thread-block cluster and summed through
+    distributed shared memory, against the fp32 product; launched with and without programmatic dependent launch; twice, the
+    same bits."""
+    from dew_b200.ops import functional as Fn
+    monkeypatch.setattr(Fn, "_SKINNY_PDL", pdl)
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    before = dict(Fn._GEMM.routes.get("sm100_skinny", {"calls": 0}))["calls"]
+    y = ops.gemm(x, w)
+    assert Fn._GEMM.routes["sm100_skinny"]["calls"] == before + 1          # the kernel under test took the call
+    assert rel_err(y, ref) <= 6e-3, rel_err(y, ref)
+    assert torch.equal(ops.gemm(x, w), y)
+    # a strided activation view (rows of a wider tensor), as the decode step passes
+    wide = torch.randn(M, K + 64, device=DEV).to(torch.bfloat16)
+    assert rel_err(ops.gemm(wide[:, :K], w), wide[:, :K].float() @ w.float().t()) <= 6e-3
+    L.check_status()
+
+
+@pytest.mark.parametrize("M,F,K", [(128, 1792, 4096), (128, 14336, 4096), (5, 64, 128), (77, 448, 1000)])
+def test_gate_up_projection_with_swiglu_in_the_epilogue(M, F, K):
+    """silu(x Wg^T) * (x Wu^T) as one kernel (the activation in the weight-streaming GEMM's epilogue) against the two-step fp32
+    computation, and through the MLP module without autograd."""
+    torch.manual_seed(F)
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, device=DEV) * 0.03).to(torch.bfloat16)
+    with torch.no_grad():
+        y = ops.linear_swiglu(x, w)
+    gu = x.float() @ w.float().t()
+    ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    assert y.shape == (M, F) and rel_err(y, ref) <= 8e-3, rel_err(y, ref)
+    with torch.no_grad():
+        assert torch.equal(ops.linear_swiglu(x, w), y)
+    # with autograd the two-step path runs and agrees
+    xg = x.clone().requires_grad_()
+    y2 = ops.linear_swiglu(xg, w)
+    assert rel_err(y2, ref) <= 8e-3
+    L.check_status()

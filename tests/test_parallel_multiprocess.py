@@ -4,6 +4,8 @@ import os
 import subprocess
 import sys
 
+import pytest
+
 from dew_b200.parallel.pp import stage_slices
 from dew_b200.parallel.sp import all_to_all_moves_less, stripe, unstripe
 
@@ -59,4 +61,30 @@ def test_sequence_parallel_conv_band_scan_and_parallel_reductions():
         assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-3000:]
         r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
         assert all(v < 1e-4 for v in r.values()), r
+        assert {"conv_out", "band_out", "scan_out", "scan_state", "vce_loss", "norm"} <= set(r)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_sequence_parallel_exchanges_over_peer_memory():
+    """The same worker on GPUs with a ``PeerLink``: halos, state hand-overs (forward and backward) and the row-statistic
+    reductions each run as one kernel over NVLink peer memory, against the unsplit computation."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    worker = os.path.join(os.path.dirname(__file__), "workers", "sp_ops_worker.py")
+    for world, port in ((2, 29691), (4, 29692)):
+        if torch.cuda.device_count() < world:
+            continue
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+               "--master-port", str(port), worker, "nccl"]
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="1"))
+        assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-3000:]
+        r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+        assert -r.pop("launches") > 0, "no library kernel ran"
+        assert all(v < 2e-3 for v in r.values()), r
         assert {"conv_out", "band_out", "scan_out", "scan_state", "vce_loss", "norm"} <= set(r)
