@@ -64,9 +64,18 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 }
 
 template <int EPI>
-__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], void* Dptr, int row, int col, int N, long long ldd,
-                                            float alpha) {
+__device__ __forceinline__ void store_chunk(const uint32_t (&r_in)[32], void* Dptr, int row, int col, int N, long long ldd,
+                                            float alpha_in, const __nv_bfloat16* __restrict__ bias) {
   const bool full = (col + 32 <= N);
+  // scale, then the bias (one bf16 value per output column); the stores below see the finished values
+  uint32_t r[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    float v = alpha_in * __uint_as_float(r_in[i]);
+    if (bias != nullptr && col + i < N) v += __bfloat162float(bias[col + i]);
+    r[i] = __float_as_uint(v);
+  }
+  constexpr float alpha = 1.f;
   if (EPI == EPI_BF16 || EPI == EPI_BF16_ACC) {
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Dptr) + static_cast<long long>(row) * ldd + col;
     if (full && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
@@ -124,6 +133,7 @@ template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  void* __restrict__ Dptr, int M, int N, int K, long long ldd, float alpha, int group_m,
+                 const __nv_bfloat16* __restrict__ bias,
                  int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle atoms the descriptors assume. The dynamic shared memory
@@ -266,7 +276,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
         const int col = n0 + c * 32;
-        if (row < M && col < N) store_chunk<EPI>(r, Dptr, row, col, N, ldd, alpha);
+        if (row < M && col < N) store_chunk<EPI>(r, Dptr, row, col, N, ldd, alpha, bias);
       }
       tc_fence_before();
       __syncwarp();
@@ -290,7 +300,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
 template <bool A_MN, bool B_MN, int EPI>
 static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, void* D, int M, int N, int K, long long ldd,
-                      float alpha, int* err, int max_pairs, cudaStream_t stream) {
+                      float alpha, int* err, int max_pairs, cudaStream_t stream, const __nv_bfloat16* bias = nullptr) {
   auto kern = gemm_pair_kernel<A_MN, B_MN, EPI>;
   static int resident[64] = {};          // co-resident clusters of this instantiation per device (0 = not asked yet)
   int dev = 0;
@@ -332,24 +342,27 @@ static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, void* D, int
   if (group_m <= 0) {
     group_m = K <= 8192 ? 16 : 8;
   }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, D, M, N, K, ldd, alpha, group_m, err);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, D, M, N, K, ldd, alpha, group_m, bias, err);
   return static_cast<int>(e);
 }
 
 template <bool A_MN, bool B_MN>
 static int launch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, void* D, int M, int N, int K,
-                      long long ldd, float alpha, int* err, int max_pairs, cudaStream_t stream) {
+                      long long ldd, float alpha, int* err, int max_pairs, cudaStream_t stream, const __nv_bfloat16* bias = nullptr) {
   switch (epi) {
-    case EPI_BF16: return launch_one<A_MN, B_MN, EPI_BF16>(ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream);
-    case EPI_F32: return launch_one<A_MN, B_MN, EPI_F32>(ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream);
-    case EPI_F32_ACC: return launch_one<A_MN, B_MN, EPI_F32_ACC>(ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream);
-    case EPI_BF16_ACC: return launch_one<A_MN, B_MN, EPI_BF16_ACC>(ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream);
+    case EPI_BF16: return launch_one<A_MN, B_MN, EPI_BF16>(ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream, bias);
+    case EPI_F32: return launch_one<A_MN, B_MN, EPI_F32>(ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream, bias);
+    case EPI_F32_ACC: return launch_one<A_MN, B_MN, EPI_F32_ACC>(ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream, bias);
+    case EPI_BF16_ACC: return launch_one<A_MN, B_MN, EPI_BF16_ACC>(ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream, bias);
   }
   return -2;
 }
 
 }  // namespace gemm_pair
 }  // namespace dewb
+
+// host-side: the bias row of the call in flight on this thread (set by the `_bias` entry point around the common launcher)
+static thread_local const __nv_bfloat16* g_pair_bias = nullptr;
 
 // Same contract as dewb_gemm_bf16 (D[M,N] = alpha * op(A) * op(B)^T, operand layouts a_mn / b_mn, epilogues 0..3),
 // computed by CTA pairs. `max_ctas` > 0 caps the grid (pairs = max_ctas / 2). Returns -6 if the device cannot place
@@ -371,8 +384,19 @@ extern "C" int dewb_gemm_pair_bf16(const void* A, const void* B, void* D, int M,
   else       r = make_tmap_2d(&tb, B, K, N, ldb, BK, 64, 2, true);
   if (r) return 2000 + r;
   const int max_pairs = max_ctas > 0 ? (max_ctas / 2 > 0 ? max_ctas / 2 : 1) : 0;
-  if (!a_mn && !b_mn) return launch_epi<false, false>(epi, ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream);
-  if (!a_mn && b_mn) return launch_epi<false, true>(epi, ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream);
-  if (a_mn && !b_mn) return launch_epi<true, false>(epi, ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream);
-  return launch_epi<true, true>(epi, ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream);
+  const __nv_bfloat16* bias = g_pair_bias;
+  if (!a_mn && !b_mn) return launch_epi<false, false>(epi, ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream, bias);
+  if (!a_mn && b_mn) return launch_epi<false, true>(epi, ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream, bias);
+  if (a_mn && !b_mn) return launch_epi<true, false>(epi, ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream, bias);
+  return launch_epi<true, true>(epi, ta, tb, D, M, N, K, ldd, alpha, err, max_pairs, stream, bias);
+}
+
+// The same product with a bias row (bf16 [N]) added in the epilogue: D = alpha * op(A) op(B)^T + bias.
+extern "C" int dewb_gemm_pair_bf16_bias(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
+                                        long long ldb, long long ldd, int a_mn, int b_mn, int epi, float alpha, int* err,
+                                        int max_ctas, void* stream_ptr) {
+  g_pair_bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  const int rc = dewb_gemm_pair_bf16(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, epi, alpha, err, max_ctas, stream_ptr);
+  g_pair_bias = nullptr;
+  return rc;
 }

@@ -58,6 +58,7 @@ struct GroupArgs {
   long long d_group_stride;
   const float* row_scale;   // fp8: per-row scale of A (length M), or null
   const float* col_scale;   // fp8: per-row scale of the stacked B operand (indexed by B's row), or null
+  const __nv_bfloat16* bias; // one value per output column added after the scale (dense mode), or null
 };
 
 struct Tile {
@@ -262,6 +263,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             r[i] = __float_as_uint(__uint_as_float(r[i]) * rs * cs);
           }
         }
+        float al = alpha;
+        if (ga.bias != nullptr && row < M && col < N) {
+          // scale, then the bias: the stores below see the finished values
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col + i < N) r[i] = __float_as_uint(alpha * __uint_as_float(r[i]) + __bfloat162float(ga.bias[col + i]));
+          al = 1.f;
+        }
         if (row < M && col < N) {
           const bool full = (col + 32 <= N);
           if (EPI == EPI_BF16 || EPI == EPI_BF16_ACC) {
@@ -272,7 +281,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               for (int j = 0; j < 4; ++j) {
                 float v[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = alpha * __uint_as_float(r[j * 8 + i]);
+                for (int i = 0; i < 8; ++i) v[i] = al * __uint_as_float(r[j * 8 + i]);
                 if (EPI == EPI_BF16_ACC) {
                   const uint4 old = o4[j];
                   v[0] += bf16_lo(old.x); v[1] += bf16_hi(old.x); v[2] += bf16_lo(old.y); v[3] += bf16_hi(old.y);
@@ -287,7 +296,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
                 if (col + i < N) {
-                  float v = alpha * __uint_as_float(r[i]);
+                  float v = al * __uint_as_float(r[i]);
                   if (EPI == EPI_BF16_ACC) v += __bfloat162float(out[i]);
                   out[i] = __float2bfloat16(v);
                 }
@@ -299,8 +308,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               float4* o4 = reinterpret_cast<float4*>(out);
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                float4 v = make_float4(alpha * __uint_as_float(r[j * 4 + 0]), alpha * __uint_as_float(r[j * 4 + 1]),
-                                       alpha * __uint_as_float(r[j * 4 + 2]), alpha * __uint_as_float(r[j * 4 + 3]));
+                float4 v = make_float4(al * __uint_as_float(r[j * 4 + 0]), al * __uint_as_float(r[j * 4 + 1]),
+                                       al * __uint_as_float(r[j * 4 + 2]), al * __uint_as_float(r[j * 4 + 3]));
                 if (EPI == EPI_F32_ACC) { const float4 o = o4[j]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
                 o4[j] = v;
               }
@@ -308,7 +317,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
                 if (col + i < N) {
-                  float v = alpha * __uint_as_float(r[i]);
+                  float v = al * __uint_as_float(r[i]);
                   if (EPI == EPI_F32_ACC) v += out[i];
                   out[i] = v;
                 }
@@ -398,6 +407,9 @@ static int sm_count() {
   return g_sm_count[dev];
 }
 
+// host-side: the bias row of the call in flight on this thread (set by the `_bias` entry point around the common launcher)
+static thread_local const __nv_bfloat16* g_dense_bias = nullptr;
+
 // D[M,N] (ldd) = alpha * op(A) * op(B)^T.
 //   a_mn = 0: A is [M, K] row-major with row stride lda;  a_mn = 1: A is stored as [K, M] row-major (lda = row stride)
 //   b_mn = 0: B is [N, K] row-major with row stride ldb;  b_mn = 1: B is stored as [K, N] row-major
@@ -423,8 +435,18 @@ extern "C" int dewb_gemm_bf16(const void* A, const void* B, void* D, int M, int 
   if (r) return 2000 + r;
   int sms = sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-  GroupArgs ga{nullptr, nullptr, 0, 0, 1, 0, nullptr, nullptr};
+  GroupArgs ga{nullptr, nullptr, 0, 0, 1, 0, nullptr, nullptr, g_dense_bias};
   return dispatch(a_mn, b_mn, epi, ta, tb, D, M, N, K, ldd, alpha, ga, err, sms, stream);
+}
+
+// The same product with a bias row (bf16 [N]) added in the epilogue: D = alpha * op(A) op(B)^T + bias.
+extern "C" int dewb_gemm_bf16_bias(const void* A, const void* B, void* D, const void* bias, int M, int N, int K, long long lda,
+                                   long long ldb, long long ldd, int a_mn, int b_mn, int epi, float alpha, int* err, int max_ctas,
+                                   void* stream_ptr) {
+  g_dense_bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  const int rc = dewb_gemm_bf16(A, B, D, M, N, K, lda, ldb, ldd, a_mn, b_mn, epi, alpha, err, max_ctas, stream_ptr);
+  g_dense_bias = nullptr;
+  return rc;
 }
 
 // Grouped rows (mixture-of-experts forward and input gradient):
@@ -447,7 +469,7 @@ extern "C" int dewb_gmm_bf16(const void* A, const void* B, void* D, const int* t
   if (!b_mn) r = make_tmap_2d(&tb, B, static_cast<uint64_t>(groups) * N, K, ldb, BN, BK, 2, true);
   else       r = make_tmap_2d(&tb, B, static_cast<uint64_t>(groups) * K, N, ldb, BK, 64, 2, true);
   if (r) return 2000 + r;
-  GroupArgs ga{tile_group, nullptr, 1, b_mn ? K : N, groups, 0, nullptr, nullptr};
+  GroupArgs ga{tile_group, nullptr, 1, b_mn ? K : N, groups, 0, nullptr, nullptr, nullptr};
   return dispatch(0, b_mn, epi, ta, tb, D, M, N, K, ldd, alpha, ga, err, sm_count(), stream);
 }
 
@@ -468,7 +490,7 @@ extern "C" int dewb_tgmm_bf16(const void* A, const void* B, void* D, const int* 
   if (r) return 1000 + r;
   r = make_tmap_2d(&tb, B, R, N, ldb, BK, 64, 2, true);
   if (r) return 2000 + r;
-  GroupArgs ga{nullptr, group_offsets, 2, 0, groups, d_group_stride, nullptr, nullptr};
+  GroupArgs ga{nullptr, group_offsets, 2, 0, groups, d_group_stride, nullptr, nullptr, nullptr};
   return dispatch(1, 1, epi, ta, tb, D, M, N, R, ldd, alpha, ga, err, sm_count(), stream);
 }
 
@@ -488,6 +510,6 @@ extern "C" int dewb_gemm_fp8(const void* A, const void* B, void* D, const float*
   if (r) return 1000 + r;
   r = make_tmap_2d(&tb, B, static_cast<uint64_t>(groups) * N, K, ldb, BN, 2 * BK, 1, true);
   if (r) return 2000 + r;
-  GroupArgs ga{tile_group, nullptr, tile_group != nullptr ? 1 : 0, N, groups, 0, a_scale, b_scale};
+  GroupArgs ga{tile_group, nullptr, tile_group != nullptr ? 1 : 0, N, groups, 0, a_scale, b_scale, nullptr};
   return launch_fp8(ta, tb, D, M, N, K, ldd, 1.f, ga, err, sm_count(), stream);
 }

@@ -114,8 +114,9 @@ _SKINNY_PDL = int(os.environ.get("DEWB_SKINNY_PDL", "1"))
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
-         alpha: float = 1.0, max_ctas: int = 0, kernel: Optional[str] = None) -> torch.Tensor:
-    """``D[M,N] = alpha * op(a) @ op(b)^T`` with fp32 accumulation.
+         alpha: float = 1.0, max_ctas: int = 0, kernel: Optional[str] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``D[M,N] = alpha * op(a) @ op(b)^T (+ bias)`` with fp32 accumulation.  ``bias`` (one value per output column) is added in
+    the epilogue of this library's dense kernels; the other routes add it afterwards.
 
     ``a`` is ``[M,K]`` (or stored ``[K,M]`` when ``a_mn``); ``b`` is ``[N,K]`` (or stored ``[K,N]`` when ``b_mn``).
     ``out`` (bf16 or fp32) may be given, and ``accumulate`` adds into it.
@@ -126,7 +127,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if K != Kb:
         raise ValueError(f"gemm: reduction sizes differ ({K} vs {Kb})")
     if not L.use_cuda(a, b):
-        return _gemm_reference(a, b, a_mn, b_mn, out_dtype, alpha, out, accumulate)
+        r = _gemm_reference(a, b, a_mn, b_mn, out_dtype, alpha, out, accumulate)
+        return r if bias is None else r.add_(bias.to(r.dtype))
+    if bias is not None and (accumulate or out is not None and out.dtype != torch.bfloat16 or out_dtype != torch.bfloat16):
+        raise ValueError("gemm: a bias joins a fresh bf16 output only")
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
         accumulate = False
@@ -135,7 +139,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                 inner_contig=(a.stride(1) == 1 and b.stride(1) == 1 and out.stride(1) == 1), M=M, N=N, K=K,
                 plain=(not a_mn and not b_mn and out.dtype == torch.bfloat16 and not accumulate and alpha == 1.0))
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
-    cell = ("decode",) if (M <= 128 and case["plain"]) else (("skinny",) if tiles < 24 else None)
+    cell = ("decode",) if (M <= 128 and case["plain"] and bias is None) else (("skinny",) if tiles < 24 else None)
+    if bias is not None:
+        case["plain"] = False                                    # (the weight-streaming kernel has no bias epilogue)
     if kernel is None and cell is None and tiles >= 148 and _pair_built():
         # measured: the pair kernel is 5-15 % faster on the layer shapes; the single-CTA kernel keeps the very wide head.
         # With DEWB_TUNE=1 the two are timed once per shape and the pick is cached on disk (ops/tuning.py).
@@ -149,7 +155,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
             kernel = first
     which = _GEMM.select(case, forced=kernel, cell=cell)
     if which == "cublas":
-        return _gemm_reference_cuda(a, b, a_mn, b_mn, alpha, out, accumulate)
+        r = _gemm_reference_cuda(a, b, a_mn, b_mn, alpha, out, accumulate)
+        return r if bias is None else r.add_(bias.to(r.dtype))
     if which == "sm100_skinny":
         rc = L.load().dewb_gemm_skinny_bf16(L.ptr(a), L.ptr(b), L.ptr(out), c_int(M), c_int(N), c_int(K), c_ll(a.stride(0)), c_ll(b.stride(0)),
                                             c_ll(out.stride(0)), c_int(skinny_split(N, K)), c_int(0), c_int(_SKINNY_PDL),
@@ -160,6 +167,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     epi = {(torch.bfloat16, False): 0, (torch.float32, False): 1, (torch.float32, True): 2,
            (torch.bfloat16, True): 3}[(out.dtype, bool(accumulate))]
     lib = L.load()
+    if bias is not None:
+        bb = bias.to(torch.bfloat16).contiguous()                 # referenced until the launch is enqueued
+        fn = lib.dewb_gemm_pair_bf16_bias if which == "sm100_pair" else lib.dewb_gemm_bf16_bias
+        rc = fn(L.ptr(a), L.ptr(b), L.ptr(out), L.ptr(bb), c_int(M), c_int(N), c_int(K), c_ll(a.stride(0)),
+                c_ll(b.stride(0)), c_ll(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)), c_int(epi),
+                c_float(alpha), L.ptr(L.status(a.device)), c_int(max_ctas), L.stream_ptr())
+        L.check(rc, which)
+        L.count_launches()
+        return out
     fn = lib.dewb_gemm_pair_bf16 if which == "sm100_pair" else lib.dewb_gemm_bf16
     rc = fn(L.ptr(a), L.ptr(b), L.ptr(out), c_int(M), c_int(N), c_int(K), c_ll(a.stride(0)),
             c_ll(b.stride(0)), c_ll(out.stride(0)), c_int(int(a_mn)), c_int(int(b_mn)), c_int(epi),
@@ -199,9 +215,7 @@ class _Linear(torch.autograd.Function):
         ctx.save_for_backward(x, weight)
         ctx.has_bias = bias is not None
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, weight)
-        if bias is not None:
-            y = y + bias
+        y = gemm(x2, weight, bias=bias)                          # the bias joins in the product's epilogue
         return y.reshape(*x.shape[:-1], weight.shape[0])
 
     @staticmethod

@@ -1239,3 +1239,25 @@ def test_gate_up_projection_with_swiglu_in_the_epilogue(M, F, K):
     y2 = ops.linear_swiglu(xg, w)
     assert rel_err(y2, ref) <= 8e-3
     L.check_status()
+
+
+@pytest.mark.parametrize("kernel", ["sm100_tcgen05", "sm100_pair"])
+@pytest.mark.parametrize("M,N,K", [(4096, 4096, 1024), (1000, 1160, 264)])
+def test_gemm_bias_in_the_epilogue(kernel, M, N, K):
+    """D = A B^T + bias with the bias row added by the product's epilogue (both dense kernels), and through the Linear autograd
+    node (forward value, bias gradient)."""
+    torch.manual_seed(M)
+    a = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    b = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(N, device=DEV).to(torch.bfloat16)
+    ref = a.float() @ b.float().t() + bias.float()
+    y = ops.gemm(a, b, bias=bias, kernel=kernel)
+    assert rel_err(y, ref) <= 6e-3, rel_err(y, ref)
+    assert rel_err(ops.gemm(a, b, bias=bias, kernel=kernel, alpha=0.5), 0.5 * (a.float() @ b.float().t()) + bias.float()) <= 6e-3
+    xa = a.clone().requires_grad_()
+    bp = bias.clone().requires_grad_()
+    out = ops.linear(xa, b, bp)
+    assert rel_err(out, ref) <= 6e-3
+    out.float().sum().backward()
+    assert rel_err(bp.grad, torch.full_like(bias, float(M))) <= 1e-2
+    L.check_status()
