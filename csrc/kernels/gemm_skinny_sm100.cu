@@ -52,6 +52,76 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
 }
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
+
+__device__ __forceinline__ void store4(__nv_bfloat16* o, int col, int N, const float (&a)[4]) {
+  if (col + 4 <= N && (reinterpret_cast<uintptr_t>(o) & 7) == 0) {
+    uint2 pk;
+    pk.x = pack_bf16(a[0], a[1]); pk.y = pack_bf16(a[2], a[3]);
+    *reinterpret_cast<uint2*>(o) = pk;
+  } else {
+    for (int i = 0; i < 4; ++i)
+      if (col + i < N) o[i] = __float2bfloat16(a[i]);
+  }
+}
+
+// Part 2 of the epilogue: this CTA's column slice of the tile, summed over the SPLIT parked partials of the cluster.  Eight
+// 16-byte loads over distributed shared memory are in flight per thread before any is used (one round trip per batch, not per load).
+template <int SPLIT>
+__device__ __forceinline__ void reduce_slices(uint32_t park_addr, __nv_bfloat16* __restrict__ out, int row, int M, int N, long long ldo,
+                                              int tile, int crank, int mode) {
+  constexpr int GROUPS = 8 / SPLIT;                              // 4-column groups summed per batch
+  uint32_t peer[SPLIT];
+#pragma unroll
+  for (int s = 0; s < SPLIT; ++s) peer[s] = map_to_cta(park_addr, s);
+  if (mode == 0) {
+    constexpr int W = BN / SPLIT;                                // columns of this CTA's slice
+    const int c0 = crank * W;
+#pragma unroll 1
+    for (int cc = 0; cc < W; cc += 4 * GROUPS) {
+      float4 v[GROUPS][SPLIT];
+#pragma unroll
+      for (int g = 0; g < GROUPS; ++g)
+#pragma unroll
+        for (int s = 0; s < SPLIT; ++s) v[g][s] = ld_cluster_f4(peer[s] + (row * PARK_LD + c0 + cc + 4 * g) * 4);
+#pragma unroll
+      for (int g = 0; g < GROUPS; ++g) {
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < SPLIT; ++s) { a[0] += v[g][s].x; a[1] += v[g][s].y; a[2] += v[g][s].z; a[3] += v[g][s].w; }
+        const int col = tile * 128 + c0 + cc + 4 * g;
+        if (row < M) store4(out + static_cast<long long>(row) * ldo + col, col, N, a);
+      }
+    }
+  } else {
+    constexpr int W = 64 / SPLIT;                                // output columns of this CTA's slice
+    constexpr int G2 = GROUPS > 1 ? GROUPS / 2 : 1;              // gate and up double the loads per group
+    const int c0 = crank * W;
+#pragma unroll 1
+    for (int cc = 0; cc < W; cc += 4 * G2) {
+      float4 gv[G2][SPLIT], uv[G2][SPLIT];
+#pragma unroll
+      for (int g = 0; g < G2; ++g)
+#pragma unroll
+        for (int s = 0; s < SPLIT; ++s) {
+          gv[g][s] = ld_cluster_f4(peer[s] + (row * PARK_LD + c0 + cc + 4 * g) * 4);
+          uv[g][s] = ld_cluster_f4(peer[s] + (row * PARK_LD + 64 + c0 + cc + 4 * g) * 4);
+        }
+#pragma unroll
+      for (int g = 0; g < G2; ++g) {
+        float ga[4] = {0.f, 0.f, 0.f, 0.f}, ua[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < SPLIT; ++s) {
+          ga[0] += gv[g][s].x; ga[1] += gv[g][s].y; ga[2] += gv[g][s].z; ga[3] += gv[g][s].w;
+          ua[0] += uv[g][s].x; ua[1] += uv[g][s].y; ua[2] += uv[g][s].z; ua[3] += uv[g][s].w;
+        }
+        const float a[4] = {silu(ga[0]) * ua[0], silu(ga[1]) * ua[1], silu(ga[2]) * ua[2], silu(ga[3]) * ua[3]};
+        const int col = tile * 64 + c0 + cc + 4 * g;
+        if (row < M) store4(out + static_cast<long long>(row) * ldo + col, col, N, a);
+      }
+    }
+  }
+}
+
 // mode 0: out[M, N] = X W^T.  mode 1 (SwiGLU): W = [gate (F rows); up (F rows)], N = F, out[M, F] = silu(X gate^T) * (X up^T).
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
@@ -229,54 +299,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_const
     cluster_wait();
     if (!dead && warp >= 2) {
       const uint32_t park_addr = smem_u32(park);
-      if (mode == 0) {
-        const int w = BN / split;                                  // columns of this CTA's slice (16 .. 64)
-        const int c0 = crank * w;
-        for (int cc = 0; cc < w; cc += 4) {
-          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int s = 0; s < split; ++s) {
-            const float4 v = ld_cluster_f4(map_to_cta(park_addr + (row * PARK_LD + c0 + cc) * 4, s));
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-          }
-          const int col = tile * 128 + c0 + cc;
-          if (row < M) {
-            __nv_bfloat16* o = out + static_cast<long long>(row) * ldo + col;
-            if (col + 4 <= N && (reinterpret_cast<uintptr_t>(o) & 7) == 0) {
-              uint2 pk;
-              pk.x = pack_bf16(acc.x, acc.y); pk.y = pack_bf16(acc.z, acc.w);
-              *reinterpret_cast<uint2*>(o) = pk;
-            } else {
-              const float a[4] = {acc.x, acc.y, acc.z, acc.w};
-              for (int i = 0; i < 4; ++i)
-                if (col + i < N) o[i] = __float2bfloat16(a[i]);
-            }
-          }
-        }
-      } else {
-        const int w = 64 / split;                                  // output columns of this CTA's slice (8 .. 32)
-        const int c0 = crank * w;
-        for (int cc = 0; cc < w; cc += 4) {
-          float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
-          for (int s = 0; s < split; ++s) {
-            const float4 a = ld_cluster_f4(map_to_cta(park_addr + (row * PARK_LD + c0 + cc) * 4, s));
-            const float4 b = ld_cluster_f4(map_to_cta(park_addr + (row * PARK_LD + 64 + c0 + cc) * 4, s));
-            g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
-            u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
-          }
-          const int col = tile * 64 + c0 + cc;
-          if (row < M) {
-            __nv_bfloat16* o = out + static_cast<long long>(row) * ldo + col;
-            const float a[4] = {silu(g.x) * u.x, silu(g.y) * u.y, silu(g.z) * u.z, silu(g.w) * u.w};
-            if (col + 4 <= N && (reinterpret_cast<uintptr_t>(o) & 7) == 0) {
-              uint2 pk;
-              pk.x = pack_bf16(a[0], a[1]); pk.y = pack_bf16(a[2], a[3]);
-              *reinterpret_cast<uint2*>(o) = pk;
-            } else {
-              for (int i = 0; i < 4; ++i)
-                if (col + i < N) o[i] = __float2bfloat16(a[i]);
-            }
-          }
-        }
+      switch (split) {
+        case 2: reduce_slices<2>(park_addr, out, row, M, N, ldo, tile, crank, mode); break;
+        case 4: reduce_slices<4>(park_addr, out, row, M, N, ldo, tile, crank, mode); break;
+        default: reduce_slices<8>(park_addr, out, row, M, N, ldo, tile, crank, mode); break;
       }
     }
     // nobody leaves while a peer may still read its shared memory

@@ -107,8 +107,10 @@ LARGE_GEMM = os.environ.get("DEWB_LARGE_GEMM", "sm100_pair")
 # Measured cell: with fewer than ~24 output tiles of 128x256 (decode-sized products, e.g. 128 x 768) the persistent
 # kernel leaves most SMs idle; the library's split-K kernels take those calls.
 _GEMM.declared[("skinny",)] = "cublas"
-# Decode-sized products (at most 128 rows) stream the weight once: the cluster split-K kernel (DEWB_DECODE_GEMM=cublas: library arm).
-_GEMM.declared[("decode",)] = os.environ.get("DEWB_DECODE_GEMM", "sm100_skinny")
+# Decode-sized products (at most 128 rows) stream the weight once.  Measured inside the TP = 8 decode step: cuBLAS's small-tile kernels
+# 6.6-7.6 us a call, this library's cluster split-K kernel 14.4 us - so the cell names the library arm; DEWB_DECODE_GEMM=sm100_skinny
+# selects the weight-streaming kernel (and with it the SwiGLU epilogue of `linear_swiglu`).
+_GEMM.declared[("decode",)] = os.environ.get("DEWB_DECODE_GEMM", "cublas")
 _SKINNY_PDL = int(os.environ.get("DEWB_SKINNY_PDL", "1"))
 
 
@@ -426,16 +428,17 @@ def packed_swiglu(gu: torch.Tensor) -> torch.Tensor:
     return (F.silu(g.float()) * u.float()).to(gu.dtype)
 
 
-def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, fused: Optional[bool] = None) -> torch.Tensor:
     """``silu(x Wg^T) * (x Wu^T)`` for the packed ``[2 F, d]`` weight.  Decode-sized inputs (at most 128 rows, no autograd) run as ONE
-    kernel: the weight-streaming GEMM applies the activation in its epilogue, so the ``[rows, 2 F]`` intermediate never exists."""
+    kernel when the weight-streaming GEMM is the decode cell's choice (or ``fused=True``): it applies the activation in its epilogue, so
+    the ``[rows, 2 F]`` intermediate never exists."""
     Fh = w_gate_up.shape[0] // 2
     x2 = x.reshape(-1, x.shape[-1])
     M, K = x2.shape
     if (L.use_cuda(x2, w_gate_up) and M <= 128 and x2.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and Fh % 64 == 0
             and K % 8 == 0 and x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and w_gate_up.is_contiguous() and x2.data_ptr() % 16 == 0
             and not (torch.is_grad_enabled() and (x.requires_grad or w_gate_up.requires_grad)) and _skinny_built()
-            and _GEMM.declared.get(("decode",)) == "sm100_skinny"):
+            and (fused if fused is not None else _GEMM.declared.get(("decode",)) == "sm100_skinny")):
         out = torch.empty((M, Fh), dtype=torch.bfloat16, device=x.device)
         rc = L.load().dewb_gemm_skinny_bf16(L.ptr(x2), L.ptr(w_gate_up), L.ptr(out), c_int(M), c_int(Fh), c_int(K), c_ll(x2.stride(0)),
                                             c_ll(w_gate_up.stride(0)), c_ll(Fh), c_int(skinny_split(Fh, K, 64)), c_int(1), c_int(_SKINNY_PDL),

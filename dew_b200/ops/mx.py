@@ -103,6 +103,42 @@ def usable(K: int, N: int) -> bool:
     return K % 128 == 0 and N % 128 == 0
 
 
+# Quantised copies of the expert weights, kept from one microbatch to the next.  A training engine that owns the weights switches
+# the cache on and calls ``weights_changed()`` after every update (its kernels write the weights without touching their version
+# counters); without an engine saying so nothing is cached.
+_WEIGHT_CACHE: dict = {}
+_WEIGHT_EPOCH = [0]
+_CACHE_ON = [False]
+
+
+def cache_weights(on: bool = True) -> None:
+    _CACHE_ON[0] = bool(on)
+    _WEIGHT_CACHE.clear()
+
+
+def weights_changed() -> None:
+    """Every weight may have changed (an optimizer step, a restore): quantised copies made before now are stale."""
+    _WEIGHT_EPOCH[0] += 1
+    _WEIGHT_CACHE.clear()
+
+
+def _quantized_weight(w: torch.Tensor, transposed: bool, ident: int = 0):
+    G_, N, K = w.shape
+    key = (ident or id(w), w.data_ptr(), tuple(w.shape), transposed)
+    stamp = (_WEIGHT_EPOCH[0], w._version)
+    if _CACHE_ON[0]:
+        hit = _WEIGHT_CACHE.get(key)
+        if hit is not None and hit[0] == stamp:
+            return hit[1], hit[2]
+    if transposed:
+        q, sc = quantize_mx(w.transpose(1, 2).contiguous().reshape(G_ * K, N), sf_rows=_pad128(G_ * K + TILE_N))
+    else:
+        q, sc = quantize_mx(w.reshape(G_ * N, K), sf_rows=_pad128(G_ * N + TILE_N))
+    if _CACHE_ON[0]:
+        _WEIGHT_CACHE[key] = (stamp, q, sc)
+    return q, sc
+
+
 class _MxGroupedLinear(torch.autograd.Function):
     """Expert projection ``x [rows, K]`` (expert-sorted, 128-aligned groups) by ``w [G, N, K]`` in MXFP8."""
 
@@ -110,9 +146,10 @@ class _MxGroupedLinear(torch.autograd.Function):
     def forward(ctx, x, w, layout):
         ctx.layout = layout
         ctx.save_for_backward(x, w)
+        ctx.ident = id(w)                  # (the backward sees an unpacked copy of the tensor object: the cache key stays the parameter's)
         G_, N, K = w.shape
         xq, xs = quantize_mx(x)
-        wq, ws = quantize_mx(w.reshape(G_ * N, K), sf_rows=_pad128(G_ * N + TILE_N))
+        wq, ws = _quantized_weight(w, False, ctx.ident)
         return gemm_mx(xq, xs, wq, ws, layout.tile_group, G_)
 
     @staticmethod
@@ -127,8 +164,7 @@ class _MxGroupedLinear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             # dX = dY W reduces over the output features: dY is quantised along N and so are the weights (transposed copy)
             dq, ds = quantize_mx(dy)
-            wt = w.transpose(1, 2).contiguous().reshape(G_ * K, N)
-            wq, ws = quantize_mx(wt, sf_rows=_pad128(G_ * K + TILE_N))
+            wq, ws = _quantized_weight(w, True, ctx.ident)
             dx = gemm_mx(dq, ds, wq, ws, layout.tile_group, G_)
         if ctx.needs_input_grad[1]:
             main = getattr(w, "main_grad", None)

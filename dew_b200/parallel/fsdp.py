@@ -607,6 +607,9 @@ class FSDPEngine:
 
     # ------------------------------------------------------------------ the step
     def step(self, state: TrainState, batch: Mapping[str, torch.Tensor]):
+        from ..ops import mx as _mx
+        _mx.cache_weights(True) if not _mx._CACHE_ON[0] else None
+        _mx.weights_changed()          # whatever changed the weights since the last step (a restore, a reload), quantised copies start afresh
         from ..training.trainer import _split_rows, tree_detach
         t = self.t
         obj = t.objective
@@ -687,6 +690,7 @@ class FSDPEngine:
                                             "tokens": state.consumed.get("tokens", 0) + int(obj.row_tokens(batch) or 0) * self.batch_ranks})
         pooled = pool(stats_all)
         metrics = {"loss": pooled, **{k: pool(v) for k, v in metrics_all.items()}, **info}
+        _mx.weights_changed()          # the update just written makes this step's quantised copies stale for whoever runs next
         return new_state, metrics
 
     def _second_phase(self, info: Dict[str, Any]) -> None:

@@ -374,6 +374,9 @@ class ShardedFSDPEngine(FSDPEngine):
         L.count_launches()
 
     def step(self, state: TrainState, batch):
+        from ..ops import mx as _mx
+        _mx.cache_weights(True) if not _mx._CACHE_ON[0] else None
+        _mx.weights_changed()          # whatever changed the weights since the last step (a restore, a reload), quantised copies start afresh
         from ..objectives.base import Aux, Step, pool
         from ..training.trainer import _split_rows, tree_detach
         t = self.t
@@ -472,6 +475,7 @@ class ShardedFSDPEngine(FSDPEngine):
                                   consumed={"examples": state.consumed.get("examples", 0) + rows_total,
                                             "tokens": state.consumed.get("tokens", 0) + int(obj.row_tokens(batch) or 0) * self.batch_ranks})
         metrics = {"loss": pool(stats_all), **{k: pool(v) for k, v in metrics_all.items()}, **info}
+        _mx.weights_changed()          # the update just written makes this step's quantised copies stale for whoever runs next
         return new_state, metrics
 
     def _await_previous_microbatch(self) -> None:

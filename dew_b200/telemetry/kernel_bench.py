@@ -306,12 +306,12 @@ def bench_moe(out, peaks, flush, iters=10):
          combine_gbs=(moved + T * d * 2) / t_c.median_ms / 1e6)
 
 
-def bench_decode(out, peaks, flush, iters=10, rows=128, max_len=2304):
+def bench_decode(out, peaks, flush, iters=10, rows=128, max_len=2304, heads=((32, 8), (4, 1))):
     """Paged decode attention at the serving configuration: 128 rows, page 64, context lengths uniform in [128, max_len], with
     the heads of one GPU (32 query / 8 KV) and of one of eight tensor-parallel ranks (4 / 1); the bytes are the keys and values
     each row reads once.  ``DEWB_DECODE_PERSIST=0`` times the one-CTA-per-chunk form instead of the balanced one."""
     from ..nn.kv_cache import KVCache, KVStore
-    for Hq, Hkv in ((32, 8), (4, 1)):
+    for Hq, Hkv in heads:
         store = KVStore(KVCache(page_size=64), 1, rows, max_len, Hkv, 128, torch.bfloat16, "cuda")
         store.k.normal_()
         store.v.normal_()
@@ -366,6 +366,34 @@ def bench_conv(out, peaks, flush, iters=10):
          fwd_frac_of_measured=2 * nbytes / t_f.median_ms / 1e6 / peaks["hbm_gbs"], fwd_bwd_ms=t_b.median_ms)
 
 
+def bench_decode_gemm(out, peaks, flush, iters=10):
+    """The four projections of a decode step (128 rows) of the dense 8 B decoder, per tensor-parallel degree 8 / 2 / 1: the
+    weight-streaming kernel (with the SwiGLU epilogue for gate | up) against the library arm (cuBLAS through torch.matmul, plus
+    this library's SwiGLU kernel where the epilogue would have done it); CUDA-graph replays, L2 flushed; the bytes are the weight."""
+    from ..ops import functional as Fn
+    d, F, Hq, Hkv, D = 4096, 14336, 32, 8, 128
+    for tp in (8, 2, 1):
+        shapes = [("qkv", (Hq + 2 * Hkv) * D // tp, d, False), ("o", d, Hq * D // tp, False), ("gate_up+swiglu", F // tp, d, True),
+                  ("down", d, F // tp, False)]
+        for name, N, K, glu in shapes:
+            x = torch.randn(128, K, device="cuda").to(torch.bfloat16)
+            w = (torch.randn((2 * N if glu else N), K, device="cuda") * 0.02).to(torch.bfloat16)
+            with torch.no_grad():
+                if glu:
+                    mine = lambda: ops.linear_swiglu(x, w, fused=True)
+                    lib = lambda: ops.packed_swiglu(torch.matmul(x, w.t()))
+                else:
+                    mine = lambda: ops.gemm(x, w, kernel="sm100_skinny")
+                    lib = lambda: torch.matmul(x, w.t())
+                t_m = device_time(mine, iters=iters, flush=flush, graph=True)
+                t_l = device_time(lib, iters=iters, flush=flush, graph=True)
+            L.check_status()
+            nbytes = w.numel() * 2
+            _row(out, kernel="decode_gemm", tp=tp, product=name, N=N, K=K, weight_mb=nbytes / 1e6, split=Fn.skinny_split(N, K, 64 if glu else 128),
+                 skinny_us=t_m.median_ms * 1e3, library_us=t_l.median_ms * 1e3, skinny_gbs=nbytes / t_m.median_ms / 1e6,
+                 skinny_frac_of_measured=nbytes / t_m.median_ms / 1e6 / peaks["hbm_gbs"], library_over_skinny=t_l.median_ms / t_m.median_ms)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=None)
@@ -373,6 +401,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--gemm-shape", default=None, help="M,N,K[,a_mn,b_mn]: time one GEMM shape only (small profiling case)")
     ap.add_argument("--tokens", type=int, default=8192, help="gemm: tokens per microbatch of the layer shapes (8192 on one GPU, 16384 from two)")
+    ap.add_argument("--decode-heads", default=None, help="Hq,Hkv: time the paged decode kernel with these head counts only (small profiling case)")
     ap.add_argument("--gdn-shape", default=None, help="B,T,H: time the gated-delta-rule kernels on one shape only (small profiling case)")
     ap.add_argument("--attn-shape", default=None, help="B,S,Hq,Hkv,D: time this library's attention kernels on one shape only")
     ap.add_argument("--flash-variant", type=int, default=None, help="forward variant: 0 = P through shared memory, 1 = P in tensor memory")
@@ -411,12 +440,15 @@ def main(argv=None):
         bench_sampling(out, peaks, flush, iters=args.iters)
     if "moe" in only:
         bench_moe(out, peaks, flush, iters=args.iters)
+    if "decode_gemm" in only:
+        bench_decode_gemm(out, peaks, flush, iters=args.iters)
     if "mx" in only:
         bench_mx(out, peaks, flush, iters=args.iters)
     if "conv" in only:
         bench_conv(out, peaks, flush, iters=args.iters)
     if "decode" in only:
-        bench_decode(out, peaks, flush, iters=args.iters)
+        heads = ((32, 8), (4, 1)) if not args.decode_heads else (tuple(int(v) for v in args.decode_heads.split(",")),)
+        bench_decode(out, peaks, flush, iters=args.iters, heads=heads)
 
 
 if __name__ == "__main__":

@@ -1210,13 +1210,13 @@ def test_weight_streaming_gemm_for_decode(M, N, K, pdl, monkeypatch):
     w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
     ref = x.float() @ w.float().t()
     before = dict(Fn._GEMM.routes.get("sm100_skinny", {"calls": 0}))["calls"]
-    y = ops.gemm(x, w)
+    y = ops.gemm(x, w, kernel="sm100_skinny")
     assert Fn._GEMM.routes["sm100_skinny"]["calls"] == before + 1          # the kernel under test took the call
     assert rel_err(y, ref) <= 6e-3, rel_err(y, ref)
-    assert torch.equal(ops.gemm(x, w), y)
+    assert torch.equal(ops.gemm(x, w, kernel="sm100_skinny"), y)
     # a strided activation view (rows of a wider tensor), as the decode step passes
     wide = torch.randn(M, K + 64, device=DEV).to(torch.bfloat16)
-    assert rel_err(ops.gemm(wide[:, :K], w), wide[:, :K].float() @ w.float().t()) <= 6e-3
+    assert rel_err(ops.gemm(wide[:, :K], w, kernel="sm100_skinny"), wide[:, :K].float() @ w.float().t()) <= 6e-3
     L.check_status()
 
 
@@ -1228,12 +1228,12 @@ def test_gate_up_projection_with_swiglu_in_the_epilogue(M, F, K):
     x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
     w = (torch.randn(2 * F, K, device=DEV) * 0.03).to(torch.bfloat16)
     with torch.no_grad():
-        y = ops.linear_swiglu(x, w)
+        y = ops.linear_swiglu(x, w, fused=True)
     gu = x.float() @ w.float().t()
     ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
     assert y.shape == (M, F) and rel_err(y, ref) <= 8e-3, rel_err(y, ref)
     with torch.no_grad():
-        assert torch.equal(ops.linear_swiglu(x, w), y)
+        assert torch.equal(ops.linear_swiglu(x, w, fused=True), y)
     # with autograd the two-step path runs and agrees
     xg = x.clone().requires_grad_()
     y2 = ops.linear_swiglu(xg, w)
