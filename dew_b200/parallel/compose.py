@@ -32,6 +32,11 @@ def build_engine(trainer):
     """The engine for ``trainer.mesh`` (a ``MeshSpec``, a built ``Mesh`` or None)."""
     from ..training.trainer import LocalEngine
     spec = trainer.mesh
+    if getattr(trainer, "offload", None) == "optimizer":
+        if spec is not None and dist.is_initialized() and dist.get_world_size() > 1:
+            raise ValueError("optimizer-state offload is a one-device engine; shard over GPUs with the fsdp axis instead")
+        from ..training.offload import HostOffloadEngine
+        return HostOffloadEngine(trainer)
     if spec is None:
         return LocalEngine(trainer)
     mesh: Mesh = spec.build() if isinstance(spec, MeshSpec) else spec

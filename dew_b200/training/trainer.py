@@ -266,7 +266,7 @@ class Trainer:
                  mesh=None, layout=None, microbatches: Optional[int] = None, accumulation: int = 1, split=None,
                  dynamic_scale: bool = False, checkpoints=None, tracker=None, step=None, profile: Optional[ProfileWindow] = None,
                  param_dtype: Optional[torch.dtype] = None, diloco=None, data_resume: str = "relaxed",
-                 skip_nonfinite: bool = False, record: bool = False, tune_kernels: bool = False):
+                 skip_nonfinite: bool = False, record: bool = False, tune_kernels: bool = False, offload: Optional[str] = None):
         self.objective = objective
         if optimizer is None:
             optimizer = OptimConfig()
@@ -286,6 +286,9 @@ class Trainer:
             from ..ops import tuning
             tuning.enable(True)
         self.tune_kernels = tune_kernels
+        if offload not in (None, "optimizer"):
+            raise ValueError(f"offload must be None or 'optimizer', not {offload!r}")
+        self.offload = offload          # 'optimizer': fp32 masters and Adam moments in pinned host memory, streamed through device slots
         self._diloco_runner = None
         self.checkpoints, self.tracker = checkpoints, tracker
         self.custom_step = step
