@@ -283,6 +283,9 @@ def main(argv=None) -> None:
         fully_shard(layer, mp_policy=mp, ignored_params=experts or None)
     fully_shard(model, mp_policy=mp, ignored_params=experts or None)
     model.to_empty(device=dev)
+    if experts:
+        # materialising replaced the parameter objects: name the expert weights again
+        experts = [p for n, p in model.named_parameters() if "w_gate_up" in n or "w_down" in n]
     with torch.no_grad():
         for n, p in model.named_parameters():
             if p.dim() >= 2:
@@ -295,7 +298,13 @@ def main(argv=None) -> None:
         for layer in model.layers:
             layer.compile()
     n_params = sum(p.numel() for p in model.parameters())
-    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+    # the expert weights are plain tensors (each rank owns its experts), everything else is sharded by FSDP2 (DTensors): the fused
+    # optimizer kernel takes one kind per call, so each kind gets its own optimizer
+    expert_ids = {id(p) for p in experts} if experts else set()
+    rest = [p for p in model.parameters() if id(p) not in expert_ids]
+    opts = [torch.optim.AdamW(rest, lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)]
+    if experts:
+        opts.append(torch.optim.AdamW(list(experts), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True))
     cos, sin = rope_tables(seq, cfg["hd"], cfg["theta"], dev)
     gen = torch.Generator().manual_seed(1234 + rank)
     n_batches = args.warmup + 2 * args.steps + 2
@@ -314,8 +323,9 @@ def main(argv=None) -> None:
             # expert gradients are rank-local sums over every rank's tokens: scale like the data-parallel mean
             for p in experts:
                 p.grad.div_(world)
-        opt.step()
-        opt.zero_grad(set_to_none=True)
+        for o in opts:
+            o.step()
+            o.zero_grad(set_to_none=True)
         return total
 
     def sync():

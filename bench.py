@@ -155,6 +155,11 @@ def main() -> None:
     ap.add_argument("--config", default="dense", choices=sorted(CONFIGS), help="training configuration (default: the headline)")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the result is then not a valid headline)")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--ep-capacity", type=float, default=None,
+                    help="moe: rows an expert owner's receive buffer holds, as a multiple of one rank's (token, choice) pairs (default 2; "
+                         "pairs past the end are dropped and reported)")
+    ap.add_argument("--trace-nonfinite", action="store_true",
+                    help="debugging aid: name the first module whose forward output is not finite (every rank prints its own), then stop")
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="moe: token exchange by this library's peer-memory kernels (default) or by NCCL all-to-all (comparison arm)")
     ap.add_argument("--profile", default=None, help="write a torch.profiler kernel table for one step to this file")
@@ -199,6 +204,8 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=dev)
     L.load()
 
+    if args.ep_capacity is not None:
+        os.environ["DEWB_EP_CAPACITY"] = str(args.ep_capacity)
     conf = CONFIGS[args.config]
     SEQ_LEN = conf["seq"]
     cfg = dict(conf["model"])
@@ -241,6 +248,20 @@ def main() -> None:
     first_rows = torch.randint(0, cfg["vocab_size"], (rows, SEQ_LEN + 1), generator=torch.Generator().manual_seed(1234))
     device_batches[0] = {"tokens": first_rows.to(dev)}
     loss_first = None
+    if args.trace_nonfinite:
+        def watch(name):
+            def hook(mod, inputs, output):
+                outs = output if isinstance(output, (tuple, list)) else (output,)
+                for j, o in enumerate(outs):
+                    if isinstance(o, torch.Tensor) and o.is_floating_point() and not bool(torch.isfinite(o).all()):
+                        ins = [(tuple(i.shape), bool(torch.isfinite(i).all())) for i in inputs if isinstance(i, torch.Tensor) and i.is_floating_point()]
+                        pars = {n: bool(torch.isfinite(p).all()) for n, p in mod.named_parameters(recurse=False)}
+                        print(f"[rank {rank}] first non-finite output: module {name!r} output {j} shape {tuple(o.shape)}; "
+                              f"inputs (shape, finite): {ins}; own parameters finite: {pars}", flush=True)
+                        os._exit(3)
+            return hook
+        for name, mod in model.named_modules():
+            mod.register_forward_hook(watch(name))
 
     def sync():
         torch.cuda.synchronize(dev)
@@ -337,6 +358,25 @@ def main() -> None:
                "ms_per_step": ms2 / args.steps}
         L.check_status()
 
+    moe_report = None
+    if args.config == "moe":
+        # the last microbatch's exchange of every sparse layer: how full the busiest owner's receive buffer was, and what was dropped
+        worst = dropped = overflowed = 0
+        cap = 1
+        for layer in model.layers:
+            ex = getattr(getattr(layer.mlp, "ep", None), "exchange", None)
+            info = getattr(ex, "last_info", None)
+            if info is None:
+                continue
+            vals = info.tolist()
+            overflowed += vals[1]
+            worst = max(worst, vals[2])
+            dropped += vals[3]
+            cap = ex.rows_cap
+        pairs = micro * SEQ_LEN * conf["mixture"]["top_k"] * world * sum(1 for _ in model.layers)
+        moe_report = {"ep_capacity_factor": float(os.environ.get("DEWB_EP_CAPACITY", "2.0")), "receive_rows": cap,
+                      "busiest_owner_rows": worst, "layers_overflowed": overflowed,
+                      "dropped_pair_fraction_last_microbatch": dropped / max(1, pairs)}
     peak_mem = torch.cuda.max_memory_allocated(dev) / 1e9
     flops = model.model_flops(tokens_per_step // world, SEQ_LEN) * 3
     if rank == 0:
@@ -351,6 +391,7 @@ def main() -> None:
             "vs_derived_mark": value / (DERIVED_MARK_TOK_S_PER_GPU * world) if args.config == "dense" else None,
             "dtype": "bf16" if args.config != "moe" else "bf16 (block-scaled MXFP8 e4m3 expert GEMMs: forward and input gradient)",
             "data": "synthetic (uniform random token ids from a seed; random-init weights)",
+            **({"moe_exchange": moe_report} if moe_report is not None else {}),
             "config": {"model": conf["name"], "params": n_params,
                        "global_batch": rows * world, "seq_len": SEQ_LEN, "micro_batch": micro,
                        "parallelism": f"fsdp{world}" + (f"+ep{world} ({args.ep} exchange)" if args.config == "moe" else ""),

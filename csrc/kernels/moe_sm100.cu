@@ -192,14 +192,26 @@ moe_plan_kernel(Peers counts_ptrs, const uint32_t* __restrict__ my_flags, int sl
   __syncthreads();
   const int rows_mine = owner_rows[rank];
   if (blockIdx.x == 0) {
-    for (int le = tid; le < per; le += blockDim.x) { offsets[le] = owner_off[rank * per + le]; local_counts[le] = total[rank * per + le]; }
+    // A receive buffer that is too small drops the pairs past its end (capacity semantics): the owner's layout is cut at the
+    // buffer's end, the dropped pairs get position -1 (not sent, contribute zero to the combine), and the caller reads how many.
+    for (int le = tid; le < per; le += blockDim.x) {
+      const int o = owner_off[rank * per + le];
+      offsets[le] = min(o, rows_cap);
+      local_counts[le] = max(0, min(total[rank * per + le], rows_cap - o));
+    }
     if (tid == 0) {
-      offsets[per] = rows_mine;
+      offsets[per] = min(rows_mine, rows_cap);
       int worst = 0;
+      long long dropped = 0;
       for (int r = 0; r < world; ++r) worst = max(worst, owner_rows[r]);
-      info[0] = rows_mine;
-      info[1] = worst > rows_cap ? 1 : 0;      // some receive buffer is too small: the pairs past its end are dropped
-      if (worst > rows_cap) atomicCAS(err, 0, ERR_BAD_ARG);
+      for (int e = 0; e < E; ++e) {
+        const int o = owner_off[e];                                  // rows of expert e past its owner's buffer end
+        dropped += max(0, min(total[e], o + total[e] - rows_cap));
+      }
+      info[0] = min(rows_mine, rows_cap);
+      info[1] = worst > rows_cap ? 1 : 0;
+      info[2] = worst;                                               // rows (with group padding) the busiest owner was sent
+      info[3] = static_cast<int>(dropped);                           // pairs dropped over all owners (the same number on every rank)
     }
   }
   const int stride = gridDim.x * blockDim.x;

@@ -18,6 +18,7 @@ count all-gather (:1168), capacity factor (docs/concepts/moe.md:95).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -142,7 +143,7 @@ class TokenExchange:
         offsets = torch.empty(self.per + 1, dtype=torch.int32, device=dev)
         local_counts = torch.empty(self.per, dtype=torch.int32, device=dev)
         tile_group = torch.empty(self.rows_cap // 128, dtype=torch.int32, device=dev)
-        info = torch.empty(2, dtype=torch.int32, device=dev)
+        info = torch.zeros(4, dtype=torch.int32, device=dev)     # {rows received, overflowed, busiest owner's rows, pairs dropped}
         L.check(lib.dewb_moe_plan(self.counts.ptr_array(), L.ptr(self.flags.tensor), ctypes.c_int(self.SLOT_COUNTS), ctypes.c_uint(self.seq),
                                   ctypes.c_ulonglong(self.limit_ns), L.ptr(ids32), L.ptr(rank_in_group), ctypes.c_int(pairs),
                                   ctypes.c_int(self.experts), ctypes.c_int(self.rank), ctypes.c_int(self.world), ctypes.c_int(self.rows_cap),
@@ -233,6 +234,7 @@ class _PullRows(torch.autograd.Function):
 def exchange_experts(exchange: TokenExchange, experts, x2: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     """plan -> dispatch -> grouped expert MLP on the received rows -> combine, all on this library's kernels."""
     plan = exchange.plan(ids, x2.shape[1])
+    exchange.last_info = plan.info            # device tensor {rows received, overflowed, busiest owner's rows, pairs dropped}: read it after the step
     rows = _PushRows.apply(x2, exchange, plan)
     out_rows = experts(rows, plan.layout)
     return _PullRows.apply(out_rows, weights.float(), exchange, plan)
@@ -265,7 +267,11 @@ class _GatherExperts(torch.autograd.Function):
 
 
 class ExpertParallel:
-    def __init__(self, group: Optional[dist.ProcessGroup] = None, fused: bool = True, capacity_factor: float = 2.0):
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, fused: bool = True, capacity_factor: Optional[float] = None):
+        # rows an owner's receive buffer holds, as a multiple of one rank's (token, choice) pairs: `world` can never overflow;
+        # pairs past the end are dropped and counted (DEWB_EP_CAPACITY overrides the default of 2)
+        if capacity_factor is None:
+            capacity_factor = float(os.environ.get("DEWB_EP_CAPACITY", "2.0"))
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0

@@ -48,3 +48,31 @@ def test_offload_refuses_what_it_does_not_do():
         dew.Trainer(LMObjective(model, 16, ema_decay=0.99), dew.OptimConfig(), offload="optimizer").engine()
     with pytest.raises(ValueError, match="offload must be"):
         dew.Trainer(LMObjective(model, 16, ema_decay=None), dew.OptimConfig(), offload="everything")
+
+
+@pytest.mark.gpu
+def test_streamed_update_on_the_gpu_matches_resident_update():
+    """bf16 compute weights on the device, fp32 masters and moments in pinned host memory crossing on a copy stream."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+
+    def make(offload):
+        torch.manual_seed(0)
+        model = CausalTransformer(vocab_size=512, emb_features=256, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64, mlp_features=512,
+                                  max_seq_len=128, qk_norm=False, tie_embeddings=False).cuda()
+        opt = dew.OptimConfig(learning_rate=1e-3, weight_decay=0.1, clip_grads=1.0, optimizer_opts={"b2": 0.95})
+        return dew.Trainer(LMObjective(model, 128, ema_decay=None), opt, key=3, microbatches=2, offload=offload, param_dtype=torch.bfloat16)
+    a, b = make(None), make("optimizer")
+    ea, eb = a.engine(), b.engine()
+    eb.bucket_elems = 100_000
+    sa, sb = ea.fresh_state(a.key), eb.fresh_state(b.key)
+    for i in range(3):
+        batch = {"tokens": torch.randint(0, 512, (4, 129), generator=torch.Generator().manual_seed(i)).cuda()}
+        sa, ma = ea.step(sa, batch)
+        sb, mb = eb.step(sb, batch)
+        assert abs(float(ma["loss"].value()) - float(mb["loss"].value())) < 2e-2
+    from dew_b200.utils.trees import flatten
+    pa, pb = flatten(sa.variables["params"]), flatten(sb.variables["params"])
+    assert all(not v.is_cuda for v in pb.values())          # the masters stayed on the host
+    worst = max(float((pa[k].cpu().float() - pb[k].float()).abs().max()) for k in pa)
+    assert worst < 5e-3, worst
