@@ -309,6 +309,12 @@ def main() -> None:
         sampler.start()
     launches0 = L.LAUNCHES
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.config == "moe":
+        for layer in model.layers:                        # the exchange's overflow / drop counters cover the timed steps only
+            ex = getattr(getattr(layer.mlp, "ep", None), "exchange", None)
+            if getattr(ex, "totals", None) is not None:
+                ex.totals.zero_()
+    timed_steps_counted = args.steps + (0 if args.skip_e2e else args.steps + 1)
     sync()
     start.record()
     for i in range(args.steps):
@@ -365,18 +371,19 @@ def main() -> None:
         cap = 1
         for layer in model.layers:
             ex = getattr(getattr(layer.mlp, "ep", None), "exchange", None)
-            info = getattr(ex, "last_info", None)
-            if info is None:
+            totals = getattr(ex, "totals", None)
+            if totals is None:
                 continue
-            vals = info.tolist()
-            overflowed += vals[1]
+            vals = totals.tolist()
+            overflowed += vals[0]
+            dropped += vals[1]
             worst = max(worst, vals[2])
-            dropped += vals[3]
             cap = ex.rows_cap
-        pairs = micro * SEQ_LEN * conf["mixture"]["top_k"] * world * sum(1 for _ in model.layers)
+        # (the counters were zeroed after the warm-up: they cover the device-timed steps and, when it runs, the end-to-end steps)
+        pairs = rows * SEQ_LEN * conf["mixture"]["top_k"] * world * sum(1 for _ in model.layers) * timed_steps_counted
         moe_report = {"ep_capacity_factor": float(os.environ.get("DEWB_EP_CAPACITY", "2.0")), "receive_rows": cap,
-                      "busiest_owner_rows": worst, "layers_overflowed": overflowed,
-                      "dropped_pair_fraction_last_microbatch": dropped / max(1, pairs)}
+                      "busiest_owner_rows": worst, "exchanges_overflowed": overflowed,
+                      "dropped_pair_fraction": dropped / max(1, pairs)}
     peak_mem = torch.cuda.max_memory_allocated(dev) / 1e9
     flops = model.model_flops(tokens_per_step // world, SEQ_LEN) * 3
     if rank == 0:

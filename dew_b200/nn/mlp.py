@@ -25,7 +25,7 @@ class SwiGLU(nn.Module):
 
     def forward(self, x):
         if self.activation == "silu":
-            if self.gate_up_proj.bias is None and type(self.gate_up_proj).__name__ == "Linear":
+            if type(self.gate_up_proj).__name__ == "Linear" and self.gate_up_proj.bias is None:
                 return self.down_proj(ops.linear_swiglu(x, self.gate_up_proj.weight))
             return self.down_proj(ops.packed_swiglu(self.gate_up_proj(x)))
         gu = self.gate_up_proj(x)

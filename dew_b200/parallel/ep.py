@@ -235,6 +235,11 @@ def exchange_experts(exchange: TokenExchange, experts, x2: torch.Tensor, weights
     """plan -> dispatch -> grouped expert MLP on the received rows -> combine, all on this library's kernels."""
     plan = exchange.plan(ids, x2.shape[1])
     exchange.last_info = plan.info            # device tensor {rows received, overflowed, busiest owner's rows, pairs dropped}: read it after the step
+    if getattr(exchange, "totals", None) is None:
+        exchange.totals = torch.zeros(3, dtype=torch.int64, device=x2.device)      # {calls overflowed, pairs dropped, busiest owner's rows ever}
+    with torch.no_grad():
+        exchange.totals[:2] += plan.info[[1, 3]]
+        exchange.totals[2] = torch.maximum(exchange.totals[2], plan.info[2].long())
     rows = _PushRows.apply(x2, exchange, plan)
     out_rows = experts(rows, plan.layout)
     return _PullRows.apply(out_rows, weights.float(), exchange, plan)
