@@ -1191,8 +1191,9 @@ def test_fused_decode_step_from_the_packed_projection():
     live = positions >= 0
     assert torch.equal(fused_in[5], qkv[5])                        # the idle row's projection was not rotated
     assert torch.equal(fused_in[live][:, :Hq + Hkv], rot[live][:, :Hq + Hkv]), "rotation differs"
-    assert torch.equal(a.v[0], b.v[0]), "value cache differs"
-    assert torch.equal(a.k[0], b.k[0]), "key cache differs"
+    # (the page past the addressable pool only collects the writes of padding positions, in no particular order)
+    assert torch.equal(a.v[0, :a.pages], b.v[0, :b.pages]), "value cache differs"
+    assert torch.equal(a.k[0, :a.pages], b.k[0, :b.pages]), "key cache differs"
     assert torch.equal(fused[live], plain[live]), float((fused[live].float() - plain[live].float()).abs().max())
 
 
