@@ -103,7 +103,9 @@ def test_flux_trains_through_the_diffusion_objective():
     torch.manual_seed(0)
     model = LB.RectifiedFlowTransformer(emb_features=64, num_heads=4, input_channels=3, text_features=16, pooled_features=None, double_layers=1,
                                         single_layers=1)
-    obj = dew.DiffusionObjective(model, dew.presets.Flow(), ema_decay=None)
+    from dew_b200.diffusion import Flow
+    from dew_b200.objectives.diffusion import DiffusionObjective
+    obj = DiffusionObjective(model, Flow(), dew.InputSpec(dew.Field("sample", (8, 8, 3))), ema_decay=None)
     trainer = dew.Trainer(obj, dew.OptimConfig(learning_rate=1e-3), key=0)
     eng = trainer.engine()
     state = eng.fresh_state(trainer.key)
