@@ -34,6 +34,17 @@ _STATIC: Dict[str, Dict[str, str]] = {
     "model": {
         "causal_transformer": "dew_b200.models.causal_transformer:CausalTransformer",
         "simple_dit": "dew_b200.models.dit:SimpleDiT",
+        "unet": "dew_b200.models.diffusion_backbones:UNet", "uvit": "dew_b200.models.diffusion_backbones:UViT",
+        "simple_udit": "dew_b200.models.diffusion_backbones:SimpleUDiT", "simple_mmdit": "dew_b200.models.diffusion_backbones:SimpleMMDiT",
+        "video_dit": "dew_b200.models.diffusion_backbones:VideoDiT", "hybrid_dit": "dew_b200.models.diffusion_backbones:HybridDiT",
+        "unet_3d": "dew_b200.models.diffusion_backbones:UNet3D", "hierarchical_mmdit": "dew_b200.models.diffusion_backbones:HierarchicalMMDiT",
+        "ssm_dit": "dew_b200.models.diffusion_backbones:SSMDiT", "jepa_encoder": "dew_b200.models.diffusion_backbones:JepaEncoder",
+        "jepa_video_encoder": "dew_b200.models.diffusion_backbones:JepaVideoEncoder",
+        "flux": "dew_b200.models.latent_backbones:RectifiedFlowTransformer", "flux2": "dew_b200.models.latent_backbones:Flux2",
+        "qwen_image": "dew_b200.models.latent_backbones:QwenImage", "z_image": "dew_b200.models.latent_backbones:ZImage",
+        "sd3": "dew_b200.models.latent_backbones:SD3Transformer", "wan": "dew_b200.models.latent_backbones:WanTransformer",
+        "edm2": "dew_b200.models.latent_backbones:EDM2UNet",
+        "kl_vae": "dew_b200.models.autoencoders:KLAutoEncoder", "vit": "dew_b200.models.autoencoders:ViT",
     },
     "objective": {
         "lm": "dew_b200.objectives.lm:LMObjective",
