@@ -96,14 +96,16 @@ class ExpertMLP(nn.Module):
     def param_count_per_expert(self) -> int:
         return 3 * self.features * self.hidden
 
-    def forward(self, xs: torch.Tensor, layout: G.GroupLayout) -> torch.Tensor:
+    def forward(self, xs: torch.Tensor, layout: G.GroupLayout, out: Optional[torch.Tensor] = None, lean: bool = False) -> torch.Tensor:
+        """``out`` / ``lean``: honoured by the block-scaled path only (see ``ops.mx.mx_grouped_linear``): the caller checks the
+        returned tensor, not the argument."""
         mode = getattr(self, "fp8", False)
         if mode and xs.dtype == torch.bfloat16:
             from ..ops import mx
             if mode != "row" and mx.usable(self.features, 2 * self.hidden) and mx.usable(self.hidden, self.features):
                 # block-scaled MXFP8 (1 x 32 blocks, ue8m0 scales applied by the tensor core)
-                h = mx.mx_grouped_linear(xs, self.gate_up, layout)
-                return mx.mx_grouped_linear(ops.packed_swiglu(h), self.down, layout)
+                h = mx.mx_grouped_linear(xs, self.gate_up, layout, None, lean)
+                return mx.mx_grouped_linear(ops.packed_swiglu(h), self.down, layout, out, lean)
             from ..ops.fp8 import fp8_grouped_linear            # row / channel scaled e4m3
             h = fp8_grouped_linear(xs, self.gate_up, layout)
             return fp8_grouped_linear(ops.packed_swiglu(h), self.down, layout)

@@ -73,23 +73,34 @@ def quantize_mx(x: torch.Tensor, sf_rows: Optional[int] = None) -> Tuple[torch.T
     return q, packed.view(torch.int32).reshape(K // 128, sf_rows)
 
 
-def gemm_mx(aq, sfa, bq, sfb, tile_group: Optional[torch.Tensor] = None, groups: int = 1) -> torch.Tensor:
+def gemm_mx(aq, sfa, bq, sfb, tile_group: Optional[torch.Tensor] = None, groups: int = 1, out: Optional[torch.Tensor] = None,
+            zero_skipped: bool = True) -> torch.Tensor:
     """``[M, K] x [groups * N, K]^T -> [M, N]`` bf16.  With ``tile_group`` the rows of ``aq`` are expert-sorted and each 128-row
-    tile multiplies its own group's ``N`` rows of ``bq``.  ``sfb`` must have at least ``groups * N + 192`` rows."""
+    tile multiplies its own group's ``N`` rows of ``bq``.  ``sfb`` must have at least ``groups * N + 192`` rows.  ``out``: write
+    into this ``[M, N]`` bf16 tensor.  Row tiles without a group are not written: with ``zero_skipped`` (default) they read zero,
+    without it they keep whatever the memory held - enough when nothing downstream reads them (an expert pipeline whose every
+    consumer walks the same tiles)."""
     M, K = aq.shape
     N = bq.shape[0] // groups
     if not L.use_cuda(aq):
         a = dequantize_mx(aq, unpack_scales(sfa, M, K))
         b = dequantize_mx(bq, unpack_scales(sfb, bq.shape[0], K))
         if tile_group is None:
-            return (a @ b.t()).to(torch.bfloat16)
-        out = torch.zeros(M, N)
-        for t, g in enumerate(tile_group.tolist()):
-            if g >= 0:
-                out[t * 128:(t + 1) * 128] = a[t * 128:(t + 1) * 128] @ b[g * N:(g + 1) * N].t()
-        return out.to(torch.bfloat16)
-    out = torch.zeros((M, N), dtype=torch.bfloat16, device=aq.device) if tile_group is not None else \
-        torch.empty((M, N), dtype=torch.bfloat16, device=aq.device)
+            res = (a @ b.t()).to(torch.bfloat16)
+        else:
+            res = torch.zeros(M, N)
+            for t, g in enumerate(tile_group.tolist()):
+                if g >= 0:
+                    res[t * 128:(t + 1) * 128] = a[t * 128:(t + 1) * 128] @ b[g * N:(g + 1) * N].t()
+            res = res.to(torch.bfloat16)
+        return res if out is None else out.copy_(res)
+    if out is None:
+        out = torch.zeros((M, N), dtype=torch.bfloat16, device=aq.device) if (tile_group is not None and zero_skipped) else \
+            torch.empty((M, N), dtype=torch.bfloat16, device=aq.device)
+    elif tuple(out.shape) != (M, N) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("gemm_mx: `out` must be a contiguous [M, N] bf16 tensor")
+    elif tile_group is not None and zero_skipped:
+        out.zero_()
     rc = L.load().dewb_gemm_mxfp8(L.ptr(aq), L.ptr(bq), L.ptr(out), L.ptr(sfa), L.ptr(sfb), L.ptr(tile_group), c_int(M), c_int(N),
                                   c_int(K), c_int(groups), c_ll(aq.stride(0)), c_ll(bq.stride(0)), c_ll(out.stride(0)),
                                   c_ll(sfa.shape[1]), c_ll(sfb.shape[1]), L.ptr(L.status(aq.device)), L.stream_ptr())
@@ -143,14 +154,17 @@ class _MxGroupedLinear(torch.autograd.Function):
     """Expert projection ``x [rows, K]`` (expert-sorted, 128-aligned groups) by ``w [G, N, K]`` in MXFP8."""
 
     @staticmethod
-    def forward(ctx, x, w, layout):
-        ctx.layout = layout
+    def forward(ctx, x, w, layout, out_holder=None, lean=False):
+        # `out_holder`: a one-element list around the destination tensor (kept out of autograd's sight: the destination is fresh
+        # memory to write, not an input whose history matters)
+        out = out_holder[0] if out_holder else None
+        ctx.layout, ctx.lean = layout, lean
         ctx.save_for_backward(x, w)
         ctx.ident = id(w)                  # (the backward sees an unpacked copy of the tensor object: the cache key stays the parameter's)
         G_, N, K = w.shape
         xq, xs = quantize_mx(x)
         wq, ws = _quantized_weight(w, False, ctx.ident)
-        return gemm_mx(xq, xs, wq, ws, layout.tile_group, G_)
+        return gemm_mx(xq, xs, wq, ws, layout.tile_group, G_, out=out, zero_skipped=not lean)
 
     @staticmethod
     def backward(ctx, dy):
@@ -165,15 +179,17 @@ class _MxGroupedLinear(torch.autograd.Function):
             # dX = dY W reduces over the output features: dY is quantised along N and so are the weights (transposed copy)
             dq, ds = quantize_mx(dy)
             wq, ws = _quantized_weight(w, True, ctx.ident)
-            dx = gemm_mx(dq, ds, wq, ws, layout.tile_group, G_)
+            dx = gemm_mx(dq, ds, wq, ws, layout.tile_group, G_, zero_skipped=not ctx.lean)
         if ctx.needs_input_grad[1]:
             main = getattr(w, "main_grad", None)
             if main is not None and dy.is_cuda:
                 G.tgmm(dy, x, layout, G_, out=main, accumulate=grad_accumulates(w))
             else:
                 dw = G.tgmm(dy, x, layout, G_).to(w.dtype)
-        return dx, dw, None
+        return dx, dw, None, None, None
 
 
-def mx_grouped_linear(x, w, layout):
-    return _MxGroupedLinear.apply(x, w, layout)
+def mx_grouped_linear(x, w, layout, out: Optional[torch.Tensor] = None, lean: bool = False):
+    """``lean``: row tiles that hold no expert's rows are left unwritten instead of zero-filled (forward and input gradient); only for
+    pipelines whose consumers never read those tiles (the expert-parallel exchange).  ``out``: the product is written there."""
+    return _MxGroupedLinear.apply(x, w, layout, [out] if out is not None else None, lean)

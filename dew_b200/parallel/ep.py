@@ -99,7 +99,13 @@ class TokenExchange:
         self.last_pull = 0
         self.rows_cap = 0
         self.features = 0
-        self.recv = self.out = self.counts = self.flags = None
+        self.recv = self.recv_back = self.out = self.counts = self.flags = None
+        # lean buffers (DEWB_EP_LEAN=0 restores the copies): the receive buffer is returned as it is (a second one takes the
+        # backward's rows, so the forward's stay intact for the weight gradient), only the padding rows of each expert group are
+        # zeroed instead of the whole buffer, and the last expert product may write straight into the buffer the peers pull from
+        self.lean = os.environ.get("DEWB_EP_LEAN", "1") == "1"
+        self.write_in_place = os.environ.get("DEWB_EP_IN_PLACE", "1") == "1"      # the last expert product writes into the pulled buffer
+        self._out_claimed = False
 
     def _ensure(self, pairs: int, features: int, device) -> None:
         share = pairs if self.world == 1 else int(pairs * self.capacity_factor)
@@ -109,7 +115,9 @@ class TokenExchange:
         self.rows_cap, self.features = need, features
         make = (lambda n, dt: _LocalBuffer(n, dt, device)) if self.world == 1 else \
             (lambda n, dt: SymmetricBuffer(n, dt, device, self.group, zero=True))
-        self.recv, self.out = make(need * features, torch.bfloat16), make(need * features, torch.bfloat16)
+        # (one row more than the plan addresses: the target of the padding-zeroing writes that have nothing to zero)
+        self.recv, self.out = make((need + 1) * features, torch.bfloat16), make(need * features, torch.bfloat16)
+        self.recv_back = make((need + 1) * features, torch.bfloat16) if self.lean else None
         if self.counts is None:
             self.counts, self.flags = make(max(64, self.experts), torch.int32), make(64, torch.int32)
             self.counter = torch.zeros(4, dtype=torch.int32, device=device)
@@ -151,26 +159,51 @@ class TokenExchange:
                                   L.ptr(L.status(dev)), L.stream_ptr()), "moe_plan")
         L.count_launches(2)
         layout = G.GroupLayout(None, local_counts, offsets, tile_group, self.rows_cap)
-        return ExchangePlan(dest_rank, dest_pos, layout, info, T, k)
+        plan = ExchangePlan(dest_rank, dest_pos, layout, info, T, k)
+        if self.lean:
+            # rows [offset + count, next offset) of every local expert: the (at most 127) alignment rows nobody pushes; a fixed-size
+            # index (entries with nothing to zero point at the spare row) keeps this free of data-dependent shapes
+            j = torch.arange(127, device=dev, dtype=torch.int64)[None, :]
+            first = (offsets[:-1] + local_counts).long()[:, None] + j
+            plan.pad_rows = torch.where(first < offsets[1:].long()[:, None], first, self.rows_cap).reshape(-1)
+        return plan
 
-    def push(self, x: torch.Tensor, plan: ExchangePlan, pair_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def push(self, x: torch.Tensor, plan: ExchangePlan, pair_scale: Optional[torch.Tensor] = None, backward: bool = False) -> torch.Tensor:
         """``x [T, d]`` bf16 -> this rank's received rows ``[rows_cap, d]`` (expert-sorted, padding rows zero)."""
         T, d = x.shape
         assert d == self.features and x.dtype == torch.bfloat16
         L.ensure_device(x)
         self.seq += 1
-        self.recv.tensor.zero_()
+        buf = self.recv_back if (self.lean and backward) else self.recv
+        if not self.lean:
+            buf.tensor.zero_()
         self._signal(self.SLOT_READY)
         ps = None if pair_scale is None else pair_scale.float().contiguous()
         xc = x.contiguous()                    # referenced until the launch is enqueued
-        L.check(L.load().dewb_moe_push(L.ptr(xc), L.ptr(ps), L.ptr(plan.dest_rank), L.ptr(plan.dest_pos), self.recv.ptr_array(),
+        L.check(L.load().dewb_moe_push(L.ptr(xc), L.ptr(ps), L.ptr(plan.dest_rank), L.ptr(plan.dest_pos), buf.ptr_array(),
                                        None, self.flags.ptr_array(), L.ptr(self.flags.tensor), ctypes.c_int(self.SLOT_READY),
                                        ctypes.c_int(self.SLOT_PUSHED), ctypes.c_uint(self.seq), ctypes.c_ulonglong(self.limit_ns),
                                        L.ptr(self.counter), ctypes.c_int(T), ctypes.c_int(d), ctypes.c_int(plan.top_k), ctypes.c_int(self.rank),
                                        ctypes.c_int(self.world), ctypes.c_int(0), L.ptr(L.status(x.device)), L.stream_ptr()), "moe_push")
         L.count_launches()
         self._wait(self.SLOT_PUSHED, self.seq)
-        return self.recv.tensor.view(self.rows_cap, d).clone()
+        if not self.lean:
+            return buf.tensor[: self.rows_cap * d].view(self.rows_cap, d).clone()
+        buf.tensor.view(self.rows_cap + 1, d).index_fill_(0, plan.pad_rows, 0)
+        # a tensor of its own over the buffer's memory, not a view: autograd saves it for the weight gradient, and the buffer's next
+        # use (the following microbatch's push, after this microbatch's backward) must not read as an in-place change of a saved view
+        base = buf.tensor
+        return torch.empty(0, dtype=base.dtype, device=base.device).set_(base.untyped_storage(), base.storage_offset(), (self.rows_cap, d), (d, 1))
+
+    def claim_out(self, d: int) -> torch.Tensor:
+        """The buffer the peers pull from, once nobody reads its previous contents any more: a producer that writes the rows there
+        (and passes this very tensor to ``pull``) saves the copy."""
+        if self.last_pull:
+            self._wait(self.SLOT_PULLED, self.last_pull)
+        self._out_claimed = True
+        # a tensor of its own over the buffer's memory (not a view: what is written there has no autograd history to join)
+        base = self.out.tensor
+        return torch.empty(0, dtype=base.dtype, device=base.device).set_(base.untyped_storage(), base.storage_offset(), (self.rows_cap, d), (d, 1))
 
     def pull(self, rows: torch.Tensor, plan: ExchangePlan, weights: Optional[torch.Tensor] = None, keep_rows: bool = False):
         """``rows [rows_cap, d]`` on every owner -> ``out [T, d]``: each token's k rows, weighted and summed (fp32 accumulate)."""
@@ -178,9 +211,12 @@ class TokenExchange:
         T, k = plan.tokens, plan.top_k
         L.ensure_device(rows)
         self.seq += 1
-        if self.last_pull:
-            self._wait(self.SLOT_PULLED, self.last_pull)          # nobody still reads the previous contents of `out`
-        self.out.tensor.view(self.rows_cap, d).copy_(rows)
+        in_place = self._out_claimed and rows.data_ptr() == self.out.tensor.data_ptr()
+        if not in_place:
+            if self.last_pull and not self._out_claimed:
+                self._wait(self.SLOT_PULLED, self.last_pull)          # nobody still reads the previous contents of `out`
+            self.out.tensor.view(self.rows_cap, d).copy_(rows)
+        self._out_claimed = False
         self._signal(self.SLOT_OUT)
         out = torch.empty(T, d, dtype=torch.bfloat16, device=rows.device)
         gathered = torch.empty(T * k, d, dtype=torch.bfloat16, device=rows.device) if keep_rows else None
@@ -224,7 +260,7 @@ class _PullRows(torch.autograd.Function):
         weights, gathered = ctx.saved_tensors
         plan = ctx.plan
         dy = dy.contiguous()
-        d_rows = ctx.exchange.push(dy, plan, pair_scale=weights.reshape(-1))
+        d_rows = ctx.exchange.push(dy, plan, pair_scale=weights.reshape(-1), backward=True)
         dw = None
         if gathered is not None:
             dw = (gathered.view(plan.tokens, plan.top_k, -1).float() * dy.float().unsqueeze(1)).sum(-1).to(weights.dtype)
@@ -241,7 +277,10 @@ def exchange_experts(exchange: TokenExchange, experts, x2: torch.Tensor, weights
         exchange.totals[:2] += plan.info[[1, 3]]
         exchange.totals[2] = torch.maximum(exchange.totals[2], plan.info[2].long())
     rows = _PushRows.apply(x2, exchange, plan)
-    out_rows = experts(rows, plan.layout)
+    if exchange.lean:
+        out_rows = experts(rows, plan.layout, out=exchange.claim_out(x2.shape[1]) if exchange.write_in_place else None, lean=True)
+    else:
+        out_rows = experts(rows, plan.layout)
     return _PullRows.apply(out_rows, weights.float(), exchange, plan)
 
 

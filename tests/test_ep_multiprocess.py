@@ -65,3 +65,33 @@ def test_expert_parallel_two_gpus_peer_memory_exchange():
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     r = json.loads(next(l for l in out.stdout.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
     assert max(r["errs"]) < 5e-2, r
+
+
+def test_expert_product_written_into_a_given_buffer_keeps_autograd_intact():
+    """The last expert product may write straight into a caller's buffer (the one peers pull from): same values and gradients as the
+    allocating form, call after call, and the buffer itself never joins the autograd graph."""
+    import torch
+    from dew_b200.ops import grouped as G
+    from dew_b200.ops import mx
+    torch.manual_seed(0)
+    E, N, K = 2, 128, 128
+    lay = G.group_layout(torch.randint(0, E, (200,)), E)
+    x = torch.zeros(lay.rows, K).bfloat16()
+    x[lay.positions] = torch.randn(200, K).bfloat16()
+    x.requires_grad_()
+    w = torch.randn(E, N, K).bfloat16().requires_grad_()
+    base = torch.zeros(lay.rows * N, dtype=torch.bfloat16)
+    grads = []
+    for _ in range(2):
+        x.grad = w.grad = None
+        out = torch.empty(0, dtype=torch.bfloat16).set_(base.untyped_storage(), 0, (lay.rows, N), (N, 1))
+        y = mx.mx_grouped_linear(x, w, lay, out, False)
+        assert y.data_ptr() == base.data_ptr() and y.grad_fn is not None
+        (y.float() * 2).sum().backward()
+        grads.append((x.grad.clone(), w.grad.clone()))
+        assert base.grad_fn is None and not base.requires_grad
+    x.grad = w.grad = None
+    y2 = mx.mx_grouped_linear(x, w, lay)
+    (y2.float() * 2).sum().backward()
+    assert torch.equal(y2, y.detach()) and torch.equal(x.grad, grads[1][0]) and torch.equal(w.grad, grads[1][1])
+    assert torch.equal(grads[0][0], grads[1][0])
