@@ -1,16 +1,27 @@
 """Decision models: one forward pass answers typed questions about a state.
 
-A request is a state (token ids) and named questions - a ``Choice`` among named options or a ``Score`` on a numeric scale
-(scored as a choice over its buckets).  The questions are laid out behind the state in one row (``layout_row``), a backbone
-reads the row, a ``DecisionHead`` scores every option of every question at that question's marker position, and the answer
-is a distribution over exactly the options the question names.  ``DecisionObjective`` trains with proper scoring rules
-(log score or Brier); ``Temperatures`` / ``binning`` / ``Abstention`` calibrate and gate the answers.
+A request is a state (text, or any JSON) and named questions, each a ``Noul`` (yes / no), a ``Choice`` among named options or a
+``Score`` over ordered levels.  A ``Layout`` writes the questions out with the state as token rows (one row per question with a
+marker per option, state-first rows for a causal backbone, or every question of a request in one joint row), rows are packed
+first-fit into windows, a backbone reads them, a head scores every option (``DecisionHead`` at the markers, ``JointSchemaHead``
+over pooled option spans, ``LabelReadout`` / ``SlotReadout`` at an answer cue), and the answer is a distribution over exactly the
+options each question names.  ``DecisionObjective`` trains on proper scoring rules (with label smoothing and a consistency term
+over grouped questions), ``Calibration`` (temperatures, binning, abstention per bucket) turns raw logits into reported answers,
+and ``Decide`` answers requests inside a token budget, plays wide choices as tournaments and speaks the JSON wire form.
 
-Reference: src/dew/decision/{questions,layout,head,objective,calibration,task}.py (23 files, 12.1 K lines).
+Reference: src/dew/decision/ (questions, layout, inputs, head, model, data, objective, scoring, metrics, calibration, task).
 """
-from .questions import Choice, Question, Score
-from .model import DecisionHead, Decide, layout_row
+from .calibration import Abstention, Binning, Calibration, Scored, Temperatures, bucket
+from .data import Example, Group, GroupedExamples, ParseTable, decisions, mixture
+from .head import DecisionHead, Head, JointSchemaHead, LabelReadout, SlotReadout
+from .inputs import DecisionInputs, collate, first_fit
+from .layout import ByteTokenizer, Encoded, Layout, Refused, Specials, Usage, render, usage_of
+from .metrics import AURC, ECE, Accuracy, Decisions, MacroF1, ScoredQuestions, default_metrics, measure
+from .model import BidirectionalBackbone, DecisionModel
 from .objective import DecisionObjective
-from .calibration import Abstention, Temperatures, binning
+from .questions import (KINDS, Answer, Choice, ChoiceAnswer, Confidence, EntropyConfidence, JevConfidence, Noul, NoulAnswer, Question,
+                        Score, ScoreAnswer, TopProbability, kind_of)
+from .scoring import Brier, Combined, LogLoss, RankedProbability, ScoringRule, Spherical
+from .task import TASK_FILE, Budget, Decide, Finalists, Knockout, Request
 
-__all__ = ["Abstention", "Choice", "Decide", "DecisionHead", "DecisionObjective", "Question", "Score", "Temperatures", "binning", "layout_row"]
+__all__ = [n for n in dir() if not n.startswith("_")]

@@ -1,66 +1,79 @@
+"""A backbone and a decision head, applied as two modules over one parameter tree.
+
+``DecisionModel(backbone, head)(inputs)`` returns ``[B, Q, K]`` option logits with ``-inf`` past each question's options.  The
+backbone is anything with ``hidden(tokens, positions, segment_ids) -> [B, L, D]`` (``models.CausalTransformer`` for the
+state-first and joint layouts) and, for the readout heads, ``head_weight() -> [V, D]``.  ``BidirectionalBackbone`` is a small
+encoder for the marker layout: learned positions, attention inside a row only.
+
+Reference: src/dew/decision/model.py (``DecisionModel``: ``states``, ``readout_logits``, the backbone / head split of the tree).
+"""
 from __future__ import annotations
 
-from typing import Dict, List, Mapping, Sequence, Tuple
+from typing import Optional
 
 import torch
 import torch.nn as nn
 
-from .questions import Question
+from .head import Head, _Block, _same_row
+from .inputs import DecisionInputs
 
 
-def layout_row(state: Sequence[int], questions: Sequence[Question], marker_id: int, max_len: int, pad_id: int = 0):
-    """State first, then one marker token per question (a causal backbone has read the whole state at every marker).
-    Returns ``(tokens [max_len], marker positions [Q])``; the state is truncated on the left if the row is too short."""
-    room = max_len - len(questions)
-    state = list(state)[-room:]
-    row = state + [marker_id] * len(questions)
-    pos = [len(state) + i for i in range(len(questions))]
-    return torch.tensor(row + [pad_id] * (max_len - len(row)), dtype=torch.long), torch.tensor(pos, dtype=torch.long)
-
-
-class DecisionHead(nn.Module):
-    """Scores option ``o`` of question ``q`` as ``<W_q h, e_{q,o}> + b_{q,o}``: a per-question projection of the hidden state
-    at the question's marker against a learned embedding per option."""
-
-    def __init__(self, features: int, questions: Sequence[Question], width: int = 64):
+class BidirectionalBackbone(nn.Module):
+    def __init__(self, vocab_size: int, features: int = 128, layers: int = 2, heads: Optional[int] = None, max_len: int = 512,
+                 dropout: float = 0.0):
         super().__init__()
-        self.questions = list(questions)
-        self.proj = nn.ModuleList([nn.Linear(features, width) for _ in self.questions])
-        self.options = nn.ParameterList([nn.Parameter(torch.randn(len(q.options), width) * width ** -0.5) for q in self.questions])
-        self.bias = nn.ParameterList([nn.Parameter(torch.zeros(len(q.options))) for q in self.questions])
+        self.features = features
+        self.embed = nn.Embedding(vocab_size, features)
+        self.position = nn.Embedding(max_len, features)
+        self.blocks = nn.ModuleList([_Block(features, heads or max(1, features // 64), activation="gelu", dropout=dropout) for _ in range(layers)])
+        self.norm = nn.LayerNorm(features)
 
-    def forward(self, hidden_at_markers: torch.Tensor) -> List[torch.Tensor]:
-        """``hidden_at_markers [B, Q, d]`` -> per question, logits ``[B, options]``."""
-        return [self.proj[i](hidden_at_markers[:, i].float()) @ self.options[i].t() + self.bias[i] for i in range(len(self.questions))]
+    def hidden(self, tokens, positions=None, segment_ids=None, cache=None, train: bool = False):
+        B, L = tokens.shape
+        if positions is None:
+            positions = torch.arange(L, device=tokens.device)[None].expand(B, -1)
+        if segment_ids is None:
+            segment_ids = torch.ones_like(tokens, dtype=torch.int32)
+        x = self.embed(tokens) + self.position(positions)
+        mask = _same_row(segment_ids, segment_ids)
+        for b in self.blocks:
+            x = b(x, mask)
+        return self.norm(x)
+
+    def head_weight(self):
+        return self.embed.weight
 
 
-class Decide(nn.Module):
-    """The task: backbone + head; ``answer(states)`` returns per request a dict question name -> {option: probability}."""
+def features_of(backbone) -> int:
+    cfg = getattr(backbone, "config", None)
+    for holder in (backbone, cfg):
+        for name in ("features", "emb_features", "hidden_size"):
+            v = getattr(holder, name, None) if holder is not None else None
+            if isinstance(v, int):
+                return v
+    raise ValueError("cannot tell the backbone's width: give it a `features` attribute")
 
-    def __init__(self, backbone, questions: Sequence[Question], marker_id: int, max_len: int = 128, width: int = 64):
+
+class DecisionModel(nn.Module):
+    def __init__(self, backbone: nn.Module, head: Head, freeze_backbone: bool = False):
         super().__init__()
-        self.backbone, self.questions, self.marker_id, self.max_len = backbone, list(questions), marker_id, max_len
-        features = backbone.config.emb_features
-        self.head = DecisionHead(features, questions, width)
+        self.backbone, self.head = backbone, head
+        if freeze_backbone:
+            for p in backbone.parameters():
+                p.requires_grad_(False)
+        self.frozen = freeze_backbone
 
-    def encode(self, states: Sequence[Sequence[int]]):
-        rows, pos = zip(*(layout_row(s, self.questions, self.marker_id, self.max_len) for s in states))
-        return torch.stack(rows), torch.stack(pos)
+    def states(self, inputs: DecisionInputs) -> torch.Tensor:
+        if self.frozen:
+            with torch.no_grad():
+                return self.backbone.hidden(inputs.tokens, inputs.positions, inputs.segment_ids)
+        return self.backbone.hidden(inputs.tokens, inputs.positions, inputs.segment_ids)
 
-    def logits(self, tokens: torch.Tensor, positions: torch.Tensor) -> List[torch.Tensor]:
-        h = self.backbone.hidden(tokens)
-        at = h.gather(1, positions.to(h.device)[..., None].expand(-1, -1, h.shape[-1]))
-        return self.head(at)
+    def forward(self, inputs: DecisionInputs) -> torch.Tensor:
+        states = self.states(inputs)
+        table = self.backbone.head_weight() if self.head.reads_table else None
+        logits = self.head(states, inputs, table)
+        return logits.float().masked_fill(~inputs.options, float("-inf"))
 
-    @torch.no_grad()
-    def answer(self, states: Sequence[Sequence[int]], temperatures=None) -> List[Dict[str, Dict[str, float]]]:
-        dev = next(self.parameters()).device
-        tokens, pos = self.encode(states)
-        logits = self.logits(tokens.to(dev), pos.to(dev))
-        out = [dict() for _ in states]
-        for qi, (q, lg) in enumerate(zip(self.questions, logits)):
-            t = 1.0 if temperatures is None else float(temperatures.value[qi])
-            probs = torch.softmax(lg / t, -1).cpu()
-            for r in range(len(states)):
-                out[r][q.name] = {o: float(p) for o, p in zip(q.options, probs[r])}
-        return out
+    def record(self):
+        return {"head": self.head.record(), "frozen": self.frozen, "features": features_of(self.backbone)}

@@ -84,9 +84,8 @@ def test_pinn_burgers_example_and_gauss_newton_on_a_linear_system():
 
 def test_route_decisions_example():
     report = _load("route_decisions").main(["--steps", "200"])
-    assert set(report) == {"parity", "half", "multiple_of_five"}
-    assert report["half"]["accuracy"] > 0.85 and report["parity"]["accuracy"] > 0.85
-    assert all(0.0 <= r["answered"] <= 1.0 for r in report.values())
+    assert report["accuracy"] > 0.8 and report["scored_questions"] == 768 and report["brier"] < 0.4
+    assert 0.3 < report["answered"] <= 1.0 and report["answered_accuracy"] >= report["accuracy"] - 0.02
 
 
 def test_sft_chat_example():
