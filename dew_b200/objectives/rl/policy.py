@@ -1,84 +1,139 @@
-"""Policy-gradient objectives over sampled completions: ``GRPO`` (group-relative advantages, clipped ratio, KL to the
-reference in the EMA slot) and ``PPO`` (clipped surrogate + value loss + entropy bonus).
-Reference: src/dew/objectives/rl (GRPO, PPO), src/dew/rl/advantage.py."""
+"""Policy-gradient objectives over sampled completions, assembled from ``dew_b200.rl.advantage`` and ``dew_b200.rl.surrogate``.
+
+``GRPO``  group-relative advantages (``advantage='grpo' | 'dr_grpo' | 'rloo'``) under one of the update rules ``rule='ppo'`` (clipped
+          ratio with asymmetric clips and the dual clip), ``'gspo'`` (sequence-level ratio), ``'cispo'``, ``'gmpo'`` or ``'reinforce'``;
+          a KL pull to the reference kept in the EMA slot (``kl_kind`` k1 / abs / k2 / k3); corrections for a sampler whose
+          log-probabilities differ from the trainer's (``behavior_logprobs`` in the batch: truncated importance weights, IcePop's
+          band, sequence rejection); any of ``surrogate.aggregate``'s reductions
+``PPO``   clipped surrogate + clipped value loss + entropy bonus; advantages given, or computed from token rewards and old values
+          by masked GAE with whitening
+
+Reference: src/dew/objectives/rl (GRPO, PPO and their options), src/dew/rl/advantage.py, src/dew/rl/surrogate.py."""
 from __future__ import annotations
+
+from typing import Optional
 
 import torch
 
+from ...rl import advantage as A
+from ...rl import surrogate as S
 from ..base import Aux, EMASpec, Objective, Ratio, Step
 
 
 def group_advantages(rewards: torch.Tensor, group: int, eps: float = 1e-6) -> torch.Tensor:
     """Standardise rewards within each group of ``group`` completions of the same prompt."""
-    r = rewards.float().reshape(-1, group)
-    return ((r - r.mean(1, keepdim=True)) / (r.std(1, keepdim=True) + eps)).reshape(-1)
+    return A.group_advantage(rewards.float(), group, eps)
 
 
 def gae(rewards, values, dones, gamma: float = 0.99, lam: float = 0.95):
     """Generalised advantage estimation over ``[T, B]`` trajectories; ``values`` has one extra bootstrap row."""
-    T = rewards.shape[0]
-    adv = torch.zeros_like(rewards)
-    last = torch.zeros_like(rewards[0])
-    for t in reversed(range(T)):
-        nonterminal = 1.0 - dones[t].float()
-        delta = rewards[t] + gamma * values[t + 1] * nonterminal - values[t]
-        last = delta + gamma * lam * nonterminal * last
-        adv[t] = last
-    return adv, adv + values[:-1]
+    return A.generalized_advantages(rewards, values[:-1], dones, gamma, lam, bootstrap=values[-1])
 
 
 def _token_logprobs(logits, tokens):
     return torch.log_softmax(logits.float(), -1).gather(-1, tokens[:, 1:, None]).squeeze(-1)
 
 
+_ADVANTAGES = {"grpo": lambda r, g: A.group_advantage(r, g), "dr_grpo": A.dr_grpo_advantage, "rloo": A.rloo_advantage}
+RULES = ("ppo", "gspo", "cispo", "gmpo", "reinforce")
+
+
 class GRPO(Objective):
     starts_from_model = True
-    """batch: ``tokens [B,S]``, ``mask [B,S]`` (1 on completion tokens), ``rewards [B]``, ``old_logprobs [B,S-1]``."""
+    """batch: ``tokens [B,S]``, ``mask [B,S]`` (1 on completion tokens), ``rewards [B]``, ``old_logprobs [B,S-1]``; optionally
+    ``behavior_logprobs [B,S-1]`` (what the sampling engine reported) and ``advantages [B]`` (overrides the group estimate)."""
 
-    def __init__(self, model, group: int = 4, clip: float = 0.2, kl: float = 0.04):
+    def __init__(self, model, group: int = 4, clip: float = 0.2, kl: float = 0.04, *, clip_high: Optional[float] = None,
+                 dual_clip: Optional[float] = None, rule: str = "ppo", advantage: str = "grpo", reduction: Optional[str] = None,
+                 kl_kind: str = "k3", importance: Optional[str] = None, importance_threshold: float = 2.0, band=(0.5, 2.0)):
+        if rule not in RULES:
+            raise ValueError(f"unknown update rule {rule!r}; known: {RULES}")
+        if advantage not in _ADVANTAGES:
+            raise ValueError(f"unknown advantage estimator {advantage!r}; known: {sorted(_ADVANTAGES)}")
+        if importance not in (None, "truncated", "band", "reject"):
+            raise ValueError("importance is None, 'truncated' (TIS), 'band' (IcePop) or 'reject' (sequence rejection)")
         self.model, self.group, self.clip, self.kl = model, group, clip, kl
+        self.clip_high, self.dual_clip, self.rule, self.advantage = clip_high, dual_clip, rule, advantage
+        self.reduction = reduction or {"gspo": "seq-mean-token-mean", "gmpo": "seq-mean-token-mean", "dr_grpo": "seq-mean-token-sum-norm"}.get(
+            rule if rule in ("gspo", "gmpo") else advantage, "token-mean")
+        self.kl_kind, self.importance, self.importance_threshold, self.band = kl_kind, importance, importance_threshold, band
         self.ema_decay = EMASpec.constant(1.0)
 
     def loss(self, variables, batch, step: Step):
-        tokens, mask = batch["tokens"], batch["mask"][:, 1:].float()
+        tokens, mask = batch["tokens"], batch["mask"][:, 1:].bool()
         lp = _token_logprobs(self.apply(variables, tokens[:, :-1]), tokens)
-        adv = group_advantages(batch["rewards"], self.group).to(lp.device)[:, None]
-        ratio = torch.exp(lp - batch["old_logprobs"].float())
-        surr = torch.minimum(ratio * adv, ratio.clamp(1 - self.clip, 1 + self.clip) * adv)
-        per = -surr
-        aux_metrics = {}
+        old = batch["old_logprobs"].float()
+        adv = batch["advantages"].float() if "advantages" in batch else _ADVANTAGES[self.advantage](batch["rewards"].float(), self.group)
+        adv = adv.to(lp.device)[:, None].expand_as(lp)
+        metrics = {}
+        if self.rule == "ppo":
+            terms, m = S.clipped_surrogate_terms(S.token_log_ratio(lp, old), adv, mask, self.clip, self.clip_high, self.dual_clip)
+        elif self.rule == "gspo":
+            terms, m = S.clipped_surrogate_terms(S.sequence_log_ratio(lp, old, mask), adv, mask, self.clip, self.clip_high, None)
+        elif self.rule == "cispo":
+            terms, m = S.cispo_terms(lp, old, adv, mask, self.clip, self.clip if self.clip_high is None else self.clip_high)
+        elif self.rule == "gmpo":
+            terms, m = S.gmpo_terms(lp, old, adv, mask, self.clip, self.clip if self.clip_high is None else self.clip_high)
+        else:
+            terms, m = S.reinforce_terms(lp, adv), {}
+        keep = mask
+        if self.importance is not None and "behavior_logprobs" in batch:
+            beh = batch["behavior_logprobs"].float()
+            if self.importance == "truncated":
+                terms = terms * S.behavior_importance_weights(old, beh, mask, self.importance_threshold)
+            elif self.importance == "band":
+                terms = terms * S.behavior_band_weights(old, beh, mask, *self.band)
+            else:
+                keep = S.sequence_rejection_mask(old, beh, mask, *self.band).bool()
+            metrics.update({f"mismatch_{k}": Ratio(v.detach(), torch.tensor(1.0)) for k, v in S.mismatch_metrics(old, beh, mask).items()})
         if self.kl and step.ema is not None:
             with torch.no_grad():
                 ref = _token_logprobs(self.apply(step.ema, tokens[:, :-1]), tokens)
-            d = ref - lp
-            klv = torch.exp(d) - d - 1                                 # the k3 estimator
-            per = per + self.kl * klv
-            aux_metrics["kl"] = Ratio((klv.detach() * mask).sum(), mask.sum())
-        aux_metrics["clip_fraction"] = Ratio((((ratio - 1).abs() > self.clip).float() * mask).sum(), mask.sum())
-        return Ratio((per * mask).sum(), mask.sum()), Aux(metrics=aux_metrics)
+            klv = S.kl_penalty(lp, ref, self.kl_kind)
+            terms = terms + self.kl * klv
+            metrics["kl"] = Ratio((klv.detach() * mask).sum(), mask.sum())
+        count = mask.float().sum()
+        for k, v in m.items():
+            metrics[k] = Ratio(v.detach() * count, count)
+        if self.reduction == "token-mean":
+            kept = keep.float()
+            return Ratio((torch.where(keep, terms, torch.zeros_like(terms))).sum(), kept.sum().clamp_min(1)), Aux(metrics=metrics)
+        rows = (keep.float().sum(-1) > 0).float().sum().clamp_min(1)
+        return Ratio(S.aggregate(terms, keep, self.reduction) * rows, rows), Aux(metrics=metrics)
 
 
 class PPO(Objective):
     starts_from_model = True
-    """The model returns ``(logits, values)``; batch: ``tokens, mask, advantages [B,S-1], returns [B,S-1], old_logprobs``."""
+    """The model returns ``(logits, values)``; batch: ``tokens, mask, old_logprobs`` and either ``advantages [B,S-1]`` + ``returns
+    [B,S-1]`` or ``token_rewards [B,S-1]`` + ``old_values [B,S-1]`` (masked GAE with whitening computes the former from the latter)."""
 
-    def __init__(self, model, clip: float = 0.2, value_coef: float = 0.5, entropy_coef: float = 0.0):
+    def __init__(self, model, clip: float = 0.2, value_coef: float = 0.5, entropy_coef: float = 0.0, *, clip_high: Optional[float] = None,
+                 dual_clip: Optional[float] = None, value_clip: Optional[float] = None, gamma: float = 1.0, lam: float = 0.95):
         self.model, self.clip, self.value_coef, self.entropy_coef = model, clip, value_coef, entropy_coef
+        self.clip_high, self.dual_clip, self.value_clip, self.gamma, self.lam = clip_high, dual_clip, value_clip, gamma, lam
 
     def loss(self, variables, batch, step: Step):
-        tokens, mask = batch["tokens"], batch["mask"][:, 1:].float()
+        tokens, maskb = batch["tokens"], batch["mask"][:, 1:].bool()
+        mask = maskb.float()
         logits, values = self.apply(variables, tokens[:, :-1])
+        values = values.float().squeeze(-1)
         lp = _token_logprobs(logits, tokens)
-        ratio = torch.exp(lp - batch["old_logprobs"].float())
-        adv = batch["advantages"].float()
-        policy = -torch.minimum(ratio * adv, ratio.clamp(1 - self.clip, 1 + self.clip) * adv)
-        value = 0.5 * (values.float().squeeze(-1) - batch["returns"].float()) ** 2
+        if "advantages" in batch:
+            adv, returns = batch["advantages"].float(), batch["returns"].float()
+        else:
+            adv, returns = A.gae(batch["token_rewards"].float(), batch["old_values"].float(), maskb, self.gamma, self.lam)
+        policy, pm = S.clipped_surrogate_terms(S.token_log_ratio(lp, batch["old_logprobs"].float()), adv, maskb, self.clip, self.clip_high, self.dual_clip)
+        if self.value_clip is not None and "old_values" in batch:
+            value, _ = S.clipped_value_loss_terms(values, batch["old_values"].float(), returns, self.value_clip)
+        else:
+            value = 0.5 * (values - returns) ** 2
         p = torch.softmax(logits.float(), -1)
         ent = -(p * torch.log(p.clamp_min(1e-12))).sum(-1)
         per = policy + self.value_coef * value - self.entropy_coef * ent
         m = mask.sum()
         return Ratio((per * mask).sum(), m), Aux(metrics={"entropy": Ratio((ent.detach() * mask).sum(), m),
-                                                           "value_loss": Ratio((value.detach() * mask).sum(), m)})
+                                                           "value_loss": Ratio((value.detach() * mask).sum(), m),
+                                                           "clip_fraction": Ratio(pm["clip_fraction"].detach() * m, m)})
 
 
 class FlowGRPO(Objective):

@@ -80,6 +80,61 @@ def test_grpo_and_ppo_losses_and_advantages():
     assert torch.isfinite(stats.total) and float(aux.metrics["entropy"].value()) > 0
 
 
+def test_policy_update_rules_agree_on_policy_and_differ_off_policy():
+    """On policy (the sampling weights are the trained ones) every update rule's gradient is REINFORCE's; off policy the clips,
+    the sequence ratio and the sampler corrections change it."""
+    torch.manual_seed(0)
+    m = _lm(5)
+    tokens = torch.randint(0, 50, (8, 10))
+    mask = torch.ones(8, 10)
+    mask[:, :3] = 0
+    with torch.no_grad():
+        old = torch.log_softmax(m(tokens[:, :-1]).float(), -1).gather(-1, tokens[:, 1:, None]).squeeze(-1)
+    rewards = torch.randn(8)
+    batch = {"tokens": tokens, "mask": mask, "rewards": rewards, "old_logprobs": old}
+
+    def grad(obj, b=batch):
+        m.zero_grad()
+        stats, aux = obj.loss(None, b, dew.Step())
+        (stats.total / stats.mass).backward()
+        return torch.cat([p.grad.flatten() for p in m.parameters() if p.grad is not None]), aux
+
+    base, _ = grad(GRPO(m, group=4, kl=0.0, rule="reinforce"))
+    for rule in ("ppo", "cispo"):
+        g, _ = grad(GRPO(m, group=4, kl=0.0, rule=rule, dual_clip=3.0 if rule == "ppo" else None))
+        assert torch.allclose(g, base, atol=1e-5), rule
+    gs, _ = grad(GRPO(m, group=4, kl=0.0, rule="gspo"))
+    rs, _ = grad(GRPO(m, group=4, kl=0.0, rule="reinforce", reduction="seq-mean-token-mean"))
+    assert torch.allclose(gs, rs, atol=1e-5)
+    gm, _ = grad(GRPO(m, group=4, kl=0.0, rule="gmpo"))
+    assert torch.isfinite(gm).all() and float(gm.norm()) > 0
+    # estimators: leave-one-out is the centred reward times g / (g - 1); Dr. GRPO drops the deviation and normalises by the row length
+    lo, _ = grad(GRPO(m, group=4, kl=0.0, rule="reinforce", advantage="rloo"))
+    dr, _ = grad(GRPO(m, group=4, kl=0.0, rule="reinforce", advantage="dr_grpo", reduction="token-mean"))
+    assert torch.allclose(lo, dr * 4 / 3, atol=1e-5)
+    # off policy: a sampler far from the trainer is cut by the truncated weights, and a rejected sequence contributes nothing
+    shifted = {**batch, "old_logprobs": old + 0.5, "behavior_logprobs": old + 0.5 + torch.tensor([3.0] * 4 + [0.0] * 4)[:, None]}
+    plain, _ = grad(GRPO(m, group=4, kl=0.0), shifted)
+    tis, aux = grad(GRPO(m, group=4, kl=0.0, importance="truncated"), shifted)
+    rej, _ = grad(GRPO(m, group=4, kl=0.0, importance="reject", band=(0.5, 2.0)), shifted)
+    assert not torch.allclose(plain, tis) and not torch.allclose(plain, rej) and "mismatch_k3_kl" in aux.metrics
+    assert float(aux.metrics["clip_fraction"].value()) > 0
+    with pytest.raises(ValueError):
+        GRPO(m, rule="trpo")
+
+    class WithValue(nn.Module):
+        def __init__(self, lm):
+            super().__init__(); self.lm = lm; self.v = nn.Linear(50, 1)
+
+        def forward(self, t):
+            lg = self.lm(t)
+            return lg, self.v(lg.float())
+    p = PPO(WithValue(m), value_clip=0.2, dual_clip=3.0, gamma=1.0, lam=0.95)
+    stats, aux = p.loss(None, {"tokens": tokens, "mask": mask, "old_logprobs": old, "token_rewards": torch.randn(8, 9) * mask[:, 1:],
+                               "old_values": torch.randn(8, 9)}, dew.Step())
+    assert torch.isfinite(stats.total) and float(aux.metrics["value_loss"].value()) > 0
+
+
 def test_distillation_pulls_student_to_teacher():
     teacher, student = _lm(3), _lm(4)
     obj = Distillation(student, teacher)

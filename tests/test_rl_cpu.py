@@ -64,14 +64,25 @@ def test_fisheye_direct_cast_matches_resampled_pinhole():
 
 
 def test_gate_race_steps_with_images():
-    env = GateRace(3, camera=Camera(size=(24, 24)), seed=1)
-    obs = env.reset()
-    assert obs["state"].shape == (3, 13) and obs["image"].shape == (3, 24, 24, 3)
+    env = GateRace(3, camera=Camera(size=(24, 24)), views=("state", "gates"))
+    obs = env.reset(1)
+    assert obs["state"].shape == (3, 13) and obs["gates"].shape == (3, 24) and obs["image"].shape == (3, 24, 24, 3)
     total = torch.zeros(3)
     for _ in range(20):
-        obs, r, done = env.step(torch.zeros(3, 4))
+        obs, r, terminated, truncated = env.step(torch.zeros(3, 4))
         total += r
-    assert torch.isfinite(total).all() and torch.isfinite(obs["image"]).all()
+    assert torch.isfinite(total).all() and torch.isfinite(obs["image"]).all() and not bool(truncated.any())
+    # the gate headed for is in view at the start: its lit frame colours some pixels
+    first = GateRace(2, camera=Camera(size=(48, 48), fov=110.0, fog=0.0), difficulty=0.0, ramp=0.0).reset(3)["image"]
+    lit = (first[..., 0] > first[..., 1]) & (first[..., 1] > 2 * first[..., 2]) & (first[..., 0] > 0.2)
+    assert int(lit[0].sum()) > 30
+    # a branch steps the race and leaves it as it was
+    before = env.state["flight"]["position"].clone()
+    with env.branch():
+        env.step(torch.ones(3, 4))
+    assert torch.equal(env.state["flight"]["position"], before)
+    restarted = env.restart(torch.tensor([True, False, False]))
+    assert int(env.state["steps"][0]) == 0 and int(env.state["steps"][1]) == 20 and restarted["state"].shape == (3, 13)
 
 
 def test_dreamer_actor_critic_improves_imagined_return():
