@@ -118,7 +118,7 @@ class Decide:
         self.model.eval()
         try:
             while pending:
-                longest = max(len(rows[i]) for i in pending[:1])
+                longest = len(rows[pending[0]])
                 # a pass grows row by row while a length holds it: take the shortest declared length that fits the first row,
                 # then first-fit the rest into that length's windows
                 length = next((l for l in self.budget.lengths if l >= longest), None)
@@ -137,7 +137,8 @@ class Decide:
                 for j, slots in enumerate(where):
                     if slots:
                         out[fits[j]] = np.stack([lg[b, q, : max(sub[j].counts)] for b, q in slots])
-                pending = [i for i in pending if i not in set(taken)]
+                done = set(taken)
+                pending = [i for i in pending if i not in done]
         finally:
             self.model.train(was_training)
         return out            # type: ignore[return-value]
@@ -302,6 +303,14 @@ class Decide:
                       "usage": reported}
         return [out[i] for i in range(len(bodies))]
 
+    # ------------------------------------------------------------------ as a served task
+    def scoring(self, *, details: bool = False, strict: bool = False, whole: bool = False) -> "WireScoring":
+        """This task as a scoring task of wire bodies for ``inference.scoring.ScoringServer``: bodies submitted from many threads
+        are laid out as they arrive and their rows scored together, a pass at a time."""
+        if strict and details:
+            raise ValueError("strict answers hold the wire's own fields alone, so they carry no details")
+        return WireScoring(self, details, strict, whole)
+
     # ------------------------------------------------------------------ saving
     def save(self, directory: str, weights: bool = True) -> str:
         os.makedirs(directory, exist_ok=True)
@@ -338,6 +347,66 @@ class Decide:
         return cls(model, Layout.from_record(rec["layout"], tokenizer), calibration=Calibration.from_record(rec["calibration"]),
                    confidence=getattr(Q, rec.get("confidence", "JevConfidence"))(),
                    budget=Budget(b["tokens"], b["rows"], tuple(b["lengths"]), b.get("options")), tournament=tour, name=rec["name"], device=device)
+
+
+class WireScoring:
+    """``Decide`` behind a ``ScoringServer``: ``admit`` parses and lays out a body (refusing what the wire form refuses, a body that
+    would have to be cut under ``whole`` included), ``forward`` scores rows inside the task's budget, ``answer`` builds the
+    response body.  Wide choices (tournaments) are played at answer time, outside the shared passes."""
+
+    def __init__(self, decide: Decide, details: bool, strict: bool, whole: bool):
+        self.decide, self.details, self.strict, self.whole = decide, details, strict, whole
+        self.admitted = 0
+        self.refusals: Dict[str, int] = {}
+
+    def admit(self, request):
+        from ..inference.scoring import ScoringRequest
+        d = self.decide
+        try:
+            r = d._read_wire(request)
+            rows, _ = d._rows_of(r.state, r.questions)
+            usage = usage_of(rows)
+            if self.whole and (usage.truncated or usage.trimmed):
+                what = "state" if usage.truncated else "instructions or options"
+                raise Refused("cut", f"the request does not fit the maximum context length, max_len={d.layout.max_len} tokens, "
+                                     f"without cutting its {what}")
+        except ValueError as refused:
+            reason = getattr(refused, "reason", "malformed")
+            self.refusals[reason] = self.refusals.get(reason, 0) + 1
+            raise
+        self.admitted += 1
+        return ScoringRequest(tuple(rows), (r, usage))
+
+    def forward(self, rows):
+        return self.decide.logits(list(rows))
+
+    def answer(self, payload, outputs):
+        d = self.decide
+        r, usage = payload
+        answers: Dict[str, Answer] = {}
+        narrow = [n for n, q in r.questions.items() if not d._wide(q)]
+        at = 0
+        if d.layout.shape == "joint":
+            for qi, name in enumerate(narrow):
+                answers[name] = d._answer(r.questions[name], outputs[0][qi])
+        else:
+            for name in narrow:
+                answers[name] = d._answer(r.questions[name], outputs[at][0])
+                at += 1
+        for name, q in r.questions.items():
+            if d._wide(q):
+                answers[name] = d._tournament(r.state, q)
+        reported: Dict[str, Any] = {"input_tokens": usage.input_tokens, "output_tokens": 0}
+        if self.details:
+            reported.update(state_tokens=usage.state_tokens, state_kept=usage.state_kept, truncated=usage.truncated,
+                            cut={k: {"rows": a, "removed": b, "unit": "tokens"} for k, (a, b) in usage.cut.items()})
+        gated = d.calibration.abstention is not None
+        return {"model": d.name, "answers": {n: _wire(r.questions[n], answers[n], details=self.details, gated=gated) for n in r.questions},
+                "usage": reported}
+
+    def metrics(self):
+        return {"admitted": float(self.admitted), "real_token_share": self.decide.real_token_share(),
+                **{f"refused/{k}": float(v) for k, v in self.refusals.items()}}
 
 
 def _wire(q: Question, a: Answer, *, details: bool, gated: bool) -> Dict[str, Any]:

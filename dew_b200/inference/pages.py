@@ -30,9 +30,65 @@ class Seat:
     reused_tokens: int          # prompt tokens already present in re-used pages (need no prefill)
 
 
+class HostTier:
+    """Evicted prefix pages kept in pinned host memory: when the device pool takes back a cached page, its keys and values (every
+    layer's) are copied to a host slot under the page's chain hash; a later prompt with that prefix copies them back into a fresh
+    device page instead of recomputing them.  Slots are recycled least recently used first.  The copies are issued on the
+    current stream, so they are ordered against the kernels that wrote the page before and overwrite it after."""
+
+    def __init__(self, store, slots: int):
+        import torch
+        self.store, self.slots = store, slots
+        pin = store.device.type == "cuda"
+        shape = (slots, store.layers, store.page_size, store.kv_heads, store.head_dim)
+        self.k = torch.zeros(shape, dtype=store.k.dtype, pin_memory=pin)
+        self.v = torch.zeros(shape, dtype=store.v.dtype, pin_memory=pin)
+        quantized = store.k_scale is not None
+        self.k_scale = torch.ones(shape[:-1], dtype=torch.float32, pin_memory=pin) if quantized else None
+        self.v_scale = torch.ones(shape[:-1], dtype=torch.float32, pin_memory=pin) if quantized else None
+        self.slot_of: "OrderedDict[bytes, int]" = OrderedDict()           # oldest first
+        self.free: List[int] = list(range(slots - 1, -1, -1))
+        self.spilled = self.fetched = 0
+
+    def has(self, name: bytes) -> bool:
+        return name in self.slot_of
+
+    def spill(self, page: int, name: bytes) -> None:
+        if self.slots <= 0:
+            return
+        if name in self.slot_of:
+            self.slot_of.move_to_end(name)
+            return
+        slot = self.free.pop() if self.free else self.slot_of.popitem(last=False)[1]
+        st = self.store
+        self.k[slot].copy_(st.k[:, page], non_blocking=True)
+        self.v[slot].copy_(st.v[:, page], non_blocking=True)
+        if self.k_scale is not None:
+            self.k_scale[slot].copy_(st.k_scale[:, page], non_blocking=True)
+            self.v_scale[slot].copy_(st.v_scale[:, page], non_blocking=True)
+        self.slot_of[name] = slot
+        self.spilled += 1
+
+    def fetch(self, name: bytes, page: int) -> bool:
+        slot = self.slot_of.get(name)
+        if slot is None:
+            return False
+        self.slot_of.move_to_end(name)
+        st = self.store
+        st.k[:, page].copy_(self.k[slot], non_blocking=True)
+        st.v[:, page].copy_(self.v[slot], non_blocking=True)
+        if self.k_scale is not None:
+            st.k_scale[:, page].copy_(self.k_scale[slot], non_blocking=True)
+            st.v_scale[:, page].copy_(self.v_scale[slot], non_blocking=True)
+        self.fetched += 1
+        return True
+
+
 class PageLedger:
-    def __init__(self, pages: int, page_size: int, prefix_cache: bool = True):
+    def __init__(self, pages: int, page_size: int, prefix_cache: bool = True, host: Optional[HostTier] = None):
         self.pages, self.page_size, self.prefix_cache = pages, page_size, prefix_cache
+        self.host = host
+        self.host_hits = 0
         self.free: List[int] = list(range(pages - 1, -1, -1))
         self.refs: Dict[int, int] = {}
         self.name_of: Dict[int, bytes] = {}                 # page -> chain hash (only full prompt pages)
@@ -52,6 +108,8 @@ class PageLedger:
             name = self.name_of.pop(page, None)
             if name is not None:
                 self.page_of.pop(name, None)
+                if self.host is not None:
+                    self.host.spill(page, name)              # its contents move to the host tier before the page is reused
             return page
         raise OutOfPages("the KV page pool is exhausted")
 
@@ -71,7 +129,12 @@ class PageLedger:
                 self.lookups += 1
                 page = self.page_of.get(name)
                 if page is None:
-                    break
+                    if self.host is None or not self.host.has(name) or self.available() == 0:
+                        break
+                    page = self._take()                      # bring the page back from the host tier under its old name
+                    self.host.fetch(name, page)
+                    self.page_of[name], self.name_of[page] = page, name
+                    self.host_hits += 1
                 self.hits += 1
                 self.idle.pop(page, None)
                 self.refs[page] = self.refs.get(page, 0) + 1

@@ -18,7 +18,7 @@ import torch
 from ..nn.kv_cache import KVCache, KVStore
 from ..sampling.text import Sampling, transform_logits
 from ..utils import keys as K
-from .pages import OutOfPages, PageLedger
+from .pages import HostTier, OutOfPages, PageLedger
 
 
 @dataclass
@@ -55,7 +55,8 @@ class _Row:
 class Server:
     def __init__(self, model, variables=None, *, slots: int, capacity: int, kv_cache: Optional[KVCache] = None,
                  chunk: Optional[int] = None, prefix_cache: bool = True, decode_steps: int = 1, sampling: Optional[Sampling] = None,
-                 tokenizer=None, prefill_budget: Optional[int] = None, cuda_graph: bool = False, clock: Callable[[], float] = time.perf_counter):
+                 tokenizer=None, prefill_budget: Optional[int] = None, cuda_graph: bool = False, clock: Callable[[], float] = time.perf_counter,
+                 host_pages: int = 0):
         self.model, self.variables, self.tokenizer = model, variables, tokenizer
         self.slots, self.capacity = slots, capacity
         limit = getattr(getattr(model, "config", None), "max_seq_len", None)
@@ -72,7 +73,8 @@ class Server:
         hd = cfg.head_dim or cfg.emb_features // cfg.num_heads
         kvh = getattr(model, "local_kv_heads", None) or (cfg.num_kv_heads or cfg.num_heads)
         self.store = KVStore(self.spec, cfg.num_layers, slots, capacity, kvh, hd, p.dtype, p.device)
-        self.ledger = PageLedger(pool, self.spec.page_size, prefix_cache)
+        self.host_tier = HostTier(self.store, host_pages) if host_pages > 0 and prefix_cache else None
+        self.ledger = PageLedger(pool, self.spec.page_size, prefix_cache, self.host_tier)
         self.chunk = chunk or 512
         self.prefill_budget = prefill_budget or 8 * self.chunk     # prompt tokens admitted per step (keeps decode latency bounded)
         self.decode_steps = decode_steps
@@ -100,7 +102,7 @@ class Server:
     def from_task(cls, task, *, slots: int, capacity: int, admission=None, kv_cache=None, chunk=None, prefix_cache=None,
                   host_pages: int = 0, decode_steps: int = 1, cuda_graph: bool = False) -> "Server":
         return cls(task.model, task.variables, slots=slots, capacity=capacity, kv_cache=kv_cache if kv_cache is not None else task.kv_cache,
-                   chunk=chunk, prefix_cache=True if prefix_cache is None else bool(prefix_cache), decode_steps=decode_steps,
+                   chunk=chunk, prefix_cache=True if prefix_cache is None else bool(prefix_cache), decode_steps=decode_steps, host_pages=host_pages,
                    sampling=task.sampling, tokenizer=task.tokenizer, cuda_graph=cuda_graph)
 
     def submit(self, prompt, max_new_tokens: int, key: int = 0, sampling: Optional[Sampling] = None, on_token=None) -> Ticket:

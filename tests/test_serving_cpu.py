@@ -41,6 +41,30 @@ def test_prefix_pages_are_reused():
     assert b.tokens == ref.tokens[0, 35:39].tolist()
 
 
+def test_evicted_prefix_pages_return_from_the_host_tier():
+    """A small device pool evicts a cached prefix; with a host tier the prefix comes back by copy instead of by recomputation,
+    and the served tokens are the same either way."""
+    m = _model()
+    shared = list(range(1, 33))                       # four full pages of 8
+    other = [(7 * i) % 90 + 5 for i in range(40)]
+
+    def serve(host_pages):
+        server = Server(m, slots=1, capacity=48, kv_cache=KVCache(page_size=8, pages=6), chunk=64, host_pages=host_pages)
+        server.submit(shared + [50, 51], 4)
+        server.run(max_steps=100)
+        server.submit(other, 4)                       # needs the whole pool: the cached prefix pages are evicted
+        server.run(max_steps=100)
+        t = server.submit(shared + [60, 61, 62], 4)
+        server.run(max_steps=100)
+        return server, t
+
+    plain, t0 = serve(0)
+    tiered, t1 = serve(8)
+    assert plain.ledger.host_hits == 0 and tiered.ledger.host_hits == 4 and tiered.host_tier.spilled >= 4 and tiered.host_tier.fetched == 4
+    ref = generate(m, None, [shared + [60, 61, 62]], 4, sampling=Sampling(temperature=0.0))
+    assert t0.tokens == t1.tokens == ref.tokens[0, 35:39].tolist()
+
+
 def test_ledger_accounting():
     led = PageLedger(pages=6, page_size=4)
     s1 = led.seat(list(range(10)), 12)
@@ -148,3 +172,48 @@ def test_text_generation_task_with_offloaded_layers():
     assert torch.equal(off([[1, 2, 3], [4, 5]], max_new_tokens=5).tokens, want)
     assert all(p.numel() == 0 for p in model.layers[1].parameters())
     task.banks.release()
+
+
+def test_scoring_server_batches_requests_from_threads_and_keeps_refusals_apart():
+    import threading
+    from dew_b200.decision import BidirectionalBackbone, Choice, Decide, DecisionHead, DecisionModel, Layout, Noul
+    from dew_b200.inference.scoring import LikelihoodScoring, ScoringServer, score
+    m = _model()
+    server = ScoringServer(LikelihoodScoring(m), max_rows=64)
+    futures = [server.submit(([1, 2, 3, i + 4], [[5, 6], [7], [8, 9, 10]])) for i in range(5)]
+    try:
+        server.submit(([1], []))
+        raise AssertionError("an empty request must be refused")
+    except ValueError:
+        pass
+    server.run()
+    direct = score(m, [[1, 2, 3, 4]] * 3, [[5, 6], [7], [8, 9, 10]])
+    got = futures[0].result()
+    assert [round(a[0], 4) for a in got] == [round(a[0], 4) for a in direct] and server.metrics()["rows"] == 15 and server.refused == 1
+    assert server.metrics()["passes"] == 1                                    # five requests, one pass
+    # a decision task served from a thread while four clients submit bodies
+    torch.manual_seed(0)
+    task = Decide(DecisionModel(BidirectionalBackbone(260, 32, 1, max_len=256), DecisionHead(32, 1)), Layout(shape="state_first", max_len=200, head_max_len=150))
+    qs = {"even": Noul("is it even"), "kind": Choice("which", ["a", "b", "c"])}
+    body = lambda i: {"state": f"number {i}", "questions": {n: q.wire() for n, q in qs.items()}}
+    wire = task.scoring(details=True)
+    served = ScoringServer(wire, max_rows=32, max_wait=0.02).start()
+    results = {}
+
+    def client(k):
+        for i in range(k, 16, 4):
+            results[i] = served.submit(body(i)).result(timeout=30)
+    threads = [threading.Thread(target=client, args=(k,)) for k in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    served.stop()
+    assert sorted(results) == list(range(16)) and served.metrics()["passes"] < 16          # bodies shared passes
+    alone = task.systemone(body(5), details=True)
+    assert results[5]["answers"] == alone["answers"] and results[5]["usage"]["input_tokens"] == alone["usage"]["input_tokens"]
+    try:
+        served.submit({"state": "x", "questions": {}})
+        raise AssertionError("a body without questions must be refused")
+    except ValueError:
+        assert wire.metrics()["refused/malformed"] == 1.0
