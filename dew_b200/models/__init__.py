@@ -13,4 +13,7 @@ def __getattr__(name):
     if name in ("KLAutoEncoder", "ViT"):
         from . import autoencoders as m
         return getattr(m, name)
+    if name in ("AutoencoderKL", "DCAE", "CausalVideoVAE", "LatentNormalization"):
+        from . import latent_autoencoders as m
+        return getattr(m, name)
     raise AttributeError(name)

@@ -45,6 +45,8 @@ _STATIC: Dict[str, Dict[str, str]] = {
         "sd3": "dew_b200.models.latent_backbones:SD3Transformer", "wan": "dew_b200.models.latent_backbones:WanTransformer",
         "edm2": "dew_b200.models.latent_backbones:EDM2UNet",
         "kl_vae": "dew_b200.models.autoencoders:KLAutoEncoder", "vit": "dew_b200.models.autoencoders:ViT",
+        "autoencoder_kl": "dew_b200.models.latent_autoencoders:AutoencoderKL", "dc_ae": "dew_b200.models.latent_autoencoders:DCAE",
+        "causal_video_vae": "dew_b200.models.latent_autoencoders:CausalVideoVAE",
     },
     "objective": {
         "lm": "dew_b200.objectives.lm:LMObjective",
