@@ -91,3 +91,15 @@ def test_route_decisions_example():
 def test_sft_chat_example():
     losses, right, answers = _load("sft_chat").main(["--steps", "150", "--device", "cpu"])
     assert losses[-1] < 0.5 * losses[0] and right >= 3 and set(answers) == {"red", "green", "blue", "pink", "grey", "gold"}
+
+
+def test_serve_decisions_example_answers_over_http():
+    one, many, metrics = _load("serve_decisions").main(["--steps", "60"])
+    assert set(one["answers"]) == {"parity", "half", "size"} and "abstained" in one["answers"]["parity"] and one["usage"]["input_tokens"] > 0
+    assert len(many) == 4 and all("answers" in m for m in many[:3]) and many[3]["reason"] == "malformed"
+    assert "dew_decide_requests" in metrics and "dew_decide_passes" in metrics
+
+
+def test_forward_only_lm_example():
+    results = _load("forward_only_lm").main(["--steps", "60", "--draws", "4"])
+    assert results["forward_only"][-1] < results["forward_only"][0] - 0.15 and results["backprop"][-1] < results["forward_only"][-1]
