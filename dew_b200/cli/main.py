@@ -1,4 +1,4 @@
-"""``dewb`` command line: ``train``, ``sweep``, ``profile``, ``inspect``, ``export``, ``data export``, ``launch``.
+"""``dewb`` command line: ``train``, ``sweep``, ``profile``, ``inspect``, ``plan``, ``export``, ``data export | analyse | shards``, ``launch``.
 
 Parity: src/dew/_cli/main.py (subcommands Train with ``--set path=value``, Profile, Inspect, Export, DataExport),
 src/dew/_cli/launch.py.  Importing this module imports no CUDA library.
@@ -124,6 +124,75 @@ def cmd_data_export(args) -> int:
     return 0
 
 
+def cmd_plan(args) -> int:
+    """Predict a recipe's training step on B200s before running it: per-family milliseconds, tokens / s, MFU and the memory the
+    layout needs (``ops.step_cost``), for the recipe's model, batch and mesh."""
+    from ..config import apply_overrides
+    from ..ops.step_cost import Transformer, transformer_step
+    cfg = apply_overrides(_load_recipe(args.recipe), args.set or [])
+    f = cfg.model.fields
+    if cfg.model.name != "causal_transformer":
+        raise SystemExit(f"the step model covers decoder-only transformers, not {cfg.model.name!r}")
+    heads = f["num_heads"]
+    mix = f.get("mixture") or {}
+    model = Transformer(features=f["emb_features"], layers=f["num_layers"], heads=heads, kv_heads=f.get("num_kv_heads") or heads,
+                        head_dim=f.get("head_dim") or f["emb_features"] // heads, mlp=f.get("mlp_features") or 4 * f["emb_features"],
+                        vocab=f["vocab_size"], experts=mix.get("experts", 0), top_k=mix.get("top_k", 0),
+                        expert_mlp=mix.get("expert_features", 0), shared_experts=1 if mix.get("shared_features") else 0,
+                        tied=bool(f.get("tie_embeddings", True)))
+    m = cfg.trainer.mesh
+    world = args.devices
+    micro = max(1, cfg.data.batch // max(1, cfg.trainer.microbatches or 1))
+    out = transformer_step(model, sequences=cfg.data.batch, seq_len=cfg.data.seq_len, microbatch=micro, world=world, tensor=max(1, m.tensor),
+                           expert=max(1, m.expert), remat=bool(f.get("remat")), mx_experts=bool(mix))
+    out["parameters"] = model.params
+    print(json.dumps(out, indent=1, default=float))
+    return 0 if out["fits"] else 1
+
+
+def _rows_of(path: str):
+    from ..data import JsonLines, TarShards
+    p = Path(path)
+    if p.is_dir():
+        return TarShards(str(p))
+    if p.suffix in (".jsonl", ".json"):
+        return JsonLines(str(p))
+    return ({"text": line} for line in p.read_text().splitlines() if line.strip())
+
+
+def cmd_data_analyse(args) -> int:
+    """Length, packing, vocabulary and duplicate statistics of a corpus (a text file, a JSON-lines file or a shard directory)."""
+    from ..data import ByteTokenizer
+    from ..data.analysis import analyse
+    report = analyse(_rows_of(args.source), ByteTokenizer(), seq_len=args.seq_len, text_key=args.text_key, sample=args.sample)
+    print(json.dumps(report, indent=1))
+    return 0
+
+
+def cmd_data_shards(args) -> int:
+    """Write a JSON-lines file as tar shards: each record's fields become a sample's members (strings as .txt-like text, the rest as
+    .json), keyed by the record's ``id`` / ``key`` where it has one."""
+    from ..data.shards import write_shards
+
+    def samples():
+        for i, row in enumerate(_rows_of(args.source)):
+            out = {"__key__": str(row.get("id", row.get("key", f"{i:09d}")))}
+            rest = {}
+            for k, v in row.items():
+                if k in ("id", "key"):
+                    continue
+                if isinstance(v, str) and k in ("text", "caption", "txt"):
+                    out["txt"] = v
+                else:
+                    rest[k] = v
+            if rest:
+                out["json"] = rest
+            yield out
+    index = write_shards(samples(), args.out, samples_per_shard=args.samples_per_shard)
+    print(json.dumps({"shards": len(index["shards"]), "samples": index["samples"], "directory": args.out}))
+    return 0
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if argv and argv[0] == "launch":
@@ -141,6 +210,12 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     p = sub.add_parser("profile"); p.add_argument("--only", default="gemm,rows,attention"); p.add_argument("--out", default=None); p.set_defaults(fn=cmd_profile)
     d = sub.add_parser("data"); ds = d.add_subparsers(dest="data_command", required=True)
     de = ds.add_parser("export"); de.add_argument("text"); de.add_argument("out"); de.set_defaults(fn=cmd_data_export)
+    da = ds.add_parser("analyse"); da.add_argument("source"); da.add_argument("--seq-len", type=int, default=2048)
+    da.add_argument("--text-key", default="text"); da.add_argument("--sample", type=int, default=10000); da.set_defaults(fn=cmd_data_analyse)
+    dh = ds.add_parser("shards"); dh.add_argument("source"); dh.add_argument("out"); dh.add_argument("--samples-per-shard", type=int, default=1000)
+    dh.set_defaults(fn=cmd_data_shards)
+    pl = sub.add_parser("plan"); pl.add_argument("recipe"); pl.add_argument("--set", action="append"); pl.add_argument("--devices", type=int, default=8)
+    pl.set_defaults(fn=cmd_plan)
     args = ap.parse_args(argv)
     return args.fn(args)
 

@@ -121,3 +121,23 @@ def test_records_rebuild_objects_and_refuse_unknown_names_and_fields():
     assert "toy_model" in R.registry("model") and R.lookup("toy_model") is Toy
     with pytest.raises(ValueError, match="already"):
         R.register("toy_model", "model")(object)
+
+
+def test_cli_plan_and_data_tools(tmp_path, capsys):
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    assert cli.main(["plan", os.path.join(root, "recipes", "lm", "train.py"), "--devices", "8", "--set", "trainer.mesh.fsdp=8"]) == 0
+    plan = json.loads(capsys.readouterr().out)
+    assert plan["fits"] and plan["tokens_per_s"] > 0 and 0.2e9 < plan["parameters"] < 0.6e9 and set(plan["by_family"]) >= {"gemm", "attention", "head", "update"}
+    rows = tmp_path / "rows.jsonl"
+    rows.write_text("\n".join(json.dumps({"id": f"r{i}", "text": f"sample text number {i % 3}", "label": i % 2}) for i in range(12)) + "\n")
+    assert cli.main(["data", "analyse", str(rows), "--seq-len", "32"]) == 0
+    report = json.loads(capsys.readouterr().out)
+    assert report["sampled"] == 12 and report["duplicates"]["exact_duplicate_share"] == 0.75 and report["packing"]["windows"] >= 6
+    assert cli.main(["data", "shards", str(rows), str(tmp_path / "shards"), "--samples-per-shard", "5"]) == 0
+    assert json.loads(capsys.readouterr().out) == {"shards": 3, "samples": 12, "directory": str(tmp_path / "shards")}
+    from dew_b200.data import TarShards
+    got = list(TarShards(str(tmp_path / "shards")))
+    assert got[4]["__key__"] == "r4" and got[4]["txt"] == "sample text number 1" and got[4]["json"] == {"label": 0}
+    assert cli.main(["data", "analyse", str(tmp_path / "shards"), "--text-key", "txt", "--seq-len", "32"]) == 0
+    assert json.loads(capsys.readouterr().out)["sampled"] == 12
