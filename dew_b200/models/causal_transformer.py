@@ -65,7 +65,7 @@ class TransformerConfig:
     attn_softcap: float = 0.0
     logit_softcap: float = 0.0
     window: Optional[int] = None
-    layer_types: Optional[Sequence[str]] = None      # per layer: attention | local | gdn | mamba2
+    layer_types: Optional[Sequence[str]] = None      # per layer: attention | local | gdn | mamba2 | mamba | mamba3 | kda | mla | lightning | differential | forgetting
     mixture: Optional[Mixture] = None
     mixer_options: Dict[str, Any] = field(default_factory=dict)
     remat: bool = False
@@ -90,7 +90,10 @@ class TransformerConfig:
         return [pattern[i % len(pattern)] for i in range(self.num_layers)]
 
 
-def _mixer(cfg: TransformerConfig, kind: str, dtype, device) -> nn.Module:
+ROTARY_KINDS = ("attention", "local", "mla", "differential", "forgetting")      # mixers called with the rotary tables and positions
+
+
+def _mixer(cfg: TransformerConfig, kind: str, dtype, device, index: int = 0) -> nn.Module:
     if kind in ("attention", "local"):
         return SelfAttention(cfg.emb_features, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, qk_norm=cfg.qk_norm,
                              causal=True, window=cfg.window if kind == "local" or cfg.layer_types is None else None,
@@ -117,7 +120,13 @@ def _mixer(cfg: TransformerConfig, kind: str, dtype, device) -> nn.Module:
     if kind == "mamba3":
         from ..nn.recurrent_mixers import Mamba3
         return Mamba3(cfg.emb_features, dtype=dtype, device=device, **cfg.mixer_options)
-    raise ValueError(f"unknown layer type {kind!r}; known: attention, local, gdn, mamba2, mamba, mamba3, kda, mla, lightning")
+    if kind == "differential":
+        from ..nn.attention_variants import DifferentialAttention
+        return DifferentialAttention(cfg.emb_features, cfg.num_heads, cfg.num_kv_heads, layer=index, norm_eps=cfg.norm_eps, dtype=dtype, device=device)
+    if kind == "forgetting":
+        from ..nn.attention_variants import ForgettingAttention
+        return ForgettingAttention(cfg.emb_features, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, dtype=dtype, device=device)
+    raise ValueError(f"unknown layer type {kind!r}; known: attention, local, gdn, mamba2, mamba, mamba3, kda, mla, lightning, differential, forgetting")
 
 
 class DecoderLayer(nn.Module):
@@ -125,7 +134,7 @@ class DecoderLayer(nn.Module):
         super().__init__()
         self.kind, self.index = kind, index
         self.input_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
-        self.mixer = _mixer(cfg, kind, dtype, device)
+        self.mixer = _mixer(cfg, kind, dtype, device, index)
         self.post_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
         mix = cfg.mixture
         sparse = mix is not None and (mix.layers is None or index in mix.layers)
@@ -154,7 +163,7 @@ class DecoderLayer(nn.Module):
         output is written back by the learned connection (no fused add + norm on this path)."""
         x, ctx = self.streams[0].read(H)
         n = self.input_norm(x)
-        if self.kind in ("attention", "local", "mla"):
+        if self.kind in ROTARY_KINDS:
             a = self.mixer(n, cos, sin, positions, segment_ids, cache, self.index)
         else:
             a = self.mixer(n, segment_ids=segment_ids, cache=cache, layer=self.index)
@@ -184,7 +193,7 @@ class DecoderLayer(nn.Module):
                 n = copy_to_region(n, self.tp.group)
         else:
             n, h = self._norm(self.input_norm, h, branch)
-        if self.kind in ("attention", "local", "mla"):
+        if self.kind in ROTARY_KINDS:
             a = self.mixer(n, cos, sin, positions, segment_ids, cache, self.index)
         else:
             a = self.mixer(n, segment_ids=segment_ids, cache=cache, layer=self.index)
