@@ -46,6 +46,25 @@ class Mixture:
     topk_groups: int = 1                             # ... of which each token may use the ``topk_groups`` best (by their top-2 sum)
 
 
+@dataclass(frozen=True)
+class Loop:
+    """A looped decoder: the layers ``[first, end)`` run ``steps`` times, each pass reading the last one's output, between the layers
+    before them (run once) and the coda after them (run once on the exit).  ``exit_gate`` adds a per-token gate on every pass's
+    exit state whose hazards give the probability of stopping there (trained by ``LMObjective(exit_entropy=...)``); the passes
+    before the last ``backprop_steps`` carry no gradient.  Reference: src/dew/nn/backbones/looping.py (``Loop``)."""
+    steps: int = 2
+    first: int = 0
+    end: Optional[int] = None
+    exit_gate: bool = False
+    backprop_steps: Optional[int] = None
+
+    def __post_init__(self):
+        if self.steps < 1 or self.first < 0 or (self.end is not None and self.end <= self.first):
+            raise ValueError("a loop runs layers [first, end) at least once")
+        if self.backprop_steps is not None and not 1 <= self.backprop_steps <= self.steps:
+            raise ValueError("backprop_steps counts the last passes that carry a gradient: between 1 and steps")
+
+
 @dataclass
 class TransformerConfig:
     vocab_size: int = 32000
@@ -78,10 +97,13 @@ class TransformerConfig:
     mlp_activation: str = "silu"                      # silu (SwiGLU) | gelu_tanh (Gemma's GeGLU) | gelu
     sandwich_norm: bool = False                       # Gemma-2: every sub-layer's output is normalised before it joins the stream
     query_scale: Optional[float] = None               # softmax scale other than head_dim ** -0.5 (Gemma-2's query_pre_attn_scalar ** -0.5)
+    loop: Optional[Loop] = None                       # a block of layers run several times (a looped / recurrent-depth decoder)
 
     def __post_init__(self):
         if isinstance(self.mixture, Mapping):             # a run record (JSON) carries the mixture as a plain mapping
             self.mixture = Mixture(**self.mixture)
+        if isinstance(self.loop, Mapping):
+            self.loop = Loop(**self.loop)
 
     def kinds(self) -> List[str]:
         if self.layer_types is None:
@@ -239,6 +261,8 @@ class CausalTransformer(nn.Module):
         self.head = None if cfg.tie_embeddings else Linear(cfg.emb_features, cfg.vocab_size, axes=("embed", "vocab"),
                                                            init_std=cfg.init_std, dtype=dtype, device=device)
         self.mtp = nn.ModuleList([MTPBlock(cfg, i, dtype, device) for i in range(cfg.mtp_depth)]) if cfg.mtp_depth > 0 else None
+        self.early_exit_gate = Linear(cfg.emb_features, 1, bias=True, init_std=cfg.init_std, dtype=dtype, device=device) \
+            if cfg.loop is not None and cfg.loop.exit_gate else None
         self._rope = None
 
     def mtp_hiddens(self, hidden: torch.Tensor, tokens: torch.Tensor, segment_ids=None) -> List[torch.Tensor]:
@@ -273,7 +297,64 @@ class CausalTransformer(nn.Module):
             self._rope = ops.rope_tables(cfg.max_seq_len, hd, cfg.rope_theta, dev, cfg.rope_scaling)
         return self._rope
 
-    def hidden(self, tokens, positions=None, segment_ids=None, cache=None, train: bool = False):
+    def _finish(self, h, branch):
+        tp = getattr(self, "tp", None)
+        if tp is not None and getattr(self, "tp_training", False):
+            from ..parallel.tp import reduce_from_region
+            n, _ = self.final_norm(h, reduce_from_region(branch, tp.group))
+        elif tp is not None:
+            n, _ = tp.reduce_add_norm(branch, h, self.final_norm.weight, self.final_norm.eps)
+            n = n.clone()        # the fused all-reduce returns views of a buffer later calls reuse; what leaves the model is owned
+        else:
+            n, _ = self.final_norm(h, branch)
+        return n
+
+    def _looped(self, h, cos, sin, positions, segment_ids, cache, train, passes: bool, steps: Optional[int]):
+        """The looped trunk: returns the final-normed exit state of the last pass, or of every pass with ``passes``."""
+        cfg, loop = self.config, self.config.loop
+        if cache is not None:
+            raise NotImplementedError("a looped decoder keeps one cache per pass; decoding with a KV cache is not built for it")
+        steps = loop.steps if steps is None else steps
+        first, end = loop.first, len(self.layers) if loop.end is None else loop.end
+        remat = cfg.remat and train and torch.is_grad_enabled()
+
+        def run(layers, h, branch):
+            for layer in layers:
+                if remat:
+                    h, branch = ckpt.checkpoint(layer, h, branch, cos, sin, positions, segment_ids, None, use_reentrant=False)
+                else:
+                    h, branch = layer(h, branch, cos, sin, positions, segment_ids, None)
+            return h, branch
+
+        h, branch = run(self.layers[:first], h, None)
+        exits = []
+        for s in range(steps):
+            cut = loop.backprop_steps is not None and s < steps - loop.backprop_steps and torch.is_grad_enabled()
+            if cut:
+                with torch.no_grad():
+                    h, branch = run(self.layers[first:end], h, branch)
+                h, branch = h.detach(), (None if branch is None else branch.detach())
+            else:
+                h, branch = run(self.layers[first:end], h, branch)
+            if passes or s == steps - 1:
+                exits.append(self._finish(*run(self.layers[end:], h, branch)))
+        return exits if passes else exits[-1]
+
+    def exit_distribution(self, states: Sequence[torch.Tensor]) -> torch.Tensor:
+        """``[passes, B, S]``: the probability a token exits at each pass, from the gate's hazards on the passes' exit states
+        (``p_k = lambda_k prod_{j<k} (1 - lambda_j)``), the last pass taking the rest."""
+        if self.early_exit_gate is None:
+            raise ValueError("the model's loop has no exit gate (Loop(exit_gate=True))")
+        stay = None
+        out = []
+        for st in states[:-1]:
+            lam = torch.sigmoid(self.early_exit_gate(st).float().squeeze(-1))
+            out.append(lam if stay is None else stay * lam)
+            stay = (1 - lam) if stay is None else stay * (1 - lam)
+        out.append(torch.ones_like(states[-1][..., 0], dtype=torch.float32) if stay is None else stay)
+        return torch.stack(out)
+
+    def hidden(self, tokens, positions=None, segment_ids=None, cache=None, train: bool = False, passes: bool = False, loop_steps: Optional[int] = None):
         cfg = self.config
         h = self.embed(tokens)
         if cfg.embed_scale:
@@ -291,22 +372,17 @@ class CausalTransformer(nn.Module):
             # hyper-connections sum the streams; AltUp averages its blocks
             h = H.sum(2) if cfg.hyper_connections > 1 else H.mean(2)
             return self.final_norm(h)
+        if cfg.loop is not None:
+            return self._looped(h, cos, sin, positions, segment_ids, cache, train, passes, loop_steps)
+        if passes:
+            raise ValueError("per-pass exits need a looped decoder (TransformerConfig(loop=Loop(...)))")
         branch = None
         for layer in self.layers:
             if cfg.remat and train and torch.is_grad_enabled():
                 h, branch = ckpt.checkpoint(layer, h, branch, cos, sin, positions, segment_ids, cache, use_reentrant=False)
             else:
                 h, branch = layer(h, branch, cos, sin, positions, segment_ids, cache)
-        tp = getattr(self, "tp", None)
-        if tp is not None and getattr(self, "tp_training", False):
-            from ..parallel.tp import reduce_from_region
-            n, _ = self.final_norm(h, reduce_from_region(branch, tp.group))
-        elif tp is not None:
-            n, _ = tp.reduce_add_norm(branch, h, self.final_norm.weight, self.final_norm.eps)
-            n = n.clone()        # the fused all-reduce returns views of a buffer later calls reuse; what leaves the model is owned
-        else:
-            n, _ = self.final_norm(h, branch)
-        return n
+        return self._finish(h, branch)
 
     def logits(self, hidden):
         tp_head = getattr(self, "tp_head", None)
@@ -331,9 +407,11 @@ class CausalTransformer(nn.Module):
         return self.logits(hidden).argmax(-1)
 
     def forward(self, tokens, train: bool = False, decode: bool = False, positions=None, segment_ids=None, cache=None,
-                return_hidden: bool = False):
-        h = self.hidden(tokens, positions, segment_ids, cache, train)
-        return h if return_hidden else self.logits(h)
+                return_hidden: bool = False, passes: bool = False, loop_steps: Optional[int] = None):
+        h = self.hidden(tokens, positions, segment_ids, cache, train, passes, loop_steps)
+        if return_hidden:
+            return h
+        return [self.logits(x) for x in h] if passes else self.logits(h)
 
     def pop_aux(self) -> Dict[str, Any]:
         """Collect what the sparse layers recorded in the last forward: the balance loss (a metric and, when the

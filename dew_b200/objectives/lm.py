@@ -23,14 +23,36 @@ class LMObjective(Objective):
                  loss_role: Optional[int] = None, exit_entropy: Optional[float] = None, pass_weights=None, indexer=None, adaptation=None):
         """``samples``: preview settings ``{"prompt": [...token ids or text], "max_new_tokens": n, "sampling": Sampling}``;
         ``loss_role``: score only the targets whose ``batch["roles"]`` entry equals this role id (chat fine-tuning on the
-        assistant's tokens).  ``exit_entropy`` / ``pass_weights`` (per-pass exits of a looped decoder), ``indexer`` (training a
-        sparse-attention indexer beside dense attention) and ``adaptation`` (in-context level stepping) name reference
-        features whose model-side parts are not in this library: asking for them raises."""
-        unsupported = {"exit_entropy": exit_entropy, "pass_weights": pass_weights, "indexer": indexer, "adaptation": adaptation}
+        assistant's tokens).
+
+        ``exit_entropy`` (beta) trains a looped decoder's exit gate: each token's loss is its cross entropy at every pass weighted
+        by the probability it exits there (from the gate's hazards, the last pass taking the rest) less beta times that
+        distribution's entropy; every pass's exit state is scored through the head.  ``pass_weights`` trains every pass count at
+        once: ``"mean"`` or one weight per pass summing to one, each pass's term its own cross entropy (no gate needed).  The two
+        are refused together.  Reports: ``ce`` (the last pass's), ``exit_ce``, ``exit_entropy`` / ``pass_<k>_ce``.
+
+        ``indexer`` (training a sparse-attention indexer beside dense attention inside the decoder) and ``adaptation`` (in-context
+        level stepping) name reference features whose model-side parts are not in this library: asking for them raises."""
+        unsupported = {"indexer": indexer, "adaptation": adaptation}
         asked = [k for k, v in unsupported.items() if v is not None]
         if asked:
-            raise NotImplementedError(f"LMObjective({', '.join(asked)}=...) needs a looped decoder / attention indexer / in-context "
+            raise NotImplementedError(f"LMObjective({', '.join(asked)}=...) needs an attention indexer inside the decoder / an in-context "
                                       "decoder, which this library does not provide")
+        loop = getattr(getattr(model, "config", None), "loop", None)
+        if exit_entropy is not None:
+            if pass_weights is not None:
+                raise ValueError("the exit objective weighs the passes its own way: give exit_entropy or pass_weights, not both")
+            if loop is None or not loop.exit_gate or not 0 <= exit_entropy < float("inf"):
+                raise ValueError("exit_entropy weighs the entropy of a looped decoder's exit distribution: it needs a model with "
+                                 f"Loop(exit_gate=True) and a finite non-negative weight, got {exit_entropy}")
+        if pass_weights is not None:
+            if loop is None:
+                raise ValueError("pass_weights train the passes of a looped decoder: the model has no loop")
+            if pass_weights != "mean":
+                pass_weights = tuple(float(w) for w in pass_weights)
+                if len(pass_weights) != loop.steps or any(w < 0 for w in pass_weights) or abs(sum(pass_weights) - 1) > 1e-6:
+                    raise ValueError(f"pass_weights are 'mean' or {loop.steps} non-negative weights summing to one")
+        self.exit_entropy, self.pass_weights = exit_entropy, pass_weights
         self.samples, self.loss_role = samples, loss_role
         self.model = model
         self.seq_len = seq_len
@@ -69,7 +91,50 @@ class LMObjective(Objective):
             targets[batch["roles"][:, 1:] != self.loss_role] = -100
         return inputs, targets, seg_in
 
+    def _pass_losses(self, variables, batch, step: Step):
+        """The looped decoder's objectives: every pass's exit state scored through the head, per token."""
+        import torch.nn.functional as F
+        inputs, targets, seg = self._targets(batch)
+        states = self.apply(variables, inputs, train=step.train, segment_ids=seg, return_hidden=True, passes=True)
+        if variables is None:
+            w = self.model.head_weight()
+        else:
+            from ..utils.trees import variables_for_call
+            named = variables_for_call(self.model, variables)
+            w = named["embed.weight"] if self.model.head is None else named["head.weight"]
+        cap = getattr(self.model.config, "logit_softcap", 0.0)
+        scored = (targets != -100)
+        mass = scored.sum().to(torch.float32)
+        ces = []
+        for st in states:
+            logits = ops.linear(st, w).float()
+            if cap > 0:
+                logits = cap * torch.tanh(logits / cap)
+            ces.append(F.cross_entropy(logits.reshape(-1, logits.shape[-1]), targets.reshape(-1), ignore_index=-100, reduction="none").reshape(targets.shape))
+        ce = torch.stack(ces)                                            # [passes, B, S]
+        metrics = {"ce": Ratio((ce[-1].detach() * scored).sum(), mass), "perplexity": Exponentiated(Ratio((ce[-1].detach() * scored).sum(), mass)),
+                   "tokens": Ratio(mass, torch.ones((), device=mass.device))}
+        if self.exit_entropy is not None:
+            p = self.model.exit_distribution(states)                    # [passes, B, S]
+            expected = (p * ce).sum(0)
+            entropy = -(p * torch.log(p.clamp_min(1e-12))).sum(0)
+            total = ((expected - self.exit_entropy * entropy) * scored).sum()
+            depth = (p * torch.arange(1, len(states) + 1, device=p.device, dtype=p.dtype)[:, None, None]).sum(0)
+            metrics.update(exit_ce=Ratio((expected.detach() * scored).sum(), mass), exit_entropy=Ratio((entropy.detach() * scored).sum(), mass),
+                           exit_depth=Ratio((depth.detach() * scored).sum(), mass))
+        else:
+            k = len(states)
+            weights = [1.0 / k] * k if self.pass_weights == "mean" else list(self.pass_weights)
+            total = sum(wk * (ce[i] * scored).sum() for i, wk in enumerate(weights) if wk > 0)
+            metrics.update({f"pass_{i + 1}_ce": Ratio((ce[i].detach() * scored).sum(), mass) for i in range(k)})
+        if self.z_loss:
+            logits = ops.linear(states[-1], w).float()
+            total = total + self.z_loss * ((torch.logsumexp(logits, -1) ** 2) * scored).sum()
+        return Ratio(total, mass), Aux(metrics=metrics)
+
     def loss(self, variables, batch: Mapping[str, torch.Tensor], step: Step):
+        if self.exit_entropy is not None or self.pass_weights is not None:
+            return self._pass_losses(variables, batch, step)
         inputs, targets, seg = self._targets(batch)
         hidden = self.apply(variables, inputs, train=step.train, segment_ids=seg, return_hidden=True)
         B, S, d = hidden.shape

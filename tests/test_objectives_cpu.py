@@ -312,9 +312,58 @@ def test_fit_cooldown_summaries_loss_role_and_preview():
     assert trainer.optimizer.schedule(9) == pytest.approx(1e-2)                    # the trunk schedule is back after the fit
     art = obj.preview(state.variables, key=0)
     assert len(art.completions) == 1 and len(art.completions[0].split()) == 4
+    with pytest.raises(ValueError):
+        LMObjective(model, 8, exit_entropy=0.1)                                    # no loop to gate
     with pytest.raises(NotImplementedError):
-        LMObjective(model, 8, exit_entropy=0.1)
+        LMObjective(model, 8, indexer=object())
     assert dew.Cooldown(0, 10, 0.0, "sqrt").factor(10) == 0.0 and dew.Cooldown(5, 10).factor(3) == 1.0
+
+
+def test_looped_decoder_trains_its_passes_and_its_exit_gate():
+    from dew_b200.models.causal_transformer import Loop
+    from dew_b200.objectives.lm import LMObjective
+    torch.manual_seed(0)
+    mk = lambda **kw: CausalTransformer(vocab_size=24, emb_features=32, num_layers=3, num_heads=2, head_dim=16, mlp_features=64, max_seq_len=16,
+                                        qk_norm=False, loop=Loop(steps=3, first=1, end=2, **kw))
+    tokens = torch.randint(0, 24, (16, 9))
+    model = mk(exit_gate=True)
+    outs = model(tokens[:, :-1], passes=True)
+    assert len(outs) == 3 and torch.allclose(model(tokens[:, :-1]), outs[-1]) and torch.allclose(model(tokens[:, :-1], loop_steps=2), outs[1])
+    p = model.exit_distribution(model(tokens[:, :-1], return_hidden=True, passes=True))
+    assert p.shape == (3, 16, 8) and torch.allclose(p.sum(0), torch.ones(16, 8), atol=1e-6)
+    # the exit objective: expected cross entropy under the exit distribution less beta times its entropy
+    obj = LMObjective(model, 8, exit_entropy=0.05)
+    stats, aux = obj.loss(None, {"tokens": tokens}, dew.Step(train=True))
+    m = {k: float(v.value()) for k, v in aux.metrics.items()}
+    assert float(stats.value()) == pytest.approx(m["exit_ce"] - 0.05 * m["exit_entropy"], rel=1e-5) and 1.0 <= m["exit_depth"] <= 3.0
+    stats.value().backward()
+    assert model.early_exit_gate.weight.grad is not None and float(model.early_exit_gate.weight.grad.abs().sum()) > 0
+    # pass weights: each pass's own cross entropy, weighed; all weight on the last pass is the plain objective
+    plain = mk()
+    last_only = LMObjective(plain, 8, pass_weights=(0.0, 0.0, 1.0))
+    a, _ = last_only.loss(None, {"tokens": tokens}, dew.Step(train=True))
+    b, _ = LMObjective(plain, 8).loss(None, {"tokens": tokens}, dew.Step(train=True))
+    assert float(a.value()) == pytest.approx(float(b.value()), rel=1e-4)
+    mean = LMObjective(plain, 8, pass_weights="mean")
+    st, aux = mean.loss(None, {"tokens": tokens}, dew.Step(train=True))
+    per = [float(aux.metrics[f"pass_{i}_ce"].value()) for i in (1, 2, 3)]
+    assert float(st.value()) == pytest.approx(sum(per) / 3, rel=1e-5)
+    tr = dew.Trainer(mean, dew.OptimConfig(learning_rate=3e-3, weight_decay=0.0), tracker=(t := dew.MemoryTracker()))
+    tr.fit([{"tokens": tokens}] * 40, steps=40, log_every=10)
+    assert t.rows[-1]["pass_1_ce"] < 0.8 * per[0] and t.rows[-1]["loss"] < t.rows[0]["loss"]          # every pass count learns
+    # the passes before the last backprop_steps carry no gradient
+    cut = mk(backprop_steps=1)
+    LMObjective(cut, 8).loss(None, {"tokens": tokens}, dew.Step(train=True))[0].value().backward()
+    assert cut.layers[0].mlp.gate_up_proj.weight.grad is None and cut.layers[1].mlp.gate_up_proj.weight.grad is not None
+    with pytest.raises(ValueError):
+        LMObjective(plain, 8, pass_weights=(0.5, 0.5))
+    with pytest.raises(ValueError):
+        LMObjective(model, 8, exit_entropy=0.1, pass_weights="mean")
+    with pytest.raises(NotImplementedError):
+        from dew_b200.nn.kv_cache import KVCache, KVStore
+        model(tokens[:, :-1], cache=object())
+    with pytest.raises(ValueError):
+        Loop(steps=2, backprop_steps=3)
 
 
 def test_node_perturbation_estimates_the_gradient_and_trains_without_backprop():
