@@ -21,6 +21,8 @@ from typing import Any, Callable, Dict, Iterable, Iterator, List, Mapping, Optio
 
 import torch
 
+from ..telemetry.trace import TRACER
+
 from ..objectives.base import Aux, Objective, Ratio, Step, pool
 from ..optim import OptimConfig, Optimizer, ema_update
 from ..utils import keys as K
@@ -393,7 +395,8 @@ class Trainer:
             if self.custom_step is not None:
                 state, m = self.custom_step(self, state, batch)
             else:
-                state, m = eng.step(state, batch)
+                with TRACER.span("train_step", step=state.step):
+                    state, m = eng.step(state, batch)
             if prof is not None and state.step >= self.profile.start + self.profile.steps:
                 prof.__exit__(None, None, None)
                 self.profile_report = prof.key_averages().table(row_limit=20)
