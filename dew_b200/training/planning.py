@@ -77,11 +77,21 @@ class FitSearch:
         peak = torch.cuda.max_memory_allocated(self.device)
         return Trial(plan, peak, peak <= self.limit_fraction * self.capacity)
 
-    def run(self, trial: Optional[Callable[[Plan], None]] = None, plans: Optional[Sequence[Plan]] = None) -> Plan:
-        for plan in plans or ladder(self.rows, self.allow_remat):
+    def run(self, trial: Optional[Callable[[Plan], None]] = None, plans: Optional[Sequence[Plan]] = None, remembered: Optional["PlanRecords"] = None,
+            key: Optional[str] = None) -> Plan:
+        """``remembered`` / ``key``: plans chosen by earlier runs of the same step (same model, batch and device): the search starts at
+        the rung an earlier run settled on instead of at the top of the ladder, and records where this one settles."""
+        rungs = list(plans or ladder(self.rows, self.allow_remat))
+        if remembered is not None and key is not None:
+            earlier = remembered.get(key)
+            if earlier is not None and earlier in rungs:
+                rungs = rungs[rungs.index(earlier):]                      # a rung that did not fit before is not tried again
+        for plan in rungs:
             t = self._run_trial(plan, trial)
             self.trials.append(t)
             if t.fits:
+                if remembered is not None and key is not None:
+                    remembered.put(key, plan, t.peak_bytes)
                 return plan
         raise NoPlanFits(f"no plan fits {self.limit_fraction:.0%} of {self.capacity / 2**30:.1f} GiB: " +
                          ", ".join(f"{t.plan.microbatch}{'r' if t.plan.remat else ''}" for t in self.trials))
@@ -92,3 +102,49 @@ class FitSearch:
             peak = "oom" if t.peak_bytes is None else f"{t.peak_bytes / 2**30:.2f}"
             rows.append(f"{t.plan.microbatch:>10} {str(t.plan.remat):>5} {peak:>9} {t.fits}")
         return "\n".join(rows)
+
+
+class PlanRecords:
+    """The plan each step settled on, kept in a JSON file beside a run's caches, keyed by a digest of what determines the step's
+    memory (``step_key``): a later run of the same step starts its search there, as a resumed run starts at its checkpoint."""
+
+    def __init__(self, path: str):
+        self.path = path
+
+    def _read(self) -> dict:
+        import json
+        import os
+        if not os.path.exists(self.path):
+            return {}
+        try:
+            with open(self.path) as f:
+                return json.load(f)
+        except (OSError, ValueError):
+            return {}
+
+    def get(self, key: str) -> Optional[Plan]:
+        rec = self._read().get(key)
+        return None if rec is None else Plan(int(rec["microbatch"]), bool(rec["remat"]))
+
+    def put(self, key: str, plan: Plan, peak_bytes: Optional[int] = None) -> None:
+        import json
+        import os
+        data = self._read()
+        data[key] = {"microbatch": plan.microbatch, "remat": plan.remat, "peak_bytes": peak_bytes}
+        os.makedirs(os.path.dirname(os.path.abspath(self.path)), exist_ok=True)
+        with open(self.path + ".tmp", "w") as f:
+            json.dump(data, f, indent=1)
+        os.replace(self.path + ".tmp", self.path)
+
+
+def step_key(model: torch.nn.Module, batch_shape: Sequence[int], dtype: str = "bfloat16", device: Optional[str] = None, extra: str = "") -> str:
+    """A digest of what a step's memory depends on: the parameters' names, shapes and dtypes, the batch's shape, the compute dtype
+    and the device."""
+    import hashlib
+    h = hashlib.sha256()
+    for n, p in model.named_parameters():
+        h.update(f"{n}:{tuple(p.shape)}:{p.dtype};".encode())
+    if device is None:
+        device = torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu"
+    h.update(f"|{tuple(batch_shape)}|{dtype}|{device}|{extra}".encode())
+    return h.hexdigest()[:20]

@@ -51,6 +51,25 @@ def test_fit_search_walks_the_ladder():
         FitSearch(2, capacity_bytes=8 * gib, measure=cost).run()
 
 
+def test_fit_search_starts_where_an_earlier_run_settled(tmp_path):
+    import torch
+    from dew_b200.training.planning import PlanRecords, step_key
+    gib = 1 << 30
+    cost = lambda p: 10 * gib + p.microbatch * 3 * gib // (3 if p.remat else 1)
+    records = PlanRecords(str(tmp_path / "cache" / "plans.json"))
+    model = torch.nn.Linear(4, 4)
+    key = step_key(model, (8, 128), device="B200")
+    assert key == step_key(torch.nn.Linear(4, 4), (8, 128), device="B200") != step_key(model, (8, 256), device="B200") != step_key(torch.nn.Linear(4, 5), (8, 128), device="B200")
+    first = FitSearch(8, capacity_bytes=16 * gib, limit_fraction=0.9, measure=cost)
+    assert first.run(remembered=records, key=key) == Plan(4, True) and len(first.trials) == 4
+    later = FitSearch(8, capacity_bytes=16 * gib, limit_fraction=0.9, measure=cost)
+    assert later.run(remembered=records, key=key) == Plan(4, True) and len(later.trials) == 1          # no rung above it is tried again
+    assert records.get("other") is None and records.get(key) == Plan(4, True)
+    # a remembered plan that no longer fits (a smaller device) walks on down from there
+    small = FitSearch(8, capacity_bytes=13 * gib, limit_fraction=0.9, measure=cost)
+    assert small.run(remembered=records, key=key) == Plan(1, True) and small.trials[0].plan == Plan(4, True)
+
+
 def test_pause_ends_the_run_at_a_fraction_and_a_resume_goes_on(tmp_path):
     import dew_b200 as dew
     from dew_b200.models import CausalTransformer
