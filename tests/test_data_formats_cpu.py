@@ -142,3 +142,46 @@ def test_video_clips_stride_padding_and_keys():
     assert a["clip"].shape == (4, 2, 2, 3) and int(a["first_frame"]) == int(b["first_frame"])
     many = {int(Clips(length=4)({"video": video, "id": f"v{i}"})["first_frame"]) for i in range(40)}
     assert len(many) > 5
+
+
+def test_rl_prompts_and_synthesised_training_rows(tmp_path):
+    import json
+    from dew_b200.data.prompts import Prompts, decode_column
+    from dew_b200.data.synthesis import Sample, best_of_n, dpo_rows, preference_pairs, scored_samples, sft_rows, write_records
+    from dew_b200.data import ByteTokenizer
+    tok = ByteTokenizer()
+    rows = [{"prompt": "2+2=", "data_source": "math", "reward_model": {"ground_truth": "4"}, "extra_info": {"split": "train"}},
+            {"prompt": [5, 6, 7], "ground_truth": "x"},
+            {"prompt": "a very long prompt " * 10}]
+    ds = Prompts(rows, tok, max_prompt_len=16, column_width=32)
+    first = ds._get(0)
+    n = int(first["prompt_length"])
+    assert first["prompt"].shape == (16,) and first["prompt"][-n:].tolist() == list(tok.encode("2+2=")) and np.all(first["prompt"][:-n] == 0)
+    assert decode_column(first["ground_truth"]) == "4" and decode_column(first["data_source"]) == "math" and json.loads(decode_column(first["extra_info"])) == {"split": "train"}
+    assert ds._get(1)["prompt"][-3:].tolist() == [5, 6, 7] and decode_column(ds._get(1)["ground_truth"]) == "x" and decode_column(ds._get(1)["data_source"]) == ""
+    long = ds._get(2)
+    assert int(long["prompt_length"]) == 16 and long["prompt"].tolist() == list(tok.encode("a very long prompt " * 10))[-16:]          # keeps its tail
+    batch = next(iter(ds.batched(2)))
+    assert batch["prompt"].shape == (2, 16) and batch["ground_truth"].shape == (2, 32)
+    path = tmp_path / "p.jsonl"
+    path.write_text("\n".join(json.dumps(r) for r in rows))
+    assert len(Prompts(str(path), tok, max_prompt_len=8)) == 3
+    # samples -> best-of-n rows and preference pairs
+    gen = lambda prompts, k: [[[p[0], d] for d in range(k)] for p in prompts]
+    reward = lambda p, c: float(c[1] == p[0] % 3) + 0.1 * (c[1] == 0)
+    samples = scored_samples(gen, [[3], [4], [8]], 3, reward)
+    assert len(samples) == 9 and samples[4].index == 1 and samples[4].draw == 1
+    best = best_of_n(samples, minimum=1.0)
+    assert [(s.index, s.completion[1]) for s in best] == [(0, 0), (1, 1), (2, 2)]
+    pairs = preference_pairs(samples, margin=0.5)
+    assert len(pairs) == 3 and all(a.reward - b.reward > 0.5 and a.index == b.index for a, b in pairs)
+    more = preference_pairs(samples, margin=0.05, per_prompt=2)
+    assert len(more) >= 3 and all(len({a.draw for a, b in more if a.index == i}) == len([1 for a, b in more if a.index == i]) for i in range(3))
+    sft = sft_rows(best, seq_len=5)
+    assert sft["tokens"].shape == (3, 6) and sft["loss_mask"][0].tolist() == [0, 1, 1, 0, 0, 0]
+    dpo = dpo_rows(pairs, seq_len=5)
+    assert dpo["chosen"].shape == dpo["rejected"].shape == (3, 6) and np.array_equal(dpo["chosen"][:, 0], dpo["rejected"][:, 0])
+    assert write_records(str(tmp_path / "out" / "pairs.jsonl"), pairs, {"generator": "toy", "n": 3}) == 3
+    lines = (tmp_path / "out" / "pairs.jsonl").read_text().splitlines()
+    assert json.loads(lines[0]) == {"provenance": {"generator": "toy", "n": 3}} and set(json.loads(lines[1])) >= {"prompt", "chosen", "rejected", "chosen_reward"}
+    assert best_of_n([Sample((1,), (2, 3), 1.0, 0, 0), Sample((1,), (2,), 1.0, 0, 1)])[0].draw == 1          # a tie goes to the shorter completion
