@@ -217,3 +217,44 @@ def test_scoring_server_batches_requests_from_threads_and_keeps_refusals_apart()
         raise AssertionError("a body without questions must be refused")
     except ValueError:
         assert wire.metrics()["refused/malformed"] == 1.0
+
+
+def test_completion_service_speaks_the_openai_shapes_and_streams():
+    import json
+    import urllib.error
+    import urllib.request
+    from dew_b200.data import ByteTokenizer
+    from dew_b200.inference.http import CompletionService
+    torch.manual_seed(0)
+    m = CausalTransformer(vocab_size=260, emb_features=32, num_layers=2, num_heads=4, num_kv_heads=2, mlp_features=64, max_seq_len=128, tie_embeddings=True).eval()
+    server = Server(m, slots=4, capacity=64, kv_cache=KVCache(page_size=8), chunk=16, tokenizer=ByteTokenizer())
+    with CompletionService(server, name="tiny") as svc:
+        base = f"http://{svc.address[0]}:{svc.address[1]}"
+
+        def post(path, body):
+            req = urllib.request.Request(base + path, data=json.dumps(body).encode(), method="POST")
+            with urllib.request.urlopen(req, timeout=60) as r:
+                return r.read()
+        out = json.loads(post("/v1/completions", {"prompt": "hello", "max_tokens": 5, "temperature": 0}))
+        prompt_ids = ByteTokenizer().encode("hello")
+        ref = generate(m, None, [list(prompt_ids)], 5, sampling=Sampling(temperature=0.0))
+        want = ref.tokens[0, len(prompt_ids): int(ref.lengths[0])].tolist()
+        assert out["object"] == "text_completion" and out["model"] == "tiny" and out["choices"][0]["token_ids"] == want
+        assert out["usage"] == {"prompt_tokens": len(prompt_ids), "completion_tokens": 5, "total_tokens": len(prompt_ids) + 5} and out["choices"][0]["finish_reason"] == "length"
+        by_ids = json.loads(post("/v1/completions", {"prompt": list(prompt_ids), "max_tokens": 5, "temperature": 0}))
+        assert by_ids["choices"][0]["token_ids"] == want
+        chat = json.loads(post("/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3, "temperature": 0}))
+        assert chat["object"] == "chat.completion" and chat["choices"][0]["message"]["role"] == "assistant" and len(chat["choices"][0]["token_ids"]) == 3
+        stream = post("/v1/completions", {"prompt": "hello", "max_tokens": 5, "temperature": 0, "stream": True}).decode()
+        chunks = [json.loads(l[6:]) for l in stream.splitlines() if l.startswith("data: {")]
+        assert [c["choices"][0]["token_ids"][0] for c in chunks[:-1]] == want and chunks[-1]["choices"][0]["finish_reason"] == "length" and "data: [DONE]" in stream
+        try:
+            post("/v1/completions", {"prompt": "x" * 100, "max_tokens": 50})
+            raise AssertionError("a prompt past the row capacity must be refused")
+        except urllib.error.HTTPError as e:
+            assert e.code == 400 and "capacity" in json.loads(e.read())["error"]["message"]
+        with urllib.request.urlopen(base + "/v1/models", timeout=10) as r:
+            assert json.loads(r.read())["data"][0]["id"] == "tiny"
+        with urllib.request.urlopen(base + "/metrics", timeout=10) as r:
+            metrics = r.read().decode()
+        assert "dew_serving_requests_total 4" in metrics and "dew_serving_completion_tokens_total 18" in metrics
