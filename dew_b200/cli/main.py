@@ -1,4 +1,4 @@
-"""``dewb`` command line: ``train``, ``sweep``, ``profile``, ``inspect``, ``plan``, ``export``, ``data export | analyse | shards``, ``launch``.
+"""``dewb`` command line: ``train``, ``sweep``, ``profile``, ``inspect``, ``plan``, ``serve``, ``export``, ``data export | analyse | shards``, ``launch``.
 
 Parity: src/dew/_cli/main.py (subcommands Train with ``--set path=value``, Profile, Inspect, Export, DataExport),
 src/dew/_cli/launch.py.  Importing this module imports no CUDA library.
@@ -193,6 +193,31 @@ def cmd_data_shards(args) -> int:
     return 0
 
 
+def cmd_serve(args) -> int:
+    """Serve a run's language model over HTTP (``/v1/completions``, ``/v1/chat/completions``, ``/metrics``)."""
+    import time
+
+    import torch
+
+    from ..inference import Server, pipeline
+    from ..inference.http import CompletionService
+    from ..nn.kv_cache import KVCache
+    task = pipeline(args.checkpoint)
+    if torch.cuda.is_available() and not args.cpu:
+        task.model.cuda()
+    server = Server.from_task(task, slots=args.slots, capacity=args.capacity, kv_cache=KVCache(page_size=args.page_size), host_pages=args.host_pages,
+                              cuda_graph=torch.cuda.is_available() and not args.cpu)
+    with CompletionService(server, name=args.name or Path(args.checkpoint).name, host=args.host, port=args.port) as service:
+        print(json.dumps({"serving": f"http://{service.address[0]}:{service.address[1]}", "model": service.name}), flush=True)
+        began = time.monotonic()
+        try:
+            while args.max_seconds is None or time.monotonic() - began < args.max_seconds:
+                time.sleep(0.2)
+        except KeyboardInterrupt:
+            pass
+    return 0
+
+
 def main(argv: Optional[Sequence[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     if argv and argv[0] == "launch":
@@ -214,6 +239,10 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     da.add_argument("--text-key", default="text"); da.add_argument("--sample", type=int, default=10000); da.set_defaults(fn=cmd_data_analyse)
     dh = ds.add_parser("shards"); dh.add_argument("source"); dh.add_argument("out"); dh.add_argument("--samples-per-shard", type=int, default=1000)
     dh.set_defaults(fn=cmd_data_shards)
+    sv = sub.add_parser("serve"); sv.add_argument("checkpoint"); sv.add_argument("--host", default="127.0.0.1"); sv.add_argument("--port", type=int, default=8000)
+    sv.add_argument("--slots", type=int, default=64); sv.add_argument("--capacity", type=int, default=2048); sv.add_argument("--page-size", type=int, default=16)
+    sv.add_argument("--host-pages", type=int, default=0); sv.add_argument("--name", default=None); sv.add_argument("--cpu", action="store_true")
+    sv.add_argument("--max-seconds", type=float, default=None); sv.set_defaults(fn=cmd_serve)
     pl = sub.add_parser("plan"); pl.add_argument("recipe"); pl.add_argument("--set", action="append"); pl.add_argument("--devices", type=int, default=8)
     pl.set_defaults(fn=cmd_plan)
     args = ap.parse_args(argv)

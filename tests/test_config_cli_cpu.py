@@ -141,3 +141,30 @@ def test_cli_plan_and_data_tools(tmp_path, capsys):
     assert got[4]["__key__"] == "r4" and got[4]["txt"] == "sample text number 1" and got[4]["json"] == {"label": 0}
     assert cli.main(["data", "analyse", str(tmp_path / "shards"), "--text-key", "txt", "--seq-len", "32"]) == 0
     assert json.loads(capsys.readouterr().out)["sampled"] == 12
+
+
+def test_cli_serve_answers_completions_from_a_run(tmp_path, capsys):
+    import threading
+    import time
+    import urllib.request
+    recipe = _recipe(tmp_path, steps=2, log_every=2, checkpoint_dir=str(tmp_path / "run"))
+    assert cli.main(["train", str(recipe), "--cpu"]) == 0
+    capsys.readouterr()
+    result = {}
+    t = threading.Thread(target=lambda: result.setdefault("code", cli.main(["serve", str(tmp_path / "run"), "--cpu", "--port", "0", "--slots", "2",
+                                                                               "--capacity", "16", "--page-size", "4", "--max-seconds", "6"])))
+    t.start()
+    address = None
+    for _ in range(100):
+        time.sleep(0.1)
+        out = capsys.readouterr().out
+        if "serving" in out:
+            address = json.loads(out.strip().splitlines()[-1])["serving"]
+            break
+    assert address is not None
+    req = urllib.request.Request(address + "/v1/completions", data=json.dumps({"prompt": "hi", "max_tokens": 3, "temperature": 0}).encode(), method="POST")
+    with urllib.request.urlopen(req, timeout=30) as r:
+        body = json.loads(r.read())
+    assert body["usage"]["completion_tokens"] == 3 and body["model"] == "run"
+    t.join(timeout=30)
+    assert result.get("code") == 0
