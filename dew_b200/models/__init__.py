@@ -16,4 +16,7 @@ def __getattr__(name):
     if name in ("AutoencoderKL", "DCAE", "CausalVideoVAE", "LatentNormalization"):
         from . import latent_autoencoders as m
         return getattr(m, name)
+    if name in ("VisionLanguageModel", "AudioEncoder", "Projector", "log_mel"):
+        from . import multimodal as m
+        return getattr(m, name)
     raise AttributeError(name)

@@ -354,9 +354,12 @@ class CausalTransformer(nn.Module):
         out.append(torch.ones_like(states[-1][..., 0], dtype=torch.float32) if stay is None else stay)
         return torch.stack(out)
 
-    def hidden(self, tokens, positions=None, segment_ids=None, cache=None, train: bool = False, passes: bool = False, loop_steps: Optional[int] = None):
+    def hidden(self, tokens, positions=None, segment_ids=None, cache=None, train: bool = False, passes: bool = False, loop_steps: Optional[int] = None,
+               embeddings: Optional[torch.Tensor] = None):
+        """``embeddings [B, S, d]``: input embeddings computed by the caller (a vision-language model splices image features into the
+        token embeddings); they replace the table lookup of ``tokens`` and are scaled like it."""
         cfg = self.config
-        h = self.embed(tokens)
+        h = self.embed(tokens) if embeddings is None else embeddings
         if cfg.embed_scale:
             h = h * (cfg.emb_features ** 0.5)
         cos, sin = self.rope_tables(h.device)
@@ -407,8 +410,8 @@ class CausalTransformer(nn.Module):
         return self.logits(hidden).argmax(-1)
 
     def forward(self, tokens, train: bool = False, decode: bool = False, positions=None, segment_ids=None, cache=None,
-                return_hidden: bool = False, passes: bool = False, loop_steps: Optional[int] = None):
-        h = self.hidden(tokens, positions, segment_ids, cache, train, passes, loop_steps)
+                return_hidden: bool = False, passes: bool = False, loop_steps: Optional[int] = None, embeddings: Optional[torch.Tensor] = None):
+        h = self.hidden(tokens, positions, segment_ids, cache, train, passes, loop_steps, embeddings)
         if return_hidden:
             return h
         return [self.logits(x) for x in h] if passes else self.logits(h)

@@ -101,7 +101,7 @@ class LMObjective(Objective):
         else:
             from ..utils.trees import variables_for_call
             named = variables_for_call(self.model, variables)
-            w = named["embed.weight"] if self.model.head is None else named["head.weight"]
+            w = named[getattr(self.model, "head_parameter", None) or ("embed.weight" if self.model.head is None else "head.weight")]
         cap = getattr(self.model.config, "logit_softcap", 0.0)
         scored = (targets != -100)
         mass = scored.sum().to(torch.float32)
@@ -143,7 +143,7 @@ class LMObjective(Objective):
         else:
             from ..utils.trees import variables_for_call
             named = variables_for_call(self.model, variables)
-            w = named["embed.weight"] if self.model.head is None else named["head.weight"]
+            w = named[getattr(self.model, "head_parameter", None) or ("embed.weight" if self.model.head is None else "head.weight")]
         tile = self.head_tile or max(1, (B * S + self.head_chunks - 1) // self.head_chunks)
         cap = getattr(self.model.config, "logit_softcap", 0.0)
         tp_head = getattr(self.model, "tp_head", None)
