@@ -84,7 +84,7 @@ class TransformerConfig:
     attn_softcap: float = 0.0
     logit_softcap: float = 0.0
     window: Optional[int] = None
-    layer_types: Optional[Sequence[str]] = None      # per layer: attention | local | gdn | mamba2 | mamba | mamba3 | kda | mla | lightning | differential | forgetting
+    layer_types: Optional[Sequence[str]] = None      # per layer: attention | local | gdn | mamba2 | mamba | mamba3 | kda | mla | lightning | differential | forgetting | gla | delta | rwkv7
     mixture: Optional[Mixture] = None
     mixer_options: Dict[str, Any] = field(default_factory=dict)
     remat: bool = False
@@ -148,7 +148,17 @@ def _mixer(cfg: TransformerConfig, kind: str, dtype, device, index: int = 0) -> 
     if kind == "forgetting":
         from ..nn.attention_variants import ForgettingAttention
         return ForgettingAttention(cfg.emb_features, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, dtype=dtype, device=device)
-    raise ValueError(f"unknown layer type {kind!r}; known: attention, local, gdn, mamba2, mamba, mamba3, kda, mla, lightning, differential, forgetting")
+    if kind == "gla":
+        from ..nn.linear_mixers import GatedLinearAttention
+        return GatedLinearAttention(cfg.emb_features, **({"num_heads": cfg.num_heads, **cfg.mixer_options})).to(device=device, dtype=dtype)
+    if kind == "delta":
+        from ..nn.linear_mixers import DeltaNet
+        return DeltaNet(cfg.emb_features, **({"num_heads": cfg.num_heads, **cfg.mixer_options})).to(device=device, dtype=dtype)
+    if kind == "rwkv7":
+        from ..nn.linear_mixers import RWKV7
+        return RWKV7(cfg.emb_features, layer_index=0, **({"num_heads": cfg.num_heads, **cfg.mixer_options})).to(device=device, dtype=dtype)
+    raise ValueError(f"unknown layer type {kind!r}; known: attention, local, gdn, mamba2, mamba, mamba3, kda, mla, lightning, differential, forgetting, "
+                     "gla, delta, rwkv7")
 
 
 class DecoderLayer(nn.Module):
