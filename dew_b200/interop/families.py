@@ -6,7 +6,7 @@ returns the release's keys nothing read, so a silent partial load cannot happen.
 
 Families: llama, mistral, qwen2 (q/k/v bias), qwen3 (per-head q/k norm), qwen3_moe, mixtral, gemma (norm weight stored
 minus one, GeGLU, scaled embeddings), gemma2 (output norms on every sub-layer, soft-capped logits, alternating local /
-global layers, query scale), phi3 (fused qkv and gate_up on disk), olmoe / granite-style Llama renames fall under llama.
+global layers, query scale), phi3 (fused qkv and gate_up on disk), granite (embedding / attention / residual multipliers, logits scaling).
 
 Reference: src/dew/interop/decoder_families.py, decoder_config.py, decoder_parts.py (family tables), unread.py (keys
 nothing read), hf_decoders.py.
@@ -105,8 +105,15 @@ def _phi3(cfg):
     return _common(cfg, window=cfg.get("sliding_window"))
 
 
+def _granite(cfg):
+    # four scalars: embeddings times one, the softmax scale itself (not 1 / sqrt(d)), every branch times one, logits over one
+    return _common(cfg, embed_multiplier=float(cfg.get("embedding_multiplier", 1.0)), query_scale=float(cfg.get("attention_multiplier", 1.0)),
+                   residual_multiplier=float(cfg.get("residual_multiplier", 1.0)), logit_divisor=float(cfg.get("logits_scaling", 1.0)))
+
+
 FAMILIES: Dict[str, Family] = {f.name: f for f in (
-    Family("llama", ("llama", "granite", "olmo", "internlm2", "yi"), "LlamaForCausalLM", _llama),
+    Family("llama", ("llama", "yi"), "LlamaForCausalLM", _llama),
+    Family("granite", ("granite",), "GraniteForCausalLM", _granite),
     Family("mistral", ("mistral",), "MistralForCausalLM", _llama),
     Family("qwen2", ("qwen2",), "Qwen2ForCausalLM", _qwen2, qkv_bias=True),
     Family("qwen3", ("qwen3",), "Qwen3ForCausalLM", _qwen3),
@@ -159,6 +166,11 @@ def write_config(c: TransformerConfig, family: str = "llama", dtype: str = "bflo
                     "query_pre_attn_scalar": (c.query_scale ** -2) if c.query_scale else out["head_dim"]})
     if fam.name == "qwen2":
         out["use_sliding_window"] = c.window is not None
+    if fam.name == "granite":
+        hd = out["head_dim"]
+        out.update({"embedding_multiplier": c.embed_multiplier if c.embed_multiplier is not None else 1.0,
+                    "attention_multiplier": c.query_scale if c.query_scale is not None else hd ** -0.5,
+                    "residual_multiplier": c.residual_multiplier, "logits_scaling": c.logit_divisor})
     return out
 
 

@@ -98,6 +98,9 @@ class TransformerConfig:
     sandwich_norm: bool = False                       # Gemma-2: every sub-layer's output is normalised before it joins the stream
     query_scale: Optional[float] = None               # softmax scale other than head_dim ** -0.5 (Gemma-2's query_pre_attn_scalar ** -0.5)
     loop: Optional[Loop] = None                       # a block of layers run several times (a looped / recurrent-depth decoder)
+    embed_multiplier: Optional[float] = None          # Granite: embeddings times this (embed_scale is the sqrt(d) special case)
+    residual_multiplier: float = 1.0                  # Granite: every sub-layer's output times this before it joins the stream
+    logit_divisor: float = 1.0                        # Granite: logits divided by this
 
     def __post_init__(self):
         if isinstance(self.mixture, Mapping):             # a run record (JSON) carries the mixture as a plain mapping
@@ -181,6 +184,7 @@ class DecoderLayer(nn.Module):
         self.mixer_out_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device) if cfg.sandwich_norm else None
         self.mlp_out_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device) if cfg.sandwich_norm else None
         self.tp = None          # set by parallel.tp.tensor_parallelize: branches are then partial sums over ranks
+        self.residual_multiplier = float(cfg.residual_multiplier)
         self.streams = None
         if cfg.hyper_connections > 1 or cfg.altup > 1:
             from ..nn.streams import AltUp, HyperConnections
@@ -231,9 +235,12 @@ class DecoderLayer(nn.Module):
             a = self.mixer(n, segment_ids=segment_ids, cache=cache, layer=self.index)
         if self.mixer_out_norm is not None:
             a = self.mixer_out_norm(a)
+        if self.residual_multiplier != 1.0:
+            a = a * self.residual_multiplier
         n, h = self._norm(self.post_norm, h, a)
         m = self.mlp(n)
-        return h, (m if self.mlp_out_norm is None else self.mlp_out_norm(m))
+        m = m if self.mlp_out_norm is None else self.mlp_out_norm(m)
+        return h, (m if self.residual_multiplier == 1.0 else m * self.residual_multiplier)
 
 
 class MTPBlock(nn.Module):
@@ -372,6 +379,8 @@ class CausalTransformer(nn.Module):
         h = self.embed(tokens) if embeddings is None else embeddings
         if cfg.embed_scale:
             h = h * (cfg.emb_features ** 0.5)
+        if cfg.embed_multiplier is not None:
+            h = h * cfg.embed_multiplier
         cos, sin = self.rope_tables(h.device)
         n_streams = max(cfg.hyper_connections, cfg.altup)
         if n_streams > 1:
@@ -408,6 +417,8 @@ class CausalTransformer(nn.Module):
             torch.distributed.all_gather(parts, local.contiguous(), group=self.tp.group)
             return torch.cat(parts, -1)
         out = ops.linear(hidden, self.head_weight())
+        if self.config.logit_divisor != 1.0:
+            out = out / self.config.logit_divisor
         if self.config.logit_softcap > 0:
             out = self.config.logit_softcap * torch.tanh(out.float() / self.config.logit_softcap)
         return out

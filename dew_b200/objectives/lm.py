@@ -146,6 +146,9 @@ class LMObjective(Objective):
             w = named[getattr(self.model, "head_parameter", None) or ("embed.weight" if self.model.head is None else "head.weight")]
         tile = self.head_tile or max(1, (B * S + self.head_chunks - 1) // self.head_chunks)
         cap = getattr(self.model.config, "logit_softcap", 0.0)
+        divisor = getattr(self.model.config, "logit_divisor", 1.0)
+        if divisor != 1.0:
+            hidden = hidden / divisor                                       # logits = h W^T / divisor
         tp_head = getattr(self.model, "tp_head", None)
         if tp_head is not None and getattr(self.model, "tp_training", False):
             # vocabulary-parallel head: every tensor rank scores its slice of the vocabulary; maxima, sums and the target
