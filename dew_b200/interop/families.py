@@ -6,7 +6,8 @@ returns the release's keys nothing read, so a silent partial load cannot happen.
 
 Families: llama, mistral, qwen2 (q/k/v bias), qwen3 (per-head q/k norm), qwen3_moe, mixtral, gemma (norm weight stored
 minus one, GeGLU, scaled embeddings), gemma2 (output norms on every sub-layer, soft-capped logits, alternating local /
-global layers, query scale), phi3 (fused qkv and gate_up on disk), granite (embedding / attention / residual multipliers, logits scaling).
+global layers, query scale), phi3 (fused qkv and gate_up on disk), granite (embedding / attention / residual multipliers, logits scaling), olmo2 (no pre-norms: every sub-layer's output is
+normalised instead; q and k normalised over all heads at once).
 
 Reference: src/dew/interop/decoder_families.py, decoder_config.py, decoder_parts.py (family tables), unread.py (keys
 nothing read), hf_decoders.py.
@@ -62,6 +63,7 @@ class Family:
     post_attention_norm: str = "post_attention_layernorm"  # the norm in front of the MLP
     mixer_out_norm: Optional[str] = None                  # Gemma-2: norm on the attention output
     mlp_out_norm: Optional[str] = None                    # Gemma-2: norm on the MLP output
+    pre_norm: bool = True                                 # False (OLMo-2): no input / pre-MLP norms on disk
     experts: Optional[str] = None                         # 'mixtral' | 'qwen' naming of sparse layers
     extra_config: Mapping[str, Any] = field(default_factory=dict)   # written into ``config.json`` on export
 
@@ -105,6 +107,10 @@ def _phi3(cfg):
     return _common(cfg, window=cfg.get("sliding_window"))
 
 
+def _olmo2(cfg):
+    return _common(cfg, pre_norm=False, sandwich_norm=True, qk_norm_full=True)
+
+
 def _granite(cfg):
     # four scalars: embeddings times one, the softmax scale itself (not 1 / sqrt(d)), every branch times one, logits over one
     return _common(cfg, embed_multiplier=float(cfg.get("embedding_multiplier", 1.0)), query_scale=float(cfg.get("attention_multiplier", 1.0)),
@@ -114,6 +120,8 @@ def _granite(cfg):
 FAMILIES: Dict[str, Family] = {f.name: f for f in (
     Family("llama", ("llama", "yi"), "LlamaForCausalLM", _llama),
     Family("granite", ("granite",), "GraniteForCausalLM", _granite),
+    Family("olmo2", ("olmo2",), "Olmo2ForCausalLM", _olmo2, pre_norm=False, mixer_out_norm="post_attention_layernorm",
+           mlp_out_norm="post_feedforward_layernorm"),
     Family("mistral", ("mistral",), "MistralForCausalLM", _llama),
     Family("qwen2", ("qwen2",), "Qwen2ForCausalLM", _qwen2, qkv_bias=True),
     Family("qwen3", ("qwen3",), "Qwen3ForCausalLM", _qwen3),
@@ -209,8 +217,9 @@ def load_state(model: CausalTransformer, tensors: Mapping[str, torch.Tensor], fa
     _put(model.embed.weight, get("model.embed_tokens.weight"))
     for i, layer in enumerate(model.layers):
         pre = f"model.layers.{i}."
-        _put(layer.input_norm.weight, get(pre + "input_layernorm.weight"), off)
-        _put(layer.post_norm.weight, get(pre + family.post_attention_norm + ".weight"), off)
+        if family.pre_norm:
+            _put(layer.input_norm.weight, get(pre + "input_layernorm.weight"), off)
+            _put(layer.post_norm.weight, get(pre + family.post_attention_norm + ".weight"), off)
         if family.mixer_out_norm:
             _put(layer.mixer_out_norm.weight, get(pre + family.mixer_out_norm + ".weight"), off)
             _put(layer.mlp_out_norm.weight, get(pre + family.mlp_out_norm + ".weight"), off)
@@ -276,8 +285,9 @@ def export_state(model: CausalTransformer, family: Family) -> Dict[str, torch.Te
     out = {"model.embed_tokens.weight": model.embed.weight.detach(), "model.norm.weight": norm(model.final_norm.weight)}
     for i, layer in enumerate(model.layers):
         pre = f"model.layers.{i}."
-        out[pre + "input_layernorm.weight"] = norm(layer.input_norm.weight)
-        out[pre + family.post_attention_norm + ".weight"] = norm(layer.post_norm.weight)
+        if family.pre_norm:
+            out[pre + "input_layernorm.weight"] = norm(layer.input_norm.weight)
+            out[pre + family.post_attention_norm + ".weight"] = norm(layer.post_norm.weight)
         if family.mixer_out_norm:
             out[pre + family.mixer_out_norm + ".weight"] = norm(layer.mixer_out_norm.weight)
             out[pre + family.mlp_out_norm + ".weight"] = norm(layer.mlp_out_norm.weight)

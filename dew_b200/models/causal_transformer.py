@@ -98,6 +98,8 @@ class TransformerConfig:
     sandwich_norm: bool = False                       # Gemma-2: every sub-layer's output is normalised before it joins the stream
     query_scale: Optional[float] = None               # softmax scale other than head_dim ** -0.5 (Gemma-2's query_pre_attn_scalar ** -0.5)
     loop: Optional[Loop] = None                       # a block of layers run several times (a looped / recurrent-depth decoder)
+    pre_norm: bool = True                             # False (OLMo-2): sub-layers read the stream as it is; only their outputs are normalised (sandwich_norm)
+    qk_norm_full: bool = False                        # OLMo-2: q and k normalised over all heads at once
     embed_multiplier: Optional[float] = None          # Granite: embeddings times this (embed_scale is the sqrt(d) special case)
     residual_multiplier: float = 1.0                  # Granite: every sub-layer's output times this before it joins the stream
     logit_divisor: float = 1.0                        # Granite: logits divided by this
@@ -123,7 +125,8 @@ def _mixer(cfg: TransformerConfig, kind: str, dtype, device, index: int = 0) -> 
         return SelfAttention(cfg.emb_features, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, qk_norm=cfg.qk_norm,
                              causal=True, window=cfg.window if kind == "local" or cfg.layer_types is None else None,
                              softcap=cfg.attn_softcap, sinks=cfg.attention_sinks, norm_eps=cfg.norm_eps,
-                             init_std=cfg.init_std, qkv_bias=cfg.qkv_bias, scale=cfg.query_scale, dtype=dtype, device=device)
+                             init_std=cfg.init_std, qkv_bias=cfg.qkv_bias, scale=cfg.query_scale, qk_norm_full=cfg.qk_norm_full,
+                             dtype=dtype, device=device)
     if kind == "gdn":
         from ..nn.linear_attention import GatedDeltaNet
         return GatedDeltaNet(cfg.emb_features, dtype=dtype, device=device, **cfg.mixer_options)
@@ -164,13 +167,26 @@ def _mixer(cfg: TransformerConfig, kind: str, dtype, device, index: int = 0) -> 
                      "gla, delta, rwkv7")
 
 
+class _NoNorm(nn.Module):
+    """Stands where a pre-norm would: adds the pending branch into the stream and hands the stream on unnormalised."""
+    weight = None
+
+    def forward(self, h, branch=None):
+        if branch is None:
+            return h
+        h = h + branch
+        return h, h
+
+
 class DecoderLayer(nn.Module):
     def __init__(self, cfg: TransformerConfig, index: int, kind: str, dtype=None, device=None):
         super().__init__()
         self.kind, self.index = kind, index
-        self.input_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
+        if not cfg.pre_norm and not cfg.sandwich_norm:
+            raise ValueError("a decoder without pre-norms normalises its sub-layers' outputs: set sandwich_norm=True with pre_norm=False")
+        self.input_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device) if cfg.pre_norm else _NoNorm()
         self.mixer = _mixer(cfg, kind, dtype, device, index)
-        self.post_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
+        self.post_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device) if cfg.pre_norm else _NoNorm()
         mix = cfg.mixture
         sparse = mix is not None and (mix.layers is None or index in mix.layers)
         if sparse:
@@ -210,6 +226,8 @@ class DecoderLayer(nn.Module):
     def _norm(self, norm, h, branch):
         """Add the pending branch into the stream and normalise; under tensor parallelism the branch is a partial sum
         and the all-reduce is fused with the add and the norm."""
+        if self.tp is not None and isinstance(norm, _NoNorm):
+            raise NotImplementedError("tensor parallelism fuses its all-reduce with a pre-norm; a decoder without pre-norms is not built for it")
         if self.tp is not None:
             if getattr(self, "tp_training", False):
                 # training: the partial sums meet in an all-reduce autograd can differentiate; the normalised activations enter

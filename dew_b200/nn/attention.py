@@ -17,7 +17,8 @@ class SelfAttention(nn.Module):
     def __init__(self, features: int, num_heads: int, num_kv_heads: Optional[int] = None, head_dim: Optional[int] = None,
                  qk_norm: bool = False, bias: bool = False, causal: bool = True, window: Optional[int] = None,
                  softcap: float = 0.0, sinks: bool = False, norm_eps: float = 1e-6, out_zero_init: bool = False,
-                 init_std: Optional[float] = None, qkv_bias: bool = False, scale: Optional[float] = None, dtype=None, device=None):
+                 init_std: Optional[float] = None, qkv_bias: bool = False, scale: Optional[float] = None, qk_norm_full: bool = False,
+                 dtype=None, device=None):
         super().__init__()
         self.features, self.num_heads = features, num_heads
         # a softmax scale other than head_dim ** -0.5 is folded into the queries (after the norm and the rotation)
@@ -29,8 +30,11 @@ class SelfAttention(nn.Module):
         self.qkv_proj = Linear(features, qkv_out, bias=bias or qkv_bias, axes=("embed", "heads"), init_std=init_std, dtype=dtype, device=device)
         self.o_proj = Linear(self.num_heads * self.head_dim, features, bias=bias, axes=("heads", "embed"),
                              init_std=init_std, zero_init=out_zero_init, dtype=dtype, device=device)
-        self.q_norm = RMSNorm(self.head_dim, norm_eps, dtype=dtype, device=device) if qk_norm else None
-        self.k_norm = RMSNorm(self.head_dim, norm_eps, dtype=dtype, device=device) if qk_norm else None
+        # OLMo-2 normalises q and k over all their heads at once (one weight of heads x head_dim); the usual form is per head
+        self.qk_norm_full = qk_norm_full
+        qw, kw = (self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim) if qk_norm_full else (self.head_dim, self.head_dim)
+        self.q_norm = RMSNorm(qw, norm_eps, dtype=dtype, device=device) if (qk_norm or qk_norm_full) else None
+        self.k_norm = RMSNorm(kw, norm_eps, dtype=dtype, device=device) if (qk_norm or qk_norm_full) else None
         self.sinks = declare(nn.Parameter(torch.zeros(num_heads, dtype=dtype, device=device)), ("heads",), "sinks") if sinks else None
         self.track_qk_max = False      # set by dew_b200.optim.qk_clip.watch: record each head's largest attention logit
         self.qk_max: Optional[torch.Tensor] = None
@@ -55,7 +59,11 @@ class SelfAttention(nn.Module):
         B, S, _ = x.shape
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = self.qkv_proj(x).view(B, S, H + 2 * Hkv, D)
-        if self.q_norm is not None:
+        if self.q_norm is not None and self.qk_norm_full:
+            q = self.q_norm(qkv[:, :, :H].reshape(B, S, H * D)).view(B, S, H, D)
+            k = self.k_norm(qkv[:, :, H:H + Hkv].reshape(B, S, Hkv * D)).view(B, S, Hkv, D)
+            qkv = torch.cat([q, k, qkv[:, :, H + Hkv:]], 2)
+        elif self.q_norm is not None:
             q = self.q_norm(qkv[:, :, :H])
             k = self.k_norm(qkv[:, :, H:H + Hkv])
             qkv = torch.cat([q, k, qkv[:, :, H + Hkv:]], 2)

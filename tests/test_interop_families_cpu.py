@@ -21,6 +21,7 @@ CASES = {
     "gemma": dict(model_type="gemma", head_dim=16, **COMMON),
     "gemma2": dict(model_type="gemma2", head_dim=16, sliding_window=8, query_pre_attn_scalar=24, **COMMON),
     "phi3": dict(model_type="phi3", pad_token_id=0, **COMMON),
+    "olmo2": dict(model_type="olmo2", **COMMON),
     "granite": dict(model_type="granite", embedding_multiplier=6.0, attention_multiplier=0.1, residual_multiplier=0.3, logits_scaling=4.0, **COMMON),
     "mixtral": dict(model_type="mixtral", num_local_experts=4, num_experts_per_tok=2, **COMMON),
     "qwen3_moe": dict(model_type="qwen3_moe", head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
