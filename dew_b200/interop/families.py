@@ -7,7 +7,8 @@ returns the release's keys nothing read, so a silent partial load cannot happen.
 Families: llama, mistral, qwen2 (q/k/v bias), qwen3 (per-head q/k norm), qwen3_moe, mixtral, gemma (norm weight stored
 minus one, GeGLU, scaled embeddings), gemma2 (output norms on every sub-layer, soft-capped logits, alternating local /
 global layers, query scale), phi3 (fused qkv and gate_up on disk), granite (embedding / attention / residual multipliers, logits scaling), olmo2 (no pre-norms: every sub-layer's output is
-normalised instead; q and k normalised over all heads at once).
+normalised instead; q and k normalised over all heads at once), olmo3 (olmo2 with sliding layers on an unscaled rotary table), gemma3 (gemma2's
+block with per-head q/k norms and one rotary base per layer kind), smollm3 (every fourth layer attends without positions).
 
 Reference: src/dew/interop/decoder_families.py, decoder_config.py, decoder_parts.py (family tables), unread.py (keys
 nothing read), hf_decoders.py.
@@ -111,6 +112,52 @@ def _olmo2(cfg):
     return _common(cfg, pre_norm=False, sandwich_norm=True, qk_norm_full=True)
 
 
+_KINDS = {"sliding_attention": "local", "full_attention": "attention"}
+
+
+def _layer_kinds(cfg) -> Optional[Tuple[str, ...]]:
+    kinds = cfg.get("layer_types")
+    return None if not kinds else tuple(_KINDS[k] for k in kinds)
+
+
+def _by_kind_rope(cfg) -> Tuple[float, Optional[dict], Optional[float]]:
+    """``rope_parameters`` keyed by layer kind (Gemma-3): the full layers' base and scaling, and the sliding layers' base."""
+    rope = cfg.get("rope_parameters") or {}
+    if "full_attention" in rope:
+        full, local = rope["full_attention"], rope.get("sliding_attention") or {}
+        scaling = {k: v for k, v in full.items() if k != "rope_theta"} if full.get("rope_type", "default") != "default" else None
+        return float(full.get("rope_theta", 10000.0)), scaling, float(local.get("rope_theta", 10000.0))
+    theta, scaling = _rope(cfg)
+    return theta, scaling, float(cfg.get("rope_local_base_freq", 10000.0))
+
+
+def _gemma3(cfg):
+    base = _gemma(cfg)
+    theta, scaling, local = _by_kind_rope(cfg)
+    base.update(sandwich_norm=True, qk_norm=True, logit_softcap=float(cfg.get("final_logit_softcapping") or 0.0),
+                attn_softcap=float(cfg.get("attn_logit_softcapping") or 0.0), window=cfg.get("sliding_window"),
+                layer_types=_layer_kinds(cfg), rope_theta=theta, rope_scaling=scaling, local_rope_theta=local,
+                query_scale=float(cfg.get("query_pre_attn_scalar", base["head_dim"])) ** -0.5)
+    return base
+
+
+def _olmo3(cfg):
+    # the sliding layers rotate by the plain table; only the full layers take the long-context scaling (the model's paper and the
+    # modelling code its release shipped with; later transformers versions build one table for every layer)
+    base = _olmo2(cfg)
+    base.update(window=cfg.get("sliding_window"), layer_types=_layer_kinds(cfg), local_rope_theta=base["rope_theta"])
+    return base
+
+
+def _smollm3(cfg):
+    kinds = _layer_kinds(cfg) or ("attention",) * cfg["num_hidden_layers"]
+    rotary = cfg.get("no_rope_layers") or [1] * len(kinds)          # 1: rotary, 0: no positions
+    if any(k == "local" and not r for k, r in zip(kinds, rotary)):
+        raise NotImplementedError("a sliding layer without rotary positions is not built")
+    window = cfg.get("sliding_window") if cfg.get("use_sliding_window") else None
+    return _common(cfg, window=window, layer_types=tuple(k if r else "nope" for k, r in zip(kinds, rotary)))
+
+
 def _granite(cfg):
     # four scalars: embeddings times one, the softmax scale itself (not 1 / sqrt(d)), every branch times one, logits over one
     return _common(cfg, embed_multiplier=float(cfg.get("embedding_multiplier", 1.0)), query_scale=float(cfg.get("attention_multiplier", 1.0)),
@@ -122,6 +169,9 @@ FAMILIES: Dict[str, Family] = {f.name: f for f in (
     Family("granite", ("granite",), "GraniteForCausalLM", _granite),
     Family("olmo2", ("olmo2",), "Olmo2ForCausalLM", _olmo2, pre_norm=False, mixer_out_norm="post_attention_layernorm",
            mlp_out_norm="post_feedforward_layernorm"),
+    Family("olmo3", ("olmo3",), "Olmo3ForCausalLM", _olmo3, pre_norm=False, mixer_out_norm="post_attention_layernorm",
+           mlp_out_norm="post_feedforward_layernorm"),
+    Family("smollm3", ("smollm3",), "SmolLM3ForCausalLM", _smollm3),
     Family("mistral", ("mistral",), "MistralForCausalLM", _llama),
     Family("qwen2", ("qwen2",), "Qwen2ForCausalLM", _qwen2, qkv_bias=True),
     Family("qwen3", ("qwen3",), "Qwen3ForCausalLM", _qwen3),
@@ -129,6 +179,9 @@ FAMILIES: Dict[str, Family] = {f.name: f for f in (
     Family("mixtral", ("mixtral",), "MixtralForCausalLM", _mixtral, experts="mixtral"),
     Family("gemma", ("gemma",), "GemmaForCausalLM", _gemma, norm_offset=1.0, extra_config={"hidden_activation": "gelu_pytorch_tanh"}),
     Family("gemma2", ("gemma2",), "Gemma2ForCausalLM", _gemma2, norm_offset=1.0, mixer_out_norm="post_attention_layernorm",
+           post_attention_norm="pre_feedforward_layernorm", mlp_out_norm="post_feedforward_layernorm",
+           extra_config={"hidden_activation": "gelu_pytorch_tanh"}),
+    Family("gemma3", ("gemma3_text",), "Gemma3ForCausalLM", _gemma3, norm_offset=1.0, mixer_out_norm="post_attention_layernorm",
            post_attention_norm="pre_feedforward_layernorm", mlp_out_norm="post_feedforward_layernorm",
            extra_config={"hidden_activation": "gelu_pytorch_tanh"}),
     Family("phi3", ("phi3",), "Phi3ForCausalLM", _phi3, fused_qkv="self_attn.qkv_proj", fused_gate_up="mlp.gate_up_proj"),
@@ -172,6 +225,17 @@ def write_config(c: TransformerConfig, family: str = "llama", dtype: str = "bflo
     if fam.name == "gemma2":
         out.update({"attn_logit_softcapping": c.attn_softcap or None, "final_logit_softcapping": c.logit_softcap or None,
                     "query_pre_attn_scalar": (c.query_scale ** -2) if c.query_scale else out["head_dim"]})
+    kinds = c.kinds()
+    if fam.name in ("gemma3", "olmo3", "smollm3"):
+        out["layer_types"] = ["sliding_attention" if k == "local" else "full_attention" for k in kinds]
+    if fam.name == "gemma3":
+        full = {"rope_type": "default", **(c.rope_scaling or {}), "rope_theta": c.rope_theta}
+        out.update({"query_pre_attn_scalar": (c.query_scale ** -2) if c.query_scale else out["head_dim"],
+                    "final_logit_softcapping": c.logit_softcap or None, "attn_logit_softcapping": c.attn_softcap or None,
+                    "rope_parameters": {"full_attention": full, "sliding_attention": {"rope_type": "default", "rope_theta": c.local_rope_theta or 10000.0}}})
+        out.pop("rope_theta"), out.pop("rope_scaling")
+    if fam.name == "smollm3":
+        out.update({"no_rope_layers": [0 if k == "nope" else 1 for k in kinds], "use_sliding_window": c.window is not None})
     if fam.name == "qwen2":
         out["use_sliding_window"] = c.window is not None
     if fam.name == "granite":

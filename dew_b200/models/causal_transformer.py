@@ -84,7 +84,7 @@ class TransformerConfig:
     attn_softcap: float = 0.0
     logit_softcap: float = 0.0
     window: Optional[int] = None
-    layer_types: Optional[Sequence[str]] = None      # per layer: attention | local | gdn | mamba2 | mamba | mamba3 | kda | mla | lightning | differential | forgetting | gla | delta | rwkv7
+    layer_types: Optional[Sequence[str]] = None      # per layer: attention | local | nope | gdn | mamba2 | mamba | mamba3 | kda | mla | lightning | differential | forgetting | gla | delta | rwkv7
     mixture: Optional[Mixture] = None
     mixer_options: Dict[str, Any] = field(default_factory=dict)
     remat: bool = False
@@ -98,6 +98,7 @@ class TransformerConfig:
     sandwich_norm: bool = False                       # Gemma-2: every sub-layer's output is normalised before it joins the stream
     query_scale: Optional[float] = None               # softmax scale other than head_dim ** -0.5 (Gemma-2's query_pre_attn_scalar ** -0.5)
     loop: Optional[Loop] = None                       # a block of layers run several times (a looped / recurrent-depth decoder)
+    local_rope_theta: Optional[float] = None          # Gemma-3 / OLMo-3: 'local' layers rotate by this base, unscaled; the others by rope_theta with rope_scaling
     pre_norm: bool = True                             # False (OLMo-2): sub-layers read the stream as it is; only their outputs are normalised (sandwich_norm)
     qk_norm_full: bool = False                        # OLMo-2: q and k normalised over all heads at once
     embed_multiplier: Optional[float] = None          # Granite: embeddings times this (embed_scale is the sqrt(d) special case)
@@ -117,16 +118,20 @@ class TransformerConfig:
         return [pattern[i % len(pattern)] for i in range(self.num_layers)]
 
 
-ROTARY_KINDS = ("attention", "local", "mla", "differential", "forgetting")      # mixers called with the rotary tables and positions
+ROTARY_KINDS = ("attention", "local", "nope", "mla", "differential", "forgetting")      # mixers called with the rotary tables and positions
 
 
 def _mixer(cfg: TransformerConfig, kind: str, dtype, device, index: int = 0) -> nn.Module:
-    if kind in ("attention", "local"):
-        return SelfAttention(cfg.emb_features, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, qk_norm=cfg.qk_norm,
-                             causal=True, window=cfg.window if kind == "local" or cfg.layer_types is None else None,
-                             softcap=cfg.attn_softcap, sinks=cfg.attention_sinks, norm_eps=cfg.norm_eps,
-                             init_std=cfg.init_std, qkv_bias=cfg.qkv_bias, scale=cfg.query_scale, qk_norm_full=cfg.qk_norm_full,
-                             dtype=dtype, device=device)
+    if kind in ("attention", "local", "nope"):
+        a = SelfAttention(cfg.emb_features, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, qk_norm=cfg.qk_norm,
+                          causal=True, window=cfg.window if kind == "local" or cfg.layer_types is None else None,
+                          softcap=cfg.attn_softcap, sinks=cfg.attention_sinks, norm_eps=cfg.norm_eps,
+                          init_std=cfg.init_std, qkv_bias=cfg.qkv_bias, scale=cfg.query_scale, qk_norm_full=cfg.qk_norm_full,
+                          dtype=dtype, device=device)
+        a.rotary = kind != "nope"                        # SmolLM3's every fourth layer attends without positions
+        if kind == "local" and cfg.local_rope_theta is not None:
+            a.own_rope = (float(cfg.local_rope_theta), None)
+        return a
     if kind == "gdn":
         from ..nn.linear_attention import GatedDeltaNet
         return GatedDeltaNet(cfg.emb_features, dtype=dtype, device=device, **cfg.mixer_options)

@@ -36,6 +36,8 @@ class SelfAttention(nn.Module):
         self.q_norm = RMSNorm(qw, norm_eps, dtype=dtype, device=device) if (qk_norm or qk_norm_full) else None
         self.k_norm = RMSNorm(kw, norm_eps, dtype=dtype, device=device) if (qk_norm or qk_norm_full) else None
         self.sinks = declare(nn.Parameter(torch.zeros(num_heads, dtype=dtype, device=device)), ("heads",), "sinks") if sinks else None
+        # a layer whose rotary table differs from the model's: (theta, scaling) builds its own; rotary False drops the rotation (NoPE)
+        self.rotary, self.own_rope, self._own = True, None, None
         self.track_qk_max = False      # set by dew_b200.optim.qk_clip.watch: record each head's largest attention logit
         self.qk_max: Optional[torch.Tensor] = None
 
@@ -72,16 +74,27 @@ class SelfAttention(nn.Module):
         q = qkv[:, :, :H]
         return (q if self.q_gain is None else q * self.q_gain), qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
 
+    def _tables(self, cos, sin):
+        if not self.rotary:
+            return None, None
+        if self.own_rope is None or cos is None:
+            return cos, sin
+        if self._own is None or self._own[0].device != cos.device or self._own[0].shape[0] != cos.shape[0]:
+            theta, scaling = self.own_rope
+            self._own = ops.rope_tables(cos.shape[0], self.head_dim, theta, cos.device, scaling)
+        return self._own
+
     def forward(self, x, cos=None, sin=None, positions=None, segment_ids=None, cache=None, layer: int = 0):
         B, S, _ = x.shape
-        if (cache is None and x.is_cuda and self.q_norm is None and self.window is None and not self.softcap
+        cos, sin = self._tables(cos, sin)
+        if (cache is None and x.is_cuda and cos is not None and self.q_norm is None and self.window is None and not self.softcap
                 and self.sinks is None and segment_ids is None and not self.track_qk_max and self.q_gain is None):
             from ..ops.attn import packed_attention
             H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
             o = packed_attention(self.qkv_proj(x).view(B, S, H + 2 * Hkv, D), cos, sin, positions, H, Hkv, self.causal)
             if o is not None:
                 return self.o_proj(o.reshape(B, S, H * D))
-        if (cache is not None and S == 1 and self.q_norm is None and self.q_gain is None and positions is not None
+        if (cache is not None and S == 1 and self.q_norm is None and self.q_gain is None and positions is not None and cos is not None
                 and hasattr(cache, "decode_packed")):
             # decode step: rotation, cache append and attention straight from the packed projection (no slices, no copies)
             H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim

@@ -22,6 +22,13 @@ CASES = {
     "gemma2": dict(model_type="gemma2", head_dim=16, sliding_window=8, query_pre_attn_scalar=24, **COMMON),
     "phi3": dict(model_type="phi3", pad_token_id=0, **COMMON),
     "olmo2": dict(model_type="olmo2", **COMMON),
+    # (unscaled rotary: the installed transformers gives OLMo-3 one table for all layers, the release's own modelling code one per layer kind)
+    "olmo3": dict(model_type="olmo3", sliding_window=8, layer_types=["sliding_attention", "full_attention"], **COMMON),
+    "smollm3": dict(model_type="smollm3", no_rope_layers=[1, 0], pad_token_id=0, **COMMON),
+    "gemma3": dict(model_type="gemma3_text", head_dim=16, sliding_window=8, query_pre_attn_scalar=24,
+                   layer_types=["sliding_attention", "full_attention"],
+                   rope_parameters={"sliding_attention": {"rope_type": "default", "rope_theta": 1000.0},
+                                    "full_attention": {"rope_type": "linear", "rope_theta": 50000.0, "factor": 2.0}}, **COMMON),
     "granite": dict(model_type="granite", embedding_multiplier=6.0, attention_multiplier=0.1, residual_multiplier=0.3, logits_scaling=4.0, **COMMON),
     "mixtral": dict(model_type="mixtral", num_local_experts=4, num_experts_per_tok=2, **COMMON),
     "qwen3_moe": dict(model_type="qwen3_moe", head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
