@@ -8,7 +8,8 @@ Families: llama, mistral, qwen2 (q/k/v bias), qwen3 (per-head q/k norm), qwen3_m
 minus one, GeGLU, scaled embeddings), gemma2 (output norms on every sub-layer, soft-capped logits, alternating local /
 global layers, query scale), phi3 (fused qkv and gate_up on disk), granite (embedding / attention / residual multipliers, logits scaling), olmo2 (no pre-norms: every sub-layer's output is
 normalised instead; q and k normalised over all heads at once), olmo3 (olmo2 with sliding layers on an unscaled rotary table), gemma3 (gemma2's
-block with per-head q/k norms and one rotary base per layer kind), smollm3 (every fourth layer attends without positions).
+block with per-head q/k norms and one rotary base per layer kind), smollm3 (every fourth layer attends without positions), deepseek_v3 (latent attention stored with
+interleaved rotary pairs, dense layers first, then sigmoid-routed experts in groups with a selection bias beside shared experts).
 
 Reference: src/dew/interop/decoder_families.py, decoder_config.py, decoder_parts.py (family tables), unread.py (keys
 nothing read), hf_decoders.py.
@@ -17,6 +18,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, List, Mapping, Optional, Sequence, Tuple
+
+import math
 
 import torch
 
@@ -158,6 +161,27 @@ def _smollm3(cfg):
     return _common(cfg, window=window, layer_types=tuple(k if r else "nope" for k, r in zip(kinds, rotary)))
 
 
+def _deepseek_v3(cfg):
+    """Latent attention on every layer; the first ``first_k_dense_replace`` layers dense, the rest routed by sigmoid scores with a selection
+    bias inside expert groups, beside always-on shared experts."""
+    n = cfg["num_hidden_layers"]
+    first, every = int(cfg.get("first_k_dense_replace", 0)), int(cfg.get("moe_layer_freq", 1) or 1)
+    width = int(cfg["moe_intermediate_size"])
+    mix = Mixture(experts=int(cfg["n_routed_experts"]), top_k=int(cfg["num_experts_per_tok"]),
+                  layers=tuple(i for i in range(n) if i >= first and i % every == 0), score_function="sigmoid",
+                  norm_topk_prob=bool(cfg.get("norm_topk_prob", True)), scaling=float(cfg.get("routed_scaling_factor", 1.0)), bias=True,
+                  groups=int(cfg.get("n_group") or 1), topk_groups=int(cfg.get("topk_group") or 1), expert_features=width,
+                  shared_features=int(cfg.get("n_shared_experts") or 0) * width)
+    theta, scaling = _rope(cfg)
+    gain = 1.0
+    if scaling and scaling.get("mscale_all_dim"):                # YaRN: the softmax scale grows by the magnitude correction squared
+        f = float(scaling["factor"])
+        gain = (1.0 if f <= 1 else 0.1 * float(scaling["mscale_all_dim"]) * math.log(f) + 1.0) ** 2
+    options = dict(kv_latent=int(cfg["kv_lora_rank"]), q_latent=cfg.get("q_lora_rank"), nope_dim=int(cfg["qk_nope_head_dim"]),
+                   rope_dim=int(cfg["qk_rope_head_dim"]), v_dim=int(cfg["v_head_dim"]), softmax_gain=gain)
+    return _common(cfg, head_dim=int(cfg["qk_rope_head_dim"]), layer_types=("mla",), mixture=mix, mixer_options=options)
+
+
 def _granite(cfg):
     # four scalars: embeddings times one, the softmax scale itself (not 1 / sqrt(d)), every branch times one, logits over one
     return _common(cfg, embed_multiplier=float(cfg.get("embedding_multiplier", 1.0)), query_scale=float(cfg.get("attention_multiplier", 1.0)),
@@ -184,6 +208,7 @@ FAMILIES: Dict[str, Family] = {f.name: f for f in (
     Family("gemma3", ("gemma3_text",), "Gemma3ForCausalLM", _gemma3, norm_offset=1.0, mixer_out_norm="post_attention_layernorm",
            post_attention_norm="pre_feedforward_layernorm", mlp_out_norm="post_feedforward_layernorm",
            extra_config={"hidden_activation": "gelu_pytorch_tanh"}),
+    Family("deepseek_v3", ("deepseek_v3",), "DeepseekV3ForCausalLM", _deepseek_v3, experts="deepseek"),
     Family("phi3", ("phi3",), "Phi3ForCausalLM", _phi3, fused_qkv="self_attn.qkv_proj", fused_gate_up="mlp.gate_up_proj"),
 )}
 
@@ -236,6 +261,16 @@ def write_config(c: TransformerConfig, family: str = "llama", dtype: str = "bflo
         out.pop("rope_theta"), out.pop("rope_scaling")
     if fam.name == "smollm3":
         out.update({"no_rope_layers": [0 if k == "nope" else 1 for k in kinds], "use_sliding_window": c.window is not None})
+    if fam.name == "deepseek_v3":
+        m, o = c.mixture, c.mixer_options
+        sparse = sorted(m.layers) if m.layers is not None else list(range(c.num_layers))
+        if sparse != list(range(sparse[0] if sparse else c.num_layers, c.num_layers)):
+            raise ValueError("a DeepSeek-V3 release says which layers are sparse by the count of dense layers in front of them")
+        out.update({"n_routed_experts": m.experts, "n_shared_experts": m.shared_features // (m.expert_features or 1), "n_group": m.groups,
+                    "topk_group": m.topk_groups, "routed_scaling_factor": m.scaling, "first_k_dense_replace": sparse[0] if sparse else c.num_layers,
+                    "moe_layer_freq": 1, "kv_lora_rank": o["kv_latent"], "q_lora_rank": o.get("q_latent"), "qk_nope_head_dim": o["nope_dim"],
+                    "qk_rope_head_dim": o["rope_dim"], "v_head_dim": o["v_dim"], "head_dim": o["rope_dim"],
+                    "num_key_value_heads": c.num_heads, "rope_interleave": True})
     if fam.name == "qwen2":
         out["use_sliding_window"] = c.window is not None
     if fam.name == "granite":
@@ -288,16 +323,19 @@ def load_state(model: CausalTransformer, tensors: Mapping[str, torch.Tensor], fa
             _put(layer.mixer_out_norm.weight, get(pre + family.mixer_out_norm + ".weight"), off)
             _put(layer.mlp_out_norm.weight, get(pre + family.mlp_out_norm + ".weight"), off)
         a = layer.mixer
-        if family.fused_qkv:
-            _put(a.qkv_proj.weight, get(pre + family.fused_qkv + ".weight"))
+        if hasattr(a, "kv_latent"):
+            _load_latent_attention(a, get, pre + "self_attn.")
         else:
-            _put(a.qkv_proj.weight, torch.cat([get(pre + f"self_attn.{n}_proj.weight") for n in "qkv"], 0))
-        if a.qkv_proj.bias is not None:
-            _put(a.qkv_proj.bias, torch.cat([get(pre + f"self_attn.{n}_proj.bias") for n in "qkv"], 0))
-        _put(a.o_proj.weight, get(pre + "self_attn.o_proj.weight"))
-        if a.q_norm is not None:
-            _put(a.q_norm.weight, get(pre + "self_attn.q_norm.weight"), off)
-            _put(a.k_norm.weight, get(pre + "self_attn.k_norm.weight"), off)
+            if family.fused_qkv:
+                _put(a.qkv_proj.weight, get(pre + family.fused_qkv + ".weight"))
+            else:
+                _put(a.qkv_proj.weight, torch.cat([get(pre + f"self_attn.{n}_proj.weight") for n in "qkv"], 0))
+            if a.qkv_proj.bias is not None:
+                _put(a.qkv_proj.bias, torch.cat([get(pre + f"self_attn.{n}_proj.bias") for n in "qkv"], 0))
+            _put(a.o_proj.weight, get(pre + "self_attn.o_proj.weight"))
+            if a.q_norm is not None:
+                _put(a.q_norm.weight, get(pre + "self_attn.q_norm.weight"), off)
+                _put(a.k_norm.weight, get(pre + "self_attn.k_norm.weight"), off)
         if getattr(layer, "sparse", False):
             _load_experts(layer.mlp, get, pre)
         elif family.fused_gate_up:
@@ -317,8 +355,54 @@ def load_state(model: CausalTransformer, tensors: Mapping[str, torch.Tensor], fa
     return left
 
 
+def _pairs_to_halves(rope: int) -> torch.Tensor:
+    """DeepSeek stores a rotary vector as pairs ``(2i, 2i + 1)``; this library rotates halves ``(i, i + rope / 2)``."""
+    return torch.cat([torch.arange(0, rope, 2), torch.arange(1, rope, 2)])
+
+
+def _load_latent_attention(a, get: _Reader, pre: str) -> None:
+    H, nope, rope = a.h, a.nope, a.rope
+    perm = _pairs_to_halves(rope)
+    if a.q_down is not None:
+        _put(a.q_down.weight, get(pre + "q_a_proj.weight"))
+        _put(a.q_norm.weight, get(pre + "q_a_layernorm.weight"))
+        q = get(pre + "q_b_proj.weight")
+    else:
+        q = get(pre + "q_proj.weight")
+    q = q.reshape(H, nope + rope, -1).clone()
+    q[:, nope:] = q[:, nope:][:, perm]
+    _put(a.q_up.weight, q.reshape(H * (nope + rope), -1))
+    kv = get(pre + "kv_a_proj_with_mqa.weight").clone()
+    kv[-rope:] = kv[-rope:][perm]
+    _put(a.kv_down.weight, kv)
+    _put(a.kv_norm.weight, get(pre + "kv_a_layernorm.weight"))
+    _put(a.kv_up.weight, get(pre + "kv_b_proj.weight"))
+    _put(a.o_proj.weight, get(pre + "o_proj.weight"))
+
+
+def _export_latent_attention(a, out: Dict[str, torch.Tensor], pre: str) -> None:
+    H, nope, rope = a.h, a.nope, a.rope
+    back = torch.argsort(_pairs_to_halves(rope))
+    q = a.q_up.weight.detach().reshape(H, nope + rope, -1).clone()
+    q[:, nope:] = q[:, nope:][:, back]
+    q = q.reshape(H * (nope + rope), -1)
+    if a.q_down is not None:
+        out[pre + "q_a_proj.weight"], out[pre + "q_a_layernorm.weight"], out[pre + "q_b_proj.weight"] = a.q_down.weight.detach(), a.q_norm.weight.detach(), q
+    else:
+        out[pre + "q_proj.weight"] = q
+    kv = a.kv_down.weight.detach().clone()
+    kv[-rope:] = kv[-rope:][back]
+    out[pre + "kv_a_proj_with_mqa.weight"], out[pre + "kv_a_layernorm.weight"] = kv, a.kv_norm.weight.detach()
+    out[pre + "kv_b_proj.weight"], out[pre + "o_proj.weight"] = a.kv_up.weight.detach(), a.o_proj.weight.detach()
+
+
 def _load_experts(mlp, get: _Reader, pre: str) -> None:
     E = mlp.mix.experts
+    if get.has(pre + "mlp.gate.e_score_correction_bias"):
+        _put(mlp.router.expert_bias, get(pre + "mlp.gate.e_score_correction_bias"))
+    if mlp.shared is not None and get.has(pre + "mlp.shared_experts.gate_proj.weight"):
+        _put(mlp.shared.gate_up_proj.weight, torch.cat([get(pre + "mlp.shared_experts.gate_proj.weight"), get(pre + "mlp.shared_experts.up_proj.weight")], 0))
+        _put(mlp.shared.down_proj.weight, get(pre + "mlp.shared_experts.down_proj.weight"))
     for gate in ("mlp.gate.weight", "block_sparse_moe.gate.weight"):
         if get.has(pre + gate):
             _put(mlp.router.weight, get(pre + gate))
@@ -356,20 +440,30 @@ def export_state(model: CausalTransformer, family: Family) -> Dict[str, torch.Te
             out[pre + family.mixer_out_norm + ".weight"] = norm(layer.mixer_out_norm.weight)
             out[pre + family.mlp_out_norm + ".weight"] = norm(layer.mlp_out_norm.weight)
         a = layer.mixer
-        w = a.qkv_proj.weight.detach()
-        if family.fused_qkv:
-            out[pre + family.fused_qkv + ".weight"] = w
+        if hasattr(a, "kv_latent"):
+            _export_latent_attention(a, out, pre + "self_attn.")
         else:
-            for n, part in zip("qkv", (w[: H * D], w[H * D:(H + Hkv) * D], w[(H + Hkv) * D:])):
-                out[pre + f"self_attn.{n}_proj.weight"] = part
-        if a.qkv_proj.bias is not None:
-            b = a.qkv_proj.bias.detach()
-            for n, part in zip("qkv", (b[: H * D], b[H * D:(H + Hkv) * D], b[(H + Hkv) * D:])):
-                out[pre + f"self_attn.{n}_proj.bias"] = part
-        out[pre + "self_attn.o_proj.weight"] = a.o_proj.weight.detach()
-        if a.q_norm is not None:
-            out[pre + "self_attn.q_norm.weight"] = norm(a.q_norm.weight)
-            out[pre + "self_attn.k_norm.weight"] = norm(a.k_norm.weight)
+            w = a.qkv_proj.weight.detach()
+            if family.fused_qkv:
+                out[pre + family.fused_qkv + ".weight"] = w
+            else:
+                for n, part in zip("qkv", (w[: H * D], w[H * D:(H + Hkv) * D], w[(H + Hkv) * D:])):
+                    out[pre + f"self_attn.{n}_proj.weight"] = part
+            if a.qkv_proj.bias is not None:
+                b = a.qkv_proj.bias.detach()
+                for n, part in zip("qkv", (b[: H * D], b[H * D:(H + Hkv) * D], b[(H + Hkv) * D:])):
+                    out[pre + f"self_attn.{n}_proj.bias"] = part
+            out[pre + "self_attn.o_proj.weight"] = a.o_proj.weight.detach()
+            if a.q_norm is not None:
+                out[pre + "self_attn.q_norm.weight"] = norm(a.q_norm.weight)
+                out[pre + "self_attn.k_norm.weight"] = norm(a.k_norm.weight)
+        if getattr(layer, "sparse", False) and family.experts == "deepseek":
+            m = layer.mlp
+            out[pre + "mlp.gate.e_score_correction_bias"] = m.router.expert_bias.detach()
+            if m.shared is not None:
+                sw = m.shared.gate_up_proj.weight.detach()
+                out[pre + "mlp.shared_experts.gate_proj.weight"], out[pre + "mlp.shared_experts.up_proj.weight"] = sw[: sw.shape[0] // 2], sw[sw.shape[0] // 2:]
+                out[pre + "mlp.shared_experts.down_proj.weight"] = m.shared.down_proj.weight.detach()
         if getattr(layer, "sparse", False):
             gu_all, dn_all = layer.mlp.experts.gate_up.detach(), layer.mlp.experts.down.detach()
             Fe = gu_all.shape[1] // 2

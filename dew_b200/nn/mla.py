@@ -14,8 +14,11 @@ from .layers import Linear, RMSNorm
 
 class MultiHeadLatentAttention(nn.Module):
     def __init__(self, features: int, num_heads: int, kv_latent: int = 512, q_latent: Optional[int] = None, nope_dim: int = 128,
-                 rope_dim: int = 64, v_dim: int = 128, norm_eps: float = 1e-6, causal: bool = True, dtype=None, device=None):
+                 rope_dim: int = 64, v_dim: int = 128, norm_eps: float = 1e-6, causal: bool = True, softmax_gain: float = 1.0,
+                 dtype=None, device=None):
         super().__init__()
+        # softmax_gain multiplies the (nope + rope) ** -0.5 scale: DeepSeek-V3's long-context releases raise it by YaRN's magnitude squared
+        self.softmax_gain = float(softmax_gain)
         self.h, self.nope, self.rope, self.vd, self.causal = num_heads, nope_dim, rope_dim, v_dim, causal
         kw = dict(dtype=dtype, device=device)
         qd = num_heads * (nope_dim + rope_dim)
@@ -60,7 +63,7 @@ class MultiHeadLatentAttention(nn.Module):
         c, k_rope = latents[..., :self.kv_latent].float(), latents[..., self.kv_latent:].float()
         q_lat = torch.einsum("rshn,hnl->rshl", q_nope.float(), w_uk.float())
         scores = torch.einsum("rshl,rtl->rsht", q_lat, c) + torch.einsum("rshd,rtd->rsht", q_rope.float(), k_rope)
-        scores = scores * (self.nope + self.rope) ** -0.5
+        scores = scores * (self.softmax_gain * (self.nope + self.rope) ** -0.5)
         t = torch.arange(latents.shape[1], device=latents.device)
         visible = (t[None, None, :] <= positions[:, :, None]) if self.causal else (t[None, None, :] < lengths[:, None, None])
         visible = visible & (t[None, None, :] < lengths[:, None, None])
@@ -96,7 +99,7 @@ class MultiHeadLatentAttention(nn.Module):
         qf = torch.cat([q_nope, q_rope], -1)
         kf = torch.cat([k_nope, k_rope.expand(B, T, H, self.rope)], -1)
         # pad v to the key width so one attention call serves both (the extra columns are dropped)
-        scale = (self.nope + self.rope) ** -0.5
+        scale = self.softmax_gain * (self.nope + self.rope) ** -0.5
         vpad = torch.nn.functional.pad(v, (0, self.nope + self.rope - self.vd)) if self.vd < self.nope + self.rope else v
         o = ops.attention(qf, kf, vpad, causal=self.causal, scale=scale, segment_ids=segment_ids)[..., :self.vd]
         return self.o_proj(o.reshape(B, T, H * self.vd))

@@ -458,13 +458,20 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 def rope_tables(max_pos: int, dim: int, theta: float = 10000.0, device="cpu", scaling: Optional[dict] = None):
-    """cos/sin tables ``[max_pos, dim/2]`` in fp32 (rotate-half convention). ``scaling`` supports
-    ``{"type": "linear", "factor": f}`` and Llama-3 style ``{"type": "llama3", factor, low_freq_factor,
-    high_freq_factor, original_max_position_embeddings}``."""
+    """cos/sin tables ``[max_pos, dim/2]`` in fp32 (rotate-half convention).  ``scaling`` (keyed by ``type`` or ``rope_type``):
+    ``linear`` (``factor``); ``llama3`` (``factor, low_freq_factor, high_freq_factor, original_max_position_embeddings``);
+    ``yarn`` (``factor, original_max_position_embeddings, beta_fast, beta_slow, mscale, mscale_all_dim, attention_factor, truncate``:
+    high frequencies extrapolate, low ones interpolate, a ramp between, and the tables carry the attention factor);
+    ``longrope`` (``short_factor`` / ``long_factor`` per frequency: the long set when the table is longer than
+    ``original_max_position_embeddings``, else the short one).  A kind this function does not know raises: silently unscaled positions
+    would read as a model that has forgotten its long context."""
     inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float64, device=device) / dim))
+    amplitude = 1.0
     if scaling:
         kind = scaling.get("type", scaling.get("rope_type", "linear"))
-        if kind == "linear":
+        if kind == "default":
+            pass
+        elif kind == "linear":
             inv = inv / scaling["factor"]
         elif kind == "llama3":
             f, lo, hi = scaling["factor"], scaling.get("low_freq_factor", 1.0), scaling.get("high_freq_factor", 4.0)
@@ -474,9 +481,40 @@ def rope_tables(max_pos: int, dim: int, theta: float = 10000.0, device="cpu", sc
             scaled = torch.where(wavelen > orig / lo, inv / f, inv)
             mid = (wavelen <= orig / lo) & (wavelen >= orig / hi)
             inv = torch.where(mid, (1 - smooth) * inv / f + smooth * inv, scaled)
+        elif kind == "yarn":
+            orig = scaling.get("original_max_position_embeddings") or max_pos
+            f = scaling.get("factor") or max_pos / orig
+
+            def magnitude(s, m=1.0):
+                return 1.0 if s <= 1 else 0.1 * m * math.log(s) + 1.0
+            amplitude = scaling.get("attention_factor")
+            if amplitude is None:
+                m, m_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+                amplitude = magnitude(f, m) / magnitude(f, m_all) if m and m_all else magnitude(f)
+
+            def turns_to_index(n):               # the frequency index whose wave makes n turns over the original context
+                return dim * math.log(orig / (n * 2 * math.pi)) / (2 * math.log(theta))
+            lo, hi = turns_to_index(scaling.get("beta_fast") or 32), turns_to_index(scaling.get("beta_slow") or 1)
+            if scaling.get("truncate", True):
+                lo, hi = math.floor(lo), math.ceil(hi)
+            lo, hi = max(lo, 0), min(hi, dim - 1)
+            if lo == hi:
+                hi += 0.001
+            keep = 1.0 - ((torch.arange(dim // 2, dtype=torch.float64, device=device) - lo) / (hi - lo)).clamp(0, 1)
+            inv = inv / f * (1 - keep) + inv * keep
+        elif kind == "longrope":
+            orig = scaling.get("original_max_position_embeddings") or max_pos
+            which = "long_factor" if max_pos > orig else "short_factor"
+            inv = inv / torch.tensor(scaling[which], dtype=torch.float64, device=device)
+            f = scaling.get("factor") or max_pos / orig
+            amplitude = scaling.get("attention_factor")
+            if amplitude is None:
+                amplitude = 1.0 if f <= 1 else math.sqrt(1 + math.log(f) / math.log(orig))
+        else:
+            raise ValueError(f"rotary scaling {kind!r} is not built (known: linear, llama3, yarn, longrope)")
     t = torch.arange(max_pos, dtype=torch.float64, device=device)
     ang = torch.outer(t, inv)
-    return ang.cos().float().contiguous(), ang.sin().float().contiguous()
+    return (ang.cos() * amplitude).float().contiguous(), (ang.sin() * amplitude).float().contiguous()
 
 
 def rope_reference(x, cos, sin, positions=None, rot_heads=None):

@@ -30,6 +30,12 @@ CASES = {
                    rope_parameters={"sliding_attention": {"rope_type": "default", "rope_theta": 1000.0},
                                     "full_attention": {"rope_type": "linear", "rope_theta": 50000.0, "factor": 2.0}}, **COMMON),
     "granite": dict(model_type="granite", embedding_multiplier=6.0, attention_multiplier=0.1, residual_multiplier=0.3, logits_scaling=4.0, **COMMON),
+    "deepseek_v3": dict(model_type="deepseek_v3", vocab_size=96, hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4,
+                        intermediate_size=128, max_position_embeddings=64, moe_intermediate_size=32, n_routed_experts=8, num_experts_per_tok=3,
+                        n_group=4, topk_group=2, n_shared_experts=2, routed_scaling_factor=2.5, first_k_dense_replace=1, q_lora_rank=24,
+                        kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, pad_token_id=0,
+                        rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 16,
+                                         "beta_fast": 32.0, "beta_slow": 1.0, "mscale": 1.0, "mscale_all_dim": 1.0}),
     "mixtral": dict(model_type="mixtral", num_local_experts=4, num_experts_per_tok=2, **COMMON),
     "qwen3_moe": dict(model_type="qwen3_moe", head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
                       norm_topk_prob=True, **COMMON),
@@ -113,3 +119,30 @@ def test_release_reads_lazily_and_dequantizes_fp8_blocks(tmp_path):
     raw = Release(tmp_path, dequantize=False)
     assert raw["model.layers.0.mlp.down_proj.weight"].dtype == torch.float8_e4m3fn
     assert "model.layers.0.mlp.down_proj.weight_scale_inv" in raw
+
+
+def test_rotary_scalings_match_transformers():
+    transformers = pytest.importorskip("transformers")
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+    from dew_b200 import ops
+    yarns = [dict(rope_type="yarn", rope_theta=10000.0, factor=8.0, original_max_position_embeddings=16, beta_fast=32.0, beta_slow=1.0),
+             dict(rope_type="yarn", rope_theta=50000.0, factor=8.0, original_max_position_embeddings=16, mscale=0.7, mscale_all_dim=1.0, truncate=False)]
+    for rp in yarns:
+        cfg = transformers.LlamaConfig(hidden_size=64, num_attention_heads=4, head_dim=16, max_position_embeddings=128, rope_parameters=dict(rp))
+        inv, gain = ROPE_INIT_FUNCTIONS["yarn"](cfg, "cpu")
+        ang = torch.outer(torch.arange(128).double(), inv.double())
+        cos, sin = ops.rope_tables(128, 16, rp["rope_theta"], "cpu", {k: v for k, v in rp.items() if k != "rope_theta"})
+        assert float((cos - (ang.cos() * gain).float()).abs().max()) < 5e-6 and float((sin - (ang.sin() * gain).float()).abs().max()) < 5e-6
+    rp = dict(rope_type="longrope", rope_theta=10000.0, short_factor=[1.0 + 0.1 * i for i in range(8)], long_factor=[2.0 + 0.3 * i for i in range(8)],
+              original_max_position_embeddings=32)
+    cfg = transformers.Phi3Config(hidden_size=64, num_attention_heads=4, max_position_embeddings=128, original_max_position_embeddings=32,
+                                  rope_parameters=dict(rp), pad_token_id=0)
+    inv, gain = ROPE_INIT_FUNCTIONS["longrope"](cfg, "cpu", seq_len=100)
+    ang = torch.outer(torch.arange(128).double(), inv.double())
+    cos, _ = ops.rope_tables(128, 16, 10000.0, "cpu", {k: v for k, v in rp.items() if k != "rope_theta"})
+    assert float((cos - (ang.cos() * gain).float()).abs().max()) < 5e-6
+    short, _ = ops.rope_tables(32, 16, 10000.0, "cpu", {k: v for k, v in rp.items() if k != "rope_theta"})      # within the original context: the short set
+    want = torch.outer(torch.arange(32).double(), 1.0 / (torch.tensor(rp["short_factor"]).double() * 10000.0 ** (torch.arange(0, 16, 2).double() / 16))).cos()
+    assert float((short - want.float()).abs().max()) < 1e-6
+    with pytest.raises(ValueError, match="not built"):
+        ops.rope_tables(32, 16, 10000.0, "cpu", {"rope_type": "dynamic", "factor": 2.0})
