@@ -8,7 +8,7 @@ Families: llama, mistral, qwen2 (q/k/v bias), qwen3 (per-head q/k norm), qwen3_m
 minus one, GeGLU, scaled embeddings), gemma2 (output norms on every sub-layer, soft-capped logits, alternating local /
 global layers, query scale), phi3 (fused qkv and gate_up on disk), granite (embedding / attention / residual multipliers, logits scaling), olmo2 (no pre-norms: every sub-layer's output is
 normalised instead; q and k normalised over all heads at once), olmo3 (olmo2 with sliding layers on an unscaled rotary table), gemma3 (gemma2's
-block with per-head q/k norms and one rotary base per layer kind), smollm3 (every fourth layer attends without positions), deepseek_v3 (latent attention stored with
+block with per-head q/k norms and one rotary base per layer kind), smollm3 (every fourth layer attends without positions), glm4 (half of every head rotates, as pairs; output norms; fused gate_up), deepseek_v3 (latent attention stored with
 interleaved rotary pairs, dense layers first, then sigmoid-routed experts in groups with a selection bias beside shared experts).
 
 Reference: src/dew/interop/decoder_families.py, decoder_config.py, decoder_parts.py (family tables), unread.py (keys
@@ -68,6 +68,7 @@ class Family:
     mixer_out_norm: Optional[str] = None                  # Gemma-2: norm on the attention output
     mlp_out_norm: Optional[str] = None                    # Gemma-2: norm on the MLP output
     pre_norm: bool = True                                 # False (OLMo-2): no input / pre-MLP norms on disk
+    rotary_pairs: bool = False                            # the release rotates pairs (2i, 2i + 1) of a head, not its halves
     experts: Optional[str] = None                         # 'mixtral' | 'qwen' naming of sparse layers
     extra_config: Mapping[str, Any] = field(default_factory=dict)   # written into ``config.json`` on export
 
@@ -182,6 +183,12 @@ def _deepseek_v3(cfg):
     return _common(cfg, head_dim=int(cfg["qk_rope_head_dim"]), layer_types=("mla",), mixture=mix, mixer_options=options)
 
 
+def _glm4(cfg):
+    rope = cfg.get("rope_parameters") or {}
+    return _common(cfg, qkv_bias=bool(cfg.get("attention_bias", True)), sandwich_norm=True,
+                   rotary_fraction=float(rope.get("partial_rotary_factor", cfg.get("partial_rotary_factor", 0.5))))
+
+
 def _granite(cfg):
     # four scalars: embeddings times one, the softmax scale itself (not 1 / sqrt(d)), every branch times one, logits over one
     return _common(cfg, embed_multiplier=float(cfg.get("embedding_multiplier", 1.0)), query_scale=float(cfg.get("attention_multiplier", 1.0)),
@@ -209,6 +216,8 @@ FAMILIES: Dict[str, Family] = {f.name: f for f in (
            post_attention_norm="pre_feedforward_layernorm", mlp_out_norm="post_feedforward_layernorm",
            extra_config={"hidden_activation": "gelu_pytorch_tanh"}),
     Family("deepseek_v3", ("deepseek_v3",), "DeepseekV3ForCausalLM", _deepseek_v3, experts="deepseek"),
+    Family("glm4", ("glm4",), "Glm4ForCausalLM", _glm4, qkv_bias=True, rotary_pairs=True, fused_gate_up="mlp.gate_up_proj",
+           mixer_out_norm="post_self_attn_layernorm", mlp_out_norm="post_mlp_layernorm"),
     Family("phi3", ("phi3",), "Phi3ForCausalLM", _phi3, fused_qkv="self_attn.qkv_proj", fused_gate_up="mlp.gate_up_proj"),
 )}
 
@@ -271,6 +280,9 @@ def write_config(c: TransformerConfig, family: str = "llama", dtype: str = "bflo
                     "moe_layer_freq": 1, "kv_lora_rank": o["kv_latent"], "q_lora_rank": o.get("q_latent"), "qk_nope_head_dim": o["nope_dim"],
                     "qk_rope_head_dim": o["rope_dim"], "v_head_dim": o["v_dim"], "head_dim": o["rope_dim"],
                     "num_key_value_heads": c.num_heads, "rope_interleave": True})
+    if fam.name == "glm4":
+        out.update({"attention_bias": c.qkv_bias, "partial_rotary_factor": c.rotary_fraction})
+        out["rope_parameters"] = {**out["rope_parameters"], "partial_rotary_factor": c.rotary_fraction}
     if fam.name == "qwen2":
         out["use_sliding_window"] = c.window is not None
     if fam.name == "granite":
@@ -326,12 +338,14 @@ def load_state(model: CausalTransformer, tensors: Mapping[str, torch.Tensor], fa
         if hasattr(a, "kv_latent"):
             _load_latent_attention(a, get, pre + "self_attn.")
         else:
+            order = head_order(a.head_dim, int(a.head_dim * model.config.rotary_fraction), family.rotary_pairs)
+            shape = (a.num_heads, a.num_kv_heads, a.head_dim, order)
             if family.fused_qkv:
-                _put(a.qkv_proj.weight, get(pre + family.fused_qkv + ".weight"))
+                _put(a.qkv_proj.weight, _reorder_qk(get(pre + family.fused_qkv + ".weight"), *shape))
             else:
-                _put(a.qkv_proj.weight, torch.cat([get(pre + f"self_attn.{n}_proj.weight") for n in "qkv"], 0))
+                _put(a.qkv_proj.weight, _reorder_qk(torch.cat([get(pre + f"self_attn.{n}_proj.weight") for n in "qkv"], 0), *shape))
             if a.qkv_proj.bias is not None:
-                _put(a.qkv_proj.bias, torch.cat([get(pre + f"self_attn.{n}_proj.bias") for n in "qkv"], 0))
+                _put(a.qkv_proj.bias, _reorder_qk(torch.cat([get(pre + f"self_attn.{n}_proj.bias") for n in "qkv"], 0), *shape))
             _put(a.o_proj.weight, get(pre + "self_attn.o_proj.weight"))
             if a.q_norm is not None:
                 _put(a.q_norm.weight, get(pre + "self_attn.q_norm.weight"), off)
@@ -353,6 +367,26 @@ def load_state(model: CausalTransformer, tensors: Mapping[str, torch.Tensor], fa
     if strict and left:
         raise KeyError(f"{len(left)} tensor(s) of the release were not read by the {family.name} mapping: {left[:6]}")
     return left
+
+
+def head_order(D: int, R: int, pairs: bool) -> Optional[torch.Tensor]:
+    """Where each dimension of a head as this library lays it out, ``[rotated a | kept a | rotated b | kept b]``, sits in the release's
+    head, which rotates its first ``R`` dimensions as pairs ``(2i, 2i + 1)`` or as halves ``(i, i + R / 2)``.  None: the same order."""
+    if R >= D and not pairs:
+        return None
+    a, b = (torch.arange(0, R, 2), torch.arange(1, R, 2)) if pairs else (torch.arange(0, R // 2), torch.arange(R // 2, R))
+    keep = (D - R) // 2
+    return torch.cat([a, torch.arange(R, R + keep), b, torch.arange(R + keep, D)])
+
+
+def _reorder_qk(t: torch.Tensor, H: int, Hkv: int, D: int, order: Optional[torch.Tensor], back: bool = False) -> torch.Tensor:
+    """Rows of a packed q | k | v weight or bias with every q and k head's dimensions reordered (``back``: undone)."""
+    if order is None:
+        return t
+    idx = torch.argsort(order) if back else order
+    heads = t.reshape(H + 2 * Hkv, D, -1).clone()
+    heads[: H + Hkv] = heads[: H + Hkv][:, idx]
+    return heads.reshape(t.shape)
 
 
 def _pairs_to_halves(rope: int) -> torch.Tensor:
@@ -443,14 +477,15 @@ def export_state(model: CausalTransformer, family: Family) -> Dict[str, torch.Te
         if hasattr(a, "kv_latent"):
             _export_latent_attention(a, out, pre + "self_attn.")
         else:
-            w = a.qkv_proj.weight.detach()
+            order = head_order(D, int(D * c.rotary_fraction), family.rotary_pairs)
+            w = _reorder_qk(a.qkv_proj.weight.detach(), H, Hkv, D, order, back=True)
             if family.fused_qkv:
                 out[pre + family.fused_qkv + ".weight"] = w
             else:
                 for n, part in zip("qkv", (w[: H * D], w[H * D:(H + Hkv) * D], w[(H + Hkv) * D:])):
                     out[pre + f"self_attn.{n}_proj.weight"] = part
             if a.qkv_proj.bias is not None:
-                b = a.qkv_proj.bias.detach()
+                b = _reorder_qk(a.qkv_proj.bias.detach(), H, Hkv, D, order, back=True)
                 for n, part in zip("qkv", (b[: H * D], b[H * D:(H + Hkv) * D], b[(H + Hkv) * D:])):
                     out[pre + f"self_attn.{n}_proj.bias"] = part
             out[pre + "self_attn.o_proj.weight"] = a.o_proj.weight.detach()

@@ -99,6 +99,7 @@ class TransformerConfig:
     query_scale: Optional[float] = None               # softmax scale other than head_dim ** -0.5 (Gemma-2's query_pre_attn_scalar ** -0.5)
     loop: Optional[Loop] = None                       # a block of layers run several times (a looped / recurrent-depth decoder)
     local_rope_theta: Optional[float] = None          # Gemma-3 / OLMo-3: 'local' layers rotate by this base, unscaled; the others by rope_theta with rope_scaling
+    rotary_fraction: float = 1.0                      # GLM / Phi / NeoX: only this share of a head's width rotates; heads are laid out [rotated a | kept a | rotated b | kept b]
     pre_norm: bool = True                             # False (OLMo-2): sub-layers read the stream as it is; only their outputs are normalised (sandwich_norm)
     qk_norm_full: bool = False                        # OLMo-2: q and k normalised over all heads at once
     embed_multiplier: Optional[float] = None          # Granite: embeddings times this (embed_scale is the sqrt(d) special case)
@@ -334,7 +335,8 @@ class CausalTransformer(nn.Module):
         dev = torch.device(device)
         if self._rope is None or self._rope[0].device != dev:
             hd = cfg.head_dim or cfg.emb_features // cfg.num_heads
-            self._rope = ops.rope_tables(cfg.max_seq_len, hd, cfg.rope_theta, dev, cfg.rope_scaling)
+            rot = None if cfg.rotary_fraction >= 1.0 else int(hd * cfg.rotary_fraction)
+            self._rope = ops.rope_tables(cfg.max_seq_len, hd, cfg.rope_theta, dev, cfg.rope_scaling, rotary_dim=rot)
         return self._rope
 
     def _finish(self, h, branch):

@@ -457,14 +457,21 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 # RoPE
 
 
-def rope_tables(max_pos: int, dim: int, theta: float = 10000.0, device="cpu", scaling: Optional[dict] = None):
-    """cos/sin tables ``[max_pos, dim/2]`` in fp32 (rotate-half convention).  ``scaling`` (keyed by ``type`` or ``rope_type``):
+def rope_tables(max_pos: int, dim: int, theta: float = 10000.0, device="cpu", scaling: Optional[dict] = None, rotary_dim: Optional[int] = None):
+    """cos/sin tables ``[max_pos, dim/2]`` in fp32 (rotate-half convention).  ``rotary_dim < dim`` (partial rotary): the frequencies are
+    those of a ``rotary_dim``-wide rotation and fill the first ``rotary_dim / 2`` columns; the others hold the identity (cos 1, sin 0),
+    so a head laid out ``[rotated a | kept a | rotated b | kept b]`` passes its kept dimensions through the same kernel unchanged.  ``scaling`` (keyed by ``type`` or ``rope_type``):
     ``linear`` (``factor``); ``llama3`` (``factor, low_freq_factor, high_freq_factor, original_max_position_embeddings``);
     ``yarn`` (``factor, original_max_position_embeddings, beta_fast, beta_slow, mscale, mscale_all_dim, attention_factor, truncate``:
     high frequencies extrapolate, low ones interpolate, a ramp between, and the tables carry the attention factor);
     ``longrope`` (``short_factor`` / ``long_factor`` per frequency: the long set when the table is longer than
     ``original_max_position_embeddings``, else the short one).  A kind this function does not know raises: silently unscaled positions
     would read as a model that has forgotten its long context."""
+    full = dim
+    if rotary_dim is not None and rotary_dim < dim:
+        if rotary_dim % 2 or (dim - rotary_dim) % 2:
+            raise ValueError(f"partial rotary wants even widths, got {rotary_dim} of {dim}")
+        dim = rotary_dim
     inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float64, device=device) / dim))
     amplitude = 1.0
     if scaling:
@@ -514,7 +521,11 @@ def rope_tables(max_pos: int, dim: int, theta: float = 10000.0, device="cpu", sc
             raise ValueError(f"rotary scaling {kind!r} is not built (known: linear, llama3, yarn, longrope)")
     t = torch.arange(max_pos, dtype=torch.float64, device=device)
     ang = torch.outer(t, inv)
-    return (ang.cos() * amplitude).float().contiguous(), (ang.sin() * amplitude).float().contiguous()
+    cos, sin = ang.cos() * amplitude, ang.sin() * amplitude
+    if full != dim:
+        cos = torch.cat([cos, torch.ones(max_pos, (full - dim) // 2, dtype=cos.dtype, device=cos.device)], 1)
+        sin = torch.cat([sin, torch.zeros(max_pos, (full - dim) // 2, dtype=sin.dtype, device=sin.device)], 1)
+    return cos.float().contiguous(), sin.float().contiguous()
 
 
 def rope_reference(x, cos, sin, positions=None, rot_heads=None):

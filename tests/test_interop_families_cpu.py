@@ -36,6 +36,7 @@ CASES = {
                         kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, pad_token_id=0,
                         rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 16,
                                          "beta_fast": 32.0, "beta_slow": 1.0, "mscale": 1.0, "mscale_all_dim": 1.0}),
+    "glm4": dict(model_type="glm4", head_dim=16, pad_token_id=0, **COMMON),
     "mixtral": dict(model_type="mixtral", num_local_experts=4, num_experts_per_tok=2, **COMMON),
     "qwen3_moe": dict(model_type="qwen3_moe", head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
                       norm_topk_prob=True, **COMMON),
