@@ -148,10 +148,21 @@ class Pretrained:
     ``config.json``; ``interop.release`` reads one file or shards, de-quantising stored fp8 blocks)."""
 
     @staticmethod
-    def load(directory: os.PathLike, dtype=None, device="cpu", strict: bool = True) -> CausalTransformer:
+    def load(directory: os.PathLike, dtype=None, device="cpu", strict: bool = True):
+        """A ``CausalTransformer`` for the families of ``interop.families``; a ``ClassicDecoder`` for the older lineage of
+        ``interop.classic`` (GPT-2, GPT-NeoX, Falcon, Phi, OPT, BLOOM, StarCoder2, GPTBigCode)."""
+        from .classic import CLASSIC, load_classic_state, read_classic_config
         from .families import family_of, load_state, read_config
         from .release import GenerationConfig, Release
         rel = Release(directory, dtype=dtype or torch.bfloat16)
+        if str(rel.config.get("model_type") or "").lower() in CLASSIC:
+            from ..models.classic_decoder import ClassicDecoder
+            fam = CLASSIC[str(rel.config["model_type"]).lower()]
+            model = ClassicDecoder(read_classic_config(rel.config), dtype=dtype, device=device)
+            model.unread_keys = load_classic_state(model, rel, fam, strict=strict)
+            model.generation_config = GenerationConfig.read(directory)
+            model.family = fam.name
+            return model
         fam = family_of(rel.config)
         model = CausalTransformer(read_config(rel.config), dtype=dtype, device=device)
         model.unread_keys = load_state(model, rel, fam, strict=strict)

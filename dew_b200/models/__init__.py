@@ -19,4 +19,7 @@ def __getattr__(name):
     if name in ("VisionLanguageModel", "AudioEncoder", "Projector", "log_mel"):
         from . import multimodal as m
         return getattr(m, name)
+    if name in ("ClassicDecoder", "ClassicConfig"):
+        from . import classic_decoder as m
+        return getattr(m, name)
     raise AttributeError(name)

@@ -47,6 +47,7 @@ _STATIC: Dict[str, Dict[str, str]] = {
         "kl_vae": "dew_b200.models.autoencoders:KLAutoEncoder", "vit": "dew_b200.models.autoencoders:ViT",
         "autoencoder_kl": "dew_b200.models.latent_autoencoders:AutoencoderKL", "dc_ae": "dew_b200.models.latent_autoencoders:DCAE",
         "causal_video_vae": "dew_b200.models.latent_autoencoders:CausalVideoVAE",
+        "classic_decoder": "dew_b200.models.classic_decoder:ClassicDecoder",
     },
     "objective": {
         "lm": "dew_b200.objectives.lm:LMObjective",
