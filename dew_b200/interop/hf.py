@@ -150,7 +150,8 @@ class Pretrained:
     @staticmethod
     def load(directory: os.PathLike, dtype=None, device="cpu", strict: bool = True):
         """A ``CausalTransformer`` for the families of ``interop.families``; a ``ClassicDecoder`` for the older lineage of
-        ``interop.classic`` (GPT-2, GPT-NeoX, Falcon, Phi, OPT, BLOOM, StarCoder2, GPTBigCode)."""
+        ``interop.classic`` (GPT-2, GPT-NeoX, Falcon, Phi, OPT, BLOOM, StarCoder2, GPTBigCode); Mamba and Mamba-2 releases through
+        ``interop.recurrent``."""
         from .classic import CLASSIC, load_classic_state, read_classic_config
         from .families import family_of, load_state, read_config
         from .release import GenerationConfig, Release
@@ -162,6 +163,13 @@ class Pretrained:
             model.unread_keys = load_classic_state(model, rel, fam, strict=strict)
             model.generation_config = GenerationConfig.read(directory)
             model.family = fam.name
+            return model
+        if str(rel.config.get("model_type") or "").lower() in ("mamba", "mamba2"):
+            from .recurrent import load_recurrent_state, read_recurrent_config
+            model = CausalTransformer(read_recurrent_config(rel.config), dtype=dtype, device=device)
+            model.unread_keys = load_recurrent_state(model, rel, strict=strict)
+            model.generation_config = GenerationConfig.read(directory)
+            model.family = str(rel.config["model_type"]).lower()
             return model
         fam = family_of(rel.config)
         model = CausalTransformer(read_config(rel.config), dtype=dtype, device=device)

@@ -100,6 +100,8 @@ class TransformerConfig:
     loop: Optional[Loop] = None                       # a block of layers run several times (a looped / recurrent-depth decoder)
     local_rope_theta: Optional[float] = None          # Gemma-3 / OLMo-3: 'local' layers rotate by this base, unscaled; the others by rope_theta with rope_scaling
     rotary_fraction: float = 1.0                      # GLM / Phi / NeoX: only this share of a head's width rotates; heads are laid out [rotated a | kept a | rotated b | kept b]
+    layer_mlp: Optional[Sequence[bool]] = None        # per layer (cycled like layer_types): False - the layer is its mixer alone (Mamba's blocks); with the
+                                                      # mixer kind 'none', a layer that is its MLP alone (Nemotron-H's and Jamba's separate blocks)
     pre_norm: bool = True                             # False (OLMo-2): sub-layers read the stream as it is; only their outputs are normalised (sandwich_norm)
     qk_norm_full: bool = False                        # OLMo-2: q and k normalised over all heads at once
     embed_multiplier: Optional[float] = None          # Granite: embeddings times this (embed_scale is the sqrt(d) special case)
@@ -190,12 +192,20 @@ class DecoderLayer(nn.Module):
         self.kind, self.index = kind, index
         if not cfg.pre_norm and not cfg.sandwich_norm:
             raise ValueError("a decoder without pre-norms normalises its sub-layers' outputs: set sandwich_norm=True with pre_norm=False")
+        self.has_mlp = True if cfg.layer_mlp is None else bool(list(cfg.layer_mlp)[index % len(cfg.layer_mlp)])
+        if kind == "none" and not self.has_mlp:
+            raise ValueError(f"layer {index} has neither a mixer nor an MLP")
+        if (kind == "none" or not self.has_mlp) and (cfg.sandwich_norm or not cfg.pre_norm or cfg.hyper_connections > 1 or cfg.altup > 1):
+            raise NotImplementedError("layers of one sub-layer are built for the plain pre-norm block")
         self.input_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device) if cfg.pre_norm else _NoNorm()
-        self.mixer = _mixer(cfg, kind, dtype, device, index)
-        self.post_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device) if cfg.pre_norm else _NoNorm()
+        self.mixer = None if kind == "none" else _mixer(cfg, kind, dtype, device, index)
+        one = kind == "none" or not self.has_mlp                  # one sub-layer: the input norm is its only norm
+        self.post_norm = None if one else (RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device) if cfg.pre_norm else _NoNorm())
         mix = cfg.mixture
-        sparse = mix is not None and (mix.layers is None or index in mix.layers)
-        if sparse:
+        sparse = self.has_mlp and mix is not None and (mix.layers is None or index in mix.layers)
+        if not self.has_mlp:
+            self.mlp = None
+        elif sparse:
             from ..nn.moe import SparseMLP
             self.mlp = SparseMLP(cfg.emb_features, mix, cfg.mlp_features or 4 * cfg.emb_features, init_std=cfg.init_std,
                                  dtype=dtype, device=device)
@@ -253,10 +263,14 @@ class DecoderLayer(nn.Module):
                 n = copy_to_region(n, self.tp.group)
         else:
             n, h = self._norm(self.input_norm, h, branch)
+        if self.mixer is None:                                    # the MLP alone
+            return h, self.mlp(n) if self.residual_multiplier == 1.0 else self.mlp(n) * self.residual_multiplier
         if self.kind in ROTARY_KINDS:
             a = self.mixer(n, cos, sin, positions, segment_ids, cache, self.index)
         else:
             a = self.mixer(n, segment_ids=segment_ids, cache=cache, layer=self.index)
+        if self.mlp is None:                                      # the mixer alone
+            return h, a if self.residual_multiplier == 1.0 else a * self.residual_multiplier
         if self.mixer_out_norm is not None:
             a = self.mixer_out_norm(a)
         if self.residual_multiplier != 1.0:
