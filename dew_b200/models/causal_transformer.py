@@ -102,6 +102,7 @@ class TransformerConfig:
     rotary_fraction: float = 1.0                      # GLM / Phi / NeoX: only this share of a head's width rotates; heads are laid out [rotated a | kept a | rotated b | kept b]
     layer_mlp: Optional[Sequence[bool]] = None        # per layer (cycled like layer_types): False - the layer is its mixer alone (Mamba's blocks); with the
                                                       # mixer kind 'none', a layer that is its MLP alone (Nemotron-H's and Jamba's separate blocks)
+    engram: Optional[Dict[str, Any]] = None           # {'layers': [i, ...], **Engram fields}: hashed n-gram memories gated into the stream in front of those layers
     pre_norm: bool = True                             # False (OLMo-2): sub-layers read the stream as it is; only their outputs are normalised (sandwich_norm)
     qk_norm_full: bool = False                        # OLMo-2: q and k normalised over all heads at once
     embed_multiplier: Optional[float] = None          # Granite: embeddings times this (embed_scale is the sqrt(d) special case)
@@ -318,6 +319,12 @@ class CausalTransformer(nn.Module):
         self.mtp = nn.ModuleList([MTPBlock(cfg, i, dtype, device) for i in range(cfg.mtp_depth)]) if cfg.mtp_depth > 0 else None
         self.early_exit_gate = Linear(cfg.emb_features, 1, bias=True, init_std=cfg.init_std, dtype=dtype, device=device) \
             if cfg.loop is not None and cfg.loop.exit_gate else None
+        self.engrams = None
+        if cfg.engram:
+            from ..nn.engram import Engram
+            fields = {k: v for k, v in cfg.engram.items() if k != "layers"}
+            self.engrams = nn.ModuleDict({str(i): Engram(cfg.emb_features, cfg.vocab_size, layer=i, norm_eps=cfg.norm_eps, dtype=dtype, device=device, **fields)
+                                          for i in cfg.engram.get("layers", (0,))})
         self._rope = None
 
     def mtp_hiddens(self, hidden: torch.Tensor, tokens: torch.Tensor, segment_ids=None) -> List[torch.Tensor]:
@@ -438,7 +445,13 @@ class CausalTransformer(nn.Module):
         if passes:
             raise ValueError("per-pass exits need a looped decoder (TransformerConfig(loop=Loop(...)))")
         branch = None
+        if self.engrams is not None and (cache is not None or tokens is None or getattr(self, "tp", None) is not None):
+            raise NotImplementedError("n-gram memories read the token ids behind each position: they run on whole sequences given as tokens, without "
+                                      "a KV cache and without tensor parallelism")
         for layer in self.layers:
+            if self.engrams is not None and str(layer.index) in self.engrams:
+                h = h if branch is None else h + branch               # the memory's gate reads the stream as the layer will see it
+                h, branch = self.engrams[str(layer.index)](h, tokens, segment_ids), None
             if cfg.remat and train and torch.is_grad_enabled():
                 h, branch = ckpt.checkpoint(layer, h, branch, cos, sin, positions, segment_ids, cache, use_reentrant=False)
             else:
