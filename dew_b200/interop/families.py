@@ -8,7 +8,7 @@ Families: llama, mistral, qwen2 (q/k/v bias), qwen3 (per-head q/k norm), qwen3_m
 minus one, GeGLU, scaled embeddings), gemma2 (output norms on every sub-layer, soft-capped logits, alternating local /
 global layers, query scale), phi3 (fused qkv and gate_up on disk), granite (embedding / attention / residual multipliers, logits scaling), olmo2 (no pre-norms: every sub-layer's output is
 normalised instead; q and k normalised over all heads at once), olmo3 (olmo2 with sliding layers on an unscaled rotary table), gemma3 (gemma2's
-block with per-head q/k norms and one rotary base per layer kind), smollm3 (every fourth layer attends without positions), glm4 (half of every head rotates, as pairs; output norms; fused gate_up), deepseek_v3 (latent attention stored with
+block with per-head q/k norms and one rotary base per layer kind), smollm3 (every fourth layer attends without positions), glm4 (half of every head rotates, as pairs; output norms; fused gate_up), gpt_oss (attention sinks and biases, sliding / full layers, a router over the top logits, biased clamped-GLU experts stored interleaved), deepseek_v3 (latent attention stored with
 interleaved rotary pairs, dense layers first, then sigmoid-routed experts in groups with a selection bias beside shared experts).
 
 Reference: src/dew/interop/decoder_families.py, decoder_config.py, decoder_parts.py (family tables), unread.py (keys
@@ -189,6 +189,12 @@ def _glm4(cfg):
                    rotary_fraction=float(rope.get("partial_rotary_factor", cfg.get("partial_rotary_factor", 0.5))))
 
 
+def _gpt_oss(cfg):
+    mix = Mixture(experts=int(cfg["num_local_experts"]), top_k=int(cfg.get("num_experts_per_tok", 4)), expert_features=int(cfg["intermediate_size"]),
+                  style="clamped_glu")
+    return _common(cfg, attn_bias=True, attention_sinks=True, window=cfg.get("sliding_window"), layer_types=_layer_kinds(cfg), mixture=mix)
+
+
 def _granite(cfg):
     # four scalars: embeddings times one, the softmax scale itself (not 1 / sqrt(d)), every branch times one, logits over one
     return _common(cfg, embed_multiplier=float(cfg.get("embedding_multiplier", 1.0)), query_scale=float(cfg.get("attention_multiplier", 1.0)),
@@ -218,6 +224,7 @@ FAMILIES: Dict[str, Family] = {f.name: f for f in (
     Family("deepseek_v3", ("deepseek_v3",), "DeepseekV3ForCausalLM", _deepseek_v3, experts="deepseek"),
     Family("glm4", ("glm4",), "Glm4ForCausalLM", _glm4, qkv_bias=True, rotary_pairs=True, fused_gate_up="mlp.gate_up_proj",
            mixer_out_norm="post_self_attn_layernorm", mlp_out_norm="post_mlp_layernorm"),
+    Family("gpt_oss", ("gpt_oss",), "GptOssForCausalLM", _gpt_oss, qkv_bias=True, experts="gpt_oss"),
     Family("phi3", ("phi3",), "Phi3ForCausalLM", _phi3, fused_qkv="self_attn.qkv_proj", fused_gate_up="mlp.gate_up_proj"),
 )}
 
@@ -260,7 +267,7 @@ def write_config(c: TransformerConfig, family: str = "llama", dtype: str = "bflo
         out.update({"attn_logit_softcapping": c.attn_softcap or None, "final_logit_softcapping": c.logit_softcap or None,
                     "query_pre_attn_scalar": (c.query_scale ** -2) if c.query_scale else out["head_dim"]})
     kinds = c.kinds()
-    if fam.name in ("gemma3", "olmo3", "smollm3"):
+    if fam.name in ("gemma3", "olmo3", "smollm3", "gpt_oss"):
         out["layer_types"] = ["sliding_attention" if k == "local" else "full_attention" for k in kinds]
     if fam.name == "gemma3":
         full = {"rope_type": "default", **(c.rope_scaling or {}), "rope_theta": c.rope_theta}
@@ -347,10 +354,16 @@ def load_state(model: CausalTransformer, tensors: Mapping[str, torch.Tensor], fa
             if a.qkv_proj.bias is not None:
                 _put(a.qkv_proj.bias, _reorder_qk(torch.cat([get(pre + f"self_attn.{n}_proj.bias") for n in "qkv"], 0), *shape))
             _put(a.o_proj.weight, get(pre + "self_attn.o_proj.weight"))
+            if a.o_proj.bias is not None:
+                _put(a.o_proj.bias, get(pre + "self_attn.o_proj.bias"))
+            if a.sinks is not None:
+                _put(a.sinks, get(pre + "self_attn.sinks"))
             if a.q_norm is not None:
                 _put(a.q_norm.weight, get(pre + "self_attn.q_norm.weight"), off)
                 _put(a.k_norm.weight, get(pre + "self_attn.k_norm.weight"), off)
-        if getattr(layer, "sparse", False):
+        if getattr(layer, "sparse", False) and family.experts == "gpt_oss":
+            _load_clamped_glu(layer.mlp, get, pre + "mlp.")
+        elif getattr(layer, "sparse", False):
             _load_experts(layer.mlp, get, pre)
         elif family.fused_gate_up:
             _put(layer.mlp.gate_up_proj.weight, get(pre + family.fused_gate_up + ".weight"))
@@ -430,6 +443,27 @@ def _export_latent_attention(a, out: Dict[str, torch.Tensor], pre: str) -> None:
     out[pre + "kv_b_proj.weight"], out[pre + "o_proj.weight"] = a.kv_up.weight.detach(), a.o_proj.weight.detach()
 
 
+def _load_clamped_glu(mlp, get: _Reader, pre: str) -> None:
+    """GPT-OSS stores ``gate_up_proj [E, d, 2F]`` input-major with gate and linear columns interleaved, ``down_proj [E, F, d]``."""
+    _put(mlp.router.weight, get(pre + "router.weight"))
+    _put(mlp.router.bias, get(pre + "router.bias"))
+    gu, gb = get(pre + "experts.gate_up_proj"), get(pre + "experts.gate_up_proj_bias")
+    _put(mlp.experts.gate_up, torch.cat([gu[..., 0::2], gu[..., 1::2]], -1).transpose(1, 2))
+    _put(mlp.experts.gate_up_bias, torch.cat([gb[..., 0::2], gb[..., 1::2]], -1))
+    _put(mlp.experts.down, get(pre + "experts.down_proj").transpose(1, 2))
+    _put(mlp.experts.down_bias, get(pre + "experts.down_proj_bias"))
+
+
+def _export_clamped_glu(mlp, out: Dict[str, torch.Tensor], pre: str) -> None:
+    out[pre + "router.weight"], out[pre + "router.bias"] = mlp.router.weight.detach(), mlp.router.bias.detach()
+    gu, gb = mlp.experts.gate_up.detach().transpose(1, 2), mlp.experts.gate_up_bias.detach()       # [E, d, 2F] halves, [E, 2F]
+    Fh = gb.shape[-1] // 2
+    out[pre + "experts.gate_up_proj"] = torch.stack([gu[..., :Fh], gu[..., Fh:]], -1).flatten(-2)
+    out[pre + "experts.gate_up_proj_bias"] = torch.stack([gb[..., :Fh], gb[..., Fh:]], -1).flatten(-2)
+    out[pre + "experts.down_proj"] = mlp.experts.down.detach().transpose(1, 2)
+    out[pre + "experts.down_proj_bias"] = mlp.experts.down_bias.detach()
+
+
 def _load_experts(mlp, get: _Reader, pre: str) -> None:
     E = mlp.mix.experts
     if get.has(pre + "mlp.gate.e_score_correction_bias"):
@@ -489,6 +523,10 @@ def export_state(model: CausalTransformer, family: Family) -> Dict[str, torch.Te
                 for n, part in zip("qkv", (b[: H * D], b[H * D:(H + Hkv) * D], b[(H + Hkv) * D:])):
                     out[pre + f"self_attn.{n}_proj.bias"] = part
             out[pre + "self_attn.o_proj.weight"] = a.o_proj.weight.detach()
+            if a.o_proj.bias is not None:
+                out[pre + "self_attn.o_proj.bias"] = a.o_proj.bias.detach()
+            if a.sinks is not None:
+                out[pre + "self_attn.sinks"] = a.sinks.detach()
             if a.q_norm is not None:
                 out[pre + "self_attn.q_norm.weight"] = norm(a.q_norm.weight)
                 out[pre + "self_attn.k_norm.weight"] = norm(a.k_norm.weight)
@@ -499,6 +537,9 @@ def export_state(model: CausalTransformer, family: Family) -> Dict[str, torch.Te
                 sw = m.shared.gate_up_proj.weight.detach()
                 out[pre + "mlp.shared_experts.gate_proj.weight"], out[pre + "mlp.shared_experts.up_proj.weight"] = sw[: sw.shape[0] // 2], sw[sw.shape[0] // 2:]
                 out[pre + "mlp.shared_experts.down_proj.weight"] = m.shared.down_proj.weight.detach()
+        if getattr(layer, "sparse", False) and family.experts == "gpt_oss":
+            _export_clamped_glu(layer.mlp, out, pre + "mlp.")
+            continue
         if getattr(layer, "sparse", False):
             gu_all, dn_all = layer.mlp.experts.gate_up.detach(), layer.mlp.experts.down.detach()
             Fe = gu_all.shape[1] // 2

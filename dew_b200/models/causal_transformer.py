@@ -44,6 +44,7 @@ class Mixture:
     balance_rate: float = 1e-3
     groups: int = 1                                  # DeepSeek-V3's group-limited routing: experts in ``groups`` groups ...
     topk_groups: int = 1                             # ... of which each token may use the ``topk_groups`` best (by their top-2 sum)
+    style: str = "swiglu"                            # 'clamped_glu': GPT-OSS's biased router over the top logits and biased clamped-GLU experts
 
 
 @dataclass(frozen=True)
@@ -94,6 +95,7 @@ class TransformerConfig:
     hyper_connections: int = 0                        # n > 1: n residual streams with learned read / write weights per sub-layer
     altup: int = 0                                    # K > 1: AltUp - K blocks, one of which every sub-layer computes on
     qkv_bias: bool = False                            # Qwen2: bias on the fused q | k | v projection only
+    attn_bias: bool = False                           # GPT-OSS: bias on q | k | v and on the output projection
     mlp_activation: str = "silu"                      # silu (SwiGLU) | gelu_tanh (Gemma's GeGLU) | gelu
     sandwich_norm: bool = False                       # Gemma-2: every sub-layer's output is normalised before it joins the stream
     query_scale: Optional[float] = None               # softmax scale other than head_dim ** -0.5 (Gemma-2's query_pre_attn_scalar ** -0.5)
@@ -128,7 +130,7 @@ ROTARY_KINDS = ("attention", "local", "nope", "mla", "differential", "forgetting
 def _mixer(cfg: TransformerConfig, kind: str, dtype, device, index: int = 0) -> nn.Module:
     if kind in ("attention", "local", "nope"):
         a = SelfAttention(cfg.emb_features, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, qk_norm=cfg.qk_norm,
-                          causal=True, window=cfg.window if kind == "local" or cfg.layer_types is None else None,
+                          causal=True, window=cfg.window if kind == "local" or cfg.layer_types is None else None, bias=cfg.attn_bias,
                           softcap=cfg.attn_softcap, sinks=cfg.attention_sinks, norm_eps=cfg.norm_eps,
                           init_std=cfg.init_std, qkv_bias=cfg.qkv_bias, scale=cfg.query_scale, qk_norm_full=cfg.qk_norm_full,
                           dtype=dtype, device=device)
@@ -206,6 +208,9 @@ class DecoderLayer(nn.Module):
         sparse = self.has_mlp and mix is not None and (mix.layers is None or index in mix.layers)
         if not self.has_mlp:
             self.mlp = None
+        elif sparse and mix.style == "clamped_glu":
+            from ..nn.gpt_oss import ClampedGluMoE
+            self.mlp = ClampedGluMoE(cfg.emb_features, mix, cfg.mlp_features or 4 * cfg.emb_features, init_std=cfg.init_std, dtype=dtype, device=device)
         elif sparse:
             from ..nn.moe import SparseMLP
             self.mlp = SparseMLP(cfg.emb_features, mix, cfg.mlp_features or 4 * cfg.emb_features, init_std=cfg.init_std,

@@ -37,6 +37,11 @@ CASES = {
                         rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "original_max_position_embeddings": 16,
                                          "beta_fast": 32.0, "beta_slow": 1.0, "mscale": 1.0, "mscale_all_dim": 1.0}),
     "glm4": dict(model_type="glm4", head_dim=16, pad_token_id=0, **COMMON),
+    "gpt_oss": dict(model_type="gpt_oss", vocab_size=96, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                    intermediate_size=32, num_local_experts=4, num_experts_per_tok=2, max_position_embeddings=64, sliding_window=8,
+                    layer_types=["sliding_attention", "full_attention"],
+                    rope_parameters={"rope_type": "yarn", "rope_theta": 150000.0, "factor": 4.0, "original_max_position_embeddings": 16,
+                                     "beta_fast": 32.0, "beta_slow": 1.0, "truncate": False}),
     "mixtral": dict(model_type="mixtral", num_local_experts=4, num_experts_per_tok=2, **COMMON),
     "qwen3_moe": dict(model_type="qwen3_moe", head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
                       norm_topk_prob=True, **COMMON),
@@ -55,8 +60,8 @@ def test_family_matches_transformers(name, tmp_path):
     cfg = transformers.AutoConfig.for_model(**CASES[name])
     cfg._attn_implementation = "eager"
     hf = transformers.AutoModelForCausalLM.from_config(cfg).float().eval()
-    for p in hf.parameters():
-        if p.dim() == 1:                      # norms away from one, biases away from zero
+    for n, p in hf.named_parameters():
+        if p.dim() == 1 or n.endswith("_bias"):   # norms away from one, biases away from zero
             p.data.add_(torch.randn_like(p) * 0.1)
     d = cfg.to_dict()
     fam = family_of(d)
