@@ -85,7 +85,7 @@ class TransformerConfig:
     attn_softcap: float = 0.0
     logit_softcap: float = 0.0
     window: Optional[int] = None
-    layer_types: Optional[Sequence[str]] = None      # per layer: attention | local | nope | gdn | mamba2 | mamba | mamba3 | kda | mla | lightning | differential | forgetting | gla | delta | rwkv7
+    layer_types: Optional[Sequence[str]] = None      # per layer: attention | local | nope | gdn | mamba2 | mamba | mamba3 | kda | mla | lightning | differential | forgetting | gla | delta | rwkv7 | memory | none
     mixture: Optional[Mixture] = None
     mixer_options: Dict[str, Any] = field(default_factory=dict)
     remat: bool = False
@@ -150,6 +150,9 @@ def _mixer(cfg: TransformerConfig, kind: str, dtype, device, index: int = 0) -> 
     if kind == "kda":
         from ..nn.kda import KimiDeltaAttention
         return KimiDeltaAttention(cfg.emb_features, dtype=dtype, device=device, **cfg.mixer_options)
+    if kind == "memory":
+        from ..nn.memory import NeuralMemory
+        return NeuralMemory(cfg.emb_features, norm_eps=cfg.norm_eps, dtype=dtype, device=device, **cfg.mixer_options)
     if kind == "mla":
         from ..nn.mla import MultiHeadLatentAttention
         return MultiHeadLatentAttention(cfg.emb_features, cfg.num_heads, norm_eps=cfg.norm_eps, dtype=dtype, device=device, **cfg.mixer_options)
