@@ -104,6 +104,7 @@ class TransformerConfig:
     rotary_fraction: float = 1.0                      # GLM / Phi / NeoX: only this share of a head's width rotates; heads are laid out [rotated a | kept a | rotated b | kept b]
     layer_mlp: Optional[Sequence[bool]] = None        # per layer (cycled like layer_types): False - the layer is its mixer alone (Mamba's blocks); with the
                                                       # mixer kind 'none', a layer that is its MLP alone (Nemotron-H's and Jamba's separate blocks)
+    depth_residual_block: int = 0                     # n > 0: block attention residuals - sub-layers read a learned softmax over the finished blocks of n layers and the partial sum
     engram: Optional[Dict[str, Any]] = None           # {'layers': [i, ...], **Engram fields}: hashed n-gram memories gated into the stream in front of those layers
     pre_norm: bool = True                             # False (OLMo-2): sub-layers read the stream as it is; only their outputs are normalised (sandwich_norm)
     qk_norm_full: bool = False                        # OLMo-2: q and k normalised over all heads at once
@@ -327,6 +328,12 @@ class CausalTransformer(nn.Module):
         self.mtp = nn.ModuleList([MTPBlock(cfg, i, dtype, device) for i in range(cfg.mtp_depth)]) if cfg.mtp_depth > 0 else None
         self.early_exit_gate = Linear(cfg.emb_features, 1, bias=True, init_std=cfg.init_std, dtype=dtype, device=device) \
             if cfg.loop is not None and cfg.loop.exit_gate else None
+        self.depth_sites = None
+        if cfg.depth_residual_block > 0:
+            if cfg.sandwich_norm or not cfg.pre_norm or cfg.loop is not None or max(cfg.hyper_connections, cfg.altup) > 1 or any(k == "none" for k in kinds):
+                raise NotImplementedError("block attention residuals are built for the plain pre-norm block")
+            from ..nn.depth_residuals import DepthResidualSites
+            self.depth_sites = DepthResidualSites(cfg.num_layers, cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device)
         self.engrams = None
         if cfg.engram:
             from ..nn.engram import Engram
@@ -452,6 +459,19 @@ class CausalTransformer(nn.Module):
             return self._looped(h, cos, sin, positions, segment_ids, cache, train, passes, loop_steps)
         if passes:
             raise ValueError("per-pass exits need a looped decoder (TransformerConfig(loop=Loop(...)))")
+        if self.depth_sites is not None:
+            if getattr(self, "tp", None) is not None:
+                raise NotImplementedError("block attention residuals are not built for tensor parallelism")
+            from ..nn.depth_residuals import depth_residual_forward
+
+            def call_mixer(layer, x):
+                n = layer.input_norm(x)
+                if layer.kind in ROTARY_KINDS:
+                    return layer.mixer(n, cos, sin, positions, segment_ids, cache, layer.index)
+                return layer.mixer(n, segment_ids=segment_ids, cache=cache, layer=layer.index)
+            out = depth_residual_forward(self.layers, self.depth_sites, h, cfg.depth_residual_block, call_mixer,
+                                         lambda layer, x: layer.mlp(layer.post_norm(x)))
+            return self.final_norm(out)
         branch = None
         if self.engrams is not None and (cache is not None or tokens is None or getattr(self, "tp", None) is not None):
             raise NotImplementedError("n-gram memories read the token ids behind each position: they run on whole sequences given as tokens, without "

@@ -38,6 +38,7 @@ class SelfAttention(nn.Module):
         self.sinks = declare(nn.Parameter(torch.zeros(num_heads, dtype=dtype, device=device)), ("heads",), "sinks") if sinks else None
         # a layer whose rotary table differs from the model's: (theta, scaling) builds its own; rotary False drops the rotation (NoPE)
         self.rotary, self.own_rope, self._own = True, None, None
+        self.head_transform = None     # a module applied to the heads' outputs [B, S, H, D] before the output projection (dew_b200.nn.dex)
         self.track_qk_max = False      # set by dew_b200.optim.qk_clip.watch: record each head's largest attention logit
         self.qk_max: Optional[torch.Tensor] = None
 
@@ -87,7 +88,7 @@ class SelfAttention(nn.Module):
     def forward(self, x, cos=None, sin=None, positions=None, segment_ids=None, cache=None, layer: int = 0):
         B, S, _ = x.shape
         cos, sin = self._tables(cos, sin)
-        if (cache is None and x.is_cuda and cos is not None and self.q_norm is None and self.window is None and not self.softcap
+        if (cache is None and x.is_cuda and cos is not None and self.head_transform is None and self.q_norm is None and self.window is None and not self.softcap
                 and self.sinks is None and segment_ids is None and not self.track_qk_max and self.q_gain is None):
             from ..ops.attn import packed_attention
             H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
@@ -95,7 +96,7 @@ class SelfAttention(nn.Module):
             if o is not None:
                 return self.o_proj(o.reshape(B, S, H * D))
         if (cache is not None and S == 1 and self.q_norm is None and self.q_gain is None and positions is not None and cos is not None
-                and hasattr(cache, "decode_packed")):
+                and self.head_transform is None and hasattr(cache, "decode_packed")):
             # decode step: rotation, cache append and attention straight from the packed projection (no slices, no copies)
             H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
             qkv = self.qkv_proj(x).view(B, H + 2 * Hkv, D)
@@ -111,4 +112,6 @@ class SelfAttention(nn.Module):
         else:
             o = ops.attention(q, k, v, causal=self.causal, window=self.window, softcap=self.softcap, sinks=self.sinks,
                               segment_ids=segment_ids)
+        if self.head_transform is not None:
+            o = self.head_transform(o)
         return self.o_proj(o.reshape(B, S, self.num_heads * self.head_dim))
