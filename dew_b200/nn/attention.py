@@ -106,7 +106,13 @@ class SelfAttention(nn.Module):
         q, k, v = self.project(x, cos, sin, positions)
         if self.track_qk_max and cache is None and self.training:
             self._record_qk_max(q, k)
-        if cache is not None:
+        if cache is None and hasattr(segment_ids, "visible"):
+            # rows that share a prefix (dew_b200.data.forked_rows.Forks): a token sees its own document causally and all of its parent
+            if self.window is not None or self.softcap or self.sinks is not None or not self.causal:
+                raise NotImplementedError("forked rows are built for plain causal attention (no window, soft cap or sinks)")
+            from .attention_variants import biased_attention
+            o = biased_attention(q, k, v, mask=segment_ids.visible()[:, None])
+        elif cache is not None:
             o = cache.attend(layer, q, k, v, positions, causal=self.causal, window=self.window, softcap=self.softcap,
                              sinks=self.sinks)
         else:
