@@ -45,7 +45,10 @@ class GRPO(Objective):
 
     def __init__(self, model, group: int = 4, clip: float = 0.2, kl: float = 0.04, *, clip_high: Optional[float] = None,
                  dual_clip: Optional[float] = None, rule: str = "ppo", advantage: str = "grpo", reduction: Optional[str] = None,
-                 kl_kind: str = "k3", importance: Optional[str] = None, importance_threshold: float = 2.0, band=(0.5, 2.0)):
+                 kl_kind: str = "k3", importance: Optional[str] = None, importance_threshold: float = 2.0, band=(0.5, 2.0),
+                 share_prefix: bool = False, min_prefix: int = 8):
+        # share_prefix: a group's rows begin with the same prompt; lay the prompt out once per group (data.forked_rows) instead of once per row
+        self.share_prefix, self.min_prefix = share_prefix, min_prefix
         if rule not in RULES:
             raise ValueError(f"unknown update rule {rule!r}; known: {RULES}")
         if advantage not in _ADVANTAGES:
@@ -59,9 +62,25 @@ class GRPO(Objective):
         self.kl_kind, self.importance, self.importance_threshold, self.band = kl_kind, importance, importance_threshold, band
         self.ema_decay = EMASpec.constant(1.0)
 
+    def _logits(self, variables, tokens, full_mask):
+        """Logits ``[B, S-1, V]`` of the inputs ``tokens[:, :-1]``; with ``share_prefix`` through the forked layout (places past a row's last
+        completion token hold zeros, which the mask never reads)."""
+        if not self.share_prefix:
+            return self.apply(variables, tokens[:, :-1])
+        from ...data.forked_rows import ForkedRows
+        B, S = tokens.shape
+        last = torch.where(full_mask.bool().any(1), S - full_mask.bool().flip(1).float().argmax(1), torch.full((B,), S, device=tokens.device))
+        rows = [tokens[i, :max(1, int(n) - 1)].tolist() for i, n in enumerate(last.tolist())]
+        packed = ForkedRows.pack(rows, window=max(S - 1, self.group * (S - 1) // 2), min_prefix=self.min_prefix)
+        dev = tokens.device
+        out = self.apply(variables, packed.tokens.to(dev), positions=packed.positions.to(dev), segment_ids=packed.forks.to(dev))
+        out = out[0] if isinstance(out, tuple) else out
+        padded, _ = packed.padded(out)
+        return torch.nn.functional.pad(padded, (0, 0, 0, S - 1 - padded.shape[1]))
+
     def loss(self, variables, batch, step: Step):
         tokens, mask = batch["tokens"], batch["mask"][:, 1:].bool()
-        lp = _token_logprobs(self.apply(variables, tokens[:, :-1]), tokens)
+        lp = _token_logprobs(self._logits(variables, tokens, batch["mask"]), tokens)
         old = batch["old_logprobs"].float()
         adv = batch["advantages"].float() if "advantages" in batch else _ADVANTAGES[self.advantage](batch["rewards"].float(), self.group)
         adv = adv.to(lp.device)[:, None].expand_as(lp)

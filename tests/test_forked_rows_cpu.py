@@ -66,3 +66,33 @@ def test_model_outputs_and_gradients_equal_the_rows_laid_whole():
                                                  layer_types=("gla",), mixer_options=dict(num_heads=2)), dtype=torch.float32)
     with pytest.raises(Exception):
         hybrid(packed.tokens, positions=packed.positions, segment_ids=packed.forks)
+
+
+def test_grpo_with_a_shared_prompt_gives_the_same_loss_and_gradients():
+    from dew_b200.objectives.base import Step
+    from dew_b200.objectives.rl.policy import GRPO
+    torch.manual_seed(0)
+    cfg = TransformerConfig(vocab_size=50, emb_features=32, num_layers=2, num_heads=4, mlp_features=64, max_seq_len=64, qk_norm=False)
+    model = CausalTransformer(cfg, dtype=torch.float32)
+    G, P, S = 4, 10, 18
+    prompts = torch.randint(1, 50, (2, P))
+    tokens = torch.zeros(2 * G, S, dtype=torch.long)
+    mask = torch.zeros(2 * G, S)
+    for i in range(2 * G):
+        n = int(torch.randint(3, S - P + 1, ()))
+        tokens[i, :P] = prompts[i // G]
+        tokens[i, P:P + n] = torch.randint(1, 50, (n,))
+        mask[i, P:P + n] = 1
+    batch = dict(tokens=tokens, mask=mask, rewards=torch.randn(2 * G), old_logprobs=torch.randn(2 * G, S - 1) * 0.1 - 3.5)
+    step = Step(step=0)
+    results = []
+    for share in (False, True):
+        obj = GRPO(model, group=G, kl=0.0, share_prefix=share, min_prefix=4)
+        stats, _ = obj.loss(None, batch, step)
+        value = stats.total / stats.mass
+        grads = torch.autograd.grad(value, list(model.parameters()), allow_unused=True)
+        results.append((value.detach(), grads))
+    assert torch.allclose(results[0][0], results[1][0], atol=1e-5)
+    for a, b in zip(results[0][1], results[1][1]):
+        if a is not None:
+            assert torch.allclose(a, b, atol=1e-5 + 1e-4 * float(a.abs().max()))
