@@ -73,6 +73,15 @@ class Dataset:
     def map(self, fn: Callable) -> "Dataset":
         c = self._copy(); c._maps.append(fn); return c
 
+    def filter(self, keep: Callable[[Any], bool]) -> "Dataset":
+        """Rows for which ``keep(row)`` is false are dropped.  (After a stage that changes the number of rows, a restored position is found by
+        reading the epoch again up to it: exact, and as slow as the rows it skips.)"""
+        c = self._copy(); c._maps.append(_Stage("filter", keep)); return c
+
+    def flat_map(self, fn: Callable[[Any], Iterable[Any]]) -> "Dataset":
+        """Every row becomes the rows ``fn(row)`` yields (none, one or several): over-length splitting, windows over a document."""
+        c = self._copy(); c._maps.append(_Stage("flat", fn)); return c
+
     def batched(self, batch: int, drop_last: bool = True) -> "Dataset":
         c = self._copy(); c._batch = batch; c.batch = batch; c._drop_last = drop_last; return c
 
@@ -107,7 +116,35 @@ class Dataset:
         lo = self._partition.index * per
         return idx[lo:lo + per]
 
+    def _through(self, row, stage: int = 0) -> Iterator[Any]:
+        """``row`` through the stages from ``stage`` on: zero, one or several rows."""
+        for j in range(stage, len(self._maps)):
+            fn = self._maps[j]
+            if isinstance(fn, _Stage):
+                if fn.kind == "filter":
+                    if not fn.fn(row):
+                        return
+                    continue
+                for out in fn.fn(row):
+                    yield from self._through(out, j + 1)
+                return
+            row = fn(row)
+        yield row
+
     def _rows(self, skip_rows: int = 0) -> Iterator[Any]:
+        if any(isinstance(fn, _Stage) for fn in self._maps):
+            # the position counts delivered rows, which no longer map to source rows: read from the start and drop what was delivered
+            epoch, dropped = 0, 0
+            while True:
+                for i in self._order(epoch):
+                    for row in self._through(self._get(int(i))):
+                        if dropped < skip_rows:
+                            dropped += 1
+                            continue
+                        yield row
+                epoch += 1
+                if not self._repeat:
+                    return
         epoch = 0
         per_epoch = len(self._order(0))
         if per_epoch:
@@ -154,6 +191,14 @@ class Dataset:
         old = int(position.get("partitions", self._partition.count))
         # elastic: the same global number of batches, re-split over the new partition count
         self._consumed = consumed * old // max(1, self._partition.count)
+
+
+class _Stage:
+    """A stage that changes the number of rows: ``filter`` or ``flat``."""
+    __slots__ = ("kind", "fn")
+
+    def __init__(self, kind: str, fn: Callable):
+        self.kind, self.fn = kind, fn
 
 
 def _prefetch(gen: Iterable[Any], depth: int = 4) -> Iterator[Any]:

@@ -73,3 +73,75 @@ class Hub(Dataset):
                     return revs[-1]
         raise FileNotFoundError(f"no local snapshot of dataset {repo_id!r} under {base} (this process has no network access: "
                                 "place the snapshot there or pass a directory)")
+
+
+class Concatenate(Dataset):
+    """Several map-style datasets read one after another as one (their own stages are not applied: concatenate sources, then chain)."""
+
+    def __init__(self, parts: Sequence[Dataset]):
+        sizes = [len(p) for p in parts]
+        if any(p._length is None for p in parts):
+            raise ValueError("only datasets of known length concatenate")
+        super().__init__(None, length=sum(sizes))
+        self._parts = list(parts)
+        self._starts = [0]
+        for n in sizes:
+            self._starts.append(self._starts[-1] + n)
+
+    def _get(self, i: int):
+        import bisect
+        j = bisect.bisect_right(self._starts, i) - 1
+        return self._parts[j]._get(i - self._starts[j])
+
+
+class TorchDataset(Dataset):
+    """A map-style ``torch.utils.data.Dataset`` (``__len__`` / ``__getitem__``) read through the shared chain.  ``fields`` names the entries
+    of a tuple sample (``("image", "label")``); a mapping sample is taken as it is."""
+
+    def __init__(self, dataset, fields: Optional[Sequence[str]] = None):
+        super().__init__(None, length=len(dataset))
+        self._dataset, self._fields = dataset, tuple(fields) if fields else None
+
+    def _get(self, i: int):
+        sample = self._dataset[i]
+        if isinstance(sample, dict):
+            return sample
+        if self._fields is None:
+            raise TypeError("a tuple sample needs field names: TorchDataset(ds, fields=('image', 'label'))")
+        if len(sample) != len(self._fields):
+            raise ValueError(f"a sample holds {len(sample)} entries, {len(self._fields)} field names were given")
+        return dict(zip(self._fields, sample))
+
+
+class HFDataset(TorchDataset):
+    """A Hugging Face ``datasets.Dataset`` (already loaded: this library fetches nothing) read as a store; ``columns`` keeps a subset."""
+
+    def __init__(self, dataset, columns: Optional[Sequence[str]] = None):
+        super().__init__(dataset)
+        self._columns = tuple(columns) if columns else None
+
+    def _get(self, i: int):
+        row = dict(self._dataset[int(i)])
+        return row if self._columns is None else {k: row[k] for k in self._columns}
+
+
+class IteratorSource(Dataset):
+    """Any re-creatable iterator read as a store: ``factory()`` returns a fresh iterator over the same records in the same order.  The
+    position counts delivered rows; a restore reads the iterator again up to it."""
+
+    def __init__(self, factory, length: Optional[int] = None):
+        super().__init__(None, length=length)
+        self._factory = factory
+
+    def _rows(self, skip_rows: int = 0):
+        while True:
+            n = 0
+            for record in self._factory():
+                for row in self._through(record):
+                    n += 1
+                    if skip_rows:
+                        skip_rows -= 1
+                        continue
+                    yield row
+            if not self._repeat or n == 0:
+                return
