@@ -58,6 +58,24 @@ class MaskedDiffusionLM(Objective):
         return x
 
 
+def entropy_bounded_choice(entropy: torch.Tensor, masked: torch.Tensor, bound: float) -> torch.Tensor:
+    """Which masked places a step commits: per row, the places in order of rising entropy for as long as their entropies, less the
+    largest among them, sum to at most ``bound`` - the joint error of committing them independently stays bounded, so a confident
+    canvas fills in a few steps and an uncertain one a place at a time.  At least one masked place per row is always chosen.
+    ``entropy, masked [R, L]`` -> boolean ``[R, L]``."""
+    inf = torch.full_like(entropy, float("inf"))
+    e = torch.where(masked, entropy, inf)
+    order = e.argsort(-1)
+    ranked = e.gather(-1, order)
+    finite = torch.isfinite(ranked)
+    cum = torch.where(finite, ranked, torch.zeros_like(ranked)).cumsum(-1)
+    # ranked rises, so the largest entropy among the first n is the n-th
+    take = finite & ((cum - ranked) <= bound)
+    take[:, 0] = finite[:, 0]
+    take = take.long().cummin(-1).values.bool()                 # a prefix of the ranking: nothing past the first refusal
+    return torch.zeros_like(masked).scatter(-1, order, take)
+
+
 class BlockDiffusionLM(MaskedDiffusionLM):
     """Masked diffusion inside blocks of ``block`` tokens; each row draws one rate per block (so blocks sit at different
     noise levels, as in semi-autoregressive sampling) and the model is expected to attend block-causally."""
@@ -82,3 +100,45 @@ class BlockDiffusionLM(MaskedDiffusionLM):
         """``[T, T]`` boolean: position i may attend to j when j's block is not later than i's."""
         b = torch.arange(T, device=device) // block
         return b[:, None] >= b[None, :]
+
+    @torch.no_grad()
+    def generate(self, variables, prompt: torch.Tensor, blocks: int, bound: float = 0.5, max_steps: Optional[int] = None, temperature: float = 0.0,
+                 generator=None, stop_id: Optional[int] = None):
+        """Semi-autoregressive generation: ``blocks`` new blocks after ``prompt [R, P]``, each started all-masked and refined until full.  A
+        step runs the model on the prompt, the finished blocks and the current canvas, and commits the masked places
+        ``entropy_bounded_choice`` picks (their argmax, or a draw at ``temperature`` > 0).  Rows that are full wait for the others; a row
+        that has produced ``stop_id`` fills the rest with it.  Returns ``(tokens [R, P + blocks * block], steps [R, blocks])`` - the model
+        calls each row's blocks took."""
+        R, P = prompt.shape
+        x = prompt
+        counts = torch.zeros(R, blocks, dtype=torch.long)
+        limit = max_steps or self.block
+        done = torch.zeros(R, dtype=torch.bool, device=prompt.device)
+        for b in range(blocks):
+            canvas = torch.full((R, self.block), self.mask_id, dtype=torch.long, device=prompt.device)
+            if stop_id is not None:
+                canvas = torch.where(done[:, None], torch.full_like(canvas, stop_id), canvas)
+            for it in range(limit):
+                masked = canvas == self.mask_id
+                if not bool(masked.any()):
+                    break
+                logits = self.apply(variables, torch.cat([x, canvas], 1))
+                logits = (logits[0] if isinstance(logits, tuple) else logits)[:, -self.block:].float()
+                logits[..., self.mask_id] = -float("inf")
+                logp = torch.log_softmax(logits, -1)
+                entropy = -(logp.exp() * logp.clamp_min(-1e30)).sum(-1)
+                if temperature > 0:
+                    draw = torch.multinomial((logits / temperature).softmax(-1).reshape(-1, logits.shape[-1]), 1, generator=generator).view(R, self.block)
+                else:
+                    draw = logits.argmax(-1)
+                last = it == limit - 1
+                choose = masked if last else entropy_bounded_choice(entropy, masked, bound)
+                canvas = torch.where(choose, draw, canvas)
+                counts[:, b] += masked.any(-1).long().cpu()
+            if stop_id is not None:
+                hit = (canvas == stop_id)
+                after = hit.long().cumsum(-1) > 0
+                canvas = torch.where(after, torch.full_like(canvas, stop_id), canvas)
+                done = done | hit.any(-1)
+            x = torch.cat([x, canvas], 1)
+        return x, counts
