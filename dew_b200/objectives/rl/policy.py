@@ -34,7 +34,7 @@ def _token_logprobs(logits, tokens):
     return torch.log_softmax(logits.float(), -1).gather(-1, tokens[:, 1:, None]).squeeze(-1)
 
 
-_ADVANTAGES = {"grpo": lambda r, g: A.group_advantage(r, g), "dr_grpo": A.dr_grpo_advantage, "rloo": A.rloo_advantage}
+_ADVANTAGES = {"grpo": lambda r, g: A.group_advantage(r, g), "dr_grpo": A.dr_grpo_advantage, "rloo": A.rloo_advantage, "global": A.global_advantage}
 RULES = ("ppo", "gspo", "cispo", "gmpo", "reinforce")
 
 

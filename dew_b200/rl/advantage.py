@@ -71,6 +71,15 @@ def dr_grpo_advantage(rewards: torch.Tensor, group: int) -> torch.Tensor:
     return group_normalised(rewards.reshape(-1, group), scale=False).reshape(-1)
 
 
+def global_advantage(rewards: torch.Tensor, group: int, eps: float = GROUP_EPS) -> torch.Tensor:
+    """REINFORCE++ with a group baseline: each reward less its group's mean, then divided by the standard deviation of those differences
+    over the whole batch (one scale for every prompt, so an easy prompt's small spread is not blown up to unit variance)."""
+    if rewards.shape[0] % group:
+        raise ValueError(f"{rewards.shape[0]} rewards do not split into groups of {group}")
+    centred = (rewards.reshape(-1, group) - rewards.reshape(-1, group).mean(1, keepdim=True)).reshape(-1)
+    return centred / (centred.std(unbiased=False) + eps)
+
+
 def rloo_advantage(rewards: torch.Tensor, group: int) -> torch.Tensor:
     if group < 2:
         raise ValueError("leave-one-out needs at least two completions per prompt")
