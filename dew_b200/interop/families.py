@@ -8,7 +8,8 @@ Families: llama, mistral, qwen2 (q/k/v bias), qwen3 (per-head q/k norm), qwen3_m
 minus one, GeGLU, scaled embeddings), gemma2 (output norms on every sub-layer, soft-capped logits, alternating local /
 global layers, query scale), phi3 (fused qkv and gate_up on disk), granite (embedding / attention / residual multipliers, logits scaling), olmo2 (no pre-norms: every sub-layer's output is
 normalised instead; q and k normalised over all heads at once), olmo3 (olmo2 with sliding layers on an unscaled rotary table), gemma3 (gemma2's
-block with per-head q/k norms and one rotary base per layer kind), smollm3 (every fourth layer attends without positions), glm4 (half of every head rotates, as pairs; output norms; fused gate_up), gpt_oss (attention sinks and biases, sliding / full layers, a router over the top logits, biased clamped-GLU experts stored interleaved), deepseek_v3 (latent attention stored with
+block with per-head q/k norms and one rotary base per layer kind), smollm3 (every fourth layer attends without positions), glm4 (half of every head rotates, as pairs; output norms; fused gate_up), qwen3_next (gated delta-rule layers with every fourth a gated softmax attention layer, a quarter of each head rotating, zero-centred norms,
+routed experts beside a gated shared expert), gpt_oss (attention sinks and biases, sliding / full layers, a router over the top logits, biased clamped-GLU experts stored interleaved), deepseek_v3 (latent attention stored with
 interleaved rotary pairs, dense layers first, then sigmoid-routed experts in groups with a selection bias beside shared experts).
 
 Reference: src/dew/interop/decoder_families.py, decoder_config.py, decoder_parts.py (family tables), unread.py (keys
@@ -116,7 +117,7 @@ def _olmo2(cfg):
     return _common(cfg, pre_norm=False, sandwich_norm=True, qk_norm_full=True)
 
 
-_KINDS = {"sliding_attention": "local", "full_attention": "attention"}
+_KINDS = {"sliding_attention": "local", "full_attention": "attention", "linear_attention": "gdn"}
 
 
 def _layer_kinds(cfg) -> Optional[Tuple[str, ...]]:
@@ -195,6 +196,23 @@ def _gpt_oss(cfg):
     return _common(cfg, attn_bias=True, attention_sinks=True, window=cfg.get("sliding_window"), layer_types=_layer_kinds(cfg), mixture=mix)
 
 
+def _qwen3_next(cfg):
+    """Gated delta-rule layers with a softmax attention layer every ``full_attention_interval``-th; gated attention outputs; a quarter of
+    each head rotating; zero-centred norm weights; routed experts beside a gated shared expert."""
+    n = cfg["num_hidden_layers"]
+    every = int(cfg.get("full_attention_interval", 4))
+    kinds = _layer_kinds(cfg) or tuple("attention" if (i + 1) % every == 0 else "gdn" for i in range(n))
+    rope = cfg.get("rope_parameters") or {}
+    sparse_step, dense_only = int(cfg.get("decoder_sparse_step", 1) or 1), set(cfg.get("mlp_only_layers") or ())
+    mix = Mixture(experts=int(cfg["num_experts"]), top_k=int(cfg["num_experts_per_tok"]), expert_features=int(cfg["moe_intermediate_size"]),
+                  norm_topk_prob=bool(cfg.get("norm_topk_prob", True)), shared_features=int(cfg.get("shared_expert_intermediate_size") or 0),
+                  shared_gate=True, layers=tuple(i for i in range(n) if i not in dense_only and (i + 1) % sparse_step == 0))
+    options = dict(num_k_heads=int(cfg["linear_num_key_heads"]), num_v_heads=int(cfg["linear_num_value_heads"]), head_k_dim=int(cfg["linear_key_head_dim"]),
+                   head_v_dim=int(cfg["linear_value_head_dim"]), conv_size=int(cfg.get("linear_conv_kernel_dim", 4)), norm_eps=float(cfg.get("rms_norm_eps", 1e-6)), qk_eps=1e-6)
+    return _common(cfg, qk_norm=True, attn_out_gate=True, layer_types=kinds, mixture=mix, mixer_options=options,
+                   rotary_fraction=float(rope.get("partial_rotary_factor", cfg.get("partial_rotary_factor", 0.25))))
+
+
 def _granite(cfg):
     # four scalars: embeddings times one, the softmax scale itself (not 1 / sqrt(d)), every branch times one, logits over one
     return _common(cfg, embed_multiplier=float(cfg.get("embedding_multiplier", 1.0)), query_scale=float(cfg.get("attention_multiplier", 1.0)),
@@ -225,6 +243,7 @@ FAMILIES: Dict[str, Family] = {f.name: f for f in (
     Family("glm4", ("glm4",), "Glm4ForCausalLM", _glm4, qkv_bias=True, rotary_pairs=True, fused_gate_up="mlp.gate_up_proj",
            mixer_out_norm="post_self_attn_layernorm", mlp_out_norm="post_mlp_layernorm"),
     Family("gpt_oss", ("gpt_oss",), "GptOssForCausalLM", _gpt_oss, qkv_bias=True, experts="gpt_oss"),
+    Family("qwen3_next", ("qwen3_next",), "Qwen3NextForCausalLM", _qwen3_next, norm_offset=1.0, experts="qwen3_next"),
     Family("phi3", ("phi3",), "Phi3ForCausalLM", _phi3, fused_qkv="self_attn.qkv_proj", fused_gate_up="mlp.gate_up_proj"),
 )}
 
@@ -287,6 +306,13 @@ def write_config(c: TransformerConfig, family: str = "llama", dtype: str = "bflo
                     "moe_layer_freq": 1, "kv_lora_rank": o["kv_latent"], "q_lora_rank": o.get("q_latent"), "qk_nope_head_dim": o["nope_dim"],
                     "qk_rope_head_dim": o["rope_dim"], "v_head_dim": o["v_dim"], "head_dim": o["rope_dim"],
                     "num_key_value_heads": c.num_heads, "rope_interleave": True})
+    if fam.name == "qwen3_next":
+        o, m = c.mixer_options, c.mixture
+        out.update({"layer_types": ["linear_attention" if k == "gdn" else "full_attention" for k in kinds], "linear_num_key_heads": o["num_k_heads"],
+                    "linear_num_value_heads": o["num_v_heads"], "linear_key_head_dim": o["head_k_dim"], "linear_value_head_dim": o["head_v_dim"],
+                    "linear_conv_kernel_dim": o.get("conv_size", 4), "shared_expert_intermediate_size": m.shared_features,
+                    "partial_rotary_factor": c.rotary_fraction, "rope_parameters": {**out["rope_parameters"], "partial_rotary_factor": c.rotary_fraction},
+                    "full_attention_interval": next((i + 1 for i, k in enumerate(kinds) if k != "gdn"), len(kinds) + 1)})
     if fam.name == "glm4":
         out.update({"attention_bias": c.qkv_bias, "partial_rotary_factor": c.rotary_fraction})
         out["rope_parameters"] = {**out["rope_parameters"], "partial_rotary_factor": c.rotary_fraction}
@@ -301,6 +327,19 @@ def write_config(c: TransformerConfig, family: str = "llama", dtype: str = "bflo
 
 
 # ------------------------------------------------------------------------------------------------ tensors
+class _Indexed:
+    """A reader behind ``[]`` (for the layer loaders that index a mapping)."""
+
+    def __init__(self, get):
+        self.get = get
+
+    def __getitem__(self, key):
+        return self.get(key)
+
+    def __contains__(self, key):
+        return self.get.has(key)
+
+
 class _Reader:
     """A release's tensors with a record of which were read."""
 
@@ -344,6 +383,20 @@ def load_state(model: CausalTransformer, tensors: Mapping[str, torch.Tensor], fa
         a = layer.mixer
         if hasattr(a, "kv_latent"):
             _load_latent_attention(a, get, pre + "self_attn.")
+        elif hasattr(a, "in_proj_qkvz"):
+            from .hf import load_gated_delta_net
+            load_gated_delta_net(a, _Indexed(get), pre + "linear_attn.")
+        elif getattr(a, "gate_proj", None) is not None:
+            # the query projection holds, per head, the query then its output gate
+            order = head_order(a.head_dim, int(a.head_dim * model.config.rotary_fraction), family.rotary_pairs)
+            H, Hkv, D = a.num_heads, a.num_kv_heads, a.head_dim
+            qg = get(pre + "self_attn.q_proj.weight").reshape(H, 2 * D, -1)
+            packed = torch.cat([qg[:, :D].reshape(H * D, -1), get(pre + "self_attn.k_proj.weight"), get(pre + "self_attn.v_proj.weight")], 0)
+            _put(a.qkv_proj.weight, _reorder_qk(packed, H, Hkv, D, order))
+            _put(a.gate_proj.weight, qg[:, D:].reshape(H * D, -1))
+            _put(a.o_proj.weight, get(pre + "self_attn.o_proj.weight"))
+            _put(a.q_norm.weight, get(pre + "self_attn.q_norm.weight")[order] if order is not None else get(pre + "self_attn.q_norm.weight"), off)
+            _put(a.k_norm.weight, get(pre + "self_attn.k_norm.weight")[order] if order is not None else get(pre + "self_attn.k_norm.weight"), off)
         else:
             order = head_order(a.head_dim, int(a.head_dim * model.config.rotary_fraction), family.rotary_pairs)
             shape = (a.num_heads, a.num_kv_heads, a.head_dim, order)
@@ -468,6 +521,11 @@ def _load_experts(mlp, get: _Reader, pre: str) -> None:
     E = mlp.mix.experts
     if get.has(pre + "mlp.gate.e_score_correction_bias"):
         _put(mlp.router.expert_bias, get(pre + "mlp.gate.e_score_correction_bias"))
+    if mlp.shared is not None and get.has(pre + "mlp.shared_expert.gate_proj.weight"):             # Qwen3-Next / Qwen2-MoE: one gated shared expert
+        _put(mlp.shared.gate_up_proj.weight, torch.cat([get(pre + "mlp.shared_expert.gate_proj.weight"), get(pre + "mlp.shared_expert.up_proj.weight")], 0))
+        _put(mlp.shared.down_proj.weight, get(pre + "mlp.shared_expert.down_proj.weight"))
+        if mlp.shared_gate is not None:
+            _put(mlp.shared_gate.weight, get(pre + "mlp.shared_expert_gate.weight"))
     if mlp.shared is not None and get.has(pre + "mlp.shared_experts.gate_proj.weight"):
         _put(mlp.shared.gate_up_proj.weight, torch.cat([get(pre + "mlp.shared_experts.gate_proj.weight"), get(pre + "mlp.shared_experts.up_proj.weight")], 0))
         _put(mlp.shared.down_proj.weight, get(pre + "mlp.shared_experts.down_proj.weight"))
@@ -510,6 +568,18 @@ def export_state(model: CausalTransformer, family: Family) -> Dict[str, torch.Te
         a = layer.mixer
         if hasattr(a, "kv_latent"):
             _export_latent_attention(a, out, pre + "self_attn.")
+        elif hasattr(a, "in_proj_qkvz"):
+            from .hf import export_gated_delta_net
+            export_gated_delta_net(a, out, pre + "linear_attn.")
+        elif getattr(a, "gate_proj", None) is not None:
+            order = head_order(D, int(D * c.rotary_fraction), family.rotary_pairs)
+            w = _reorder_qk(a.qkv_proj.weight.detach(), H, Hkv, D, order, back=True)
+            qg = torch.cat([w[: H * D].reshape(H, D, -1), a.gate_proj.weight.detach().reshape(H, D, -1)], 1)
+            out[pre + "self_attn.q_proj.weight"] = qg.reshape(2 * H * D, -1)
+            out[pre + "self_attn.k_proj.weight"], out[pre + "self_attn.v_proj.weight"] = w[H * D:(H + Hkv) * D], w[(H + Hkv) * D:]
+            out[pre + "self_attn.o_proj.weight"] = a.o_proj.weight.detach()
+            back = torch.argsort(order) if order is not None else slice(None)
+            out[pre + "self_attn.q_norm.weight"], out[pre + "self_attn.k_norm.weight"] = norm(a.q_norm.weight)[back], norm(a.k_norm.weight)[back]
         else:
             order = head_order(D, int(D * c.rotary_fraction), family.rotary_pairs)
             w = _reorder_qk(a.qkv_proj.weight.detach(), H, Hkv, D, order, back=True)
@@ -539,6 +609,16 @@ def export_state(model: CausalTransformer, family: Family) -> Dict[str, torch.Te
                 out[pre + "mlp.shared_experts.down_proj.weight"] = m.shared.down_proj.weight.detach()
         if getattr(layer, "sparse", False) and family.experts == "gpt_oss":
             _export_clamped_glu(layer.mlp, out, pre + "mlp.")
+            continue
+        if getattr(layer, "sparse", False) and family.experts == "qwen3_next":
+            m = layer.mlp
+            out[pre + "mlp.gate.weight"] = m.router.weight.detach()
+            out[pre + "mlp.experts.gate_up_proj"], out[pre + "mlp.experts.down_proj"] = m.experts.gate_up.detach(), m.experts.down.detach()
+            if m.shared is not None:
+                sw = m.shared.gate_up_proj.weight.detach()
+                out[pre + "mlp.shared_expert.gate_proj.weight"], out[pre + "mlp.shared_expert.up_proj.weight"] = sw[: sw.shape[0] // 2], sw[sw.shape[0] // 2:]
+                out[pre + "mlp.shared_expert.down_proj.weight"] = m.shared.down_proj.weight.detach()
+                out[pre + "mlp.shared_expert_gate.weight"] = m.shared_gate.weight.detach()
             continue
         if getattr(layer, "sparse", False):
             gu_all, dn_all = layer.mlp.experts.gate_up.detach(), layer.mlp.experts.down.detach()

@@ -211,6 +211,29 @@ def _ba_from_grouped(w: torch.Tensor, hk: int, hv: int) -> torch.Tensor:
     return torch.cat([blk[:, :rep].reshape(hv, -1), blk[:, rep:].reshape(hv, -1)], 0)
 
 
+def _qkvz_to_grouped(w: torch.Tensor, hk: int, hv: int, dk: int, dv: int) -> torch.Tensor:
+    rep = hv // hk
+    kd, vd = hk * dk, hv * dv
+    q, k, v, z = w[:kd], w[kd:2 * kd], w[2 * kd:2 * kd + vd], w[2 * kd + vd:]
+    blk = torch.cat([q.reshape(hk, dk, -1), k.reshape(hk, dk, -1), v.reshape(hk, rep * dv, -1), z.reshape(hk, rep * dv, -1)], 1)
+    return blk.reshape(w.shape)
+
+
+def _ba_to_grouped(w: torch.Tensor, hk: int, hv: int) -> torch.Tensor:
+    rep = hv // hk
+    return torch.cat([w[:hv].reshape(hk, rep, -1), w[hv:].reshape(hk, rep, -1)], 1).reshape(w.shape)
+
+
+def export_gated_delta_net(mixer, out: Dict[str, torch.Tensor], prefix: str = "") -> None:
+    """The inverse of ``load_gated_delta_net``: a ``GatedDeltaNet`` mixer's tensors under Qwen3-Next's names and groupings."""
+    out[prefix + "in_proj_qkvz.weight"] = _qkvz_to_grouped(mixer.in_proj_qkvz.weight.detach(), mixer.hk, mixer.hv, mixer.dk, mixer.dv)
+    out[prefix + "in_proj_ba.weight"] = _ba_to_grouped(mixer.in_proj_ba.weight.detach(), mixer.hk, mixer.hv)
+    w = mixer.conv1d.weight.detach()
+    out[prefix + "conv1d.weight"] = w.reshape(w.shape[0], 1, w.shape[-1])
+    out[prefix + "A_log"], out[prefix + "dt_bias"] = mixer.A_log.detach(), mixer.dt_bias.detach()
+    out[prefix + "norm.weight"], out[prefix + "out_proj.weight"] = mixer.norm_weight.detach(), mixer.out_proj.weight.detach()
+
+
 def load_gated_delta_net(mixer, hf: Mapping[str, torch.Tensor], prefix: str = "") -> None:
     """Copy a Qwen3-Next ``linear_attn`` layer (``in_proj_qkvz``, ``in_proj_ba``, ``conv1d``, ``A_log``, ``dt_bias``, ``norm``,
     ``out_proj``) into a ``GatedDeltaNet`` mixer, reordering the fused projections."""

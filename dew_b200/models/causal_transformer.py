@@ -95,6 +95,7 @@ class TransformerConfig:
     hyper_connections: int = 0                        # n > 1: n residual streams with learned read / write weights per sub-layer
     altup: int = 0                                    # K > 1: AltUp - K blocks, one of which every sub-layer computes on
     qkv_bias: bool = False                            # Qwen2: bias on the fused q | k | v projection only
+    attn_out_gate: bool = False                       # Qwen3-Next: a sigmoid gate from the layer's input on the heads' outputs
     attn_bias: bool = False                           # GPT-OSS: bias on q | k | v and on the output projection
     mlp_activation: str = "silu"                      # silu (SwiGLU) | gelu_tanh (Gemma's GeGLU) | gelu
     sandwich_norm: bool = False                       # Gemma-2: every sub-layer's output is normalised before it joins the stream
@@ -134,7 +135,7 @@ def _mixer(cfg: TransformerConfig, kind: str, dtype, device, index: int = 0) -> 
                           causal=True, window=cfg.window if kind == "local" or cfg.layer_types is None else None, bias=cfg.attn_bias,
                           softcap=cfg.attn_softcap, sinks=cfg.attention_sinks, norm_eps=cfg.norm_eps,
                           init_std=cfg.init_std, qkv_bias=cfg.qkv_bias, scale=cfg.query_scale, qk_norm_full=cfg.qk_norm_full,
-                          dtype=dtype, device=device)
+                          out_gate=cfg.attn_out_gate, dtype=dtype, device=device)
         a.rotary = kind != "nope"                        # SmolLM3's every fourth layer attends without positions
         if kind == "local" and cfg.local_rope_theta is not None:
             a.own_rope = (float(cfg.local_rope_theta), None)

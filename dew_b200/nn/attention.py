@@ -18,7 +18,7 @@ class SelfAttention(nn.Module):
                  qk_norm: bool = False, bias: bool = False, causal: bool = True, window: Optional[int] = None,
                  softcap: float = 0.0, sinks: bool = False, norm_eps: float = 1e-6, out_zero_init: bool = False,
                  init_std: Optional[float] = None, qkv_bias: bool = False, scale: Optional[float] = None, qk_norm_full: bool = False,
-                 dtype=None, device=None):
+                 out_gate: bool = False, dtype=None, device=None):
         super().__init__()
         self.features, self.num_heads = features, num_heads
         # a softmax scale other than head_dim ** -0.5 is folded into the queries (after the norm and the rotation)
@@ -30,6 +30,8 @@ class SelfAttention(nn.Module):
         self.qkv_proj = Linear(features, qkv_out, bias=bias or qkv_bias, axes=("embed", "heads"), init_std=init_std, dtype=dtype, device=device)
         self.o_proj = Linear(self.num_heads * self.head_dim, features, bias=bias, axes=("heads", "embed"),
                              init_std=init_std, zero_init=out_zero_init, dtype=dtype, device=device)
+        # Qwen3-Next: the heads' outputs pass a sigmoid gate computed from the layer's input, before the output projection
+        self.gate_proj = Linear(features, self.num_heads * self.head_dim, axes=("embed", "heads"), init_std=init_std, dtype=dtype, device=device) if out_gate else None
         # OLMo-2 normalises q and k over all their heads at once (one weight of heads x head_dim); the usual form is per head
         self.qk_norm_full = qk_norm_full
         qw, kw = (self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim) if qk_norm_full else (self.head_dim, self.head_dim)
@@ -88,7 +90,7 @@ class SelfAttention(nn.Module):
     def forward(self, x, cos=None, sin=None, positions=None, segment_ids=None, cache=None, layer: int = 0):
         B, S, _ = x.shape
         cos, sin = self._tables(cos, sin)
-        if (cache is None and x.is_cuda and cos is not None and self.head_transform is None and self.q_norm is None and self.window is None and not self.softcap
+        if (cache is None and x.is_cuda and cos is not None and self.head_transform is None and self.gate_proj is None and self.q_norm is None and self.window is None and not self.softcap
                 and self.sinks is None and segment_ids is None and not self.track_qk_max and self.q_gain is None):
             from ..ops.attn import packed_attention
             H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
@@ -96,7 +98,7 @@ class SelfAttention(nn.Module):
             if o is not None:
                 return self.o_proj(o.reshape(B, S, H * D))
         if (cache is not None and S == 1 and self.q_norm is None and self.q_gain is None and positions is not None and cos is not None
-                and self.head_transform is None and hasattr(cache, "decode_packed")):
+                and self.head_transform is None and self.gate_proj is None and hasattr(cache, "decode_packed")):
             # decode step: rotation, cache append and attention straight from the packed projection (no slices, no copies)
             H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
             qkv = self.qkv_proj(x).view(B, H + 2 * Hkv, D)
@@ -120,4 +122,7 @@ class SelfAttention(nn.Module):
                               segment_ids=segment_ids)
         if self.head_transform is not None:
             o = self.head_transform(o)
-        return self.o_proj(o.reshape(B, S, self.num_heads * self.head_dim))
+        o = o.reshape(B, S, self.num_heads * self.head_dim)
+        if self.gate_proj is not None:
+            o = o * torch.sigmoid(self.gate_proj(x).float()).to(o.dtype)
+        return self.o_proj(o)

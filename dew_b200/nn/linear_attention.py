@@ -48,9 +48,12 @@ class ShortConv(nn.Module):
 
 class GatedDeltaNet(nn.Module):
     def __init__(self, features: int, num_k_heads: int = 16, num_v_heads: int = 32, head_k_dim: int = 128, head_v_dim: int = 128,
-                 conv_size: int = 4, norm_eps: float = 1e-6, dtype=None, device=None):
+                 conv_size: int = 4, norm_eps: float = 1e-6, qk_eps: Optional[float] = None, dtype=None, device=None):
         super().__init__()
         self.features = features
+        # how q and k are l2-normalised: None - x / max(|x|, 1e-12) (the row kernel on a GPU); a number - x * rsqrt(sum x^2 + qk_eps), the form
+        # the Qwen3-Next releases were trained with (1e-6), which differs by a part in a thousand where the projections are small
+        self.qk_eps = qk_eps
         self.hk, self.hv, self.dk, self.dv = num_k_heads, num_v_heads, head_k_dim, head_v_dim
         self.key_dim, self.value_dim = num_k_heads * head_k_dim, num_v_heads * head_v_dim
         self.in_proj_qkvz = Linear(features, 2 * self.key_dim + 2 * self.value_dim, axes=("embed", "heads"), dtype=dtype, device=device)
@@ -83,8 +86,13 @@ class GatedDeltaNet(nn.Module):
         state = cache.recurrent(layer, B, self) if cache is not None and hasattr(cache, "recurrent") else None
         qkv = self.conv1d(qkv, segment_ids, state["conv"] if state is not None else None)
         q, k, v = qkv.split([self.key_dim, self.key_dim, self.value_dim], -1)
-        q = ops.l2_normalize(q.reshape(B, T, self.hk, self.dk))        # bf16 row kernel on a GPU, fp32 F.normalize elsewhere
-        k = ops.l2_normalize(k.reshape(B, T, self.hk, self.dk))
+        if self.qk_eps is None:
+            q = ops.l2_normalize(q.reshape(B, T, self.hk, self.dk))        # bf16 row kernel on a GPU, fp32 F.normalize elsewhere
+            k = ops.l2_normalize(k.reshape(B, T, self.hk, self.dk))
+        else:
+            q, k = q.reshape(B, T, self.hk, self.dk).float(), k.reshape(B, T, self.hk, self.dk).float()
+            q = (q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + self.qk_eps)).to(x.dtype)
+            k = (k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + self.qk_eps)).to(x.dtype)
         v = v.reshape(B, T, self.hv, self.dv)
         rep = self.hv // self.hk
         decode = state is not None and T == 1
