@@ -4,7 +4,7 @@ offsets, extra norms, expert naming).  ``family_of(config)`` picks the entry by 
 ``load_state`` / ``export_state`` move tensors between a release's names and a ``CausalTransformer``, and ``load_state``
 returns the release's keys nothing read, so a silent partial load cannot happen.
 
-Families: llama, mistral, qwen2 (q/k/v bias), qwen3 (per-head q/k norm), qwen3_moe, mixtral, gemma (norm weight stored
+Families: llama, mistral, qwen2 (q/k/v bias), qwen3 (per-head q/k norm), qwen3_moe, qwen2_moe (a gated shared expert), mixtral, gemma (norm weight stored
 minus one, GeGLU, scaled embeddings), gemma2 (output norms on every sub-layer, soft-capped logits, alternating local /
 global layers, query scale), phi3 (fused qkv and gate_up on disk), granite (embedding / attention / residual multipliers, logits scaling), olmo2 (no pre-norms: every sub-layer's output is
 normalised instead; q and k normalised over all heads at once), olmo3 (olmo2 with sliding layers on an unscaled rotary table), gemma3 (gemma2's
@@ -89,6 +89,16 @@ def _qwen3(cfg):
 
 def _qwen3_moe(cfg):
     return _common(cfg, qk_norm=True, mixture=_mixture(cfg, always_norm=False))
+
+
+def _qwen2_moe(cfg):
+    n = cfg["num_hidden_layers"]
+    sparse_step, dense_only = int(cfg.get("decoder_sparse_step", 1) or 1), set(cfg.get("mlp_only_layers") or ())
+    mix = Mixture(experts=int(cfg["num_experts"]), top_k=int(cfg["num_experts_per_tok"]), expert_features=int(cfg["moe_intermediate_size"]),
+                  norm_topk_prob=bool(cfg.get("norm_topk_prob", False)), shared_features=int(cfg.get("shared_expert_intermediate_size") or 0),
+                  shared_gate=True, layers=tuple(i for i in range(n) if i not in dense_only and (i + 1) % sparse_step == 0))
+    use_window = cfg.get("use_sliding_window", False)
+    return _common(cfg, qkv_bias=True, mixture=mix, window=cfg.get("sliding_window") if use_window else None)
 
 
 def _mixtral(cfg):
@@ -230,7 +240,8 @@ FAMILIES: Dict[str, Family] = {f.name: f for f in (
     Family("mistral", ("mistral",), "MistralForCausalLM", _llama),
     Family("qwen2", ("qwen2",), "Qwen2ForCausalLM", _qwen2, qkv_bias=True),
     Family("qwen3", ("qwen3",), "Qwen3ForCausalLM", _qwen3),
-    Family("qwen3_moe", ("qwen3_moe", "qwen2_moe"), "Qwen3MoeForCausalLM", _qwen3_moe, experts="qwen"),
+    Family("qwen3_moe", ("qwen3_moe",), "Qwen3MoeForCausalLM", _qwen3_moe, experts="qwen"),
+    Family("qwen2_moe", ("qwen2_moe",), "Qwen2MoeForCausalLM", _qwen2_moe, qkv_bias=True, experts="qwen"),
     Family("mixtral", ("mixtral",), "MixtralForCausalLM", _mixtral, experts="mixtral"),
     Family("gemma", ("gemma",), "GemmaForCausalLM", _gemma, norm_offset=1.0, extra_config={"hidden_activation": "gelu_pytorch_tanh"}),
     Family("gemma2", ("gemma2",), "Gemma2ForCausalLM", _gemma2, norm_offset=1.0, mixer_out_norm="post_attention_layernorm",
@@ -306,6 +317,8 @@ def write_config(c: TransformerConfig, family: str = "llama", dtype: str = "bflo
                     "moe_layer_freq": 1, "kv_lora_rank": o["kv_latent"], "q_lora_rank": o.get("q_latent"), "qk_nope_head_dim": o["nope_dim"],
                     "qk_rope_head_dim": o["rope_dim"], "v_head_dim": o["v_dim"], "head_dim": o["rope_dim"],
                     "num_key_value_heads": c.num_heads, "rope_interleave": True})
+    if fam.name == "qwen2_moe":
+        out.update({"shared_expert_intermediate_size": c.mixture.shared_features, "use_sliding_window": c.window is not None})
     if fam.name == "qwen3_next":
         o, m = c.mixer_options, c.mixture
         out.update({"layer_types": ["linear_attention" if k == "gdn" else "full_attention" for k in kinds], "linear_num_key_heads": o["num_k_heads"],
@@ -625,6 +638,11 @@ def export_state(model: CausalTransformer, family: Family) -> Dict[str, torch.Te
             Fe = gu_all.shape[1] // 2
             mixtral = family.experts == "mixtral"
             out[pre + ("block_sparse_moe.gate.weight" if mixtral else "mlp.gate.weight")] = layer.mlp.router.weight.detach()
+            if layer.mlp.shared is not None and getattr(layer.mlp, "shared_gate", None) is not None:
+                sw = layer.mlp.shared.gate_up_proj.weight.detach()
+                out[pre + "mlp.shared_expert.gate_proj.weight"], out[pre + "mlp.shared_expert.up_proj.weight"] = sw[: sw.shape[0] // 2], sw[sw.shape[0] // 2:]
+                out[pre + "mlp.shared_expert.down_proj.weight"] = layer.mlp.shared.down_proj.weight.detach()
+                out[pre + "mlp.shared_expert_gate.weight"] = layer.mlp.shared_gate.weight.detach()
             for j in range(gu_all.shape[0]):
                 base = pre + (f"block_sparse_moe.experts.{j}." if mixtral else f"mlp.experts.{j}.")
                 g_n, u_n, d_n = ("w1", "w3", "w2") if mixtral else ("gate_proj", "up_proj", "down_proj")

@@ -42,6 +42,7 @@ CASES = {
                     layer_types=["sliding_attention", "full_attention"],
                     rope_parameters={"rope_type": "yarn", "rope_theta": 150000.0, "factor": 4.0, "original_max_position_embeddings": 16,
                                      "beta_fast": 32.0, "beta_slow": 1.0, "truncate": False}),
+    "qwen2_moe": dict(model_type="qwen2_moe", num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=48, **COMMON),
     "qwen3_next": dict(model_type="qwen3_next", vocab_size=96, hidden_size=64, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
                        intermediate_size=128, moe_intermediate_size=32, shared_expert_intermediate_size=48, num_experts=4, num_experts_per_tok=2,
                        max_position_embeddings=64, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16, linear_value_head_dim=16,
