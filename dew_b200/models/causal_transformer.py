@@ -10,6 +10,8 @@ normalised value).
 """
 from __future__ import annotations
 
+import contextlib
+
 from dataclasses import dataclass, field
 from typing import Mapping, Any, Dict, List, Optional, Sequence, Tuple
 
@@ -58,6 +60,8 @@ class Loop:
     end: Optional[int] = None
     exit_gate: bool = False
     backprop_steps: Optional[int] = None
+    messages: int = 0                # n > 0: cross-pass messages - every pass starts from the prelude's output and reads the summaries the pass
+    message_rank: int = 16           # before left of every block of n looped layers, merged into each sub-layer's input (nn/cross_pass.py)
 
     def __post_init__(self):
         if self.steps < 1 or self.first < 0 or (self.end is not None and self.end <= self.first):
@@ -227,6 +231,7 @@ class DecoderLayer(nn.Module):
         self.mixer_out_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device) if cfg.sandwich_norm else None
         self.mlp_out_norm = RMSNorm(cfg.emb_features, cfg.norm_eps, dtype=dtype, device=device) if cfg.sandwich_norm else None
         self.tp = None          # set by parallel.tp.tensor_parallelize: branches are then partial sums over ranks
+        self.cross = None       # set by the model for the layers of a loop with messages: one merge per sub-layer input
         self.residual_multiplier = float(cfg.residual_multiplier)
         self.streams = None
         if cfg.hyper_connections > 1 or cfg.altup > 1:
@@ -265,8 +270,21 @@ class DecoderLayer(nn.Module):
             return self.tp.reduce_add_norm(branch, h, norm.weight, norm.eps)
         return norm(h, branch)
 
-    def forward(self, h, branch, cos, sin, positions, segment_ids, cache):
+    def _merged(self, h, branch, cos, sin, positions, segment_ids, bank):
+        """The layer with the earlier pass's summaries merged into each sub-layer's input, before its norm."""
+        h = h if branch is None else h + branch
+        n = self.input_norm(self.cross[0](h, bank))
+        if self.kind in ROTARY_KINDS:
+            a = self.mixer(n, cos, sin, positions, segment_ids, None, self.index)
+        else:
+            a = self.mixer(n, segment_ids=segment_ids, cache=None, layer=self.index)
+        h = h + a
+        return h, self.mlp(self.post_norm(self.cross[1](h, bank)))
+
+    def forward(self, h, branch, cos, sin, positions, segment_ids, cache, bank=None):
         """(stream, pending branch) -> (stream, pending branch); the branch is added by the next norm."""
+        if bank is not None and self.cross is not None:
+            return self._merged(h, branch, cos, sin, positions, segment_ids, bank)
         if branch is None:
             n = self.input_norm(h)
             if self.tp is not None and getattr(self, "tp_training", False):
@@ -329,6 +347,13 @@ class CausalTransformer(nn.Module):
         self.mtp = nn.ModuleList([MTPBlock(cfg, i, dtype, device) for i in range(cfg.mtp_depth)]) if cfg.mtp_depth > 0 else None
         self.early_exit_gate = Linear(cfg.emb_features, 1, bias=True, init_std=cfg.init_std, dtype=dtype, device=device) \
             if cfg.loop is not None and cfg.loop.exit_gate else None
+        if cfg.loop is not None and cfg.loop.messages > 0:
+            if cfg.sandwich_norm or not cfg.pre_norm or cfg.layer_mlp is not None or cfg.residual_multiplier != 1.0:
+                raise NotImplementedError("cross-pass messages are built for the plain pre-norm block")
+            from ..nn.cross_pass import CrossPassMerge
+            first, end = cfg.loop.first, cfg.num_layers if cfg.loop.end is None else cfg.loop.end
+            for layer in self.layers[first:end]:
+                layer.cross = nn.ModuleList(CrossPassMerge(cfg.emb_features, cfg.loop.message_rank, cfg.norm_eps, device=device) for _ in range(2))
         self.depth_sites = None
         if cfg.depth_residual_block > 0:
             if cfg.sandwich_norm or not cfg.pre_norm or cfg.loop is not None or max(cfg.hyper_connections, cfg.altup) > 1 or any(k == "none" for k in kinds):
@@ -407,6 +432,29 @@ class CausalTransformer(nn.Module):
 
         h, branch = run(self.layers[:first], h, None)
         exits = []
+        if loop.messages > 0:
+            if getattr(self, "tp", None) is not None:
+                raise NotImplementedError("cross-pass messages are not built for tensor parallelism")
+            start, bank = (h, branch), None
+            looped = list(self.layers[first:end])
+            for s in range(steps):
+                cut = loop.backprop_steps is not None and s < steps - loop.backprop_steps and torch.is_grad_enabled()
+                with torch.no_grad() if cut else contextlib.nullcontext():
+                    h, branch = start
+                    summaries = []
+                    for j, layer in enumerate(looped):
+                        if remat and not cut:
+                            h, branch = ckpt.checkpoint(layer, h, branch, cos, sin, positions, segment_ids, None, bank, use_reentrant=False)
+                        else:
+                            h, branch = layer(h, branch, cos, sin, positions, segment_ids, None, bank)
+                        if (j + 1) % loop.messages == 0 or j == len(looped) - 1:
+                            summaries.append(h if branch is None else h + branch)
+                    bank = torch.stack(summaries, 2)
+                    if cut:
+                        bank = bank.detach()
+                if passes or s == steps - 1:
+                    exits.append(self._finish(*run(self.layers[end:], h, branch)))
+            return exits if passes else exits[-1]
         for s in range(steps):
             cut = loop.backprop_steps is not None and s < steps - loop.backprop_steps and torch.is_grad_enabled()
             if cut:
