@@ -34,6 +34,23 @@ def _token_logprobs(logits, tokens):
     return torch.log_softmax(logits.float(), -1).gather(-1, tokens[:, 1:, None]).squeeze(-1)
 
 
+def forked_logits(call, tokens: torch.Tensor, full_mask: torch.Tensor, window: int, min_prefix: int = 8) -> torch.Tensor:
+    """Logits ``[B, S-1, V]`` of the inputs ``tokens[:, :-1]`` computed with rows that begin alike laid out once (``data.forked_rows``):
+    each row is cut after its last masked token, the rows are grouped by common prefix and packed, ``call(tokens, positions=...,
+    segment_ids=forks)`` runs the model, and the outputs are gathered back row by row.  Places past a row's last masked token hold zeros,
+    which the mask never reads.  (The grouping reads the token ids on the host.)"""
+    from ...data.forked_rows import ForkedRows
+    B, S = tokens.shape
+    last = torch.where(full_mask.bool().any(1), S - full_mask.bool().flip(1).float().argmax(1), torch.full((B,), S, device=tokens.device))
+    rows = [tokens[i, :max(1, int(n) - 1)].tolist() for i, n in enumerate(last.tolist())]
+    packed = ForkedRows.pack(rows, window=window, min_prefix=min_prefix)
+    dev = tokens.device
+    out = call(packed.tokens.to(dev), positions=packed.positions.to(dev), segment_ids=packed.forks.to(dev))
+    out = out[0] if isinstance(out, tuple) else out
+    padded, _ = packed.padded(out)
+    return torch.nn.functional.pad(padded, (0, 0, 0, S - 1 - padded.shape[1]))
+
+
 _ADVANTAGES = {"grpo": lambda r, g: A.group_advantage(r, g), "dr_grpo": A.dr_grpo_advantage, "rloo": A.rloo_advantage, "global": A.global_advantage}
 RULES = ("ppo", "gspo", "cispo", "gmpo", "reinforce")
 
@@ -63,20 +80,11 @@ class GRPO(Objective):
         self.ema_decay = EMASpec.constant(1.0)
 
     def _logits(self, variables, tokens, full_mask):
-        """Logits ``[B, S-1, V]`` of the inputs ``tokens[:, :-1]``; with ``share_prefix`` through the forked layout (places past a row's last
-        completion token hold zeros, which the mask never reads)."""
+        """Logits ``[B, S-1, V]`` of the inputs ``tokens[:, :-1]``; with ``share_prefix`` through the forked layout."""
         if not self.share_prefix:
             return self.apply(variables, tokens[:, :-1])
-        from ...data.forked_rows import ForkedRows
-        B, S = tokens.shape
-        last = torch.where(full_mask.bool().any(1), S - full_mask.bool().flip(1).float().argmax(1), torch.full((B,), S, device=tokens.device))
-        rows = [tokens[i, :max(1, int(n) - 1)].tolist() for i, n in enumerate(last.tolist())]
-        packed = ForkedRows.pack(rows, window=max(S - 1, self.group * (S - 1) // 2), min_prefix=self.min_prefix)
-        dev = tokens.device
-        out = self.apply(variables, packed.tokens.to(dev), positions=packed.positions.to(dev), segment_ids=packed.forks.to(dev))
-        out = out[0] if isinstance(out, tuple) else out
-        padded, _ = packed.padded(out)
-        return torch.nn.functional.pad(padded, (0, 0, 0, S - 1 - padded.shape[1]))
+        S = tokens.shape[1]
+        return forked_logits(lambda *a, **k: self.apply(variables, *a, **k), tokens, full_mask, max(S - 1, self.group * (S - 1) // 2), self.min_prefix)
 
     def loss(self, variables, batch, step: Step):
         tokens, mask = batch["tokens"], batch["mask"][:, 1:].bool()

@@ -96,3 +96,33 @@ def test_grpo_with_a_shared_prompt_gives_the_same_loss_and_gradients():
     for a, b in zip(results[0][1], results[1][1]):
         if a is not None:
             assert torch.allclose(a, b, atol=1e-5 + 1e-4 * float(a.abs().max()))
+
+
+def test_dpo_with_a_shared_prompt_gives_the_same_loss_and_gradients():
+    from dew_b200.objectives.base import Step
+    from dew_b200.objectives.rl.preference import DPO
+    torch.manual_seed(0)
+    cfg = TransformerConfig(vocab_size=50, emb_features=32, num_layers=2, num_heads=4, mlp_features=64, max_seq_len=64, qk_norm=False)
+    model = CausalTransformer(cfg, dtype=torch.float32)
+    reference = {k: v.detach().clone() + 0.01 * torch.randn_like(v) for k, v in model.named_parameters()}
+    B, P, S = 3, 9, 16
+    chosen, rejected = torch.zeros(B, S, dtype=torch.long), torch.zeros(B, S, dtype=torch.long)
+    cm, rm = torch.zeros(B, S), torch.zeros(B, S)
+    for i in range(B):
+        prompt = torch.randint(1, 50, (P,))
+        nc, nr = int(torch.randint(2, S - P + 1, ())), int(torch.randint(2, S - P + 1, ()))
+        chosen[i, :P], rejected[i, :P] = prompt, prompt
+        chosen[i, P:P + nc], rejected[i, P:P + nr] = torch.randint(1, 50, (nc,)), torch.randint(1, 50, (nr,))
+        cm[i, P:P + nc], rm[i, P:P + nr] = 1, 1
+    batch = dict(chosen=chosen, rejected=rejected, chosen_mask=cm, rejected_mask=rm)
+    from dew_b200.utils.trees import unflatten
+    results = []
+    for share in (False, True):
+        obj = DPO(model, beta=0.5, share_prefix=share, min_prefix=4)
+        stats, aux = obj.loss(None, batch, Step(step=0))
+        value = stats.total / stats.mass
+        results.append((value.detach(), torch.autograd.grad(value, list(model.parameters()), allow_unused=True)))
+    assert torch.allclose(results[0][0], results[1][0], atol=1e-5)
+    for a, b in zip(results[0][1], results[1][1]):
+        if a is not None:
+            assert torch.allclose(a, b, atol=1e-5 + 1e-4 * float(a.abs().max()))
