@@ -4,7 +4,7 @@ offsets, extra norms, expert naming).  ``family_of(config)`` picks the entry by 
 ``load_state`` / ``export_state`` move tensors between a release's names and a ``CausalTransformer``, and ``load_state``
 returns the release's keys nothing read, so a silent partial load cannot happen.
 
-Families: llama, mistral, qwen2 (q/k/v bias), qwen3 (per-head q/k norm), qwen3_moe, qwen2_moe (a gated shared expert), mixtral, gemma (norm weight stored
+Families: llama, mistral, qwen2 (q/k/v bias), dream (qwen2's tensors under bidirectional attention), qwen3 (per-head q/k norm), qwen3_moe, qwen2_moe (a gated shared expert), mixtral, gemma (norm weight stored
 minus one, GeGLU, scaled embeddings), gemma2 (output norms on every sub-layer, soft-capped logits, alternating local /
 global layers, query scale), phi3 (fused qkv and gate_up on disk), granite (embedding / attention / residual multipliers, logits scaling), olmo2 (no pre-norms: every sub-layer's output is
 normalised instead; q and k normalised over all heads at once), olmo3 (olmo2 with sliding layers on an unscaled rotary table), gemma3 (gemma2's
@@ -81,6 +81,11 @@ def _llama(cfg):
 def _qwen2(cfg):
     use_window = cfg.get("use_sliding_window", False)
     return _common(cfg, qkv_bias=True, window=cfg.get("sliding_window") if use_window else None)
+
+
+def _dream(cfg):
+    """Dream: Qwen2's block read bidirectionally (a masked-diffusion language model)."""
+    return dict(_qwen2(cfg), causal=False)
 
 
 def _qwen3(cfg):
@@ -239,6 +244,7 @@ FAMILIES: Dict[str, Family] = {f.name: f for f in (
     Family("smollm3", ("smollm3",), "SmolLM3ForCausalLM", _smollm3),
     Family("mistral", ("mistral",), "MistralForCausalLM", _llama),
     Family("qwen2", ("qwen2",), "Qwen2ForCausalLM", _qwen2, qkv_bias=True),
+    Family("dream", ("dream",), "DreamModel", _dream, qkv_bias=True),
     Family("qwen3", ("qwen3",), "Qwen3ForCausalLM", _qwen3),
     Family("qwen3_moe", ("qwen3_moe",), "Qwen3MoeForCausalLM", _qwen3_moe, experts="qwen"),
     Family("qwen2_moe", ("qwen2_moe",), "Qwen2MoeForCausalLM", _qwen2_moe, qkv_bias=True, experts="qwen"),

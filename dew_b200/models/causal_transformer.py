@@ -99,6 +99,7 @@ class TransformerConfig:
     hyper_connections: int = 0                        # n > 1: n residual streams with learned read / write weights per sub-layer
     altup: int = 0                                    # K > 1: AltUp - K blocks, one of which every sub-layer computes on
     qkv_bias: bool = False                            # Qwen2: bias on the fused q | k | v projection only
+    causal: bool = True                               # False: every token sees the whole row (masked-diffusion decoders: LLaDA, Dream)
     attn_out_gate: bool = False                       # Qwen3-Next: a sigmoid gate from the layer's input on the heads' outputs
     attn_bias: bool = False                           # GPT-OSS: bias on q | k | v and on the output projection
     mlp_activation: str = "silu"                      # silu (SwiGLU) | gelu_tanh (Gemma's GeGLU) | gelu
@@ -136,7 +137,7 @@ ROTARY_KINDS = ("attention", "local", "nope", "mla", "differential", "forgetting
 def _mixer(cfg: TransformerConfig, kind: str, dtype, device, index: int = 0) -> nn.Module:
     if kind in ("attention", "local", "nope"):
         a = SelfAttention(cfg.emb_features, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, qk_norm=cfg.qk_norm,
-                          causal=True, window=cfg.window if kind == "local" or cfg.layer_types is None else None, bias=cfg.attn_bias,
+                          causal=cfg.causal, window=cfg.window if kind == "local" or cfg.layer_types is None else None, bias=cfg.attn_bias,
                           softcap=cfg.attn_softcap, sinks=cfg.attention_sinks, norm_eps=cfg.norm_eps,
                           init_std=cfg.init_std, qkv_bias=cfg.qkv_bias, scale=cfg.query_scale, qk_norm_full=cfg.qk_norm_full,
                           out_gate=cfg.attn_out_gate, dtype=dtype, device=device)

@@ -52,3 +52,37 @@ def test_block_generation_commits_confident_places_together_and_counts_steps():
     stopper = BlockDiffusionLM(Oracle([1, 2, 3, 4, 5, 0, 7, 8, 9, 10, 5, 6], [True] * 12), mask_id=11, block=4)
     out, _ = stopper.generate(None, prompt, blocks=2, bound=1.0, stop_id=0)
     assert out[0].tolist() == [1, 2, 3, 4, 5, 0, 0, 0, 0, 0, 0, 0]
+
+
+def test_masked_diffusion_trains_the_decoder_read_bidirectionally():
+    """A pattern only the right-hand neighbour reveals: a causal decoder cannot fill it in, a bidirectional one can."""
+    from dew_b200.models.causal_transformer import CausalTransformer, TransformerConfig
+    from dew_b200.objectives.base import Step
+    from dew_b200.objectives.discrete import MaskedDiffusionLM
+    torch.manual_seed(0)
+    V, MASK = 12, 11
+
+    def batch(n):
+        right = torch.randint(0, 5, (n, 4))
+        rows = torch.stack([right + 5, right], 2).reshape(n, 8)          # each even place is its right neighbour plus five
+        return {"tokens": rows}
+    accuracy = {}
+    for causal in (True, False):
+        torch.manual_seed(1)
+        model = CausalTransformer(TransformerConfig(vocab_size=V, emb_features=32, num_layers=2, num_heads=4, mlp_features=64, max_seq_len=8, qk_norm=False,
+                                                    causal=causal), dtype=torch.float32)
+        obj = MaskedDiffusionLM(model, mask_id=MASK)
+        opt = torch.optim.Adam(model.parameters(), lr=3e-3)
+        for i in range(150):
+            stats, _ = obj.loss(None, batch(32), Step(step=i, key=i))
+            opt.zero_grad()
+            (stats.total / stats.mass).backward()
+            opt.step()
+        test = batch(64)["tokens"]
+        hidden = test.clone()
+        hidden[:, 0::2] = MASK                                           # hide the even places, keep what reveals them
+        with torch.no_grad():
+            out = model(hidden)
+            out = out[0] if isinstance(out, tuple) else out
+        accuracy[causal] = float((out.argmax(-1)[:, 0::2] == test[:, 0::2]).float().mean())
+    assert accuracy[False] > 0.7 and accuracy[True] < 0.4, accuracy

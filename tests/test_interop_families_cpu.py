@@ -157,3 +157,30 @@ def test_rotary_scalings_match_transformers():
     assert float((short - want.float()).abs().max()) < 1e-6
     with pytest.raises(ValueError, match="not built"):
         ops.rope_tables(32, 16, 10000.0, "cpu", {"rope_type": "dynamic", "factor": 2.0})
+
+
+def test_dream_is_qwen2_read_bidirectionally():
+    transformers = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    cfg = transformers.AutoConfig.for_model(**CASES["qwen2"])
+    cfg._attn_implementation = "eager"
+    hf = transformers.AutoModelForCausalLM.from_config(cfg).float().eval()
+    d = dict(cfg.to_dict(), model_type="Dream", architectures=["DreamModel"])
+    fam = family_of(d)
+    assert fam.name == "dream"
+    config = read_config(d)
+    assert config.causal is False
+    ours = CausalTransformer(config, dtype=torch.float32).eval()
+    assert load_state(ours, dict(hf.state_dict()), fam) == []
+    tokens = torch.randint(0, 96, (2, 12))
+    everything = torch.zeros(2, 1, 12, 12)                                   # an additive mask that hides nothing
+    with torch.no_grad():
+        want = hf(tokens, attention_mask=everything).logits
+        got = _logits(ours, tokens)
+        causal = hf(tokens).logits
+    assert float((got - want).abs().max()) <= 2e-6 * max(1.0, float(want.abs().max()))
+    assert float((got - causal).abs().max()) > 1e-3
+    later = tokens.clone()
+    later[:, -1] = (later[:, -1] + 1) % 96
+    with torch.no_grad():
+        assert not torch.allclose(_logits(ours, later)[:, 0], got[:, 0])       # the first place reads the last
