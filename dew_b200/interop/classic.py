@@ -1,13 +1,14 @@
 """Published checkpoints of the decoder lineage before RMSNorm and gated MLPs, read into (and written from) ``ClassicDecoder``: GPT-2
 (Conv1D weights stored ``[in, out]``, learned positions), GPTBigCode (multi-query GPT-2 with Linear weights), GPT-NeoX (two-norm parallel
-block, q | k | v interleaved per head, a quarter of each head rotating), Falcon-7B (one-norm parallel block, multi-query, no biases), Phi
+block, q | k | v interleaved per head, a quarter of each head rotating), Falcon (7B: one-norm parallel block, multi-query; 40B / 180B: grouped keys stored per group, one or two norms), GPT-J (one-norm
+parallel block, rotary pairs over part of each head, a biased head), Phi
 (one-norm parallel block, half of each head rotating, a biased output head), OPT (position table offset by two, ReLU, pre- or post-norm, the
 350m size's embedding projections), BLOOM (ALiBi, a norm on the embeddings, per-head q | k | v) and StarCoder2 (rotary, grouped keys, a
 sliding window).  One ``ClassicFamily`` row per family says how its ``config.json`` reads as a ``ClassicConfig`` and under which names and
 storage forms its tensors sit; ``load_state`` returns the keys nothing read, so a partial load cannot pass silently, and
 ``export_state`` writes the same names back.
 
-Reference: src/dew/interop/families/gpt2.py, gpt_bigcode.py, gpt_neox.py, falcon.py, phi.py, opt.py, bloom.py, starcoder2.py.
+Reference: src/dew/interop/families/gpt2.py, gpt_bigcode.py, (GPT-J: the parts of decoder_parts.py), gpt_neox.py, falcon.py, phi.py, opt.py, bloom.py, starcoder2.py.
 """
 from __future__ import annotations
 
@@ -49,14 +50,26 @@ def _gpt_neox(cfg):
                 attn_bias=bool(cfg.get("attention_bias", True)), tie_embeddings=bool(cfg.get("tie_word_embeddings", False)))
 
 
+def _gptj(cfg):
+    E, H = cfg["n_embd"], cfg["n_head"]
+    return dict(vocab_size=cfg["vocab_size"], emb_features=E, num_layers=cfg["n_layer"], num_heads=H, mlp_features=cfg.get("n_inner") or 4 * E,
+                max_seq_len=cfg["n_positions"], norm_eps=cfg.get("layer_norm_epsilon", 1e-5), activation=_ACT[cfg.get("activation_function", "gelu_new")],
+                positions="rotary", rope_theta=_theta(cfg), rotary_fraction=float(cfg.get("rotary_dim") or E // H) / (E // H), block="parallel",
+                parallel_norms=1, attn_bias=False, mlp_bias=True, tie_embeddings=bool(cfg.get("tie_word_embeddings", False)), head_bias=True)
+
+
 def _falcon(cfg):
-    if cfg.get("new_decoder_architecture") or cfg.get("alibi") or not cfg.get("parallel_attn", True):
-        raise NotImplementedError("of Falcon, the 7B layout is built: one-norm parallel block, rotary positions (not the 40B / 180B two-norm grouped layout, nor ALiBi)")
+    new = bool(cfg.get("new_decoder_architecture"))
+    if cfg.get("alibi") or not (new or cfg.get("parallel_attn", True)):
+        raise NotImplementedError("of Falcon, the rotary parallel-block layouts are built: 7B's (one norm, multi-query) and 40B / 180B's (grouped keys, "
+                                  "one or two norms) - not ALiBi, nor the sequential block")
     E = cfg["hidden_size"]
+    kv = int(cfg.get("num_kv_heads") or cfg["num_attention_heads"]) if new else (1 if cfg.get("multi_query", True) else None)
+    norms = int(cfg.get("num_ln_in_parallel_attn") or 2) if new else 1
     return dict(vocab_size=cfg["vocab_size"], emb_features=E, num_layers=cfg["num_hidden_layers"], num_heads=cfg["num_attention_heads"],
-                num_kv_heads=1 if cfg.get("multi_query", True) else None, mlp_features=cfg.get("ffn_hidden_size") or 4 * E,
+                num_kv_heads=kv, parallel_norms=norms, mlp_features=cfg.get("ffn_hidden_size") or 4 * E,
                 max_seq_len=cfg.get("max_position_embeddings", 2048), norm_eps=cfg.get("layer_norm_epsilon", 1e-5), activation=_ACT[cfg.get("activation", "gelu")],
-                positions="rotary", rope_theta=_theta(cfg), block="parallel", parallel_norms=1, attn_bias=bool(cfg.get("bias", False)),
+                positions="rotary", rope_theta=_theta(cfg), block="parallel", attn_bias=bool(cfg.get("bias", False)),
                 mlp_bias=bool(cfg.get("bias", False)), tie_embeddings=bool(cfg.get("tie_word_embeddings", True)))
 
 
@@ -104,6 +117,8 @@ class ClassicFamily:
     read_config: Callable[[Mapping[str, Any]], Dict[str, Any]]
     names: Mapping[str, str]                       # slot -> the release's name; layer slots are formatted with the layer index
     qkv: str = "split"                             # split: q, k, v tensors | packed: one tensor q | k | v | by_head: one tensor, (q, k, v) per head
+                                                   # | grouped: one tensor, per key head its queries then its key then its value
+    rotary_pairs: bool = False                     # the release rotates pairs (2i, 2i + 1) of a head's rotating part, not its halves
     transposed: bool = False                       # GPT-2's Conv1D stores weights [in, out]
     extra_config: Mapping[str, Any] = field(default_factory=dict)
 
@@ -125,6 +140,15 @@ CLASSIC: Dict[str, ClassicFamily] = {f.name: f for f in (
     ClassicFamily("falcon", "FalconForCausalLM", _falcon, _names(
         "transformer.", "h.{}.", embed="word_embeddings", final_norm="ln_f", head="/lm_head", norm1="@input_layernorm", qkv="@self_attention.query_key_value",
         out="@self_attention.dense", fc1="@mlp.dense_h_to_4h", fc2="@mlp.dense_4h_to_h"), qkv="packed"),
+    ClassicFamily("falcon_grouped", "FalconForCausalLM", _falcon, _names(
+        "transformer.", "h.{}.", embed="word_embeddings", final_norm="ln_f", head="/lm_head", norm1="@ln_attn", norm2="@ln_mlp", qkv="@self_attention.query_key_value",
+        out="@self_attention.dense", fc1="@mlp.dense_h_to_4h", fc2="@mlp.dense_4h_to_h"), qkv="grouped"),
+    ClassicFamily("falcon_grouped_one_norm", "FalconForCausalLM", _falcon, _names(
+        "transformer.", "h.{}.", embed="word_embeddings", final_norm="ln_f", head="/lm_head", norm1="@input_layernorm", qkv="@self_attention.query_key_value",
+        out="@self_attention.dense", fc1="@mlp.dense_h_to_4h", fc2="@mlp.dense_4h_to_h"), qkv="grouped"),
+    ClassicFamily("gptj", "GPTJForCausalLM", _gptj, _names(
+        "transformer.", "h.{}.", embed="wte", final_norm="ln_f", head="/lm_head", norm1="@ln_1", q="@attn.q_proj", k="@attn.k_proj", v="@attn.v_proj",
+        out="@attn.out_proj", fc1="@mlp.fc_in", fc2="@mlp.fc_out"), rotary_pairs=True),
     ClassicFamily("phi", "PhiForCausalLM", _phi, _names(
         "model.", "layers.{}.", embed="embed_tokens", final_norm="final_layernorm", head="/lm_head", norm1="@input_layernorm", q="@self_attn.q_proj",
         k="@self_attn.k_proj", v="@self_attn.v_proj", out="@self_attn.dense", fc1="@mlp.fc1", fc2="@mlp.fc2")),
@@ -144,6 +168,8 @@ CLASSIC: Dict[str, ClassicFamily] = {f.name: f for f in (
 
 def classic_family_of(cfg: Mapping[str, Any]) -> ClassicFamily:
     mt = str(cfg.get("model_type") or "").lower()
+    if mt == "falcon" and cfg.get("new_decoder_architecture"):
+        return CLASSIC["falcon_grouped" if int(cfg.get("num_ln_in_parallel_attn") or 2) == 2 else "falcon_grouped_one_norm"]
     if mt in CLASSIC:
         return CLASSIC[mt]
     arch = (cfg.get("architectures") or [""])[0]
@@ -164,6 +190,9 @@ def _qkv_to_ours(t: torch.Tensor, fam: ClassicFamily, H: int, Hkv: int, D: int, 
     if fam.qkv == "by_head":
         per = t.reshape(H, 3, D, -1)
         t = torch.cat([per[:, 0], per[:, 1], per[:, 2]], 0).reshape(t.shape)
+    elif fam.qkv == "grouped":
+        per = t.reshape(Hkv, H // Hkv + 2, D, -1)
+        t = torch.cat([per[:, :-2].reshape(H, D, -1), per[:, -2], per[:, -1]], 0).reshape(t.shape)
     if order is not None:
         heads = t.reshape(H + 2 * Hkv, D, -1).clone()
         heads[: H + Hkv] = heads[: H + Hkv][:, order]
@@ -179,6 +208,10 @@ def _qkv_to_theirs(t: torch.Tensor, fam: ClassicFamily, H: int, Hkv: int, D: int
     if fam.qkv == "by_head":
         parts = t.reshape(3, H, D, -1)
         t = torch.stack([parts[0], parts[1], parts[2]], 1).reshape(t.shape)
+    elif fam.qkv == "grouped":
+        heads = t.reshape(H + 2 * Hkv, D, -1)
+        q, k, v = heads[:H].reshape(Hkv, H // Hkv, D, -1), heads[H:H + Hkv, None], heads[H + Hkv:, None]
+        t = torch.cat([q, k, v], 1).reshape(t.shape)
     return t
 
 
@@ -192,7 +225,7 @@ def load_classic_state(model: ClassicDecoder, tensors: Mapping[str, torch.Tensor
     get = _Reader(tensors)
     c = model.config
     H, Hkv, D = c.num_heads, c.num_kv_heads or c.num_heads, c.head_dim
-    order = head_order(D, int(D * c.rotary_fraction), False) if c.positions == "rotary" else None
+    order = head_order(D, int(D * c.rotary_fraction), family.rotary_pairs) if c.positions == "rotary" else None
     if family.qkv == "by_head" and Hkv != H:
         raise ValueError("per-head interleaved q | k | v storage holds as many key heads as query heads")
 
@@ -236,7 +269,7 @@ def load_classic_state(model: ClassicDecoder, tensors: Mapping[str, torch.Tensor
 def export_classic_state(model: ClassicDecoder, family: ClassicFamily) -> Dict[str, torch.Tensor]:
     c = model.config
     H, Hkv, D = c.num_heads, c.num_kv_heads or c.num_heads, c.head_dim
-    order = head_order(D, int(D * c.rotary_fraction), False) if c.positions == "rotary" else None
+    order = head_order(D, int(D * c.rotary_fraction), family.rotary_pairs) if c.positions == "rotary" else None
     out: Dict[str, torch.Tensor] = {}
 
     def module(m, key, matrix=True):

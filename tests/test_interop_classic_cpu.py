@@ -14,6 +14,11 @@ CASES = {
     "gpt_neox_sequential": dict(model_type="gpt_neox", vocab_size=96, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
                                 max_position_embeddings=64, rotary_pct=0.5, use_parallel_residual=False),
     "falcon": dict(model_type="falcon", vocab_size=96, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, max_position_embeddings=64),
+    "falcon_grouped": dict(model_type="falcon", vocab_size=96, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_kv_heads=2,
+                           new_decoder_architecture=True, max_position_embeddings=64),
+    "falcon_grouped_one_norm": dict(model_type="falcon", vocab_size=96, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_kv_heads=2,
+                                    new_decoder_architecture=True, num_ln_in_parallel_attn=1, max_position_embeddings=64),
+    "gptj": dict(model_type="gptj", vocab_size=96, n_embd=64, n_layer=2, n_head=4, n_positions=64, rotary_dim=8),
     "phi": dict(model_type="phi", vocab_size=96, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128, max_position_embeddings=64),
     "opt": dict(model_type="opt", vocab_size=96, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, ffn_dim=128, max_position_embeddings=64,
                 word_embed_proj_dim=64),
@@ -37,7 +42,7 @@ def test_classic_family_matches_transformers(name):
             p.data.add_(torch.randn_like(p) * 0.1)
     d = cfg.to_dict()
     fam = classic_family_of(d)
-    assert fam.name == CASES[name]["model_type"]
+    assert fam.name == (name if name.startswith("falcon_grouped") else CASES[name]["model_type"])
     ours = ClassicDecoder(read_classic_config(d), dtype=torch.float32).eval()
     assert load_classic_state(ours, dict(hf.state_dict()), fam) == []
     tokens = torch.randint(3, 96, (2, 24))
@@ -78,8 +83,8 @@ def test_alibi_slopes_and_generation():
 def test_unknown_and_unbuilt_layouts_raise():
     with pytest.raises(KeyError, match="no classic decoder family"):
         classic_family_of({"model_type": "llama"})
-    with pytest.raises(NotImplementedError, match="7B layout"):
-        read_classic_config(dict(CASES["falcon"], new_decoder_architecture=True))
+    with pytest.raises(NotImplementedError, match="not ALiBi"):
+        read_classic_config(dict(CASES["falcon"], alibi=True))
     torch.manual_seed(0)
     m = ClassicDecoder(read_classic_config(CASES["gpt2"]), dtype=torch.float32)
     state = export_classic_state(m, CLASSIC["gpt2"])
