@@ -465,7 +465,8 @@ def rope_tables(max_pos: int, dim: int, theta: float = 10000.0, device="cpu", sc
     ``yarn`` (``factor, original_max_position_embeddings, beta_fast, beta_slow, mscale, mscale_all_dim, attention_factor, truncate``:
     high frequencies extrapolate, low ones interpolate, a ramp between, and the tables carry the attention factor);
     ``longrope`` (``short_factor`` / ``long_factor`` per frequency: the long set when the table is longer than
-    ``original_max_position_embeddings``, else the short one).  A kind this function does not know raises: silently unscaled positions
+    ``original_max_position_embeddings``, else the short one); ``dynamic`` (NTK-aware: the base grows with the table's length over the original
+    context).  A kind this function does not know raises: silently unscaled positions
     would read as a model that has forgotten its long context."""
     full = dim
     if rotary_dim is not None and rotary_dim < dim:
@@ -517,8 +518,14 @@ def rope_tables(max_pos: int, dim: int, theta: float = 10000.0, device="cpu", sc
             amplitude = scaling.get("attention_factor")
             if amplitude is None:
                 amplitude = 1.0 if f <= 1 else math.sqrt(1 + math.log(f) / math.log(orig))
+        elif kind == "dynamic":
+            # NTK-aware scaling by the length in use; a table is built once for max_pos positions, so that is the length it is scaled for
+            orig = scaling.get("original_max_position_embeddings") or max_pos
+            if max_pos > orig:
+                base = theta * ((scaling["factor"] * max_pos / orig) - (scaling["factor"] - 1)) ** (dim / (dim - 2))
+                inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float64, device=device) / dim))
         else:
-            raise ValueError(f"rotary scaling {kind!r} is not built (known: linear, llama3, yarn, longrope)")
+            raise ValueError(f"rotary scaling {kind!r} is not built (known: linear, llama3, yarn, longrope, dynamic)")
     t = torch.arange(max_pos, dtype=torch.float64, device=device)
     ang = torch.outer(t, inv)
     cos, sin = ang.cos() * amplitude, ang.sin() * amplitude

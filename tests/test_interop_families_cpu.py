@@ -155,8 +155,14 @@ def test_rotary_scalings_match_transformers():
     short, _ = ops.rope_tables(32, 16, 10000.0, "cpu", {k: v for k, v in rp.items() if k != "rope_theta"})      # within the original context: the short set
     want = torch.outer(torch.arange(32).double(), 1.0 / (torch.tensor(rp["short_factor"]).double() * 10000.0 ** (torch.arange(0, 16, 2).double() / 16))).cos()
     assert float((short - want.float()).abs().max()) < 1e-6
+    rp = dict(rope_type="dynamic", rope_theta=10000.0, factor=2.0)
+    cfg = transformers.LlamaConfig(hidden_size=64, num_attention_heads=4, head_dim=16, max_position_embeddings=32, rope_parameters=dict(rp))
+    inv, gain = ROPE_INIT_FUNCTIONS["dynamic"](cfg, "cpu", seq_len=128)
+    ang = torch.outer(torch.arange(128).double(), inv.double())
+    cos, _ = ops.rope_tables(128, 16, 10000.0, "cpu", {"rope_type": "dynamic", "factor": 2.0, "original_max_position_embeddings": 32})
+    assert float((cos - (ang.cos() * gain).float()).abs().max()) < 5e-6
     with pytest.raises(ValueError, match="not built"):
-        ops.rope_tables(32, 16, 10000.0, "cpu", {"rope_type": "dynamic", "factor": 2.0})
+        ops.rope_tables(32, 16, 10000.0, "cpu", {"rope_type": "su", "factor": 2.0})
 
 
 def test_dream_is_qwen2_read_bidirectionally():
